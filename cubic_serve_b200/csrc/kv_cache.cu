@@ -1,0 +1,185 @@
+// Fused per-head RMSNorm (optional) + RoPE + KV quantize-on-write.
+//
+// One launch after the QKV GEMM replaces the reference's separate q/k norm,
+// M-RoPE (position/qwen_mrope.py:25) and cache quantization kernels
+// (cache_quantization_native.cu:49).  One warp owns one (token, head); lane l
+// holds channels l, l+32, l+64, l+96, so a rotate-half RoPE pair (c, c+64) and
+// a 32-channel quantization group (c/32) are both warp-local.
+#include "ptx.cuh"
+#include "kv_layout.cuh"
+
+namespace cb {
+
+struct KvWriteParams {
+  const __nv_bfloat16* qkv;    // [T, (Hq + 2*Hkv) * D]
+  __nv_bfloat16* q_out;        // [T, Hq * D]
+  uint8_t* cache;              // [pages][Hkv][blob]
+  const int* positions;        // [T] rotary position
+  const int* slots;            // [T] page * 16 + offset, < 0: do not write (padding row)
+  const __nv_bfloat16* q_norm; // [D] or null
+  const __nv_bfloat16* k_norm; // [D] or null
+  const float* inv_freq;       // [D/2]
+  int T, Hq, Hkv;
+  int rotary_dim;              // <= D, multiple of 2; pairs (c, c + rotary_dim/2)
+  float eps;
+  KvLayout lay;
+};
+
+__device__ __forceinline__ void quantize_store(const float (&v)[4], int bits, bool is_v, uint8_t* blob,
+                                               const KvLayout& lay, int tok, int lane) {
+  const float qmax = bits == 8 ? 127.f : 7.f;
+  const int bias = bits == 8 ? 128 : 8;
+  uint8_t* codes = blob + (is_v ? lay.v_code_off : 0);
+  float* scales = reinterpret_cast<float*>(blob + (is_v ? lay.v_scale_off : lay.k_scale_off));
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float amax = warp_max(fabsf(v[k]));
+    const float scale = amax > 0.f ? amax / qmax : 1.f;
+    float c = rintf(v[k] / scale);
+    c = fminf(fmaxf(c, -qmax), qmax);
+    const uint32_t code = static_cast<uint32_t>(static_cast<int>(c) + bias);
+    const int ch = lane + 32 * k;
+    int shift;
+    if (bits == 8) {
+      const int pos = is_v ? v_code_pos(8, lay.head_dim, tok, ch, &shift) : k_code_pos(8, tok, ch, &shift);
+      codes[pos] = static_cast<uint8_t>(code);
+    } else if (!is_v) {
+      // channels c and c+16 of a 32-block share a byte: lanes l and l+16
+      const uint32_t other = __shfl_down_sync(0xffffffffu, code, 16);
+      if (lane < 16) {
+        const int pos = k_code_pos(4, tok, ch, &shift);
+        codes[pos] = static_cast<uint8_t>(code | (other << 4));
+      }
+    } else {
+      // even/odd tokens share a byte and may be written by different warps
+      const int pos = v_code_pos(4, lay.head_dim, tok, ch, &shift);
+      uint32_t* word = reinterpret_cast<uint32_t*>(codes + (pos & ~3));
+      const int bit = (pos & 3) * 8 + shift;
+      atomicAnd(word, ~(0xFu << bit));
+      atomicOr(word, code << bit);
+    }
+    if (lane == 0) scales[tok * (lay.head_dim / kKvGroup) + k] = scale;
+  }
+}
+
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(const KvWriteParams p) {
+  const int warp_global = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = p.Hq + 2 * p.Hkv;
+  if (warp_global >= p.T * heads) return;
+  const int t = warp_global / heads;
+  const int h = warp_global - t * heads;
+  const int D = p.lay.head_dim;  // == 128
+  const __nv_bfloat16* src = p.qkv + (static_cast<size_t>(t) * heads + h) * D;
+  float v[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(src[lane + 32 * k]);
+
+  const bool is_q = h < p.Hq;
+  const bool is_k = !is_q && h < p.Hq + p.Hkv;
+  if (is_q || is_k) {
+    const __nv_bfloat16* nw = is_q ? p.q_norm : p.k_norm;
+    if (nw) {
+      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / static_cast<float>(D) + p.eps);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        // round to bf16 after the norm, as an unfused norm kernel would
+        v[k] = __bfloat162float(__float2bfloat16(v[k] * inv * __bfloat162float(nw[lane + 32 * k])));
+      }
+    }
+    const int half = p.rotary_dim >> 1;
+    const float pos = static_cast<float>(p.positions[t]);
+    // pairs (c, c + half) for c < half; with D = 128 and half = 64: (l, l+64), (l+32, l+96)
+    if (half == 64) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int c = lane + 32 * k;
+        float s, co;
+        sincosf(pos * p.inv_freq[c], &s, &co);
+        const float a = v[k], b = v[k + 2];
+        v[k] = a * co - b * s;
+        v[k + 2] = b * co + a * s;
+      }
+    } else if (half == 32) {
+      // partial rotary over the first 64 channels: pairs (l, l+32)
+      float s, co;
+      sincosf(pos * p.inv_freq[lane], &s, &co);
+      const float a = v[0], b = v[1];
+      v[0] = a * co - b * s;
+      v[1] = b * co + a * s;
+    }
+  }
+  if (is_q) {
+    __nv_bfloat16* dst = p.q_out + (static_cast<size_t>(t) * p.Hq + h) * D;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dst[lane + 32 * k] = __float2bfloat16(v[k]);
+    return;
+  }
+  const int slot = p.slots[t];
+  if (slot < 0) return;
+  const int kvh = is_k ? h - p.Hq : h - p.Hq - p.Hkv;
+  const int page = slot >> 4, tok = slot & 15;
+  uint8_t* blob = p.cache + (static_cast<size_t>(page) * p.Hkv + kvh) * p.lay.blob_bytes;
+  // the cache stores what attention will see: bf16-rounded values
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(__float2bfloat16(v[k]));
+  quantize_store(v, is_k ? p.lay.k_bits : p.lay.v_bits, !is_k, blob, p.lay, tok, lane);
+}
+
+// Copy whole pages (all kv heads) src -> dst: copy-on-write of a shared page.
+__global__ void __launch_bounds__(256)
+copy_pages_kernel(uint8_t* cache, const int* src_pages, const int* dst_pages, int page_bytes_vec) {
+  const int s = src_pages[blockIdx.x], d = dst_pages[blockIdx.x];
+  if (s < 0 || d < 0 || s == d) return;
+  const uint4* sp = reinterpret_cast<const uint4*>(cache + static_cast<size_t>(s) * page_bytes_vec * 16);
+  uint4* dp = reinterpret_cast<uint4*>(cache + static_cast<size_t>(d) * page_bytes_vec * 16);
+  for (int i = threadIdx.x; i < page_bytes_vec; i += blockDim.x) dp[i] = sp[i];
+}
+
+}  // namespace cb
+
+extern "C" {
+
+int cb_kv_blob_bytes(int head_dim, int k_bits, int v_bits) {
+  return cb::make_kv_layout(head_dim, k_bits, v_bits).blob_bytes;
+}
+
+int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* positions, const void* slots,
+                     const void* q_norm, const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D,
+                     int rotary_dim, float eps, int k_bits, int v_bits, void* stream) {
+  using namespace cb;
+  if (T <= 0) return 0;
+  if (D != 128) return -10;
+  if (!(k_bits == 8 || k_bits == 4) || !(v_bits == 8 || v_bits == 4)) return -11;
+  if (!(rotary_dim == 128 || rotary_dim == 64 || rotary_dim == 0)) return -12;
+  KvWriteParams p;
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.q_out = static_cast<__nv_bfloat16*>(q_out);
+  p.cache = static_cast<uint8_t*>(cache);
+  p.positions = static_cast<const int*>(positions);
+  p.slots = static_cast<const int*>(slots);
+  p.q_norm = static_cast<const __nv_bfloat16*>(q_norm);
+  p.k_norm = static_cast<const __nv_bfloat16*>(k_norm);
+  p.inv_freq = static_cast<const float*>(inv_freq);
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.rotary_dim = rotary_dim; p.eps = eps;
+  p.lay = make_kv_layout(D, k_bits, v_bits);
+  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+  rope_kv_write_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_copy_pages(void* cache, const void* src_pages, const void* dst_pages, int n, long long page_bytes,
+                  void* stream) {
+  if (n <= 0) return 0;
+  if (page_bytes % 16 != 0) return -10;
+  cb::copy_pages_kernel<<<n, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(cache), static_cast<const int*>(src_pages), static_cast<const int*>(dst_pages),
+      static_cast<int>(page_bytes / 16));
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

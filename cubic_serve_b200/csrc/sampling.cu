@@ -1,0 +1,180 @@
+// Token sampling over full-vocabulary bf16 logits: greedy (first-max, lowest id
+// wins ties), temperature / top-k (<= 20) / top-p with a counter-based Philox
+// stream, optional grammar bitmask, and the speculative accept/resample step.
+//
+// Counterparts in the reference: sampling/greedy.cu:14-117 (vocab-sharded exact
+// argmax with min-id ties and grammar mask), sampling/topk_topp.py:23 (root
+// top-k/top-p/temperature + Philox), sampling/speculative.py (K=1 verify).
+#include "ptx.cuh"
+
+namespace cb {
+
+static constexpr int kSampleThreads = 512;
+static constexpr int kMaxTopK = 20;
+
+struct Cand {
+  float v;
+  int i;
+};
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__device__ __forceinline__ Cand block_best(Cand c, Cand* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, c.v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, c.i, o);
+    if (better(ov, oi, c.v, c.i)) { c.v = ov; c.i = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = c;
+  __syncthreads();
+  Cand r = (l < (blockDim.x >> 5)) ? red[l] : Cand{-INFINITY, 0x7fffffff};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, r.v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, r.i, o);
+    if (better(ov, oi, r.v, r.i)) { r.v = ov; r.i = oi; }
+  }
+  __syncthreads();
+  return r;
+}
+
+// Philox4x32-10, one 128-bit draw per (seed, row counter)
+__device__ __forceinline__ float philox_uniform(unsigned long long seed, unsigned long long ctr) {
+  uint32_t c0 = static_cast<uint32_t>(ctr), c1 = static_cast<uint32_t>(ctr >> 32), c2 = 0, c3 = 0;
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return (static_cast<float>(c0 >> 8) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+struct SampleParams {
+  const __nv_bfloat16* logits;  // [rows, ld]
+  const uint32_t* mask;         // [rows, mask_words] allowed-token bits or null
+  const float* temperature;     // [rows] 0 = greedy
+  const float* top_p;           // [rows]
+  const int* top_k;             // [rows] 0 = up to kMaxTopK
+  const unsigned long long* seeds;     // [rows]
+  const unsigned long long* counters;  // [rows] per-request draw index
+  int* out_ids;                 // [rows]
+  float* out_logprob;           // [rows] log-prob of the chosen token within the candidate set (or null)
+  int vocab, ld, mask_words;
+};
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_kernel(const SampleParams p) {
+  __shared__ Cand red[kSampleThreads / 32];
+  __shared__ Cand top[kMaxTopK];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lg = p.logits + static_cast<size_t>(row) * p.ld;
+  const uint32_t* mk = p.mask ? p.mask + static_cast<size_t>(row) * p.mask_words : nullptr;
+  const float temp = p.temperature ? p.temperature[row] : 0.f;
+  int K = 1;
+  if (temp > 0.f) {
+    K = p.top_k ? p.top_k[row] : 0;
+    if (K <= 0 || K > kMaxTopK) K = kMaxTopK;
+  }
+  float pv = INFINITY;
+  int pi = -1;
+  for (int k = 0; k < K; ++k) {
+    Cand best{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < p.vocab; i += kSampleThreads) {
+      if (mk && !((mk[i >> 5] >> (i & 31)) & 1u)) continue;
+      float v = __bfloat162float(lg[i]);
+      if (!(v == v)) v = -INFINITY;  // NaN never wins
+      // strictly after the previous pick in (value desc, id asc) order
+      if (v < pv || (v == pv && i > pi)) {
+        if (better(v, i, best.v, best.i)) { best.v = v; best.i = i; }
+      }
+    }
+    best = block_best(best, red);
+    if (threadIdx.x == 0) top[k] = best;
+    pv = best.v;
+    pi = best.i;
+    if (best.i == 0x7fffffff) { K = k; break; }  // fewer allowed tokens than K (uniform across the block)
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  if (K == 0) { p.out_ids[row] = 0; if (p.out_logprob) p.out_logprob[row] = 0.f; return; }
+  if (temp <= 0.f || K == 1) {
+    p.out_ids[row] = top[0].i;
+    if (p.out_logprob) p.out_logprob[row] = 0.f;
+    return;
+  }
+  float probs[kMaxTopK];
+  const float inv_t = 1.f / temp;
+  float sum = 0.f;
+  for (int k = 0; k < K; ++k) { probs[k] = __expf((top[k].v - top[0].v) * inv_t); sum += probs[k]; }
+  const float tp = p.top_p ? p.top_p[row] : 1.f;
+  int keep = K;
+  if (tp < 1.f) {
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) { acc += probs[k] / sum; if (acc >= tp) { keep = k + 1; break; } }
+  }
+  float ksum = 0.f;
+  for (int k = 0; k < keep; ++k) ksum += probs[k];
+  const float u = philox_uniform(p.seeds ? p.seeds[row] : 0ull, p.counters ? p.counters[row] : 0ull) * ksum;
+  float acc = 0.f;
+  int pick = keep - 1;
+  for (int k = 0; k < keep; ++k) { acc += probs[k]; if (u < acc) { pick = k; break; } }
+  p.out_ids[row] = top[pick].i;
+  if (p.out_logprob) p.out_logprob[row] = __logf(probs[pick] / ksum);
+}
+
+// Greedy speculative verification: per request, row r holds the target's choice
+// after consuming draft token r (row 0 = after the root).  accepted = length of
+// the longest prefix with draft[r] == target[r]; the bonus token is
+// target[accepted].  (reference: generation/tp_sampling.py:154, greedy branch)
+__global__ void verify_greedy_kernel(const int* target_ids, const int* draft_ids, const int* depth, int max_depth,
+                                     const int* forced_reject_at, int* accepted, int* bonus, int requests) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= requests) return;
+  const int d = depth[r];
+  int a = 0;
+  const int cap = forced_reject_at ? forced_reject_at[r] : d;  // acceptance-forcing hook (benchmarks)
+  while (a < d && a < cap && draft_ids[r * max_depth + a] == target_ids[r * (max_depth + 1) + a]) ++a;
+  accepted[r] = a;
+  bonus[r] = target_ids[r * (max_depth + 1) + a];
+}
+
+}  // namespace cb
+
+extern "C" {
+
+int cb_sample(const void* logits, int ld, const void* mask, int mask_words, const void* temperature,
+              const void* top_p, const void* top_k, const void* seeds, const void* counters, void* out_ids,
+              void* out_logprob, int rows, int vocab, void* stream) {
+  using namespace cb;
+  if (rows <= 0) return 0;
+  SampleParams p;
+  p.logits = static_cast<const __nv_bfloat16*>(logits);
+  p.mask = static_cast<const uint32_t*>(mask);
+  p.temperature = static_cast<const float*>(temperature);
+  p.top_p = static_cast<const float*>(top_p);
+  p.top_k = static_cast<const int*>(top_k);
+  p.seeds = static_cast<const unsigned long long*>(seeds);
+  p.counters = static_cast<const unsigned long long*>(counters);
+  p.out_ids = static_cast<int*>(out_ids);
+  p.out_logprob = static_cast<float*>(out_logprob);
+  p.vocab = vocab; p.ld = ld; p.mask_words = mask_words;
+  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_verify_greedy(const void* target_ids, const void* draft_ids, const void* depth, int max_depth,
+                     const void* forced_reject_at, void* accepted, void* bonus, int requests, void* stream) {
+  if (requests <= 0) return 0;
+  cb::verify_greedy_kernel<<<(requests + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const int*>(target_ids), static_cast<const int*>(draft_ids), static_cast<const int*>(depth),
+      max_depth, static_cast<const int*>(forced_reject_at), static_cast<int*>(accepted), static_cast<int*>(bonus),
+      requests);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,471 @@
+// Weight-quantized GEMM for sm_100a:  y[M,N] = x[M,K] * W[N,K]^T  (+ residual)
+//
+// Replaces the reference's Marlin / Triton weight-only GEMM family
+// (quantization/common/marlin/native/template/kernel.cuh:50,
+//  quantization/common/kernels.py:68) with one tcgen05 kernel.
+//
+// Operand roles are swapped relative to the maths: the *weight* tile is the
+// UMMA "A" operand (128 output features -> 128 TMEM lanes) and the activation
+// tile is the "B" operand (batch rows -> UMMA N, any multiple of 16 up to 256).
+// A decode batch of 16..256 rows therefore always fills the 128-row MMA, and
+// one CTA dequantizes each weight exactly once per 256 batch rows.
+//
+// Pipeline per k-block (64 columns of K), S stages:
+//   warp 0   : bulk copy of the packed weight tile (4 KiB) + its group metadata
+//              (1 KiB) and a TMA tile load of x (128-byte swizzle)  -> full[s]
+//   warps 2-9: wait full[s]; decode 4-bit codes -> bf16, write the swizzled
+//              K-major A tile in shared memory                      -> ready[s]
+//   warp 1   : wait ready[s]; 4 x tcgen05.mma (K=16) into TMEM; commit -> empty[s]
+//   warps 2-9: epilogue, tcgen05.ld -> registers -> bf16 (or fp32 split-K
+//              partials whose last-arriving CTA sums them in split order).
+//
+// Packed weight storage is produced at load time by ops/wq_pack.py:
+//   codes  [n_tile][k_block][half h(2)][row r(128)][16 bytes]   (4096 B per stage)
+//          word j (0..3) nibble i (0..7) of those 16 bytes is k = 32h + 8j + i,
+//          stored offset-binary (code + 8; the reserved most-negative code -> 8).
+//   meta   [n_tile][meta_block][2][128] 32-bit words            (1024 B per block)
+//          CUBIC4 : word0 = scale (fp32), word1 = half2(a, b); one block per K group
+//          AFFINE4: word h = half2(scale, offset) of 32-column sub-block h of the
+//                   k-block; w = code * scale + offset; one block per k-block
+//          NVFP4  : word h = half2(block scale of columns 32h..32h+15, ..+16..31)
+#include "ptx.cuh"
+#include <cuda.h>
+
+namespace cb {
+
+enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 = 3 };
+
+static constexpr int kTileN = 128;       // output features per CTA (UMMA M)
+static constexpr int kBlockK = 64;       // K columns per stage (one 128-byte swizzle row)
+static constexpr int kCodeBytes = 4096;  // 128 x 64 x 4 bit
+static constexpr int kMetaBytes = 1024;
+static constexpr int kATileBytes = kTileN * kBlockK * 2;  // 16 KiB bf16
+static constexpr int kNumDequantWarps = 8;
+static constexpr int kThreads = (2 + kNumDequantWarps) * 32;
+
+struct WqGemmParams {
+  const uint8_t* codes;
+  const uint8_t* meta;
+  __nv_bfloat16* y;         // [M, ldy]
+  const __nv_bfloat16* residual;  // optional [M, ldy]
+  float* workspace;         // split-K partials: [tiles][splits][mb][128] fp32
+  uint32_t* counters;       // one per (m_tile, n_tile); zero on entry, zero on exit
+  uint32_t* status;         // device status word (Status)
+  int M, N, K;
+  int ldy;
+  int mb;                   // batch rows per CTA (multiple of 16, <= 256)
+  int k_blocks;             // K / 64
+  int splits;               // split-K factor (k_blocks % splits may be != 0)
+  int meta_k_blocks;        // k-blocks covered by one metadata block (1 or group/64)
+  int meta_blocks;          // metadata blocks per n-tile
+  int stages;
+  float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
+  uint32_t tmem_cols;       // power of two >= max(32, mb)
+};
+
+struct __align__(8) SmemCtl {
+  uint64_t full[8];
+  uint64_t ready[8];
+  uint64_t empty[8];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t is_last;
+};
+
+template <int FMT>
+__device__ __forceinline__ void decode8(uint32_t w, float c0, float c1, float c2, uint32_t (&out)[4]);
+
+template <>
+__device__ __forceinline__ void decode8<kFmtBf16>(uint32_t, float, float, float, uint32_t (&)[4]) {}
+
+// CUBIC4: offset-binary nibble n -> c = n - 8;  w = c * (A + |c| * (B + |c| * C))
+template <>
+__device__ __forceinline__ void decode8<kFmtCubic4>(uint32_t w, float A, float B, float C,
+                                                    uint32_t (&out)[4]) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t bits = ((w >> (4 * i)) & 0xFu) | 0x4B000000u;  // 2^23 + n
+    float c = __uint_as_float(bits) - 8388616.0f;            // n - 8
+    float m = fabsf(c);
+    float p = fmaf(m, C, B);
+    p = fmaf(m, p, A);
+    v[i] = c * p;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+}
+
+// AFFINE4: w = n * scale + offset  (offset already folds the zero point)
+template <>
+__device__ __forceinline__ void decode8<kFmtAffine4>(uint32_t w, float scale, float offset, float,
+                                                     uint32_t (&out)[4]) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t bits = ((w >> (4 * i)) & 0xFu) | 0x4B000000u;
+    float n = __uint_as_float(bits) - 8388608.0f;
+    v[i] = fmaf(n, scale, offset);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+}
+
+// NVFP4: nibble = sign(1) exp(2) man(1).  Placing exp|man at fp32 bits 24..22
+// and multiplying by 2^126 yields {0,.5,1,1.5,2,3,4,6} exactly (the e=0 codes
+// become fp32 subnormals, which the multiply normalises).
+template <>
+__device__ __forceinline__ void decode8<kFmtNvfp4>(uint32_t w, float scale, float, float,
+                                                   uint32_t (&out)[4]) {
+  float v[8];
+  const float rebias = __uint_as_float(0x7E800000u);  // 2^126
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t nib = (w >> (4 * i)) & 0xFu;
+    uint32_t bits = ((nib & 7u) << 22) | ((nib & 8u) << 28);
+    v[i] = (__uint_as_float(bits) * rebias) * scale;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
+               const __grid_constant__ CUtensorMap tmap_w,  // only for kFmtBf16
+               const WqGemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // carve: [stage: x tile | A tile | packed codes+meta] * S, then control block
+  const uint32_t x_bytes = static_cast<uint32_t>(p.mb) * 128u;
+  const uint32_t stage_bytes = x_bytes + kATileBytes + (FMT == kFmtBf16 ? 0 : kCodeBytes + kMetaBytes);
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x;
+  const int split = blockIdx.y;
+  const int m_tile = blockIdx.z;
+  const int m0 = m_tile * p.mb;
+  const int S = p.stages;
+
+  // k-block range of this split (balanced contiguous ranges)
+  const int kb_lo = static_cast<int>((static_cast<long long>(p.k_blocks) * split) / p.splits);
+  const int kb_hi = static_cast<int>((static_cast<long long>(p.k_blocks) * (split + 1)) / p.splits);
+  const int iters = kb_hi - kb_lo;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->ready[s]), kNumDequantWarps);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->acc_full), 1);
+    ctl->abort_flag = 0;
+    ctl->is_last = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x);
+      const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? kATileBytes : kCodeBytes + kMetaBytes);
+      for (int i = 0; i < iters; ++i) {
+        const int s = i % S;
+        const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
+        if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
+        const int kb = kb_lo + i;
+        uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
+        const uint32_t bar = smem_u32(&ctl->full[s]);
+        mbar_expect_tx(bar, tx);
+        tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, m0, bar);
+        if (FMT == kFmtBf16) {
+          tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, n_tile * kTileN, bar);
+        } else {
+          const uint8_t* csrc = p.codes + (static_cast<size_t>(n_tile) * p.k_blocks + kb) * kCodeBytes;
+          const uint8_t* msrc = p.meta + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMetaBytes;
+          bulk_g2s(smem_u32(st + x_bytes + kATileBytes), csrc, kCodeBytes, bar);
+          bulk_g2s(smem_u32(st + x_bytes + kATileBytes + kCodeBytes), msrc, kMetaBytes, bar);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+      bool ok = true;
+      for (int i = 0; i < iters && ok; ++i) {
+        const int s = i % S;
+        const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
+        ok = mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag);
+        if (ok && FMT != kFmtBf16) ok = mbar_wait(smem_u32(&ctl->ready[s]), ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(st));
+        const uint64_t adesc = umma_desc_sw128(smem_u32(st + x_bytes));
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
+          umma_f16(tmem_base, adesc + 2u * k4, bdesc + 2u * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&ctl->empty[s]));
+      }
+      tc_commit(smem_u32(&ctl->acc_full));
+    }
+  } else {
+    // ------------------------------------------------- dequant + epilogue
+    const int dq = threadIdx.x - 64;  // 0..255
+    const int r = dq & 127;           // row of the weight tile
+    const int h = dq >> 7;            // which 32-column half of the k-block
+    if (FMT != kFmtBf16) {
+      for (int i = 0; i < iters; ++i) {
+        const int s = i % S;
+        const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
+        if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
+        uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
+        const uint8_t* pk = st + x_bytes + kATileBytes;
+        const uint4 words = *reinterpret_cast<const uint4*>(pk + (h * 128 + r) * 16);
+        const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
+        float c0, c1, c2, c1b = 0.f;
+        if (FMT == kFmtCubic4) {
+          const float sc = __uint_as_float(meta[r]);
+          const __half2 ab = *reinterpret_cast<const __half2*>(&meta[128 + r]);
+          const float a = __low2float(ab), b = __high2float(ab);
+          c0 = sc * a * (1.0f / 7.0f);
+          c1 = sc * b * (1.0f / 49.0f);
+          c2 = sc * (1.0f - a - b) * (1.0f / 343.0f);
+        } else {
+          const __half2 so = *reinterpret_cast<const __half2*>(&meta[h * 128 + r]);
+          c0 = __low2float(so);
+          c1 = __high2float(so);
+          c2 = 0.f;
+          c1b = c1;
+        }
+        uint8_t* arow = st + x_bytes + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t wv[4] = {words.x, words.y, words.z, words.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t o[4];
+          if (FMT == kFmtNvfp4) {
+            // columns 32h + 8j ..: block scale index (8j)/16 selects low/high half
+            decode8<FMT>(wv[j], (j < 2) ? c0 : c1b, 0.f, 0.f, o);
+          } else {
+            decode8<FMT>(wv[j], c0, c1, c2, o);
+          }
+          const int chunk = h * 4 + j;
+          *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->ready[s]));
+      }
+    }
+    // epilogue: TMEM lane = output feature, column = batch row
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->acc_full), 0, abort_flag));
+    tc_fence_after();
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int pair = (warp - 2) >> 2;        // two warps share a quadrant; alternate chunks
+    const int n = n_tile * kTileN + quad * 32 + lane;
+    const int chunks = p.mb >> 4;
+    if (acc_ok && iters > 0) {
+      if (p.splits == 1) {
+        for (int ci = pair; ci < chunks; ci += 2) {
+          uint32_t acc[16];
+          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
+          tmem_ld_wait();
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + ci * 16 + j;
+              if (m < p.M) {
+                float v = __uint_as_float(acc[j]) * p.alpha;
+                const size_t off = static_cast<size_t>(m) * p.ldy + n;
+                if (p.residual) v += __bfloat162float(p.residual[off]);
+                p.y[off] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      } else {
+        float* ws = p.workspace +
+                    ((static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits + split) * (static_cast<size_t>(p.mb) * kTileN);
+        for (int ci = pair; ci < chunks; ci += 2) {
+          uint32_t acc[16];
+          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            ws[static_cast<size_t>(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
+        }
+      }
+    }
+    if (p.splits > 1) {
+      // last-arriving split sums all partials in split order (deterministic)
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
+      if (dq == 0) {
+        const uint32_t idx = m_tile * gridDim.x + n_tile;
+        const uint32_t prev = atomicAdd(&p.counters[idx], 1u);
+        const uint32_t last = (prev == static_cast<uint32_t>(p.splits) - 1u) ? 1u : 0u;
+        if (last) p.counters[idx] = 0;
+        ctl->is_last = last;
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
+      if (ctl->is_last && !*abort_flag) {
+        __threadfence();
+        const float* wsb = p.workspace +
+                           (static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits * (static_cast<size_t>(p.mb) * kTileN);
+        const size_t part = static_cast<size_t>(p.mb) * kTileN;
+        const int nn = n_tile * kTileN + r;
+        if (nn < p.N) {
+          for (int mm = h; mm < p.mb; mm += 2) {
+            const int m = m0 + mm;
+            if (m >= p.M) break;
+            float v = 0.f;
+            for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(wsb + sp * part + static_cast<size_t>(mm) * kTileN + r);
+            v *= p.alpha;
+            const size_t off = static_cast<size_t>(m) * p.ldy + nn;
+            if (p.residual) v += __bfloat162float(p.residual[off]);
+            p.y[off] = __float2bfloat16(v);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+  if (threadIdx.x == 0 && ctl->abort_flag) atomicExch(p.status, static_cast<uint32_t>(kErrBarrierTimeout));
+}
+
+// ------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 row-major [rows, cols] (row stride ld elements), box = {64 cols, box_rows}, 128-byte swizzle
+static int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                          uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int FMT>
+static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemmParams& p, dim3 grid, size_t smem,
+                      cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wq_gemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  wq_gemm_kernel<FMT><<<grid, kThreads, smem, stream>>>(tx, tw, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace cb
+
+extern "C" {
+
+// Bytes of split-K workspace / counters a launch with these sizes needs.
+long long cb_wq_gemm_workspace_bytes(int M, int N, int splits) {
+  int mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+  long long m_tiles = (M + mb - 1) / mb;
+  long long n_tiles = (N + 127) / 128;
+  return splits > 1 ? m_tiles * n_tiles * splits * mb * 128LL * 4LL : 0;
+}
+
+// x: bf16 [M, K] row-major (ldx elements per row); y: bf16 [M, ldy].
+// fmt: 0 cubic4, 1 affine4, 2 nvfp4 (W4A16), 3 bf16 weights (codes = W [N,K] bf16).
+// Returns 0 or a negative argument error / positive cudaError_t.
+int cb_wq_gemm(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+               const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
+               void* counters, void* status, void* stream) {
+  using namespace cb;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % 8) != 0) return -10;
+  if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4) return -11;
+  if (fmt == kFmtCubic4 && (group_k % kBlockK) != 0) return -12;
+  WqGemmParams p{};
+  p.codes = static_cast<const uint8_t*>(codes);
+  p.meta = static_cast<const uint8_t*>(meta);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.workspace = static_cast<float*>(workspace);
+  p.counters = static_cast<uint32_t*>(counters);
+  p.status = static_cast<uint32_t*>(status);
+  p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.alpha = alpha;
+  p.mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+  p.k_blocks = K / kBlockK;
+  if (splits < 1) splits = 1;
+  if (splits > p.k_blocks) splits = p.k_blocks;
+  if (splits > 1 && (!workspace || !counters)) return -13;
+  p.splits = splits;
+  p.meta_k_blocks = (fmt == kFmtCubic4) ? group_k / kBlockK : 1;
+  p.meta_blocks = (p.k_blocks + p.meta_k_blocks - 1) / p.meta_k_blocks;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.mb)) cols <<= 1;
+  p.tmem_cols = cols;
+  const size_t stage = static_cast<size_t>(p.mb) * 128 + kATileBytes + (fmt == kFmtBf16 ? 0 : kCodeBytes + kMetaBytes);
+  const size_t budget = 232448 - 1024 - 1024 - sizeof(SmemCtl);
+  int stages = static_cast<int>(budget / stage);
+  if (stages > 8) stages = 8;
+  if (stages < 2) return -14;
+  p.stages = stages;
+  const size_t smem = stages * stage + sizeof(SmemCtl) + 1024;
+
+  CUtensorMap tx, tw;
+  if (make_tmap_bf16(&tx, x, M, K, ldx, p.mb) != 0) return -20;
+  if (fmt == kFmtBf16) {
+    if (make_tmap_bf16(&tw, codes, N, K, K, kTileN) != 0) return -21;
+  } else {
+    tw = tx;
+  }
+  const int n_tiles = (N + kTileN - 1) / kTileN;
+  const int m_tiles = (M + p.mb - 1) / p.mb;
+  dim3 grid(n_tiles, splits, m_tiles);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (fmt) {
+    case kFmtCubic4: return launch_fmt<kFmtCubic4>(tx, tw, p, grid, smem, st);
+    case kFmtAffine4: return launch_fmt<kFmtAffine4>(tx, tw, p, grid, smem, st);
+    case kFmtNvfp4: return launch_fmt<kFmtNvfp4>(tx, tw, p, grid, smem, st);
+    default: return launch_fmt<kFmtBf16>(tx, tw, p, grid, smem, st);
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,122 @@
+"""Independent PyTorch oracles for the native kernels (fp32 math, CPU or GPU).
+
+These never call the native library.  They follow the reference's eager
+oracles in spirit (``ops/eager/attention.py``, ``ops/eager/kv_cache.py``): a
+candidate kernel is always compared against code that shares nothing with it.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+PAGE_TOKENS = 16
+KV_GROUP = 32
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, zero_centered: bool = False) -> torch.Tensor:
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    ww = w.float() + (1.0 if zero_centered else 0.0)
+    return xf * inv * ww
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return torch.nn.functional.silu(g) * u
+
+
+def rope_inv_freq(rotary_dim: int, theta: float, device=None) -> torch.Tensor:
+    return 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, device=device, dtype=torch.float32) / rotary_dim))
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE on ``[T, H, D]`` over the first ``2 * len(inv_freq)`` channels."""
+    half = inv_freq.numel()
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    a, b, rest = xf[..., :half], xf[..., half:2 * half], xf[..., 2 * half:]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], -1)
+
+
+def kv_quantize(x: torch.Tensor, bits: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Symmetric per-(token, head, 32-channel group) quantization.
+
+    ``x``: ``[..., D]`` -> integer codes (float tensor) and fp32 scales ``[..., D/32]``.
+    Range +-127 (8 bit), +-31 (6 bit), +-7 (4 bit); round-to-nearest-even.
+    """
+    qmax = float((1 << (bits - 1)) - 1)
+    g = x.float().reshape(*x.shape[:-1], x.shape[-1] // KV_GROUP, KV_GROUP)
+    amax = g.abs().amax(-1)
+    scale = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
+    codes = torch.round(g / scale[..., None]).clamp(-qmax, qmax)
+    return codes.reshape(x.shape), scale
+
+
+def kv_dequantize(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    g = codes.reshape(*codes.shape[:-1], codes.shape[-1] // KV_GROUP, KV_GROUP)
+    return (g * scale[..., None]).reshape(codes.shape)
+
+
+def attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, visible: torch.Tensor,
+                   scale: float | None = None) -> torch.Tensor:
+    """GQA attention of query rows of ONE request against its dense K/V.
+
+    ``q``: ``[R, Hq, D]``; ``k``/``v``: ``[S, Hkv, D]``; ``visible[r]`` = number of
+    leading tokens row ``r`` may see.  Returns fp32 ``[R, Hq, D]``.
+    """
+    r, hq, d = q.shape
+    s, hkv, _ = k.shape
+    g = hq // hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    kf = k.float().repeat_interleave(g, dim=1)
+    vf = v.float().repeat_interleave(g, dim=1)
+    logits = torch.einsum("rhd,shd->rhs", q.float(), kf) * scale
+    mask = torch.arange(s, device=q.device)[None, :] >= visible[:, None]
+    logits = logits.masked_fill(mask[:, None, :], float("-inf"))
+    p = torch.softmax(logits, -1)
+    return torch.einsum("rhs,shd->rhd", p, vf)
+
+
+# ---------------------------------------------------------------- cache blob codec
+def _k_pos(bits: int, tok: torch.Tensor, ch: torch.Tensor):
+    if bits == 8:
+        return (ch >> 4) * 256 + tok * 16 + (ch & 15), torch.zeros_like(ch)
+    c = ch & 31
+    return (ch >> 5) * 256 + tok * 16 + (c & 15), torch.where(c >= 16, 4, 0)
+
+
+def _v_pos(bits: int, d: int, tok: torch.Tensor, ch: torch.Tensor):
+    p = tok >> 1
+    chunk = (ch >> 2) ^ ((p & 3) << 2)
+    if bits == 8:
+        return p * (d * 2) + chunk * 8 + (ch & 3) * 2 + (tok & 1), torch.zeros_like(ch)
+    return p * d + chunk * 4 + (ch & 3), torch.where((tok & 1) == 1, 4, 0)
+
+
+def blob_layout(d: int, k_bits: int, v_bits: int) -> dict:
+    kc = PAGE_TOKENS * d * k_bits // 8
+    vc = PAGE_TOKENS * d * v_bits // 8
+    sc = PAGE_TOKENS * (d // KV_GROUP) * 4
+    return {"k_scale": kc, "v_code": kc + sc, "v_scale": kc + sc + vc, "bytes": kc + 2 * sc + vc}
+
+
+def decode_cache_page(blob: torch.Tensor, d: int, k_bits: int, v_bits: int):
+    """One (page, head) blob ``uint8 [blob_bytes]`` -> dequantized fp32 K, V ``[16, D]``."""
+    lay = blob_layout(d, k_bits, v_bits)
+    tok = torch.arange(PAGE_TOKENS, device=blob.device)[:, None].expand(PAGE_TOKENS, d)
+    ch = torch.arange(d, device=blob.device)[None, :].expand(PAGE_TOKENS, d)
+    b32 = blob.to(torch.int32)
+
+    def codes(region_off: int, pos, shift, bits):
+        raw = (b32[region_off + pos] >> shift) & ((1 << bits) - 1 if bits < 8 else 255)
+        return (raw - (1 << (bits - 1))).float()
+
+    kp, ks = _k_pos(k_bits, tok, ch)
+    vp, vs = _v_pos(v_bits, d, tok, ch)
+    kcodes = codes(0, kp, ks, k_bits)
+    vcodes = codes(lay["v_code"], vp, vs, v_bits)
+    ksc = blob[lay["k_scale"]:lay["v_code"]].contiguous().view(torch.float32).reshape(PAGE_TOKENS, d // KV_GROUP)
+    vsc = blob[lay["v_scale"]:lay["bytes"]].contiguous().view(torch.float32).reshape(PAGE_TOKENS, d // KV_GROUP)
+    return kv_dequantize(kcodes, ksc), kv_dequantize(vcodes, vsc)

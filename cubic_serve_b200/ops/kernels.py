@@ -1,0 +1,203 @@
+"""Tensor-level wrappers over the native sm_100a kernels.
+
+Every wrapper takes CUDA tensors, launches on the current stream and raises
+``NativeLibraryError`` on a non-zero launch code.  There is deliberately no
+PyTorch fallback on the GPU path: a missing library is an error.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import native
+from .wq_pack import FMT_BF16, FMT_CUBIC4, PackedWeight
+
+PAGE_TOKENS = 16
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Workspace:
+    """Per-device scratch shared by split-K GEMMs and split-KV attention.
+
+    ``counters`` must stay zero between launches (the kernels restore it);
+    ``status`` collects device-side error codes and is polled by ``check_status``.
+    """
+
+    def __init__(self, device: torch.device, gemm_bytes: int = 64 << 20, attn_floats: int = 0,
+                 counters: int = 1 << 16) -> None:
+        self.device = device
+        self.gemm = torch.empty(gemm_bytes, dtype=torch.uint8, device=device)
+        self.attn = torch.empty(max(attn_floats, 1), dtype=torch.float32, device=device)
+        self.gemm_counters = torch.zeros(counters, dtype=torch.int32, device=device)
+        self.attn_counters = torch.zeros(counters, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def ensure_attn(self, floats: int) -> None:
+        if floats > self.attn.numel():
+            self.attn = torch.empty(floats, dtype=torch.float32, device=self.device)
+
+    def check_status(self) -> None:
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            raise native.NativeLibraryError(f"device kernel reported status {code} (bounded wait ran out)")
+
+
+_workspaces: dict[int, Workspace] = {}
+
+
+def workspace(device: torch.device) -> Workspace:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        ws = _workspaces[idx] = Workspace(torch.device("cuda", idx))
+    return ws
+
+
+def sm_count(device: torch.device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
+    """Split-K factor: fill the SMs when the (n-tile x m-tile) grid is small."""
+    n_tiles = -(-n // 128)
+    m_tiles = -(-m // 256)
+    tiles = n_tiles * m_tiles
+    k_blocks = k // 64
+    if tiles >= sms or k_blocks < 8:
+        return 1
+    splits = max(1, sms // tiles)
+    return max(1, min(splits, k_blocks // 4, 16))
+
+
+def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
+            residual: torch.Tensor | None = None, splits: int | None = None,
+            ws: Workspace | None = None) -> torch.Tensor:
+    """``out[M, N] = x[M, K] @ W[N, K]^T * alpha (+ residual)`` with W in packed form."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    m, k = x.shape
+    assert k == w.k, (k, w.k)
+    if out is None:
+        out = torch.empty((m, w.n), dtype=torch.bfloat16, device=x.device)
+    assert out.stride(1) == 1 and out.shape == (m, w.n)
+    if residual is not None:
+        assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
+    ws = ws or workspace(x.device)
+    if splits is None:
+        splits = choose_splits(m, w.n, k)
+    l = native.lib()
+    if splits > 1:
+        need = l.cb_wq_gemm_workspace_bytes(m, w.n, splits)
+        if need > ws.gemm.numel():
+            splits = 1
+    code = l.cb_wq_gemm(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta), out.data_ptr(),
+                        out.stride(0), _ptr(residual), float(w.alpha), m, w.n, k, w.group_k, splits,
+                        ws.gemm.data_ptr(), ws.gemm_counters.data_ptr(), ws.status.data_ptr(), _stream())
+    native.check(code, "cb_wq_gemm")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor | None = None,
+            residual: torch.Tensor | None = None, zero_centered: bool = False) -> torch.Tensor:
+    """RMSNorm; with ``residual`` the sum ``x + residual`` is written back into ``residual`` first."""
+    rows, h = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    code = native.lib().cb_rmsnorm(x.data_ptr(), _ptr(residual), _ptr(residual), weight.data_ptr(), out.data_ptr(),
+                                   rows, h, float(eps), int(zero_centered), _stream())
+    native.check(code, "cb_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    rows, two_i = gate_up.shape
+    i = two_i // 2
+    if out is None:
+        out = torch.empty((rows, i), dtype=gate_up.dtype, device=gate_up.device)
+    native.check(native.lib().cb_swiglu(gate_up.data_ptr(), out.data_ptr(), rows, i, _stream()), "cb_swiglu")
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None, vocab_start: int = 0) -> torch.Tensor:
+    t = ids.numel()
+    h = table.shape[1]
+    if out is None:
+        out = torch.empty((t, h), dtype=table.dtype, device=table.device)
+    code = native.lib().cb_embedding(ids.data_ptr(), table.data_ptr(), out.data_ptr(), t, h, vocab_start,
+                                     table.shape[0], _stream())
+    native.check(code, "cb_embedding")
+    return out
+
+
+def kv_blob_bytes(head_dim: int, k_bits: int, v_bits: int) -> int:
+    d = head_dim
+    scale = PAGE_TOKENS * (d // 32) * 4
+    return PAGE_TOKENS * d * k_bits // 8 + PAGE_TOKENS * d * v_bits // 8 + 2 * scale
+
+
+def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                  slots: torch.Tensor, inv_freq: torch.Tensor, hq: int, hkv: int, head_dim: int,
+                  k_bits: int, v_bits: int, q_norm: torch.Tensor | None = None,
+                  k_norm: torch.Tensor | None = None, eps: float = 1e-6, rotary_dim: int | None = None) -> None:
+    t = qkv.shape[0]
+    code = native.lib().cb_rope_kv_write(qkv.data_ptr(), q_out.data_ptr(), cache.data_ptr(), positions.data_ptr(),
+                                         slots.data_ptr(), _ptr(q_norm), _ptr(k_norm), inv_freq.data_ptr(), t, hq,
+                                         hkv, head_dim, head_dim if rotary_dim is None else rotary_dim, float(eps),
+                                         k_bits, v_bits, _stream())
+    native.check(code, "cb_rope_kv_write")
+
+
+def copy_pages(cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
+    page_bytes = cache.stride(0) * cache.element_size()
+    native.check(native.lib().cb_copy_pages(cache.data_ptr(), src.data_ptr(), dst.data_ptr(), src.numel(),
+                                            page_bytes, _stream()), "cb_copy_pages")
+
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
+                    rb_req: torch.Tensor, rb_qstart: torch.Tensor, rb_qcount: torch.Tensor, rb_ctx: torch.Tensor,
+                    hq: int, hkv: int, head_dim: int, k_bits: int, v_bits: int, scale: float | None = None,
+                    splits: int = 1, ws: Workspace | None = None) -> torch.Tensor:
+    """Attention of row blocks over the paged quantized cache (see ``csrc/paged_attn.cu``)."""
+    rbs = rb_req.numel()
+    ws = ws or workspace(q.device)
+    l = native.lib()
+    if splits > 1:
+        ws.ensure_attn(l.cb_paged_attn_partial_floats(rbs, hkv, splits))
+        assert rbs * hkv <= ws.attn_counters.numel()
+    code = l.cb_paged_attn(q.data_ptr(), out.data_ptr(), cache.data_ptr(), page_table.data_ptr(), rb_req.data_ptr(),
+                           rb_qstart.data_ptr(), rb_qcount.data_ptr(), rb_ctx.data_ptr(), rbs, hq, hkv, head_dim,
+                           page_table.shape[1], k_bits, v_bits,
+                           float(scale if scale is not None else 1.0 / math.sqrt(head_dim)), splits,
+                           ws.attn.data_ptr(), ws.attn_counters.data_ptr(), ws.status.data_ptr(), _stream())
+    native.check(code, "cb_paged_attn")
+    return out
+
+
+def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: torch.Tensor | None = None,
+           top_p: torch.Tensor | None = None, top_k: torch.Tensor | None = None,
+           seeds: torch.Tensor | None = None, counters: torch.Tensor | None = None,
+           mask: torch.Tensor | None = None, out_logprob: torch.Tensor | None = None,
+           vocab: int | None = None) -> torch.Tensor:
+    rows = logits.shape[0]
+    code = native.lib().cb_sample(logits.data_ptr(), logits.stride(0), _ptr(mask),
+                                  0 if mask is None else mask.shape[1], _ptr(temperature), _ptr(top_p), _ptr(top_k),
+                                  _ptr(seeds), _ptr(counters), out_ids.data_ptr(), _ptr(out_logprob), rows,
+                                  vocab or logits.shape[1], _stream())
+    native.check(code, "cb_sample")
+    return out_ids
+
+
+def verify_greedy(target_ids: torch.Tensor, draft_ids: torch.Tensor, depth: torch.Tensor, max_depth: int,
+                  accepted: torch.Tensor, bonus: torch.Tensor, forced_reject_at: torch.Tensor | None = None) -> None:
+    code = native.lib().cb_verify_greedy(target_ids.data_ptr(), draft_ids.data_ptr(), depth.data_ptr(), max_depth,
+                                         _ptr(forced_reject_at), accepted.data_ptr(), bonus.data_ptr(),
+                                         depth.numel(), _stream())
+    native.check(code, "cb_verify_greedy")

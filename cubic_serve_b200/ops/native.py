@@ -1,0 +1,131 @@
+"""Build and load the sm_100a native library (``libcubic_b200.so``).
+
+The kernels are plain CUDA C++ with ``extern "C"`` launchers; Python reaches
+them through ``ctypes`` with raw device pointers and the current CUDA stream,
+the same split the reference uses (driver-API launches, no CPython extension:
+``ops/cuda/native.py:101-255`` there).  The library is compiled ahead of time
+into the package directory so that it ships with a source snapshot.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import threading
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent.parent / "csrc"
+LIB_PATH = Path(__file__).resolve().parent.parent / "libcubic_b200.so"
+SOURCES = ("wq_gemm.cu", "elementwise.cu", "kv_cache.cu", "paged_attn.cu", "sampling.cu")
+NVCC_FLAGS = (
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+)
+
+_lock = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+
+class NativeLibraryError(RuntimeError):
+    """The native library is missing, failed to build, or a launch failed."""
+
+
+def _nvcc() -> str:
+    home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cand = Path(home) / "bin" / "nvcc"
+    return str(cand) if cand.exists() else "nvcc"
+
+
+def sources() -> list[Path]:
+    return [CSRC / s for s in SOURCES if (CSRC / s).exists()] + sorted(
+        p for p in CSRC.glob("*.cu") if p.name not in SOURCES
+    )
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    return any(p.stat().st_mtime > built for p in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``libcubic_b200.so``."""
+    if not force and not needs_build():
+        return LIB_PATH
+    objdir = CSRC / "build"
+    objdir.mkdir(exist_ok=True)
+    procs = []
+    objs = []
+    for src in sources():
+        obj = objdir / (src.stem + ".o")
+        objs.append(str(obj))
+        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for src, proc in procs:
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise NativeLibraryError(f"nvcc failed for {src.name}:\n{out}")
+        if verbose and out:
+            print(out)
+    tmp = LIB_PATH.with_suffix(".so.tmp")
+    link = [_nvcc(), "-shared", "-o", str(tmp), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    res = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise NativeLibraryError(f"link failed:\n{res.stdout}")
+    os.replace(tmp, LIB_PATH)
+    return LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    """Return the loaded library; build it first if a compiler is available and it is stale."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if needs_build():
+                try:
+                    build()
+                except (OSError, NativeLibraryError) as exc:
+                    if not LIB_PATH.exists():
+                        raise NativeLibraryError(
+                            f"{LIB_PATH.name} is missing and could not be built: {exc}"
+                        ) from exc
+            _lib = ctypes.CDLL(str(LIB_PATH))
+            _declare(_lib)
+        return _lib
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    vp, i, f, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+    l.cb_wq_gemm.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, vp, vp, vp]
+    l.cb_wq_gemm.restype = i
+    l.cb_wq_gemm_workspace_bytes.argtypes = [i, i, i]
+    l.cb_wq_gemm_workspace_bytes.restype = ll
+    l.cb_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i, i, f, i, vp]
+    l.cb_rmsnorm.restype = i
+    l.cb_swiglu.argtypes = [vp, vp, i, i, vp]
+    l.cb_swiglu.restype = i
+    l.cb_embedding.argtypes = [vp, vp, vp, i, i, i, i, vp]
+    l.cb_embedding.restype = i
+    l.cb_kv_blob_bytes.argtypes = [i, i, i]
+    l.cb_kv_blob_bytes.restype = i
+    l.cb_rope_kv_write.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, f, i, i, vp]
+    l.cb_rope_kv_write.restype = i
+    l.cb_copy_pages.argtypes = [vp, vp, vp, i, ll, vp]
+    l.cb_copy_pages.restype = i
+    l.cb_paged_attn_partial_floats.argtypes = [i, i, i]
+    l.cb_paged_attn_partial_floats.restype = ll
+    l.cb_paged_attn.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp, vp, vp, vp]
+    l.cb_paged_attn.restype = i
+    l.cb_sample.argtypes = [vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, i, i, vp]
+    l.cb_sample.restype = i
+    l.cb_verify_greedy.argtypes = [vp, vp, vp, i, vp, vp, vp, i, vp]
+    l.cb_verify_greedy.restype = i
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeLibraryError(f"{what} failed with code {code}")

@@ -1,0 +1,164 @@
+"""Re-tile checkpoint payloads into the layout the tcgen05 GEMM streams.
+
+The reference repacks every format into Marlin tiles at load time
+(``quantization/common/marlin/repack.py:149-280``); this is the same step for
+the sm_100a kernel in ``csrc/wq_gemm.cu``:
+
+* ``codes``: ``uint8 [n_tiles, k_blocks, 2, 128, 16]`` -- per (128-row tile,
+  64-column k-block) one contiguous 4 KiB block that a single bulk copy moves;
+  nibble ``i`` of 32-bit word ``j`` in row ``r``, half ``h`` is column
+  ``64*kb + 32*h + 8*j + i`` stored offset-binary;
+* ``meta``: ``uint8 [n_tiles, meta_blocks, 2, 128, 4]`` -- 1 KiB per block.
+
+All functions are pure tensor code and run on CPU or GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+FMT_CUBIC4 = 0
+FMT_AFFINE4 = 1
+FMT_NVFP4 = 2
+FMT_BF16 = 3
+
+TILE_N = 128
+BLOCK_K = 64
+
+
+@dataclass
+class PackedWeight:
+    fmt: int
+    n: int
+    k: int
+    group_k: int
+    codes: torch.Tensor          # uint8 (or bf16 [N, K] for FMT_BF16)
+    meta: torch.Tensor | None    # uint8
+    alpha: float = 1.0
+
+    def to(self, device) -> "PackedWeight":
+        return PackedWeight(self.fmt, self.n, self.k, self.group_k, self.codes.to(device),
+                            None if self.meta is None else self.meta.to(device), self.alpha)
+
+    @property
+    def nbytes(self) -> int:
+        return self.codes.numel() * self.codes.element_size() + (0 if self.meta is None else self.meta.numel())
+
+
+def _tile_nibbles(nib: torch.Tensor) -> torch.Tensor:
+    """``uint8 [N, K]`` values 0..15 -> tiled code bytes (N padded to 128 with `pad` already applied)."""
+    n, k = nib.shape
+    nt, kb = n // TILE_N, k // BLOCK_K
+    v = nib.reshape(nt, TILE_N, kb, 2, 4, 4, 2).to(torch.int32)   # [nt, r, kb, h, j, byte, lo/hi]
+    byts = (v[..., 0] | (v[..., 1] << 4)).to(torch.uint8)          # [nt, r, kb, h, j, byte]
+    return byts.permute(0, 2, 3, 1, 4, 5).contiguous().reshape(nt, kb, 2, TILE_N, 16)
+
+
+def _pad_rows(t: torch.Tensor, rows: int, value) -> torch.Tensor:
+    if t.shape[0] == rows:
+        return t
+    pad = torch.full((rows - t.shape[0], *t.shape[1:]), value, dtype=t.dtype, device=t.device)
+    return torch.cat([t, pad], 0)
+
+
+def pack_cubic4(codes: torch.Tensor, scale: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+                group_k: int) -> PackedWeight:
+    """Signed 4-bit Cubic codes ``int8 [N, K]`` (reserved code already 0) + variant-A metadata."""
+    n, k = codes.shape
+    if k % BLOCK_K or group_k % BLOCK_K:
+        raise ValueError("K and the Cubic group must be multiples of 64")
+    n_pad = -(-n // TILE_N) * TILE_N
+    nib = _pad_rows((codes.to(torch.int16) + 8).to(torch.uint8), n_pad, 8)
+    groups = -(-k // group_k)
+    sc = _pad_rows(scale.float().reshape(n, groups), n_pad, 0.0)
+    ab = torch.stack([_pad_rows(a.half().reshape(n, groups), n_pad, 0.0),
+                      _pad_rows(b.half().reshape(n, groups), n_pad, 0.0)], -1)  # [N, G, 2] fp16
+    w0 = sc.view(torch.int32)
+    w1 = ab.contiguous().view(torch.int32).reshape(n_pad, groups)
+    words = torch.stack([w0, w1], 0)                                # [2, N, G]
+    nt = n_pad // TILE_N
+    meta = words.reshape(2, nt, TILE_N, groups).permute(1, 3, 0, 2).contiguous()  # [nt, G, 2, 128]
+    return PackedWeight(FMT_CUBIC4, n, k, group_k, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, groups, 2, TILE_N, 4))
+
+
+def pack_affine4(q: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, group_k: int) -> PackedWeight:
+    """Unsigned 4-bit codes ``uint8 [N, K]`` with ``w = q * scale + offset`` per (row, K-group).
+
+    Covers INT pack-quantized (``offset = -zero_point * scale``), AWQ and GGUF
+    Q4_K (``scale = d * sc``, ``offset = -dmin * m`` per 32-column sub-block).
+    ``group_k`` must be a multiple of 32 (or the whole K).
+    """
+    n, k = q.shape
+    if k % BLOCK_K or group_k % 32:
+        raise ValueError("K must be a multiple of 64 and the group a multiple of 32")
+    n_pad = -(-n // TILE_N) * TILE_N
+    nib = _pad_rows(q.to(torch.uint8), n_pad, 0)
+    groups = -(-k // group_k)
+    reps = group_k // 32
+    so = torch.stack([scale.half().reshape(n, groups), offset.half().reshape(n, groups)], -1)  # [N, G, 2]
+    so = _pad_rows(so, n_pad, 0.0)
+    so32 = so.repeat_interleave(reps, dim=1)[:, : k // 32]          # [N, K/32, 2]
+    words = so32.contiguous().view(torch.int32).reshape(n_pad, k // 32)
+    nt, kb = n_pad // TILE_N, k // BLOCK_K
+    meta = words.reshape(nt, TILE_N, kb, 2).permute(0, 2, 3, 1).contiguous()  # [nt, kb, h, 128]
+    return PackedWeight(FMT_AFFINE4, n, k, group_k, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4))
+
+
+def pack_nvfp4(packed: torch.Tensor, block_scale: torch.Tensor, global_scale: float) -> PackedWeight:
+    """NVFP4 ``weight_packed uint8 [N, K/2]`` (low nibble first), e4m3 block scales ``[N, K/16]``.
+
+    ``global_scale`` multiplies the result (pass ``1 / weight_global_scale`` for
+    compressed-tensors checkpoints, ``weight_scale_2`` for ModelOpt).
+    """
+    n, k2 = packed.shape
+    k = k2 * 2
+    if k % BLOCK_K:
+        raise ValueError("K must be a multiple of 64")
+    n_pad = -(-n // TILE_N) * TILE_N
+    p32 = packed.to(torch.int32)
+    nib = torch.stack([p32 & 15, p32 >> 4], -1).reshape(n, k).to(torch.uint8)
+    nib = _pad_rows(nib, n_pad, 0)
+    bs = _pad_rows(block_scale.float().half().reshape(n, k // 16), n_pad, 0.0)
+    words = bs.reshape(n_pad, k // 32, 2).contiguous().view(torch.int32).reshape(n_pad, k // 32)
+    nt, kb = n_pad // TILE_N, k // BLOCK_K
+    meta = words.reshape(nt, TILE_N, kb, 2).permute(0, 2, 3, 1).contiguous()
+    return PackedWeight(FMT_NVFP4, n, k, 16, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4),
+                        alpha=float(global_scale))
+
+
+def pack_bf16(weight: torch.Tensor) -> PackedWeight:
+    n, k = weight.shape
+    if k % BLOCK_K:
+        raise ValueError("K must be a multiple of 64")
+    return PackedWeight(FMT_BF16, n, k, k, weight.to(torch.bfloat16).contiguous(), None)
+
+
+def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
+    """Oracle: rebuild the fp32 ``[N, K]`` matrix a PackedWeight represents (CPU or GPU)."""
+    if pw.fmt == FMT_BF16:
+        return pw.codes.float()
+    nt, kb = pw.codes.shape[0], pw.codes.shape[1]
+    byts = pw.codes.reshape(nt, kb, 2, TILE_N, 4, 4).permute(0, 3, 1, 2, 4, 5).to(torch.int32)  # [nt, r, kb, h, j, byte]
+    nib = torch.stack([byts & 15, byts >> 4], -1).reshape(nt * TILE_N, kb * BLOCK_K).float()
+    n_pad, k = nib.shape
+    words = pw.meta.reshape(nt, -1, 2, TILE_N, 4).view(torch.int32).reshape(nt, -1, 2, TILE_N)
+    if pw.fmt == FMT_CUBIC4:
+        g = words.shape[1]
+        scale = words[:, :, 0].permute(0, 2, 1).reshape(n_pad, g).contiguous().view(torch.float32)
+        ab = words[:, :, 1].permute(0, 2, 1).reshape(n_pad, g).contiguous().view(torch.float16).reshape(n_pad, g, 2).float()
+        col = torch.arange(k, device=nib.device) // pw.group_k
+        s, a, b = scale[:, col], ab[..., 0][:, col], ab[..., 1][:, col]
+        c = nib - 8.0
+        m = c.abs()
+        A, B, C = s * a / 7.0, s * b / 49.0, s * (1.0 - a - b) / 343.0
+        return (c * (A + m * (B + m * C)))[: pw.n]
+    pair = words.permute(0, 3, 1, 2).reshape(n_pad, -1).contiguous().view(torch.float16).reshape(n_pad, k // 32, 2).float()
+    if pw.fmt == FMT_AFFINE4:
+        col = torch.arange(k, device=nib.device) // 32
+        return (nib * pair[..., 0][:, col] + pair[..., 1][:, col])[: pw.n]
+    # NVFP4
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device=nib.device)
+    bs = pair.reshape(n_pad, k // 16)
+    col = torch.arange(k, device=nib.device) // 16
+    return (lut[nib.long()] * bs[:, col] * pw.alpha)[: pw.n]

@@ -1,0 +1,266 @@
+"""Numerics of every native kernel against fp32 PyTorch oracles (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+from cubic_serve_b200.ops import eager, wq_pack
+from cubic_serve_b200.quantization import cubic
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _k():
+    from cubic_serve_b200.ops import kernels
+    return kernels
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+def _cubic_weight(n, k, seed=0, group=128):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(n, k, generator=g) * 0.02
+    scheme = cubic.CubicScheme(bits=4, group_in=group)
+    payload = cubic.quantize(w, scheme)
+    dense = cubic.decode(payload, scheme, (n, k))
+    codes = cubic.unpack_codes(payload["weight_packed"], 4, k)
+    pw = wq_pack.pack_cubic4(codes, payload["weight_scale"], payload["weight_a"], payload["weight_b"], group)
+    return pw, dense
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(1, 128, 256, 1), (16, 256, 512, 1), (40, 384, 1024, 1),
+                                          (256, 256, 4096, 1), (300, 128, 512, 1), (64, 200, 512, 1),
+                                          (32, 256, 2048, 4), (256, 128, 4096, 3)])
+def test_wq_gemm_cubic4(m, n, k, splits):
+    K = _k()
+    pw, dense = _cubic_weight(n, k, seed=m + n)
+    assert _rel(wq_pack.unpack_to_dense(pw), dense) < 1e-6
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
+    ref = x.float() @ dense.to(torch.bfloat16).float().t()
+    y = K.wq_gemm(x.to(DEV), pw.to(DEV), splits=splits)
+    torch.cuda.synchronize()
+    K.workspace(y.device).check_status()
+    assert y.shape == (m, n)
+    assert _rel(y.cpu(), ref) < 1e-2
+    # repeat: split-K counters must have been restored
+    y2 = K.wq_gemm(x.to(DEV), pw.to(DEV), splits=splits)
+    assert torch.equal(y, y2)
+
+
+def test_wq_gemm_residual_and_bf16():
+    K = _k()
+    m, n, k = 48, 256, 512
+    w = (torch.randn(n, k) * 0.05).to(torch.bfloat16)
+    x = (torch.randn(m, k) * 0.5).to(torch.bfloat16)
+    res = torch.randn(m, n).to(torch.bfloat16)
+    ref = x.float() @ w.float().t() + res.float()
+    y = K.wq_gemm(x.to(DEV), wq_pack.pack_bf16(w).to(DEV), residual=res.to(DEV))
+    assert _rel(y.cpu(), ref) < 1e-2
+
+
+def test_wq_gemm_affine4_and_nvfp4():
+    K = _k()
+    m, n, k = 32, 256, 512
+    g = torch.Generator().manual_seed(3)
+    q = torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8)
+    scale = (torch.rand(n, k // 64, generator=g) * 0.01 + 0.001)
+    zero = torch.randint(0, 16, (n, k // 64), generator=g).float()
+    pw = wq_pack.pack_affine4(q, scale, -zero * scale, 64)
+    dense = wq_pack.unpack_to_dense(pw)
+    expect = (q.float() - zero.repeat_interleave(64, 1)) * scale.half().float().repeat_interleave(64, 1)
+    assert _rel(dense, expect) < 2e-3
+    x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16)
+    y = K.wq_gemm(x.to(DEV), pw.to(DEV))
+    assert _rel(y.cpu(), x.float() @ dense.to(torch.bfloat16).float().t()) < 1e-2
+
+    packed = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+    bs = (torch.rand(n, k // 16, generator=g) * 2 + 0.25).to(torch.float8_e4m3fn)
+    pw4 = wq_pack.pack_nvfp4(packed, bs.float(), 0.01)
+    dense4 = wq_pack.unpack_to_dense(pw4)
+    y4 = K.wq_gemm(x.to(DEV), pw4.to(DEV))
+    assert _rel(y4.cpu(), x.float() @ (dense4 / 0.01).to(torch.bfloat16).float().t() * 0.01) < 1e-2
+
+
+def test_rmsnorm_swiglu_embedding():
+    K = _k()
+    x = torch.randn(37, 4096).to(torch.bfloat16).to(DEV)
+    w = torch.randn(4096).to(torch.bfloat16).to(DEV)
+    res = torch.randn(37, 4096).to(torch.bfloat16).to(DEV)
+    assert _rel(K.rmsnorm(x, w, 1e-6), eager.rmsnorm(x, w, 1e-6)) < 5e-3
+    summed = (x.float() + res.float()).to(torch.bfloat16)
+    res2 = res.clone()
+    out = K.rmsnorm(x, w, 1e-6, residual=res2, zero_centered=True)
+    assert torch.equal(res2, summed)
+    assert _rel(out, eager.rmsnorm(summed, w, 1e-6, zero_centered=True)) < 5e-3
+    gu = torch.randn(19, 2 * 1536).to(torch.bfloat16).to(DEV)
+    assert _rel(K.swiglu(gu), eager.swiglu(gu)) < 5e-3
+    table = torch.randn(1000, 256).to(torch.bfloat16).to(DEV)
+    ids = torch.tensor([5, 999, 0, 1200, 17], dtype=torch.int32, device=DEV)
+    e = K.embedding(ids, table)
+    assert torch.equal(e[0], table[5]) and torch.equal(e[1], table[999]) and bool((e[3] == 0).all())
+
+
+def _make_cache(pages, hkv, d, kb, vb):
+    blob = eager.blob_layout(d, kb, vb)["bytes"]
+    assert blob == _k().kv_blob_bytes(d, kb, vb)
+    return torch.zeros(pages, hkv, blob, dtype=torch.uint8, device=DEV)
+
+
+@pytest.mark.parametrize("kb,vb", [(8, 8), (4, 8), (4, 4), (8, 4)])
+def test_rope_kv_write_roundtrip(kb, vb):
+    K = _k()
+    hq, hkv, d, t = 8, 2, 128, 37
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, generator=g).to(torch.bfloat16).to(DEV)
+    pos = torch.arange(100, 100 + t, dtype=torch.int32, device=DEV)
+    pages = torch.randperm(8, generator=g)[: (t + 15) // 16].to(torch.int32)
+    slots = (pages[torch.arange(t) // 16] * 16 + torch.arange(t) % 16).to(torch.int32).to(DEV)
+    slots[3] = -1  # padding row: nothing written
+    cache = _make_cache(8, hkv, d, kb, vb)
+    inv = eager.rope_inv_freq(d, 1e6, DEV)
+    qn = (torch.rand(d, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    kn = (torch.rand(d, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
+    q_out = torch.empty(t, hq * d, dtype=torch.bfloat16, device=DEV)
+    K.rope_kv_write(qkv, q_out, cache, pos, slots, inv, hq, hkv, d, kb, vb, q_norm=qn, k_norm=kn, eps=1e-6)
+    x = qkv.view(t, hq + 2 * hkv, d)
+    qr = eager.rope(eager.rmsnorm(x[:, :hq], qn, 1e-6).to(torch.bfloat16), pos, inv)
+    kr = eager.rope(eager.rmsnorm(x[:, hq:hq + hkv], kn, 1e-6).to(torch.bfloat16), pos, inv).to(torch.bfloat16).float()
+    vr = x[:, hq + hkv:].float()
+    assert _rel(q_out.view(t, hq, d), qr) < 5e-3
+    kq, ksc = eager.kv_quantize(kr, kb)
+    vq, vsc = eager.kv_quantize(vr, vb)
+    kd, vd = eager.kv_dequantize(kq, ksc), eager.kv_dequantize(vq, vsc)
+    for tok in range(t):
+        if tok == 3:
+            continue
+        page, off = int(slots[tok]) // 16, int(slots[tok]) % 16
+        for h in range(hkv):
+            kk, vv = eager.decode_cache_page(cache[page, h], d, kb, vb)
+            # one code step of slack where rounding sits on a tie after bf16 effects
+            assert (kk[off] - kd[tok, h]).abs().max() <= ksc[tok, h].max() * 1.01
+            assert _rel(kk[off], kd[tok, h]) < (0.02 if kb == 8 else 0.2)
+            assert _rel(vv[off], vd[tok, h]) < 1e-6
+
+
+def _fill_cache_random(cache, t_total, hkv, d, kb, vb, page_ids, seed=0):
+    """Write random K/V for tokens 0..t_total-1 of one request through the write kernel."""
+    K = _k()
+    g = torch.Generator().manual_seed(seed)
+    hq = hkv
+    qkv = torch.randn(t_total, (hq + 2 * hkv) * d, generator=g).to(torch.bfloat16).to(DEV)
+    pos = torch.arange(t_total, dtype=torch.int32, device=DEV)
+    slots = (page_ids[torch.arange(t_total) // 16] * 16 + torch.arange(t_total) % 16).to(torch.int32).to(DEV)
+    q_out = torch.empty(t_total, hq * d, dtype=torch.bfloat16, device=DEV)
+    K.rope_kv_write(qkv, q_out, cache, pos, slots, eager.rope_inv_freq(d, 1e4, DEV), hq, hkv, d, kb, vb,
+                    rotary_dim=0)
+
+
+def _dense_kv(cache, page_ids, t_total, hkv, d, kb, vb):
+    ks, vs = [], []
+    for p in page_ids.tolist():
+        kh, vh = zip(*[eager.decode_cache_page(cache[p, h], d, kb, vb) for h in range(hkv)])
+        ks.append(torch.stack(kh, 1))
+        vs.append(torch.stack(vh, 1))
+    return torch.cat(ks)[:t_total], torch.cat(vs)[:t_total]
+
+
+@pytest.mark.parametrize("kb,vb,hq,hkv,splits", [(8, 8, 8, 2, 1), (8, 8, 8, 2, 3), (4, 8, 16, 2, 1),
+                                                 (4, 4, 8, 1, 2), (8, 4, 16, 1, 1)])
+def test_paged_attention_decode(kb, vb, hq, hkv, splits):
+    K = _k()
+    d = 128
+    lens = [1, 17, 100, 333]
+    n_pages = 64
+    cache = _make_cache(n_pages, hkv, d, kb, vb)
+    cache.view(torch.float32)[:] = float("nan")  # stale slots must not leak into the result
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(7)).to(torch.int32)
+    max_pages = 24
+    table = torch.zeros(len(lens), max_pages, dtype=torch.int32)
+    used = 0
+    dense = []
+    for r, ln in enumerate(lens):
+        np_ = (ln + 15) // 16
+        ids = perm[used:used + np_]
+        used += np_
+        table[r, :np_] = ids
+        _fill_cache_random(cache, ln, hkv, d, kb, vb, ids, seed=r)
+        dense.append(_dense_kv(cache, ids, ln, hkv, d, kb, vb))
+    q = torch.randn(len(lens), hq, d, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).to(DEV)
+    out = torch.zeros_like(q)
+    ar = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    K.paged_attention(q, out, cache, table.to(DEV), ar, ar.clone(), torch.ones_like(ar),
+                      torch.tensor(lens, dtype=torch.int32, device=DEV), hq, hkv, d, kb, vb, splits=splits)
+    torch.cuda.synchronize()
+    K.workspace(q.device).check_status()
+    for r, ln in enumerate(lens):
+        k, v = dense[r]
+        ref = eager.attention_rows(q[r:r + 1], k, v, torch.tensor([ln], device=DEV))
+        assert _rel(out[r:r + 1], ref) < 2e-2, (r, ln)
+
+
+def test_paged_attention_prefill_rows():
+    """Causal chunk: 4 positions x 4 heads per row block, context from earlier pages."""
+    K = _k()
+    kb = vb = 8
+    hq, hkv, d = 8, 2, 128
+    g_ = hq // hkv
+    qb = 16 // g_
+    total, chunk_start = 77, 30          # tokens 30..76 are the query chunk
+    n_pages = 8
+    cache = _make_cache(n_pages, hkv, d, kb, vb)
+    ids = torch.tensor([5, 2, 7, 0, 3], dtype=torch.int32)
+    _fill_cache_random(cache, total, hkv, d, kb, vb, ids, seed=11)
+    k, v = _dense_kv(cache, ids, total, hkv, d, kb, vb)
+    nq = total - chunk_start
+    q = torch.randn(nq, hq, d, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+    out = torch.zeros_like(q)
+    table = torch.zeros(1, 8, dtype=torch.int32)
+    table[0, :5] = ids
+    nblk = (nq + qb - 1) // qb
+    starts = torch.arange(nblk, dtype=torch.int32) * qb
+    K.paged_attention(q, out, cache, table.to(DEV), torch.zeros(nblk, dtype=torch.int32, device=DEV),
+                      starts.to(DEV), torch.clamp(nq - starts, max=qb).to(torch.int32).to(DEV),
+                      (chunk_start + starts + 1).to(torch.int32).to(DEV), hq, hkv, d, kb, vb)
+    vis = torch.arange(chunk_start + 1, total + 1, device=DEV)
+    ref = eager.attention_rows(q, k, v, vis)
+    assert _rel(out, ref) < 2e-2
+
+
+def test_sampler():
+    K = _k()
+    rows, vocab = 6, 5000
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(rows, vocab, generator=g).to(torch.bfloat16)
+    logits[0, 77] = logits[0, 4000] = 9.0   # tie: lowest id wins
+    lg = logits.to(DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    K.sample(lg, out)
+    expect = [int((logits[r].float() == logits[r].float().max()).nonzero()[0]) for r in range(rows)]
+    assert out.tolist() == expect and out[0].item() == 77
+    # grammar mask: only ids 10..19 allowed
+    mask = torch.zeros(rows, (vocab + 31) // 32, dtype=torch.int32)
+    mask[:, 0] = sum(1 << b for b in range(10, 20))
+    K.sample(lg, out, mask=mask.to(DEV))
+    assert out.tolist() == [10 + int(logits[r, 10:20].float().argmax()) for r in range(rows)]
+    # stochastic: top_k = 3 draws stay inside the top-3 set and follow the seed
+    temp = torch.full((rows,), 0.8, device=DEV)
+    top_k = torch.full((rows,), 3, dtype=torch.int32, device=DEV)
+    top_p = torch.full((rows,), 1.0, device=DEV)
+    seeds = torch.arange(rows, dtype=torch.int64, device=DEV) + 123
+    ctr = torch.zeros(rows, dtype=torch.int64, device=DEV)
+    a = torch.empty(rows, dtype=torch.int32, device=DEV)
+    b = torch.empty_like(a)
+    K.sample(lg, a, temperature=temp, top_p=top_p, top_k=top_k, seeds=seeds, counters=ctr)
+    K.sample(lg, b, temperature=temp, top_p=top_p, top_k=top_k, seeds=seeds, counters=ctr)
+    assert torch.equal(a, b)
+    top3 = logits.float().topk(3, -1).indices
+    assert all(int(a[r]) in top3[r].tolist() for r in range(rows))
+    seen = set()
+    for c in range(40):
+        K.sample(lg[:1], a[:1], temperature=temp[:1], top_p=top_p[:1], top_k=top_k[:1], seeds=seeds[:1],
+                 counters=ctr[:1] + c)
+        seen.add(int(a[0]))
+    assert len(seen) >= 2
