@@ -1,0 +1,222 @@
+#!/usr/bin/env python
+"""Headline serving benchmark: output tokens/s of the dense 8B-class decoder at 256 concurrent requests.
+
+Config (BASELINE.json, second entry): 36 layers, hidden 4096, 32 q / 8 kv heads of 128, SwiGLU 12288, vocab
+151936, RoPE theta 1e6; random-init N(0, 0.02) weights quantized offline to 4-bit CubicQuant (group 128);
+INT8 K / INT8 V paged cache; 256 concurrent requests with 1024 random input tokens each; greedy decoding
+under CUDA graphs; tensor parallel over ``--gpus`` ranks.
+
+A *step* is one engine iteration in the steady decode phase: every one of the 256 running requests gets one
+new token (context 1024 + i at step i).  The prompts are prefilled through the same engine before the timed
+region (that phase is reported separately as ``prefill_tok_s``); nothing inside a timed step is skipped:
+embedding, all layers, lm_head, sampling, and -- for the end-to-end number -- the per-step host -> device copy of
+the step's inputs from pinned memory and the device -> host read of the sampled tokens.
+
+Prints ONE JSON line on rank 0.  ``--impl reference`` runs the reference arm (see ``baseline/``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_TOK_S = 2226.0   # reference's published dense total tok/s @ C=256 (4x SM120, different model/hardware)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="dense-8b")
+    ap.add_argument("--concurrency", type=int, default=256)
+    ap.add_argument("--input-len", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collective path")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_reference(args) -> None:
+    from baseline.reference_arm import run as ref_run
+    print(json.dumps(ref_run(args)), flush=True)
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.models.config import NAMED_CONFIGS
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    tp = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from cubic_serve_b200.parallel.tp import TensorParallel
+        tp = TensorParallel(dist.group.WORLD, dev, mode=args.comm)
+
+    cfg = NAMED_CONFIGS[args.model]()
+    if args.layers:
+        from dataclasses import replace
+        cfg = replace(cfg, num_layers=args.layers)
+    C, L = args.concurrency, args.input_len
+    total_steps = args.warmup + args.steps
+    max_len = L + total_steps + 8
+    pages_per_req = -(-max_len // 16)
+    num_pages = C * pages_per_req + 8
+    prefill_tokens = 8192
+
+    weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
+    runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=8, v_bits=8, tp=tp)
+    ex = GpuExecutor(runner, max_rows=C, max_prefill_tokens=prefill_tokens, max_model_len=max_len)
+    ex.capture_decode_graphs([C])
+    ex.timing = True
+    eng = LLMEngine(ex, num_pages=num_pages,
+                    scheduler_config=SchedulerConfig(max_running_requests=C, max_batched_tokens=prefill_tokens,
+                                                     prefill_chunk_tokens=prefill_tokens, max_model_len=max_len,
+                                                     enable_prefix_cache=False))
+    rng = np.random.default_rng(1)
+    prompts = rng.integers(0, cfg.vocab_size, size=(C, L)).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 4, ignore_eos=True)
+    for p in prompts:
+        eng.add_request(p, SamplingParams(**vars(sp)))
+
+    def sync():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    # ---- prefill phase (untimed for the headline; reported on the side)
+    sync()
+    t0 = time.perf_counter()
+    n_prefill_steps = 0
+    while any(r.remaining > 1 for r in eng.scheduler.running + eng.scheduler.waiting) or eng.scheduler.waiting:
+        eng.step()
+        n_prefill_steps += 1
+    sync()
+    prefill_s = time.perf_counter() - t0
+    assert len(eng.scheduler.running) == C, len(eng.scheduler.running)
+
+    # ---- decode: W warm-up steps, K timed steps
+    for _ in range(args.warmup):
+        outs = eng.step()
+        assert len(outs) == C
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ex.device_ms = []
+    sync()
+    t0 = time.perf_counter()
+    launches = 0
+    for _ in range(args.steps):
+        outs = eng.step()
+        launches += ex.kernel_launches_last
+    sync()
+    wall_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else {}
+    assert len(outs) == C
+    runner.ws.check_status()
+    dev_ms = float(sum(ex.device_ms))
+    stats = torch.tensor([dev_ms, wall_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms = stats.tolist()
+    tokens = C * args.steps
+    value = tokens / (dev_ms / 1e3)
+    e2e = tokens / (wall_ms / 1e3)
+    if rank == 0:
+        line = {
+            "metric": "output tok/s @256 concurrent (decode steps, device-timed, max over ranks)",
+            "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": "bf16 activations, 4-bit CubicQuant weights, INT8 KV",
+            "data": "synthetic (random token ids; random-init N(0,0.02) weights quantized offline)",
+            "impl": "ours",
+            "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
+                       "global_batch": C, "seq_len": L, "parallelism": f"tp{world}",
+                       "comm": args.comm if world > 1 else "none", "cuda_graphs": True, "kv_cache": "int8/int8",
+                       "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
+                       "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,
+                       "weights_gb": round(weights.nbytes() / 1e9, 2)},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(ex.h2d_bytes_last),
+                    "d2h_bytes_per_step": int(ex.d2h_bytes_last), "api": "LLMEngine.step()"},
+            "gpu_launches": int(launches),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

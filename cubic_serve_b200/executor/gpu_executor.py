@@ -1,0 +1,235 @@
+"""Per-rank GPU executor: batch metadata staging, CUDA-graph buckets, replay.
+
+Mirrors the reference worker's replay path (``runtime/quantized_graph.py:1566``
+command loop -> ``executor.replay_batch`` -> fill pinned metadata -> H2D ->
+``graph.replay()`` -> sample) with one difference in structure: all per-step
+metadata lives in ONE pinned byte buffer mirrored by ONE device buffer, so a
+step is a single ``cudaMemcpyAsync`` followed by a graph launch and a single
+D2H read of the sampled ids.
+
+Decode steps replay graphs captured per power-of-two row capacity; prefill
+chunks (variable token counts) launch the same kernels eagerly.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..models.decoder import DecoderRunner, StepBatch
+from ..ops import kernels as K
+
+
+@dataclass
+class Segment:
+    """One request's slice of a step: ``count`` new tokens starting at ``start`` (its position)."""
+    request_slot: int            # row of the persistent page table owned by the request
+    token_ids: np.ndarray | list  # the new tokens (len == count)
+    start: int                   # position of the first new token
+    pages: np.ndarray | list     # physical page ids of the request, covering start + count tokens
+    sample: bool = True          # whether the last token's logits are sampled
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    seed: int = 0
+    draw: int = 0
+
+
+class _Staging:
+    """Typed views over one pinned host buffer and its device mirror."""
+
+    def __init__(self, max_tokens: int, max_rows: int, max_row_blocks: int, max_pages: int, device) -> None:
+        self.max_tokens, self.max_rows, self.max_row_blocks, self.max_pages = max_tokens, max_rows, max_row_blocks, max_pages
+        fields = [
+            ("token_ids", np.int32, max_tokens), ("positions", np.int32, max_tokens), ("slots", np.int32, max_tokens),
+            ("rb_req", np.int32, max_row_blocks), ("rb_qstart", np.int32, max_row_blocks),
+            ("rb_qcount", np.int32, max_row_blocks), ("rb_ctx", np.int32, max_row_blocks),
+            ("top_k", np.int32, max_rows), ("temperature", np.float32, max_rows), ("top_p", np.float32, max_rows),
+            ("logit_rows", np.int64, max_rows), ("seeds", np.int64, max_rows), ("draws", np.int64, max_rows),
+            ("page_table", np.int32, max_rows * max_pages),
+        ]
+        off = 0
+        self.offsets = {}
+        for name, dt, n in fields:
+            off = (off + 15) & ~15
+            self.offsets[name] = (off, dt, n)
+            off += np.dtype(dt).itemsize * n
+        self.nbytes = (off + 15) & ~15
+        self.host = torch.empty(self.nbytes, dtype=torch.uint8, pin_memory=torch.cuda.is_available())
+        self.dev = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.h_np = self.host.numpy()
+        self.h = {}
+        self.d = {}
+        tmap = {np.int32: torch.int32, np.float32: torch.float32, np.int64: torch.int64}
+        for name, (o, dt, n) in self.offsets.items():
+            size = np.dtype(dt).itemsize * n
+            self.h[name] = self.h_np[o:o + size].view(dt)
+            self.d[name] = self.dev[o:o + size].view(tmap[dt])
+        self.d["page_table"] = self.d["page_table"].view(max_rows, max_pages)
+        self.h["page_table"] = self.h["page_table"].reshape(max_rows, max_pages)
+
+    def upload(self, nbytes: int | None = None) -> int:
+        n = self.nbytes if nbytes is None else nbytes
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)
+        return n
+
+
+class GpuExecutor:
+    def __init__(self, runner: DecoderRunner, max_rows: int = 256, max_prefill_tokens: int = 8192,
+                 max_model_len: int = 4096, use_graphs: bool = True) -> None:
+        self.runner = runner
+        self.cfg = runner.cfg
+        self.device = runner.device
+        self.G = runner.hq // runner.hkv
+        self.qb = 16 // self.G                                  # query positions per attention row block
+        self.max_rows = max_rows
+        self.max_tokens = max(max_prefill_tokens, max_rows)
+        assert self.max_tokens <= runner.max_tokens
+        self.max_pages = -(-max_model_len // K.PAGE_TOKENS)
+        max_rb = max(max_rows, self.max_tokens // self.qb + max_rows)
+        self.stage = _Staging(self.max_tokens, max_rows, max_rb, self.max_pages, self.device)
+        v_local = runner.w.lm_head.n
+        self.logits = torch.empty(max_rows, v_local, dtype=torch.bfloat16, device=self.device)
+        self.out_ids = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.use_graphs = use_graphs
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+        self.kernel_launches_last = 0
+        self.graph_launches = {}
+        self.timing = False              # record device time of the compute part of every step
+        self.device_ms: list[float] = []
+        self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+
+    # ----------------------------------------------------------------- batches
+    def _fill(self, segs: list[Segment], pad_rows_to: int | None = None) -> StepBatch:
+        st = self.stage
+        h = st.h
+        t = 0
+        rb = 0
+        rows = 0
+        qb = self.qb
+        for si, s in enumerate(segs):
+            n = len(s.token_ids)
+            h["token_ids"][t:t + n] = s.token_ids
+            pos = np.arange(s.start, s.start + n, dtype=np.int32)
+            h["positions"][t:t + n] = pos
+            pages = np.asarray(s.pages, dtype=np.int32)
+            h["slots"][t:t + n] = pages[pos >> 4] * 16 + (pos & 15)
+            h["page_table"][si, :len(pages)] = pages
+            nb = -(-n // qb)
+            starts = np.arange(nb, dtype=np.int32) * qb
+            h["rb_req"][rb:rb + nb] = si
+            h["rb_qstart"][rb:rb + nb] = t + starts
+            h["rb_qcount"][rb:rb + nb] = np.minimum(n - starts, qb)
+            h["rb_ctx"][rb:rb + nb] = s.start + starts + 1
+            rb += nb
+            if s.sample:
+                h["logit_rows"][rows] = t + n - 1
+                h["temperature"][rows] = s.temperature
+                h["top_p"][rows] = s.top_p
+                h["top_k"][rows] = s.top_k
+                h["seeds"][rows] = s.seed
+                h["draws"][rows] = s.draw
+                rows += 1
+            t += n
+        if pad_rows_to is not None and pad_rows_to > t:
+            # decode bucket padding: rows that write nothing and attend to nothing
+            p = pad_rows_to
+            h["token_ids"][t:p] = 0
+            h["positions"][t:p] = 0
+            h["slots"][t:p] = -1
+            h["rb_req"][rb:p] = 0
+            h["rb_qstart"][rb:p] = np.arange(rb, p, dtype=np.int32)
+            h["rb_qcount"][rb:p] = 0
+            h["rb_ctx"][rb:p] = 0
+            h["logit_rows"][rows:p] = np.arange(rows, p)
+            h["temperature"][rows:p] = 0
+            t, rb, rows_cap = p, p, p
+        else:
+            rows_cap = rows
+        d = st.d
+        splits = self._splits(rb)
+        return StepBatch(num_tokens=t, num_row_blocks=rb, num_logit_rows=rows_cap, token_ids=d["token_ids"],
+                         positions=d["positions"], slots=d["slots"], page_table=d["page_table"], rb_req=d["rb_req"],
+                         rb_qstart=d["rb_qstart"], rb_qcount=d["rb_qcount"], rb_ctx=d["rb_ctx"],
+                         logit_rows=d["logit_rows"], attn_splits=splits), rows
+
+    def _splits(self, row_blocks: int) -> int:
+        ctas = max(1, row_blocks * self.runner.hkv)
+        return int(min(32, max(1, -(-296 // ctas))))
+
+    # ------------------------------------------------------------------- run
+    def _body(self, b: StepBatch) -> None:
+        r = self.runner
+        hidden = r.forward_hidden(b)
+        if b.num_logit_rows:
+            logits = r.forward_logits(b, hidden, self.logits)
+            d = self.stage.d
+            n = b.num_logit_rows
+            K.sample(logits, self.out_ids[:n], temperature=d["temperature"][:n], top_p=d["top_p"][:n],
+                     top_k=d["top_k"][:n], seeds=d["seeds"][:n], counters=d["draws"][:n], vocab=logits.shape[1])
+            r.launches_per_step += 1
+
+    def capture_decode_graphs(self, capacities: list[int] | None = None) -> list[int]:
+        """Capture one graph per decode row capacity (largest first, like the reference)."""
+        caps = capacities or [c for c in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512) if c <= self.max_rows]
+        for cap in sorted(caps, reverse=True):
+            dummy = [Segment(0, [0], 0, [0])]
+            b, _ = self._fill(dummy, pad_rows_to=cap)
+            # the warm-up run below must not touch real cache pages: the single real row is turned into padding too
+            self.stage.h["slots"][:cap] = -1
+            self.stage.h["rb_qcount"][:cap] = 0
+            self.stage.upload()
+            with torch.cuda.stream(self.stream):
+                for _ in range(2):
+                    self._body(b)
+                self.stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.stream):
+                    self._body(b)
+            self.graphs[cap] = g
+            self.graph_launches[cap] = self.runner.launches_per_step
+        torch.cuda.synchronize(self.device)
+        return sorted(self.graphs)
+
+    def copy_pages(self, pairs) -> None:
+        """Copy-on-write page copies (all layers) ahead of a step."""
+        if not pairs:
+            return
+        src = torch.tensor([p[0] for p in pairs], dtype=torch.int32, device=self.device)
+        dst = torch.tensor([p[1] for p in pairs], dtype=torch.int32, device=self.device)
+        with torch.cuda.stream(self.stream):
+            for cache in self.runner.kv:
+                K.copy_pages(cache, src, dst)
+
+    def execute(self, segs: list[Segment]) -> np.ndarray:
+        """Run one step and return the sampled token id of every sampling segment (host array)."""
+        total = sum(len(s.token_ids) for s in segs)
+        decode = all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs)
+        cap = None
+        if decode:
+            cap = next((c for c in sorted(self.graphs) if c >= total), None)
+        b, rows = self._fill(segs, pad_rows_to=cap)
+        with torch.cuda.stream(self.stream):
+            self.h2d_bytes_last = self.stage.upload()
+            if self.timing:
+                self._ev[0].record(self.stream)
+            if cap is not None:
+                self.graphs[cap].replay()
+                self.kernel_launches_last = self.graph_launches[cap]
+            else:
+                self._body(b)
+                self.kernel_launches_last = self.runner.launches_per_step
+            if self.timing:
+                self._ev[1].record(self.stream)
+            if rows:
+                self.out_host[:rows].copy_(self.out_ids[:rows], non_blocking=True)
+            self.stream.synchronize()
+        self.d2h_bytes_last = rows * 4
+        if self.timing:
+            self.device_ms.append(self._ev[0].elapsed_time(self._ev[1]))
+        return self.out_host[:rows].numpy().copy()

@@ -1,0 +1,177 @@
+"""Model architecture description shared by the loader, the runners and the benchmarks.
+
+Plays the role of the reference's ``ModelSpec`` / per-family config parsers
+(``contracts/model.py:66-273``, ``models/qwen3_5/model.py:498``) for the decoder
+families this engine serves: plain GQA decoders (Llama/Qwen3 style, dense or
+MoE) and hybrid linear-attention decoders.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+
+
+@dataclass(frozen=True)
+class QuantSpec:
+    """How the linear weights are stored."""
+    method: str = "cubic"          # cubic | int | awq | fp8 | fp8_block | nvfp4 | gguf | none
+    bits: int = 4
+    group_size: int = 128
+    lm_head_quantized: bool = False
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    name: str = "toy"
+    family: str = "gqa_decoder"    # gqa_decoder | gqa_moe | qwen3_5 | qwen3_5_moe | qwen4_exp
+    num_layers: int = 2
+    hidden_size: int = 256
+    num_q_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 64
+    intermediate_size: int = 512
+    vocab_size: int = 1024
+    rope_theta: float = 10000.0
+    rotary_dim: int | None = None
+    rms_eps: float = 1e-6
+    qk_norm: bool = False
+    zero_centered_norm: bool = False
+    tie_embeddings: bool = False
+    max_position: int = 40960
+    # MoE
+    num_experts: int = 0
+    experts_per_token: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    # MTP head (1 extra decoder layer sharing embeddings and lm_head)
+    mtp_layers: int = 0
+    quant: QuantSpec = field(default_factory=QuantSpec)
+    eos_token_id: int | None = None
+
+    @property
+    def q_size(self) -> int:
+        return self.num_q_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self), indent=1)
+
+    @staticmethod
+    def from_dict(d: dict) -> "ModelConfig":
+        d = dict(d)
+        q = d.pop("quant", None)
+        if isinstance(q, dict):
+            d["quant"] = QuantSpec(**q)
+        return ModelConfig(**d)
+
+    @staticmethod
+    def from_hf_config(path: str | Path) -> "ModelConfig":
+        """Parse a HuggingFace ``config.json`` (Llama / Qwen2 / Qwen3 / Qwen3-MoE style)."""
+        cfg = json.loads(Path(path).read_text())
+        text = cfg.get("text_config", cfg)
+        qc = cfg.get("quantization_config") or text.get("quantization_config") or {}
+        arch = (cfg.get("architectures") or ["?"])[0]
+        heads = text["num_attention_heads"]
+        hd = text.get("head_dim") or text["hidden_size"] // heads
+        n_exp = text.get("num_experts") or text.get("num_local_experts") or 0
+        return ModelConfig(
+            name=cfg.get("_name_or_path") or arch,
+            family="gqa_moe" if n_exp else "gqa_decoder",
+            num_layers=text["num_hidden_layers"],
+            hidden_size=text["hidden_size"],
+            num_q_heads=heads,
+            num_kv_heads=text.get("num_key_value_heads", heads),
+            head_dim=hd,
+            intermediate_size=text.get("intermediate_size", 0),
+            vocab_size=text["vocab_size"],
+            rope_theta=float(text.get("rope_theta", 10000.0)),
+            rms_eps=float(text.get("rms_norm_eps", 1e-6)),
+            qk_norm="Qwen3" in arch,
+            tie_embeddings=bool(text.get("tie_word_embeddings", False)),
+            max_position=int(text.get("max_position_embeddings", 40960)),
+            num_experts=n_exp,
+            experts_per_token=text.get("num_experts_per_tok", 0) if n_exp else 0,
+            moe_intermediate_size=text.get("moe_intermediate_size", 0) if n_exp else 0,
+            norm_topk_prob=bool(text.get("norm_topk_prob", True)),
+            quant=quant_spec_from_hf(qc),
+            eos_token_id=(text.get("eos_token_id") if isinstance(text.get("eos_token_id"), int) else None),
+        )
+
+
+def quant_spec_from_hf(qc: dict) -> QuantSpec:
+    """Map a ``quantization_config`` block to a QuantSpec (reference: ``models/quantization.py:79-124``)."""
+    if not qc:
+        return QuantSpec(method="none", bits=16, group_size=0)
+    method = qc.get("quant_method", "")
+    fmt = qc.get("format", "")
+    if method == "cubic" or fmt == "cubic-pack-quantized":
+        w = _first_group_weights(qc)
+        gs = w.get("group_size", 128)
+        return QuantSpec("cubic", int(w.get("num_bits", 4)), int(gs[1] if isinstance(gs, list) else gs))
+    if method == "awq":
+        return QuantSpec("awq", int(qc.get("bits", 4)), int(qc.get("group_size", 128)))
+    if method == "gguf":
+        return QuantSpec("gguf", 4, 256)
+    if fmt == "pack-quantized":
+        w = _first_group_weights(qc)
+        return QuantSpec("int", int(w.get("num_bits", 4)), int(w.get("group_size") or 0))
+    if fmt == "float-quantized":
+        w = _first_group_weights(qc)
+        block = w.get("block_structure") or qc.get("weight_block_size")
+        return QuantSpec("fp8_block" if block else "fp8", 8, 128 if block else 0)
+    if fmt == "nvfp4-pack-quantized" or qc.get("quant_algo") == "NVFP4" or method == "modelopt":
+        return QuantSpec("nvfp4", 4, 16)
+    if method == "fp8":
+        return QuantSpec("fp8_block" if qc.get("weight_block_size") else "fp8", 8, 128)
+    raise ValueError(f"unsupported quantization_config: {method or fmt!r}")
+
+
+def _first_group_weights(qc: dict) -> dict:
+    groups = qc.get("config_groups") or {}
+    for g in groups.values():
+        if isinstance(g, dict) and isinstance(g.get("weights"), dict):
+            return g["weights"]
+    return qc
+
+
+# ----------------------------------------------------------------- named configs
+def toy_config() -> ModelConfig:
+    """CPU toy decoder: 2 layers, hidden 256, 4q/2kv heads of 64, FFN 512, vocab 1024."""
+    return ModelConfig(name="toy", num_layers=2, hidden_size=256, num_q_heads=4, num_kv_heads=2, head_dim=64,
+                       intermediate_size=512, vocab_size=1024, rope_theta=10000.0, rms_eps=1e-6)
+
+
+def dense_8b_config() -> ModelConfig:
+    return ModelConfig(name="dense-8b", num_layers=36, hidden_size=4096, num_q_heads=32, num_kv_heads=8,
+                       head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6, rms_eps=1e-6,
+                       quant=QuantSpec("cubic", 4, 128))
+
+
+def moe_30b_config() -> ModelConfig:
+    return ModelConfig(name="moe-30b-a3b", family="gqa_moe", num_layers=48, hidden_size=2048, num_q_heads=32,
+                       num_kv_heads=4, head_dim=128, intermediate_size=0, vocab_size=151936, rope_theta=1e6,
+                       num_experts=128, experts_per_token=8, moe_intermediate_size=768,
+                       quant=QuantSpec("nvfp4", 4, 16))
+
+
+def moe_235b_config() -> ModelConfig:
+    return ModelConfig(name="moe-235b-a22b", family="gqa_moe", num_layers=94, hidden_size=4096, num_q_heads=64,
+                       num_kv_heads=4, head_dim=128, intermediate_size=0, vocab_size=151936, rope_theta=1e6,
+                       num_experts=128, experts_per_token=8, moe_intermediate_size=1536,
+                       quant=QuantSpec("fp8_block", 8, 128))
+
+
+NAMED_CONFIGS = {
+    "toy": toy_config,
+    "dense-8b": dense_8b_config,
+    "moe-30b-a3b": moe_30b_config,
+    "moe-235b-a22b": moe_235b_config,
+}

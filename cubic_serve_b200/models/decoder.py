@@ -1,0 +1,255 @@
+"""GQA decoder executed with the native sm_100a kernels (dense FFN or MoE).
+
+One ``DecoderRunner`` is the per-rank model body: it owns the rank-local packed
+weights, fixed-address activation buffers and the quantized paged KV cache, and
+exposes ``forward(batch)`` which is safe to capture in a CUDA graph (no host
+synchronisation, no allocation).  It corresponds to the reference's captured
+stage body (``executor/quantized_model_runner.py:213``,
+``executor/text_graph.py:126``): norm -> QKV GEMM -> RoPE + KV quantize-on-write
+-> paged attention -> o_proj (+collective) -> norm -> gate/up -> SwiGLU -> down
+(+collective) -> final norm -> lm_head -> sampler.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import wq_pack
+from ..ops.eager import rope_inv_freq
+from ..quantization import cubic
+from .config import ModelConfig
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    qkv: wq_pack.PackedWeight
+    o: wq_pack.PackedWeight
+    gate_up: wq_pack.PackedWeight | None = None
+    down: wq_pack.PackedWeight | None = None
+    q_norm: torch.Tensor | None = None
+    k_norm: torch.Tensor | None = None
+    moe: object | None = None
+
+
+@dataclass
+class DecoderWeights:
+    embed: torch.Tensor                     # [V(/tp), H] bf16
+    layers: list[LayerWeights]
+    final_norm: torch.Tensor
+    lm_head: wq_pack.PackedWeight           # [V(/tp), H]
+    vocab_start: int = 0
+    extras: dict = field(default_factory=dict)
+
+    def nbytes(self) -> int:
+        total = self.embed.numel() * 2 + self.lm_head.nbytes
+        for l in self.layers:
+            for w in (l.qkv, l.o, l.gate_up, l.down):
+                if w is not None:
+                    total += w.nbytes
+        return total
+
+
+def quantize_linear(w: torch.Tensor, cfg: ModelConfig) -> wq_pack.PackedWeight:
+    """Quantize a dense ``[N, K]`` matrix with the config's weight format and re-tile it for the GEMM."""
+    q = cfg.quant
+    if q.method == "none":
+        return wq_pack.pack_bf16(w)
+    if q.method == "cubic":
+        if q.bits != 4:
+            raise NotImplementedError("the tcgen05 GEMM consumes 4-bit Cubic codes")
+        scheme = cubic.CubicScheme(bits=4, group_in=q.group_size)
+        out_codes, sc, aa, bb = [], [], [], []
+        for r0 in range(0, w.shape[0], 8192):  # bounded temporaries
+            p = cubic.quantize(w[r0:r0 + 8192], scheme)
+            out_codes.append(cubic.unpack_codes(p["weight_packed"], 4, w.shape[1]))
+            sc.append(p["weight_scale"]); aa.append(p["weight_a"]); bb.append(p["weight_b"])
+        return wq_pack.pack_cubic4(torch.cat(out_codes), torch.cat(sc), torch.cat(aa), torch.cat(bb), q.group_size)
+    if q.method in ("int", "awq", "gguf"):
+        g = q.group_size if q.method != "gguf" else 32
+        n, k = w.shape
+        wg = w.float().reshape(n, k // g, g)
+        lo, hi = wg.amin(-1), wg.amax(-1)
+        scale = ((hi - lo) / 15.0).clamp_min(1e-8)
+        qv = torch.round((wg - lo[..., None]) / scale[..., None]).clamp(0, 15).to(torch.uint8).reshape(n, k)
+        return wq_pack.pack_affine4(qv, scale, lo, g)
+    if q.method == "nvfp4":
+        from ..quantization import nvfp4
+        payload = nvfp4.quantize(w)
+        return wq_pack.pack_nvfp4(payload["weight_packed"], payload["weight_scale"].float(),
+                                  1.0 / float(payload["weight_global_scale"]))
+    raise NotImplementedError(f"weight format {q.method}")
+
+
+def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                           std: float = 0.02) -> DecoderWeights:
+    """Random-init N(0, std) weights, quantized offline into the config's format, rank-local TP shards.
+
+    Column-parallel: QKV (whole heads per rank), gate/up; row-parallel: o_proj,
+    down; vocab-sharded embedding and lm_head (reference ownership planners:
+    ``models/parallel_weights.py:72-352``).
+    """
+    assert cfg.num_q_heads % tp_size == 0 and cfg.num_kv_heads % tp_size == 0
+    gen = torch.Generator(device=device).manual_seed(seed * 1000 + tp_rank)
+    H, D = cfg.hidden_size, cfg.head_dim
+    hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
+    inter = cfg.intermediate_size // tp_size
+
+    def rnd(n, k):
+        return torch.randn(n, k, device=device, generator=gen, dtype=torch.float32) * std
+
+    def norm_w():
+        return torch.ones(H, device=device, dtype=torch.bfloat16)
+
+    layers = []
+    for _ in range(cfg.num_layers):
+        lw = LayerWeights(
+            ln1=norm_w(), ln2=norm_w(),
+            qkv=quantize_linear(rnd((hq + 2 * hkv) * D, H), cfg),
+            o=quantize_linear(rnd(H, hq * D), cfg),
+        )
+        if cfg.qk_norm:
+            lw.q_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
+            lw.k_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
+        if cfg.is_moe:
+            from .moe import random_moe_weights
+            lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std)
+        else:
+            lw.gate_up = quantize_linear(rnd(2 * inter, H), cfg)
+            lw.down = quantize_linear(rnd(H, inter), cfg)
+        layers.append(lw)
+    v_local = cfg.vocab_size // tp_size
+    embed = (torch.randn(v_local, H, device=device, generator=gen) * std).to(torch.bfloat16)
+    if cfg.tie_embeddings:
+        head = embed
+    else:
+        head = (torch.randn(v_local, H, device=device, generator=gen) * std).to(torch.bfloat16)
+    lm_head = quantize_linear(head.float(), cfg) if cfg.quant.lm_head_quantized else wq_pack.pack_bf16(head)
+    return DecoderWeights(embed=embed, layers=layers, final_norm=norm_w(), lm_head=lm_head,
+                          vocab_start=tp_rank * v_local)
+
+
+@dataclass
+class StepBatch:
+    """Device-side, fixed-address inputs of one forward step (filled by the executor)."""
+    num_tokens: int
+    num_row_blocks: int
+    num_logit_rows: int
+    token_ids: torch.Tensor      # int32 [T]
+    positions: torch.Tensor      # int32 [T]
+    slots: torch.Tensor          # int32 [T]  page*16 + offset, -1 = padding row
+    page_table: torch.Tensor     # int32 [R, max_pages]
+    rb_req: torch.Tensor         # int32 [RB]
+    rb_qstart: torch.Tensor
+    rb_qcount: torch.Tensor
+    rb_ctx: torch.Tensor
+    logit_rows: torch.Tensor     # int64 [R] rows of the hidden state that feed lm_head
+    attn_splits: int = 1
+
+
+class DecoderRunner:
+    def __init__(self, cfg: ModelConfig, weights: DecoderWeights, num_pages: int, max_tokens: int,
+                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None) -> None:
+        self.cfg = cfg
+        self.w = weights
+        self.device = device or weights.embed.device
+        self.tp = tp
+        self.tp_size = tp.size if tp is not None else 1
+        self.k_bits, self.v_bits = k_bits, v_bits
+        self.hq = cfg.num_q_heads // self.tp_size
+        self.hkv = cfg.num_kv_heads // self.tp_size
+        self.D = cfg.head_dim
+        self.max_tokens = max_tokens
+        H = cfg.hidden_size
+        dev = self.device
+        blob = K.kv_blob_bytes(self.D, k_bits, v_bits)
+        self.num_pages = num_pages
+        # one cache tensor per layer: [pages, kv_heads, blob]; zero-filled so that
+        # never-written slots hold finite scales
+        self.kv = [torch.zeros(num_pages, self.hkv, blob, dtype=torch.uint8, device=dev)
+                   for _ in range(cfg.num_layers)]
+        self.inv_freq = rope_inv_freq(cfg.rotary_dim or self.D, cfg.rope_theta, dev)
+        bf = torch.bfloat16
+        T = max_tokens
+        self.h = torch.empty(T, H, dtype=bf, device=dev)           # residual stream
+        self.x = torch.empty(T, H, dtype=bf, device=dev)           # normed activations
+        self.qkv = torch.empty(T, (self.hq + 2 * self.hkv) * self.D, dtype=bf, device=dev)
+        self.q = torch.empty(T, self.hq * self.D, dtype=bf, device=dev)
+        self.attn = torch.empty(T, self.hq * self.D, dtype=bf, device=dev)
+        self.part = torch.empty(T, H, dtype=bf, device=dev)        # row-parallel partial sums (TP > 1)
+        inter = (cfg.intermediate_size // self.tp_size) if not cfg.is_moe else 0
+        self.gu = torch.empty(T, 2 * inter, dtype=bf, device=dev) if inter else None
+        self.act = torch.empty(T, inter, dtype=bf, device=dev) if inter else None
+        self.ws = K.workspace(dev)
+        self.launches_per_step = 0
+
+    # ---------------------------------------------------------------- forward
+    def forward_hidden(self, b: StepBatch) -> torch.Tensor:
+        """Run all layers for ``b.num_tokens`` rows; returns the residual stream view ``[T, H]``."""
+        cfg, w = self.cfg, self.w
+        T = b.num_tokens
+        h, x = self.h[:T], self.x[:T]
+        qkv, q, attn = self.qkv[:T], self.q[:T], self.attn[:T]
+        n = 0
+        K.embedding(b.token_ids[:T], w.embed, out=h, vocab_start=w.vocab_start)
+        n += 1
+        if self.tp is not None:
+            self.tp.all_reduce(h)
+        pending = None  # partial sum waiting to be folded into h by the next norm (TP > 1)
+        for li, lw in enumerate(w.layers):
+            K.rmsnorm(pending if pending is not None else h, lw.ln1, cfg.rms_eps, out=x,
+                      residual=h if pending is not None else None, zero_centered=cfg.zero_centered_norm)
+            K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
+            K.rope_kv_write(qkv, q, self.kv[li], b.positions, b.slots, self.inv_freq, self.hq, self.hkv, self.D,
+                            self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
+                            rotary_dim=cfg.rotary_dim)
+            K.paged_attention(q.view(T, self.hq, self.D), attn.view(T, self.hq, self.D), self.kv[li], b.page_table,
+                              b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, self.hq, self.hkv,
+                              self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)
+            n += 4
+            if self.tp is None:
+                K.wq_gemm(attn, lw.o, out=h, residual=h, ws=self.ws)
+                K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x, zero_centered=cfg.zero_centered_norm)
+            else:
+                part = self.part[:T]
+                K.wq_gemm(attn, lw.o, out=part, ws=self.ws)
+                self.tp.all_reduce(part)
+                K.rmsnorm(part, lw.ln2, cfg.rms_eps, out=x, residual=h, zero_centered=cfg.zero_centered_norm)
+            n += 2
+            if lw.moe is not None:
+                out = lw.moe.forward(x, self)  # returns the (partial) FFN output [T, H]
+                n += lw.moe.launches
+                if self.tp is None:
+                    h.add_(out)
+                    pending = None
+                else:
+                    self.tp.all_reduce(out)
+                    pending = out
+            else:
+                gu, act = self.gu[:T], self.act[:T]
+                K.wq_gemm(x, lw.gate_up, out=gu, ws=self.ws)
+                K.swiglu(gu, out=act)
+                n += 3
+                if self.tp is None:
+                    K.wq_gemm(act, lw.down, out=h, residual=h, ws=self.ws)
+                else:
+                    part = self.part[:T]
+                    K.wq_gemm(act, lw.down, out=part, ws=self.ws)
+                    self.tp.all_reduce(part)
+                    pending = part
+        if pending is not None:
+            h.add_(pending)
+        self.launches_per_step = n
+        return h
+
+    def forward_logits(self, b: StepBatch, hidden: torch.Tensor, logits_out: torch.Tensor) -> torch.Tensor:
+        """Final norm + lm_head for the selected rows -> bf16 logits ``[R, V(/tp)]``."""
+        R = b.num_logit_rows
+        rows = torch.index_select(hidden, 0, b.logit_rows[:R])
+        xn = K.rmsnorm(rows, self.w.final_norm, self.cfg.rms_eps, zero_centered=self.cfg.zero_centered_norm)
+        K.wq_gemm(xn, self.w.lm_head, out=logits_out[:R], ws=self.ws)
+        self.launches_per_step += 2
+        return logits_out[:R]

@@ -31,7 +31,7 @@ class Workspace:
     ``status`` collects device-side error codes and is polled by ``check_status``.
     """
 
-    def __init__(self, device: torch.device, gemm_bytes: int = 64 << 20, attn_floats: int = 0,
+    def __init__(self, device: torch.device, gemm_bytes: int = 64 << 20, attn_floats: int = 4 << 20,
                  counters: int = 1 << 16) -> None:
         self.device = device
         self.gemm = torch.empty(gemm_bytes, dtype=torch.uint8, device=device)
@@ -39,9 +39,12 @@ class Workspace:
         self.gemm_counters = torch.zeros(counters, dtype=torch.int32, device=device)
         self.attn_counters = torch.zeros(counters, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._retired: list[torch.Tensor] = []
 
     def ensure_attn(self, floats: int) -> None:
         if floats > self.attn.numel():
+            # captured graphs may hold the old address: retire, never free
+            self._retired.append(self.attn)
             self.attn = torch.empty(floats, dtype=torch.float32, device=self.device)
 
     def check_status(self) -> None:

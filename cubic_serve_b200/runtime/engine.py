@@ -1,0 +1,136 @@
+"""The synchronous serving engine: scheduler + page pool + an executor.
+
+``LLMEngine.step()`` is one iteration of the reference's dispatch loop
+(``runtime/performance.py:10519`` ``_dispatch`` -> ``_next_batch_locked`` ->
+worker replay -> ``_receive_batch`` commit), without the process boundary: the
+async front end (``runtime/async_engine.py``) drives it from a dispatcher thread.
+The executor is anything with ``execute(segments) -> token ids`` and
+``copy_pages(pairs)``: the native GPU executor, the tensor-parallel group
+executor, or the eager CPU executor.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass
+
+from ..executor.gpu_executor import Segment
+from .cache.pool import PagePool
+from .cache.prefix import PrefixCache
+from .scheduler import (AdmissionError, BatchPlan, ContinuousScheduler, FinishReason, Request, RequestStatus,
+                        SamplingParams, SchedulerConfig)
+
+
+@dataclass
+class StepOutput:
+    request_id: str
+    token_id: int | None
+    finished: bool
+    finish_reason: FinishReason | None = None
+
+
+class EnginePoisoned(RuntimeError):
+    """A step failed; the engine fails closed (reference: ``performance.py:10991-11016``)."""
+
+
+class LLMEngine:
+    def __init__(self, executor, num_pages: int, scheduler_config: SchedulerConfig | None = None,
+                 eos_token_id: int | None = None) -> None:
+        self.executor = executor
+        self.cfg = scheduler_config or SchedulerConfig()
+        self.pool = PagePool(num_pages)
+        self.prefix = PrefixCache(self.pool, enabled=self.cfg.enable_prefix_cache)
+        self.scheduler = ContinuousScheduler(self.cfg, self.pool, self.prefix)
+        self.eos_token_id = eos_token_id
+        self._ids = itertools.count()
+        self.requests: dict[str, Request] = {}
+        self.poisoned = False
+        self.steps = 0
+        self.generated_tokens = 0
+        self.prefill_tokens = 0
+        self.last_step_seconds = 0.0
+
+    # ------------------------------------------------------------------ API
+    def add_request(self, prompt_token_ids: list[int], sampling: SamplingParams | None = None,
+                    request_id: str | None = None) -> str:
+        if self.poisoned:
+            raise EnginePoisoned("engine is poisoned")
+        rid = request_id or f"req-{next(self._ids)}"
+        if rid in self.requests:
+            raise AdmissionError(f"duplicate request id {rid}")
+        if len(self.scheduler.waiting) + len(self.scheduler.running) >= 4 * self.cfg.max_running_requests:
+            raise AdmissionError("too many queued requests", status=429)
+        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams())
+        self.scheduler.add(req)
+        self.requests[rid] = req
+        return rid
+
+    def abort(self, request_id: str) -> bool:
+        r = self.scheduler.abort(request_id)
+        self.requests.pop(request_id, None)
+        return r is not None
+
+    @property
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work
+
+    def step(self) -> list[StepOutput]:
+        if self.poisoned:
+            raise EnginePoisoned("engine is poisoned")
+        t0 = time.perf_counter()
+        plan = self.scheduler.next_plan()
+        if plan is None:
+            return []
+        try:
+            outputs = self._run(plan)
+        except Exception:
+            self.poisoned = True
+            self.pool.poison()
+            raise
+        self.last_step_seconds = time.perf_counter() - t0
+        self.steps += 1
+        return outputs
+
+    def _run(self, plan: BatchPlan) -> list[StepOutput]:
+        if plan.copies:
+            self.executor.copy_pages(plan.copies)
+        segs = []
+        for s in plan.segments:
+            r = s.request
+            toks = r.tokens[s.start:s.start + s.count]
+            sp = r.sampling
+            segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
+                                sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF, r.draws))
+        ids = self.executor.execute(segs) if segs else []
+        sampled = {}
+        it = iter(ids)
+        for s in plan.segments:
+            if s.sample:
+                sampled[s.request.request_id] = int(next(it))
+            else:
+                self.prefill_tokens += s.count
+        finished = {r.request_id: r for r in self.scheduler.commit(plan, sampled, self.eos_token_id)}
+        outs = []
+        for s in plan.segments:
+            if not s.sample:
+                continue
+            rid = s.request.request_id
+            self.generated_tokens += 1
+            fin = finished.get(rid)
+            outs.append(StepOutput(rid, sampled[rid], fin is not None, fin.finish_reason if fin else None))
+            if fin is not None:
+                self.requests.pop(rid, None)
+        return outs
+
+    def generate(self, prompts: list[list[int]], sampling: SamplingParams | None = None) -> list[list[int]]:
+        """Blocking helper: run all prompts to completion, return the generated ids per prompt."""
+        ids = [self.add_request(p, SamplingParams(**vars(sampling)) if sampling else None) for p in prompts]
+        reqs = [self.requests[i] for i in ids]
+        while self.has_unfinished:
+            self.step()
+        return [r.output for r in reqs]
+
+    def stats(self) -> dict:
+        s = self.scheduler.stats()
+        s.update(steps=self.steps, generated_tokens=self.generated_tokens, prefill_tokens=self.prefill_tokens)
+        return s
