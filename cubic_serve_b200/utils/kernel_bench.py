@@ -1,0 +1,120 @@
+"""Micro-benchmarks of single native kernels (CUDA-event timed) -- also the small cases used for ncu captures.
+
+Examples::
+
+    python -m cubic_serve_b200.utils.kernel_bench gemm --m 256 --n 24576 --k 4096
+    python -m cubic_serve_b200.utils.kernel_bench attn --rows 256 --ctx 1280
+    python -m cubic_serve_b200.utils.kernel_bench sweep
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from ..ops import eager, kernels as K, wq_pack
+
+DEV = "cuda"
+
+
+def timeit(fn, iters: int = 20, warmup: int = 5, flush: torch.Tensor | None = None) -> float:
+    """Median milliseconds per call, CUDA events on the launching stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def random_cubic_weight(n: int, k: int, group: int = 128) -> wq_pack.PackedWeight:
+    """Random codes with unit-ish curve metadata directly in packed form (no quantizer pass)."""
+    nt, kb, g = (n + 127) // 128, k // 64, k // group
+    codes = torch.randint(0, 256, (nt, kb, 2, 128, 16), dtype=torch.uint8, device=DEV)
+    meta = torch.zeros(nt, g, 2, 128, dtype=torch.int32, device=DEV)
+    meta[:, :, 0] = torch.full((1,), 0.02, device=DEV).view(torch.int32)
+    meta[:, :, 1] = torch.tensor([0.75, 0.25], dtype=torch.float16, device=DEV).view(torch.int32)
+    return wq_pack.PackedWeight(wq_pack.FMT_CUBIC4, n, k, group, codes, meta.view(torch.uint8).reshape(nt, g, 2, 128, 4))
+
+
+def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str = "cubic4") -> dict:
+    if fmt == "bf16":
+        w = wq_pack.pack_bf16(torch.randn(n, k, device=DEV) * 0.02)
+        wbytes = n * k * 2
+    else:
+        w = random_cubic_weight(n, k)
+        wbytes = n * k // 2 + n * (k // 128) * 8
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    y = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    ms = timeit(lambda: K.wq_gemm(x, w, out=y, splits=splits), iters=iters, warmup=min(5, iters), flush=flush)
+    K.workspace(torch.device(DEV)).check_status()
+    return {"op": f"wq_gemm[{fmt}]", "m": m, "n": n, "k": k, "splits": splits or K.choose_splits(m, n, k),
+            "us": round(ms * 1e3, 1), "tflops": round(2 * m * n * k / ms / 1e9, 1),
+            "weight_gbs": round(wbytes / ms / 1e6, 1)}
+
+
+def bench_attn(rows: int, ctx: int, hq: int, hkv: int, kb: int, vb: int, splits: int, iters: int) -> dict:
+    d = 128
+    pages_per = -(-ctx // 16)
+    blob = K.kv_blob_bytes(d, kb, vb)
+    cache = torch.randint(0, 255, (rows * pages_per + 1, hkv, blob), dtype=torch.uint8, device=DEV)
+    lay = eager.blob_layout(d, kb, vb)
+    one = torch.full((64,), 0.01, device=DEV).view(torch.uint8)
+    cache[:, :, lay["k_scale"]:lay["v_code"]] = one
+    cache[:, :, lay["v_scale"]:] = one
+    table = (torch.randperm(rows * pages_per, device=DEV).to(torch.int32) + 1).view(rows, pages_per)
+    q = torch.randn(rows, hq, d, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    ar = torch.arange(rows, dtype=torch.int32, device=DEV)
+    ones, ctxs = torch.ones_like(ar), torch.full_like(ar, ctx)
+    ms = timeit(lambda: K.paged_attention(q, out, cache, table, ar, ar, ones, ctxs, hq, hkv, d, kb, vb, splits=splits),
+                iters=iters, warmup=min(5, iters))
+    K.workspace(torch.device(DEV)).check_status()
+    kv_bytes = rows * pages_per * hkv * blob
+    return {"op": f"paged_attn[k{kb}v{vb}]", "rows": rows, "ctx": ctx, "hq": hq, "hkv": hkv, "splits": splits,
+            "us": round(ms * 1e3, 1), "kv_gbs": round(kv_bytes / ms / 1e6, 1)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["gemm", "attn", "sweep"])
+    ap.add_argument("--m", type=int, default=256)
+    ap.add_argument("--n", type=int, default=24576)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--fmt", default="cubic4")
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--rows", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=1280)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--kbits", type=int, default=8)
+    ap.add_argument("--vbits", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    if a.op == "gemm":
+        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.splits or None, a.iters, a.fmt)))
+    elif a.op == "attn":
+        print(json.dumps(bench_attn(a.rows, a.ctx, a.hq, a.hkv, a.kbits, a.vbits, max(1, a.splits), a.iters)))
+    else:
+        for m in (16, 64, 256, 512):
+            for n, k in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)):
+                print(json.dumps(bench_gemm(m, n, k, None, a.iters)), flush=True)
+        print(json.dumps(bench_gemm(256, 151936, 4096, None, a.iters, "bf16")), flush=True)
+        for kb, vb in ((8, 8), (4, 8), (4, 4)):
+            print(json.dumps(bench_attn(256, 1280, 32, 8, kb, vb, 1, a.iters)), flush=True)
+        print(json.dumps(bench_attn(8, 4096, 32, 8, 8, 8, 8, a.iters)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -142,7 +142,8 @@ def test_rope_kv_write_roundtrip(kb, vb):
             # one code step of slack where rounding sits on a tie after bf16 effects
             assert (kk[off] - kd[tok, h]).abs().max() <= ksc[tok, h].max() * 1.01
             assert _rel(kk[off], kd[tok, h]) < (0.02 if kb == 8 else 0.2)
-            assert _rel(vv[off], vd[tok, h]) < 1e-6
+            assert (vv[off] - vd[tok, h]).abs().max() <= vsc[tok, h].max() * 1.01
+            assert _rel(vv[off], vd[tok, h]) < (0.01 if vb == 8 else 0.1)
 
 
 def _fill_cache_random(cache, t_total, hkv, d, kb, vb, page_ids, seed=0):
