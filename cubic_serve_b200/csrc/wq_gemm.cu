@@ -21,13 +21,15 @@
 //
 // Packed weight storage is produced at load time by ops/wq_pack.py:
 //   codes  [n_tile][k_block][half h(2)][row r(128)][16 bytes]   (4096 B per stage)
-//          word j (0..3) nibble i (0..7) of those 16 bytes is k = 32h + 8j + i,
+//          word j (0..3) of those 16 bytes covers columns 32h + 8j .. + 7; its
+//          nibble i (i < 4) is column 2i, nibble i + 4 is column 2i + 1; codes are
 //          stored offset-binary (code + 8; the reserved most-negative code -> 8).
 //   meta   [n_tile][meta_block][2][128] 32-bit words            (1024 B per block)
-//          CUBIC4 : word0 = scale (fp32), word1 = half2(a, b); one block per K group
-//          AFFINE4: word h = half2(scale, offset) of 32-column sub-block h of the
-//                   k-block; w = code * scale + offset; one block per k-block
-//          NVFP4  : word h = half2(block scale of columns 32h..32h+15, ..+16..31)
+//          CUBIC4 : word0 = bf16x2(A, B), word1 = bf16x2(C, 0) with A = s*a/7,
+//                   B = s*b/49, C = s*(1-a-b)/343; one block per K group
+//          AFFINE4: word h = bf16x2(scale, offset + 8*scale) of 32-column sub-block h
+//                   of the k-block; w = (code - 8) * scale + that; one block per k-block
+//          NVFP4  : word h = bf16x2(block scale of columns 32h..32h+15, ..+16..31)
 #include "ptx.cuh"
 #include <cuda.h>
 
@@ -73,61 +75,75 @@ struct __align__(8) SmemCtl {
   uint32_t is_last;
 };
 
+// ---- packed bf16x2 decode ---------------------------------------------------
+// A 32-bit word holds 8 codes; nibble i (i < 4) is column 2i and nibble i + 4 is
+// column 2i + 1 of the 8-column chunk, so ONE mask pulls an adjacent column pair
+// into the two halves of a register:  ((w >> 4i) & 0x000F000F) | 0x43004300 is
+// the bf16 pair (128 + n_lo, 128 + n_hi).  All arithmetic then runs two weights
+// per instruction on the FMA pipe and produces bf16 directly -- no float -> bf16
+// conversion (those run on the quarter-rate XU pipe and were the bottleneck of
+// an fp32 formulation: 87 % XU utilisation in the first profile).
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_dup(uint32_t lo16) { return (lo16 & 0xFFFFu) * 0x00010001u; }
+
 template <int FMT>
-__device__ __forceinline__ void decode8(uint32_t w, float c0, float c1, float c2, uint32_t (&out)[4]);
+__device__ __forceinline__ void decode8(uint32_t w, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t (&out)[4]);
 
 template <>
-__device__ __forceinline__ void decode8<kFmtBf16>(uint32_t, float, float, float, uint32_t (&)[4]) {}
+__device__ __forceinline__ void decode8<kFmtBf16>(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t (&)[4]) {}
 
-// CUBIC4: offset-binary nibble n -> c = n - 8;  w = c * (A + |c| * (B + |c| * C))
+// CUBIC4: c = n - 8;  w = c * (A + |c| * (B + |c| * C)),  A/B/C broadcast bf16x2
 template <>
-__device__ __forceinline__ void decode8<kFmtCubic4>(uint32_t w, float A, float B, float C,
+__device__ __forceinline__ void decode8<kFmtCubic4>(uint32_t w, uint32_t A, uint32_t B, uint32_t C,
                                                     uint32_t (&out)[4]) {
-  float v[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t bits = ((w >> (4 * i)) & 0xFu) | 0x4B000000u;  // 2^23 + n
-    float c = __uint_as_float(bits) - 8388616.0f;            // n - 8
-    float m = fabsf(c);
-    float p = fmaf(m, C, B);
-    p = fmaf(m, p, A);
-    v[i] = c * p;
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;  // 128 + n
+    const uint32_t c = bf2_sub(x, 0x43084308u);                        // n - 8 (exact)
+    const uint32_t m = c & 0x7FFF7FFFu;                                // |c|
+    uint32_t p = bf2_fma(m, C, B);
+    p = bf2_fma(m, p, A);
+    out[i] = bf2_mul(c, p);
   }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
 }
 
-// AFFINE4: w = n * scale + offset  (offset already folds the zero point)
+// AFFINE4: w = (n - 8) * scale + offset8   (offset8 = offset + 8 * scale, small in magnitude)
 template <>
-__device__ __forceinline__ void decode8<kFmtAffine4>(uint32_t w, float scale, float offset, float,
+__device__ __forceinline__ void decode8<kFmtAffine4>(uint32_t w, uint32_t scale, uint32_t offset8, uint32_t,
                                                      uint32_t (&out)[4]) {
-  float v[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t bits = ((w >> (4 * i)) & 0xFu) | 0x4B000000u;
-    float n = __uint_as_float(bits) - 8388608.0f;
-    v[i] = fmaf(n, scale, offset);
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+    out[i] = bf2_fma(bf2_sub(x, 0x43084308u), scale, offset8);
   }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
 }
 
-// NVFP4: nibble = sign(1) exp(2) man(1).  Placing exp|man at fp32 bits 24..22
-// and multiplying by 2^126 yields {0,.5,1,1.5,2,3,4,6} exactly (the e=0 codes
-// become fp32 subnormals, which the multiply normalises).
+// NVFP4: nibble = sign(1) exp(2) man(1).  exp|man placed at bf16 bits 8..6 and
+// multiplied by 2^126 gives {0,.5,1,1.5,2,3,4,6} exactly (exp = 0 codes are bf16
+// subnormals that the multiply normalises); then one multiply by the block scale.
 template <>
-__device__ __forceinline__ void decode8<kFmtNvfp4>(uint32_t w, float scale, float, float,
+__device__ __forceinline__ void decode8<kFmtNvfp4>(uint32_t w, uint32_t scale, uint32_t, uint32_t,
                                                    uint32_t (&out)[4]) {
-  float v[8];
-  const float rebias = __uint_as_float(0x7E800000u);  // 2^126
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t nib = (w >> (4 * i)) & 0xFu;
-    uint32_t bits = ((nib & 7u) << 22) | ((nib & 8u) << 28);
-    v[i] = (__uint_as_float(bits) * rebias) * scale;
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = (w >> (4 * i)) & 0x000F000Fu;
+    const uint32_t bits = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
+    out[i] = bf2_mul(bf2_mul(bits, 0x7E807E80u), scale);
   }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) out[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
 }
 
 template <int FMT>
@@ -238,19 +254,18 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint8_t* pk = st + x_bytes + kATileBytes;
         const uint4 words = *reinterpret_cast<const uint4*>(pk + (h * 128 + r) * 16);
         const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
-        float c0, c1, c2, c1b = 0.f;
+        // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
+        uint32_t c0, c1, c2, c1b = 0;
         if (FMT == kFmtCubic4) {
-          const float sc = __uint_as_float(meta[r]);
-          const __half2 ab = *reinterpret_cast<const __half2*>(&meta[128 + r]);
-          const float a = __low2float(ab), b = __high2float(ab);
-          c0 = sc * a * (1.0f / 7.0f);
-          c1 = sc * b * (1.0f / 49.0f);
-          c2 = sc * (1.0f - a - b) * (1.0f / 343.0f);
+          const uint32_t ab = meta[r], cz = meta[128 + r];
+          c0 = bf2_dup(ab);        // A = s * a / 7
+          c1 = bf2_dup(ab >> 16);  // B = s * b / 49
+          c2 = bf2_dup(cz);        // C = s * (1 - a - b) / 343
         } else {
-          const __half2 so = *reinterpret_cast<const __half2*>(&meta[h * 128 + r]);
-          c0 = __low2float(so);
-          c1 = __high2float(so);
-          c2 = 0.f;
+          const uint32_t so = meta[h * 128 + r];
+          c0 = bf2_dup(so);
+          c1 = bf2_dup(so >> 16);
+          c2 = 0;
           c1b = c1;
         }
         uint8_t* arow = st + x_bytes + (r >> 3) * 1024 + (r & 7) * 128;
@@ -260,7 +275,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           uint32_t o[4];
           if (FMT == kFmtNvfp4) {
             // columns 32h + 8j ..: block scale index (8j)/16 selects low/high half
-            decode8<FMT>(wv[j], (j < 2) ? c0 : c1b, 0.f, 0.f, o);
+            decode8<FMT>(wv[j], (j < 2) ? c0 : c1b, 0u, 0u, o);
           } else {
             decode8<FMT>(wv[j], c0, c1, c2, o);
           }

@@ -34,6 +34,7 @@ class Segment:
     top_k: int = 0
     seed: int = 0
     draw: int = 0
+    uid: int = -1                # identity of the request owning the slot (page-table row reuse detection)
 
 
 class _Staging:
@@ -75,67 +76,102 @@ class _Staging:
         return n
 
 
-class GpuExecutor:
-    def __init__(self, runner: DecoderRunner, max_rows: int = 256, max_prefill_tokens: int = 8192,
-                 max_model_len: int = 4096, use_graphs: bool = True) -> None:
-        self.runner = runner
-        self.cfg = runner.cfg
-        self.device = runner.device
-        self.G = runner.hq // runner.hkv
-        self.qb = 16 // self.G                                  # query positions per attention row block
-        self.max_rows = max_rows
-        self.max_tokens = max(max_prefill_tokens, max_rows)
-        assert self.max_tokens <= runner.max_tokens
-        self.max_pages = -(-max_model_len // K.PAGE_TOKENS)
-        max_rb = max(max_rows, self.max_tokens // self.qb + max_rows)
-        self.stage = _Staging(self.max_tokens, max_rows, max_rb, self.max_pages, self.device)
-        v_local = runner.w.lm_head.n
-        self.logits = torch.empty(max_rows, v_local, dtype=torch.bfloat16, device=self.device)
-        self.out_ids = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=torch.cuda.is_available())
-        self.use_graphs = use_graphs
-        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
-        self.stream = torch.cuda.Stream(device=self.device)
-        self.h2d_bytes_last = 0
-        self.d2h_bytes_last = 0
-        self.kernel_launches_last = 0
-        self.graph_launches = {}
-        self.timing = False              # record device time of the compute part of every step
-        self.device_ms: list[float] = []
-        self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+class BatchBuilder:
+    """Host side of a step: turns segments into the staged metadata arrays (no CUDA calls except the upload)."""
 
-    # ----------------------------------------------------------------- batches
+    def __init__(self, max_rows: int, max_tokens: int, max_model_len: int, group: int, kv_heads: int, device) -> None:
+        self.qb = 16 // group                                   # query positions per attention row block
+        self.kv_heads = kv_heads
+        self.max_rows = max_rows
+        self.max_tokens = max_tokens
+        self.max_pages = -(-max_model_len // K.PAGE_TOKENS)
+        max_rb = max(max_rows, max_tokens // self.qb + max_rows)
+        self.stage = _Staging(max_tokens, max_rows, max_rb, self.max_pages, device)
+        self._page_rows: list[tuple[int, int]] = [(-2, 0)] * max_rows
+
+    def _splits(self, row_blocks: int) -> int:
+        ctas = max(1, row_blocks * self.kv_heads)
+        return int(min(32, max(1, -(-296 // ctas))))
+
+    def fill(self, segs: list[Segment], pad_rows_to: int | None = None):
+        return self._fill(segs, pad_rows_to)
+
+    def _sync_page_row(self, s: Segment) -> None:
+        """Bring row ``request_slot`` of the host page table up to date (only the new tail is written)."""
+        slot = s.request_slot
+        known_uid, known_len = self._page_rows[slot]
+        pages = s.pages
+        n = len(pages)
+        if known_uid != s.uid or s.uid < 0 or n < known_len:
+            self.stage.h["page_table"][slot, :n] = pages
+        elif n > known_len:
+            self.stage.h["page_table"][slot, known_len:n] = pages[known_len:]
+        else:
+            return
+        self._page_rows[slot] = (s.uid, n)
+
+    def invalidate_page_rows(self, slots) -> None:
+        """Force a full rewrite of these page-table rows (used after copy-on-write replaced a page)."""
+        for slot in slots:
+            self._page_rows[slot] = (-2, 0)
+
     def _fill(self, segs: list[Segment], pad_rows_to: int | None = None) -> StepBatch:
         st = self.stage
         h = st.h
-        t = 0
-        rb = 0
-        rows = 0
         qb = self.qb
-        for si, s in enumerate(segs):
-            n = len(s.token_ids)
-            h["token_ids"][t:t + n] = s.token_ids
-            pos = np.arange(s.start, s.start + n, dtype=np.int32)
-            h["positions"][t:t + n] = pos
-            pages = np.asarray(s.pages, dtype=np.int32)
-            h["slots"][t:t + n] = pages[pos >> 4] * 16 + (pos & 15)
-            h["page_table"][si, :len(pages)] = pages
-            nb = -(-n // qb)
-            starts = np.arange(nb, dtype=np.int32) * qb
-            h["rb_req"][rb:rb + nb] = si
-            h["rb_qstart"][rb:rb + nb] = t + starts
-            h["rb_qcount"][rb:rb + nb] = np.minimum(n - starts, qb)
-            h["rb_ctx"][rb:rb + nb] = s.start + starts + 1
-            rb += nb
-            if s.sample:
-                h["logit_rows"][rows] = t + n - 1
-                h["temperature"][rows] = s.temperature
-                h["top_p"][rows] = s.top_p
-                h["top_k"][rows] = s.top_k
-                h["seeds"][rows] = s.seed
-                h["draws"][rows] = s.draw
-                rows += 1
-            t += n
+        for s in segs:
+            self._sync_page_row(s)
+        if all(len(s.token_ids) == 1 for s in segs):
+            # decode fast path: one token, one row block and one sampled row per segment
+            n = len(segs)
+            h["token_ids"][:n] = [s.token_ids[0] for s in segs]
+            starts = np.fromiter((s.start for s in segs), dtype=np.int32, count=n)
+            h["positions"][:n] = starts
+            h["slots"][:n] = [s.pages[s.start >> 4] * 16 + (s.start & 15) for s in segs]
+            h["rb_req"][:n] = [s.request_slot for s in segs]
+            ar = np.arange(n, dtype=np.int32)
+            h["rb_qstart"][:n] = ar
+            h["rb_qcount"][:n] = 1
+            h["rb_ctx"][:n] = starts + 1
+            t = rb = n
+            rows = 0
+            if all(s.sample for s in segs):
+                h["logit_rows"][:n] = ar
+                h["temperature"][:n] = [s.temperature for s in segs]
+                h["top_p"][:n] = [s.top_p for s in segs]
+                h["top_k"][:n] = [s.top_k for s in segs]
+                h["seeds"][:n] = [s.seed for s in segs]
+                h["draws"][:n] = [s.draw for s in segs]
+                rows = n
+            else:
+                for i, s in enumerate(segs):
+                    if s.sample:
+                        h["logit_rows"][rows] = i
+                        h["temperature"][rows], h["top_p"][rows], h["top_k"][rows] = s.temperature, s.top_p, s.top_k
+                        h["seeds"][rows], h["draws"][rows] = s.seed, s.draw
+                        rows += 1
+        else:
+            t = rb = rows = 0
+            for s in segs:
+                n = len(s.token_ids)
+                h["token_ids"][t:t + n] = s.token_ids
+                pos = np.arange(s.start, s.start + n, dtype=np.int32)
+                h["positions"][t:t + n] = pos
+                pages = np.asarray(s.pages, dtype=np.int32)
+                h["slots"][t:t + n] = pages[pos >> 4] * 16 + (pos & 15)
+                nb = -(-n // qb)
+                starts = np.arange(nb, dtype=np.int32) * qb
+                h["rb_req"][rb:rb + nb] = s.request_slot
+                h["rb_qstart"][rb:rb + nb] = t + starts
+                h["rb_qcount"][rb:rb + nb] = np.minimum(n - starts, qb)
+                h["rb_ctx"][rb:rb + nb] = s.start + starts + 1
+                rb += nb
+                if s.sample:
+                    h["logit_rows"][rows] = t + n - 1
+                    h["temperature"][rows], h["top_p"][rows], h["top_k"][rows] = s.temperature, s.top_p, s.top_k
+                    h["seeds"][rows], h["draws"][rows] = s.seed, s.draw
+                    rows += 1
+                t += n
         if pad_rows_to is not None and pad_rows_to > t:
             # decode bucket padding: rows that write nothing and attend to nothing
             p = pad_rows_to
@@ -158,10 +194,37 @@ class GpuExecutor:
                          rb_qstart=d["rb_qstart"], rb_qcount=d["rb_qcount"], rb_ctx=d["rb_ctx"],
                          logit_rows=d["logit_rows"], attn_splits=splits), rows
 
-    def _splits(self, row_blocks: int) -> int:
-        ctas = max(1, row_blocks * self.runner.hkv)
-        return int(min(32, max(1, -(-296 // ctas))))
 
+class GpuExecutor:
+    def __init__(self, runner: DecoderRunner, max_rows: int = 256, max_prefill_tokens: int = 8192,
+                 max_model_len: int = 4096, use_graphs: bool = True) -> None:
+        self.runner = runner
+        self.cfg = runner.cfg
+        self.device = runner.device
+        self.max_rows = max_rows
+        self.max_tokens = max(max_prefill_tokens, max_rows)
+        assert self.max_tokens <= runner.max_tokens
+        self.builder = BatchBuilder(max_rows, self.max_tokens, max_model_len, runner.hq // runner.hkv, runner.hkv,
+                                    self.device)
+        self.stage = self.builder.stage
+        self._fill = self.builder._fill
+        self.invalidate_page_rows = self.builder.invalidate_page_rows
+        v_local = runner.w.lm_head.n
+        self.logits = torch.empty(max_rows, v_local, dtype=torch.bfloat16, device=self.device)
+        self.out_ids = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.use_graphs = use_graphs
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.stream = torch.cuda.Stream(device=self.device)
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+        self.kernel_launches_last = 0
+        self.graph_launches = {}
+        self.timing = False              # record device time of the compute part of every step
+        self.device_ms: list[float] = []
+        self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+
+    # ----------------------------------------------------------------- batches
     # ------------------------------------------------------------------- run
     def _body(self, b: StepBatch) -> None:
         r = self.runner
@@ -180,6 +243,7 @@ class GpuExecutor:
         for cap in sorted(caps, reverse=True):
             dummy = [Segment(0, [0], 0, [0])]
             b, _ = self._fill(dummy, pad_rows_to=cap)
+            self.invalidate_page_rows([0])
             # the warm-up run below must not touch real cache pages: the single real row is turned into padding too
             self.stage.h["slots"][:cap] = -1
             self.stage.h["rb_qcount"][:cap] = 0

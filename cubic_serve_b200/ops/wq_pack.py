@@ -6,8 +6,9 @@ the sm_100a kernel in ``csrc/wq_gemm.cu``:
 
 * ``codes``: ``uint8 [n_tiles, k_blocks, 2, 128, 16]`` -- per (128-row tile,
   64-column k-block) one contiguous 4 KiB block that a single bulk copy moves;
-  nibble ``i`` of 32-bit word ``j`` in row ``r``, half ``h`` is column
-  ``64*kb + 32*h + 8*j + i`` stored offset-binary;
+  32-bit word ``j`` of row ``r``, half ``h`` covers columns ``64*kb + 32*h + 8*j .. +7``;
+  its nibble ``i`` (``i < 4``) is column ``2i`` of those, nibble ``i + 4`` is column
+  ``2i + 1`` (an adjacent column pair comes out with one mask), offset-binary;
 * ``meta``: ``uint8 [n_tiles, meta_blocks, 2, 128, 4]`` -- 1 KiB per block.
 
 All functions are pure tensor code and run on CPU or GPU.
@@ -50,9 +51,25 @@ def _tile_nibbles(nib: torch.Tensor) -> torch.Tensor:
     """``uint8 [N, K]`` values 0..15 -> tiled code bytes (N padded to 128 with `pad` already applied)."""
     n, k = nib.shape
     nt, kb = n // TILE_N, k // BLOCK_K
-    v = nib.reshape(nt, TILE_N, kb, 2, 4, 4, 2).to(torch.int32)   # [nt, r, kb, h, j, byte, lo/hi]
-    byts = (v[..., 0] | (v[..., 1] << 4)).to(torch.uint8)          # [nt, r, kb, h, j, byte]
+    v = nib.reshape(nt, TILE_N, kb, 2, 4, 4, 2).to(torch.int32)   # [nt, r, kb, h, j, pair p, even/odd e]
+    # nibble index inside the word = p + 4*e  ->  byte (p + 4e) // 2, low/high nibble (p + 4e) % 2
+    nibs = v.permute(0, 1, 2, 3, 4, 6, 5).reshape(nt, TILE_N, kb, 2, 4, 4, 2)  # [.., nibble index // 2, nibble index % 2]
+    byts = (nibs[..., 0] | (nibs[..., 1] << 4)).to(torch.uint8)    # [nt, r, kb, h, j, byte]
     return byts.permute(0, 2, 3, 1, 4, 5).contiguous().reshape(nt, kb, 2, TILE_N, 16)
+
+
+def _untile_nibbles(codes: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``_tile_nibbles``: tiled bytes -> ``float [N_pad, K]`` nibble values."""
+    nt, kb = codes.shape[0], codes.shape[1]
+    byts = codes.reshape(nt, kb, 2, TILE_N, 4, 4).permute(0, 3, 1, 2, 4, 5).to(torch.int32)  # [nt, r, kb, h, j, byte]
+    nibs = torch.stack([byts & 15, byts >> 4], -1).reshape(nt, TILE_N, kb, 2, 4, 2, 4)        # [.., e, p]
+    return nibs.permute(0, 1, 2, 3, 4, 6, 5).reshape(nt * TILE_N, kb * BLOCK_K).float()
+
+
+def _bf16_pair_words(lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
+    """Two fp32 tensors -> int32 words holding bf16(lo) in bits 0..15 and bf16(hi) in bits 16..31."""
+    pair = torch.stack([lo.float().to(torch.bfloat16), hi.float().to(torch.bfloat16)], -1).contiguous()
+    return pair.view(torch.int32).reshape(lo.shape)
 
 
 def _pad_rows(t: torch.Tensor, rows: int, value) -> torch.Tensor:
@@ -72,10 +89,11 @@ def pack_cubic4(codes: torch.Tensor, scale: torch.Tensor, a: torch.Tensor, b: to
     nib = _pad_rows((codes.to(torch.int16) + 8).to(torch.uint8), n_pad, 8)
     groups = -(-k // group_k)
     sc = _pad_rows(scale.float().reshape(n, groups), n_pad, 0.0)
-    ab = torch.stack([_pad_rows(a.half().reshape(n, groups), n_pad, 0.0),
-                      _pad_rows(b.half().reshape(n, groups), n_pad, 0.0)], -1)  # [N, G, 2] fp16
-    w0 = sc.view(torch.int32)
-    w1 = ab.contiguous().view(torch.int32).reshape(n_pad, groups)
+    af = _pad_rows(a.float().reshape(n, groups), n_pad, 0.0)
+    bf = _pad_rows(b.float().reshape(n, groups), n_pad, 0.0)
+    # polynomial in the integer code c: w = c * (A + |c| * (B + |c| * C))
+    w0 = _bf16_pair_words(sc * af / 7.0, sc * bf / 49.0)
+    w1 = _bf16_pair_words(sc * (1.0 - af - bf) / 343.0, torch.zeros_like(sc))
     words = torch.stack([w0, w1], 0)                                # [2, N, G]
     nt = n_pad // TILE_N
     meta = words.reshape(2, nt, TILE_N, groups).permute(1, 3, 0, 2).contiguous()  # [nt, G, 2, 128]
@@ -96,10 +114,9 @@ def pack_affine4(q: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, gro
     nib = _pad_rows(q.to(torch.uint8), n_pad, 0)
     groups = -(-k // group_k)
     reps = group_k // 32
-    so = torch.stack([scale.half().reshape(n, groups), offset.half().reshape(n, groups)], -1)  # [N, G, 2]
-    so = _pad_rows(so, n_pad, 0.0)
-    so32 = so.repeat_interleave(reps, dim=1)[:, : k // 32]          # [N, K/32, 2]
-    words = so32.contiguous().view(torch.int32).reshape(n_pad, k // 32)
+    sc = _pad_rows(scale.float().reshape(n, groups), n_pad, 0.0)
+    of = _pad_rows(offset.float().reshape(n, groups), n_pad, 0.0)
+    words = _bf16_pair_words(sc, of + 8.0 * sc).repeat_interleave(reps, dim=1)[:, : k // 32].contiguous()
     nt, kb = n_pad // TILE_N, k // BLOCK_K
     meta = words.reshape(nt, TILE_N, kb, 2).permute(0, 2, 3, 1).contiguous()  # [nt, kb, h, 128]
     return PackedWeight(FMT_AFFINE4, n, k, group_k, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4))
@@ -119,8 +136,8 @@ def pack_nvfp4(packed: torch.Tensor, block_scale: torch.Tensor, global_scale: fl
     p32 = packed.to(torch.int32)
     nib = torch.stack([p32 & 15, p32 >> 4], -1).reshape(n, k).to(torch.uint8)
     nib = _pad_rows(nib, n_pad, 0)
-    bs = _pad_rows(block_scale.float().half().reshape(n, k // 16), n_pad, 0.0)
-    words = bs.reshape(n_pad, k // 32, 2).contiguous().view(torch.int32).reshape(n_pad, k // 32)
+    bs = _pad_rows(block_scale.float().reshape(n, k // 16), n_pad, 0.0).reshape(n_pad, k // 32, 2)
+    words = _bf16_pair_words(bs[..., 0], bs[..., 1])
     nt, kb = n_pad // TILE_N, k // BLOCK_K
     meta = words.reshape(nt, TILE_N, kb, 2).permute(0, 2, 3, 1).contiguous()
     return PackedWeight(FMT_NVFP4, n, k, 16, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4),
@@ -135,30 +152,35 @@ def pack_bf16(weight: torch.Tensor) -> PackedWeight:
 
 
 def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
-    """Oracle: rebuild the fp32 ``[N, K]`` matrix a PackedWeight represents (CPU or GPU)."""
+    """Oracle: rebuild the fp32 ``[N, K]`` matrix a PackedWeight represents, from its packed bytes (CPU or GPU).
+
+    Uses the bf16-rounded metadata exactly as stored but evaluates in fp32, i.e. it is
+    the value the kernel approximates with packed bf16 arithmetic.
+    """
     if pw.fmt == FMT_BF16:
         return pw.codes.float()
-    nt, kb = pw.codes.shape[0], pw.codes.shape[1]
-    byts = pw.codes.reshape(nt, kb, 2, TILE_N, 4, 4).permute(0, 3, 1, 2, 4, 5).to(torch.int32)  # [nt, r, kb, h, j, byte]
-    nib = torch.stack([byts & 15, byts >> 4], -1).reshape(nt * TILE_N, kb * BLOCK_K).float()
+    nt = pw.codes.shape[0]
+    nib = _untile_nibbles(pw.codes)
     n_pad, k = nib.shape
     words = pw.meta.reshape(nt, -1, 2, TILE_N, 4).view(torch.int32).reshape(nt, -1, 2, TILE_N)
+
+    def halves(w):  # int32 words -> (lo, hi) fp32 from bf16 halves
+        pair = w.contiguous().view(torch.bfloat16).reshape(*w.shape, 2).float()
+        return pair[..., 0], pair[..., 1]
+
     if pw.fmt == FMT_CUBIC4:
         g = words.shape[1]
-        scale = words[:, :, 0].permute(0, 2, 1).reshape(n_pad, g).contiguous().view(torch.float32)
-        ab = words[:, :, 1].permute(0, 2, 1).reshape(n_pad, g).contiguous().view(torch.float16).reshape(n_pad, g, 2).float()
+        A, B = halves(words[:, :, 0].permute(0, 2, 1).reshape(n_pad, g))
+        C, _ = halves(words[:, :, 1].permute(0, 2, 1).reshape(n_pad, g))
         col = torch.arange(k, device=nib.device) // pw.group_k
-        s, a, b = scale[:, col], ab[..., 0][:, col], ab[..., 1][:, col]
         c = nib - 8.0
         m = c.abs()
-        A, B, C = s * a / 7.0, s * b / 49.0, s * (1.0 - a - b) / 343.0
-        return (c * (A + m * (B + m * C)))[: pw.n]
-    pair = words.permute(0, 3, 1, 2).reshape(n_pad, -1).contiguous().view(torch.float16).reshape(n_pad, k // 32, 2).float()
+        return (c * (A[:, col] + m * (B[:, col] + m * C[:, col])))[: pw.n]
+    lo, hi = halves(words.permute(0, 3, 1, 2).reshape(n_pad, -1))   # [N, K/32] each
     if pw.fmt == FMT_AFFINE4:
         col = torch.arange(k, device=nib.device) // 32
-        return (nib * pair[..., 0][:, col] + pair[..., 1][:, col])[: pw.n]
-    # NVFP4
+        return ((nib - 8.0) * lo[:, col] + hi[:, col])[: pw.n]
     lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device=nib.device)
-    bs = pair.reshape(n_pad, k // 16)
+    bs = torch.stack([lo, hi], -1).reshape(n_pad, k // 16)
     col = torch.arange(k, device=nib.device) // 16
     return (lut[nib.long()] * bs[:, col] * pw.alpha)[: pw.n]

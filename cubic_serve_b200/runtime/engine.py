@@ -94,13 +94,16 @@ class LLMEngine:
     def _run(self, plan: BatchPlan) -> list[StepOutput]:
         if plan.copies:
             self.executor.copy_pages(plan.copies)
+            if hasattr(self.executor, "invalidate_page_rows"):
+                self.executor.invalidate_page_rows([s.request.slot for s in plan.segments])
         segs = []
         for s in plan.segments:
             r = s.request
             toks = r.tokens[s.start:s.start + s.count]
             sp = r.sampling
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
-                                sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF, r.draws))
+                                sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF, r.draws,
+                                r.arrival))
         ids = self.executor.execute(segs) if segs else []
         sampled = {}
         it = iter(ids)

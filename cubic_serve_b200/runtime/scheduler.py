@@ -69,14 +69,19 @@ class Request:
     slot: int = -1                 # row of the executor's page table
     draws: int = 0                 # sampler draw counter
     preemptions: int = 0
+    tokens: list[int] = field(default_factory=list)   # prompt + output, maintained incrementally
 
-    @property
-    def tokens(self) -> list[int]:
-        return self.prompt + self.output
+    def __post_init__(self) -> None:
+        if not self.tokens:
+            self.tokens = list(self.prompt) + list(self.output)
+
+    def append_output(self, tok: int) -> None:
+        self.output.append(tok)
+        self.tokens.append(tok)
 
     @property
     def num_tokens(self) -> int:
-        return len(self.prompt) + len(self.output)
+        return len(self.tokens)
 
     @property
     def is_prefill(self) -> bool:
@@ -286,13 +291,13 @@ class ContinuousScheduler:
             if r.status is not RequestStatus.RUNNING:
                 continue
             r.num_computed += seg.count
-            full = min(r.num_computed, len(r.tokens)) // BLOCK
-            if full > r.num_published:
+            full = r.num_computed // BLOCK
+            if full > r.num_published and self.prefix.enabled:
                 self.prefix.publish(r.tokens[:full * BLOCK], r.pages[:full])
                 r.num_published = full
             if seg.sample:
                 tok = sampled[r.request_id]
-                r.output.append(tok)
+                r.append_output(tok)
                 r.draws += 1
                 sp = r.sampling
                 stop = tok in sp.stop_token_ids or (eos_token_id is not None and tok == eos_token_id and not sp.ignore_eos)

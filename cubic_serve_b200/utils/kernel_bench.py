@@ -42,8 +42,9 @@ def random_cubic_weight(n: int, k: int, group: int = 128) -> wq_pack.PackedWeigh
     nt, kb, g = (n + 127) // 128, k // 64, k // group
     codes = torch.randint(0, 256, (nt, kb, 2, 128, 16), dtype=torch.uint8, device=DEV)
     meta = torch.zeros(nt, g, 2, 128, dtype=torch.int32, device=DEV)
-    meta[:, :, 0] = torch.full((1,), 0.02, device=DEV).view(torch.int32)
-    meta[:, :, 1] = torch.tensor([0.75, 0.25], dtype=torch.float16, device=DEV).view(torch.int32)
+    s, a, b = 0.02, 0.75, 0.25   # scale and curve -> bf16 polynomial coefficients A, B, C
+    meta[:, :, 0] = torch.tensor([s * a / 7, s * b / 49], dtype=torch.bfloat16, device=DEV).view(torch.int32)
+    meta[:, :, 1] = torch.tensor([s * (1 - a - b) / 343, 0.0], dtype=torch.bfloat16, device=DEV).view(torch.int32)
     return wq_pack.PackedWeight(wq_pack.FMT_CUBIC4, n, k, group, codes, meta.view(torch.uint8).reshape(nt, g, 2, 128, 4))
 
 

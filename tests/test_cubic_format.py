@@ -89,7 +89,8 @@ def test_quantizer_error_and_pack_roundtrip():
     codes = cubic.unpack_codes(p["weight_packed"], 4, 512)
     pw = wq_pack.pack_cubic4(codes, p["weight_scale"], p["weight_a"], p["weight_b"], 128)
     assert pw.codes.shape == (2, 8, 2, 128, 16)
-    assert torch.allclose(wq_pack.unpack_to_dense(pw), d, atol=1e-7)
+    # the packed metadata holds the curve coefficients rounded to bf16
+    assert ((wq_pack.unpack_to_dense(pw) - d).norm() / d.norm()).item() < 4e-3
 
 
 def test_bad_payload_rejected():

@@ -37,9 +37,9 @@ def _cubic_weight(n, k, seed=0, group=128):
 def test_wq_gemm_cubic4(m, n, k, splits):
     K = _k()
     pw, dense = _cubic_weight(n, k, seed=m + n)
-    assert _rel(wq_pack.unpack_to_dense(pw), dense) < 1e-6
+    assert _rel(wq_pack.unpack_to_dense(pw), dense) < 4e-3      # bf16 curve coefficients
     x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
-    ref = x.float() @ dense.to(torch.bfloat16).float().t()
+    ref = x.float() @ dense.t()
     y = K.wq_gemm(x.to(DEV), pw.to(DEV), splits=splits)
     torch.cuda.synchronize()
     K.workspace(y.device).check_status()
@@ -71,7 +71,7 @@ def test_wq_gemm_affine4_and_nvfp4():
     pw = wq_pack.pack_affine4(q, scale, -zero * scale, 64)
     dense = wq_pack.unpack_to_dense(pw)
     expect = (q.float() - zero.repeat_interleave(64, 1)) * scale.half().float().repeat_interleave(64, 1)
-    assert _rel(dense, expect) < 2e-3
+    assert _rel(dense, expect) < 4e-3
     x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16)
     y = K.wq_gemm(x.to(DEV), pw.to(DEV))
     assert _rel(y.cpu(), x.float() @ dense.to(torch.bfloat16).float().t()) < 1e-2
