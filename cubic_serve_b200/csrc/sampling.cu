@@ -64,7 +64,9 @@ struct SampleParams {
   const unsigned long long* counters;  // [rows] per-request draw index
   int* out_ids;                 // [rows]
   float* out_logprob;           // [rows] log-prob of the chosen token within the candidate set (or null)
+  float* out_value;             // [rows] raw logit of the chosen token (or null); used by the vocab-sharded merge
   int vocab, ld, mask_words;
+  int id_offset;                // added to every emitted id (first vocabulary id of this shard)
 };
 
 __global__ void __launch_bounds__(kSampleThreads)
@@ -101,10 +103,16 @@ sample_kernel(const SampleParams p) {
   }
   __syncthreads();
   if (threadIdx.x != 0) return;
-  if (K == 0) { p.out_ids[row] = 0; if (p.out_logprob) p.out_logprob[row] = 0.f; return; }
-  if (temp <= 0.f || K == 1) {
-    p.out_ids[row] = top[0].i;
+  if (K == 0) {
+    p.out_ids[row] = p.id_offset;
     if (p.out_logprob) p.out_logprob[row] = 0.f;
+    if (p.out_value) p.out_value[row] = -INFINITY;
+    return;
+  }
+  if (temp <= 0.f || K == 1) {
+    p.out_ids[row] = top[0].i + p.id_offset;
+    if (p.out_logprob) p.out_logprob[row] = 0.f;
+    if (p.out_value) p.out_value[row] = top[0].v;
     return;
   }
   float probs[kMaxTopK];
@@ -123,8 +131,9 @@ sample_kernel(const SampleParams p) {
   float acc = 0.f;
   int pick = keep - 1;
   for (int k = 0; k < keep; ++k) { acc += probs[k]; if (u < acc) { pick = k; break; } }
-  p.out_ids[row] = top[pick].i;
+  p.out_ids[row] = top[pick].i + p.id_offset;
   if (p.out_logprob) p.out_logprob[row] = __logf(probs[pick] / ksum);
+  if (p.out_value) p.out_value[row] = top[pick].v;
 }
 
 // Greedy speculative verification: per request, row r holds the target's choice
@@ -149,7 +158,7 @@ extern "C" {
 
 int cb_sample(const void* logits, int ld, const void* mask, int mask_words, const void* temperature,
               const void* top_p, const void* top_k, const void* seeds, const void* counters, void* out_ids,
-              void* out_logprob, int rows, int vocab, void* stream) {
+              void* out_logprob, void* out_value, int id_offset, int rows, int vocab, void* stream) {
   using namespace cb;
   if (rows <= 0) return 0;
   SampleParams p;
@@ -162,6 +171,8 @@ int cb_sample(const void* logits, int ld, const void* mask, int mask_words, cons
   p.counters = static_cast<const unsigned long long*>(counters);
   p.out_ids = static_cast<int*>(out_ids);
   p.out_logprob = static_cast<float*>(out_logprob);
+  p.out_value = static_cast<float*>(out_value);
+  p.id_offset = id_offset;
   p.vocab = vocab; p.ld = ld; p.mask_words = mask_words;
   sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return static_cast<int>(cudaGetLastError());

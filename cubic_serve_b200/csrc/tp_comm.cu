@@ -1,0 +1,302 @@
+// Tensor-parallel glue kernels over NVLink peer memory (plain P2P loads/stores,
+// release/acquire flags at system scope, every wait bounded).
+//
+// Together with the scatter-push / gather-wait modes of wq_gemm.cu they replace
+// the reference's "all_gather_single + ordered rank-sum (+ residual + RMSNorm)"
+// sequence (ops/cuda/collective/fixed_rank_sum.py:350-373,596-722) with a
+// reduce-scatter -> norm -> all-gather pipeline that moves the minimum number of
+// bytes over the links and has no NCCL call:
+//
+//   row-parallel GEMM  --(epilogue pushes partial rows to their owner)-->
+//   tp_reduce_norm     : owner waits for all partials, sums them in ASCENDING
+//                        RANK ORDER in fp32 (the reference's determinism
+//                        contract), adds the residual it keeps for its rows,
+//                        applies RMSNorm and pushes the normalised rows to every
+//                        rank's gathered activation buffer
+//   column-parallel GEMM waits for all rows (inside its producer warp).
+//
+// Counters only ever increase; a consumer compares against (epoch + 1) * expected
+// with its own epoch word, so nothing is reset while a peer may still write.
+#include "ptx.cuh"
+
+namespace cb {
+
+static constexpr int kMaxRanksTp = 8;
+
+__device__ __forceinline__ uint32_t ld_acq_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_rel_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acq_sys(p) - target) < 0) {
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+  return true;
+}
+
+struct ReduceNormParams {
+  const __nv_bfloat16* recv;     // local [size][rows_per_rank][H] partial rows, slot = source rank
+  const uint32_t* rs_flag;       // local arrival counters [size]
+  uint32_t* rs_state;            // local {epoch, done CTAs}
+  uint32_t rs_expected;          // arrivals per source per epoch; 0 = nothing to reduce (input is h itself)
+  __nv_bfloat16* h;              // local residual rows [rows_per_rank][H] (read-modify-write)
+  const __nv_bfloat16* norm_w;   // [H]
+  __nv_bfloat16* x_peer[kMaxRanksTp];   // every rank's gathered activations [M_pad][H]
+  uint32_t* ag_flag_peer[kMaxRanksTp];  // every rank's gather arrival counters [size]
+  uint32_t* status;
+  int rank, size, rows_per_rank, H, M;
+  float eps;
+  int zero_centered;
+};
+
+static constexpr int kRnThreads = 256;
+static constexpr int kRnMaxVec = 4;  // H <= 256 * 4 * 8 = 8192
+
+__global__ void __launch_bounds__(kRnThreads)
+tp_reduce_norm_kernel(const ReduceNormParams p) {
+  __shared__ float red[8];
+  __shared__ uint32_t ok_flag;
+  const int row = blockIdx.x;
+  const int m = p.rank * p.rows_per_rank + row;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (p.rs_expected) {
+    if (threadIdx.x < p.size) {
+      const uint32_t target = (p.rs_state[0] + 1u) * p.rs_expected;
+      if (!wait_ge(p.rs_flag + threadIdx.x, target)) ok_flag = 0;
+    }
+    __syncthreads();
+  }
+  const bool ok = ok_flag != 0;
+  const int nvec = p.H >> 3;
+  if (ok && m < p.M) {
+    float vals[kRnMaxVec][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < kRnMaxVec; ++it) {
+      const int v = threadIdx.x + it * kRnThreads;
+      if (v < nvec) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        uint4 hv = reinterpret_cast<const uint4*>(p.h + static_cast<size_t>(row) * p.H)[v];
+        if (p.rs_expected) {
+          for (int r = 0; r < p.size; ++r) {  // ascending rank order, fp32
+            const uint4 pv = __ldcg(reinterpret_cast<const uint4*>(
+                p.recv + (static_cast<size_t>(r) * p.rows_per_rank + row) * p.H) + v);
+            const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&pv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(pp[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+          // bf16(residual + bf16(sum)), the reference's rounding points
+          const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&hv);
+          uint4 ov;
+          __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 s = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
+            const float2 hh = __bfloat1622float2(hp[j]);
+            op[j] = __floats2bfloat162_rn(hh.x + s.x, hh.y + s.y);
+          }
+          reinterpret_cast<uint4*>(p.h + static_cast<size_t>(row) * p.H)[v] = ov;
+          hv = ov;
+        }
+        const __nv_bfloat162* hp2 = reinterpret_cast<const __nv_bfloat162*>(&hv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(hp2[j]);
+          vals[it][2 * j] = f.x;
+          vals[it][2 * j + 1] = f.y;
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    }
+    // block reduction of the sum of squares
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < (kRnThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / static_cast<float>(p.H) + p.eps);
+#pragma unroll
+    for (int it = 0; it < kRnMaxVec; ++it) {
+      const int v = threadIdx.x + it * kRnThreads;
+      if (v < nvec) {
+        const uint4 wv = reinterpret_cast<const uint4*>(p.norm_w)[v];
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        uint4 ov;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 ww = __bfloat1622float2(wp[j]);
+          if (p.zero_centered) { ww.x += 1.f; ww.y += 1.f; }
+          op[j] = __floats2bfloat162_rn(vals[it][2 * j] * inv * ww.x, vals[it][2 * j + 1] * inv * ww.y);
+        }
+        // all-gather by push: the same 16 bytes to every rank's buffer (self included)
+        for (int r = 0; r < p.size; ++r)
+          reinterpret_cast<uint4*>(p.x_peer[r] + static_cast<size_t>(m) * p.H)[v] = ov;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.size) red_rel_sys_add(p.ag_flag_peer[threadIdx.x] + p.rank, 1u);
+  if (threadIdx.x == 0) {
+    if (!ok) atomicExch(p.status, static_cast<uint32_t>(kErrFlagTimeout));
+    if (p.rs_expected) {
+      if (atomicAdd(&p.rs_state[1], 1u) == gridDim.x - 1u) {
+        p.rs_state[1] = 0;
+        __threadfence();
+        atomicAdd(&p.rs_state[0], 1u);
+      }
+    }
+  }
+}
+
+// Stand-alone wait for a gathered buffer (for consumers that are not the GEMM).
+__global__ void tp_wait_kernel(const uint32_t* ag_flag, uint32_t* ag_state, uint32_t expected, int size,
+                               uint32_t* status) {
+  __shared__ uint32_t ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < size) {
+    if (!wait_ge(ag_flag + threadIdx.x, (ag_state[0] + 1u) * expected)) ok_flag = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!ok_flag) atomicExch(status, static_cast<uint32_t>(kErrFlagTimeout));
+    atomicAdd(&ag_state[0], 1u);
+  }
+}
+
+// Vocab-sharded greedy merge: every rank publishes its local (best logit, global id) per row
+// to all ranks, then each rank takes the best over ranks (ties: lowest id), so all ranks agree.
+struct ArgmaxMergeParams {
+  const float* local_val;    // [rows]
+  const int* local_id;       // [rows] already global ids
+  float* slot_val[kMaxRanksTp];   // every rank's exchange area [size][rows_max]
+  int* slot_id[kMaxRanksTp];
+  uint32_t* flag_peer[kMaxRanksTp];  // every rank's counters [size]
+  const float* my_val;       // local exchange area
+  const int* my_id;
+  const uint32_t* my_flag;
+  uint32_t* my_state;        // {epoch}
+  int* out_id;               // [rows]
+  uint32_t* status;
+  int rank, size, rows, rows_max;
+};
+
+__global__ void __launch_bounds__(256)
+tp_argmax_merge_kernel(const ArgmaxMergeParams p) {
+  __shared__ uint32_t ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  for (int i = threadIdx.x; i < p.rows; i += blockDim.x) {
+    const float v = p.local_val[i];
+    const int id = p.local_id[i];
+    for (int r = 0; r < p.size; ++r) {
+      p.slot_val[r][p.rank * p.rows_max + i] = v;
+      p.slot_id[r][p.rank * p.rows_max + i] = id;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < p.size) {
+    red_rel_sys_add(p.flag_peer[threadIdx.x] + p.rank, 1u);
+    if (!wait_ge(p.my_flag + threadIdx.x, p.my_state[0] + 1u)) ok_flag = 0;
+  }
+  __syncthreads();
+  if (ok_flag) {
+    for (int i = threadIdx.x; i < p.rows; i += blockDim.x) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int r = 0; r < p.size; ++r) {
+        const float v = __ldcg(p.my_val + r * p.rows_max + i);
+        const int id = __ldcg(p.my_id + r * p.rows_max + i);
+        if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+      }
+      p.out_id[i] = bi;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!ok_flag) atomicExch(p.status, static_cast<uint32_t>(kErrFlagTimeout));
+    atomicAdd(&p.my_state[0], 1u);
+  }
+}
+
+}  // namespace cb
+
+extern "C" {
+
+struct CbReduceNorm {
+  const void* recv; const void* rs_flag; void* rs_state; unsigned rs_expected;
+  void* h; const void* norm_w; void* x_peer[8]; void* ag_flag_peer[8]; void* status;
+  int rank, size, rows_per_rank, H, M; float eps; int zero_centered;
+};
+
+int cb_tp_reduce_norm(const CbReduceNorm* a, void* stream) {
+  using namespace cb;
+  if (a->size < 1 || a->size > kMaxRanksTp || a->H % 8 != 0 || a->H > kRnThreads * kRnMaxVec * 8) return -10;
+  ReduceNormParams p;
+  p.recv = static_cast<const __nv_bfloat16*>(a->recv);
+  p.rs_flag = static_cast<const uint32_t*>(a->rs_flag);
+  p.rs_state = static_cast<uint32_t*>(a->rs_state);
+  p.rs_expected = a->rs_expected;
+  p.h = static_cast<__nv_bfloat16*>(a->h);
+  p.norm_w = static_cast<const __nv_bfloat16*>(a->norm_w);
+  for (int r = 0; r < a->size; ++r) {
+    p.x_peer[r] = static_cast<__nv_bfloat16*>(a->x_peer[r]);
+    p.ag_flag_peer[r] = static_cast<uint32_t*>(a->ag_flag_peer[r]);
+  }
+  p.status = static_cast<uint32_t*>(a->status);
+  p.rank = a->rank; p.size = a->size; p.rows_per_rank = a->rows_per_rank; p.H = a->H; p.M = a->M;
+  p.eps = a->eps; p.zero_centered = a->zero_centered;
+  tp_reduce_norm_kernel<<<a->rows_per_rank, kRnThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int cb_tp_wait(const void* ag_flag, void* ag_state, unsigned expected, int size, void* status, void* stream) {
+  cb::tp_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(ag_flag), static_cast<uint32_t*>(ag_state), expected, size,
+      static_cast<uint32_t*>(status));
+  return static_cast<int>(cudaGetLastError());
+}
+
+struct CbArgmaxMerge {
+  const void* local_val; const void* local_id; void* slot_val[8]; void* slot_id[8]; void* flag_peer[8];
+  const void* my_val; const void* my_id; const void* my_flag; void* my_state; void* out_id; void* status;
+  int rank, size, rows, rows_max;
+};
+
+int cb_tp_argmax_merge(const CbArgmaxMerge* a, void* stream) {
+  using namespace cb;
+  if (a->size < 1 || a->size > kMaxRanksTp || a->rows > a->rows_max) return -10;
+  ArgmaxMergeParams p;
+  p.local_val = static_cast<const float*>(a->local_val);
+  p.local_id = static_cast<const int*>(a->local_id);
+  for (int r = 0; r < a->size; ++r) {
+    p.slot_val[r] = static_cast<float*>(a->slot_val[r]);
+    p.slot_id[r] = static_cast<int*>(a->slot_id[r]);
+    p.flag_peer[r] = static_cast<uint32_t*>(a->flag_peer[r]);
+  }
+  p.my_val = static_cast<const float*>(a->my_val);
+  p.my_id = static_cast<const int*>(a->my_id);
+  p.my_flag = static_cast<const uint32_t*>(a->my_flag);
+  p.my_state = static_cast<uint32_t*>(a->my_state);
+  p.out_id = static_cast<int*>(a->out_id);
+  p.status = static_cast<uint32_t*>(a->status);
+  p.rank = a->rank; p.size = a->size; p.rows = a->rows; p.rows_max = a->rows_max;
+  tp_argmax_merge_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -45,6 +45,31 @@ static constexpr int kATileBytes = kTileN * kBlockK * 2;  // 16 KiB bf16
 static constexpr int kNumDequantWarps = 8;
 static constexpr int kThreads = (2 + kNumDequantWarps) * 32;
 
+// Tensor-parallel links of a launch (all pointers are device addresses valid on
+// THIS GPU: local buffers, or peers' symmetric buffers mapped over NVLink).
+//   kTpGatherWait : the activation operand is an all-gathered buffer that peers
+//                   fill with plain P2P stores; the producer warp prefetches
+//                   weights, then waits (bounded) for every rank's rows before
+//                   the first activation TMA load -- all-gather fused into the
+//                   column-parallel GEMM.
+//   kTpScatterPush: the output is a partial sum; the epilogue stores each bf16
+//                   partial tile straight into the row owner's receive buffer
+//                   (slot = this rank) and raises that owner's arrival counter
+//                   -- reduce-scatter fused into the row-parallel GEMM.
+enum TpMode : int { kTpNone = 0, kTpGatherWait = 1, kTpScatterPush = 2 };
+static constexpr int kMaxRanks = 8;
+
+struct TpLink {
+  int mode;
+  int rank, size;
+  int rows_per_rank;                  // multiple of 16; row m belongs to rank m / rows_per_rank
+  __nv_bfloat16* recv[kMaxRanks];     // push: owner o's receive buffer [size][rows_per_rank][N]
+  uint32_t* rs_flag[kMaxRanks];       // push: owner o's arrival counters [size]
+  const uint32_t* ag_flag;            // wait: local arrival counters [size]
+  uint32_t* ag_state;                 // wait: local {epoch, done CTAs}
+  uint32_t ag_expected;               // wait: arrivals per source rank per epoch
+};
+
 struct WqGemmParams {
   const uint8_t* codes;
   const uint8_t* meta;
@@ -63,7 +88,29 @@ struct WqGemmParams {
   int stages;
   float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
   uint32_t tmem_cols;       // power of two >= max(32, mb)
+  TpLink tp;
 };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until a monotonically increasing counter reaches `target` (wrap-safe).
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, volatile uint32_t* abort_flag) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys(p) - target) < 0) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_flag = 2;
+      return false;
+    }
+  }
+  return true;
+}
 
 struct __align__(8) SmemCtl {
   uint64_t full[8];
@@ -197,15 +244,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
       const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? kATileBytes : kCodeBytes + kMetaBytes);
-      for (int i = 0; i < iters; ++i) {
+      auto load_weights = [&](int i) {
         const int s = i % S;
-        const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
-        if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
         const int kb = kb_lo + i;
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint32_t bar = smem_u32(&ctl->full[s]);
         mbar_expect_tx(bar, tx);
-        tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, m0, bar);
         if (FMT == kFmtBf16) {
           tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, n_tile * kTileN, bar);
         } else {
@@ -213,6 +257,30 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const uint8_t* msrc = p.meta + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMetaBytes;
           bulk_g2s(smem_u32(st + x_bytes + kATileBytes), csrc, kCodeBytes, bar);
           bulk_g2s(smem_u32(st + x_bytes + kATileBytes + kCodeBytes), msrc, kMetaBytes, bar);
+        }
+      };
+      auto load_x = [&](int i) {
+        const int s = i % S;
+        uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
+        tma_load_2d(smem_u32(st), &tmap_x, (kb_lo + i) * kBlockK, m0, smem_u32(&ctl->full[s]));
+      };
+      // weights of the first S stages go out before anything else, so that an
+      // all-gather still in flight overlaps with weight streaming
+      const int pre = iters < S ? iters : S;
+      for (int i = 0; i < pre; ++i) load_weights(i);
+      bool ok = true;
+      if (p.tp.mode & kTpGatherWait) {
+        const uint32_t target = (p.tp.ag_state[0] + 1u) * p.tp.ag_expected;
+        for (int r = 0; r < p.tp.size && ok; ++r) ok = wait_counter(p.tp.ag_flag + r, target, abort_flag);
+      }
+      if (ok) {
+        for (int i = 0; i < pre; ++i) load_x(i);
+        for (int i = pre; i < iters; ++i) {
+          const int s = i % S;
+          const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
+          if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
+          load_weights(i);
+          load_x(i);
         }
       }
     }
@@ -294,6 +362,19 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int pair = (warp - 2) >> 2;        // two warps share a quadrant; alternate chunks
     const int n = n_tile * kTileN + quad * 32 + lane;
     const int chunks = p.mb >> 4;
+    // where element (m, n) of the result goes: the local output, or (scatter-push)
+    // the receive buffer of the rank that owns row m
+    auto store_out = [&](int m, int nn, float v) {
+      if (p.tp.mode & kTpScatterPush) {
+        const int o = m / p.tp.rows_per_rank;
+        const int lr = m - o * p.tp.rows_per_rank;
+        p.tp.recv[o][(static_cast<size_t>(p.tp.rank) * p.tp.rows_per_rank + lr) * p.N + nn] = __float2bfloat16(v);
+      } else {
+        const size_t off = static_cast<size_t>(m) * p.ldy + nn;
+        if (p.residual) v += __bfloat162float(p.residual[off]);
+        p.y[off] = __float2bfloat16(v);
+      }
+    };
     if (acc_ok && iters > 0) {
       if (p.splits == 1) {
         for (int ci = pair; ci < chunks; ci += 2) {
@@ -305,10 +386,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + ci * 16 + j;
               if (m < p.M) {
-                float v = __uint_as_float(acc[j]) * p.alpha;
-                const size_t off = static_cast<size_t>(m) * p.ldy + n;
-                if (p.residual) v += __bfloat162float(p.residual[off]);
-                p.y[off] = __float2bfloat16(v);
+                store_out(m, n, __uint_as_float(acc[j]) * p.alpha);
               }
             }
           }
@@ -350,23 +428,42 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
             if (m >= p.M) break;
             float v = 0.f;
             for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(wsb + sp * part + static_cast<size_t>(mm) * kTileN + r);
-            v *= p.alpha;
-            const size_t off = static_cast<size_t>(m) * p.ldy + nn;
-            if (p.residual) v += __bfloat162float(p.residual[off]);
-            p.y[off] = __float2bfloat16(v);
+            store_out(m, nn, v * p.alpha);
           }
         }
       }
     }
   }
 
+  if ((p.tp.mode & kTpScatterPush) && warp >= 2) {
+    // every partial row of this CTA is on its way: make the stores visible system-wide,
+    // then raise the arrival counter of each owner whose rows this tile touched
+    const bool pusher = (p.splits == 1) || ctl->is_last;
+    __threadfence_system();
+    asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
+    if (pusher && threadIdx.x == 64 && !ctl->abort_flag) {
+      const int m_last = min(p.M, m0 + p.mb) - 1;
+      for (int o = m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
+        red_release_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
-  if (threadIdx.x == 0 && ctl->abort_flag) atomicExch(p.status, static_cast<uint32_t>(kErrBarrierTimeout));
+  if ((p.tp.mode & kTpGatherWait) && threadIdx.x == 0) {
+    // the last CTA of the grid closes the epoch of the gathered buffer
+    const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(&p.tp.ag_state[1], 1u) == total - 1u) {
+      p.tp.ag_state[1] = 0;
+      __threadfence();
+      atomicAdd(&p.tp.ag_state[0], 1u);
+    }
+  }
+  if (threadIdx.x == 0 && ctl->abort_flag)
+    atomicExch(p.status, static_cast<uint32_t>(ctl->abort_flag == 2 ? kErrFlagTimeout : kErrBarrierTimeout));
 }
 
 // ------------------------------------------------------------------ host
@@ -429,9 +526,30 @@ long long cb_wq_gemm_workspace_bytes(int M, int N, int splits) {
 // x: bf16 [M, K] row-major (ldx elements per row); y: bf16 [M, ldy].
 // fmt: 0 cubic4, 1 affine4, 2 nvfp4 (W4A16), 3 bf16 weights (codes = W [N,K] bf16).
 // Returns 0 or a negative argument error / positive cudaError_t.
+// Tensor-parallel link description passed from the host (see TpLink).
+struct CbTpLink {
+  int mode, rank, size, rows_per_rank;
+  void* recv[8];
+  void* rs_flag[8];
+  const void* ag_flag;
+  void* ag_state;
+  unsigned ag_expected;
+};
+
+int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                  const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
+                  void* counters, void* status, void* stream, const CbTpLink* link);
+
 int cb_wq_gemm(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
                void* counters, void* status, void* stream) {
+  return cb_wq_gemm_tp(fmt, x, ldx, codes, meta, y, ldy, residual, alpha, M, N, K, group_k, splits, workspace, counters,
+                       status, stream, nullptr);
+}
+
+int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+               const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
+               void* counters, void* status, void* stream, const CbTpLink* link) {
   using namespace cb;
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % 8) != 0) return -10;
   if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4) return -11;
@@ -445,6 +563,19 @@ int cb_wq_gemm(int fmt, const void* x, int ldx, const void* codes, const void* m
   p.counters = static_cast<uint32_t*>(counters);
   p.status = static_cast<uint32_t*>(status);
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.alpha = alpha;
+  p.tp.mode = kTpNone;
+  if (link && link->mode != kTpNone) {
+    if (link->size < 1 || link->size > kMaxRanks || link->rows_per_rank <= 0 || (link->rows_per_rank % 16) != 0) return -30;
+    p.tp.mode = link->mode; p.tp.rank = link->rank; p.tp.size = link->size; p.tp.rows_per_rank = link->rows_per_rank;
+    for (int r = 0; r < link->size; ++r) {
+      p.tp.recv[r] = static_cast<__nv_bfloat16*>(link->recv[r]);
+      p.tp.rs_flag[r] = static_cast<uint32_t*>(link->rs_flag[r]);
+    }
+    p.tp.ag_flag = static_cast<const uint32_t*>(link->ag_flag);
+    p.tp.ag_state = static_cast<uint32_t*>(link->ag_state);
+    p.tp.ag_expected = link->ag_expected;
+    if ((link->mode & kTpScatterPush) && static_cast<long long>(link->rows_per_rank) * link->size < M) return -31;
+  }
   p.mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
   p.k_blocks = K / kBlockK;
   if (splits < 1) splits = 1;

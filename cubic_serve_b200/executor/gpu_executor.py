@@ -227,15 +227,7 @@ class GpuExecutor:
     # ----------------------------------------------------------------- batches
     # ------------------------------------------------------------------- run
     def _body(self, b: StepBatch) -> None:
-        r = self.runner
-        hidden = r.forward_hidden(b)
-        if b.num_logit_rows:
-            logits = r.forward_logits(b, hidden, self.logits)
-            d = self.stage.d
-            n = b.num_logit_rows
-            K.sample(logits, self.out_ids[:n], temperature=d["temperature"][:n], top_p=d["top_p"][:n],
-                     top_k=d["top_k"][:n], seeds=d["seeds"][:n], counters=d["draws"][:n], vocab=logits.shape[1])
-            r.launches_per_step += 1
+        self.runner.run_step(b, self.stage.d, self.logits, self.out_ids)
 
     def capture_decode_graphs(self, capacities: list[int] | None = None) -> list[int]:
         """Capture one graph per decode row capacity (largest first, like the reference)."""

@@ -1,0 +1,107 @@
+"""Structured-output constraints: request-local ``mask -> apply -> accept`` boundary.
+
+The reference routes json_schema / regex / choice / grammar / structural_tag constraints through xgrammar
+(``generation/constraints.py:46-531``, ``generation/xgrammar.py:280``): a matcher per request fills a token
+bitmask before sampling, the sampler applies it, and the accepted token advances (or, for speculative
+rounds, rolls back) the matcher.  The sampler kernel here takes exactly that bitmask (``mask`` argument of
+``ops.kernels.sample``).  This module owns the matcher life cycle; it works without xgrammar for the
+constraint kinds that need no grammar engine (``choice``) and reports the others as unavailable when the
+optional dependency is missing.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from ..contracts.request import StructuredKind, StructuredOutput
+
+try:  # optional extra
+    import xgrammar as _xgr
+except Exception:  # pragma: no cover
+    _xgr = None
+
+
+def constraint_supported(s: StructuredOutput) -> bool:
+    if s.kind in (StructuredKind.NONE, StructuredKind.JSON_OBJECT, StructuredKind.CHOICE):
+        return True
+    return _xgr is not None
+
+
+class ChoiceMatcher:
+    """Rewindable matcher for ``choice`` constraints: the output must be exactly one of the given strings."""
+
+    def __init__(self, choices: list[str], tokenizer, eos_token_id: int) -> None:
+        self.seqs = [list(tokenizer.encode(c, add_special_tokens=False)) for c in choices]
+        self.eos = eos_token_id
+        self.pos = 0
+        self.alive = list(range(len(self.seqs)))
+        self._history: list[list[int]] = []
+
+    def fill_bitmask(self, bitmask: np.ndarray) -> None:
+        """``bitmask``: uint32 words of one row, bit set = token allowed."""
+        bitmask[:] = 0
+        for i in self.alive:
+            seq = self.seqs[i]
+            tok = seq[self.pos] if self.pos < len(seq) else self.eos
+            bitmask[tok >> 5] |= np.uint32(1 << (tok & 31))
+
+    def accept(self, token: int) -> bool:
+        nxt = [i for i in self.alive if (self.seqs[i][self.pos] if self.pos < len(self.seqs[i]) else self.eos) == token]
+        if not nxt:
+            return False
+        self._history.append(self.alive)
+        self.alive = nxt
+        self.pos += 1
+        return True
+
+    def rollback(self, n: int) -> None:
+        for _ in range(n):
+            self.alive = self._history.pop()
+            self.pos -= 1
+
+    @property
+    def finished(self) -> bool:
+        return any(self.pos > len(self.seqs[i]) for i in self.alive)
+
+
+@dataclass
+class GrammarTransaction:
+    """Per-round view used by speculative decoding: accept draft tokens tentatively, roll back the rejected tail."""
+    matcher: object
+    accepted: int = 0
+
+    def try_accept(self, token: int) -> bool:
+        ok = self.matcher.accept(token)
+        if ok:
+            self.accepted += 1
+        return ok
+
+    def commit(self, keep: int) -> None:
+        if keep < self.accepted:
+            self.matcher.rollback(self.accepted - keep)
+        self.accepted = 0
+
+
+def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_size: int):
+    """Build a matcher for a constraint, or ``None`` when the request is unconstrained."""
+    if s.kind is StructuredKind.NONE:
+        return None
+    if s.kind is StructuredKind.CHOICE:
+        return ChoiceMatcher(list(s.schema), tokenizer, eos_token_id)
+    if _xgr is None:
+        raise RuntimeError("xgrammar is not installed")
+    info = _xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=vocab_size)
+    compiler = _xgr.GrammarCompiler(info)
+    if s.kind is StructuredKind.JSON_OBJECT:
+        compiled = compiler.compile_builtin_json_grammar()
+    elif s.kind in (StructuredKind.JSON_SCHEMA, StructuredKind.TOOL_SCHEMA):
+        import json
+        compiled = compiler.compile_json_schema(json.dumps(s.schema))
+    elif s.kind is StructuredKind.REGEX:
+        compiled = compiler.compile_regex(s.schema)
+    elif s.kind is StructuredKind.GRAMMAR:
+        compiled = compiler.compile_grammar(s.schema)
+    else:
+        raise RuntimeError(f"unsupported constraint kind {s.kind}")
+    return _xgr.GrammarMatcher(compiled)

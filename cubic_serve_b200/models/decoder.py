@@ -122,14 +122,18 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             lw.down = quantize_linear(rnd(H, inter), cfg)
         layers.append(lw)
     v_local = cfg.vocab_size // tp_size
-    embed = (torch.randn(v_local, H, device=device, generator=gen) * std).to(torch.bfloat16)
+    # the embedding table is generated identically on every rank (rank-independent stream), kept whole
+    # for the fused path (each rank embeds only the rows it owns) and sliced for the vocab-sharded baseline
+    shared = torch.Generator(device=device).manual_seed(seed * 1000 + 999)
+    embed_full = (torch.randn(cfg.vocab_size, H, device=device, generator=shared) * std).to(torch.bfloat16)
+    embed = embed_full[tp_rank * v_local:(tp_rank + 1) * v_local]
     if cfg.tie_embeddings:
         head = embed
     else:
         head = (torch.randn(v_local, H, device=device, generator=gen) * std).to(torch.bfloat16)
     lm_head = quantize_linear(head.float(), cfg) if cfg.quant.lm_head_quantized else wq_pack.pack_bf16(head)
     return DecoderWeights(embed=embed, layers=layers, final_norm=norm_w(), lm_head=lm_head,
-                          vocab_start=tp_rank * v_local)
+                          vocab_start=tp_rank * v_local, extras={"embed_full": embed_full})
 
 
 @dataclass
@@ -253,3 +257,84 @@ class DecoderRunner:
         K.wq_gemm(xn, self.w.lm_head, out=logits_out[:R], ws=self.ws)
         self.launches_per_step += 2
         return logits_out[:R]
+
+    # ------------------------------------------------------- fused tensor parallel
+    def forward_hidden_fused(self, b: StepBatch) -> int:
+        """All layers on the fused NVLink path; returns the buffer set that holds the final normalised rows.
+
+        The residual stream is sharded by ROWS (each rank keeps the rows it owns), activations that feed a
+        column-parallel GEMM are all-gathered by push, partial sums of row-parallel GEMMs are
+        reduce-scattered by push; see ``parallel/tp.py``.
+        """
+        cfg, w, f = self.cfg, self.w, self.tp.fused
+        T, H = b.num_tokens, cfg.hidden_size
+        f.begin_step(T)
+        lo = f.rank * f.rpr
+        cnt = max(0, min(T, lo + f.rpr) - lo)
+        n = 0
+        if cnt:
+            K.embedding(b.token_ids[lo:lo + cnt], w.extras["embed_full"], out=f.h_local[:cnt])
+            n += 1
+        qkv, q, attn = self.qkv[:T], self.q[:T], self.attn[:T]
+        s = 0
+        f.reduce_norm(w.layers[0].ln1, s, 0, cfg.rms_eps, cfg.zero_centered_norm, reduce=False)
+        n += 1
+        for li, lw in enumerate(w.layers):
+            f.gemm_gather(lw.qkv, qkv, s)
+            K.rope_kv_write(qkv, q, self.kv[li], b.positions, b.slots, self.inv_freq, self.hq, self.hkv, self.D,
+                            self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
+                            rotary_dim=cfg.rotary_dim)
+            K.paged_attention(q.view(T, self.hq, self.D), attn.view(T, self.hq, self.D), self.kv[li], b.page_table,
+                              b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, self.hq, self.hkv,
+                              self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)
+            s ^= 1
+            f.gemm_scatter(attn, lw.o, s)
+            f.reduce_norm(lw.ln2, s, H, cfg.rms_eps, cfg.zero_centered_norm)
+            gu, act = self.gu[:T], self.act[:T]
+            f.gemm_gather(lw.gate_up, gu, s)
+            K.swiglu(gu, out=act)
+            s ^= 1
+            f.gemm_scatter(act, lw.down, s)
+            nxt = w.layers[li + 1].ln1 if li + 1 < len(w.layers) else w.final_norm
+            f.reduce_norm(nxt, s, H, cfg.rms_eps, cfg.zero_centered_norm)
+            n += 9
+        self.launches_per_step = n
+        return s
+
+    def run_step(self, b: StepBatch, d: dict, logits_buf: torch.Tensor, out_ids: torch.Tensor) -> None:
+        """Whole step: layers, final norm, lm_head, sampling (and the cross-rank token agreement under TP)."""
+        R = b.num_logit_rows
+        fused = self.tp is not None and self.tp.fused is not None
+        if not fused:
+            hidden = self.forward_hidden(b)
+            if not R:
+                return
+            logits = self.forward_logits(b, hidden, logits_buf)
+        else:
+            f = self.tp.fused
+            s = self.forward_hidden_fused(b)
+            if R == b.num_tokens:
+                logits = f.gemm_gather(self.w.lm_head, logits_buf[:R], s)
+            else:
+                x = f.wait_gather(s)
+                if R:
+                    rows = torch.index_select(x, 0, b.logit_rows[:R])
+                    logits = K.wq_gemm(rows, self.w.lm_head, out=logits_buf[:R], ws=self.ws)
+            self.launches_per_step += 2
+        if self.tp is None:
+            K.sample(logits, out_ids[:R], temperature=d["temperature"][:R], top_p=d["top_p"][:R], top_k=d["top_k"][:R],
+                     seeds=d["seeds"][:R], counters=d["draws"][:R], vocab=logits.shape[1])
+            self.launches_per_step += 1
+            return
+        # vocab-sharded: local greedy candidate per row, then agreement across ranks
+        if not hasattr(self, "_cand_val"):
+            self._cand_val = torch.empty(logits_buf.shape[0], dtype=torch.float32, device=self.device)
+            self._cand_id = torch.empty(logits_buf.shape[0], dtype=torch.int32, device=self.device)
+        if R:
+            K.sample(logits, self._cand_id[:R], vocab=logits.shape[1], out_value=self._cand_val[:R],
+                     id_offset=self.w.vocab_start)
+        if fused:
+            self.tp.fused.argmax_merge(self._cand_val, self._cand_id, out_ids, R)
+        elif R:
+            self.tp.argmax_merge_nccl(self._cand_val, self._cand_id, out_ids, R)
+        self.launches_per_step += 2

@@ -6,6 +6,7 @@ PyTorch fallback on the GPU path: a missing library is an error.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
@@ -83,14 +84,15 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
 
 def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, splits: int | None = None,
-            ws: Workspace | None = None) -> torch.Tensor:
+            ws: Workspace | None = None, link=None) -> torch.Tensor:
     """``out[M, N] = x[M, K] @ W[N, K]^T * alpha (+ residual)`` with W in packed form."""
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
     m, k = x.shape
     assert k == w.k, (k, w.k)
-    if out is None:
+    push = link is not None and (link.mode & 2)
+    if out is None and not push:
         out = torch.empty((m, w.n), dtype=torch.bfloat16, device=x.device)
-    assert out.stride(1) == 1 and out.shape == (m, w.n)
+    assert push or (out.stride(1) == 1 and out.shape == (m, w.n))
     if residual is not None:
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
@@ -101,9 +103,11 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
         need = l.cb_wq_gemm_workspace_bytes(m, w.n, splits)
         if need > ws.gemm.numel():
             splits = 1
-    code = l.cb_wq_gemm(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta), out.data_ptr(),
-                        out.stride(0), _ptr(residual), float(w.alpha), m, w.n, k, w.group_k, splits,
-                        ws.gemm.data_ptr(), ws.gemm_counters.data_ptr(), ws.status.data_ptr(), _stream())
+    code = l.cb_wq_gemm_tp(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
+                           None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual),
+                           float(w.alpha), m, w.n, k, w.group_k, splits, ws.gemm.data_ptr(),
+                           ws.gemm_counters.data_ptr(), ws.status.data_ptr(), _stream(),
+                           None if link is None else ctypes.byref(link))
     native.check(code, "cb_wq_gemm")
     return out
 
@@ -188,12 +192,12 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: torch.Tenso
            top_p: torch.Tensor | None = None, top_k: torch.Tensor | None = None,
            seeds: torch.Tensor | None = None, counters: torch.Tensor | None = None,
            mask: torch.Tensor | None = None, out_logprob: torch.Tensor | None = None,
-           vocab: int | None = None) -> torch.Tensor:
+           vocab: int | None = None, out_value: torch.Tensor | None = None, id_offset: int = 0) -> torch.Tensor:
     rows = logits.shape[0]
     code = native.lib().cb_sample(logits.data_ptr(), logits.stride(0), _ptr(mask),
                                   0 if mask is None else mask.shape[1], _ptr(temperature), _ptr(top_p), _ptr(top_k),
-                                  _ptr(seeds), _ptr(counters), out_ids.data_ptr(), _ptr(out_logprob), rows,
-                                  vocab or logits.shape[1], _stream())
+                                  _ptr(seeds), _ptr(counters), out_ids.data_ptr(), _ptr(out_logprob),
+                                  _ptr(out_value), int(id_offset), rows, vocab or logits.shape[1], _stream())
     native.check(code, "cb_sample")
     return out_ids
 

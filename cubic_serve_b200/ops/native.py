@@ -16,7 +16,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_PATH = Path(__file__).resolve().parent.parent / "libcubic_b200.so"
-SOURCES = ("wq_gemm.cu", "elementwise.cu", "kv_cache.cu", "paged_attn.cu", "sampling.cu")
+SOURCES = ("wq_gemm.cu", "elementwise.cu", "kv_cache.cu", "paged_attn.cu", "sampling.cu", "tp_comm.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -120,10 +120,43 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_paged_attn_partial_floats.restype = ll
     l.cb_paged_attn.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp, vp, vp, vp]
     l.cb_paged_attn.restype = i
-    l.cb_sample.argtypes = [vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, i, i, vp]
+    l.cb_sample.argtypes = [vp, i, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, vp]
     l.cb_sample.restype = i
     l.cb_verify_greedy.argtypes = [vp, vp, vp, i, vp, vp, vp, i, vp]
     l.cb_verify_greedy.restype = i
+    l.cb_wq_gemm_tp.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, vp, vp, vp, vp]
+    l.cb_wq_gemm_tp.restype = i
+    l.cb_tp_reduce_norm.argtypes = [vp, vp]
+    l.cb_tp_reduce_norm.restype = i
+    l.cb_tp_wait.argtypes = [vp, vp, ctypes.c_uint, i, vp, vp]
+    l.cb_tp_wait.restype = i
+    l.cb_tp_argmax_merge.argtypes = [vp, vp]
+    l.cb_tp_argmax_merge.restype = i
+
+
+class TpLinkStruct(ctypes.Structure):
+    """Mirror of ``CbTpLink`` in ``csrc/wq_gemm.cu``."""
+    _fields_ = [("mode", ctypes.c_int), ("rank", ctypes.c_int), ("size", ctypes.c_int),
+                ("rows_per_rank", ctypes.c_int), ("recv", ctypes.c_void_p * 8), ("rs_flag", ctypes.c_void_p * 8),
+                ("ag_flag", ctypes.c_void_p), ("ag_state", ctypes.c_void_p), ("ag_expected", ctypes.c_uint)]
+
+
+class ReduceNormStruct(ctypes.Structure):
+    """Mirror of ``CbReduceNorm`` in ``csrc/tp_comm.cu``."""
+    _fields_ = [("recv", ctypes.c_void_p), ("rs_flag", ctypes.c_void_p), ("rs_state", ctypes.c_void_p),
+                ("rs_expected", ctypes.c_uint), ("h", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
+                ("x_peer", ctypes.c_void_p * 8), ("ag_flag_peer", ctypes.c_void_p * 8), ("status", ctypes.c_void_p),
+                ("rank", ctypes.c_int), ("size", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("H", ctypes.c_int),
+                ("M", ctypes.c_int), ("eps", ctypes.c_float), ("zero_centered", ctypes.c_int)]
+
+
+class ArgmaxMergeStruct(ctypes.Structure):
+    """Mirror of ``CbArgmaxMerge`` in ``csrc/tp_comm.cu``."""
+    _fields_ = [("local_val", ctypes.c_void_p), ("local_id", ctypes.c_void_p), ("slot_val", ctypes.c_void_p * 8),
+                ("slot_id", ctypes.c_void_p * 8), ("flag_peer", ctypes.c_void_p * 8), ("my_val", ctypes.c_void_p),
+                ("my_id", ctypes.c_void_p), ("my_flag", ctypes.c_void_p), ("my_state", ctypes.c_void_p),
+                ("out_id", ctypes.c_void_p), ("status", ctypes.c_void_p), ("rank", ctypes.c_int),
+                ("size", ctypes.c_int), ("rows", ctypes.c_int), ("rows_max", ctypes.c_int)]
 
 
 def check(code: int, what: str) -> None:
