@@ -1,0 +1,182 @@
+"""``cubic`` command line: ``serve``, ``inspect-model``, ``qualify``, ``bench``.
+
+Flag surface follows the reference CLI (``cli.py:281-528`` there): Server / Model and generation / Devices and
+parallelism / Memory and cache / Scheduling / Advanced groups, JSON sub-configs for speculative decoding
+(``--speculative-config '{"method":"mtp","num_speculative_tokens":3,"mode":"dynamic"}'``) and structured
+outputs, cache dtypes chosen independently for K and V.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from dataclasses import dataclass
+
+KV_DTYPES = ("auto", "bfloat16", "float16", "fp8", "int8", "int6", "int4")
+KV_BITS = {"auto": 8, "int8": 8, "int6": 6, "int4": 4, "fp8": 8, "bfloat16": 16, "float16": 16}
+
+
+@dataclass(frozen=True)
+class SpeculativeConfig:
+    method: str = "none"
+    num_speculative_tokens: int = 0
+    mode: str = "fixed"            # fixed | dynamic
+    max_tokens: int = 0
+    policy: dict | None = None
+
+
+def parse_speculative_config(text: str | None) -> SpeculativeConfig:
+    if not text:
+        return SpeculativeConfig()
+    try:
+        cfg = json.loads(text)
+    except ValueError as exc:
+        raise argparse.ArgumentTypeError(f"--speculative-config is not valid JSON: {exc}") from exc
+    if not isinstance(cfg, dict) or cfg.get("method") != "mtp":
+        raise argparse.ArgumentTypeError('--speculative-config needs {"method": "mtp", ...}')
+    n = cfg.get("num_speculative_tokens")
+    if not isinstance(n, int) or not 1 <= n <= 7:
+        raise argparse.ArgumentTypeError("num_speculative_tokens must be an integer in [1, 7]")
+    mode = cfg.get("mode", "fixed")
+    if mode not in ("fixed", "dynamic"):
+        raise argparse.ArgumentTypeError("mode must be fixed or dynamic")
+    return SpeculativeConfig("mtp", n, mode, int(cfg.get("max_tokens", n)), cfg.get("policy"))
+
+
+def parse_devices(text: str | None) -> list[int]:
+    if not text:
+        return [0]
+    out: list[int] = []
+    for part in text.split(","):
+        part = part.strip()
+        if ".." in part or "-" in part:
+            a, b = part.replace("..", "-").split("-")
+            out.extend(range(int(a), int(b) + 1))
+        elif part:
+            out.append(int(part))
+    if len(set(out)) != len(out) or not out:
+        raise argparse.ArgumentTypeError("--devices must list distinct device ids")
+    return out
+
+
+def validate_topology(devices: list[int], tp: int, pp: int, ep: int, spec: SpeculativeConfig) -> None:
+    if pp not in (1, 2):
+        raise SystemExit("--pp-size must be 1 or 2")
+    if tp * pp != len(devices):
+        raise SystemExit(f"--tp-size x --pp-size = {tp * pp} must equal the number of devices ({len(devices)})")
+    if ep < 1 or tp % ep:
+        raise SystemExit("--ep-size must divide --tp-size")
+    if spec.method == "mtp" and pp != 1:
+        raise SystemExit("MTP speculative decoding requires --pp-size 1")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="cubic", description="Blackwell-native quantized LLM serving")
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    ins = sub.add_parser("inspect-model", help="print the architecture, quantization and tensor inventory of a checkpoint")
+    ins.add_argument("model")
+    ins.add_argument("--json", action="store_true")
+
+    q = sub.add_parser("qualify", help="run the numerical witness checks of the native kernels on this GPU")
+    q.add_argument("--device", type=int, default=0)
+    q.add_argument("--quick", action="store_true")
+
+    s = sub.add_parser("serve", help="serve a checkpoint over OpenAI / Anthropic compatible HTTP")
+    s.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
+    g = s.add_argument_group("Server")
+    g.add_argument("--served-model-name")
+    g.add_argument("--host", default="127.0.0.1")
+    g.add_argument("--port", type=int, default=8000)
+    g.add_argument("--api-key", default=os.environ.get("CUBIC_API_KEY"))
+    g.add_argument("--http-keep-alive-seconds", type=int, default=5)
+    g.add_argument("--log-config")
+    g = s.add_argument_group("Model and generation")
+    g.add_argument("--compute-mode", choices=("wna16", "wna8"), default="wna16")
+    g.add_argument("--dtype", choices=("bfloat16",), default="bfloat16")
+    g.add_argument("--max-model-len", type=int)
+    g.add_argument("--chat-template")
+    g.add_argument("--reasoning-parser", default="auto")
+    g.add_argument("--tool-call-parser", default="hermes")
+    g.add_argument("--thinking", action=argparse.BooleanOptionalAction, default=None)
+    g.add_argument("--structured-outputs-config")
+    g.add_argument("--speculative-config")
+    g = s.add_argument_group("Devices and parallelism")
+    g.add_argument("--devices", "--device", dest="devices")
+    g.add_argument("--tp-size", type=int, default=None)
+    g.add_argument("--pp-size", type=int, default=1)
+    g.add_argument("--ep-size", type=int, default=1)
+    g.add_argument("--tp-comm", choices=("fused", "nccl"), default="fused")
+    g = s.add_argument_group("Memory and cache")
+    g.add_argument("--gpu-memory-gib", type=float)
+    g.add_argument("--gpu-reserve-gib", type=float, default=4.0)
+    g.add_argument("--k-cache-dtype", choices=KV_DTYPES, default="auto")
+    g.add_argument("--v-cache-dtype", choices=KV_DTYPES, default="auto")
+    g.add_argument("--enable-kv-cache-rotation", action="store_true")
+    g.add_argument("--prefix-cache", action=argparse.BooleanOptionalAction, default=True)
+    g = s.add_argument_group("Scheduling")
+    g.add_argument("--max-running-requests", type=int, default=256)
+    g.add_argument("--token-budget", type=int, default=8192)
+    g.add_argument("--cuda-graph-max-tokens", default="auto")
+    g.add_argument("--prefill-chunk-tokens", type=int, default=4096)
+    g = s.add_argument_group("Advanced")
+    g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
+    g.add_argument("--startup-numerical-audit", action="store_true")
+    g.add_argument("--model-adapter")
+    g.add_argument("--operator-config")
+    g.add_argument("--seed", type=int, default=0)
+    return ap
+
+
+def _kv_bits(name: str) -> int:
+    bits = KV_BITS[name]
+    if bits not in (8, 4):
+        raise SystemExit(f"KV cache dtype {name} is not available in this build (int8 and int4 are)")
+    return bits
+
+
+def _serve(args) -> int:
+    from .runtime.serving import build_backend, run_http_server
+    spec = parse_speculative_config(args.speculative_config)
+    devices = parse_devices(args.devices)
+    tp = args.tp_size or max(1, len(devices) // args.pp_size)
+    validate_topology(devices, tp, args.pp_size, args.ep_size, spec)
+    os.environ.setdefault("OMP_NUM_THREADS", "4")
+    os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
+    sys.setswitchinterval(0.001)
+    backend, model_name = build_backend(args, devices, tp, spec, _kv_bits(args.k_cache_dtype), _kv_bits(args.v_cache_dtype))
+    return run_http_server(backend, model_name, args)
+
+
+def _inspect(args) -> int:
+    from .models.checkpoint import inspect_checkpoint
+    info = inspect_checkpoint(args.model)
+    if args.json:
+        print(json.dumps(info, indent=1, default=str))
+    else:
+        for k, v in info.items():
+            print(f"{k}: {v}")
+    return 0
+
+
+def _qualify(args) -> int:
+    from .guardrail.qualify import run_qualification
+    report = run_qualification(args.device, quick=args.quick)
+    print(json.dumps(report, indent=1))
+    return 0 if report["ok"] else 1
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = build_parser().parse_args(argv)
+    if args.command == "serve":
+        return _serve(args)
+    if args.command == "inspect-model":
+        return _inspect(args)
+    if args.command == "qualify":
+        return _qualify(args)
+    return 2
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

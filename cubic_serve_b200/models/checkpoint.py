@@ -1,0 +1,399 @@
+"""Checkpoint admission: HF-style safetensors directories (all weight formats) and GGUF files.
+
+Counterpart of the reference's ``inspect_checkpoint`` (``models/checkpoint.py:1010``),
+``CheckpointWeights.admit`` (``models/quantized_checkpoint.py:207``) and the GGUF readers
+(``models/gguf.py:172``, ``models/gguf_weights.py:433``).  The inventory is *closed*: every tensor in the
+shards must be claimed by exactly one logical weight, otherwise admission fails.  A logical linear weight
+``<module>.weight`` of a quantized checkpoint is stored as payload tensors named ``<module>.<suffix>``.
+
+``load_decoder_weights`` turns an admitted checkpoint into rank-local ``DecoderWeights`` (tensor-parallel
+slices taken on whole heads / whole scale groups) ready for the native runner; ``write_random_checkpoint``
+produces a random-init checkpoint in any format with exactly that on-disk layout (used by tests and benchmarks,
+there being no network to fetch real ones).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+
+from ..ops import wq_pack
+from ..quantization import cubic, formats
+from .config import ModelConfig, QuantSpec
+
+PAYLOAD_SUFFIXES = {
+    "cubic": ("weight_packed", "weight_scale", "weight_a", "weight_b", "weight_ab", "weight_scale_global",
+              "weight_a_global", "weight_b_global", "weight_metadata", "weight_curve_a", "weight_curve_b"),
+    "int": ("weight_packed", "weight_scale", "weight_zero_point", "weight_shape", "weight_g_idx"),
+    "awq": ("qweight", "qzeros", "scales"),
+    "fp8": ("weight", "weight_scale", "input_scale"),
+    "fp8_block": ("weight", "weight_scale_inv", "weight_scale"),
+    "nvfp4": ("weight_packed", "weight", "weight_scale", "weight_global_scale", "input_global_scale", "weight_scale_2",
+              "input_scale"),
+    "none": ("weight",),
+}
+
+
+class CheckpointError(ValueError):
+    pass
+
+
+@dataclass
+class TensorRef:
+    name: str
+    file: str
+    dtype: str
+    shape: tuple[int, ...]
+
+
+class SafetensorsDirectory:
+    """Lazy reader over one or many ``*.safetensors`` shards."""
+
+    def __init__(self, path: str | Path) -> None:
+        from safetensors import safe_open
+        self.path = Path(path)
+        index = self.path / "model.safetensors.index.json"
+        self.tensors: dict[str, TensorRef] = {}
+        self._open = safe_open
+        files = sorted(p.name for p in self.path.glob("*.safetensors"))
+        if index.exists():
+            wm = json.loads(index.read_text())["weight_map"]
+            files = sorted(set(wm.values()))
+        if not files:
+            raise CheckpointError(f"no safetensors shards in {self.path}")
+        for f in files:
+            with safe_open(str(self.path / f), framework="pt") as sf:
+                for name in sf.keys():
+                    if name in self.tensors:
+                        raise CheckpointError(f"tensor {name} appears in two shards")
+                    sl = sf.get_slice(name)
+                    self.tensors[name] = TensorRef(name, f, str(sl.get_dtype()), tuple(sl.get_shape()))
+        self._handles: dict[str, object] = {}
+
+    def get(self, name: str) -> torch.Tensor:
+        ref = self.tensors[name]
+        h = self._handles.get(ref.file)
+        if h is None:
+            h = self._handles[ref.file] = self._open(str(self.path / ref.file), framework="pt")
+        return h.get_tensor(name)
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.tensors
+
+
+def _layer_modules(cfg: ModelConfig, i: int) -> dict[str, str]:
+    p = f"model.layers.{i}"
+    mods = {"q": f"{p}.self_attn.q_proj", "k": f"{p}.self_attn.k_proj", "v": f"{p}.self_attn.v_proj",
+            "o": f"{p}.self_attn.o_proj"}
+    if not cfg.is_moe:
+        mods.update(gate=f"{p}.mlp.gate_proj", up=f"{p}.mlp.up_proj", down=f"{p}.mlp.down_proj")
+    return mods
+
+
+def logical_inventory(cfg: ModelConfig) -> tuple[dict[str, tuple[int, int]], list[str]]:
+    """Logical linear weights ``module -> (N, K)`` and the plain (unquantized) tensor names of a GQA decoder."""
+    H, D = cfg.hidden_size, cfg.head_dim
+    linears: dict[str, tuple[int, int]] = {}
+    plain = ["model.embed_tokens.weight", "model.norm.weight"]
+    if not cfg.tie_embeddings:
+        plain.append("lm_head.weight")
+    for i in range(cfg.num_layers):
+        m = _layer_modules(cfg, i)
+        linears[m["q"]] = (cfg.q_size, H)
+        linears[m["k"]] = (cfg.kv_size, H)
+        linears[m["v"]] = (cfg.kv_size, H)
+        linears[m["o"]] = (H, cfg.q_size)
+        if cfg.is_moe:
+            plain.append(f"model.layers.{i}.mlp.gate.weight")
+            for e in range(cfg.num_experts):
+                ep = f"model.layers.{i}.mlp.experts.{e}"
+                linears[f"{ep}.gate_proj"] = (cfg.moe_intermediate_size, H)
+                linears[f"{ep}.up_proj"] = (cfg.moe_intermediate_size, H)
+                linears[f"{ep}.down_proj"] = (H, cfg.moe_intermediate_size)
+        else:
+            linears[m["gate"]] = (cfg.intermediate_size, H)
+            linears[m["up"]] = (cfg.intermediate_size, H)
+            linears[m["down"]] = (H, cfg.intermediate_size)
+        plain += [f"model.layers.{i}.input_layernorm.weight", f"model.layers.{i}.post_attention_layernorm.weight"]
+        if cfg.qk_norm:
+            plain += [f"model.layers.{i}.self_attn.q_norm.weight", f"model.layers.{i}.self_attn.k_norm.weight"]
+    return linears, plain
+
+
+@dataclass
+class AdmittedCheckpoint:
+    cfg: ModelConfig
+    store: SafetensorsDirectory
+    payloads: dict[str, dict[str, str]]      # module -> suffix -> tensor name
+    plain: dict[str, str]
+
+    def payload(self, module: str) -> dict[str, torch.Tensor]:
+        return {suffix: self.store.get(name) for suffix, name in self.payloads[module].items()}
+
+
+def admit_checkpoint(path: str | Path) -> AdmittedCheckpoint:
+    path = Path(path)
+    cfg = ModelConfig.from_hf_config(path / "config.json")
+    store = SafetensorsDirectory(path)
+    linears, plain = logical_inventory(cfg)
+    method = cfg.quant.method
+    suffixes = PAYLOAD_SUFFIXES.get(method)
+    if suffixes is None:
+        raise CheckpointError(f"no loader for weight format {method!r}")
+    claimed: set[str] = set()
+    payloads: dict[str, dict[str, str]] = {}
+    for module in linears:
+        found = {s: f"{module}.{s}" for s in suffixes if f"{module}.{s}" in store}
+        if not found and f"{module}.weight" in store:
+            found = {"weight": f"{module}.weight"}     # ignored (unquantized) module of a quantized checkpoint
+        if not found:
+            raise CheckpointError(f"no payload tensors for {module}")
+        payloads[module] = found
+        claimed.update(found.values())
+    plain_map = {}
+    for name in plain:
+        if name not in store:
+            raise CheckpointError(f"missing tensor {name}")
+        plain_map[name] = name
+        claimed.add(name)
+    unowned = sorted(set(store.tensors) - claimed)
+    if unowned:
+        raise CheckpointError(f"checkpoint has {len(unowned)} tensors no logical weight owns, e.g. {unowned[:3]}")
+    return AdmittedCheckpoint(cfg, store, payloads, plain_map)
+
+
+def inspect_checkpoint(path: str | Path) -> dict:
+    path = Path(path)
+    if path.suffix == ".gguf":
+        from .gguf import inspect_gguf
+        return inspect_gguf(path)
+    ck = admit_checkpoint(path)
+    total = sum(math.prod(t.shape) for t in ck.store.tensors.values())
+    by_dtype: dict[str, int] = {}
+    for t in ck.store.tensors.values():
+        by_dtype[t.dtype] = by_dtype.get(t.dtype, 0) + 1
+    return {"model": ck.cfg.name, "family": ck.cfg.family, "layers": ck.cfg.num_layers, "hidden": ck.cfg.hidden_size,
+            "heads": f"{ck.cfg.num_q_heads}q/{ck.cfg.num_kv_heads}kv x {ck.cfg.head_dim}", "vocab": ck.cfg.vocab_size,
+            "quantization": f"{ck.cfg.quant.method} {ck.cfg.quant.bits}-bit group {ck.cfg.quant.group_size}",
+            "tensors": len(ck.store.tensors), "elements": total, "dtypes": by_dtype,
+            "logical_linears": len(ck.payloads)}
+
+
+# ------------------------------------------------------------ rank-local load
+def _slice_rows(payload: dict, method: str, lo: int, hi: int, n: int) -> dict:
+    """Output-dimension slice of a payload (all formats keep N as the leading axis except AWQ)."""
+    out = {}
+    for k, t in payload.items():
+        if method == "awq":
+            out[k] = t[:, lo // 8:hi // 8] if k in ("qweight", "qzeros") else t[:, lo:hi]
+        elif k == "weight_zero_point":
+            out[k] = t          # packed along N: handled after decode
+        elif t.dim() >= 1 and t.shape[0] == n:
+            out[k] = t[lo:hi]
+        elif k == "weight_scale_inv":
+            out[k] = t[lo // 128:-(-hi // 128)]
+        else:
+            out[k] = t
+    return out
+
+
+def _dense_of(method: str, payload: dict, shape, q: QuantSpec) -> torch.Tensor:
+    if "weight" in payload and len(payload) == 1:
+        return payload["weight"].float()
+    if method == "cubic":
+        return cubic.decode(payload, cubic.CubicScheme(q.bits, q.group_size), shape)
+    if method == "int":
+        return formats.int_dense(payload, q.bits, q.group_size, shape)
+    if method == "awq":
+        return formats.awq_dense(payload, q.group_size)
+    if method in ("fp8", "fp8_block"):
+        return formats.fp8_dense(payload)
+    if method == "nvfp4":
+        return formats.nvfp4_dense(payload)
+    raise CheckpointError(method)
+
+
+def pack_logical(method: str, parts: list[tuple[dict, tuple[int, int]]], q: QuantSpec, k_slice: tuple[int, int] | None = None
+                 ) -> wq_pack.PackedWeight:
+    """Concatenate logical matrices along N (e.g. q, k, v) and pack them for the GEMM.
+
+    4-bit Cubic / INT / AWQ / NVFP4 payloads stay 4-bit; everything else is decoded to bf16 at load.
+    ``k_slice`` selects a column range (row-parallel shards), aligned to the scale groups.
+    """
+    lo, hi = k_slice if k_slice else (0, parts[0][1][1])
+    native4 = method == "cubic" and q.bits == 4 or method in ("awq",) or (method == "int" and q.bits == 4) or method == "nvfp4"
+    plain = any(len(p) == 1 and "weight" in p and p["weight"].dtype in (torch.bfloat16, torch.float16, torch.float32)
+                for p, _ in parts)
+    if not native4 or plain:
+        dense = torch.cat([_dense_of(method, p, s, q) for p, s in parts], 0)
+        return wq_pack.pack_bf16(dense[:, lo:hi])
+    if method == "cubic":
+        g = q.group_size
+        if lo % g or (hi % g and hi != parts[0][1][1]):
+            raise CheckpointError("column shard cuts a Cubic scale group")
+        codes, sc, aa, bb = [], [], [], []
+        for p, s in parts:
+            codes.append(cubic.unpack_codes(p["weight_packed"], 4, s[1])[:, lo:hi])
+            t = cubic.metadata_triple(p, cubic.CubicScheme(4, g, metadata=_cubic_variant(p)), s)
+            sc.append(t[0][:, lo // g:-(-hi // g)]); aa.append(t[1][:, lo // g:-(-hi // g)]); bb.append(t[2][:, lo // g:-(-hi // g)])
+        return wq_pack.pack_cubic4(torch.cat(codes), torch.cat(sc), torch.cat(aa), torch.cat(bb), g)
+    if method in ("int", "awq"):
+        g = q.group_size if q.group_size > 0 else parts[0][1][1]
+        qs, ss, zs = [], [], []
+        for p, s in parts:
+            cq, cs, cz = formats.int_decode(p, 4, q.group_size, s) if method == "int" else formats.awq_decode(p, g)
+            qs.append(cq[:, lo:hi]); ss.append(cs[:, lo // g:-(-hi // g)]); zs.append(cz[:, lo // g:-(-hi // g)])
+        qq, sc, zz = torch.cat(qs), torch.cat(ss), torch.cat(zs)
+        return wq_pack.pack_affine4(qq.to(torch.uint8), sc, -zz * sc, min(g, hi - lo))
+    # nvfp4: every part carries its own global scale; fold the ratio into the block scales
+    mults = [formats.nvfp4_global_multiplier(p) for p, _ in parts]
+    ref = max(mults)
+    packed = torch.cat([(p["weight_packed"] if "weight_packed" in p else p["weight"])[:, lo // 2:hi // 2] for p, _ in parts])
+    scales = torch.cat([p["weight_scale"].float()[:, lo // 16:hi // 16] * (m / ref) for (p, _), m in zip(parts, mults)])
+    return wq_pack.pack_nvfp4(packed, scales, ref)
+
+
+def _cubic_variant(p: dict) -> str:
+    if "weight_ab" in p:
+        return cubic.METADATA_B
+    if "weight_metadata" in p:
+        return cubic.METADATA_C
+    return cubic.METADATA_A
+
+
+def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_size: int = 1):
+    """Admitted checkpoint -> rank-local ``DecoderWeights`` (dense FFN decoders)."""
+    from .decoder import DecoderWeights, LayerWeights
+    cfg, q = ck.cfg, ck.cfg.quant
+    if cfg.is_moe:
+        raise CheckpointError("MoE checkpoints are loaded by models.moe.load_moe_layer")
+    method = q.method
+    D = cfg.head_dim
+    hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
+    inter = cfg.intermediate_size // tp_size
+    bf = torch.bfloat16
+
+    def rows(module: str, lo: int, hi: int, n: int):
+        return _slice_rows(ck.payload(module), method, lo, hi, n), (hi - lo, ck_shapes[module][1])
+
+    ck_shapes, _ = logical_inventory(cfg)
+    layers = []
+    for i in range(cfg.num_layers):
+        m = _layer_modules(cfg, i)
+        qkv = pack_logical(method, [rows(m["q"], tp_rank * hq * D, (tp_rank + 1) * hq * D, cfg.q_size),
+                                    rows(m["k"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size),
+                                    rows(m["v"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size)], q)
+        o = pack_logical(method, [(ck.payload(m["o"]), ck_shapes[m["o"]])], q,
+                         (tp_rank * hq * D, (tp_rank + 1) * hq * D))
+        gu = pack_logical(method, [rows(m["gate"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size),
+                                   rows(m["up"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size)], q)
+        down = pack_logical(method, [(ck.payload(m["down"]), ck_shapes[m["down"]])], q,
+                            (tp_rank * inter, (tp_rank + 1) * inter))
+        p = f"model.layers.{i}"
+        lw = LayerWeights(ln1=ck.store.get(f"{p}.input_layernorm.weight").to(device, bf),
+                          ln2=ck.store.get(f"{p}.post_attention_layernorm.weight").to(device, bf),
+                          qkv=qkv.to(device), o=o.to(device), gate_up=gu.to(device), down=down.to(device))
+        if cfg.qk_norm:
+            lw.q_norm = ck.store.get(f"{p}.self_attn.q_norm.weight").to(device, bf)
+            lw.k_norm = ck.store.get(f"{p}.self_attn.k_norm.weight").to(device, bf)
+        layers.append(lw)
+    embed_full = ck.store.get("model.embed_tokens.weight").to(device, bf)
+    v_local = cfg.vocab_size // tp_size
+    head = embed_full if cfg.tie_embeddings else ck.store.get("lm_head.weight").to(device, bf)
+    head = head[tp_rank * v_local:(tp_rank + 1) * v_local].contiguous()
+    return DecoderWeights(embed=embed_full[tp_rank * v_local:(tp_rank + 1) * v_local], layers=layers,
+                          final_norm=ck.store.get("model.norm.weight").to(device, bf), lm_head=wq_pack.pack_bf16(head),
+                          vocab_start=tp_rank * v_local, extras={"embed_full": embed_full})
+
+
+# ------------------------------------------------------- random checkpoints
+def _quant_config_json(q: QuantSpec) -> dict | None:
+    if q.method == "none":
+        return None
+    if q.method == "cubic":
+        return {"quant_method": "cubic", "format": "cubic-pack-quantized", "ignore": ["lm_head"], "config_groups": {
+            "group_0": {"targets": ["Linear"], "input_activations": None, "weights": {
+                "num_bits": q.bits, "group_size": q.group_size, "dynamic": False, "symmetric": True,
+                "packing": "little-endian-bitstream", "reserved_code": "zero",
+                "metadata_format": cubic.METADATA_A, "scale_dtype": "float32", "param_dtype": "float16"}}}}
+    if q.method == "int":
+        return {"quant_method": "compressed-tensors", "format": "pack-quantized", "ignore": ["lm_head"], "config_groups": {
+            "group_0": {"targets": ["Linear"], "weights": {"num_bits": q.bits, "group_size": q.group_size,
+                                                           "symmetric": True, "type": "int", "strategy": "group"}}}}
+    if q.method == "awq":
+        return {"quant_method": "awq", "bits": 4, "group_size": q.group_size, "version": "gemm", "zero_point": True}
+    if q.method == "fp8":
+        return {"quant_method": "compressed-tensors", "format": "float-quantized", "config_groups": {
+            "group_0": {"targets": ["Linear"], "weights": {"num_bits": 8, "type": "float", "strategy": "channel"}}}}
+    if q.method == "fp8_block":
+        return {"quant_method": "fp8", "weight_block_size": [128, 128]}
+    if q.method == "nvfp4":
+        return {"quant_method": "compressed-tensors", "format": "nvfp4-pack-quantized", "config_groups": {
+            "group_0": {"targets": ["Linear"], "weights": {"num_bits": 4, "type": "float", "group_size": 16}}}}
+    raise CheckpointError(q.method)
+
+
+def quantize_payload(w: torch.Tensor, q: QuantSpec) -> dict[str, torch.Tensor]:
+    if q.method == "none":
+        return {"weight": w.to(torch.bfloat16)}
+    if q.method == "cubic":
+        return cubic.quantize(w, cubic.CubicScheme(q.bits, q.group_size))
+    if q.method == "int":
+        return formats.int_quantize(w, q.bits, q.group_size, True)
+    if q.method == "awq":
+        n, k = w.shape
+        g = q.group_size
+        wg = w.float().reshape(n, k // g, g)
+        lo, hi = wg.amin(-1), wg.amax(-1)
+        s = ((hi - lo) / 15).clamp_min(1e-8)
+        z = torch.round(-lo / s).clamp(0, 15)
+        qv = torch.round(wg / s[..., None] + z[..., None]).clamp(0, 15).reshape(n, k)
+        return {"qweight": formats.awq_pack(qv.t().contiguous()), "qzeros": formats.awq_pack(z.t().contiguous()),
+                "scales": s.t().contiguous().half()}
+    if q.method == "fp8":
+        return formats.fp8_quantize(w, block=False)
+    if q.method == "fp8_block":
+        return formats.fp8_quantize(w, block=True)
+    if q.method == "nvfp4":
+        return formats.nvfp4_quantize(w)
+    raise CheckpointError(q.method)
+
+
+def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Path:
+    """Random-init decoder written as a HuggingFace-style directory in ``cfg.quant``'s on-disk format."""
+    from safetensors.torch import save_file
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    g = torch.Generator().manual_seed(seed)
+    linears, plain = logical_inventory(cfg)
+    tensors: dict[str, torch.Tensor] = {}
+    for module, (n, k) in linears.items():
+        w = torch.randn(n, k, generator=g) * std
+        for suffix, t in quantize_payload(w, cfg.quant).items():
+            tensors[f"{module}.{suffix}"] = t.contiguous()
+    for name in plain:
+        if name.endswith("norm.weight"):
+            tensors[name] = torch.ones(cfg.head_dim if "_norm" in name.split(".")[-2] and "self_attn" in name else cfg.hidden_size,
+                                       dtype=torch.bfloat16)
+        elif name.endswith("mlp.gate.weight"):
+            tensors[name] = (torch.randn(cfg.num_experts, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
+        else:
+            tensors[name] = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
+    save_file(tensors, str(path / "model.safetensors"))
+    hf = {"architectures": ["Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_norm else "LlamaForCausalLM")],
+          "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_q_heads,
+          "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size,
+          "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,
+          "tie_word_embeddings": cfg.tie_embeddings, "max_position_embeddings": cfg.max_position, "_name_or_path": cfg.name}
+    if cfg.is_moe:
+        hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token,
+                  moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)
+    qc = _quant_config_json(cfg.quant)
+    if qc:
+        hf["quantization_config"] = qc
+    (path / "config.json").write_text(json.dumps(hf, indent=1))
+    return path

@@ -1,0 +1,79 @@
+import pytest
+import torch
+
+from cubic_serve_b200.ops import wq_pack
+from cubic_serve_b200.quantization import formats as F
+
+
+def _rel(a, b):
+    return ((a - b).norm() / b.norm()).item()
+
+
+@pytest.mark.parametrize("bits,sym", [(4, True), (4, False), (8, True), (3, True)])
+def test_int_roundtrip(bits, sym):
+    w = torch.randn(64, 256, generator=torch.Generator().manual_seed(bits)) * 0.02
+    p = F.int_quantize(w, bits, 128, sym)
+    per = 32 // bits
+    assert p["weight_packed"].shape == (64, -(-256 // per)) and p["weight_packed"].dtype == torch.int32
+    d = F.int_dense(p, bits, 128, (64, 256))
+    assert _rel(d, w) < {3: 0.35, 4: 0.15, 8: 0.01}[bits]
+    q, s, z = F.int_decode(p, bits, 128, (64, 256))
+    assert int(q.max()) < (1 << bits) and s.shape == (64, 2)
+    if bits == 4:
+        pw = F.to_packed_weight("int", p, (64, 256), 4, 128)
+        assert pw.fmt == wq_pack.FMT_AFFINE4 and _rel(wq_pack.unpack_to_dense(pw), d) < 5e-3
+
+
+def test_int_word_layout_is_lsb_first():
+    codes = torch.tensor([[1, 2, 3, 4, 5, 6, 7, 8, 9]])
+    words = F.int_pack(codes, 4)
+    assert words.tolist() == [[0x87654321 - 2 ** 32, 9]]
+    assert F.int_unpack(words, 4, 9).tolist() == codes.tolist()
+
+
+def test_awq_order_and_decode():
+    vals = torch.arange(16).reshape(1, 16) % 16
+    w = F.awq_pack(vals)
+    # value i of a group of eight sits at nibble position AWQ_ORDER.index(i)
+    assert (int(w[0, 0]) >> (4 * F.AWQ_ORDER.index(3))) & 15 == 3
+    assert F.awq_unpack(w).tolist() == vals.tolist()
+    g = torch.Generator().manual_seed(0)
+    k, n, grp = 128, 64, 64
+    q = torch.randint(0, 16, (k, n), generator=g)
+    z = torch.randint(0, 16, (k // grp, n), generator=g)
+    s = (torch.rand(k // grp, n, generator=g) * 0.01 + 0.001).half()
+    payload = {"qweight": F.awq_pack(q), "qzeros": F.awq_pack(z), "scales": s}
+    dense = F.awq_dense(payload, grp)
+    expect = ((q.float() - z.repeat_interleave(grp, 0).float()) * s.float().repeat_interleave(grp, 0)).t()
+    assert torch.allclose(dense, expect)
+    pw = F.to_packed_weight("awq", payload, (n, k), 4, grp)
+    assert _rel(wq_pack.unpack_to_dense(pw), dense) < 5e-3
+
+
+def test_fp8_channel_and_block():
+    w = torch.randn(200, 300, generator=torch.Generator().manual_seed(1)) * 0.05
+    assert _rel(F.fp8_dense(F.fp8_quantize(w)), w) < 0.04
+    pb = F.fp8_quantize(w, block=True)
+    assert pb["weight_scale_inv"].shape == (2, 3)
+    assert _rel(F.fp8_dense(pb), w) < 0.04
+    q, s = F.fp8_activation_quantize(torch.zeros(2, 8))
+    assert float(s.min()) == pytest.approx(1.0 / (448 * 512))
+
+
+def test_nvfp4_levels_and_both_global_conventions():
+    w = torch.randn(32, 128, generator=torch.Generator().manual_seed(2)) * 0.02
+    p = F.nvfp4_quantize(w)
+    assert p["weight_packed"].shape == (32, 64) and p["weight_scale"].dtype == torch.float8_e4m3fn
+    d = F.nvfp4_dense(p)
+    assert _rel(d, w) < 0.15
+    modelopt = {"weight": p["weight_packed"], "weight_scale": p["weight_scale"],
+                "weight_scale_2": 1.0 / p["weight_global_scale"]}
+    assert torch.allclose(F.nvfp4_dense(modelopt), d, rtol=1e-5)
+    # nibble semantics: 0x9 -> -0.5, 0x7 -> 6 ; low nibble first
+    one = {"weight_packed": torch.tensor([[0x79] * 8], dtype=torch.uint8),
+           "weight_scale": torch.ones(1, 1).to(torch.float8_e4m3fn), "weight_global_scale": torch.ones(1)}
+    assert F.nvfp4_dense(one)[0, :2].tolist() == [-0.5, 6.0]
+    pw = F.to_packed_weight("nvfp4", p, (32, 128))
+    assert _rel(wq_pack.unpack_to_dense(pw), d) < 1e-5
+    xq, xs = F.nvfp4_activation_quantize(torch.randn(4, 64), 100.0)
+    assert xq.shape == (4, 64) and xs.shape == (4, 4)
