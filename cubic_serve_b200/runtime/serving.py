@@ -1,0 +1,125 @@
+"""Assemble a serving stack from CLI arguments and run it behind an HTTP server.
+
+``build_backend`` follows the reference's start-up order (``cli.py:1074`` ``_serve_model`` /
+``runtime/quantized_graph.py:263`` worker there): read the device memory budget, admit the checkpoint, load
+rank-local weights, size the KV page pool from the memory that is left, capture the decode graph buckets
+(largest first), then open the door.
+"""
+from __future__ import annotations
+
+import logging
+import threading
+import time
+from pathlib import Path
+
+log = logging.getLogger("cubic.serve")
+
+
+def _tokenizer_for(model: str, vocab_size: int):
+    path = Path(model)
+    if path.is_dir() and any((path / f).exists() for f in ("tokenizer.json", "tokenizer_config.json")):
+        from transformers import AutoTokenizer
+        return AutoTokenizer.from_pretrained(str(path))
+    from ..inputs.chat import ByteTokenizer
+    tok = ByteTokenizer()
+    if tok.vocab_size > vocab_size:
+        raise SystemExit("the built-in byte tokenizer needs a vocabulary of at least 259 entries")
+    return tok
+
+
+def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int, v_bits: int, max_model_len: int,
+                  max_running: int) -> int:
+    """Pages that fit in the remaining device memory (one page = 16 tokens of every layer's rank-local KV heads)."""
+    from ..ops.kernels import kv_blob_bytes
+    per_page = cfg.num_layers * (cfg.num_kv_heads // tp) * kv_blob_bytes(cfg.head_dim, k_bits, v_bits)
+    budget = max(0, free_bytes - reserve_bytes)
+    pages = budget // per_page
+    cap = max_running * (-(-max_model_len // 16)) + 64
+    return int(max(64, min(pages, cap)))
+
+
+def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: int):
+    import torch
+
+    from ..models.config import NAMED_CONFIGS
+    from ..runtime.async_engine import TokenChatBackend
+    from ..runtime.engine import LLMEngine
+    from ..runtime.scheduler import SchedulerConfig
+    if tp != 1 or args.pp_size != 1:
+        from ..executor.multiproc import build_multiproc_backend
+        return build_multiproc_backend(args, devices, tp, spec, k_bits, v_bits)
+    model = args.model
+    eager = args.execution_mode != "cuda" or not torch.cuda.is_available()
+    if model.startswith("random:"):
+        cfg = NAMED_CONFIGS[model.split(":", 1)[1]]()
+        ck = None
+    else:
+        from ..models.checkpoint import admit_checkpoint
+        ck = admit_checkpoint(model)
+        cfg = ck.cfg
+    max_len = args.max_model_len or min(cfg.max_position, 8192)
+    sched = SchedulerConfig(max_running_requests=args.max_running_requests, max_batched_tokens=args.token_budget,
+                            prefill_chunk_tokens=min(args.prefill_chunk_tokens, args.token_budget), max_model_len=max_len,
+                            enable_prefix_cache=args.prefix_cache)
+    if eager:
+        from ..executor.eager_executor import EagerPagedExecutor
+        from ..models.reference import random_dense_weights
+        if ck is not None:
+            raise SystemExit("eager execution mode serves random:<config> models only")
+        pages = 4096
+        executor = EagerPagedExecutor(cfg, random_dense_weights(cfg, args.seed), pages, kv_bits=(k_bits, v_bits))
+    else:
+        from ..executor.gpu_executor import GpuExecutor
+        from ..models.checkpoint import load_decoder_weights
+        from ..models.decoder import DecoderRunner, random_decoder_weights
+        dev = torch.device("cuda", devices[0])
+        torch.cuda.set_device(dev)
+        weights = load_decoder_weights(ck, dev) if ck is not None else random_decoder_weights(cfg, dev, args.seed)
+        free, _total = torch.cuda.mem_get_info(dev)
+        if args.gpu_memory_gib:
+            free = min(free, int(args.gpu_memory_gib * 2 ** 30) - torch.cuda.memory_allocated(dev))
+        pages = plan_kv_pages(free, int(args.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, 1, k_bits, v_bits, max_len,
+                              args.max_running_requests)
+        runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits)
+        executor = GpuExecutor(runner, max_rows=args.max_running_requests, max_prefill_tokens=args.token_budget,
+                               max_model_len=max_len)
+        caps = executor.capture_decode_graphs()
+        log.info("captured decode graphs for capacities %s; %d KV pages", caps, pages)
+    tok = _tokenizer_for(model, cfg.vocab_size)
+    engine = LLMEngine(executor, num_pages=pages, scheduler_config=sched, eos_token_id=getattr(tok, "eos_token_id", None))
+    backend = TokenChatBackend(engine, tok, default_thinking=args.thinking)
+    return backend, (args.served_model_name or cfg.name)
+
+
+class StatusReporter(threading.Thread):
+    """``[STATUS]`` line every 10 s of activity (reference: ``runtime/logging.py:316``)."""
+
+    def __init__(self, backend, period: float = 10.0) -> None:
+        super().__init__(daemon=True, name="cubic-status")
+        self.backend, self.period = backend, period
+        self._last_tokens = 0
+
+    def run(self) -> None:
+        while self.backend.ready:
+            time.sleep(self.period)
+            eng = self.backend.engine
+            s = eng.stats()
+            tokens = self.backend.stats["tokens"]
+            rate = (tokens - self._last_tokens) / self.period
+            self._last_tokens = tokens
+            if s["running"] or s["waiting"] or rate:
+                log.info("[STATUS] n_req=%d waiting=%d kv=%.0f%% prefix=%.0f%% decode=%.1f tok/s", s["running"],
+                         s["waiting"], 100 * s["kv_used_frac"], 100 * s["prefix_hit_rate"], rate)
+
+
+def run_http_server(backend, model_name: str, args) -> int:
+    import uvicorn
+
+    from ..api.server import CubicASGIApp
+    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    app = CubicASGIApp(backend, model_name, args.served_model_name, args.api_key)
+    StatusReporter(backend).start()
+    config = uvicorn.Config(app, host=args.host, port=args.port, log_level="warning",
+                            timeout_keep_alive=args.http_keep_alive_seconds, lifespan="on")
+    uvicorn.Server(config).run()
+    return 0

@@ -1,0 +1,70 @@
+"""Random checkpoints in every on-disk format: closed inventory, decode, TP slicing, GEMM packing."""
+import json
+from dataclasses import replace
+
+import pytest
+import torch
+
+from cubic_serve_b200.models import checkpoint as C
+from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+from cubic_serve_b200.ops import wq_pack
+
+BASE = ModelConfig(name="tiny", num_layers=2, hidden_size=256, num_q_heads=4, num_kv_heads=2, head_dim=128,
+                   intermediate_size=512, vocab_size=320, qk_norm=True)
+
+
+@pytest.mark.parametrize("method,bits,group", [("cubic", 4, 128), ("int", 4, 128), ("int", 8, 128), ("awq", 4, 128),
+                                               ("fp8", 8, 0), ("fp8_block", 8, 128), ("nvfp4", 4, 16), ("none", 16, 0)])
+def test_write_admit_load(tmp_path, method, bits, group):
+    cfg = replace(BASE, quant=QuantSpec(method, bits, group))
+    path = C.write_random_checkpoint(tmp_path / method, cfg, seed=1)
+    ck = C.admit_checkpoint(path)
+    assert ck.cfg.quant.method == method and ck.cfg.num_layers == 2 and ck.cfg.qk_norm
+    info = C.inspect_checkpoint(path)
+    assert info["logical_linears"] == 2 * 7
+    # dense decode of one module equals the packed GEMM operand built from it
+    mod = "model.layers.1.mlp.down_proj"
+    dense = C._dense_of(method, ck.payload(mod), (256, 512), cfg.quant)
+    assert dense.shape == (256, 512) and float(dense.abs().mean()) > 1e-4
+    w = C.load_decoder_weights(ck, "cpu")
+    got = wq_pack.unpack_to_dense(w.layers[1].down)
+    assert ((got - dense).norm() / dense.norm()).item() < 6e-3
+    q = C._dense_of(method, ck.payload("model.layers.0.self_attn.q_proj"), (512, 256), cfg.quant)
+    k = C._dense_of(method, ck.payload("model.layers.0.self_attn.k_proj"), (256, 256), cfg.quant)
+    v = C._dense_of(method, ck.payload("model.layers.0.self_attn.v_proj"), (256, 256), cfg.quant)
+    qkv = wq_pack.unpack_to_dense(w.layers[0].qkv)
+    assert ((qkv - torch.cat([q, k, v])).norm() / qkv.norm()).item() < 6e-3
+    # tensor-parallel rank 1 of 2: whole heads of q/k/v, column shard of o/down
+    w1 = C.load_decoder_weights(ck, "cpu", tp_rank=1, tp_size=2)
+    qkv1 = wq_pack.unpack_to_dense(w1.layers[0].qkv)
+    assert ((qkv1 - torch.cat([q[256:], k[128:], v[128:]])).norm() / qkv1.norm()).item() < 6e-3
+    d1 = wq_pack.unpack_to_dense(w1.layers[1].down)
+    assert ((d1 - dense[:, 256:]).norm() / d1.norm()).item() < 6e-3
+    assert w1.vocab_start == 160 and w1.lm_head.n == 160
+
+
+def test_closed_inventory_rejects_stray_and_missing(tmp_path):
+    from safetensors.torch import load_file, save_file
+    cfg = replace(BASE, quant=QuantSpec("cubic", 4, 128))
+    path = C.write_random_checkpoint(tmp_path / "c", cfg)
+    t = load_file(str(path / "model.safetensors"))
+    t["model.layers.0.stray"] = torch.zeros(1)
+    save_file(t, str(path / "model.safetensors"))
+    with pytest.raises(C.CheckpointError, match="no logical weight owns"):
+        C.admit_checkpoint(path)
+    del t["model.layers.0.stray"], t["model.norm.weight"]
+    save_file(t, str(path / "model.safetensors"))
+    with pytest.raises(C.CheckpointError, match="missing tensor"):
+        C.admit_checkpoint(path)
+
+
+def test_quantization_config_parsing_variants():
+    from cubic_serve_b200.models.config import quant_spec_from_hf
+    assert quant_spec_from_hf({}).method == "none"
+    assert quant_spec_from_hf({"quant_method": "awq", "bits": 4, "group_size": 64}).group_size == 64
+    assert quant_spec_from_hf({"quant_method": "modelopt", "quant_algo": "NVFP4"}).method == "nvfp4"
+    assert quant_spec_from_hf({"quant_method": "fp8", "weight_block_size": [128, 128]}).method == "fp8_block"
+    c = quant_spec_from_hf({"format": "cubic-pack-quantized", "config_groups": {"g": {"weights": {"num_bits": 4, "group_size": [1, 64]}}}})
+    assert (c.method, c.bits, c.group_size) == ("cubic", 4, 64)
+    with pytest.raises(ValueError):
+        quant_spec_from_hf({"quant_method": "bitsandbytes"})

@@ -1,0 +1,49 @@
+import argparse
+
+import pytest
+
+from cubic_serve_b200 import cli
+from cubic_serve_b200.models.config import dense_8b_config
+from cubic_serve_b200.runtime.serving import plan_kv_pages
+
+
+def test_serve_flag_surface():
+    a = cli.build_parser().parse_args([
+        "serve", "random:toy", "--devices", "0-3", "--tp-size", "4", "--k-cache-dtype", "int4", "--v-cache-dtype", "int8",
+        "--no-prefix-cache", "--max-running-requests", "64", "--speculative-config",
+        '{"method":"mtp","num_speculative_tokens":3,"mode":"dynamic"}', "--api-key", "k", "--no-thinking"])
+    assert cli.parse_devices(a.devices) == [0, 1, 2, 3] and a.tp_size == 4 and a.prefix_cache is False
+    assert a.thinking is False and a.k_cache_dtype == "int4"
+    spec = cli.parse_speculative_config(a.speculative_config)
+    assert (spec.method, spec.num_speculative_tokens, spec.mode) == ("mtp", 3, "dynamic")
+    cli.validate_topology([0, 1, 2, 3], 4, 1, 2, spec)
+
+
+@pytest.mark.parametrize("text", ['{"method":"eagle"}', '{"method":"mtp","num_speculative_tokens":9}', "not json",
+                                  '{"method":"mtp","num_speculative_tokens":2,"mode":"x"}'])
+def test_bad_speculative_config(text):
+    with pytest.raises(argparse.ArgumentTypeError):
+        cli.parse_speculative_config(text)
+
+
+def test_topology_rules():
+    none = cli.SpeculativeConfig()
+    with pytest.raises(SystemExit):
+        cli.validate_topology([0, 1], 2, 3, 1, none)
+    with pytest.raises(SystemExit):
+        cli.validate_topology([0, 1, 2], 2, 1, 1, none)
+    with pytest.raises(SystemExit):
+        cli.validate_topology([0, 1, 2, 3], 4, 1, 3, none)
+    with pytest.raises(SystemExit):
+        cli.validate_topology([0, 1, 2, 3], 2, 2, 1, cli.SpeculativeConfig("mtp", 2))
+    assert cli.parse_devices("0,2,5") == [0, 2, 5] and cli.parse_devices("4..7") == [4, 5, 6, 7]
+    with pytest.raises(argparse.ArgumentTypeError):
+        cli.parse_devices("1,1")
+
+
+def test_kv_page_planning():
+    cfg = dense_8b_config()
+    pages = plan_kv_pages(100 << 30, 4 << 30, cfg, 1, 8, 8, 2048, 256)
+    per_page = 36 * 8 * 4608
+    assert pages == min((96 << 30) // per_page, 256 * 128 + 64)
+    assert plan_kv_pages(100 << 30, 4 << 30, cfg, 8, 4, 8, 2048, 256) == 256 * 128 + 64
