@@ -295,7 +295,7 @@ paged_attn_kernel(const AttnParams p) {
   bool ok = true;
   for (int i = 0; i < my_pages && ok; ++i) {
     const int s = i % kAttnStages;
-    ok = mbar_wait(smem_u32(&my_bars[s]), static_cast<uint32_t>(i / kAttnStages) & 1u, abort_flag);
+    ok = mbar_wait_t<20>(smem_u32(&my_bars[s]), static_cast<uint32_t>(i / kAttnStages) & 1u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
     process_page<KBITS, VBITS>(my_stages + s * stage_stride, p.lay, qf, st, (first + i * kAttnWarps) * kPageTokens,

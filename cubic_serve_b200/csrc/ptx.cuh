@@ -70,19 +70,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any role gives up it
-// is set and every other waiter returns false immediately.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+// is set and every other waiter returns false (checked every 256 polls, like
+// the clock budget, so that the poll loop itself stays two instructions long).
+//
+// kSleepNs > 0 puts the warp to sleep between polls.  A CTA of this library has
+// one MMA-issuing thread and one copy-issuing thread on the critical path and
+// hundreds of consumer threads; consumers that poll hot take the issue slots
+// the two critical threads need (measured: the MMA thread's loop took 680
+// cycles per k-block next to 16 spinning warps).  Consumers therefore use a
+// sleeping wait, the two critical threads the hot one.
+template <int kSleepNs>
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
+  long long t0 = 0;
+  uint32_t polls = 0;
   while (true) {
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
-      *abort_flag = 1;
-      return false;
+    if ((++polls & 0xFFu) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  return mbar_wait_t<0>(bar, parity, abort_flag);
+}
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  return mbar_wait_t<32>(bar, parity, abort_flag);
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA / UMMA)

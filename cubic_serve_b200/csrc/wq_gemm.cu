@@ -13,10 +13,10 @@
 // Pipeline per k-block (64 columns of K), S stages:
 //   warp 0   : bulk copy of the packed weight tile (4 KiB) + its group metadata
 //              (1 KiB) and a TMA tile load of x (128-byte swizzle)  -> full[s]
-//   warps 2-9: wait full[s]; decode 4-bit codes -> bf16, write the swizzled
+//   warps 2-17: wait full[s]; decode 4-bit codes -> bf16, write the swizzled
 //              K-major A tile in shared memory                      -> ready[s]
 //   warp 1   : wait ready[s]; 4 x tcgen05.mma (K=16) into TMEM; commit -> empty[s]
-//   warps 2-9: epilogue, tcgen05.ld -> registers -> bf16 (or fp32 split-K
+//   warps 2-17: epilogue, tcgen05.ld -> registers -> bf16 (or fp32 split-K
 //              partials whose last-arriving CTA sums them in split order).
 //
 // Packed weight storage is produced at load time by ops/wq_pack.py:
@@ -42,7 +42,7 @@ static constexpr int kBlockK = 64;       // K columns per stage (one 128-byte sw
 static constexpr int kCodeBytes = 4096;  // 128 x 64 x 4 bit
 static constexpr int kMetaBytes = 1024;
 static constexpr int kATileBytes = kTileN * kBlockK * 2;  // 16 KiB bf16
-static constexpr int kNumDequantWarps = 8;
+static constexpr int kNumDequantWarps = 16;  // 4 per scheduler: the decode chains are latency-bound with fewer
 static constexpr int kThreads = (2 + kNumDequantWarps) * 32;
 
 // Tensor-parallel links of a launch (all pointers are device addresses valid on
@@ -89,6 +89,7 @@ struct WqGemmParams {
   float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
   uint32_t tmem_cols;       // power of two >= max(32, mb)
   TpLink tp;
+  unsigned long long* trace;  // optional pipeline timeline of CTA (0,0,0): [iteration][8] clock64 stamps
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -238,6 +239,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
+  unsigned long long* trace = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -279,8 +281,10 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           const int s = i % S;
           const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
+          if (trace) trace[i * 8 + 0] = clock64();
           load_weights(i);
           load_x(i);
+          if (trace) trace[i * 8 + 1] = clock64();
         }
       }
     }
@@ -292,9 +296,11 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       for (int i = 0; i < iters && ok; ++i) {
         const int s = i % S;
         const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
-        ok = mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag);
-        if (ok && FMT != kFmtBf16) ok = mbar_wait(smem_u32(&ctl->ready[s]), ph, abort_flag);
+        // decoded formats: `ready` implies `full` (the decode warps waited for the copies themselves)
+        ok = (FMT == kFmtBf16) ? mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag)
+                               : mbar_wait(smem_u32(&ctl->ready[s]), ph, abort_flag);
         if (!ok) break;
+        if (trace) trace[i * 8 + 4] = clock64();
         tc_fence_after();
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint64_t bdesc = umma_desc_sw128(smem_u32(st));
@@ -305,22 +311,26 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           umma_f16(tmem_base, adesc + 2u * k4, bdesc + 2u * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
         }
         tc_commit(smem_u32(&ctl->empty[s]));
+        if (trace) trace[i * 8 + 5] = clock64();
       }
       tc_commit(smem_u32(&ctl->acc_full));
     }
   } else {
     // ------------------------------------------------- dequant + epilogue
-    const int dq = threadIdx.x - 64;  // 0..255
+    const int dq = threadIdx.x - 64;  // 0..511
     const int r = dq & 127;           // row of the weight tile
-    const int h = dq >> 7;            // which 32-column half of the k-block
+    const int part = dq >> 7;         // 16-column quarter of the k-block this thread decodes
+    const int h = part >> 1;          // 32-column half (metadata sub-block)
+    const int q = part & 1;           // 16-column quarter inside the half
     if (FMT != kFmtBf16) {
       for (int i = 0; i < iters; ++i) {
         const int s = i % S;
         const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
-        if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
+        if (!mbar_wait_relaxed(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
+        if (trace && dq == 0) trace[i * 8 + 2] = clock64();
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint8_t* pk = st + x_bytes + kATileBytes;
-        const uint4 words = *reinterpret_cast<const uint4*>(pk + (h * 128 + r) * 16);
+        const uint2 words = *reinterpret_cast<const uint2*>(pk + (h * 128 + r) * 16 + q * 8);
         const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
         // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
         uint32_t c0, c1, c2, c1b = 0;
@@ -337,29 +347,33 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           c1b = c1;
         }
         uint8_t* arow = st + x_bytes + (r >> 3) * 1024 + (r & 7) * 128;
-        const uint32_t wv[4] = {words.x, words.y, words.z, words.w};
+        const uint32_t wv[2] = {words.x, words.y};
+        uint32_t o[2][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t o[4];
+        for (int j = 0; j < 2; ++j) {
           if (FMT == kFmtNvfp4) {
-            // columns 32h + 8j ..: block scale index (8j)/16 selects low/high half
-            decode8<FMT>(wv[j], (j < 2) ? c0 : c1b, 0u, 0u, o);
+            // columns 32h + 16q + 8j: the 16-column block scale is the low (q = 0) or high (q = 1) half
+            decode8<FMT>(wv[j], q ? c1b : c0, 0u, 0u, o[j]);
           } else {
-            decode8<FMT>(wv[j], c0, c1, c2, o);
+            decode8<FMT>(wv[j], c0, c1, c2, o[j]);
           }
-          const int chunk = h * 4 + j;
-          *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int chunk = h * 4 + q * 2 + j;
+          *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->ready[s]));
+        if (trace && dq == 0) trace[i * 8 + 3] = clock64();
       }
     }
     // epilogue: TMEM lane = output feature, column = batch row
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->acc_full), 0, abort_flag));
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_t<200>(smem_u32(&ctl->acc_full), 0, abort_flag));
     tc_fence_after();
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
-    const int pair = (warp - 2) >> 2;        // two warps share a quadrant; alternate chunks
+    const int pair = (warp - 2) >> 2;        // four warps share a quadrant; they interleave 16-column chunks
     const int n = n_tile * kTileN + quad * 32 + lane;
     const int chunks = p.mb >> 4;
     // where element (m, n) of the result goes: the local output, or (scatter-push)
@@ -377,7 +391,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     };
     if (acc_ok && iters > 0) {
       if (p.splits == 1) {
-        for (int ci = pair; ci < chunks; ci += 2) {
+        for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
           uint32_t acc[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
           tmem_ld_wait();
@@ -394,7 +408,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       } else {
         float* ws = p.workspace +
                     ((static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits + split) * (static_cast<size_t>(p.mb) * kTileN);
-        for (int ci = pair; ci < chunks; ci += 2) {
+        for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
           uint32_t acc[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
           tmem_ld_wait();
@@ -420,14 +434,14 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __threadfence();
         const float* wsb = p.workspace +
                            (static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits * (static_cast<size_t>(p.mb) * kTileN);
-        const size_t part = static_cast<size_t>(p.mb) * kTileN;
+        const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
         const int nn = n_tile * kTileN + r;
         if (nn < p.N) {
-          for (int mm = h; mm < p.mb; mm += 2) {
+          for (int mm = part; mm < p.mb; mm += 4) {
             const int m = m0 + mm;
             if (m >= p.M) break;
             float v = 0.f;
-            for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(wsb + sp * part + static_cast<size_t>(mm) * kTileN + r);
+            for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(wsb + sp * part_elems + static_cast<size_t>(mm) * kTileN + r);
             store_out(m, nn, v * p.alpha);
           }
         }
@@ -513,7 +527,17 @@ static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemm
 
 }  // namespace cb
 
+static unsigned long long* g_trace_buffer = nullptr;
+static int g_stage_override = 0;
+
 extern "C" {
+
+// Debug hooks: a device buffer of [k-blocks][8] 64-bit words receives the pipeline timeline of CTA (0,0,0)
+// of every following launch (null switches it off); a non-zero stage count overrides the automatic choice.
+void cb_wq_gemm_debug(void* trace_buffer, int stages) {
+  g_trace_buffer = static_cast<unsigned long long*>(trace_buffer);
+  g_stage_override = stages;
+}
 
 // Bytes of split-K workspace / counters a launch with these sizes needs.
 long long cb_wq_gemm_workspace_bytes(int M, int N, int splits) {
@@ -591,7 +615,9 @@ int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SmemCtl);
   int stages = static_cast<int>(budget / stage);
   if (stages > 8) stages = 8;
+  if (g_stage_override > 0 && g_stage_override < stages) stages = g_stage_override;
   if (stages < 2) return -14;
+  p.trace = g_trace_buffer;
   p.stages = stages;
   const size_t smem = stages * stage + sizeof(SmemCtl) + 1024;
 

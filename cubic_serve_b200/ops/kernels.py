@@ -76,7 +76,8 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     m_tiles = -(-m // 256)
     tiles = n_tiles * m_tiles
     k_blocks = k // 64
-    if tiles >= sms or k_blocks < 8:
+    if tiles >= sms or k_blocks < 8 or m > 128:
+        # with >= 128 batch rows the fp32 partial tiles (512 B per row and tile) cost more than the idle SMs
         return 1
     splits = max(1, sms // tiles)
     return max(1, min(splits, k_blocks // 4, 16))
