@@ -89,6 +89,11 @@ struct WqGemmParams {
   float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
   uint32_t tmem_cols;       // power of two >= max(32, mb)
   TpLink tp;
+  // grouped (mixture-of-experts) mode: blockIdx.y indexes a device-side work list
+  // group_tiles = {count, then {expert, first row, rows} per item}; rows are contiguous in x / y; weights
+  // of expert e start at codes + e * group_code_stride (meta likewise).  Split-K is not combined with it.
+  const int* group_tiles;
+  size_t group_code_stride, group_meta_stride;
   unsigned long long* trace;  // optional pipeline timeline of CTA (0,0,0): [iteration][8] clock64 stamps
 };
 
@@ -209,9 +214,24 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tile = blockIdx.x;
-  const int split = blockIdx.y;
+  const bool grouped = p.group_tiles != nullptr;
+  const int split = grouped ? 0 : blockIdx.y;
   const int m_tile = blockIdx.z;
-  const int m0 = m_tile * p.mb;
+  int m0 = m_tile * p.mb;
+  int m_end = p.M;                       // first row this CTA must NOT write
+  const uint8_t* codes_base = p.codes;
+  const uint8_t* meta_base = p.meta;
+  int w_row0 = 0;                        // bf16 weights: first row of this expert in the stacked [E * N, K] matrix
+  if (grouped) {
+    const int item = blockIdx.y;
+    if (item >= p.group_tiles[0]) return;   // uniform for the CTA, before any barrier or TMEM allocation
+    const int e = p.group_tiles[1 + 3 * item];
+    m0 = p.group_tiles[2 + 3 * item];
+    m_end = m0 + p.group_tiles[3 + 3 * item];
+    w_row0 = e * p.N;
+    codes_base += static_cast<size_t>(e) * p.group_code_stride;
+    meta_base += static_cast<size_t>(e) * p.group_meta_stride;
+  }
   const int S = p.stages;
 
   // k-block range of this split (balanced contiguous ranges)
@@ -246,74 +266,89 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
       const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? kATileBytes : kCodeBytes + kMetaBytes);
-      auto load_weights = [&](int i) {
-        const int s = i % S;
+      // stage index and phase are carried as counters: `i % S` and `i / S` with a run-time S cost two
+      // integer divisions (~300 cycles on one thread), which was most of the per-k-block time of this loop
+      auto load_weights = [&](int i, int s) {
         const int kb = kb_lo + i;
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint32_t bar = smem_u32(&ctl->full[s]);
         mbar_expect_tx(bar, tx);
         if (FMT == kFmtBf16) {
-          tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, n_tile * kTileN, bar);
+          tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row0 + n_tile * kTileN, bar);
         } else {
-          const uint8_t* csrc = p.codes + (static_cast<size_t>(n_tile) * p.k_blocks + kb) * kCodeBytes;
-          const uint8_t* msrc = p.meta + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMetaBytes;
+          const uint8_t* csrc = codes_base + (static_cast<size_t>(n_tile) * p.k_blocks + kb) * kCodeBytes;
+          const uint8_t* msrc = meta_base + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMetaBytes;
           bulk_g2s(smem_u32(st + x_bytes + kATileBytes), csrc, kCodeBytes, bar);
           bulk_g2s(smem_u32(st + x_bytes + kATileBytes + kCodeBytes), msrc, kMetaBytes, bar);
         }
       };
-      auto load_x = [&](int i) {
-        const int s = i % S;
+      auto load_x = [&](int i, int s) {
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         tma_load_2d(smem_u32(st), &tmap_x, (kb_lo + i) * kBlockK, m0, smem_u32(&ctl->full[s]));
       };
       // weights of the first S stages go out before anything else, so that an
       // all-gather still in flight overlaps with weight streaming
       const int pre = iters < S ? iters : S;
-      for (int i = 0; i < pre; ++i) load_weights(i);
+      for (int i = 0; i < pre; ++i) load_weights(i, i);
       bool ok = true;
       if (p.tp.mode & kTpGatherWait) {
         const uint32_t target = (p.tp.ag_state[0] + 1u) * p.tp.ag_expected;
         for (int r = 0; r < p.tp.size && ok; ++r) ok = wait_counter(p.tp.ag_flag + r, target, abort_flag);
       }
       if (ok) {
-        for (int i = 0; i < pre; ++i) load_x(i);
+        for (int i = 0; i < pre; ++i) load_x(i, i);
+        int s = 0;
+        uint32_t ph = 1;                      // second pass over the ring: wait for the first release
         for (int i = pre; i < iters; ++i) {
-          const int s = i % S;
-          const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
           if (trace) trace[i * 8 + 0] = clock64();
-          load_weights(i);
-          load_x(i);
+          load_weights(i, s);
+          load_x(i, s);
           if (trace) trace[i * 8 + 1] = clock64();
+          if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop with warp-uniform values and one elected lane issues the tcgen05
+    // instructions: descriptors and addresses then live in uniform registers instead of being moved
+    // there from a divergent lane's registers before every MMA.
+    {
+      const bool leader = elect_one();
       const uint32_t idesc = umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+      const uint32_t tmem_d = __shfl_sync(0xffffffffu, tmem_base, 0);
+      const uint32_t smem_base = smem_u32(smem);
+      const uint64_t desc_hi = umma_desc_sw128(0);      // every field except the start address
       bool ok = true;
+      int s = 0;
+      uint32_t ph = 0;
+      uint32_t accumulate = 0;
       for (int i = 0; i < iters && ok; ++i) {
-        const int s = i % S;
-        const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
         // decoded formats: `ready` implies `full` (the decode warps waited for the copies themselves)
         ok = (FMT == kFmtBf16) ? mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag)
                                : mbar_wait(smem_u32(&ctl->ready[s]), ph, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (trace) trace[i * 8 + 4] = clock64();
+        if (trace && leader) trace[i * 8 + 4] = clock64();
         tc_fence_after();
-        uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
-        const uint64_t bdesc = umma_desc_sw128(smem_u32(st));
-        const uint64_t adesc = umma_desc_sw128(smem_u32(st + x_bytes));
+        const uint32_t st = smem_base + static_cast<uint32_t>(s) * stage_bytes;
+        const uint64_t bdesc = desc_hi | static_cast<uint64_t>((st & 0x3FFFFu) >> 4);
+        const uint64_t adesc = desc_hi | static_cast<uint64_t>(((st + x_bytes) & 0x3FFFFu) >> 4);
+        if (leader) {
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
-          umma_f16(tmem_base, adesc + 2u * k4, bdesc + 2u * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          for (int k4 = 0; k4 < 4; ++k4) {
+            // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
+            umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+          }
+          tc_commit(smem_u32(&ctl->empty[s]));
         }
-        tc_commit(smem_u32(&ctl->empty[s]));
-        if (trace) trace[i * 8 + 5] = clock64();
+        accumulate = 1;
+        if (trace && leader) trace[i * 8 + 5] = clock64();
+        if (++s == S) { s = 0; ph ^= 1u; }
       }
-      tc_commit(smem_u32(&ctl->acc_full));
+      if (leader) tc_commit(smem_u32(&ctl->acc_full));
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------- dequant + epilogue
@@ -323,9 +358,9 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int h = part >> 1;          // 32-column half (metadata sub-block)
     const int q = part & 1;           // 16-column quarter inside the half
     if (FMT != kFmtBf16) {
+      int s = 0;
+      uint32_t ph = 0;
       for (int i = 0; i < iters; ++i) {
-        const int s = i % S;
-        const uint32_t ph = static_cast<uint32_t>(i / S) & 1u;
         if (!mbar_wait_relaxed(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
         if (trace && dq == 0) trace[i * 8 + 2] = clock64();
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
@@ -367,6 +402,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->ready[s]));
         if (trace && dq == 0) trace[i * 8 + 3] = clock64();
+        if (++s == S) { s = 0; ph ^= 1u; }
       }
     }
     // epilogue: TMEM lane = output feature, column = batch row
@@ -399,7 +435,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + ci * 16 + j;
-              if (m < p.M) {
+              if (m < m_end) {
                 store_out(m, n, __uint_as_float(acc[j]) * p.alpha);
               }
             }
@@ -435,14 +471,37 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const float* wsb = p.workspace +
                            (static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits * (static_cast<size_t>(p.mb) * kTileN);
         const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
-        const int nn = n_tile * kTileN + r;
-        if (nn < p.N) {
-          for (int mm = part; mm < p.mb; mm += 4) {
-            const int m = m0 + mm;
-            if (m >= p.M) break;
-            float v = 0.f;
-            for (int sp = 0; sp < p.splits; ++sp) v += __ldcg(wsb + sp * part_elems + static_cast<size_t>(mm) * kTileN + r);
-            store_out(m, nn, v * p.alpha);
+        // all 512 threads, four consecutive output features per thread: 16-byte partial loads straight from
+        // L2 (.cg), 8-byte bf16 stores
+        const int rows_here = min(p.mb, m_end - m0);
+        const int n_base = n_tile * kTileN;
+        for (int idx = dq; idx < rows_here * (kTileN / 4); idx += kNumDequantWarps * 32) {
+          const int mm = idx >> 5;             // kTileN / 4 = 32 float4 per row
+          const int c4 = (idx & 31) * 4;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(wsb + sp * part_elems + static_cast<size_t>(mm) * kTileN + c4));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          const int m = m0 + mm;
+          const float o4[4] = {acc.x, acc.y, acc.z, acc.w};
+          if (!(p.tp.mode & kTpScatterPush) && n_base + c4 + 3 < p.N && ((p.ldy & 3) == 0)) {
+            const size_t off = static_cast<size_t>(m) * p.ldy + n_base + c4;
+            float r4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (p.residual) {
+              const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + off);
+              const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+              const float2 a0 = __bfloat1622float2(rp[0]), a1 = __bfloat1622float2(rp[1]);
+              r4[0] = a0.x; r4[1] = a0.y; r4[2] = a1.x; r4[3] = a1.y;
+            }
+            uint2 ov;
+            ov.x = pack_bf16x2(o4[0] * p.alpha + r4[0], o4[1] * p.alpha + r4[1]);
+            ov.y = pack_bf16x2(o4[2] * p.alpha + r4[2], o4[3] * p.alpha + r4[3]);
+            *reinterpret_cast<uint2*>(p.y + off) = ov;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (n_base + c4 + j < p.N) store_out(m, n_base + c4 + j, o4[j] * p.alpha);
           }
         }
       }
@@ -527,6 +586,9 @@ static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemm
 
 }  // namespace cb
 
+// set by cb_wq_gemm_grouped around its call of the common launcher (host-side, single-threaded use per process)
+static struct { const int* tiles; size_t code_stride, meta_stride; int max_items, num_experts; } g_grouped = {};
+static int g_mb_hint = 0;
 static unsigned long long* g_trace_buffer = nullptr;
 static int g_stage_override = 0;
 
@@ -563,6 +625,13 @@ struct CbTpLink {
 int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                   const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
                   void* counters, void* status, void* stream, const CbTpLink* link);
+
+// Grouped GEMM over experts: x / y rows are sorted by expert; `tiles` is the device work list written by
+// cb_moe_route (items of at most `mb` rows); `max_items` sizes the grid (ceil(routes / mb) + experts).
+int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                       float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
+                       int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
+                       void* stream);
 
 int cb_wq_gemm(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
@@ -601,6 +670,7 @@ int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void
     if ((link->mode & kTpScatterPush) && static_cast<long long>(link->rows_per_rank) * link->size < M) return -31;
   }
   p.mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+  if (g_grouped.tiles && g_mb_hint > 0) p.mb = g_mb_hint;
   p.k_blocks = K / kBlockK;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
@@ -624,13 +694,19 @@ int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void
   CUtensorMap tx, tw;
   if (make_tmap_bf16(&tx, x, M, K, ldx, p.mb) != 0) return -20;
   if (fmt == kFmtBf16) {
-    if (make_tmap_bf16(&tw, codes, N, K, K, kTileN) != 0) return -21;
+    const uint64_t w_rows = static_cast<uint64_t>(N) * (g_grouped.tiles ? g_grouped.num_experts : 1);
+    if (make_tmap_bf16(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
   } else {
     tw = tx;
   }
   const int n_tiles = (N + kTileN - 1) / kTileN;
   const int m_tiles = (M + p.mb - 1) / p.mb;
   dim3 grid(n_tiles, splits, m_tiles);
+  if (g_grouped.tiles) {
+    p.group_tiles = g_grouped.tiles;
+    p.group_code_stride = g_grouped.code_stride; p.group_meta_stride = g_grouped.meta_stride;
+    grid = dim3(n_tiles, g_grouped.max_items, 1);
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (fmt) {
     case kFmtCubic4: return launch_fmt<kFmtCubic4>(tx, tw, p, grid, smem, st);
@@ -638,6 +714,25 @@ int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void
     case kFmtNvfp4: return launch_fmt<kFmtNvfp4>(tx, tw, p, grid, smem, st);
     default: return launch_fmt<kFmtBf16>(tx, tw, p, grid, smem, st);
   }
+}
+
+int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                       float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
+                       int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
+                       void* stream) {
+  if (!tiles || max_items <= 0 || mb <= 0 || mb > 256 || (mb % 16) != 0 || num_experts <= 0) return -40;
+  g_grouped.num_experts = num_experts;
+  g_grouped.tiles = static_cast<const int*>(tiles);
+  g_grouped.code_stride = static_cast<size_t>(code_stride);
+  g_grouped.meta_stride = static_cast<size_t>(meta_stride);
+  g_grouped.max_items = max_items;
+  g_mb_hint = mb;
+  // the tensor map spans all rows; every work item starts at its own row offset
+  const int rc = cb_wq_gemm_tp(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, total_rows, N, K, group_k, 1, nullptr,
+                               nullptr, status, stream, nullptr);
+  g_grouped.tiles = nullptr;
+  g_mb_hint = 0;
+  return rc;
 }
 
 }  // extern "C"

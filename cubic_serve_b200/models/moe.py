@@ -1,0 +1,106 @@
+"""Mixture-of-experts FFN on the native kernels (router -> permute -> grouped expert GEMMs -> combine).
+
+Semantics of the reference's fused MoE (``ops/cuda/moe/fused.py``): stable top-k over router logits, softmax
+over the selected logits, SwiGLU experts, weighted combine in fixed route order.  Expert parallelism follows
+the reference's serving path (``runtime/README.md:140-160`` there): tokens are replicated, a rank computes only
+the experts it owns (routes to other experts contribute +0) and the per-rank partial outputs are summed like any
+row-parallel partial.  The expert GEMMs are ONE grouped launch each (gate/up and down) over a device-side work
+list, so variable routing needs no host round trip and is CUDA-graph safe.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import wq_pack
+from .config import ModelConfig
+
+
+def stack_experts(packed: list[wq_pack.PackedWeight]) -> tuple[wq_pack.PackedWeight, int, int]:
+    """Stack per-expert packed weights along a leading axis; returns (stacked, code stride, meta stride) in bytes."""
+    first = packed[0]
+    codes = torch.stack([p.codes for p in packed])
+    meta = torch.stack([p.meta for p in packed]) if first.meta is not None else None
+    stacked = wq_pack.PackedWeight(first.fmt, first.n, first.k, first.group_k, codes, meta, first.alpha)
+    cs = codes[0].numel() * codes.element_size()
+    ms = meta[0].numel() if meta is not None else 0
+    return stacked, cs, ms
+
+
+@dataclass
+class MoeLayer:
+    router: wq_pack.PackedWeight          # bf16 [E, H]
+    gate_up: wq_pack.PackedWeight         # stacked [E_local] x [2I, H]
+    down: wq_pack.PackedWeight            # stacked [E_local] x [H, I]
+    strides: tuple[int, int, int, int]    # code / meta strides of gate_up and down
+    num_experts: int
+    top_k: int
+    expert_lo: int
+    expert_count: int
+    normalize: bool = True
+    scratch: K.MoeScratch | None = None
+    launches: int = 7
+
+    def ensure_scratch(self, max_tokens: int, hidden: int, device) -> K.MoeScratch:
+        if self.scratch is None or self.scratch.topk_ids.shape[0] < max_tokens:
+            mb = 64 if max_tokens * self.top_k >= 32 * self.expert_count else 32
+            self.scratch = K.MoeScratch(max_tokens, self.top_k, hidden, self.gate_up.n, self.expert_count, mb, device)
+            self.logits = torch.empty(max_tokens, self.num_experts, dtype=torch.bfloat16, device=device)
+            self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
+        return self.scratch
+
+    def forward(self, x: torch.Tensor, runner=None, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``x``: normalised activations ``[T, H]``; returns this rank's (partial) FFN output ``[T, H]``."""
+        t, h = x.shape
+        sc = self.ensure_scratch(runner.max_tokens if runner is not None else t, h, x.device)
+        ws = runner.ws if runner is not None else None
+        logits = K.wq_gemm(x, self.router, out=self.logits[:t], ws=ws)
+        K.moe_route(logits, x, self.top_k, sc, self.normalize, self.expert_lo, self.expert_count)
+        rows = t * self.top_k
+        K.wq_gemm_grouped(sc.xs, self.gate_up, sc.gu, rows, sc, self.strides[0], self.strides[1], ws)
+        K.swiglu(sc.gu[:rows], out=sc.act[:rows])
+        K.wq_gemm_grouped(sc.act, self.down, sc.y, rows, sc, self.strides[2], self.strides[3], ws)
+        return K.moe_combine(sc.y, sc, t, self.out[:t], residual)
+
+
+def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size: int = 1, std: float = 0.02) -> MoeLayer:
+    """Random experts for EP = tp_size (contiguous expert-id slices per rank), router replicated."""
+    from .decoder import quantize_linear
+    H, I, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
+    local = E // tp_size
+    shared = torch.Generator(device=device).manual_seed(12345)
+    router = (torch.randn(E, H, device=device, generator=shared) * std).to(torch.bfloat16)
+    gus, downs = [], []
+    for _ in range(local):
+        gus.append(quantize_linear(torch.randn(2 * I, H, device=device, generator=gen) * std, cfg))
+        downs.append(quantize_linear(torch.randn(H, I, device=device, generator=gen) * std, cfg))
+    gu, gcs, gms = stack_experts(gus)
+    dn, dcs, dms = stack_experts(downs)
+    return MoeLayer(wq_pack.pack_bf16(router), gu, dn, (gcs, gms, dcs, dms), E, cfg.experts_per_token,
+                    tp_rank * local, local, cfg.norm_topk_prob)
+
+
+def moe_reference(x: torch.Tensor, router: torch.Tensor, gate_up: list[torch.Tensor], down: list[torch.Tensor],
+                  top_k: int, normalize: bool = True, expert_lo: int = 0) -> torch.Tensor:
+    """Independent fp32 oracle: dense per-token loop over the selected experts (local experts only)."""
+    xf = x.float()
+    logits = (xf @ router.float().t()).to(torch.bfloat16).float()
+    t, e = logits.shape
+    out = torch.zeros(t, x.shape[1], device=x.device)
+    # stable top-k with lowest id on ties: sort by (-value, id)
+    order = torch.argsort(-logits, dim=-1, stable=True)[:, :top_k]
+    sel = torch.gather(logits, 1, order)
+    w = torch.softmax(sel, -1) if normalize else torch.softmax(logits, -1).gather(1, order)
+    for ti in range(t):
+        for r in range(top_k):
+            le = int(order[ti, r]) - expert_lo
+            if not 0 <= le < len(gate_up):
+                continue
+            gu = (xf[ti] @ gate_up[le].float().t()).to(torch.bfloat16).float()
+            i = gu.shape[0] // 2
+            act = (torch.nn.functional.silu(gu[:i]) * gu[i:]).to(torch.bfloat16).float()
+            y = (act @ down[le].float().t()).to(torch.bfloat16).float()
+            out[ti] += w[ti, r] * y
+    return out

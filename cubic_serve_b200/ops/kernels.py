@@ -71,16 +71,18 @@ def sm_count(device: torch.device) -> int:
 
 
 def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
-    """Split-K factor: fill the SMs when the (n-tile x m-tile) grid is small."""
+    """Split-K factor: fill the SMs when the (n-tile x m-tile) grid is small.
+
+    Every split CTA writes an fp32 partial tile and the last one sums them (vectorised, from L2), so a split
+    pays off while each CTA still has >= 8 k-blocks of work.
+    """
     n_tiles = -(-n // 128)
     m_tiles = -(-m // 256)
     tiles = n_tiles * m_tiles
     k_blocks = k // 64
-    if tiles >= sms or k_blocks < 8 or m > 128:
-        # with >= 128 batch rows the fp32 partial tiles (512 B per row and tile) cost more than the idle SMs
+    if tiles * 2 > sms or k_blocks < 16:
         return 1
-    splits = max(1, sms // tiles)
-    return max(1, min(splits, k_blocks // 4, 16))
+    return max(1, min(sms // tiles, k_blocks // 8, 8))
 
 
 def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
@@ -209,3 +211,60 @@ def verify_greedy(target_ids: torch.Tensor, draft_ids: torch.Tensor, depth: torc
                                          _ptr(forced_reject_at), accepted.data_ptr(), bonus.data_ptr(),
                                          depth.numel(), _stream())
     native.check(code, "cb_verify_greedy")
+
+
+# ------------------------------------------------------------------ mixture of experts
+class MoeScratch:
+    """Fixed-address routing buffers for up to ``max_tokens`` tokens (graph-capturable)."""
+
+    def __init__(self, max_tokens: int, top_k: int, hidden: int, inter2: int, local_experts: int, mb: int, device) -> None:
+        routes = max_tokens * top_k
+        self.mb = mb
+        self.max_items = -(-routes // mb) + local_experts
+        i32 = dict(dtype=torch.int32, device=device)
+        self.topk_ids = torch.empty(max_tokens, top_k, **i32)
+        self.topk_w = torch.empty(max_tokens, top_k, dtype=torch.float32, device=device)
+        self.counts = torch.zeros(local_experts, **i32)
+        self.offsets = torch.zeros(local_experts, **i32)
+        self.cursors = torch.zeros(local_experts, **i32)
+        self.total = torch.zeros(1, **i32)
+        self.tiles = torch.zeros(1 + 3 * self.max_items, **i32)
+        self.route_pos = torch.empty(max_tokens, top_k, **i32)
+        bf = dict(dtype=torch.bfloat16, device=device)
+        # + mb rows of slack: a work item's TMA tile may run past the last route (those rows are never stored)
+        self.xs = torch.zeros(routes + mb, hidden, **bf)
+        self.gu = torch.zeros(routes + mb, inter2, **bf)
+        self.act = torch.zeros(routes + mb, inter2 // 2, **bf)
+        self.y = torch.zeros(routes + mb, hidden, **bf)
+
+
+def moe_route(router_logits: torch.Tensor, x: torch.Tensor, top_k: int, sc: MoeScratch, normalize: bool = True,
+              expert_lo: int = 0, expert_count: int | None = None) -> None:
+    t, e = router_logits.shape
+    cnt = e if expert_count is None else expert_count
+    code = native.lib().cb_moe_route(router_logits.data_ptr(), router_logits.stride(0), x.data_ptr(), t, e, top_k,
+                                     x.shape[1], int(normalize), expert_lo, cnt, sc.mb, sc.topk_ids.data_ptr(),
+                                     sc.topk_w.data_ptr(), sc.counts.data_ptr(), sc.offsets.data_ptr(),
+                                     sc.cursors.data_ptr(), sc.total.data_ptr(), sc.tiles.data_ptr(),
+                                     sc.route_pos.data_ptr(), sc.xs.data_ptr(), _stream())
+    native.check(code, "cb_moe_route")
+
+
+def wq_gemm_grouped(x: torch.Tensor, w: PackedWeight, out: torch.Tensor, rows: int, sc: MoeScratch,
+                    code_stride: int, meta_stride: int, ws: Workspace | None = None) -> torch.Tensor:
+    """Per-expert ``out[rows of e] = x[rows of e] @ W_e^T`` over the work list in ``sc.tiles``; ``w`` stacks the experts."""
+    ws = ws or workspace(x.device)
+    code = native.lib().cb_wq_gemm_grouped(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
+                                           out.data_ptr(), out.stride(0), float(w.alpha), rows, w.n, w.k, w.group_k,
+                                           sc.tiles.data_ptr(), sc.max_items, sc.mb, w.codes.shape[0], code_stride, meta_stride,
+                                           ws.status.data_ptr(), _stream())
+    native.check(code, "cb_wq_gemm_grouped")
+    return out
+
+
+def moe_combine(y: torch.Tensor, sc: MoeScratch, tokens: int, out: torch.Tensor,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
+    code = native.lib().cb_moe_combine(y.data_ptr(), sc.route_pos.data_ptr(), sc.topk_w.data_ptr(), tokens,
+                                       sc.topk_ids.shape[1], y.shape[1], _ptr(residual), out.data_ptr(), _stream())
+    native.check(code, "cb_moe_combine")
+    return out

@@ -16,7 +16,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_PATH = Path(__file__).resolve().parent.parent / "libcubic_b200.so"
-SOURCES = ("wq_gemm.cu", "elementwise.cu", "kv_cache.cu", "paged_attn.cu", "sampling.cu", "tp_comm.cu")
+SOURCES = ("wq_gemm.cu", "elementwise.cu", "kv_cache.cu", "paged_attn.cu", "sampling.cu", "tp_comm.cu", "moe.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -132,6 +132,12 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_tp_wait.restype = i
     l.cb_tp_argmax_merge.argtypes = [vp, vp]
     l.cb_tp_argmax_merge.restype = i
+    l.cb_moe_route.argtypes = [vp, i, vp, i, i, i, i, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    l.cb_moe_route.restype = i
+    l.cb_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp, vp]
+    l.cb_moe_combine.restype = i
+    l.cb_wq_gemm_grouped.argtypes = [i, vp, i, vp, vp, vp, i, f, i, i, i, i, vp, i, i, i, ll, ll, vp, vp]
+    l.cb_wq_gemm_grouped.restype = i
 
 
 class TpLinkStruct(ctypes.Structure):

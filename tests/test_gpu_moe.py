@@ -1,0 +1,75 @@
+"""MoE routing, grouped expert GEMM and combine against a dense per-token oracle."""
+from dataclasses import replace
+
+import pytest
+import torch
+
+from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+from cubic_serve_b200.ops import wq_pack
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("method,tokens,ep", [("nvfp4", 37, 1), ("cubic", 200, 1), ("nvfp4", 64, 2), ("none", 5, 1)])
+def test_moe_layer_matches_oracle(method, tokens, ep):
+    from cubic_serve_b200.models.moe import moe_reference, random_moe_weights
+    cfg = ModelConfig(family="gqa_moe", hidden_size=256, num_experts=16, experts_per_token=4, moe_intermediate_size=128,
+                      quant=QuantSpec(method, 4 if method != "none" else 16, {"nvfp4": 16, "cubic": 128, "none": 0}[method]))
+    x = (torch.randn(tokens, 256, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16).to(DEV)
+    total = torch.zeros(tokens, 256, device=DEV)
+    ref_total = torch.zeros(tokens, 256, device=DEV)
+    for rank in range(ep):
+        gen = torch.Generator(device=DEV).manual_seed(7 + rank)
+        layer = random_moe_weights(cfg, DEV, gen, tp_rank=rank, tp_size=ep, std=0.05)
+        out = layer.forward(x)
+        torch.cuda.synchronize()
+        sc = layer.scratch
+        counts = sc.counts.cpu()
+        assert int(sc.total) == int(counts.sum())
+        assert int(sc.total) == (tokens * 4 if ep == 1 else int(((sc.topk_ids // (16 // ep)) == rank).sum()))
+        n_items = int(sc.tiles[0])
+        assert n_items == int(((counts + sc.mb - 1) // sc.mb).sum())
+        local = 16 // ep
+        gu = [wq_pack.unpack_to_dense(wq_pack.PackedWeight(layer.gate_up.fmt, layer.gate_up.n, layer.gate_up.k,
+                                                             layer.gate_up.group_k, layer.gate_up.codes[e],
+                                                             None if layer.gate_up.meta is None else layer.gate_up.meta[e],
+                                                             layer.gate_up.alpha)) for e in range(local)]
+        dn = [wq_pack.unpack_to_dense(wq_pack.PackedWeight(layer.down.fmt, layer.down.n, layer.down.k, layer.down.group_k,
+                                                             layer.down.codes[e],
+                                                             None if layer.down.meta is None else layer.down.meta[e],
+                                                             layer.down.alpha)) for e in range(local)]
+        ref = moe_reference(x, layer.router.codes, gu, dn, 4, True, expert_lo=rank * local)
+        total += out.float()
+        ref_total += ref
+    from cubic_serve_b200.ops import kernels as K
+    K.workspace(torch.device(DEV)).check_status()
+    assert _rel(total, ref_total) < 3e-2
+
+
+def test_router_stable_ties_and_weights():
+    from cubic_serve_b200.ops import kernels as K
+    t, e, k = 9, 64, 8
+    logits = torch.zeros(t, e)
+    logits[:, 10:30] = 1.0                                   # a 20-way tie: lowest ids win
+    logits[3, 50] = 5.0
+    x = torch.randn(t, 128).to(torch.bfloat16).to(DEV)
+    sc = K.MoeScratch(t, k, 128, 256, e, 32, DEV)
+    K.moe_route(logits.to(torch.bfloat16).to(DEV), x, k, sc)
+    ids = sc.topk_ids.cpu()
+    assert ids[0].tolist() == list(range(10, 18))
+    assert ids[3].tolist() == [50] + list(range(10, 17))
+    w = sc.topk_w.cpu()
+    assert torch.allclose(w.sum(-1), torch.ones(t), atol=1e-5)
+    assert torch.allclose(w[0], torch.full((k,), 1 / k), atol=1e-6)
+    # every route landed in its expert's range and carries its token's row
+    off, cnt, pos = sc.offsets.cpu(), sc.counts.cpu(), sc.route_pos.cpu()
+    for ti in range(t):
+        for r in range(k):
+            ex = int(ids[ti, r])
+            assert off[ex] <= pos[ti, r] < off[ex] + cnt[ex]
+            assert torch.equal(sc.xs[int(pos[ti, r])], x[ti])

@@ -1,0 +1,88 @@
+import pytest
+
+from cubic_serve_b200.runtime.speculative import (CostCurve, DraftAction, DraftPlanner, DraftPolicyConfig,
+                                                  RequestDraftState)
+
+
+def test_config_validation():
+    DraftPolicyConfig.from_dict({"decision_tokens": 10})
+    for bad in ({"cost_sample_window": 2}, {"history_decay": 1.0}, {"prior_success": 0}, {"bogus": 1}, {"terminal_stop_margin": -1}):
+        with pytest.raises(ValueError):
+            DraftPolicyConfig.from_dict(bad)
+
+
+def test_survival_curve_prior_and_updates():
+    s = RequestDraftState(3, 4)
+    assert s.survival() == pytest.approx((0.8, 0.64, 0.512, 0.4096))        # Beta(4, 1) prior mean 0.8 per depth
+    for _ in range(50):
+        s.observe(accepted=1, proposed=3)                                     # depth 1 always accepted, depth 2 never
+    sv = s.survival()
+    assert sv[0] > 0.95 and sv[1] < 0.2 and sv[2] < sv[1] and sv == tuple(sorted(sv, reverse=True))
+    assert s.expected_tokens(0) == 1.0 and s.expected_tokens(2) == pytest.approx(1 + sv[0] + sv[1])
+    with pytest.raises(ValueError):
+        s.observe(accepted=4, proposed=3)
+    with pytest.raises(ValueError):
+        s.observe(accepted=0, proposed=4)
+
+
+def test_decisions_need_boundary_and_move_one_level():
+    s = RequestDraftState(2, 4)
+    assert s.move_toward(4).action is DraftAction.HOLD                       # not ready yet
+    for _ in range(8):
+        s.observe(accepted=2, proposed=2)                                     # 8 rounds x 3 tokens = 24
+    assert s.ready
+    d = s.move_toward(4)
+    assert (d.action, d.previous_tokens, d.next_tokens) == (DraftAction.PROMOTE, 2, 3) and not s.ready
+    for _ in range(8):
+        s.observe(accepted=0, proposed=3)
+    assert not s.ready                                                         # 8 rounds but only 8 tokens
+    for _ in range(16):
+        s.observe(accepted=0, proposed=3)
+    assert s.move_toward(0).next_tokens == 2
+    s2 = RequestDraftState(1, 2)
+    for _ in range(24):
+        s2.observe(accepted=0, proposed=1)
+    d = s2.move_toward(0)
+    assert d.next_tokens == 0 and s2.stopped
+    with pytest.raises(RuntimeError):
+        s2.observe(accepted=0, proposed=1)
+    assert RequestDraftState(3, 3).stop_for_capacity().next_tokens == 0
+
+
+def test_cost_curve_median_ema_and_interpolation():
+    c = CostCurve(alpha=0.5, window=3)
+    assert c.estimate(8) is None
+    c.observe(8, 10.0)
+    c.observe(8, 100.0); c.observe(8, 12.0)
+    assert c.estimate(8) == 10.0                                             # window not full yet
+    c.observe(8, 14.0)                                                       # median(100, 12, 14) = 14
+    assert c.estimate(8) == pytest.approx(12.0)
+    c.observe(32, 30.0)
+    assert c.estimate(20) == pytest.approx(12 + (20 - 8) / 24 * 18)
+    assert c.estimate(4) == pytest.approx(12.0)                              # no downward extrapolation
+    assert c.estimate(64) == pytest.approx(60.0)
+
+
+def test_planner_prefers_drafting_when_cheap_and_stops_when_useless():
+    p = DraftPlanner((8, 16, 32, 64, 128))
+    for cap, ms in ((8, 5.0), (16, 5.2), (32, 5.6), (64, 6.5), (128, 8.0)):
+        p.target_cost.observe(cap, ms)
+        p.proposal_cost.observe(cap, 0.3)
+    good = [RequestDraftState(2, 4) for _ in range(8)]
+    for s in good:
+        for _ in range(12):
+            s.observe(accepted=2, proposed=2)
+    assert p.best_uniform_k(good, 4) >= 3                                     # high acceptance: longer drafts
+    plans = p.plan({f"r{i}": s for i, s in enumerate(good)})
+    assert all(pl.draft_tokens == 3 and pl.decision.action is DraftAction.PROMOTE for pl in plans)
+    bad = [RequestDraftState(1, 4) for _ in range(8)]
+    for s in bad:
+        for _ in range(150):
+            s.observe(accepted=0, proposed=1)
+    assert p.best_uniform_k(bad, 4) == 0
+    # marginal benefit below the 3 % stop margin keeps drafting alive
+    p2 = DraftPlanner((8,), DraftPolicyConfig(terminal_stop_margin=0.5))
+    p2.target_cost.observe(8, 5.0)
+    p2.proposal_cost.observe(8, 0.01)
+    assert p2.best_uniform_k(bad, 1) == 1
+    assert DraftPlanner((8,)).best_uniform_k(good, 4) == 4                    # no cost data yet: keep the maximum
