@@ -38,6 +38,8 @@ def parse_args():
     ap.add_argument("--input-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collective path")
+    ap.add_argument("--kv", default="", help="K,V cache bits, e.g. 8,8 or 4,8 (default: 8,8 dense, 4,8 MoE)")
+    ap.add_argument("--prefill-tokens", type=int, default=8192, help="token budget of a prefill step")
     return ap.parse_args()
 
 
@@ -118,25 +120,26 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    tp = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-        from cubic_serve_b200.parallel.tp import TensorParallel
-        tp = TensorParallel(dist.group.WORLD, dev, mode=args.comm)
-
     cfg = NAMED_CONFIGS[args.model]()
     if args.layers:
         from dataclasses import replace
         cfg = replace(cfg, num_layers=args.layers)
+    k_bits, v_bits = (int(b) for b in (args.kv or ("4,8" if cfg.is_moe else "8,8")).split(","))
+    tp = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        from cubic_serve_b200.parallel.tp import TensorParallel
+        tp = TensorParallel(dist.group.WORLD, dev, mode=args.comm if not cfg.is_moe else "nccl", hidden=cfg.hidden_size,
+                            max_tokens=args.prefill_tokens, rows_max=max(args.concurrency, 512))
     C, L = args.concurrency, args.input_len
     total_steps = args.warmup + args.steps
     max_len = L + total_steps + 8
     pages_per_req = -(-max_len // 16)
     num_pages = C * pages_per_req + 8
-    prefill_tokens = 8192
+    prefill_tokens = args.prefill_tokens
 
     weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
-    runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=8, v_bits=8, tp=tp)
+    runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=k_bits, v_bits=v_bits, tp=tp)
     ex = GpuExecutor(runner, max_rows=C, max_prefill_tokens=prefill_tokens, max_model_len=max_len)
     ex.capture_decode_graphs([C])
     ex.timing = True
@@ -199,12 +202,12 @@ def main() -> None:
             "metric": "output tok/s @256 concurrent (decode steps, device-timed, max over ranks)",
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": "bf16 activations, 4-bit CubicQuant weights, INT8 KV",
+            "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": f"bf16 activations, {cfg.quant.method} {cfg.quant.bits}-bit weights, INT{k_bits}/INT{v_bits} KV",
             "data": "synthetic (random token ids; random-init N(0,0.02) weights quantized offline)",
             "impl": "ours",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
                        "global_batch": C, "seq_len": L, "parallelism": f"tp{world}",
-                       "comm": args.comm if world > 1 else "none", "cuda_graphs": True, "kv_cache": "int8/int8",
+                       "comm": (tp.mode if tp is not None else "none"), "cuda_graphs": True, "kv_cache": f"int{k_bits}/int{v_bits}",
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,
                        "weights_gb": round(weights.nbytes() / 1e9, 2)},

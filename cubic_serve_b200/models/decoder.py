@@ -47,7 +47,10 @@ class DecoderWeights:
     def nbytes(self) -> int:
         total = self.embed.numel() * 2 + self.lm_head.nbytes
         for l in self.layers:
-            for w in (l.qkv, l.o, l.gate_up, l.down):
+            ws = [l.qkv, l.o, l.gate_up, l.down]
+            if l.moe is not None:
+                ws += [l.moe.router, l.moe.gate_up, l.moe.down]
+            for w in ws:
                 if w is not None:
                     total += w.nbytes
         return total
@@ -224,12 +227,12 @@ class DecoderRunner:
                 K.rmsnorm(part, lw.ln2, cfg.rms_eps, out=x, residual=h, zero_centered=cfg.zero_centered_norm)
             n += 2
             if lw.moe is not None:
-                out = lw.moe.forward(x, self)  # returns the (partial) FFN output [T, H]
                 n += lw.moe.launches
                 if self.tp is None:
-                    h.add_(out)
+                    lw.moe.forward(x, self, residual=h, out=h)     # combine adds into the residual stream
                     pending = None
                 else:
+                    out = lw.moe.forward(x, self)                  # this rank's experts only: a partial sum
                     self.tp.all_reduce(out)
                     pending = out
             else:

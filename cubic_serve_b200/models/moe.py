@@ -51,8 +51,12 @@ class MoeLayer:
             self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
         return self.scratch
 
-    def forward(self, x: torch.Tensor, runner=None, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """``x``: normalised activations ``[T, H]``; returns this rank's (partial) FFN output ``[T, H]``."""
+    def forward(self, x: torch.Tensor, runner=None, residual: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        """``x``: normalised activations ``[T, H]``; returns this rank's (partial) FFN output ``[T, H]``.
+
+        With ``residual`` the combine adds it (``out`` may alias ``residual``: the residual stream is updated in place).
+        """
         t, h = x.shape
         sc = self.ensure_scratch(runner.max_tokens if runner is not None else t, h, x.device)
         ws = runner.ws if runner is not None else None
@@ -62,7 +66,7 @@ class MoeLayer:
         K.wq_gemm_grouped(sc.xs, self.gate_up, sc.gu, rows, sc, self.strides[0], self.strides[1], ws)
         K.swiglu(sc.gu[:rows], out=sc.act[:rows])
         K.wq_gemm_grouped(sc.act, self.down, sc.y, rows, sc, self.strides[2], self.strides[3], ws)
-        return K.moe_combine(sc.y, sc, t, self.out[:t], residual)
+        return K.moe_combine(sc.y, sc, t, self.out[:t] if out is None else out, residual)
 
 
 def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size: int = 1, std: float = 0.02) -> MoeLayer:
