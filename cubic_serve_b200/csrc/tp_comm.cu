@@ -15,8 +15,10 @@
 //                        rank's gathered activation buffer
 //   column-parallel GEMM waits for all rows (inside its producer warp).
 //
-// Counters only ever increase; a consumer compares against (epoch + 1) * expected
-// with its own epoch word, so nothing is reset while a peer may still write.
+// Counters only ever increase; a consumer keeps the cumulative number of arrivals
+// it has already consumed in its own state word and waits for (consumed +
+// expected of this launch), so nothing is reset while a peer may still write and
+// the expected count may differ from launch to launch (prefill vs decode shapes).
 #include "ptx.cuh"
 
 namespace cb {
@@ -42,7 +44,7 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target) {
 struct ReduceNormParams {
   const __nv_bfloat16* recv;     // local [size][rows_per_rank][H] partial rows, slot = source rank
   const uint32_t* rs_flag;       // local arrival counters [size]
-  uint32_t* rs_state;            // local {epoch, done CTAs}
+  uint32_t* rs_state;            // local {arrivals consumed so far, done CTAs}
   uint32_t rs_expected;          // arrivals per source per epoch; 0 = nothing to reduce (input is h itself)
   __nv_bfloat16* h;              // local residual rows [rows_per_rank][H] (read-modify-write)
   const __nv_bfloat16* norm_w;   // [H]
@@ -67,7 +69,7 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
   __syncthreads();
   if (p.rs_expected) {
     if (threadIdx.x < p.size) {
-      const uint32_t target = (p.rs_state[0] + 1u) * p.rs_expected;
+      const uint32_t target = p.rs_state[0] + p.rs_expected;
       if (!wait_ge(p.rs_flag + threadIdx.x, target)) ok_flag = 0;
     }
     __syncthreads();
@@ -156,7 +158,7 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
       if (atomicAdd(&p.rs_state[1], 1u) == gridDim.x - 1u) {
         p.rs_state[1] = 0;
         __threadfence();
-        atomicAdd(&p.rs_state[0], 1u);
+        atomicAdd(&p.rs_state[0], p.rs_expected);   // every CTA of this launch has read the old value by now
       }
     }
   }
@@ -169,12 +171,12 @@ __global__ void tp_wait_kernel(const uint32_t* ag_flag, uint32_t* ag_state, uint
   if (threadIdx.x == 0) ok_flag = 1;
   __syncthreads();
   if (threadIdx.x < size) {
-    if (!wait_ge(ag_flag + threadIdx.x, (ag_state[0] + 1u) * expected)) ok_flag = 0;
+    if (!wait_ge(ag_flag + threadIdx.x, ag_state[0] + expected)) ok_flag = 0;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     if (!ok_flag) atomicExch(status, static_cast<uint32_t>(kErrFlagTimeout));
-    atomicAdd(&ag_state[0], 1u);
+    atomicAdd(&ag_state[0], expected);
   }
 }
 

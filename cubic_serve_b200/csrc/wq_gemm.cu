@@ -66,7 +66,7 @@ struct TpLink {
   __nv_bfloat16* recv[kMaxRanks];     // push: owner o's receive buffer [size][rows_per_rank][N]
   uint32_t* rs_flag[kMaxRanks];       // push: owner o's arrival counters [size]
   const uint32_t* ag_flag;            // wait: local arrival counters [size]
-  uint32_t* ag_state;                 // wait: local {epoch, done CTAs}
+  uint32_t* ag_state;                 // wait: local {arrivals consumed so far, done CTAs}
   uint32_t ag_expected;               // wait: arrivals per source rank per epoch
 };
 
@@ -292,7 +292,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       for (int i = 0; i < pre; ++i) load_weights(i, i);
       bool ok = true;
       if (p.tp.mode & kTpGatherWait) {
-        const uint32_t target = (p.tp.ag_state[0] + 1u) * p.tp.ag_expected;
+        const uint32_t target = p.tp.ag_state[0] + p.tp.ag_expected;   // arrivals consumed so far + this launch's
         for (int r = 0; r < p.tp.size && ok; ++r) ok = wait_counter(p.tp.ag_flag + r, target, abort_flag);
       }
       if (ok) {
@@ -532,7 +532,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (atomicAdd(&p.tp.ag_state[1], 1u) == total - 1u) {
       p.tp.ag_state[1] = 0;
       __threadfence();
-      atomicAdd(&p.tp.ag_state[0], 1u);
+      atomicAdd(&p.tp.ag_state[0], p.tp.ag_expected);
     }
   }
   if (threadIdx.x == 0 && ctl->abort_flag)

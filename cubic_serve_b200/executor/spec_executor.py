@@ -1,0 +1,166 @@
+"""Speculative decoding round on the GPU: MTP proposals -> target review -> greedy verification.
+
+One round, in the order of the reference's ``execute_draft_batch`` (``runtime/performance.py:7189-7556`` there):
+(1) proposal passes of the MTP head, depth by depth, chaining draft tokens and hidden states on the device;
+(2) ONE target pass over ``[root, d1 .. dK]`` per request (segment length K + 1, every row sampled);
+(3) greedy verification on the device (longest matching prefix, bonus token = the target's choice after it);
+(4) the hidden state of the last accepted position becomes the head's input for the next round.
+Rejected positions need no repair: their KV slots are simply rewritten by the next round.
+
+``force_acceptance`` replaces natural agreement by a seeded per-depth Bernoulli draw -- only meaningful for
+benchmarks with random weights, where a draft never matches on its own.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..models.mtp import MtpRunner
+from ..ops import kernels as K
+from .gpu_executor import GpuExecutor, Segment
+
+
+class SpeculativeGpuExecutor(GpuExecutor):
+    def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
+                 **kw) -> None:
+        super().__init__(runner, **kw)
+        self.mtp = mtp
+        self.speculative_depth = depth
+        self.force_acceptance = force_acceptance
+        self._rng = np.random.default_rng(seed)
+        dev, H = self.device, runner.cfg.hidden_size
+        rows = self.max_rows
+        self.last_hidden = torch.zeros(rows, H, dtype=torch.bfloat16, device=dev)      # by request slot
+        self.hidden_rows = torch.empty(runner.max_tokens, H, dtype=torch.bfloat16, device=dev)
+        self.draft_ids = torch.zeros(rows, depth, dtype=torch.int32, device=dev)
+        self.target_ids = torch.zeros(rows, depth + 1, dtype=torch.int32, device=dev)
+        self.accepted = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.bonus = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.depth_t = torch.full((rows,), depth, dtype=torch.int32, device=dev)
+        self.forced = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.mtp_logits = torch.empty(rows, runner.w.lm_head.n, dtype=torch.bfloat16, device=dev)
+        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0}
+
+    # ------------------------------------------------------------- plain steps
+    def execute(self, segs):
+        """Prefill / non-speculative steps also feed the MTP head (its KV cache and ``last_hidden``)."""
+        ids = self._execute_with_hidden(segs)
+        return ids
+
+    def _execute_with_hidden(self, segs):
+        total = sum(len(s.token_ids) for s in segs)
+        b, rows = self._fill(segs)
+        r = self.runner
+        with torch.cuda.stream(self.stream):
+            self.h2d_bytes_last = self.stage.upload()
+            hidden = r.forward_hidden(b)
+            d = self.stage.d
+            if rows:
+                logits = r.forward_logits(b, hidden, self.logits)
+                K.sample(logits, self.out_ids[:rows], temperature=d["temperature"][:rows], top_p=d["top_p"][:rows],
+                         top_k=d["top_k"][:rows], seeds=d["seeds"][:rows], counters=d["draws"][:rows], vocab=logits.shape[1])
+            # MTP pass over the same rows: row i is preceded by the target hidden of row i - 1 (the first row of a
+            # segment by the request's carried hidden)
+            prev = self.hidden_rows[:total]
+            prev[1:].copy_(hidden[:total - 1])
+            first, last, slots = [], [], []
+            t = 0
+            for s in segs:
+                first.append(t)
+                t += len(s.token_ids)
+                last.append(t - 1)
+                slots.append(s.request_slot)
+            fi = torch.tensor(first, device=self.device)
+            la = torch.tensor(last, device=self.device)
+            sl = torch.tensor(slots, device=self.device)
+            prev.index_copy_(0, fi, self.last_hidden.index_select(0, sl))
+            self.mtp.forward(b, prev)
+            self.last_hidden.index_copy_(0, sl, hidden.index_select(0, la))
+            if rows:
+                self.out_host[:rows].copy_(self.out_ids[:rows], non_blocking=True)
+            self.stream.synchronize()
+        self.kernel_launches_last = r.launches_per_step + self.mtp.launches + 3
+        self.d2h_bytes_last = rows * 4
+        return self.out_host[:rows].numpy().copy()
+
+    # ------------------------------------------------------- speculative round
+    def execute_speculative(self, segs: list[Segment]):
+        """``segs``: one decode segment per request (its root token).  Returns per request the emitted tokens."""
+        R, Kd = len(segs), self.speculative_depth
+        r, dev = self.runner, self.device
+        sl = torch.tensor([s.request_slot for s in segs], device=dev)
+        launches = 0
+        with torch.cuda.stream(self.stream):
+            ev0, ev1 = self._ev
+            if self.timing:
+                ev0.record(self.stream)
+            prev = self.last_hidden.index_select(0, sl)
+            # ---- proposals: depth d consumes the token at position start + d - 1
+            for d in range(Kd):
+                step = [Segment(s.request_slot, [s.token_ids[0] if d == 0 else 0], s.start + d, s.pages, True, uid=s.uid)
+                        for s in segs]
+                b, _ = self._fill(step)
+                self.h2d_bytes_last = self.stage.upload()
+                if d > 0:
+                    self.stage.d["token_ids"][:R].copy_(self.draft_ids[:R, d - 1])
+                hid = self.mtp.forward(b, prev)
+                lg = self.mtp.logits(hid, R, self.mtp_logits)
+                tmp = self.out_ids[:R]
+                K.sample(lg, tmp, vocab=lg.shape[1])
+                self.draft_ids[:R, d].copy_(tmp)
+                prev = hid[:R].clone()
+                launches += self.mtp.launches + 4
+            # ---- target review over [root, d1 .. dK]
+            review = [Segment(s.request_slot, [s.token_ids[0]] + [0] * Kd, s.start, s.pages, True, uid=s.uid) for s in segs]
+            b, _ = self._fill(review)
+            T = R * (Kd + 1)
+            self.stage.h["logit_rows"][:T] = np.arange(T)
+            self.stage.h["temperature"][:T] = 0
+            self.stage.upload()
+            toks = torch.cat([torch.tensor([s.token_ids[0] for s in segs], dtype=torch.int32, device=dev)[:, None],
+                              self.draft_ids[:R]], 1).reshape(-1)
+            self.stage.d["token_ids"][:T].copy_(toks)
+            b.num_logit_rows = T
+            hidden = r.forward_hidden(b)
+            logits_buf = self._review_logits(T)
+            logits = r.forward_logits(b, hidden, logits_buf)
+            tgt = self.target_ids[:R].view(-1)
+            K.sample(logits, tgt, vocab=logits.shape[1])
+            launches += r.launches_per_step + 1
+            # ---- verification
+            forced = None
+            if self.force_acceptance is not None:
+                draws = self._rng.random((R, Kd)) < self.force_acceptance
+                first_fail = np.where(draws.all(1), Kd, draws.argmin(1)).astype(np.int32)
+                self.forced[:R].copy_(torch.from_numpy(first_fail), non_blocking=True)
+                forced = self.forced
+                # forced acceptance: the draft is *declared* equal to the target up to the drawn depth
+                agree = self.target_ids[:R, :Kd].clone()
+                keep = torch.arange(Kd, device=dev)[None, :] < self.forced[:R, None]
+                self.draft_ids[:R] = torch.where(keep, agree, self.draft_ids[:R])
+            K.verify_greedy(self.target_ids, self.draft_ids, self.depth_t, Kd, self.accepted, self.bonus, forced)
+            rows = torch.arange(R, device=dev) * (Kd + 1) + self.accepted[:R].long()
+            self.last_hidden.index_copy_(0, sl, hidden.index_select(0, rows))
+            if self.timing:
+                ev1.record(self.stream)
+            acc = self.accepted[:R].cpu()
+            tg = self.target_ids[:R].cpu()
+            self.stream.synchronize()
+        if self.timing:
+            self.device_ms.append(ev0.elapsed_time(ev1))
+        out = []
+        for i in range(R):
+            a = int(acc[i])
+            out.append([int(t) for t in tg[i, :a + 1]])
+            self.stats["accepted"] += a
+            self.stats["emitted"] += a + 1
+        self.stats["rounds"] += 1
+        self.stats["proposed"] += R * Kd
+        self.kernel_launches_last = launches + 2
+        self.d2h_bytes_last = R * (Kd + 2) * 4
+        return out
+
+    def _review_logits(self, rows: int) -> torch.Tensor:
+        if not hasattr(self, "_rl") or self._rl.shape[0] < rows:
+            self._rl = torch.empty(rows, self.runner.w.lm_head.n, dtype=torch.bfloat16, device=self.device)
+        return self._rl

@@ -1,0 +1,101 @@
+"""Multi-token-prediction (MTP) draft head on the native kernels.
+
+Structure of the reference's MTP head (``models/qwen3_5/model.py:1512-1644``, ``executor/mtp_runner.py:152``):
+
+    u = fc([ rmsnorm_e(embed(token)) ; rmsnorm_h(previous hidden) ])      # 2H -> H
+    u = one full-attention decoder layer (own KV pages)                  # same layer code as the target
+    logits = lm_head(rmsnorm(u))                                          # embeddings and lm_head are SHARED
+
+Depth 1 consumes the target's hidden state of the last verified position, deeper proposals chain the head's
+own output hidden.  The head writes its KV into its own one-layer cache at the same page ids / slots as the
+target, so no extra page accounting is needed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import wq_pack
+from .config import ModelConfig
+from .decoder import DecoderRunner, LayerWeights, StepBatch, quantize_linear
+
+
+@dataclass
+class MtpWeights:
+    enorm: torch.Tensor
+    hnorm: torch.Tensor
+    fc: wq_pack.PackedWeight          # [H, 2H]
+    layer: LayerWeights
+    norm: torch.Tensor
+
+
+def random_mtp_weights(cfg: ModelConfig, device, seed: int = 1, std: float = 0.02) -> MtpWeights:
+    gen = torch.Generator(device=device).manual_seed(seed * 7919)
+    H, D = cfg.hidden_size, cfg.head_dim
+
+    def rnd(n, k):
+        return torch.randn(n, k, device=device, generator=gen) * std
+
+    ones = lambda n: torch.ones(n, device=device, dtype=torch.bfloat16)  # noqa: E731
+    layer = LayerWeights(ln1=ones(H), ln2=ones(H), qkv=quantize_linear(rnd((cfg.num_q_heads + 2 * cfg.num_kv_heads) * D, H), cfg),
+                         o=quantize_linear(rnd(H, cfg.q_size), cfg),
+                         gate_up=quantize_linear(rnd(2 * cfg.intermediate_size, H), cfg),
+                         down=quantize_linear(rnd(H, cfg.intermediate_size), cfg))
+    return MtpWeights(ones(H), ones(H), quantize_linear(rnd(H, 2 * H), cfg), layer, ones(H))
+
+
+class MtpRunner:
+    """Runs the draft head for a batch of rows; shares buffers, embeddings and lm_head with the target runner."""
+
+    def __init__(self, target: DecoderRunner, weights: MtpWeights) -> None:
+        self.t = target
+        self.w = weights
+        cfg, dev = target.cfg, target.device
+        blob = K.kv_blob_bytes(target.D, target.k_bits, target.v_bits)
+        self.kv = torch.zeros(target.num_pages, target.hkv, blob, dtype=torch.uint8, device=dev)
+        T, H = target.max_tokens, cfg.hidden_size
+        bf = torch.bfloat16
+        self.cat = torch.empty(T, 2 * H, dtype=bf, device=dev)
+        self.emb = torch.empty(T, H, dtype=bf, device=dev)
+        self.h = torch.empty(T, H, dtype=bf, device=dev)
+        self.launches = 0
+
+    def forward(self, b: StepBatch, prev_hidden: torch.Tensor) -> torch.Tensor:
+        """One pass over ``b.num_tokens`` rows.  ``prev_hidden[i]`` is the hidden state that precedes row i.
+
+        Returns the head's output hidden ``[T, H]`` (the residual stream after its decoder layer).
+        """
+        t, w, cfg = self.t, self.w, self.t.cfg
+        T, H = b.num_tokens, cfg.hidden_size
+        emb, cat, h = self.emb[:T], self.cat[:T], self.h[:T]
+        K.embedding(b.token_ids[:T], t.w.embed, out=emb, vocab_start=t.w.vocab_start)
+        # the two normalised halves sit side by side in `cat` (row stride 2H); the norm kernel writes dense
+        # rows, so it goes through dense temporaries and the halves are copied in
+        e_n = K.rmsnorm(emb, w.enorm, cfg.rms_eps)
+        h_n = K.rmsnorm(prev_hidden[:T], w.hnorm, cfg.rms_eps)
+        cat[:, :H].copy_(e_n)
+        cat[:, H:].copy_(h_n)
+        K.wq_gemm(cat, w.fc, out=h, ws=t.ws)
+        lw = w.layer
+        x, qkv, q, attn = t.x[:T], t.qkv[:T], t.q[:T], t.attn[:T]
+        K.rmsnorm(h, lw.ln1, cfg.rms_eps, out=x)
+        K.wq_gemm(x, lw.qkv, out=qkv, ws=t.ws)
+        K.rope_kv_write(qkv, q, self.kv, b.positions, b.slots, t.inv_freq, t.hq, t.hkv, t.D, t.k_bits, t.v_bits,
+                        q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps, rotary_dim=cfg.rotary_dim)
+        K.paged_attention(q.view(T, t.hq, t.D), attn.view(T, t.hq, t.D), self.kv, b.page_table,
+                          b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, t.hq, t.hkv, t.D, t.k_bits,
+                          t.v_bits, splits=b.attn_splits, ws=t.ws)
+        K.wq_gemm(attn, lw.o, out=h, residual=h, ws=t.ws)
+        K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x)
+        gu, act = t.gu[:T], t.act[:T]
+        K.wq_gemm(x, lw.gate_up, out=gu, ws=t.ws)
+        K.swiglu(gu, out=act)
+        K.wq_gemm(act, lw.down, out=h, residual=h, ws=t.ws)
+        self.launches = 16
+        return h
+
+    def logits(self, hidden: torch.Tensor, rows: int, out: torch.Tensor) -> torch.Tensor:
+        xn = K.rmsnorm(hidden[:rows], self.w.norm, self.t.cfg.rms_eps)
+        return K.wq_gemm(xn, self.t.w.lm_head, out=out[:rows], ws=self.t.ws)

@@ -41,6 +41,7 @@ class LLMEngine:
         self.pool = PagePool(num_pages)
         self.prefix = PrefixCache(self.pool, enabled=self.cfg.enable_prefix_cache)
         self.scheduler = ContinuousScheduler(self.cfg, self.pool, self.prefix)
+        self.scheduler.decode_lookahead = getattr(executor, "speculative_depth", 0)
         self.eos_token_id = eos_token_id
         self._ids = itertools.count()
         self.requests: dict[str, Request] = {}
@@ -104,12 +105,19 @@ class LLMEngine:
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
                                 sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF, r.draws,
                                 r.arrival))
-        ids = self.executor.execute(segs) if segs else []
+        spec = getattr(self.executor, "speculative_depth", 0)
+        if spec and segs and all(len(s.token_ids) == 1 and s.sample for s in segs):
+            # speculative round: every request gets its accepted drafts plus one bonus token
+            ids = self.executor.execute_speculative(segs)
+            self.spec_rounds = getattr(self, "spec_rounds", 0) + 1
+        else:
+            ids = self.executor.execute(segs) if segs else []
         sampled = {}
         it = iter(ids)
         for s in plan.segments:
             if s.sample:
-                sampled[s.request.request_id] = int(next(it))
+                v = next(it)
+                sampled[s.request.request_id] = [int(t) for t in v] if isinstance(v, (list, tuple)) else int(v)
             else:
                 self.prefill_tokens += s.count
         finished = {r.request_id: r for r in self.scheduler.commit(plan, sampled, self.eos_token_id)}
@@ -118,9 +126,13 @@ class LLMEngine:
             if not s.sample:
                 continue
             rid = s.request.request_id
-            self.generated_tokens += 1
+            toks = sampled[rid] if isinstance(sampled[rid], list) else [sampled[rid]]
             fin = finished.get(rid)
-            outs.append(StepOutput(rid, sampled[rid], fin is not None, fin.finish_reason if fin else None))
+            toks = toks[:s.request.last_committed]      # a stop / length limit may cut a speculative burst short
+            self.generated_tokens += len(toks)
+            for j, tok in enumerate(toks):
+                last = j == len(toks) - 1
+                outs.append(StepOutput(rid, tok, fin is not None and last, fin.finish_reason if (fin and last) else None))
             if fin is not None:
                 self.requests.pop(rid, None)
         return outs

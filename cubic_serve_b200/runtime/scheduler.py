@@ -69,6 +69,7 @@ class Request:
     slot: int = -1                 # row of the executor's page table
     draws: int = 0                 # sampler draw counter
     preemptions: int = 0
+    last_committed: int = 0        # tokens kept by the most recent commit (a stop can cut a speculative burst)
     tokens: list[int] = field(default_factory=list)   # prompt + output, maintained incrementally
 
     def __post_init__(self) -> None:
@@ -142,6 +143,7 @@ class ContinuousScheduler:
         self._clock = itertools.count()
         self._free_slots = list(range(cfg.max_running_requests - 1, -1, -1))
         self._rotate = 0
+        self.decode_lookahead = 0      # extra positions reserved per decode row (speculative drafts)
 
     # ---------------------------------------------------------------- admission
     def add(self, req: Request) -> None:
@@ -266,9 +268,11 @@ class ContinuousScheduler:
     def _try_segment(self, r: Request, n: int, plan: BatchPlan, scheduled: set) -> bool:
         if r.status is not RequestStatus.RUNNING:
             return False
+        reserve = n + (self.decode_lookahead if n == 1 and r.remaining == 1 else 0)
         while True:
             try:
-                self._ensure_pages(r, r.num_computed + n, plan.copies)
+                self._ensure_pages(r, min(r.num_computed + reserve, self.cfg.max_model_len + self.decode_lookahead),
+                                   plan.copies)
                 break
             except OutOfPages:
                 victim = self._preempt_newest(keep=r)
@@ -296,17 +300,27 @@ class ContinuousScheduler:
                 self.prefix.publish(r.tokens[:full * BLOCK], r.pages[:full])
                 r.num_published = full
             if seg.sample:
-                tok = sampled[r.request_id]
-                r.append_output(tok)
-                r.draws += 1
+                toks = sampled[r.request_id]
+                # a speculative round hands back several tokens (accepted drafts + the bonus token); each extra
+                # token also means one more position whose KV is already in the cache
+                toks = [toks] if isinstance(toks, int) else list(toks)
                 sp = r.sampling
-                stop = tok in sp.stop_token_ids or (eos_token_id is not None and tok == eos_token_id and not sp.ignore_eos)
-                if stop:
-                    self._retire(r, FinishReason.STOP)
-                    finished.append(r)
-                elif len(r.output) >= sp.max_tokens or r.num_tokens >= self.cfg.max_model_len:
-                    self._retire(r, FinishReason.LENGTH)
-                    finished.append(r)
+                r.last_committed = 0
+                for j, tok in enumerate(toks):
+                    r.append_output(tok)
+                    r.last_committed += 1
+                    r.draws += 1
+                    if j:
+                        r.num_computed += 1
+                    stop = tok in sp.stop_token_ids or (eos_token_id is not None and tok == eos_token_id and not sp.ignore_eos)
+                    if stop:
+                        self._retire(r, FinishReason.STOP)
+                        finished.append(r)
+                        break
+                    if len(r.output) >= sp.max_tokens or r.num_tokens >= self.cfg.max_model_len:
+                        self._retire(r, FinishReason.LENGTH)
+                        finished.append(r)
+                        break
         return finished
 
     def _retire(self, r: Request, reason: FinishReason) -> None:

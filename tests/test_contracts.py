@@ -1,0 +1,40 @@
+import pytest
+
+from cubic_serve_b200.contracts.execution import GraphBucket, GroupKind, LaunchPlan, ParallelTopology, ReplayLeasePool
+
+
+def test_topology_tp4_pp2_ep2():
+    t = ParallelTopology.single_node(range(8), tp=4, pp=2, ep=2)
+    assert t.world_size == 8 and t.etp == 2 and t.sampler_rank == 4
+    p = t.placement(6)
+    assert (p.stage, p.tensor_rank, p.expert_rank, p.expert_tensor_rank, p.device) == (1, 2, 1, 0, 6)
+    names = {g.name: g.ranks for g in t.groups}
+    assert names["tp:1"] == (4, 5, 6, 7) and names["pp:3"] == (3, 7)
+    assert names["ep:0:1"] == (1, 3) and names["etp:1:0"] == (4, 5)
+    kinds = {g.kind for g in t.groups_of(6)}
+    assert kinds == {GroupKind.TENSOR, GroupKind.PIPELINE, GroupKind.EXPERT, GroupKind.EXPERT_TENSOR}
+    assert t.expert_slice(6, 128) == (64, 128) and t.expert_slice(1, 128) == (0, 64)
+    assert t.layer_range(0, 94) == (0, 47) and t.layer_range(1, 94) == (47, 94)
+
+
+@pytest.mark.parametrize("kw", [dict(tp=3, pp=1, ep=2), dict(tp=2, pp=3, ep=1), dict(tp=4, pp=1, ep=1)])
+def test_topology_rejects(kw):
+    with pytest.raises(ValueError):
+        ParallelTopology.single_node(range(6 if kw["pp"] == 3 else 3), **kw)
+
+
+def test_launch_plan_and_lease():
+    buckets = [GraphBucket(c) for c in (256, 128, 64, 32)]
+    plan = LaunchPlan.choose(buckets, 70)
+    assert plan.bucket.capacity == 128 and plan.padding_rows == 58
+    with pytest.raises(ValueError):
+        LaunchPlan.choose(buckets, 300)
+    pool = ReplayLeasePool()
+    a = pool.acquire()
+    with pytest.raises(RuntimeError):
+        pool.acquire()
+    pool.release(a)
+    b = pool.acquire()
+    with pytest.raises(RuntimeError):
+        pool.release(a)
+    pool.release(b)

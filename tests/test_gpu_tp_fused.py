@@ -24,7 +24,6 @@ def test_scatter_reduce_norm_gather_pipeline(size, m):
     from cubic_serve_b200.parallel.tp import FusedTp, local_fabric
     H, N1 = 512, 1024
     g = torch.Generator().manual_seed(size * 100 + m)
-    h = (torch.randn(m, H, generator=g)).to(torch.bfloat16).to(DEV)
     w1 = (torch.randn(N1, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     w2 = (torch.randn(H, N1, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     n1 = (torch.rand(H, generator=g) + 0.5).to(torch.bfloat16).to(DEV)
@@ -33,27 +32,29 @@ def test_scatter_reduce_norm_gather_pipeline(size, m):
     w1s = [wq_pack.pack_bf16(w1[r * N1 // size:(r + 1) * N1 // size]) for r in range(size)]
     w2s = [wq_pack.pack_bf16(w2[:, r * N1 // size:(r + 1) * N1 // size].contiguous()) for r in range(size)]
 
-    href = h.clone()
-    for rep in range(3):                                   # several epochs through the same buffers
-        x = eager.rmsnorm(href, n1, 1e-6).to(torch.bfloat16)
+    # several launches through the same buffers and counters, with a DIFFERENT row count in between (a prefill
+    # step followed by decode steps): the consumers' expected arrival counts change from launch to launch
+    for rep, rows in enumerate([m, m, max(1, m // 2 + 5), m]):
+        h = (torch.randn(rows, H, generator=g)).to(torch.bfloat16).to(DEV)
+        x = eager.rmsnorm(h, n1, 1e-6).to(torch.bfloat16)
         y = (x.float() @ w1.float().t()).to(torch.bfloat16)
         partial = [(y[:, r * N1 // size:(r + 1) * N1 // size].float()
                     @ w2[:, r * N1 // size:(r + 1) * N1 // size].float().t()).to(torch.bfloat16) for r in range(size)]
-        z = torch.zeros(m, H, device=DEV)
+        z = torch.zeros(rows, H, device=DEV)
         for pr in partial:                                 # ascending rank order, fp32
             z += pr.float()
-        href2 = (href.float() + z.to(torch.bfloat16).float()).to(torch.bfloat16)
+        href2 = (h.float() + z.to(torch.bfloat16).float()).to(torch.bfloat16)
         xref2 = eager.rmsnorm(href2, n2, 1e-6)
 
         for f in ranks:
-            f.begin_step(m)
+            f.begin_step(rows)
             lo = f.rank * f.rpr
-            cnt = max(0, min(m, lo + f.rpr) - lo)
-            if rep == 0 and cnt:
+            cnt = max(0, min(rows, lo + f.rpr) - lo)
+            if cnt:
                 f.h_local[:cnt] = h[lo:lo + cnt]
         for f in ranks:
             f.reduce_norm(n1, 0, 0, 1e-6, reduce=False)
-        ys = [f.gemm_gather(w1s[f.rank], torch.empty(m, N1 // size, dtype=torch.bfloat16, device=DEV), 0) for f in ranks]
+        ys = [f.gemm_gather(w1s[f.rank], torch.empty(rows, N1 // size, dtype=torch.bfloat16, device=DEV), 0) for f in ranks]
         for f in ranks:
             f.gemm_scatter(ys[f.rank], w2s[f.rank], 1)
         for f in ranks:
@@ -64,10 +65,9 @@ def test_scatter_reduce_norm_gather_pipeline(size, m):
             f.ws.check_status()
             assert _rel(xg, xref2) < 1e-2, (rep, f.rank)
             lo = f.rank * f.rpr
-            cnt = max(0, min(m, lo + f.rpr) - lo)
+            cnt = max(0, min(rows, lo + f.rpr) - lo)
             if cnt:
                 assert _rel(f.h_local[:cnt], href2[lo:lo + cnt]) < 1e-2
-        href = href2
         assert _rel(torch.cat([y_ for y_ in ys], 1), y) < 1e-2
 
 
