@@ -197,22 +197,23 @@ class BatchBuilder:
 
 class GpuExecutor:
     def __init__(self, runner: DecoderRunner, max_rows: int = 256, max_prefill_tokens: int = 8192,
-                 max_model_len: int = 4096, use_graphs: bool = True) -> None:
+                 max_model_len: int = 4096, use_graphs: bool = True, rows_per_request: int = 1) -> None:
+        """``rows_per_request`` > 1 sizes the sampled-row staging for speculative review (K + 1 rows per request)."""
         self.runner = runner
         self.cfg = runner.cfg
         self.device = runner.device
         self.max_rows = max_rows
         self.max_tokens = max(max_prefill_tokens, max_rows)
         assert self.max_tokens <= runner.max_tokens
-        self.builder = BatchBuilder(max_rows, self.max_tokens, max_model_len, runner.hq // runner.hkv, runner.hkv,
-                                    self.device)
+        self.builder = BatchBuilder(max_rows * rows_per_request, self.max_tokens, max_model_len,
+                                    runner.hq // runner.hkv, runner.hkv, self.device)
         self.stage = self.builder.stage
         self._fill = self.builder._fill
         self.invalidate_page_rows = self.builder.invalidate_page_rows
         v_local = runner.w.lm_head.n
         self.logits = torch.empty(max_rows, v_local, dtype=torch.bfloat16, device=self.device)
-        self.out_ids = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.out_ids = torch.zeros(max_rows * rows_per_request, dtype=torch.int32, device=self.device)
+        self.out_host = torch.zeros(max_rows * rows_per_request, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.use_graphs = use_graphs
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.stream = torch.cuda.Stream(device=self.device)

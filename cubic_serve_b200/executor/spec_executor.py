@@ -23,7 +23,7 @@ from .gpu_executor import GpuExecutor, Segment
 class SpeculativeGpuExecutor(GpuExecutor):
     def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
                  **kw) -> None:
-        super().__init__(runner, **kw)
+        super().__init__(runner, rows_per_request=depth + 1, use_graphs=False, **kw)
         self.mtp = mtp
         self.speculative_depth = depth
         self.force_acceptance = force_acceptance

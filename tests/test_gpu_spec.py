@@ -56,6 +56,6 @@ def test_forced_acceptance_rate_and_tokens_per_round():
     runner.ws.check_status()
     assert all(len(o) == 60 for o in out)
     rate = ex.stats["accepted"] / ex.stats["proposed"]
-    per_round = ex.stats["emitted"] / (ex.stats["rounds"] * 6)
-    # first-failure model with p = 0.7 and depth 4: E[accepted] = p + p^2 + p^3 + p^4 = 1.77
-    assert 0.3 < rate < 0.6 and 2.2 < per_round < 3.4, (rate, per_round)
+    per_round = ex.stats["emitted"] / (ex.stats["proposed"] / 4)      # tokens per request and verify step
+    # first-failure model with p = 0.7 and depth 4: E[accepted] = p + p^2 + p^3 + p^4 = 1.77 (about 140 samples here)
+    assert 0.3 < rate < 0.6 and 2.0 < per_round < 3.4, (rate, per_round)
