@@ -1,0 +1,254 @@
+"""Process-per-GPU execution: a controller-side executor proxy and the rank worker loop.
+
+Shape of the reference's controller / worker split (``runtime/performance.py:8813-9247`` ``_ProcessController``,
+``runtime/quantized_graph.py:263`` worker there): the controller process owns HTTP, tokenisation, scheduling
+and the page pool; one spawned worker per GPU owns the weights shard, the KV cache and the captured graphs.
+A step is broadcast to every rank over pipes (all ranks execute the same batch), the sampler rank answers with
+the token ids.  Liveness: a worker that exits, or a result that does not arrive within the watchdog period,
+poisons the executor (fail closed) with a message that names the rank and decodes the exit signal.
+"""
+from __future__ import annotations
+
+import multiprocessing as mp
+import os
+import signal
+import socket
+import time
+from dataclasses import dataclass
+
+import numpy as np
+
+
+class WorkerFailure(RuntimeError):
+    pass
+
+
+@dataclass
+class WorkerSpec:
+    model: str                   # checkpoint dir or random:<config>
+    devices: list[int]
+    tp: int
+    k_bits: int
+    v_bits: int
+    max_rows: int
+    token_budget: int
+    max_model_len: int
+    num_pages: int | None
+    tp_comm: str = "fused"
+    seed: int = 0
+    gpu_reserve_gib: float = 4.0
+
+
+def describe_exit(code: int | None) -> str:
+    """Human-readable reason for a child exit code (negative = killed by that signal)."""
+    if code is None:
+        return "still running"
+    if code == 0:
+        return "exited normally"
+    if code < 0:
+        try:
+            name = signal.Signals(-code).name
+        except ValueError:
+            name = f"signal {-code}"
+        hint = {"SIGSEGV": " (memory fault in native code)", "SIGKILL": " (killed, often by the out-of-memory killer)",
+                "SIGBUS": " (bus error, often a full /dev/shm)"}.get(name, "")
+        return f"terminated by {name}{hint}"
+    return f"exited with status {code}"
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
+    """Rank process: build everything, report readiness, then serve commands until told to close."""
+    import torch
+    import torch.distributed as dist
+
+    from ..models.config import NAMED_CONFIGS
+    from ..models.decoder import DecoderRunner, random_decoder_weights
+    from ..parallel.tp import TensorParallel
+    from ..runtime.serving import plan_kv_pages
+    from .gpu_executor import GpuExecutor
+    try:
+        dev = torch.device("cuda", spec.devices[rank])
+        torch.cuda.set_device(dev)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        tp = None
+        if spec.tp > 1:
+            dist.init_process_group("nccl", rank=rank, world_size=spec.tp, device_id=dev)
+        conn.send(("progress", rank, "process group up"))
+        if spec.model.startswith("random:"):
+            cfg = NAMED_CONFIGS[spec.model.split(":", 1)[1]]()
+            weights = random_decoder_weights(cfg, dev, spec.seed, rank, spec.tp)
+        else:
+            from ..models.checkpoint import admit_checkpoint, load_decoder_weights
+            ck = admit_checkpoint(spec.model)
+            cfg = ck.cfg
+            weights = load_decoder_weights(ck, dev, rank, spec.tp)
+        conn.send(("progress", rank, "weights loaded"))
+        if spec.tp > 1:
+            tp = TensorParallel(dist.group.WORLD, dev, mode=spec.tp_comm, hidden=cfg.hidden_size,
+                                max_tokens=spec.token_budget, rows_max=max(512, spec.max_rows))
+        pages = spec.num_pages
+        if pages is None:
+            free, _ = torch.cuda.mem_get_info(dev)
+            pages = plan_kv_pages(free, int(spec.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, spec.tp, spec.k_bits,
+                                  spec.v_bits, spec.max_model_len, spec.max_rows)
+            if spec.tp > 1:                                   # every rank must agree: take the minimum
+                t = torch.tensor([pages], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                pages = int(t.item())
+        runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=spec.token_budget, k_bits=spec.k_bits,
+                               v_bits=spec.v_bits, tp=tp)
+        ex = GpuExecutor(runner, max_rows=spec.max_rows, max_prefill_tokens=spec.token_budget,
+                         max_model_len=spec.max_model_len)
+        caps = ex.capture_decode_graphs()
+        conn.send(("ready", rank, {"pages": pages, "capacities": caps, "vocab": cfg.vocab_size, "name": cfg.name}))
+        while True:
+            cmd = conn.recv()
+            if cmd[0] == "execute":
+                ids = ex.execute(cmd[1])
+                runner.ws.check_status()
+                if rank == 0:
+                    conn.send(("result", ids, ex.kernel_launches_last))
+            elif cmd[0] == "copy":
+                ex.copy_pages(cmd[1])
+                ex.invalidate_page_rows(cmd[2])
+            elif cmd[0] == "close":
+                break
+        if spec.tp > 1:
+            dist.destroy_process_group()
+    except Exception as exc:  # noqa: BLE001 - reported to the controller, which fails closed
+        try:
+            conn.send(("error", rank, f"{type(exc).__name__}: {exc}"))
+        except Exception:  # noqa: BLE001
+            pass
+        raise
+
+
+class MultiprocExecutor:
+    """Controller-side proxy with the executor contract (``execute`` / ``copy_pages``)."""
+
+    def __init__(self, spec: WorkerSpec, startup_timeout: float = 1800.0, result_timeout: float = 600.0,
+                 worker_target=_worker_main, start: bool = True) -> None:
+        self.spec = spec
+        self.result_timeout = result_timeout
+        self.startup_timeout = startup_timeout
+        self.poisoned = False
+        self.info: dict = {}
+        self.h2d_bytes_last = self.d2h_bytes_last = self.kernel_launches_last = 0
+        self._procs: list = []
+        self._conns: list = []
+        if start:
+            self._spawn(worker_target)
+            self._await_ready()
+
+    def _spawn(self, target) -> None:
+        ctx = mp.get_context("spawn")
+        port = _free_port()
+        for r in range(self.spec.tp):
+            parent, child = ctx.Pipe()
+            p = ctx.Process(target=target, args=(r, self.spec, port, child), name=f"cubic-rank-{r}", daemon=True)
+            p.start()
+            child.close()
+            self._procs.append(p)
+            self._conns.append(parent)
+
+    def _fail(self, message: str) -> None:
+        self.poisoned = True
+        raise WorkerFailure(message)
+
+    def _check_alive(self) -> None:
+        for r, p in enumerate(self._procs):
+            if not p.is_alive():
+                self._fail(f"rank {r} {describe_exit(p.exitcode)}")
+
+    def _await_ready(self) -> None:
+        """Each rank must report readiness; any validated progress message renews that rank's lease."""
+        deadline = [time.time() + self.startup_timeout] * len(self._conns)
+        ready = [False] * len(self._conns)
+        while not all(ready):
+            for r, c in enumerate(self._conns):
+                if ready[r]:
+                    continue
+                if c.poll(0.05):
+                    try:
+                        msg = c.recv()
+                    except EOFError:
+                        self._check_alive()
+                        self._fail(f"rank {r} closed its pipe during start-up")
+                    if msg[0] == "ready":
+                        ready[r] = True
+                        self.info = self.info or msg[2]
+                        if msg[2]["pages"] != self.info["pages"]:
+                            self._fail("ranks disagree on the number of KV pages")
+                    elif msg[0] == "progress":
+                        deadline[r] = time.time() + self.startup_timeout
+                    elif msg[0] == "error":
+                        self._fail(f"rank {r} failed during start-up: {msg[2]}")
+                elif time.time() > deadline[r]:
+                    self._fail(f"rank {r} made no start-up progress for {self.startup_timeout:.0f} s")
+            self._check_alive()
+
+    # ------------------------------------------------------------- executor API
+    def execute(self, segs) -> np.ndarray:
+        if self.poisoned:
+            raise WorkerFailure("executor is poisoned")
+        for c in self._conns:
+            c.send(("execute", segs))
+        c0 = self._conns[0]
+        t0 = time.time()
+        while not c0.poll(0.01):
+            self._check_alive()
+            if time.time() - t0 > self.result_timeout:
+                self._fail(f"no result from the sampler rank within {self.result_timeout:.0f} s")
+        try:
+            msg = c0.recv()
+        except EOFError:
+            self._check_alive()
+            self._fail("sampler rank closed its pipe")
+        if msg[0] == "error":
+            self._fail(f"rank {msg[1]} failed: {msg[2]}")
+        self.kernel_launches_last = msg[2]
+        return msg[1]
+
+    def copy_pages(self, pairs) -> None:
+        for c in self._conns:
+            c.send(("copy", pairs, []))
+
+    def invalidate_page_rows(self, slots) -> None:
+        for c in self._conns:
+            c.send(("copy", [], list(slots)))
+
+    def close(self) -> None:
+        for c in self._conns:
+            try:
+                c.send(("close",))
+            except (OSError, BrokenPipeError):
+                pass
+        for p in self._procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+
+
+def build_multiproc_backend(args, devices, tp, spec_cfg, k_bits, v_bits):
+    from ..runtime.async_engine import TokenChatBackend
+    from ..runtime.engine import LLMEngine
+    from ..runtime.scheduler import SchedulerConfig
+    from ..runtime.serving import _tokenizer_for
+    if args.pp_size != 1:
+        raise SystemExit("pipeline parallel serving is not available in this build; use --pp-size 1")
+    max_len = args.max_model_len or 8192
+    spec = WorkerSpec(args.model, devices, tp, k_bits, v_bits, args.max_running_requests, args.token_budget, max_len,
+                      None, args.tp_comm, args.seed, args.gpu_reserve_gib)
+    ex = MultiprocExecutor(spec)
+    sched = SchedulerConfig(max_running_requests=args.max_running_requests, max_batched_tokens=args.token_budget,
+                            prefill_chunk_tokens=min(args.prefill_chunk_tokens, args.token_budget), max_model_len=max_len,
+                            enable_prefix_cache=args.prefix_cache)
+    tok = _tokenizer_for(args.model, ex.info["vocab"])
+    engine = LLMEngine(ex, num_pages=ex.info["pages"], scheduler_config=sched, eos_token_id=getattr(tok, "eos_token_id", None))
+    return TokenChatBackend(engine, tok, default_thinking=args.thinking), (args.served_model_name or ex.info["name"])

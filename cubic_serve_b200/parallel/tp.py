@@ -146,7 +146,7 @@ class FusedTp:
         for r in range(self.size):
             link.recv[r] = self.b.recv_ptrs[r] + self._recv_off(s)
             link.rs_flag[r] = self.b.flags_ptrs[r] + self._flag_off(s, 0)
-        K.wq_gemm(x, w, out=None, ws=self.ws, link=link, splits=1 if x.shape[0] >= 64 else None)
+        K.wq_gemm(x, w, out=None, ws=self.ws, link=link)
 
     def n_tiles_expected(self, n: int, m: int) -> int:
         """Arrivals per source rank at one owner: (n tiles) x (m tiles overlapping the owner's rows)."""
@@ -180,7 +180,7 @@ class FusedTp:
         link.ag_flag = self.b.flags.data_ptr() + self._flag_off(s, 1)
         link.ag_state = self._state_ptr(s, 1)
         link.ag_expected = self.rpr
-        return K.wq_gemm(self.x_view(s), w, out=out, ws=self.ws, link=link, splits=1)
+        return K.wq_gemm(self.x_view(s), w, out=out, ws=self.ws, link=link)
 
     def wait_gather(self, s: int) -> torch.Tensor:
         native.check(native.lib().cb_tp_wait(self.b.flags.data_ptr() + self._flag_off(s, 1), self._state_ptr(s, 1),
