@@ -218,7 +218,12 @@ def main() -> None:
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing the communicator down: destroying a process group whose collectives are
+        # referenced by live CUDA graphs can block forever, and there is nothing left to flush
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
