@@ -410,7 +410,6 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     tc_fence_after();
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     const int pair = (warp - 2) >> 2;        // four warps share a quadrant; they interleave 16-column chunks
-    const int n = n_tile * kTileN + quad * 32 + lane;
     const int chunks = p.mb >> 4;
     // where element (m, n) of the result goes: the local output, or (scatter-push)
     // the receive buffer of the rank that owns row m
@@ -427,18 +426,56 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     };
     if (acc_ok && iters > 0) {
       if (p.splits == 1) {
+        // TMEM -> registers -> fp32 tile [row][128 features] in the (now idle) stage memory, then all 512 threads
+        // write 16-byte row segments: coalesced for the local output and for the peers' receive buffers alike
+        float* stg = reinterpret_cast<float*>(smem);
         for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
           uint32_t acc[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
           tmem_ld_wait();
-          if (n < p.N) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + ci * 16 + j;
-              if (m < m_end) {
-                store_out(m, n, __uint_as_float(acc[j]) * p.alpha);
+          for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]) * p.alpha;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
+        const int rows_here = min(p.mb, m_end - m0);
+        const int n_base = n_tile * kTileN;
+        const bool vec_ok = (p.ldy & 7) == 0 && (p.N & 7) == 0;
+        for (int idx = dq; idx < rows_here * (kTileN / 8); idx += kNumDequantWarps * 32) {
+          const int mm = idx >> 4;                 // kTileN / 8 = 16 segments of 8 features per row
+          const int n0 = n_base + (idx & 15) * 8;
+          if (n0 >= p.N) continue;
+          const int m = m0 + mm;
+          const float4 f0 = *reinterpret_cast<const float4*>(stg + mm * kTileN + (idx & 15) * 8);
+          const float4 f1 = *reinterpret_cast<const float4*>(stg + mm * kTileN + (idx & 15) * 8 + 4);
+          float v[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+          if (vec_ok && n0 + 7 < p.N) {
+            __nv_bfloat16* dst;
+            if (p.tp.mode & kTpScatterPush) {
+              const int o = m / p.tp.rows_per_rank;
+              const int lr = m - o * p.tp.rows_per_rank;
+              dst = p.tp.recv[o] + (static_cast<size_t>(p.tp.rank) * p.tp.rows_per_rank + lr) * p.N + n0;
+            } else {
+              const size_t off = static_cast<size_t>(m) * p.ldy + n0;
+              dst = p.y + off;
+              if (p.residual) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + off);
+                const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 r2 = __bfloat1622float2(rp[j]);
+                  v[2 * j] += r2.x;
+                  v[2 * j + 1] += r2.y;
+                }
               }
             }
+            uint4 ov;
+            ov.x = pack_bf16x2(v[0], v[1]); ov.y = pack_bf16x2(v[2], v[3]);
+            ov.z = pack_bf16x2(v[4], v[5]); ov.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(dst) = ov;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (n0 + j < p.N) store_out(m, n0 + j, v[j]);
           }
         }
       } else {
@@ -485,7 +522,15 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
           const int m = m0 + mm;
           const float o4[4] = {acc.x, acc.y, acc.z, acc.w};
-          if (!(p.tp.mode & kTpScatterPush) && n_base + c4 + 3 < p.N && ((p.ldy & 3) == 0)) {
+          if ((p.tp.mode & kTpScatterPush) && n_base + c4 + 3 < p.N && ((p.N & 3) == 0)) {
+            const int o = m / p.tp.rows_per_rank;
+            const int lr = m - o * p.tp.rows_per_rank;
+            uint2 ov;
+            ov.x = pack_bf16x2(o4[0] * p.alpha, o4[1] * p.alpha);
+            ov.y = pack_bf16x2(o4[2] * p.alpha, o4[3] * p.alpha);
+            *reinterpret_cast<uint2*>(p.tp.recv[o] + (static_cast<size_t>(p.tp.rank) * p.tp.rows_per_rank + lr) * p.N +
+                                      n_base + c4) = ov;
+          } else if (!(p.tp.mode & kTpScatterPush) && n_base + c4 + 3 < p.N && ((p.ldy & 3) == 0)) {
             const size_t off = static_cast<size_t>(m) * p.ldy + n_base + c4;
             float r4[4] = {0.f, 0.f, 0.f, 0.f};
             if (p.residual) {
