@@ -149,9 +149,11 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
       }
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < p.size) red_rel_sys_add(p.ag_flag_peer[threadIdx.x] + p.rank, 1u);
+  if (threadIdx.x < p.size) {
+    __threadfence_system();   // cumulative: covers the row pushed by the whole CTA (ordered by the barrier above)
+    red_rel_sys_add(p.ag_flag_peer[threadIdx.x] + p.rank, 1u);
+  }
   if (threadIdx.x == 0) {
     if (!ok) atomicExch(p.status, static_cast<uint32_t>(kErrFlagTimeout));
     if (p.rs_expected) {
@@ -209,9 +211,9 @@ tp_argmax_merge_kernel(const ArgmaxMergeParams p) {
       p.slot_id[r][p.rank * p.rows_max + i] = id;
     }
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x < p.size) {
+    __threadfence_system();
     red_rel_sys_add(p.flag_peer[threadIdx.x] + p.rank, 1u);
     if (!wait_ge(p.my_flag + threadIdx.x, p.my_state[0] + 1u)) ok_flag = 0;
   }
