@@ -40,6 +40,9 @@ def parse_args():
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collective path")
     ap.add_argument("--kv", default="", help="K,V cache bits, e.g. 8,8 or 4,8 (default: 8,8 dense, 4,8 MoE)")
     ap.add_argument("--prefill-tokens", type=int, default=8192, help="token budget of a prefill step")
+    ap.add_argument("--spec-depth", type=int, default=0, help="MTP draft tokens per round (0 = no speculation)")
+    ap.add_argument("--accept", type=float, default=0.7,
+                    help="forced per-depth acceptance probability of speculative rounds (random weights never agree)")
     return ap.parse_args()
 
 
@@ -133,15 +136,23 @@ def main() -> None:
                             max_tokens=args.prefill_tokens, rows_max=max(args.concurrency, 512))
     C, L = args.concurrency, args.input_len
     total_steps = args.warmup + args.steps
-    max_len = L + total_steps + 8
+    max_len = L + total_steps * (1 + args.spec_depth) + 8 + args.spec_depth
     pages_per_req = -(-max_len // 16)
     num_pages = C * pages_per_req + 8
     prefill_tokens = args.prefill_tokens
 
     weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
     runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=k_bits, v_bits=v_bits, tp=tp)
-    ex = GpuExecutor(runner, max_rows=C, max_prefill_tokens=prefill_tokens, max_model_len=max_len)
-    ex.capture_decode_graphs([C])
+    if args.spec_depth:
+        from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
+        from cubic_serve_b200.models.mtp import MtpRunner, random_mtp_weights
+        assert world == 1, "speculative rounds run with tensor parallel size 1 in this benchmark"
+        ex = SpeculativeGpuExecutor(runner, MtpRunner(runner, random_mtp_weights(cfg, dev)), args.spec_depth,
+                                    force_acceptance=args.accept, max_rows=C, max_prefill_tokens=prefill_tokens,
+                                    max_model_len=max_len)
+    else:
+        ex = GpuExecutor(runner, max_rows=C, max_prefill_tokens=prefill_tokens, max_model_len=max_len)
+        ex.capture_decode_graphs([C])
     ex.timing = True
     eng = LLMEngine(ex, num_pages=num_pages,
                     scheduler_config=SchedulerConfig(max_running_requests=C, max_batched_tokens=prefill_tokens,
@@ -149,7 +160,7 @@ def main() -> None:
                                                      enable_prefix_cache=False))
     rng = np.random.default_rng(1)
     prompts = rng.integers(0, cfg.vocab_size, size=(C, L)).tolist()
-    sp = SamplingParams(temperature=0.0, max_tokens=total_steps + 4, ignore_eos=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=total_steps * (1 + args.spec_depth) + 4, ignore_eos=True)
     for p in prompts:
         eng.add_request(p, SamplingParams(**vars(sp)))
 
@@ -173,7 +184,7 @@ def main() -> None:
     # ---- decode: W warm-up steps, K timed steps
     for _ in range(args.warmup):
         outs = eng.step()
-        assert len(outs) == C
+        assert len(outs) >= C
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -181,20 +192,22 @@ def main() -> None:
     sync()
     t0 = time.perf_counter()
     launches = 0
+    emitted = 0
     for _ in range(args.steps):
         outs = eng.step()
+        emitted += len(outs)
         launches += ex.kernel_launches_last
     sync()
     wall_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else {}
-    assert len(outs) == C
+    assert len(outs) >= C
     runner.ws.check_status()
     dev_ms = float(sum(ex.device_ms))
     stats = torch.tensor([dev_ms, wall_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     dev_ms, wall_ms = stats.tolist()
-    tokens = C * args.steps
+    tokens = emitted
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / (wall_ms / 1e3)
     if rank == 0:
@@ -210,7 +223,10 @@ def main() -> None:
                        "comm": (tp.mode if tp is not None else "none"), "cuda_graphs": True, "kv_cache": f"int{k_bits}/int{v_bits}",
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,
-                       "weights_gb": round(weights.nbytes() / 1e9, 2)},
+                       "weights_gb": round(weights.nbytes() / 1e9, 2),
+                       **({"speculative": {"depth": args.spec_depth, "forced_acceptance": args.accept,
+                                           "tokens_per_verify_step": round(emitted / (C * args.steps), 3),
+                                           "verify_step_ms": round(dev_ms / args.steps, 3)}} if args.spec_depth else {})},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(ex.h2d_bytes_last),
                     "d2h_bytes_per_step": int(ex.d2h_bytes_last), "api": "LLMEngine.step()"},

@@ -1,0 +1,43 @@
+"""Host-side batch staging: decode fast path, prefill row blocks, padding rows, incremental page-table rows."""
+import numpy as np
+
+from cubic_serve_b200.executor.gpu_executor import BatchBuilder, Segment
+
+
+def test_decode_fast_path_and_padding():
+    bb = BatchBuilder(max_rows=8, max_tokens=256, max_model_len=256, group=4, kv_heads=2, device="cpu")
+    segs = [Segment(i, [10 + i], 33 + i, list(range(i * 10, i * 10 + 4)), True, 0.5, 0.9, 3, 7, 2, uid=i) for i in range(3)]
+    b, rows = bb.fill(segs, pad_rows_to=8)
+    h = bb.stage.h
+    assert (rows, b.num_tokens, b.num_row_blocks, b.num_logit_rows) == (3, 8, 8, 8)
+    assert h["token_ids"][:3].tolist() == [10, 11, 12] and h["positions"][:3].tolist() == [33, 34, 35]
+    # slot = page * 16 + offset with page = pages[pos >> 4]
+    assert h["slots"][:3].tolist() == [2 * 16 + 1, 12 * 16 + 2, 22 * 16 + 3]
+    assert h["slots"][3:8].tolist() == [-1] * 5 and h["rb_qcount"][:8].tolist() == [1, 1, 1, 0, 0, 0, 0, 0]
+    assert h["rb_ctx"][:3].tolist() == [34, 35, 36] and h["rb_req"][:3].tolist() == [0, 1, 2]
+    assert h["page_table"][1, :4].tolist() == [10, 11, 12, 13]
+    assert np.allclose(h["temperature"][:3], 0.5) and h["temperature"][3] == 0 and h["top_k"][:3].tolist() == [3, 3, 3]
+    assert b.attn_splits == min(32, -(-296 // (8 * 2)))
+
+
+def test_prefill_blocks_and_incremental_page_rows():
+    bb = BatchBuilder(max_rows=4, max_tokens=256, max_model_len=256, group=8, kv_heads=1, device="cpu")   # 2 positions per block
+    seg = Segment(2, list(range(100, 105)), 16, [7, 8], True, uid=5)
+    b, rows = bb.fill([seg, Segment(0, [1, 2], 0, [3], False, uid=6)])
+    h = bb.stage.h
+    assert (b.num_tokens, b.num_row_blocks, rows) == (7, 4, 1)
+    assert h["rb_qstart"][:4].tolist() == [0, 2, 4, 5] and h["rb_qcount"][:4].tolist() == [2, 2, 1, 2]
+    assert h["rb_ctx"][:4].tolist() == [17, 19, 21, 1] and h["rb_req"][:4].tolist() == [2, 2, 2, 0]
+    assert h["logit_rows"][0] == 4 and h["slots"][:5].tolist() == [8 * 16 + i for i in range(5)]
+    # the request grows by one page: only the new entry is written
+    h["page_table"][2, 0] = 99                        # would be overwritten by a full rewrite
+    seg2 = Segment(2, [1], 32, [7, 8, 9], True, uid=5)
+    bb.fill([seg2])
+    assert h["page_table"][2, :3].tolist() == [99, 8, 9]
+    # a different request reusing the slot rewrites the row; so does an explicit invalidation
+    bb.fill([Segment(2, [1], 0, [4], True, uid=6)])
+    assert h["page_table"][2, 0] == 4
+    h["page_table"][2, 0] = 55
+    bb.invalidate_page_rows([2])
+    bb.fill([Segment(2, [1], 1, [4], True, uid=6)])
+    assert h["page_table"][2, 0] == 4
