@@ -38,6 +38,7 @@ def parse_args():
     ap.add_argument("--input-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collective path")
+    ap.add_argument("--pp", type=int, default=1, choices=[1, 2], help="pipeline stages (tp = gpus / pp)")
     ap.add_argument("--kv", default="", help="K,V cache bits, e.g. 8,8 or 4,8 (default: 8,8 dense, 4,8 MoE)")
     ap.add_argument("--prefill-tokens", type=int, default=8192, help="token budget of a prefill step")
     ap.add_argument("--spec-depth", type=int, default=0, help="MTP draft tokens per round (0 = no speculation)")
@@ -128,12 +129,26 @@ def main() -> None:
         from dataclasses import replace
         cfg = replace(cfg, num_layers=args.layers)
     k_bits, v_bits = (int(b) for b in (args.kv or ("4,8" if cfg.is_moe else "8,8")).split(","))
-    tp = None
+    tp = pp = None
+    tp_size, tp_rank, layer_range = world // args.pp, rank % (world // args.pp), None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from cubic_serve_b200.parallel.tp import TensorParallel
-        tp = TensorParallel(dist.group.WORLD, dev, mode=args.comm if not cfg.is_moe else "nccl", hidden=cfg.hidden_size,
-                            max_tokens=args.prefill_tokens, rows_max=max(args.concurrency, 512))
+        tp_group = dist.group.WORLD
+        if args.pp > 1:
+            from cubic_serve_b200.contracts.execution import ParallelTopology
+            from cubic_serve_b200.parallel.pp import PipelineStage
+            topo = ParallelTopology.single_node(range(world), tp_size, args.pp)
+            pp = PipelineStage.from_topology(topo, rank, dist.group.WORLD)
+            layer_range = topo.layer_range(pp.stage, cfg.num_layers)
+            for stage in range(args.pp):
+                if tp_size > 1:
+                    g = dist.new_group(list(range(stage * tp_size, (stage + 1) * tp_size)))
+                    tp_group = g if stage == pp.stage else tp_group
+        if tp_size > 1:
+            mode = args.comm if not cfg.is_moe and pp is None else "nccl"
+            tp = TensorParallel(tp_group, dev, mode=mode, hidden=cfg.hidden_size,
+                                max_tokens=args.prefill_tokens, rows_max=max(args.concurrency, 512))
     C, L = args.concurrency, args.input_len
     total_steps = args.warmup + args.steps
     max_len = L + total_steps * (1 + args.spec_depth) + 8 + args.spec_depth
@@ -141,8 +156,9 @@ def main() -> None:
     num_pages = C * pages_per_req + 8
     prefill_tokens = args.prefill_tokens
 
-    weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
-    runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=k_bits, v_bits=v_bits, tp=tp)
+    weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=tp_rank, tp_size=tp_size, layer_range=layer_range)
+    runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=k_bits, v_bits=v_bits,
+                           tp=tp, pp=pp)
     if args.spec_depth:
         from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
         from cubic_serve_b200.models.mtp import MtpRunner, random_mtp_weights
@@ -219,7 +235,7 @@ def main() -> None:
             "data": "synthetic (random token ids; random-init N(0,0.02) weights quantized offline)",
             "impl": "ours",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
-                       "global_batch": C, "seq_len": L, "parallelism": f"tp{world}",
+                       "global_batch": C, "seq_len": L, "parallelism": f"tp{tp_size}" + (f"pp{args.pp}" if args.pp > 1 else ""),
                        "comm": (tp.mode if tp is not None else "none"), "cuda_graphs": True, "kv_cache": f"int{k_bits}/int{v_bits}",
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,

@@ -239,6 +239,10 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int kb_hi = static_cast<int>((static_cast<long long>(p.k_blocks) * (split + 1)) / p.splits);
   const int iters = kb_hi - kb_lo;
 
+  // timeline rows 0..2, slots 6/7 hold kernel-level stamps: entry, set-up done, accumulator complete,
+  // epilogue stores issued, split-K reduction done
+  unsigned long long* trace = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+  if (trace && threadIdx.x == 64) trace[6] = clock64();
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
@@ -259,7 +263,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
-  unsigned long long* trace = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
+  if (trace && threadIdx.x == 64) trace[7] = clock64();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -408,6 +412,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // epilogue: TMEM lane = output feature, column = batch row
     const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_t<200>(smem_u32(&ctl->acc_full), 0, abort_flag));
     tc_fence_after();
+    if (trace && dq == 0) trace[8 + 6] = clock64();
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     const int pair = (warp - 2) >> 2;        // four warps share a quadrant; they interleave 16-column chunks
     const int chunks = p.mb >> 4;
@@ -491,6 +496,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
     }
+    if (trace && dq == 0) trace[8 + 7] = clock64();
     if (p.splits > 1) {
       // last-arriving split sums all partials in split order (deterministic)
       __threadfence();
@@ -570,6 +576,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
   tc_fence_before();
   __syncthreads();
+  if (trace && threadIdx.x == 64) trace[16 + 6] = clock64();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);

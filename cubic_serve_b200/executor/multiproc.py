@@ -37,6 +37,11 @@ class WorkerSpec:
     tp_comm: str = "fused"
     seed: int = 0
     gpu_reserve_gib: float = 4.0
+    pp: int = 1                  # pipeline stages; rank = stage * tp + tensor rank
+
+    @property
+    def world(self) -> int:
+        return self.tp * self.pp
 
 
 def describe_exit(code: int | None) -> str:
@@ -69,6 +74,8 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
 
     from ..models.config import NAMED_CONFIGS
     from ..models.decoder import DecoderRunner, random_decoder_weights
+    from ..contracts.execution import ParallelTopology
+    from ..parallel.pp import PipelineStage
     from ..parallel.tp import TensorParallel
     from ..runtime.serving import plan_kv_pages
     from .gpu_executor import GpuExecutor
@@ -76,33 +83,46 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
         dev = torch.device("cuda", spec.devices[rank])
         torch.cuda.set_device(dev)
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-        tp = None
-        if spec.tp > 1:
-            dist.init_process_group("nccl", rank=rank, world_size=spec.tp, device_id=dev)
+        topo = ParallelTopology.single_node(spec.devices, spec.tp, spec.pp)
+        place = topo.placement(rank)
+        tp = pp = tp_group = None
+        if spec.world > 1:
+            dist.init_process_group("nccl", rank=rank, world_size=spec.world, device_id=dev)
+            tp_group = dist.group.WORLD
+            if spec.pp > 1 and spec.tp > 1:                   # every rank creates every stage's group, in order
+                for stage in range(spec.pp):
+                    g = dist.new_group(list(range(stage * spec.tp, (stage + 1) * spec.tp)))
+                    if stage == place.stage:
+                        tp_group = g
         conn.send(("progress", rank, "process group up"))
+        t_rank = place.tensor_rank
         if spec.model.startswith("random:"):
             cfg = NAMED_CONFIGS[spec.model.split(":", 1)[1]]()
-            weights = random_decoder_weights(cfg, dev, spec.seed, rank, spec.tp)
+            layers = topo.layer_range(place.stage, cfg.num_layers)
+            weights = random_decoder_weights(cfg, dev, spec.seed, t_rank, spec.tp, layer_range=layers)
         else:
             from ..models.checkpoint import admit_checkpoint, load_decoder_weights
             ck = admit_checkpoint(spec.model)
             cfg = ck.cfg
-            weights = load_decoder_weights(ck, dev, rank, spec.tp)
+            layers = topo.layer_range(place.stage, cfg.num_layers)
+            weights = load_decoder_weights(ck, dev, t_rank, spec.tp, layer_range=layers)
         conn.send(("progress", rank, "weights loaded"))
+        if spec.pp > 1:
+            pp = PipelineStage.from_topology(topo, rank, dist.group.WORLD)
         if spec.tp > 1:
-            tp = TensorParallel(dist.group.WORLD, dev, mode=spec.tp_comm, hidden=cfg.hidden_size,
+            tp = TensorParallel(tp_group, dev, mode="nccl" if spec.pp > 1 else spec.tp_comm, hidden=cfg.hidden_size,
                                 max_tokens=spec.token_budget, rows_max=max(512, spec.max_rows))
         pages = spec.num_pages
         if pages is None:
             free, _ = torch.cuda.mem_get_info(dev)
             pages = plan_kv_pages(free, int(spec.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, spec.tp, spec.k_bits,
-                                  spec.v_bits, spec.max_model_len, spec.max_rows)
-            if spec.tp > 1:                                   # every rank must agree: take the minimum
+                                  spec.v_bits, spec.max_model_len, spec.max_rows, layers=layers[1] - layers[0])
+            if spec.world > 1:                                # every rank must agree: take the minimum
                 t = torch.tensor([pages], device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
                 pages = int(t.item())
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=spec.token_budget, k_bits=spec.k_bits,
-                               v_bits=spec.v_bits, tp=tp)
+                               v_bits=spec.v_bits, tp=tp, pp=pp)
         ex = GpuExecutor(runner, max_rows=spec.max_rows, max_prefill_tokens=spec.token_budget,
                          max_model_len=spec.max_model_len)
         caps = ex.capture_decode_graphs()
@@ -119,7 +139,7 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
                 ex.invalidate_page_rows(cmd[2])
             elif cmd[0] == "close":
                 break
-        if spec.tp > 1:
+        if spec.world > 1:
             dist.destroy_process_group()
     except Exception as exc:  # noqa: BLE001 - reported to the controller, which fails closed
         try:
@@ -149,7 +169,7 @@ class MultiprocExecutor:
     def _spawn(self, target) -> None:
         ctx = mp.get_context("spawn")
         port = _free_port()
-        for r in range(self.spec.tp):
+        for r in range(self.spec.world):
             parent, child = ctx.Pipe()
             p = ctx.Process(target=target, args=(r, self.spec, port, child), name=f"cubic-rank-{r}", daemon=True)
             p.start()
@@ -240,11 +260,9 @@ def build_multiproc_backend(args, devices, tp, spec_cfg, k_bits, v_bits):
     from ..runtime.engine import LLMEngine
     from ..runtime.scheduler import SchedulerConfig
     from ..runtime.serving import _tokenizer_for
-    if args.pp_size != 1:
-        raise SystemExit("pipeline parallel serving is not available in this build; use --pp-size 1")
     max_len = args.max_model_len or 8192
     spec = WorkerSpec(args.model, devices, tp, k_bits, v_bits, args.max_running_requests, args.token_budget, max_len,
-                      None, args.tp_comm, args.seed, args.gpu_reserve_gib)
+                      None, args.tp_comm, args.seed, args.gpu_reserve_gib, args.pp_size)
     ex = MultiprocExecutor(spec)
     sched = SchedulerConfig(max_running_requests=args.max_running_requests, max_batched_tokens=args.token_budget,
                             prefill_chunk_tokens=min(args.prefill_chunk_tokens, args.token_budget), max_model_len=max_len,

@@ -265,8 +265,12 @@ def _cubic_variant(p: dict) -> str:
     return cubic.METADATA_A
 
 
-def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_size: int = 1):
-    """Admitted checkpoint -> rank-local ``DecoderWeights`` (dense FFN decoders)."""
+def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_size: int = 1,
+                         layer_range: tuple[int, int] | None = None):
+    """Admitted checkpoint -> rank-local ``DecoderWeights`` (dense FFN decoders).
+
+    ``layer_range`` = ``[lo, hi)`` loads only the decoder layers of one pipeline stage.
+    """
     from .decoder import DecoderWeights, LayerWeights
     cfg, q = ck.cfg, ck.cfg.quant
     if cfg.is_moe:
@@ -282,7 +286,7 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
 
     ck_shapes, _ = logical_inventory(cfg)
     layers = []
-    for i in range(cfg.num_layers):
+    for i in range(*(layer_range or (0, cfg.num_layers))):
         m = _layer_modules(cfg, i)
         qkv = pack_logical(method, [rows(m["q"], tp_rank * hq * D, (tp_rank + 1) * hq * D, cfg.q_size),
                                     rows(m["k"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size),

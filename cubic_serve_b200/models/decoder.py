@@ -88,15 +88,16 @@ def quantize_linear(w: torch.Tensor, cfg: ModelConfig) -> wq_pack.PackedWeight:
 
 
 def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                           std: float = 0.02) -> DecoderWeights:
+                           std: float = 0.02, layer_range: tuple[int, int] | None = None) -> DecoderWeights:
     """Random-init N(0, std) weights, quantized offline into the config's format, rank-local TP shards.
 
     Column-parallel: QKV (whole heads per rank), gate/up; row-parallel: o_proj,
     down; vocab-sharded embedding and lm_head (reference ownership planners:
-    ``models/parallel_weights.py:72-352``).
+    ``models/parallel_weights.py:72-352``).  ``layer_range`` keeps only the layers ``[lo, hi)`` of one pipeline
+    stage; every layer draws from its own generator, so a stage holds exactly the weights the whole model would.
     """
     assert cfg.num_q_heads % tp_size == 0 and cfg.num_kv_heads % tp_size == 0
-    gen = torch.Generator(device=device).manual_seed(seed * 1000 + tp_rank)
+    gen = torch.Generator(device=device)
     H, D = cfg.hidden_size, cfg.head_dim
     hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
     inter = cfg.intermediate_size // tp_size
@@ -108,7 +109,9 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
         return torch.ones(H, device=device, dtype=torch.bfloat16)
 
     layers = []
-    for _ in range(cfg.num_layers):
+    lo, hi = layer_range or (0, cfg.num_layers)
+    for li in range(lo, hi):
+        gen.manual_seed((seed * 1000 + tp_rank) * 4096 + li)
         lw = LayerWeights(
             ln1=norm_w(), ln2=norm_w(),
             qkv=quantize_linear(rnd((hq + 2 * hkv) * D, H), cfg),
@@ -124,6 +127,7 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             lw.gate_up = quantize_linear(rnd(2 * inter, H), cfg)
             lw.down = quantize_linear(rnd(H, inter), cfg)
         layers.append(lw)
+    gen.manual_seed((seed * 1000 + tp_rank) * 4096 + 4095)
     v_local = cfg.vocab_size // tp_size
     # the embedding table is generated identically on every rank (rank-independent stream), kept whole
     # for the fused path (each rank embeds only the rows it owns) and sliced for the vocab-sharded baseline
@@ -159,11 +163,14 @@ class StepBatch:
 
 class DecoderRunner:
     def __init__(self, cfg: ModelConfig, weights: DecoderWeights, num_pages: int, max_tokens: int,
-                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None) -> None:
+                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None, pp=None) -> None:
         self.cfg = cfg
-        self.w = weights
+        self.w = weights            # ``weights.layers`` holds only the layers of this pipeline stage
         self.device = device or weights.embed.device
         self.tp = tp
+        self.pp = pp                # parallel.pp.PipelineStage or None
+        if pp is not None and tp is not None and tp.fused is not None:
+            raise ValueError("pipeline stages use the NCCL tensor-parallel collectives (tp mode 'nccl')")
         self.tp_size = tp.size if tp is not None else 1
         self.k_bits, self.v_bits = k_bits, v_bits
         self.hq = cfg.num_q_heads // self.tp_size
@@ -177,7 +184,7 @@ class DecoderRunner:
         # one cache tensor per layer: [pages, kv_heads, blob]; zero-filled so that
         # never-written slots hold finite scales
         self.kv = [torch.zeros(num_pages, self.hkv, blob, dtype=torch.uint8, device=dev)
-                   for _ in range(cfg.num_layers)]
+                   for _ in range(len(weights.layers))]
         self.inv_freq = rope_inv_freq(cfg.rotary_dim or self.D, cfg.rope_theta, dev)
         bf = torch.bfloat16
         T = max_tokens
@@ -195,33 +202,58 @@ class DecoderRunner:
 
     # ---------------------------------------------------------------- forward
     def forward_hidden(self, b: StepBatch) -> torch.Tensor:
-        """Run all layers for ``b.num_tokens`` rows; returns the residual stream view ``[T, H]``."""
+        """Run this stage's layers for ``b.num_tokens`` rows; returns the residual stream view ``[T, H]``.
+
+        With pipeline parallelism the rows are processed in wavefront lanes: a later stage receives a lane's
+        rows from its predecessor, an earlier stage sends them on, and the next lane's compute overlaps the
+        successor's work on the previous one (reference: ``runtime/performance.py:199-211``).
+        """
+        T = b.num_tokens
+        pp = self.pp
+        self.launches_per_step = 0
+        if pp is None:
+            self._run_layers(b, 0, T, 0, b.num_row_blocks, embed=True)
+            return self.h[:T]
+        from ..parallel.pp import split_lanes
+        for t0, t1, rb0, rb1 in split_lanes(T, b.num_row_blocks, pp.lanes):
+            if not pp.is_first:
+                pp.recv(self.h[t0:t1])
+            self._run_layers(b, t0, t1, rb0, rb1, embed=pp.is_first)
+            if not pp.is_last:
+                pp.send(self.h[t0:t1])
+        return self.h[:T]
+
+    def _run_layers(self, b: StepBatch, t0: int, t1: int, rb0: int, rb1: int, embed: bool) -> None:
+        """Layers of this stage over rows ``[t0, t1)`` whose attention row blocks are ``[rb0, rb1)``."""
         cfg, w = self.cfg, self.w
         T = b.num_tokens
-        h, x = self.h[:T], self.x[:T]
-        qkv, q, attn = self.qkv[:T], self.q[:T], self.attn[:T]
+        h, x = self.h[t0:t1], self.x[t0:t1]
+        qkv, q, attn = self.qkv[t0:t1], self.q[t0:t1], self.attn[t0:t1]
+        # attention addresses query rows by their absolute index, so it gets the whole q / out buffers
+        q_all, attn_all = self.q[:T].view(T, self.hq, self.D), self.attn[:T].view(T, self.hq, self.D)
         n = 0
-        K.embedding(b.token_ids[:T], w.embed, out=h, vocab_start=w.vocab_start)
-        n += 1
-        if self.tp is not None:
-            self.tp.all_reduce(h)
+        if embed:
+            K.embedding(b.token_ids[t0:t1], w.embed, out=h, vocab_start=w.vocab_start)
+            n += 1
+            if self.tp is not None:
+                self.tp.all_reduce(h)
         pending = None  # partial sum waiting to be folded into h by the next norm (TP > 1)
         for li, lw in enumerate(w.layers):
             K.rmsnorm(pending if pending is not None else h, lw.ln1, cfg.rms_eps, out=x,
                       residual=h if pending is not None else None, zero_centered=cfg.zero_centered_norm)
             K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
-            K.rope_kv_write(qkv, q, self.kv[li], b.positions, b.slots, self.inv_freq, self.hq, self.hkv, self.D,
-                            self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
+            K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
+                            self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
                             rotary_dim=cfg.rotary_dim)
-            K.paged_attention(q.view(T, self.hq, self.D), attn.view(T, self.hq, self.D), self.kv[li], b.page_table,
-                              b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, self.hq, self.hkv,
-                              self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)
+            K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
+                              b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
+                              splits=b.attn_splits, ws=self.ws)
             n += 4
             if self.tp is None:
                 K.wq_gemm(attn, lw.o, out=h, residual=h, ws=self.ws)
                 K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x, zero_centered=cfg.zero_centered_norm)
             else:
-                part = self.part[:T]
+                part = self.part[t0:t1]
                 K.wq_gemm(attn, lw.o, out=part, ws=self.ws)
                 self.tp.all_reduce(part)
                 K.rmsnorm(part, lw.ln2, cfg.rms_eps, out=x, residual=h, zero_centered=cfg.zero_centered_norm)
@@ -236,21 +268,20 @@ class DecoderRunner:
                     self.tp.all_reduce(out)
                     pending = out
             else:
-                gu, act = self.gu[:T], self.act[:T]
+                gu, act = self.gu[t0:t1], self.act[t0:t1]
                 K.wq_gemm(x, lw.gate_up, out=gu, ws=self.ws)
                 K.swiglu(gu, out=act)
                 n += 3
                 if self.tp is None:
                     K.wq_gemm(act, lw.down, out=h, residual=h, ws=self.ws)
                 else:
-                    part = self.part[:T]
+                    part = self.part[t0:t1]
                     K.wq_gemm(act, lw.down, out=part, ws=self.ws)
                     self.tp.all_reduce(part)
                     pending = part
         if pending is not None:
             h.add_(pending)
-        self.launches_per_step = n
-        return h
+        self.launches_per_step += n
 
     def forward_logits(self, b: StepBatch, hidden: torch.Tensor, logits_out: torch.Tensor) -> torch.Tensor:
         """Final norm + lm_head for the selected rows -> bf16 logits ``[R, V(/tp)]``."""
@@ -308,9 +339,13 @@ class DecoderRunner:
         """Whole step: layers, final norm, lm_head, sampling (and the cross-rank token agreement under TP)."""
         R = b.num_logit_rows
         fused = self.tp is not None and self.tp.fused is not None
+        pp = self.pp
         if not fused:
             hidden = self.forward_hidden(b)
             if not R:
+                return
+            if pp is not None and not pp.is_last:
+                pp.share_token_ids(out_ids[:R])        # receive what the last stage sampled
                 return
             logits = self.forward_logits(b, hidden, logits_buf)
         else:
@@ -328,6 +363,8 @@ class DecoderRunner:
             K.sample(logits, out_ids[:R], temperature=d["temperature"][:R], top_p=d["top_p"][:R], top_k=d["top_k"][:R],
                      seeds=d["seeds"][:R], counters=d["draws"][:R], vocab=logits.shape[1])
             self.launches_per_step += 1
+            if pp is not None:
+                pp.share_token_ids(out_ids[:R])
             return
         # vocab-sharded: local greedy candidate per row, then agreement across ranks
         if not hasattr(self, "_cand_val"):
@@ -341,3 +378,5 @@ class DecoderRunner:
         elif R:
             self.tp.argmax_merge_nccl(self._cand_val, self._cand_id, out_ids, R)
         self.launches_per_step += 2
+        if pp is not None and R:
+            pp.share_token_ids(out_ids[:R])

@@ -28,10 +28,11 @@ def _tokenizer_for(model: str, vocab_size: int):
 
 
 def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int, v_bits: int, max_model_len: int,
-                  max_running: int) -> int:
-    """Pages that fit in the remaining device memory (one page = 16 tokens of every layer's rank-local KV heads)."""
+                  max_running: int, layers: int | None = None) -> int:
+    """Pages that fit in the remaining device memory (one page = 16 tokens of every local layer's rank-local KV
+    heads; ``layers`` = decoder layers held by this pipeline stage, default all)."""
     from ..ops.kernels import kv_blob_bytes
-    per_page = cfg.num_layers * (cfg.num_kv_heads // tp) * kv_blob_bytes(cfg.head_dim, k_bits, v_bits)
+    per_page = (layers or cfg.num_layers) * (cfg.num_kv_heads // tp) * kv_blob_bytes(cfg.head_dim, k_bits, v_bits)
     budget = max(0, free_bytes - reserve_bytes)
     pages = budget // per_page
     cap = max_running * (-(-max_model_len // 16)) + 64
