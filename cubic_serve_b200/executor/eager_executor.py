@@ -42,6 +42,10 @@ class EagerPagedExecutor:
             logits = self._run_segment(s)
             if not s.sample:
                 continue
+            if getattr(s, "mask", None) is not None:              # structured output: disallowed tokens cannot win
+                bits = np.unpackbits(np.asarray(s.mask, dtype=np.uint32).view(np.uint8), bitorder="little")
+                allowed = torch.from_numpy(bits[:logits.numel()].astype(bool))
+                logits = logits.masked_fill(~allowed, float("-inf"))
             if s.temperature <= 0:
                 out.append(int(logits.argmax()))
             else:

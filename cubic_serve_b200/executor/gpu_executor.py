@@ -35,6 +35,7 @@ class Segment:
     seed: int = 0
     draw: int = 0
     uid: int = -1                # identity of the request owning the slot (page-table row reuse detection)
+    mask: np.ndarray | None = None   # allowed-token bitmask of the sampled row (uint32 words, bit set = allowed)
 
 
 class _Staging:
@@ -230,6 +231,34 @@ class GpuExecutor:
     def _body(self, b: StepBatch) -> None:
         self.runner.run_step(b, self.stage.d, self.logits, self.out_ids)
 
+    def _stage_masks(self, segs: list[Segment]) -> bool:
+        """Upload the allowed-token bitmasks of this step's sampled rows; rows without one allow everything.
+
+        Returns False (and removes the mask from the step inputs) when no segment is constrained.  Constrained
+        steps run eagerly: the captured decode graphs sample without a mask.
+        """
+        sampled = [s for s in segs if s.sample]
+        if not any(s.mask is not None for s in sampled):
+            self.stage.d.pop("mask", None)
+            return False
+        words = -(-self.cfg.vocab_size // 32)
+        if getattr(self, "_mask_host", None) is None:
+            rows = self.out_ids.numel()
+            self._mask_host = torch.empty(rows, words, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+            self._mask_dev = torch.empty(rows, words, dtype=torch.int32, device=self.device)
+        hm = self._mask_host.numpy().view(np.uint32)
+        for i, s in enumerate(sampled):
+            if s.mask is None:
+                hm[i] = 0xFFFFFFFF
+            else:
+                hm[i] = s.mask
+        n = len(sampled)
+        with torch.cuda.stream(self.stream):
+            self._mask_dev[:n].copy_(self._mask_host[:n], non_blocking=True)
+        self.stage.d["mask"] = self._mask_dev
+        self.h2d_mask_bytes_last = n * words * 4
+        return True
+
     def capture_decode_graphs(self, capacities: list[int] | None = None) -> list[int]:
         """Capture one graph per decode row capacity (largest first, like the reference)."""
         caps = capacities or [c for c in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512) if c <= self.max_rows]
@@ -266,7 +295,8 @@ class GpuExecutor:
     def execute(self, segs: list[Segment]) -> np.ndarray:
         """Run one step and return the sampled token id of every sampling segment (host array)."""
         total = sum(len(s.token_ids) for s in segs)
-        decode = all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs)
+        masked = self._stage_masks(segs)
+        decode = all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs) and not masked
         cap = None
         if decode:
             cap = next((c for c in sorted(self.graphs) if c >= total), None)

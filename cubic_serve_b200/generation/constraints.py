@@ -83,6 +83,30 @@ class GrammarTransaction:
         self.accepted = 0
 
 
+class GrammarEngineMatcher:
+    """Adapter giving an xgrammar ``GrammarMatcher`` the ``fill_bitmask / accept / rollback`` interface."""
+
+    def __init__(self, matcher, vocab_size: int) -> None:
+        self.m = matcher
+        self.vocab_size = vocab_size
+        self._bitmask = _xgr.allocate_token_bitmask(1, vocab_size)      # int32 torch tensor [1, words]
+
+    def fill_bitmask(self, bitmask: np.ndarray) -> None:
+        self.m.fill_next_token_bitmask(self._bitmask, 0)
+        words = self._bitmask[0].numpy().view(np.uint32)
+        bitmask[:len(words)] = words[:len(bitmask)]
+
+    def accept(self, token: int) -> bool:
+        return bool(self.m.accept_token(int(token)))
+
+    def rollback(self, n: int) -> None:
+        self.m.rollback(n)
+
+    @property
+    def finished(self) -> bool:
+        return bool(self.m.is_terminated())
+
+
 def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_size: int):
     """Build a matcher for a constraint, or ``None`` when the request is unconstrained."""
     if s.kind is StructuredKind.NONE:
@@ -90,6 +114,8 @@ def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_siz
     if s.kind is StructuredKind.CHOICE:
         return ChoiceMatcher(list(s.schema), tokenizer, eos_token_id)
     if _xgr is None:
+        if s.kind is StructuredKind.JSON_OBJECT:
+            return None            # without a grammar engine json_object stays a prompt-level instruction
         raise RuntimeError("xgrammar is not installed")
     info = _xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=vocab_size)
     compiler = _xgr.GrammarCompiler(info)
@@ -104,4 +130,4 @@ def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_siz
         compiled = compiler.compile_grammar(s.schema)
     else:
         raise RuntimeError(f"unsupported constraint kind {s.kind}")
-    return _xgr.GrammarMatcher(compiled)
+    return GrammarEngineMatcher(_xgr.GrammarMatcher(compiled), vocab_size)

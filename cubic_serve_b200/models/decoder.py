@@ -359,9 +359,12 @@ class DecoderRunner:
                     rows = torch.index_select(x, 0, b.logit_rows[:R])
                     logits = K.wq_gemm(rows, self.w.lm_head, out=logits_buf[:R], ws=self.ws)
             self.launches_per_step += 2
+        mask = d.get("mask")             # allowed-token bitmask rows [R, ceil(V / 32)] (structured output) or None
+        if mask is not None:
+            mask = mask[:R, self.w.vocab_start // 32:]       # this rank's vocabulary shard starts at a word boundary
         if self.tp is None:
             K.sample(logits, out_ids[:R], temperature=d["temperature"][:R], top_p=d["top_p"][:R], top_k=d["top_k"][:R],
-                     seeds=d["seeds"][:R], counters=d["draws"][:R], vocab=logits.shape[1])
+                     seeds=d["seeds"][:R], counters=d["draws"][:R], vocab=logits.shape[1], mask=mask)
             self.launches_per_step += 1
             if pp is not None:
                 pp.share_token_ids(out_ids[:R])
@@ -372,7 +375,7 @@ class DecoderRunner:
             self._cand_id = torch.empty(logits_buf.shape[0], dtype=torch.int32, device=self.device)
         if R:
             K.sample(logits, self._cand_id[:R], vocab=logits.shape[1], out_value=self._cand_val[:R],
-                     id_offset=self.w.vocab_start)
+                     id_offset=self.w.vocab_start, mask=mask)
         if fused:
             self.tp.fused.argmax_merge(self._cand_val, self._cand_id, out_ids, R)
         elif R:

@@ -198,7 +198,7 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: torch.Tenso
            vocab: int | None = None, out_value: torch.Tensor | None = None, id_offset: int = 0) -> torch.Tensor:
     rows = logits.shape[0]
     code = native.lib().cb_sample(logits.data_ptr(), logits.stride(0), _ptr(mask),
-                                  0 if mask is None else mask.shape[1], _ptr(temperature), _ptr(top_p), _ptr(top_k),
+                                  0 if mask is None else mask.stride(0), _ptr(temperature), _ptr(top_p), _ptr(top_k),
                                   _ptr(seeds), _ptr(counters), out_ids.data_ptr(), _ptr(out_logprob),
                                   _ptr(out_value), int(id_offset), rows, vocab or logits.shape[1], _stream())
     native.check(code, "cb_sample")

@@ -115,8 +115,13 @@ class TokenChatBackend:
         s = req.sampling
         eos = getattr(self.tokenizer, "eos_token_id", None)
         max_tokens = s.max_tokens or self.default_max_tokens
+        matcher = None
+        if req.structured.kind is not StructuredKind.NONE and self.engine._mask_words and eos is not None:
+            from ..generation.constraints import compile_matcher
+            matcher = compile_matcher(req.structured, self.tokenizer, eos, self.engine._mask_words * 32)
         sp = SamplingParams(temperature=s.temperature, top_p=s.top_p, top_k=s.top_k, seed=s.seed, max_tokens=max_tokens,
-                            stop_token_ids=tuple(s.stop_token_ids) + ((eos,) if eos is not None else ()))
+                            stop_token_ids=tuple(s.stop_token_ids) + ((eos,) if eos is not None else ()),
+                            matcher=matcher)
         with self._lock:
             self._live[req.request_id] = live
             self._inbox.append((req.request_id, prepared.token_ids, sp))

@@ -14,6 +14,8 @@ import itertools
 import time
 from dataclasses import dataclass
 
+import numpy as np
+
 from ..executor.gpu_executor import Segment
 from .cache.pool import PagePool
 from .cache.prefix import PrefixCache
@@ -43,6 +45,8 @@ class LLMEngine:
         self.scheduler = ContinuousScheduler(self.cfg, self.pool, self.prefix)
         self.scheduler.decode_lookahead = getattr(executor, "speculative_depth", 0)
         self.eos_token_id = eos_token_id
+        vocab = getattr(getattr(executor, "cfg", None), "vocab_size", None) or getattr(executor, "vocab_size", 0)
+        self._mask_words = -(-int(vocab) // 32) if vocab else 0
         self._ids = itertools.count()
         self.requests: dict[str, Request] = {}
         self.poisoned = False
@@ -102,11 +106,16 @@ class LLMEngine:
             r = s.request
             toks = r.tokens[s.start:s.start + s.count]
             sp = r.sampling
+            mask = None
+            if s.sample and sp.matcher is not None:
+                mask = np.zeros(self._mask_words, dtype=np.uint32)
+                sp.matcher.fill_bitmask(mask)
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
                                 sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF, r.draws,
-                                r.arrival))
+                                r.arrival, mask))
         spec = getattr(self.executor, "speculative_depth", 0)
-        if spec and segs and all(len(s.token_ids) == 1 and s.sample for s in segs):
+        constrained = any(s.mask is not None for s in segs)
+        if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample for s in segs):
             # speculative round: every request gets its accepted drafts plus one bonus token
             ids = self.executor.execute_speculative(segs)
             self.spec_rounds = getattr(self, "spec_rounds", 0) + 1
@@ -118,6 +127,9 @@ class LLMEngine:
             if s.sample:
                 v = next(it)
                 sampled[s.request.request_id] = [int(t) for t in v] if isinstance(v, (list, tuple)) else int(v)
+                m = s.request.sampling.matcher
+                if m is not None and not isinstance(v, (list, tuple)) and not m.accept(int(v)):
+                    raise RuntimeError(f"request {s.request.request_id}: sampled token {int(v)} violates its constraint")
             else:
                 self.prefill_tokens += s.count
         finished = {r.request_id: r for r in self.scheduler.commit(plan, sampled, self.eos_token_id)}

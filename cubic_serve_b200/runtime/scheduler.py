@@ -41,6 +41,9 @@ class SamplingParams:
     max_tokens: int = 256
     stop_token_ids: tuple[int, ...] = ()
     ignore_eos: bool = False
+    # structured output: an object with ``fill_bitmask(uint32 words)`` and ``accept(token) -> bool``
+    # (``generation/constraints.py``); the engine masks the sampler with it and advances it on every commit
+    matcher: object | None = None
 
     def validate(self) -> None:
         if not 0.0 <= self.temperature <= 2.0:

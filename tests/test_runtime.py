@@ -138,3 +138,36 @@ def test_engine_eager_executor_matches_reference_decoder():
     # cold vs prefix-resumed: same continuation
     out2 = eng.generate([prompts[0].tolist()], SamplingParams(max_tokens=6))
     assert out2[0] == ref[0].tolist() and eng.prefix.hit_tokens >= 16
+
+
+def test_choice_constraint_masks_sampling_end_to_end():
+    """A ``choice`` matcher forces the engine's output to be exactly one of the options, then EOS."""
+    from cubic_serve_b200.generation.constraints import ChoiceMatcher
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [ord(c) for c in text]
+
+    cfg = toy_config()
+    w = random_dense_weights(cfg, seed=0)
+    eng = LLMEngine(EagerPagedExecutor(cfg, w, num_pages=32), num_pages=32,
+                    scheduler_config=SchedulerConfig(max_running_requests=4, max_model_len=64))
+    eos = 3
+    options = ["yes", "no", "maybe"]
+    outs = []
+    for seed in range(3):
+        m = ChoiceMatcher(options, Tok(), eos)
+        sp = SamplingParams(temperature=1.0, top_k=20, seed=seed, max_tokens=12, stop_token_ids=(eos,), matcher=m)
+        free = SamplingParams(max_tokens=5)
+        rid = eng.add_request([5, 6, 7, 8 + seed], sp)
+        other = eng.add_request([9, 10, 11], free)               # an unconstrained request shares the steps
+        reqs = {rid: eng.requests[rid], other: eng.requests[other]}
+        while eng.has_unfinished:
+            eng.step()
+        toks = reqs[rid].output
+        assert toks[-1] == eos
+        text = "".join(chr(t) for t in toks[:-1])
+        assert text in options
+        assert len(reqs[other].output) == 5
+        outs.append(text)
+    assert eng._mask_words == cfg.vocab_size // 32
