@@ -228,7 +228,7 @@ def main() -> None:
     e2e = tokens / (wall_ms / 1e3)
     if rank == 0:
         line = {
-            "metric": "output tok/s @256 concurrent (decode steps, device-timed, max over ranks)",
+            "metric": f"output tok/s @{C} concurrent (decode steps, device-timed, max over ranks)",
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": f"bf16 activations, {cfg.quant.method} {cfg.quant.bits}-bit weights, INT{k_bits}/INT{v_bits} KV",

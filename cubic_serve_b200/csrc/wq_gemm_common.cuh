@@ -1,0 +1,208 @@
+// Shared pieces of the weight-quantized GEMM kernels: formats, tile constants, the tensor-parallel link,
+// launch parameters, the packed bf16x2 decoders and the tensor-map helper.  Included by wq_gemm.cu (one CTA
+// per tile: grouped expert GEMMs, explicit split-K) and wq_gemm_sk.cu (persistent stream-K kernel).
+#pragma once
+#include "ptx.cuh"
+#include <cuda.h>
+
+namespace cb {
+
+enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 = 3 };
+
+static constexpr int kTileN = 128;       // output features per CTA (UMMA M)
+static constexpr int kBlockK = 64;       // K columns per stage (one 128-byte swizzle row)
+static constexpr int kCodeBytes = 4096;  // 128 x 64 x 4 bit
+static constexpr int kMetaBytes = 1024;
+static constexpr int kATileBytes = kTileN * kBlockK * 2;  // 16 KiB bf16
+static constexpr int kNumDequantWarps = 16;  // 4 per scheduler: the decode chains are latency-bound with fewer
+static constexpr int kThreads = (2 + kNumDequantWarps) * 32;
+
+// Tensor-parallel links of a launch (all pointers are device addresses valid on
+// THIS GPU: local buffers, or peers' symmetric buffers mapped over NVLink).
+//   kTpGatherWait : the activation operand is an all-gathered buffer that peers
+//                   fill with plain P2P stores; the producer warp prefetches
+//                   weights, then waits (bounded) for every rank's rows before
+//                   the first activation TMA load -- all-gather fused into the
+//                   column-parallel GEMM.
+//   kTpScatterPush: the output is a partial sum; the epilogue stores each bf16
+//                   partial tile straight into the row owner's receive buffer
+//                   (slot = this rank) and raises that owner's arrival counter
+//                   -- reduce-scatter fused into the row-parallel GEMM.
+enum TpMode : int { kTpNone = 0, kTpGatherWait = 1, kTpScatterPush = 2 };
+static constexpr int kMaxRanks = 8;
+
+struct TpLink {
+  int mode;
+  int rank, size;
+  int rows_per_rank;                  // multiple of 16; row m belongs to rank m / rows_per_rank
+  __nv_bfloat16* recv[kMaxRanks];     // push: owner o's receive buffer [size][rows_per_rank][N]
+  uint32_t* rs_flag[kMaxRanks];       // push: owner o's arrival counters [size]
+  const uint32_t* ag_flag;            // wait: local arrival counters [size]
+  uint32_t* ag_state;                 // wait: local {arrivals consumed so far, done CTAs}
+  uint32_t ag_expected;               // wait: arrivals per source rank per epoch
+};
+
+struct WqGemmParams {
+  const uint8_t* codes;
+  const uint8_t* meta;
+  __nv_bfloat16* y;         // [M, ldy]
+  const __nv_bfloat16* residual;  // optional [M, ldy]
+  float* workspace;         // split-K partials: [tiles][splits][mb][128] fp32
+  uint32_t* counters;       // one per (m_tile, n_tile); zero on entry, zero on exit
+  uint32_t* status;         // device status word (Status)
+  int M, N, K;
+  int ldy;
+  int mb;                   // batch rows per CTA (multiple of 16, <= 256)
+  int k_blocks;             // K / 64
+  int splits;               // split-K factor (k_blocks % splits may be != 0)
+  int meta_k_blocks;        // k-blocks covered by one metadata block (1 or group/64)
+  int meta_blocks;          // metadata blocks per n-tile
+  int stages;
+  float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
+  uint32_t tmem_cols;       // power of two >= max(32, mb)
+  TpLink tp;
+  // grouped (mixture-of-experts) mode: blockIdx.y indexes a device-side work list
+  // group_tiles = {count, then {expert, first row, rows} per item}; rows are contiguous in x / y; weights
+  // of expert e start at codes + e * group_code_stride (meta likewise).  Split-K is not combined with it.
+  const int* group_tiles;
+  size_t group_code_stride, group_meta_stride;
+  unsigned long long* trace;  // optional pipeline timeline of CTA (0,0,0): [iteration][8] clock64 stamps
+  // persistent stream-K kernel only (wq_gemm_sk.cu)
+  int n_tiles, tiles;       // tile = m_tile * n_tiles + n_tile
+  int sk_tiles, sk_ctas;    // tiles [0, sk_tiles) are dealt by k-block to CTAs [0, sk_ctas); the rest are whole
+  int ax_stages, c_stages;  // ring depths: {activation tile + decoded tile}, {packed codes + metadata}
+  int meta_shift;           // log2(meta_k_blocks)
+  uint32_t acc_cols;        // TMEM columns per accumulator buffer (two buffers)
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until a monotonically increasing counter reaches `target` (wrap-safe).
+__device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target, volatile uint32_t* abort_flag) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys(p) - target) < 0) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_flag = 2;
+      return false;
+    }
+  }
+  return true;
+}
+
+// ---- packed bf16x2 decode ---------------------------------------------------
+// A 32-bit word holds 8 codes; nibble i (i < 4) is column 2i and nibble i + 4 is
+// column 2i + 1 of the 8-column chunk, so ONE mask pulls an adjacent column pair
+// into the two halves of a register:  ((w >> 4i) & 0x000F000F) | 0x43004300 is
+// the bf16 pair (128 + n_lo, 128 + n_hi).  All arithmetic then runs two weights
+// per instruction on the FMA pipe and produces bf16 directly -- no float -> bf16
+// conversion (those run on the quarter-rate XU pipe and were the bottleneck of
+// an fp32 formulation: 87 % XU utilisation in the first profile).
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_dup(uint32_t lo16) { return (lo16 & 0xFFFFu) * 0x00010001u; }
+
+template <int FMT>
+__device__ __forceinline__ void decode8(uint32_t w, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t (&out)[4]);
+
+template <>
+__device__ __forceinline__ void decode8<kFmtBf16>(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t (&)[4]) {}
+
+// CUBIC4: c = n - 8;  w = c * (A + |c| * (B + |c| * C)),  A/B/C broadcast bf16x2
+template <>
+__device__ __forceinline__ void decode8<kFmtCubic4>(uint32_t w, uint32_t A, uint32_t B, uint32_t C,
+                                                    uint32_t (&out)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;  // 128 + n
+    const uint32_t c = bf2_sub(x, 0x43084308u);                        // n - 8 (exact)
+    const uint32_t m = c & 0x7FFF7FFFu;                                // |c|
+    uint32_t p = bf2_fma(m, C, B);
+    p = bf2_fma(m, p, A);
+    out[i] = bf2_mul(c, p);
+  }
+}
+
+// AFFINE4: w = (n - 8) * scale + offset8   (offset8 = offset + 8 * scale, small in magnitude)
+template <>
+__device__ __forceinline__ void decode8<kFmtAffine4>(uint32_t w, uint32_t scale, uint32_t offset8, uint32_t,
+                                                     uint32_t (&out)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t x = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+    out[i] = bf2_fma(bf2_sub(x, 0x43084308u), scale, offset8);
+  }
+}
+
+// NVFP4: nibble = sign(1) exp(2) man(1).  exp|man placed at bf16 bits 8..6 and
+// multiplied by 2^126 gives {0,.5,1,1.5,2,3,4,6} exactly (exp = 0 codes are bf16
+// subnormals that the multiply normalises); then one multiply by the block scale.
+template <>
+__device__ __forceinline__ void decode8<kFmtNvfp4>(uint32_t w, uint32_t scale, uint32_t, uint32_t,
+                                                   uint32_t (&out)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = (w >> (4 * i)) & 0x000F000Fu;
+    const uint32_t bits = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
+    out[i] = bf2_mul(bf2_mul(bits, 0x7E807E80u), scale);
+  }
+}
+
+// ------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 row-major [rows, cols] (row stride ld elements), box = {64 cols, box_rows}, 128-byte swizzle
+static inline int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                          uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+
+// Persistent stream-K launcher (wq_gemm_sk.cu).  `workspace_bytes` bounds the fp32 partial-tile slots the
+// schedule may use; returns 0, a negative argument error or a positive cudaError_t.
+int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, size_t workspace_bytes,
+                   int sm_count, int min_units, cudaStream_t stream);
+
+}  // namespace cb

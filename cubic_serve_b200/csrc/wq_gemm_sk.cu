@@ -1,0 +1,743 @@
+// Persistent stream-K form of the weight-quantized GEMM (see wq_gemm.cu for the operand roles, the packed
+// weight layout and the decode arithmetic, which are shared through wq_gemm_common.cuh).
+//
+// Why a second kernel.  Profiles of the one-CTA-per-tile kernel at decode batch 256 showed three losses that
+// no tuning inside that structure removes:
+//   * wave quantisation: 192 weight tiles on 148 SMs run as two waves (35 % of the machine idle on average);
+//   * prologue (barrier set-up, first copies, first decode) and epilogue (TMEM -> global) are 14 % of a tile
+//     and overlap with nothing, because shared memory allows one CTA per SM;
+//   * the four-stage ring that carried {activation tile, decoded tile, packed codes} together was latency
+//     bound: a stage went release -> copy issue -> copy latency -> decode -> MMA before it could be reused.
+// This kernel launches at most one CTA per SM and deals K-BLOCKS, not tiles, to the CTAs:
+//   * tiles [0, sk_tiles) are "streamed": their sk_tiles * k_blocks units are split evenly over sk_ctas CTAs,
+//     so a tile may be produced by several CTAs, each writing an fp32 partial; the last to arrive sums the
+//     partials in part order (deterministic) and writes the result;
+//   * the remaining tiles are whole tiles, tile = sk_tiles + w * grid + cta for w = 0, 1, ...
+//   Every CTA therefore gets the same number of k-blocks (+-1) whatever the tile count.
+// Inside a CTA the rings are decoupled and the accumulator is double buffered:
+//   warp 0      activation tiles (and bf16 weight tiles) by TMA into the AX ring          -> x_full
+//   warp 2      packed codes + metadata by bulk copy into the deeper C ring               -> c_full
+//   warps 7-22  decode, two groups of 8 warps that take alternate k-blocks: wait c_full, decode 32
+//               weights per thread in registers (one 16-byte code load, four 16-byte tile stores),
+//               wait for the AX slot to be free, store the swizzled bf16 tile             -> a_ready, c_empty
+//               (per-k-block costs -- waits, fence, arrive, metadata -- are paid by 8 warps, not 16)
+//   warp 1      MMA: wait a_ready & x_full, 4 x tcgen05.mma into accumulator (segment & 1),
+//               commit -> ax_empty; after a segment's last k-block commit -> acc_full
+//   warps 3-6   epilogue: wait acc_full, tcgen05.ld, write bf16 output (or the fp32 partial),
+//               release the accumulator -> acc_empty; fix-up reduction for streamed tiles;
+//               tensor-parallel push + arrival counters when the launch carries a TpLink.
+// The epilogue of segment i overlaps the main loop of segment i + 1.
+// Every wait is bounded (ptx.cuh); on a timeout the CTA-wide abort flag makes every role fall through to the
+// common exit, which frees tensor memory and records a status word.
+#include "wq_gemm_common.cuh"
+
+namespace cb {
+
+static constexpr int kSkDecodeWarps = 16;
+static constexpr int kSkDecodeGroups = 2;       // group g decodes the k-blocks with (index & 1) == g
+static constexpr int kSkGroupWarps = kSkDecodeWarps / kSkDecodeGroups;
+static constexpr int kSkEpiScratchBytes = 4 * 16 * 32 * 4;   // per epilogue warp: 16 rows x 32 features fp32
+static constexpr int kSkEpiWarps = 4;
+static constexpr int kSkFirstEpiWarp = 3;      // any four consecutive warps cover the four TMEM lane quadrants
+static constexpr int kSkFirstDecodeWarp = 7;
+static constexpr int kSkThreads = (kSkFirstDecodeWarp + kSkDecodeWarps) * 32;   // 736
+static constexpr int kSkMaxAx = 6;
+static constexpr int kSkMaxC = 8;
+static constexpr int kSkCStageBytes = kCodeBytes + kMetaBytes;
+
+struct __align__(8) SkCtl {
+  uint64_t x_full[kSkMaxAx];     // activation (and bf16 weight) tile landed            (transaction bytes)
+  uint64_t a_ready[kSkMaxAx];    // decoded weight tile stored by the 8 warps of a group (8 arrivals)
+  uint64_t ax_empty[kSkMaxAx];   // the MMAs that read the slot have retired            (tcgen05.commit)
+  uint64_t c_full[kSkMaxC];      // packed codes + metadata landed                      (transaction bytes)
+  uint64_t c_empty[kSkMaxC];     // the group's warps hold the codes in registers       (8 arrivals)
+  uint64_t acc_full[2];          // accumulator of a segment complete                   (tcgen05.commit)
+  uint64_t acc_empty[2];         // epilogue warps have read the accumulator            (4 arrivals)
+  uint64_t tail_full;            // accumulator of the CTA's LAST segment complete; completes once, so waiters
+                                 // that arrive many segments early cannot mistake an older phase for it
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t is_last;
+};
+
+// One contiguous run of k-blocks of one tile, as dealt to a CTA.
+struct SkSegment {
+  int tile, kb_lo, kb_hi;
+  int part, parts;               // this run is part `part` of `parts` runs that make up the tile
+};
+
+// The deal.  Identical arithmetic on every thread of every role, so all roles of a CTA walk the same list.
+struct SkIter {
+  // 32-bit arithmetic throughout: the streamed region has at most one tile per SM, so units * CTAs < 2^31
+  // (checked on the host); 64-bit divisions cost several hundred cycles each at kernel start
+  uint32_t u, u_end, total;      // streamed units of this CTA, and of the whole launch
+  int next_whole;
+  __device__ __forceinline__ void init(const WqGemmParams& p, int cta) {
+    total = static_cast<uint32_t>(p.sk_tiles) * static_cast<uint32_t>(p.k_blocks);
+    if (cta < p.sk_ctas) {
+      u = total * static_cast<uint32_t>(cta) / static_cast<uint32_t>(p.sk_ctas);
+      u_end = total * static_cast<uint32_t>(cta + 1) / static_cast<uint32_t>(p.sk_ctas);
+    } else {
+      u = u_end = 0;
+    }
+    next_whole = p.sk_tiles + cta;
+  }
+  __device__ __forceinline__ bool has_more(const WqGemmParams& p) const { return u < u_end || next_whole < p.tiles; }
+  __device__ __forceinline__ bool next(const WqGemmParams& p, int cta, int grid, SkSegment& s) {
+    if (u < u_end) {
+      const uint32_t kbs = static_cast<uint32_t>(p.k_blocks);
+      const uint32_t ctas = static_cast<uint32_t>(p.sk_ctas);
+      const uint32_t tile = u / kbs;
+      const uint32_t first = tile * kbs;
+      const uint32_t end = (u_end < first + kbs) ? u_end : first + kbs;
+      s.tile = static_cast<int>(tile);
+      s.kb_lo = static_cast<int>(u - first);
+      s.kb_hi = static_cast<int>(end - first);
+      // CTA that owns unit v: the largest g with floor(total * g / ctas) <= v
+      const int g_first = static_cast<int>(((first + 1u) * ctas - 1u) / total);
+      const int g_last = static_cast<int>(((first + kbs) * ctas - 1u) / total);
+      s.parts = g_last - g_first + 1;
+      s.part = cta - g_first;
+      u = end;
+      return true;
+    }
+    if (next_whole < p.tiles) {
+      s.tile = next_whole;
+      s.kb_lo = 0;
+      s.kb_hi = p.k_blocks;
+      s.part = 0;
+      s.parts = 1;
+      next_whole += grid;
+      return true;
+    }
+    return false;
+  }
+};
+
+// Ring position: slot index and how many times the ring has wrapped.
+struct SkRing {
+  int s = 0;
+  uint32_t wraps = 0;
+  __device__ __forceinline__ void advance(int depth) {
+    if (++s == depth) { s = 0; ++wraps; }
+  }
+};
+
+// fp32 partial slot of (cta, part): a CTA has at most one run that starts inside a tile (its first, part > 0)
+// and at most one that ends inside a tile (its last, part == 0)
+__device__ __forceinline__ float* sk_slot(const WqGemmParams& p, int cta, int part) {
+  return p.workspace + (static_cast<size_t>(cta) * 2 + (part == 0 ? 1 : 0)) * (static_cast<size_t>(p.mb) * kTileN);
+}
+
+__device__ __forceinline__ void epi_bar() {
+  asm volatile("bar.sync 1, %0;" ::"r"(kSkEpiWarps * 32));
+}
+
+__device__ __forceinline__ void tail_bar() {
+  asm volatile("bar.sync 2, %0;" ::"r"((kSkEpiWarps + kSkDecodeWarps) * 32));
+}
+
+// Four consecutive output features n0..n0+3 of row m from unscaled fp32 accumulators: scale, add the residual,
+// round once to bf16, store locally or (scatter-push) into the receive buffer of the rank that owns row m.
+__device__ __forceinline__ void sk_store4(const WqGemmParams& p, int m, int n0, const float4 v) {
+  if (n0 >= p.N) return;
+  float o4[4] = {v.x * p.alpha, v.y * p.alpha, v.z * p.alpha, v.w * p.alpha};
+  __nv_bfloat16* dst;
+  const __nv_bfloat16* res = nullptr;
+  bool vec;
+  if (p.tp.mode & kTpScatterPush) {
+    const int o = m / p.tp.rows_per_rank;
+    const int lr = m - o * p.tp.rows_per_rank;
+    dst = p.tp.recv[o] + (static_cast<size_t>(p.tp.rank) * p.tp.rows_per_rank + lr) * p.N + n0;
+    vec = (p.N & 3) == 0;
+  } else {
+    const size_t off = static_cast<size_t>(m) * p.ldy + n0;
+    dst = p.y + off;
+    if (p.residual) res = p.residual + off;
+    vec = (p.ldy & 3) == 0;
+  }
+  if (vec && n0 + 3 < p.N) {
+    if (res) {
+      const uint2 rv = *reinterpret_cast<const uint2*>(res);
+      const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+      const float2 a0 = __bfloat1622float2(rp[0]), a1 = __bfloat1622float2(rp[1]);
+      o4[0] += a0.x; o4[1] += a0.y; o4[2] += a1.x; o4[3] += a1.y;
+    }
+    uint2 ov;
+    ov.x = pack_bf16x2(o4[0], o4[1]);
+    ov.y = pack_bf16x2(o4[2], o4[3]);
+    *reinterpret_cast<uint2*>(dst) = ov;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (n0 + j < p.N) {
+        float w = o4[j];
+        if (res) w += __bfloat162float(res[j]);
+        dst[j] = __float2bfloat16(w);
+      }
+    }
+  }
+}
+
+// Fix-up of a streamed tile by the last CTA to arrive: sum the fp32 partials of all parts IN PART ORDER
+// (bit-identical whichever CTA happens to be last) and write the tile.  `own` (optional) is this CTA's own part
+// still in shared memory, read instead of its copy in L2.  kBatch items per thread are in flight at once: the
+// partials come from L2 at ~1 k cycles per round trip, so the loop is latency bound without batching.
+template <int kBatch>
+__device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkSegment& seg, int cta, int tid,
+                                                int nthreads, int m0, int rows_here, int n_base, const float* own) {
+  const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
+  const int g_first = cta - seg.part;
+  const int parts = seg.parts;
+  const int own_part = own ? seg.part : -1;
+  const float* slots = p.workspace + static_cast<size_t>(g_first) * 2 * part_elems;   // part q > 0 at + q * 2 * part_elems
+  const int items = rows_here * (kTileN / 4);
+  for (int base = tid; base < items; base += nthreads * kBatch) {
+    float4 acc[kBatch];
+    int e[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int idx = base + b * nthreads;
+      const int safe = idx < items ? idx : tid;            // out-of-range slots re-read a valid item, never stored
+      e[b] = (safe >> 5) * kTileN + (safe & 31) * 4;
+      acc[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // the test on the part is uniform over the CTA and sits OUTSIDE the batch loop, so the kBatch loads of a
+    // part are issued back to back; unrolling by two lets the next part's loads start under this part's adds
+#pragma unroll 2
+    for (int sp = 0; sp < parts; ++sp) {
+      float4 v[kBatch];
+      if (sp == own_part) {
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) v[b] = *reinterpret_cast<const float4*>(own + e[b]);
+      } else {
+        const float* src = slots + (static_cast<size_t>(sp) * 2 + (sp == 0 ? 1 : 0)) * part_elems;
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) v[b] = __ldcg(reinterpret_cast<const float4*>(src + e[b]));
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) { acc[b].x += v[b].x; acc[b].y += v[b].y; acc[b].z += v[b].z; acc[b].w += v[b].w; }
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const int idx = base + b * nthreads;
+      if (idx < items) sk_store4(p, m0 + (idx >> 5), n_base + (idx & 31) * 4, acc[b]);
+    }
+  }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(kSkThreads, 1)
+wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                  const __grid_constant__ CUtensorMap tmap_w,  // only for kFmtBf16
+                  const WqGemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t x_bytes = static_cast<uint32_t>(p.mb) * 128u;
+  const uint32_t ax_bytes = x_bytes + kATileBytes;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* c_ring = smem + static_cast<size_t>(p.ax_stages) * ax_bytes;
+  float* epi_scratch = reinterpret_cast<float*>(c_ring + (FMT == kFmtBf16 ? 0 : static_cast<size_t>(p.c_stages) * kSkCStageBytes));
+  SkCtl* ctl = reinterpret_cast<SkCtl*>(reinterpret_cast<uint8_t*>(epi_scratch) + kSkEpiScratchBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+  const int grid = gridDim.x;
+  const int S = p.ax_stages;
+  const int NC = p.c_stages;
+  // timeline of CTA 0 (debug hook): row i = i-th k-block this CTA processes; slots as in wq_gemm.cu
+  unsigned long long* trace = (p.trace && cta == 0) ? p.trace : nullptr;
+  if (trace && threadIdx.x == 0) trace[6] = clock64();
+  // every CTA: wall-clock entry / exit in slots 0 / 1 of row `cta` (the buffer has >= gridDim.x rows)
+  if (p.trace && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[cta * 8 + 0] = t;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSkMaxAx; ++s) {
+      mbar_init(smem_u32(&ctl->x_full[s]), 1);
+      mbar_init(smem_u32(&ctl->a_ready[s]), kSkGroupWarps);
+      mbar_init(smem_u32(&ctl->ax_empty[s]), 1);
+    }
+    for (int s = 0; s < kSkMaxC; ++s) {
+      mbar_init(smem_u32(&ctl->c_full[s]), 1);
+      mbar_init(smem_u32(&ctl->c_empty[s]), kSkGroupWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+      mbar_init(smem_u32(&ctl->acc_empty[b]), kSkEpiWarps);
+    }
+    mbar_init(smem_u32(&ctl->tail_full), 1);
+    ctl->abort_flag = 0;
+    ctl->is_last = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  SkIter it;
+  it.init(p, cta);
+  SkSegment seg;
+
+  if (warp == 0) {
+    // ------------------------------------------------ activation (and bf16 weight) tiles
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_x);
+      if (FMT == kFmtBf16) tma_prefetch_desc(&tmap_w);
+      bool ok = true;
+      if (p.tp.mode & kTpGatherWait) {
+        // the packed weights stream meanwhile (warp 2 does not wait): all-gather overlapped with weight traffic
+        const uint32_t target = p.tp.ag_state[0] + p.tp.ag_expected;
+        for (int r = 0; r < p.tp.size && ok; ++r) ok = wait_counter(p.tp.ag_flag + r, target, abort_flag);
+      }
+      const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? static_cast<uint32_t>(kATileBytes) : 0u);
+      SkRing r;
+      while (ok && it.next(p, cta, grid, seg)) {
+        const int m_tile = seg.tile / p.n_tiles;
+        const int n_tile = seg.tile - m_tile * p.n_tiles;
+        const int m0 = m_tile * p.mb;
+        for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
+          if (r.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
+          uint8_t* st = smem + static_cast<size_t>(r.s) * ax_bytes;
+          const uint32_t bar = smem_u32(&ctl->x_full[r.s]);
+          mbar_expect_tx(bar, tx);
+          tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, m0, bar);
+          if (FMT == kFmtBf16) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, n_tile * kTileN, bar);
+          r.advance(S);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------ packed codes + metadata
+    if (FMT != kFmtBf16 && lane == 0) {
+      bool ok = true;
+      SkRing r;
+      while (ok && it.next(p, cta, grid, seg)) {
+        const int n_tile = seg.tile % p.n_tiles;
+        const uint8_t* cbase = p.codes + static_cast<size_t>(n_tile) * p.k_blocks * kCodeBytes;
+        const uint8_t* mbase = p.meta + static_cast<size_t>(n_tile) * p.meta_blocks * kMetaBytes;
+        for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
+          if (r.wraps && !mbar_wait_park(smem_u32(&ctl->c_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
+          const uint32_t dst = smem_u32(c_ring + static_cast<size_t>(r.s) * kSkCStageBytes);
+          const uint32_t bar = smem_u32(&ctl->c_full[r.s]);
+          mbar_expect_tx(bar, kSkCStageBytes);
+          bulk_g2s(dst, cbase + static_cast<size_t>(kb) * kCodeBytes, kCodeBytes, bar);
+          bulk_g2s(dst + kCodeBytes, mbase + static_cast<size_t>(kb >> p.meta_shift) * kMetaBytes, kMetaBytes, bar);
+          r.advance(NC);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (warp-uniform loop, one elected lane issues)
+    const bool leader = elect_one();
+    const uint32_t idesc = umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint64_t desc_hi = umma_desc_sw128(0);
+    SkRing r;
+    int seg_idx = 0;
+    int i_global = 0;
+    bool ok = true;
+    while (ok && it.next(p, cta, grid, seg)) {
+      const int buf = seg_idx & 1;
+      const uint32_t use = static_cast<uint32_t>(seg_idx >> 1);
+      const bool tail = !it.has_more(p);
+      if (use) {
+        ok = mbar_wait_park(smem_u32(&ctl->acc_empty[buf]), (use - 1u) & 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf) * p.acc_cols;
+      uint32_t accumulate = 0;
+      for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb, ++i_global) {
+        if (FMT != kFmtBf16) ok = mbar_wait_park(smem_u32(&ctl->a_ready[r.s]), r.wraps & 1u, abort_flag);
+        ok = ok && mbar_wait_park(smem_u32(&ctl->x_full[r.s]), r.wraps & 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (trace && leader && i_global < 64) trace[i_global * 8 + 4] = clock64();
+        tc_fence_after();
+        const uint32_t st = smem_base + static_cast<uint32_t>(r.s) * ax_bytes;
+        const uint64_t bdesc = desc_hi | static_cast<uint64_t>((st & 0x3FFFFu) >> 4);
+        const uint64_t adesc = desc_hi | static_cast<uint64_t>(((st + x_bytes) & 0x3FFFFu) >> 4);
+        if (leader) {
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
+            umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+          }
+          tc_commit(smem_u32(&ctl->ax_empty[r.s]));
+          if (kb == seg.kb_hi - 1) {
+            tc_commit(smem_u32(&ctl->acc_full[buf]));
+            if (tail) tc_commit(smem_u32(&ctl->tail_full));
+          }
+        }
+        accumulate = 1;
+        if (trace && leader && i_global < 64) trace[i_global * 8 + 5] = clock64();
+        r.advance(S);
+      }
+      ++seg_idx;
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------ decode (warps 7..22) and epilogue (warps 3..6)
+    // Geometry of the current segment (set by seg_geometry) and the shared LAST-segment epilogue.
+    int m0 = 0, rows_here = 0, n_base = 0;
+    auto seg_geometry = [&]() {
+      const int m_tile = seg.tile / p.n_tiles;
+      const int n_tile = seg.tile - m_tile * p.n_tiles;
+      m0 = m_tile * p.mb;
+      rows_here = min(p.mb, p.M - m0);
+      n_base = n_tile * kTileN;
+    };
+    // Last segment of the CTA: nothing is left to overlap with, so all 20 of these warps (640 threads) do the
+    // epilogue together.  The rings are idle once the accumulator is complete, so the whole fp32 tile is staged
+    // in their memory ([row][128 features]); then every warp writes full 256-byte rows (or 512-byte fp32 rows
+    // of the partial), and a last arriver reduces with 640 threads, reading its own part from shared memory.
+    // All 640 threads execute every tail_bar() whatever happened before: work is switched off by `ok`, never
+    // the control flow.
+    auto tail_epilogue = [&](int seg_idx, bool ok) {
+      const int tt = threadIdx.x - kSkFirstEpiWarp * 32;      // 0..639
+      const int nthr = (kSkEpiWarps + kSkDecodeWarps) * 32;
+      const int buf = seg_idx & 1;
+      ok = ok && mbar_wait_park(smem_u32(&ctl->tail_full), 0u, abort_flag);
+      ok = __all_sync(0xffffffffu, ok) && !*abort_flag;
+      tc_fence_after();
+      if (trace && tt == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 6] = clock64();
+      seg_geometry();
+      const bool whole = seg.parts == 1;
+      float* stg = reinterpret_cast<float*>(smem);
+      if (ok) {
+        const int quad = warp & 3;                              // TMEM lane quadrant this warp may read
+        const int slice = (warp - kSkFirstEpiWarp) >> 2;        // five warps share a quadrant
+        const uint32_t taddr = tmem_base + static_cast<uint32_t>(buf) * p.acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
+        for (int ci = slice; ci < (p.mb >> 4); ci += (kSkEpiWarps + kSkDecodeWarps) / 4) {
+          uint32_t acc[16];
+          tmem_ld_32x16(taddr + ci * 16, acc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
+        }
+      }
+      tc_fence_before();
+      tail_bar();
+      bool finalized = whole;
+      if (whole) {
+        if (ok)
+          for (int idx = tt; idx < rows_here * (kTileN / 4); idx += nthr)
+            sk_store4(p, m0 + (idx >> 5), n_base + (idx & 31) * 4, *reinterpret_cast<const float4*>(stg + static_cast<size_t>(idx) * 4));
+      } else {
+        if (ok) {
+          float* slot = sk_slot(p, cta, seg.part);
+          for (int idx = tt; idx < p.mb * (kTileN / 4); idx += nthr)
+            *reinterpret_cast<float4*>(slot + static_cast<size_t>(idx) * 4) = *reinterpret_cast<const float4*>(stg + static_cast<size_t>(idx) * 4);
+        }
+        __threadfence();
+        tail_bar();
+        if (tt == 0) {
+          uint32_t last = 0;
+          if (ok) {
+            const uint32_t prev = atomicAdd(&p.counters[seg.tile], 1u);
+            last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
+            if (last) p.counters[seg.tile] = 0;
+          }
+          ctl->is_last = last;
+        }
+        tail_bar();
+        if (ctl->is_last && !*abort_flag) {
+          __threadfence();
+          finalized = true;
+          sk_reduce_write<4>(p, seg, cta, tt, nthr, m0, rows_here, n_base, stg);
+        }
+      }
+      if (p.tp.mode & kTpScatterPush) {
+        // every row of the finished tile is on its way: barrier (all stores ordered before thread 0), ONE
+        // system-scope fence, then the owners' arrival counters
+        tail_bar();
+        if (finalized && tt == 0 && !*abort_flag) {
+          __threadfence_system();
+          const int m_last = min(p.M, m0 + p.mb) - 1;
+          for (int o = m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
+            red_release_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+        }
+      }
+      if (trace && tt == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
+    };
+
+    if (warp >= kSkFirstDecodeWarp) {
+      // ---------------------------------------------- decode
+      const int g = (warp - kSkFirstDecodeWarp) / kSkGroupWarps;                   // this warp's group
+      const int dq = threadIdx.x - kSkFirstDecodeWarp * 32 - g * kSkGroupWarps * 32;   // 0..255 inside the group
+      const int r = dq & 127;           // row of the weight tile
+      const int h = dq >> 7;            // 32-column half of the k-block (one 16-byte code chunk, one metadata sub-block)
+      const uint32_t code_off = static_cast<uint32_t>((h * 128 + r) * 16);
+      const uint32_t a_off = x_bytes + static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+      uint32_t chunk_off[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) chunk_off[j] = static_cast<uint32_t>(((h * 4 + j) ^ (r & 7)) << 4);
+      SkRing rc, ra;
+      int i_global = 0;
+      int seg_idx = 0;
+      bool ok = true;
+      // never leaves the loop early: the last segment ends at barriers shared with the epilogue warps
+      while (it.next(p, cta, grid, seg)) {
+        const bool tail = !it.has_more(p);
+        if (FMT != kFmtBf16 && ok) {
+          for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb, ++i_global, rc.advance(NC), ra.advance(S)) {
+            if ((i_global & 1) != g) continue;                   // the other group's k-block
+            if (!mbar_wait_park(smem_u32(&ctl->c_full[rc.s]), rc.wraps & 1u, abort_flag)) { ok = false; break; }
+            if (trace && dq == 0 && i_global < 64) trace[i_global * 8 + 2] = clock64();
+            const uint8_t* pk = c_ring + static_cast<size_t>(rc.s) * kSkCStageBytes;
+            const uint4 words = *reinterpret_cast<const uint4*>(pk + code_off);
+            const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
+            // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
+            uint32_t c0, c1, c2;
+            if (FMT == kFmtCubic4) {
+              const uint32_t ab = meta[r], cz = meta[128 + r];
+              c0 = bf2_dup(ab);        // A = s * a / 7
+              c1 = bf2_dup(ab >> 16);  // B = s * b / 49
+              c2 = bf2_dup(cz);        // C = s * (1 - a - b) / 343
+            } else {
+              const uint32_t so = meta[h * 128 + r];
+              c0 = bf2_dup(so);
+              c1 = bf2_dup(so >> 16);
+              c2 = 0;
+            }
+            // the codes and metadata are in registers: hand the slot back to the copy warp right away
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->c_empty[rc.s]));
+            uint32_t o[4][4];
+            if (FMT == kFmtNvfp4) {
+              // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
+              decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
+              decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
+              decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
+              decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+            } else {
+              decode8<FMT>(words.x, c0, c1, c2, o[0]);
+              decode8<FMT>(words.y, c0, c1, c2, o[1]);
+              decode8<FMT>(words.z, c0, c1, c2, o[2]);
+              decode8<FMT>(words.w, c0, c1, c2, o[3]);
+            }
+            // the arithmetic above ran while the slot may still be read by MMAs; only the stores wait for it
+            if (ra.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[ra.s]), (ra.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
+            uint8_t* arow = smem + static_cast<size_t>(ra.s) * ax_bytes + a_off;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(arow + chunk_off[j]) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[ra.s]));
+            if (trace && dq == 0 && i_global < 64) trace[i_global * 8 + 3] = clock64();
+          }
+        }
+        if (tail) tail_epilogue(seg_idx, ok);
+        ++seg_idx;
+      }
+    } else {
+      // ---------------------------------------------- epilogue of every segment but the last (warps 3..6)
+      // These four warps meet at a named barrier inside the loop, so none of them may leave the loop early:
+      // after a failed wait they keep walking the segment list with the work switched off.
+      const int quad = warp & 3;                                 // TMEM lane quadrant this warp may read
+      const int et = threadIdx.x - kSkFirstEpiWarp * 32;         // 0..127
+      int seg_idx = 0;
+      while (it.next(p, cta, grid, seg)) {
+        if (!it.has_more(p)) {
+          tail_epilogue(seg_idx, true);
+          break;
+        }
+        const int buf = seg_idx & 1;
+        const uint32_t use = static_cast<uint32_t>(seg_idx >> 1);
+        bool ok = mbar_wait_park(smem_u32(&ctl->acc_full[buf]), use & 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok) && !*abort_flag;
+        tc_fence_after();
+        if (trace && et == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 6] = clock64();
+        seg_geometry();
+        const bool whole = seg.parts == 1;
+        if (ok) {
+          // TMEM gives a thread one output feature (lane) and 16 batch rows (registers); memory wants rows of
+          // consecutive features.  Each warp transposes 16 x 32 fp32 through its own 2 KiB of shared memory:
+          // lane L then owns rows (L >> 3) + 4 i, features 4 (L & 7) .. + 3 of the chunk: 8-byte bf16 (or
+          // 16-byte fp32 partial) stores, eight lanes covering the 64 contiguous bytes of one row.
+          float* scr = epi_scratch + (warp - kSkFirstEpiWarp) * (16 * 32);
+          const int f4 = (lane & 7) * 4;
+          float* slot = whole ? nullptr : sk_slot(p, cta, seg.part) + quad * 32 + f4;
+          const uint32_t taddr = tmem_base + static_cast<uint32_t>(buf) * p.acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
+          for (int c0 = 0; c0 < p.mb; c0 += 16) {
+            uint32_t acc[16];
+            tmem_ld_32x16(taddr + c0, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) scr[j * 32 + lane] = __uint_as_float(acc[j]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = (lane >> 3) + 4 * i;
+              const float4 v = *reinterpret_cast<const float4*>(scr + row * 32 + f4);
+              if (!whole) {
+                *reinterpret_cast<float4*>(slot + static_cast<size_t>(c0 + row) * kTileN) = v;
+              } else if (c0 + row < rows_here) {
+                sk_store4(p, m0 + c0 + row, n_base + quad * 32 + f4, v);
+              }
+            }
+            __syncwarp();                                  // the scratch is rewritten by the next chunk
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[buf]));
+        if (trace && et == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
+
+        bool finalized = whole;
+        if (!whole) {
+          // streamed tile: publish the partial, count arrivals; the last arriver sums all parts in part order
+          __threadfence();
+          epi_bar();
+          if (et == 0) {
+            uint32_t last = 0;
+            if (ok) {
+              const uint32_t prev = atomicAdd(&p.counters[seg.tile], 1u);
+              last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
+              if (last) p.counters[seg.tile] = 0;
+            }
+            ctl->is_last = last;
+          }
+          epi_bar();
+          const bool last = ctl->is_last != 0;
+          epi_bar();                                   // is_last has been read by all before it can change again
+          if (last && !*abort_flag) {
+            __threadfence();
+            finalized = true;
+            sk_reduce_write<4>(p, seg, cta, et, kSkEpiWarps * 32, m0, rows_here, n_base, nullptr);
+          }
+        }
+        if (p.tp.mode & kTpScatterPush) {
+          epi_bar();
+          if (finalized && et == 0 && !*abort_flag) {
+            __threadfence_system();
+            const int m_last = min(p.M, m0 + p.mb) - 1;
+            for (int o = m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
+              red_release_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+          }
+        }
+        ++seg_idx;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (trace && threadIdx.x == 0) trace[7] = clock64();
+  if (p.trace && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[cta * 8 + 1] = t;
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+  if ((p.tp.mode & kTpGatherWait) && threadIdx.x == 0) {
+    // the last CTA of the grid closes the epoch of the gathered buffer
+    if (atomicAdd(&p.tp.ag_state[1], 1u) == static_cast<uint32_t>(grid) - 1u) {
+      p.tp.ag_state[1] = 0;
+      __threadfence();
+      atomicAdd(&p.tp.ag_state[0], p.tp.ag_expected);
+    }
+  }
+  if (threadIdx.x == 0 && ctl->abort_flag)
+    atomicExch(p.status, static_cast<uint32_t>(ctl->abort_flag == 2 ? kErrFlagTimeout : kErrBarrierTimeout));
+}
+
+template <int FMT>
+static int launch_sk_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemmParams& p, int grid, size_t smem,
+                         cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  wq_gemm_sk_kernel<FMT><<<grid, kSkThreads, smem, stream>>>(tx, tw, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Schedule and launch.  `min_units` > 0 overrides the smallest run of k-blocks a CTA may be dealt in the
+// streamed region (tests use 1..2 to force many-part tiles); 0 picks it from a cost model: a run costs about
+// 0.34 us per k-block, every extra part of a tile costs the reducer about mb / 256 us, so the best number of
+// parts is sqrt(k_blocks * 0.34 * 256 / mb) and the run length k_blocks over that.
+int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, size_t workspace_bytes,
+                   int sm_count, int min_units, cudaStream_t stream) {
+  if (sm_count < 1) return -15;
+  p.n_tiles = (p.N + kTileN - 1) / kTileN;
+  const int m_tiles = (p.M + p.mb - 1) / p.mb;
+  p.tiles = p.n_tiles * m_tiles;
+  if (p.meta_k_blocks < 1 || (p.meta_k_blocks & (p.meta_k_blocks - 1)) != 0) return -16;
+  p.meta_shift = 0;
+  while ((1 << p.meta_shift) < p.meta_k_blocks) ++p.meta_shift;
+  uint32_t cols = 32;
+  while (cols < static_cast<uint32_t>(p.mb)) cols <<= 1;
+  p.acc_cols = cols;
+  p.tmem_cols = 2 * cols;
+
+  if (min_units <= 0) {
+    int est = 1;
+    while (static_cast<long long>(est) * est * 87 < static_cast<long long>(p.k_blocks) * p.mb) ++est;   // ceil(sqrt(kb * mb / 87))
+    min_units = est < 4 ? 4 : est;
+  }
+  p.sk_tiles = p.tiles <= sm_count ? p.tiles : p.tiles % sm_count;
+  p.sk_ctas = 0;
+  if (p.sk_tiles > 0) {
+    // a CTA of the streamed region owns two fp32 partial slots (see sk_slot)
+    const size_t part_bytes = static_cast<size_t>(p.mb) * kTileN * sizeof(float);
+    const long long slots_fit = (p.workspace && p.counters) ? static_cast<long long>(workspace_bytes / (2 * part_bytes)) : 0;
+    long long want = static_cast<long long>(p.sk_tiles) * p.k_blocks / min_units;
+    if (want > sm_count) want = sm_count;
+    if (want < 1) want = 1;
+    if (want > slots_fit) want = slots_fit;
+    if (want < 1) {
+      p.sk_tiles = 0;            // no scratch: every tile stays whole, one per CTA and wave
+    } else {
+      p.sk_ctas = static_cast<int>(want);   // may be < sk_tiles: a CTA then covers several tiles, split only at run ends
+    }
+  }
+  if (static_cast<long long>(p.sk_tiles) * p.k_blocks * (sm_count + 1) >= (1LL << 31)) return -19;   // SkIter is 32-bit
+  int grid = p.tiles - p.sk_tiles;
+  if (grid > sm_count) grid = sm_count;
+  if (grid < p.sk_ctas) grid = p.sk_ctas;
+  if (grid < 1) return -17;
+
+  const size_t ax = static_cast<size_t>(p.mb) * 128 + kATileBytes;
+  const size_t budget = 232448 - 1024 - 1024 - sizeof(SkCtl) - kSkEpiScratchBytes;
+  int S, NC;
+  if (fmt == kFmtBf16) {
+    NC = 0;
+    S = static_cast<int>(budget / ax);
+  } else {
+    S = static_cast<int>((budget - 4 * kSkCStageBytes) / ax);
+    if (S > kSkMaxAx) S = kSkMaxAx;
+    NC = static_cast<int>((budget - S * ax) / kSkCStageBytes);
+    if (NC > kSkMaxC) NC = kSkMaxC;
+  }
+  if (S > kSkMaxAx) S = kSkMaxAx;
+  if (S < 2 || (fmt != kFmtBf16 && NC < 2)) return -14;
+  p.ax_stages = S;
+  p.c_stages = NC;
+  const size_t smem = S * ax + static_cast<size_t>(NC) * kSkCStageBytes + kSkEpiScratchBytes + sizeof(SkCtl) + 1024;
+  switch (fmt) {
+    case kFmtCubic4: return launch_sk_fmt<kFmtCubic4>(tx, tw, p, grid, smem, stream);
+    case kFmtAffine4: return launch_sk_fmt<kFmtAffine4>(tx, tw, p, grid, smem, stream);
+    case kFmtNvfp4: return launch_sk_fmt<kFmtNvfp4>(tx, tw, p, grid, smem, stream);
+    default: return launch_sk_fmt<kFmtBf16>(tx, tw, p, grid, smem, stream);
+  }
+}
+
+}  // namespace cb

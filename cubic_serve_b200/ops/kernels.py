@@ -85,10 +85,32 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     return max(1, min(sms // tiles, k_blocks // 8, 8))
 
 
+def use_stream_k(m: int, n: int, fmt: int, sms: int = 148) -> bool:
+    """Which GEMM kernel serves a shape when the caller does not say.
+
+    Measured on a B200 inside CUDA graphs (cubic4, K = 4096): the persistent stream-K kernel is 1.45-1.55x
+    faster when there are more weight tiles than SMs and at most 128 batch rows (it removes the second,
+    partly empty wave: N = 24576 runs 69 -> 45 us), and 5 % faster for the bf16 lm_head; with fewer tiles
+    than SMs its fixed costs (start-up, fp32 partial tiles summed by the last CTA) make it 10-25 % slower
+    than one CTA per (tile, split), and at 256 batch rows both kernels are bound by the activation-tile
+    traffic into shared memory, where the reduction of 128 KiB partials costs more than the wave it saves.
+    """
+    tiles = -(-n // 128) * -(-m // 256)
+    if tiles <= sms:
+        return False
+    return m <= 128 or fmt == FMT_BF16
+
+
 def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, splits: int | None = None,
-            ws: Workspace | None = None, link=None) -> torch.Tensor:
-    """``out[M, N] = x[M, K] @ W[N, K]^T * alpha (+ residual)`` with W in packed form."""
+            ws: Workspace | None = None, link=None, min_units: int | None = None) -> torch.Tensor:
+    """``out[M, N] = x[M, K] @ W[N, K]^T * alpha (+ residual)`` with W in packed form.
+
+    Two kernels: one CTA per (weight tile, K split) (``csrc/wq_gemm.cu``) and the persistent stream-K kernel
+    (``csrc/wq_gemm_sk.cu``).  With neither ``splits`` nor ``min_units`` given the faster one for the shape is
+    used (``use_stream_k``).  ``splits`` forces the first with that split-K factor; ``min_units`` forces the
+    second (0 = its own schedule, > 0 = the smallest run of k-blocks a CTA is dealt).
+    """
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
     m, k = x.shape
     assert k == w.k, (k, w.k)
@@ -99,9 +121,19 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
     if residual is not None:
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
+    l = native.lib()
+    if splits is None and min_units is None and use_stream_k(m, w.n, w.fmt, sm_count(x.device)):
+        min_units = 0
+    if splits is None and min_units is not None:
+        code = l.cb_wq_gemm_sk(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
+                               None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual),
+                               float(w.alpha), m, w.n, k, w.group_k, int(min_units), ws.gemm.data_ptr(),
+                               ws.gemm.numel(), ws.gemm_counters.data_ptr(), ws.status.data_ptr(), _stream(),
+                               None if link is None else ctypes.byref(link))
+        native.check(code, "cb_wq_gemm_sk")
+        return out
     if splits is None:
         splits = choose_splits(m, w.n, k)
-    l = native.lib()
     if splits > 1:
         need = l.cb_wq_gemm_workspace_bytes(m, w.n, splits)
         if need > ws.gemm.numel():

@@ -126,6 +126,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_verify_greedy.restype = i
     l.cb_wq_gemm_tp.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, vp, vp, vp, vp]
     l.cb_wq_gemm_tp.restype = i
+    l.cb_wq_gemm_sk.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, ll, vp, vp, vp, vp]
+    l.cb_wq_gemm_sk.restype = i
     l.cb_tp_reduce_norm.argtypes = [vp, vp]
     l.cb_tp_reduce_norm.restype = i
     l.cb_tp_wait.argtypes = [vp, vp, ctypes.c_uint, i, vp, vp]

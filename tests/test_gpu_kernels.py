@@ -50,6 +50,48 @@ def test_wq_gemm_cubic4(m, n, k, splits):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("m,n,k,min_units", [
+    (1, 128, 256, 0), (16, 256, 512, 0), (40, 384, 1024, 0), (300, 128, 512, 0), (64, 200, 512, 0),
+    (256, 256, 4096, 0),            # automatic schedule: tiles split into several runs
+    (32, 256, 2048, 1),             # one k-block per run: 32 parts per tile
+    (256, 384, 4096, 3),            # runs that straddle tile boundaries (64 k-blocks per tile, 3 per run)
+    (48, 1280, 1024, 5),            # ten tiles, runs of five k-blocks, some CTAs own two partial runs
+    (520, 640, 512, 2),             # three row tiles (256 + 256 + 8 rows)
+    (16, 128 * 150, 256, 0),        # more tiles than SMs: whole tiles + a streamed remainder
+    (272, 128 * 80, 256, 1),        # two row tiles x 80 column tiles = 160 tiles, streamed remainder of 12
+])
+def test_wq_gemm_stream_k(m, n, k, min_units):
+    """The persistent stream-K kernel against the fp32 oracle, including forced many-part tiles."""
+    K = _k()
+    pw, dense = _cubic_weight(n, k, seed=m + n)
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
+    ref = x.float() @ dense.t()
+    res = torch.randn(m, n, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    y = K.wq_gemm(x.to(DEV), pw.to(DEV), min_units=min_units)
+    torch.cuda.synchronize()
+    K.workspace(y.device).check_status()
+    assert _rel(y.cpu(), ref) < 1e-2
+    assert _rel(K.wq_gemm(x.to(DEV), pw.to(DEV)).cpu(), ref) < 1e-2     # whichever kernel the dispatcher picks
+    # again with a residual: counters must have been restored, the fix-up adds the residual exactly once
+    y2 = K.wq_gemm(x.to(DEV), pw.to(DEV), residual=res.to(DEV), min_units=min_units)
+    torch.cuda.synchronize()
+    K.workspace(y.device).check_status()
+    assert _rel(y2.cpu(), ref + res.float()) < 1e-2
+    assert torch.equal(K.wq_gemm(x.to(DEV), pw.to(DEV), min_units=min_units), y)      # deterministic
+
+
+def test_wq_gemm_stream_k_bf16_weights():
+    K = _k()
+    for m, n, k, mu in ((48, 256, 512, 0), (256, 1000, 1024, 2), (24, 128 * 150 + 40, 256, 0)):
+        g = torch.Generator().manual_seed(n)
+        w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
+        x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16)
+        y = K.wq_gemm(x.to(DEV), wq_pack.pack_bf16(w).to(DEV), min_units=mu)
+        torch.cuda.synchronize()
+        K.workspace(y.device).check_status()
+        assert _rel(y.cpu(), x.float() @ w.float().t()) < 1e-2
+
+
 def test_wq_gemm_residual_and_bf16():
     K = _k()
     m, n, k = 48, 256, 512
