@@ -146,7 +146,7 @@ def main() -> None:
                     g = dist.new_group(list(range(stage * tp_size, (stage + 1) * tp_size)))
                     tp_group = g if stage == pp.stage else tp_group
         if tp_size > 1:
-            mode = args.comm if not cfg.is_moe and pp is None else "nccl"
+            mode = args.comm if pp is None else "nccl"
             tp = TensorParallel(tp_group, dev, mode=mode, hidden=cfg.hidden_size,
                                 max_tokens=args.prefill_tokens, rows_max=max(args.concurrency, 512))
     C, L = args.concurrency, args.input_len

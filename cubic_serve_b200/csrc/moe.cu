@@ -203,6 +203,25 @@ int cb_moe_route(const void* logits, int ld, const void* x, int T, int E, int k,
   return static_cast<int>(cudaGetLastError());
 }
 
+// Scan + permutation only, for callers that have already filled topk_ids ([T,k], -1 = no route) and counts
+// (expert-parallel receive side: the "tokens" are the records received from the other ranks).
+int cb_moe_permute(const void* x, const void* topk_ids, int T, int k, int H, int expert_lo, int expert_count, int mb,
+                   const void* counts, void* offsets, void* cursors, void* total, void* tiles, void* route_pos,
+                   void* xs, void* stream) {
+  using namespace cb;
+  if (T <= 0) return 0;
+  if (k > kMaxTopK || k < 1 || H % 8 != 0 || expert_count > 256) return -10;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  moe_scan_kernel<<<1, 256, 0, st>>>(static_cast<const int*>(counts), static_cast<int*>(offsets),
+                                     static_cast<int*>(cursors), expert_count, mb, static_cast<int*>(total),
+                                     static_cast<int*>(tiles));
+  moe_scatter_kernel<<<(T * k + 3) / 4, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                                       static_cast<const int*>(topk_ids), T, k, H, expert_lo,
+                                                       expert_count, static_cast<int*>(cursors),
+                                                       static_cast<int*>(route_pos), static_cast<__nv_bfloat16*>(xs));
+  return static_cast<int>(cudaGetLastError());
+}
+
 int cb_moe_combine(const void* y, const void* route_pos, const void* topk_w, int T, int k, int H, const void* residual,
                    void* out, void* stream) {
   using namespace cb;

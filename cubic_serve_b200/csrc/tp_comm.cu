@@ -54,6 +54,8 @@ struct ReduceNormParams {
   int rank, size, rows_per_rank, H, M;
   float eps;
   int zero_centered;
+  int local_only;                // 1: keep the normalised rows on this rank (no all-gather, no counters); the
+                                 // consumer is a later kernel of the same stream (expert-parallel dispatch)
 };
 
 static constexpr int kRnThreads = 256;
@@ -144,13 +146,17 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
           op[j] = __floats2bfloat162_rn(vals[it][2 * j] * inv * ww.x, vals[it][2 * j + 1] * inv * ww.y);
         }
         // all-gather by push: the same 16 bytes to every rank's buffer (self included)
-        for (int r = 0; r < p.size; ++r)
-          reinterpret_cast<uint4*>(p.x_peer[r] + static_cast<size_t>(m) * p.H)[v] = ov;
+        if (p.local_only) {
+          reinterpret_cast<uint4*>(p.x_peer[p.rank] + static_cast<size_t>(m) * p.H)[v] = ov;
+        } else {
+          for (int r = 0; r < p.size; ++r)
+            reinterpret_cast<uint4*>(p.x_peer[r] + static_cast<size_t>(m) * p.H)[v] = ov;
+        }
       }
     }
   }
   __syncthreads();
-  if (threadIdx.x < p.size) {
+  if (threadIdx.x < p.size && !p.local_only) {
     __threadfence_system();   // cumulative: covers the row pushed by the whole CTA (ordered by the barrier above)
     red_rel_sys_add(p.ag_flag_peer[threadIdx.x] + p.rank, 1u);
   }
@@ -244,7 +250,7 @@ extern "C" {
 struct CbReduceNorm {
   const void* recv; const void* rs_flag; void* rs_state; unsigned rs_expected;
   void* h; const void* norm_w; void* x_peer[8]; void* ag_flag_peer[8]; void* status;
-  int rank, size, rows_per_rank, H, M; float eps; int zero_centered;
+  int rank, size, rows_per_rank, H, M; float eps; int zero_centered; int local_only;
 };
 
 int cb_tp_reduce_norm(const CbReduceNorm* a, void* stream) {
@@ -263,7 +269,7 @@ int cb_tp_reduce_norm(const CbReduceNorm* a, void* stream) {
   }
   p.status = static_cast<uint32_t*>(a->status);
   p.rank = a->rank; p.size = a->size; p.rows_per_rank = a->rows_per_rank; p.H = a->H; p.M = a->M;
-  p.eps = a->eps; p.zero_centered = a->zero_centered;
+  p.eps = a->eps; p.zero_centered = a->zero_centered; p.local_only = a->local_only;
   tp_reduce_norm_kernel<<<a->rows_per_rank, kRnThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -199,6 +199,12 @@ class DecoderRunner:
         self.act = torch.empty(T, inter, dtype=bf, device=dev) if inter else None
         self.ws = K.workspace(dev)
         self.launches_per_step = 0
+        self.ep = None
+        if cfg.is_moe and tp is not None and tp.fused is not None:
+            # expert parallelism over the tensor-parallel group: fused dispatch / combine on the row-sharded stream
+            from ..parallel.ep import FusedEp, symmetric_ep_buffers
+            bufs = symmetric_ep_buffers(tp.group, H, cfg.experts_per_token, tp.fused.b.max_tokens, dev)
+            self.ep = FusedEp(bufs, dev, cfg.num_experts, 2 * cfg.moe_intermediate_size, ws=self.ws)
 
     # ---------------------------------------------------------------- forward
     def forward_hidden(self, b: StepBatch) -> torch.Tensor:
@@ -323,13 +329,23 @@ class DecoderRunner:
                               self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)
             s ^= 1
             f.gemm_scatter(attn, lw.o, s)
+            nxt = w.layers[li + 1].ln1 if li + 1 < len(w.layers) else w.final_norm
+            if lw.moe is not None:
+                # MoE block on the row-sharded stream: the normalised rows stay on their home rank, the
+                # expert-parallel kernels move each row only to the ranks that own one of its experts and add
+                # the combined result into h_local; the next norm then gathers for the attention GEMM
+                f.reduce_norm(lw.ln2, s, H, cfg.rms_eps, cfg.zero_centered_norm, local_only=True)
+                self.ep.forward(lw.moe, f.b.xfull[s, lo:lo + f.rpr], cnt, f.h_local)
+                s ^= 1
+                f.reduce_norm(nxt, s, 0, cfg.rms_eps, cfg.zero_centered_norm, reduce=False)
+                n += 7 + self.ep.launches
+                continue
             f.reduce_norm(lw.ln2, s, H, cfg.rms_eps, cfg.zero_centered_norm)
             gu, act = self.gu[:T], self.act[:T]
             f.gemm_gather(lw.gate_up, gu, s)
             K.swiglu(gu, out=act)
             s ^= 1
             f.gemm_scatter(act, lw.down, s)
-            nxt = w.layers[li + 1].ln1 if li + 1 < len(w.layers) else w.final_norm
             f.reduce_norm(nxt, s, H, cfg.rms_eps, cfg.zero_centered_norm)
             n += 9
         self.launches_per_step = n

@@ -138,6 +138,16 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_moe_route.restype = i
     l.cb_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp, vp]
     l.cb_moe_combine.restype = i
+    l.cb_moe_permute.argtypes = [vp, vp, i, i, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
+    l.cb_moe_permute.restype = i
+    l.cb_ep_dispatch.argtypes = [vp, vp]
+    l.cb_ep_dispatch.restype = i
+    l.cb_ep_unpack.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp, vp, vp]
+    l.cb_ep_unpack.restype = i
+    l.cb_ep_combine_push.argtypes = [vp, vp]
+    l.cb_ep_combine_push.restype = i
+    l.cb_ep_finish.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, vp, vp]
+    l.cb_ep_finish.restype = i
     l.cb_wq_gemm_grouped.argtypes = [i, vp, i, vp, vp, vp, i, f, i, i, i, i, vp, i, i, i, ll, ll, vp, vp]
     l.cb_wq_gemm_grouped.restype = i
 
@@ -155,7 +165,26 @@ class ReduceNormStruct(ctypes.Structure):
                 ("rs_expected", ctypes.c_uint), ("h", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
                 ("x_peer", ctypes.c_void_p * 8), ("ag_flag_peer", ctypes.c_void_p * 8), ("status", ctypes.c_void_p),
                 ("rank", ctypes.c_int), ("size", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("H", ctypes.c_int),
-                ("M", ctypes.c_int), ("eps", ctypes.c_float), ("zero_centered", ctypes.c_int)]
+                ("M", ctypes.c_int), ("eps", ctypes.c_float), ("zero_centered", ctypes.c_int),
+                ("local_only", ctypes.c_int)]
+
+
+class EpDispatchStruct(ctypes.Structure):
+    """Mirror of ``CbEpDispatch`` in ``csrc/ep_comm.cu``."""
+    _fields_ = [("logits", ctypes.c_void_p), ("x", ctypes.c_void_p), ("ld", ctypes.c_int), ("cnt", ctypes.c_int),
+                ("E", ctypes.c_int), ("k", ctypes.c_int), ("H", ctypes.c_int), ("normalize", ctypes.c_int),
+                ("experts_per_rank", ctypes.c_int), ("rank", ctypes.c_int), ("size", ctypes.c_int),
+                ("cap", ctypes.c_int), ("xin_peer", ctypes.c_void_p * 8), ("ids_peer", ctypes.c_void_p * 8),
+                ("w_peer", ctypes.c_void_p * 8), ("cnt_peer", ctypes.c_void_p * 8), ("flag_peer", ctypes.c_void_p * 8),
+                ("local_cnt", ctypes.c_void_p), ("sent", ctypes.c_void_p), ("done", ctypes.c_void_p)]
+
+
+class EpCombineStruct(ctypes.Structure):
+    """Mirror of ``CbEpCombine`` in ``csrc/ep_comm.cu``."""
+    _fields_ = [("y", ctypes.c_void_p), ("route_pos", ctypes.c_void_p), ("topk_w", ctypes.c_void_p),
+                ("cnt_in", ctypes.c_void_p), ("size", ctypes.c_int), ("cap", ctypes.c_int), ("k", ctypes.c_int),
+                ("H", ctypes.c_int), ("rank", ctypes.c_int), ("yin_peer", ctypes.c_void_p * 8),
+                ("flag_peer", ctypes.c_void_p * 8), ("done", ctypes.c_void_p)]
 
 
 class ArgmaxMergeStruct(ctypes.Structure):

@@ -156,8 +156,12 @@ class FusedTp:
         return -(-n // 128) * m_tiles
 
     def reduce_norm(self, norm_w: torch.Tensor, s: int, n_out: int, eps: float, zero_centered: bool = False,
-                    reduce: bool = True) -> None:
-        """Owner-side rank-ordered sum + residual + RMSNorm, then all-gather push into set ``s``."""
+                    reduce: bool = True, local_only: bool = False) -> None:
+        """Owner-side rank-ordered sum + residual + RMSNorm, then all-gather push into set ``s``.
+
+        ``local_only`` keeps the normalised rows on this rank (its own rows of set ``s``, no counters): the
+        consumer is the expert-parallel dispatch on the same stream.
+        """
         a = native.ReduceNormStruct()
         a.recv = self.b.recv.data_ptr() + self._recv_off(s)
         a.rs_flag = self.b.flags.data_ptr() + self._flag_off(s, 0)
@@ -170,7 +174,7 @@ class FusedTp:
             a.ag_flag_peer[r] = self.b.flags_ptrs[r] + self._flag_off(s, 1)
         a.status = self.ws.status.data_ptr()
         a.rank, a.size, a.rows_per_rank, a.H, a.M = self.rank, self.size, self.rpr, self.b.hidden, self.m
-        a.eps, a.zero_centered = float(eps), int(zero_centered)
+        a.eps, a.zero_centered, a.local_only = float(eps), int(zero_centered), int(local_only)
         native.check(native.lib().cb_tp_reduce_norm(ctypes.byref(a), K._stream()), "cb_tp_reduce_norm")
 
     def gemm_gather(self, w, out: torch.Tensor, s: int) -> torch.Tensor:

@@ -73,3 +73,63 @@ def test_router_stable_ties_and_weights():
             ex = int(ids[ti, r])
             assert off[ex] <= pos[ti, r] < off[ex] + cnt[ex]
             assert torch.equal(sc.xs[int(pos[ti, r])], x[ti])
+
+
+@pytest.mark.parametrize("method,tokens,ranks", [("none", 50, 4), ("nvfp4", 200, 8), ("cubic", 7, 2)])
+def test_expert_parallel_dispatch_combine_matches_single_rank(method, tokens, ranks):
+    """Row-sharded tokens, experts spread over emulated ranks on one device: dispatch -> experts -> combine must
+    reproduce residual + MoE(x) of the one-rank layer.  The ranks' kernels run phase by phase (a rank's wait is
+    always for launches that are already in the stream)."""
+    from cubic_serve_b200.models.decoder import quantize_linear
+    from cubic_serve_b200.models.moe import MoeLayer, stack_experts
+    from cubic_serve_b200.ops import kernels as K
+    from cubic_serve_b200.parallel.ep import FusedEp, local_ep_fabric
+    from cubic_serve_b200.parallel.tp import rows_per_rank
+    E, k, H, I = 16, 4, 256, 128
+    cfg = ModelConfig(family="gqa_moe", hidden_size=H, num_experts=E, experts_per_token=k, moe_intermediate_size=I,
+                      quant=QuantSpec(method, 4 if method != "none" else 16, {"nvfp4": 16, "cubic": 128, "none": 0}[method]))
+    g = torch.Generator(device=DEV).manual_seed(11)
+    router = wq_pack.pack_bf16((torch.randn(E, H, device=DEV, generator=g) * 0.05).to(torch.bfloat16))
+    gus = [quantize_linear(torch.randn(2 * I, H, device=DEV, generator=g) * 0.05, cfg) for _ in range(E)]
+    dns = [quantize_linear(torch.randn(H, I, device=DEV, generator=g) * 0.05, cfg) for _ in range(E)]
+
+    def layer_for(lo, n):
+        gu, gcs, gms = stack_experts(gus[lo:lo + n])
+        dn, dcs, dms = stack_experts(dns[lo:lo + n])
+        return MoeLayer(router, gu, dn, (gcs, gms, dcs, dms), E, k, lo, n, True)
+
+    x = (torch.randn(tokens, H, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    resid = (torch.randn(tokens, H, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+    want = layer_for(0, E).forward(x, residual=resid, out=torch.empty_like(resid)).float()
+
+    rpr = rows_per_rank(tokens, ranks)
+    fabric = local_ep_fabric(ranks, H, k, max_tokens=max(tokens, 64), device=DEV)
+    eps = [FusedEp(b, torch.device(DEV), E, 2 * I) for b in fabric]
+    layers = [layer_for(r * (E // ranks), E // ranks) for r in range(ranks)]
+    h_rows, x_rows, cnts = [], [], []
+    for r in range(ranks):
+        lo = r * rpr
+        cnt = max(0, min(tokens, lo + rpr) - lo)
+        cnts.append(cnt)
+        xr = torch.zeros(rpr, H, dtype=torch.bfloat16, device=DEV)
+        hr = torch.zeros(rpr, H, dtype=torch.bfloat16, device=DEV)
+        xr[:cnt], hr[:cnt] = x[lo:lo + cnt], resid[lo:lo + cnt]
+        x_rows.append(xr)
+        h_rows.append(hr)
+    for rounds in range(2):                                  # twice: counters are cumulative, buffers are reused
+        for r in range(ranks):
+            h_rows[r][:cnts[r]] = resid[r * rpr:r * rpr + cnts[r]]
+        for r in range(ranks):
+            eps[r].dispatch(layers[r], x_rows[r], cnts[r])
+        for r in range(ranks):
+            eps[r].experts(layers[r])
+        for r in range(ranks):
+            eps[r].finish(cnts[r], h_rows[r])
+        torch.cuda.synchronize()
+        K.workspace(torch.device(DEV)).check_status()
+        got = torch.cat([h_rows[r][:cnts[r]] for r in range(ranks)]).float()
+        assert got.shape == want.shape
+        assert _rel(got, want) < 2e-2
+    # every row went only to ranks that own one of its experts, once per rank
+    sent = torch.stack([(eps[r].sent[:cnts[r]] >= 0).sum() for r in range(ranks)]).sum().item()
+    assert tokens <= sent <= tokens * min(k, ranks)
