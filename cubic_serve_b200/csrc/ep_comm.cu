@@ -130,20 +130,16 @@ ep_dispatch_kernel(const EpDispatchParams p) {
       }
     }
   }
-  // every row of this CTA is on its way: CTA barrier, one cumulative system fence, count the CTA; the last
-  // CTA publishes the per-destination counts and raises the arrival counters
+  // every row of this CTA is on its way: CTA barrier, count the CTA in (acquire-release); the last CTA
+  // publishes the per-destination counts and raises the arrival counters with a release at system scope
   __syncthreads();
   __shared__ uint32_t is_last;
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    is_last = atomicAdd(p.done, 1u) == gridDim.x - 1u ? 1u : 0u;
-  }
+  if (threadIdx.x == 0) is_last = atom_add_acq_rel_gpu(p.done, 1u) == gridDim.x - 1u ? 1u : 0u;
   __syncthreads();
   if (is_last && threadIdx.x < p.size) {
-    __threadfence();
+    // the release below is cumulative: it covers the rows of every CTA (release sequence on `done`, CTA barriers)
     const int c = atomicExch(&p.local_cnt[threadIdx.x], 0);
     p.cnt_peer[threadIdx.x][p.rank] = c;
-    __threadfence_system();
     ep_red_rel(p.flag_peer[threadIdx.x] + p.rank, 1u);
     if (threadIdx.x == 0) *p.done = 0;
   }
@@ -241,13 +237,9 @@ ep_combine_push_kernel(const EpCombineParams p) {
   }
   __syncthreads();
   __shared__ uint32_t is_last;
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    is_last = atomicAdd(p.done, 1u) == gridDim.x - 1u ? 1u : 0u;
-  }
+  if (threadIdx.x == 0) is_last = atom_add_acq_rel_gpu(p.done, 1u) == gridDim.x - 1u ? 1u : 0u;
   __syncthreads();
   if (is_last && threadIdx.x < p.size) {
-    __threadfence_system();
     ep_red_rel(p.flag_peer[threadIdx.x] + p.rank, 1u);
     if (threadIdx.x == 0) *p.done = 0;
   }

@@ -269,6 +269,24 @@ __device__ __forceinline__ uint32_t umma_idesc(uint32_t m, uint32_t n, uint32_t 
   return d;
 }
 
+// One release fence at system scope followed by relaxed updates: a thread that raises several peers' counters
+// pays for ONE fence (each `red.release.sys` carries its own, ~4 us apiece on this platform when measured).
+__device__ __forceinline__ void fence_acq_rel_sys() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+__device__ __forceinline__ void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Device-scope acquire-release counter increment: CTAs that count themselves in with it form a release
+// sequence, so whatever the LAST one publishes afterwards with a release at system scope also covers the
+// writes of all earlier CTAs (causality is transitive), without a system-scope fence per CTA.
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 // ---------------------------------------------------------------- misc math
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;

@@ -157,7 +157,7 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
   }
   __syncthreads();
   if (threadIdx.x < p.size && !p.local_only) {
-    __threadfence_system();   // cumulative: covers the row pushed by the whole CTA (ordered by the barrier above)
+    // release at system scope, cumulative: covers the row pushed by the whole CTA (ordered by the barrier above)
     red_rel_sys_add(p.ag_flag_peer[threadIdx.x] + p.rank, 1u);
   }
   if (threadIdx.x == 0) {
@@ -219,7 +219,6 @@ tp_argmax_merge_kernel(const ArgmaxMergeParams p) {
   }
   __syncthreads();
   if (threadIdx.x < p.size) {
-    __threadfence_system();
     red_rel_sys_add(p.flag_peer[threadIdx.x] + p.rank, 1u);
     if (!wait_ge(p.my_flag + threadIdx.x, p.my_state[0] + 1u)) ok_flag = 0;
   }

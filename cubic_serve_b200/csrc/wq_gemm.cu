@@ -408,15 +408,14 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // every partial row of this CTA is on its way: make the stores visible system-wide,
     // then raise the arrival counter of each owner whose rows this tile touched
     const bool pusher = (p.splits == 1) || ctl->is_last;
-    // CTA barrier first (every thread's stores are then visible to thread 64), then ONE system-scope fence by
-    // the signalling thread: fences are cumulative, so the counter update is ordered after all of the tile's
-    // stores without 512 threads each draining their own
+    // CTA barrier first (every thread's stores then happen before thread 64 continues), then ONE release fence
+    // at system scope by that thread (cumulative: it orders all of the tile's stores) and relaxed counter updates
     asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
     if (pusher && threadIdx.x == 64 && !ctl->abort_flag) {
-      __threadfence_system();
       const int m_last = min(p.M, m0 + p.mb) - 1;
+      fence_acq_rel_sys();
       for (int o = m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
-        red_release_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+        red_relaxed_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
     }
   }
   tc_fence_before();

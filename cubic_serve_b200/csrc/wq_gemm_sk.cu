@@ -459,14 +459,14 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
       if (p.tp.mode & kTpScatterPush) {
-        // every row of the finished tile is on its way: barrier (all stores ordered before thread 0), ONE
-        // system-scope fence, then the owners' arrival counters
+        // every row of the finished tile is on its way: barrier (all stores ordered before thread 0), then the
+        // owners' arrival counters after ONE release fence at system scope (cumulative)
         tail_bar();
         if (finalized && tt == 0 && !*abort_flag) {
-          __threadfence_system();
           const int m_last = min(p.M, m0 + p.mb) - 1;
+          fence_acq_rel_sys();
           for (int o = m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
-            red_release_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+            red_relaxed_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
         }
       }
       if (trace && tt == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
@@ -622,10 +622,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (p.tp.mode & kTpScatterPush) {
           epi_bar();
           if (finalized && et == 0 && !*abort_flag) {
-            __threadfence_system();
             const int m_last = min(p.M, m0 + p.mb) - 1;
+            fence_acq_rel_sys();
             for (int o = m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
-              red_release_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+              red_relaxed_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
           }
         }
         ++seg_idx;

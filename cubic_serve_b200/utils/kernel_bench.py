@@ -132,9 +132,55 @@ def bench_attn(rows: int, ctx: int, hq: int, hkv: int, kb: int, vb: int, splits:
             "us": round(ms * 1e3, 1), "kv_gbs": round(kv_bytes / ms / 1e6, 1)}
 
 
+def bench_fused_tp(ranks: int, m: int, hidden: int, inter: int, iters: int) -> dict:
+    """One o_proj -> norm -> gate/up boundary of the fused tensor-parallel path with all ranks on THIS device.
+
+    The ranks' kernels run stage by stage (every producer of a stage is in the stream before any consumer), so
+    the waits inside the kernels find their counters raised; "peer" buffers are other tensors of this process.
+    It times the three kernels per rank (scatter-push GEMM, rank-ordered reduce + norm + gather push,
+    gather-wait GEMM) without any NVLink hop, and gives ncu a one-GPU program that launches them.
+    """
+    from ..parallel.tp import FusedTp, local_fabric
+    dev = torch.device(DEV)
+    fab = [FusedTp(b, dev) for b in local_fabric(ranks, hidden, max(m, 64), 64, DEV)]
+    o_w = [random_cubic_weight(hidden, hidden // ranks) for _ in range(ranks)]          # row-parallel shard
+    gu_w = [random_cubic_weight(2 * inter // ranks, hidden) for _ in range(ranks)]       # column-parallel shard
+    norm = torch.ones(hidden, dtype=torch.bfloat16, device=DEV)
+    attn = [torch.randn(m, hidden // ranks, device=DEV, dtype=torch.bfloat16) for _ in range(ranks)]
+    gu = [torch.empty(m, 2 * inter // ranks, device=DEV, dtype=torch.bfloat16) for _ in range(ranks)]
+    for f in fab:
+        f.begin_step(m)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    t = [[], [], []]
+    for it in range(iters + 2):
+        s = it & 1
+        ev[0].record()
+        for f in fab:
+            f.gemm_scatter(attn[f.rank], o_w[f.rank], s)
+        ev[1].record()
+        for f in fab:
+            f.reduce_norm(norm, s, hidden, 1e-6)
+        ev[2].record()
+        for f in fab:
+            f.gemm_gather(gu_w[f.rank], gu[f.rank], s)
+        ev[3].record()
+        torch.cuda.synchronize()
+        fab[0].ws.check_status()
+        if it >= 2:
+            for j in range(3):
+                t[j].append(ev[j].elapsed_time(ev[j + 1]) / ranks)
+    med = [sorted(x)[len(x) // 2] * 1e3 for x in t]
+    return {"op": "fused_tp_site[emulated ranks on one device]", "ranks": ranks, "m": m, "hidden": hidden, "inter": inter,
+            "gemm_scatter_us": round(med[0], 1), "reduce_norm_us": round(med[1], 1), "gemm_gather_us": round(med[2], 1),
+            "timing": "eager launches, per rank (sum over ranks / ranks)"}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn", "sweep"])
+    ap.add_argument("op", choices=["gemm", "attn", "sweep", "fused-tp"])
+    ap.add_argument("--ranks", type=int, default=4)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--inter", type=int, default=12288)
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -151,6 +197,8 @@ def main() -> None:
     a = ap.parse_args()
     if a.op == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.splits or None, a.iters, a.fmt, a.kernel)))
+    elif a.op == "fused-tp":
+        print(json.dumps(bench_fused_tp(a.ranks, a.m, a.hidden, a.inter, a.iters)))
     elif a.op == "attn":
         print(json.dumps(bench_attn(a.rows, a.ctx, a.hq, a.hkv, a.kbits, a.vbits, max(1, a.splits), a.iters)))
     else:
