@@ -67,7 +67,39 @@ struct SampleParams {
   float* out_value;             // [rows] raw logit of the chosen token (or null); used by the vocab-sharded merge
   int vocab, ld, mask_words;
   int id_offset;                // added to every emitted id (first vocabulary id of this shard)
+  // vocab-sharded sampling: instead of sampling, emit the row's K best (value, global id) pairs, padded to
+  // kMaxTopK with (-inf, INT_MAX); cb_sample_merge draws from the union over the ranks
+  float* cand_val;              // [rows, kMaxTopK] or null
+  int* cand_id;                 // [rows, kMaxTopK]
 };
+
+// The draw itself, shared by the one-GPU sampler and the merge of rank-local candidates: `top` holds K
+// candidates in (value desc, id asc) order.
+struct Draw {
+  int id;
+  float logprob, value;
+};
+__device__ __forceinline__ Draw draw_from_top(const Cand* top, int K, float temp, float tp, unsigned long long seed,
+                                              unsigned long long ctr) {
+  if (K == 0) return Draw{0, 0.f, -INFINITY};
+  if (temp <= 0.f || K == 1) return Draw{top[0].i, 0.f, top[0].v};
+  float probs[kMaxTopK];
+  const float inv_t = 1.f / temp;
+  float sum = 0.f;
+  for (int k = 0; k < K; ++k) { probs[k] = __expf((top[k].v - top[0].v) * inv_t); sum += probs[k]; }
+  int keep = K;
+  if (tp < 1.f) {
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) { acc += probs[k] / sum; if (acc >= tp) { keep = k + 1; break; } }
+  }
+  float ksum = 0.f;
+  for (int k = 0; k < keep; ++k) ksum += probs[k];
+  const float u = philox_uniform(seed, ctr) * ksum;
+  float acc = 0.f;
+  int pick = keep - 1;
+  for (int k = 0; k < keep; ++k) { acc += probs[k]; if (u < acc) { pick = k; break; } }
+  return Draw{top[pick].i, __logf(probs[pick] / ksum), top[pick].v};
+}
 
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const SampleParams p) {
@@ -103,37 +135,80 @@ sample_kernel(const SampleParams p) {
   }
   __syncthreads();
   if (threadIdx.x != 0) return;
-  if (K == 0) {
-    p.out_ids[row] = p.id_offset;
-    if (p.out_logprob) p.out_logprob[row] = 0.f;
-    if (p.out_value) p.out_value[row] = -INFINITY;
+  if (p.cand_val) {
+    for (int k = 0; k < kMaxTopK; ++k) {
+      p.cand_val[row * kMaxTopK + k] = k < K ? top[k].v : -INFINITY;
+      p.cand_id[row * kMaxTopK + k] = k < K ? top[k].i + p.id_offset : 0x7fffffff;
+    }
     return;
   }
-  if (temp <= 0.f || K == 1) {
-    p.out_ids[row] = top[0].i + p.id_offset;
-    if (p.out_logprob) p.out_logprob[row] = 0.f;
-    if (p.out_value) p.out_value[row] = top[0].v;
-    return;
+  const Draw d = draw_from_top(top, K, temp, p.top_p ? p.top_p[row] : 1.f, p.seeds ? p.seeds[row] : 0ull,
+                               p.counters ? p.counters[row] : 0ull);
+  p.out_ids[row] = d.id + p.id_offset;
+  if (p.out_logprob) p.out_logprob[row] = d.logprob;
+  if (p.out_value) p.out_value[row] = d.value;
+}
+
+// Merge of the ranks' candidates (vocab-sharded sampling; reference: generation/tp_sampling.py:681
+// sample_sharded_broadcast_tp): the global top-K of a row is contained in the union of the local top-Ks, so the
+// draw over the merged set equals the draw over the full vocabulary.  Every rank runs this on the same gathered
+// data with the same Philox stream and gets the same token: no broadcast.  One warp per row.
+__global__ void __launch_bounds__(128)
+sample_merge_kernel(const float* cand_val, const int* cand_id, int sources, long long source_stride, int rows,
+                    const float* temperature, const float* top_p, const int* top_k, const unsigned long long* seeds,
+                    const unsigned long long* counters, int* out_ids, float* out_logprob) {
+  __shared__ Cand tops[4][kMaxTopK];
+  const int wrp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + wrp;
+  if (row >= rows) return;
+  const float temp = temperature ? temperature[row] : 0.f;
+  int K = 1;
+  if (temp > 0.f) {
+    K = top_k ? top_k[row] : 0;
+    if (K <= 0 || K > kMaxTopK) K = kMaxTopK;
   }
-  float probs[kMaxTopK];
-  const float inv_t = 1.f / temp;
-  float sum = 0.f;
-  for (int k = 0; k < K; ++k) { probs[k] = __expf((top[k].v - top[0].v) * inv_t); sum += probs[k]; }
-  const float tp = p.top_p ? p.top_p[row] : 1.f;
-  int keep = K;
-  if (tp < 1.f) {
-    float acc = 0.f;
-    for (int k = 0; k < K; ++k) { acc += probs[k] / sum; if (acc >= tp) { keep = k + 1; break; } }
+  // lane l holds candidates l, l + 32, ... of the sources x kMaxTopK pool (<= 8 x 20 = 160 -> 5 per lane)
+  Cand mine[5];
+  const int pool = sources * kMaxTopK;
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    const int c = lane + 32 * j;
+    mine[j] = Cand{-INFINITY, 0x7fffffff};
+    if (c < pool) {
+      const int src = c / kMaxTopK, k = c - src * kMaxTopK;
+      const long long off = static_cast<long long>(src) * source_stride + static_cast<long long>(row) * kMaxTopK + k;
+      mine[j] = Cand{__ldcg(cand_val + off), __ldcg(cand_id + off)};
+    }
   }
-  float ksum = 0.f;
-  for (int k = 0; k < keep; ++k) ksum += probs[k];
-  const float u = philox_uniform(p.seeds ? p.seeds[row] : 0ull, p.counters ? p.counters[row] : 0ull) * ksum;
-  float acc = 0.f;
-  int pick = keep - 1;
-  for (int k = 0; k < keep; ++k) { acc += probs[k]; if (u < acc) { pick = k; break; } }
-  p.out_ids[row] = top[pick].i + p.id_offset;
-  if (p.out_logprob) p.out_logprob[row] = __logf(probs[pick] / ksum);
-  if (p.out_value) p.out_value[row] = top[pick].v;
+  int found = 0;
+  for (int r = 0; r < K; ++r) {
+    Cand best{-INFINITY, 0x7fffffff};
+    int bj = -1;
+#pragma unroll
+    for (int j = 0; j < 5; ++j)
+      if (mine[j].i != 0x7fffffff && better(mine[j].v, mine[j].i, best.v, best.i)) { best = mine[j]; bj = j; }
+    Cand w = best;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, w.v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, w.i, o);
+      if (better(ov, oi, w.v, w.i)) { w.v = ov; w.i = oi; }
+    }
+    if (w.i == 0x7fffffff) break;                        // pool exhausted (uniform over the warp)
+    if (bj >= 0 && best.i == w.i) {                      // ids are unique across shards: exactly one lane owns it
+#pragma unroll
+      for (int j = 0; j < 5; ++j)
+        if (j == bj) mine[j].i = 0x7fffffff;
+    }
+    if (lane == 0) tops[wrp][r] = w;
+    ++found;
+  }
+  __syncwarp();
+  if (lane != 0) return;
+  const Draw d = draw_from_top(tops[wrp], found, temp, top_p ? top_p[row] : 1.f, seeds ? seeds[row] : 0ull,
+                               counters ? counters[row] : 0ull);
+  out_ids[row] = d.id;
+  if (out_logprob) out_logprob[row] = d.logprob;
 }
 
 // Greedy speculative verification: per request, row r holds the target's choice
@@ -174,7 +249,43 @@ int cb_sample(const void* logits, int ld, const void* mask, int mask_words, cons
   p.out_value = static_cast<float*>(out_value);
   p.id_offset = id_offset;
   p.vocab = vocab; p.ld = ld; p.mask_words = mask_words;
+  p.cand_val = nullptr;
+  p.cand_id = nullptr;
   sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Rank-local half of vocab-sharded sampling: the row's best candidates (20 slots per row, see SampleParams).
+int cb_sample_candidates(const void* logits, int ld, const void* mask, int mask_words, const void* temperature,
+                         const void* top_k, void* cand_val, void* cand_id, int id_offset, int rows, int vocab,
+                         void* stream) {
+  using namespace cb;
+  if (rows <= 0) return 0;
+  SampleParams p{};
+  p.logits = static_cast<const __nv_bfloat16*>(logits);
+  p.mask = static_cast<const uint32_t*>(mask);
+  p.temperature = static_cast<const float*>(temperature);
+  p.top_k = static_cast<const int*>(top_k);
+  p.id_offset = id_offset;
+  p.vocab = vocab; p.ld = ld; p.mask_words = mask_words;
+  p.cand_val = static_cast<float*>(cand_val);
+  p.cand_id = static_cast<int*>(cand_id);
+  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Merge `sources` candidate sets (source s at cand + s * source_stride elements, [rows, 20] each) and draw.
+int cb_sample_merge(const void* cand_val, const void* cand_id, int sources, long long source_stride, int rows,
+                    const void* temperature, const void* top_p, const void* top_k, const void* seeds,
+                    const void* counters, void* out_ids, void* out_logprob, void* stream) {
+  using namespace cb;
+  if (rows <= 0) return 0;
+  if (sources < 1 || sources > 8) return -10;
+  sample_merge_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(cand_val), static_cast<const int*>(cand_id), sources, source_stride, rows,
+      static_cast<const float*>(temperature), static_cast<const float*>(top_p), static_cast<const int*>(top_k),
+      static_cast<const unsigned long long*>(seeds), static_cast<const unsigned long long*>(counters),
+      static_cast<int*>(out_ids), static_cast<float*>(out_logprob));
   return static_cast<int>(cudaGetLastError());
 }
 

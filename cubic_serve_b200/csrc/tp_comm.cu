@@ -242,9 +242,71 @@ tp_argmax_merge_kernel(const ArgmaxMergeParams p) {
   }
 }
 
+// Small all-gather by push: every rank stores `segments` runs of `seg_words` 32-bit words (run g starts at
+// local + g * seg_stride) into slot `rank` of every rank's exchange area (same inner layout), raises the peers'
+// counters and waits for all of theirs, so that when the kernel ends the local area holds every rank's data.
+// Used for the candidates of vocab-sharded sampling; like the greedy merge it is also a step barrier.
+struct ExchangeParams {
+  const uint32_t* local;
+  uint32_t* area_peer[kMaxRanksTp];   // every rank's area [size][area_words]
+  uint32_t* flag_peer[kMaxRanksTp];   // every rank's counters [size]
+  const uint32_t* my_flag;
+  uint32_t* my_state;                 // {epoch}
+  uint32_t* status;
+  int rank, size, segments, seg_words, seg_stride, area_words;
+};
+
+__global__ void __launch_bounds__(256)
+tp_exchange_kernel(const ExchangeParams p) {
+  __shared__ uint32_t ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  for (int g = 0; g < p.segments; ++g) {
+    for (int i = threadIdx.x; i < p.seg_words; i += blockDim.x) {
+      const uint32_t v = p.local[g * p.seg_stride + i];
+      for (int r = 0; r < p.size; ++r)
+        p.area_peer[r][static_cast<size_t>(p.rank) * p.area_words + g * p.seg_stride + i] = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < p.size) {
+    red_rel_sys_add(p.flag_peer[threadIdx.x] + p.rank, 1u);      // release at system scope, cumulative over the CTA
+    if (!wait_ge(p.my_flag + threadIdx.x, p.my_state[0] + 1u)) ok_flag = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!ok_flag) atomicExch(p.status, static_cast<uint32_t>(kErrFlagTimeout));
+    atomicAdd(&p.my_state[0], 1u);
+  }
+}
+
 }  // namespace cb
 
 extern "C" {
+
+struct CbExchange {
+  const void* local; void* area_peer[8]; void* flag_peer[8]; const void* my_flag; void* my_state; void* status;
+  int rank, size, segments, seg_words, seg_stride, area_words;
+};
+
+int cb_tp_exchange(const CbExchange* a, void* stream) {
+  using namespace cb;
+  if (a->size < 1 || a->size > kMaxRanksTp || a->segments < 1 || a->seg_words < 0 ||
+      (a->segments - 1) * a->seg_stride + a->seg_words > a->area_words)
+    return -10;
+  ExchangeParams p;
+  p.local = static_cast<const uint32_t*>(a->local);
+  for (int r = 0; r < a->size; ++r) {
+    p.area_peer[r] = static_cast<uint32_t*>(a->area_peer[r]);
+    p.flag_peer[r] = static_cast<uint32_t*>(a->flag_peer[r]);
+  }
+  p.my_flag = static_cast<const uint32_t*>(a->my_flag);
+  p.my_state = static_cast<uint32_t*>(a->my_state);
+  p.status = static_cast<uint32_t*>(a->status);
+  p.rank = a->rank; p.size = a->size; p.segments = a->segments; p.seg_words = a->seg_words;
+  p.seg_stride = a->seg_stride; p.area_words = a->area_words;
+  tp_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
 
 struct CbReduceNorm {
   const void* recv; const void* rs_flag; void* rs_state; unsigned rs_expected;

@@ -351,6 +351,16 @@ class DecoderRunner:
         self.launches_per_step = n
         return s
 
+    def _dummy_val(self) -> torch.Tensor:
+        if not hasattr(self, "_cand_val"):
+            self._cand_val = torch.zeros(1, dtype=torch.float32, device=self.device)
+            self._cand_id = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._cand_val
+
+    def _dummy_id(self) -> torch.Tensor:
+        self._dummy_val()
+        return self._cand_id
+
     def run_step(self, b: StepBatch, d: dict, logits_buf: torch.Tensor, out_ids: torch.Tensor) -> None:
         """Whole step: layers, final norm, lm_head, sampling (and the cross-rank token agreement under TP)."""
         R = b.num_logit_rows
@@ -385,17 +395,15 @@ class DecoderRunner:
             if pp is not None:
                 pp.share_token_ids(out_ids[:R])
             return
-        # vocab-sharded: local greedy candidate per row, then agreement across ranks
-        if not hasattr(self, "_cand_val"):
-            self._cand_val = torch.empty(logits_buf.shape[0], dtype=torch.float32, device=self.device)
-            self._cand_id = torch.empty(logits_buf.shape[0], dtype=torch.int32, device=self.device)
-        if R:
-            K.sample(logits, self._cand_id[:R], vocab=logits.shape[1], out_value=self._cand_val[:R],
-                     id_offset=self.w.vocab_start, mask=mask)
+        # vocab-sharded: rank-local candidates (one for a greedy row, up to 20 for a sampled one), exchanged
+        # between the ranks, then the same merge + draw on every rank
         if fused:
-            self.tp.fused.argmax_merge(self._cand_val, self._cand_id, out_ids, R)
+            if R:
+                self.tp.fused.sample_sharded(logits, R, out_ids, d, self.w.vocab_start, mask)
+            else:
+                self.tp.fused.argmax_merge(self._dummy_val(), self._dummy_id(), out_ids, 0)   # step barrier only
         elif R:
-            self.tp.argmax_merge_nccl(self._cand_val, self._cand_id, out_ids, R)
-        self.launches_per_step += 2
+            self.tp.sample_sharded_nccl(logits, R, out_ids, d, self.w.vocab_start, mask)
+        self.launches_per_step += 3
         if pp is not None and R:
             pp.share_token_ids(out_ids[:R])

@@ -237,6 +237,33 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: torch.Tenso
     return out_ids
 
 
+SAMPLE_CANDIDATES = 20      # candidate slots per row of vocab-sharded sampling (= the largest top-k)
+
+
+def sample_candidates(logits: torch.Tensor, cand_val: torch.Tensor, cand_id: torch.Tensor,
+                      temperature: torch.Tensor | None = None, top_k: torch.Tensor | None = None,
+                      mask: torch.Tensor | None = None, vocab: int | None = None, id_offset: int = 0) -> None:
+    """Rank-local half of vocab-sharded sampling: the best (logit, global id) pairs of every row, ``[rows, 20]``."""
+    rows = logits.shape[0]
+    code = native.lib().cb_sample_candidates(logits.data_ptr(), logits.stride(0), _ptr(mask),
+                                             0 if mask is None else mask.stride(0), _ptr(temperature), _ptr(top_k),
+                                             cand_val.data_ptr(), cand_id.data_ptr(), int(id_offset), rows,
+                                             vocab or logits.shape[1], _stream())
+    native.check(code, "cb_sample_candidates")
+
+
+def sample_merge(cand_val: torch.Tensor, cand_id: torch.Tensor, sources: int, source_stride: int, rows: int,
+                 out_ids: torch.Tensor, temperature: torch.Tensor | None = None, top_p: torch.Tensor | None = None,
+                 top_k: torch.Tensor | None = None, seeds: torch.Tensor | None = None,
+                 counters: torch.Tensor | None = None, out_logprob: torch.Tensor | None = None) -> torch.Tensor:
+    """Draw every row's token from the union of ``sources`` candidate sets (same result on every rank)."""
+    code = native.lib().cb_sample_merge(cand_val.data_ptr(), cand_id.data_ptr(), sources, source_stride, rows,
+                                        _ptr(temperature), _ptr(top_p), _ptr(top_k), _ptr(seeds), _ptr(counters),
+                                        out_ids.data_ptr(), _ptr(out_logprob), _stream())
+    native.check(code, "cb_sample_merge")
+    return out_ids
+
+
 def verify_greedy(target_ids: torch.Tensor, draft_ids: torch.Tensor, depth: torch.Tensor, max_depth: int,
                   accepted: torch.Tensor, bonus: torch.Tensor, forced_reject_at: torch.Tensor | None = None) -> None:
     code = native.lib().cb_verify_greedy(target_ids.data_ptr(), draft_ids.data_ptr(), depth.data_ptr(), max_depth,

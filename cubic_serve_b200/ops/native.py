@@ -124,6 +124,12 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_sample.restype = i
     l.cb_verify_greedy.argtypes = [vp, vp, vp, i, vp, vp, vp, i, vp]
     l.cb_verify_greedy.restype = i
+    l.cb_sample_candidates.argtypes = [vp, i, vp, i, vp, vp, vp, vp, i, i, i, vp]
+    l.cb_sample_candidates.restype = i
+    l.cb_sample_merge.argtypes = [vp, vp, i, ll, i, vp, vp, vp, vp, vp, vp, vp, vp]
+    l.cb_sample_merge.restype = i
+    l.cb_tp_exchange.argtypes = [vp, vp]
+    l.cb_tp_exchange.restype = i
     l.cb_wq_gemm_tp.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, vp, vp, vp, vp]
     l.cb_wq_gemm_tp.restype = i
     l.cb_wq_gemm_sk.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, ll, vp, vp, vp, vp]
@@ -167,6 +173,14 @@ class ReduceNormStruct(ctypes.Structure):
                 ("rank", ctypes.c_int), ("size", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("H", ctypes.c_int),
                 ("M", ctypes.c_int), ("eps", ctypes.c_float), ("zero_centered", ctypes.c_int),
                 ("local_only", ctypes.c_int)]
+
+
+class ExchangeStruct(ctypes.Structure):
+    """Mirror of ``CbExchange`` in ``csrc/tp_comm.cu``."""
+    _fields_ = [("local", ctypes.c_void_p), ("area_peer", ctypes.c_void_p * 8), ("flag_peer", ctypes.c_void_p * 8),
+                ("my_flag", ctypes.c_void_p), ("my_state", ctypes.c_void_p), ("status", ctypes.c_void_p),
+                ("rank", ctypes.c_int), ("size", ctypes.c_int), ("segments", ctypes.c_int), ("seg_words", ctypes.c_int),
+                ("seg_stride", ctypes.c_int), ("area_words", ctypes.c_int)]
 
 
 class EpDispatchStruct(ctypes.Structure):

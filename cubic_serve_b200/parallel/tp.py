@@ -27,7 +27,8 @@ from ..ops import native
 
 MODE_GATHER_WAIT = 1
 MODE_SCATTER_PUSH = 2
-FLAG_WORDS = 64          # per rank: [set(2)][kind(2: rs, ag)][8 sources] + argmax [8] + pad
+FLAG_WORDS = 64          # per rank: [set(2)][kind(2: rs, ag)][8 sources] + argmax [8] + candidates [8] + pad
+CAND = K.SAMPLE_CANDIDATES
 
 
 def rows_per_rank(m: int, size: int) -> int:
@@ -46,11 +47,13 @@ class TpBuffers:
     flags: torch.Tensor           # int32 [FLAG_WORDS]
     xchg_val: torch.Tensor        # fp32 [size, rows_max]
     xchg_id: torch.Tensor         # int32 [size, rows_max]
+    cand: torch.Tensor            # int32 [size, 2 * rows_max * CAND]  per source: values (fp32 bits) then ids
     recv_ptrs: list[int] = field(default_factory=list)
     xfull_ptrs: list[int] = field(default_factory=list)
     flags_ptrs: list[int] = field(default_factory=list)
     xval_ptrs: list[int] = field(default_factory=list)
     xid_ptrs: list[int] = field(default_factory=list)
+    cand_ptrs: list[int] = field(default_factory=list)
 
 
 def _alloc_local(rank: int, size: int, hidden: int, max_tokens: int, rows_max: int, device, alloc) -> TpBuffers:
@@ -63,6 +66,7 @@ def _alloc_local(rank: int, size: int, hidden: int, max_tokens: int, rows_max: i
         flags=alloc((FLAG_WORDS,), torch.int32),
         xchg_val=alloc((size, rows_max), torch.float32),
         xchg_id=alloc((size, rows_max), torch.int32),
+        cand=alloc((size, 2 * rows_max * CAND), torch.int32),
     )
 
 
@@ -76,6 +80,7 @@ def local_fabric(size: int, hidden: int, max_tokens: int, rows_max: int, device)
         b.flags_ptrs = [o.flags.data_ptr() for o in bufs]
         b.xval_ptrs = [o.xchg_val.data_ptr() for o in bufs]
         b.xid_ptrs = [o.xchg_id.data_ptr() for o in bufs]
+        b.cand_ptrs = [o.cand.data_ptr() for o in bufs]
     return bufs
 
 
@@ -97,7 +102,7 @@ def symmetric_buffers(group, hidden: int, max_tokens: int, rows_max: int, device
     torch.cuda.synchronize(device)
     dist.barrier(group)
     ptrs = [[int(p) for p in h.buffer_ptrs] for _, h in handles]
-    b.recv_ptrs, b.xfull_ptrs, b.flags_ptrs, b.xval_ptrs, b.xid_ptrs = ptrs
+    b.recv_ptrs, b.xfull_ptrs, b.flags_ptrs, b.xval_ptrs, b.xid_ptrs, b.cand_ptrs = ptrs
     b._handles = handles  # keep the mappings alive
     return b
 
@@ -116,6 +121,8 @@ class FusedTp:
         self.rpr = self.rpr_max
         self.m = 0
         self._links: dict = {}
+        self.rows_max = bufs.xchg_val.shape[1]
+        self.cand_local = torch.zeros(2, self.rows_max, CAND, dtype=torch.int32, device=device)
 
     # ---------------------------------------------------------------- helpers
     def begin_step(self, m: int) -> None:
@@ -207,6 +214,35 @@ class FusedTp:
         native.check(native.lib().cb_tp_argmax_merge(ctypes.byref(a), K._stream()), "cb_tp_argmax_merge")
 
 
+    def sample_sharded(self, logits: torch.Tensor, rows: int, out_ids: torch.Tensor, d: dict, vocab_start: int,
+                       mask: torch.Tensor | None = None) -> None:
+        """Vocab-sharded sampling: local candidates -> push to every rank -> identical merge + draw everywhere.
+
+        Replaces the reference's gather-to-root + broadcast (``generation/tp_sampling.py:681``): every rank runs
+        the same draw on the same gathered candidates, so no broadcast is needed; the exchange doubles as the
+        end-of-step barrier.  Greedy rows carry one candidate, sampled rows up to 20.
+        """
+        val, ids = self.cand_local[0].view(torch.float32), self.cand_local[1]
+        K.sample_candidates(logits, val, ids, temperature=d["temperature"][:rows], top_k=d["top_k"][:rows], mask=mask,
+                            vocab=logits.shape[1], id_offset=vocab_start)
+        a = native.ExchangeStruct()
+        a.local = self.cand_local.data_ptr()
+        off = 40 * 4
+        for r in range(self.size):
+            a.area_peer[r] = self.b.cand_ptrs[r]
+            a.flag_peer[r] = self.b.flags_ptrs[r] + off
+        a.my_flag = self.b.flags.data_ptr() + off
+        a.my_state = self.state.data_ptr() + 10 * 4
+        a.status = self.ws.status.data_ptr()
+        a.rank, a.size, a.segments = self.rank, self.size, 2
+        a.seg_words, a.seg_stride, a.area_words = rows * CAND, self.rows_max * CAND, 2 * self.rows_max * CAND
+        native.check(native.lib().cb_tp_exchange(ctypes.byref(a), K._stream()), "cb_tp_exchange")
+        area = self.b.cand
+        K.sample_merge(area.view(torch.float32), area.view(-1)[self.rows_max * CAND:], self.size, area.stride(0), rows,
+                       out_ids, temperature=d["temperature"][:rows], top_p=d["top_p"][:rows], top_k=d["top_k"][:rows],
+                       seeds=d["seeds"][:rows], counters=d["draws"][:rows])
+
+
 class TensorParallel:
     """What the decoder runner sees: ``size``, ``rank``, ``mode`` and the collective entry points."""
 
@@ -227,6 +263,22 @@ class TensorParallel:
     def all_reduce(self, t: torch.Tensor) -> None:
         import torch.distributed as dist
         dist.all_reduce(t, group=self.group)
+
+    def sample_sharded_nccl(self, logits: torch.Tensor, rows: int, out_ids: torch.Tensor, d: dict, vocab_start: int,
+                            mask: torch.Tensor | None = None) -> None:
+        """Baseline of ``FusedTp.sample_sharded``: NCCL all-gather of the candidates, same merge kernel."""
+        import torch.distributed as dist
+        if not hasattr(self, "_cand_local"):
+            self._cand_local = torch.zeros(2, self.rows_max, CAND, dtype=torch.int32, device=self.device)
+            self._cand_all = torch.zeros(self.size, 2, self.rows_max, CAND, dtype=torch.int32, device=self.device)
+        val, ids = self._cand_local[0].view(torch.float32), self._cand_local[1]
+        K.sample_candidates(logits, val, ids, temperature=d["temperature"][:rows], top_k=d["top_k"][:rows], mask=mask,
+                            vocab=logits.shape[1], id_offset=vocab_start)
+        dist.all_gather_into_tensor(self._cand_all, self._cand_local, group=self.group)
+        flat = self._cand_all.view(self.size, -1)
+        K.sample_merge(flat.view(torch.float32), flat.view(-1)[self.rows_max * CAND:], self.size, flat.stride(0), rows,
+                       out_ids, temperature=d["temperature"][:rows], top_p=d["top_p"][:rows], top_k=d["top_k"][:rows],
+                       seeds=d["seeds"][:rows], counters=d["draws"][:rows])
 
     def argmax_merge_nccl(self, local_val: torch.Tensor, local_id: torch.Tensor, out_id: torch.Tensor, rows: int) -> None:
         """Baseline: all_gather of (value, id) and a small torch reduction (reference ``tp_sampling.py:1225``)."""
