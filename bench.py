@@ -190,8 +190,10 @@ def main() -> None:
     sync()
     t0 = time.perf_counter()
     n_prefill_steps = 0
+    first_token_at: dict[str, float] = {}          # request id -> seconds from submission to its first token
     while any(r.remaining > 1 for r in eng.scheduler.running + eng.scheduler.waiting) or eng.scheduler.waiting:
-        eng.step()
+        for o in eng.step():
+            first_token_at.setdefault(o.request_id, time.perf_counter() - t0)
         n_prefill_steps += 1
     sync()
     prefill_s = time.perf_counter() - t0
@@ -239,6 +241,9 @@ def main() -> None:
                        "comm": (tp.mode if tp is not None else "none"), "cuda_graphs": True, "kv_cache": f"int{k_bits}/int{v_bits}",
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,
+                       # all C requests are submitted at t = 0: TTFT includes queueing behind earlier prefill chunks
+                       "ttft_p50_ms": round(1e3 * float(np.median(sorted(first_token_at.values()))), 1) if first_token_at else None,
+                       "tpot_p50_ms": round(float(np.median(ex.device_ms)) / max(1.0, emitted / (C * args.steps)), 3),
                        "weights_gb": round(weights.nbytes() / 1e9, 2),
                        **({"speculative": {"depth": args.spec_depth, "forced_acceptance": args.accept,
                                            "tokens_per_verify_step": round(emitted / (C * args.steps), 3),

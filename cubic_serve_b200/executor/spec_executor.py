@@ -84,14 +84,32 @@ class SpeculativeGpuExecutor(GpuExecutor):
         return self.out_host[:rows].numpy().copy()
 
     # ------------------------------------------------------- speculative round
-    def execute_speculative(self, segs: list[Segment]):
-        """``segs``: one decode segment per request (its root token).  Returns per request the emitted tokens."""
-        R, Kd = len(segs), self.speculative_depth
+    def execute_speculative(self, segs: list[Segment], depths: list[int] | None = None):
+        """``segs``: one decode segment per request (its root token).  Returns per request the emitted tokens.
+
+        ``depths`` (dynamic draft length, one entry per request, each <= the configured depth): the round runs
+        ``max(depths)`` proposal passes and a review of that length; a request with a smaller depth only has
+        that many of its drafts verified.  All zero = a plain decode step.
+        """
+        R = len(segs)
+        Kd = self.speculative_depth if depths is None else min(self.speculative_depth, max(depths, default=0))
+        if Kd == 0:
+            ids = self.execute(segs)
+            self.last_round = {"depth": 0, "accepted": [0] * R, "proposed": [0] * R, "proposal_ms": 0.0,
+                               "target_ms": self.device_ms[-1] if (self.timing and self.device_ms) else 0.0}
+            return [[int(t)] for t in ids]
+        per_req = [Kd] * R if depths is None else [min(int(d), Kd) for d in depths]
         r, dev = self.runner, self.device
         sl = torch.tensor([s.request_slot for s in segs], device=dev)
         launches = 0
+        # compact [R, Kd] / [R, Kd + 1] views: the verification kernel's row strides follow the round's depth
+        draft_ids = self.draft_ids.view(-1)[:R * Kd].view(R, Kd)
+        target_ids = self.target_ids.view(-1)[:R * (Kd + 1)].view(R, Kd + 1)
+        self.depth_t[:R].copy_(torch.tensor(per_req, dtype=torch.int32), non_blocking=True)
         with torch.cuda.stream(self.stream):
             ev0, ev1 = self._ev
+            if not hasattr(self, "_ev_mid"):
+                self._ev_mid = torch.cuda.Event(enable_timing=True)
             if self.timing:
                 ev0.record(self.stream)
             prev = self.last_hidden.index_select(0, sl)
@@ -102,14 +120,16 @@ class SpeculativeGpuExecutor(GpuExecutor):
                 b, _ = self._fill(step)
                 self.h2d_bytes_last = self.stage.upload()
                 if d > 0:
-                    self.stage.d["token_ids"][:R].copy_(self.draft_ids[:R, d - 1])
+                    self.stage.d["token_ids"][:R].copy_(draft_ids[:, d - 1])
                 hid = self.mtp.forward(b, prev)
                 lg = self.mtp.logits(hid, R, self.mtp_logits)
                 tmp = self.out_ids[:R]
                 K.sample(lg, tmp, vocab=lg.shape[1])
-                self.draft_ids[:R, d].copy_(tmp)
+                draft_ids[:, d].copy_(tmp)
                 prev = hid[:R].clone()
                 launches += self.mtp.launches + 4
+            if self.timing:
+                self._ev_mid.record(self.stream)
             # ---- target review over [root, d1 .. dK]
             review = [Segment(s.request_slot, [s.token_ids[0]] + [0] * Kd, s.start, s.pages, True, uid=s.uid) for s in segs]
             b, _ = self._fill(review)
@@ -118,13 +138,13 @@ class SpeculativeGpuExecutor(GpuExecutor):
             self.stage.h["temperature"][:T] = 0
             self.stage.upload()
             toks = torch.cat([torch.tensor([s.token_ids[0] for s in segs], dtype=torch.int32, device=dev)[:, None],
-                              self.draft_ids[:R]], 1).reshape(-1)
+                              draft_ids], 1).reshape(-1)
             self.stage.d["token_ids"][:T].copy_(toks)
             b.num_logit_rows = T
             hidden = r.forward_hidden(b)
             logits_buf = self._review_logits(T)
             logits = r.forward_logits(b, hidden, logits_buf)
-            tgt = self.target_ids[:R].view(-1)
+            tgt = target_ids.view(-1)
             K.sample(logits, tgt, vocab=logits.shape[1])
             launches += r.launches_per_step + 1
             # ---- verification
@@ -135,19 +155,21 @@ class SpeculativeGpuExecutor(GpuExecutor):
                 self.forced[:R].copy_(torch.from_numpy(first_fail), non_blocking=True)
                 forced = self.forced
                 # forced acceptance: the draft is *declared* equal to the target up to the drawn depth
-                agree = self.target_ids[:R, :Kd].clone()
+                agree = target_ids[:, :Kd].clone()
                 keep = torch.arange(Kd, device=dev)[None, :] < self.forced[:R, None]
-                self.draft_ids[:R] = torch.where(keep, agree, self.draft_ids[:R])
-            K.verify_greedy(self.target_ids, self.draft_ids, self.depth_t, Kd, self.accepted, self.bonus, forced)
+                draft_ids.copy_(torch.where(keep, agree, draft_ids))
+            K.verify_greedy(target_ids, draft_ids, self.depth_t[:R], Kd, self.accepted, self.bonus, forced)
             rows = torch.arange(R, device=dev) * (Kd + 1) + self.accepted[:R].long()
             self.last_hidden.index_copy_(0, sl, hidden.index_select(0, rows))
             if self.timing:
                 ev1.record(self.stream)
             acc = self.accepted[:R].cpu()
-            tg = self.target_ids[:R].cpu()
+            tg = target_ids.cpu()
             self.stream.synchronize()
+        prop_ms = tgt_ms = 0.0
         if self.timing:
             self.device_ms.append(ev0.elapsed_time(ev1))
+            prop_ms, tgt_ms = ev0.elapsed_time(self._ev_mid), self._ev_mid.elapsed_time(ev1)
         out = []
         for i in range(R):
             a = int(acc[i])
@@ -155,7 +177,9 @@ class SpeculativeGpuExecutor(GpuExecutor):
             self.stats["accepted"] += a
             self.stats["emitted"] += a + 1
         self.stats["rounds"] += 1
-        self.stats["proposed"] += R * Kd
+        self.stats["proposed"] += sum(per_req)
+        self.last_round = {"depth": Kd, "accepted": [int(a) for a in acc], "proposed": per_req, "proposal_ms": prop_ms,
+                           "target_ms": tgt_ms}
         self.kernel_launches_last = launches + 2
         self.d2h_bytes_last = R * (Kd + 2) * 4
         return out

@@ -45,6 +45,10 @@ class LLMEngine:
         self.scheduler = ContinuousScheduler(self.cfg, self.pool, self.prefix)
         self.scheduler.decode_lookahead = getattr(executor, "speculative_depth", 0)
         self.eos_token_id = eos_token_id
+        # dynamic draft length (reference: runtime/speculative.py DynamicDraftPlanner.plan): per-request acceptance
+        # history + measured round costs choose each request's draft length; off = the executor's fixed depth
+        self.draft_planner = None
+        self._draft_states: dict = {}
         vocab = getattr(getattr(executor, "cfg", None), "vocab_size", None) or getattr(executor, "vocab_size", 0)
         self._mask_words = -(-int(vocab) // 32) if vocab else 0
         self._ids = itertools.count()
@@ -117,7 +121,7 @@ class LLMEngine:
         constrained = any(s.mask is not None for s in segs)
         if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample for s in segs):
             # speculative round: every request gets its accepted drafts plus one bonus token
-            ids = self.executor.execute_speculative(segs)
+            ids = self._speculative_round(plan, segs, spec)
             self.spec_rounds = getattr(self, "spec_rounds", 0) + 1
         else:
             ids = self.executor.execute(segs) if segs else []
@@ -147,7 +151,37 @@ class LLMEngine:
                 outs.append(StepOutput(rid, tok, fin is not None and last, fin.finish_reason if (fin and last) else None))
             if fin is not None:
                 self.requests.pop(rid, None)
+                self._draft_states.pop(rid, None)
         return outs
+
+    def enable_dynamic_draft(self, config=None, graph_capacities: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512,
+                                                                                    1024, 2048, 4096)) -> None:
+        """Let the planner choose every request's draft length (up to the executor's depth) round by round."""
+        from .speculative import DraftPlanner, DraftPolicyConfig
+        self._draft_cfg = config or DraftPolicyConfig()
+        self.draft_planner = DraftPlanner(graph_capacities, self._draft_cfg)
+
+    def _speculative_round(self, plan: BatchPlan, segs: list, max_depth: int):
+        if self.draft_planner is None:
+            return self.executor.execute_speculative(segs)
+        from .speculative import RequestDraftState
+        rids = [s.request.request_id for s in plan.segments]
+        for rid in rids:
+            if rid not in self._draft_states:
+                self._draft_states[rid] = RequestDraftState(max_depth, max_depth, self._draft_cfg)
+        planned = {p.request_id: p.draft_tokens for p in self.draft_planner.plan({rid: self._draft_states[rid] for rid in rids})}
+        depths = [planned.get(rid, max_depth) for rid in rids]
+        ids = self.executor.execute_speculative(segs, depths)
+        info = getattr(self.executor, "last_round", None)
+        if info:
+            for rid, acc, prop in zip(rids, info["accepted"], info["proposed"]):
+                st = self._draft_states[rid]
+                if prop > 0 and not st.stopped:
+                    st.observe(min(acc, prop), prop)
+            if info["target_ms"]:
+                self.draft_planner.observe_round(sum(p + 1 for p in info["proposed"]), info["target_ms"], len(rids),
+                                                 info["proposal_ms"], info["depth"])
+        return ids
 
     def generate(self, prompts: list[list[int]], sampling: SamplingParams | None = None) -> list[list[int]]:
         """Blocking helper: run all prompts to completion, return the generated ids per prompt."""

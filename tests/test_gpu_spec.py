@@ -59,3 +59,24 @@ def test_forced_acceptance_rate_and_tokens_per_round():
     per_round = ex.stats["emitted"] / (ex.stats["proposed"] / 4)      # tokens per request and verify step
     # first-failure model with p = 0.7 and depth 4: E[accepted] = p + p^2 + p^3 + p^4 = 1.77 (about 140 samples here)
     assert 0.3 < rate < 0.6 and 2.0 < per_round < 3.4, (rate, per_round)
+
+
+def test_dynamic_draft_length_stays_lossless_and_adapts():
+    """With the planner on, random weights (drafts almost never match) drive every request's draft length down
+    one level per decision boundary until drafting stops; the emitted tokens stay those of plain greedy decoding."""
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    from cubic_serve_b200.runtime.speculative import DraftPolicyConfig
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (21, 35, 50)]
+    eng, ex, runner = _build(0)
+    plain = eng.generate(prompts, SamplingParams(max_tokens=40, ignore_eos=True))
+    eng2, ex2, runner2 = _build(3)
+    ex2.timing = True
+    eng2.enable_dynamic_draft(DraftPolicyConfig(decision_tokens=2, decision_min_rounds=2))
+    spec = eng2.generate(prompts, SamplingParams(max_tokens=40, ignore_eos=True))
+    runner2.ws.check_status()
+    agree = np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)])
+    assert all(len(o) == 40 for o in spec) and agree >= 0.9
+    # fewer proposals than the fixed depth would have made: the planner shortened / stopped the drafts
+    assert ex2.stats["proposed"] < ex2.stats["rounds"] * 3 * len(prompts)
+    assert eng2.pool.num_used == 0

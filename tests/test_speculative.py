@@ -86,3 +86,44 @@ def test_planner_prefers_drafting_when_cheap_and_stops_when_useless():
     p2.proposal_cost.observe(8, 0.01)
     assert p2.best_uniform_k(bad, 1) == 1
     assert DraftPlanner((8,)).best_uniform_k(good, 4) == 4                    # no cost data yet: keep the maximum
+
+
+def test_engine_round_loop_uses_planned_depths():
+    """LLMEngine asks the planner for every request's draft length, passes them to the executor, and feeds the
+    acceptance back; with drafts that never match the lengths shrink to zero and decoding continues."""
+    import numpy as np
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+
+    class FakeSpec:
+        speculative_depth = 3
+        vocab_size = 64
+
+        def __init__(self):
+            self.seen = []
+            self.last_round = None
+
+        def copy_pages(self, pairs):
+            pass
+
+        def execute(self, segs):
+            return np.asarray([7 for s in segs if s.sample], dtype=np.int32)
+
+        def execute_speculative(self, segs, depths=None):
+            depths = depths or [self.speculative_depth] * len(segs)
+            self.seen.append(list(depths))
+            self.last_round = {"depth": max(depths), "accepted": [0] * len(segs), "proposed": list(depths),
+                               "proposal_ms": 1.0 * max(depths), "target_ms": 5.0}
+            return [[9] for _ in segs]                     # nothing accepted: only the bonus token
+
+    ex = FakeSpec()
+    eng = LLMEngine(ex, num_pages=64, scheduler_config=SchedulerConfig(max_running_requests=4, max_model_len=256,
+                                                                       enable_prefix_cache=False))
+    eng.enable_dynamic_draft(DraftPolicyConfig(decision_tokens=2, decision_min_rounds=2))
+    out = eng.generate([[1, 2, 3], [4, 5, 6, 7]], SamplingParams(max_tokens=30, ignore_eos=True))
+    assert all(len(o) == 30 for o in out)
+    assert ex.seen[0] == [3, 3]
+    assert max(ex.seen[-1]) < 3                             # shortened
+    flat = [d for round_ in ex.seen for d in round_]
+    assert all(a >= b for a, b in zip([r[0] for r in ex.seen], [r[0] for r in ex.seen][1:]))   # monotone, one level a time
+    assert set(flat) <= {0, 1, 2, 3}
