@@ -82,12 +82,28 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         pages = plan_kv_pages(free, int(args.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, 1, k_bits, v_bits, max_len,
                               args.max_running_requests)
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits)
-        executor = GpuExecutor(runner, max_rows=args.max_running_requests, max_prefill_tokens=args.token_budget,
-                               max_model_len=max_len)
-        caps = executor.capture_decode_graphs()
-        log.info("captured decode graphs for capacities %s; %d KV pages", caps, pages)
+        depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None else 0
+        if depth:
+            # MTP speculative decoding (--speculative-config): draft head + review rounds instead of graph decode
+            from ..executor.spec_executor import SpeculativeGpuExecutor
+            from ..models.mtp import MtpRunner, random_mtp_weights
+            if ck is not None:
+                raise SystemExit("this checkpoint carries no MTP head weights; speculative decoding serves "
+                                 "random:<config> models only")
+            mtp = MtpRunner(runner, random_mtp_weights(cfg, dev, args.seed + 1))
+            executor = SpeculativeGpuExecutor(runner, mtp, depth, max_rows=args.max_running_requests,
+                                              max_prefill_tokens=args.token_budget, max_model_len=max_len)
+            log.info("MTP speculative decoding: depth %d, %s draft length; %d KV pages", depth, spec.mode, pages)
+        else:
+            executor = GpuExecutor(runner, max_rows=args.max_running_requests, max_prefill_tokens=args.token_budget,
+                                   max_model_len=max_len)
+            caps = executor.capture_decode_graphs()
+            log.info("captured decode graphs for capacities %s; %d KV pages", caps, pages)
     tok = _tokenizer_for(model, cfg.vocab_size)
     engine = LLMEngine(executor, num_pages=pages, scheduler_config=sched, eos_token_id=getattr(tok, "eos_token_id", None))
+    if spec is not None and getattr(spec, "mode", "fixed") == "dynamic" and getattr(executor, "speculative_depth", 0):
+        from .speculative import DraftPolicyConfig
+        engine.enable_dynamic_draft(DraftPolicyConfig.from_dict(spec.policy) if spec.policy else None)
     backend = TokenChatBackend(engine, tok, default_thinking=args.thinking)
     return backend, (args.served_model_name or cfg.name)
 
