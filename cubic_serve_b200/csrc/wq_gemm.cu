@@ -91,7 +91,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
-      mbar_init(smem_u32(&ctl->ready[s]), kNumDequantWarps);
+      mbar_init(smem_u32(&ctl->ready[s]), kNumDequantWarps / 2);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     mbar_init(smem_u32(&ctl->acc_full), 1);
@@ -149,7 +149,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         int s = 0;
         uint32_t ph = 1;                      // second pass over the ring: wait for the first release
         for (int i = pre; i < iters; ++i) {
-          if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
+          if (!mbar_wait_park(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
           if (trace) trace[i * 8 + 0] = clock64();
           load_weights(i, s);
           load_x(i, s);
@@ -175,8 +175,8 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t accumulate = 0;
       for (int i = 0; i < iters && ok; ++i) {
         // decoded formats: `ready` implies `full` (the decode warps waited for the copies themselves)
-        ok = (FMT == kFmtBf16) ? mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag)
-                               : mbar_wait(smem_u32(&ctl->ready[s]), ph, abort_flag);
+        ok = (FMT == kFmtBf16) ? mbar_wait_park(smem_u32(&ctl->full[s]), ph, abort_flag)
+                               : mbar_wait_park(smem_u32(&ctl->ready[s]), ph, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (trace && leader) trace[i * 8 + 4] = clock64();
@@ -202,22 +202,30 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ------------------------------------------------- dequant + epilogue
     const int dq = threadIdx.x - 64;  // 0..511
-    const int r = dq & 127;           // row of the weight tile
-    const int part = dq >> 7;         // 16-column quarter of the k-block this thread decodes
-    const int h = part >> 1;          // 32-column half (metadata sub-block)
-    const int q = part & 1;           // 16-column quarter inside the half
     if (FMT != kFmtBf16) {
-      int s = 0;
+      // Two groups of eight warps take alternate k-blocks; a thread decodes 32 weights (one 16-byte code load,
+      // four 16-byte tile stores), so the per-k-block costs -- barrier wait, metadata, fence, arrive -- are
+      // paid by 8 warps instead of 16 (the decode is instruction-issue bound: see the stream-K profile).
+      const int grp = dq >> 8;          // decode group
+      const int dg = dq & 255;
+      const int r = dg & 127;           // row of the weight tile
+      const int h = dg >> 7;            // 32-column half of the k-block (one metadata sub-block)
+      const uint32_t code_off = static_cast<uint32_t>((h * 128 + r) * 16);
+      const uint32_t a_off = x_bytes + static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+      uint32_t chunk_off[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) chunk_off[j] = static_cast<uint32_t>(((h * 4 + j) ^ (r & 7)) << 4);
+      int s = grp;                      // S >= 2
       uint32_t ph = 0;
-      for (int i = 0; i < iters; ++i) {
-        if (!mbar_wait_relaxed(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
+      for (int i = grp; i < iters; i += 2) {
+        if (!mbar_wait_park(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
         if (trace && dq == 0) trace[i * 8 + 2] = clock64();
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint8_t* pk = st + x_bytes + kATileBytes;
-        const uint2 words = *reinterpret_cast<const uint2*>(pk + (h * 128 + r) * 16 + q * 8);
+        const uint4 words = *reinterpret_cast<const uint4*>(pk + code_off);
         const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
         // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
-        uint32_t c0, c1, c2, c1b = 0;
+        uint32_t c0, c1, c2;
         if (FMT == kFmtCubic4) {
           const uint32_t ab = meta[r], cz = meta[128 + r];
           c0 = bf2_dup(ab);        // A = s * a / 7
@@ -228,34 +236,34 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           c0 = bf2_dup(so);
           c1 = bf2_dup(so >> 16);
           c2 = 0;
-          c1b = c1;
         }
-        uint8_t* arow = st + x_bytes + (r >> 3) * 1024 + (r & 7) * 128;
-        const uint32_t wv[2] = {words.x, words.y};
-        uint32_t o[2][4];
+        uint32_t o[4][4];
+        if (FMT == kFmtNvfp4) {
+          // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
+          decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
+          decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
+          decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
+          decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+        } else {
+          decode8<FMT>(words.x, c0, c1, c2, o[0]);
+          decode8<FMT>(words.y, c0, c1, c2, o[1]);
+          decode8<FMT>(words.z, c0, c1, c2, o[2]);
+          decode8<FMT>(words.w, c0, c1, c2, o[3]);
+        }
+        uint8_t* arow = st + a_off;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          if (FMT == kFmtNvfp4) {
-            // columns 32h + 16q + 8j: the 16-column block scale is the low (q = 0) or high (q = 1) half
-            decode8<FMT>(wv[j], q ? c1b : c0, 0u, 0u, o[j]);
-          } else {
-            decode8<FMT>(wv[j], c0, c1, c2, o[j]);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int chunk = h * 4 + q * 2 + j;
-          *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
-        }
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(arow + chunk_off[j]) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->ready[s]));
         if (trace && dq == 0) trace[i * 8 + 3] = clock64();
-        if (++s == S) { s = 0; ph ^= 1u; }
+        s += 2;
+        if (s >= S) { s -= S; ph ^= 1u; }
       }
     }
     // epilogue: TMEM lane = output feature, column = batch row
-    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_t<200>(smem_u32(&ctl->acc_full), 0, abort_flag));
+    const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_full), 0, abort_flag));
     tc_fence_after();
     if (trace && dq == 0) trace[8 + 6] = clock64();
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
@@ -593,13 +601,17 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
     tw = tx;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (stream_k && !g_grouped.tiles) {
+  if (stream_k) {
     static int sms[64] = {0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -18;
     if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -18;
+    if (g_grouped.tiles) {
+      p.group_tiles = g_grouped.tiles;
+      p.group_code_stride = g_grouped.code_stride; p.group_meta_stride = g_grouped.meta_stride;
+    }
     return launch_streamk(fmt, tx, tw, p, static_cast<size_t>(workspace_bytes < 0 ? 0 : workspace_bytes), sms[dev],
-                          min_units, st);
+                          min_units, st, g_grouped.tiles ? g_grouped.max_items : 0);
   }
   const int n_tiles = (N + kTileN - 1) / kTileN;
   const int m_tiles = (M + p.mb - 1) / p.mb;
@@ -617,6 +629,11 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   }
 }
 
+static int g_grouped_persistent = 1;
+
+// 1 (default): grouped GEMMs run on the persistent kernel; 0: one CTA per (work item, weight tile).
+void cb_wq_gemm_grouped_mode(int persistent) { g_grouped_persistent = persistent; }
+
 int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                        float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
                        int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
@@ -629,8 +646,8 @@ int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const
   g_grouped.max_items = max_items;
   g_mb_hint = mb;
   // the tensor map spans all rows; every work item starts at its own row offset
-  const int rc = cb_wq_gemm_tp(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, total_rows, N, K, group_k, 1, nullptr,
-                               nullptr, status, stream, nullptr);
+  const int rc = wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, total_rows, N, K, group_k, 1, nullptr,
+                                  nullptr, status, stream, nullptr, g_grouped_persistent != 0, 0, 0);
   g_grouped.tiles = nullptr;
   g_mb_hint = 0;
   return rc;

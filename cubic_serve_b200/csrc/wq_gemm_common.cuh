@@ -203,6 +203,6 @@ static inline int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t ro
 // Persistent stream-K launcher (wq_gemm_sk.cu).  `workspace_bytes` bounds the fp32 partial-tile slots the
 // schedule may use; returns 0, a negative argument error or a positive cudaError_t.
 int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, size_t workspace_bytes,
-                   int sm_count, int min_units, cudaStream_t stream);
+                   int sm_count, int min_units, cudaStream_t stream, int grouped_max_items = 0);
 
 }  // namespace cb

@@ -72,7 +72,9 @@ struct SkIter {
   // (checked on the host); 64-bit divisions cost several hundred cycles each at kernel start
   uint32_t u, u_end, total;      // streamed units of this CTA, and of the whole launch
   int next_whole;
+  int tiles;                     // whole-tile bound: p.tiles, or (work items) x n_tiles in grouped mode
   __device__ __forceinline__ void init(const WqGemmParams& p, int cta) {
+    tiles = p.group_tiles ? p.group_tiles[0] * p.n_tiles : p.tiles;
     total = static_cast<uint32_t>(p.sk_tiles) * static_cast<uint32_t>(p.k_blocks);
     if (cta < p.sk_ctas) {
       u = total * static_cast<uint32_t>(cta) / static_cast<uint32_t>(p.sk_ctas);
@@ -82,7 +84,7 @@ struct SkIter {
     }
     next_whole = p.sk_tiles + cta;
   }
-  __device__ __forceinline__ bool has_more(const WqGemmParams& p) const { return u < u_end || next_whole < p.tiles; }
+  __device__ __forceinline__ bool has_more(const WqGemmParams&) const { return u < u_end || next_whole < tiles; }
   __device__ __forceinline__ bool next(const WqGemmParams& p, int cta, int grid, SkSegment& s) {
     if (u < u_end) {
       const uint32_t kbs = static_cast<uint32_t>(p.k_blocks);
@@ -101,7 +103,7 @@ struct SkIter {
       u = end;
       return true;
     }
-    if (next_whole < p.tiles) {
+    if (next_whole < tiles) {
       s.tile = next_whole;
       s.kb_lo = 0;
       s.kb_hi = p.k_blocks;
@@ -113,6 +115,28 @@ struct SkIter {
     return false;
   }
 };
+
+// Where a tile lives: first batch row, number of valid rows, weight tile index, and (grouped expert GEMMs) the
+// expert whose weights it uses.  Dense: tile = m_tile * n_tiles + n_tile.  Grouped: tile = item * n_tiles +
+// n_tile with item = {expert, first row, rows} from the device work list written by the MoE routing kernels.
+struct SkCoords {
+  int m0, rows, n_tile, expert;
+};
+__device__ __forceinline__ SkCoords sk_coords(const WqGemmParams& p, int tile) {
+  SkCoords c;
+  const int outer = tile / p.n_tiles;
+  c.n_tile = tile - outer * p.n_tiles;
+  if (p.group_tiles) {
+    c.expert = p.group_tiles[1 + 3 * outer];
+    c.m0 = p.group_tiles[2 + 3 * outer];
+    c.rows = p.group_tiles[3 + 3 * outer];
+  } else {
+    c.expert = 0;
+    c.m0 = outer * p.mb;
+    c.rows = min(p.mb, p.M - c.m0);
+  }
+  return c;
+}
 
 // Ring position: slot index and how many times the ring has wrapped.
 struct SkRing {
@@ -302,16 +326,15 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? static_cast<uint32_t>(kATileBytes) : 0u);
       SkRing r;
       while (ok && it.next(p, cta, grid, seg)) {
-        const int m_tile = seg.tile / p.n_tiles;
-        const int n_tile = seg.tile - m_tile * p.n_tiles;
-        const int m0 = m_tile * p.mb;
+        const SkCoords c = sk_coords(p, seg.tile);
+        const int w_row = c.expert * p.N + c.n_tile * kTileN;   // bf16 weights: experts stacked as [E * N, K]
         for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
           if (r.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
           uint8_t* st = smem + static_cast<size_t>(r.s) * ax_bytes;
           const uint32_t bar = smem_u32(&ctl->x_full[r.s]);
           mbar_expect_tx(bar, tx);
-          tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, m0, bar);
-          if (FMT == kFmtBf16) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, n_tile * kTileN, bar);
+          tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, c.m0, bar);
+          if (FMT == kFmtBf16) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row, bar);
           r.advance(S);
         }
       }
@@ -322,9 +345,11 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       bool ok = true;
       SkRing r;
       while (ok && it.next(p, cta, grid, seg)) {
-        const int n_tile = seg.tile % p.n_tiles;
-        const uint8_t* cbase = p.codes + static_cast<size_t>(n_tile) * p.k_blocks * kCodeBytes;
-        const uint8_t* mbase = p.meta + static_cast<size_t>(n_tile) * p.meta_blocks * kMetaBytes;
+        const SkCoords c = sk_coords(p, seg.tile);
+        const uint8_t* cbase = p.codes + static_cast<size_t>(c.expert) * p.group_code_stride +
+                               static_cast<size_t>(c.n_tile) * p.k_blocks * kCodeBytes;
+        const uint8_t* mbase = p.meta + static_cast<size_t>(c.expert) * p.group_meta_stride +
+                               static_cast<size_t>(c.n_tile) * p.meta_blocks * kMetaBytes;
         for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
           if (r.wraps && !mbar_wait_park(smem_u32(&ctl->c_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
           const uint32_t dst = smem_u32(c_ring + static_cast<size_t>(r.s) * kSkCStageBytes);
@@ -392,11 +417,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // Geometry of the current segment (set by seg_geometry) and the shared LAST-segment epilogue.
     int m0 = 0, rows_here = 0, n_base = 0;
     auto seg_geometry = [&]() {
-      const int m_tile = seg.tile / p.n_tiles;
-      const int n_tile = seg.tile - m_tile * p.n_tiles;
-      m0 = m_tile * p.mb;
-      rows_here = min(p.mb, p.M - m0);
-      n_base = n_tile * kTileN;
+      const SkCoords c = sk_coords(p, seg.tile);
+      m0 = c.m0;
+      rows_here = c.rows;
+      n_base = c.n_tile * kTileN;
     };
     // Last segment of the CTA: nothing is left to overlap with, so all 20 of these warps (640 threads) do the
     // epilogue together.  The rings are idle once the accumulator is complete, so the whole fp32 tile is staged
@@ -675,11 +699,17 @@ static int launch_sk_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqG
 // 0.34 us per k-block, every extra part of a tile costs the reducer about mb / 256 us, so the best number of
 // parts is sqrt(k_blocks * 0.34 * 256 / mb) and the run length k_blocks over that.
 int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, size_t workspace_bytes,
-                   int sm_count, int min_units, cudaStream_t stream) {
+                   int sm_count, int min_units, cudaStream_t stream, int grouped_max_items) {
   if (sm_count < 1) return -15;
   p.n_tiles = (p.N + kTileN - 1) / kTileN;
   const int m_tiles = (p.M + p.mb - 1) / p.mb;
   p.tiles = p.n_tiles * m_tiles;
+  if (p.group_tiles) {
+    // grouped expert GEMMs: whole tiles only (the tile count lives on the device), one persistent CTA per SM at
+    // most; what this buys over one CTA per tile is the set-up and epilogue of ~30 waves of small tiles
+    p.tiles = 0;
+    workspace_bytes = 0;
+  }
   if (p.meta_k_blocks < 1 || (p.meta_k_blocks & (p.meta_k_blocks - 1)) != 0) return -16;
   p.meta_shift = 0;
   while ((1 << p.meta_shift) < p.meta_k_blocks) ++p.meta_shift;
@@ -695,6 +725,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
   }
   p.sk_tiles = p.tiles <= sm_count ? p.tiles : p.tiles % sm_count;
   p.sk_ctas = 0;
+  if (p.group_tiles) p.sk_tiles = 0;
   if (p.sk_tiles > 0) {
     // a CTA of the streamed region owns two fp32 partial slots (see sk_slot)
     const size_t part_bytes = static_cast<size_t>(p.mb) * kTileN * sizeof(float);
@@ -710,7 +741,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
     }
   }
   if (static_cast<long long>(p.sk_tiles) * p.k_blocks * (sm_count + 1) >= (1LL << 31)) return -19;   // SkIter is 32-bit
-  int grid = p.tiles - p.sk_tiles;
+  int grid = p.group_tiles ? grouped_max_items * p.n_tiles : p.tiles - p.sk_tiles;
   if (grid > sm_count) grid = sm_count;
   if (grid < p.sk_ctas) grid = p.sk_ctas;
   if (grid < 1) return -17;

@@ -15,9 +15,14 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
 
 
-@pytest.mark.parametrize("method,tokens,ep", [("nvfp4", 37, 1), ("cubic", 200, 1), ("nvfp4", 64, 2), ("none", 5, 1)])
-def test_moe_layer_matches_oracle(method, tokens, ep):
+@pytest.mark.parametrize("persistent", [1, 0])
+@pytest.mark.parametrize("method,tokens,ep", [("nvfp4", 37, 1), ("cubic", 200, 1), ("nvfp4", 64, 2), ("none", 5, 1),
+                                              ("cubic", 700, 1)])
+def test_moe_layer_matches_oracle(method, tokens, ep, persistent):
+    """Both grouped-GEMM kernels: the persistent one (default) and one CTA per (work item, weight tile)."""
     from cubic_serve_b200.models.moe import moe_reference, random_moe_weights
+    from cubic_serve_b200.ops import native
+    native.lib().cb_wq_gemm_grouped_mode(persistent)
     cfg = ModelConfig(family="gqa_moe", hidden_size=256, num_experts=16, experts_per_token=4, moe_intermediate_size=128,
                       quant=QuantSpec(method, 4 if method != "none" else 16, {"nvfp4": 16, "cubic": 128, "none": 0}[method]))
     x = (torch.randn(tokens, 256, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16).to(DEV)
@@ -47,6 +52,7 @@ def test_moe_layer_matches_oracle(method, tokens, ep):
         total += out.float()
         ref_total += ref
     from cubic_serve_b200.ops import kernels as K
+    native.lib().cb_wq_gemm_grouped_mode(1)
     K.workspace(torch.device(DEV)).check_status()
     assert _rel(total, ref_total) < 3e-2
 
