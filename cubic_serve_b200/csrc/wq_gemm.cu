@@ -229,12 +229,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (FMT == kFmtCubic4) {
           const uint32_t ab = meta[r], cz = meta[128 + r];
           c0 = bf2_dup(ab);        // A = s * a / 7
-          c1 = bf2_dup(ab >> 16);  // B = s * b / 49
+          c1 = bf2_dup_hi(ab);  // B = s * b / 49
           c2 = bf2_dup(cz);        // C = s * (1 - a - b) / 343
         } else {
           const uint32_t so = meta[h * 128 + r];
           c0 = bf2_dup(so);
-          c1 = bf2_dup(so >> 16);
+          c1 = bf2_dup_hi(so);
           c2 = 0;
         }
         uint32_t o[4][4];

@@ -119,7 +119,22 @@ __device__ __forceinline__ uint32_t bf2_fma(uint32_t a, uint32_t b, uint32_t c) 
   asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
-__device__ __forceinline__ uint32_t bf2_dup(uint32_t lo16) { return (lo16 & 0xFFFFu) * 0x00010001u; }
+// low 16 bits of a word duplicated into both halves: one byte permute
+__device__ __forceinline__ uint32_t bf2_dup(uint32_t lo16) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(r) : "r"(lo16));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_dup_hi(uint32_t w) {      // high 16 bits into both halves
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(r) : "r"(w));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf2_abs(uint32_t a) {
+  uint32_t r;
+  asm("abs.bf16x2 %0, %1;" : "=r"(r) : "r"(a));
+  return r;
+}
 
 template <int FMT>
 __device__ __forceinline__ void decode8(uint32_t w, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t (&out)[4]);
@@ -135,7 +150,7 @@ __device__ __forceinline__ void decode8<kFmtCubic4>(uint32_t w, uint32_t A, uint
   for (int i = 0; i < 4; ++i) {
     const uint32_t x = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;  // 128 + n
     const uint32_t c = bf2_sub(x, 0x43084308u);                        // n - 8 (exact)
-    const uint32_t m = c & 0x7FFF7FFFu;                                // |c|
+    const uint32_t m = bf2_abs(c);                                     // |c| (a source modifier of the next fma)
     uint32_t p = bf2_fma(m, C, B);
     p = bf2_fma(m, p, A);
     out[i] = bf2_mul(c, p);

@@ -145,6 +145,10 @@ struct SkRing {
   __device__ __forceinline__ void advance(int depth) {
     if (++s == depth) { s = 0; ++wraps; }
   }
+  __device__ __forceinline__ void advance_by(int n, int depth) {   // n <= depth
+    s += n;
+    if (s >= depth) { s -= depth; ++wraps; }
+  }
 };
 
 // fp32 partial slot of (cta, part): a CTA has at most one run that starts inside a tile (its first, part > 0)
@@ -515,10 +519,16 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       while (it.next(p, cta, grid, seg)) {
         const bool tail = !it.has_more(p);
         if (FMT != kFmtBf16 && ok) {
-          for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb, ++i_global, rc.advance(NC), ra.advance(S)) {
-            if ((i_global & 1) != g) continue;                   // the other group's k-block
+          // this group's k-blocks of the segment are every other one; the rings are stepped over the other
+          // group's k-blocks arithmetically instead of by empty loop iterations
+          const int len = seg.kb_hi - seg.kb_lo;
+          const int skip = ((i_global & 1) != g) ? 1 : 0;
+          rc.advance_by(skip, NC);
+          ra.advance_by(skip, S);
+          for (int jj = skip; jj < len; jj += 2) {
+            const int ig = i_global + jj;
             if (!mbar_wait_park(smem_u32(&ctl->c_full[rc.s]), rc.wraps & 1u, abort_flag)) { ok = false; break; }
-            if (trace && dq == 0 && i_global < 64) trace[i_global * 8 + 2] = clock64();
+            if (trace && dq == 0 && ig < 64) trace[ig * 8 + 2] = clock64();
             const uint8_t* pk = c_ring + static_cast<size_t>(rc.s) * kSkCStageBytes;
             const uint4 words = *reinterpret_cast<const uint4*>(pk + code_off);
             const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
@@ -527,12 +537,12 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             if (FMT == kFmtCubic4) {
               const uint32_t ab = meta[r], cz = meta[128 + r];
               c0 = bf2_dup(ab);        // A = s * a / 7
-              c1 = bf2_dup(ab >> 16);  // B = s * b / 49
+              c1 = bf2_dup_hi(ab);  // B = s * b / 49
               c2 = bf2_dup(cz);        // C = s * (1 - a - b) / 343
             } else {
               const uint32_t so = meta[h * 128 + r];
               c0 = bf2_dup(so);
-              c1 = bf2_dup(so >> 16);
+              c1 = bf2_dup_hi(so);
               c2 = 0;
             }
             // the codes and metadata are in registers: hand the slot back to the copy warp right away
@@ -560,8 +570,12 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[ra.s]));
-            if (trace && dq == 0 && i_global < 64) trace[i_global * 8 + 3] = clock64();
+            if (trace && dq == 0 && ig < 64) trace[ig * 8 + 3] = clock64();
+            const int step = len - jj < 2 ? len - jj : 2;
+            rc.advance_by(step, NC);
+            ra.advance_by(step, S);
           }
+          i_global += len;
         }
         if (tail) tail_epilogue(seg_idx, ok);
         ++seg_idx;
