@@ -131,8 +131,8 @@ def build_parser() -> argparse.ArgumentParser:
 
 def _kv_bits(name: str) -> int:
     bits = KV_BITS[name]
-    if bits not in (8, 4):
-        raise SystemExit(f"KV cache dtype {name} is not available in this build (int8 and int4 are)")
+    if bits not in (8, 6, 4):
+        raise SystemExit(f"KV cache dtype {name} is not available in this build (int8, int6 and int4 are)")
     return bits
 
 

@@ -27,8 +27,8 @@ struct KvWriteParams {
 
 __device__ __forceinline__ void quantize_store(const float (&v)[4], int bits, bool is_v, uint8_t* blob,
                                                const KvLayout& lay, int tok, int lane) {
-  const float qmax = bits == 8 ? 127.f : 7.f;
-  const int bias = bits == 8 ? 128 : 8;
+  const float qmax = bits == 8 ? 127.f : (bits == 6 ? 31.f : 7.f);
+  const int bias = bits == 8 ? 128 : (bits == 6 ? 32 : 8);
   uint8_t* codes = blob + (is_v ? lay.v_code_off : 0);
   float* scales = reinterpret_cast<float*>(blob + (is_v ? lay.v_scale_off : lay.k_scale_off));
 #pragma unroll
@@ -37,9 +37,19 @@ __device__ __forceinline__ void quantize_store(const float (&v)[4], int bits, bo
     const float scale = amax > 0.f ? amax / qmax : 1.f;
     float c = rintf(v[k] / scale);
     c = fminf(fmaxf(c, -qmax), qmax);
-    const uint32_t code = static_cast<uint32_t>(static_cast<int>(c) + bias);
+    uint32_t code = static_cast<uint32_t>(static_cast<int>(c) + bias);
     const int ch = lane + 32 * k;
     int shift;
+    if (bits == 6) {
+      // two high bits into the second plane (fields of one 16-bit word come from several lanes, and for V
+      // from two tokens = two warps: atomics on the enclosing 32-bit word), low nibble as a 4-bit code below
+      const int pos = is_v ? v_hi_pos(lay.head_dim, tok, ch, &shift) : k_hi_pos(lay.head_dim, tok, ch, &shift);
+      uint32_t* word = reinterpret_cast<uint32_t*>(codes + (pos & ~3));
+      const int bit = (pos & 2) * 8 + shift;
+      atomicAnd(word, ~(0x3u << bit));
+      atomicOr(word, (code >> 4) << bit);
+      code &= 15u;
+    }
     if (bits == 8) {
       const int pos = is_v ? v_code_pos(8, lay.head_dim, tok, ch, &shift) : k_code_pos(8, tok, ch, &shift);
       codes[pos] = static_cast<uint8_t>(code);
@@ -153,7 +163,7 @@ int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* posi
   using namespace cb;
   if (T <= 0) return 0;
   if (D != 128) return -10;
-  if (!(k_bits == 8 || k_bits == 4) || !(v_bits == 8 || v_bits == 4)) return -11;
+  if (!(k_bits == 8 || k_bits == 6 || k_bits == 4) || !(v_bits == 8 || v_bits == 6 || v_bits == 4)) return -11;
   if (!(rotary_dim == 128 || rotary_dim == 64 || rotary_dim == 0)) return -12;
   KvWriteParams p;
   p.qkv = static_cast<const __nv_bfloat16*>(qkv);

@@ -112,6 +112,19 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
           mma_f16(acc[nt], qf[j], b0, b1);
         }
       }
+    } else if (KBITS == 6) {
+      // nibble plane as for 4 bits, plus one 16-bit word of high bits per 32-bit word of nibbles: a multiply
+      // spreads four 2-bit fields over the four code bytes (kv_layout.cuh)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(blob + cg * 256 + (nt * 8 + g) * 16 + t4 * 4);
+        const uint32_t hb = *reinterpret_cast<const uint16_t*>(blob + kPageTokens * kD / 2 + cg * 128 + (nt * 8 + g) * 8 + t4 * 2);
+        const uint32_t lo = (w & 0x0F0F0F0Fu) | (((hb & 0xFFu) * 0x410410u) & 0x30303030u);
+        const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) | (((hb >> 8) * 0x410410u) & 0x30303030u);
+        mma_f16(acc[nt], qf[cg * 2], u8x2_to_f16x2(lo, 0x5140u, 0x64206420u), u8x2_to_f16x2(lo, 0x5342u, 0x64206420u));
+        mma_f16(acc[nt], qf[cg * 2 + 1], u8x2_to_f16x2(hi, 0x5140u, 0x64206420u),
+                u8x2_to_f16x2(hi, 0x5342u, 0x64206420u));
+      }
     } else {
       // 4-bit: one 32-bit word = this lane's 4 channels of both k-steps of the group
 #pragma unroll
@@ -197,15 +210,26 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
       const uint32_t lo = *reinterpret_cast<const uint32_t*>(vcodes + t4 * 128 + chunk * 4);
       const uint32_t hi = *reinterpret_cast<const uint32_t*>(vcodes + (t4 + 4) * 128 + chunk * 4);
       // spread nibbles: even tokens -> bytes (sub), odd tokens -> bytes (sub) of a second word
-      const uint32_t le = lo & 0x0F0F0F0Fu, lod = (lo >> 4) & 0x0F0F0F0Fu;
-      const uint32_t he = hi & 0x0F0F0F0Fu, hod = (hi >> 4) & 0x0F0F0F0Fu;
+      uint32_t le = lo & 0x0F0F0F0Fu, lod = (lo >> 4) & 0x0F0F0F0Fu;
+      uint32_t he = hi & 0x0F0F0F0Fu, hod = (hi >> 4) & 0x0F0F0F0Fu;
+      if (VBITS == 6) {
+        // high bits: one 16-bit word per nibble word (low byte = even token, high byte = odd token)
+        const uint8_t* hp = vcodes + kPageTokens * kD / 2;
+        const uint32_t hl = *reinterpret_cast<const uint16_t*>(hp + t4 * 64 + chunk * 2);
+        const uint32_t hh = *reinterpret_cast<const uint16_t*>(hp + (t4 + 4) * 64 + chunk * 2);
+        le |= ((hl & 0xFFu) * 0x410410u) & 0x30303030u;
+        lod |= ((hl >> 8) * 0x410410u) & 0x30303030u;
+        he |= ((hh & 0xFFu) * 0x410410u) & 0x30303030u;
+        hod |= ((hh >> 8) * 0x410410u) & 0x30303030u;
+      }
+      const uint32_t vbias = VBITS == 6 ? 0x64206420u : 0x64086408u;
 #pragma unroll
       for (int sub = 0; sub < 4; ++sub) {
         // f16x2 (even tok, odd tok) of channel `sub`: byte `sub` of le and of lod
         const uint32_t pl = prmt(le, lod, sub | ((4u + sub) << 4));          // bytes: [e_sub, o_sub, x, x]
         const uint32_t ph = prmt(he, hod, sub | ((4u + sub) << 4));
-        const uint32_t b0 = u8x2_to_f16x2(pl, 0x5140u, 0x64086408u);
-        const uint32_t b1 = u8x2_to_f16x2(ph, 0x5140u, 0x64086408u);
+        const uint32_t b0 = u8x2_to_f16x2(pl, 0x5140u, vbias);
+        const uint32_t b1 = u8x2_to_f16x2(ph, 0x5140u, vbias);
         mma_f16(st.o[cg * 4 + sub], a, b0, b1);
       }
     }
@@ -474,6 +498,11 @@ int cb_paged_attn(const void* q, void* out, const void* cache, const void* page_
   if (k_bits == 4 && v_bits == 8) return launch_attn<4, 8>(p, grid, smem, st);
   if (k_bits == 4 && v_bits == 4) return launch_attn<4, 4>(p, grid, smem, st);
   if (k_bits == 8 && v_bits == 4) return launch_attn<8, 4>(p, grid, smem, st);
+  if (k_bits == 6 && v_bits == 6) return launch_attn<6, 6>(p, grid, smem, st);
+  if (k_bits == 6 && v_bits == 8) return launch_attn<6, 8>(p, grid, smem, st);
+  if (k_bits == 8 && v_bits == 6) return launch_attn<8, 6>(p, grid, smem, st);
+  if (k_bits == 4 && v_bits == 6) return launch_attn<4, 6>(p, grid, smem, st);
+  if (k_bits == 6 && v_bits == 4) return launch_attn<6, 4>(p, grid, smem, st);
   return -13;
 }
 

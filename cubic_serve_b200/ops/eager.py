@@ -95,6 +95,18 @@ def _v_pos(bits: int, d: int, tok: torch.Tensor, ch: torch.Tensor):
     return p * d + chunk * 4 + (ch & 3), torch.where((tok & 1) == 1, 4, 0)
 
 
+def _k_hi_pos(d: int, tok: torch.Tensor, ch: torch.Tensor):
+    """6-bit K: byte offset of the 16-bit word of high bits (from the start of the code region) and bit shift."""
+    c = ch & 31
+    return PAGE_TOKENS * d // 2 + (ch >> 5) * 128 + tok * 8 + ((c & 15) >> 2) * 2, torch.where(c >= 16, 8, 0) + 2 * (c & 3)
+
+
+def _v_hi_pos(d: int, tok: torch.Tensor, ch: torch.Tensor):
+    p = tok >> 1
+    chunk = (ch >> 2) ^ ((p & 3) << 2)
+    return PAGE_TOKENS * d // 2 + p * (d // 2) + chunk * 2, torch.where((tok & 1) == 1, 8, 0) + 2 * (ch & 3)
+
+
 def blob_layout(d: int, k_bits: int, v_bits: int) -> dict:
     kc = PAGE_TOKENS * d * k_bits // 8
     vc = PAGE_TOKENS * d * v_bits // 8
@@ -109,14 +121,21 @@ def decode_cache_page(blob: torch.Tensor, d: int, k_bits: int, v_bits: int):
     ch = torch.arange(d, device=blob.device)[None, :].expand(PAGE_TOKENS, d)
     b32 = blob.to(torch.int32)
 
-    def codes(region_off: int, pos, shift, bits):
-        raw = (b32[region_off + pos] >> shift) & ((1 << bits) - 1 if bits < 8 else 255)
+    def codes(region_off: int, pos, shift, bits, hi=None):
+        if bits == 6:
+            # nibble plane (4-bit layout) + plane of the two high bits, read as little-endian 16-bit words
+            low = (b32[region_off + pos] >> shift) & 15
+            hpos, hshift = hi
+            word = b32[region_off + hpos] | (b32[region_off + hpos + 1] << 8)
+            raw = low | (((word >> hshift) & 3) << 4)
+        else:
+            raw = (b32[region_off + pos] >> shift) & ((1 << bits) - 1 if bits < 8 else 255)
         return (raw - (1 << (bits - 1))).float()
 
     kp, ks = _k_pos(k_bits, tok, ch)
     vp, vs = _v_pos(v_bits, d, tok, ch)
-    kcodes = codes(0, kp, ks, k_bits)
-    vcodes = codes(lay["v_code"], vp, vs, v_bits)
+    kcodes = codes(0, kp, ks, k_bits, _k_hi_pos(d, tok, ch))
+    vcodes = codes(lay["v_code"], vp, vs, v_bits, _v_hi_pos(d, tok, ch))
     ksc = blob[lay["k_scale"]:lay["v_code"]].contiguous().view(torch.float32).reshape(PAGE_TOKENS, d // KV_GROUP)
     vsc = blob[lay["v_scale"]:lay["bytes"]].contiguous().view(torch.float32).reshape(PAGE_TOKENS, d // KV_GROUP)
     return kv_dequantize(kcodes, ksc), kv_dequantize(vcodes, vsc)

@@ -151,7 +151,7 @@ def _make_cache(pages, hkv, d, kb, vb):
     return torch.zeros(pages, hkv, blob, dtype=torch.uint8, device=DEV)
 
 
-@pytest.mark.parametrize("kb,vb", [(8, 8), (4, 8), (4, 4), (8, 4)])
+@pytest.mark.parametrize("kb,vb", [(8, 8), (4, 8), (4, 4), (8, 4), (6, 6), (6, 8), (4, 6)])
 def test_rope_kv_write_roundtrip(kb, vb):
     K = _k()
     hq, hkv, d, t = 8, 2, 128, 37
@@ -183,9 +183,9 @@ def test_rope_kv_write_roundtrip(kb, vb):
             kk, vv = eager.decode_cache_page(cache[page, h], d, kb, vb)
             # one code step of slack where rounding sits on a tie after bf16 effects
             assert (kk[off] - kd[tok, h]).abs().max() <= ksc[tok, h].max() * 1.01
-            assert _rel(kk[off], kd[tok, h]) < (0.02 if kb == 8 else 0.2)
+            assert _rel(kk[off], kd[tok, h]) < {8: 0.02, 6: 0.06, 4: 0.2}[kb]
             assert (vv[off] - vd[tok, h]).abs().max() <= vsc[tok, h].max() * 1.01
-            assert _rel(vv[off], vd[tok, h]) < (0.01 if vb == 8 else 0.1)
+            assert _rel(vv[off], vd[tok, h]) < {8: 0.01, 6: 0.03, 4: 0.1}[vb]
 
 
 def _fill_cache_random(cache, t_total, hkv, d, kb, vb, page_ids, seed=0):
@@ -211,7 +211,8 @@ def _dense_kv(cache, page_ids, t_total, hkv, d, kb, vb):
 
 
 @pytest.mark.parametrize("kb,vb,hq,hkv,splits", [(8, 8, 8, 2, 1), (8, 8, 8, 2, 3), (4, 8, 16, 2, 1),
-                                                 (4, 4, 8, 1, 2), (8, 4, 16, 1, 1)])
+                                                 (4, 4, 8, 1, 2), (8, 4, 16, 1, 1), (6, 6, 8, 2, 1), (6, 8, 16, 2, 2),
+                                                 (8, 6, 8, 1, 1), (4, 6, 8, 2, 1), (6, 4, 16, 1, 3)])
 def test_paged_attention_decode(kb, vb, hq, hkv, splits):
     K = _k()
     d = 128
