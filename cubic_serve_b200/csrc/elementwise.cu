@@ -90,12 +90,11 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* residua
 
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]   (gate and up halves concatenated)
 __global__ void __launch_bounds__(256)
-swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, size_t total_vec) {
-  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
-  if (idx >= total_vec) return;
-  const int per_row = I >> 3;
-  const size_t row = idx / per_row;
-  const int v = static_cast<int>(idx - row * per_row);
+swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I) {
+  // grid = (vector blocks of a row, rows): no per-thread 64-bit division
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= (I >> 3)) return;
+  const size_t row = blockIdx.y;
   const uint4 g = reinterpret_cast<const uint4*>(gu + row * 2 * I)[v];
   const uint4 u = reinterpret_cast<const uint4*>(gu + row * 2 * I + I)[v];
   const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
@@ -148,10 +147,19 @@ int cb_swiglu(const void* gate_up, void* out, int rows, int I, void* stream) {
   using namespace cb;
   if (rows <= 0) return 0;
   if (I % 8 != 0) return -10;
-  const size_t total = static_cast<size_t>(rows) * (I >> 3);
-  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-  swiglu_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), I, total);
+  if (rows > 65535) {
+    // the row index rides in gridDim.y: split very long batches
+    for (int r0 = 0; r0 < rows; r0 += 65535) {
+      const int n = rows - r0 < 65535 ? rows - r0 : 65535;
+      const int rc = cb_swiglu(static_cast<const __nv_bfloat16*>(gate_up) + static_cast<size_t>(r0) * 2 * I,
+                               static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(r0) * I, n, I, stream);
+      if (rc) return rc;
+    }
+    return 0;
+  }
+  const dim3 grid(static_cast<unsigned>(((I >> 3) + 255) / 256), static_cast<unsigned>(rows));
+  swiglu_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), I);
   return static_cast<int>(cudaGetLastError());
 }
 

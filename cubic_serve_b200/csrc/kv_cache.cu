@@ -2,9 +2,9 @@
 //
 // One launch after the QKV GEMM replaces the reference's separate q/k norm,
 // M-RoPE (position/qwen_mrope.py:25) and cache quantization kernels
-// (cache_quantization_native.cu:49).  One warp owns one (token, head); lane l
-// holds channels l, l+32, l+64, l+96, so a rotate-half RoPE pair (c, c+64) and
-// a 32-channel quantization group (c/32) are both warp-local.
+// (cache_quantization_native.cu:49).  One warp handles one (token, head) at a
+// time; lane l holds channels l, l+32, l+64, l+96, so a rotate-half RoPE pair
+// (c, c+64) and a 32-channel quantization group (c/32) are both warp-local.
 #include "ptx.cuh"
 #include "kv_layout.cuh"
 
@@ -41,13 +41,12 @@ __device__ __forceinline__ void quantize_store(const float (&v)[4], int bits, bo
     const int ch = lane + 32 * k;
     int shift;
     if (bits == 6) {
-      // two high bits into the second plane (fields of one 16-bit word come from several lanes, and for V
-      // from two tokens = two warps: atomics on the enclosing 32-bit word), low nibble as a 4-bit code below
+      // two high bits into the second plane (the fields of one 32-bit word come from several lanes and from
+      // several tokens = several warps: atomics), low nibble as a 4-bit code below
       const int pos = is_v ? v_hi_pos(lay.head_dim, tok, ch, &shift) : k_hi_pos(lay.head_dim, tok, ch, &shift);
-      uint32_t* word = reinterpret_cast<uint32_t*>(codes + (pos & ~3));
-      const int bit = (pos & 2) * 8 + shift;
-      atomicAnd(word, ~(0x3u << bit));
-      atomicOr(word, (code >> 4) << bit);
+      uint32_t* word = reinterpret_cast<uint32_t*>(codes + pos);
+      atomicAnd(word, ~(0x3u << shift));
+      atomicOr(word, (code >> 4) << shift);
       code &= 15u;
     }
     if (bits == 8) {
@@ -72,71 +71,79 @@ __device__ __forceinline__ void quantize_store(const float (&v)[4], int bits, bo
   }
 }
 
-__global__ void __launch_bounds__(128)
+static constexpr int kRopeWarps = 8;
+
+// One CTA per token; its eight warps share the token's heads (warp w takes heads w, w + 8, ...).  The rotary
+// angles depend on (position, channel) only, so each lane computes its two sin / cos pairs ONCE and reuses them
+// for every head of the token: full-precision sincosf on arguments of thousands of radians is the expensive
+// part of this kernel, and one warp per (token, head) paid it 6x as often.
+__global__ void __launch_bounds__(kRopeWarps * 32)
 rope_kv_write_kernel(const KvWriteParams p) {
-  const int warp_global = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int heads = p.Hq + 2 * p.Hkv;
-  if (warp_global >= p.T * heads) return;
-  const int t = warp_global / heads;
-  const int h = warp_global - t * heads;
   const int D = p.lay.head_dim;  // == 128
-  const __nv_bfloat16* src = p.qkv + (static_cast<size_t>(t) * heads + h) * D;
-  float v[4];
+  const int half = p.rotary_dim >> 1;
+  const float pos = static_cast<float>(p.positions[t]);
+  float sn[2] = {0.f, 0.f}, cs[2] = {1.f, 1.f};
+  if (half == 64) {
 #pragma unroll
-  for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(src[lane + 32 * k]);
-
-  const bool is_q = h < p.Hq;
-  const bool is_k = !is_q && h < p.Hq + p.Hkv;
-  if (is_q || is_k) {
-    const __nv_bfloat16* nw = is_q ? p.q_norm : p.k_norm;
-    if (nw) {
-      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-      ss = warp_sum(ss);
-      const float inv = rsqrtf(ss / static_cast<float>(D) + p.eps);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        // round to bf16 after the norm, as an unfused norm kernel would
-        v[k] = __bfloat162float(__float2bfloat16(v[k] * inv * __bfloat162float(nw[lane + 32 * k])));
-      }
-    }
-    const int half = p.rotary_dim >> 1;
-    const float pos = static_cast<float>(p.positions[t]);
-    // pairs (c, c + half) for c < half; with D = 128 and half = 64: (l, l+64), (l+32, l+96)
-    if (half == 64) {
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int c = lane + 32 * k;
-        float s, co;
-        sincosf(pos * p.inv_freq[c], &s, &co);
-        const float a = v[k], b = v[k + 2];
-        v[k] = a * co - b * s;
-        v[k + 2] = b * co + a * s;
-      }
-    } else if (half == 32) {
-      // partial rotary over the first 64 channels: pairs (l, l+32)
-      float s, co;
-      sincosf(pos * p.inv_freq[lane], &s, &co);
-      const float a = v[0], b = v[1];
-      v[0] = a * co - b * s;
-      v[1] = b * co + a * s;
-    }
-  }
-  if (is_q) {
-    __nv_bfloat16* dst = p.q_out + (static_cast<size_t>(t) * p.Hq + h) * D;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) dst[lane + 32 * k] = __float2bfloat16(v[k]);
-    return;
+    for (int k = 0; k < 2; ++k) sincosf(pos * p.inv_freq[lane + 32 * k], &sn[k], &cs[k]);
+  } else if (half == 32) {
+    sincosf(pos * p.inv_freq[lane], &sn[0], &cs[0]);
   }
   const int slot = p.slots[t];
-  if (slot < 0) return;
-  const int kvh = is_k ? h - p.Hq : h - p.Hq - p.Hkv;
-  const int page = slot >> 4, tok = slot & 15;
-  uint8_t* blob = p.cache + (static_cast<size_t>(page) * p.Hkv + kvh) * p.lay.blob_bytes;
-  // the cache stores what attention will see: bf16-rounded values
+  for (int h = warp; h < heads; h += kRopeWarps) {
+    const __nv_bfloat16* src = p.qkv + (static_cast<size_t>(t) * heads + h) * D;
+    float v[4];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(__float2bfloat16(v[k]));
-  quantize_store(v, is_k ? p.lay.k_bits : p.lay.v_bits, !is_k, blob, p.lay, tok, lane);
+    for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(src[lane + 32 * k]);
+
+    const bool is_q = h < p.Hq;
+    const bool is_k = !is_q && h < p.Hq + p.Hkv;
+    if (is_q || is_k) {
+      const __nv_bfloat16* nw = is_q ? p.q_norm : p.k_norm;
+      if (nw) {
+        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / static_cast<float>(D) + p.eps);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // round to bf16 after the norm, as an unfused norm kernel would
+          v[k] = __bfloat162float(__float2bfloat16(v[k] * inv * __bfloat162float(nw[lane + 32 * k])));
+        }
+      }
+      // pairs (c, c + half) for c < half; with D = 128 and half = 64: (l, l+64), (l+32, l+96)
+      if (half == 64) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const float a = v[k], b = v[k + 2];
+          v[k] = a * cs[k] - b * sn[k];
+          v[k + 2] = b * cs[k] + a * sn[k];
+        }
+      } else if (half == 32) {
+        // partial rotary over the first 64 channels: pairs (l, l+32)
+        const float a = v[0], b = v[1];
+        v[0] = a * cs[0] - b * sn[0];
+        v[1] = b * cs[0] + a * sn[0];
+      }
+    }
+    if (is_q) {
+      __nv_bfloat16* dst = p.q_out + (static_cast<size_t>(t) * p.Hq + h) * D;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) dst[lane + 32 * k] = __float2bfloat16(v[k]);
+      continue;
+    }
+    if (slot < 0) continue;
+    const int kvh = is_k ? h - p.Hq : h - p.Hq - p.Hkv;
+    const int page = slot >> 4, tok = slot & 15;
+    uint8_t* blob = p.cache + (static_cast<size_t>(page) * p.Hkv + kvh) * p.lay.blob_bytes;
+    // the cache stores what attention will see: bf16-rounded values
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(__float2bfloat16(v[k]));
+    quantize_store(v, is_k ? p.lay.k_bits : p.lay.v_bits, !is_k, blob, p.lay, tok, lane);
+  }
 }
 
 // Copy whole pages (all kv heads) src -> dst: copy-on-write of a shared page.
@@ -176,9 +183,7 @@ int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* posi
   p.inv_freq = static_cast<const float*>(inv_freq);
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.rotary_dim = rotary_dim; p.eps = eps;
   p.lay = make_kv_layout(D, k_bits, v_bits);
-  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
-  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
-  rope_kv_write_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  rope_kv_write_kernel<<<static_cast<unsigned>(T), kRopeWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -20,13 +20,17 @@
 //
 //   6-bit (K or V): the low nibble of the offset-binary code (code + 32) sits in a plane with exactly the
 //                   4-bit layout above; the two high bits sit in a second plane right after it (16 * D / 4
-//                   bytes) whose 16-bit words line up with the 32-bit words of the nibble plane:
-//                   K: word [ch/32][tok][t] holds the high bits of channels 32*blk + 4*t + e (bits 2e, 2e+1)
-//                      and 32*blk + 16 + 4*t + e (bits 8 + 2e, 9 + 2e);
-//                   V: word [tok/2][chunk'] holds those of channels 4*chunk + e for the even token (bits 2e,
-//                      2e+1) and the odd token (bits 8 + 2e, 9 + 2e).
-//                   One multiply spreads a byte of high bits over four code bytes:
-//                   (x * 0x410410) & 0x30303030 puts bits (2e, 2e+1) of x at bits (4, 5) of byte e.
+//                   bytes) of 32-bit words.  One word serves the TWO nibble words a thread of the attention
+//                   kernel loads together (X and Y below), with every 2-bit field already at the byte of its
+//                   code, so a code byte is  nibble | ((word >> s) & 0x30)  with one shift per group of four:
+//                       field of X, first set : bits 8e + 4, 8e + 5      (word        & 0x30303030)
+//                       field of X, second set: bits 8e + 6, 8e + 7      ((word >> 2) & 0x30303030)
+//                       field of Y, first set : bits 8e + 0, 8e + 1      ((word << 4) & 0x30303030)
+//                       field of Y, second set: bits 8e + 2, 8e + 3      ((word << 2) & 0x30303030)
+//                   K: word [ch/32][tok % 8][t]; X = token tok % 8, Y = token tok % 8 + 8; first / second set
+//                      = channels 32*blk + 4*t + e / 32*blk + 16 + 4*t + e.
+//                   V: word [(tok/2) % 4][chunk']; X = token pair (tok/2) % 4, Y = that pair + 4; first /
+//                      second set = even / odd token; e = ch % 4.
 //
 // Every region is a multiple of 16 bytes so one bulk copy moves a whole blob.
 #pragma once
@@ -70,18 +74,18 @@ __host__ __device__ inline int k_code_pos(int bits, int tok, int ch, int* shift)
   return blk * 256 + tok * 16 + (c & 15);
 }
 
-// 6-bit: byte offset of the 16-bit word (relative to the START of the code region, i.e. past the nibble
-// plane) and the bit position of the two high bits of K element (tok, ch)
+// 6-bit: byte offset of the 32-bit word of high bits (relative to the START of the code region, i.e. past the
+// nibble plane) and the bit position of the two high bits of element (tok, ch)
 __host__ __device__ inline int k_hi_pos(int head_dim, int tok, int ch, int* shift) {
   const int blk = ch >> 5, c = ch & 31;
-  *shift = ((c >= 16) ? 8 : 0) + 2 * (c & 3);
-  return kPageTokens * head_dim / 2 + blk * 128 + tok * 8 + ((c & 15) >> 2) * 2;
+  *shift = 8 * (c & 3) + ((tok >= 8) ? 0 : 4) + ((c >= 16) ? 2 : 0);
+  return kPageTokens * head_dim / 2 + blk * 128 + (tok & 7) * 16 + ((c & 15) >> 2) * 4;
 }
 __host__ __device__ inline int v_hi_pos(int head_dim, int tok, int ch, int* shift) {
   const int p = tok >> 1;
   const int chunk = (ch >> 2) ^ ((p & 3) << 2);
-  *shift = ((tok & 1) ? 8 : 0) + 2 * (ch & 3);
-  return kPageTokens * head_dim / 2 + p * (head_dim / 2) + chunk * 2;
+  *shift = 8 * (ch & 3) + ((p >= 4) ? 0 : 4) + ((tok & 1) ? 2 : 0);
+  return kPageTokens * head_dim / 2 + (p & 3) * head_dim + chunk * 4;
 }
 
 // byte offset (and nibble shift) of V element (tok, ch) inside the V code region

@@ -113,14 +113,16 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
         }
       }
     } else if (KBITS == 6) {
-      // nibble plane as for 4 bits, plus one 16-bit word of high bits per 32-bit word of nibbles: a multiply
-      // spreads four 2-bit fields over the four code bytes (kv_layout.cuh)
+      // nibble plane as for 4 bits; one 32-bit word of high bits serves both tokens (g and g + 8) of this lane,
+      // every 2-bit field already at the byte of its code (kv_layout.cuh)
+      const uint32_t hb = *reinterpret_cast<const uint32_t*>(blob + kPageTokens * kD / 2 + cg * 128 + g * 16 + t4 * 4);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const uint32_t w = *reinterpret_cast<const uint32_t*>(blob + cg * 256 + (nt * 8 + g) * 16 + t4 * 4);
-        const uint32_t hb = *reinterpret_cast<const uint16_t*>(blob + kPageTokens * kD / 2 + cg * 128 + (nt * 8 + g) * 8 + t4 * 2);
-        const uint32_t lo = (w & 0x0F0F0F0Fu) | (((hb & 0xFFu) * 0x410410u) & 0x30303030u);
-        const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) | (((hb >> 8) * 0x410410u) & 0x30303030u);
+        const uint32_t h1 = nt == 0 ? hb : (hb << 4);
+        const uint32_t h2 = nt == 0 ? (hb >> 2) : (hb << 2);
+        const uint32_t lo = (w & 0x0F0F0F0Fu) | (h1 & 0x30303030u);
+        const uint32_t hi = ((w >> 4) & 0x0F0F0F0Fu) | (h2 & 0x30303030u);
         mma_f16(acc[nt], qf[cg * 2], u8x2_to_f16x2(lo, 0x5140u, 0x64206420u), u8x2_to_f16x2(lo, 0x5342u, 0x64206420u));
         mma_f16(acc[nt], qf[cg * 2 + 1], u8x2_to_f16x2(hi, 0x5140u, 0x64206420u),
                 u8x2_to_f16x2(hi, 0x5342u, 0x64206420u));
@@ -213,14 +215,12 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
       uint32_t le = lo & 0x0F0F0F0Fu, lod = (lo >> 4) & 0x0F0F0F0Fu;
       uint32_t he = hi & 0x0F0F0F0Fu, hod = (hi >> 4) & 0x0F0F0F0Fu;
       if (VBITS == 6) {
-        // high bits: one 16-bit word per nibble word (low byte = even token, high byte = odd token)
-        const uint8_t* hp = vcodes + kPageTokens * kD / 2;
-        const uint32_t hl = *reinterpret_cast<const uint16_t*>(hp + t4 * 64 + chunk * 2);
-        const uint32_t hh = *reinterpret_cast<const uint16_t*>(hp + (t4 + 4) * 64 + chunk * 2);
-        le |= ((hl & 0xFFu) * 0x410410u) & 0x30303030u;
-        lod |= ((hl >> 8) * 0x410410u) & 0x30303030u;
-        he |= ((hh & 0xFFu) * 0x410410u) & 0x30303030u;
-        hod |= ((hh >> 8) * 0x410410u) & 0x30303030u;
+        // high bits: one 32-bit word for both token pairs (t4 and t4 + 4) of this lane, fields in place
+        const uint32_t hw = *reinterpret_cast<const uint32_t*>(vcodes + kPageTokens * kD / 2 + t4 * 128 + chunk * 4);
+        le |= hw & 0x30303030u;
+        lod |= (hw >> 2) & 0x30303030u;
+        he |= (hw << 4) & 0x30303030u;
+        hod |= (hw << 2) & 0x30303030u;
       }
       const uint32_t vbias = VBITS == 6 ? 0x64206420u : 0x64086408u;
 #pragma unroll

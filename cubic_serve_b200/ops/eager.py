@@ -96,15 +96,17 @@ def _v_pos(bits: int, d: int, tok: torch.Tensor, ch: torch.Tensor):
 
 
 def _k_hi_pos(d: int, tok: torch.Tensor, ch: torch.Tensor):
-    """6-bit K: byte offset of the 16-bit word of high bits (from the start of the code region) and bit shift."""
+    """6-bit K: byte offset of the 32-bit word of high bits (from the start of the code region) and bit shift."""
     c = ch & 31
-    return PAGE_TOKENS * d // 2 + (ch >> 5) * 128 + tok * 8 + ((c & 15) >> 2) * 2, torch.where(c >= 16, 8, 0) + 2 * (c & 3)
+    shift = 8 * (c & 3) + torch.where(tok >= 8, 0, 4) + torch.where(c >= 16, 2, 0)
+    return PAGE_TOKENS * d // 2 + (ch >> 5) * 128 + (tok & 7) * 16 + ((c & 15) >> 2) * 4, shift
 
 
 def _v_hi_pos(d: int, tok: torch.Tensor, ch: torch.Tensor):
     p = tok >> 1
     chunk = (ch >> 2) ^ ((p & 3) << 2)
-    return PAGE_TOKENS * d // 2 + p * (d // 2) + chunk * 2, torch.where((tok & 1) == 1, 8, 0) + 2 * (ch & 3)
+    shift = 8 * (ch & 3) + torch.where(p >= 4, 0, 4) + torch.where((tok & 1) == 1, 2, 0)
+    return PAGE_TOKENS * d // 2 + (p & 3) * d + chunk * 4, shift
 
 
 def blob_layout(d: int, k_bits: int, v_bits: int) -> dict:
@@ -123,11 +125,12 @@ def decode_cache_page(blob: torch.Tensor, d: int, k_bits: int, v_bits: int):
 
     def codes(region_off: int, pos, shift, bits, hi=None):
         if bits == 6:
-            # nibble plane (4-bit layout) + plane of the two high bits, read as little-endian 16-bit words
+            # nibble plane (4-bit layout) + plane of the two high bits, read as little-endian 32-bit words
             low = (b32[region_off + pos] >> shift) & 15
             hpos, hshift = hi
-            word = b32[region_off + hpos] | (b32[region_off + hpos + 1] << 8)
-            raw = low | (((word >> hshift) & 3) << 4)
+            word = (b32[region_off + hpos].long() | (b32[region_off + hpos + 1].long() << 8)
+                    | (b32[region_off + hpos + 2].long() << 16) | (b32[region_off + hpos + 3].long() << 24))
+            raw = (low.long() | (((word >> hshift) & 3) << 4)).to(torch.int32)
         else:
             raw = (b32[region_off + pos] >> shift) & ((1 << bits) - 1 if bits < 8 else 255)
         return (raw - (1 << (bits - 1))).float()
