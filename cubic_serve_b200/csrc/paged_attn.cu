@@ -78,7 +78,9 @@ struct WarpState {
   float o[16][4];   // O accumulators: n-tile (cg*4 + sub) x {row g: 2 cols, row g+8: 2 cols}
 };
 
-template <int KBITS, int VBITS>
+// UPPER = false: MMA rows 8..15 of the block hold no query (decode: one position x G <= 8 heads), so their scores,
+// softmax state and output rescaling are skipped; the tensor-core instructions still compute them, at no cost.
+template <int KBITS, int VBITS, bool UPPER>
 __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout& lay, const uint32_t (&qf)[8][4],
                                              WarpState& st, int page_tok0, int limit_lo, int limit_hi, int g,
                                              int t4) {
@@ -143,8 +145,10 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
       const float k0 = ksc[(nt * 8 + 2 * t4) * 4 + cg], k1 = ksc[(nt * 8 + 2 * t4 + 1) * 4 + cg];
       s[nt][0] = fmaf(acc[nt][0], k0, s[nt][0]);
       s[nt][1] = fmaf(acc[nt][1], k1, s[nt][1]);
-      s[nt][2] = fmaf(acc[nt][2], k0, s[nt][2]);
-      s[nt][3] = fmaf(acc[nt][3], k1, s[nt][3]);
+      if (UPPER) {
+        s[nt][2] = fmaf(acc[nt][2], k0, s[nt][2]);
+        s[nt][3] = fmaf(acc[nt][3], k1, s[nt][3]);
+      }
     }
   }
   // ---- causal / length mask and online softmax (log2 domain; Q carries the scale)
@@ -152,15 +156,15 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < (UPPER ? 4 : 2); ++c) {
       const int tok = page_tok0 + nt * 8 + 2 * t4 + (c & 1);
       const int lim = (c < 2) ? limit_lo : limit_hi;
       if (tok >= lim) s[nt][c] = -INFINITY;
       mx[c >> 1] = fmaxf(mx[c >> 1], s[nt][c]);
     }
-  float alpha[2], muse[2];
+  float alpha[2] = {1.f, 1.f}, muse[2] = {0.f, 0.f};
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
+  for (int r = 0; r < (UPPER ? 2 : 1); ++r) {
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
     mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     const float mnew = fmaxf(st.m[r], mx[r]);
@@ -174,15 +178,24 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
   for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      pr[nt][c] = fast_exp2(s[nt][c] - muse[c >> 1]);
-      st.l[c >> 1] += pr[nt][c];
+      if (UPPER || c < 2) {
+        pr[nt][c] = fast_exp2(s[nt][c] - muse[c >> 1]);
+        st.l[c >> 1] += pr[nt][c];
+      } else {
+        pr[nt][c] = 0.f;
+      }
     }
+  // the running maximum settles after the first pages: skip the 64 multiplies when no row's maximum moved
+  if (__any_sync(0xffffffffu, alpha[0] != 1.f || (UPPER && alpha[1] != 1.f))) {
 #pragma unroll
-  for (int n = 0; n < 16; ++n) {
-    st.o[n][0] *= alpha[0];
-    st.o[n][1] *= alpha[0];
-    st.o[n][2] *= alpha[1];
-    st.o[n][3] *= alpha[1];
+    for (int n = 0; n < 16; ++n) {
+      st.o[n][0] *= alpha[0];
+      st.o[n][1] *= alpha[0];
+      if (UPPER) {
+        st.o[n][2] *= alpha[1];
+        st.o[n][3] *= alpha[1];
+      }
+    }
   }
   // ---- O += P V, V group scales folded into P per channel group
 #pragma unroll
@@ -196,9 +209,9 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
     const float v11 = (9 + 2 * t4 < vis) ? vsc[(8 + 2 * t4 + 1) * 4 + cg] : 0.f;
     uint32_t a[4];
     a[0] = pack_f16x2(pr[0][0] * v00, pr[0][1] * v01);
-    a[1] = pack_f16x2(pr[0][2] * v00, pr[0][3] * v01);
+    a[1] = UPPER ? pack_f16x2(pr[0][2] * v00, pr[0][3] * v01) : 0u;
     a[2] = pack_f16x2(pr[1][0] * v10, pr[1][1] * v11);
-    a[3] = pack_f16x2(pr[1][2] * v10, pr[1][3] * v11);
+    a[3] = UPPER ? pack_f16x2(pr[1][2] * v10, pr[1][3] * v11) : 0u;
     const int chunk = (cg * 8 + g) ^ ((t4 & 3) << 2);
     if (VBITS == 8) {
       const uint2 lo = *reinterpret_cast<const uint2*>(vcodes + t4 * 256 + chunk * 8);
@@ -270,6 +283,7 @@ paged_attn_kernel(const AttnParams p) {
   const int pg_lo = split * pps;
   const int pg_hi = min(total_pages, pg_lo + pps);
 
+  const bool upper_rows = qcount * G > 8;     // uniform over the CTA: do MMA rows 8..15 hold a query?
   int limit[2];
   uint32_t qf[8][4];
 #pragma unroll
@@ -322,8 +336,12 @@ paged_attn_kernel(const AttnParams p) {
     ok = mbar_wait_t<20>(smem_u32(&my_bars[s]), static_cast<uint32_t>(i / kAttnStages) & 1u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
-    process_page<KBITS, VBITS>(my_stages + s * stage_stride, p.lay, qf, st, (first + i * kAttnWarps) * kPageTokens,
-                               limit[0], limit[1], g, t4);
+    if (upper_rows)
+      process_page<KBITS, VBITS, true>(my_stages + s * stage_stride, p.lay, qf, st,
+                                       (first + i * kAttnWarps) * kPageTokens, limit[0], limit[1], g, t4);
+    else
+      process_page<KBITS, VBITS, false>(my_stages + s * stage_stride, p.lay, qf, st,
+                                        (first + i * kAttnWarps) * kPageTokens, limit[0], limit[1], g, t4);
     __syncwarp();
     if (lane == 0 && i + kAttnStages < my_pages) issue(i + kAttnStages);
   }
