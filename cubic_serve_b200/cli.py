@@ -126,6 +126,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--model-adapter")
     g.add_argument("--operator-config")
     g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--operator-config", help="JSON file with launch policies of the native kernels (ops/strategies.py)")
     return ap
 
 
@@ -142,6 +143,11 @@ def _serve(args) -> int:
     devices = parse_devices(args.devices)
     tp = args.tp_size or max(1, len(devices) // args.pp_size)
     validate_topology(devices, tp, args.pp_size, args.ep_size, spec)
+    if args.operator_config:
+        # through the environment as well, so that spawned rank workers install the same policies
+        from .ops import strategies
+        strategies.install(strategies.load_operator_config(args.operator_config))
+        os.environ["CUBIC_OPERATOR_CONFIG"] = os.path.abspath(args.operator_config)
     os.environ.setdefault("OMP_NUM_THREADS", "4")
     os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
     sys.setswitchinterval(0.001)

@@ -91,8 +91,10 @@ class BatchBuilder:
         self._page_rows: list[tuple[int, int]] = [(-2, 0)] * max_rows
 
     def _splits(self, row_blocks: int) -> int:
+        from ..ops.strategies import active
+        a = active().attention
         ctas = max(1, row_blocks * self.kv_heads)
-        return int(min(32, max(1, -(-296 // ctas))))
+        return int(min(a.max_splits, max(1, -(-a.target_ctas // ctas))))
 
     def fill(self, segs: list[Segment], pad_rows_to: int | None = None):
         return self._fill(segs, pad_rows_to)

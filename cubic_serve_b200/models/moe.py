@@ -45,7 +45,10 @@ class MoeLayer:
 
     def ensure_scratch(self, max_tokens: int, hidden: int, device) -> K.MoeScratch:
         if self.scratch is None or self.scratch.topk_ids.shape[0] < max_tokens:
-            mb = 64 if max_tokens * self.top_k >= 32 * self.expert_count else 32
+            from ..ops.strategies import active
+            pol = active().moe
+            big = max_tokens * self.top_k >= pol.large_routes_per_expert * self.expert_count
+            mb = pol.rows_per_item_large if big else pol.rows_per_item_small
             self.scratch = K.MoeScratch(max_tokens, self.top_k, hidden, self.gate_up.n, self.expert_count, mb, device)
             self.logits = torch.empty(max_tokens, self.num_experts, dtype=torch.bfloat16, device=device)
             self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)

@@ -76,13 +76,15 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     Every split CTA writes an fp32 partial tile and the last one sums them (vectorised, from L2), so a split
     pays off while each CTA still has >= 8 k-blocks of work.
     """
+    from .strategies import active
+    g = active().gemm
     n_tiles = -(-n // 128)
     m_tiles = -(-m // 256)
     tiles = n_tiles * m_tiles
     k_blocks = k // 64
-    if tiles * 2 > sms or k_blocks < 16:
+    if tiles * 2 > sms or k_blocks < 2 * g.split_k_min_blocks:
         return 1
-    return max(1, min(sms // tiles, k_blocks // 8, 8))
+    return max(1, min(sms // tiles, k_blocks // g.split_k_min_blocks, g.split_k_max))
 
 
 def use_stream_k(m: int, n: int, fmt: int, sms: int = 148) -> bool:
@@ -95,10 +97,12 @@ def use_stream_k(m: int, n: int, fmt: int, sms: int = 148) -> bool:
     than one CTA per (tile, split), and at 256 batch rows both kernels are bound by the activation-tile
     traffic into shared memory, where the reduction of 128 KiB partials costs more than the wave it saves.
     """
+    from .strategies import active
+    g = active().gemm
     tiles = -(-n // 128) * -(-m // 256)
-    if tiles <= sms:
+    if tiles <= g.stream_k_min_tile_ratio * sms:
         return False
-    return m <= 128 or fmt == FMT_BF16
+    return m <= g.stream_k_max_rows or (fmt == FMT_BF16 and g.stream_k_bf16)
 
 
 def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
@@ -123,7 +127,8 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
     ws = ws or workspace(x.device)
     l = native.lib()
     if splits is None and min_units is None and use_stream_k(m, w.n, w.fmt, sm_count(x.device)):
-        min_units = 0
+        from .strategies import active
+        min_units = active().gemm.stream_k_min_units
     if splits is None and min_units is not None:
         code = l.cb_wq_gemm_sk(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
                                None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual),
