@@ -124,7 +124,6 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
     g.add_argument("--startup-numerical-audit", action="store_true")
     g.add_argument("--model-adapter")
-    g.add_argument("--operator-config")
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--operator-config", help="JSON file with launch policies of the native kernels (ops/strategies.py)")
     return ap
