@@ -45,6 +45,12 @@ static constexpr int kSkMaxAx = 6;
 static constexpr int kSkMaxC = 8;
 static constexpr int kSkCStageBytes = kCodeBytes + kMetaBytes;
 
+// One contiguous run of k-blocks of one tile, as dealt to a CTA.
+struct SkSegment {
+  int tile, kb_lo, kb_hi;
+  int part, parts;               // this run is part `part` of `parts` runs that make up the tile
+};
+
 struct __align__(8) SkCtl {
   uint64_t x_full[kSkMaxAx];     // activation (and bf16 weight) tile landed            (transaction bytes)
   uint64_t a_ready[kSkMaxAx];    // decoded weight tile stored by the 8 warps of a group (8 arrivals)
@@ -58,12 +64,11 @@ struct __align__(8) SkCtl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t is_last;
-};
-
-// One contiguous run of k-blocks of one tile, as dealt to a CTA.
-struct SkSegment {
-  int tile, kb_lo, kb_hi;
-  int part, parts;               // this run is part `part` of `parts` runs that make up the tile
+  // streamed tiles whose LAST partial arrived from this CTA while it still had segments to run: their fix-up
+  // waits for the end of the CTA, where all 20 epilogue + decode warps do it (at most two: the CTA's first run
+  // and the run before its whole tiles)
+  uint32_t deferred_count;
+  SkSegment deferred[2];
 };
 
 // The deal.  Identical arithmetic on every thread of every role, so all roles of a CTA walk the same list.
@@ -300,6 +305,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     mbar_init(smem_u32(&ctl->tail_full), 1);
     ctl->abort_flag = 0;
     ctl->is_last = 0;
+    ctl->deferred_count = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -497,6 +503,26 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             red_relaxed_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
         }
       }
+      // fix-ups deferred by the earlier segments of this CTA (see SkCtl::deferred), now with 640 threads
+      tail_bar();
+      const uint32_t n_def = ctl->deferred_count;
+      for (uint32_t di = 0; di < n_def; ++di) {
+        const SkSegment ds = ctl->deferred[di];
+        const SkCoords c = sk_coords(p, ds.tile);
+        if (!*abort_flag) {
+          __threadfence();
+          sk_reduce_write<4>(p, ds, cta, tt, nthr, c.m0, c.rows, c.n_tile * kTileN, nullptr);
+        }
+        if (p.tp.mode & kTpScatterPush) {
+          tail_bar();
+          if (tt == 0 && !*abort_flag) {
+            const int m_last = min(p.M, c.m0 + p.mb) - 1;
+            fence_acq_rel_sys();
+            for (int o = c.m0 / p.tp.rows_per_rank; o <= m_last / p.tp.rows_per_rank; ++o)
+              red_relaxed_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
+          }
+        }
+      }
       if (trace && tt == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
     };
 
@@ -651,10 +677,11 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           epi_bar();
           const bool last = ctl->is_last != 0;
           epi_bar();                                   // is_last has been read by all before it can change again
-          if (last && !*abort_flag) {
-            __threadfence();
-            finalized = true;
-            sk_reduce_write<4>(p, seg, cta, et, kSkEpiWarps * 32, m0, rows_here, n_base, nullptr);
+          if (last && !*abort_flag && et == 0) {
+            // summing the partials here would hold these four warps (and with them the accumulator hand-off of
+            // the running main loop) for tens of microseconds: note the tile, finish it at the end of the CTA
+            ctl->deferred[ctl->deferred_count] = seg;
+            ctl->deferred_count = ctl->deferred_count + 1;
           }
         }
         if (p.tp.mode & kTpScatterPush) {

@@ -90,12 +90,13 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
 def use_stream_k(m: int, n: int, fmt: int, sms: int = 148) -> bool:
     """Which GEMM kernel serves a shape when the caller does not say.
 
-    Measured on a B200 inside CUDA graphs (cubic4, K = 4096): the persistent stream-K kernel is 1.45-1.55x
-    faster when there are more weight tiles than SMs and at most 128 batch rows (it removes the second,
-    partly empty wave: N = 24576 runs 69 -> 45 us), and 5 % faster for the bf16 lm_head; with fewer tiles
-    than SMs its fixed costs (start-up, fp32 partial tiles summed by the last CTA) make it 10-25 % slower
-    than one CTA per (tile, split), and at 256 batch rows both kernels are bound by the activation-tile
-    traffic into shared memory, where the reduction of 128 KiB partials costs more than the wave it saves.
+    Measured on a B200 inside CUDA graphs (cubic4, K = 4096): the persistent stream-K kernel wins when there are
+    more weight tiles than SMs, because it removes the second, partly empty wave: N = 24576 runs 69 -> 45 us at
+    16-64 batch rows, 70 -> 54 us at 128 and 80 -> 70 us at 256 (the fix-up of a streamed tile is deferred to the
+    end of its CTA and done by 640 threads), and the bf16 lm_head is 5 % faster.  With fewer tiles than SMs its
+    fixed costs (start-up, fp32 partial tiles summed by the last CTA) make it 10-25 % slower than one CTA per
+    (tile, split); batches of more than 256 rows (several row tiles, prefill) stay on the per-tile kernel.
+    The thresholds live in the operator configuration (``ops/strategies.py``).
     """
     from .strategies import active
     g = active().gemm

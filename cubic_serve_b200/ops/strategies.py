@@ -22,7 +22,7 @@ from dataclasses import dataclass, field, fields, replace
 
 @dataclass(frozen=True)
 class GemmPolicy:
-    stream_k_max_rows: int = 128        # persistent kernel for quantized weights only up to this many batch rows ...
+    stream_k_max_rows: int = 256        # persistent kernel for quantized weights only up to this many batch rows ...
     stream_k_min_tile_ratio: float = 1.0   # ... and only when tiles > ratio * SMs (wave quantisation is what it removes)
     stream_k_bf16: bool = True          # bf16 weights (lm_head): persistent kernel whenever tiles > SMs
     stream_k_min_units: int = 0         # 0 = the kernel's own cost model

@@ -28,10 +28,11 @@ def test_policy_drives_kernel_choice():
     old = S.active()
     try:
         S.install(S.OperatorConfig())
-        assert K.use_stream_k(64, 24576, FMT_CUBIC4) and not K.use_stream_k(256, 24576, FMT_CUBIC4)
+        assert K.use_stream_k(64, 24576, FMT_CUBIC4) and K.use_stream_k(256, 24576, FMT_CUBIC4)
+        assert not K.use_stream_k(512, 24576, FMT_CUBIC4)
         assert K.use_stream_k(256, 151936, FMT_BF16) and not K.use_stream_k(16, 6144, FMT_CUBIC4)
         assert K.choose_splits(256, 4096, 4096) == 4
-        S.install(S.operator_config_from_dict({"gemm": {"stream_k_max_rows": 256, "split_k_max": 2}}))
-        assert K.use_stream_k(256, 24576, FMT_CUBIC4) and K.choose_splits(256, 4096, 4096) == 2
+        S.install(S.operator_config_from_dict({"gemm": {"stream_k_max_rows": 64, "split_k_max": 2}}))
+        assert not K.use_stream_k(256, 24576, FMT_CUBIC4) and K.choose_splits(256, 4096, 4096) == 2
     finally:
         S.install(old)
