@@ -104,9 +104,7 @@ swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ 
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float2 a = __bfloat1622float2(gp[j]), b = __bfloat1622float2(up[j]);
-    a.x = a.x / (1.f + __expf(-a.x));
-    a.y = a.y / (1.f + __expf(-a.y));
-    op[j] = __floats2bfloat162_rn(a.x * b.x, a.y * b.y);
+    op[j] = __floats2bfloat162_rn(cb::silu_fast(a.x) * b.x, cb::silu_fast(a.y) * b.y);
   }
   reinterpret_cast<uint4*>(out + row * I)[v] = o;
 }

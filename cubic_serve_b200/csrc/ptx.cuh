@@ -288,6 +288,13 @@ __device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t* p, uint32_t v
 }
 
 // ---------------------------------------------------------------- misc math
+// silu(x) = x / (1 + e^-x) with the approximate exponential and reciprocal (ex2.approx, rcp.approx): six
+// instructions.  e^-x overflows to +inf below x = -88.7 and the quotient is then -0, the limit.  Every kernel
+// that applies SwiGLU uses this one function, so the fused and the stand-alone activation agree bit for bit.
+__device__ __forceinline__ float silu_fast(float x) {
+  return __fdividef(x, 1.f + __expf(-x));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -298,6 +298,14 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const int rows_here = min(p.mb, m_end - m0);
         const int n_base = n_tile * kTileN;
         const bool vec_ok = (p.ldy & 7) == 0 && (p.N & 7) == 0;
+        if (p.swiglu) {
+          // 64 activation features per tile row: 16 items of four
+          for (int idx = dq; idx < rows_here * 16; idx += kNumDequantWarps * 32) {
+            const int mm = idx >> 4, j0 = (idx & 15) * 4;
+            const float* gp = stg + mm * kTileN + act_gate_col(j0);
+            store_act4(p, m0 + mm, n_tile, j0, *reinterpret_cast<const float4*>(gp), *reinterpret_cast<const float4*>(gp + 16));
+          }
+        } else
         for (int idx = dq; idx < rows_here * (kTileN / 8); idx += kNumDequantWarps * 32) {
           const int mm = idx >> 4;                 // kTileN / 8 = 16 segments of 8 features per row
           const int n0 = n_base + (idx & 15) * 8;
@@ -371,6 +379,22 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // L2 (.cg), 8-byte bf16 stores
         const int rows_here = min(p.mb, m_end - m0);
         const int n_base = n_tile * kTileN;
+        if (p.swiglu) {
+          for (int idx = dq; idx < rows_here * 16; idx += kNumDequantWarps * 32) {
+            const int mm = idx >> 4, j0 = (idx & 15) * 4;
+            const size_t e = static_cast<size_t>(mm) * kTileN + act_gate_col(j0);
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+            for (int sp = 0; sp < p.splits; ++sp) {
+              const float4 a = __ldcg(reinterpret_cast<const float4*>(wsb + sp * part_elems + e));
+              const float4 b = __ldcg(reinterpret_cast<const float4*>(wsb + sp * part_elems + e + 16));
+              g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+              u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+            }
+            g.x *= p.alpha; g.y *= p.alpha; g.z *= p.alpha; g.w *= p.alpha;
+            u.x *= p.alpha; u.y *= p.alpha; u.z *= p.alpha; u.w *= p.alpha;
+            store_act4(p, m0 + mm, n_tile, j0, g, u);
+          }
+        } else
         for (int idx = dq; idx < rows_here * (kTileN / 4); idx += kNumDequantWarps * 32) {
           const int mm = idx >> 5;             // kTileN / 4 = 32 float4 per row
           const int c4 = (idx & 31) * 4;
@@ -521,6 +545,10 @@ int cb_wq_gemm_sk(int fmt, const void* x, int ldx, const void* codes, const void
                   const void* residual, float alpha, int M, int N, int K, int group_k, int min_units, void* workspace,
                   long long workspace_bytes, void* counters, void* status, void* stream, const CbTpLink* link);
 
+// Epilogue of the NEXT launch made by this thread: 1 = fused SwiGLU (the weight rows are gate / up interleaved, the
+// output has N / 2 columns).  Set and cleared by the *_act entry points only.
+static thread_local int g_epilogue_swiglu = 0;
+
 static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                             const void* residual, float alpha, int M, int N, int K, int group_k, int splits,
                             void* workspace, void* counters, void* status, void* stream, const CbTpLink* link,
@@ -557,6 +585,8 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.counters = static_cast<uint32_t*>(counters);
   p.status = static_cast<uint32_t*>(status);
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.alpha = alpha;
+  p.swiglu = g_epilogue_swiglu;
+  if (p.swiglu && (residual || (link && (link->mode & kTpScatterPush)))) return -51;
   p.tp.mode = kTpNone;
   if (link && link->mode != kTpNone) {
     if (link->size < 1 || link->size > kMaxRanks || link->rows_per_rank <= 0 || (link->rows_per_rank % 16) != 0) return -30;
@@ -631,8 +661,40 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
 
 static int g_grouped_persistent = 1;
 
+// Gate/up projection with the activation fused: y[M, N / 2] = silu(x Wg^T) * (x Wu^T), W in the interleaved row
+// order (16 gate rows, 16 up rows, ...).  `stream_k` picks the persistent kernel; `splits` applies to the per-tile one.
+// `link` may make the kernel wait for gathered activation rows; the output is always local.
+int cb_wq_gemm_act(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy, float alpha,
+                   int M, int N, int K, int group_k, int stream_k, int splits, int min_units, void* workspace,
+                   long long workspace_bytes, void* counters, void* status, void* stream, const CbTpLink* link) {
+  if ((N % 32) != 0 || ldy < N / 2) return -50;
+  g_epilogue_swiglu = 1;
+  const int rc = wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, M, N, K, group_k, stream_k ? 1 : splits,
+                                  workspace, counters, status, stream, link, stream_k != 0, min_units, workspace_bytes);
+  g_epilogue_swiglu = 0;
+  return rc;
+}
+
 // 1 (default): grouped GEMMs run on the persistent kernel; 0: one CTA per (work item, weight tile).
 void cb_wq_gemm_grouped_mode(int persistent) { g_grouped_persistent = persistent; }
+
+int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                       float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
+                       int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
+                       void* stream);
+
+// Grouped gate/up projection with the fused SwiGLU epilogue (every expert's rows interleaved): y has N / 2 columns.
+int cb_wq_gemm_grouped_act(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                           float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
+                           int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
+                           void* stream) {
+  if ((N % 32) != 0 || ldy < N / 2) return -50;
+  g_epilogue_swiglu = 1;
+  const int rc = cb_wq_gemm_grouped(fmt, x, ldx, codes, meta, y, ldy, alpha, total_rows, N, K, group_k, tiles, max_items,
+                                    mb, num_experts, code_stride, meta_stride, status, stream);
+  g_epilogue_swiglu = 0;
+  return rc;
+}
 
 int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                        float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,

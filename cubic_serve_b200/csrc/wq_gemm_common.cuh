@@ -67,6 +67,10 @@ struct WqGemmParams {
   const int* group_tiles;
   size_t group_code_stride, group_meta_stride;
   unsigned long long* trace;  // optional pipeline timeline of CTA (0,0,0): [iteration][8] clock64 stamps
+  // fused SwiGLU epilogue (gate/up projection): the weight rows were interleaved at load time so that a
+  // 128-row tile holds 64 output features as four blocks of {16 gate rows, 16 up rows}; the epilogue writes
+  // act[m, 64 * n_tile + 16 * q + i] = silu(tile row 32 q + i) * (tile row 32 q + 16 + i), ldy = row stride of act
+  int swiglu;
   // persistent stream-K kernel only (wq_gemm_sk.cu)
   int n_tiles, tiles;       // tile = m_tile * n_tiles + n_tile
   int sk_tiles, sk_ctas;    // tiles [0, sk_tiles) are dealt by k-block to CTAs [0, sk_ctas); the rest are whole
@@ -95,6 +99,35 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
   }
   return true;
 }
+
+// SwiGLU on a pair of accumulators, with the rounding points of the unfused path (the projection's output is
+// rounded to bf16, the activation is computed in fp32 from those and rounded once)
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  g = __bfloat162float(__float2bfloat16(g));
+  u = __bfloat162float(__float2bfloat16(u));
+  return silu_fast(g) * u;
+}
+// Four consecutive activation features j0..j0+3 (j0 % 4 == 0) of tile `n_tile` for row m from the fp32 gate / up
+// values of the tile row (already scaled by alpha)
+__device__ __forceinline__ void store_act4(const WqGemmParams& p, int m, int n_tile, int j0, const float4 g, const float4 u) {
+  const int n_out = p.N >> 1;
+  const int n0 = n_tile * 64 + j0;
+  if (n0 >= n_out) return;
+  const float a[4] = {silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z), silu_mul(g.w, u.w)};
+  __nv_bfloat16* dst = p.y + static_cast<size_t>(m) * p.ldy + n0;
+  if ((p.ldy & 3) == 0 && n0 + 3 < n_out) {
+    uint2 ov;
+    ov.x = pack_bf16x2(a[0], a[1]);
+    ov.y = pack_bf16x2(a[2], a[3]);
+    *reinterpret_cast<uint2*>(dst) = ov;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (n0 + j < n_out) dst[j] = __float2bfloat16(a[j]);
+  }
+}
+// offset of activation feature j (0..63) of a tile inside a 128-float tile row: gate value there, up value 16 on
+__device__ __forceinline__ int act_gate_col(int j) { return ((j >> 4) << 5) + (j & 15); }
 
 // ---- packed bf16x2 decode ---------------------------------------------------
 // A 32-bit word holds 8 codes; nibble i (i < 4) is column 2i and nibble i + 4 is

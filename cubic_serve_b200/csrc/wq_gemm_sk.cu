@@ -212,6 +212,35 @@ __device__ __forceinline__ void sk_store4(const WqGemmParams& p, int m, int n0, 
   }
 }
 
+// The same fix-up with the fused SwiGLU epilogue: 16 items of four activation features per row, each from the gate
+// and the up float4 of every part.  Out of line: it runs once per streamed tile and its registers stay out of the
+// kernel's allocation.
+__device__ __noinline__ void sk_reduce_write_act(const WqGemmParams& p, const float* slots, int parts, int own_part,
+                                                 const float* own, int tid, int nthreads, int m0, int rows_here, int n_tile) {
+  const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
+  for (int idx = tid; idx < rows_here * 16; idx += nthreads) {
+    const int mm = idx >> 4, j0 = (idx & 15) * 4;
+    const int e = mm * kTileN + act_gate_col(j0);
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+    for (int sp = 0; sp < parts; ++sp) {
+      float4 a, b;
+      if (sp == own_part) {
+        a = *reinterpret_cast<const float4*>(own + e);
+        b = *reinterpret_cast<const float4*>(own + e + 16);
+      } else {
+        const float* src = slots + (static_cast<size_t>(sp) * 2 + (sp == 0 ? 1 : 0)) * part_elems;
+        a = __ldcg(reinterpret_cast<const float4*>(src + e));
+        b = __ldcg(reinterpret_cast<const float4*>(src + e + 16));
+      }
+      g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+      u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+    }
+    g.x *= p.alpha; g.y *= p.alpha; g.z *= p.alpha; g.w *= p.alpha;
+    u.x *= p.alpha; u.y *= p.alpha; u.z *= p.alpha; u.w *= p.alpha;
+    store_act4(p, m0 + mm, n_tile, j0, g, u);
+  }
+}
+
 // Fix-up of a streamed tile by the last CTA to arrive: sum the fp32 partials of all parts IN PART ORDER
 // (bit-identical whichever CTA happens to be last) and write the tile.  `own` (optional) is this CTA's own part
 // still in shared memory, read instead of its copy in L2.  kBatch items per thread are in flight at once: the
@@ -224,6 +253,10 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
   const int parts = seg.parts;
   const int own_part = own ? seg.part : -1;
   const float* slots = p.workspace + static_cast<size_t>(g_first) * 2 * part_elems;   // part q > 0 at + q * 2 * part_elems
+  if (p.swiglu) {
+    sk_reduce_write_act(p, slots, parts, own_part, own, tid, nthreads, m0, rows_here, n_base / kTileN);
+    return;
+  }
   const int items = rows_here * (kTileN / 4);
   for (int base = tid; base < items; base += nthreads * kBatch) {
     float4 acc[kBatch];
@@ -263,7 +296,7 @@ template <int FMT>
 __global__ void __launch_bounds__(kSkThreads, 1)
 wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
                   const __grid_constant__ CUtensorMap tmap_w,  // only for kFmtBf16
-                  const WqGemmParams p) {
+                  const __grid_constant__ WqGemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t x_bytes = static_cast<uint32_t>(p.mb) * 128u;
   const uint32_t ax_bytes = x_bytes + kATileBytes;
@@ -465,7 +498,16 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       tail_bar();
       bool finalized = whole;
       if (whole) {
-        if (ok)
+        if (ok && p.swiglu) {
+          for (int idx = tt; idx < rows_here * 16; idx += nthr) {
+            const int mm = idx >> 4, j0 = (idx & 15) * 4;
+            const float* gp = stg + mm * kTileN + act_gate_col(j0);
+            float4 g = *reinterpret_cast<const float4*>(gp), u = *reinterpret_cast<const float4*>(gp + 16);
+            g.x *= p.alpha; g.y *= p.alpha; g.z *= p.alpha; g.w *= p.alpha;
+            u.x *= p.alpha; u.y *= p.alpha; u.z *= p.alpha; u.w *= p.alpha;
+            store_act4(p, m0 + mm, n_base / kTileN, j0, g, u);
+          }
+        } else if (ok)
           for (int idx = tt; idx < rows_here * (kTileN / 4); idx += nthr)
             sk_store4(p, m0 + (idx >> 5), n_base + (idx & 31) * 4, *reinterpret_cast<const float4*>(stg + static_cast<size_t>(idx) * 4));
       } else {
@@ -642,14 +684,31 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int j = 0; j < 16; ++j) scr[j * 32 + lane] = __uint_as_float(acc[j]);
             __syncwarp();
+            if (whole && p.swiglu) {
+              // this warp's 32 tile rows are 16 gate + 16 up rows of the same 16 features: lane L owns rows
+              // (L >> 2) + 8 i, features 4 (L & 3) .. + 3 (all 32 lanes busy, 32 contiguous bytes per row)
+              const int a4 = (lane & 3) * 4;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int row = (lane >> 3) + 4 * i;
-              const float4 v = *reinterpret_cast<const float4*>(scr + row * 32 + f4);
-              if (!whole) {
-                *reinterpret_cast<float4*>(slot + static_cast<size_t>(c0 + row) * kTileN) = v;
-              } else if (c0 + row < rows_here) {
-                sk_store4(p, m0 + c0 + row, n_base + quad * 32 + f4, v);
+              for (int i = 0; i < 2; ++i) {
+                const int row = (lane >> 2) + 8 * i;
+                if (c0 + row < rows_here) {
+                  float4 g = *reinterpret_cast<const float4*>(scr + row * 32 + a4);
+                  float4 u = *reinterpret_cast<const float4*>(scr + row * 32 + 16 + a4);
+                  g.x *= p.alpha; g.y *= p.alpha; g.z *= p.alpha; g.w *= p.alpha;
+                  u.x *= p.alpha; u.y *= p.alpha; u.z *= p.alpha; u.w *= p.alpha;
+                  store_act4(p, m0 + c0 + row, n_base / kTileN, quad * 16 + a4, g, u);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int row = (lane >> 3) + 4 * i;
+                const float4 v = *reinterpret_cast<const float4*>(scr + row * 32 + f4);
+                if (!whole) {
+                  *reinterpret_cast<float4*>(slot + static_cast<size_t>(c0 + row) * kTileN) = v;
+                } else if (c0 + row < rows_here) {
+                  sk_store4(p, m0 + c0 + row, n_base + quad * 32 + f4, v);
+                }
               }
             }
             __syncwarp();                                  // the scratch is rewritten by the next chunk

@@ -199,6 +199,14 @@ class DecoderRunner:
         self.act = torch.empty(T, inter, dtype=bf, device=dev) if inter else None
         self.ws = K.workspace(dev)
         self.launches_per_step = 0
+        from ..ops.strategies import active
+        if active().gemm.fuse_swiglu and torch.device(dev).type == "cuda":
+            # gate / up rows interleaved once, so that the GEMM epilogue applies the activation (no [T, 2I] round trip)
+            for lw in weights.layers:
+                if lw.moe is not None:
+                    lw.moe.fuse_activation()
+                elif lw.gate_up is not None and (lw.gate_up.n // 2) % 16 == 0:
+                    lw.gate_up = wq_pack.swiglu_interleave(lw.gate_up)
         self.ep = None
         if cfg.is_moe and tp is not None and tp.fused is not None:
             # expert parallelism over the tensor-parallel group: fused dispatch / combine on the row-sharded stream
@@ -275,9 +283,7 @@ class DecoderRunner:
                     pending = out
             else:
                 gu, act = self.gu[t0:t1], self.act[t0:t1]
-                K.wq_gemm(x, lw.gate_up, out=gu, ws=self.ws)
-                K.swiglu(gu, out=act)
-                n += 3
+                n += 1 + K.gate_up_act(x, lw.gate_up, gu, act, ws=self.ws)
                 if self.tp is None:
                     K.wq_gemm(act, lw.down, out=h, residual=h, ws=self.ws)
                 else:
@@ -342,12 +348,11 @@ class DecoderRunner:
                 continue
             f.reduce_norm(lw.ln2, s, H, cfg.rms_eps, cfg.zero_centered_norm)
             gu, act = self.gu[:T], self.act[:T]
-            f.gemm_gather(lw.gate_up, gu, s)
-            K.swiglu(gu, out=act)
+            fused = 2 - f.gate_up_act(lw.gate_up, gu, act, s)
             s ^= 1
             f.gemm_scatter(act, lw.down, s)
             f.reduce_norm(nxt, s, H, cfg.rms_eps, cfg.zero_centered_norm)
-            n += 9
+            n += 9 - fused
         self.launches_per_step = n
         return s
 

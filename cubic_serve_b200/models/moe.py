@@ -43,6 +43,19 @@ class MoeLayer:
     scratch: K.MoeScratch | None = None
     launches: int = 7
 
+    def fuse_activation(self) -> None:
+        """Re-order every expert's ``[gate; up]`` rows so that the grouped GEMM applies SwiGLU in its epilogue."""
+        self.gate_up = wq_pack.swiglu_interleave(self.gate_up, stacked=True)
+
+    def experts(self, sc: K.MoeScratch, rows: int, ws) -> None:
+        """Grouped gate/up GEMM, SwiGLU, grouped down GEMM over the sorted rows ``sc.xs`` -> ``sc.y``."""
+        if self.gate_up.act_interleaved:
+            K.wq_gemm_grouped(sc.xs, self.gate_up, sc.act, rows, sc, self.strides[0], self.strides[1], ws, swiglu=True)
+        else:
+            K.wq_gemm_grouped(sc.xs, self.gate_up, sc.gu, rows, sc, self.strides[0], self.strides[1], ws)
+            K.swiglu(sc.gu[:rows], out=sc.act[:rows])
+        K.wq_gemm_grouped(sc.act, self.down, sc.y, rows, sc, self.strides[2], self.strides[3], ws)
+
     def ensure_scratch(self, max_tokens: int, hidden: int, device) -> K.MoeScratch:
         if self.scratch is None or self.scratch.topk_ids.shape[0] < max_tokens:
             from ..ops.strategies import active
@@ -66,9 +79,7 @@ class MoeLayer:
         logits = K.wq_gemm(x, self.router, out=self.logits[:t], ws=ws)
         K.moe_route(logits, x, self.top_k, sc, self.normalize, self.expert_lo, self.expert_count)
         rows = t * self.top_k
-        K.wq_gemm_grouped(sc.xs, self.gate_up, sc.gu, rows, sc, self.strides[0], self.strides[1], ws)
-        K.swiglu(sc.gu[:rows], out=sc.act[:rows])
-        K.wq_gemm_grouped(sc.act, self.down, sc.y, rows, sc, self.strides[2], self.strides[3], ws)
+        self.experts(sc, rows, ws)
         return K.moe_combine(sc.y, sc, t, self.out[:t] if out is None else out, residual)
 
 

@@ -61,6 +61,10 @@ class MtpRunner:
         self.emb = torch.empty(T, H, dtype=bf, device=dev)
         self.h = torch.empty(T, H, dtype=bf, device=dev)
         self.launches = 0
+        from ..ops.strategies import active
+        lw = weights.layer
+        if active().gemm.fuse_swiglu and torch.device(dev).type == "cuda" and (lw.gate_up.n // 2) % 16 == 0:
+            lw.gate_up = wq_pack.swiglu_interleave(lw.gate_up)
 
     def forward(self, b: StepBatch, prev_hidden: torch.Tensor) -> torch.Tensor:
         """One pass over ``b.num_tokens`` rows.  ``prev_hidden[i]`` is the hidden state that precedes row i.
@@ -90,10 +94,9 @@ class MtpRunner:
         K.wq_gemm(attn, lw.o, out=h, residual=h, ws=t.ws)
         K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x)
         gu, act = t.gu[:T], t.act[:T]
-        K.wq_gemm(x, lw.gate_up, out=gu, ws=t.ws)
-        K.swiglu(gu, out=act)
+        fused = 2 - K.gate_up_act(x, lw.gate_up, gu, act, ws=t.ws)
         K.wq_gemm(act, lw.down, out=h, residual=h, ws=t.ws)
-        self.launches = 16
+        self.launches = 16 - fused
         return h
 
     def logits(self, hidden: torch.Tensor, rows: int, out: torch.Tensor) -> torch.Tensor:

@@ -153,6 +153,52 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
     return out
 
 
+def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None, splits: int | None = None,
+                ws: Workspace | None = None, min_units: int | None = None, link=None) -> torch.Tensor:
+    """Gate/up projection with SwiGLU in the GEMM epilogue: ``out[M, N/2] = silu(x Wg^T) * (x Wu^T)``.
+
+    ``w`` is the ``[gate; up]`` matrix in the interleaved row order (``wq_pack.swiglu_interleave``).  The projection
+    ``link`` (gather-wait only) as in ``wq_gemm``.  The projection is rounded to bf16 before the activation, as when ``wq_gemm`` and ``swiglu`` run as two kernels, so both paths
+    give the same values; the ``[M, N]`` intermediate is never written.  Kernel choice as in ``wq_gemm``.
+    """
+    assert w.act_interleaved, "weight rows are not in the SwiGLU order"
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    m, k = x.shape
+    assert k == w.k, (k, w.k)
+    if out is None:
+        out = torch.empty((m, w.n // 2), dtype=torch.bfloat16, device=x.device)
+    assert out.stride(1) == 1 and out.shape == (m, w.n // 2)
+    ws = ws or workspace(x.device)
+    l = native.lib()
+    stream_k = splits is None and (min_units is not None or use_stream_k(m, w.n, w.fmt, sm_count(x.device)))
+    if stream_k and min_units is None:
+        from .strategies import active
+        min_units = active().gemm.stream_k_min_units
+    if not stream_k:
+        if splits is None:
+            splits = choose_splits(m, w.n, k)
+        if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
+            splits = 1
+    code = l.cb_wq_gemm_act(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta), out.data_ptr(),
+                            out.stride(0), float(w.alpha), m, w.n, k, w.group_k, int(stream_k), int(splits or 1),
+                            int(min_units or 0), ws.gemm.data_ptr(), ws.gemm.numel(), ws.gemm_counters.data_ptr(),
+                            ws.status.data_ptr(), _stream(), None if link is None else ctypes.byref(link))
+    native.check(code, "cb_wq_gemm_act")
+    return out
+
+
+def gate_up_act(x: torch.Tensor, w: PackedWeight, gu: torch.Tensor, act: torch.Tensor, ws: Workspace | None = None,
+                link=None) -> int:
+    """``act = swiglu(x @ W^T)`` for a ``[gate; up]`` projection: one launch when the rows of ``w`` are interleaved
+    for the fused epilogue, else the GEMM into ``gu`` followed by the activation kernel.  Returns the launch count."""
+    if w.act_interleaved:
+        wq_gemm_act(x, w, out=act, ws=ws, link=link)
+        return 1
+    wq_gemm(x, w, out=gu, ws=ws, link=link)
+    swiglu(gu, out=act)
+    return 2
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, zero_centered: bool = False) -> torch.Tensor:
     """RMSNorm; with ``residual`` the sum ``x + residual`` is written back into ``residual`` first."""
@@ -316,10 +362,15 @@ def moe_route(router_logits: torch.Tensor, x: torch.Tensor, top_k: int, sc: MoeS
 
 
 def wq_gemm_grouped(x: torch.Tensor, w: PackedWeight, out: torch.Tensor, rows: int, sc: MoeScratch,
-                    code_stride: int, meta_stride: int, ws: Workspace | None = None) -> torch.Tensor:
-    """Per-expert ``out[rows of e] = x[rows of e] @ W_e^T`` over the work list in ``sc.tiles``; ``w`` stacks the experts."""
+                    code_stride: int, meta_stride: int, ws: Workspace | None = None, swiglu: bool = False) -> torch.Tensor:
+    """Per-expert ``out[rows of e] = x[rows of e] @ W_e^T`` over the work list in ``sc.tiles``; ``w`` stacks the experts.
+
+    ``swiglu``: every expert's ``[gate; up]`` rows are interleaved and ``out`` (``N / 2`` columns) gets the activation.
+    """
     ws = ws or workspace(x.device)
-    code = native.lib().cb_wq_gemm_grouped(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
+    assert swiglu == w.act_interleaved
+    entry = native.lib().cb_wq_gemm_grouped_act if swiglu else native.lib().cb_wq_gemm_grouped
+    code = entry(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
                                            out.data_ptr(), out.stride(0), float(w.alpha), rows, w.n, w.k, w.group_k,
                                            sc.tiles.data_ptr(), sc.max_items, sc.mb, w.codes.shape[0], code_stride, meta_stride,
                                            ws.status.data_ptr(), _stream())

@@ -134,6 +134,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_tp.restype = i
     l.cb_wq_gemm_sk.argtypes = [i, vp, i, vp, vp, vp, i, vp, f, i, i, i, i, i, vp, ll, vp, vp, vp, vp]
     l.cb_wq_gemm_sk.restype = i
+    l.cb_wq_gemm_act.argtypes = [i, vp, i, vp, vp, vp, i, f, i, i, i, i, i, i, i, vp, ll, vp, vp, vp, vp]
+    l.cb_wq_gemm_act.restype = i
     l.cb_tp_reduce_norm.argtypes = [vp, vp]
     l.cb_tp_reduce_norm.restype = i
     l.cb_tp_wait.argtypes = [vp, vp, ctypes.c_uint, i, vp, vp]
@@ -158,6 +160,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_ep_finish.restype = i
     l.cb_wq_gemm_grouped.argtypes = [i, vp, i, vp, vp, vp, i, f, i, i, i, i, vp, i, i, i, ll, ll, vp, vp]
     l.cb_wq_gemm_grouped.restype = i
+    l.cb_wq_gemm_grouped_act.argtypes = l.cb_wq_gemm_grouped.argtypes
+    l.cb_wq_gemm_grouped_act.restype = i
 
 
 class TpLinkStruct(ctypes.Structure):

@@ -28,6 +28,7 @@ class GemmPolicy:
     stream_k_min_units: int = 0         # 0 = the kernel's own cost model
     split_k_max: int = 8                # per-tile kernel: largest split-K factor
     split_k_min_blocks: int = 8         # ... and the fewest k-blocks a split may get
+    fuse_swiglu: bool = True            # SwiGLU in the epilogue of the gate/up GEMM (weight rows re-ordered at load)
 
 
 @dataclass(frozen=True)

@@ -37,10 +37,11 @@ class PackedWeight:
     codes: torch.Tensor          # uint8 (or bf16 [N, K] for FMT_BF16)
     meta: torch.Tensor | None    # uint8
     alpha: float = 1.0
+    act_interleaved: bool = False   # gate / up rows interleaved for the fused SwiGLU epilogue (swiglu_interleave)
 
     def to(self, device) -> "PackedWeight":
         return PackedWeight(self.fmt, self.n, self.k, self.group_k, self.codes.to(device),
-                            None if self.meta is None else self.meta.to(device), self.alpha)
+                            None if self.meta is None else self.meta.to(device), self.alpha, self.act_interleaved)
 
     @property
     def nbytes(self) -> int:
@@ -149,6 +150,57 @@ def pack_bf16(weight: torch.Tensor) -> PackedWeight:
     if k % BLOCK_K:
         raise ValueError("K must be a multiple of 64")
     return PackedWeight(FMT_BF16, n, k, k, weight.to(torch.bfloat16).contiguous(), None)
+
+
+def swiglu_row_order(inter: int) -> torch.Tensor:
+    """Row order of a ``[gate; up]`` matrix (``2 * inter`` rows) for the fused SwiGLU epilogue of the GEMM.
+
+    A 128-row weight tile then holds 64 output features as four blocks of {16 gate rows, 16 up rows}: the four
+    epilogue warps of a tile (one TMEM lane quadrant each) find a feature's gate and up accumulators 16 lanes
+    apart.  ``order[i]`` is the source row of new row ``i``.
+    """
+    if inter % 16:
+        raise ValueError("the fused SwiGLU epilogue needs an intermediate size that is a multiple of 16")
+    i = torch.arange(2 * inter)
+    feature = (i // 32) * 16 + i % 16
+    return feature + ((i % 32) // 16) * inter
+
+
+def permute_rows(pw: PackedWeight, order: torch.Tensor) -> PackedWeight:
+    """Reorder the output rows of a packed matrix (new row ``i`` = old row ``order[i]``) without re-quantizing."""
+    if order.numel() != pw.n:
+        raise ValueError("row order must cover every row")
+    if pw.fmt == FMT_BF16:
+        return PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, pw.codes[order.to(pw.codes.device)].contiguous(), None, pw.alpha)
+    nt = pw.codes.shape[0]
+    full = torch.cat([order, torch.arange(pw.n, nt * TILE_N)]).to(pw.codes.device)
+
+    def rows(t: torch.Tensor) -> torch.Tensor:       # [nt, x, y, 128, w]: the row index is (dim 0, dim 3)
+        shape = t.shape
+        flat = t.permute(0, 3, 1, 2, 4).reshape(nt * TILE_N, -1)[full]
+        return flat.reshape(nt, TILE_N, shape[1], shape[2], shape[4]).permute(0, 2, 3, 1, 4).contiguous()
+
+    return PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, rows(pw.codes), rows(pw.meta), pw.alpha)
+
+
+def swiglu_interleave(pw: PackedWeight, stacked: bool = False) -> PackedWeight:
+    """``[gate; up]`` projection re-ordered for the fused SwiGLU epilogue (``kernels.wq_gemm_act``).
+
+    ``stacked``: ``codes`` / ``meta`` carry a leading expert dimension and every expert is re-ordered.
+    """
+    if pw.act_interleaved:
+        return pw
+    order = swiglu_row_order(pw.n // 2)
+    if not stacked:
+        out = permute_rows(pw, order)
+    else:
+        per = [permute_rows(PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, pw.codes[e],
+                                         None if pw.meta is None else pw.meta[e], pw.alpha), order)
+               for e in range(pw.codes.shape[0])]
+        out = PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, torch.stack([q.codes for q in per]),
+                           None if pw.meta is None else torch.stack([q.meta for q in per]), pw.alpha)
+    out.act_interleaved = True
+    return out
 
 
 def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:

@@ -151,9 +151,7 @@ class FusedEp:
                                         sc.total.data_ptr(), sc.tiles.data_ptr(), sc.route_pos.data_ptr(),
                                         sc.xs.data_ptr(), st), "cb_moe_permute")
         rows = virt * k
-        K.wq_gemm_grouped(sc.xs, layer.gate_up, sc.gu, rows, sc, layer.strides[0], layer.strides[1], self.ws)
-        K.swiglu(sc.gu[:rows], out=sc.act[:rows])
-        K.wq_gemm_grouped(sc.act, layer.down, sc.y, rows, sc, layer.strides[2], layer.strides[3], self.ws)
+        layer.experts(sc, rows, self.ws)
 
         c = native.EpCombineStruct()
         c.y, c.route_pos, c.topk_w, c.cnt_in = sc.y.data_ptr(), sc.route_pos.data_ptr(), sc.topk_w.data_ptr(), b.cnt_in.data_ptr()

@@ -184,14 +184,21 @@ class FusedTp:
         a.eps, a.zero_centered, a.local_only = float(eps), int(zero_centered), int(local_only)
         native.check(native.lib().cb_tp_reduce_norm(ctypes.byref(a), K._stream()), "cb_tp_reduce_norm")
 
-    def gemm_gather(self, w, out: torch.Tensor, s: int) -> torch.Tensor:
-        """Column-parallel GEMM on the gathered activations of set ``s`` (waits for them in-kernel)."""
+    def _gather_link(self, s: int):
         link = native.TpLinkStruct()
         link.mode, link.rank, link.size, link.rows_per_rank = MODE_GATHER_WAIT, self.rank, self.size, self.rpr
         link.ag_flag = self.b.flags.data_ptr() + self._flag_off(s, 1)
         link.ag_state = self._state_ptr(s, 1)
         link.ag_expected = self.rpr
-        return K.wq_gemm(self.x_view(s), w, out=out, ws=self.ws, link=link)
+        return link
+
+    def gemm_gather(self, w, out: torch.Tensor, s: int) -> torch.Tensor:
+        """Column-parallel GEMM on the gathered activations of set ``s`` (waits for them in-kernel)."""
+        return K.wq_gemm(self.x_view(s), w, out=out, ws=self.ws, link=self._gather_link(s))
+
+    def gate_up_act(self, w, gu: torch.Tensor, act: torch.Tensor, s: int) -> int:
+        """Column-parallel gate/up projection + SwiGLU on the gathered activations of set ``s``; returns the launches."""
+        return K.gate_up_act(self.x_view(s), w, gu, act, ws=self.ws, link=self._gather_link(s))
 
     def wait_gather(self, s: int) -> torch.Tensor:
         native.check(native.lib().cb_tp_wait(self.b.flags.data_ptr() + self._flag_off(s, 1), self._state_ptr(s, 1),

@@ -86,8 +86,9 @@ def random_cubic_weight(n: int, k: int, group: int = 128) -> wq_pack.PackedWeigh
 
 
 def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str = "cubic4",
-               kernel: str = "auto") -> dict:
-    """``kernel``: auto (the dispatcher's choice), tile (one CTA per tile and K split), streamk (persistent)."""
+               kernel: str = "auto", act: bool = False) -> dict:
+    """``kernel``: auto (the dispatcher's choice), tile (one CTA per tile and K split), streamk (persistent).
+    ``act``: the weight is a [gate; up] projection and SwiGLU runs in the epilogue (output ``[m, n / 2]``)."""
     if fmt == "bf16":
         w = wq_pack.pack_bf16(torch.randn(n, k, device=DEV) * 0.02)
         wbytes = n * k * 2
@@ -98,14 +99,18 @@ def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str 
     y = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
     stream_k = kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(m, n, w.fmt))
-    if stream_k:
+    sp = None if stream_k else (splits or K.choose_splits(m, n, k))
+    if act:
+        w = wq_pack.swiglu_interleave(w)
+        y = torch.empty(m, n // 2, device=DEV, dtype=torch.bfloat16)
+        call = lambda: K.wq_gemm_act(x, w, out=y, splits=sp, min_units=0 if stream_k else None)   # noqa: E731
+    elif stream_k:
         call = lambda: K.wq_gemm(x, w, out=y, min_units=0)                                   # noqa: E731
     else:
-        sp = splits or K.choose_splits(m, n, k)
         call = lambda: K.wq_gemm(x, w, out=y, splits=sp)                                     # noqa: E731
     ms = timeit_graph(call, flush, launches=max(3, min(10, iters)))
     K.workspace(torch.device(DEV)).check_status()
-    return {"op": f"wq_gemm[{fmt}]", "m": m, "n": n, "k": k, "kernel": "streamk" if stream_k else "tile",
+    return {"op": f"wq_gemm[{fmt}]" + ("+swiglu" if act else ""), "m": m, "n": n, "k": k, "kernel": "streamk" if stream_k else "tile",
             "splits": None if stream_k else sp, "us": round(ms * 1e3, 1), "timing": "in-graph, L2 flushed",
             "tflops": round(2 * m * n * k / ms / 1e9, 1), "weight_gbs": round(wbytes / ms / 1e6, 1)}
 
@@ -194,9 +199,10 @@ def main() -> None:
     ap.add_argument("--vbits", type=int, default=8)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kernel", default="auto", choices=["auto", "tile", "streamk"])
+    ap.add_argument("--act", action="store_true", help="gemm: [gate; up] projection with SwiGLU in the epilogue")
     a = ap.parse_args()
     if a.op == "gemm":
-        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.splits or None, a.iters, a.fmt, a.kernel)))
+        print(json.dumps(bench_gemm(a.m, a.n, a.k, a.splits or None, a.iters, a.fmt, a.kernel, a.act)))
     elif a.op == "fused-tp":
         print(json.dumps(bench_fused_tp(a.ranks, a.m, a.hidden, a.inter, a.iters)))
     elif a.op == "attn":

@@ -77,3 +77,29 @@ def test_nvfp4_levels_and_both_global_conventions():
     assert _rel(wq_pack.unpack_to_dense(pw), d) < 1e-5
     xq, xs = F.nvfp4_activation_quantize(torch.randn(4, 64), 100.0)
     assert xq.shape == (4, 64) and xs.shape == (4, 4)
+
+
+def test_swiglu_row_order_and_packed_permutation():
+    """Interleaved [gate; up] rows: 16 gate rows then the 16 up rows of the same features, for every packed format."""
+    inter = 80
+    order = wq_pack.swiglu_row_order(inter)
+    assert sorted(order.tolist()) == list(range(2 * inter))
+    for i in (0, 15, 16, 31, 32, 128, 159):
+        feature = (i // 32) * 16 + i % 16
+        assert int(order[i]) == feature + (inter if (i % 32) >= 16 else 0)
+    with pytest.raises(ValueError):
+        wq_pack.swiglu_row_order(40)
+    g = torch.Generator().manual_seed(0)
+    q = torch.randint(0, 16, (2 * inter, 256), generator=g, dtype=torch.uint8)
+    scale = torch.rand(2 * inter, 4, generator=g) * 0.01 + 0.001
+    pw = wq_pack.pack_affine4(q, scale, -8 * scale, 64)
+    dense = wq_pack.unpack_to_dense(pw)
+    pi = wq_pack.swiglu_interleave(pw)
+    assert pi.act_interleaved and wq_pack.swiglu_interleave(pi) is pi
+    assert torch.equal(wq_pack.unpack_to_dense(pi)[:2 * inter], dense[:2 * inter][order])
+    stacked = wq_pack.PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, torch.stack([pw.codes, pi.codes]),
+                                   torch.stack([pw.meta, pi.meta]))
+    both = wq_pack.swiglu_interleave(stacked, stacked=True)
+    assert torch.equal(both.codes[0], pi.codes) and torch.equal(both.meta[0], pi.meta)
+    wb = wq_pack.pack_bf16(torch.randn(2 * inter, 64, generator=g))
+    assert torch.equal(wq_pack.swiglu_interleave(wb).codes, wb.codes[order])

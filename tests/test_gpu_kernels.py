@@ -80,6 +80,65 @@ def test_wq_gemm_stream_k(m, n, k, min_units):
     assert torch.equal(K.wq_gemm(x.to(DEV), pw.to(DEV), min_units=min_units), y)      # deterministic
 
 
+@pytest.mark.parametrize("m,inter,k,splits,min_units", [
+    (1, 64, 256, 1, None), (40, 192, 1024, 1, None), (300, 128, 512, 1, None),     # per-tile kernel, staged epilogue
+    (16, 80, 512, 1, None),                                                        # last tile only partly filled
+    (64, 256, 2048, 4, None),                                                      # per-tile kernel, split-K fix-up
+    (16, 256, 512, None, 0), (256, 192, 4096, None, 0),                            # persistent kernel, own schedule
+    (32, 128, 2048, None, 1), (256, 192, 4096, None, 3), (48, 640, 1024, None, 5),  # many-part tiles, deferred fix-ups
+    (520, 320, 512, None, 2), (16, 64 * 150, 256, None, 0),                        # row tiles; more tiles than SMs
+])
+def test_wq_gemm_fused_swiglu(m, inter, k, splits, min_units):
+    """SwiGLU in the GEMM epilogue (interleaved gate / up rows) against the two-kernel path and the fp32 oracle."""
+    K = _k()
+    pw, dense = _cubic_weight(2 * inter, k, seed=m + inter)
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
+    ref = eager.swiglu((x.float() @ dense.t()).to(torch.bfloat16))
+    pwi = wq_pack.swiglu_interleave(pw).to(DEV)
+    assert pwi.act_interleaved and not pw.act_interleaved
+    act = K.wq_gemm_act(x.to(DEV), pwi, splits=splits, min_units=min_units)
+    torch.cuda.synchronize()
+    K.workspace(act.device).check_status()
+    assert act.shape == (m, inter)
+    assert _rel(act.cpu(), ref) < 1.5e-2
+    # the same kernel and schedule without the fusion (the interleaved matrix as a plain weight: a row keeps its
+    # tile, hence its split points along K), columns put back in [gate | up] order, then the activation kernel:
+    # identical values
+    plain = wq_pack.PackedWeight(pwi.fmt, pwi.n, pwi.k, pwi.group_k, pwi.codes, pwi.meta, pwi.alpha)
+    gu_i = K.wq_gemm(x.to(DEV), plain, splits=splits, min_units=min_units)
+    gu = torch.empty_like(gu_i)
+    gu[:, wq_pack.swiglu_row_order(inter).to(DEV)] = gu_i
+    assert torch.equal(act, K.swiglu(gu))
+    # into a wider buffer (row stride > inter), and whichever kernel the dispatcher picks
+    wide = torch.zeros(m, inter + 64, dtype=torch.bfloat16, device=DEV)
+    K.wq_gemm_act(x.to(DEV), pwi, out=wide[:, :inter], splits=splits, min_units=min_units)
+    assert torch.equal(wide[:, :inter], act) and not wide[:, inter:].any()
+    assert _rel(K.wq_gemm_act(x.to(DEV), pwi).cpu(), ref) < 1.5e-2
+
+
+def test_wq_gemm_fused_swiglu_other_formats():
+    K = _k()
+    m, inter, k = 48, 128, 512
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(DEV)
+    q = torch.randint(0, 16, (2 * inter, k), generator=g, dtype=torch.uint8)
+    scale = torch.rand(2 * inter, k // 64, generator=g) * 0.01 + 0.001
+    zero = torch.randint(0, 16, (2 * inter, k // 64), generator=g).float()
+    packed = torch.randint(0, 256, (2 * inter, k // 2), generator=g, dtype=torch.uint8)
+    bs = (torch.rand(2 * inter, k // 16, generator=g) * 2 + 0.25).to(torch.float8_e4m3fn)
+    for pw in (wq_pack.pack_affine4(q, scale, -zero * scale, 64), wq_pack.pack_nvfp4(packed, bs.float(), 0.01),
+               wq_pack.pack_bf16(torch.randn(2 * inter, k, generator=g) * 0.05)):
+        pwi = wq_pack.swiglu_interleave(pw).to(DEV)
+        plain = wq_pack.PackedWeight(pwi.fmt, pwi.n, pwi.k, pwi.group_k, pwi.codes, pwi.meta, pwi.alpha)
+        order = wq_pack.swiglu_row_order(inter).to(DEV)
+        for kw in ({"splits": 1}, {"min_units": 2}):
+            gu_i = K.wq_gemm(x, plain, **kw)
+            gu = torch.empty_like(gu_i)
+            gu[:, order] = gu_i
+            assert torch.equal(K.wq_gemm_act(x, pwi, **kw), K.swiglu(gu))
+            assert _rel(gu, K.wq_gemm(x, pw.to(DEV), **kw)) < 2e-3
+
+
 def test_wq_gemm_stream_k_bf16_weights():
     K = _k()
     for m, n, k, mu in ((48, 256, 512, 0), (256, 1000, 1024, 2), (24, 128 * 150 + 40, 256, 0)):

@@ -51,6 +51,12 @@ def test_moe_layer_matches_oracle(method, tokens, ep, persistent):
         ref = moe_reference(x, layer.router.codes, gu, dn, 4, True, expert_lo=rank * local)
         total += out.float()
         ref_total += ref
+        # SwiGLU in the epilogue of the grouped gate/up GEMM (rows of every expert interleaved): the grouped GEMM
+        # gives a tile all of its k-blocks in order, so the output is identical
+        plain = out.clone()
+        layer.fuse_activation()
+        assert layer.gate_up.act_interleaved
+        assert torch.equal(layer.forward(x), plain)
     from cubic_serve_b200.ops import kernels as K
     native.lib().cb_wq_gemm_grouped_mode(1)
     K.workspace(torch.device(DEV)).check_status()
