@@ -212,6 +212,100 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, ui
       : "memory");
 }
 
+// ------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 0 and 1, one SM each) issue ONE MMA of M = 256: each supplies 128 rows of A and half
+// of the N rows of B from its own shared memory (same offsets in both), each gets 128 lanes x N columns of D in its
+// own tensor memory.  Rank 0 issues the instructions; completions are multicast to barriers at the same offset in
+// both CTAs; barriers that rank 0 waits on are raised by rank 1 through the cluster address of rank 0's barrier.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// All threads of all CTAs of the cluster (the hardware barrier: it waits only for threads that exist and run).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier of another CTA of the cluster (address from cluster_map).  Default semantics (release at CTA
+// scope), as for a local arrive: what the arrival publishes here is this CTA's own shared memory, already made
+// visible to the async proxy by fence.proxy.async, and it is read in place by the pair's MMA.  The cluster-scope
+// release form was measured at ~3.5 us per arrival on the critical path of the pair kernel.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Parked wait with acquire at cluster scope (the barrier also counts arrivals from the peer CTA).
+__device__ __forceinline__ bool mbar_try_wait_hint_cluster(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_park_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  long long t0 = 0;
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait_hint_cluster(bar, parity, 20000u)) return true;
+    if ((++polls & 0xFu) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// 2-D tiled TMA load into THIS CTA's shared memory whose completion bytes go to a barrier of either CTA of the pair
+// (cluster address).  No multicast: every CTA fetches its own box.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(tmap), "r"(x), "r"(y), "r"(cluster_bar)
+      : "memory");
+}
+// Tensor memory of the pair: one warp of EACH CTA (same warp index) executes these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// All previously issued pair MMAs of this thread arrive, when they retire, on the barrier at this offset in every
+// CTA of `cta_mask` (bit r = rank r).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint32_t cta_mask) {
+  asm volatile(
+      "{\n\t.reg .b16 m;\n\t"
+      "cvt.u16.u32 m, %1;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t}" ::"r"(bar),
+      "r"(cta_mask)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives lane
 // (base_lane + t), registers r[0..31] = columns col..col+31.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

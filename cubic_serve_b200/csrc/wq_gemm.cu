@@ -545,6 +545,11 @@ int cb_wq_gemm_sk(int fmt, const void* x, int ldx, const void* codes, const void
                   const void* residual, float alpha, int M, int N, int K, int group_k, int min_units, void* workspace,
                   long long workspace_bytes, void* counters, void* status, void* stream, const CbTpLink* link);
 
+// Persistent kernel on CTA pairs (cta_group::2): 0 never; 1 (default) eligible launches with more than 256 batch
+// rows (measured: 5-20 % faster than one CTA per SM from 512 rows up, 2-8 % slower at exactly 256, where the decode
+// warps and not the activation traffic set the pace); 2 every eligible launch.
+static int g_pair_mode = 1;
+
 // Epilogue of the NEXT launch made by this thread: 1 = fused SwiGLU (the weight rows are gate / up interleaved, the
 // output has N / 2 columns).  Set and cleared by the *_act entry points only.
 static thread_local int g_epilogue_swiglu = 0;
@@ -622,8 +627,11 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.stages = stages;
   const size_t smem = stages * stage + sizeof(SmemCtl) + 1024;
 
+  if (g_grouped.tiles) p.group_tiles = g_grouped.tiles;
+  p.pair = (stream_k && (g_pair_mode == 2 || (g_pair_mode == 1 && M > 256)) && streamk_pair_eligible(p, N)) ? 1 : 0;
   CUtensorMap tx, tw;
-  if (make_tmap_bf16(&tx, x, M, K, ldx, p.mb) != 0) return -20;
+  // with CTA pairs each CTA of a pair fetches half of the rows of an activation tile
+  if (make_tmap_bf16(&tx, x, M, K, ldx, p.pair ? p.mb / 2 : p.mb) != 0) return -20;
   if (fmt == kFmtBf16) {
     const uint64_t w_rows = static_cast<uint64_t>(N) * (g_grouped.tiles ? g_grouped.num_experts : 1);
     if (make_tmap_bf16(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
@@ -677,6 +685,13 @@ int cb_wq_gemm_act(int fmt, const void* x, int ldx, const void* codes, const voi
 
 // 1 (default): grouped GEMMs run on the persistent kernel; 0: one CTA per (work item, weight tile).
 void cb_wq_gemm_grouped_mode(int persistent) { g_grouped_persistent = persistent; }
+
+// 0: one CTA per SM works alone; 1 (default): CTA pairs for eligible launches of more than 256 batch rows; 2: for
+// every eligible launch.
+void cb_wq_gemm_pair_mode(int pairs) { g_pair_mode = pairs; }
+
+// CTA pairs of the persistent kernel that can be resident at once on the current device (0: cannot be launched).
+int cb_wq_gemm_resident_pairs(int fmt) { return cb::streamk_resident_pairs(fmt); }
 
 int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                        float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,

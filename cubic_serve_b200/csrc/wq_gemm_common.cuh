@@ -71,6 +71,9 @@ struct WqGemmParams {
   // 128-row tile holds 64 output features as four blocks of {16 gate rows, 16 up rows}; the epilogue writes
   // act[m, 64 * n_tile + 16 * q + i] = silu(tile row 32 q + i) * (tile row 32 q + 16 + i), ldy = row stride of act
   int swiglu;
+  // persistent kernel on CTA pairs (cta_group::2): the schedule's tile is a PAIR of adjacent weight tiles, CTA rank r of
+  // the pair owns weight tile 2 * pair_tile + r and loads batch rows [m0 + r * mb / 2, + mb / 2) of the activation tile
+  int pair;
   // persistent stream-K kernel only (wq_gemm_sk.cu)
   int n_tiles, tiles;       // tile = m_tile * n_tiles + n_tile
   int sk_tiles, sk_ctas;    // tiles [0, sk_tiles) are dealt by k-block to CTAs [0, sk_ctas); the rest are whole
@@ -250,6 +253,8 @@ static inline int make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t ro
 
 // Persistent stream-K launcher (wq_gemm_sk.cu).  `workspace_bytes` bounds the fp32 partial-tile slots the
 // schedule may use; returns 0, a negative argument error or a positive cudaError_t.
+bool streamk_pair_eligible(const WqGemmParams& p, int N);
+int streamk_resident_pairs(int fmt);
 int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, size_t workspace_bytes,
                    int sm_count, int min_units, cudaStream_t stream, int grouped_max_items = 0);
 

@@ -15,13 +15,13 @@
 //   * the remaining tiles are whole tiles, tile = sk_tiles + w * grid + cta for w = 0, 1, ...
 //   Every CTA therefore gets the same number of k-blocks (+-1) whatever the tile count.
 // Inside a CTA the rings are decoupled and the accumulator is double buffered:
-//   warp 0      activation tiles (and bf16 weight tiles) by TMA into the AX ring          -> x_full
+//   warp 0      activation tiles (and bf16 weight tiles) by TMA into the AX ring          -> full
 //   warp 2      packed codes + metadata by bulk copy into the deeper C ring               -> c_full
 //   warps 7-22  decode, two groups of 8 warps that take alternate k-blocks: wait c_full, decode 32
 //               weights per thread in registers (one 16-byte code load, four 16-byte tile stores),
-//               wait for the AX slot to be free, store the swizzled bf16 tile             -> a_ready, c_empty
+//               wait for the AX slot to be free, store the swizzled bf16 tile             -> full, c_empty
 //               (per-k-block costs -- waits, fence, arrive, metadata -- are paid by 8 warps, not 16)
-//   warp 1      MMA: wait a_ready & x_full, 4 x tcgen05.mma into accumulator (segment & 1),
+//   warp 1      MMA: wait full, 4 x tcgen05.mma into accumulator (segment & 1),
 //               commit -> ax_empty; after a segment's last k-block commit -> acc_full
 //   warps 3-6   epilogue: wait acc_full, tcgen05.ld, write bf16 output (or the fp32 partial),
 //               release the accumulator -> acc_empty; fix-up reduction for streamed tiles;
@@ -52,8 +52,8 @@ struct SkSegment {
 };
 
 struct __align__(8) SkCtl {
-  uint64_t x_full[kSkMaxAx];     // activation (and bf16 weight) tile landed            (transaction bytes)
-  uint64_t a_ready[kSkMaxAx];    // decoded weight tile stored by the 8 warps of a group (8 arrivals)
+  uint64_t full[kSkMaxAx];       // activation (and bf16 weight) tile landed (transaction bytes + the producer's
+                                 // arrival) AND decoded weight tile stored by the 8 warps of a group (8 arrivals)
   uint64_t ax_empty[kSkMaxAx];   // the MMAs that read the slot have retired            (tcgen05.commit)
   uint64_t c_full[kSkMaxC];      // packed codes + metadata landed                      (transaction bytes)
   uint64_t c_empty[kSkMaxC];     // the group's warps hold the codes in registers       (8 arrivals)
@@ -126,11 +126,16 @@ struct SkIter {
 // n_tile with item = {expert, first row, rows} from the device work list written by the MoE routing kernels.
 struct SkCoords {
   int m0, rows, n_tile, expert;
+  int tile_id;                   // index of the (row tile, weight tile) this CTA produces: arrival counter of the tile
 };
-__device__ __forceinline__ SkCoords sk_coords(const WqGemmParams& p, int tile) {
+// `rank`: rank of the CTA in its pair (0 without pairs).  With pairs the schedule's tile is a pair of adjacent
+// weight tiles and rank r owns weight tile 2 * pair_tile + r.
+__device__ __forceinline__ SkCoords sk_coords(const WqGemmParams& p, int tile, int rank) {
   SkCoords c;
-  const int outer = tile / p.n_tiles;
-  c.n_tile = tile - outer * p.n_tiles;
+  const int nts = p.n_tiles >> p.pair;
+  const int outer = tile / nts;
+  c.n_tile = ((tile - outer * nts) << p.pair) + rank;
+  c.tile_id = outer * p.n_tiles + c.n_tile;
   if (p.group_tiles) {
     c.expert = p.group_tiles[1 + 3 * outer];
     c.m0 = p.group_tiles[2 + 3 * outer];
@@ -158,8 +163,9 @@ struct SkRing {
 
 // fp32 partial slot of (cta, part): a CTA has at most one run that starts inside a tile (its first, part > 0)
 // and at most one that ends inside a tile (its last, part == 0)
-__device__ __forceinline__ float* sk_slot(const WqGemmParams& p, int cta, int part) {
-  return p.workspace + (static_cast<size_t>(cta) * 2 + (part == 0 ? 1 : 0)) * (static_cast<size_t>(p.mb) * kTileN);
+// (`unit` = the CTA's index in the launch: the pair index * 2 + rank with CTA pairs)
+__device__ __forceinline__ float* sk_slot(const WqGemmParams& p, int unit, int part) {
+  return p.workspace + (static_cast<size_t>(unit) * 2 + (part == 0 ? 1 : 0)) * (static_cast<size_t>(p.mb) * kTileN);
 }
 
 __device__ __forceinline__ void epi_bar() {
@@ -218,6 +224,7 @@ __device__ __forceinline__ void sk_store4(const WqGemmParams& p, int m, int n0, 
 __device__ __noinline__ void sk_reduce_write_act(const WqGemmParams& p, const float* slots, int parts, int own_part,
                                                  const float* own, int tid, int nthreads, int m0, int rows_here, int n_tile) {
   const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
+  const size_t stride = static_cast<size_t>(2) << p.pair;      // slots between consecutive parts of a tile
   for (int idx = tid; idx < rows_here * 16; idx += nthreads) {
     const int mm = idx >> 4, j0 = (idx & 15) * 4;
     const int e = mm * kTileN + act_gate_col(j0);
@@ -228,7 +235,7 @@ __device__ __noinline__ void sk_reduce_write_act(const WqGemmParams& p, const fl
         a = *reinterpret_cast<const float4*>(own + e);
         b = *reinterpret_cast<const float4*>(own + e + 16);
       } else {
-        const float* src = slots + (static_cast<size_t>(sp) * 2 + (sp == 0 ? 1 : 0)) * part_elems;
+        const float* src = slots + (static_cast<size_t>(sp) * stride + (sp == 0 ? 1 : 0)) * part_elems;
         a = __ldcg(reinterpret_cast<const float4*>(src + e));
         b = __ldcg(reinterpret_cast<const float4*>(src + e + 16));
       }
@@ -246,13 +253,14 @@ __device__ __noinline__ void sk_reduce_write_act(const WqGemmParams& p, const fl
 // still in shared memory, read instead of its copy in L2.  kBatch items per thread are in flight at once: the
 // partials come from L2 at ~1 k cycles per round trip, so the loop is latency bound without batching.
 template <int kBatch>
-__device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkSegment& seg, int cta, int tid,
+__device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkSegment& seg, int unit, int tid,
                                                 int nthreads, int m0, int rows_here, int n_base, const float* own) {
   const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
-  const int g_first = cta - seg.part;
+  const size_t stride = static_cast<size_t>(2) << p.pair;      // slots between consecutive parts (CTAs, or pairs of CTAs)
+  const int g_first = unit - (seg.part << p.pair);             // the CTA (of this rank) that holds part 0
   const int parts = seg.parts;
   const int own_part = own ? seg.part : -1;
-  const float* slots = p.workspace + static_cast<size_t>(g_first) * 2 * part_elems;   // part q > 0 at + q * 2 * part_elems
+  const float* slots = p.workspace + static_cast<size_t>(g_first) * 2 * part_elems;   // part q > 0 at + q * stride * part_elems
   if (p.swiglu) {
     sk_reduce_write_act(p, slots, parts, own_part, own, tid, nthreads, m0, rows_here, n_base / kTileN);
     return;
@@ -277,7 +285,7 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) v[b] = *reinterpret_cast<const float4*>(own + e[b]);
       } else {
-        const float* src = slots + (static_cast<size_t>(sp) * 2 + (sp == 0 ? 1 : 0)) * part_elems;
+        const float* src = slots + (static_cast<size_t>(sp) * stride + (sp == 0 ? 1 : 0)) * part_elems;
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) v[b] = __ldcg(reinterpret_cast<const float4*>(src + e[b]));
       }
@@ -292,13 +300,18 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
   }
 }
 
-template <int FMT>
+// PAIR: the launch is made of clusters of two CTAs that issue MMAs of M = 256 together (cta_group::2).  Rank r of a
+// pair owns weight tile 2 * pair_tile + r and HALF of the activation tile (batch rows r * mb / 2 ...), so every SM
+// fetches half the activation bytes per k-block; that traffic is what bounds the one-CTA form at 256 batch rows.
+// Rank 0 issues the MMAs for both.  Barriers rank 0 waits on (full, acc_empty) also count the arrivals
+// of rank 1; the completions of the MMAs (ax_empty, acc_full, tail_full) are multicast to both CTAs.
+template <int FMT, bool PAIR>
 __global__ void __launch_bounds__(kSkThreads, 1)
 wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
                   const __grid_constant__ CUtensorMap tmap_w,  // only for kFmtBf16
                   const __grid_constant__ WqGemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  const uint32_t x_bytes = static_cast<uint32_t>(p.mb) * 128u;
+  const uint32_t x_bytes = static_cast<uint32_t>(PAIR ? p.mb >> 1 : p.mb) * 128u;   // this CTA's rows of the activation tile
   const uint32_t ax_bytes = x_bytes + kATileBytes;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* c_ring = smem + static_cast<size_t>(p.ax_stages) * ax_bytes;
@@ -307,24 +320,27 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int cta = blockIdx.x;
-  const int grid = gridDim.x;
+  const int rank = PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int cta = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);   // index in the deal
+  const int grid = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int unit = blockIdx.x;                   // owner index of the fp32 partial slots
+  constexpr uint32_t kPeers = PAIR ? 2u : 1u;
   const int S = p.ax_stages;
   const int NC = p.c_stages;
   // timeline of CTA 0 (debug hook): row i = i-th k-block this CTA processes; slots as in wq_gemm.cu
-  unsigned long long* trace = (p.trace && cta == 0) ? p.trace : nullptr;
+  // (with CTA pairs rank 1 of the first pair records too, in rows 64..127, on its own SM's clock)
+  unsigned long long* trace = (p.trace && blockIdx.x <= (PAIR ? 1u : 0u)) ? p.trace + blockIdx.x * 64 * 8 : nullptr;
   if (trace && threadIdx.x == 0) trace[6] = clock64();
   // every CTA: wall-clock entry / exit in slots 0 / 1 of row `cta` (the buffer has >= gridDim.x rows)
   if (p.trace && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.trace[cta * 8 + 0] = t;
+    p.trace[blockIdx.x * 8 + 0] = t;
   }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSkMaxAx; ++s) {
-      mbar_init(smem_u32(&ctl->x_full[s]), 1);
-      mbar_init(smem_u32(&ctl->a_ready[s]), kSkGroupWarps);
+      mbar_init(smem_u32(&ctl->full[s]), 1 + (FMT == kFmtBf16 ? 0 : kSkGroupWarps * kPeers));
       mbar_init(smem_u32(&ctl->ax_empty[s]), 1);
     }
     for (int s = 0; s < kSkMaxC; ++s) {
@@ -333,7 +349,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->acc_full[b]), 1);
-      mbar_init(smem_u32(&ctl->acc_empty[b]), kSkEpiWarps);
+      mbar_init(smem_u32(&ctl->acc_empty[b]), kSkEpiWarps * kPeers);
     }
     mbar_init(smem_u32(&ctl->tail_full), 1);
     ctl->abort_flag = 0;
@@ -342,11 +358,17 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), p.tmem_cols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(&ctl->tmem_base), p.tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&ctl->tmem_base), p.tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();        // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
@@ -369,15 +391,24 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? static_cast<uint32_t>(kATileBytes) : 0u);
       SkRing r;
       while (ok && it.next(p, cta, grid, seg)) {
-        const SkCoords c = sk_coords(p, seg.tile);
+        const SkCoords c = sk_coords(p, seg.tile, rank);
         const int w_row = c.expert * p.N + c.n_tile * kTileN;   // bf16 weights: experts stacked as [E * N, K]
         for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
           if (r.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
           uint8_t* st = smem + static_cast<size_t>(r.s) * ax_bytes;
-          const uint32_t bar = smem_u32(&ctl->x_full[r.s]);
-          mbar_expect_tx(bar, tx);
-          tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, c.m0, bar);
-          if (FMT == kFmtBf16) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row, bar);
+          const uint32_t bar = smem_u32(&ctl->full[r.s]);
+          if (PAIR) {
+            // both CTAs' copies complete on rank 0's barrier, which expects the bytes of both; a completion that
+            // lands before the expectation is posted only drives the count negative inside the same phase
+            const uint32_t bar0 = cluster_map(bar, 0);
+            if (rank == 0) mbar_expect_tx(bar, 2u * tx);
+            tma_load_2d_pair(smem_u32(st), &tmap_x, kb * kBlockK, c.m0 + rank * (p.mb >> 1), bar0);
+            if (FMT == kFmtBf16) tma_load_2d_pair(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row, bar0);
+          } else {
+            mbar_expect_tx(bar, tx);
+            tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, c.m0, bar);
+            if (FMT == kFmtBf16) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row, bar);
+          }
           r.advance(S);
         }
       }
@@ -388,7 +419,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       bool ok = true;
       SkRing r;
       while (ok && it.next(p, cta, grid, seg)) {
-        const SkCoords c = sk_coords(p, seg.tile);
+        const SkCoords c = sk_coords(p, seg.tile, rank);
         const uint8_t* cbase = p.codes + static_cast<size_t>(c.expert) * p.group_code_stride +
                                static_cast<size_t>(c.n_tile) * p.k_blocks * kCodeBytes;
         const uint8_t* mbase = p.meta + static_cast<size_t>(c.expert) * p.group_meta_stride +
@@ -405,15 +436,19 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer (warp-uniform loop, one elected lane issues)
+    // ------------------------------------------------ MMA issuer (warp-uniform loop, one elected lane issues).
+    // The chain of dependent instructions per k-block (barrier test, vote, fence, four MMAs, commit) is the pace of
+    // the kernel when the operands are ready ahead of time, so the activation tile and the decoded weight tile
+    // complete ONE barrier (`full`), tested once.  (A loop run by a single thread of the warp was measured slower:
+    // 550-700 cycles from the barrier to the commit instead of 150-300.)
     const bool leader = elect_one();
-    const uint32_t idesc = umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+    const uint32_t idesc = umma_idesc(PAIR ? 2 * kTileN : kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
     const uint32_t smem_base = smem_u32(smem);
     const uint64_t desc_hi = umma_desc_sw128(0);
     SkRing r;
     int seg_idx = 0;
     int i_global = 0;
-    bool ok = true;
+    bool ok = !(PAIR && rank != 0);        // rank 1 of a pair issues nothing: rank 0's MMAs use both CTAs' operands
     while (ok && it.next(p, cta, grid, seg)) {
       const int buf = seg_idx & 1;
       const uint32_t use = static_cast<uint32_t>(seg_idx >> 1);
@@ -427,8 +462,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf) * p.acc_cols;
       uint32_t accumulate = 0;
       for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb, ++i_global) {
-        if (FMT != kFmtBf16) ok = mbar_wait_park(smem_u32(&ctl->a_ready[r.s]), r.wraps & 1u, abort_flag);
-        ok = ok && mbar_wait_park(smem_u32(&ctl->x_full[r.s]), r.wraps & 1u, abort_flag);
+        ok = mbar_wait_park(smem_u32(&ctl->full[r.s]), r.wraps & 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (trace && leader && i_global < 64) trace[i_global * 8 + 4] = clock64();
@@ -440,12 +474,21 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
-            umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            if (PAIR) umma_f16_pair(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            else umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
           }
-          tc_commit(smem_u32(&ctl->ax_empty[r.s]));
-          if (kb == seg.kb_hi - 1) {
-            tc_commit(smem_u32(&ctl->acc_full[buf]));
-            if (tail) tc_commit(smem_u32(&ctl->tail_full));
+          if (PAIR) {
+            tc_commit_pair(smem_u32(&ctl->ax_empty[r.s]), 3u);
+            if (kb == seg.kb_hi - 1) {
+              tc_commit_pair(smem_u32(&ctl->acc_full[buf]), 3u);
+              if (tail) tc_commit_pair(smem_u32(&ctl->tail_full), 3u);
+            }
+          } else {
+            tc_commit(smem_u32(&ctl->ax_empty[r.s]));
+            if (kb == seg.kb_hi - 1) {
+              tc_commit(smem_u32(&ctl->acc_full[buf]));
+              if (tail) tc_commit(smem_u32(&ctl->tail_full));
+            }
           }
         }
         accumulate = 1;
@@ -458,9 +501,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ------------------------------------------------ decode (warps 7..22) and epilogue (warps 3..6)
     // Geometry of the current segment (set by seg_geometry) and the shared LAST-segment epilogue.
-    int m0 = 0, rows_here = 0, n_base = 0;
+    int m0 = 0, rows_here = 0, n_base = 0, tile_id = 0;
     auto seg_geometry = [&]() {
-      const SkCoords c = sk_coords(p, seg.tile);
+      const SkCoords c = sk_coords(p, seg.tile, rank);
+      tile_id = c.tile_id;
       m0 = c.m0;
       rows_here = c.rows;
       n_base = c.n_tile * kTileN;
@@ -512,7 +556,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             sk_store4(p, m0 + (idx >> 5), n_base + (idx & 31) * 4, *reinterpret_cast<const float4*>(stg + static_cast<size_t>(idx) * 4));
       } else {
         if (ok) {
-          float* slot = sk_slot(p, cta, seg.part);
+          float* slot = sk_slot(p, unit, seg.part);
           for (int idx = tt; idx < p.mb * (kTileN / 4); idx += nthr)
             *reinterpret_cast<float4*>(slot + static_cast<size_t>(idx) * 4) = *reinterpret_cast<const float4*>(stg + static_cast<size_t>(idx) * 4);
         }
@@ -521,9 +565,9 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (tt == 0) {
           uint32_t last = 0;
           if (ok) {
-            const uint32_t prev = atomicAdd(&p.counters[seg.tile], 1u);
+            const uint32_t prev = atomicAdd(&p.counters[tile_id], 1u);
             last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
-            if (last) p.counters[seg.tile] = 0;
+            if (last) p.counters[tile_id] = 0;
           }
           ctl->is_last = last;
         }
@@ -531,7 +575,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (ctl->is_last && !*abort_flag) {
           __threadfence();
           finalized = true;
-          sk_reduce_write<4>(p, seg, cta, tt, nthr, m0, rows_here, n_base, stg);
+          sk_reduce_write<4>(p, seg, unit, tt, nthr, m0, rows_here, n_base, stg);
         }
       }
       if (p.tp.mode & kTpScatterPush) {
@@ -550,10 +594,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t n_def = ctl->deferred_count;
       for (uint32_t di = 0; di < n_def; ++di) {
         const SkSegment ds = ctl->deferred[di];
-        const SkCoords c = sk_coords(p, ds.tile);
+        const SkCoords c = sk_coords(p, ds.tile, rank);
         if (!*abort_flag) {
           __threadfence();
-          sk_reduce_write<4>(p, ds, cta, tt, nthr, c.m0, c.rows, c.n_tile * kTileN, nullptr);
+          sk_reduce_write<4>(p, ds, unit, tt, nthr, c.m0, c.rows, c.n_tile * kTileN, nullptr);
         }
         if (p.tp.mode & kTpScatterPush) {
           tail_bar();
@@ -637,7 +681,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
               *reinterpret_cast<uint4*>(arow + chunk_off[j]) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->a_ready[ra.s]));
+            if (lane == 0) {
+              if (PAIR && rank != 0) mbar_arrive_cluster(cluster_map(smem_u32(&ctl->full[ra.s]), 0));
+              else mbar_arrive(smem_u32(&ctl->full[ra.s]));
+            }
             if (trace && dq == 0 && ig < 64) trace[ig * 8 + 3] = clock64();
             const int step = len - jj < 2 ? len - jj : 2;
             rc.advance_by(step, NC);
@@ -675,7 +722,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           // 16-byte fp32 partial) stores, eight lanes covering the 64 contiguous bytes of one row.
           float* scr = epi_scratch + (warp - kSkFirstEpiWarp) * (16 * 32);
           const int f4 = (lane & 7) * 4;
-          float* slot = whole ? nullptr : sk_slot(p, cta, seg.part) + quad * 32 + f4;
+          float* slot = whole ? nullptr : sk_slot(p, unit, seg.part) + quad * 32 + f4;
           const uint32_t taddr = tmem_base + static_cast<uint32_t>(buf) * p.acc_cols + (static_cast<uint32_t>(quad * 32) << 16);
           for (int c0 = 0; c0 < p.mb; c0 += 16) {
             uint32_t acc[16];
@@ -716,7 +763,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_empty[buf]));
+        if (lane == 0) {
+          if (PAIR && rank != 0) mbar_arrive_cluster(cluster_map(smem_u32(&ctl->acc_empty[buf]), 0));
+          else mbar_arrive(smem_u32(&ctl->acc_empty[buf]));
+        }
         if (trace && et == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
 
         bool finalized = whole;
@@ -727,9 +777,9 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (et == 0) {
             uint32_t last = 0;
             if (ok) {
-              const uint32_t prev = atomicAdd(&p.counters[seg.tile], 1u);
+              const uint32_t prev = atomicAdd(&p.counters[tile_id], 1u);
               last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
-              if (last) p.counters[seg.tile] = 0;
+              if (last) p.counters[tile_id] = 0;
             }
             ctl->is_last = last;
           }
@@ -759,19 +809,23 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   tc_fence_before();
   __syncthreads();
+  // a CTA of a pair leaves only when its peer is done too: until then the peer may arrive on this CTA's barriers
+  // and rank 0's MMAs may read this CTA's shared memory; the tensor memory of the pair is freed after it
+  if (PAIR) cluster_sync_all();
   if (trace && threadIdx.x == 0) trace[7] = clock64();
   if (p.trace && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.trace[cta * 8 + 1] = t;
+    p.trace[blockIdx.x * 8 + 1] = t;
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, p.tmem_cols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, p.tmem_cols);
+    else tmem_dealloc(tmem_base, p.tmem_cols);
   }
   if ((p.tp.mode & kTpGatherWait) && threadIdx.x == 0) {
     // the last CTA of the grid closes the epoch of the gathered buffer
-    if (atomicAdd(&p.tp.ag_state[1], 1u) == static_cast<uint32_t>(grid) - 1u) {
+    if (atomicAdd(&p.tp.ag_state[1], 1u) == gridDim.x - 1u) {
       p.tp.ag_state[1] = 0;
       __threadfence();
       atomicAdd(&p.tp.ag_state[0], p.tp.ag_expected);
@@ -786,12 +840,82 @@ static int launch_sk_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqG
                          cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+    cudaError_t e = cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  wq_gemm_sk_kernel<FMT><<<grid, kSkThreads, smem, stream>>>(tx, tw, p);
+  wq_gemm_sk_kernel<FMT, false><<<grid, kSkThreads, smem, stream>>>(tx, tw, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+// CTA pairs: `grid` CTAs (even) launched as clusters of two.
+template <int FMT>
+static int launch_sk_pair_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemmParams& p, int grid, size_t smem,
+                              cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kSkThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, wq_gemm_sk_kernel<FMT, true>, tx, tw, p));
+}
+
+// How many CTA pairs can be resident at once (both CTAs of a cluster sit in one GPC, so a GPC with an odd number of
+// usable SMs leaves one out): the persistent schedule must not launch more, or the surplus pairs run as a second wave.
+template <int FMT>
+static int max_resident_pairs() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    if (cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024) != cudaSuccess)
+      return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(kSkThreads, 1, 1);
+    cfg.dynamicSmemBytes = 232448 - 1024;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, wq_gemm_sk_kernel<FMT, true>, &cfg) != cudaSuccess) n = 0;
+    cached[dev] = n > 0 ? n : -1;
+  }
+  return cached[dev] > 0 ? cached[dev] : 0;
+}
+static int max_resident_pairs_fmt(int fmt) {
+  switch (fmt) {
+    case kFmtCubic4: return max_resident_pairs<kFmtCubic4>();
+    case kFmtAffine4: return max_resident_pairs<kFmtAffine4>();
+    case kFmtNvfp4: return max_resident_pairs<kFmtNvfp4>();
+    default: return max_resident_pairs<kFmtBf16>();
+  }
+}
+
+int streamk_resident_pairs(int fmt) { return max_resident_pairs_fmt(fmt); }
+
+// Whether a launch with these sizes runs on CTA pairs: 256 batch rows per tile (that is where the activation tile
+// bounds the one-CTA form), an even number of weight tiles, not the grouped (expert) mode.
+bool streamk_pair_eligible(const WqGemmParams& p, int N) {
+  const int n_tiles = (N + kTileN - 1) / kTileN;
+  return p.mb == 256 && (n_tiles & 1) == 0 && p.group_tiles == nullptr;
 }
 
 // Schedule and launch.  `min_units` > 0 overrides the smallest run of k-blocks a CTA may be dealt in the
@@ -804,6 +928,15 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
   p.n_tiles = (p.N + kTileN - 1) / kTileN;
   const int m_tiles = (p.M + p.mb - 1) / p.mb;
   p.tiles = p.n_tiles * m_tiles;
+  if (p.pair) {
+    // the deal is over PAIRS of CTAs and pairs of adjacent weight tiles; below, "CTA" and "SM" read "pair"
+    if (!streamk_pair_eligible(p, p.N) || sm_count < 2) return -15;
+    p.tiles = (p.n_tiles >> 1) * m_tiles;
+    sm_count >>= 1;
+    const int resident = max_resident_pairs_fmt(fmt);
+    if (resident < 1) return -15;
+    if (sm_count > resident) sm_count = resident;
+  }
   if (p.group_tiles) {
     // grouped expert GEMMs: whole tiles only (the tile count lives on the device), one persistent CTA per SM at
     // most; what this buys over one CTA per tile is the set-up and epilogue of ~30 waves of small tiles
@@ -829,7 +962,8 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
   if (p.sk_tiles > 0) {
     // a CTA of the streamed region owns two fp32 partial slots (see sk_slot)
     const size_t part_bytes = static_cast<size_t>(p.mb) * kTileN * sizeof(float);
-    const long long slots_fit = (p.workspace && p.counters) ? static_cast<long long>(workspace_bytes / (2 * part_bytes)) : 0;
+    const long long slots_fit =
+        (p.workspace && p.counters) ? static_cast<long long>(workspace_bytes / ((p.pair ? 4 : 2) * part_bytes)) : 0;
     long long want = static_cast<long long>(p.sk_tiles) * p.k_blocks / min_units;
     if (want > sm_count) want = sm_count;
     if (want < 1) want = 1;
@@ -846,7 +980,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
   if (grid < p.sk_ctas) grid = p.sk_ctas;
   if (grid < 1) return -17;
 
-  const size_t ax = static_cast<size_t>(p.mb) * 128 + kATileBytes;
+  const size_t ax = static_cast<size_t>(p.pair ? p.mb >> 1 : p.mb) * 128 + kATileBytes;
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SkCtl) - kSkEpiScratchBytes;
   int S, NC;
   if (fmt == kFmtBf16) {
@@ -862,7 +996,19 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
   if (S < 2 || (fmt != kFmtBf16 && NC < 2)) return -14;
   p.ax_stages = S;
   p.c_stages = NC;
-  const size_t smem = S * ax + static_cast<size_t>(NC) * kSkCStageBytes + kSkEpiScratchBytes + sizeof(SkCtl) + 1024;
+  size_t smem = S * ax + static_cast<size_t>(NC) * kSkCStageBytes + kSkEpiScratchBytes + sizeof(SkCtl) + 1024;
+  if (p.pair) {
+    // the last segment's epilogue stages the fp32 tile [mb][128] in the ring memory
+    const size_t stage_bytes = static_cast<size_t>(p.mb) * kTileN * sizeof(float);
+    const size_t rings = S * ax + static_cast<size_t>(NC) * kSkCStageBytes;
+    if (rings < stage_bytes) smem += stage_bytes - rings;
+    switch (fmt) {
+      case kFmtCubic4: return launch_sk_pair_fmt<kFmtCubic4>(tx, tw, p, 2 * grid, smem, stream);
+      case kFmtAffine4: return launch_sk_pair_fmt<kFmtAffine4>(tx, tw, p, 2 * grid, smem, stream);
+      case kFmtNvfp4: return launch_sk_pair_fmt<kFmtNvfp4>(tx, tw, p, 2 * grid, smem, stream);
+      default: return launch_sk_pair_fmt<kFmtBf16>(tx, tw, p, 2 * grid, smem, stream);
+    }
+  }
   switch (fmt) {
     case kFmtCubic4: return launch_sk_fmt<kFmtCubic4>(tx, tw, p, grid, smem, stream);
     case kFmtAffine4: return launch_sk_fmt<kFmtAffine4>(tx, tw, p, grid, smem, stream);

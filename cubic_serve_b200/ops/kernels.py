@@ -87,21 +87,29 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     return max(1, min(sms // tiles, k_blocks // g.split_k_min_blocks, g.split_k_max))
 
 
-def use_stream_k(m: int, n: int, fmt: int, sms: int = 148) -> bool:
+def use_stream_k(m: int, n: int, fmt: int, sms: int = 148, k: int = 4096) -> bool:
     """Which GEMM kernel serves a shape when the caller does not say.
 
     Measured on a B200 inside CUDA graphs (cubic4, K = 4096): the persistent stream-K kernel wins when there are
     more weight tiles than SMs, because it removes the second, partly empty wave: N = 24576 runs 69 -> 45 us at
-    16-64 batch rows, 70 -> 54 us at 128 and 80 -> 70 us at 256 (the fix-up of a streamed tile is deferred to the
+    16-64 batch rows, 70 -> 54 us at 128 and 80 -> 69 us at 256 (the fix-up of a streamed tile is deferred to the
     end of its CTA and done by 640 threads), and the bf16 lm_head is 5 % faster.  With fewer tiles than SMs its
     fixed costs (start-up, fp32 partial tiles summed by the last CTA) make it 10-25 % slower than one CTA per
-    (tile, split); batches of more than 256 rows (several row tiles, prefill) stay on the per-tile kernel.
+    (tile, split).  Above 256 rows (prefill chunks, several row tiles) the persistent kernel runs on CTA pairs
+    (cta_group::2, half an activation tile per SM): 4096 x 24576 x 4096 takes 700 us against 778 us, 4096 x 4096 x
+    12288 342 against 425; it is chosen when every pair gets enough k-blocks to amortise its start-up
+    (512 x 6144 x 4096, 41 k-blocks per pair, is 48 us against 41 us on the per-tile kernel).
     The thresholds live in the operator configuration (``ops/strategies.py``).
     """
     from .strategies import active
     g = active().gemm
-    tiles = -(-n // 128) * -(-m // 256)
-    if tiles <= g.stream_k_min_tile_ratio * sms:
+    n_tiles = -(-n // 128)
+    m_tiles = -(-m // 256)
+    if m > max(g.stream_k_max_rows, 256) and fmt != FMT_BF16:
+        pairs = sms // 2
+        return (g.cta_pairs and n_tiles % 2 == 0 and pairs > 0
+                and (n_tiles // 2) * m_tiles * (k // 64) >= g.pair_min_blocks * pairs)
+    if n_tiles * m_tiles <= g.stream_k_min_tile_ratio * sms:
         return False
     return m <= g.stream_k_max_rows or (fmt == FMT_BF16 and g.stream_k_bf16)
 
@@ -127,7 +135,7 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
     l = native.lib()
-    if splits is None and min_units is None and use_stream_k(m, w.n, w.fmt, sm_count(x.device)):
+    if splits is None and min_units is None and use_stream_k(m, w.n, w.fmt, sm_count(x.device), k):
         from .strategies import active
         min_units = active().gemm.stream_k_min_units
     if splits is None and min_units is not None:
@@ -170,7 +178,7 @@ def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = Non
     assert out.stride(1) == 1 and out.shape == (m, w.n // 2)
     ws = ws or workspace(x.device)
     l = native.lib()
-    stream_k = splits is None and (min_units is not None or use_stream_k(m, w.n, w.fmt, sm_count(x.device)))
+    stream_k = splits is None and (min_units is not None or use_stream_k(m, w.n, w.fmt, sm_count(x.device), k))
     if stream_k and min_units is None:
         from .strategies import active
         min_units = active().gemm.stream_k_min_units

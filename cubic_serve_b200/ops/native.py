@@ -148,6 +148,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_moe_combine.restype = i
     l.cb_wq_gemm_grouped_mode.argtypes = [i]
     l.cb_wq_gemm_grouped_mode.restype = None
+    l.cb_wq_gemm_pair_mode.argtypes = [i]
+    l.cb_wq_gemm_pair_mode.restype = None
+    l.cb_wq_gemm_resident_pairs.argtypes = [i]
+    l.cb_wq_gemm_resident_pairs.restype = i
     l.cb_moe_permute.argtypes = [vp, vp, i, i, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
     l.cb_moe_permute.restype = i
     l.cb_ep_dispatch.argtypes = [vp, vp]

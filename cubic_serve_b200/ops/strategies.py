@@ -29,6 +29,8 @@ class GemmPolicy:
     split_k_max: int = 8                # per-tile kernel: largest split-K factor
     split_k_min_blocks: int = 8         # ... and the fewest k-blocks a split may get
     fuse_swiglu: bool = True            # SwiGLU in the epilogue of the gate/up GEMM (weight rows re-ordered at load)
+    cta_pairs: bool = True              # persistent kernel on CTA pairs (cta_group::2) above stream_k_max_rows ...
+    pair_min_blocks: int = 80           # ... when every pair gets at least this many k-blocks (else one CTA per tile)
 
 
 @dataclass(frozen=True)

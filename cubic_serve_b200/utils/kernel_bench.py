@@ -110,7 +110,8 @@ def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str 
         call = lambda: K.wq_gemm(x, w, out=y, splits=sp)                                     # noqa: E731
     ms = timeit_graph(call, flush, launches=max(3, min(10, iters)))
     K.workspace(torch.device(DEV)).check_status()
-    return {"op": f"wq_gemm[{fmt}]" + ("+swiglu" if act else ""), "m": m, "n": n, "k": k, "kernel": "streamk" if stream_k else "tile",
+    from ..ops import native
+    return {"op": f"wq_gemm[{fmt}]" + ("+swiglu" if act else ""), "resident_pairs": native.lib().cb_wq_gemm_resident_pairs(w.fmt), "m": m, "n": n, "k": k, "kernel": "streamk" if stream_k else "tile",
             "splits": None if stream_k else sp, "us": round(ms * 1e3, 1), "timing": "in-graph, L2 flushed",
             "tflops": round(2 * m * n * k / ms / 1e9, 1), "weight_gbs": round(wbytes / ms / 1e6, 1)}
 
@@ -199,8 +200,12 @@ def main() -> None:
     ap.add_argument("--vbits", type=int, default=8)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kernel", default="auto", choices=["auto", "tile", "streamk"])
+    ap.add_argument("--pairs", type=int, default=1, choices=[0, 1, 2],
+                    help="persistent kernel on CTA pairs (cta_group::2): never (0), above 256 rows (1), wherever eligible (2)")
     ap.add_argument("--act", action="store_true", help="gemm: [gate; up] projection with SwiGLU in the epilogue")
     a = ap.parse_args()
+    from ..ops import native
+    native.lib().cb_wq_gemm_pair_mode(a.pairs)
     if a.op == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.splits or None, a.iters, a.fmt, a.kernel, a.act)))
     elif a.op == "fused-tp":

@@ -139,6 +139,52 @@ def test_wq_gemm_fused_swiglu_other_formats():
             assert _rel(gu, K.wq_gemm(x, pw.to(DEV), **kw)) < 2e-3
 
 
+@pytest.mark.parametrize("m,n,k,min_units", [
+    (256, 256, 4096, 0), (256, 512, 4096, 0),     # one pair-tile, two pair-tiles, automatic schedule
+    (256, 1024, 1024, 3),                         # runs of three k-blocks that straddle pair-tile boundaries
+    (300, 512, 512, 2),                           # two row tiles, the second with 44 rows (rank 1's half is all padding)
+    (512, 128 * 40, 256, 0),                      # 40 pair-tiles on 74 pairs
+    (272, 128 * 160, 256, 1),                     # more pair-tiles than pairs: whole pair-tiles + a streamed remainder
+    (4096, 1024, 512, 0),                         # a prefill chunk: 16 row tiles
+])
+def test_wq_gemm_stream_k_cta_pairs(m, n, k, min_units):
+    """Persistent kernel on CTA pairs (cta_group::2, M = 256 MMAs, half an activation tile per CTA) against the
+    fp32 oracle and against the same launch with pairs switched off."""
+    from cubic_serve_b200.ops import native
+    K = _k()
+    pw, dense = _cubic_weight(n, k, seed=m + n)
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
+    ref = x.float() @ dense.t()
+    res = torch.randn(m, n, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16)
+    lib = native.lib()
+    try:
+        lib.cb_wq_gemm_pair_mode(2)
+        y = K.wq_gemm(x.to(DEV), pw.to(DEV), min_units=min_units)
+        torch.cuda.synchronize()
+        K.workspace(y.device).check_status()
+        assert _rel(y.cpu(), ref) < 1e-2
+        y2 = K.wq_gemm(x.to(DEV), pw.to(DEV), residual=res.to(DEV), min_units=min_units)
+        torch.cuda.synchronize()
+        K.workspace(y.device).check_status()
+        assert _rel(y2.cpu(), ref + res.float()) < 1e-2
+        assert torch.equal(K.wq_gemm(x.to(DEV), pw.to(DEV), min_units=min_units), y)      # deterministic
+        lib.cb_wq_gemm_pair_mode(0)
+        single = K.wq_gemm(x.to(DEV), pw.to(DEV), min_units=min_units)
+        assert _rel(y, single) < 2e-3
+        # bf16 weights (TMA-loaded A tiles of both CTAs complete on rank 0's barrier) and the fused activation
+        lib.cb_wq_gemm_pair_mode(2)
+        wb = (torch.randn(n, k, generator=torch.Generator().manual_seed(3)) * 0.05).to(torch.bfloat16)
+        yb = K.wq_gemm(x.to(DEV), wq_pack.pack_bf16(wb).to(DEV), min_units=min_units)
+        assert _rel(yb.cpu(), x.float() @ wb.float().t()) < 1e-2
+        pwi = wq_pack.swiglu_interleave(pw).to(DEV)
+        act = K.wq_gemm_act(x.to(DEV), pwi, min_units=min_units)
+        assert _rel(act.cpu(), eager.swiglu(ref.to(torch.bfloat16))) < 1.5e-2
+        torch.cuda.synchronize()
+        K.workspace(y.device).check_status()
+    finally:
+        lib.cb_wq_gemm_pair_mode(1)
+
+
 def test_wq_gemm_stream_k_bf16_weights():
     K = _k()
     for m, n, k, mu in ((48, 256, 512, 0), (256, 1000, 1024, 2), (24, 128 * 150 + 40, 256, 0)):

@@ -29,10 +29,15 @@ def test_policy_drives_kernel_choice():
     try:
         S.install(S.OperatorConfig())
         assert K.use_stream_k(64, 24576, FMT_CUBIC4) and K.use_stream_k(256, 24576, FMT_CUBIC4)
-        assert not K.use_stream_k(512, 24576, FMT_CUBIC4)
+        # above 256 rows: CTA pairs when every pair gets enough k-blocks
+        assert K.use_stream_k(512, 24576, FMT_CUBIC4) and K.use_stream_k(4096, 4096, FMT_CUBIC4, k=12288)
+        assert not K.use_stream_k(512, 6144, FMT_CUBIC4) and not K.use_stream_k(1024, 4096, FMT_CUBIC4)
+        assert not K.use_stream_k(4096, 24576 + 128, FMT_CUBIC4)          # odd number of weight tiles
         assert K.use_stream_k(256, 151936, FMT_BF16) and not K.use_stream_k(16, 6144, FMT_CUBIC4)
         assert K.choose_splits(256, 4096, 4096) == 4
         S.install(S.operator_config_from_dict({"gemm": {"stream_k_max_rows": 64, "split_k_max": 2}}))
         assert not K.use_stream_k(256, 24576, FMT_CUBIC4) and K.choose_splits(256, 4096, 4096) == 2
+        S.install(S.operator_config_from_dict({"gemm": {"cta_pairs": False}}))
+        assert not K.use_stream_k(512, 24576, FMT_CUBIC4) and K.use_stream_k(256, 24576, FMT_CUBIC4)
     finally:
         S.install(old)
