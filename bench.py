@@ -158,7 +158,7 @@ def main() -> None:
 
     weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=tp_rank, tp_size=tp_size, layer_range=layer_range)
     runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=k_bits, v_bits=v_bits,
-                           tp=tp, pp=pp)
+                           tp=tp, pp=pp, max_requests=max(C, 1))
     if args.spec_depth:
         from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
         from cubic_serve_b200.models.mtp import MtpRunner, random_mtp_weights

@@ -49,6 +49,9 @@ class _Staging:
             ("rb_qcount", np.int32, max_row_blocks), ("rb_ctx", np.int32, max_row_blocks),
             ("top_k", np.int32, max_rows), ("temperature", np.float32, max_rows), ("top_p", np.float32, max_rows),
             ("logit_rows", np.int64, max_rows), ("seeds", np.int64, max_rows), ("draws", np.int64, max_rows),
+            # the step's rows grouped by request (recurrent layers walk a request's rows in order)
+            ("seg_row0", np.int32, max_rows), ("seg_count", np.int32, max_rows), ("seg_slot", np.int32, max_rows),
+            ("seg_pos0", np.int32, max_rows),
             ("page_table", np.int32, max_rows * max_pages),
         ]
         off = 0
@@ -136,7 +139,11 @@ class BatchBuilder:
             h["rb_qstart"][:n] = ar
             h["rb_qcount"][:n] = 1
             h["rb_ctx"][:n] = starts + 1
-            t = rb = n
+            h["seg_row0"][:n] = ar
+            h["seg_count"][:n] = 1
+            h["seg_slot"][:n] = h["rb_req"][:n]
+            h["seg_pos0"][:n] = starts
+            t = rb = nseg = n
             rows = 0
             if all(s.sample for s in segs):
                 h["logit_rows"][:n] = ar
@@ -155,8 +162,10 @@ class BatchBuilder:
                         rows += 1
         else:
             t = rb = rows = 0
-            for s in segs:
+            nseg = len(segs)
+            for i, s in enumerate(segs):
                 n = len(s.token_ids)
+                h["seg_row0"][i], h["seg_count"][i], h["seg_slot"][i], h["seg_pos0"][i] = t, n, s.request_slot, s.start
                 h["token_ids"][t:t + n] = s.token_ids
                 pos = np.arange(s.start, s.start + n, dtype=np.int32)
                 h["positions"][t:t + n] = pos
@@ -187,7 +196,11 @@ class BatchBuilder:
             h["rb_ctx"][rb:p] = 0
             h["logit_rows"][rows:p] = np.arange(rows, p)
             h["temperature"][rows:p] = 0
-            t, rb, rows_cap = p, p, p
+            h["seg_row0"][nseg:p] = np.arange(nseg, p, dtype=np.int32)
+            h["seg_count"][nseg:p] = 0
+            h["seg_slot"][nseg:p] = 0
+            h["seg_pos0"][nseg:p] = 0
+            t, rb, rows_cap, nseg = p, p, p, p
         else:
             rows_cap = rows
         d = st.d
@@ -195,7 +208,8 @@ class BatchBuilder:
         return StepBatch(num_tokens=t, num_row_blocks=rb, num_logit_rows=rows_cap, token_ids=d["token_ids"],
                          positions=d["positions"], slots=d["slots"], page_table=d["page_table"], rb_req=d["rb_req"],
                          rb_qstart=d["rb_qstart"], rb_qcount=d["rb_qcount"], rb_ctx=d["rb_ctx"],
-                         logit_rows=d["logit_rows"], attn_splits=splits), rows
+                         logit_rows=d["logit_rows"], attn_splits=splits,
+                         segments=K.GdnSegments(d["seg_row0"], d["seg_count"], d["seg_slot"], d["seg_pos0"], nseg)), rows
 
 
 class GpuExecutor:
@@ -208,6 +222,8 @@ class GpuExecutor:
         self.max_rows = max_rows
         self.max_tokens = max(max_prefill_tokens, max_rows)
         assert self.max_tokens <= runner.max_tokens
+        if runner.cfg.is_hybrid and max_rows * rows_per_request > runner.max_requests:
+            raise ValueError("the runner's recurrent state has fewer rows than the executor has request slots")
         self.builder = BatchBuilder(max_rows * rows_per_request, self.max_tokens, max_model_len,
                                     runner.hq // runner.hkv, runner.hkv, self.device)
         self.stage = self.builder.stage

@@ -23,6 +23,10 @@ from .gpu_executor import GpuExecutor, Segment
 class SpeculativeGpuExecutor(GpuExecutor):
     def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
                  **kw) -> None:
+        if runner.cfg.is_hybrid:
+            # a rejected draft would have to roll the recurrent state back to the accepted prefix (the reference's
+            # fold kernel, ops/cuda/linear_attention/gated_delta_fold.cu); not built
+            raise NotImplementedError("speculative decoding is not available for models with Gated DeltaNet layers")
         super().__init__(runner, rows_per_request=depth + 1, use_graphs=False, **kw)
         self.mtp = mtp
         self.speculative_depth = depth

@@ -44,6 +44,13 @@ class ModelConfig:
     experts_per_token: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    # hybrid family (qwen3_5 style): every ``gdn_interval``-th layer is full attention, the others are Gated
+    # DeltaNet linear-attention layers with ``gdn_k_heads`` key / ``gdn_v_heads`` value heads of width 128
+    # (reference: ``models/qwen3_5/model.py:1399``); 0 = no such layers
+    gdn_interval: int = 0
+    gdn_k_heads: int = 0
+    gdn_v_heads: int = 0
+    attn_output_gate: bool = False      # full-attention output multiplied by sigmoid(gate projection)
     # MTP head (1 extra decoder layer sharing embeddings and lm_head)
     mtp_layers: int = 0
     quant: QuantSpec = field(default_factory=QuantSpec)
@@ -60,6 +67,14 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def is_hybrid(self) -> bool:
+        return self.gdn_interval > 0
+
+    def layer_is_gdn(self, layer: int) -> bool:
+        """Layer ``layer`` (global index) is a Gated DeltaNet layer (every ``gdn_interval``-th one is full attention)."""
+        return self.gdn_interval > 0 and (layer + 1) % self.gdn_interval != 0
 
     def to_json(self) -> str:
         return json.dumps(asdict(self), indent=1)
@@ -82,9 +97,18 @@ class ModelConfig:
         heads = text["num_attention_heads"]
         hd = text.get("head_dim") or text["hidden_size"] // heads
         n_exp = text.get("num_experts") or text.get("num_local_experts") or 0
+        hybrid = {}
+        if text.get("linear_num_value_heads"):
+            if int(text.get("linear_key_head_dim", 128)) != 128 or int(text.get("linear_value_head_dim", 128)) != 128:
+                raise ValueError("Gated DeltaNet layers are built for key / value head width 128")
+            hybrid = dict(gdn_interval=int(text.get("full_attention_interval", 4)),
+                          gdn_k_heads=int(text["linear_num_key_heads"]), gdn_v_heads=int(text["linear_num_value_heads"]),
+                          attn_output_gate=bool(text.get("attn_output_gate", True)), zero_centered_norm=True,
+                          rotary_dim=int(hd * float(text.get("partial_rotary_factor", 0.25))))
         return ModelConfig(
+            **hybrid,
             name=cfg.get("_name_or_path") or arch,
-            family="gqa_moe" if n_exp else "gqa_decoder",
+            family=("qwen3_5_moe" if n_exp else "qwen3_5") if hybrid else ("gqa_moe" if n_exp else "gqa_decoder"),
             num_layers=text["num_hidden_layers"],
             hidden_size=text["hidden_size"],
             num_q_heads=heads,
@@ -162,6 +186,14 @@ def moe_30b_config() -> ModelConfig:
                        quant=QuantSpec("nvfp4", 4, 16))
 
 
+def hybrid_8b_config() -> ModelConfig:
+    """8B-class hybrid decoder: three Gated DeltaNet layers for every full-attention layer (qwen3_5 layout)."""
+    return ModelConfig(name="hybrid-8b", family="qwen3_5", num_layers=36, hidden_size=4096, num_q_heads=32, num_kv_heads=8,
+                       head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e7, rotary_dim=64,
+                       qk_norm=True, zero_centered_norm=True, gdn_interval=4, gdn_k_heads=16, gdn_v_heads=32,
+                       attn_output_gate=True, quant=QuantSpec("cubic", 4, 128))
+
+
 def moe_235b_config() -> ModelConfig:
     return ModelConfig(name="moe-235b-a22b", family="gqa_moe", num_layers=94, hidden_size=4096, num_q_heads=64,
                        num_kv_heads=4, head_dim=128, intermediate_size=0, vocab_size=151936, rope_theta=1e6,
@@ -173,5 +205,6 @@ NAMED_CONFIGS = {
     "toy": toy_config,
     "dense-8b": dense_8b_config,
     "moe-30b-a3b": moe_30b_config,
+    "hybrid-8b": hybrid_8b_config,
     "moe-235b-a22b": moe_235b_config,
 }

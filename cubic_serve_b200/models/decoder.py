@@ -23,11 +23,27 @@ from .config import ModelConfig
 
 
 @dataclass
+class GdnWeights:
+    """Gated DeltaNet mixer of one layer (rank-local heads).  ``in_proj`` rows: q [Hk 128] | k [Hk 128] | v [Hv 128] |
+    z [Hv 128] | b [Hv] | a [Hv] (reference modules ``in_proj_qkvz`` + ``in_proj_ba``, ``models/qwen3_5/model.py:498``)."""
+    in_proj: wq_pack.PackedWeight
+    conv_w: torch.Tensor                 # fp32 [2 Hk 128 + Hv 128, 4]
+    a_log: torch.Tensor                  # fp32 [Hv]
+    dt_bias: torch.Tensor                # fp32 [Hv]
+    norm_w: torch.Tensor                 # fp32 [128]
+    out: wq_pack.PackedWeight            # [H, Hv 128]
+    hk: int = 0
+    hv: int = 0
+
+
+@dataclass
 class LayerWeights:
     ln1: torch.Tensor
     ln2: torch.Tensor
-    qkv: wq_pack.PackedWeight
-    o: wq_pack.PackedWeight
+    qkv: wq_pack.PackedWeight | None = None     # None for Gated DeltaNet layers
+    o: wq_pack.PackedWeight | None = None
+    gdn: GdnWeights | None = None
+    attn_gate: wq_pack.PackedWeight | None = None   # [hq D, H]: output gate of the hybrid family's attention layers
     gate_up: wq_pack.PackedWeight | None = None
     down: wq_pack.PackedWeight | None = None
     q_norm: torch.Tensor | None = None
@@ -47,7 +63,9 @@ class DecoderWeights:
     def nbytes(self) -> int:
         total = self.embed.numel() * 2 + self.lm_head.nbytes
         for l in self.layers:
-            ws = [l.qkv, l.o, l.gate_up, l.down]
+            ws = [l.qkv, l.o, l.gate_up, l.down, l.attn_gate]
+            if l.gdn is not None:
+                ws += [l.gdn.in_proj, l.gdn.out]
             if l.moe is not None:
                 ws += [l.moe.router, l.moe.gate_up, l.moe.down]
             for w in ws:
@@ -106,18 +124,32 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
         return torch.randn(n, k, device=device, generator=gen, dtype=torch.float32) * std
 
     def norm_w():
-        return torch.ones(H, device=device, dtype=torch.bfloat16)
+        # zero-centred norms multiply by (1 + w)
+        return torch.full((H,), 0.0 if cfg.zero_centered_norm else 1.0, device=device, dtype=torch.bfloat16)
 
     layers = []
     lo, hi = layer_range or (0, cfg.num_layers)
     for li in range(lo, hi):
         gen.manual_seed((seed * 1000 + tp_rank) * 4096 + li)
-        lw = LayerWeights(
-            ln1=norm_w(), ln2=norm_w(),
-            qkv=quantize_linear(rnd((hq + 2 * hkv) * D, H), cfg),
-            o=quantize_linear(rnd(H, hq * D), cfg),
-        )
-        if cfg.qk_norm:
+        if cfg.layer_is_gdn(li):
+            gk, gv = cfg.gdn_k_heads // tp_size, cfg.gdn_v_heads // tp_size
+            f32 = dict(device=device, dtype=torch.float32)
+            lw = LayerWeights(ln1=norm_w(), ln2=norm_w(), gdn=GdnWeights(
+                in_proj=quantize_linear(rnd(2 * gk * 128 + 2 * gv * 128 + 2 * gv, H), cfg),
+                conv_w=torch.randn((2 * gk + gv) * 128, 4, generator=gen, **f32) * 0.3,
+                a_log=torch.randn(gv, generator=gen, **f32) * 0.5,
+                dt_bias=torch.randn(gv, generator=gen, **f32) * 0.5,
+                norm_w=torch.ones(128, **f32),
+                out=quantize_linear(rnd(H, gv * 128), cfg), hk=gk, hv=gv))
+        else:
+            lw = LayerWeights(
+                ln1=norm_w(), ln2=norm_w(),
+                qkv=quantize_linear(rnd((hq + 2 * hkv) * D, H), cfg),
+                o=quantize_linear(rnd(H, hq * D), cfg),
+            )
+            if cfg.attn_output_gate:
+                lw.attn_gate = quantize_linear(rnd(hq * D, H), cfg)
+        if cfg.qk_norm and lw.gdn is None:
             lw.q_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
             lw.k_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
         if cfg.is_moe:
@@ -159,11 +191,13 @@ class StepBatch:
     rb_ctx: torch.Tensor
     logit_rows: torch.Tensor     # int64 [R] rows of the hidden state that feed lm_head
     attn_splits: int = 1
+    segments: object | None = None   # K.GdnSegments: the step's rows grouped by request (Gated DeltaNet layers)
 
 
 class DecoderRunner:
     def __init__(self, cfg: ModelConfig, weights: DecoderWeights, num_pages: int, max_tokens: int,
-                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None, pp=None) -> None:
+                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None, pp=None, max_requests: int = 256) -> None:
+        """``max_requests``: rows of the per-request recurrent state of Gated DeltaNet layers (= page-table rows)."""
         self.cfg = cfg
         self.w = weights            # ``weights.layers`` holds only the layers of this pipeline stage
         self.device = device or weights.embed.device
@@ -183,8 +217,27 @@ class DecoderRunner:
         self.num_pages = num_pages
         # one cache tensor per layer: [pages, kv_heads, blob]; zero-filled so that
         # never-written slots hold finite scales
-        self.kv = [torch.zeros(num_pages, self.hkv, blob, dtype=torch.uint8, device=dev)
-                   for _ in range(len(weights.layers))]
+        self.kv = [torch.zeros(0 if lw.gdn is not None else num_pages, self.hkv, blob, dtype=torch.uint8, device=dev)
+                   for lw in weights.layers]
+        # Gated DeltaNet layers: per request the last three conv inputs of every channel and one 128 x 128 fp32 state
+        # per value head; a request's row is its page-table row, reset implicitly when it starts at position 0
+        self.max_requests = max_requests
+        self.gdn_conv_state, self.gdn_state = {}, {}
+        gdn_first = next((lw.gdn for lw in weights.layers if lw.gdn is not None), None)
+        if gdn_first is not None:
+            if tp is not None and tp.fused is not None:
+                raise ValueError("Gated DeltaNet layers use the NCCL tensor-parallel collectives (tp mode 'nccl')")
+            gk, gv = gdn_first.hk, gdn_first.hv
+            C = (2 * gk + gv) * 128
+            for li, lw in enumerate(weights.layers):
+                if lw.gdn is not None:
+                    self.gdn_conv_state[li] = torch.zeros(max_requests, 3, C, dtype=torch.bfloat16, device=dev)
+                    self.gdn_state[li] = torch.zeros(max_requests, gv, 128, 128, dtype=torch.float32, device=dev)
+            self.gdn_in = torch.empty(max_tokens, gdn_first.in_proj.n, dtype=torch.bfloat16, device=dev)
+            self.gdn_mix = torch.empty(max_tokens, C, dtype=torch.bfloat16, device=dev)
+            self.gdn_out = torch.empty(max_tokens, gv * 128, dtype=torch.bfloat16, device=dev)
+        if any(lw.attn_gate is not None for lw in weights.layers):
+            self.gate = torch.empty(max_tokens, self.hq * self.D, dtype=torch.bfloat16, device=dev)
         self.inv_freq = rope_inv_freq(cfg.rotary_dim or self.D, cfg.rope_theta, dev)
         bf = torch.bfloat16
         T = max_tokens
@@ -237,6 +290,24 @@ class DecoderRunner:
                 pp.send(self.h[t0:t1])
         return self.h[:T]
 
+    def _gdn_mixer(self, li: int, g: GdnWeights, x: torch.Tensor, b: StepBatch, t0: int, t1: int) -> torch.Tensor:
+        """Gated DeltaNet token mixer of layer ``li`` over rows ``[t0, t1)``: projection, causal conv + SiLU, gated
+        delta rule + gated norm.  Returns the ``[rows, Hv 128]`` input of the output projection."""
+        if b.segments is None:
+            raise RuntimeError("Gated DeltaNet layers need the step's request segments (StepBatch.segments)")
+        if t0 != 0 or t1 != b.num_tokens:
+            raise NotImplementedError("pipeline lanes split a step's rows; Gated DeltaNet layers take whole steps")
+        proj = self.gdn_in[t0:t1]
+        K.wq_gemm(x, g.in_proj, out=proj, ws=self.ws)
+        C = (2 * g.hk + g.hv) * 128
+        mix, out = self.gdn_mix[t0:t1], self.gdn_out[t0:t1]
+        K.gdn_conv(proj, g.conv_w, self.gdn_conv_state[li], b.segments, mix)
+        z = proj[:, C:C + g.hv * 128]
+        ba = proj[:, C + g.hv * 128:]
+        K.gdn_delta(mix, z, ba, g.a_log, g.dt_bias, g.norm_w, self.gdn_state[li], b.segments, out, g.hk, g.hv,
+                    eps_norm=self.cfg.rms_eps)
+        return out
+
     def _run_layers(self, b: StepBatch, t0: int, t1: int, rb0: int, rb1: int, embed: bool) -> None:
         """Layers of this stage over rows ``[t0, t1)`` whose attention row blocks are ``[rb0, rb1)``."""
         cfg, w = self.cfg, self.w
@@ -255,20 +326,30 @@ class DecoderRunner:
         for li, lw in enumerate(w.layers):
             K.rmsnorm(pending if pending is not None else h, lw.ln1, cfg.rms_eps, out=x,
                       residual=h if pending is not None else None, zero_centered=cfg.zero_centered_norm)
-            K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
-            K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
-                            self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
-                            rotary_dim=cfg.rotary_dim)
-            K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
-                              b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
-                              splits=b.attn_splits, ws=self.ws)
-            n += 4
+            if lw.gdn is not None:
+                mixed, o_w = self._gdn_mixer(li, lw.gdn, x, b, t0, t1), lw.gdn.out
+                n += 4
+            else:
+                K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
+                K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
+                                self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
+                                rotary_dim=cfg.rotary_dim)
+                K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
+                                  b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
+                                  splits=b.attn_splits, ws=self.ws)
+                n += 4
+                if lw.attn_gate is not None:
+                    gate = self.gate[t0:t1]
+                    K.wq_gemm(x, lw.attn_gate, out=gate, ws=self.ws)
+                    K.sigmoid_gate(attn, gate)
+                    n += 2
+                mixed, o_w = attn, lw.o
             if self.tp is None:
-                K.wq_gemm(attn, lw.o, out=h, residual=h, ws=self.ws)
+                K.wq_gemm(mixed, o_w, out=h, residual=h, ws=self.ws)
                 K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x, zero_centered=cfg.zero_centered_norm)
             else:
                 part = self.part[t0:t1]
-                K.wq_gemm(attn, lw.o, out=part, ws=self.ws)
+                K.wq_gemm(mixed, o_w, out=part, ws=self.ws)
                 self.tp.all_reduce(part)
                 K.rmsnorm(part, lw.ln2, cfg.rms_eps, out=x, residual=h, zero_centered=cfg.zero_centered_norm)
             n += 2

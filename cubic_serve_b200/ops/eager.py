@@ -142,3 +142,54 @@ def decode_cache_page(blob: torch.Tensor, d: int, k_bits: int, v_bits: int):
     ksc = blob[lay["k_scale"]:lay["v_code"]].contiguous().view(torch.float32).reshape(PAGE_TOKENS, d // KV_GROUP)
     vsc = blob[lay["v_scale"]:lay["bytes"]].contiguous().view(torch.float32).reshape(PAGE_TOKENS, d // KV_GROUP)
     return kv_dequantize(kcodes, ksc), kv_dequantize(vcodes, vsc)
+
+
+# ------------------------------------------------------------------ gated delta net (hybrid family) oracles
+def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, bias: torch.Tensor | None = None):
+    """Depthwise causal conv1d (kernel 4) + SiLU over ONE request's rows ``x[n, C]`` (bf16); ``state[3, C]`` = its
+    previous three inputs (None = zeros).  Returns ``(y[n, C] bf16, new state[3, C] bf16)``.  fp32 arithmetic, the
+    order of ``csrc/gdn.cu`` (reference oracle: ``ops/eager/hybrid.py:255``)."""
+    n, c = x.shape
+    hist = torch.zeros(3, c) if state is None else state.float().cpu()
+    seq = torch.cat([hist, x.float().cpu()], 0)
+    wf = w.float().cpu()
+    y = torch.empty(n, c)
+    for t in range(n):
+        win = seq[t:t + 4]                                  # inputs t-3 .. t
+        a = wf[:, 0] * win[0] + wf[:, 1] * win[1] + wf[:, 2] * win[2] + wf[:, 3] * win[3]
+        if bias is not None:
+            a = a + bias.float().cpu()
+        y[t] = a / (1 + torch.exp(-a))
+    return y.to(torch.bfloat16), seq[-3:].to(torch.bfloat16)
+
+
+def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+              norm_w: torch.Tensor, state: torch.Tensor | None, hk: int, hv: int, eps_norm: float = 1e-6,
+              eps_l2: float = 1e-6):
+    """Gated delta rule + gated RMSNorm over ONE request's rows (fp32 recurrence; reference oracle:
+    ``ops/eager/hybrid.py:340-548``).  ``state[Hv, 128, 128]`` fp32 or None.  Returns ``(out[n, Hv 128] bf16, state)``."""
+    n = qkv.shape[0]
+    d = 128
+    bf = torch.bfloat16
+    q = qkv[:, :hk * d].float().cpu().view(n, hk, d)
+    k = qkv[:, hk * d:2 * hk * d].float().cpu().view(n, hk, d)
+    v = qkv[:, 2 * hk * d:2 * hk * d + hv * d].float().cpu().view(n, hv, d)
+    zz = z.float().cpu().view(n, hv, d)
+    b, a = ba[:, :hv].float().cpu(), ba[:, hv:2 * hv].float().cpu()
+    S = torch.zeros(hv, d, d) if state is None else state.float().cpu().clone()
+    rep = hv // hk
+    out = torch.empty(n, hv, d)
+    for t in range(n):
+        qn = (q[t] * torch.rsqrt((q[t] * q[t]).sum(-1, keepdim=True) + eps_l2)).to(bf).float() * (d ** -0.5)
+        kn = (k[t] * torch.rsqrt((k[t] * k[t]).sum(-1, keepdim=True) + eps_l2)).to(bf).float()
+        qn, kn = qn.repeat_interleave(rep, 0), kn.repeat_interleave(rep, 0)          # [Hv, d]
+        beta = torch.sigmoid(b[t])
+        decay = torch.exp(-torch.exp(a_log.float().cpu()) * torch.nn.functional.softplus(a[t] + dt_bias.float().cpu()))
+        S = S * decay[:, None, None]
+        mem = (S * kn[:, None, :]).sum(-1)                                           # [Hv, d_v]
+        delta = (v[t] - mem) * beta[:, None]
+        S = S + delta[:, :, None] * kn[:, None, :]
+        o = (S * qn[:, None, :]).sum(-1).to(bf).float()
+        normed = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps_norm)).to(bf).float()
+        out[t] = normed * norm_w.float().cpu()[None, :] * (zz[t] / (1 + torch.exp(-zz[t])))
+    return out.reshape(n, hv * d).to(bf), S

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+from dataclasses import dataclass
 
 import torch
 
@@ -391,4 +392,66 @@ def moe_combine(y: torch.Tensor, sc: MoeScratch, tokens: int, out: torch.Tensor,
     code = native.lib().cb_moe_combine(y.data_ptr(), sc.route_pos.data_ptr(), sc.topk_w.data_ptr(), tokens,
                                        sc.topk_ids.shape[1], y.shape[1], _ptr(residual), out.data_ptr(), _stream())
     native.check(code, "cb_moe_combine")
+    return out
+
+
+# ------------------------------------------------------------------ gated delta net (hybrid family)
+@dataclass
+class GdnSegments:
+    """A step's token rows grouped by request: rows ``[row0, row0 + count)`` of state slot ``slot``, the first at
+    absolute position ``pos0`` (0 = the request starts here, from zero state).  int32 device tensors of length >= num."""
+    row0: torch.Tensor
+    count: torch.Tensor
+    slot: torch.Tensor
+    pos0: torch.Tensor
+    num: int
+
+    def struct(self) -> "native.GdnSegmentsStruct":
+        s = native.GdnSegmentsStruct()
+        s.row0, s.count, s.slot, s.pos0 = self.row0.data_ptr(), self.count.data_ptr(), self.slot.data_ptr(), self.pos0.data_ptr()
+        s.num = int(self.num)
+        return s
+
+
+def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, seg: GdnSegments, out: torch.Tensor,
+             bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Depthwise causal conv1d (kernel 4) + SiLU over ``x[T, C]`` per request segment; ``state[slots, 3, C]`` holds
+    every request's last three inputs and is updated.  ``w``: fp32 ``[C, 4]`` (tap 3 multiplies the current input)."""
+    c = w.shape[0]
+    assert w.dtype == torch.float32 and w.shape[1] == 4 and w.is_contiguous()
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] >= c
+    assert state.dtype == torch.bfloat16 and state.shape[1:] == (3, c) and state.is_contiguous()
+    st = seg.struct()
+    code = native.lib().cb_gdn_conv(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), w.data_ptr(), _ptr(bias),
+                                    state.data_ptr(), ctypes.byref(st), c, _stream())
+    native.check(code, "cb_gdn_conv")
+    return out
+
+
+def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+              norm_w: torch.Tensor, state: torch.Tensor, seg: GdnSegments, out: torch.Tensor, hk: int, hv: int,
+              eps_norm: float = 1e-6, eps_l2: float = 1e-6) -> torch.Tensor:
+    """Gated delta rule + gated RMSNorm per (segment, value head); ``state[slots, Hv, 128, 128]`` fp32 is updated.
+
+    ``qkv[T, 2 Hk 128 + Hv 128]`` (after ``gdn_conv``), ``z[T, Hv 128]``, ``ba[T, 2 Hv]`` = ``[b | a]``.
+    """
+    assert state.dtype == torch.float32 and state.shape[1:] == (hv, 128, 128) and state.is_contiguous()
+    for t in (a_log, dt_bias, norm_w):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    d = native.GdnDeltaStruct()
+    d.qkv, d.ldqkv, d.z, d.ldz, d.ba, d.ldba = qkv.data_ptr(), qkv.stride(0), z.data_ptr(), z.stride(0), ba.data_ptr(), ba.stride(0)
+    d.a_log, d.dt_bias, d.norm_w, d.state = a_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr(), state.data_ptr()
+    d.out, d.ldo, d.Hk, d.Hv, d.eps_norm, d.eps_l2 = out.data_ptr(), out.stride(0), hk, hv, eps_norm, eps_l2
+    st = seg.struct()
+    native.check(native.lib().cb_gdn_delta(ctypes.byref(d), ctypes.byref(st), _stream()), "cb_gdn_delta")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = x * sigmoid(gate)`` (bf16; the output gate of the hybrid family's full-attention layers)."""
+    rows, cols = x.shape
+    out = x if out is None else out
+    code = native.lib().cb_sigmoid_gate(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), out.data_ptr(),
+                                        out.stride(0), rows, cols, _stream())
+    native.check(code, "cb_sigmoid_gate")
     return out

@@ -148,6 +148,12 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_moe_combine.restype = i
     l.cb_wq_gemm_grouped_mode.argtypes = [i]
     l.cb_wq_gemm_grouped_mode.restype = None
+    l.cb_gdn_conv.argtypes = [vp, i, vp, i, vp, vp, vp, vp, i, vp]
+    l.cb_gdn_conv.restype = i
+    l.cb_gdn_delta.argtypes = [vp, vp, vp]
+    l.cb_gdn_delta.restype = i
+    l.cb_sigmoid_gate.argtypes = [vp, i, vp, i, vp, i, i, i, vp]
+    l.cb_sigmoid_gate.restype = i
     l.cb_wq_gemm_pair_mode.argtypes = [i]
     l.cb_wq_gemm_pair_mode.restype = None
     l.cb_wq_gemm_resident_pairs.argtypes = [i]
@@ -173,6 +179,21 @@ class TpLinkStruct(ctypes.Structure):
     _fields_ = [("mode", ctypes.c_int), ("rank", ctypes.c_int), ("size", ctypes.c_int),
                 ("rows_per_rank", ctypes.c_int), ("recv", ctypes.c_void_p * 8), ("rs_flag", ctypes.c_void_p * 8),
                 ("ag_flag", ctypes.c_void_p), ("ag_state", ctypes.c_void_p), ("ag_expected", ctypes.c_uint)]
+
+
+class GdnSegmentsStruct(ctypes.Structure):
+    """Mirror of ``CbGdnSegments`` in ``csrc/gdn.cu``."""
+    _fields_ = [("row0", ctypes.c_void_p), ("count", ctypes.c_void_p), ("slot", ctypes.c_void_p),
+                ("pos0", ctypes.c_void_p), ("num", ctypes.c_int)]
+
+
+class GdnDeltaStruct(ctypes.Structure):
+    """Mirror of ``CbGdnDelta`` in ``csrc/gdn.cu``."""
+    _fields_ = [("qkv", ctypes.c_void_p), ("ldqkv", ctypes.c_int), ("z", ctypes.c_void_p), ("ldz", ctypes.c_int),
+                ("ba", ctypes.c_void_p), ("ldba", ctypes.c_int), ("a_log", ctypes.c_void_p),
+                ("dt_bias", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("state", ctypes.c_void_p),
+                ("out", ctypes.c_void_p), ("ldo", ctypes.c_int), ("Hk", ctypes.c_int), ("Hv", ctypes.c_int),
+                ("eps_norm", ctypes.c_float), ("eps_l2", ctypes.c_float)]
 
 
 class ReduceNormStruct(ctypes.Structure):

@@ -40,6 +40,10 @@ class LLMEngine:
                  eos_token_id: int | None = None) -> None:
         self.executor = executor
         self.cfg = scheduler_config or SchedulerConfig()
+        if getattr(getattr(executor, "cfg", None), "is_hybrid", False) and self.cfg.enable_prefix_cache:
+            # recurrent (Gated DeltaNet) state is not part of the paged prefix cache: every request prefills from 0
+            from dataclasses import replace
+            self.cfg = replace(self.cfg, enable_prefix_cache=False)
         self.pool = PagePool(num_pages)
         self.prefix = PrefixCache(self.pool, enabled=self.cfg.enable_prefix_cache)
         self.scheduler = ContinuousScheduler(self.cfg, self.pool, self.prefix)

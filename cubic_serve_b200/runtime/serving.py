@@ -32,8 +32,14 @@ def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int
     """Pages that fit in the remaining device memory (one page = 16 tokens of every local layer's rank-local KV
     heads; ``layers`` = decoder layers held by this pipeline stage, default all)."""
     from ..ops.kernels import kv_blob_bytes
-    per_page = (layers or cfg.num_layers) * (cfg.num_kv_heads // tp) * kv_blob_bytes(cfg.head_dim, k_bits, v_bits)
+    n_layers = layers or cfg.num_layers
+    n_gdn = sum(cfg.layer_is_gdn(i) for i in range(cfg.num_layers)) if layers is None else 0
+    per_page = (n_layers - n_gdn) * (cfg.num_kv_heads // tp) * kv_blob_bytes(cfg.head_dim, k_bits, v_bits)
     budget = max(0, free_bytes - reserve_bytes)
+    if n_gdn:
+        # Gated DeltaNet layers keep, per request, one 128 x 128 fp32 state per value head and three conv inputs
+        gk, gv = cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp
+        budget = max(0, budget - n_gdn * max_running * (gv * 128 * 128 * 4 + 3 * (2 * gk + gv) * 128 * 2))
     pages = budget // per_page
     cap = max_running * (-(-max_model_len // 16)) + 64
     return int(max(64, min(pages, cap)))
@@ -81,7 +87,8 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
             free = min(free, int(args.gpu_memory_gib * 2 ** 30) - torch.cuda.memory_allocated(dev))
         pages = plan_kv_pages(free, int(args.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, 1, k_bits, v_bits, max_len,
                               args.max_running_requests)
-        runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits)
+        runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits,
+                               max_requests=args.max_running_requests)
         depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None else 0
         if depth:
             # MTP speculative decoding (--speculative-config): draft head + review rounds instead of graph decode

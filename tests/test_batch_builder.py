@@ -18,6 +18,10 @@ def test_decode_fast_path_and_padding():
     assert h["page_table"][1, :4].tolist() == [10, 11, 12, 13]
     assert np.allclose(h["temperature"][:3], 0.5) and h["temperature"][3] == 0 and h["top_k"][:3].tolist() == [3, 3, 3]
     assert b.attn_splits == min(32, -(-296 // (8 * 2)))
+    # request segments (recurrent layers): one row each, padding segments have no rows
+    assert b.segments.num == 8 and h["seg_count"][:8].tolist() == [1, 1, 1, 0, 0, 0, 0, 0]
+    assert h["seg_row0"][:8].tolist() == list(range(8)) and h["seg_slot"][:3].tolist() == [0, 1, 2]
+    assert h["seg_pos0"][:3].tolist() == [33, 34, 35]
 
 
 def test_prefill_blocks_and_incremental_page_rows():
@@ -29,6 +33,8 @@ def test_prefill_blocks_and_incremental_page_rows():
     assert h["rb_qstart"][:4].tolist() == [0, 2, 4, 5] and h["rb_qcount"][:4].tolist() == [2, 2, 1, 2]
     assert h["rb_ctx"][:4].tolist() == [17, 19, 21, 1] and h["rb_req"][:4].tolist() == [2, 2, 2, 0]
     assert h["logit_rows"][0] == 4 and h["slots"][:5].tolist() == [8 * 16 + i for i in range(5)]
+    assert b.segments.num == 2 and h["seg_row0"][:2].tolist() == [0, 5] and h["seg_count"][:2].tolist() == [5, 2]
+    assert h["seg_slot"][:2].tolist() == [2, 0] and h["seg_pos0"][:2].tolist() == [16, 0]
     # the request grows by one page: only the new entry is written
     h["page_table"][2, 0] = 99                        # would be overwritten by a full rewrite
     seg2 = Segment(2, [1], 32, [7, 8, 9], True, uid=5)

@@ -38,3 +38,20 @@ def test_launch_plan_and_lease():
     with pytest.raises(RuntimeError):
         pool.release(a)
     pool.release(b)
+
+
+def test_hybrid_config_layer_types_and_hf_parse(tmp_path):
+    import json
+    from cubic_serve_b200.models.config import ModelConfig, hybrid_8b_config
+    cfg = hybrid_8b_config()
+    assert cfg.is_hybrid and [cfg.layer_is_gdn(i) for i in range(8)] == [True, True, True, False] * 2
+    assert not ModelConfig().is_hybrid and not ModelConfig().layer_is_gdn(0)
+    hf = {"architectures": ["Qwen3NextForCausalLM"], "num_hidden_layers": 8, "hidden_size": 512, "num_attention_heads": 4,
+          "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 1024, "vocab_size": 1000, "rms_norm_eps": 1e-6,
+          "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 128, "linear_value_head_dim": 128,
+          "full_attention_interval": 4, "partial_rotary_factor": 0.25}
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    got = ModelConfig.from_hf_config(tmp_path / "config.json")
+    assert got.family == "qwen3_5" and got.gdn_interval == 4 and (got.gdn_k_heads, got.gdn_v_heads) == (2, 4)
+    assert got.rotary_dim == 32 and got.zero_centered_norm and got.attn_output_gate
+    assert sum(got.layer_is_gdn(i) for i in range(8)) == 6
