@@ -93,8 +93,12 @@ struct GdnDeltaParams {
   GdnSegments seg;
 };
 
-// grid (Hv, segments), 256 threads: thread t owns state row v = t >> 1 and the key columns [64 (t & 1), + 64).
-// two CTAs per SM (128 registers per thread): one CTA's state load / store overlaps the other's arithmetic
+// grid (Hv, segments), 256 threads.  Eight lanes share a state row: lane l8 = lane & 7 owns the float4 chunks
+// l8, l8 + 8, l8 + 16, l8 + 24 of the row's 128 key columns, so one load instruction of a warp covers four whole
+// 512-byte rows (fully coalesced; the state is the only large operand: 64 KiB per CTA read and written once per
+// step).  A thread holds four rows: warp * 16 + (lane >> 3) + 4 i.  Row sums (S k and S q) are reduced over the
+// eight lanes by shuffles.  Two CTAs per SM (128 registers per thread): one CTA's state load / store overlaps the
+// other's arithmetic.
 __global__ void __launch_bounds__(256, 2)
 gdn_delta_kernel(const GdnDeltaParams p) {
   const int head = blockIdx.x;
@@ -103,53 +107,59 @@ gdn_delta_kernel(const GdnDeltaParams p) {
   if (n <= 0) return;
   const int row0 = p.seg.row0[s];
   const int tid = threadIdx.x;
-  const int vi = tid >> 1;
-  const int kh = (tid & 1) * 64;
+  const int lane = tid & 31;
+  const int l8 = lane & 7;
+  const int vrow = (tid >> 5) * 16 + (lane >> 3);        // + 4 i
   const int khead = head / (p.Hv / p.Hk);
-  __shared__ float qs[kGdnDim], ks[kGdnDim];
+  __shared__ __align__(16) float qs[kGdnDim];
+  __shared__ __align__(16) float ks[kGdnDim];
   __shared__ float red[3][8];
 
-  float* sp = p.state + ((static_cast<size_t>(p.seg.slot[s]) * p.Hv + head) * kGdnDim + vi) * kGdnDim + kh;
-  float S[64];
+  float* sp = p.state + ((static_cast<size_t>(p.seg.slot[s]) * p.Hv + head) * kGdnDim + vrow) * kGdnDim + l8 * 4;
+  float4 S[4][4];                                        // [row i][chunk c]: columns 4 (l8 + 8 c) .. + 3
   if (p.seg.pos0[s] > 0) {
 #pragma unroll
-    for (int j = 0; j < 64; j += 4) {
-      const float4 v4 = *reinterpret_cast<const float4*>(sp + j);
-      S[j] = v4.x; S[j + 1] = v4.y; S[j + 2] = v4.z; S[j + 3] = v4.w;
-    }
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) S[i][c] = *reinterpret_cast<const float4*>(sp + (4 * i) * kGdnDim + 32 * c);
   } else {
 #pragma unroll
-    for (int j = 0; j < 64; ++j) S[j] = 0.f;
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) S[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   const float neg_exp_a = -__expf(p.a_log[head]);
   const float dtb = p.dt_bias[head];
-  const float nw = p.norm_w[vi];
   const int q_off = khead * kGdnDim, k_off = (p.Hk + khead) * kGdnDim, v_off = (2 * p.Hk + head) * kGdnDim;
+  float nw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) nw[i] = p.norm_w[vrow + 4 * i];
 
-  // operands of the first row; every iteration loads the next row's before it computes
-  const __nv_bfloat16* row = p.qkv + static_cast<size_t>(row0) * p.ldqkv;
-  float qk_next = 0.f, v_next, b_next, a_next, z_next;
-  if (tid < 128) qk_next = __bfloat162float(row[q_off + tid]);
-  else qk_next = __bfloat162float(row[k_off + tid - 128]);
-  v_next = __bfloat162float(row[v_off + vi]);
-  b_next = __bfloat162float(p.ba[static_cast<size_t>(row0) * p.ldba + head]);
-  a_next = __bfloat162float(p.ba[static_cast<size_t>(row0) * p.ldba + p.Hv + head]);
-  z_next = __bfloat162float(p.z[static_cast<size_t>(row0) * p.ldz + head * kGdnDim + vi]);
+  // operands of a row: thread tid carries q[tid] (tid < 128) or k[tid - 128] into the norm, every thread the v and
+  // z of its four state rows; each iteration loads the next row's before it computes
+  float qk_next, v_next[4], z_next[4], b_next, a_next;
+  auto load_row = [&](size_t r) {
+    const __nv_bfloat16* row = p.qkv + r * p.ldqkv;
+    qk_next = __bfloat162float(tid < 128 ? row[q_off + tid] : row[k_off + tid - 128]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v_next[i] = __bfloat162float(row[v_off + vrow + 4 * i]);
+      z_next[i] = __bfloat162float(p.z[r * p.ldz + head * kGdnDim + vrow + 4 * i]);
+    }
+    b_next = __bfloat162float(p.ba[r * p.ldba + head]);
+    a_next = __bfloat162float(p.ba[r * p.ldba + p.Hv + head]);
+  };
+  load_row(static_cast<size_t>(row0));
 
   for (int t = 0; t < n; ++t) {
-    const float qk = qk_next, v = v_next, bb = b_next, aa = a_next, zz = z_next;
-    if (t + 1 < n) {
-      const size_t r = static_cast<size_t>(row0 + t + 1);
-      const __nv_bfloat16* nrow = p.qkv + r * p.ldqkv;
-      qk_next = __bfloat162float(tid < 128 ? nrow[q_off + tid] : nrow[k_off + tid - 128]);
-      v_next = __bfloat162float(nrow[v_off + vi]);
-      b_next = __bfloat162float(p.ba[r * p.ldba + head]);
-      a_next = __bfloat162float(p.ba[r * p.ldba + p.Hv + head]);
-      z_next = __bfloat162float(p.z[r * p.ldz + head * kGdnDim + vi]);
-    }
+    const float qk = qk_next, bb = b_next, aa = a_next;
+    float v[4], zz[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[i] = v_next[i]; zz[i] = z_next[i]; }
+    if (t + 1 < n) load_row(static_cast<size_t>(row0 + t + 1));
     // L2 norms of q (warps 0-3) and k (warps 4-7)
     const float sq = warp_sum(qk * qk);
-    if ((tid & 31) == 0) red[0][tid >> 5] = sq;
+    if (lane == 0) red[0][tid >> 5] = sq;
     __syncthreads();
     {
       const int base = tid < 128 ? 0 : 4;
@@ -166,35 +176,66 @@ gdn_delta_kernel(const GdnDeltaParams p) {
     const float softplus = x > 20.f ? x : log1pf(__expf(x));
     const float decay = __expf(neg_exp_a * softplus);
 
-    float mem = 0.f;
+    float4 kv[4];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) {
-      S[j] *= decay;
-      mem = fmaf(S[j], ks[kh + j], mem);
-    }
-    mem += __shfl_xor_sync(0xffffffffu, mem, 1);
-    const float delta = (v - mem) * beta;
-    float o = 0.f;
+    for (int c = 0; c < 4; ++c) kv[c] = *reinterpret_cast<const float4*>(ks + 4 * (l8 + 8 * c));
+    float mem[4];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) {
-      S[j] = fmaf(delta, ks[kh + j], S[j]);
-      o = fmaf(S[j], qs[kh + j], o);
+    for (int i = 0; i < 4; ++i) {
+      float m = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float4& e = S[i][c];
+        e.x *= decay; e.y *= decay; e.z *= decay; e.w *= decay;
+        m = fmaf(e.x, kv[c].x, m); m = fmaf(e.y, kv[c].y, m); m = fmaf(e.z, kv[c].z, m); m = fmaf(e.w, kv[c].w, m);
+      }
+      m += __shfl_xor_sync(0xffffffffu, m, 1);
+      m += __shfl_xor_sync(0xffffffffu, m, 2);
+      m += __shfl_xor_sync(0xffffffffu, m, 4);
+      mem[i] = m;
     }
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    // gated RMSNorm over the head's 128 outputs (each value is held by two lanes: count it once)
-    const float ob = __bfloat162float(__float2bfloat16(o));      // the recurrence output is stored in bf16
-    const float ss = warp_sum((tid & 1) ? 0.f : ob * ob);
-    if ((tid & 31) == 0) red[1 + (t & 1)][tid >> 5] = ss;
+    float4 qv[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) qv[c] = *reinterpret_cast<const float4*>(qs + 4 * (l8 + 8 * c));
+    float ob[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float delta = (v[i] - mem[i]) * beta;
+      float o = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float4& e = S[i][c];
+        e.x = fmaf(delta, kv[c].x, e.x); e.y = fmaf(delta, kv[c].y, e.y);
+        e.z = fmaf(delta, kv[c].z, e.z); e.w = fmaf(delta, kv[c].w, e.w);
+        o = fmaf(e.x, qv[c].x, o); o = fmaf(e.y, qv[c].y, o); o = fmaf(e.z, qv[c].z, o); o = fmaf(e.w, qv[c].w, o);
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      ob[i] = __bfloat162float(__float2bfloat16(o));       // the recurrence output is stored in bf16
+      if (l8 == 0) ss = fmaf(ob[i], ob[i], ss);            // every row counted once
+    }
+    // gated RMSNorm over the head's 128 outputs
+    ss = warp_sum(ss);
+    if (lane == 0) red[1 + (t & 1)][tid >> 5] = ss;
     __syncthreads();
-    if ((tid & 1) == 0) {
+    if (l8 == 0) {
       const float* rr = red[1 + (t & 1)];
       const float tot = rr[0] + rr[1] + rr[2] + rr[3] + rr[4] + rr[5] + rr[6] + rr[7];
-      const float normed = __bfloat162float(__float2bfloat16(ob * rsqrtf(tot * (1.f / kGdnDim) + p.eps_norm)));
-      p.out[static_cast<size_t>(row0 + t) * p.ldo + head * kGdnDim + vi] = __float2bfloat16(normed * nw * silu_fast(zz));
+      const float inv = rsqrtf(tot * (1.f / kGdnDim) + p.eps_norm);
+      __nv_bfloat16* orow = p.out + static_cast<size_t>(row0 + t) * p.ldo + head * kGdnDim + vrow;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float normed = __bfloat162float(__float2bfloat16(ob[i] * inv));
+        orow[4 * i] = __float2bfloat16(normed * nw[i] * silu_fast(zz[i]));
+      }
     }
   }
 #pragma unroll
-  for (int j = 0; j < 64; j += 4) *reinterpret_cast<float4*>(sp + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) *reinterpret_cast<float4*>(sp + (4 * i) * kGdnDim + 32 * c) = S[i][c];
 }
 
 // out = x * sigmoid(gate): the output gate of the hybrid family's full-attention layers (bf16, in place allowed)

@@ -22,8 +22,28 @@ struct KvWriteParams {
   int T, Hq, Hkv;
   int rotary_dim;              // <= D, multiple of 2; pairs (c, c + rotary_dim/2)
   float eps;
+  int rotate;                  // normalised Walsh-Hadamard transform of every q / k / v head vector (after RoPE)
   KvLayout lay;
 };
+
+// Normalised Walsh-Hadamard transform of a 128-vector held as v[a] = x[lane + 32 a]: index bits 5-6 are the
+// register index, bits 0-4 the lane.  fp32 stages, the caller rounds once (reference:
+// ops/cuda/cache_rotation_native.cu:12).  The transform is its own inverse, and q . k is unchanged when both are
+// transformed, so attention over a rotated cache needs only the transform of its output (V's rotation undone).
+__device__ __forceinline__ void hadamard128(float (&v)[4], int lane) {
+  float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+  v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[k], m);
+      v[k] = (lane & m) ? o - v[k] : v[k] + o;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] *= 0.08838834764831845f;     // 1 / sqrt(128)
+}
 
 __device__ __forceinline__ void quantize_store(const float (&v)[4], int bits, bool is_v, uint8_t* blob,
                                                const KvLayout& lay, int tok, int lane) {
@@ -129,6 +149,7 @@ rope_kv_write_kernel(const KvWriteParams p) {
         v[1] = b * cs[0] + a * sn[0];
       }
     }
+    if (p.rotate) hadamard128(v, lane);
     if (is_q) {
       __nv_bfloat16* dst = p.q_out + (static_cast<size_t>(t) * p.Hq + h) * D;
 #pragma unroll
@@ -144,6 +165,25 @@ rope_kv_write_kernel(const KvWriteParams p) {
     for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(__float2bfloat16(v[k]));
     quantize_store(v, is_k ? p.lay.k_bits : p.lay.v_bits, !is_k, blob, p.lay, tok, lane);
   }
+}
+
+// Walsh-Hadamard transform of `vectors` consecutive 128-vectors per row (in place allowed): undoes the rotation of
+// V on the attention output.  One warp per vector.
+__global__ void __launch_bounds__(256)
+hadamard_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_bfloat16* __restrict__ y, int ldy, int vectors,
+                int rows) {
+  const int lane = threadIdx.x & 31;
+  const long long w = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (w >= static_cast<long long>(rows) * vectors) return;
+  const int r = static_cast<int>(w / vectors), h = static_cast<int>(w - static_cast<long long>(r) * vectors);
+  const __nv_bfloat16* src = x + static_cast<size_t>(r) * ldx + h * 128;
+  __nv_bfloat16* dst = y + static_cast<size_t>(r) * ldy + h * 128;
+  float v[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(src[lane + 32 * k]);
+  hadamard128(v, lane);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) dst[lane + 32 * k] = __float2bfloat16(v[k]);
 }
 
 // Copy whole pages (all kv heads) src -> dst: copy-on-write of a shared page.
@@ -166,7 +206,7 @@ int cb_kv_blob_bytes(int head_dim, int k_bits, int v_bits) {
 
 int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* positions, const void* slots,
                      const void* q_norm, const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D,
-                     int rotary_dim, float eps, int k_bits, int v_bits, void* stream) {
+                     int rotary_dim, float eps, int k_bits, int v_bits, int rotate, void* stream) {
   using namespace cb;
   if (T <= 0) return 0;
   if (D != 128) return -10;
@@ -181,9 +221,18 @@ int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* posi
   p.q_norm = static_cast<const __nv_bfloat16*>(q_norm);
   p.k_norm = static_cast<const __nv_bfloat16*>(k_norm);
   p.inv_freq = static_cast<const float*>(inv_freq);
-  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.rotary_dim = rotary_dim; p.eps = eps;
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.rotary_dim = rotary_dim; p.eps = eps; p.rotate = rotate;
   p.lay = make_kv_layout(D, k_bits, v_bits);
   rope_kv_write_kernel<<<static_cast<unsigned>(T), kRopeWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// y[r, 128 h .. 128 h + 127] = normalised Walsh-Hadamard transform of x[r, same], h < vectors (bf16, in place allowed).
+int cb_hadamard(const void* x, int ldx, void* y, int ldy, int vectors, int rows, void* stream) {
+  if (rows <= 0 || vectors <= 0) return 0;
+  const long long warps = static_cast<long long>(rows) * vectors;
+  cb::hadamard_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy, vectors, rows);
   return static_cast<int>(cudaGetLastError());
 }
 

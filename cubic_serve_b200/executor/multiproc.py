@@ -38,6 +38,7 @@ class WorkerSpec:
     seed: int = 0
     gpu_reserve_gib: float = 4.0
     pp: int = 1                  # pipeline stages; rank = stage * tp + tensor rank
+    kv_rotation: bool = False    # Walsh-Hadamard rotation of q / k / v before the cache write
 
     @property
     def world(self) -> int:
@@ -122,7 +123,8 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
                 pages = int(t.item())
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=spec.token_budget, k_bits=spec.k_bits,
-                               v_bits=spec.v_bits, tp=tp, pp=pp)
+                               v_bits=spec.v_bits, tp=tp, pp=pp, max_requests=spec.max_rows,
+                               kv_rotation=spec.kv_rotation)
         ex = GpuExecutor(runner, max_rows=spec.max_rows, max_prefill_tokens=spec.token_budget,
                          max_model_len=spec.max_model_len)
         caps = ex.capture_decode_graphs()
@@ -262,7 +264,8 @@ def build_multiproc_backend(args, devices, tp, spec_cfg, k_bits, v_bits):
     from ..runtime.serving import _tokenizer_for
     max_len = args.max_model_len or 8192
     spec = WorkerSpec(args.model, devices, tp, k_bits, v_bits, args.max_running_requests, args.token_budget, max_len,
-                      None, args.tp_comm, args.seed, args.gpu_reserve_gib, args.pp_size)
+                      None, args.tp_comm, args.seed, args.gpu_reserve_gib, args.pp_size,
+                      bool(getattr(args, "enable_kv_cache_rotation", False)))
     ex = MultiprocExecutor(spec)
     sched = SchedulerConfig(max_running_requests=args.max_running_requests, max_batched_tokens=args.token_budget,
                             prefill_chunk_tokens=min(args.prefill_chunk_tokens, args.token_budget), max_model_len=max_len,

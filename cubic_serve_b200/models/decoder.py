@@ -196,8 +196,11 @@ class StepBatch:
 
 class DecoderRunner:
     def __init__(self, cfg: ModelConfig, weights: DecoderWeights, num_pages: int, max_tokens: int,
-                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None, pp=None, max_requests: int = 256) -> None:
-        """``max_requests``: rows of the per-request recurrent state of Gated DeltaNet layers (= page-table rows)."""
+                 k_bits: int = 8, v_bits: int = 8, tp=None, device=None, pp=None, max_requests: int = 256,
+                 kv_rotation: bool = False) -> None:
+        """``max_requests``: rows of the per-request recurrent state of Gated DeltaNet layers (= page-table rows).
+        ``kv_rotation``: q / k / v head vectors are Walsh-Hadamard transformed before the cache write (smoother
+        channels for INT4 / INT6 codes); the attention output is transformed back."""
         self.cfg = cfg
         self.w = weights            # ``weights.layers`` holds only the layers of this pipeline stage
         self.device = device or weights.embed.device
@@ -207,6 +210,7 @@ class DecoderRunner:
             raise ValueError("pipeline stages use the NCCL tensor-parallel collectives (tp mode 'nccl')")
         self.tp_size = tp.size if tp is not None else 1
         self.k_bits, self.v_bits = k_bits, v_bits
+        self.kv_rotation = kv_rotation
         self.hq = cfg.num_q_heads // self.tp_size
         self.hkv = cfg.num_kv_heads // self.tp_size
         self.D = cfg.head_dim
@@ -333,11 +337,14 @@ class DecoderRunner:
                 K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
                 K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
                                 self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
-                                rotary_dim=cfg.rotary_dim)
+                                rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation)
                 K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
                                   b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
                                   splits=b.attn_splits, ws=self.ws)
                 n += 4
+                if self.kv_rotation:
+                    K.hadamard(attn)
+                    n += 1
                 if lw.attn_gate is not None:
                     gate = self.gate[t0:t1]
                     K.wq_gemm(x, lw.attn_gate, out=gate, ws=self.ws)
@@ -410,10 +417,13 @@ class DecoderRunner:
             f.gemm_gather(lw.qkv, qkv, s)
             K.rope_kv_write(qkv, q, self.kv[li], b.positions, b.slots, self.inv_freq, self.hq, self.hkv, self.D,
                             self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
-                            rotary_dim=cfg.rotary_dim)
+                            rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation)
             K.paged_attention(q.view(T, self.hq, self.D), attn.view(T, self.hq, self.D), self.kv[li], b.page_table,
                               b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, self.hq, self.hkv,
                               self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)
+            if self.kv_rotation:
+                K.hadamard(attn)
+                n += 1
             s ^= 1
             f.gemm_scatter(attn, lw.o, s)
             nxt = w.layers[li + 1].ln1 if li + 1 < len(w.layers) else w.final_norm

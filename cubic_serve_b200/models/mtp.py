@@ -87,10 +87,13 @@ class MtpRunner:
         K.rmsnorm(h, lw.ln1, cfg.rms_eps, out=x)
         K.wq_gemm(x, lw.qkv, out=qkv, ws=t.ws)
         K.rope_kv_write(qkv, q, self.kv, b.positions, b.slots, t.inv_freq, t.hq, t.hkv, t.D, t.k_bits, t.v_bits,
-                        q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps, rotary_dim=cfg.rotary_dim)
+                        q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps, rotary_dim=cfg.rotary_dim,
+                        rotate=t.kv_rotation)
         K.paged_attention(q.view(T, t.hq, t.D), attn.view(T, t.hq, t.D), self.kv, b.page_table,
                           b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, t.hq, t.hkv, t.D, t.k_bits,
                           t.v_bits, splits=b.attn_splits, ws=t.ws)
+        if t.kv_rotation:
+            K.hadamard(attn)
         K.wq_gemm(attn, lw.o, out=h, residual=h, ws=t.ws)
         K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x)
         gu, act = t.gu[:T], t.act[:T]

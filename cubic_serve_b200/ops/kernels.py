@@ -249,13 +249,27 @@ def kv_blob_bytes(head_dim: int, k_bits: int, v_bits: int) -> int:
 def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                   slots: torch.Tensor, inv_freq: torch.Tensor, hq: int, hkv: int, head_dim: int,
                   k_bits: int, v_bits: int, q_norm: torch.Tensor | None = None,
-                  k_norm: torch.Tensor | None = None, eps: float = 1e-6, rotary_dim: int | None = None) -> None:
+                  k_norm: torch.Tensor | None = None, eps: float = 1e-6, rotary_dim: int | None = None,
+                  rotate: bool = False) -> None:
+    """``rotate``: every q / k / v head vector is Walsh-Hadamard transformed (after RoPE) before it is written, which
+    spreads outlier channels over the 32-channel quantization groups; ``q . k`` is unchanged and the attention
+    output is transformed back with ``hadamard`` (reference: ``ops/cuda/cache_rotation_native.cu:12``)."""
     t = qkv.shape[0]
     code = native.lib().cb_rope_kv_write(qkv.data_ptr(), q_out.data_ptr(), cache.data_ptr(), positions.data_ptr(),
                                          slots.data_ptr(), _ptr(q_norm), _ptr(k_norm), inv_freq.data_ptr(), t, hq,
                                          hkv, head_dim, head_dim if rotary_dim is None else rotary_dim, float(eps),
-                                         k_bits, v_bits, _stream())
+                                         k_bits, v_bits, int(rotate), _stream())
     native.check(code, "cb_rope_kv_write")
+
+
+def hadamard(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Normalised Walsh-Hadamard transform of every consecutive 128-vector of the rows of ``x`` (bf16; its own inverse)."""
+    rows, cols = x.shape
+    assert cols % 128 == 0 and x.stride(1) == 1 and x.dtype == torch.bfloat16
+    out = x if out is None else out
+    native.check(native.lib().cb_hadamard(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), cols // 128, rows,
+                                          _stream()), "cb_hadamard")
+    return out
 
 
 def copy_pages(cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:

@@ -112,7 +112,9 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_embedding.restype = i
     l.cb_kv_blob_bytes.argtypes = [i, i, i]
     l.cb_kv_blob_bytes.restype = i
-    l.cb_rope_kv_write.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, f, i, i, vp]
+    l.cb_rope_kv_write.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, f, i, i, i, vp]
+    l.cb_hadamard.argtypes = [vp, i, vp, i, i, i, vp]
+    l.cb_hadamard.restype = i
     l.cb_rope_kv_write.restype = i
     l.cb_copy_pages.argtypes = [vp, vp, vp, i, ll, vp]
     l.cb_copy_pages.restype = i

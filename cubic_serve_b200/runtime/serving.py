@@ -88,7 +88,8 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         pages = plan_kv_pages(free, int(args.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, 1, k_bits, v_bits, max_len,
                               args.max_running_requests)
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits,
-                               max_requests=args.max_running_requests)
+                               max_requests=args.max_running_requests,
+                               kv_rotation=bool(getattr(args, "enable_kv_cache_rotation", False)))
         depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None else 0
         if depth:
             # MTP speculative decoding (--speculative-config): draft head + review rounds instead of graph decode

@@ -138,6 +138,30 @@ def bench_attn(rows: int, ctx: int, hq: int, hkv: int, kb: int, vb: int, splits:
             "us": round(ms * 1e3, 1), "kv_gbs": round(kv_bytes / ms / 1e6, 1)}
 
 
+def bench_gdn(requests: int, tokens: int, hk: int, hv: int) -> dict:
+    """Gated DeltaNet kernels of one layer: ``requests`` segments of ``tokens`` rows each (1 = a decode step)."""
+    d, T = 128, requests * tokens
+    C = (2 * hk + hv) * d
+    i32 = dict(dtype=torch.int32, device=DEV)
+    seg = K.GdnSegments(torch.arange(requests, **i32) * tokens, torch.full((requests,), tokens, **i32),
+                        torch.arange(requests, **i32), torch.full((requests,), 5, **i32), requests)
+    proj = torch.randn(T, C + hv * d + 2 * hv, device=DEV).to(torch.bfloat16)
+    w = torch.randn(C, 4, device=DEV) * 0.3
+    conv_state = torch.zeros(requests, 3, C, dtype=torch.bfloat16, device=DEV)
+    state = torch.randn(requests, hv, d, d, device=DEV) * 0.01
+    mix = torch.empty(T, C, dtype=torch.bfloat16, device=DEV)
+    out = torch.empty(T, hv * d, dtype=torch.bfloat16, device=DEV)
+    a_log, dt_bias, norm_w = torch.zeros(hv, device=DEV), torch.zeros(hv, device=DEV), torch.ones(d, device=DEV)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    conv_ms = timeit_graph(lambda: K.gdn_conv(proj, w, conv_state, seg, mix), flush, launches=5)
+    delta_ms = timeit_graph(lambda: K.gdn_delta(mix, proj[:, C:C + hv * d], proj[:, C + hv * d:], a_log, dt_bias, norm_w,
+                                                state, seg, out, hk, hv), flush, launches=5)
+    state_bytes = 2 * state.numel() * 4                       # read + written once per step
+    return {"op": "gdn", "requests": requests, "tokens_per_request": tokens, "hk": hk, "hv": hv,
+            "conv_us": round(conv_ms * 1e3, 1), "delta_us": round(delta_ms * 1e3, 1),
+            "delta_state_gbs": round(state_bytes / delta_ms / 1e6, 1), "timing": "in-graph, L2 flushed"}
+
+
 def bench_fused_tp(ranks: int, m: int, hidden: int, inter: int, iters: int) -> dict:
     """One o_proj -> norm -> gate/up boundary of the fused tensor-parallel path with all ranks on THIS device.
 
@@ -183,7 +207,8 @@ def bench_fused_tp(ranks: int, m: int, hidden: int, inter: int, iters: int) -> d
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn", "sweep", "fused-tp"])
+    ap.add_argument("op", choices=["gemm", "attn", "sweep", "fused-tp", "gdn"],
+                    help="gdn: --rows requests x --ctx tokens per request (1 = decode) through one Gated DeltaNet layer")
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--inter", type=int, default=12288)
@@ -206,7 +231,9 @@ def main() -> None:
     a = ap.parse_args()
     from ..ops import native
     native.lib().cb_wq_gemm_pair_mode(a.pairs)
-    if a.op == "gemm":
+    if a.op == "gdn":
+        print(json.dumps(bench_gdn(a.rows, a.ctx, 16, 32)))
+    elif a.op == "gemm":
         print(json.dumps(bench_gemm(a.m, a.n, a.k, a.splits or None, a.iters, a.fmt, a.kernel, a.act)))
     elif a.op == "fused-tp":
         print(json.dumps(bench_fused_tp(a.ranks, a.m, a.hidden, a.inter, a.iters)))

@@ -413,3 +413,49 @@ def test_sampler():
                  counters=ctr[:1] + c)
         seen.add(int(a[0]))
     assert len(seen) >= 2
+
+
+def test_hadamard_rotation_kernel_and_rotated_cache():
+    """Walsh-Hadamard rotation: the stand-alone kernel against the matrix, its own inverse, and the fused
+    q / k / v rotation of the cache write: attention over a rotated INT4 cache, rotated back, matches attention over
+    the plain cache within the quantization error, and is the better of the two on outlier channels."""
+    K = _k()
+    g = torch.Generator().manual_seed(0)
+    H = torch.ones(1, 1)
+    for _ in range(7):
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    H = H / 128 ** 0.5
+    x = torch.randn(5, 3 * 128, generator=g).to(torch.bfloat16)
+    y = K.hadamard(x.to(DEV).clone())
+    want = (x.float().view(5, 3, 128) @ H).view(5, 384)
+    assert _rel(y.cpu(), want) < 5e-3
+    assert _rel(K.hadamard(y.clone()).cpu(), x) < 1e-2
+
+    hq, hkv, d, T = 8, 2, 128, 40
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, generator=g)
+    qkv[:, hq * d + 5] *= 30.0                          # an outlier channel in K head 0 ...
+    qkv[:, (hq + hkv) * d + 77] *= 30.0                 # ... and one in V head 0
+    qkv = qkv.to(torch.bfloat16).to(DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = (torch.arange(T, dtype=torch.int32, device=DEV) + 16)          # pages 1..3
+    inv_freq = eager.rope_inv_freq(d, 1e6, DEV)
+    table = torch.tensor([[1, 2, 3]], dtype=torch.int32, device=DEV)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    outs = {}
+    for bits in (8, 4):
+        for rot in (False, True):
+            cache = torch.zeros(8, hkv, K.kv_blob_bytes(d, bits, bits), dtype=torch.uint8, device=DEV)
+            q = torch.empty(T, hq * d, dtype=torch.bfloat16, device=DEV)
+            K.rope_kv_write(qkv, q, cache, pos, slots, inv_freq, hq, hkv, d, bits, bits, rotate=rot)
+            out = torch.zeros(T, hq, d, dtype=torch.bfloat16, device=DEV)
+            # one row block: the last 4 query rows of the request attend to the whole context
+            K.paged_attention(q.view(T, hq, d), out, cache, table, torch.zeros(1, **i32), torch.tensor([T - 4], **i32),
+                              torch.tensor([4], **i32), torch.tensor([T - 3], **i32), hq, hkv, d, bits, bits)
+            o = out[T - 4:].reshape(4, hq * d).clone()
+            outs[bits, rot] = K.hadamard(o) if rot else o
+    torch.cuda.synchronize()
+    K.workspace(torch.device(DEV)).check_status()
+    ref = outs[8, False].float()
+    assert _rel(outs[8, True], ref) < 3e-2
+    err_plain, err_rot = _rel(outs[4, False], ref), _rel(outs[4, True], ref)
+    assert err_rot < err_plain and err_rot < 0.2, (err_plain, err_rot)
