@@ -232,7 +232,8 @@ class GpuExecutor:
         v_local = runner.w.lm_head.n
         self.logits = torch.empty(max_rows, v_local, dtype=torch.bfloat16, device=self.device)
         self.out_ids = torch.zeros(max_rows * rows_per_request, dtype=torch.int32, device=self.device)
-        self.out_host = torch.zeros(max_rows * rows_per_request, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        # two result buffers: a step may be launched before the previous step's ids have been read (``launch`` / ``collect``)
+        self.out_host = torch.zeros(2, max_rows * rows_per_request, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.use_graphs = use_graphs
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.stream = torch.cuda.Stream(device=self.device)
@@ -242,7 +243,11 @@ class GpuExecutor:
         self.graph_launches = {}
         self.timing = False              # record device time of the compute part of every step
         self.device_ms: list[float] = []
-        self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        self._ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2)]
+        self._done = [torch.cuda.Event(), torch.cuda.Event()]
+        self._uploaded = torch.cuda.Event()
+        self._upload_pending = False
+        self._launches = 0
 
     # ----------------------------------------------------------------- batches
     # ------------------------------------------------------------------- run
@@ -312,29 +317,57 @@ class GpuExecutor:
 
     def execute(self, segs: list[Segment]) -> np.ndarray:
         """Run one step and return the sampled token id of every sampling segment (host array)."""
+        return self.collect(self.launch(segs))
+
+    def launch(self, segs: list[Segment], feedback_rows: int = 0) -> dict:
+        """Enqueue one step without waiting for it: stage + upload the inputs, replay the graph (or run eagerly),
+        enqueue the device -> host copy of the sampled ids.  ``collect`` waits and returns them.
+
+        ``feedback_rows`` > 0: the input token of row ``i < feedback_rows`` is the id the PREVIOUS launch sampled for
+        its row ``i`` (copied on the device, the host does not know it yet): the engine uses it to launch a decode
+        step while it still processes the previous step's results.  At most two launches may be outstanding.
+        """
         total = sum(len(s.token_ids) for s in segs)
         masked = self._stage_masks(segs)
         decode = all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs) and not masked
         cap = None
         if decode:
             cap = next((c for c in sorted(self.graphs) if c >= total), None)
+        if self._upload_pending:
+            # the pinned staging buffer is rewritten below: the previous launch's upload must have left it
+            self._uploaded.synchronize()
+            self._upload_pending = False
         b, rows = self._fill(segs, pad_rows_to=cap)
+        k = self._launches & 1
+        self._launches += 1
         with torch.cuda.stream(self.stream):
-            self.h2d_bytes_last = self.stage.upload()
+            h2d = self.stage.upload()
+            self._uploaded.record(self.stream)
+            self._upload_pending = True
+            if feedback_rows:
+                self.stage.d["token_ids"][:feedback_rows].copy_(self.out_ids[:feedback_rows], non_blocking=True)
             if self.timing:
-                self._ev[0].record(self.stream)
+                self._ev[k][0].record(self.stream)
             if cap is not None:
                 self.graphs[cap].replay()
-                self.kernel_launches_last = self.graph_launches[cap]
+                launches = self.graph_launches[cap]
             else:
                 self._body(b)
-                self.kernel_launches_last = self.runner.launches_per_step
+                launches = self.runner.launches_per_step
             if self.timing:
-                self._ev[1].record(self.stream)
+                self._ev[k][1].record(self.stream)
             if rows:
-                self.out_host[:rows].copy_(self.out_ids[:rows], non_blocking=True)
-            self.stream.synchronize()
+                self.out_host[k, :rows].copy_(self.out_ids[:rows], non_blocking=True)
+            self._done[k].record(self.stream)
+        return {"k": k, "rows": rows, "h2d": h2d, "launches": launches}
+
+    def collect(self, handle: dict) -> np.ndarray:
+        """Wait for a launched step and return its sampled ids (host array)."""
+        k, rows = handle["k"], handle["rows"]
+        self._done[k].synchronize()
+        self.h2d_bytes_last = handle["h2d"]
+        self.kernel_launches_last = handle["launches"]
         self.d2h_bytes_last = rows * 4
         if self.timing:
-            self.device_ms.append(self._ev[0].elapsed_time(self._ev[1]))
-        return self.out_host[:rows].numpy().copy()
+            self.device_ms.append(self._ev[k][0].elapsed_time(self._ev[k][1]))
+        return self.out_host[k, :rows].numpy().copy()

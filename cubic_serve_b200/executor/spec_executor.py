@@ -81,11 +81,11 @@ class SpeculativeGpuExecutor(GpuExecutor):
             self.mtp.forward(b, prev)
             self.last_hidden.index_copy_(0, sl, hidden.index_select(0, la))
             if rows:
-                self.out_host[:rows].copy_(self.out_ids[:rows], non_blocking=True)
+                self.out_host[0, :rows].copy_(self.out_ids[:rows], non_blocking=True)
             self.stream.synchronize()
         self.kernel_launches_last = r.launches_per_step + self.mtp.launches + 3
         self.d2h_bytes_last = rows * 4
-        return self.out_host[:rows].numpy().copy()
+        return self.out_host[0, :rows].numpy().copy()
 
     # ------------------------------------------------------- speculative round
     def execute_speculative(self, segs: list[Segment], depths: list[int] | None = None):
@@ -111,7 +111,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
         target_ids = self.target_ids.view(-1)[:R * (Kd + 1)].view(R, Kd + 1)
         self.depth_t[:R].copy_(torch.tensor(per_req, dtype=torch.int32), non_blocking=True)
         with torch.cuda.stream(self.stream):
-            ev0, ev1 = self._ev
+            ev0, ev1 = self._ev[0]
             if not hasattr(self, "_ev_mid"):
                 self._ev_mid = torch.cuda.Event(enable_timing=True)
             if self.timing:

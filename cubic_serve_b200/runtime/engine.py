@@ -52,6 +52,10 @@ class LLMEngine:
         # dynamic draft length (reference: runtime/speculative.py DynamicDraftPlanner.plan): per-request acceptance
         # history + measured round costs choose each request's draft length; off = the executor's fixed depth
         self.draft_planner = None
+        # launch the next decode step before this one's results are read (steady decode state only)
+        self.overlap_decode = True
+        self._ahead = None
+        self._ahead_stale = False
         self._draft_states: dict = {}
         vocab = getattr(getattr(executor, "cfg", None), "vocab_size", None) or getattr(executor, "vocab_size", 0)
         self._mask_words = -(-int(vocab) // 32) if vocab else 0
@@ -88,14 +92,36 @@ class LLMEngine:
         return self.scheduler.has_work
 
     def step(self) -> list[StepOutput]:
+        """One engine step.  In the steady decode state the NEXT step is launched before this step's results are
+        read (``overlap_decode``): the device then never waits for the host's scheduling and output handling.
+        The look-ahead step takes its input tokens from the device and is planned by
+        ``ContinuousScheduler.lookahead_plan``; whenever its conditions fail the step runs the regular way."""
         if self.poisoned:
             raise EnginePoisoned("engine is poisoned")
         t0 = time.perf_counter()
-        plan = self.scheduler.next_plan()
-        if plan is None:
-            return []
         try:
-            outputs = self._run(plan)
+            ahead, self._ahead = self._ahead, None
+            if ahead is not None:
+                plan, handle = ahead
+            else:
+                plan = self.scheduler.next_plan()
+                if plan is None:
+                    return []
+                handle = None
+            if handle is None and not self._can_overlap(plan):
+                outputs = self._run(plan)
+            else:
+                if handle is None:
+                    handle = self.executor.launch(self._segments(plan))
+                nxt = self.scheduler.lookahead_plan(plan) if self._can_overlap(plan) else None
+                if nxt is not None:
+                    rows = len(nxt.segments)
+                    self._ahead = (nxt, self.executor.launch(self._segments(nxt, ahead=True), feedback_rows=rows))
+                outputs = self._complete(plan, self.executor.collect(handle))
+                if self._ahead is not None and len(self.scheduler.running) != len(self._ahead[0].segments):
+                    # a request ended in this step: its look-ahead row is dropped at commit, and no further step is
+                    # launched from the shortened one until a regular plan has been made
+                    self._ahead_stale = True
         except Exception:
             self.poisoned = True
             self.pool.poison()
@@ -104,23 +130,38 @@ class LLMEngine:
         self.steps += 1
         return outputs
 
-    def _run(self, plan: BatchPlan) -> list[StepOutput]:
-        if plan.copies:
-            self.executor.copy_pages(plan.copies)
-            if hasattr(self.executor, "invalidate_page_rows"):
-                self.executor.invalidate_page_rows([s.request.slot for s in plan.segments])
+    def _can_overlap(self, plan: BatchPlan) -> bool:
+        if not self.overlap_decode or not hasattr(self.executor, "launch") or getattr(self.executor, "speculative_depth", 0):
+            return False
+        if getattr(self, "_ahead_stale", False):
+            self._ahead_stale = False
+            return False
+        return bool(plan.segments) and not plan.copies and all(
+            s.count == 1 and s.sample and s.request.sampling.matcher is None for s in plan.segments)
+
+    def _segments(self, plan: BatchPlan, ahead: bool = False) -> list:
+        """Executor segments of a plan.  ``ahead``: the plan is a look-ahead step whose input tokens are not known on
+        the host yet (the previous step's commit will append them); draws count that commit in."""
         segs = []
         for s in plan.segments:
             r = s.request
-            toks = r.tokens[s.start:s.start + s.count]
+            toks = [0] if ahead else r.tokens[s.start:s.start + s.count]
             sp = r.sampling
             mask = None
             if s.sample and sp.matcher is not None:
                 mask = np.zeros(self._mask_words, dtype=np.uint32)
                 sp.matcher.fill_bitmask(mask)
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
-                                sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF, r.draws,
-                                r.arrival, mask))
+                                sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF,
+                                r.draws + (1 if ahead else 0), r.arrival, mask))
+        return segs
+
+    def _run(self, plan: BatchPlan) -> list[StepOutput]:
+        if plan.copies:
+            self.executor.copy_pages(plan.copies)
+            if hasattr(self.executor, "invalidate_page_rows"):
+                self.executor.invalidate_page_rows([s.request.slot for s in plan.segments])
+        segs = self._segments(plan)
         spec = getattr(self.executor, "speculative_depth", 0)
         constrained = any(s.mask is not None for s in segs)
         if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample for s in segs):
@@ -129,11 +170,18 @@ class LLMEngine:
             self.spec_rounds = getattr(self, "spec_rounds", 0) + 1
         else:
             ids = self.executor.execute(segs) if segs else []
+        return self._complete(plan, ids)
+
+    def _complete(self, plan: BatchPlan, ids) -> list[StepOutput]:
+        """Second half of a step: match ids to requests, commit, build the outputs.  Rows of a look-ahead step whose
+        request ended in the step before are skipped."""
         sampled = {}
         it = iter(ids)
         for s in plan.segments:
             if s.sample:
                 v = next(it)
+                if s.request.status is not RequestStatus.RUNNING:
+                    continue
                 sampled[s.request.request_id] = [int(t) for t in v] if isinstance(v, (list, tuple)) else int(v)
                 m = s.request.sampling.matcher
                 if m is not None and not isinstance(v, (list, tuple)) and not m.accept(int(v)):
@@ -143,7 +191,7 @@ class LLMEngine:
         finished = {r.request_id: r for r in self.scheduler.commit(plan, sampled, self.eos_token_id)}
         outs = []
         for s in plan.segments:
-            if not s.sample:
+            if not s.sample or s.request.request_id not in sampled:
                 continue
             rid = s.request.request_id
             toks = sampled[rid] if isinstance(sampled[rid], list) else [sampled[rid]]

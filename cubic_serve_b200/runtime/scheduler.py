@@ -289,6 +289,36 @@ class ContinuousScheduler:
         scheduled.add(r.request_id)
         return True
 
+    def lookahead_plan(self, prev: BatchPlan) -> BatchPlan | None:
+        """The decode step that follows ``prev`` if ``prev`` finishes nobody, planned BEFORE ``prev`` is committed.
+
+        Only for the steady state: ``prev`` is one sampled decode row for every running request, nothing waits, no
+        request can reach its length limit in ``prev``, none is constrained by a matcher, and the pages of the next
+        position can be had without evicting or preempting anybody.  The rows keep ``prev``'s order, so row ``i`` of
+        the new step continues row ``i`` of ``prev`` (its input token is still on the device).  A request that
+        ``prev`` ends after all (stop token) simply leaves its row's result unused: ``commit`` skips rows whose
+        request is no longer running.  Returns None whenever a condition fails; nothing is rolled back then (pages
+        reserved so far are the ones the next regular plan would reserve).
+        """
+        if self.waiting or len(prev.segments) != len(self.running) or prev.copies or prev.preempted:
+            return None
+        segs = []
+        for s in prev.segments:
+            r = s.request
+            sp = r.sampling
+            if s.count != 1 or not s.sample or r.status is not RequestStatus.RUNNING or sp.matcher is not None:
+                return None
+            if len(r.output) + 2 > sp.max_tokens or r.num_tokens + 2 > self.cfg.max_model_len:
+                return None                       # ``prev`` may end it by length: plan the next step the regular way
+            start = s.start + 1
+            need = -(-(start + 1) // BLOCK) - len(r.pages)
+            if need > 0:
+                if need > self.pool.num_free:
+                    return None
+                r.pages.extend(self.pool.alloc(need))
+            segs.append(PlannedSegment(r, start, 1, True))
+        return BatchPlan(segs)
+
     # ----------------------------------------------------------------- commit
     def commit(self, plan: BatchPlan, sampled: dict[str, int], eos_token_id: int | None = None) -> list[Request]:
         """Apply a finished step: advance computed counts, append sampled tokens, retire finished requests."""

@@ -171,3 +171,76 @@ def test_choice_constraint_masks_sampling_end_to_end():
         assert len(reqs[other].output) == 5
         outs.append(text)
     assert eng._mask_words == cfg.vocab_size // 32
+
+
+class _FeedbackExecutor:
+    """Executor double with the launch / collect interface: the sampled id is a function of the row's input token
+    and position, and a look-ahead launch reads its input tokens from the previous launch's ids ("device" memory)."""
+
+    def __init__(self, vocab=97, eos=None):
+        self.vocab, self.eos = vocab, eos
+        self.dev_ids = np.zeros(0, dtype=np.int64)
+        self.launches = self.feedback_launches = 0
+        self.outstanding = 0
+
+    def launch(self, segs, feedback_rows=0):
+        assert self.outstanding < 2
+        self.outstanding += 1
+        self.launches += 1
+        self.feedback_launches += bool(feedback_rows)
+        out = []
+        for i, s in enumerate(segs):
+            tok = int(self.dev_ids[i]) if i < feedback_rows else int(s.token_ids[-1])
+            if s.sample:
+                out.append((tok * 7 + (s.start + len(s.token_ids) - 1) * 3 + 1) % self.vocab)
+        self.dev_ids = np.asarray(out, dtype=np.int64)
+        return {"ids": self.dev_ids.copy()}
+
+    def collect(self, handle):
+        self.outstanding -= 1
+        return handle["ids"]
+
+    def execute(self, segs):
+        return self.collect(self.launch(segs))
+
+    def copy_pages(self, pairs):
+        pass
+
+
+def _run_engine(overlap, eos, arrivals):
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    ex = _FeedbackExecutor(eos=eos)
+    eng = LLMEngine(ex, num_pages=256, scheduler_config=SchedulerConfig(max_running_requests=8, max_batched_tokens=64,
+                                                                         prefill_chunk_tokens=64, max_model_len=128,
+                                                                         enable_prefix_cache=False), eos_token_id=eos)
+    eng.overlap_decode = overlap
+    rng = np.random.default_rng(3)
+    reqs, step = {}, 0
+    pending = sorted(arrivals)
+    while pending or eng.has_unfinished or eng._ahead is not None:
+        while pending and pending[0][0] <= step:
+            _, n_prompt, max_tokens = pending.pop(0)
+            rid = eng.add_request(rng.integers(1, 90, n_prompt).tolist(), SamplingParams(max_tokens=max_tokens))
+            reqs[rid] = eng.requests[rid]
+        eng.step()
+        step += 1
+        assert step < 500
+    assert eng.pool.num_used == 0
+    return [r.output for r in reqs.values()], ex
+
+
+def test_overlapped_decode_steps_give_the_same_tokens():
+    """Look-ahead launches (next decode step enqueued before this step's ids are read, input tokens fed back on the
+    "device") must not change any request's tokens: stop tokens ending a request while its look-ahead row is in
+    flight, length limits, and requests arriving in the middle of a decode phase."""
+    arrivals = [(0, 5, 30), (0, 9, 17), (0, 3, 40), (12, 7, 25), (13, 4, 6), (40, 11, 33)]
+    base, _ = _run_engine(False, None, arrivals)
+    # stop tokens that do occur in the middle of some request's output
+    for eos in (None, base[2][10], base[0][4], base[5][20]):
+        plain, ex0 = _run_engine(False, eos, arrivals)
+        fast, ex1 = _run_engine(True, eos, arrivals)
+        assert fast == plain
+        assert ex0.feedback_launches == 0 and ex1.feedback_launches > 10
+        if eos is not None:
+            assert any(o and o[-1] == eos and len(o) < m for o, (_, _, m) in zip(plain, arrivals))   # a request was stopped
