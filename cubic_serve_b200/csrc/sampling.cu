@@ -227,6 +227,41 @@ __global__ void verify_greedy_kernel(const int* target_ids, const int* draft_ids
   bonus[r] = target_ids[r * (max_depth + 1) + a];
 }
 
+// Thinking-token budgets, enforced on the device so that decode graphs (and steps launched ahead of the host) need no
+// host decision: an integer state machine per request slot, run on every sampled id right after the sampler.
+//   left[slot]  >= 0: the request is in its reasoning phase and may still emit that many thinking tokens; < 0: inactive
+//   fpos[slot]  > 0 : the forced end sequence is being emitted, next index
+// A row's `init` value re-arms its slot first: -2 = keep, -1 = no budget, >= 0 = reasoning starts (or resumes after a
+// re-prefill) with that many tokens left.  When the budget is used up the sampled id is replaced by the tokens of the
+// end sequence, one per step; sampling the closing token on its own ends the phase.
+// Reference: ops/cuda/sampling/reasoning_budget.cu:94 (sampling rows; its review / proposal prefixes belong to the
+// speculative path, which does not enforce budgets here).
+__global__ void __launch_bounds__(128)
+reasoning_budget_kernel(int* __restrict__ ids, const int* __restrict__ row_slot, const int* __restrict__ init,
+                        int* __restrict__ left, int* __restrict__ fpos, int rows, int end_id, int4 seq, int seq_len) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const int slot = row_slot[row];
+  if (slot < 0) return;
+  const int in = init[row];
+  int L = left[slot], f = fpos[slot];
+  if (in >= -1) { L = in; f = 0; }
+  if (L >= 0) {
+    int tok = ids[row];
+    if (f > 0 || L == 0) {
+      tok = f == 0 ? seq.x : (f == 1 ? seq.y : (f == 2 ? seq.z : seq.w));
+      if (++f >= seq_len) { L = -1; f = 0; }
+    } else if (tok == end_id) {
+      L = -1;
+    } else {
+      --L;
+    }
+    ids[row] = tok;
+  }
+  left[slot] = L;
+  fpos[slot] = f;
+}
+
 }  // namespace cb
 
 extern "C" {
@@ -296,6 +331,19 @@ int cb_verify_greedy(const void* target_ids, const void* draft_ids, const void* 
       static_cast<const int*>(target_ids), static_cast<const int*>(draft_ids), static_cast<const int*>(depth),
       max_depth, static_cast<const int*>(forced_reject_at), static_cast<int*>(accepted), static_cast<int*>(bonus),
       requests);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ids[rows] (in place), row_slot / init [rows], left / fpos [slots]; `seq` = 1..4 tokens of the forced end sequence
+// (it contains `end_id`).
+int cb_reasoning_budget(void* ids, const void* row_slot, const void* init, void* left, void* fpos, int rows, int end_id,
+                        const int* seq, int seq_len, void* stream) {
+  if (rows <= 0) return 0;
+  if (!seq || seq_len < 1 || seq_len > 4) return -20;
+  int4 q = make_int4(seq[0], seq_len > 1 ? seq[1] : 0, seq_len > 2 ? seq[2] : 0, seq_len > 3 ? seq[3] : 0);
+  cb::reasoning_budget_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int*>(ids), static_cast<const int*>(row_slot), static_cast<const int*>(init), static_cast<int*>(left),
+      static_cast<int*>(fpos), rows, end_id, q, seq_len);
   return static_cast<int>(cudaGetLastError());
 }
 

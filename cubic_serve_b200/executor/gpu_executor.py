@@ -36,6 +36,7 @@ class Segment:
     draw: int = 0
     uid: int = -1                # identity of the request owning the slot (page-table row reuse detection)
     mask: np.ndarray | None = None   # allowed-token bitmask of the sampled row (uint32 words, bit set = allowed)
+    budget_init: int = -2        # thinking budget of the sampled row's request: -2 keep, -1 none, >= 0 (re)start with it
 
 
 class _Staging:
@@ -52,6 +53,8 @@ class _Staging:
             # the step's rows grouped by request (recurrent layers walk a request's rows in order)
             ("seg_row0", np.int32, max_rows), ("seg_count", np.int32, max_rows), ("seg_slot", np.int32, max_rows),
             ("seg_pos0", np.int32, max_rows),
+            # per sampled row: the request's slot and its thinking-budget command (device-side budget state machine)
+            ("row_slot", np.int32, max_rows), ("budget_init", np.int32, max_rows),
             ("page_table", np.int32, max_rows * max_pages),
         ]
         off = 0
@@ -146,6 +149,8 @@ class BatchBuilder:
             t = rb = nseg = n
             rows = 0
             if all(s.sample for s in segs):
+                h["row_slot"][:n] = h["rb_req"][:n]
+                h["budget_init"][:n] = [s.budget_init for s in segs]
                 h["logit_rows"][:n] = ar
                 h["temperature"][:n] = [s.temperature for s in segs]
                 h["top_p"][:n] = [s.top_p for s in segs]
@@ -157,6 +162,7 @@ class BatchBuilder:
                 for i, s in enumerate(segs):
                     if s.sample:
                         h["logit_rows"][rows] = i
+                        h["row_slot"][rows], h["budget_init"][rows] = s.request_slot, s.budget_init
                         h["temperature"][rows], h["top_p"][rows], h["top_k"][rows] = s.temperature, s.top_p, s.top_k
                         h["seeds"][rows], h["draws"][rows] = s.seed, s.draw
                         rows += 1
@@ -180,6 +186,7 @@ class BatchBuilder:
                 rb += nb
                 if s.sample:
                     h["logit_rows"][rows] = t + n - 1
+                    h["row_slot"][rows], h["budget_init"][rows] = s.request_slot, s.budget_init
                     h["temperature"][rows], h["top_p"][rows], h["top_k"][rows] = s.temperature, s.top_p, s.top_k
                     h["seeds"][rows], h["draws"][rows] = s.seed, s.draw
                     rows += 1
@@ -195,6 +202,7 @@ class BatchBuilder:
             h["rb_qcount"][rb:p] = 0
             h["rb_ctx"][rb:p] = 0
             h["logit_rows"][rows:p] = np.arange(rows, p)
+            h["row_slot"][rows:p] = -1
             h["temperature"][rows:p] = 0
             h["seg_row0"][nseg:p] = np.arange(nseg, p, dtype=np.int32)
             h["seg_count"][nseg:p] = 0
@@ -248,6 +256,12 @@ class GpuExecutor:
         self._uploaded = torch.cuda.Event()
         self._upload_pending = False
         self._launches = 0
+
+    @property
+    def reasoning_end_id(self) -> int | None:
+        """Closing token of a reasoning block when thinking budgets are enforced on the device, else None."""
+        r = self.runner.reasoning
+        return None if r is None else r.end_token_id
 
     # ----------------------------------------------------------------- batches
     # ------------------------------------------------------------------- run

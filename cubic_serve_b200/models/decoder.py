@@ -211,6 +211,7 @@ class DecoderRunner:
         self.tp_size = tp.size if tp is not None else 1
         self.k_bits, self.v_bits = k_bits, v_bits
         self.kv_rotation = kv_rotation
+        self.reasoning = None        # K.ReasoningBudget once enable_reasoning_budget() was called
         self.hq = cfg.num_q_heads // self.tp_size
         self.hkv = cfg.num_kv_heads // self.tp_size
         self.D = cfg.head_dim
@@ -457,8 +458,22 @@ class DecoderRunner:
         self._dummy_val()
         return self._cand_id
 
+    def enable_reasoning_budget(self, end_token_id: int, forced_tokens: list[int]) -> None:
+        """Enforce thinking-token budgets on the device (before the decode graphs are captured): after the budget of
+        a request is used up its sampled ids are replaced by ``forced_tokens`` (1-4 tokens, ending the reasoning
+        block); sampling ``end_token_id`` on its own ends the phase.  Every rank and stage runs the same state
+        machine on the same ids."""
+        self.reasoning = K.ReasoningBudget(self.max_requests, end_token_id, forced_tokens, self.device)
+
     def run_step(self, b: StepBatch, d: dict, logits_buf: torch.Tensor, out_ids: torch.Tensor) -> None:
-        """Whole step: layers, final norm, lm_head, sampling (and the cross-rank token agreement under TP)."""
+        """Whole step: layers, final norm, lm_head, sampling (and the cross-rank token agreement under TP), then the
+        thinking-budget state machine on the sampled ids when it is enabled."""
+        self._run_step(b, d, logits_buf, out_ids)
+        if self.reasoning is not None and b.num_logit_rows:
+            self.reasoning.apply(out_ids, d["row_slot"], d["budget_init"], b.num_logit_rows)
+            self.launches_per_step += 1
+
+    def _run_step(self, b: StepBatch, d: dict, logits_buf: torch.Tensor, out_ids: torch.Tensor) -> None:
         R = b.num_logit_rows
         fused = self.tp is not None and self.tp.fused is not None
         pp = self.pp

@@ -469,3 +469,24 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor | None =
                                         out.stride(0), rows, cols, _stream())
     native.check(code, "cb_sigmoid_gate")
     return out
+
+
+# ------------------------------------------------------------------ thinking-token budgets
+class ReasoningBudget:
+    """Device state of the thinking-token budgets: one counter per request slot (see ``csrc/sampling.cu``)."""
+
+    def __init__(self, slots: int, end_token_id: int, forced_tokens: list[int], device) -> None:
+        if not 1 <= len(forced_tokens) <= 4 or end_token_id not in forced_tokens:
+            raise ValueError("the forced end sequence has 1 to 4 tokens and contains the closing token")
+        self.end_token_id = int(end_token_id)
+        self.forced = [int(t) for t in forced_tokens]
+        self._seq = (ctypes.c_int * len(self.forced))(*self.forced)
+        self.left = torch.full((slots,), -1, dtype=torch.int32, device=device)
+        self.fpos = torch.zeros(slots, dtype=torch.int32, device=device)
+
+    def apply(self, ids: torch.Tensor, row_slot: torch.Tensor, init: torch.Tensor, rows: int) -> None:
+        """Run the state machine on the step's ``rows`` sampled ids in place."""
+        code = native.lib().cb_reasoning_budget(ids.data_ptr(), row_slot.data_ptr(), init.data_ptr(), self.left.data_ptr(),
+                                                self.fpos.data_ptr(), rows, self.end_token_id, self._seq,
+                                                len(self.forced), _stream())
+        native.check(code, "cb_reasoning_budget")

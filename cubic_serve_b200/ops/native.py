@@ -150,6 +150,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_moe_combine.restype = i
     l.cb_wq_gemm_grouped_mode.argtypes = [i]
     l.cb_wq_gemm_grouped_mode.restype = None
+    l.cb_reasoning_budget.argtypes = [vp, vp, vp, vp, vp, i, i, ctypes.POINTER(ctypes.c_int), i, vp]
+    l.cb_reasoning_budget.restype = i
     l.cb_gdn_conv.argtypes = [vp, i, vp, i, vp, vp, vp, vp, i, vp]
     l.cb_gdn_conv.restype = i
     l.cb_gdn_delta.argtypes = [vp, vp, vp]

@@ -121,7 +121,8 @@ class TokenChatBackend:
             matcher = compile_matcher(req.structured, self.tokenizer, eos, self.engine._mask_words * 32)
         sp = SamplingParams(temperature=s.temperature, top_p=s.top_p, top_k=s.top_k, seed=s.seed, max_tokens=max_tokens,
                             stop_token_ids=tuple(s.stop_token_ids) + ((eos,) if eos is not None else ()),
-                            matcher=matcher)
+                            matcher=matcher,
+                            thinking_budget=req.reasoning.budget_tokens if prepared.starts_in_reasoning else None)
         with self._lock:
             self._live[req.request_id] = live
             self._inbox.append((req.request_id, prepared.token_ids, sp))

@@ -56,6 +56,7 @@ class LLMEngine:
         self.overlap_decode = True
         self._ahead = None
         self._ahead_stale = False
+        self._budget_sig: dict[str, tuple[int, int]] = {}
         self._draft_states: dict = {}
         vocab = getattr(getattr(executor, "cfg", None), "vocab_size", None) or getattr(executor, "vocab_size", 0)
         self._mask_words = -(-int(vocab) // 32) if vocab else 0
@@ -143,6 +144,7 @@ class LLMEngine:
         """Executor segments of a plan.  ``ahead``: the plan is a look-ahead step whose input tokens are not known on
         the host yet (the previous step's commit will append them); draws count that commit in."""
         segs = []
+        end_id = getattr(self.executor, "reasoning_end_id", None)
         for s in plan.segments:
             r = s.request
             toks = [0] if ahead else r.tokens[s.start:s.start + s.count]
@@ -153,8 +155,21 @@ class LLMEngine:
                 sp.matcher.fill_bitmask(mask)
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
                                 sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF,
-                                r.draws + (1 if ahead else 0), r.arrival, mask))
+                                r.draws + (1 if ahead else 0), r.arrival, mask,
+                                self._budget_init(r) if s.sample and end_id is not None else -2))
         return segs
+
+    def _budget_init(self, r: Request) -> int:
+        """Thinking-budget command of a sampled row: the device counter of the request's slot is (re)armed on the
+        first sampled step after the request got its slot (admission, or re-admission after a preemption)."""
+        sig = (r.slot, r.preemptions)
+        if self._budget_sig.get(r.request_id) == sig:
+            return -2
+        self._budget_sig[r.request_id] = sig
+        b = r.sampling.thinking_budget
+        if b is None or self.executor.reasoning_end_id in r.output:
+            return -1
+        return max(0, b - len(r.output))
 
     def _run(self, plan: BatchPlan) -> list[StepOutput]:
         if plan.copies:
@@ -204,6 +219,7 @@ class LLMEngine:
             if fin is not None:
                 self.requests.pop(rid, None)
                 self._draft_states.pop(rid, None)
+                self._budget_sig.pop(rid, None)
         return outs
 
     def enable_dynamic_draft(self, config=None, graph_capacities: tuple[int, ...] = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512,

@@ -44,6 +44,9 @@ class SamplingParams:
     # structured output: an object with ``fill_bitmask(uint32 words)`` and ``accept(token) -> bool``
     # (``generation/constraints.py``); the engine masks the sampler with it and advances it on every commit
     matcher: object | None = None
+    # thinking-token budget of a request that starts inside a reasoning block: after this many tokens the executor
+    # forces the end of the block (enforced on the device, see ``csrc/sampling.cu``); None = unlimited
+    thinking_budget: int | None = None
 
     def validate(self) -> None:
         if not 0.0 <= self.temperature <= 2.0:
@@ -54,6 +57,8 @@ class SamplingParams:
             raise ValueError("top_k must be in [0, 20]")
         if self.max_tokens < 1:
             raise ValueError("max_tokens must be >= 1")
+        if self.thinking_budget is not None and self.thinking_budget < 0:
+            raise ValueError("thinking_budget must be >= 0")
 
 
 @dataclass

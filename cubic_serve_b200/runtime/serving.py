@@ -27,6 +27,24 @@ def _tokenizer_for(model: str, vocab_size: int):
     return tok
 
 
+def reasoning_end_tokens(tok) -> tuple[int, list[int]] | None:
+    """``(closing token id, forced end sequence)`` of the tokenizer's ``</think>`` marker, or None when the marker is
+    not a single token.  The forced sequence is what ends a reasoning block whose budget is used up: the marker
+    framed by line breaks when that tokenizes to at most four tokens, else the marker alone."""
+    try:
+        ids = tok.encode("</think>", add_special_tokens=False)
+    except TypeError:
+        ids = tok.encode("</think>")
+    if len(ids) != 1:
+        return None
+    end = int(ids[0])
+    try:
+        framed = [int(t) for t in tok.encode("\n</think>\n\n", add_special_tokens=False)]
+    except TypeError:
+        framed = [int(t) for t in tok.encode("\n</think>\n\n")]
+    return end, (framed if end in framed and len(framed) <= 4 else [end])
+
+
 def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int, v_bits: int, max_model_len: int,
                   max_running: int, layers: int | None = None) -> int:
     """Pages that fit in the remaining device memory (one page = 16 tokens of every local layer's rank-local KV
@@ -103,6 +121,9 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
                                               max_prefill_tokens=args.token_budget, max_model_len=max_len)
             log.info("MTP speculative decoding: depth %d, %s draft length; %d KV pages", depth, spec.mode, pages)
         else:
+            think = reasoning_end_tokens(_tokenizer_for(model, cfg.vocab_size))
+            if think is not None:
+                runner.enable_reasoning_budget(*think)       # thinking-token budgets are enforced on the device
             executor = GpuExecutor(runner, max_rows=args.max_running_requests, max_prefill_tokens=args.token_budget,
                                    max_model_len=max_len)
             caps = executor.capture_decode_graphs()

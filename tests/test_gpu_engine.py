@@ -49,3 +49,72 @@ def test_overlapped_decode_matches_stepwise_on_device():
     # sampling with temperature: the draw counters of look-ahead rows count the pending commit
     sp2 = SamplingParams(max_tokens=16, temperature=0.8, top_k=20, seed=7, ignore_eos=True)
     assert _engine(True)[0].generate(prompts[:4], sp2) == _engine(False)[0].generate(prompts[:4], sp2)
+
+
+def test_thinking_budget_state_machine_and_engine():
+    """Device-side thinking budgets: the kernel against a Python model of the state machine, then end to end: after
+    the budget the forced end sequence appears in the request's output, other requests are untouched."""
+    from cubic_serve_b200.ops import kernels as K
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    dev = torch.device("cuda")
+    end, seq = 7, [3, 7, 9]
+    rb = K.ReasoningBudget(8, end, seq, dev)
+    rng = np.random.default_rng(0)
+    left, fpos = [-1] * 8, [0] * 8
+    for step in range(40):
+        rows = 6
+        slots = rng.permutation(8)[:rows].astype(np.int32)            # a request has one sampled row per step
+        if step % 5 == 0:
+            slots[rng.integers(0, rows)] = -1                           # a padding row now and then
+        init = rng.choice([-2, -2, -2, -1, 0, 2, 5], rows).astype(np.int32)
+        ids = rng.integers(0, 12, rows).astype(np.int32)
+        want = ids.copy()
+        for r in range(rows):
+            s = int(slots[r])
+            if s < 0:
+                continue
+            if init[r] >= -1:
+                left[s], fpos[s] = int(init[r]), 0
+            if left[s] >= 0:
+                if fpos[s] > 0 or left[s] == 0:
+                    want[r] = seq[fpos[s]]
+                    fpos[s] += 1
+                    if fpos[s] >= len(seq):
+                        left[s], fpos[s] = -1, 0
+                elif want[r] == end:
+                    left[s] = -1
+                else:
+                    left[s] -= 1
+        d_ids = torch.tensor(ids, device=dev)
+        rb.apply(d_ids, torch.tensor(slots, device=dev), torch.tensor(init, device=dev), rows)
+        assert d_ids.cpu().tolist() == want.tolist()
+        assert rb.left.cpu().tolist() == left and rb.fpos.cpu().tolist() == fpos
+
+    # end to end (decode graphs + overlapped launches): request 1 has a budget of 5 tokens
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SchedulerConfig
+    cfg = ModelConfig(name="eng", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, rope_theta=1e6, quant=QuantSpec("cubic", 4, 128))
+    outs = {}
+    for budgets in (False, True):
+        runner = DecoderRunner(cfg, random_decoder_weights(cfg, dev, seed=0, std=0.05), num_pages=256, max_tokens=512,
+                               max_requests=16)
+        runner.enable_reasoning_budget(2047, [2046, 2047])
+        ex = GpuExecutor(runner, max_rows=16, max_prefill_tokens=512, max_model_len=256)
+        ex.capture_decode_graphs()
+        eng = LLMEngine(ex, 256, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
+                                                 enable_prefix_cache=False))
+        prompts = [np.random.default_rng(i).integers(0, 2000, 20 + i).tolist() for i in range(3)]
+        ids = [eng.add_request(p, SamplingParams(max_tokens=14, ignore_eos=True,
+                                                 thinking_budget=5 if (budgets and i == 1) else None))
+               for i, p in enumerate(prompts)]
+        reqs = [eng.requests[i] for i in ids]
+        while eng.has_unfinished:
+            eng.step()
+        outs[budgets] = [r.output for r in reqs]
+        runner.ws.check_status()
+    plain, forced = outs[False], outs[True]
+    assert forced[0] == plain[0] and forced[2] == plain[2]
+    assert forced[1][:5] == plain[1][:5] and forced[1][5:7] == [2046, 2047] and len(forced[1]) == 14
