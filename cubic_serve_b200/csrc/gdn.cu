@@ -99,6 +99,14 @@ struct GdnDeltaParams {
 // step).  A thread holds four rows: warp * 16 + (lane >> 3) + 4 i.  Row sums (S k and S q) are reduced over the
 // eight lanes by shuffles.  Two CTAs per SM (128 registers per thread): one CTA's state load / store overlaps the
 // other's arithmetic.
+//
+// A segment is walked in blocks of 16 tokens, three phases per block:
+//   A (parallel, four warp tasks per token)  L2-normalised q / k, v, z, beta and decay of the block's tokens into shared memory
+//   B (the recurrence, no CTA barrier inside)  per token: decay, S k, delta, rank-one update, S q; outputs to shared memory
+//   C (parallel, a warp per token)  gated RMSNorm of the block's outputs, coalesced stores
+// so the token-serial part is only the arithmetic that really depends on the state.
+static constexpr int kGdnBlock = 16;
+
 __global__ void __launch_bounds__(256, 2)
 gdn_delta_kernel(const GdnDeltaParams p) {
   const int head = blockIdx.x;
@@ -107,13 +115,17 @@ gdn_delta_kernel(const GdnDeltaParams p) {
   if (n <= 0) return;
   const int row0 = p.seg.row0[s];
   const int tid = threadIdx.x;
+  const int warp = tid >> 5;
   const int lane = tid & 31;
   const int l8 = lane & 7;
-  const int vrow = (tid >> 5) * 16 + (lane >> 3);        // + 4 i
+  const int vrow = warp * 16 + (lane >> 3);              // + 4 i
   const int khead = head / (p.Hv / p.Hk);
-  __shared__ __align__(16) float qs[kGdnDim];
-  __shared__ __align__(16) float ks[kGdnDim];
-  __shared__ float red[3][8];
+  __shared__ __align__(16) float qs[kGdnBlock][kGdnDim];
+  __shared__ __align__(16) float ks[kGdnBlock][kGdnDim];
+  __shared__ float vs[kGdnBlock][kGdnDim];
+  __shared__ float os[kGdnBlock][kGdnDim];
+  __shared__ float zs[kGdnBlock][kGdnDim];
+  __shared__ float2 coef[kGdnBlock];                      // {beta, decay}
 
   float* sp = p.state + ((static_cast<size_t>(p.seg.slot[s]) * p.Hv + head) * kGdnDim + vrow) * kGdnDim + l8 * 4;
   float4 S[4][4];                                        // [row i][chunk c]: columns 4 (l8 + 8 c) .. + 3
@@ -133,104 +145,115 @@ gdn_delta_kernel(const GdnDeltaParams p) {
   const int q_off = khead * kGdnDim, k_off = (p.Hk + khead) * kGdnDim, v_off = (2 * p.Hk + head) * kGdnDim;
   float nw[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) nw[i] = p.norm_w[vrow + 4 * i];
+  for (int a = 0; a < 4; ++a) nw[a] = p.norm_w[lane + 32 * a];
 
-  // operands of a row: thread tid carries q[tid] (tid < 128) or k[tid - 128] into the norm, every thread the v and
-  // z of its four state rows; each iteration loads the next row's before it computes
-  float qk_next, v_next[4], z_next[4], b_next, a_next;
-  auto load_row = [&](size_t r) {
-    const __nv_bfloat16* row = p.qkv + r * p.ldqkv;
-    qk_next = __bfloat162float(tid < 128 ? row[q_off + tid] : row[k_off + tid - 128]);
+  for (int t0 = 0; t0 < n; t0 += kGdnBlock) {
+    const int nb = min(kGdnBlock, n - t0);
+    // ---- A: operands of the block's tokens.  Four independent tasks per token (q, k, v + z, coefficients) dealt
+    // to the eight warps, so that a one-token decode step still uses four warps at once
+    for (int task = warp; task < nb * 4; task += 8) {
+      const int j = task >> 2, part = task & 3;
+      const size_t r = static_cast<size_t>(row0 + t0 + j);
+      const __nv_bfloat16* row = p.qkv + r * p.ldqkv;
+      if (part < 2) {
+        // stored boundary of the oracle: normalised q / k are rounded to bf16; q carries the 1 / sqrt(d_k) scale
+        const __nv_bfloat16* src = row + (part == 0 ? q_off : k_off);
+        float x[4];
+        float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v_next[i] = __bfloat162float(row[v_off + vrow + 4 * i]);
-      z_next[i] = __bfloat162float(p.z[r * p.ldz + head * kGdnDim + vrow + 4 * i]);
-    }
-    b_next = __bfloat162float(p.ba[r * p.ldba + head]);
-    a_next = __bfloat162float(p.ba[r * p.ldba + p.Hv + head]);
-  };
-  load_row(static_cast<size_t>(row0));
-
-  for (int t = 0; t < n; ++t) {
-    const float qk = qk_next, bb = b_next, aa = a_next;
-    float v[4], zz[4];
+        for (int a = 0; a < 4; ++a) {
+          x[a] = __bfloat162float(src[lane + 32 * a]);
+          ss = fmaf(x[a], x[a], ss);
+        }
+        const float inv = rsqrtf(warp_sum(ss) + p.eps_l2);
+        float* dst = part == 0 ? qs[j] : ks[j];
+        const float scale = part == 0 ? 0.08838834764831845f : 1.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { v[i] = v_next[i]; zz[i] = z_next[i]; }
-    if (t + 1 < n) load_row(static_cast<size_t>(row0 + t + 1));
-    // L2 norms of q (warps 0-3) and k (warps 4-7)
-    const float sq = warp_sum(qk * qk);
-    if (lane == 0) red[0][tid >> 5] = sq;
-    __syncthreads();
-    {
-      const int base = tid < 128 ? 0 : 4;
-      const float tot = red[0][base] + red[0][base + 1] + red[0][base + 2] + red[0][base + 3];
-      const float inv = rsqrtf(tot + p.eps_l2);
-      // stored boundary of the oracle: normalised q / k are rounded to bf16; q carries the 1 / sqrt(d_k) scale
-      const float nv = __bfloat162float(__float2bfloat16(qk * inv));
-      if (tid < 128) qs[tid] = nv * 0.08838834764831845f;
-      else ks[tid - 128] = nv;
-    }
-    __syncthreads();
-    const float beta = 1.f / (1.f + __expf(-bb));
-    const float x = aa + dtb;
-    const float softplus = x > 20.f ? x : log1pf(__expf(x));
-    const float decay = __expf(neg_exp_a * softplus);
-
-    float4 kv[4];
+        for (int a = 0; a < 4; ++a) dst[lane + 32 * a] = __bfloat162float(__float2bfloat16(x[a] * inv)) * scale;
+      } else if (part == 2) {
+        const __nv_bfloat16* zrow = p.z + r * p.ldz + head * kGdnDim;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) kv[c] = *reinterpret_cast<const float4*>(ks + 4 * (l8 + 8 * c));
-    float mem[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float m = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float4& e = S[i][c];
-        e.x *= decay; e.y *= decay; e.z *= decay; e.w *= decay;
-        m = fmaf(e.x, kv[c].x, m); m = fmaf(e.y, kv[c].y, m); m = fmaf(e.z, kv[c].z, m); m = fmaf(e.w, kv[c].w, m);
+        for (int a = 0; a < 4; ++a) {
+          vs[j][lane + 32 * a] = __bfloat162float(row[v_off + lane + 32 * a]);
+          zs[j][lane + 32 * a] = __bfloat162float(zrow[lane + 32 * a]);
+        }
+      } else if (lane == 0) {
+        const float bb = __bfloat162float(p.ba[r * p.ldba + head]);
+        const float x = __bfloat162float(p.ba[r * p.ldba + p.Hv + head]) + dtb;
+        const float softplus = x > 20.f ? x : log1pf(__expf(x));
+        coef[j] = make_float2(1.f / (1.f + __expf(-bb)), __expf(neg_exp_a * softplus));
       }
-      m += __shfl_xor_sync(0xffffffffu, m, 1);
-      m += __shfl_xor_sync(0xffffffffu, m, 2);
-      m += __shfl_xor_sync(0xffffffffu, m, 4);
-      mem[i] = m;
     }
-    float4 qv[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) qv[c] = *reinterpret_cast<const float4*>(qs + 4 * (l8 + 8 * c));
-    float ob[4];
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float delta = (v[i] - mem[i]) * beta;
-      float o = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float4& e = S[i][c];
-        e.x = fmaf(delta, kv[c].x, e.x); e.y = fmaf(delta, kv[c].y, e.y);
-        e.z = fmaf(delta, kv[c].z, e.z); e.w = fmaf(delta, kv[c].w, e.w);
-        o = fmaf(e.x, qv[c].x, o); o = fmaf(e.y, qv[c].y, o); o = fmaf(e.z, qv[c].z, o); o = fmaf(e.w, qv[c].w, o);
-      }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      ob[i] = __bfloat162float(__float2bfloat16(o));       // the recurrence output is stored in bf16
-      if (l8 == 0) ss = fmaf(ob[i], ob[i], ss);            // every row counted once
-    }
-    // gated RMSNorm over the head's 128 outputs
-    ss = warp_sum(ss);
-    if (lane == 0) red[1 + (t & 1)][tid >> 5] = ss;
     __syncthreads();
-    if (l8 == 0) {
-      const float* rr = red[1 + (t & 1)];
-      const float tot = rr[0] + rr[1] + rr[2] + rr[3] + rr[4] + rr[5] + rr[6] + rr[7];
-      const float inv = rsqrtf(tot * (1.f / kGdnDim) + p.eps_norm);
-      __nv_bfloat16* orow = p.out + static_cast<size_t>(row0 + t) * p.ldo + head * kGdnDim + vrow;
+    // ---- B: the recurrence
+    for (int j = 0; j < nb; ++j) {
+      const float beta = coef[j].x, decay = coef[j].y;
+      float4 kv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kv[c] = *reinterpret_cast<const float4*>(&ks[j][4 * (l8 + 8 * c)]);
+      float mem[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float normed = __bfloat162float(__float2bfloat16(ob[i] * inv));
-        orow[4 * i] = __float2bfloat16(normed * nw[i] * silu_fast(zz[i]));
+        float m = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float4& e = S[i][c];
+          e.x *= decay; e.y *= decay; e.z *= decay; e.w *= decay;
+          m = fmaf(e.x, kv[c].x, m); m = fmaf(e.y, kv[c].y, m); m = fmaf(e.z, kv[c].z, m); m = fmaf(e.w, kv[c].w, m);
+        }
+        mem[i] = m;
+      }
+#pragma unroll
+      for (int sh = 1; sh < 8; sh <<= 1)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mem[i] += __shfl_xor_sync(0xffffffffu, mem[i], sh);
+      float4 qv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) qv[c] = *reinterpret_cast<const float4*>(&qs[j][4 * (l8 + 8 * c)]);
+      float o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float delta = (vs[j][vrow + 4 * i] - mem[i]) * beta;
+        float acc = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float4& e = S[i][c];
+          e.x = fmaf(delta, kv[c].x, e.x); e.y = fmaf(delta, kv[c].y, e.y);
+          e.z = fmaf(delta, kv[c].z, e.z); e.w = fmaf(delta, kv[c].w, e.w);
+          acc = fmaf(e.x, qv[c].x, acc); acc = fmaf(e.y, qv[c].y, acc); acc = fmaf(e.z, qv[c].z, acc); acc = fmaf(e.w, qv[c].w, acc);
+        }
+        o[i] = acc;
+      }
+#pragma unroll
+      for (int sh = 1; sh < 8; sh <<= 1)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], sh);
+      if (l8 == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) os[j][vrow + 4 * i] = __bfloat162float(__float2bfloat16(o[i]));   // stored in bf16
       }
     }
+    __syncthreads();
+    // ---- C: gated RMSNorm over each token's 128 outputs
+    for (int j = warp; j < nb; j += 8) {
+      const size_t r = static_cast<size_t>(row0 + t0 + j);
+      float ob[4];
+      float ss = 0.f;
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        ob[a] = os[j][lane + 32 * a];
+        ss = fmaf(ob[a], ob[a], ss);
+      }
+      const float inv = rsqrtf(warp_sum(ss) * (1.f / kGdnDim) + p.eps_norm);
+      __nv_bfloat16* orow = p.out + r * p.ldo + head * kGdnDim;
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float normed = __bfloat162float(__float2bfloat16(ob[a] * inv));
+        orow[lane + 32 * a] = __float2bfloat16(normed * nw[a] * silu_fast(zs[j][lane + 32 * a]));
+      }
+    }
+    // (the next block's phase A writes q / k / v / z: z of this block is still being read here, hence the barrier)
+    if (t0 + kGdnBlock < n) __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i)

@@ -52,7 +52,104 @@ def run_qualification(device: int = 0, quick: bool = False) -> dict:
     pw = wq_pack.pack_bf16(w).to(dev)
     same = torch.equal(K.wq_gemm(x_small, pw), K.wq_gemm(x_big, pw)[:16])
     results.append({"kernel": "wq_gemm padding isolation", "shape": [16, 64], "class": "exact" if same else "mismatch", "rel_l2": 0.0})
+    results += _qualify_gemm_variants(dev, g, quick)
+    results += _qualify_recurrent_and_rotation(dev, g)
+    results.append(_qualify_graph_replay(dev))
     torch.cuda.synchronize(dev)
     K.workspace(dev).check_status()
     ok = all(r["class"] != "mismatch" for r in results)
     return {"ok": ok, "device": torch.cuda.get_device_name(dev), "seconds": round(time.time() - t0, 2), "results": results}
+
+
+def _verdict(name: str, shape, got, ref, bound: float) -> dict:
+    v = compare_tensors(got, ref, bound)
+    return {"kernel": name, "shape": list(shape), "class": v.klass.value, "rel_l2": v.rel_l2}
+
+
+def _qualify_gemm_variants(dev, g, quick: bool) -> list[dict]:
+    """The persistent stream-K kernel (forced many-part tiles), its CTA-pair form (cta_group::2) and the fused
+    SwiGLU epilogue against the fp32 oracle."""
+    from ..ops import eager, kernels as K, native, wq_pack
+    from ..quantization import cubic
+    out = []
+    m, n, k = (256, 512, 1024) if quick else (272, 1024, 2048)
+    w = torch.randn(n, k, generator=g) * 0.02
+    p = cubic.quantize(w, cubic.CubicScheme(4, 128))
+    pw = wq_pack.pack_cubic4(cubic.unpack_codes(p["weight_packed"], 4, k), p["weight_scale"], p["weight_a"], p["weight_b"], 128)
+    dense = wq_pack.unpack_to_dense(pw)[:n].to(dev)
+    x = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    ref = x.float() @ dense.t()
+    bound = reduction_bound(ref, torch.bfloat16, k)
+    lib = native.lib()
+    try:
+        for pairs, label in ((0, "stream-K"), (2, "stream-K, CTA pairs")):
+            lib.cb_wq_gemm_pair_mode(pairs)
+            out.append(_verdict(f"wq_gemm[cubic4] {label}", (m, n, k), K.wq_gemm(x, pw.to(dev), min_units=3), ref, bound))
+        act = K.wq_gemm_act(x, wq_pack.swiglu_interleave(pw).to(dev), min_units=3)
+        out.append(_verdict("wq_gemm[cubic4] + SwiGLU epilogue", (m, n // 2, k), act, eager.swiglu(ref.to(torch.bfloat16)),
+                            2.0 ** -5))
+    finally:
+        lib.cb_wq_gemm_pair_mode(1)
+    return out
+
+
+def _qualify_recurrent_and_rotation(dev, g) -> list[dict]:
+    """Gated DeltaNet kernels against their oracles (a fresh request and one that continues from stored state) and
+    the Walsh-Hadamard rotation against the matrix."""
+    from ..ops import eager, kernels as K
+    out = []
+    hk, hv, d = 2, 4, 128
+    counts, slots, pos0 = [7, 1], [1, 0], [0, 4]
+    T, C = sum(counts), (2 * hk + hv) * d
+    i32 = dict(dtype=torch.int32, device=dev)
+    seg = K.GdnSegments(torch.tensor([0, 7], **i32), torch.tensor(counts, **i32), torch.tensor(slots, **i32),
+                        torch.tensor(pos0, **i32), 2)
+    x = torch.randn(T, C, generator=g).to(torch.bfloat16)
+    w = torch.randn(C, 4, generator=g) * 0.4
+    cstate = torch.randn(2, 3, C, generator=g).to(torch.bfloat16)
+    mix = torch.empty(T, C, dtype=torch.bfloat16, device=dev)
+    K.gdn_conv(x.to(dev), w.to(dev), cstate.clone().to(dev), seg, mix)
+    want = torch.cat([eager.gdn_conv(x[:7], w, None)[0], eager.gdn_conv(x[7:], w, cstate[0])[0]])
+    out.append(_verdict("gdn_conv", (T, C), mix, want.to(dev), 2.0 ** -6))
+    z = torch.randn(T, hv * d, generator=g).to(torch.bfloat16)
+    ba = torch.randn(T, 2 * hv, generator=g).to(torch.bfloat16)
+    a_log, dt_bias, nw = torch.randn(hv, generator=g) * 0.5, torch.randn(hv, generator=g) * 0.5, torch.ones(d)
+    state = torch.randn(2, hv, d, d, generator=g) * 0.05
+    got = torch.empty(T, hv * d, dtype=torch.bfloat16, device=dev)
+    K.gdn_delta(mix, z.to(dev), ba.to(dev), a_log.to(dev), dt_bias.to(dev), nw.to(dev), state.clone().to(dev), seg, got, hk, hv)
+    mc = mix.cpu()
+    want = torch.cat([eager.gdn_delta(mc[:7], z[:7], ba[:7], a_log, dt_bias, nw, None, hk, hv)[0],
+                      eager.gdn_delta(mc[7:], z[7:], ba[7:], a_log, dt_bias, nw, state[0], hk, hv)[0]])
+    out.append(_verdict("gdn_delta", (T, hv * d), got, want.to(dev), 2.0 ** -5))
+    h = torch.ones(1, 1)
+    for _ in range(7):
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    v = torch.randn(9, 256, generator=g).to(torch.bfloat16)
+    want = (v.float().view(9, 2, 128) @ (h / 128 ** 0.5)).view(9, 256)
+    out.append(_verdict("hadamard", (9, 256), K.hadamard(v.to(dev).clone()), want.to(dev), 2.0 ** -6))
+    return out
+
+
+def _qualify_graph_replay(dev) -> dict:
+    """A toy decoder generates the same tokens with eager launches and with captured decode graphs (padded rows)."""
+    from ..executor.gpu_executor import GpuExecutor
+    from ..models.config import ModelConfig, QuantSpec
+    from ..models.decoder import DecoderRunner, random_decoder_weights
+    from ..runtime.engine import LLMEngine
+    from ..runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = ModelConfig(name="qualify", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, rope_theta=1e6, quant=QuantSpec("cubic", 4, 128))
+    weights = random_decoder_weights(cfg, dev, seed=0, std=0.05)
+    outs = []
+    for graphs in (False, True):
+        runner = DecoderRunner(cfg, weights, num_pages=64, max_tokens=256, max_requests=8)
+        ex = GpuExecutor(runner, max_rows=8, max_prefill_tokens=256, max_model_len=128, use_graphs=graphs)
+        if graphs:
+            ex.capture_decode_graphs()
+        eng = LLMEngine(ex, 64, SchedulerConfig(max_running_requests=8, max_model_len=128, max_batched_tokens=256,
+                                                enable_prefix_cache=False))
+        prompts = [[(7 * i + 3 * j) % 2000 for j in range(9 + 4 * i)] for i in range(3)]      # 3 rows in a 4-row graph
+        outs.append(eng.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True)))
+    same = outs[0] == outs[1]
+    return {"kernel": "decode graph replay == eager launches", "shape": [3, 10], "class": "exact" if same else "mismatch",
+            "rel_l2": 0.0}

@@ -118,3 +118,12 @@ def test_thinking_budget_state_machine_and_engine():
     plain, forced = outs[False], outs[True]
     assert forced[0] == plain[0] and forced[2] == plain[2]
     assert forced[1][:5] == plain[1][:5] and forced[1][5:7] == [2046, 2047] and len(forced[1]) == 14
+
+
+def test_qualification_run_passes():
+    from cubic_serve_b200.guardrail.qualify import run_qualification
+    rep = run_qualification(0, quick=True)
+    assert rep["ok"], [r for r in rep["results"] if r["class"] == "mismatch"]
+    names = " ".join(r["kernel"] for r in rep["results"])
+    for part in ("CTA pairs", "SwiGLU", "gdn_delta", "hadamard", "graph replay"):
+        assert part in names
