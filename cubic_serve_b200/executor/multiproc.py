@@ -125,10 +125,15 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=spec.token_budget, k_bits=spec.k_bits,
                                v_bits=spec.v_bits, tp=tp, pp=pp, max_requests=spec.max_rows,
                                kv_rotation=spec.kv_rotation)
+        from ..runtime.serving import _tokenizer_for, reasoning_end_tokens
+        think = reasoning_end_tokens(_tokenizer_for(spec.model, cfg.vocab_size))
+        if think is not None:
+            runner.enable_reasoning_budget(*think)      # every rank runs the same budget state machine
         ex = GpuExecutor(runner, max_rows=spec.max_rows, max_prefill_tokens=spec.token_budget,
                          max_model_len=spec.max_model_len)
         caps = ex.capture_decode_graphs()
-        conn.send(("ready", rank, {"pages": pages, "capacities": caps, "vocab": cfg.vocab_size, "name": cfg.name}))
+        conn.send(("ready", rank, {"pages": pages, "capacities": caps, "vocab": cfg.vocab_size, "name": cfg.name,
+                                   "reasoning_end_id": ex.reasoning_end_id, "hybrid": cfg.is_hybrid}))
         while True:
             cmd = conn.recv()
             if cmd[0] == "execute":
@@ -216,6 +221,16 @@ class MultiprocExecutor:
             self._check_alive()
 
     # ------------------------------------------------------------- executor API
+    @property
+    def reasoning_end_id(self) -> int | None:
+        return self.info.get("reasoning_end_id")
+
+    @property
+    def cfg(self):
+        """Family properties of the served model that the engine reads (recurrent layers switch prefix caching off)."""
+        from types import SimpleNamespace
+        return SimpleNamespace(is_hybrid=bool(self.info.get("hybrid", False)))
+
     def execute(self, segs) -> np.ndarray:
         if self.poisoned:
             raise WorkerFailure("executor is poisoned")

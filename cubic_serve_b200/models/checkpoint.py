@@ -87,8 +87,13 @@ class SafetensorsDirectory:
 
 def _layer_modules(cfg: ModelConfig, i: int) -> dict[str, str]:
     p = f"model.layers.{i}"
-    mods = {"q": f"{p}.self_attn.q_proj", "k": f"{p}.self_attn.k_proj", "v": f"{p}.self_attn.v_proj",
-            "o": f"{p}.self_attn.o_proj"}
+    if cfg.layer_is_gdn(i):
+        # Gated DeltaNet layer of the hybrid family (reference weight schema: models/qwen3_5/model.py:498)
+        mods = {"qkvz": f"{p}.linear_attn.in_proj_qkvz", "ba": f"{p}.linear_attn.in_proj_ba",
+                "gdn_out": f"{p}.linear_attn.out_proj"}
+    else:
+        mods = {"q": f"{p}.self_attn.q_proj", "k": f"{p}.self_attn.k_proj", "v": f"{p}.self_attn.v_proj",
+                "o": f"{p}.self_attn.o_proj"}
     if not cfg.is_moe:
         mods.update(gate=f"{p}.mlp.gate_proj", up=f"{p}.mlp.up_proj", down=f"{p}.mlp.down_proj")
     return mods
@@ -103,10 +108,19 @@ def logical_inventory(cfg: ModelConfig) -> tuple[dict[str, tuple[int, int]], lis
         plain.append("lm_head.weight")
     for i in range(cfg.num_layers):
         m = _layer_modules(cfg, i)
-        linears[m["q"]] = (cfg.q_size, H)
-        linears[m["k"]] = (cfg.kv_size, H)
-        linears[m["v"]] = (cfg.kv_size, H)
-        linears[m["o"]] = (H, cfg.q_size)
+        if cfg.layer_is_gdn(i):
+            gk, gv = cfg.gdn_k_heads, cfg.gdn_v_heads
+            linears[m["qkvz"]] = (2 * gk * 128 + 2 * gv * 128, H)
+            linears[m["ba"]] = (2 * gv, H)
+            linears[m["gdn_out"]] = (H, gv * 128)
+            lp = f"model.layers.{i}.linear_attn"
+            plain += [f"{lp}.conv1d.weight", f"{lp}.dt_bias", f"{lp}.A_log", f"{lp}.norm.weight"]
+        else:
+            # with an output gate the query projection carries [q_h | gate_h] per head
+            linears[m["q"]] = (cfg.q_size * (2 if cfg.attn_output_gate else 1), H)
+            linears[m["k"]] = (cfg.kv_size, H)
+            linears[m["v"]] = (cfg.kv_size, H)
+            linears[m["o"]] = (H, cfg.q_size)
         if cfg.is_moe:
             plain.append(f"model.layers.{i}.mlp.gate.weight")
             for e in range(cfg.num_experts):
@@ -119,7 +133,7 @@ def logical_inventory(cfg: ModelConfig) -> tuple[dict[str, tuple[int, int]], lis
             linears[m["up"]] = (cfg.intermediate_size, H)
             linears[m["down"]] = (H, cfg.intermediate_size)
         plain += [f"model.layers.{i}.input_layernorm.weight", f"model.layers.{i}.post_attention_layernorm.weight"]
-        if cfg.qk_norm:
+        if cfg.qk_norm and not cfg.layer_is_gdn(i):
             plain += [f"model.layers.{i}.self_attn.q_norm.weight", f"model.layers.{i}.self_attn.k_norm.weight"]
     return linears, plain
 
@@ -271,7 +285,7 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
 
     ``layer_range`` = ``[lo, hi)`` loads only the decoder layers of one pipeline stage.
     """
-    from .decoder import DecoderWeights, LayerWeights
+    from .decoder import DecoderWeights, GdnWeights, LayerWeights
     cfg, q = ck.cfg, ck.cfg.quant
     if cfg.is_moe:
         raise CheckpointError("MoE checkpoints are loaded by models.moe.load_moe_layer")
@@ -281,27 +295,78 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
     inter = cfg.intermediate_size // tp_size
     bf = torch.bfloat16
 
+    cache: dict[str, dict] = {}
+
+    def payload(module: str) -> dict:
+        if module not in cache:
+            cache.clear()                     # one module at a time: a layer's row ranges come from the same tensors
+            cache[module] = ck.payload(module)
+        return cache[module]
+
     def rows(module: str, lo: int, hi: int, n: int):
-        return _slice_rows(ck.payload(module), method, lo, hi, n), (hi - lo, ck_shapes[module][1])
+        return _slice_rows(payload(module), method, lo, hi, n), (hi - lo, ck_shapes[module][1])
 
     ck_shapes, _ = logical_inventory(cfg)
     layers = []
     for i in range(*(layer_range or (0, cfg.num_layers))):
         m = _layer_modules(cfg, i)
-        qkv = pack_logical(method, [rows(m["q"], tp_rank * hq * D, (tp_rank + 1) * hq * D, cfg.q_size),
-                                    rows(m["k"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size),
-                                    rows(m["v"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size)], q)
-        o = pack_logical(method, [(ck.payload(m["o"]), ck_shapes[m["o"]])], q,
-                         (tp_rank * hq * D, (tp_rank + 1) * hq * D))
+        p = f"model.layers.{i}"
+        gdn = attn_gate = qkv = o = None
+        if cfg.layer_is_gdn(i):
+            # The checkpoint groups the projection rows by key head: [q | k | v x r | z x r] (and [b x r | a x r]) for
+            # each of the Hk key heads, r = Hv / Hk value heads per key head.  The kernels take q | k | v | z of all
+            # (rank-local) heads in turn, so the rows are gathered section by section; a rank owns whole key heads.
+            gk_all, gv_all = cfg.gdn_k_heads, cfg.gdn_v_heads
+            r = gv_all // gk_all
+            gk, gv = gk_all // tp_size, gv_all // tp_size
+            group = (2 + 2 * r) * 128
+            heads = range(tp_rank * gk, (tp_rank + 1) * gk)
+            n_all = ck_shapes[m["qkvz"]][0]
+            parts = []
+            for lo, width in ((0, 128), (128, 128), (256, r * 128), (256 + r * 128, r * 128)):
+                parts += [rows(m["qkvz"], h * group + lo, h * group + lo + width, n_all) for h in heads]
+            in_proj = pack_logical(method, parts, q)
+            ba = _dense_of(method, ck.payload(m["ba"]), ck_shapes[m["ba"]], q).view(gk_all, 2, r, cfg.hidden_size)
+            ba = ba[tp_rank * gk:(tp_rank + 1) * gk]
+            in_ba = wq_pack.pack_bf16(torch.cat([ba[:, 0].reshape(gv, -1), ba[:, 1].reshape(gv, -1)]))
+            out = pack_logical(method, [(ck.payload(m["gdn_out"]), ck_shapes[m["gdn_out"]])], q,
+                               (tp_rank * gv * 128, (tp_rank + 1) * gv * 128))
+            lp = f"{p}.linear_attn"
+            # conv channels: q of all key heads | k | v (rank-local slices of each section)
+            cw = ck.store.get(f"{lp}.conv1d.weight").float().reshape(-1, 4)
+            qk, vv = gk_all * 128, gv_all * 128
+            sel = torch.cat([torch.arange(tp_rank * gk * 128, (tp_rank + 1) * gk * 128),
+                             qk + torch.arange(tp_rank * gk * 128, (tp_rank + 1) * gk * 128),
+                             2 * qk + torch.arange(tp_rank * gv * 128, (tp_rank + 1) * gv * 128)])
+            assert cw.shape[0] == 2 * qk + vv
+            f32 = dict(device=device, dtype=torch.float32)
+            gdn = GdnWeights(in_proj=in_proj.to(device), in_ba=in_ba.to(device), conv_w=cw[sel].contiguous().to(**f32),
+                             a_log=ck.store.get(f"{lp}.A_log")[tp_rank * gv:(tp_rank + 1) * gv].to(**f32),
+                             dt_bias=ck.store.get(f"{lp}.dt_bias")[tp_rank * gv:(tp_rank + 1) * gv].to(**f32),
+                             norm_w=ck.store.get(f"{lp}.norm.weight").to(**f32), out=out.to(device), hk=gk, hv=gv)
+        else:
+            if cfg.attn_output_gate:
+                # query projection rows per head: [q_h | gate_h]
+                heads = range(tp_rank * hq, (tp_rank + 1) * hq)
+                qn = 2 * cfg.q_size
+                q_parts = [rows(m["q"], h * 2 * D, h * 2 * D + D, qn) for h in heads]
+                attn_gate = pack_logical(method, [rows(m["q"], h * 2 * D + D, (h + 1) * 2 * D, qn) for h in heads], q)
+            else:
+                q_parts = [rows(m["q"], tp_rank * hq * D, (tp_rank + 1) * hq * D, cfg.q_size)]
+            qkv = pack_logical(method, q_parts + [rows(m["k"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size),
+                                                  rows(m["v"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size)], q)
+            o = pack_logical(method, [(ck.payload(m["o"]), ck_shapes[m["o"]])], q,
+                             (tp_rank * hq * D, (tp_rank + 1) * hq * D))
         gu = pack_logical(method, [rows(m["gate"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size),
                                    rows(m["up"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size)], q)
         down = pack_logical(method, [(ck.payload(m["down"]), ck_shapes[m["down"]])], q,
                             (tp_rank * inter, (tp_rank + 1) * inter))
-        p = f"model.layers.{i}"
         lw = LayerWeights(ln1=ck.store.get(f"{p}.input_layernorm.weight").to(device, bf),
                           ln2=ck.store.get(f"{p}.post_attention_layernorm.weight").to(device, bf),
-                          qkv=qkv.to(device), o=o.to(device), gate_up=gu.to(device), down=down.to(device))
-        if cfg.qk_norm:
+                          qkv=None if qkv is None else qkv.to(device), o=None if o is None else o.to(device), gdn=gdn,
+                          attn_gate=None if attn_gate is None else attn_gate.to(device),
+                          gate_up=gu.to(device), down=down.to(device))
+        if cfg.qk_norm and gdn is None:
             lw.q_norm = ck.store.get(f"{p}.self_attn.q_norm.weight").to(device, bf)
             lw.k_norm = ck.store.get(f"{p}.self_attn.k_norm.weight").to(device, bf)
         layers.append(lw)
@@ -377,10 +442,21 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
     tensors: dict[str, torch.Tensor] = {}
     for module, (n, k) in linears.items():
         w = torch.randn(n, k, generator=g) * std
+        if module.endswith("in_proj_ba"):
+            tensors[f"{module}.weight"] = w.to(torch.bfloat16)      # a 2 Hv-row module: left unquantized
+            continue
         for suffix, t in quantize_payload(w, cfg.quant).items():
             tensors[f"{module}.{suffix}"] = t.contiguous()
     for name in plain:
-        if name.endswith("norm.weight"):
+        if ".linear_attn." in name:
+            gk, gv = cfg.gdn_k_heads, cfg.gdn_v_heads
+            if name.endswith("conv1d.weight"):
+                tensors[name] = (torch.randn((2 * gk + gv) * 128, 1, 4, generator=g) * 0.3).to(torch.bfloat16)
+            elif name.endswith("norm.weight"):
+                tensors[name] = torch.ones(128, dtype=torch.bfloat16)
+            else:                              # A_log, dt_bias
+                tensors[name] = torch.randn(gv, generator=g) * 0.5
+        elif name.endswith("norm.weight"):
             tensors[name] = torch.ones(cfg.head_dim if "_norm" in name.split(".")[-2] and "self_attn" in name else cfg.hidden_size,
                                        dtype=torch.bfloat16)
         elif name.endswith("mlp.gate.weight"):
@@ -388,11 +464,16 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
         else:
             tensors[name] = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
     save_file(tensors, str(path / "model.safetensors"))
-    hf = {"architectures": ["Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_norm else "LlamaForCausalLM")],
+    arch = "Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_norm else "LlamaForCausalLM")
+    hf = {"architectures": ["Qwen3NextForCausalLM" if cfg.is_hybrid else arch],
           "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_q_heads,
           "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size,
           "vocab_size": cfg.vocab_size, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,
           "tie_word_embeddings": cfg.tie_embeddings, "max_position_embeddings": cfg.max_position, "_name_or_path": cfg.name}
+    if cfg.is_hybrid:
+        hf.update(linear_num_key_heads=cfg.gdn_k_heads, linear_num_value_heads=cfg.gdn_v_heads, linear_key_head_dim=128,
+                  linear_value_head_dim=128, full_attention_interval=cfg.gdn_interval, attn_output_gate=cfg.attn_output_gate,
+                  partial_rotary_factor=(cfg.rotary_dim or cfg.head_dim) / cfg.head_dim)
     if cfg.is_moe:
         hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token,
                   moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)

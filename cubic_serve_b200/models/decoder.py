@@ -25,8 +25,10 @@ from .config import ModelConfig
 @dataclass
 class GdnWeights:
     """Gated DeltaNet mixer of one layer (rank-local heads).  ``in_proj`` rows: q [Hk 128] | k [Hk 128] | v [Hv 128] |
-    z [Hv 128] | b [Hv] | a [Hv] (reference modules ``in_proj_qkvz`` + ``in_proj_ba``, ``models/qwen3_5/model.py:498``)."""
+    z [Hv 128]; ``in_ba`` rows: b [Hv] | a [Hv], kept in bf16 (64 rows: too small to quantize; reference modules
+    ``in_proj_qkvz`` and ``in_proj_ba``, ``models/qwen3_5/model.py:498``)."""
     in_proj: wq_pack.PackedWeight
+    in_ba: wq_pack.PackedWeight
     conv_w: torch.Tensor                 # fp32 [2 Hk 128 + Hv 128, 4]
     a_log: torch.Tensor                  # fp32 [Hv]
     dt_bias: torch.Tensor                # fp32 [Hv]
@@ -65,7 +67,7 @@ class DecoderWeights:
         for l in self.layers:
             ws = [l.qkv, l.o, l.gate_up, l.down, l.attn_gate]
             if l.gdn is not None:
-                ws += [l.gdn.in_proj, l.gdn.out]
+                ws += [l.gdn.in_proj, l.gdn.in_ba, l.gdn.out]
             if l.moe is not None:
                 ws += [l.moe.router, l.moe.gate_up, l.moe.down]
             for w in ws:
@@ -135,7 +137,8 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             gk, gv = cfg.gdn_k_heads // tp_size, cfg.gdn_v_heads // tp_size
             f32 = dict(device=device, dtype=torch.float32)
             lw = LayerWeights(ln1=norm_w(), ln2=norm_w(), gdn=GdnWeights(
-                in_proj=quantize_linear(rnd(2 * gk * 128 + 2 * gv * 128 + 2 * gv, H), cfg),
+                in_proj=quantize_linear(rnd(2 * gk * 128 + 2 * gv * 128, H), cfg),
+                in_ba=wq_pack.pack_bf16(rnd(2 * gv, H)),
                 conv_w=torch.randn((2 * gk + gv) * 128, 4, generator=gen, **f32) * 0.3,
                 a_log=torch.randn(gv, generator=gen, **f32) * 0.5,
                 dt_bias=torch.randn(gv, generator=gen, **f32) * 0.5,
@@ -239,6 +242,7 @@ class DecoderRunner:
                     self.gdn_conv_state[li] = torch.zeros(max_requests, 3, C, dtype=torch.bfloat16, device=dev)
                     self.gdn_state[li] = torch.zeros(max_requests, gv, 128, 128, dtype=torch.float32, device=dev)
             self.gdn_in = torch.empty(max_tokens, gdn_first.in_proj.n, dtype=torch.bfloat16, device=dev)
+            self.gdn_ba = torch.empty(max_tokens, 2 * gv, dtype=torch.bfloat16, device=dev)
             self.gdn_mix = torch.empty(max_tokens, C, dtype=torch.bfloat16, device=dev)
             self.gdn_out = torch.empty(max_tokens, gv * 128, dtype=torch.bfloat16, device=dev)
         if any(lw.attn_gate is not None for lw in weights.layers):
@@ -302,13 +306,13 @@ class DecoderRunner:
             raise RuntimeError("Gated DeltaNet layers need the step's request segments (StepBatch.segments)")
         if t0 != 0 or t1 != b.num_tokens:
             raise NotImplementedError("pipeline lanes split a step's rows; Gated DeltaNet layers take whole steps")
-        proj = self.gdn_in[t0:t1]
+        proj, ba = self.gdn_in[t0:t1], self.gdn_ba[t0:t1]
         K.wq_gemm(x, g.in_proj, out=proj, ws=self.ws)
+        K.wq_gemm(x, g.in_ba, out=ba, ws=self.ws)
         C = (2 * g.hk + g.hv) * 128
         mix, out = self.gdn_mix[t0:t1], self.gdn_out[t0:t1]
         K.gdn_conv(proj, g.conv_w, self.gdn_conv_state[li], b.segments, mix)
         z = proj[:, C:C + g.hv * 128]
-        ba = proj[:, C + g.hv * 128:]
         K.gdn_delta(mix, z, ba, g.a_log, g.dt_bias, g.norm_w, self.gdn_state[li], b.segments, out, g.hk, g.hv,
                     eps_norm=self.cfg.rms_eps)
         return out
@@ -333,7 +337,7 @@ class DecoderRunner:
                       residual=h if pending is not None else None, zero_centered=cfg.zero_centered_norm)
             if lw.gdn is not None:
                 mixed, o_w = self._gdn_mixer(li, lw.gdn, x, b, t0, t1), lw.gdn.out
-                n += 4
+                n += 5
             else:
                 K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
                 K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,

@@ -68,3 +68,44 @@ def test_quantization_config_parsing_variants():
     assert (c.method, c.bits, c.group_size) == ("cubic", 4, 64)
     with pytest.raises(ValueError):
         quant_spec_from_hf({"quant_method": "bitsandbytes"})
+
+
+@pytest.mark.parametrize("method,bits,group", [("cubic", 4, 128), ("awq", 4, 128), ("fp8_block", 8, 128), ("none", 16, 0)])
+def test_hybrid_checkpoint_row_mapping(tmp_path, method, bits, group):
+    """Gated DeltaNet layers: the checkpoint's per-key-head grouping of in_proj_qkvz / in_proj_ba rows and the
+    [q_h | gate_h] rows of the gated query projection map to the kernels' section layout, also per TP rank."""
+    cfg = ModelConfig(name="hyb", family="qwen3_5", num_layers=4, hidden_size=256, num_q_heads=4, num_kv_heads=2, head_dim=128,
+                      intermediate_size=512, vocab_size=512, rotary_dim=64, qk_norm=True, zero_centered_norm=True,
+                      gdn_interval=4, gdn_k_heads=2, gdn_v_heads=4, attn_output_gate=True, quant=QuantSpec(method, bits, group))
+    path = C.write_random_checkpoint(tmp_path / method, cfg, seed=2)
+    ck = C.admit_checkpoint(path)
+    assert ck.cfg.is_hybrid and ck.cfg.gdn_k_heads == 2 and ck.cfg.attn_output_gate and ck.cfg.rotary_dim == 64
+    H, r = 256, 2
+    qkvz = C._dense_of(method, ck.payload("model.layers.0.linear_attn.in_proj_qkvz"), (2 * 2 * 128 + 2 * 4 * 128, H), cfg.quant)
+    g = qkvz.view(2, (2 + 2 * r) * 128, H)                     # [key head, q | k | v x r | z x r, H]
+    sect = lambda lo, n, heads: torch.cat([g[h, lo:lo + n] for h in heads])
+    ba = ck.store.get("model.layers.0.linear_attn.in_proj_ba.weight").float().view(2, 2, r, H)
+    conv = ck.store.get("model.layers.0.linear_attn.conv1d.weight").float().reshape(-1, 4)
+    for tp, rank in ((1, 0), (2, 1)):
+        w = C.load_decoder_weights(ck, "cpu", tp_rank=rank, tp_size=tp)
+        heads = range(rank * 2 // tp, (rank + 1) * 2 // tp)
+        gd = w.layers[0].gdn
+        assert (gd.hk, gd.hv) == (2 // tp, 4 // tp) and w.layers[0].qkv is None and w.layers[3].gdn is None
+        want = torch.cat([sect(0, 128, heads), sect(128, 128, heads), sect(256, r * 128, heads), sect(256 + r * 128, r * 128, heads)])
+        got = wq_pack.unpack_to_dense(gd.in_proj)[:want.shape[0]]
+        assert ((got - want).norm() / want.norm()).item() < 6e-3
+        want_ba = torch.cat([torch.cat([ba[h, 0] for h in heads]), torch.cat([ba[h, 1] for h in heads])])
+        assert torch.allclose(wq_pack.unpack_to_dense(gd.in_ba).float(), want_ba.to(torch.bfloat16).float())
+        qk = 2 * 128
+        idx = torch.cat([torch.arange(h * 128, (h + 1) * 128) for h in heads])
+        vidx = torch.cat([torch.arange(h * r * 128, (h + 1) * r * 128) for h in heads])
+        assert torch.equal(gd.conv_w, torch.cat([conv[idx], conv[qk + idx], conv[2 * qk + vidx]]))
+        assert gd.a_log.shape == (4 // tp,) and gd.norm_w.shape == (128,)
+        # the gated attention layer: q rows of every head, then k, v; the gate rows in their own matrix
+        qp = C._dense_of(method, ck.payload("model.layers.3.self_attn.q_proj"), (2 * 4 * 128, H), cfg.quant).view(4, 2, 128, H)
+        hq = range(rank * 4 // tp, (rank + 1) * 4 // tp)
+        lw = w.layers[3]
+        got_q = wq_pack.unpack_to_dense(lw.qkv)[:len(hq) * 128]
+        assert ((got_q - torch.cat([qp[h, 0] for h in hq])).norm() / got_q.norm()).item() < 6e-3
+        got_g = wq_pack.unpack_to_dense(lw.attn_gate)[:len(hq) * 128]
+        assert ((got_g - torch.cat([qp[h, 1] for h in hq])).norm() / got_g.norm()).item() < 6e-3

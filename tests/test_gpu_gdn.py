@@ -139,7 +139,8 @@ def test_hybrid_layers_match_fp32_reference():
         proj = (xn.float() @ dense(g.in_proj).t()).to(bf)
         C = (2 * g.hk + g.hv) * 128
         mix, _ = eager.gdn_conv(proj[:, :C], g.conv_w, None)
-        out, _ = eager.gdn_delta(mix, proj[:, C:C + g.hv * 128], proj[:, C + g.hv * 128:], g.a_log, g.dt_bias, g.norm_w,
+        ba = (xn.float() @ dense(g.in_ba).t()).to(bf)
+        out, _ = eager.gdn_delta(mix, proj[:, C:C + g.hv * 128], ba, g.a_log, g.dt_bias, g.norm_w,
                                  None, g.hk, g.hv, eps_norm=cfg.rms_eps)
         x = (x + out.float() @ dense(g.out).t()).to(bf).float()
         xn = eager.rmsnorm(x.to(bf), lw.ln2.cpu(), cfg.rms_eps, zero_centered=True)
