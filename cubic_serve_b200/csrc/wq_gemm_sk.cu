@@ -17,10 +17,10 @@
 // Inside a CTA the rings are decoupled and the accumulator is double buffered:
 //   warp 0      activation tiles (and bf16 weight tiles) by TMA into the AX ring          -> full
 //   warp 2      packed codes + metadata by bulk copy into the deeper C ring               -> c_full
-//   warps 7-22  decode, two groups of 8 warps that take alternate k-blocks: wait c_full, decode 32
-//               weights per thread in registers (one 16-byte code load, four 16-byte tile stores),
+//   warps 7-22  decode, four groups of 4 warps, group g takes every fourth k-block: wait c_full, decode 64
+//               weights per thread in registers (two 16-byte code loads, eight 16-byte tile stores),
 //               wait for the AX slot to be free, store the swizzled bf16 tile             -> full, c_empty
-//               (per-k-block costs -- waits, fence, arrive, metadata -- are paid by 8 warps, not 16)
+//               (per-k-block costs -- waits, fence, arrive, metadata -- are paid by 4 warps, not 16)
 //   warp 1      MMA: wait full, 4 x tcgen05.mma into accumulator (segment & 1),
 //               commit -> ax_empty; after a segment's last k-block commit -> acc_full
 //   warps 3-6   epilogue: wait acc_full, tcgen05.ld, write bf16 output (or the fp32 partial),
@@ -34,7 +34,7 @@
 namespace cb {
 
 static constexpr int kSkDecodeWarps = 16;
-static constexpr int kSkDecodeGroups = 2;       // group g decodes the k-blocks with (index & 1) == g
+static constexpr int kSkDecodeGroups = 4;       // group g decodes the k-blocks with (index & 3) == g
 static constexpr int kSkGroupWarps = kSkDecodeWarps / kSkDecodeGroups;
 static constexpr int kSkEpiScratchBytes = 4 * 16 * 32 * 4;   // per epilogue warp: 16 rows x 32 features fp32
 static constexpr int kSkEpiWarps = 4;
@@ -53,10 +53,10 @@ struct SkSegment {
 
 struct __align__(8) SkCtl {
   uint64_t full[kSkMaxAx];       // activation (and bf16 weight) tile landed (transaction bytes + the producer's
-                                 // arrival) AND decoded weight tile stored by the 8 warps of a group (8 arrivals)
+                                 // arrival) AND decoded weight tile stored by the 4 warps of a group (4 arrivals)
   uint64_t ax_empty[kSkMaxAx];   // the MMAs that read the slot have retired            (tcgen05.commit)
   uint64_t c_full[kSkMaxC];      // packed codes + metadata landed                      (transaction bytes)
-  uint64_t c_empty[kSkMaxC];     // the group's warps hold the codes in registers       (8 arrivals)
+  uint64_t c_empty[kSkMaxC];     // the group's warps hold the codes in registers       (4 arrivals)
   uint64_t acc_full[2];          // accumulator of a segment complete                   (tcgen05.commit)
   uint64_t acc_empty[2];         // epilogue warps have read the accumulator            (4 arrivals)
   uint64_t tail_full;            // accumulator of the CTA's LAST segment complete; completes once, so waiters
@@ -155,8 +155,9 @@ struct SkRing {
   __device__ __forceinline__ void advance(int depth) {
     if (++s == depth) { s = 0; ++wraps; }
   }
-  __device__ __forceinline__ void advance_by(int n, int depth) {   // n <= depth
+  __device__ __forceinline__ void advance_by(int n, int depth) {   // n <= 4, depth >= 2
     s += n;
+    if (s >= depth) { s -= depth; ++wraps; }
     if (s >= depth) { s -= depth; ++wraps; }
   }
 };
@@ -615,14 +616,14 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (warp >= kSkFirstDecodeWarp) {
       // ---------------------------------------------- decode
       const int g = (warp - kSkFirstDecodeWarp) / kSkGroupWarps;                   // this warp's group
-      const int dq = threadIdx.x - kSkFirstDecodeWarp * 32 - g * kSkGroupWarps * 32;   // 0..255 inside the group
-      const int r = dq & 127;           // row of the weight tile
-      const int h = dq >> 7;            // 32-column half of the k-block (one 16-byte code chunk, one metadata sub-block)
-      const uint32_t code_off = static_cast<uint32_t>((h * 128 + r) * 16);
+      const int r = threadIdx.x - kSkFirstDecodeWarp * 32 - g * kSkGroupWarps * 32;    // row of the weight tile, 0..127
+      // A thread decodes one whole 128-byte row of the k-block (64 weights: two 16-byte code chunks, the halves
+      // h = 0, 1), so that what is paid per k-block and thread (barrier waits and arrivals, ring arithmetic, the
+      // proxy fence) is paid once per 64 weights; a profile of the two-group form (32 weights per thread) showed
+      // ~270 instructions per thread and k-block against ~110 of decode arithmetic.
+      const uint32_t code_off = static_cast<uint32_t>(r * 16);
       const uint32_t a_off = x_bytes + static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
-      uint32_t chunk_off[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) chunk_off[j] = static_cast<uint32_t>(((h * 4 + j) ^ (r & 7)) << 4);
+      const uint32_t sw = static_cast<uint32_t>(r & 7);
       SkRing rc, ra;
       int i_global = 0;
       int seg_idx = 0;
@@ -631,62 +632,79 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       while (it.next(p, cta, grid, seg)) {
         const bool tail = !it.has_more(p);
         if (FMT != kFmtBf16 && ok) {
-          // this group's k-blocks of the segment are every other one; the rings are stepped over the other
-          // group's k-blocks arithmetically instead of by empty loop iterations
+          // this group's k-blocks are every fourth one; the rings are stepped over the other groups' k-blocks
+          // arithmetically instead of by empty loop iterations
           const int len = seg.kb_hi - seg.kb_lo;
-          const int skip = ((i_global & 1) != g) ? 1 : 0;
-          rc.advance_by(skip, NC);
-          ra.advance_by(skip, S);
-          for (int jj = skip; jj < len; jj += 2) {
+          const int skip = (g - i_global) & (kSkDecodeGroups - 1);
+          rc.advance_by(skip < len ? skip : len, NC);
+          ra.advance_by(skip < len ? skip : len, S);
+          for (int jj = skip; jj < len; jj += kSkDecodeGroups) {
             const int ig = i_global + jj;
             if (!mbar_wait_park(smem_u32(&ctl->c_full[rc.s]), rc.wraps & 1u, abort_flag)) { ok = false; break; }
-            if (trace && dq == 0 && ig < 64) trace[ig * 8 + 2] = clock64();
+            if (trace && r == 0 && ig < 64) trace[ig * 8 + 2] = clock64();
             const uint8_t* pk = c_ring + static_cast<size_t>(rc.s) * kSkCStageBytes;
-            const uint4 words = *reinterpret_cast<const uint4*>(pk + code_off);
+            const uint4 w0 = *reinterpret_cast<const uint4*>(pk + code_off);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(pk + code_off + 128 * 16);
             const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
             // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
-            uint32_t c0, c1, c2;
+            uint32_t m0, m1;
             if (FMT == kFmtCubic4) {
-              const uint32_t ab = meta[r], cz = meta[128 + r];
-              c0 = bf2_dup(ab);        // A = s * a / 7
-              c1 = bf2_dup_hi(ab);  // B = s * b / 49
-              c2 = bf2_dup(cz);        // C = s * (1 - a - b) / 343
+              m0 = meta[r];            // {A = s a / 7, B = s b / 49}: one scale group covers the whole k-block
+              m1 = meta[128 + r];      // {C = s (1 - a - b) / 343, -}
             } else {
-              const uint32_t so = meta[h * 128 + r];
-              c0 = bf2_dup(so);
-              c1 = bf2_dup_hi(so);
-              c2 = 0;
+              m0 = meta[r];            // {scale, offset} (or the two 16-column block scales) of half 0
+              m1 = meta[128 + r];      // ... of half 1
             }
             // the codes and metadata are in registers: hand the slot back to the copy warp right away
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->c_empty[rc.s]));
-            uint32_t o[4][4];
-            if (FMT == kFmtNvfp4) {
-              // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
-              decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
-              decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
-              decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
-              decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
-            } else {
-              decode8<FMT>(words.x, c0, c1, c2, o[0]);
-              decode8<FMT>(words.y, c0, c1, c2, o[1]);
-              decode8<FMT>(words.z, c0, c1, c2, o[2]);
-              decode8<FMT>(words.w, c0, c1, c2, o[3]);
-            }
-            // the arithmetic above ran while the slot may still be read by MMAs; only the stores wait for it
-            if (ra.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[ra.s]), (ra.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
-            uint8_t* arow = smem + static_cast<size_t>(ra.s) * ax_bytes + a_off;
+            uint8_t* arow = nullptr;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(arow + chunk_off[j]) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            for (int h = 0; h < 2; ++h) {
+              const uint4 words = h ? w1 : w0;
+              uint32_t c0, c1, c2;
+              if (FMT == kFmtCubic4) {
+                c0 = bf2_dup(m0);
+                c1 = bf2_dup_hi(m0);
+                c2 = bf2_dup(m1);
+              } else {
+                const uint32_t so = h ? m1 : m0;
+                c0 = bf2_dup(so);
+                c1 = bf2_dup_hi(so);
+                c2 = 0;
+              }
+              uint32_t o[4][4];
+              if (FMT == kFmtNvfp4) {
+                // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
+                decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
+                decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
+                decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
+                decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+              } else {
+                decode8<FMT>(words.x, c0, c1, c2, o[0]);
+                decode8<FMT>(words.y, c0, c1, c2, o[1]);
+                decode8<FMT>(words.z, c0, c1, c2, o[2]);
+                decode8<FMT>(words.w, c0, c1, c2, o[3]);
+              }
+              if (h == 0) {
+                // the arithmetic above ran while the slot may still be read by MMAs; only the stores wait for it
+                if (ra.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[ra.s]), (ra.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
+                arow = smem + static_cast<size_t>(ra.s) * ax_bytes + a_off;
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4*>(arow + (((static_cast<uint32_t>(h * 4 + j)) ^ sw) << 4)) =
+                    make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            }
+            if (!ok) break;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
               if (PAIR && rank != 0) mbar_arrive_cluster(cluster_map(smem_u32(&ctl->full[ra.s]), 0));
               else mbar_arrive(smem_u32(&ctl->full[ra.s]));
             }
-            if (trace && dq == 0 && ig < 64) trace[ig * 8 + 3] = clock64();
-            const int step = len - jj < 2 ? len - jj : 2;
+            if (trace && r == 0 && ig < 64) trace[ig * 8 + 3] = clock64();
+            const int step = len - jj < kSkDecodeGroups ? len - jj : kSkDecodeGroups;
             rc.advance_by(step, NC);
             ra.advance_by(step, S);
           }
