@@ -268,6 +268,15 @@ __device__ __forceinline__ bool mbar_wait_park_cluster(uint32_t bar, uint32_t pa
     }
   }
 }
+// 16 bytes from the shared memory of a CTA of the cluster (address from cluster_map)
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 // 2-D tiled TMA load into THIS CTA's shared memory whose completion bytes go to a barrier of either CTA of the pair
 // (cluster address).  No multicast: every CTA fetches its own box.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t cluster_bar) {

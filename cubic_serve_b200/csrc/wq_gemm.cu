@@ -91,7 +91,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
-      mbar_init(smem_u32(&ctl->ready[s]), kNumDequantWarps / 2);
+      mbar_init(smem_u32(&ctl->ready[s]), kNumDequantWarps / 4);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     mbar_init(smem_u32(&ctl->acc_full), 1);
@@ -203,63 +203,67 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------- dequant + epilogue
     const int dq = threadIdx.x - 64;  // 0..511
     if (FMT != kFmtBf16) {
-      // Two groups of eight warps take alternate k-blocks; a thread decodes 32 weights (one 16-byte code load,
-      // four 16-byte tile stores), so the per-k-block costs -- barrier wait, metadata, fence, arrive -- are
-      // paid by 8 warps instead of 16 (the decode is instruction-issue bound: see the stream-K profile).
-      const int grp = dq >> 8;          // decode group
-      const int dg = dq & 255;
-      const int r = dg & 127;           // row of the weight tile
-      const int h = dg >> 7;            // 32-column half of the k-block (one metadata sub-block)
-      const uint32_t code_off = static_cast<uint32_t>((h * 128 + r) * 16);
+      // Four groups of four warps, group g takes every fourth k-block; a thread decodes one whole 128-byte row of
+      // the k-block (64 weights: two 16-byte code loads, eight 16-byte tile stores), so the per-k-block costs --
+      // barrier wait, metadata, fence, arrive, ring arithmetic -- are paid once per 64 weights by 4 warps (the
+      // decode is instruction-issue bound: see the stream-K profile).
+      const int grp = dq >> 7;          // decode group
+      const int r = dq & 127;           // row of the weight tile
+      const uint32_t code_off = static_cast<uint32_t>(r * 16);
       const uint32_t a_off = x_bytes + static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
-      uint32_t chunk_off[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) chunk_off[j] = static_cast<uint32_t>(((h * 4 + j) ^ (r & 7)) << 4);
-      int s = grp;                      // S >= 2
-      uint32_t ph = 0;
-      for (int i = grp; i < iters; i += 2) {
+      const uint32_t sw = static_cast<uint32_t>(r & 7);
+      int s = grp % S;                  // k-block i lives in stage i % S, phase (i / S) & 1
+      uint32_t ph = static_cast<uint32_t>(grp / S) & 1u;
+      for (int i = grp; i < iters; i += 4) {
         if (!mbar_wait_park(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
         if (trace && dq == 0) trace[i * 8 + 2] = clock64();
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint8_t* pk = st + x_bytes + kATileBytes;
-        const uint4 words = *reinterpret_cast<const uint4*>(pk + code_off);
+        const uint4 w0 = *reinterpret_cast<const uint4*>(pk + code_off);
+        const uint4 w1 = *reinterpret_cast<const uint4*>(pk + code_off + 128 * 16);
         const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
-        // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
-        uint32_t c0, c1, c2;
-        if (FMT == kFmtCubic4) {
-          const uint32_t ab = meta[r], cz = meta[128 + r];
-          c0 = bf2_dup(ab);        // A = s * a / 7
-          c1 = bf2_dup_hi(ab);  // B = s * b / 49
-          c2 = bf2_dup(cz);        // C = s * (1 - a - b) / 343
-        } else {
-          const uint32_t so = meta[h * 128 + r];
-          c0 = bf2_dup(so);
-          c1 = bf2_dup_hi(so);
-          c2 = 0;
-        }
-        uint32_t o[4][4];
-        if (FMT == kFmtNvfp4) {
-          // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
-          decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
-          decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
-          decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
-          decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
-        } else {
-          decode8<FMT>(words.x, c0, c1, c2, o[0]);
-          decode8<FMT>(words.y, c0, c1, c2, o[1]);
-          decode8<FMT>(words.z, c0, c1, c2, o[2]);
-          decode8<FMT>(words.w, c0, c1, c2, o[3]);
-        }
+        // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py): Cubic {A, B} and {C, -} of the
+        // row's scale group; the other formats {scale, offset} (or two block scales) of each 32-column half
+        const uint32_t m0 = meta[r], m1 = meta[128 + r];
         uint8_t* arow = st + a_off;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(arow + chunk_off[j]) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+        for (int h = 0; h < 2; ++h) {
+          const uint4 words = h ? w1 : w0;
+          uint32_t c0, c1, c2;
+          if (FMT == kFmtCubic4) {
+            c0 = bf2_dup(m0);        // A = s * a / 7
+            c1 = bf2_dup_hi(m0);     // B = s * b / 49
+            c2 = bf2_dup(m1);        // C = s * (1 - a - b) / 343
+          } else {
+            const uint32_t so = h ? m1 : m0;
+            c0 = bf2_dup(so);
+            c1 = bf2_dup_hi(so);
+            c2 = 0;
+          }
+          uint32_t o[4][4];
+          if (FMT == kFmtNvfp4) {
+            // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
+            decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
+            decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
+            decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
+            decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+          } else {
+            decode8<FMT>(words.x, c0, c1, c2, o[0]);
+            decode8<FMT>(words.y, c0, c1, c2, o[1]);
+            decode8<FMT>(words.z, c0, c1, c2, o[2]);
+            decode8<FMT>(words.w, c0, c1, c2, o[3]);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(arow + ((static_cast<uint32_t>(h * 4 + j) ^ sw) << 4)) =
+                make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->ready[s]));
         if (trace && dq == 0) trace[i * 8 + 3] = clock64();
-        s += 2;
-        if (s >= S) { s -= S; ph ^= 1u; }
+        s += 4;
+        while (s >= S) { s -= S; ph ^= 1u; }
       }
     }
     // epilogue: TMEM lane = output feature, column = batch row
@@ -344,6 +348,17 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
               if (n0 + j < p.N) store_out(m, n0 + j, v[j]);
           }
         }
+      } else if (p.cluster_splitk) {
+        // the tile's K splits are one cluster: the raw fp32 partial is staged in this CTA's (now idle) stage memory
+        // and summed by the cluster below, after all threads of all its CTAs have met
+        float* stg = reinterpret_cast<float*>(smem);
+        for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
+          uint32_t acc[16];
+          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
+        }
       } else {
         float* ws = p.workspace +
                     ((static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits + split) * (static_cast<size_t>(p.mb) * kTileN);
@@ -358,7 +373,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
     }
     if (trace && dq == 0) trace[8 + 7] = clock64();
-    if (p.splits > 1) {
+    if (p.splits > 1 && !p.cluster_splitk) {
       // last-arriving split sums all partials in split order (deterministic)
       __threadfence();
       asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
@@ -436,6 +451,75 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   }
 
+  if (p.cluster_splitk) {
+    // Split-K through distributed shared memory.  Every thread of every CTA of the cluster meets here (all roles fall
+    // through to this point, also after a failed wait); then CTA `rank` sums, in split order, the rows
+    // [rank * chunk, (rank + 1) * chunk) of the `splits` partial tiles, read in place from the peers' shared memory,
+    // and writes them; nobody leaves before its peers have finished reading.
+    cluster_sync_all();
+    if (warp >= 2 && !*abort_flag) {
+      const int dq = threadIdx.x - 64;
+      const int rank = static_cast<int>(cluster_ctarank());
+      const int rows_here = min(p.mb, m_end - m0);
+      const int chunk = (rows_here + p.splits - 1) / p.splits;
+      const int row_lo = rank * chunk, row_hi = min(rows_here, row_lo + chunk);
+      const uint32_t stg0 = smem_u32(smem);
+      const int n_base = n_tile * kTileN;
+      if (p.swiglu) {
+        for (int idx = dq; idx < (row_hi - row_lo) * 16; idx += kNumDequantWarps * 32) {
+          const int mm = row_lo + (idx >> 4), j0 = (idx & 15) * 4;
+          const uint32_t off = static_cast<uint32_t>(mm * kTileN + act_gate_col(j0)) * 4u;
+          float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const uint32_t base = cluster_map(stg0, static_cast<uint32_t>(sp)) + off;
+            const float4 a = ld_cluster_f4(base), b = ld_cluster_f4(base + 64u);
+            g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+            u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+          }
+          g.x *= p.alpha; g.y *= p.alpha; g.z *= p.alpha; g.w *= p.alpha;
+          u.x *= p.alpha; u.y *= p.alpha; u.z *= p.alpha; u.w *= p.alpha;
+          store_act4(p, m0 + mm, n_tile, j0, g, u);
+        }
+      } else {
+        for (int idx = dq; idx < (row_hi - row_lo) * (kTileN / 4); idx += kNumDequantWarps * 32) {
+          const int mm = row_lo + (idx >> 5), c4 = (idx & 31) * 4;
+          if (n_base + c4 >= p.N) continue;
+          const uint32_t off = static_cast<uint32_t>(mm * kTileN + c4) * 4u;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp = 0; sp < p.splits; ++sp) {
+            const float4 v = ld_cluster_f4(cluster_map(stg0, static_cast<uint32_t>(sp)) + off);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          const float o4[4] = {acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha};
+          const size_t o = static_cast<size_t>(m0 + mm) * p.ldy + n_base + c4;
+          if (n_base + c4 + 3 < p.N && (p.ldy & 3) == 0) {
+            float r4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (p.residual) {
+              const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + o);
+              const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+              const float2 a0 = __bfloat1622float2(rp[0]), a1 = __bfloat1622float2(rp[1]);
+              r4[0] = a0.x; r4[1] = a0.y; r4[2] = a1.x; r4[3] = a1.y;
+            }
+            uint2 ov;
+            ov.x = pack_bf16x2(o4[0] + r4[0], o4[1] + r4[1]);
+            ov.y = pack_bf16x2(o4[2] + r4[2], o4[3] + r4[3]);
+            *reinterpret_cast<uint2*>(p.y + o) = ov;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n_base + c4 + j < p.N) {
+                float w = o4[j];
+                if (p.residual) w += __bfloat162float(p.residual[o + j]);
+                p.y[o + j] = __float2bfloat16(w);
+              }
+            }
+          }
+        }
+      }
+    }
+    cluster_sync_all();
+  }
+
   if ((p.tp.mode & kTpScatterPush) && warp >= 2) {
     // every partial row of this CTA is on its way: make the stores visible system-wide,
     // then raise the arrival counter of each owner whose rows this tile touched
@@ -471,13 +555,40 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
 }
 
 template <int FMT>
-static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemmParams& p, dim3 grid, size_t smem,
+static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, dim3 grid, size_t smem,
                       cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(wq_gemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
+  }
+  if (p.cluster_splitk) {
+    // the K splits of a tile (grid.y) as one cluster; only if every cluster of the launch can be resident at once
+    // (a cluster's CTAs share a GPC), otherwise the launch would run in waves: fall back to the workspace path
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = grid.y;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int resident[9] = {0};      // by cluster size; the shared-memory footprint is one CTA per SM in every case
+    int& r = resident[grid.y];
+    if (r == 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, wq_gemm_kernel<FMT>, &cfg) != cudaSuccess) n = 0;
+      r = n > 0 ? n : -1;
+    }
+    if (r >= static_cast<int>(grid.x * grid.z))
+      return static_cast<int>(cudaLaunchKernelEx(&cfg, wq_gemm_kernel<FMT>, tx, tw, p));
+    p.cluster_splitk = 0;
+    if (!p.workspace || !p.counters) return -13;
   }
   wq_gemm_kernel<FMT><<<grid, kThreads, smem, stream>>>(tx, tw, p);
   return static_cast<int>(cudaGetLastError());
@@ -545,6 +656,10 @@ int cb_wq_gemm_sk(int fmt, const void* x, int ldx, const void* codes, const void
                   const void* residual, float alpha, int M, int N, int K, int group_k, int min_units, void* workspace,
                   long long workspace_bytes, void* counters, void* status, void* stream, const CbTpLink* link);
 
+// 1 (default): the K splits of a tile of the per-tile kernel form a cluster and reduce through distributed shared
+// memory; 0: fp32 partial tiles in the workspace, summed by the last split to arrive.
+static int g_cluster_splitk = 1;
+
 // Persistent kernel on CTA pairs (cta_group::2): 0 never; 1 (default) eligible launches with more than 256 batch
 // rows (measured: 5-20 % faster than one CTA per SM from 512 rows up, 2-8 % slower at exactly 256, where the decode
 // warps and not the activation traffic set the pace); 2 every eligible launch.
@@ -610,7 +725,11 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.k_blocks = K / kBlockK;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
-  if (splits > 1 && (!workspace || !counters)) return -13;
+  // K splits of the per-tile kernel meet in a thread-block cluster (distributed shared memory) unless the tile's rows
+  // are pushed to other ranks (their arrival counters are raised once per tile by the last split)
+  p.cluster_splitk = (splits > 1 && splits <= 8 && g_cluster_splitk && !stream_k && !g_grouped.tiles &&
+                      !(p.tp.mode & kTpScatterPush)) ? 1 : 0;
+  if (splits > 1 && !p.cluster_splitk && (!workspace || !counters)) return -13;
   p.splits = splits;
   p.meta_k_blocks = (fmt == kFmtCubic4) ? group_k / kBlockK : 1;
   p.meta_blocks = (p.k_blocks + p.meta_k_blocks - 1) / p.meta_k_blocks;
@@ -689,6 +808,9 @@ void cb_wq_gemm_grouped_mode(int persistent) { g_grouped_persistent = persistent
 // 0: one CTA per SM works alone; 1 (default): CTA pairs for eligible launches of more than 256 batch rows; 2: for
 // every eligible launch.
 void cb_wq_gemm_pair_mode(int pairs) { g_pair_mode = pairs; }
+
+// 1 (default): split-K of the per-tile kernel through a cluster's distributed shared memory; 0: through the workspace.
+void cb_wq_gemm_cluster_splitk(int on) { g_cluster_splitk = on; }
 
 // CTA pairs of the persistent kernel that can be resident at once on the current device (0: cannot be launched).
 int cb_wq_gemm_resident_pairs(int fmt) { return cb::streamk_resident_pairs(fmt); }

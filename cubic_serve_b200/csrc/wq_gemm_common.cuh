@@ -74,6 +74,9 @@ struct WqGemmParams {
   // persistent kernel on CTA pairs (cta_group::2): the schedule's tile is a PAIR of adjacent weight tiles, CTA rank r of
   // the pair owns weight tile 2 * pair_tile + r and loads batch rows [m0 + r * mb / 2, + mb / 2) of the activation tile
   int pair;
+  // per-tile kernel with K splits: the `splits` CTAs of a tile form a thread-block cluster and sum their fp32 partial
+  // tiles through distributed shared memory (no workspace, no fences, no arrival counter)
+  int cluster_splitk;
   // persistent stream-K kernel only (wq_gemm_sk.cu)
   int n_tiles, tiles;       // tile = m_tile * n_tiles + n_tile
   int sk_tiles, sk_ctas;    // tiles [0, sk_tiles) are dealt by k-block to CTAs [0, sk_ctas); the rest are whole

@@ -459,3 +459,30 @@ def test_hadamard_rotation_kernel_and_rotated_cache():
     assert _rel(outs[8, True], ref) < 3e-2
     err_plain, err_rot = _rel(outs[4, False], ref), _rel(outs[4, True], ref)
     assert err_rot < err_plain and err_rot < 0.2, (err_plain, err_rot)
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(256, 512, 4096, 4), (40, 384, 1024, 2), (300, 256, 2048, 8), (17, 200, 1024, 3)])
+def test_wq_gemm_split_k_through_cluster_shared_memory(m, n, k, splits):
+    """The K splits of a tile as one thread-block cluster (partials summed through distributed shared memory) give
+    bit-identical results to the workspace path (same summation order), with residual and fused activation."""
+    from cubic_serve_b200.ops import native
+    K = _k()
+    pw, dense = _cubic_weight(n, k, seed=m + n)
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16).to(DEV)
+    res = torch.randn(m, n, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV)
+    lib = native.lib()
+    outs = {}
+    try:
+        for mode in (1, 0):
+            lib.cb_wq_gemm_cluster_splitk(mode)
+            y = K.wq_gemm(x, pw.to(DEV), splits=splits)
+            yr = K.wq_gemm(x, pw.to(DEV), residual=res, splits=splits)
+            act = K.wq_gemm_act(x, wq_pack.swiglu_interleave(pw).to(DEV), splits=splits) if n % 32 == 0 else y
+            torch.cuda.synchronize()
+            K.workspace(y.device).check_status()
+            outs[mode] = (y.clone(), yr.clone(), act.clone())
+    finally:
+        lib.cb_wq_gemm_cluster_splitk(1)
+    assert _rel(outs[1][0].cpu(), x.float().cpu() @ dense.t()) < 1e-2
+    for a, b in zip(outs[1], outs[0]):
+        assert torch.equal(a, b)
