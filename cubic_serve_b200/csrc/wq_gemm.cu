@@ -554,6 +554,33 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     atomicExch(p.status, static_cast<uint32_t>(ctl->abort_flag == 2 ? kErrFlagTimeout : kErrBarrierTimeout));
 }
 
+// Clusters of `size` CTAs of the per-tile kernel (one CTA per SM) that can be resident at once; a cluster's CTAs
+// share a GPC, so this is less than SMs / size when GPCs do not hold a multiple of `size` usable SMs.
+template <int FMT>
+static int resident_clusters(int size) {
+  static int cached[9] = {0};
+  if (size < 1 || size > 8) return 0;
+  if (cached[size] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, static_cast<unsigned>(size), 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = 232448 - 1024;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(size);
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaFuncSetAttribute(wq_gemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, wq_gemm_kernel<FMT>, &cfg) != cudaSuccess)
+      n = 0;
+    cached[size] = n > 0 ? n : -1;
+  }
+  return cached[size] > 0 ? cached[size] : 0;
+}
+
 template <int FMT>
 static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, dim3 grid, size_t smem,
                       cudaStream_t stream) {
@@ -578,14 +605,7 @@ static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    static int resident[9] = {0};      // by cluster size; the shared-memory footprint is one CTA per SM in every case
-    int& r = resident[grid.y];
-    if (r == 0) {
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, wq_gemm_kernel<FMT>, &cfg) != cudaSuccess) n = 0;
-      r = n > 0 ? n : -1;
-    }
-    if (r >= static_cast<int>(grid.x * grid.z))
+    if (resident_clusters<FMT>(static_cast<int>(grid.y)) >= static_cast<int>(grid.x * grid.z))
       return static_cast<int>(cudaLaunchKernelEx(&cfg, wq_gemm_kernel<FMT>, tx, tw, p));
     p.cluster_splitk = 0;
     if (!p.workspace || !p.counters) return -13;
@@ -811,6 +831,17 @@ void cb_wq_gemm_pair_mode(int pairs) { g_pair_mode = pairs; }
 
 // 1 (default): split-K of the per-tile kernel through a cluster's distributed shared memory; 0: through the workspace.
 void cb_wq_gemm_cluster_splitk(int on) { g_cluster_splitk = on; }
+
+// Clusters of `size` K splits of the per-tile kernel that fit on the current device at once (0: unknown / none).
+int cb_wq_gemm_resident_clusters(int fmt, int size) {
+  if (!g_cluster_splitk) return 0;
+  switch (fmt) {
+    case cb::kFmtCubic4: return cb::resident_clusters<cb::kFmtCubic4>(size);
+    case cb::kFmtAffine4: return cb::resident_clusters<cb::kFmtAffine4>(size);
+    case cb::kFmtNvfp4: return cb::resident_clusters<cb::kFmtNvfp4>(size);
+    default: return cb::resident_clusters<cb::kFmtBf16>(size);
+  }
+}
 
 // CTA pairs of the persistent kernel that can be resident at once on the current device (0: cannot be launched).
 int cb_wq_gemm_resident_pairs(int fmt) { return cb::streamk_resident_pairs(fmt); }

@@ -71,11 +71,29 @@ def sm_count(device: torch.device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
-def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
+_CLUSTER_CAPACITY_GUESS = {2: 72, 3: 40, 4: 32, 5: 24, 6: 16, 7: 16, 8: 16}      # 8 GPCs of 16-18 usable SMs
+_cluster_capacity: dict[tuple[int, int], int] = {}
+
+
+def resident_clusters(fmt: int, size: int) -> int:
+    """Clusters of ``size`` K splits of the per-tile GEMM that fit on the device at once (its CTAs share a GPC)."""
+    key = (fmt, size)
+    if key not in _cluster_capacity:
+        n = 0
+        if torch.cuda.is_available():
+            n = native.lib().cb_wq_gemm_resident_clusters(fmt, size)
+        _cluster_capacity[key] = n if n > 0 else _CLUSTER_CAPACITY_GUESS.get(size, 0)
+    return _cluster_capacity[key]
+
+
+def choose_splits(m: int, n: int, k: int, sms: int = 148, fmt: int = FMT_CUBIC4, cluster: bool = True) -> int:
     """Split-K factor: fill the SMs when the (n-tile x m-tile) grid is small.
 
-    Every split CTA writes an fp32 partial tile and the last one sums them (vectorised, from L2), so a split
-    pays off while each CTA still has >= 8 k-blocks of work.
+    The splits of a tile form a thread-block cluster and sum their partial tiles through distributed shared
+    memory; that only works when all clusters of the launch are resident at once, so the largest factor whose
+    clusters fit is taken (48 tiles: 2, because only ~40 clusters of 3 fit on 8 GPCs).  ``cluster`` False (rows
+    pushed to other ranks: partials go through the workspace, the last split sums them) keeps the plain rule.  A
+    split pays off while each CTA still has >= 8 k-blocks of work.
     """
     from .strategies import active
     g = active().gemm
@@ -85,7 +103,12 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148) -> int:
     k_blocks = k // 64
     if tiles * 2 > sms or k_blocks < 2 * g.split_k_min_blocks:
         return 1
-    return max(1, min(sms // tiles, k_blocks // g.split_k_min_blocks, g.split_k_max))
+    base = max(1, min(sms // tiles, k_blocks // g.split_k_min_blocks, g.split_k_max))
+    if cluster:
+        for s in range(min(base, 8), 1, -1):
+            if tiles <= resident_clusters(fmt, s):
+                return s
+    return base
 
 
 def use_stream_k(m: int, n: int, fmt: int, sms: int = 148, k: int = 4096) -> bool:
@@ -148,7 +171,7 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
         native.check(code, "cb_wq_gemm_sk")
         return out
     if splits is None:
-        splits = choose_splits(m, w.n, k)
+        splits = choose_splits(m, w.n, k, fmt=w.fmt, cluster=not push)
     if splits > 1:
         need = l.cb_wq_gemm_workspace_bytes(m, w.n, splits)
         if need > ws.gemm.numel():
@@ -185,7 +208,7 @@ def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = Non
         min_units = active().gemm.stream_k_min_units
     if not stream_k:
         if splits is None:
-            splits = choose_splits(m, w.n, k)
+            splits = choose_splits(m, w.n, k, fmt=w.fmt)
         if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
             splits = 1
     code = l.cb_wq_gemm_act(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta), out.data_ptr(),

@@ -162,6 +162,8 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_pair_mode.restype = None
     l.cb_wq_gemm_cluster_splitk.argtypes = [i]
     l.cb_wq_gemm_cluster_splitk.restype = None
+    l.cb_wq_gemm_resident_clusters.argtypes = [i, i]
+    l.cb_wq_gemm_resident_clusters.restype = i
     l.cb_wq_gemm_resident_pairs.argtypes = [i]
     l.cb_wq_gemm_resident_pairs.restype = i
     l.cb_moe_permute.argtypes = [vp, vp, i, i, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
