@@ -283,6 +283,27 @@ paged_attn_kernel(const AttnParams p) {
   const int pg_lo = split * pps;
   const int pg_hi = min(total_pages, pg_lo + pps);
 
+  // The first copies of this warp's page stream are issued before anything else: their DRAM latency then overlaps
+  // the query load and conversion below instead of following them (every CTA pays this start-up once).
+  const int* ptab = p.page_table + static_cast<size_t>(req) * p.max_pages;
+  const int first = pg_lo + warp;
+  const int my_pages = first < pg_hi ? (pg_hi - first + kAttnWarps - 1) / kAttnWarps : 0;
+  auto issue = [&](int i, int page) {
+    const int s = i % kAttnStages;
+    const uint8_t* src = p.cache + (static_cast<size_t>(page) * p.Hkv + kvh) * blob_bytes;
+    const uint32_t bar = smem_u32(&my_bars[s]);
+    mbar_expect_tx(bar, blob_bytes);
+    bulk_g2s(smem_u32(my_stages + s * stage_stride), src, blob_bytes, bar);
+  };
+  if (lane == 0) {
+    int pg[kAttnStages];
+#pragma unroll
+    for (int i = 0; i < kAttnStages; ++i) pg[i] = i < my_pages ? ptab[first + i * kAttnWarps] : 0;   // loads first ...
+#pragma unroll
+    for (int i = 0; i < kAttnStages; ++i)
+      if (i < my_pages) issue(i, pg[i]);                                                               // ... then copies
+  }
+
   const bool upper_rows = qcount * G > 8;     // uniform over the CTA: do MMA rows 8..15 hold a query?
   int limit[2];
   uint32_t qf[8][4];
@@ -316,26 +337,17 @@ paged_attn_kernel(const AttnParams p) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) st.o[n][c] = 0.f;
 
-  // ---- per-warp page stream: pages pg_lo + warp, + 4, ...
-  const int* ptab = p.page_table + static_cast<size_t>(req) * p.max_pages;
-  const int first = pg_lo + warp;
-  const int my_pages = first < pg_hi ? (pg_hi - first + kAttnWarps - 1) / kAttnWarps : 0;
-  auto issue = [&](int i) {
-    const int s = i % kAttnStages;
-    const int page = ptab[first + i * kAttnWarps];
-    const uint8_t* src = p.cache + (static_cast<size_t>(page) * p.Hkv + kvh) * blob_bytes;
-    const uint32_t bar = smem_u32(&my_bars[s]);
-    mbar_expect_tx(bar, blob_bytes);
-    bulk_g2s(smem_u32(my_stages + s * stage_stride), src, blob_bytes, bar);
-  };
-  if (lane == 0)
-    for (int i = 0; i < min(my_pages, kAttnStages); ++i) issue(i);
+  // ---- per-warp page stream (set up before the query load, see above): pages pg_lo + warp, + 4, ...
+  // The page id of the copy issued at the end of iteration i is loaded at the START of iteration i - 1, so that lane 0
+  // never sits on a page-table load between two pages.
+  int page_next = (lane == 0 && kAttnStages < my_pages) ? ptab[first + kAttnStages * kAttnWarps] : 0;
   bool ok = true;
   for (int i = 0; i < my_pages && ok; ++i) {
     const int s = i % kAttnStages;
     ok = mbar_wait_t<20>(smem_u32(&my_bars[s]), static_cast<uint32_t>(i / kAttnStages) & 1u, abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;
+    const int page_after = (lane == 0 && i + 1 + kAttnStages < my_pages) ? ptab[first + (i + 1 + kAttnStages) * kAttnWarps] : 0;
     if (upper_rows)
       process_page<KBITS, VBITS, true>(my_stages + s * stage_stride, p.lay, qf, st,
                                        (first + i * kAttnWarps) * kPageTokens, limit[0], limit[1], g, t4);
@@ -343,7 +355,8 @@ paged_attn_kernel(const AttnParams p) {
       process_page<KBITS, VBITS, false>(my_stages + s * stage_stride, p.lay, qf, st,
                                         (first + i * kAttnWarps) * kPageTokens, limit[0], limit[1], g, t4);
     __syncwarp();
-    if (lane == 0 && i + kAttnStages < my_pages) issue(i + kAttnStages);
+    if (lane == 0 && i + kAttnStages < my_pages) issue(i + kAttnStages, page_next);
+    page_next = page_after;
   }
   // if a wait gave up, copies may still be in flight: give them a bounded time to land
   if (!ok && lane == 0) {

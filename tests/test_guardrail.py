@@ -17,3 +17,39 @@ def test_compare_classes():
     assert compare_tensors(nan, o, b).klass is DifferenceClass.MISMATCH
     assert compare_tensors(o[:4], o, b).klass is DifferenceClass.MISMATCH
     assert poisoned_padding_preserved(o, o.clone()) and not poisoned_padding_preserved(o, far)
+
+
+def test_trace_record_and_replay(tmp_path):
+    """A recorded run replays token for token on a fresh engine (other prefill chunking, look-ahead launches on or
+    off); a changed model is reported with the request and position of the first different token."""
+    import numpy as np
+    from cubic_serve_b200.executor.eager_executor import EagerPagedExecutor
+    from cubic_serve_b200.guardrail.replay import TraceRecorder, load_trace, replay_trace
+    from cubic_serve_b200.models.config import toy_config
+    from cubic_serve_b200.models.reference import random_dense_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = toy_config()
+
+    def engine(seed=0, chunk=64):
+        return LLMEngine(EagerPagedExecutor(cfg, random_dense_weights(cfg, seed), num_pages=64), num_pages=64,
+                         scheduler_config=SchedulerConfig(max_running_requests=4, max_batched_tokens=64,
+                                                          prefill_chunk_tokens=chunk, max_model_len=128))
+
+    rng = np.random.default_rng(0)
+    rec = TraceRecorder(engine())
+    rec.add_request(rng.integers(0, cfg.vocab_size, 21).tolist(), SamplingParams(max_tokens=6))
+    rec.add_request(rng.integers(0, cfg.vocab_size, 9).tolist(), SamplingParams(max_tokens=9, temperature=0.7, top_k=8, seed=3))
+    for _ in range(3):
+        rec.step()
+    rec.add_request(rng.integers(0, cfg.vocab_size, 33).tolist(), SamplingParams(max_tokens=4))     # arrives mid-run
+    rec.run()
+    path = rec.save(tmp_path / "trace.jsonl")
+    trace = load_trace(path)
+    assert sum(r["kind"] == "request" for r in trace) == 3 and trace[-1]["kind"] == "step"
+    rep = replay_trace(path, engine())
+    assert rep.ok and rep.tokens == 6 + 9 + 4, rep
+    rep2 = replay_trace(trace, engine(chunk=16))                    # same tokens with 16-token prefill chunks
+    assert rep2.ok
+    bad = replay_trace(trace, engine(seed=1))                       # other weights: a difference is located
+    assert not bad.ok and bad.first_difference["position"] >= 0 and "request_id" in bad.first_difference
