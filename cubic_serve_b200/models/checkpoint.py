@@ -22,21 +22,8 @@ from pathlib import Path
 import torch
 
 from ..ops import wq_pack
-from ..quantization import cubic, formats
+from ..quantization import cubic, formats, registry
 from .config import ModelConfig, QuantSpec
-
-PAYLOAD_SUFFIXES = {
-    "cubic": ("weight_packed", "weight_scale", "weight_a", "weight_b", "weight_ab", "weight_scale_global",
-              "weight_a_global", "weight_b_global", "weight_metadata", "weight_curve_a", "weight_curve_b"),
-    "int": ("weight_packed", "weight_scale", "weight_zero_point", "weight_shape", "weight_g_idx"),
-    "awq": ("qweight", "qzeros", "scales"),
-    "fp8": ("weight", "weight_scale", "input_scale"),
-    "fp8_block": ("weight", "weight_scale_inv", "weight_scale"),
-    "nvfp4": ("weight_packed", "weight", "weight_scale", "weight_global_scale", "input_global_scale", "weight_scale_2",
-              "input_scale"),
-    "none": ("weight",),
-}
-
 
 class CheckpointError(ValueError):
     pass
@@ -155,9 +142,10 @@ def admit_checkpoint(path: str | Path) -> AdmittedCheckpoint:
     store = SafetensorsDirectory(path)
     linears, plain = logical_inventory(cfg)
     method = cfg.quant.method
-    suffixes = PAYLOAD_SUFFIXES.get(method)
-    if suffixes is None:
-        raise CheckpointError(f"no loader for weight format {method!r}")
+    try:
+        suffixes = registry.get(method).payload_suffixes
+    except registry.QuantizationRegistryError as exc:
+        raise CheckpointError(f"no loader for weight format {method!r}") from exc
     claimed: set[str] = set()
     payloads: dict[str, dict[str, str]] = {}
     for module in linears:
@@ -216,19 +204,11 @@ def _slice_rows(payload: dict, method: str, lo: int, hi: int, n: int) -> dict:
 
 
 def _dense_of(method: str, payload: dict, shape, q: QuantSpec) -> torch.Tensor:
-    if "weight" in payload and len(payload) == 1:
-        return payload["weight"].float()
-    if method == "cubic":
-        return cubic.decode(payload, cubic.CubicScheme(q.bits, q.group_size), shape)
-    if method == "int":
-        return formats.int_dense(payload, q.bits, q.group_size, shape)
-    if method == "awq":
-        return formats.awq_dense(payload, q.group_size)
-    if method in ("fp8", "fp8_block"):
-        return formats.fp8_dense(payload)
-    if method == "nvfp4":
-        return formats.nvfp4_dense(payload)
-    raise CheckpointError(method)
+    """Dense fp32 matrix of a payload, decoded by the format's quantization extension."""
+    try:
+        return registry.get(method).dense(payload, shape, q)
+    except registry.QuantizationRegistryError as exc:
+        raise CheckpointError(method) from exc
 
 
 def pack_logical(method: str, parts: list[tuple[dict, tuple[int, int]]], q: QuantSpec, k_slice: tuple[int, int] | None = None
@@ -381,55 +361,11 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
 
 # ------------------------------------------------------- random checkpoints
 def _quant_config_json(q: QuantSpec) -> dict | None:
-    if q.method == "none":
-        return None
-    if q.method == "cubic":
-        return {"quant_method": "cubic", "format": "cubic-pack-quantized", "ignore": ["lm_head"], "config_groups": {
-            "group_0": {"targets": ["Linear"], "input_activations": None, "weights": {
-                "num_bits": q.bits, "group_size": q.group_size, "dynamic": False, "symmetric": True,
-                "packing": "little-endian-bitstream", "reserved_code": "zero",
-                "metadata_format": cubic.METADATA_A, "scale_dtype": "float32", "param_dtype": "float16"}}}}
-    if q.method == "int":
-        return {"quant_method": "compressed-tensors", "format": "pack-quantized", "ignore": ["lm_head"], "config_groups": {
-            "group_0": {"targets": ["Linear"], "weights": {"num_bits": q.bits, "group_size": q.group_size,
-                                                           "symmetric": True, "type": "int", "strategy": "group"}}}}
-    if q.method == "awq":
-        return {"quant_method": "awq", "bits": 4, "group_size": q.group_size, "version": "gemm", "zero_point": True}
-    if q.method == "fp8":
-        return {"quant_method": "compressed-tensors", "format": "float-quantized", "config_groups": {
-            "group_0": {"targets": ["Linear"], "weights": {"num_bits": 8, "type": "float", "strategy": "channel"}}}}
-    if q.method == "fp8_block":
-        return {"quant_method": "fp8", "weight_block_size": [128, 128]}
-    if q.method == "nvfp4":
-        return {"quant_method": "compressed-tensors", "format": "nvfp4-pack-quantized", "config_groups": {
-            "group_0": {"targets": ["Linear"], "weights": {"num_bits": 4, "type": "float", "group_size": 16}}}}
-    raise CheckpointError(q.method)
+    return registry.get(q.method).config_json(q)
 
 
 def quantize_payload(w: torch.Tensor, q: QuantSpec) -> dict[str, torch.Tensor]:
-    if q.method == "none":
-        return {"weight": w.to(torch.bfloat16)}
-    if q.method == "cubic":
-        return cubic.quantize(w, cubic.CubicScheme(q.bits, q.group_size))
-    if q.method == "int":
-        return formats.int_quantize(w, q.bits, q.group_size, True)
-    if q.method == "awq":
-        n, k = w.shape
-        g = q.group_size
-        wg = w.float().reshape(n, k // g, g)
-        lo, hi = wg.amin(-1), wg.amax(-1)
-        s = ((hi - lo) / 15).clamp_min(1e-8)
-        z = torch.round(-lo / s).clamp(0, 15)
-        qv = torch.round(wg / s[..., None] + z[..., None]).clamp(0, 15).reshape(n, k)
-        return {"qweight": formats.awq_pack(qv.t().contiguous()), "qzeros": formats.awq_pack(z.t().contiguous()),
-                "scales": s.t().contiguous().half()}
-    if q.method == "fp8":
-        return formats.fp8_quantize(w, block=False)
-    if q.method == "fp8_block":
-        return formats.fp8_quantize(w, block=True)
-    if q.method == "nvfp4":
-        return formats.nvfp4_quantize(w)
-    raise CheckpointError(q.method)
+    return registry.get(q.method).quantize(w, q)
 
 
 def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Path:

@@ -131,39 +131,10 @@ class ModelConfig:
 
 
 def quant_spec_from_hf(qc: dict) -> QuantSpec:
-    """Map a ``quantization_config`` block to a QuantSpec (reference: ``models/quantization.py:79-124``)."""
-    if not qc:
-        return QuantSpec(method="none", bits=16, group_size=0)
-    method = qc.get("quant_method", "")
-    fmt = qc.get("format", "")
-    if method == "cubic" or fmt == "cubic-pack-quantized":
-        w = _first_group_weights(qc)
-        gs = w.get("group_size", 128)
-        return QuantSpec("cubic", int(w.get("num_bits", 4)), int(gs[1] if isinstance(gs, list) else gs))
-    if method == "awq":
-        return QuantSpec("awq", int(qc.get("bits", 4)), int(qc.get("group_size", 128)))
-    if method == "gguf":
-        return QuantSpec("gguf", 4, 256)
-    if fmt == "pack-quantized":
-        w = _first_group_weights(qc)
-        return QuantSpec("int", int(w.get("num_bits", 4)), int(w.get("group_size") or 0))
-    if fmt == "float-quantized":
-        w = _first_group_weights(qc)
-        block = w.get("block_structure") or qc.get("weight_block_size")
-        return QuantSpec("fp8_block" if block else "fp8", 8, 128 if block else 0)
-    if fmt == "nvfp4-pack-quantized" or qc.get("quant_algo") == "NVFP4" or method == "modelopt":
-        return QuantSpec("nvfp4", 4, 16)
-    if method == "fp8":
-        return QuantSpec("fp8_block" if qc.get("weight_block_size") else "fp8", 8, 128)
-    raise ValueError(f"unsupported quantization_config: {method or fmt!r}")
-
-
-def _first_group_weights(qc: dict) -> dict:
-    groups = qc.get("config_groups") or {}
-    for g in groups.values():
-        if isinstance(g, dict) and isinstance(g.get("weights"), dict):
-            return g["weights"]
-    return qc
+    """Map a ``quantization_config`` block to a QuantSpec: the registered quantization extensions are asked in turn
+    (``quantization/registry.py``; reference: ``models/quantization.py:79-124``)."""
+    from ..quantization import registry
+    return registry.detect(qc or {})
 
 
 # ----------------------------------------------------------------- named configs

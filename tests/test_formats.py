@@ -103,3 +103,38 @@ def test_swiglu_row_order_and_packed_permutation():
     assert torch.equal(both.codes[0], pi.codes) and torch.equal(both.meta[0], pi.meta)
     wb = wq_pack.pack_bf16(torch.randn(2 * inter, 64, generator=g))
     assert torch.equal(wq_pack.swiglu_interleave(wb).codes, wb.codes[order])
+
+
+def test_quantization_registry_builtins_and_plugins():
+    from cubic_serve_b200.models.config import QuantSpec
+    from cubic_serve_b200.quantization import registry as R
+    assert {"none", "cubic", "int", "awq", "fp8", "fp8_block", "nvfp4", "gguf"} <= set(R.names())
+    assert R.get("cubic").native_format == wq_pack.FMT_CUBIC4 and R.get("fp8").native_format is None
+    assert R.detect({}).method == "none"
+    assert R.detect({"quant_method": "fp8", "weight_block_size": [128, 128]}).method == "fp8_block"
+    assert R.detect({"format": "pack-quantized", "config_groups": {"g": {"weights": {"num_bits": 8, "group_size": 64}}}}) == \
+        QuantSpec("int", 8, 64)
+    assert R.resolve_compute_mode("nvfp4") == "w4a16" and R.resolve_compute_mode("cubic", "auto") == "w4a16"
+    with pytest.raises(R.QuantizationRegistryError):
+        R.resolve_compute_mode("cubic", "w4a4")
+    with pytest.raises(R.QuantizationRegistryError):
+        R.get("bitsandbytes")
+    with pytest.raises(ValueError):
+        R.detect({"quant_method": "bitsandbytes"})
+    # an out-of-tree format: sign bits with one scale per row
+    ext = R.QuantizationExtension(
+        "sign1", ("weight_sign", "weight_scale"), ("w1a16",), None,
+        lambda qc: QuantSpec("sign1", 1, 0) if qc.get("quant_method") == "sign1" else None,
+        lambda p, shape, q: (p["weight_sign"].float() * 2 - 1) * p["weight_scale"].float()[:, None],
+        lambda w, q: {"weight_sign": (w > 0).to(torch.uint8), "weight_scale": w.abs().mean(1)},
+        lambda q: {"quant_method": "sign1"})
+    R.register(ext)
+    try:
+        with pytest.raises(R.QuantizationRegistryError):
+            R.register(ext)
+        spec = R.detect({"quant_method": "sign1"})
+        w = torch.randn(8, 16)
+        back = R.get(spec.method).dense(R.get("sign1").quantize(w, spec), (8, 16), spec)
+        assert back.shape == (8, 16) and torch.equal(back > 0, w > 0)
+    finally:
+        R._extensions.pop("sign1", None)
