@@ -123,7 +123,7 @@ def build_parser() -> argparse.ArgumentParser:
     g = s.add_argument_group("Advanced")
     g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
     g.add_argument("--startup-numerical-audit", action="store_true")
-    g.add_argument("--model-adapter")
+    g.add_argument("--model-adapter", help="Python file defining MODEL_DEFINITION (loaded after a source-policy audit)")
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--operator-config", help="JSON file with launch policies of the native kernels (ops/strategies.py)")
     return ap

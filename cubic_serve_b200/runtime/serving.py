@@ -95,19 +95,21 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         executor = EagerPagedExecutor(cfg, random_dense_weights(cfg, args.seed), pages, kv_bits=(k_bits, v_bits))
     else:
         from ..executor.gpu_executor import GpuExecutor
-        from ..models.checkpoint import load_decoder_weights
-        from ..models.decoder import DecoderRunner, random_decoder_weights
         dev = torch.device("cuda", devices[0])
         torch.cuda.set_device(dev)
-        weights = load_decoder_weights(ck, dev) if ck is not None else random_decoder_weights(cfg, dev, args.seed)
+        from ..models import registry as model_registry
+        if getattr(args, "model_adapter", None):
+            model_registry.load_adapter(args.model_adapter)          # audited, then registered (may replace a family)
+        defn = model_registry.get(cfg.family)
+        weights = defn.load_weights(ck, dev) if ck is not None else defn.random_weights(cfg, dev, args.seed)
         free, _total = torch.cuda.mem_get_info(dev)
         if args.gpu_memory_gib:
             free = min(free, int(args.gpu_memory_gib * 2 ** 30) - torch.cuda.memory_allocated(dev))
         pages = plan_kv_pages(free, int(args.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, 1, k_bits, v_bits, max_len,
                               args.max_running_requests)
-        runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits,
-                               max_requests=args.max_running_requests,
-                               kv_rotation=bool(getattr(args, "enable_kv_cache_rotation", False)))
+        runner = defn.build_runner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits,
+                                   max_requests=args.max_running_requests,
+                                   kv_rotation=bool(getattr(args, "enable_kv_cache_rotation", False)))
         depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None else 0
         if depth:
             # MTP speculative decoding (--speculative-config): draft head + review rounds instead of graph decode

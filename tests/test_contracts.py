@@ -55,3 +55,38 @@ def test_hybrid_config_layer_types_and_hf_parse(tmp_path):
     assert got.family == "qwen3_5" and got.gdn_interval == 4 and (got.gdn_k_heads, got.gdn_v_heads) == (2, 4)
     assert got.rotary_dim == 32 and got.zero_centered_norm and got.attn_output_gate
     assert sum(got.layer_is_gdn(i) for i in range(8)) == 6
+
+
+def test_model_registry_and_adapter_source_policy(tmp_path):
+    from cubic_serve_b200.models import registry as R
+    assert {"gqa_decoder", "gqa_moe", "qwen3_5"} <= set(R.families())
+    assert R.for_architecture("Qwen3NextForCausalLM").family == "qwen3_5"
+    assert R.for_architecture("LlamaForCausalLM") is R.get("gqa_decoder")
+    import pytest
+    with pytest.raises(R.ModelRegistryError):
+        R.for_architecture("GPT2LMHeadModel")
+    good = tmp_path / "toy_adapter.py"
+    good.write_text(
+        "from cubic_serve_b200.models.config import ModelConfig\n"
+        "from cubic_serve_b200.models.registry import ModelDefinition, get\n"
+        "base = get('gqa_decoder')\n"
+        "def parse(path):\n"
+        "    return ModelConfig(name='adapted', num_layers=3)\n"
+        "MODEL_DEFINITION = ModelDefinition('toy_adapter', ('ToyForCausalLM',), parse, base.random_weights,\n"
+        "                                   base.load_weights, base.build_runner, 'test adapter')\n")
+    d = R.load_adapter(good)
+    try:
+        assert d.family == "toy_adapter" and R.for_architecture("ToyForCausalLM") is d
+        assert d.parse_config(tmp_path).num_layers == 3
+    finally:
+        R._definitions.pop("toy_adapter", None)
+    for body, needle in (("import os\n", "import of 'os'"), ("from subprocess import run\n", "subprocess"),
+                         ("x = open('/etc/passwd')\n", "'open'"), ("y = ().__class__.__subclasses__()\n", "__subclasses__"),
+                         ("import torch\ntorch.__builtins__\n", "__builtins__"), ("from . import sibling\n", "import from ."),
+                         ("def f(:\n", "syntax error")):
+        bad = tmp_path / "bad.py"
+        bad.write_text(body + "MODEL_DEFINITION = None\n")
+        v = R.audit_source(bad.read_text())
+        assert v and any(needle in x.what for x in v), (body, v)
+        with pytest.raises(R.ModelRegistryError):
+            R.load_adapter(bad)
