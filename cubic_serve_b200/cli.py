@@ -83,6 +83,9 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--device", type=int, default=0)
     q.add_argument("--quick", action="store_true")
 
+    ci = sub.add_parser("check-install", help="check python modules, the native library and the GPUs")
+    ci.add_argument("--build", action="store_true", help="(re)build the native library first")
+    ci.add_argument("--json", action="store_true")
     s = sub.add_parser("serve", help="serve a checkpoint over OpenAI / Anthropic compatible HTTP")
     s.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
     g = s.add_argument_group("Server")
@@ -180,6 +183,11 @@ def main(argv: list[str] | None = None) -> int:
         return _inspect(args)
     if args.command == "qualify":
         return _qualify(args)
+    if args.command == "check-install":
+        from .utils.check_install import format_report, run_checks
+        report = run_checks(build=args.build)
+        print(json.dumps(report, indent=1) if args.json else format_report(report))
+        return 0 if report["ok"] else 1
     return 2
 
 

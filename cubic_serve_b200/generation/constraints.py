@@ -107,6 +107,24 @@ class GrammarEngineMatcher:
         return bool(self.m.is_terminated())
 
 
+def _tokenizer_info(tokenizer, eos_token_id: int, vocab_size: int):
+    """The grammar engine's view of the vocabulary.  HuggingFace tokenizers are read by the engine itself; a tokenizer
+    that only offers ``decode`` (the built-in byte tokenizer) is described token by token as a raw vocabulary (ids
+    above the tokenizer's own range are padding of the model's vocabulary and never allowed)."""
+    if hasattr(tokenizer, "get_vocab") and hasattr(tokenizer, "convert_ids_to_tokens"):
+        return _xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=vocab_size)
+    own = int(getattr(tokenizer, "vocab_size", vocab_size))
+    vocab: list = []
+    for i in range(vocab_size):
+        if i < 256 and own >= 256:
+            vocab.append(bytes([i]))                       # byte-level ids
+        elif i < own:
+            vocab.append(tokenizer.decode([i], skip_special_tokens=False) or f"<special_{i}>")
+        else:
+            vocab.append(f"<unused_{i}>")
+    return _xgr.TokenizerInfo(vocab, vocab_type=_xgr.VocabType.RAW, vocab_size=vocab_size, stop_token_ids=[int(eos_token_id)])
+
+
 def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_size: int):
     """Build a matcher for a constraint, or ``None`` when the request is unconstrained."""
     if s.kind is StructuredKind.NONE:
@@ -117,8 +135,7 @@ def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_siz
         if s.kind is StructuredKind.JSON_OBJECT:
             return None            # without a grammar engine json_object stays a prompt-level instruction
         raise RuntimeError("xgrammar is not installed")
-    info = _xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=vocab_size)
-    compiler = _xgr.GrammarCompiler(info)
+    compiler = _xgr.GrammarCompiler(_tokenizer_info(tokenizer, eos_token_id, vocab_size))
     if s.kind is StructuredKind.JSON_OBJECT:
         compiled = compiler.compile_builtin_json_grammar()
     elif s.kind in (StructuredKind.JSON_SCHEMA, StructuredKind.TOOL_SCHEMA):

@@ -244,3 +244,55 @@ def test_overlapped_decode_steps_give_the_same_tokens():
         assert ex0.feedback_launches == 0 and ex1.feedback_launches > 10
         if eos is not None:
             assert any(o and o[-1] == eos and len(o) < m for o, (_, _, m) in zip(plain, arrivals))   # a request was stopped
+
+
+def test_grammar_engine_constraints_end_to_end():
+    """xgrammar-backed constraints (regex, JSON schema) through the adapter: masks reach the sampler, the output
+    matches, the matcher can roll back (speculative rounds); the byte tokenizer is described as a raw vocabulary."""
+    pytest = __import__("pytest")
+    pytest.importorskip("xgrammar")
+    import json
+    import re
+    from cubic_serve_b200.contracts.request import StructuredKind, StructuredOutput
+    from cubic_serve_b200.generation.constraints import GrammarTransaction, compile_matcher
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    tok = ByteTokenizer()
+    cfg = toy_config()
+    w = random_dense_weights(cfg, seed=0)
+    eng = LLMEngine(EagerPagedExecutor(cfg, w, num_pages=64), num_pages=64,
+                    scheduler_config=SchedulerConfig(max_running_requests=4, max_model_len=128))
+    eos = tok.eos_token_id
+    pattern = r"(yes|no)-[0-9]{3}"
+    for seed in range(2):
+        m = compile_matcher(StructuredOutput(StructuredKind.REGEX, pattern), tok, eos, cfg.vocab_size)
+        rid = eng.add_request([5, 6, 7, 8 + seed], SamplingParams(temperature=1.0, top_k=20, seed=seed, max_tokens=16,
+                                                                  stop_token_ids=(eos,), matcher=m))
+        req = eng.requests[rid]
+        while eng.has_unfinished:
+            eng.step()
+        assert req.output[-1] == eos and re.fullmatch(pattern, tok.decode(req.output[:-1]))
+        assert m.finished
+    # JSON schema by a random walk inside the masks, with a rejected speculative tail rolled back on the way
+    schema = {"type": "object", "properties": {"n": {"type": "integer"}, "ok": {"type": "boolean"}}, "required": ["n", "ok"],
+              "additionalProperties": False}
+    m = compile_matcher(StructuredOutput(StructuredKind.JSON_SCHEMA, schema), tok, eos, cfg.vocab_size)
+    rng = np.random.default_rng(0)
+    out: list[int] = []
+    for step in range(400):
+        bm = np.zeros(cfg.vocab_size // 32, dtype=np.uint32)
+        m.fill_bitmask(bm)
+        allowed = [i for i in range(cfg.vocab_size) if bm[i // 32] >> (i % 32) & 1 and chr(i % 256) not in " \n\t\r"]
+        t = int(rng.choice(allowed))
+        if step == 5:
+            tr = GrammarTransaction(m)
+            assert tr.try_accept(t)
+            tr.commit(0)                    # the draft token is rejected after all: the matcher is back where it was
+            bm2 = np.zeros_like(bm)
+            m.fill_bitmask(bm2)
+            assert np.array_equal(bm, bm2)
+        assert m.accept(t)
+        if t == eos:
+            break
+        out.append(t)
+    doc = json.loads(tok.decode(out))
+    assert isinstance(doc["n"], int) and isinstance(doc["ok"], bool) and set(doc) == {"n", "ok"}
