@@ -243,6 +243,7 @@ class GpuExecutor:
         # two result buffers: a step may be launched before the previous step's ids have been read (``launch`` / ``collect``)
         self.out_host = torch.zeros(2, max_rows * rows_per_request, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.use_graphs = use_graphs
+        self.graph_masks = False         # True once decode graphs were captured with the mask buffer as an input
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.stream = torch.cuda.Stream(device=self.device)
         self.h2d_bytes_last = 0
@@ -268,21 +269,36 @@ class GpuExecutor:
     def _body(self, b: StepBatch) -> None:
         self.runner.run_step(b, self.stage.d, self.logits, self.out_ids)
 
+    def _mask_buffers(self) -> None:
+        if getattr(self, "_mask_host", None) is None:
+            words = -(-self.cfg.vocab_size // 32)
+            rows = self.out_ids.numel()
+            self._mask_host = torch.empty(rows, words, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+            self._mask_dev = torch.full((rows, words), -1, dtype=torch.int32, device=self.device)     # everything allowed
+            self._mask_rows_dirty = 0
+
     def _stage_masks(self, segs: list[Segment]) -> bool:
         """Upload the allowed-token bitmasks of this step's sampled rows; rows without one allow everything.
 
-        Returns False (and removes the mask from the step inputs) when no segment is constrained.  Constrained
-        steps run eagerly: the captured decode graphs sample without a mask.
+        With ``graph_masks`` (set by ``capture_decode_graphs``) the sampler ALWAYS reads the device mask buffer, in
+        graphs and eagerly: it holds all-ones rows except where a constrained step wrote masks, and those rows are
+        reset by one fill when the next unconstrained step comes.  Constrained decode steps then replay the same
+        graphs as any other.  Without it the mask is a step input only when a segment is constrained, and such steps
+        run eagerly.  Returns whether this step carries masks.
         """
         sampled = [s for s in segs if s.sample]
-        if not any(s.mask is not None for s in sampled):
-            self.stage.d.pop("mask", None)
+        constrained = any(s.mask is not None for s in sampled)
+        if not constrained:
+            if self.graph_masks:
+                if self._mask_rows_dirty:
+                    with torch.cuda.stream(self.stream):
+                        self._mask_dev[:self._mask_rows_dirty].fill_(-1)
+                    self._mask_rows_dirty = 0
+            else:
+                self.stage.d.pop("mask", None)
             return False
-        words = -(-self.cfg.vocab_size // 32)
-        if getattr(self, "_mask_host", None) is None:
-            rows = self.out_ids.numel()
-            self._mask_host = torch.empty(rows, words, dtype=torch.int32, pin_memory=torch.cuda.is_available())
-            self._mask_dev = torch.empty(rows, words, dtype=torch.int32, device=self.device)
+        self._mask_buffers()
+        words = self._mask_host.shape[1]
         hm = self._mask_host.numpy().view(np.uint32)
         for i, s in enumerate(sampled):
             if s.mask is None:
@@ -292,6 +308,7 @@ class GpuExecutor:
         n = len(sampled)
         with torch.cuda.stream(self.stream):
             self._mask_dev[:n].copy_(self._mask_host[:n], non_blocking=True)
+        self._mask_rows_dirty = max(self._mask_rows_dirty, n)
         self.stage.d["mask"] = self._mask_dev
         self.h2d_mask_bytes_last = n * words * 4
         return True
@@ -299,6 +316,11 @@ class GpuExecutor:
     def capture_decode_graphs(self, capacities: list[int] | None = None) -> list[int]:
         """Capture one graph per decode row capacity (largest first, like the reference)."""
         caps = capacities or [c for c in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512) if c <= self.max_rows]
+        # the captured sampler reads the mask buffer (all-ones rows unless a constrained step wrote masks), so that
+        # structured-output requests decode in the same graphs; 4 bytes per 32 vocabulary entries and row
+        self._mask_buffers()
+        self.graph_masks = True
+        self.stage.d["mask"] = self._mask_dev
         for cap in sorted(caps, reverse=True):
             dummy = [Segment(0, [0], 0, [0])]
             b, _ = self._fill(dummy, pad_rows_to=cap)
@@ -343,7 +365,8 @@ class GpuExecutor:
         """
         total = sum(len(s.token_ids) for s in segs)
         masked = self._stage_masks(segs)
-        decode = all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs) and not masked
+        decode = (all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs)
+                  and (self.graph_masks or not masked))
         cap = None
         if decode:
             cap = next((c for c in sorted(self.graphs) if c >= total), None)

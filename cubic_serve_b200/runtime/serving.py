@@ -164,10 +164,14 @@ def run_http_server(backend, model_name: str, args) -> int:
     import uvicorn
 
     from ..api.server import CubicASGIApp
-    logging.basicConfig(level=logging.INFO, format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    from .logging import LogConfig, close_logging, serve_logging
+    handles = serve_logging(LogConfig.from_file(getattr(args, "log_config", None)))
     app = CubicASGIApp(backend, model_name, args.served_model_name, args.api_key)
     StatusReporter(backend).start()
     config = uvicorn.Config(app, host=args.host, port=args.port, log_level="warning",
                             timeout_keep_alive=args.http_keep_alive_seconds, lifespan="on")
-    uvicorn.Server(config).run()
+    try:
+        uvicorn.Server(config).run()
+    finally:
+        close_logging(handles)
     return 0

@@ -127,3 +127,36 @@ def test_qualification_run_passes():
     names = " ".join(r["kernel"] for r in rep["results"])
     for part in ("CTA pairs", "SwiGLU", "gdn_delta", "hadamard", "graph replay"):
         assert part in names
+
+
+def test_constrained_requests_decode_in_graphs():
+    """Structured-output masks are an input of the captured sampler: a constrained request decodes by graph replay
+    (no eager step), next to an unconstrained one whose tokens do not change."""
+    from cubic_serve_b200.generation.constraints import ChoiceMatcher
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [ord(c) for c in text]
+
+    eos = 3
+    options = ["yes", "no", "maybe"]
+    free_prompt = np.random.default_rng(5).integers(0, 2000, 30).tolist()
+    eng0, _, _ = _engine(False)
+    baseline = eng0.generate([free_prompt], SamplingParams(max_tokens=10, ignore_eos=True))[0]
+    eng, ex, runner = _engine(True)
+    eager_steps = []
+    body = ex._body
+    ex._body = lambda b: (eager_steps.append(b.num_tokens), body(b))[1]
+    m = ChoiceMatcher(options, Tok(), eos)
+    rid = eng.add_request([5, 6, 7, 8], SamplingParams(temperature=1.0, top_k=20, seed=1, max_tokens=12,
+                                                       stop_token_ids=(eos,), matcher=m))
+    other = eng.add_request(free_prompt, SamplingParams(max_tokens=10, ignore_eos=True))
+    reqs = {rid: eng.requests[rid], other: eng.requests[other]}
+    while eng.has_unfinished:
+        eng.step()
+    runner.ws.check_status()
+    toks = reqs[rid].output
+    assert toks[-1] == eos and "".join(chr(t) for t in toks[:-1]) in options
+    assert reqs[other].output == baseline
+    assert eager_steps and all(n > 1 for n in eager_steps)          # only the prefill step ran eagerly
