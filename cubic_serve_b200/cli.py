@@ -82,6 +82,8 @@ def build_parser() -> argparse.ArgumentParser:
     q = sub.add_parser("qualify", help="run the numerical witness checks of the native kernels on this GPU")
     q.add_argument("--device", type=int, default=0)
     q.add_argument("--quick", action="store_true")
+    q.add_argument("--evidence-dir", help="directory of start-up receipts (default: $CUBIC_EVIDENCE_DIR or the user cache)")
+    q.add_argument("--reuse", action="store_true", help="accept a passing receipt made by the same code on the same GPU model")
 
     ci = sub.add_parser("check-install", help="check python modules, the native library and the GPUs")
     ci.add_argument("--build", action="store_true", help="(re)build the native library first")
@@ -125,7 +127,13 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prefill-chunk-tokens", type=int, default=4096)
     g = s.add_argument_group("Advanced")
     g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
-    g.add_argument("--startup-numerical-audit", action="store_true")
+    g.add_argument("--startup-numerical-audit", action="store_true",
+                   help="qualify the kernels against their oracles before serving (a passing receipt of the same code on "
+                        "the same GPU model is reused); a failure refuses to serve")
+    g.add_argument("--evidence-dir", help="directory of start-up receipts and cached plans")
+    g.add_argument("--tune-launch-plans", action="store_true",
+                   help="time the launch forms of every weight GEMM of the model at every decode capacity at start-up "
+                        "(cached as start-up evidence) instead of using the built-in rules")
     g.add_argument("--model-adapter", help="Python file defining MODEL_DEFINITION (loaded after a source-policy audit)")
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--operator-config", help="JSON file with launch policies of the native kernels (ops/strategies.py)")
@@ -169,8 +177,9 @@ def _inspect(args) -> int:
 
 
 def _qualify(args) -> int:
-    from .guardrail.qualify import run_qualification
-    report = run_qualification(args.device, quick=args.quick)
+    from .guardrail.qualify import qualify_with_receipt
+    report, reused = qualify_with_receipt(args.device, quick=args.quick, evidence_dir=args.evidence_dir, force=not args.reuse)
+    report = dict(report, receipt="reused" if reused else "new")
     print(json.dumps(report, indent=1))
     return 0 if report["ok"] else 1
 

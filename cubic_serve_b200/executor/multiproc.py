@@ -118,10 +118,16 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
             free, _ = torch.cuda.mem_get_info(dev)
             pages = plan_kv_pages(free, int(spec.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, spec.tp, spec.k_bits,
                                   spec.v_bits, spec.max_model_len, spec.max_rows, layers=layers[1] - layers[0])
-            if spec.world > 1:                                # every rank must agree: take the minimum
-                t = torch.tensor([pages], device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MIN)
-                pages = int(t.item())
+        if spec.world > 1:
+            # every rank runs the same code on the same model; the KV pool is the smallest any rank can hold
+            import dataclasses
+
+            from ..contracts.implementation import digest_of, identity
+            from ..runtime.preparation import consensus
+            agreed = consensus({"implementation": identity().digest, "model": digest_of(dataclasses.asdict(cfg)),
+                                "tp": spec.tp, "pp": spec.pp, "kv_bits": [spec.k_bits, spec.v_bits],
+                                "fixed_pages": spec.num_pages, "pages": pages}, minimum=("pages",))
+            pages = int(agreed["pages"])
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=spec.token_budget, k_bits=spec.k_bits,
                                v_bits=spec.v_bits, tp=tp, pp=pp, max_requests=spec.max_rows,
                                kv_rotation=spec.kv_rotation)

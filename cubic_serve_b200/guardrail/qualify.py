@@ -153,3 +153,14 @@ def _qualify_graph_replay(dev) -> dict:
     same = outs[0] == outs[1]
     return {"kernel": "decode graph replay == eager launches", "shape": [3, 10], "class": "exact" if same else "mismatch",
             "rel_l2": 0.0}
+
+
+def qualify_with_receipt(device: int = 0, quick: bool = False, evidence_dir=None, force: bool = False, run=None):
+    """``run_qualification`` behind a start-up receipt: a passing report made by the same implementation (source
+    closure + native sources + build flags) on the same GPU model is returned without running anything.  Returns
+    ``(report, reused)``."""
+    from ..contracts.implementation import PACKAGE_NAME, identity
+    from ..runtime.preparation import EvidenceStore, StartupQualification, device_description
+    ident = identity("qualification", (f"{PACKAGE_NAME}.guardrail.qualify",))
+    sq = StartupQualification(EvidenceStore(evidence_dir), ident, device_description(device))
+    return sq.ensure(run or (lambda: run_qualification(device, quick=quick)), operands={"quick": bool(quick)}, force=force)

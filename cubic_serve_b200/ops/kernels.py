@@ -86,6 +86,11 @@ def resident_clusters(fmt: int, size: int) -> int:
     return _cluster_capacity[key]
 
 
+# Measured launch plans (``ops/autotune.py``): "fmt:m:n:k:act" -> (use the persistent kernel, split-K factor of the
+# per-tile kernel).  Consulted before the rules below when the caller forces nothing; empty unless a plan was installed.
+TUNED_PLANS: dict[str, tuple[bool, int]] = {}
+
+
 def choose_splits(m: int, n: int, k: int, sms: int = 148, fmt: int = FMT_CUBIC4, cluster: bool = True) -> int:
     """Split-K factor: fill the SMs when the (n-tile x m-tile) grid is small.
 
@@ -159,6 +164,10 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
     l = native.lib()
+    if splits is None and min_units is None and link is None and TUNED_PLANS:
+        tuned = TUNED_PLANS.get(f"{w.fmt}:{m}:{w.n}:{k}:0")
+        if tuned is not None:
+            splits, min_units = (None, 0) if tuned[0] else (tuned[1], None)
     if splits is None and min_units is None and use_stream_k(m, w.n, w.fmt, sm_count(x.device), k):
         from .strategies import active
         min_units = active().gemm.stream_k_min_units
@@ -202,6 +211,10 @@ def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = Non
     assert out.stride(1) == 1 and out.shape == (m, w.n // 2)
     ws = ws or workspace(x.device)
     l = native.lib()
+    if splits is None and min_units is None and link is None and TUNED_PLANS:
+        tuned = TUNED_PLANS.get(f"{w.fmt}:{m}:{w.n}:{k}:1")
+        if tuned is not None:
+            splits, min_units = (None, 0) if tuned[0] else (tuned[1], None)
     stream_k = splits is None and (min_units is not None or use_stream_k(m, w.n, w.fmt, sm_count(x.device), k))
     if stream_k and min_units is None:
         from .strategies import active

@@ -9,6 +9,8 @@ into the package directory so that it ships with a source snapshot.
 from __future__ import annotations
 
 import ctypes
+import hashlib
+import json
 import os
 import subprocess
 import threading
@@ -16,6 +18,7 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_PATH = Path(__file__).resolve().parent.parent / "libcubic_b200.so"
+MANIFEST_PATH = LIB_PATH.with_suffix(".manifest.json")
 SOURCES = ("wq_gemm.cu", "elementwise.cu", "kv_cache.cu", "paged_attn.cu", "sampling.cu", "tp_comm.cu", "moe.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -42,12 +45,71 @@ def sources() -> list[Path]:
     )
 
 
+def _sha(path: Path) -> str:
+    h = hashlib.sha256()
+    with path.open("rb") as f:
+        for block in iter(lambda: f.read(1 << 20), b""):
+            h.update(block)
+    return h.hexdigest()
+
+
+def _source_digests() -> dict[str, str]:
+    deps = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
+    return {p.name: _sha(p) for p in deps}
+
+
+def read_manifest() -> dict | None:
+    """The bundle manifest written beside the library by ``build``: source digests, flags, compiler, library digest."""
+    try:
+        return json.loads(MANIFEST_PATH.read_text())
+    except (OSError, ValueError):
+        return None
+
+
+def verify_bundle(check_library: bool = True) -> list[str]:
+    """Problems of the built bundle against the sources in the tree (empty = the library is what the sources build):
+    missing library or manifest, a source whose content differs from the one compiled, other flags, a library file
+    that is not the one the manifest describes."""
+    if not LIB_PATH.exists():
+        return [f"{LIB_PATH.name} is missing"]
+    man = read_manifest()
+    if man is None:
+        return [f"{MANIFEST_PATH.name} is missing or unreadable"]
+    problems = []
+    now = _source_digests()
+    built = man.get("sources", {})
+    for name in sorted(set(now) | set(built)):
+        if name not in built:
+            problems.append(f"{name} was added after the build")
+        elif name not in now:
+            problems.append(f"{name} was compiled but is gone")
+        elif now[name] != built[name]:
+            problems.append(f"{name} changed after the build")
+    if list(man.get("flags", [])) != list(NVCC_FLAGS):
+        problems.append("the compiler flags changed after the build")
+    if check_library and man.get("library_sha256") != _sha(LIB_PATH):
+        problems.append(f"{LIB_PATH.name} is not the file the manifest describes")
+    return problems
+
+
 def needs_build() -> bool:
+    """Content-addressed staleness check: file times do not survive a copy of the tree to another machine, the
+    digests in the manifest do.  A library without a manifest falls back to comparing file times."""
     if not LIB_PATH.exists():
         return True
-    built = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
-    return any(p.stat().st_mtime > built for p in deps)
+    if read_manifest() is None:
+        built = LIB_PATH.stat().st_mtime
+        deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+        return any(p.stat().st_mtime > built for p in deps)
+    return bool(verify_bundle(check_library=False))
+
+
+def _nvcc_version() -> str:
+    try:
+        out = subprocess.run([_nvcc(), "--version"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True).stdout
+        return out.strip().splitlines()[-1] if out.strip() else ""
+    except OSError:
+        return ""
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
@@ -77,6 +139,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if res.returncode != 0:
         raise NativeLibraryError(f"link failed:\n{res.stdout}")
     os.replace(tmp, LIB_PATH)
+    manifest = {"library": LIB_PATH.name, "library_sha256": _sha(LIB_PATH), "arch": "sm_100a", "flags": list(NVCC_FLAGS),
+                "nvcc": _nvcc_version(), "sources": _source_digests()}
+    MANIFEST_PATH.write_text(json.dumps(manifest, indent=1, sort_keys=True) + "\n")
     return LIB_PATH
 
 

@@ -100,6 +100,13 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         from ..models import registry as model_registry
         if getattr(args, "model_adapter", None):
             model_registry.load_adapter(args.model_adapter)          # audited, then registered (may replace a family)
+        if getattr(args, "startup_numerical_audit", False):
+            from ..guardrail.qualify import qualify_with_receipt
+            report, reused = qualify_with_receipt(devices[0], quick=True, evidence_dir=getattr(args, "evidence_dir", None))
+            if not report["ok"]:
+                bad = [r["kernel"] for r in report["results"] if r["class"] == "mismatch"]
+                raise SystemExit(f"start-up qualification failed on this GPU: {bad}")
+            log.info("start-up qualification: %d checks passed (%s receipt)", len(report["results"]), "reused" if reused else "new")
         defn = model_registry.get(cfg.family)
         weights = defn.load_weights(ck, dev) if ck is not None else defn.random_weights(cfg, dev, args.seed)
         free, _total = torch.cuda.mem_get_info(dev)
@@ -128,6 +135,16 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
                 runner.enable_reasoning_budget(*think)       # thinking-token budgets are enforced on the device
             executor = GpuExecutor(runner, max_rows=args.max_running_requests, max_prefill_tokens=args.token_budget,
                                    max_model_len=max_len)
+            if getattr(args, "tune_launch_plans", False):
+                # measured launch form per (projection, decode capacity); kept as start-up evidence, so measured once
+                from ..contracts.implementation import identity
+                from ..ops import autotune
+                from .preparation import EvidenceStore, StartupPreparation, device_description
+                prep = StartupPreparation(EvidenceStore(getattr(args, "evidence_dir", None)), identity(),
+                                          device_description(devices[0]))
+                rows = [c for c in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512) if c <= args.max_running_requests]
+                n = autotune.install(autotune.prepare(cfg, rows, dev, prep))
+                log.info("launch plans: %d measured entries replace the rules (%s)", n, "cached" if prep.hits else "measured now")
             caps = executor.capture_decode_graphs()
             log.info("captured decode graphs for capacities %s; %d KV pages", caps, pages)
     tok = _tokenizer_for(model, cfg.vocab_size)

@@ -48,9 +48,12 @@ def run_checks(build: bool = False) -> dict:
             add("native entry points", not missing, "all present" if not missing else f"missing {missing}")
         except OSError as exc:
             add("native entry points", False, f"cannot load: {exc}")
-        stale = [p.name for p in native.CSRC.glob("*.cu*") if p.stat().st_mtime > lib_path.stat().st_mtime]
-        add("native library is newer than its sources", not stale, "up to date" if not stale else f"rebuild: {stale[:4]} changed",
+        problems = native.verify_bundle()
+        add("native library matches its sources (bundle manifest)", not problems,
+            "source digests, flags and library digest agree" if not problems else "rebuild: " + "; ".join(problems[:4]),
             required=False)
+        from ..contracts.implementation import identity
+        add("implementation identity", True, identity().short(), required=False)
     try:
         import torch
         if torch.cuda.is_available():

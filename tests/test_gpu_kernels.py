@@ -486,3 +486,24 @@ def test_wq_gemm_split_k_through_cluster_shared_memory(m, n, k, splits):
     assert _rel(outs[1][0].cpu(), x.float().cpu() @ dense.t()) < 1e-2
     for a, b in zip(outs[1], outs[0]):
         assert torch.equal(a, b)
+
+
+def test_autotune_measures_and_installed_plans_are_used():
+    from cubic_serve_b200.ops import autotune, kernels as K, wq_pack
+    plan = autotune.tune([(wq_pack.FMT_CUBIC4, 512, 1024, False), (wq_pack.FMT_CUBIC4, 512, 1024, True)], [16], "cuda:0")
+    assert set(plan) == {"0:16:512:1024:0", "0:16:512:1024:1"}
+    for e in plan.values():
+        assert e["us"] > 0 and e["rule_us"] > 0 and {"tile1", "tile2", "tile4", "stream_k"} <= set(e["all_us"])
+    w = autotune._random_weight(wq_pack.FMT_CUBIC4, 512, 1024, False, "cuda:0")
+    x = (torch.randn(16, 1024, device="cuda:0") * 0.5).to(torch.bfloat16)
+    want = x.float() @ wq_pack.unpack_to_dense(w)[:512].to("cuda:0").t()
+    by_rule = K.wq_gemm(x, w)
+    try:
+        for forced in ({"use": True, "kernel": "tile", "splits": 4}, {"use": True, "kernel": "stream_k", "splits": 0}):
+            assert autotune.install({"0:16:512:1024:0": forced}) == 1
+            got = K.wq_gemm(x, w)
+            assert ((got.float() - want).norm() / want.norm()).item() < 1e-2
+            assert ((got.float() - by_rule.float()).norm() / want.norm()).item() < 1e-2
+    finally:
+        autotune.install(None)
+    K.workspace(torch.device("cuda:0")).check_status()

@@ -41,3 +41,26 @@ def test_policy_drives_kernel_choice():
         assert not K.use_stream_k(512, 24576, FMT_CUBIC4) and K.use_stream_k(256, 24576, FMT_CUBIC4)
     finally:
         S.install(old)
+
+
+def test_autotune_shapes_candidates_and_install():
+    from cubic_serve_b200.models.config import NAMED_CONFIGS
+    from cubic_serve_b200.ops import autotune, kernels as K, wq_pack
+    shapes = autotune.model_shapes(NAMED_CONFIGS["dense-8b"]())
+    assert (wq_pack.FMT_CUBIC4, 6144, 4096, False) in shapes and (wq_pack.FMT_CUBIC4, 24576, 4096, True) in shapes
+    assert (wq_pack.FMT_BF16, 151936, 4096, False) in shapes
+    tp2 = autotune.model_shapes(NAMED_CONFIGS["dense-8b"](), tp=2)
+    assert (wq_pack.FMT_CUBIC4, 3072, 4096, False) in tp2 and (wq_pack.FMT_CUBIC4, 4096, 6144, False) in tp2
+    # splits leave at least four k-blocks per CTA and at most ~4 CTAs per SM; the persistent kernel is always timed
+    assert autotune.candidates(16, 151936, 4096) == [("tile", 1), ("stream_k", 0)]
+    assert ("tile", 8) in autotune.candidates(16, 4096, 4096) and ("tile", 8) not in autotune.candidates(16, 4096, 1024)
+    w = autotune._random_weight(wq_pack.FMT_CUBIC4, 256, 512, True, "cpu")
+    assert w.act_interleaved and (w.n, w.k) == (256, 512)
+    plan = {autotune.plan_key(0, 16, 6144, 4096, False): {"use": True, "kernel": "tile", "splits": 3},
+            autotune.plan_key(0, 16, 4096, 4096, False): {"use": False, "kernel": "tile", "splits": 4},
+            autotune.plan_key(3, 64, 151936, 4096, False): {"use": True, "kernel": "stream_k", "splits": 0}}
+    try:
+        assert autotune.install(plan) == 2
+        assert K.TUNED_PLANS == {"0:16:6144:4096:0": (False, 3), "3:64:151936:4096:0": (True, 0)}
+    finally:
+        assert autotune.install(None) == 0 and not K.TUNED_PLANS
