@@ -88,6 +88,13 @@ def build_parser() -> argparse.ArgumentParser:
     ci = sub.add_parser("check-install", help="check python modules, the native library and the GPUs")
     ci.add_argument("--build", action="store_true", help="(re)build the native library first")
     ci.add_argument("--json", action="store_true")
+    au = sub.add_parser("audit-checkpoint", help="inventory, shard digests, decode statistics and (with --reference) "
+                                                 "quantization error of a checkpoint")
+    au.add_argument("checkpoint")
+    au.add_argument("--reference", help="the unquantized checkpoint this one was made from")
+    au.add_argument("--no-digests", action="store_true")
+    au.add_argument("--json", action="store_true")
+    au.add_argument("--verbose", action="store_true")
     s = sub.add_parser("serve", help="serve a checkpoint over OpenAI / Anthropic compatible HTTP")
     s.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
     g = s.add_argument_group("Server")
@@ -192,6 +199,11 @@ def main(argv: list[str] | None = None) -> int:
         return _inspect(args)
     if args.command == "qualify":
         return _qualify(args)
+    if args.command == "audit-checkpoint":
+        from .utils.audit_checkpoint import audit_checkpoint, format_report as format_audit
+        report = audit_checkpoint(args.checkpoint, args.reference, digests=not args.no_digests)
+        print(json.dumps(report, indent=1) if args.json else format_audit(report, args.verbose))
+        return 0 if report["ok"] else 1
     if args.command == "check-install":
         from .utils.check_install import format_report, run_checks
         report = run_checks(build=args.build)
