@@ -125,6 +125,33 @@ def _tokenizer_info(tokenizer, eos_token_id: int, vocab_size: int):
     return _xgr.TokenizerInfo(vocab, vocab_type=_xgr.VocabType.RAW, vocab_size=vocab_size, stop_token_ids=[int(eos_token_id)])
 
 
+def _compile_structural_tag(compiler, spec):
+    """Structural tags: free text in which every occurrence of a trigger opens a tagged region whose body follows a
+    JSON schema (tool calls written inline).  Both wire forms are taken: the engine's own
+    ``{"type": "structural_tag", "format": {...}}`` and the older ``{"structures": [{"begin", "schema", "end"}],
+    "triggers": [...]}`` of the OpenAI-compatible servers."""
+    import json
+    if isinstance(spec, str):
+        spec = json.loads(spec)
+    if not isinstance(spec, dict):
+        raise ValueError("a structural tag is a JSON object")
+    if "structures" in spec:
+        structures, triggers = spec.get("structures"), spec.get("triggers")
+        if not isinstance(structures, list) or not structures or not isinstance(triggers, list) or not triggers:
+            raise ValueError("structural_tag needs non-empty 'structures' and 'triggers'")
+        tags = []
+        for item in structures:
+            if not isinstance(item, dict) or not isinstance(item.get("begin"), str) or not isinstance(item.get("end"), str):
+                raise ValueError("every structure needs 'begin' and 'end' strings")
+            if not any(item["begin"].startswith(t) for t in triggers):
+                raise ValueError(f"no trigger is a prefix of the tag {item['begin']!r}")
+            schema = item.get("schema", {})
+            tags.append(_xgr.StructuralTagItem(begin=item["begin"], schema=schema if isinstance(schema, str) else json.dumps(schema),
+                                               end=item["end"]))
+        return compiler.compile_structural_tag(tags, [str(t) for t in triggers])
+    return compiler.compile_structural_tag(spec)
+
+
 def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_size: int):
     """Build a matcher for a constraint, or ``None`` when the request is unconstrained."""
     if s.kind is StructuredKind.NONE:
@@ -145,6 +172,8 @@ def compile_matcher(s: StructuredOutput, tokenizer, eos_token_id: int, vocab_siz
         compiled = compiler.compile_regex(s.schema)
     elif s.kind is StructuredKind.GRAMMAR:
         compiled = compiler.compile_grammar(s.schema)
+    elif s.kind is StructuredKind.STRUCTURAL_TAG:
+        compiled = _compile_structural_tag(compiler, s.schema)
     else:
         raise RuntimeError(f"unsupported constraint kind {s.kind}")
     return GrammarEngineMatcher(_xgr.GrammarMatcher(compiled), vocab_size)

@@ -296,3 +296,43 @@ def test_grammar_engine_constraints_end_to_end():
         out.append(t)
     doc = json.loads(tok.decode(out))
     assert isinstance(doc["n"], int) and isinstance(doc["ok"], bool) and set(doc) == {"n", "ok"}
+
+
+def test_structural_tags_constrain_only_the_tagged_regions():
+    pytest = __import__("pytest")
+    pytest.importorskip("xgrammar")
+    from cubic_serve_b200.contracts.request import StructuredKind, StructuredOutput
+    from cubic_serve_b200.generation.constraints import compile_matcher
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    tok = ByteTokenizer()
+    eos, vocab = tok.eos_token_id, 512
+
+    def allowed(m):
+        bm = np.zeros(vocab // 32, dtype=np.uint32)
+        m.fill_bitmask(bm)
+        return {i for i in range(vocab) if bm[i // 32] >> (i % 32) & 1}
+
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["a"], "additionalProperties": False}
+    legacy = {"structures": [{"begin": "<tool=add>", "schema": schema, "end": "</tool>"}], "triggers": ["<tool="]}
+    m = compile_matcher(StructuredOutput(StructuredKind.STRUCTURAL_TAG, legacy), tok, eos, vocab)
+    assert {ord("x"), ord("<"), eos} <= allowed(m)                     # free text: anything goes, the answer may end
+    for ch in b'ok <tool=add>{"a"':
+        assert m.accept(ch)
+    inside = allowed(m)
+    assert ord(":") in inside and ord("x") not in inside and eos not in inside     # the schema rules inside the tag
+    for ch in b': 12}</tool> done':
+        assert ch in allowed(m) and m.accept(ch)
+    assert eos in allowed(m)
+    # a tag whose name no structure defines cannot be opened
+    m2 = compile_matcher(StructuredOutput(StructuredKind.STRUCTURAL_TAG, legacy), tok, eos, vocab)
+    for ch in b"<tool=":
+        assert m2.accept(ch)
+    assert allowed(m2) == {ord("a")}
+    current = {"type": "structural_tag", "format": {"type": "triggered_tags", "triggers": ["<f>"], "tags": [
+        {"begin": "<f>", "content": {"type": "json_schema", "json_schema": {"type": "integer"}}, "end": "</f>"}]}}
+    m3 = compile_matcher(StructuredOutput(StructuredKind.STRUCTURAL_TAG, current), tok, eos, vocab)
+    for ch in b"x<f>42</f>":
+        assert m3.accept(ch)
+    with pytest.raises(ValueError):
+        compile_matcher(StructuredOutput(StructuredKind.STRUCTURAL_TAG, {"structures": [{"begin": "<a>", "end": "</a>"}],
+                                                                         "triggers": ["<b"]}), tok, eos, vocab)
