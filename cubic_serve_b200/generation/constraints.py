@@ -83,6 +83,51 @@ class GrammarTransaction:
         self.accepted = 0
 
 
+class DelayedMatcher:
+    """A constraint that starts after the reasoning block: while the model is thinking every token is allowed; once
+    the closing sequence (``</think>``, one or several token ids) has been emitted the inner matcher rules.  Rewindable
+    across the boundary, like the matchers it wraps (reference: delayed constraints of ``generation/constraints.py``)."""
+
+    def __init__(self, inner, end_sequence: list[int]) -> None:
+        if not end_sequence:
+            raise ValueError("a delayed constraint needs the token sequence that ends the reasoning block")
+        self.inner = inner
+        self.end = [int(t) for t in end_sequence]
+        self.free: list[int] = []          # tokens accepted while unconstrained (only the tail is ever looked at)
+        self.active = False
+        self._log: list[bool] = []         # per accepted token: did the inner matcher consume it?
+
+    def fill_bitmask(self, bitmask: np.ndarray) -> None:
+        if self.active:
+            self.inner.fill_bitmask(bitmask)
+        else:
+            bitmask[:] = np.uint32(0xFFFFFFFF)
+
+    def accept(self, token: int) -> bool:
+        if self.active:
+            ok = self.inner.accept(token)
+            if ok:
+                self._log.append(True)
+            return ok
+        self.free.append(int(token))
+        self._log.append(False)
+        if self.free[-len(self.end):] == self.end:
+            self.active = True
+        return True
+
+    def rollback(self, n: int) -> None:
+        for _ in range(n):
+            if self._log.pop():
+                self.inner.rollback(1)
+            else:
+                self.free.pop()
+                self.active = False        # the token that completed the closing sequence is among those taken back
+
+    @property
+    def finished(self) -> bool:
+        return self.active and self.inner.finished
+
+
 class GrammarEngineMatcher:
     """Adapter giving an xgrammar ``GrammarMatcher`` the ``fill_bitmask / accept / rollback`` interface."""
 

@@ -119,6 +119,12 @@ class TokenChatBackend:
         if req.structured.kind is not StructuredKind.NONE and self.engine._mask_words and eos is not None:
             from ..generation.constraints import compile_matcher
             matcher = compile_matcher(req.structured, self.tokenizer, eos, self.engine._mask_words * 32)
+            if matcher is not None and prepared.starts_in_reasoning:
+                # the constraint describes the answer, not the thinking that precedes it
+                from ..generation.constraints import DelayedMatcher
+                end = self._reasoning_end_sequence()
+                if end:
+                    matcher = DelayedMatcher(matcher, end)
         sp = SamplingParams(temperature=s.temperature, top_p=s.top_p, top_k=s.top_k, seed=s.seed, max_tokens=max_tokens,
                             stop_token_ids=tuple(s.stop_token_ids) + ((eos,) if eos is not None else ()),
                             matcher=matcher,
@@ -128,6 +134,19 @@ class TokenChatBackend:
             self._inbox.append((req.request_id, prepared.token_ids, sp))
         self._wake.set()
         return self._events(live)
+
+    def _reasoning_end_sequence(self) -> list[int]:
+        """Token ids of the marker that closes a reasoning block (empty when the tokenizer cannot encode it)."""
+        if not hasattr(self, "_think_end"):
+            try:
+                try:
+                    ids = self.tokenizer.encode("</think>", add_special_tokens=False)
+                except TypeError:
+                    ids = self.tokenizer.encode("</think>")
+                self._think_end = [int(t) for t in ids]
+            except Exception:  # noqa: BLE001 - a tokenizer without the marker leaves the constraint undelayed
+                self._think_end = []
+        return self._think_end
 
     async def _events(self, live: _Live):
         try:

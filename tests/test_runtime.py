@@ -336,3 +336,37 @@ def test_structural_tags_constrain_only_the_tagged_regions():
     with pytest.raises(ValueError):
         compile_matcher(StructuredOutput(StructuredKind.STRUCTURAL_TAG, {"structures": [{"begin": "<a>", "end": "</a>"}],
                                                                          "triggers": ["<b"]}), tok, eos, vocab)
+
+
+def test_delayed_constraint_starts_after_the_reasoning_block():
+    from cubic_serve_b200.generation.constraints import ChoiceMatcher, DelayedMatcher, GrammarTransaction
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    tok = ByteTokenizer()
+    eos = tok.eos_token_id
+    end = list(b"</t>")
+    m = DelayedMatcher(ChoiceMatcher(["yes", "no"], tok, eos), end)
+
+    def allowed(m):
+        bm = np.zeros(16, dtype=np.uint32)
+        m.fill_bitmask(bm)
+        return {i for i in range(512) if bm[i // 32] >> (i % 32) & 1}
+
+    assert len(allowed(m)) == 512 and not m.finished
+    for ch in b"hmm </t":
+        assert m.accept(ch)
+    assert len(allowed(m)) == 512                       # the closing sequence is not complete yet
+    assert m.accept(ord(">")) and m.active
+    assert allowed(m) == {ord("y"), ord("n")}
+    # a speculative round that crosses the boundary and is rejected puts the matcher back into the thinking phase
+    m.rollback(2)
+    assert not m.active and len(allowed(m)) == 512
+    tr = GrammarTransaction(m)
+    for ch in b"t>ye":
+        assert tr.try_accept(ch)
+    tr.commit(3)                                        # keep "t>y", drop "e"
+    assert m.active and allowed(m) == {ord("e")}
+    assert not m.accept(ord("x"))
+    for ch in b"es":
+        assert m.accept(ch)
+    assert allowed(m) == {eos} and m.accept(eos) and m.finished
+    __import__("pytest").raises(ValueError, DelayedMatcher, None, [])
