@@ -12,6 +12,7 @@ chunks (variable token counts) launch the same kernels eagerly.
 """
 from __future__ import annotations
 
+import logging
 from dataclasses import dataclass
 
 import numpy as np
@@ -19,6 +20,9 @@ import torch
 
 from ..models.decoder import DecoderRunner, StepBatch
 from ..ops import kernels as K
+from .graph_runtime import CudaGraphRuntime, GraphState
+
+log = logging.getLogger(__name__)
 
 
 @dataclass
@@ -244,12 +248,12 @@ class GpuExecutor:
         self.out_host = torch.zeros(2, max_rows * rows_per_request, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.use_graphs = use_graphs
         self.graph_masks = False         # True once decode graphs were captured with the mask buffer as an input
-        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.graph_rt = CudaGraphRuntime(resources=(0, 1))      # capture -> qualify -> seal -> replay; result-buffer leases
+        self._leases: list = [None, None]
         self.stream = torch.cuda.Stream(device=self.device)
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self.kernel_launches_last = 0
-        self.graph_launches = {}
         self.timing = False              # record device time of the compute part of every step
         self.device_ms: list[float] = []
         self._ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(2)]
@@ -321,6 +325,7 @@ class GpuExecutor:
         self._mask_buffers()
         self.graph_masks = True
         self.stage.d["mask"] = self._mask_dev
+        rt = CudaGraphRuntime(resources=(0, 1))
         for cap in sorted(caps, reverse=True):
             dummy = [Segment(0, [0], 0, [0])]
             b, _ = self._fill(dummy, pad_rows_to=cap)
@@ -336,10 +341,42 @@ class GpuExecutor:
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=self.stream):
                     self._body(b)
-            self.graphs[cap] = g
-            self.graph_launches[cap] = self.runner.launches_per_step
+                rt.add(cap, g, self.runner.launches_per_step)
+                rt.qualify(cap, lambda slot: self._replay_equals_eager(slot, b, cap))
         torch.cuda.synchronize(self.device)
-        return sorted(self.graphs)
+        ready = rt.seal()
+        self.graph_rt = rt
+        for c, why in rt.poison_log:
+            log.error("decode graph for %d rows is out of service: %s", c, why)
+        return list(ready.sealed)
+
+    def _replay_equals_eager(self, slot, b: StepBatch, cap: int):
+        """Qualification of a captured decode graph: the eager step on the capture inputs and one replay must sample
+        the same ids and produce the same logits (to rounding of differently ordered partial sums).  Runs on
+        ``self.stream``, inside ``capture_decode_graphs``."""
+        self.logits[:cap].zero_()              # rows a step does not write (another pipeline stage samples) compare equal
+        self.out_ids[:cap].fill_(-7)
+        self._body(b)
+        self.stream.synchronize()
+        want_ids, want = self.out_ids[:cap].clone(), self.logits[:cap].float()
+        self.logits[:cap].zero_()
+        self.out_ids[:cap].fill_(-7)
+        slot.graph.replay()
+        self.stream.synchronize()
+        got = self.logits[:cap].float()
+        if not torch.isfinite(got).all():
+            return "the replay produced non-finite logits"
+        err = ((got - want).norm() / want.norm().clamp_min(1e-12)).item()
+        if err > 1e-3:
+            return f"replayed logits differ from the eager step's (relative L2 {err:.3g})"
+        if not torch.equal(self.out_ids[:cap], want_ids):
+            return "the replay sampled other ids than the eager step"
+        return True
+
+    @property
+    def graphs(self) -> dict:
+        """Sealed decode graphs by capacity (read-only view)."""
+        return {c: s.graph for c, s in self.graph_rt.slots.items() if s.state is GraphState.SEALED}
 
     def copy_pages(self, pairs) -> None:
         """Copy-on-write page copies (all layers) ahead of a step."""
@@ -365,17 +402,16 @@ class GpuExecutor:
         """
         total = sum(len(s.token_ids) for s in segs)
         masked = self._stage_masks(segs)
-        decode = (all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and bool(self.graphs)
-                  and (self.graph_masks or not masked))
-        cap = None
-        if decode:
-            cap = next((c for c in sorted(self.graphs) if c >= total), None)
+        decode = (all(len(s.token_ids) == 1 for s in segs) and self.use_graphs and (self.graph_masks or not masked))
+        cap = self.graph_rt.dispatch(total) if decode else None
         if self._upload_pending:
             # the pinned staging buffer is rewritten below: the previous launch's upload must have left it
             self._uploaded.synchronize()
             self._upload_pending = False
         b, rows = self._fill(segs, pad_rows_to=cap)
         k = self._launches & 1
+        # the result buffer of this launch must have been collected: a third outstanding launch is an error, not an overwrite
+        self._leases[k] = self.graph_rt.leases.acquire(k, f"launch {self._launches}")
         self._launches += 1
         with torch.cuda.stream(self.stream):
             h2d = self.stage.upload()
@@ -386,8 +422,7 @@ class GpuExecutor:
             if self.timing:
                 self._ev[k][0].record(self.stream)
             if cap is not None:
-                self.graphs[cap].replay()
-                launches = self.graph_launches[cap]
+                launches = self.graph_rt.replay(cap, self._leases[k]).launches
             else:
                 self._body(b)
                 launches = self.runner.launches_per_step
@@ -402,6 +437,8 @@ class GpuExecutor:
         """Wait for a launched step and return its sampled ids (host array)."""
         k, rows = handle["k"], handle["rows"]
         self._done[k].synchronize()
+        self.graph_rt.leases.release(self._leases[k])
+        self._leases[k] = None
         self.h2d_bytes_last = handle["h2d"]
         self.kernel_launches_last = handle["launches"]
         self.d2h_bytes_last = rows * 4
