@@ -78,6 +78,9 @@ def build_parser() -> argparse.ArgumentParser:
     ins = sub.add_parser("inspect-model", help="print the architecture, quantization and tensor inventory of a checkpoint")
     ins.add_argument("model")
     ins.add_argument("--json", action="store_true")
+    ins.add_argument("--tp", type=int, default=1, help="also print what each rank of this split would own")
+    ins.add_argument("--pp", type=int, default=1)
+    ins.add_argument("--ep", type=int, default=1)
 
     q = sub.add_parser("qualify", help="run the numerical witness checks of the native kernels on this GPU")
     q.add_argument("--device", type=int, default=0)
@@ -174,7 +177,26 @@ def _serve(args) -> int:
 
 def _inspect(args) -> int:
     from .models.checkpoint import inspect_checkpoint
-    info = inspect_checkpoint(args.model)
+    if args.model.startswith("random:"):
+        from .models.config import NAMED_CONFIGS
+        cfg = NAMED_CONFIGS[args.model.split(":", 1)[1]]()
+        info = {"model": cfg.name, "family": cfg.family, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
+                "quantization": f"{cfg.quant.method} {cfg.quant.bits}-bit group {cfg.quant.group_size}"}
+    else:
+        info = inspect_checkpoint(args.model)
+        cfg = None
+    if args.tp * args.pp * args.ep > 1:
+        from pathlib import Path
+
+        from .models.config import ModelConfig
+        from .models.parallel_weights import PartitionError, plan_partition
+        if cfg is None and (Path(args.model) / "config.json").exists():
+            cfg = ModelConfig.from_hf_config(Path(args.model) / "config.json")
+        if cfg is not None:
+            try:
+                info["partition"] = plan_partition(cfg, args.tp, args.pp, args.ep).summary()
+            except PartitionError as exc:
+                info["partition_error"] = str(exc)
     if args.json:
         print(json.dumps(info, indent=1, default=str))
     else:

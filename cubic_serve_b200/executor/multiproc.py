@@ -278,12 +278,30 @@ class MultiprocExecutor:
                 p.kill()
 
 
+def _check_partition(model: str, tp: int, pp: int) -> None:
+    """Refuse a split the model does not admit before any worker is spawned (the planner names what does not divide)."""
+    from ..models.config import NAMED_CONFIGS, ModelConfig
+    from ..models.parallel_weights import PartitionError, plan_partition
+    from pathlib import Path
+    if model.startswith("random:"):
+        cfg = NAMED_CONFIGS[model.split(":", 1)[1]]()
+    elif (Path(model) / "config.json").exists():
+        cfg = ModelConfig.from_hf_config(Path(model) / "config.json")
+    else:
+        return
+    try:
+        plan_partition(cfg, tp, pp)
+    except PartitionError as exc:
+        raise SystemExit(f"--tp-size {tp} --pp-size {pp} does not fit {cfg.name}: {exc}") from exc
+
+
 def build_multiproc_backend(args, devices, tp, spec_cfg, k_bits, v_bits):
     from ..runtime.async_engine import TokenChatBackend
     from ..runtime.engine import LLMEngine
     from ..runtime.scheduler import SchedulerConfig
     from ..runtime.serving import _tokenizer_for
     max_len = args.max_model_len or 8192
+    _check_partition(args.model, tp, args.pp_size)
     spec = WorkerSpec(args.model, devices, tp, k_bits, v_bits, args.max_running_requests, args.token_budget, max_len,
                       None, args.tp_comm, args.seed, args.gpu_reserve_gib, args.pp_size,
                       bool(getattr(args, "enable_kv_cache_rotation", False)))

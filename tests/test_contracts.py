@@ -90,3 +90,57 @@ def test_model_registry_and_adapter_source_policy(tmp_path):
         assert v and any(needle in x.what for x in v), (body, v)
         with pytest.raises(R.ModelRegistryError):
             R.load_adapter(bad)
+
+
+def test_axis_spans_and_partition_plans():
+    import pytest
+    from cubic_serve_b200.models.config import NAMED_CONFIGS
+    from cubic_serve_b200.models.parallel_weights import AxisSpan, PartitionError, plan_partition, storage_bits
+    s = AxisSpan.shard(32, 3, 8)
+    assert (s.start, s.stop, s.size) == (12, 16, 4) and s.scaled(128).slice() == slice(1536, 2048) and not s.full
+    assert AxisSpan.whole(7).full
+    with pytest.raises(PartitionError):
+        AxisSpan.shard(12288, 0, 5)
+    with pytest.raises(PartitionError, match="multiples of 64"):
+        AxisSpan.shard(768, 0, 8, 64)
+    with pytest.raises(PartitionError):
+        AxisSpan(3, 2, 10)
+    dense = NAMED_CONFIGS["dense-8b"]()
+    one = plan_partition(dense).ranks[0]
+    assert 4.3 < storage_bits(dense) < 4.5
+    assert 5.5e9 < one.weight_bytes < 7.5e9                   # ~6.4 GB of 4-bit weights + bf16 embedding and head
+    plan = plan_partition(dense, tp=4, pp=2)
+    assert [r["stage"] for r in plan.summary()] == [0, 0, 0, 0, 1, 1, 1, 1]
+    r5 = plan.ranks[5]
+    assert r5.tensor_rank == 1 and r5.layers == (18, 36) and r5.experts is None
+    q = next(x for x in r5.shares if x.module == "model.layers.18.self_attn.q_proj")
+    o = next(x for x in r5.shares if x.module == "model.layers.18.self_attn.o_proj")
+    assert (q.rows.start, q.rows.stop, q.cols.full) == (1024, 2048, True) and (o.cols.start, o.cols.stop) == (1024, 2048)
+    total = sum(r.weight_bytes for r in plan.ranks)
+    assert abs(total - one.weight_bytes) / one.weight_bytes < 0.25         # a split moves bytes, it does not create many
+    with pytest.raises(PartitionError, match="key/value heads"):
+        plan_partition(dense, tp=16)
+    import dataclasses
+    moe = NAMED_CONFIGS["moe-30b-a3b"]()
+    with pytest.raises(PartitionError, match="key/value heads"):
+        plan_partition(moe, tp=8)                              # 4 key/value heads
+    wide = dataclasses.replace(moe, num_kv_heads=8)
+    with pytest.raises(PartitionError, match="expert intermediate size"):
+        plan_partition(wide, tp=8)                             # 768 / 8 = 96 columns: not a multiple of the K block
+    ep = plan_partition(wide, tp=8, ep=8)                      # whole experts per rank instead
+    assert ep.ranks[3].experts.size == moe.num_experts // 8 and ep.ranks[3].experts.start == 3 * (moe.num_experts // 8)
+    assert plan_partition(moe, tp=4).ranks[0].experts.full
+    hybrid = plan_partition(NAMED_CONFIGS["hybrid-8b"](), tp=2)
+    assert any(x.module.endswith("linear_attn.in_proj_qkvz") for x in hybrid.ranks[1].shares)
+    with pytest.raises(PartitionError):
+        plan_partition(dense, pp=99)
+
+
+def test_inspect_model_prints_partitions(capsys):
+    import json
+    from cubic_serve_b200.cli import main
+    assert main(["inspect-model", "random:dense-8b", "--tp", "2", "--json"]) == 0
+    info = json.loads(capsys.readouterr().out)
+    assert len(info["partition"]) == 2 and info["partition"][1]["tensor_rank"] == 1
+    assert main(["inspect-model", "random:dense-8b", "--tp", "3", "--json"]) == 0
+    assert "partition_error" in json.loads(capsys.readouterr().out)
