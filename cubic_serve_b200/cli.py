@@ -33,15 +33,17 @@ def parse_speculative_config(text: str | None) -> SpeculativeConfig:
         cfg = json.loads(text)
     except ValueError as exc:
         raise argparse.ArgumentTypeError(f"--speculative-config is not valid JSON: {exc}") from exc
-    if not isinstance(cfg, dict) or cfg.get("method") != "mtp":
-        raise argparse.ArgumentTypeError('--speculative-config needs {"method": "mtp", ...}')
+    if not isinstance(cfg, dict) or cfg.get("method") not in ("mtp", "ngram"):
+        raise argparse.ArgumentTypeError('--speculative-config needs {"method": "mtp" | "ngram", ...}')
     n = cfg.get("num_speculative_tokens")
     if not isinstance(n, int) or not 1 <= n <= 7:
         raise argparse.ArgumentTypeError("num_speculative_tokens must be an integer in [1, 7]")
     mode = cfg.get("mode", "fixed")
     if mode not in ("fixed", "dynamic"):
         raise argparse.ArgumentTypeError("mode must be fixed or dynamic")
-    return SpeculativeConfig("mtp", n, mode, int(cfg.get("max_tokens", n)), cfg.get("policy"))
+    if cfg["method"] == "ngram" and mode != "fixed":
+        raise argparse.ArgumentTypeError("n-gram drafts have no planned length: a request without a match drafts nothing")
+    return SpeculativeConfig(cfg["method"], n, mode, int(cfg.get("max_tokens", n)), cfg.get("policy"))
 
 
 def parse_devices(text: str | None) -> list[int]:
@@ -69,6 +71,8 @@ def validate_topology(devices: list[int], tp: int, pp: int, ep: int, spec: Specu
         raise SystemExit("--ep-size must divide --tp-size")
     if spec.method == "mtp" and pp != 1:
         raise SystemExit("MTP speculative decoding requires --pp-size 1")
+    if spec.method in ("mtp", "ngram") and tp * pp != 1:
+        raise SystemExit("speculative decoding runs in the single-process executor: use one device")
 
 
 def build_parser() -> argparse.ArgumentParser:

@@ -134,35 +134,8 @@ class SpeculativeGpuExecutor(GpuExecutor):
                 launches += self.mtp.launches + 4
             if self.timing:
                 self._ev_mid.record(self.stream)
-            # ---- target review over [root, d1 .. dK]
-            review = [Segment(s.request_slot, [s.token_ids[0]] + [0] * Kd, s.start, s.pages, True, uid=s.uid) for s in segs]
-            b, _ = self._fill(review)
-            T = R * (Kd + 1)
-            self.stage.h["logit_rows"][:T] = np.arange(T)
-            self.stage.h["temperature"][:T] = 0
-            self.stage.upload()
-            toks = torch.cat([torch.tensor([s.token_ids[0] for s in segs], dtype=torch.int32, device=dev)[:, None],
-                              draft_ids], 1).reshape(-1)
-            self.stage.d["token_ids"][:T].copy_(toks)
-            b.num_logit_rows = T
-            hidden = r.forward_hidden(b)
-            logits_buf = self._review_logits(T)
-            logits = r.forward_logits(b, hidden, logits_buf)
-            tgt = target_ids.view(-1)
-            K.sample(logits, tgt, vocab=logits.shape[1])
+            hidden = self._review_and_verify(segs, Kd, draft_ids, target_ids)
             launches += r.launches_per_step + 1
-            # ---- verification
-            forced = None
-            if self.force_acceptance is not None:
-                draws = self._rng.random((R, Kd)) < self.force_acceptance
-                first_fail = np.where(draws.all(1), Kd, draws.argmin(1)).astype(np.int32)
-                self.forced[:R].copy_(torch.from_numpy(first_fail), non_blocking=True)
-                forced = self.forced
-                # forced acceptance: the draft is *declared* equal to the target up to the drawn depth
-                agree = target_ids[:, :Kd].clone()
-                keep = torch.arange(Kd, device=dev)[None, :] < self.forced[:R, None]
-                draft_ids.copy_(torch.where(keep, agree, draft_ids))
-            K.verify_greedy(target_ids, draft_ids, self.depth_t[:R], Kd, self.accepted, self.bonus, forced)
             rows = torch.arange(R, device=dev) * (Kd + 1) + self.accepted[:R].long()
             self.last_hidden.index_copy_(0, sl, hidden.index_select(0, rows))
             if self.timing:
@@ -188,7 +161,125 @@ class SpeculativeGpuExecutor(GpuExecutor):
         self.d2h_bytes_last = R * (Kd + 2) * 4
         return out
 
+    def _review_and_verify(self, segs: list[Segment], Kd: int, draft_ids: torch.Tensor, target_ids: torch.Tensor) -> torch.Tensor:
+        """ONE target pass over ``[root, d1 .. dK]`` of every request (greedy ids of all rows into ``target_ids``) and
+        the device-side verification (``self.accepted``, ``self.bonus``; per-request depths in ``self.depth_t``).
+        Runs on ``self.stream``; returns the hidden states of the review rows."""
+        r, dev = self.runner, self.device
+        R = len(segs)
+        review = [Segment(s.request_slot, [s.token_ids[0]] + [0] * Kd, s.start, s.pages, True, uid=s.uid) for s in segs]
+        b, _ = self._fill(review)
+        T = R * (Kd + 1)
+        self.stage.h["logit_rows"][:T] = np.arange(T)
+        self.stage.h["temperature"][:T] = 0
+        self.h2d_bytes_last = self.stage.upload()
+        toks = torch.cat([torch.tensor([s.token_ids[0] for s in segs], dtype=torch.int32, device=dev)[:, None],
+                          draft_ids], 1).reshape(-1)
+        self.stage.d["token_ids"][:T].copy_(toks)
+        b.num_logit_rows = T
+        hidden = r.forward_hidden(b)
+        logits = r.forward_logits(b, hidden, self._review_logits(T))
+        K.sample(logits, target_ids.view(-1), vocab=logits.shape[1])
+        forced = None
+        if self.force_acceptance is not None:
+            draws = self._rng.random((R, Kd)) < self.force_acceptance
+            first_fail = np.where(draws.all(1), Kd, draws.argmin(1)).astype(np.int32)
+            self.forced[:R].copy_(torch.from_numpy(first_fail), non_blocking=True)
+            forced = self.forced
+            # forced acceptance: the draft is *declared* equal to the target up to the drawn depth
+            agree = target_ids[:, :Kd].clone()
+            keep = torch.arange(Kd, device=dev)[None, :] < self.forced[:R, None]
+            draft_ids.copy_(torch.where(keep, agree, draft_ids))
+        K.verify_greedy(target_ids, draft_ids, self.depth_t[:R], Kd, self.accepted, self.bonus, forced)
+        return hidden
+
     def _review_logits(self, rows: int) -> torch.Tensor:
         if not hasattr(self, "_rl") or self._rl.shape[0] < rows:
             self._rl = torch.empty(rows, self.runner.w.lm_head.n, dtype=torch.bfloat16, device=self.device)
         return self._rl
+
+
+class NgramSpeculativeGpuExecutor(SpeculativeGpuExecutor):
+    """Speculative rounds whose drafts come from the host (n-gram / prompt lookup, ``runtime/ngram.py``): no draft
+    model, no proposal passes, no carried hidden state -- a round is the target review over ``[root, d1 .. dk]`` plus
+    the device-side verification.  Requests without a draft take part with depth 0 (their row is a plain decode row);
+    a step in which nobody has a draft is a plain decode step and replays the captured decode graphs."""
+
+    draft_source = "ngram"
+
+    def __init__(self, runner, depth: int, **kw) -> None:
+        if runner.cfg.is_hybrid:
+            raise NotImplementedError("speculative decoding is not available for models with Gated DeltaNet layers")
+        kw.setdefault("use_graphs", True)
+        GpuExecutor.__init__(self, runner, rows_per_request=depth + 1, **kw)
+        self.mtp = None
+        self.speculative_depth = depth
+        self.force_acceptance = None
+        dev, rows = self.device, self.max_rows
+        self.draft_ids = torch.zeros(rows, depth, dtype=torch.int32, device=dev)
+        self.target_ids = torch.zeros(rows, depth + 1, dtype=torch.int32, device=dev)
+        self.accepted = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.bonus = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.depth_t = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.forced = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self._draft_host = torch.zeros(rows, depth, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0}
+
+    def execute(self, segs):
+        return GpuExecutor.execute(self, segs)
+
+    def execute_speculative(self, segs: list[Segment], depths: list[int] | None = None, drafts: list[list[int]] | None = None):
+        """``drafts[i]``: the host's proposal for request ``i`` (possibly empty, at most the configured depth;
+        ``depths`` may shorten it further).  Returns per request the emitted tokens."""
+        R = len(segs)
+        drafts = [list(d)[:self.speculative_depth] for d in (drafts or [[]] * R)]
+        if depths is not None:
+            drafts = [d[:max(0, int(k))] for d, k in zip(drafts, depths)]
+        per_req = [len(d) for d in drafts]
+        Kd = max(per_req, default=0)
+        if Kd == 0:
+            ids = self.execute(segs)
+            self.last_round = {"depth": 0, "accepted": [0] * R, "proposed": [0] * R, "proposal_ms": 0.0,
+                               "target_ms": self.device_ms[-1] if (self.timing and self.device_ms) else 0.0}
+            return [[int(t)] for t in ids]
+        dev = self.device
+        draft_ids = self.draft_ids.view(-1)[:R * Kd].view(R, Kd)
+        target_ids = self.target_ids.view(-1)[:R * (Kd + 1)].view(R, Kd + 1)
+        host = self._draft_host.view(-1)[:R * Kd].view(R, Kd)
+        host.zero_()
+        for i, d in enumerate(drafts):
+            if d:
+                host[i, :len(d)] = torch.tensor(d, dtype=torch.int32)
+        if self._upload_pending:
+            self._uploaded.synchronize()                    # a plain step's staging upload may still be in flight
+            self._upload_pending = False
+        with torch.cuda.stream(self.stream):
+            ev0, ev1 = self._ev[0]
+            if self.timing:
+                ev0.record(self.stream)
+            draft_ids.copy_(host, non_blocking=True)
+            self.depth_t[:R].copy_(torch.tensor(per_req, dtype=torch.int32), non_blocking=True)
+            self._review_and_verify(segs, Kd, draft_ids, target_ids)
+            if self.timing:
+                ev1.record(self.stream)
+            acc = self.accepted[:R].cpu()
+            tg = target_ids.cpu()
+            self.stream.synchronize()
+        tgt_ms = 0.0
+        if self.timing:
+            tgt_ms = ev0.elapsed_time(ev1)
+            self.device_ms.append(tgt_ms)
+        out = []
+        for i in range(R):
+            a = int(acc[i])
+            out.append([int(t) for t in tg[i, :a + 1]])
+            self.stats["accepted"] += a
+            self.stats["emitted"] += a + 1
+        self.stats["rounds"] += 1
+        self.stats["proposed"] += sum(per_req)
+        self.last_round = {"depth": Kd, "accepted": [int(a) for a in acc], "proposed": per_req, "proposal_ms": 0.0,
+                           "target_ms": tgt_ms}
+        self.kernel_launches_last = self.runner.launches_per_step + 3
+        self.h2d_bytes_last += R * Kd * 4
+        self.d2h_bytes_last = R * (Kd + 2) * 4
+        return out

@@ -55,6 +55,7 @@ class LLMEngine:
         # launch the next decode step before this one's results are read (steady decode state only)
         self.overlap_decode = True
         self._ahead = None
+        self.ngram = None                # n-gram draft proposer (created by the first round of an n-gram executor)
         self._ahead_stale = False
         self._budget_sig: dict[str, tuple[int, int]] = {}
         self._draft_states: dict = {}
@@ -179,7 +180,9 @@ class LLMEngine:
         segs = self._segments(plan)
         spec = getattr(self.executor, "speculative_depth", 0)
         constrained = any(s.mask is not None for s in segs)
-        if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample for s in segs):
+        # rounds verify drafts against the target's greedy choice, so they serve greedy requests; a step with a sampled
+        # (temperature > 0) or constrained request runs the plain way
+        if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample and s.temperature == 0 for s in segs):
             # speculative round: every request gets its accepted drafts plus one bonus token
             ids = self._speculative_round(plan, segs, spec)
             self.spec_rounds = getattr(self, "spec_rounds", 0) + 1
@@ -219,6 +222,8 @@ class LLMEngine:
             if fin is not None:
                 self.requests.pop(rid, None)
                 self._draft_states.pop(rid, None)
+                if self.ngram is not None:
+                    self.ngram.forget(rid)
                 self._budget_sig.pop(rid, None)
         return outs
 
@@ -230,6 +235,8 @@ class LLMEngine:
         self.draft_planner = DraftPlanner(graph_capacities, self._draft_cfg)
 
     def _speculative_round(self, plan: BatchPlan, segs: list, max_depth: int):
+        if getattr(self.executor, "draft_source", "model") == "ngram":
+            return self._ngram_round(plan, segs, max_depth)
         if self.draft_planner is None:
             return self.executor.execute_speculative(segs)
         from .speculative import RequestDraftState
@@ -250,6 +257,19 @@ class LLMEngine:
                 self.draft_planner.observe_round(sum(p + 1 for p in info["proposed"]), info["target_ms"], len(rids),
                                                  info["proposal_ms"], info["depth"])
         return ids
+
+    def _ngram_round(self, plan: BatchPlan, segs: list, max_depth: int):
+        """Drafts from the requests' own token histories (``runtime/ngram.py``); a request proposes at most what its
+        token limit still allows."""
+        if self.ngram is None:
+            from .ngram import NgramProposer
+            self.ngram = NgramProposer()
+        drafts = []
+        for s in plan.segments:
+            r = s.request
+            room = max(0, r.sampling.max_tokens - len(r.output) - 1)
+            drafts.append(self.ngram.propose(r.request_id, r.tokens, min(max_depth, room)))
+        return self.executor.execute_speculative(segs, drafts=drafts)
 
     def generate(self, prompts: list[list[int]], sampling: SamplingParams | None = None) -> list[list[int]]:
         """Blocking helper: run all prompts to completion, return the generated ids per prompt."""

@@ -118,7 +118,14 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
                                    max_requests=args.max_running_requests,
                                    kv_rotation=bool(getattr(args, "enable_kv_cache_rotation", False)))
         depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None else 0
-        if depth:
+        if depth and getattr(spec, "method", "mtp") == "ngram":
+            # prompt-lookup drafts: no draft model; steps without a draft replay the decode graphs
+            from ..executor.spec_executor import NgramSpeculativeGpuExecutor
+            executor = NgramSpeculativeGpuExecutor(runner, depth, max_rows=args.max_running_requests,
+                                                   max_prefill_tokens=args.token_budget, max_model_len=max_len)
+            caps = executor.capture_decode_graphs()
+            log.info("n-gram speculative decoding: depth %d; decode graphs %s; %d KV pages", depth, caps, pages)
+        elif depth:
             # MTP speculative decoding (--speculative-config): draft head + review rounds instead of graph decode
             from ..executor.spec_executor import SpeculativeGpuExecutor
             from ..models.mtp import MtpRunner, random_mtp_weights

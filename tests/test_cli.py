@@ -16,7 +16,14 @@ def test_serve_flag_surface():
     assert a.thinking is False and a.k_cache_dtype == "int4"
     spec = cli.parse_speculative_config(a.speculative_config)
     assert (spec.method, spec.num_speculative_tokens, spec.mode) == ("mtp", 3, "dynamic")
-    cli.validate_topology([0, 1, 2, 3], 4, 1, 2, spec)
+    cli.validate_topology([0, 1, 2, 3], 4, 1, 2, cli.SpeculativeConfig())
+    cli.validate_topology([0], 1, 1, 1, spec)
+    with pytest.raises(SystemExit):                      # rounds run in the single-process executor only
+        cli.validate_topology([0, 1, 2, 3], 4, 1, 2, spec)
+    ngram = cli.parse_speculative_config('{"method":"ngram","num_speculative_tokens":4}')
+    assert (ngram.method, ngram.num_speculative_tokens, ngram.mode) == ("ngram", 4, "fixed")
+    with pytest.raises(argparse.ArgumentTypeError):
+        cli.parse_speculative_config('{"method":"ngram","num_speculative_tokens":4,"mode":"dynamic"}')
 
 
 @pytest.mark.parametrize("text", ['{"method":"eagle"}', '{"method":"mtp","num_speculative_tokens":9}', "not json",

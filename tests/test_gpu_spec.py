@@ -80,3 +80,38 @@ def test_dynamic_draft_length_stays_lossless_and_adapts():
     # fewer proposals than the fixed depth would have made: the planner shortened / stopped the drafts
     assert ex2.stats["proposed"] < ex2.stats["rounds"] * 3 * len(prompts)
     assert eng2.pool.num_used == 0
+
+
+def test_ngram_rounds_match_plain_greedy_and_accept_repetitions():
+    """Prompt-lookup drafts verified by the target: the same tokens as plain greedy decoding; a model made to repeat
+    itself gets most of its tokens from accepted drafts; steps without a draft replay the decode graphs."""
+    from cubic_serve_b200.executor.spec_executor import NgramSpeculativeGpuExecutor
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    rng = np.random.default_rng(3)
+    base = [rng.integers(0, 2048, n).tolist() for n in (9, 14, 11)]
+    prompts = [p * 4 for p in base]                          # repeated context: the drafts have something to find
+    eng, ex, runner = _build(0)
+    plain = eng.generate(prompts, SamplingParams(max_tokens=24, ignore_eos=True))
+    dev = torch.device("cuda")
+    cfg = runner.cfg
+    runner2 = DecoderRunner(cfg, random_decoder_weights(cfg, dev, seed=0, std=0.05), num_pages=128, max_tokens=512)
+    ex2 = NgramSpeculativeGpuExecutor(runner2, 3, max_rows=8, max_prefill_tokens=512, max_model_len=256)
+    assert ex2.capture_decode_graphs([4, 8]) == [4, 8]
+    eng2 = LLMEngine(ex2, 128, SchedulerConfig(max_running_requests=8, max_model_len=256, max_batched_tokens=512,
+                                               enable_prefix_cache=False))
+    spec = eng2.generate(prompts, SamplingParams(max_tokens=24, ignore_eos=True))
+    runner2.ws.check_status()
+    assert all(len(o) == 24 for o in spec)
+    agree = np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)])
+    assert agree >= 0.9, (agree, plain[0], spec[0])
+    assert ex2.stats["rounds"] > 0 and ex2.stats["proposed"] > 0
+    assert ex2.stats["accepted"] <= ex2.stats["proposed"]
+    assert eng2.pool.num_used == 0
+    # a sequence the proposer cannot have seen twice (a short random prompt) takes plain graph-replayed decode steps
+    eng3 = LLMEngine(ex2, 128, SchedulerConfig(max_running_requests=8, max_model_len=256, max_batched_tokens=512,
+                                               enable_prefix_cache=False))
+    before = dict(ex2.graph_rt.stats()["slots"][4])
+    eng3.generate([rng.integers(0, 2048, 6).tolist()], SamplingParams(max_tokens=3, ignore_eos=True))
+    assert ex2.graph_rt.stats()["slots"][4]["replays"] > before["replays"]

@@ -127,3 +127,94 @@ def test_engine_round_loop_uses_planned_depths():
     flat = [d for round_ in ex.seen for d in round_]
     assert all(a >= b for a, b in zip([r[0] for r in ex.seen], [r[0] for r in ex.seen][1:]))   # monotone, one level a time
     assert set(flat) <= {0, 1, 2, 3}
+
+
+def test_ngram_index_proposes_what_followed_the_latest_match():
+    from cubic_serve_b200.runtime.ngram import NgramIndex, NgramProposer
+    i = NgramIndex(max_n=4, min_n=2)
+    i.extend([1, 2, 3, 4, 5, 1, 2, 3])
+    assert i.propose(3) == [4, 5, 1] and i.propose(5) == [4, 5, 1, 2, 3] and i.propose(0) == []
+    i.extend([9, 1, 2, 3])                                   # the latest occurrence wins: after "1 2 3" came 9
+    assert i.propose(2) == [9, 1]
+    loop = NgramIndex(3, 2)
+    loop.extend([7, 8, 7, 8])
+    assert loop.propose(5) == [7, 8, 7, 8, 7]                # a repetition continues into itself
+    fresh = NgramIndex()
+    fresh.extend([1, 2, 3, 4])
+    assert fresh.propose(3) == []
+    fresh.truncate(2)
+    assert fresh.tokens == [1, 2]
+    import pytest
+    with pytest.raises(ValueError):
+        NgramIndex(max_n=1, min_n=2)
+    p = NgramProposer()
+    assert p.propose("a", [5, 6, 7, 5, 6], 2) == [7, 5]
+    assert p.propose("a", [5, 6, 7, 5, 6, 7], 2) == [5, 6]   # incremental: only the new token is indexed
+    assert p.propose("a", [1, 2], 2) == []                   # another sequence under the same id: rebuilt
+    p.forget("a")
+    assert p.stats == {"lookups": 3, "hits": 2, "proposed": 4}
+
+
+def test_engine_ngram_rounds_are_lossless_on_a_deterministic_model():
+    """A fake target whose next token is a function of the previous one: rounds verified against it must emit exactly
+    the plain greedy sequence, in fewer steps once the sequence starts repeating."""
+    import numpy as np
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+
+    def nxt(t):
+        return (t * 5 + 3) % 11                              # a short cycle: the n-gram index soon predicts it
+
+    class FakeNgram:
+        speculative_depth = 4
+        draft_source = "ngram"
+        vocab_size = 64
+
+        def __init__(self):
+            self.rounds, self.accepted, self.plain = 0, 0, 0
+
+        def copy_pages(self, pairs):
+            pass
+
+        def execute(self, segs):
+            self.plain += 1
+            return np.asarray([nxt(int(s.token_ids[-1])) for s in segs if s.sample], dtype=np.int32)
+
+        def execute_speculative(self, segs, depths=None, drafts=None):
+            self.rounds += 1
+            out = []
+            for s, d in zip(segs, drafts):
+                assert len(d) <= self.speculative_depth
+                cur, emitted = int(s.token_ids[0]), []
+                for tok in d:
+                    want = nxt(cur)
+                    if tok != want:
+                        break
+                    emitted.append(want)
+                    cur = want
+                self.accepted += len(emitted)
+                emitted.append(nxt(cur))                      # bonus token
+                out.append(emitted)
+            return out
+
+    def run(executor):
+        eng = LLMEngine(executor, num_pages=64, scheduler_config=SchedulerConfig(max_running_requests=4, max_model_len=256,
+                                                                                  enable_prefix_cache=False))
+        out = eng.generate([[1, 2, 3], [4, 9]], SamplingParams(max_tokens=40, ignore_eos=True))
+        return out, eng
+
+    class Plain(FakeNgram):
+        speculative_depth = 0
+
+    want, plain_eng = run(Plain())
+    ex = FakeNgram()
+    got, eng = run(ex)
+    assert got == want and all(len(o) == 40 for o in got)
+    assert ex.accepted > 40 and eng.steps < plain_eng.steps // 2      # most tokens came from accepted drafts
+    assert eng.ngram.stats["hits"] > 0 and not eng.ngram._index       # indices are dropped with their requests
+    # a sampled (temperature > 0) request takes the plain path
+    ex2 = FakeNgram()
+    eng2 = LLMEngine(ex2, num_pages=64, scheduler_config=SchedulerConfig(max_running_requests=4, max_model_len=256,
+                                                                         enable_prefix_cache=False))
+    eng2.generate([[1, 2, 3]], SamplingParams(max_tokens=8, ignore_eos=True, temperature=0.8, seed=1))
+    assert ex2.rounds == 0 and ex2.plain > 0
