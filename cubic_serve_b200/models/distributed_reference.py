@@ -1,0 +1,147 @@
+"""Eager tensor x pipeline parallel reference decoder over ``torch.distributed`` (gloo on CPU, NCCL on GPUs).
+
+The oracle for everything that shards a model: every rank holds exactly the rows / columns of every weight that
+``parallel_weights.plan_partition`` assigns to it, computes with plain PyTorch in fp32, and meets the others only in
+the reference collectives below.  Partial sums are gathered and added in rank order, so the result does not depend on
+arrival order and equals the single-process ``EagerDecoder`` up to fp32 summation order.  It is slow on purpose: one
+collective per operator, no fusion, no overlap -- the thing the fused kernels are compared with, never a serving path.
+
+Reference counterpart: ``executor/distributed_reference.py`` (bit-exact eager TP x PP reference, operands gathered per
+operator) and the reference collectives of ``executor/eager_nccl.py`` (``tp_all_reduce``, ``tp_all_gather``,
+``pipeline_send`` / ``pipeline_recv``).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import eager
+from .config import ModelConfig
+from .parallel_weights import PartitionPlan, RankPartition
+from .reference import DenseLayer, DenseWeights
+
+
+# ------------------------------------------------------------------ reference collectives
+def tp_all_gather(x: torch.Tensor, group, dim: int = -1) -> torch.Tensor:
+    """Concatenation of every rank's ``x`` along ``dim`` in rank order."""
+    parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim)
+
+
+def tp_all_reduce(x: torch.Tensor, group) -> torch.Tensor:
+    """Sum of every rank's ``x``, added in rank order (identical bits on all ranks)."""
+    parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    total = parts[0].clone()
+    for p in parts[1:]:
+        total += p
+    return total
+
+
+def pipeline_send(x: torch.Tensor, dst: int) -> None:
+    dist.send(x.contiguous(), dst)
+
+
+def pipeline_recv(like: torch.Tensor, src: int) -> torch.Tensor:
+    out = torch.empty_like(like)
+    dist.recv(out, src)
+    return out
+
+
+# ------------------------------------------------------------------ sharding by the ownership plan
+def shard_dense_weights(w: DenseWeights, cfg: ModelConfig, part: RankPartition) -> DenseWeights:
+    """The rank's shard of dense reference weights, cut by the spans of its ``RankPartition`` (layers of its stage
+    only; embedding and head are split over the vocabulary)."""
+    spans = {s.module: s for s in part.shares}
+
+    def cut(t: torch.Tensor, module: str) -> torch.Tensor:
+        s = spans[module]
+        assert tuple(t.shape) == (s.rows.total, s.cols.total), (module, tuple(t.shape), s)
+        return t[s.rows.slice(), s.cols.slice()].contiguous()
+
+    layers = []
+    for i in range(*part.layers):
+        l, p = w.layers[i], f"model.layers.{i}"
+        layers.append(DenseLayer(
+            l.ln1, l.ln2, cut(l.wq, f"{p}.self_attn.q_proj"), cut(l.wk, f"{p}.self_attn.k_proj"),
+            cut(l.wv, f"{p}.self_attn.v_proj"), cut(l.wo, f"{p}.self_attn.o_proj"), cut(l.w_gate, f"{p}.mlp.gate_proj"),
+            cut(l.w_up, f"{p}.mlp.up_proj"), cut(l.w_down, f"{p}.mlp.down_proj"), l.q_norm, l.k_norm))
+    return DenseWeights(w.embed, layers, w.final_norm, w.lm_head)
+
+
+class DistributedEagerDecoder:
+    """One rank of the reference.  ``tp_group``: the ranks of this stage; ``prev`` / ``next``: global ranks of the
+    same tensor rank in the neighbouring stages (None at the ends)."""
+
+    def __init__(self, cfg: ModelConfig, plan: PartitionPlan, rank: int, full: DenseWeights, tp_group) -> None:
+        self.cfg, self.plan, self.part = cfg, plan, plan.ranks[rank]
+        self.w = shard_dense_weights(full, cfg, self.part)
+        self.tp_group, self.tp = tp_group, plan.tp
+        self.prev = rank - plan.tp if self.part.stage > 0 else None
+        self.next = rank + plan.tp if self.part.stage < plan.pp - 1 else None
+        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta)
+        v = cfg.vocab_size // plan.tp
+        self.vocab = slice(self.part.tensor_rank * v, (self.part.tensor_rank + 1) * v)
+
+    def _sum(self, x: torch.Tensor) -> torch.Tensor:
+        return tp_all_reduce(x, self.tp_group) if self.tp > 1 else x
+
+    @torch.no_grad()
+    def forward(self, tokens: torch.Tensor, start: int, cache: list | None):
+        """As ``EagerDecoder.forward`` for this rank's heads and layers.  Returns the full-vocabulary logits on the
+        ranks of the last stage (None elsewhere) and this rank's cache."""
+        cfg, w = self.cfg, self.w
+        B, S = tokens.shape
+        D = cfg.head_dim
+        Hq, Hkv = cfg.num_q_heads // self.tp, cfg.num_kv_heads // self.tp
+        pos = torch.arange(start, start + S)
+        if self.prev is None:
+            h = w.embed[tokens].float()
+        else:
+            h = pipeline_recv(torch.empty(B, S, cfg.hidden_size), self.prev)
+        new_cache = []
+        for li, l in enumerate(w.layers):
+            x = eager.rmsnorm(h, l.ln1, cfg.rms_eps, cfg.zero_centered_norm)
+            q = (x @ l.wq.t()).view(B, S, Hq, D)
+            k = (x @ l.wk.t()).view(B, S, Hkv, D)
+            v = (x @ l.wv.t()).view(B, S, Hkv, D)
+            if l.q_norm is not None:
+                q = eager.rmsnorm(q, l.q_norm, cfg.rms_eps)
+                k = eager.rmsnorm(k, l.k_norm, cfg.rms_eps)
+            q = torch.stack([eager.rope(q[b], pos, self.inv_freq) for b in range(B)])
+            k = torch.stack([eager.rope(k[b], pos, self.inv_freq) for b in range(B)])
+            if cache is not None and cache[li] is not None:
+                k = torch.cat([cache[li][0], k], 1)
+                v = torch.cat([cache[li][1], v], 1)
+            new_cache.append((k, v))
+            vis = torch.arange(start + 1, start + S + 1)
+            attn = torch.stack([eager.attention_rows(q[b], k[b], v[b], vis) for b in range(B)])
+            h = h + self._sum(attn.reshape(B, S, Hq * D) @ l.wo.t())            # row-parallel: partial sums
+            x = eager.rmsnorm(h, l.ln2, cfg.rms_eps, cfg.zero_centered_norm)
+            h = h + self._sum((torch.nn.functional.silu(x @ l.w_gate.t()) * (x @ l.w_up.t())) @ l.w_down.t())
+        if self.next is not None:
+            pipeline_send(h, self.next)
+            return None, new_cache
+        local = eager.rmsnorm(h, w.final_norm, cfg.rms_eps, cfg.zero_centered_norm) @ w.lm_head[self.vocab].t()
+        logits = tp_all_gather(local, self.tp_group) if self.tp > 1 else local
+        return logits, new_cache
+
+    @torch.no_grad()
+    def generate(self, prompts: torch.Tensor, steps: int, world_group=None):
+        """Greedy decode on all ranks; the last stage's choice is broadcast so that every rank feeds the same token.
+        Returns ``(tokens [B, steps], logits of every step)`` -- logits are None except on the last stage."""
+        last_stage_rank0 = (self.plan.pp - 1) * self.plan.tp
+        out, all_logits = [], []
+        cache = None
+        tokens, start = prompts, 0
+        for _ in range(steps):
+            logits, cache = self.forward(tokens, start, cache)
+            nxt = logits[:, -1].argmax(-1) if logits is not None else torch.zeros(prompts.shape[0], dtype=torch.long)
+            if self.plan.pp > 1:
+                dist.broadcast(nxt, last_stage_rank0, group=world_group)
+            out.append(nxt)
+            all_logits.append(None if logits is None else logits[:, -1])
+            start += tokens.shape[1]
+            tokens = nxt[:, None]
+        return torch.stack(out, 1), all_logits

@@ -1,0 +1,79 @@
+"""The eager TP x PP reference over gloo equals the single-process eager decoder."""
+import datetime
+import multiprocessing as mp
+import os
+import socket
+
+import pytest
+import torch
+
+from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+
+
+def _cfg():
+    return ModelConfig(name="dist-toy", num_layers=4, hidden_size=64, num_q_heads=4, num_kv_heads=2, head_dim=16,
+                       intermediate_size=128, vocab_size=128, rope_theta=1e4, qk_norm=True, quant=QuantSpec("none", 16, 0))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank(rank, world, tp, pp, port, q):
+    import torch.distributed as dist
+    from cubic_serve_b200.models.distributed_reference import DistributedEagerDecoder
+    from cubic_serve_b200.models.parallel_weights import plan_partition
+    from cubic_serve_b200.models.reference import random_dense_weights
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    torch.set_num_threads(1)
+    cfg = _cfg()
+    plan = plan_partition(cfg, tp, pp)
+    groups = [dist.new_group(list(range(s * tp, (s + 1) * tp))) for s in range(pp)]     # every rank creates every group
+    dec = DistributedEagerDecoder(cfg, plan, rank, random_dense_weights(cfg, seed=5, std=0.08), groups[rank // tp])
+    prompts = torch.tensor([[3, 17, 99, 4, 56], [8, 8, 120, 33, 2]])
+    toks, logits = dec.generate(prompts, 6)
+    q.put((rank, toks.tolist(), None if logits[0] is None else torch.stack(logits, 1)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("tp,pp", [(2, 1), (2, 2)])
+def test_distributed_reference_equals_single_process(tp, pp):
+    from cubic_serve_b200.models.reference import EagerDecoder, random_dense_weights
+    cfg = _cfg()
+    want_toks, want_logits = EagerDecoder(cfg, random_dense_weights(cfg, seed=5, std=0.08)).generate(
+        torch.tensor([[3, 17, 99, 4, 56], [8, 8, 120, 33, 2]]), 6)
+    world = tp * pp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank, args=(r, world, tp, pp, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=180) for _ in procs), key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+    for rank, toks, logits in got:
+        assert toks == want_toks.tolist(), rank                   # every rank decoded the same tokens
+        if rank >= (pp - 1) * tp:                                 # last stage: full-vocabulary logits, rank-order sums
+            assert logits is not None and torch.allclose(logits, want_logits, rtol=1e-4, atol=1e-5)
+        else:
+            assert logits is None
+    last = [l for r, _, l in got if r >= (pp - 1) * tp]
+    assert all(torch.equal(last[0], l) for l in last[1:])         # identical bits on all tensor ranks
+
+
+def test_shards_follow_the_ownership_plan():
+    from cubic_serve_b200.models.distributed_reference import shard_dense_weights
+    from cubic_serve_b200.models.parallel_weights import plan_partition
+    from cubic_serve_b200.models.reference import random_dense_weights
+    cfg = _cfg()
+    w = random_dense_weights(cfg, seed=1)
+    plan = plan_partition(cfg, 2, 2)
+    s = shard_dense_weights(w, cfg, plan.ranks[3])                # stage 1, tensor rank 1
+    assert len(s.layers) == 2
+    assert torch.equal(s.layers[0].wq, w.layers[2].wq[32:64]) and torch.equal(s.layers[0].wo, w.layers[2].wo[:, 32:64])
+    assert torch.equal(s.layers[1].w_down, w.layers[3].w_down[:, 64:128]) and s.layers[1].wk.shape == (16, 64)
