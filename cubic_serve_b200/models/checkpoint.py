@@ -173,6 +173,7 @@ def inspect_checkpoint(path: str | Path) -> dict:
     if path.suffix == ".gguf":
         from .gguf import inspect_gguf
         return inspect_gguf(path)
+    from ..contracts.model import WeightManifest
     ck = admit_checkpoint(path)
     total = sum(math.prod(t.shape) for t in ck.store.tensors.values())
     by_dtype: dict[str, int] = {}
@@ -182,6 +183,7 @@ def inspect_checkpoint(path: str | Path) -> dict:
             "heads": f"{ck.cfg.num_q_heads}q/{ck.cfg.num_kv_heads}kv x {ck.cfg.head_dim}", "vocab": ck.cfg.vocab_size,
             "quantization": f"{ck.cfg.quant.method} {ck.cfg.quant.bits}-bit group {ck.cfg.quant.group_size}",
             "tensors": len(ck.store.tensors), "elements": total, "dtypes": by_dtype,
+            "manifest_digest": WeightManifest.from_store(ck.store).digest,
             "logical_linears": len(ck.payloads)}
 
 

@@ -49,18 +49,13 @@ def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int
                   max_running: int, layers: int | None = None) -> int:
     """Pages that fit in the remaining device memory (one page = 16 tokens of every local layer's rank-local KV
     heads; ``layers`` = decoder layers held by this pipeline stage, default all)."""
-    from ..ops.kernels import kv_blob_bytes
+    from ..contracts.model import CacheSpec, ModelSpec, StateSpec
     n_layers = layers or cfg.num_layers
     n_gdn = sum(cfg.layer_is_gdn(i) for i in range(cfg.num_layers)) if layers is None else 0
-    per_page = (n_layers - n_gdn) * (cfg.num_kv_heads // tp) * kv_blob_bytes(cfg.head_dim, k_bits, v_bits)
-    budget = max(0, free_bytes - reserve_bytes)
-    if n_gdn:
-        # Gated DeltaNet layers keep, per request, one 128 x 128 fp32 state per value head and three conv inputs
-        gk, gv = cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp
-        budget = max(0, budget - n_gdn * max_running * (gv * 128 * 128 * 4 + 3 * (2 * gk + gv) * 128 * 2))
-    pages = budget // per_page
-    cap = max_running * (-(-max_model_len // 16)) + 64
-    return int(max(64, min(pages, cap)))
+    cache = CacheSpec(n_layers - n_gdn, cfg.num_kv_heads // tp, cfg.head_dim, k_bits, v_bits)
+    # Gated DeltaNet layers keep, per request, one 128 x 128 fp32 state per value head and three conv inputs
+    state = StateSpec(n_gdn, cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp) if n_gdn else None
+    return ModelSpec(cfg.name, cfg.family, "", cache, state).kv_pages(free_bytes, reserve_bytes, max_model_len, max_running)
 
 
 def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: int):

@@ -144,3 +144,41 @@ def test_inspect_model_prints_partitions(capsys):
     assert len(info["partition"]) == 2 and info["partition"][1]["tensor_rank"] == 1
     assert main(["inspect-model", "random:dense-8b", "--tp", "3", "--json"]) == 0
     assert "partition_error" in json.loads(capsys.readouterr().out)
+
+
+def test_model_spec_cache_state_and_manifest(tmp_path):
+    import dataclasses
+    import pytest
+    from cubic_serve_b200.contracts.model import CacheSpec, ModelSpec, StateSpec, WeightManifest
+    from cubic_serve_b200.models.checkpoint import SafetensorsDirectory, inspect_checkpoint, write_random_checkpoint
+    from cubic_serve_b200.models.config import NAMED_CONFIGS, ModelConfig, QuantSpec
+    from cubic_serve_b200.ops.kernels import kv_blob_bytes
+    c = CacheSpec(layers=36, kv_heads=8, head_dim=128, k_bits=8, v_bits=4)
+    assert c.blob_bytes == kv_blob_bytes(128, 8, 4) == 16 * 128 + 16 * 64 + 2 * 16 * 4 * 4
+    assert c.page_bytes == 36 * 8 * c.blob_bytes and c.bytes_per_token() == c.page_bytes / 16
+    assert CacheSpec(1, 1, 128, 6, 6).blob_bytes == kv_blob_bytes(128, 6, 6)
+    with pytest.raises(ValueError):
+        CacheSpec(1, 1, 128, 5, 8)
+    s = StateSpec(layers=27, k_heads=16, v_heads=32)
+    assert s.delta_bytes == 32 * 128 * 128 * 4 and s.conv_bytes == 3 * 64 * 128 * 2
+    dense = ModelSpec.from_config(NAMED_CONFIGS["dense-8b"](), 8, 8)
+    assert dense.state is None and dense.cache.layers == 36
+    # 20 GiB for pages: not capped by the request limit
+    pages = dense.kv_pages(26 << 30, 6 << 30, 32768, 256)
+    assert pages == (20 << 30) // dense.cache.page_bytes
+    hybrid = ModelSpec.from_config(NAMED_CONFIGS["hybrid-8b"](), 8, 8, tp=2)
+    assert hybrid.state.layers == 27 and hybrid.cache.layers == 9 and hybrid.cache.kv_heads == 4
+    with_state = hybrid.kv_pages(26 << 30, 6 << 30, 32768, 256)
+    assert with_state == ((20 << 30) - 256 * hybrid.state.bytes_per_request) // hybrid.cache.page_bytes
+    stage = ModelSpec.from_config(NAMED_CONFIGS["dense-8b"](), 4, 8, tp=4, layers=(18, 36))
+    assert stage.cache.layers == 18 and stage.cache.kv_heads == 2 and stage.digest != dense.digest
+    with pytest.raises(ValueError):
+        ModelSpec.from_config(NAMED_CONFIGS["dense-8b"](), tp=3)
+    cfg = ModelConfig(name="toy", num_layers=1, hidden_size=128, num_q_heads=2, num_kv_heads=1, head_dim=64,
+                      intermediate_size=256, vocab_size=256, rope_theta=1e4, quant=QuantSpec("cubic", 4, 128))
+    a = write_random_checkpoint(tmp_path / "a", cfg, seed=0)
+    b = write_random_checkpoint(tmp_path / "b", dataclasses.replace(cfg, intermediate_size=384), seed=0)
+    ma, mb = WeightManifest.from_store(SafetensorsDirectory(a)), WeightManifest.from_store(SafetensorsDirectory(b))
+    assert len(ma) == len(mb) and ma.digest != mb.digest and ma.files == ("model.safetensors",)
+    assert ma.digest == WeightManifest.from_store(SafetensorsDirectory(a)).digest == inspect_checkpoint(a)["manifest_digest"]
+    assert ModelSpec.from_config(cfg, manifest=ma).digest != ModelSpec.from_config(cfg, manifest=mb).digest
