@@ -101,6 +101,12 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
             cfg = NAMED_CONFIGS[spec.model.split(":", 1)[1]]()
             layers = topo.layer_range(place.stage, cfg.num_layers)
             weights = random_decoder_weights(cfg, dev, spec.seed, t_rank, spec.tp, layer_range=layers)
+        elif spec.model.endswith(".gguf"):
+            import gguf
+
+            from ..models.gguf import config_from_gguf, load_gguf_decoder_weights
+            layers = topo.layer_range(place.stage, config_from_gguf(gguf.GGUFReader(spec.model)).num_layers)
+            cfg, weights = load_gguf_decoder_weights(spec.model, dev, t_rank, spec.tp, layer_range=layers)
         else:
             from ..models.checkpoint import admit_checkpoint, load_decoder_weights
             ck = admit_checkpoint(spec.model)

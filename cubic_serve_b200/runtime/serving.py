@@ -20,6 +20,13 @@ def _tokenizer_for(model: str, vocab_size: int):
     if path.is_dir() and any((path / f).exists() for f in ("tokenizer.json", "tokenizer_config.json")):
         from transformers import AutoTokenizer
         return AutoTokenizer.from_pretrained(str(path))
+    if path.suffix == ".gguf" and path.exists():
+        # the file carries its tokenizer as metadata; a file without one falls through to the byte tokenizer
+        try:
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(str(path.parent), gguf_file=path.name)
+        except Exception as exc:  # noqa: BLE001
+            log.warning("no tokenizer could be built from %s (%s): using the byte tokenizer", path.name, type(exc).__name__)
     from ..inputs.chat import ByteTokenizer
     tok = ByteTokenizer()
     if tok.vocab_size > vocab_size:
@@ -70,9 +77,17 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         return build_multiproc_backend(args, devices, tp, spec, k_bits, v_bits)
     model = args.model
     eager = args.execution_mode != "cuda" or not torch.cuda.is_available()
+    gguf_weights = None
     if model.startswith("random:"):
         cfg = NAMED_CONFIGS[model.split(":", 1)[1]]()
         ck = None
+    elif model.endswith(".gguf"):
+        import gguf
+
+        from ..models.gguf import config_from_gguf
+        cfg = config_from_gguf(gguf.GGUFReader(model))
+        ck = None
+        gguf_weights = model
     else:
         from ..models.checkpoint import admit_checkpoint
         ck = admit_checkpoint(model)
@@ -84,7 +99,7 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
     if eager:
         from ..executor.eager_executor import EagerPagedExecutor
         from ..models.reference import random_dense_weights
-        if ck is not None:
+        if ck is not None or gguf_weights is not None:
             raise SystemExit("eager execution mode serves random:<config> models only")
         pages = 4096
         executor = EagerPagedExecutor(cfg, random_dense_weights(cfg, args.seed), pages, kv_bits=(k_bits, v_bits))
@@ -103,7 +118,11 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
                 raise SystemExit(f"start-up qualification failed on this GPU: {bad}")
             log.info("start-up qualification: %d checks passed (%s receipt)", len(report["results"]), "reused" if reused else "new")
         defn = model_registry.get(cfg.family)
-        weights = defn.load_weights(ck, dev) if ck is not None else defn.random_weights(cfg, dev, args.seed)
+        if gguf_weights is not None:
+            from ..models.gguf import load_gguf_decoder_weights
+            cfg, weights = load_gguf_decoder_weights(gguf_weights, dev)
+        else:
+            weights = defn.load_weights(ck, dev) if ck is not None else defn.random_weights(cfg, dev, args.seed)
         free, _total = torch.cuda.mem_get_info(dev)
         if args.gpu_memory_gib:
             free = min(free, int(args.gpu_memory_gib * 2 ** 30) - torch.cuda.memory_allocated(dev))
