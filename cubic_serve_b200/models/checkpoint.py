@@ -269,9 +269,13 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
     """
     from .decoder import DecoderWeights, GdnWeights, LayerWeights
     cfg, q = ck.cfg, ck.cfg.quant
-    if cfg.is_moe:
-        raise CheckpointError("MoE checkpoints are loaded by models.moe.load_moe_layer")
     method = q.method
+    if tp_size > 1:
+        from .parallel_weights import PartitionError, plan_partition
+        try:                              # name what does not divide before any tensor is read
+            plan_partition(cfg, tp_size, 1, tp_size if cfg.is_moe else 1)
+        except PartitionError as exc:
+            raise CheckpointError(f"{cfg.name} does not split over {tp_size} ranks: {exc}") from exc
     D = cfg.head_dim
     hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
     inter = cfg.intermediate_size // tp_size
@@ -339,15 +343,21 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
                                                   rows(m["v"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size)], q)
             o = pack_logical(method, [(ck.payload(m["o"]), ck_shapes[m["o"]])], q,
                              (tp_rank * hq * D, (tp_rank + 1) * hq * D))
-        gu = pack_logical(method, [rows(m["gate"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size),
-                                   rows(m["up"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size)], q)
-        down = pack_logical(method, [(ck.payload(m["down"]), ck_shapes[m["down"]])], q,
-                            (tp_rank * inter, (tp_rank + 1) * inter))
+        moe = gu = down = None
+        if cfg.is_moe:
+            from .moe import load_moe_layer
+            moe = load_moe_layer(ck, i, device, tp_rank, tp_size)
+        else:
+            gu = pack_logical(method, [rows(m["gate"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size),
+                                       rows(m["up"], tp_rank * inter, (tp_rank + 1) * inter, cfg.intermediate_size)], q)
+            down = pack_logical(method, [(ck.payload(m["down"]), ck_shapes[m["down"]])], q,
+                                (tp_rank * inter, (tp_rank + 1) * inter))
         lw = LayerWeights(ln1=ck.store.get(f"{p}.input_layernorm.weight").to(device, bf),
                           ln2=ck.store.get(f"{p}.post_attention_layernorm.weight").to(device, bf),
                           qkv=None if qkv is None else qkv.to(device), o=None if o is None else o.to(device), gdn=gdn,
                           attn_gate=None if attn_gate is None else attn_gate.to(device),
-                          gate_up=gu.to(device), down=down.to(device))
+                          gate_up=None if gu is None else gu.to(device), down=None if down is None else down.to(device),
+                          moe=moe)
         if cfg.qk_norm and gdn is None:
             lw.q_norm = ck.store.get(f"{p}.self_attn.q_norm.weight").to(device, bf)
             lw.k_norm = ck.store.get(f"{p}.self_attn.k_norm.weight").to(device, bf)

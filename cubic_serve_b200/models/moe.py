@@ -100,6 +100,30 @@ def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size:
                     tp_rank * local, local, cfg.norm_topk_prob)
 
 
+def load_moe_layer(ck, layer: int, device, tp_rank: int = 0, tp_size: int = 1) -> MoeLayer:
+    """Experts of decoder layer ``layer`` from an admitted checkpoint.  Expert parallelism over the tensor-parallel
+    ranks: rank ``r`` owns the contiguous expert ids ``[r E / tp, (r + 1) E / tp)`` whole; the router is replicated.
+    Payloads keep the checkpoint's quantization (``pack_logical`` re-tiles, it does not re-quantize)."""
+    from .checkpoint import CheckpointError, logical_inventory, pack_logical
+    cfg, q = ck.cfg, ck.cfg.quant
+    E = cfg.num_experts
+    if E % tp_size:
+        raise CheckpointError(f"{E} experts do not split over {tp_size} ranks")
+    local = E // tp_size
+    shapes, _ = logical_inventory(cfg)
+    gus, downs = [], []
+    for e in range(tp_rank * local, (tp_rank + 1) * local):
+        ep = f"model.layers.{layer}.mlp.experts.{e}"
+        gate, up, down = f"{ep}.gate_proj", f"{ep}.up_proj", f"{ep}.down_proj"
+        gus.append(pack_logical(q.method, [(ck.payload(gate), shapes[gate]), (ck.payload(up), shapes[up])], q))
+        downs.append(pack_logical(q.method, [(ck.payload(down), shapes[down])], q))
+    gu, gcs, gms = stack_experts(gus)
+    dn, dcs, dms = stack_experts(downs)
+    router = ck.store.get(f"model.layers.{layer}.mlp.gate.weight").to(torch.bfloat16)
+    return MoeLayer(wq_pack.pack_bf16(router).to(device), gu.to(device), dn.to(device), (gcs, gms, dcs, dms), E,
+                    cfg.experts_per_token, tp_rank * local, local, cfg.norm_topk_prob)
+
+
 def moe_reference(x: torch.Tensor, router: torch.Tensor, gate_up: list[torch.Tensor], down: list[torch.Tensor],
                   top_k: int, normalize: bool = True, expert_lo: int = 0) -> torch.Tensor:
     """Independent fp32 oracle: dense per-token loop over the selected experts (local experts only)."""

@@ -109,3 +109,45 @@ def test_hybrid_checkpoint_row_mapping(tmp_path, method, bits, group):
         assert ((got_q - torch.cat([qp[h, 0] for h in hq])).norm() / got_q.norm()).item() < 6e-3
         got_g = wq_pack.unpack_to_dense(lw.attn_gate)[:len(hq) * 128]
         assert ((got_g - torch.cat([qp[h, 1] for h in hq])).norm() / got_g.norm()).item() < 6e-3
+
+
+@pytest.mark.parametrize("method,bits,group", [("cubic", 4, 128), ("int", 4, 128), ("none", 16, 0)])
+def test_moe_checkpoint_experts_and_router(tmp_path, method, bits, group):
+    """Experts of a written MoE checkpoint arrive whole on their owning rank, [gate; up] stacked, values equal to
+    the format's own decode of the payload; the router is replicated."""
+    import dataclasses
+    from cubic_serve_b200.models.checkpoint import _dense_of, admit_checkpoint, load_decoder_weights, logical_inventory
+    from cubic_serve_b200.ops import wq_pack
+    cfg = dataclasses.replace(BASE, name="tiny-moe", family="gqa_moe", num_experts=4, experts_per_token=2,
+                              moe_intermediate_size=128, quant=QuantSpec(method, bits, group))
+    path = C.write_random_checkpoint(tmp_path / "moe", cfg, seed=2)
+    ck = admit_checkpoint(path)
+    assert ck.cfg.is_moe and ck.cfg.num_experts == 4
+    shapes, _ = logical_inventory(ck.cfg)
+
+    def dense(module):
+        return _dense_of(method, ck.payload(module), shapes[module], ck.cfg.quant)
+
+    def expert(stacked, j):
+        return wq_pack.PackedWeight(stacked.fmt, stacked.n, stacked.k, stacked.group_k, stacked.codes[j],
+                                    None if stacked.meta is None else stacked.meta[j], stacked.alpha)
+
+    def rel(a, b):
+        return ((a - b).norm() / b.norm()).item()
+
+    full = load_decoder_weights(ck, "cpu")
+    moe = full.layers[1].moe
+    assert full.layers[1].gate_up is None and (moe.expert_lo, moe.expert_count, moe.num_experts, moe.top_k) == (0, 4, 4, 2)
+    assert torch.equal(moe.router.codes.float(), ck.store.get("model.layers.1.mlp.gate.weight").float())
+    r1 = load_decoder_weights(ck, "cpu", tp_rank=1, tp_size=2).layers[1].moe
+    assert (r1.expert_lo, r1.expert_count) == (2, 2) and r1.gate_up.codes.shape[0] == 2
+    for j, e in ((0, 2), (1, 3)):
+        ep = f"model.layers.1.mlp.experts.{e}"
+        want_gu = torch.cat([dense(f"{ep}.gate_proj"), dense(f"{ep}.up_proj")])
+        assert rel(wq_pack.unpack_to_dense(expert(r1.gate_up, j))[:256], want_gu) < 6e-3
+        assert rel(wq_pack.unpack_to_dense(expert(r1.down, j))[:256], dense(f"{ep}.down_proj")) < 6e-3
+        assert rel(wq_pack.unpack_to_dense(expert(moe.gate_up, e))[:256], want_gu) < 6e-3
+    gcs, gms, dcs, dms = r1.strides
+    assert gcs == r1.gate_up.codes[0].numel() * r1.gate_up.codes.element_size()
+    with pytest.raises(C.CheckpointError):
+        load_decoder_weights(ck, "cpu", tp_rank=0, tp_size=3)

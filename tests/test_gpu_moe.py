@@ -145,3 +145,38 @@ def test_expert_parallel_dispatch_combine_matches_single_rank(method, tokens, ra
     # every row went only to ranks that own one of its experts, once per rank
     sent = torch.stack([(eps[r].sent[:cnts[r]] >= 0).sum() for r in range(ranks)]).sum().item()
     assert tokens <= sent <= tokens * min(k, ranks)
+
+
+def test_moe_checkpoint_serves_and_matches_the_oracle(tmp_path):
+    """A written MoE checkpoint: the loaded expert layer equals the dense oracle built from the checkpoint's own
+    decode, and the engine decodes with it (graphs captured, qualification passed)."""
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.models.checkpoint import _dense_of, admit_checkpoint, load_decoder_weights, logical_inventory, \
+        write_random_checkpoint
+    from cubic_serve_b200.models.decoder import DecoderRunner
+    from cubic_serve_b200.models.moe import moe_reference
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = ModelConfig(name="moe-ck", family="gqa_moe", num_layers=2, hidden_size=256, num_q_heads=4, num_kv_heads=2,
+                      head_dim=128, intermediate_size=512, vocab_size=512, qk_norm=True, num_experts=8, experts_per_token=2,
+                      moe_intermediate_size=128, quant=QuantSpec("cubic", 4, 128))
+    ck = admit_checkpoint(write_random_checkpoint(tmp_path / "moe", cfg, seed=4, std=0.05))
+    w = load_decoder_weights(ck, torch.device(DEV))
+    layer = w.layers[0].moe
+    shapes, _ = logical_inventory(ck.cfg)
+    dense = lambda m: _dense_of("cubic", ck.payload(m), shapes[m], ck.cfg.quant).to(DEV)  # noqa: E731
+    gu = [torch.cat([dense(f"model.layers.0.mlp.experts.{e}.gate_proj"), dense(f"model.layers.0.mlp.experts.{e}.up_proj")])
+          for e in range(8)]
+    dn = [dense(f"model.layers.0.mlp.experts.{e}.down_proj") for e in range(8)]
+    x = (torch.randn(40, 256, generator=torch.Generator().manual_seed(2)) * 0.5).to(torch.bfloat16).to(DEV)
+    out = layer.forward(x)
+    ref = moe_reference(x, layer.router.codes, gu, dn, 2, ck.cfg.norm_topk_prob)
+    assert _rel(out, ref) < 2e-2
+    runner = DecoderRunner(ck.cfg, w, num_pages=64, max_tokens=256)
+    ex = GpuExecutor(runner, max_rows=4, max_prefill_tokens=256, max_model_len=128)
+    assert ex.capture_decode_graphs([4]) == [4]
+    eng = LLMEngine(ex, 64, SchedulerConfig(max_running_requests=4, max_model_len=128, max_batched_tokens=256,
+                                            enable_prefix_cache=False))
+    outs = eng.generate([[5, 9, 200, 31, 7], [3, 3, 100]], SamplingParams(max_tokens=6, ignore_eos=True))
+    runner.ws.check_status()
+    assert all(len(o) == 6 and all(0 <= t < 512 for t in o) for o in outs)
