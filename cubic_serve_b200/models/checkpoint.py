@@ -122,6 +122,24 @@ def logical_inventory(cfg: ModelConfig) -> tuple[dict[str, tuple[int, int]], lis
         plain += [f"model.layers.{i}.input_layernorm.weight", f"model.layers.{i}.post_attention_layernorm.weight"]
         if cfg.qk_norm and not cfg.layer_is_gdn(i):
             plain += [f"model.layers.{i}.self_attn.q_norm.weight", f"model.layers.{i}.self_attn.k_norm.weight"]
+    if cfg.mtp_layers:
+        # multi-token-prediction head: fc over [normed embedding ; normed hidden] and one full-attention decoder layer
+        # with a dense feed-forward (reference schema: models/qwen3_5/model.py:1512-1644)
+        if cfg.mtp_layers != 1:
+            raise CheckpointError(f"checkpoints with {cfg.mtp_layers} MTP layers are not served (one layer is)")
+        mp = "mtp.layers.0"
+        linears["mtp.fc"] = (H, 2 * H)
+        linears[f"{mp}.self_attn.q_proj"] = (cfg.q_size, H)
+        linears[f"{mp}.self_attn.k_proj"] = (cfg.kv_size, H)
+        linears[f"{mp}.self_attn.v_proj"] = (cfg.kv_size, H)
+        linears[f"{mp}.self_attn.o_proj"] = (H, cfg.q_size)
+        linears[f"{mp}.mlp.gate_proj"] = (cfg.intermediate_size, H)
+        linears[f"{mp}.mlp.up_proj"] = (cfg.intermediate_size, H)
+        linears[f"{mp}.mlp.down_proj"] = (H, cfg.intermediate_size)
+        plain += ["mtp.pre_fc_norm_embedding.weight", "mtp.pre_fc_norm_hidden.weight", "mtp.norm.weight",
+                  f"{mp}.input_layernorm.weight", f"{mp}.post_attention_layernorm.weight"]
+        if cfg.qk_norm:
+            plain += [f"{mp}.self_attn.q_norm.weight", f"{mp}.self_attn.k_norm.weight"]
     return linears, plain
 
 
@@ -371,6 +389,36 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
                           vocab_start=tp_rank * v_local, extras={"embed_full": embed_full})
 
 
+def load_mtp_weights(ck: AdmittedCheckpoint, device):
+    """The checkpoint's multi-token-prediction head as ``models.mtp.MtpWeights`` (single rank: speculative rounds run
+    in the single-process executor)."""
+    from .decoder import LayerWeights
+    from .mtp import MtpWeights
+    cfg, q = ck.cfg, ck.cfg.quant
+    if not cfg.mtp_layers:
+        raise CheckpointError("this checkpoint carries no MTP head (no mtp_num_hidden_layers in its config)")
+    if cfg.is_moe or cfg.is_hybrid:
+        raise CheckpointError("MTP heads are served for dense full-attention decoders")
+    shapes, _ = logical_inventory(cfg)
+    bf = torch.bfloat16
+    mp = "mtp.layers.0"
+
+    def fused(*modules: str):
+        return pack_logical(q.method, [(ck.payload(m), shapes[m]) for m in modules], q).to(device)
+
+    def vec(name: str):
+        return ck.store.get(name).to(device, bf)
+
+    layer = LayerWeights(ln1=vec(f"{mp}.input_layernorm.weight"), ln2=vec(f"{mp}.post_attention_layernorm.weight"),
+                         qkv=fused(f"{mp}.self_attn.q_proj", f"{mp}.self_attn.k_proj", f"{mp}.self_attn.v_proj"),
+                         o=fused(f"{mp}.self_attn.o_proj"), gate_up=fused(f"{mp}.mlp.gate_proj", f"{mp}.mlp.up_proj"),
+                         down=fused(f"{mp}.mlp.down_proj"))
+    if cfg.qk_norm:
+        layer.q_norm, layer.k_norm = vec(f"{mp}.self_attn.q_norm.weight"), vec(f"{mp}.self_attn.k_norm.weight")
+    return MtpWeights(vec("mtp.pre_fc_norm_embedding.weight"), vec("mtp.pre_fc_norm_hidden.weight"), fused("mtp.fc"), layer,
+                      vec("mtp.norm.weight"))
+
+
 # ------------------------------------------------------- random checkpoints
 def _quant_config_json(q: QuantSpec) -> dict | None:
     return registry.get(q.method).config_json(q)
@@ -404,6 +452,8 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
                 tensors[name] = torch.ones(128, dtype=torch.bfloat16)
             else:                              # A_log, dt_bias
                 tensors[name] = torch.randn(gv, generator=g) * 0.5
+        elif "pre_fc_norm" in name:
+            tensors[name] = torch.ones(cfg.hidden_size, dtype=torch.bfloat16)
         elif name.endswith("norm.weight"):
             tensors[name] = torch.ones(cfg.head_dim if "_norm" in name.split(".")[-2] and "self_attn" in name else cfg.hidden_size,
                                        dtype=torch.bfloat16)
@@ -422,6 +472,8 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
         hf.update(linear_num_key_heads=cfg.gdn_k_heads, linear_num_value_heads=cfg.gdn_v_heads, linear_key_head_dim=128,
                   linear_value_head_dim=128, full_attention_interval=cfg.gdn_interval, attn_output_gate=cfg.attn_output_gate,
                   partial_rotary_factor=(cfg.rotary_dim or cfg.head_dim) / cfg.head_dim)
+    if cfg.mtp_layers:
+        hf["mtp_num_hidden_layers"] = cfg.mtp_layers
     if cfg.is_moe:
         hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token,
                   moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)

@@ -41,6 +41,7 @@ class ModelConfig:
     max_position: int = 40960
     # MoE
     num_experts: int = 0
+    mtp_layers: int = 0              # multi-token-prediction draft layers carried by the checkpoint (``mtp.*`` tensors)
     experts_per_token: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
@@ -125,6 +126,7 @@ class ModelConfig:
             experts_per_token=text.get("num_experts_per_tok", 0) if n_exp else 0,
             moe_intermediate_size=text.get("moe_intermediate_size", 0) if n_exp else 0,
             norm_topk_prob=bool(text.get("norm_topk_prob", True)),
+            mtp_layers=int(text.get("mtp_num_hidden_layers") or text.get("num_nextn_predict_layers") or 0),
             quant=quant_spec_from_hf(qc),
             eos_token_id=(text.get("eos_token_id") if isinstance(text.get("eos_token_id"), int) else None),
         )

@@ -143,10 +143,15 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
             # MTP speculative decoding (--speculative-config): draft head + review rounds instead of graph decode
             from ..executor.spec_executor import SpeculativeGpuExecutor
             from ..models.mtp import MtpRunner, random_mtp_weights
+            if ck is not None and not cfg.mtp_layers or gguf_weights is not None:
+                raise SystemExit("this checkpoint carries no MTP head (no mtp.* tensors): use "
+                                 '--speculative-config \'{"method":"ngram",...}\' or a checkpoint with the head')
             if ck is not None:
-                raise SystemExit("this checkpoint carries no MTP head weights; speculative decoding serves "
-                                 "random:<config> models only")
-            mtp = MtpRunner(runner, random_mtp_weights(cfg, dev, args.seed + 1))
+                from ..models.checkpoint import load_mtp_weights
+                mtp_weights = load_mtp_weights(ck, dev)
+            else:
+                mtp_weights = random_mtp_weights(cfg, dev, args.seed + 1)
+            mtp = MtpRunner(runner, mtp_weights)
             executor = SpeculativeGpuExecutor(runner, mtp, depth, max_rows=args.max_running_requests,
                                               max_prefill_tokens=args.token_budget, max_model_len=max_len)
             log.info("MTP speculative decoding: depth %d, %s draft length; %d KV pages", depth, spec.mode, pages)

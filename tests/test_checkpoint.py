@@ -151,3 +151,31 @@ def test_moe_checkpoint_experts_and_router(tmp_path, method, bits, group):
     assert gcs == r1.gate_up.codes[0].numel() * r1.gate_up.codes.element_size()
     with pytest.raises(C.CheckpointError):
         load_decoder_weights(ck, "cpu", tp_rank=0, tp_size=3)
+
+
+def test_mtp_head_from_checkpoint(tmp_path):
+    import dataclasses
+    from cubic_serve_b200.models.checkpoint import _dense_of, admit_checkpoint, load_mtp_weights, logical_inventory
+    cfg = dataclasses.replace(BASE, name="tiny-mtp", mtp_layers=1, quant=QuantSpec("cubic", 4, 128))
+    path = C.write_random_checkpoint(tmp_path / "mtp", cfg, seed=5)
+    assert json.loads((path / "config.json").read_text())["mtp_num_hidden_layers"] == 1
+    ck = admit_checkpoint(path)
+    assert ck.cfg.mtp_layers == 1 and "mtp.fc" in ck.payloads and "mtp.norm.weight" in ck.plain
+    shapes, _ = logical_inventory(ck.cfg)
+    dense = lambda m: _dense_of("cubic", ck.payload(m), shapes[m], ck.cfg.quant)  # noqa: E731
+    w = load_mtp_weights(ck, "cpu")
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()  # noqa: E731
+    assert (w.fc.n, w.fc.k) == (256, 512) and rel(wq_pack.unpack_to_dense(w.fc)[:256], dense("mtp.fc")) < 6e-3
+    mp = "mtp.layers.0"
+    qkv = torch.cat([dense(f"{mp}.self_attn.q_proj"), dense(f"{mp}.self_attn.k_proj"), dense(f"{mp}.self_attn.v_proj")])
+    assert rel(wq_pack.unpack_to_dense(w.layer.qkv)[:qkv.shape[0]], qkv) < 6e-3
+    assert w.layer.q_norm.shape == (128,) and w.enorm.shape == (256,) and w.norm.dtype == torch.bfloat16
+    # the same tensors under a config that does not announce the head are foreign tensors: closed inventory
+    hf = json.loads((path / "config.json").read_text())
+    del hf["mtp_num_hidden_layers"]
+    (path / "config.json").write_text(json.dumps(hf))
+    with pytest.raises(C.CheckpointError, match="no logical weight owns"):
+        admit_checkpoint(path)
+    plain = admit_checkpoint(C.write_random_checkpoint(tmp_path / "plain", BASE, seed=5))
+    with pytest.raises(C.CheckpointError, match="no MTP head"):
+        load_mtp_weights(plain, "cpu")

@@ -115,3 +115,32 @@ def test_ngram_rounds_match_plain_greedy_and_accept_repetitions():
     before = dict(ex2.graph_rt.stats()["slots"][4])
     eng3.generate([rng.integers(0, 2048, 6).tolist()], SamplingParams(max_tokens=3, ignore_eos=True))
     assert ex2.graph_rt.stats()["slots"][4]["replays"] > before["replays"]
+
+
+def test_mtp_head_loaded_from_a_checkpoint_drafts_losslessly(tmp_path):
+    import dataclasses
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
+    from cubic_serve_b200.models.checkpoint import admit_checkpoint, load_decoder_weights, load_mtp_weights, \
+        write_random_checkpoint
+    from cubic_serve_b200.models.decoder import DecoderRunner
+    from cubic_serve_b200.models.mtp import MtpRunner
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    dev = torch.device("cuda")
+    cfg = ModelConfig(name="spec-ck", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, rope_theta=1e6, qk_norm=True, mtp_layers=1,
+                      quant=QuantSpec("cubic", 4, 128))
+    ck = admit_checkpoint(write_random_checkpoint(tmp_path / "ck", cfg, seed=1, std=0.05))
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (21, 34)]
+    sched = SchedulerConfig(max_running_requests=8, max_model_len=256, max_batched_tokens=512, enable_prefix_cache=False)
+    kw = dict(max_rows=8, max_prefill_tokens=512, max_model_len=256)
+    r1 = DecoderRunner(ck.cfg, load_decoder_weights(ck, dev), num_pages=128, max_tokens=512)
+    plain = LLMEngine(GpuExecutor(r1, use_graphs=False, **kw), 128, sched).generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    r2 = DecoderRunner(ck.cfg, load_decoder_weights(ck, dev), num_pages=128, max_tokens=512)
+    ex = SpeculativeGpuExecutor(r2, MtpRunner(r2, load_mtp_weights(ck, dev)), 2, **kw)
+    spec = LLMEngine(ex, 128, sched).generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    r2.ws.check_status()
+    agree = np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)])
+    assert agree >= 0.9 and ex.stats["rounds"] > 0, (agree, plain, spec)
