@@ -81,6 +81,37 @@ def _error_body(protocol: str, status: int, message: str, code: str, param: str 
     return {"error": {"message": message, "type": code, "param": param, "code": status}}
 
 
+def render_metrics(backend, model: str) -> str:
+    """Engine and scheduler counters in the Prometheus text exposition format (``GET /metrics``, behind the API key
+    like every route but ``/health``).  Reads plain counters: no lock is taken and no step is delayed."""
+    label = '{model="%s"}' % model.replace("\\", "\\\\").replace('"', '\\"')
+    rows: list[tuple[str, str, str, float]] = []
+    engine = getattr(backend, "engine", None)
+    served = getattr(backend, "stats", None) or {}
+    rows.append(("cubic_ready", "gauge", "1 when the backend accepts requests", 1.0 if getattr(backend, "ready", True) else 0.0))
+    if isinstance(served, dict):
+        rows.append(("cubic_requests_total", "counter", "requests admitted", float(served.get("requests", 0))))
+        rows.append(("cubic_streamed_tokens_total", "counter", "tokens handed to response streams", float(served.get("tokens", 0))))
+    if engine is not None:
+        s = engine.stats()
+        for key, name, kind, text in (
+                ("running", "cubic_requests_running", "gauge", "requests in the running batch"),
+                ("waiting", "cubic_requests_waiting", "gauge", "requests waiting for admission"),
+                ("kv_used_frac", "cubic_kv_cache_usage_ratio", "gauge", "fraction of KV pages in use"),
+                ("prefix_hit_rate", "cubic_prefix_cache_hit_ratio", "gauge", "prompt tokens served from cached pages"),
+                ("steps", "cubic_engine_steps_total", "counter", "engine steps"),
+                ("generated_tokens", "cubic_generated_tokens_total", "counter", "tokens sampled"),
+                ("prefill_tokens", "cubic_prefill_tokens_total", "counter", "prompt tokens computed")):
+            if key in s:
+                rows.append((name, kind, text, float(s[key])))
+        rows.append(("cubic_last_step_seconds", "gauge", "host time of the last engine step", float(getattr(engine, "last_step_seconds", 0.0))))
+        rows.append(("cubic_engine_poisoned", "gauge", "1 after a step failed (the engine refuses work)", 1.0 if getattr(engine, "poisoned", False) else 0.0))
+    out = []
+    for name, kind, text, value in rows:
+        out += [f"# HELP {name} {text}", f"# TYPE {name} {kind}", f"{name}{label} {value:g}"]
+    return "\n".join(out) + "\n"
+
+
 class CubicASGIApp:
     def __init__(self, backend: ChatBackend, model_id: str, served_model_name: str | None = None,
                  api_key: str | None = None) -> None:
@@ -108,6 +139,10 @@ class CubicASGIApp:
             if not self._authorized(headers):
                 await self._json(send, 401, _error_body(protocol, 401, "invalid or missing API key", "authentication_error"))
                 return
+            if path == "/metrics" and method == "GET":
+                await self._text(send, 200, render_metrics(self.backend, self.served_model_name),
+                                 "text/plain; version=0.0.4; charset=utf-8")
+                return
             if path == "/v1/models" and method == "GET":
                 await self._json(send, 200, {"object": "list", "data": [
                     {"id": self.served_model_name, "object": "model", "created": self.created, "owned_by": "cubic-serve-b200"}]})
@@ -121,6 +156,12 @@ class CubicASGIApp:
             await self._json(send, 404, _error_body(protocol, 404, "unknown route", "not_found_error"))
         except Exception:  # noqa: BLE001 - last-resort guard: never leak internals
             await self._json(send, 500, _error_body(protocol, 500, "internal server error", "server_error"))
+
+    async def _text(self, send, status: int, text: str, content_type: str) -> None:
+        body = text.encode()
+        await send({"type": "http.response.start", "status": status,
+                    "headers": [(b"content-type", content_type.encode()), (b"content-length", str(len(body)).encode())]})
+        await send({"type": "http.response.body", "body": body})
 
     async def _lifespan(self, receive, send) -> None:
         while True:

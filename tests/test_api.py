@@ -171,6 +171,9 @@ def test_server_routes_auth_errors():
     assert run(_call(app, "POST", "/v1/chat/completions", {**ok, "temperature": 9}, h))[0] == 400
     assert run(_call(app, "GET", "/v1/chat/completions", None, h))[0] == 405
     assert run(_call(app, "GET", "/nope", None, h))[0] == 404
+    assert run(_call(app, "GET", "/metrics"))[0] == 401                      # metrics sit behind the key too
+    st, body = run(_call(app, "GET", "/metrics", None, h))
+    assert st == 200 and b'cubic_ready{model="model-x"} 1' in body
     st, body = run(_call(app, "POST", "/v1/messages", {"model": "model-x", "max_tokens": 5,
                                                        "messages": [{"role": "user", "content": "hi"}]}, h))
     assert st == 200 and json.loads(body)["type"] == "message"
@@ -225,11 +228,16 @@ def test_real_backend_end_to_end_on_cpu():
             _call(app, "POST", "/v1/chat/completions", body),
             _call(app, "POST", "/v1/chat/completions", {**body, "stream": True, "stream_options": {"include_usage": True}}),
             _call(app, "POST", "/v1/messages", {**body, "max_tokens": 4}))
+        m = await _call(app, "GET", "/metrics")
         backend.close()
-        return r1, r2, r3
+        return r1, r2, r3, m
 
-    (s1, b1), (s2, b2), (s3, b3) = asyncio.run(go())
-    assert s1 == s2 == s3 == 200
+    (s1, b1), (s2, b2), (s3, b3), (sm, bm) = asyncio.run(go())
+    assert s1 == s2 == s3 == sm == 200
+    metrics = {l.split(" ")[0]: float(l.split(" ")[1]) for l in bm.decode().splitlines() if l and not l.startswith("#")}
+    assert metrics['cubic_requests_total{model="toy"}'] == 3 and metrics['cubic_generated_tokens_total{model="toy"}'] == 16
+    assert metrics['cubic_ready{model="toy"}'] == 1 and metrics['cubic_requests_running{model="toy"}'] == 0
+    assert "# TYPE cubic_kv_cache_usage_ratio gauge" in bm.decode()
     j1 = json.loads(b1)
     assert j1["usage"]["completion_tokens"] == 6 and j1["choices"][0]["finish_reason"] == "length"
     frames = [f for f in b2.decode().split("\n\n") if f]
