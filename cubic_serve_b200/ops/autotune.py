@@ -56,6 +56,13 @@ def _random_weight(fmt: int, n: int, k: int, act: bool, device) -> wq_pack.Packe
         groups = k // 128
         pw = wq_pack.pack_cubic4(codes, torch.rand(n, groups, generator=g) * 0.02 + 0.01, torch.full((n, groups), 0.8),
                                  torch.full((n, groups), 0.1), 128)
+    elif fmt == wq_pack.FMT_AFFINE4:
+        codes = torch.randint(0, 16, (n, k), generator=g, dtype=torch.uint8)
+        groups = k // 128
+        pw = wq_pack.pack_affine4(codes, torch.rand(n, groups, generator=g) * 0.01 + 0.005, torch.full((n, groups), -0.04), 128)
+    elif fmt == wq_pack.FMT_NVFP4:
+        packed = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+        pw = wq_pack.pack_nvfp4(packed, torch.rand(n, k // 16, generator=g) * 0.5 + 0.25, 0.02)
     else:
         raise NotImplementedError(f"no synthetic weight for format {fmt}")
     if act:

@@ -56,6 +56,9 @@ def test_autotune_shapes_candidates_and_install():
     assert ("tile", 8) in autotune.candidates(16, 4096, 4096) and ("tile", 8) not in autotune.candidates(16, 4096, 1024)
     w = autotune._random_weight(wq_pack.FMT_CUBIC4, 256, 512, True, "cpu")
     assert w.act_interleaved and (w.n, w.k) == (256, 512)
+    for fmt in (wq_pack.FMT_AFFINE4, wq_pack.FMT_NVFP4, wq_pack.FMT_BF16):
+        assert autotune._random_weight(fmt, 128, 256, False, "cpu").fmt == fmt
+    assert (wq_pack.FMT_NVFP4, 5120, 2048, False) in autotune.model_shapes(NAMED_CONFIGS["moe-30b-a3b"]())
     plan = {autotune.plan_key(0, 16, 6144, 4096, False): {"use": True, "kernel": "tile", "splits": 3},
             autotune.plan_key(0, 16, 4096, 4096, False): {"use": False, "kernel": "tile", "splits": 4},
             autotune.plan_key(3, 64, 151936, 4096, False): {"use": True, "kernel": "stream_k", "splits": 0}}
