@@ -53,6 +53,7 @@ def run_qualification(device: int = 0, quick: bool = False) -> dict:
     same = torch.equal(K.wq_gemm(x_small, pw), K.wq_gemm(x_big, pw)[:16])
     results.append({"kernel": "wq_gemm padding isolation", "shape": [16, 64], "class": "exact" if same else "mismatch", "rel_l2": 0.0})
     results += _qualify_gemm_variants(dev, g, quick)
+    results += _qualify_cross_m(dev, g, quick)
     results += _qualify_recurrent_and_rotation(dev, g)
     results.append(_qualify_graph_replay(dev))
     torch.cuda.synchronize(dev)
@@ -90,6 +91,38 @@ def _qualify_gemm_variants(dev, g, quick: bool) -> list[dict]:
                             2.0 ** -5))
     finally:
         lib.cb_wq_gemm_pair_mode(1)
+    return out
+
+
+def _qualify_cross_m(dev, g, quick: bool) -> list[dict]:
+    """Cross-M audit: the result of a row must not depend on how many other rows share its batch beyond the order of
+    fp32 partial sums (another launch form may split K elsewhere).  The first rows of a large batch are compared with
+    the same rows run alone, for the kernels whose launch form changes with the row count: the weight GEMM (per-tile
+    splits vs persistent kernel), the fused SwiGLU GEMM and row-wise RMSNorm.  ``exact`` = batch invariant bit for bit,
+    ``rounding`` = equal to within the bf16 output rounding.  (Reference: ``guardrail/quantized_graph/cross_m.py``.)"""
+    from ..ops import kernels as K, wq_pack
+    from ..quantization import cubic
+    out = []
+    shapes = [(1024, 1024)] if quick else [(1024, 1024), (6144, 4096)]
+    for n, k in shapes:
+        w = torch.randn(n, k, generator=g) * 0.02
+        p = cubic.quantize(w, cubic.CubicScheme(4, 128))
+        pw = wq_pack.pack_cubic4(cubic.unpack_codes(p["weight_packed"], 4, k), p["weight_scale"], p["weight_a"], p["weight_b"],
+                                 128)
+        x = (torch.randn(256, k, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+        big = K.wq_gemm(x, pw.to(dev))
+        bound = 4 * 2.0 ** -8                       # a few bf16 output roundings of differently ordered fp32 sums
+        for m in (1, 16, 64):
+            out.append(_verdict(f"cross-M wq_gemm[cubic4] rows {m} of 256", (m, n, k), K.wq_gemm(x[:m].contiguous(), pw.to(dev)),
+                                big[:m], bound))
+        pa = wq_pack.swiglu_interleave(pw).to(dev)
+        big_a = K.wq_gemm_act(x, pa)
+        out.append(_verdict("cross-M wq_gemm + SwiGLU rows 16 of 256", (16, n // 2, k), K.wq_gemm_act(x[:16].contiguous(), pa),
+                            big_a[:16], 8 * 2.0 ** -8))
+    xs = torch.randn(256, 4096, generator=g).to(torch.bfloat16).to(dev)
+    wn = torch.randn(4096, generator=g).to(torch.bfloat16).to(dev)
+    out.append(_verdict("cross-M rmsnorm rows 3 of 256", (3, 4096), K.rmsnorm(xs[:3].contiguous(), wn, 1e-6),
+                        K.rmsnorm(xs, wn, 1e-6)[:3], 2.0 ** -8))
     return out
 
 

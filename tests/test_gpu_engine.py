@@ -125,8 +125,11 @@ def test_qualification_run_passes():
     rep = run_qualification(0, quick=True)
     assert rep["ok"], [r for r in rep["results"] if r["class"] == "mismatch"]
     names = " ".join(r["kernel"] for r in rep["results"])
-    for part in ("CTA pairs", "SwiGLU", "gdn_delta", "hadamard", "graph replay"):
+    for part in ("CTA pairs", "SwiGLU", "gdn_delta", "hadamard", "graph replay", "cross-M wq_gemm", "cross-M rmsnorm"):
         assert part in names
+    cross = {r["kernel"]: r["class"] for r in rep["results"] if r["kernel"].startswith("cross-M")}
+    assert cross["cross-M rmsnorm rows 3 of 256"] == "exact"            # row-wise kernels are batch invariant bit for bit
+    print("cross-M classes:", cross)
 
 
 def test_constrained_requests_decode_in_graphs():
