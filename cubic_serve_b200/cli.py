@@ -91,6 +91,8 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--quick", action="store_true")
     q.add_argument("--evidence-dir", help="directory of start-up receipts (default: $CUBIC_EVIDENCE_DIR or the user cache)")
     q.add_argument("--reuse", action="store_true", help="accept a passing receipt made by the same code on the same GPU model")
+    q.add_argument("--save", help="write the report (verdict, error and result digest of every check) to this JSON file")
+    q.add_argument("--against", help="compare with a report saved earlier: which checks kept their bits, which changed")
 
     ci = sub.add_parser("check-install", help="check python modules, the native library and the GPUs")
     ci.add_argument("--build", action="store_true", help="(re)build the native library first")
@@ -213,6 +215,16 @@ def _qualify(args) -> int:
     from .guardrail.qualify import qualify_with_receipt
     report, reused = qualify_with_receipt(args.device, quick=args.quick, evidence_dir=args.evidence_dir, force=not args.reuse)
     report = dict(report, receipt="reused" if reused else "new")
+    if args.save:
+        from pathlib import Path
+        Path(args.save).write_text(json.dumps(report, indent=1))
+    if args.against:
+        from pathlib import Path
+
+        from .guardrail.qualify import compare_reports
+        diff = compare_reports(json.loads(Path(args.against).read_text()), report)
+        print(json.dumps(diff, indent=1))
+        return 0 if diff["ok"] else 1
     print(json.dumps(report, indent=1))
     return 0 if report["ok"] else 1
 

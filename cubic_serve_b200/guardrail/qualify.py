@@ -62,9 +62,36 @@ def run_qualification(device: int = 0, quick: bool = False) -> dict:
     return {"ok": ok, "device": torch.cuda.get_device_name(dev), "seconds": round(time.time() - t0, 2), "results": results}
 
 
+def tensor_digest(t: torch.Tensor) -> str:
+    """Digest of a result's bits: two builds that print the same digest computed the same values."""
+    import hashlib
+    raw = t.detach().contiguous().cpu()
+    return hashlib.sha256(raw.view(torch.uint8).numpy().tobytes()).hexdigest()[:16]
+
+
 def _verdict(name: str, shape, got, ref, bound: float) -> dict:
     v = compare_tensors(got, ref, bound)
-    return {"kernel": name, "shape": list(shape), "class": v.klass.value, "rel_l2": v.rel_l2}
+    return {"kernel": name, "shape": list(shape), "class": v.klass.value, "rel_l2": v.rel_l2, "digest": tensor_digest(got)}
+
+
+def compare_reports(old: dict, new: dict) -> dict:
+    """Operator artifacts of two qualification reports side by side: which checks kept their bits, which changed
+    (and whether both sides still pass), which appeared or disappeared.  Reports come from ``run_qualification``
+    (``cubic qualify --save``); only checks that carry a result digest can be called identical."""
+    a = {r["kernel"] + " " + str(r["shape"]): r for r in old.get("results", [])}
+    b = {r["kernel"] + " " + str(r["shape"]): r for r in new.get("results", [])}
+    same, changed, regressed = [], [], []
+    for key in sorted(set(a) & set(b)):
+        ra, rb = a[key], b[key]
+        if rb["class"] == "mismatch" and ra["class"] != "mismatch":
+            regressed.append(key)
+        elif ra.get("digest") and ra.get("digest") == rb.get("digest"):
+            same.append(key)
+        else:
+            changed.append({"check": key, "old": {k: ra.get(k) for k in ("class", "rel_l2", "digest")},
+                            "new": {k: rb.get(k) for k in ("class", "rel_l2", "digest")}})
+    return {"identical": same, "changed": changed, "regressed": regressed, "added": sorted(set(b) - set(a)),
+            "removed": sorted(set(a) - set(b)), "ok": not regressed and new.get("ok", False)}
 
 
 def _qualify_gemm_variants(dev, g, quick: bool) -> list[dict]:

@@ -53,3 +53,21 @@ def test_trace_record_and_replay(tmp_path):
     assert rep2.ok
     bad = replay_trace(trace, engine(seed=1))                       # other weights: a difference is located
     assert not bad.ok and bad.first_difference["position"] >= 0 and "request_id" in bad.first_difference
+
+
+def test_qualification_reports_compare_by_result_digest():
+    import torch
+    from cubic_serve_b200.guardrail.qualify import compare_reports, tensor_digest
+    x = torch.arange(12, dtype=torch.float32).view(3, 4).to(torch.bfloat16)
+    assert tensor_digest(x) == tensor_digest(x.clone()) and tensor_digest(x) != tensor_digest(x + 1)
+    assert tensor_digest(x.t()) == tensor_digest(x.t().contiguous())                  # values, not strides
+    row = lambda k, c, d, e=0.001: {"kernel": k, "shape": [4, 4], "class": c, "rel_l2": e, "digest": d}  # noqa: E731
+    old = {"ok": True, "results": [row("gemm", "rounding", "aa"), row("norm", "exact", "bb"), row("attn", "rounding", "cc"),
+                                   row("gone", "exact", "dd")]}
+    new = {"ok": True, "results": [row("gemm", "rounding", "aa"), row("norm", "rounding", "b2", 0.002),
+                                   row("attn", "mismatch", "c2", 0.5), row("fresh", "exact", "ee")]}
+    d = compare_reports(old, new)
+    assert d["identical"] == ["gemm [4, 4]"] and [c["check"] for c in d["changed"]] == ["norm [4, 4]"]
+    assert d["regressed"] == ["attn [4, 4]"] and d["added"] == ["fresh [4, 4]"] and d["removed"] == ["gone [4, 4]"]
+    assert not d["ok"]
+    assert compare_reports(old, old)["ok"] and len(compare_reports(old, old)["identical"]) == 4
