@@ -134,30 +134,3 @@ class LaunchPlan:
         if not fitting:
             raise ValueError(f"no graph bucket holds {live_rows} rows")
         return LaunchPlan(min(fitting, key=lambda b: b.capacity), live_rows)
-
-
-@dataclass
-class ReplayLease:
-    """Exclusive topology-wide permission to replay one step (reference: ``executor/replay_lease.py:33``)."""
-    token: int
-    released: bool = False
-
-
-class ReplayLeasePool:
-    """At most one step may be in flight across the topology; a second acquire before release is an error."""
-
-    def __init__(self) -> None:
-        self._next = 0
-        self._active: ReplayLease | None = None
-
-    def acquire(self) -> ReplayLease:
-        if self._active is not None and not self._active.released:
-            raise RuntimeError("a replay lease is already held")
-        self._next += 1
-        self._active = ReplayLease(self._next)
-        return self._active
-
-    def release(self, lease: ReplayLease) -> None:
-        if lease is not self._active or lease.released:
-            raise RuntimeError("releasing a lease that is not active")
-        lease.released = True

@@ -1,6 +1,6 @@
 import pytest
 
-from cubic_serve_b200.contracts.execution import GraphBucket, GroupKind, LaunchPlan, ParallelTopology, ReplayLeasePool
+from cubic_serve_b200.contracts.execution import GraphBucket, GroupKind, LaunchPlan, ParallelTopology
 
 
 def test_topology_tp4_pp2_ep2():
@@ -29,15 +29,6 @@ def test_launch_plan_and_lease():
     assert plan.bucket.capacity == 128 and plan.padding_rows == 58
     with pytest.raises(ValueError):
         LaunchPlan.choose(buckets, 300)
-    pool = ReplayLeasePool()
-    a = pool.acquire()
-    with pytest.raises(RuntimeError):
-        pool.acquire()
-    pool.release(a)
-    b = pool.acquire()
-    with pytest.raises(RuntimeError):
-        pool.release(a)
-    pool.release(b)
 
 
 def test_hybrid_config_layer_types_and_hf_parse(tmp_path):
