@@ -43,8 +43,17 @@ def inspect_gguf(path: str | Path) -> dict:
     f = reader.fields.get("general.architecture")
     if f is not None:
         arch = bytes(f.parts[-1]).decode("utf-8", errors="replace")
-    return {"file": str(path), "architecture": arch, "tensors": len(reader.tensors), "types": types,
+    info = {"file": str(path), "architecture": arch, "tensors": len(reader.tensors), "types": types,
             "admitted": not rejected, "rejected": rejected[:8]}
+    try:
+        cfg = config_from_gguf(reader)
+        info.update(model=cfg.name, layers=cfg.num_layers, hidden=cfg.hidden_size, vocab=cfg.vocab_size,
+                    heads=f"{cfg.num_q_heads}q/{cfg.num_kv_heads}kv x {cfg.head_dim}", intermediate=cfg.intermediate_size,
+                    rope_theta=cfg.rope_theta, qk_norm=cfg.qk_norm, tied_embeddings=cfg.tie_embeddings,
+                    qk_rows_unpermuted=arch in PERMUTED_QK_ARCHITECTURES, served=not rejected)
+    except gq.GGUFFormatError as exc:
+        info.update(served=False, reason=str(exc))
+    return info
 
 
 def load_gguf_tensors(path: str | Path):

@@ -164,6 +164,10 @@ def test_gguf_mixed_block_types_and_closed_inventory(tmp_path):
     want = np.concatenate([dense["0.q"], dense["0.k"], dense["0.v"]])
     assert _rel(wq_pack.unpack_to_dense(w.layers[0].qkv).numpy(), want) < 4e-3
     assert w.layers[0].gate_up.fmt == wq_pack.FMT_AFFINE4
+    from cubic_serve_b200.models.gguf import inspect_gguf
+    info = inspect_gguf(path)
+    assert info["served"] and info["architecture"] == "qwen2" and info["layers"] == 2 and info["heads"] == "4q/2kv x 64"
+    assert info["types"]["Q4_K"] == 12 and info["types"]["Q8_0"] == 2 and not info["qk_rows_unpermuted"]
     bad = tmp_path / "bad.gguf"
     wtr = gguf.GGUFWriter(str(bad), "gpt2")
     wtr.add_block_count(1)
@@ -174,6 +178,7 @@ def test_gguf_mixed_block_types_and_closed_inventory(tmp_path):
     wtr.close()
     with pytest.raises(gq.GGUFFormatError, match="not served"):
         load_gguf_decoder_weights(bad)
+    assert inspect_gguf(bad)["served"] is False and "not served" in inspect_gguf(bad)["reason"]
 
 
 @pytest.mark.gpu
