@@ -175,3 +175,26 @@ def test_hybrid_engine_chunked_prefill_and_graph_decode_agree():
     # a second wave of requests reuses the state slots: same prompts, same tokens
     b2 = eng_b.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     assert b2 == b
+
+
+def test_hybrid_moe_family_decodes_the_same_eagerly_and_in_graphs():
+    """The hybrid family with routed experts (Gated DeltaNet / gated attention mixers, mixture-of-experts feed-forward):
+    one-shot prefill with eager decode against chunked prefill with CUDA-graph decode."""
+    import dataclasses
+    import numpy as np
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    cfg = dataclasses.replace(_hybrid_cfg(), name="hybrid-moe-toy", family="qwen3_5_moe", num_experts=8, experts_per_token=2,
+                              moe_intermediate_size=128)
+    assert cfg.is_hybrid and cfg.is_moe
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, cfg.vocab_size, n).tolist() for n in (19, 33, 8)]
+    eng_a, run_a = _engine(cfg, graphs=False, chunk=512)
+    a = eng_a.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    eng_b, run_b = _engine(cfg, graphs=True, chunk=16)
+    b = eng_b.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+    run_a.ws.check_status()
+    run_b.ws.check_status()
+    assert run_b.w.layers[0].moe is not None and run_b.w.layers[0].gdn is not None and run_b.w.layers[3].gdn is None
+    assert all(len(o) == 10 for o in b)
+    agree = np.mean([x == y for pa, pb in zip(a, b) for x, y in zip(pa, pb)])
+    assert agree >= 0.9, (agree, a[0], b[0])
