@@ -296,7 +296,7 @@ def _check_partition(model: str, tp: int, pp: int) -> None:
     else:
         return
     try:
-        plan_partition(cfg, tp, pp)
+        plan_partition(cfg, tp, pp, tp if cfg.is_moe else 1)      # experts are owned whole: EP over the TP ranks
     except PartitionError as exc:
         raise SystemExit(f"--tp-size {tp} --pp-size {pp} does not fit {cfg.name}: {exc}") from exc
 
