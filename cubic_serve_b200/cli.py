@@ -104,6 +104,15 @@ def build_parser() -> argparse.ArgumentParser:
     au.add_argument("--no-digests", action="store_true")
     au.add_argument("--json", action="store_true")
     au.add_argument("--verbose", action="store_true")
+    tr = sub.add_parser("trace", help="record an execution trace of synthetic requests, or replay a recorded trace and "
+                                      "report the first token that differs (another build, execution mode or topology)")
+    tr.add_argument("action", choices=("record", "replay"))
+    tr.add_argument("trace", help="trace file (JSON lines)")
+    tr.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
+    tr.add_argument("--requests", type=int, default=8, help="record: number of synthetic requests")
+    tr.add_argument("--max-tokens", type=int, default=16)
+    tr.add_argument("--serve-args", default="", help="further `cubic serve` flags for the engine, one string "
+                                                     "(e.g. \"--execution-mode eager --max-running-requests 8\")")
     s = sub.add_parser("serve", help="serve a checkpoint over OpenAI / Anthropic compatible HTTP")
     s.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
     g = s.add_argument_group("Server")
@@ -181,6 +190,47 @@ def _serve(args) -> int:
     return run_http_server(backend, model_name, args)
 
 
+def _trace(args) -> int:
+    """``cubic trace record|replay``: the engine is built exactly as ``cubic serve`` builds it (same flags)."""
+    import shlex
+
+    import numpy as np
+
+    from .guardrail.replay import TraceRecorder, replay_trace
+    from .runtime.scheduler import SamplingParams
+    from .runtime.serving import build_backend
+    sargs = build_parser().parse_args(["serve", args.model, *shlex.split(args.serve_args)])
+    spec = parse_speculative_config(sargs.speculative_config)
+    devices = parse_devices(sargs.devices)
+    tp = sargs.tp_size or max(1, len(devices) // sargs.pp_size)
+    validate_topology(devices, tp, sargs.pp_size, sargs.ep_size, spec)
+    backend, _name = build_backend(sargs, devices, tp, spec, _kv_bits(sargs.k_cache_dtype), _kv_bits(sargs.v_cache_dtype))
+    engine = backend.engine
+    backend.close()                                 # stop the serving thread: this command steps the engine itself
+    try:
+        if args.action == "record":
+            rec = TraceRecorder(engine)
+            rng = np.random.default_rng(sargs.seed)
+            vocab = min(engine.executor.cfg.vocab_size if hasattr(engine.executor, "cfg") else 256, 50000)
+            for i in range(args.requests):
+                prompt = rng.integers(1, vocab, int(rng.integers(4, 48))).tolist()
+                rec.add_request(prompt, SamplingParams(max_tokens=args.max_tokens, ignore_eos=True), f"trace-{i}")
+                if i % 3 == 2:
+                    rec.step()                      # arrivals spread over steps: prefill and decode rows mix
+            rec.run()
+            rec.save(args.trace)
+            tokens = sum(len(t) for r in rec.records if r["kind"] == "step" for t in r["emitted"].values())
+            print(json.dumps({"recorded": args.trace, "requests": args.requests, "tokens": tokens}))
+            return 0
+        report = replay_trace(args.trace, engine)
+        print(report.to_json())
+        return 0 if report.ok else 1
+    finally:
+        stop = getattr(engine.executor, "close", None)      # multi-process executors own worker processes
+        if stop:
+            stop()
+
+
 def _inspect(args) -> int:
     from .models.checkpoint import inspect_checkpoint
     if args.model.startswith("random:"):
@@ -237,6 +287,8 @@ def main(argv: list[str] | None = None) -> int:
         return _inspect(args)
     if args.command == "qualify":
         return _qualify(args)
+    if args.command == "trace":
+        return _trace(args)
     if args.command == "audit-checkpoint":
         from .utils.audit_checkpoint import audit_checkpoint, format_report as format_audit
         report = audit_checkpoint(args.checkpoint, args.reference, digests=not args.no_digests)

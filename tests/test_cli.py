@@ -1,4 +1,5 @@
 import argparse
+import json
 
 import pytest
 
@@ -54,3 +55,32 @@ def test_kv_page_planning():
     per_page = 36 * 8 * 4608
     assert pages == min((96 << 30) // per_page, 256 * 128 + 64)
     assert plan_kv_pages(100 << 30, 4 << 30, cfg, 8, 4, 8, 2048, 256) == 256 * 128 + 64
+
+
+def test_trace_record_and_replay_between_two_schedules(tmp_path, capsys):
+    """``cubic trace``: a trace recorded with four request slots replays token for token on an engine with two."""
+    trace = tmp_path / "t.jsonl"
+    assert cli.main(["trace", "record", str(trace), "random:toy", "--requests", "5", "--max-tokens", "5",
+                     "--serve-args", "--execution-mode eager --max-running-requests 4"]) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["tokens"] == 25 and trace.exists()
+    assert cli.main(["trace", "replay", str(trace), "random:toy",
+                     "--serve-args", "--execution-mode eager --max-running-requests 2"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["ok"] and rep["tokens"] == 25 and rep["first_difference"] is None
+    # a trace that another model produced does not replay: the first difference is located
+    lines = trace.read_text().splitlines()
+    doctored = []
+    for line in lines:
+        r = json.loads(line)
+        if r["kind"] == "step" and r["emitted"]:
+            rid = next(iter(r["emitted"]))
+            r["emitted"][rid][0] = (r["emitted"][rid][0] + 1) % 200
+            doctored.append(json.dumps(r))
+            doctored += lines[len(doctored):]
+            break
+        doctored.append(line)
+    trace.write_text("\n".join(doctored) + "\n")
+    assert cli.main(["trace", "replay", str(trace), "random:toy", "--serve-args", "--execution-mode eager"]) == 1
+    diff = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["first_difference"]
+    assert diff["position"] == 0 and "request_id" in diff
