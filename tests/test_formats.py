@@ -138,3 +138,63 @@ def test_quantization_registry_builtins_and_plugins():
         assert back.shape == (8, 16) and torch.equal(back > 0, w > 0)
     finally:
         R._extensions.pop("sign1", None)
+
+
+def test_out_of_tree_format_through_an_installed_entry_point(tmp_path, monkeypatch):
+    """A synthetic external distribution publishes a weight format under the entry-point group; the registry finds
+    it when a checkpoint names the format, and a checkpoint written in it is admitted, audited and loaded."""
+    import importlib
+    import sys
+    import textwrap
+
+    import torch
+
+    from cubic_serve_b200.models import checkpoint as C
+    from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+    from cubic_serve_b200.quantization import registry
+
+    site = tmp_path / "site"
+    (site / "halfscale_fmt").mkdir(parents=True)
+    (site / "halfscale_fmt" / "__init__.py").write_text(textwrap.dedent('''
+        import torch
+        from cubic_serve_b200.quantization.registry import QuantizationExtension
+
+        def _detect(qc):
+            if qc.get("quant_method") == "halfscale":
+                from cubic_serve_b200.models.config import QuantSpec
+                return QuantSpec("halfscale", 8, 0)
+            return None
+
+        def extension():
+            # int8 codes with one fp32 scale per row, stored as <module>.codes / <module>.row_scale
+            return QuantizationExtension(
+                "halfscale", ("codes", "row_scale"), ("w8a16",), None, _detect,
+                lambda p, shape, q: p["codes"].float() * p["row_scale"].float()[:, None],
+                lambda w, q: {"codes": torch.round(w / (w.abs().amax(1, keepdim=True) / 127)).to(torch.int8),
+                              "row_scale": (w.abs().amax(1) / 127).float()},
+                lambda q: {"quant_method": "halfscale"}, "test format")
+    '''))
+    info = site / "halfscale_fmt-0.1.dist-info"
+    info.mkdir()
+    (info / "METADATA").write_text("Metadata-Version: 2.1\nName: halfscale-fmt\nVersion: 0.1\n")
+    (info / "entry_points.txt").write_text(f"[{registry.ENTRY_POINT_GROUP}]\nhalfscale = halfscale_fmt:extension\n")
+    monkeypatch.syspath_prepend(str(site))
+    importlib.invalidate_caches()
+    monkeypatch.setattr(registry, "_entry_points_loaded", False)
+    try:
+        with pytest.raises(registry.QuantizationRegistryError):
+            registry.resolve_compute_mode("halfscale", "w4a16")       # found by discovery, offers w8a16 only
+        assert registry.get("halfscale").compute_modes == ("w8a16",)
+        assert registry.detect({"quant_method": "halfscale"}).method == "halfscale"
+        cfg = ModelConfig(name="ext", num_layers=1, hidden_size=128, num_q_heads=2, num_kv_heads=1, head_dim=64,
+                          intermediate_size=256, vocab_size=256, quant=QuantSpec("halfscale", 8, 0))
+        ck = C.admit_checkpoint(C.write_random_checkpoint(tmp_path / "ck", cfg, seed=0))
+        assert ck.cfg.quant.method == "halfscale" and set(ck.payloads["model.layers.0.mlp.down_proj"]) == {"codes", "row_scale"}
+        w = C.load_decoder_weights(ck, "cpu")
+        from cubic_serve_b200.ops import wq_pack
+        assert w.layers[0].down.fmt == wq_pack.FMT_BF16               # no native layout: decoded to bf16 at load
+        from cubic_serve_b200.utils.audit_checkpoint import audit_checkpoint
+        assert audit_checkpoint(ck.store.path, digests=False)["ok"]
+    finally:
+        registry._extensions.pop("halfscale", None)
+        sys.modules.pop("halfscale_fmt", None)
