@@ -163,3 +163,44 @@ def test_constrained_requests_decode_in_graphs():
     assert toks[-1] == eos and "".join(chr(t) for t in toks[:-1]) in options
     assert reqs[other].output == baseline
     assert eager_steps and all(n > 1 for n in eager_steps)          # only the prefill step ran eagerly
+
+
+def test_prefix_resume_equals_cold_start_on_device():
+    """Cold vs prefix-resumed identity on the native executor: a request that finds its prompt's pages in the prefix
+    cache (shared pages, copy-on-write of the partly filled last page) continues exactly as the cold request did;
+    a request that shares only the first part of a cached prompt reuses those pages and prefills the rest."""
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    dev = torch.device("cuda")
+    cfg = ModelConfig(name="pfx", num_layers=2, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, rope_theta=1e6, quant=QuantSpec("cubic", 4, 128))
+    weights = random_decoder_weights(cfg, dev, seed=0, std=0.05)
+
+    def engine(prefix):
+        runner = DecoderRunner(cfg, weights, num_pages=256, max_tokens=512)
+        ex = GpuExecutor(runner, max_rows=16, max_prefill_tokens=512, max_model_len=256)
+        ex.capture_decode_graphs([4, 16])
+        return LLMEngine(ex, 256, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
+                                                  enable_prefix_cache=prefix)), runner
+
+    rng = np.random.default_rng(4)
+    base = rng.integers(0, 2048, 70).tolist()                   # four full pages and a part of the fifth
+    fork = base[:48] + rng.integers(0, 2048, 20).tolist()       # shares three pages with it
+    sp = SamplingParams(max_tokens=12, ignore_eos=True)
+    cold_eng, r0 = engine(False)
+    cold = [cold_eng.generate([p], sp)[0] for p in (base, fork)]
+    eng, r1 = engine(True)
+    first = eng.generate([base], sp)[0]
+    assert first == cold[0] and eng.prefix.hit_tokens == 0
+    again = eng.generate([base], sp)[0]                         # every full page of the prompt comes from the cache
+    assert eng.prefix.hit_tokens >= 64 and again == cold[0]
+    hits = eng.prefix.hit_tokens
+    forked = eng.generate([fork], sp)[0]
+    assert eng.prefix.hit_tokens - hits >= 48 and forked == cold[1]
+    both = eng.generate([base, fork], sp)                       # two requests sharing cached pages in one batch
+    assert both == cold
+    r0.ws.check_status()
+    r1.ws.check_status()
+    assert eng.pool.num_used == len(eng.prefix)                 # only cache entries keep pages
