@@ -181,8 +181,10 @@ def _serve(args) -> int:
     if args.operator_config:
         # through the environment as well, so that spawned rank workers install the same policies
         from .ops import strategies
-        strategies.install(strategies.load_operator_config(args.operator_config))
+        ctx = strategies.launch_context(args.model, tp, devices[0])
+        strategies.install(strategies.load_operator_config(args.operator_config, ctx))
         os.environ["CUBIC_OPERATOR_CONFIG"] = os.path.abspath(args.operator_config)
+        os.environ["CUBIC_OPERATOR_CONTEXT"] = json.dumps(ctx)
     os.environ.setdefault("OMP_NUM_THREADS", "4")
     os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
     sys.setswitchinterval(0.001)

@@ -9,8 +9,9 @@ deployment can pin or change a policy without touching code.  Here the families 
 ``attention``  how many KV splits a decode step uses for a given number of row blocks
 ``moe``        rows per work item of the grouped expert GEMMs
 
-``load_operator_config(path)`` reads ``{"gemm": {...}, "attention": {...}, "moe": {...}}``; unknown families or keys
-are errors (a typo must not silently keep the default).  ``CUBIC_OPERATOR_CONFIG=/path.json`` or
+``load_operator_config(path)`` reads ``{"gemm": {...}, "attention": {...}, "moe": {...}, "profiles": [...]}``; unknown
+families or keys are errors (a typo must not silently keep the default).  Profiles override the base by device name,
+model name, SM count and tensor-parallel size (reference: profiles by device / model / shape).  ``CUBIC_OPERATOR_CONFIG=/path.json`` or
 ``cubic serve --operator-config`` installs it process-wide before any kernel is launched.
 """
 from __future__ import annotations
@@ -87,21 +88,80 @@ def _family(cls, data: object, name: str):
     return replace(base, **typed)
 
 
-def operator_config_from_dict(data: object) -> OperatorConfig:
+_FAMILIES = {"gemm": GemmPolicy, "attention": AttentionPolicy, "moe": MoePolicy}
+_MATCH_KEYS = ("device", "model", "sms", "tp")
+
+
+def _profile_matches(match: object, context: dict) -> bool:
+    """``match``: ``{"device": "NVIDIA B200*", "model": "dense-*", "sms": 148, "tp": 8}`` -- strings are shell patterns
+    (case-insensitive), numbers compare equal; a key the context does not provide does not match."""
+    import fnmatch
+    if not isinstance(match, dict) or not match:
+        raise ValueError("operator config: a profile needs a non-empty 'match' object")
+    unknown = sorted(set(match) - set(_MATCH_KEYS))
+    if unknown:
+        raise ValueError(f"operator config: unknown match key(s) {unknown} (known: {list(_MATCH_KEYS)})")
+    for key, want in match.items():
+        have = context.get(key)
+        if have is None:
+            return False
+        if isinstance(want, str):
+            if not fnmatch.fnmatchcase(str(have).lower(), want.lower()):
+                return False
+        elif have != want:
+            return False
+    return True
+
+
+def operator_config_from_dict(data: object, context: dict | None = None) -> OperatorConfig:
+    """Top-level families are the base; ``"profiles": [{"match": {...}, "gemm": {...}, ...}, ...]`` are overrides by
+    device name, model name, SM count and tensor-parallel size: every profile that matches ``context`` is applied in
+    file order, a later one winning key by key.  Profiles are validated even when they do not match."""
     if not isinstance(data, dict):
         raise ValueError("operator config must be a JSON object")
-    families = {"gemm": GemmPolicy, "attention": AttentionPolicy, "moe": MoePolicy}
-    unknown = sorted(set(data) - set(families))
+    unknown = sorted(set(data) - set(_FAMILIES) - {"profiles"})
     if unknown:
         raise ValueError(f"operator config: unknown family {unknown}")
-    cfg = OperatorConfig(**{name: _family(cls, data.get(name, {}), name) for name, cls in families.items()})
+    merged = {name: dict(data.get(name, {})) if isinstance(data.get(name, {}), dict) else data.get(name) for name in _FAMILIES}
+    profiles = data.get("profiles", [])
+    if not isinstance(profiles, list):
+        raise ValueError("operator config: 'profiles' must be a list")
+    for i, prof in enumerate(profiles):
+        if not isinstance(prof, dict):
+            raise ValueError(f"operator config: profile {i} must be an object")
+        bad = sorted(set(prof) - set(_FAMILIES) - {"match", "name"})
+        if bad:
+            raise ValueError(f"operator config: unknown key(s) {bad} in profile {i}")
+        for name, cls in _FAMILIES.items():
+            _family(cls, prof.get(name, {}), f"profiles[{i}].{name}")          # a typo is an error in any profile
+        if _profile_matches(prof.get("match"), context or {}):
+            for name in _FAMILIES:
+                if isinstance(merged[name], dict):
+                    merged[name].update(prof.get(name, {}))
+    cfg = OperatorConfig(**{name: _family(cls, merged[name], name) for name, cls in _FAMILIES.items()})
     cfg.validate()
     return cfg
 
 
-def load_operator_config(path: str) -> OperatorConfig:
+def load_operator_config(path: str, context: dict | None = None) -> OperatorConfig:
     with open(path, "r", encoding="utf-8") as f:
-        return operator_config_from_dict(json.load(f))
+        return operator_config_from_dict(json.load(f), context)
+
+
+def launch_context(model: str | None = None, tp: int = 1, device: int = 0) -> dict:
+    """What profiles can match on, for the current process: GPU name and SM count (when a GPU is visible), the model
+    name and the tensor-parallel size."""
+    ctx: dict = {"tp": int(tp)}
+    if model:
+        ctx["model"] = model.split(":", 1)[1] if model.startswith("random:") else os.path.basename(model.rstrip("/"))
+    try:
+        import torch
+        if torch.cuda.is_available():
+            p = torch.cuda.get_device_properties(device)
+            ctx.update(device=p.name, sms=p.multi_processor_count)
+    except Exception:  # noqa: BLE001 - no GPU: device keys stay absent and device-specific profiles do not match
+        pass
+    return ctx
 
 
 _active: OperatorConfig | None = None
@@ -112,7 +172,8 @@ def active() -> OperatorConfig:
     global _active
     if _active is None:
         path = os.environ.get("CUBIC_OPERATOR_CONFIG")
-        _active = load_operator_config(path) if path else OperatorConfig()
+        ctx = json.loads(os.environ.get("CUBIC_OPERATOR_CONTEXT") or "null")      # set by the process that chose profiles
+        _active = load_operator_config(path, ctx if ctx is not None else launch_context()) if path else OperatorConfig()
     return _active
 
 

@@ -67,3 +67,31 @@ def test_autotune_shapes_candidates_and_install():
         assert K.TUNED_PLANS == {"0:16:6144:4096:0": (False, 3), "3:64:151936:4096:0": (True, 0)}
     finally:
         assert autotune.install(None) == 0 and not K.TUNED_PLANS
+
+
+def test_operator_profiles_override_by_device_model_and_topology(tmp_path):
+    import json
+    import pytest
+    from cubic_serve_b200.ops import strategies as S
+    data = {"gemm": {"split_k_max": 4},
+            "profiles": [{"name": "b200", "match": {"device": "nvidia b200*"}, "gemm": {"split_k_max": 8, "pair_min_blocks": 96}},
+                         {"match": {"model": "moe-*", "tp": 4}, "moe": {"rows_per_item_small": 48}, "gemm": {"split_k_max": 6}},
+                         {"match": {"sms": 132}, "attention": {"target_ctas": 264}}]}
+    base = S.operator_config_from_dict(data)
+    assert base.gemm.split_k_max == 4 and base.moe.rows_per_item_small == 32           # no context: nothing matches
+    b200 = S.operator_config_from_dict(data, {"device": "NVIDIA B200", "sms": 148, "model": "dense-8b", "tp": 1})
+    assert (b200.gemm.split_k_max, b200.gemm.pair_min_blocks, b200.attention.target_ctas) == (8, 96, 296)
+    moe = S.operator_config_from_dict(data, {"device": "NVIDIA B200", "sms": 148, "model": "moe-30b-a3b", "tp": 4})
+    assert moe.gemm.split_k_max == 6 and moe.gemm.pair_min_blocks == 96 and moe.moe.rows_per_item_small == 48   # later wins
+    h100 = S.operator_config_from_dict(data, {"device": "NVIDIA H100", "sms": 132, "model": "moe-30b-a3b", "tp": 2})
+    assert h100.gemm.split_k_max == 4 and h100.attention.target_ctas == 264
+    for bad in ({"profiles": [{"match": {"gpu": "x"}}]}, {"profiles": [{"match": {}}]}, {"profiles": {}},
+                {"profiles": [{"match": {"tp": 2}, "gemm": {"splitk": 1}}]}, {"profiles": [{"match": {"tp": 2}, "extra": 1}]}):
+        with pytest.raises(ValueError):
+            S.operator_config_from_dict(bad, {"tp": 1})
+    f = tmp_path / "op.json"
+    f.write_text(json.dumps(data))
+    assert S.load_operator_config(str(f), {"sms": 132}).attention.target_ctas == 264
+    ctx = S.launch_context("random:dense-8b", tp=2)
+    assert ctx["model"] == "dense-8b" and ctx["tp"] == 2
+    assert S.launch_context("/models/Qwen3-8B-cubic/", 1)["model"] == "Qwen3-8B-cubic"
