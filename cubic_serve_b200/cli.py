@@ -104,6 +104,14 @@ def build_parser() -> argparse.ArgumentParser:
     au.add_argument("--no-digests", action="store_true")
     au.add_argument("--json", action="store_true")
     au.add_argument("--verbose", action="store_true")
+    qz = sub.add_parser("quantize", help="quantize an unquantized checkpoint into a registered weight format "
+                                         "(round to nearest; check the result with audit-checkpoint --reference)")
+    qz.add_argument("source")
+    qz.add_argument("destination")
+    qz.add_argument("--format", default="cubic")
+    qz.add_argument("--bits", type=int, default=4)
+    qz.add_argument("--group-size", type=int, default=128)
+    qz.add_argument("--shard-gib", type=float, default=4.0)
     tr = sub.add_parser("trace", help="record an execution trace of synthetic requests, or replay a recorded trace and "
                                       "report the first token that differs (another build, execution mode or topology)")
     tr.add_argument("action", choices=("record", "replay"))
@@ -289,6 +297,11 @@ def main(argv: list[str] | None = None) -> int:
         return _inspect(args)
     if args.command == "qualify":
         return _qualify(args)
+    if args.command == "quantize":
+        from .utils.quantize_checkpoint import quantize_checkpoint
+        print(json.dumps(quantize_checkpoint(args.source, args.destination, args.format, args.bits, args.group_size,
+                                             int(args.shard_gib * 2 ** 30))))
+        return 0
     if args.command == "trace":
         return _trace(args)
     if args.command == "audit-checkpoint":

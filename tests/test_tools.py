@@ -90,3 +90,32 @@ def test_wheel_check(tmp_path):
     missing = {k: v for k, v in good.items() if not k.endswith(".so")}
     problems = check_wheel(wheel("missing.whl", {**missing, "tests/test_x.py": ""}))
     assert "cubic_serve_b200/libcubic_b200.so is not in the wheel" in problems and any("do not belong" in p for p in problems)
+
+
+def test_quantize_then_audit_then_load(tmp_path, capsys):
+    """bf16 checkpoint -> ``cubic quantize`` -> the audit against the source passes, the loader takes it, shards
+    and index are written when the shard limit is small."""
+    from cubic_serve_b200.cli import main
+    from cubic_serve_b200.models.checkpoint import admit_checkpoint, load_decoder_weights
+    from cubic_serve_b200.ops import wq_pack
+    from cubic_serve_b200.utils.quantize_checkpoint import quantize_checkpoint
+    src = write_random_checkpoint(tmp_path / "src", _cfg(QuantSpec("none", 16, 0)), seed=9)
+    (src / "tokenizer_config.json").write_text("{}")
+    assert main(["quantize", str(src), str(tmp_path / "q4"), "--format", "cubic", "--bits", "4", "--group-size", "128"]) == 0
+    stats = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert stats["quantized"] == 14 and stats["shards"] == 1 and stats["compression"] > 1.5
+    assert (tmp_path / "q4" / "model.safetensors").exists() and (tmp_path / "q4" / "tokenizer_config.json").exists()
+    audit = audit_checkpoint(tmp_path / "q4", src, digests=False)
+    assert audit["ok"] and audit["summary"]["quantized"] == 14 and audit["summary"]["rel_error_max"] < 0.18
+    ck = admit_checkpoint(tmp_path / "q4")
+    assert ck.cfg.quant.method == "cubic" and load_decoder_weights(ck, "cpu").layers[0].qkv.fmt == wq_pack.FMT_CUBIC4
+    sharded = quantize_checkpoint(src, tmp_path / "i8", "int", 8, 128, shard_bytes=200_000)
+    assert sharded["shards"] > 1 and (tmp_path / "i8" / "model.safetensors.index.json").exists()
+    a8 = audit_checkpoint(tmp_path / "i8", src, digests=False)
+    assert a8["ok"] and a8["summary"]["rel_error_max"] < 0.02
+    import pytest
+    from cubic_serve_b200.models.checkpoint import CheckpointError
+    with pytest.raises(CheckpointError, match="already quantized"):
+        quantize_checkpoint(tmp_path / "q4", tmp_path / "again", "cubic", 4, 128)
+    with pytest.raises(ValueError):
+        quantize_checkpoint(src, tmp_path / "x", "no-such-format", 4, 128)
