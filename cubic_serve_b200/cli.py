@@ -1,4 +1,5 @@
-"""``cubic`` command line: ``serve``, ``inspect-model``, ``qualify``, ``bench``.
+"""``cubic`` command line: ``serve``, ``inspect-model``, ``qualify``, ``check-install``, ``audit-checkpoint``,
+``quantize``, ``trace``.
 
 Flag surface follows the reference CLI (``cli.py:281-528`` there): Server / Model and generation / Devices and
 parallelism / Memory and cache / Scheduling / Advanced groups, JSON sub-configs for speculative decoding

@@ -74,6 +74,10 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
     from ..runtime.scheduler import SchedulerConfig
     if tp != 1 or args.pp_size != 1:
         from ..executor.multiproc import build_multiproc_backend
+        for flag in ("startup_numerical_audit", "tune_launch_plans"):
+            if getattr(args, flag, False):
+                log.warning("--%s applies to single-process serving; the rank workers of this deployment start without it "
+                            "(run `cubic qualify` on one GPU of the node instead)", flag.replace("_", "-"))
         return build_multiproc_backend(args, devices, tp, spec, k_bits, v_bits)
     model = args.model
     eager = args.execution_mode != "cuda" or not torch.cuda.is_available()
