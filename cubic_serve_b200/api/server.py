@@ -114,7 +114,8 @@ def render_metrics(backend, model: str) -> str:
 
 class CubicASGIApp:
     def __init__(self, backend: ChatBackend, model_id: str, served_model_name: str | None = None,
-                 api_key: str | None = None) -> None:
+                 api_key: str | None = None, sampling_defaults: dict | None = None) -> None:
+        self.sampling_defaults = dict(sampling_defaults or {})      # the checkpoint's generation_config.json
         self.backend = backend
         self.model_id = model_id
         self.served_model_name = served_model_name or model_id
@@ -217,9 +218,9 @@ class CubicASGIApp:
                 return
             body = decode_strict_json(raw)
             if protocol == "openai":
-                req = normalize_openai_chat_completions(body, self.served_model_name)
+                req = normalize_openai_chat_completions(body, self.served_model_name, self.sampling_defaults)
             else:
-                req = normalize_anthropic_messages(body, self.served_model_name)
+                req = normalize_anthropic_messages(body, self.served_model_name, self.sampling_defaults)
             if req.model not in (self.served_model_name, self.model_id):
                 raise RequestError(f"model {req.model!r} is not served here", param="model", status=404,
                                    code="model_not_found")

@@ -34,6 +34,35 @@ def _as_number(body: dict, key: str, default, lo=None, hi=None):
     return v
 
 
+def _default(defaults: dict | None, key: str, fallback):
+    """The deployment's default for a sampling field (the checkpoint's ``generation_config.json``), else ``fallback``."""
+    v = (defaults or {}).get(key)
+    return fallback if v is None else v
+
+
+def sampling_defaults_from_generation_config(path) -> dict:
+    """``temperature`` / ``top_p`` / ``top_k`` of a checkpoint's ``generation_config.json`` (reference:
+    ``generation/sampler.py:121``).  ``do_sample: false`` means greedy; ``top_k`` is capped at the sampler's 20; values
+    out of range are ignored rather than turned into request errors for every client."""
+    import json
+    from pathlib import Path
+    try:
+        raw = json.loads(Path(path).read_text())
+    except (OSError, ValueError):
+        return {}
+    out: dict = {}
+    t, p, k = raw.get("temperature"), raw.get("top_p"), raw.get("top_k")
+    if isinstance(t, (int, float)) and not isinstance(t, bool) and 0.0 <= t <= 2.0:
+        out["temperature"] = float(t)
+    if isinstance(p, (int, float)) and not isinstance(p, bool) and 0.0 < p <= 1.0:
+        out["top_p"] = float(p)
+    if isinstance(k, int) and not isinstance(k, bool) and k >= 0:
+        out["top_k"] = min(20, k)
+    if raw.get("do_sample") is False:
+        out["temperature"] = 0.0
+    return out
+
+
 def _stops(v) -> tuple[str, ...]:
     if v is None:
         return ()
@@ -131,7 +160,8 @@ def _openai_structured(body: dict) -> StructuredOutput:
     raise RequestError(f"unsupported response_format type {rf['type']!r}", param="response_format")
 
 
-def normalize_openai_chat_completions(body: Any, default_model: str | None = None) -> CanonicalChatRequest:
+def normalize_openai_chat_completions(body: Any, default_model: str | None = None,
+                                      sampling_defaults: dict | None = None) -> CanonicalChatRequest:
     _require(isinstance(body, dict), "request body must be a JSON object")
     model = body.get("model") or default_model
     _require(isinstance(model, str) and model, "model is required", "model")
@@ -172,9 +202,9 @@ def normalize_openai_chat_completions(body: Any, default_model: str | None = Non
     tlp = body.get("top_logprobs") or 0
     _require(isinstance(tlp, int) and 0 <= tlp <= 20, "top_logprobs must be in [0, 20]", "top_logprobs")
     sampling = SamplingMeta(
-        temperature=float(_as_number(body, "temperature", 1.0)),
-        top_p=float(_as_number(body, "top_p", 1.0)),
-        top_k=int(_as_number(body, "top_k", 0)),
+        temperature=float(_as_number(body, "temperature", _default(sampling_defaults, "temperature", 1.0))),
+        top_p=float(_as_number(body, "top_p", _default(sampling_defaults, "top_p", 1.0))),
+        top_k=int(_as_number(body, "top_k", _default(sampling_defaults, "top_k", 0))),
         seed=seed, max_tokens=max_tokens, stop=_stops(body.get("stop")),
         stop_token_ids=tuple(int(t) for t in (body.get("stop_token_ids") or [])),
         presence_penalty=float(_as_number(body, "presence_penalty", 0.0, -2.0, 2.0)),
@@ -239,7 +269,8 @@ def _anthropic_parts(content, role: str):
     return tuple(parts), tuple(calls), tuple(results)
 
 
-def normalize_anthropic_messages(body: Any, default_model: str | None = None) -> CanonicalChatRequest:
+def normalize_anthropic_messages(body: Any, default_model: str | None = None,
+                                 sampling_defaults: dict | None = None) -> CanonicalChatRequest:
     _require(isinstance(body, dict), "request body must be a JSON object")
     model = body.get("model") or default_model
     _require(isinstance(model, str) and model, "model is required", "model")
@@ -294,8 +325,9 @@ def normalize_anthropic_messages(body: Any, default_model: str | None = None) ->
         else:
             reasoning = ReasoningControl(False)
     sampling = SamplingMeta(
-        temperature=float(_as_number(body, "temperature", 1.0, 0.0, 1.0)),
-        top_p=float(_as_number(body, "top_p", 1.0)), top_k=min(20, int(_as_number(body, "top_k", 0, 0))),
+        temperature=float(_as_number(body, "temperature", min(1.0, _default(sampling_defaults, "temperature", 1.0)), 0.0, 1.0)),
+        top_p=float(_as_number(body, "top_p", _default(sampling_defaults, "top_p", 1.0))),
+        top_k=min(20, int(_as_number(body, "top_k", _default(sampling_defaults, "top_k", 0), 0))),
         max_tokens=max_tokens, stop=_stops(body.get("stop_sequences")))
     return CanonicalChatRequest(
         protocol="anthropic", model=model, messages=tuple(messages), sampling=sampling,

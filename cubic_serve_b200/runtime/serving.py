@@ -213,7 +213,11 @@ def run_http_server(backend, model_name: str, args) -> int:
     from ..api.server import CubicASGIApp
     from .logging import LogConfig, close_logging, serve_logging
     handles = serve_logging(LogConfig.from_file(getattr(args, "log_config", None)))
-    app = CubicASGIApp(backend, model_name, args.served_model_name, args.api_key)
+    from ..inputs.normalize import sampling_defaults_from_generation_config
+    defaults = sampling_defaults_from_generation_config(Path(args.model) / "generation_config.json")
+    if defaults:
+        log.info("sampling defaults from generation_config.json: %s", defaults)
+    app = CubicASGIApp(backend, model_name, args.served_model_name, args.api_key, sampling_defaults=defaults)
     StatusReporter(backend).start()
     config = uvicorn.Config(app, host=args.host, port=args.port, log_level="warning",
                             timeout_keep_alive=args.http_keep_alive_seconds, lifespan="on")

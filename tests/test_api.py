@@ -246,3 +246,25 @@ def test_real_backend_end_to_end_on_cpu():
     assert streamed == (j1["choices"][0]["message"]["content"] or "")        # greedy: same text both ways
     assert json.loads(b3)["usage"]["output_tokens"] == 4
     assert eng.pool.num_used == len(eng.prefix)
+
+
+def test_sampling_defaults_from_generation_config(tmp_path):
+    from cubic_serve_b200.inputs.normalize import (normalize_anthropic_messages, normalize_openai_chat_completions,
+                                                   sampling_defaults_from_generation_config)
+    f = tmp_path / "generation_config.json"
+    f.write_text(json.dumps({"temperature": 0.6, "top_p": 0.95, "top_k": 50, "do_sample": True, "eos_token_id": [1, 2]}))
+    d = sampling_defaults_from_generation_config(f)
+    assert d == {"temperature": 0.6, "top_p": 0.95, "top_k": 20}                     # top_k capped at the sampler's limit
+    body = {"model": "m", "messages": [{"role": "user", "content": "hi"}]}
+    r = normalize_openai_chat_completions(body, "m", d)
+    assert (r.sampling.temperature, r.sampling.top_p, r.sampling.top_k) == (0.6, 0.95, 20)
+    r = normalize_openai_chat_completions({**body, "temperature": 0.1, "top_k": 5}, "m", d)   # the request wins
+    assert (r.sampling.temperature, r.sampling.top_p, r.sampling.top_k) == (0.1, 0.95, 5)
+    assert normalize_openai_chat_completions(body, "m").sampling.temperature == 1.0
+    a = normalize_anthropic_messages({**body, "max_tokens": 8}, "m", d)
+    assert (a.sampling.temperature, a.sampling.top_k) == (0.6, 20)
+    f.write_text(json.dumps({"do_sample": False, "temperature": 5.0, "top_p": 0}))
+    assert sampling_defaults_from_generation_config(f) == {"temperature": 0.0}        # greedy; out-of-range values ignored
+    assert sampling_defaults_from_generation_config(tmp_path / "missing.json") == {}
+    app = CubicASGIApp(ScriptedBackend(), "model-x", sampling_defaults=d)
+    assert app.sampling_defaults["top_p"] == 0.95
