@@ -119,3 +119,23 @@ def test_quantize_then_audit_then_load(tmp_path, capsys):
         quantize_checkpoint(tmp_path / "q4", tmp_path / "again", "cubic", 4, 128)
     with pytest.raises(ValueError):
         quantize_checkpoint(src, tmp_path / "x", "no-such-format", 4, 128)
+
+
+def test_every_module_of_the_package_imports_without_a_gpu():
+    """Import smoke of the whole package (rarely used entry points included): no module may need CUDA, a network or
+    an optional dependency at import time."""
+    import importlib
+    import pkgutil
+
+    import cubic_serve_b200
+    failed = {}
+    # the kernel library sits in the package directory but is a plain shared object (ctypes), not a Python module
+    names = [m.name for m in pkgutil.walk_packages(cubic_serve_b200.__path__, "cubic_serve_b200.")
+             if not m.name.endswith(".libcubic_b200")]
+    assert len(names) > 60
+    for name in names:
+        try:
+            importlib.import_module(name)
+        except Exception as exc:  # noqa: BLE001 - collected and reported together
+            failed[name] = f"{type(exc).__name__}: {exc}"
+    assert not failed, failed
