@@ -237,10 +237,10 @@ class TokenChatBackend:
                 live = by_engine_id.get(o.request_id)
                 if live is None:
                     continue
-                self.stats["tokens"] += 1
+                self.stats["tokens"] += o.token_id is not None
                 evs = []
                 hit_stop_token = o.finished and o.finish_reason is FinishReason.STOP
-                if not hit_stop_token:
+                if not hit_stop_token and o.token_id is not None:
                     evs = live.pipeline.feed(o.token_id)
                 if live.pipeline.stopped and not o.finished:
                     self.engine.abort(o.request_id)

@@ -54,12 +54,14 @@ class PrefixCache:
             return []
         limit = None if max_tokens is None else max_tokens // BLOCK
         pages: list[int] = []
+        found = []
         for d in block_digests(tokens, extra, limit):
             page = self._map.get(d)
             if page is None:
                 break
-            self._map.move_to_end(d)
+            found.append(d)
             pages.append(page)
+        self._touch(found)
         self.lookups += 1
         self.lookup_tokens += len(tokens)
         if pages:
@@ -73,14 +75,27 @@ class PrefixCache:
         if not self.enabled:
             return 0
         added = 0
-        for d, page in zip(block_digests(tokens, extra, len(pages)), pages):
+        chain = block_digests(tokens, extra, len(pages))
+        for d, page in zip(chain, pages):
             if d in self._map:
-                self._map.move_to_end(d)
                 continue
             self.pool.retain([page])
             self._map[d] = page
             added += 1
+        self._touch(chain[:len(pages)])
         return added
+
+    def _touch(self, chain) -> None:
+        """Mark a chain of blocks as used, leaf first and root last: a block is only reachable through the blocks
+        before it, so within a chain the LEAF must be the first to go.  (Touching in chain order would make the
+        root the least recently used one; evicting it strands the rest of the chain, unreachable yet holding
+        pages.)"""
+        for d in reversed(chain):
+            self._map.move_to_end(d)
+
+    def evictable(self) -> int:
+        """Entries whose page only the cache holds (what ``evict`` could free right now)."""
+        return sum(1 for page in self._map.values() if self.pool.refcount(page) == 1)
 
     def evict(self, need_pages: int) -> int:
         """Drop least-recently-used entries whose page nobody else holds until ``need_pages`` were freed."""

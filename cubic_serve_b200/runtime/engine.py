@@ -110,6 +110,8 @@ class LLMEngine:
                 if plan is None:
                     return []
                 handle = None
+                if plan.finished and not plan.segments:
+                    return self._ended_by_scheduler(plan)
             if handle is None and not self._can_overlap(plan):
                 outputs = self._run(plan)
             else:
@@ -132,13 +134,28 @@ class LLMEngine:
         self.steps += 1
         return outputs
 
+    def _ended_by_scheduler(self, plan: BatchPlan) -> list[StepOutput]:
+        """Outputs of requests that the scheduler ended while planning (out of cache pages for good): no token, only
+        the finish event, so that the client's stream closes."""
+        outs = []
+        for r in plan.finished:
+            if self.requests.pop(r.request_id, None) is None:
+                continue
+            self._draft_states.pop(r.request_id, None)
+            self._budget_sig.pop(r.request_id, None)
+            if self.ngram is not None:
+                self.ngram.forget(r.request_id)
+            outs.append(StepOutput(r.request_id, None, True, r.finish_reason))
+        plan.finished = []
+        return outs
+
     def _can_overlap(self, plan: BatchPlan) -> bool:
         if not self.overlap_decode or not hasattr(self.executor, "launch") or getattr(self.executor, "speculative_depth", 0):
             return False
         if getattr(self, "_ahead_stale", False):
             self._ahead_stale = False
             return False
-        return bool(plan.segments) and not plan.copies and all(
+        return bool(plan.segments) and not plan.copies and not plan.finished and all(
             s.count == 1 and s.sample and s.request.sampling.matcher is None for s in plan.segments)
 
     def _segments(self, plan: BatchPlan, ahead: bool = False) -> list:
@@ -156,7 +173,7 @@ class LLMEngine:
                 sp.matcher.fill_bitmask(mask)
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
                                 sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF,
-                                r.draws + (1 if ahead else 0), r.arrival, mask,
+                                r.draws + (1 if ahead else 0), (r.arrival << 16) | (r.preemptions & 0xFFFF), mask,
                                 self._budget_init(r) if s.sample and end_id is not None else -2))
         return segs
 
@@ -188,7 +205,7 @@ class LLMEngine:
             self.spec_rounds = getattr(self, "spec_rounds", 0) + 1
         else:
             ids = self.executor.execute(segs) if segs else []
-        return self._complete(plan, ids)
+        return self._complete(plan, ids) + self._ended_by_scheduler(plan)
 
     def _complete(self, plan: BatchPlan, ids) -> list[StepOutput]:
         """Second half of a step: match ids to requests, commit, build the outputs.  Rows of a look-ahead step whose

@@ -114,6 +114,9 @@ class BatchPlan:
     segments: list[PlannedSegment]
     copies: list[tuple[int, int]] = field(default_factory=list)   # (src page, dst page) copy-on-write
     preempted: list[Request] = field(default_factory=list)
+    # requests the scheduler itself ended while planning: the pool cannot hold their next position even when
+    # they run alone (finish reason LENGTH); the engine reports them without a token
+    finished: list[Request] = field(default_factory=list)
 
     @property
     def num_tokens(self) -> int:
@@ -164,7 +167,11 @@ class ContinuousScheduler:
         if need > self.pool.num_pages - self.pool.reserved:
             raise AdmissionError("prompt can never fit in the KV cache")
         req.arrival = next(self._clock)
-        req.sampling.max_tokens = min(req.sampling.max_tokens, self.cfg.max_model_len - len(req.prompt))
+        # a request alone in the pool must be able to reach its last position: cap the output length by what the
+        # pool can ever hold (otherwise it would wait for pages that no eviction or preemption can free)
+        pool_tokens = (self.pool.num_pages - self.pool.reserved) * BLOCK - self.decode_lookahead
+        req.sampling.max_tokens = max(1, min(req.sampling.max_tokens, self.cfg.max_model_len - len(req.prompt),
+                                             pool_tokens - len(req.prompt)))
         self.waiting.append(req)
 
     def abort(self, request_id: str) -> Request | None:
@@ -212,16 +219,31 @@ class ContinuousScheduler:
             req.num_computed = len(pages) * BLOCK
             req.num_cached_prefix = req.num_computed
             req.num_published = len(pages)
+        if self.running:
+            # beside running requests, admit only what can hold its whole current context: a request that was
+            # preempted for lack of pages would otherwise come straight back, prefill and be preempted again
+            need = -(-(req.num_tokens + 1) // BLOCK) - len(req.pages)
+            if need > self.pool.num_free + self.prefix.evictable():
+                if pages:
+                    self.pool.release(pages)
+                    req.pages = []
+                    req.num_computed = req.num_cached_prefix = req.num_published = 0
+                return False
         req.slot = self._free_slots.pop()
         req.status = RequestStatus.RUNNING
         self.running.append(req)
         return True
 
     def _preempt_newest(self, keep: Request | None) -> Request | None:
-        victims = [r for r in self.running if r is not keep]
+        """Preempt the newest running request that arrived AFTER ``keep`` (any request if ``keep`` is None).  A
+        request never takes pages from an older one: two requests that do not fit together would otherwise preempt
+        each other in turn, each time recomputing a whole context for one token of progress."""
+        victims = [r for r in self.running if r is not keep and (keep is None or r.arrival > keep.arrival)]
         if not victims:
             return None
-        v = max(victims, key=lambda r: r.arrival)
+        return self._preempt(max(victims, key=lambda r: r.arrival))
+
+    def _preempt(self, v: Request) -> Request:
         self.running.remove(v)
         self.pool.release(v.pages)
         v.pages = []
@@ -271,7 +293,7 @@ class ContinuousScheduler:
                 if self._try_segment(r, n, plan, scheduled):
                     budget -= n
         plan.segments = [s for s in plan.segments if s.request.status is RequestStatus.RUNNING and s.request.slot >= 0]
-        return plan if plan.segments or plan.preempted else None
+        return plan if plan.segments or plan.preempted or plan.finished else None
 
     def _try_segment(self, r: Request, n: int, plan: BatchPlan, scheduled: set) -> bool:
         if r.status is not RequestStatus.RUNNING:
@@ -285,6 +307,13 @@ class ContinuousScheduler:
             except OutOfPages:
                 victim = self._preempt_newest(keep=r)
                 if victim is None:
+                    if len(self.running) > 1:
+                        # r is the newest: it gives way itself and waits until older requests have finished
+                        plan.preempted.append(self._preempt(r))
+                    else:
+                        # alone and still out of pages: nothing can ever free any, so the request ends here
+                        self._retire(r, FinishReason.LENGTH)
+                        plan.finished.append(r)
                     return False
                 plan.preempted.append(victim)
                 plan.segments = [s for s in plan.segments if s.request is not victim]

@@ -47,3 +47,50 @@ def test_prefill_blocks_and_incremental_page_rows():
     bb.invalidate_page_rows([2])
     bb.fill([Segment(2, [1], 1, [4], True, uid=6)])
     assert h["page_table"][2, 0] == 4
+
+
+def test_page_rows_follow_a_request_through_preemption_and_readmission():
+    """Scheduler + batch builder under tight memory: after every planned step the staged page-table row of each
+    scheduled request equals the request's pages, also when a preempted request gets its old slot back with other
+    pages (the row's identity changes with every admission)."""
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+
+    class Ex:
+        vocab_size = 97
+
+        def __init__(self):
+            self.bb = BatchBuilder(max_rows=6, max_tokens=128, max_model_len=128, group=4, kv_heads=2, device="cpu")
+            self.invalidate_page_rows = self.bb.invalidate_page_rows
+            self.checked = 0
+
+        def copy_pages(self, pairs):
+            pass
+
+        def execute(self, segs):
+            self.bb.fill(segs)
+            table = self.bb.stage.h["page_table"]
+            for s in segs:
+                assert table[s.request_slot, :len(s.pages)].tolist() == list(s.pages), (s.request_slot, s.uid)
+                self.checked += 1
+            return np.asarray([(int(s.token_ids[-1]) * 31 + s.start) % 97 for s in segs if s.sample], dtype=np.int32)
+
+    ex = Ex()
+    eng = LLMEngine(ex, num_pages=14, scheduler_config=SchedulerConfig(
+        max_running_requests=6, max_model_len=96, max_batched_tokens=96, prefill_chunk_tokens=48, enable_prefix_cache=False))
+    reqs = [eng.requests[eng.add_request([(7 * r + i) % 97 for i in range(30 + r)],
+                                         SamplingParams(max_tokens=30, ignore_eos=True), f"p{r}")] for r in range(6)]
+    for _ in range(3000):
+        if not eng.has_unfinished:
+            break
+        eng.step()
+    assert not eng.has_unfinished and ex.checked > 100
+    assert sum(r.preemptions for r in reqs) > 0
+
+
+def test_same_slot_same_arrival_new_admission_rewrites_the_row():
+    bb = BatchBuilder(max_rows=2, max_tokens=64, max_model_len=128, group=4, kv_heads=2, device="cpu")
+    bb.fill([Segment(1, [5], 48, [7, 8, 9, 7], True, uid=(3 << 16) | 0)])
+    # the same request (arrival 3) re-admitted after a preemption: same slot, same page count, other pages
+    bb.fill([Segment(1, [5], 48, [4, 5, 6, 7], True, uid=(3 << 16) | 1)])
+    assert bb.stage.h["page_table"][1, :4].tolist() == [4, 5, 6, 7]

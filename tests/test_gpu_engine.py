@@ -8,7 +8,7 @@ from cubic_serve_b200.models.config import ModelConfig, QuantSpec
 pytestmark = pytest.mark.gpu
 
 
-def _engine(overlap, eos=None):
+def _engine(overlap, eos=None, pool_pages=256):
     from cubic_serve_b200.executor.gpu_executor import GpuExecutor
     from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
     from cubic_serve_b200.runtime.engine import LLMEngine
@@ -19,7 +19,7 @@ def _engine(overlap, eos=None):
     runner = DecoderRunner(cfg, random_decoder_weights(cfg, dev, seed=0, std=0.05), num_pages=256, max_tokens=512)
     ex = GpuExecutor(runner, max_rows=16, max_prefill_tokens=512, max_model_len=256)
     ex.capture_decode_graphs()
-    eng = LLMEngine(ex, 256, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
+    eng = LLMEngine(ex, pool_pages, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
                                              enable_prefix_cache=False), eos_token_id=eos)
     eng.overlap_decode = overlap
     return eng, ex, runner
@@ -49,6 +49,26 @@ def test_overlapped_decode_matches_stepwise_on_device():
     # sampling with temperature: the draw counters of look-ahead rows count the pending commit
     sp2 = SamplingParams(max_tokens=16, temperature=0.8, top_k=20, seed=7, ignore_eos=True)
     assert _engine(True)[0].generate(prompts[:4], sp2) == _engine(False)[0].generate(prompts[:4], sp2)
+
+
+def test_preempted_requests_read_their_own_pages_after_readmission():
+    """A pool too small for all requests: some are preempted, re-admitted (often into their old slot, with other
+    pages) and must produce the tokens of an unpreempted run.  A stale page-table row would make attention read
+    pages that now belong to other requests."""
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (40, 37, 45, 33, 50, 41)]
+    sp = SamplingParams(max_tokens=40, ignore_eos=True)
+    want = _engine(False)[0].generate(prompts, sp)
+    for overlap in (False, True):
+        eng, _, runner = _engine(overlap, pool_pages=20)          # 19 usable pages; six requests end at 5-6 pages each
+        ids = [eng.add_request(p, SamplingParams(**vars(sp))) for p in prompts]
+        reqs = [eng.requests[i] for i in ids]
+        while eng.has_unfinished:
+            eng.step()
+        runner.ws.check_status()
+        assert sum(r.preemptions for r in reqs) > 0
+        assert [r.output for r in reqs] == want
 
 
 def test_thinking_budget_state_machine_and_engine():
@@ -104,7 +124,7 @@ def test_thinking_budget_state_machine_and_engine():
         runner.enable_reasoning_budget(2047, [2046, 2047])
         ex = GpuExecutor(runner, max_rows=16, max_prefill_tokens=512, max_model_len=256)
         ex.capture_decode_graphs()
-        eng = LLMEngine(ex, 256, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
+        eng = LLMEngine(ex, pool_pages, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
                                                  enable_prefix_cache=False))
         prompts = [np.random.default_rng(i).integers(0, 2000, 20 + i).tolist() for i in range(3)]
         ids = [eng.add_request(p, SamplingParams(max_tokens=14, ignore_eos=True,

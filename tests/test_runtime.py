@@ -370,3 +370,25 @@ def test_delayed_constraint_starts_after_the_reasoning_block():
         assert m.accept(ch)
     assert allowed(m) == {eos} and m.accept(eos) and m.finished
     __import__("pytest").raises(ValueError, DelayedMatcher, None, [])
+
+
+def test_prefix_cache_evicts_a_chain_from_its_leaf():
+    """After a match or a publish the blocks of a chain are ordered leaf (oldest) to root (newest): eviction drops
+    the leaf first and never strands later blocks behind a missing first block."""
+    from cubic_serve_b200.runtime.cache.pool import PagePool
+    from cubic_serve_b200.runtime.cache.prefix import PrefixCache
+    pool = PagePool(16)
+    cache = PrefixCache(pool)
+    toks = list(range(64))
+    pages = pool.alloc(4)
+    cache.publish(toks, pages)
+    pool.release(pages)                                  # only the cache holds them now
+    assert cache.evictable() == 4
+    assert cache.evict(1) == 1
+    got = cache.match(toks)
+    assert got == pages[:3]                              # the first three blocks are still reachable
+    pool.release(got)
+    assert cache.evict(2) == 2
+    got = cache.match(toks)
+    assert got == pages[:1]
+    pool.release(got)

@@ -108,3 +108,63 @@ def test_preemption_under_tight_memory_recomputes_the_same_tokens():
             want.append(last)
             pos += 1
         assert out[f"p{i}"] == want
+
+
+def test_a_lone_request_that_outgrows_the_pool_ends_with_length_instead_of_waiting_forever():
+    """A 4-page pool, a 20-token prompt, 200 requested tokens: the request can never hold its last position.  It is
+    cut to what the pool can hold and ends with finish reason LENGTH; the engine does not spin."""
+    from cubic_serve_b200.runtime.scheduler import FinishReason
+    eng = LLMEngine(CountingExecutor(), num_pages=4, scheduler_config=SchedulerConfig(
+        max_running_requests=2, max_model_len=4096, max_batched_tokens=64, enable_prefix_cache=False))
+    rid = eng.add_request(list(range(20)), SamplingParams(max_tokens=200, ignore_eos=True), "lone")
+    req = eng.requests[rid]
+    outs = []
+    for _ in range(400):
+        if not eng.has_unfinished:
+            break
+        outs += eng.step()
+    assert not eng.has_unfinished and eng.pool.num_used == 0
+    assert outs[-1].finished and outs[-1].finish_reason is FinishReason.LENGTH
+    assert 0 < len(req.output) <= (4 - eng.pool.reserved) * 16 - 20
+
+
+def test_scheduler_ends_a_running_request_that_cannot_grow_even_alone():
+    """The safety net behind the admission cap: pages taken away from under a lone request (here: by shrinking the
+    free list by hand) must end it with LENGTH and a token-less finish event, not leave it RUNNING forever."""
+    from cubic_serve_b200.runtime.scheduler import FinishReason
+    eng = LLMEngine(CountingExecutor(), num_pages=8, scheduler_config=SchedulerConfig(
+        max_running_requests=2, max_model_len=4096, max_batched_tokens=64, enable_prefix_cache=False))
+    eng.add_request(list(range(20)), SamplingParams(max_tokens=60, ignore_eos=True), "r")
+    eng.step()
+    stolen = eng.pool.alloc(eng.pool.num_free)          # somebody else holds every free page from now on
+    outs = []
+    for _ in range(100):
+        if not eng.has_unfinished:
+            break
+        outs += eng.step()
+    assert not eng.has_unfinished
+    assert outs[-1].finished and outs[-1].token_id is None and outs[-1].finish_reason is FinishReason.LENGTH
+    eng.pool.release(stolen)
+    assert eng.pool.num_used == 0
+
+
+def test_requests_that_do_not_fit_together_do_not_preempt_each_other_in_turn():
+    """Three requests whose contexts cannot be resident together: the older ones are never preempted by a newer one,
+    and nobody is preempted more than a couple of times (each preemption is a full recompute)."""
+    ex = CountingExecutor()
+    eng = LLMEngine(ex, num_pages=9, scheduler_config=SchedulerConfig(
+        max_running_requests=3, max_model_len=128, max_batched_tokens=128, prefill_chunk_tokens=64, enable_prefix_cache=False))
+    reqs = []
+    for i in range(3):
+        rid = eng.add_request([(5 * i + j) % 97 for j in range(40)], SamplingParams(max_tokens=40, ignore_eos=True), f"q{i}")
+        reqs.append(eng.requests[rid])
+    out = {}
+    for _ in range(3000):
+        if not eng.has_unfinished:
+            break
+        for o in eng.step():
+            out.setdefault(o.request_id, []).append(o.token_id)
+    assert not eng.has_unfinished and eng.pool.num_used == 0
+    assert reqs[0].preemptions == 0
+    assert all(r.preemptions <= 2 for r in reqs), [r.preemptions for r in reqs]
+    assert all(len(out[f"q{i}"]) == 40 for i in range(3))
