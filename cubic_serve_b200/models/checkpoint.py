@@ -174,6 +174,12 @@ def admit_checkpoint(path: str | Path) -> AdmittedCheckpoint:
             raise CheckpointError(f"no payload tensors for {module}")
         payloads[module] = found
         claimed.update(found.values())
+        if "weight_g_idx" in found:
+            # activation-order checkpoints permute the columns' scale groups; the loaders assume group = column // G
+            g_idx = store.get(found["weight_g_idx"]).to(torch.int64).flatten()
+            g = cfg.quant.group_size if cfg.quant.group_size > 0 else max(1, g_idx.numel())
+            if not torch.equal(g_idx, torch.arange(g_idx.numel()) // g):
+                raise CheckpointError(f"{module}: act-order (non-trivial weight_g_idx) checkpoints are not supported")
     plain_map = {}
     for name in plain:
         if name not in store:
@@ -206,14 +212,19 @@ def inspect_checkpoint(path: str | Path) -> dict:
 
 
 # ------------------------------------------------------------ rank-local load
-def _slice_rows(payload: dict, method: str, lo: int, hi: int, n: int) -> dict:
+def _slice_rows(payload: dict, method: str, lo: int, hi: int, n: int, bits: int = 4) -> dict:
     """Output-dimension slice of a payload (all formats keep N as the leading axis except AWQ)."""
     out = {}
     for k, t in payload.items():
         if method == "awq":
             out[k] = t[:, lo // 8:hi // 8] if k in ("qweight", "qzeros") else t[:, lo:hi]
         elif k == "weight_zero_point":
-            out[k] = t          # packed along N: handled after decode
+            # zero points are packed ALONG N (``[words(N), groups]``): unpack all N, keep rows [lo, hi), pack again,
+            # so that the decoder of the slice finds row lo's zero point first
+            zp = formats.int_unpack(t.t().contiguous(), bits, n)[:, lo:hi]
+            out[k] = formats.int_pack(zp, bits).t().contiguous()
+        elif k in ("weight_shape", "weight_g_idx"):
+            out[k] = t
         elif t.dim() >= 1 and t.shape[0] == n:
             out[k] = t[lo:hi]
         elif k == "weight_scale_inv":
@@ -308,7 +319,7 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
         return cache[module]
 
     def rows(module: str, lo: int, hi: int, n: int):
-        return _slice_rows(payload(module), method, lo, hi, n), (hi - lo, ck_shapes[module][1])
+        return _slice_rows(payload(module), method, lo, hi, n, q.bits), (hi - lo, ck_shapes[module][1])
 
     ck_shapes, _ = logical_inventory(cfg)
     layers = []

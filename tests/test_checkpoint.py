@@ -179,3 +179,45 @@ def test_mtp_head_from_checkpoint(tmp_path):
     plain = admit_checkpoint(C.write_random_checkpoint(tmp_path / "plain", BASE, seed=5))
     with pytest.raises(C.CheckpointError, match="no MTP head"):
         load_mtp_weights(plain, "cpu")
+
+
+def test_asymmetric_int_checkpoint_slices_zero_points_with_the_rows(tmp_path):
+    """Zero points are packed along N.  A tensor-parallel rank > 0 (or the per-head row gathering of the hybrid
+    family) decodes a row slice [lo, hi) with lo > 0 and must find the zero points of THOSE rows."""
+    from safetensors.torch import load_file, save_file
+    from cubic_serve_b200.quantization import formats
+    cfg = replace(BASE, quant=QuantSpec("int", 4, 128))
+    path = C.write_random_checkpoint(tmp_path / "int_asym", cfg, seed=3)
+    t = load_file(str(path / "model.safetensors"))
+    g = torch.Generator().manual_seed(5)
+    dense = {}
+    for name in [n for n in t if n.endswith(".weight_packed")]:
+        module = name[:-len(".weight_packed")]
+        n, k = (int(v) for v in t[f"{module}.weight_shape"])
+        w = torch.randn(n, k, generator=g) * 0.02 + 0.01 * torch.randn(n, 1, generator=g)     # rows with an offset
+        for suffix, v in formats.int_quantize(w, 4, 128, symmetric=False).items():
+            t[f"{module}.{suffix}"] = v.contiguous()
+        dense[module] = formats.int_dense({s: t[f"{module}.{s}"] for s in ("weight_packed", "weight_scale", "weight_zero_point")},
+                                          4, 128, (n, k))
+    save_file(t, str(path / "model.safetensors"))
+    ck = C.admit_checkpoint(path)
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()
+    # _slice_rows of the upper half decodes to the upper half of the full decode
+    mod = "model.layers.0.self_attn.q_proj"
+    sl = C._slice_rows(ck.payload(mod), "int", 256, 512, 512, 4)
+    assert torch.equal(formats.int_dense(sl, 4, 128, (256, 256)), dense[mod][256:])
+    w1 = C.load_decoder_weights(ck, "cpu", tp_rank=1, tp_size=2)
+    q, k, v = (dense[f"model.layers.0.self_attn.{p}_proj"] for p in "qkv")
+    assert rel(wq_pack.unpack_to_dense(w1.layers[0].qkv), torch.cat([q[256:], k[128:], v[128:]])) < 6e-3
+    gu = wq_pack.unpack_to_dense(w1.layers[1].gate_up)
+    gate, up = dense["model.layers.1.mlp.gate_proj"][256:], dense["model.layers.1.mlp.up_proj"][256:]
+    assert rel(gu.sort(0).values, torch.cat([gate, up]).sort(0).values) < 6e-3        # rows are interleaved at load
+    assert rel(wq_pack.unpack_to_dense(w1.layers[1].down), dense["model.layers.1.mlp.down_proj"][:, 256:]) < 6e-3
+    # an act-order checkpoint (non-trivial g_idx) is refused at admission, a trivial g_idx is admitted
+    t[f"{mod}.weight_g_idx"] = (torch.arange(256) // 128).to(torch.int32)
+    save_file(t, str(path / "model.safetensors"))
+    C.admit_checkpoint(path)
+    t[f"{mod}.weight_g_idx"] = (torch.arange(256).flip(0) // 128).to(torch.int32)
+    save_file(t, str(path / "model.safetensors"))
+    with pytest.raises(C.CheckpointError, match="act-order"):
+        C.admit_checkpoint(path)
