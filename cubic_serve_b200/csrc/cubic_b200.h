@@ -19,7 +19,9 @@ extern "C" {
 //     inputs and outputs but no caching allocator to ask for temporaries.
 //
 // It computes  y[M, N] = alpha * x[M, K] * W[N, K]^T (+ residual)  with the same
-// kernel as cb_wq_gemm and the same argument meaning (fmt: 0 cubic4, 1 affine4,
+// kernel as cb_wq_gemm in its workspace form (the K splits of an output tile meet
+// through fp32 partial sums in global memory; the last split to arrive adds them
+// in split order) and the same argument meaning (fmt: 0 cubic4, 1 affine4,
 // 2 nvfp4, 3 bf16 weights; x and y are bf16 row-major; codes / meta are the packed
 // weight produced by ops/wq_pack.py).  The split-K partial sums and the per-tile
 // arrival counters live in a scratch array that is part of the library image

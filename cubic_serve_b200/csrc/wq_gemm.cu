@@ -31,6 +31,7 @@
 //                   of the k-block; w = (code - 8) * scale + that; one block per k-block
 //          NVFP4  : word h = bf16x2(block scale of columns 32h..32h+15, ..+16..31)
 #include "wq_gemm_common.cuh"
+#include <atomic>
 
 namespace cb {
 
@@ -86,8 +87,8 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   // timeline rows 0..2, slots 6/7 hold kernel-level stamps: entry, set-up done, accumulator complete,
   // epilogue stores issued, split-K reduction done
-  unsigned long long* trace = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;
-  if (trace && threadIdx.x == 64) trace[6] = clock64();
+  CB_TRACE_ONLY(unsigned long long* trace = (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.trace : nullptr;)
+  CB_STAMP(threadIdx.x == 64, 6);
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&ctl->full[s]), 1);
@@ -108,7 +109,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
-  if (trace && threadIdx.x == 64) trace[7] = clock64();
+  CB_STAMP(threadIdx.x == 64, 7);
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -150,10 +151,10 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         uint32_t ph = 1;                      // second pass over the ring: wait for the first release
         for (int i = pre; i < iters; ++i) {
           if (!mbar_wait_park(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag)) break;
-          if (trace) trace[i * 8 + 0] = clock64();
+          CB_STAMP(true, i * 8 + 0);
           load_weights(i, s);
           load_x(i, s);
-          if (trace) trace[i * 8 + 1] = clock64();
+          CB_STAMP(true, i * 8 + 1);
           if (++s == S) { s = 0; ph ^= 1u; }
         }
       }
@@ -179,7 +180,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                : mbar_wait_park(smem_u32(&ctl->ready[s]), ph, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (trace && leader) trace[i * 8 + 4] = clock64();
+        CB_STAMP(leader, i * 8 + 4);
         tc_fence_after();
         const uint32_t st = smem_base + static_cast<uint32_t>(s) * stage_bytes;
         const uint64_t bdesc = desc_hi | static_cast<uint64_t>((st & 0x3FFFFu) >> 4);
@@ -193,7 +194,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tc_commit(smem_u32(&ctl->empty[s]));
         }
         accumulate = 1;
-        if (trace && leader) trace[i * 8 + 5] = clock64();
+        CB_STAMP(leader, i * 8 + 5);
         if (++s == S) { s = 0; ph ^= 1u; }
       }
       if (leader) tc_commit(smem_u32(&ctl->acc_full));
@@ -216,7 +217,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t ph = static_cast<uint32_t>(grp / S) & 1u;
       for (int i = grp; i < iters; i += 4) {
         if (!mbar_wait_park(smem_u32(&ctl->full[s]), ph, abort_flag)) break;
-        if (trace && dq == 0) trace[i * 8 + 2] = clock64();
+        CB_STAMP(dq == 0, i * 8 + 2);
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint8_t* pk = st + x_bytes + kATileBytes;
         const uint4 w0 = *reinterpret_cast<const uint4*>(pk + code_off);
@@ -261,7 +262,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&ctl->ready[s]));
-        if (trace && dq == 0) trace[i * 8 + 3] = clock64();
+        CB_STAMP(dq == 0, i * 8 + 3);
         s += 4;
         while (s >= S) { s -= S; ph ^= 1u; }
       }
@@ -269,7 +270,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // epilogue: TMEM lane = output feature, column = batch row
     const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_full), 0, abort_flag));
     tc_fence_after();
-    if (trace && dq == 0) trace[8 + 6] = clock64();
+    CB_STAMP(dq == 0, 8 + 6);
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     const int pair = (warp - 2) >> 2;        // four warps share a quadrant; they interleave 16-column chunks
     const int chunks = p.mb >> 4;
@@ -372,7 +373,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
       }
     }
-    if (trace && dq == 0) trace[8 + 7] = clock64();
+    CB_STAMP(dq == 0, 8 + 7);
     if (p.splits > 1 && !p.cluster_splitk) {
       // last-arriving split sums all partials in split order (deterministic)
       __threadfence();
@@ -536,7 +537,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
   tc_fence_before();
   __syncthreads();
-  if (trace && threadIdx.x == 64) trace[16 + 6] = clock64();
+  CB_STAMP(threadIdx.x == 64, 16 + 6);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
@@ -558,8 +559,11 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
 // share a GPC, so this is less than SMs / size when GPCs do not hold a multiple of `size` usable SMs.
 template <int FMT>
 static int resident_clusters(int size) {
-  static int cached[9] = {0};
-  if (size < 1 || size > 8) return 0;
+  // per device: a function attribute set with one device current does not carry over to another device
+  static int cached_dev[64][9] = {};
+  int dev = 0;
+  if (size < 1 || size > 8 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  int* cached = cached_dev[dev];
   if (cached[size] == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, static_cast<unsigned>(size), 1);
@@ -584,11 +588,13 @@ static int resident_clusters(int size) {
 template <int FMT>
 static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams p, dim3 grid, size_t smem,
                       cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};     // per device, like the attribute itself
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -18;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(wq_gemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured[dev] = true;
   }
   if (p.cluster_splitk) {
     // the K splits of a tile (grid.y) as one cluster; only if every cluster of the launch can be resident at once
@@ -616,20 +622,35 @@ static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams
 
 }  // namespace cb
 
-// set by cb_wq_gemm_grouped around its call of the common launcher (host-side, single-threaded use per process)
-static struct { const int* tiles; size_t code_stride, meta_stride; int max_items, num_experts; } g_grouped = {};
-static int g_mb_hint = 0;
+// Per-launch options of the common launcher.  Everything that steers ONE launch travels in this struct (not in
+// process-wide variables), so launches made concurrently from several host threads cannot see each other's choices.
+struct WqLaunchOpts {
+  const int* tiles = nullptr;          // grouped (expert) launch: device work list, see WqGemmParams::group_tiles
+  size_t code_stride = 0, meta_stride = 0;
+  int max_items = 0, num_experts = 0;
+  int mb_hint = 0;                     // grouped launch: batch rows per work item
+  int swiglu = 0;                      // fused SwiGLU epilogue (gate / up rows interleaved)
+  int cluster_splitk = -1;             // -1: the process default; 0 / 1: workspace / cluster reduction for this launch
+  bool stream_k = false;
+  int min_units = 0;
+  long long workspace_bytes = 0;
+};
+
+#ifdef CB_KERNEL_TRACE
 static unsigned long long* g_trace_buffer = nullptr;
 static int g_stage_override = 0;
+#endif
 
 extern "C" {
 
-// Debug hooks: a device buffer of [k-blocks][8] 64-bit words receives the pipeline timeline of CTA (0,0,0)
+#ifdef CB_KERNEL_TRACE
+// Development builds only: a device buffer of [k-blocks][8] 64-bit words receives the pipeline timeline of CTA (0,0,0)
 // of every following launch (null switches it off); a non-zero stage count overrides the automatic choice.
 void cb_wq_gemm_debug(void* trace_buffer, int stages) {
   g_trace_buffer = static_cast<unsigned long long*>(trace_buffer);
   g_stage_override = stages;
 }
+#endif
 
 // Bytes of split-K workspace / counters a launch with these sizes needs.
 long long cb_wq_gemm_workspace_bytes(int M, int N, int splits) {
@@ -678,41 +699,57 @@ int cb_wq_gemm_sk(int fmt, const void* x, int ldx, const void* codes, const void
 
 // 1 (default): the K splits of a tile of the per-tile kernel form a cluster and reduce through distributed shared
 // memory; 0: fp32 partial tiles in the workspace, summed by the last split to arrive.
-static int g_cluster_splitk = 1;
+static std::atomic<int> g_cluster_splitk{1};
 
 // Persistent kernel on CTA pairs (cta_group::2): 0 never; 1 (default) eligible launches with more than 256 batch
 // rows (measured: 5-20 % faster than one CTA per SM from 512 rows up, 2-8 % slower at exactly 256, where the decode
 // warps and not the activation traffic set the pace); 2 every eligible launch.
-static int g_pair_mode = 1;
-
-// Epilogue of the NEXT launch made by this thread: 1 = fused SwiGLU (the weight rows are gate / up interleaved, the
-// output has N / 2 columns).  Set and cleared by the *_act entry points only.
-static thread_local int g_epilogue_swiglu = 0;
+static std::atomic<int> g_pair_mode{1};
 
 static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                             const void* residual, float alpha, int M, int N, int K, int group_k, int splits,
                             void* workspace, void* counters, void* status, void* stream, const CbTpLink* link,
-                            bool stream_k, int min_units, long long workspace_bytes);
+                            const WqLaunchOpts& o);
 
 int cb_wq_gemm_tp(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                const void* residual, float alpha, int M, int N, int K, int group_k, int splits, void* workspace,
                void* counters, void* status, void* stream, const CbTpLink* link) {
   return wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, residual, alpha, M, N, K, group_k, splits, workspace,
-                          counters, status, stream, link, false, 0, 0);
+                          counters, status, stream, link, WqLaunchOpts{});
+}
+
+// Same as cb_wq_gemm, but the K splits always meet through `workspace` / `counters` (never through a cluster's
+// distributed shared memory), whatever the process default says.
+int cb_wq_gemm_workspace_splitk(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                                const void* residual, float alpha, int M, int N, int K, int group_k, int splits,
+                                void* workspace, void* counters, void* status, void* stream) {
+  WqLaunchOpts o;
+  o.cluster_splitk = 0;
+  return wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, residual, alpha, M, N, K, group_k, splits, workspace,
+                          counters, status, stream, nullptr, o);
 }
 
 int cb_wq_gemm_sk(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                   const void* residual, float alpha, int M, int N, int K, int group_k, int min_units, void* workspace,
                   long long workspace_bytes, void* counters, void* status, void* stream, const CbTpLink* link) {
+  WqLaunchOpts o;
+  o.stream_k = true;
+  o.min_units = min_units;
+  o.workspace_bytes = workspace_bytes;
   return wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, residual, alpha, M, N, K, group_k, 1, workspace, counters,
-                          status, stream, link, true, min_units, workspace_bytes);
+                          status, stream, link, o);
 }
 
 static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                             const void* residual, float alpha, int M, int N, int K, int group_k, int splits,
                             void* workspace, void* counters, void* status, void* stream, const CbTpLink* link,
-                            bool stream_k, int min_units, long long workspace_bytes) {
+                            const WqLaunchOpts& o) {
   using namespace cb;
+  const bool stream_k = o.stream_k;
+  const int min_units = o.min_units;
+  const long long workspace_bytes = o.workspace_bytes;
+  const int pair_mode = g_pair_mode.load(std::memory_order_relaxed);
+  const int cluster_default = o.cluster_splitk >= 0 ? o.cluster_splitk : g_cluster_splitk.load(std::memory_order_relaxed);
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % 8) != 0) return -10;
   if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4) return -11;
   if (fmt == kFmtCubic4 && (group_k % kBlockK) != 0) return -12;
@@ -725,7 +762,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.counters = static_cast<uint32_t*>(counters);
   p.status = static_cast<uint32_t*>(status);
   p.M = M; p.N = N; p.K = K; p.ldy = ldy; p.alpha = alpha;
-  p.swiglu = g_epilogue_swiglu;
+  p.swiglu = o.swiglu;
   if (p.swiglu && (residual || (link && (link->mode & kTpScatterPush)))) return -51;
   p.tp.mode = kTpNone;
   if (link && link->mode != kTpNone) {
@@ -741,13 +778,13 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
     if ((link->mode & kTpScatterPush) && static_cast<long long>(link->rows_per_rank) * link->size < M) return -31;
   }
   p.mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
-  if (g_grouped.tiles && g_mb_hint > 0) p.mb = g_mb_hint;
+  if (o.tiles && o.mb_hint > 0) p.mb = o.mb_hint;
   p.k_blocks = K / kBlockK;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
   // K splits of the per-tile kernel meet in a thread-block cluster (distributed shared memory) unless the tile's rows
   // are pushed to other ranks (their arrival counters are raised once per tile by the last split)
-  p.cluster_splitk = (splits > 1 && splits <= 8 && g_cluster_splitk && !stream_k && !g_grouped.tiles &&
+  p.cluster_splitk = (splits > 1 && splits <= 8 && cluster_default && !stream_k && !o.tiles &&
                       !(p.tp.mode & kTpScatterPush)) ? 1 : 0;
   if (splits > 1 && !p.cluster_splitk && (!workspace || !counters)) return -13;
   p.splits = splits;
@@ -760,19 +797,21 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SmemCtl);
   int stages = static_cast<int>(budget / stage);
   if (stages > 8) stages = 8;
+#ifdef CB_KERNEL_TRACE
   if (g_stage_override > 0 && g_stage_override < stages) stages = g_stage_override;
-  if (stages < 2) return -14;
   p.trace = g_trace_buffer;
+#endif
+  if (stages < 2) return -14;
   p.stages = stages;
   const size_t smem = stages * stage + sizeof(SmemCtl) + 1024;
 
-  if (g_grouped.tiles) p.group_tiles = g_grouped.tiles;
-  p.pair = (stream_k && (g_pair_mode == 2 || (g_pair_mode == 1 && M > 256)) && streamk_pair_eligible(p, N)) ? 1 : 0;
+  if (o.tiles) p.group_tiles = o.tiles;
+  p.pair = (stream_k && (pair_mode == 2 || (pair_mode == 1 && M > 256)) && streamk_pair_eligible(p, N)) ? 1 : 0;
   CUtensorMap tx, tw;
   // with CTA pairs each CTA of a pair fetches half of the rows of an activation tile
   if (make_tmap_bf16(&tx, x, M, K, ldx, p.pair ? p.mb / 2 : p.mb) != 0) return -20;
   if (fmt == kFmtBf16) {
-    const uint64_t w_rows = static_cast<uint64_t>(N) * (g_grouped.tiles ? g_grouped.num_experts : 1);
+    const uint64_t w_rows = static_cast<uint64_t>(N) * (o.tiles ? o.num_experts : 1);
     if (make_tmap_bf16(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
   } else {
     tw = tx;
@@ -783,20 +822,20 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -18;
     if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -18;
-    if (g_grouped.tiles) {
-      p.group_tiles = g_grouped.tiles;
-      p.group_code_stride = g_grouped.code_stride; p.group_meta_stride = g_grouped.meta_stride;
+    if (o.tiles) {
+      p.group_tiles = o.tiles;
+      p.group_code_stride = o.code_stride; p.group_meta_stride = o.meta_stride;
     }
     return launch_streamk(fmt, tx, tw, p, static_cast<size_t>(workspace_bytes < 0 ? 0 : workspace_bytes), sms[dev],
-                          min_units, st, g_grouped.tiles ? g_grouped.max_items : 0);
+                          min_units, st, o.tiles ? o.max_items : 0);
   }
   const int n_tiles = (N + kTileN - 1) / kTileN;
   const int m_tiles = (M + p.mb - 1) / p.mb;
   dim3 grid(n_tiles, splits, m_tiles);
-  if (g_grouped.tiles) {
-    p.group_tiles = g_grouped.tiles;
-    p.group_code_stride = g_grouped.code_stride; p.group_meta_stride = g_grouped.meta_stride;
-    grid = dim3(n_tiles, g_grouped.max_items, 1);
+  if (o.tiles) {
+    p.group_tiles = o.tiles;
+    p.group_code_stride = o.code_stride; p.group_meta_stride = o.meta_stride;
+    grid = dim3(n_tiles, o.max_items, 1);
   }
   switch (fmt) {
     case kFmtCubic4: return launch_fmt<kFmtCubic4>(tx, tw, p, grid, smem, st);
@@ -806,7 +845,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   }
 }
 
-static int g_grouped_persistent = 1;
+static std::atomic<int> g_grouped_persistent{1};
 
 // Gate/up projection with the activation fused: y[M, N / 2] = silu(x Wg^T) * (x Wu^T), W in the interleaved row
 // order (16 gate rows, 16 up rows, ...).  `stream_k` picks the persistent kernel; `splits` applies to the per-tile one.
@@ -815,26 +854,28 @@ int cb_wq_gemm_act(int fmt, const void* x, int ldx, const void* codes, const voi
                    int M, int N, int K, int group_k, int stream_k, int splits, int min_units, void* workspace,
                    long long workspace_bytes, void* counters, void* status, void* stream, const CbTpLink* link) {
   if ((N % 32) != 0 || ldy < N / 2) return -50;
-  g_epilogue_swiglu = 1;
-  const int rc = wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, M, N, K, group_k, stream_k ? 1 : splits,
-                                  workspace, counters, status, stream, link, stream_k != 0, min_units, workspace_bytes);
-  g_epilogue_swiglu = 0;
-  return rc;
+  WqLaunchOpts o;
+  o.swiglu = 1;
+  o.stream_k = stream_k != 0;
+  o.min_units = min_units;
+  o.workspace_bytes = workspace_bytes;
+  return wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, M, N, K, group_k, stream_k ? 1 : splits,
+                          workspace, counters, status, stream, link, o);
 }
 
 // 1 (default): grouped GEMMs run on the persistent kernel; 0: one CTA per (work item, weight tile).
-void cb_wq_gemm_grouped_mode(int persistent) { g_grouped_persistent = persistent; }
+void cb_wq_gemm_grouped_mode(int persistent) { g_grouped_persistent.store(persistent); }
 
 // 0: one CTA per SM works alone; 1 (default): CTA pairs for eligible launches of more than 256 batch rows; 2: for
 // every eligible launch.
-void cb_wq_gemm_pair_mode(int pairs) { g_pair_mode = pairs; }
+void cb_wq_gemm_pair_mode(int pairs) { g_pair_mode.store(pairs); }
 
 // 1 (default): split-K of the per-tile kernel through a cluster's distributed shared memory; 0: through the workspace.
-void cb_wq_gemm_cluster_splitk(int on) { g_cluster_splitk = on; }
+void cb_wq_gemm_cluster_splitk(int on) { g_cluster_splitk.store(on); }
 
 // Clusters of `size` K splits of the per-tile kernel that fit on the current device at once (0: unknown / none).
 int cb_wq_gemm_resident_clusters(int fmt, int size) {
-  if (!g_cluster_splitk) return 0;
+  if (!g_cluster_splitk.load()) return 0;
   switch (fmt) {
     case cb::kFmtCubic4: return cb::resident_clusters<cb::kFmtCubic4>(size);
     case cb::kFmtAffine4: return cb::resident_clusters<cb::kFmtAffine4>(size);
@@ -846,10 +887,24 @@ int cb_wq_gemm_resident_clusters(int fmt, int size) {
 // CTA pairs of the persistent kernel that can be resident at once on the current device (0: cannot be launched).
 int cb_wq_gemm_resident_pairs(int fmt) { return cb::streamk_resident_pairs(fmt); }
 
-int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
-                       float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
-                       int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
-                       void* stream);
+static int wq_gemm_grouped_launch(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
+                                  float alpha, int total_rows, int N, int K, int group_k, const void* tiles,
+                                  int max_items, int mb, int num_experts, long long code_stride, long long meta_stride,
+                                  void* status, void* stream, int swiglu) {
+  if (!tiles || max_items <= 0 || mb <= 0 || mb > 256 || (mb % 16) != 0 || num_experts <= 0) return -40;
+  WqLaunchOpts o;
+  o.num_experts = num_experts;
+  o.tiles = static_cast<const int*>(tiles);
+  o.code_stride = static_cast<size_t>(code_stride);
+  o.meta_stride = static_cast<size_t>(meta_stride);
+  o.max_items = max_items;
+  o.mb_hint = mb;
+  o.swiglu = swiglu;
+  o.stream_k = g_grouped_persistent.load(std::memory_order_relaxed) != 0;
+  // the tensor map spans all rows; every work item starts at its own row offset
+  return wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, total_rows, N, K, group_k, 1, nullptr,
+                          nullptr, status, stream, nullptr, o);
+}
 
 // Grouped gate/up projection with the fused SwiGLU epilogue (every expert's rows interleaved): y has N / 2 columns.
 int cb_wq_gemm_grouped_act(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
@@ -857,30 +912,16 @@ int cb_wq_gemm_grouped_act(int fmt, const void* x, int ldx, const void* codes, c
                            int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
                            void* stream) {
   if ((N % 32) != 0 || ldy < N / 2) return -50;
-  g_epilogue_swiglu = 1;
-  const int rc = cb_wq_gemm_grouped(fmt, x, ldx, codes, meta, y, ldy, alpha, total_rows, N, K, group_k, tiles, max_items,
-                                    mb, num_experts, code_stride, meta_stride, status, stream);
-  g_epilogue_swiglu = 0;
-  return rc;
+  return wq_gemm_grouped_launch(fmt, x, ldx, codes, meta, y, ldy, alpha, total_rows, N, K, group_k, tiles, max_items, mb,
+                                num_experts, code_stride, meta_stride, status, stream, 1);
 }
 
 int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
                        float alpha, int total_rows, int N, int K, int group_k, const void* tiles, int max_items,
                        int mb, int num_experts, long long code_stride, long long meta_stride, void* status,
                        void* stream) {
-  if (!tiles || max_items <= 0 || mb <= 0 || mb > 256 || (mb % 16) != 0 || num_experts <= 0) return -40;
-  g_grouped.num_experts = num_experts;
-  g_grouped.tiles = static_cast<const int*>(tiles);
-  g_grouped.code_stride = static_cast<size_t>(code_stride);
-  g_grouped.meta_stride = static_cast<size_t>(meta_stride);
-  g_grouped.max_items = max_items;
-  g_mb_hint = mb;
-  // the tensor map spans all rows; every work item starts at its own row offset
-  const int rc = wq_gemm_dispatch(fmt, x, ldx, codes, meta, y, ldy, nullptr, alpha, total_rows, N, K, group_k, 1, nullptr,
-                                  nullptr, status, stream, nullptr, g_grouped_persistent != 0, 0, 0);
-  g_grouped.tiles = nullptr;
-  g_mb_hint = 0;
-  return rc;
+  return wq_gemm_grouped_launch(fmt, x, ldx, codes, meta, y, ldy, alpha, total_rows, N, K, group_k, tiles, max_items, mb,
+                                num_experts, code_stride, meta_stride, status, stream, 0);
 }
 
 }  // extern "C"

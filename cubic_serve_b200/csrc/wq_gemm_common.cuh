@@ -85,6 +85,19 @@ struct WqGemmParams {
   uint32_t acc_cols;        // TMEM columns per accumulator buffer (two buffers)
 };
 
+// Pipeline timeline of the first CTA(s) of a launch, for development builds only (-DCB_KERNEL_TRACE): clock64
+// stamps into `p.trace` ([row][8] 64-bit words).  The product build compiles the stamps and the hook out.
+#ifdef CB_KERNEL_TRACE
+#define CB_TRACE_ONLY(...) __VA_ARGS__
+#define CB_STAMP(cond, idx) do { if (trace && (cond)) trace[idx] = clock64(); } while (0)
+#define CB_WALL_STAMP(slot) do { if (p.trace && threadIdx.x == 0) { unsigned long long t_; \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[blockIdx.x * 8 + (slot)] = t_; } } while (0)
+#else
+#define CB_TRACE_ONLY(...)
+#define CB_STAMP(cond, idx) do { } while (0)
+#define CB_WALL_STAMP(slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

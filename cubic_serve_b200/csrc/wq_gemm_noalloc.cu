@@ -9,10 +9,11 @@
 // In host code this name is only a handle for cudaGetSymbolAddress, never an address.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[CB_NOALLOC_SCRATCH_BYTES];
 
-// the regular entry point (wq_gemm.cu); it takes the scratch as plain device pointers
-extern "C" int cb_wq_gemm(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y, int ldy,
-                          const void* residual, float alpha, int M, int N, int K, int group_k, int splits,
-                          void* workspace, void* counters, void* status, void* stream);
+// the regular split-K entry point in its workspace form (wq_gemm.cu): the K splits meet through the partial sums and
+// counters handed in as plain device pointers, never through a cluster's shared memory
+extern "C" int cb_wq_gemm_workspace_splitk(int fmt, const void* x, int ldx, const void* codes, const void* meta, void* y,
+                                           int ldy, const void* residual, float alpha, int M, int N, int K, int group_k,
+                                           int splits, void* workspace, void* counters, void* status, void* stream);
 
 namespace {
 
@@ -54,8 +55,8 @@ extern "C" int cb_wq_gemm_splitk_noalloc(int fmt, const void* x, int ldx, const 
   // cut short may have left some raised
   const cudaError_t e = cudaMemsetAsync(counters, 0, n_tiles * 4u, st);
   if (e != cudaSuccess) return static_cast<int>(e);
-  return cb_wq_gemm(fmt, x, ldx, codes, meta, y, ldy, residual, alpha, M, N, K, group_k, splits, base, counters, status,
-                    stream);
+  return cb_wq_gemm_workspace_splitk(fmt, x, ldx, codes, meta, y, ldy, residual, alpha, M, N, K, group_k, splits, base,
+                                     counters, status, stream);
 }
 
 extern "C" int cb_wq_gemm_splitk_noalloc_status(unsigned* status_out) {

@@ -330,14 +330,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int NC = p.c_stages;
   // timeline of CTA 0 (debug hook): row i = i-th k-block this CTA processes; slots as in wq_gemm.cu
   // (with CTA pairs rank 1 of the first pair records too, in rows 64..127, on its own SM's clock)
-  unsigned long long* trace = (p.trace && blockIdx.x <= (PAIR ? 1u : 0u)) ? p.trace + blockIdx.x * 64 * 8 : nullptr;
-  if (trace && threadIdx.x == 0) trace[6] = clock64();
+  CB_TRACE_ONLY(unsigned long long* trace = (p.trace && blockIdx.x <= (PAIR ? 1u : 0u)) ? p.trace + blockIdx.x * 64 * 8 : nullptr;)
+  CB_STAMP(threadIdx.x == 0, 6);
   // every CTA: wall-clock entry / exit in slots 0 / 1 of row `cta` (the buffer has >= gridDim.x rows)
-  if (p.trace && threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.trace[blockIdx.x * 8 + 0] = t;
-  }
+  CB_WALL_STAMP(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSkMaxAx; ++s) {
@@ -466,7 +462,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         ok = mbar_wait_park(smem_u32(&ctl->full[r.s]), r.wraps & 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (trace && leader && i_global < 64) trace[i_global * 8 + 4] = clock64();
+        CB_STAMP(leader && i_global < 64, i_global * 8 + 4);
         tc_fence_after();
         const uint32_t st = smem_base + static_cast<uint32_t>(r.s) * ax_bytes;
         const uint64_t bdesc = desc_hi | static_cast<uint64_t>((st & 0x3FFFFu) >> 4);
@@ -493,7 +489,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
         accumulate = 1;
-        if (trace && leader && i_global < 64) trace[i_global * 8 + 5] = clock64();
+        CB_STAMP(leader && i_global < 64, i_global * 8 + 5);
         r.advance(S);
       }
       ++seg_idx;
@@ -523,7 +519,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       ok = ok && mbar_wait_park(smem_u32(&ctl->tail_full), 0u, abort_flag);
       ok = __all_sync(0xffffffffu, ok) && !*abort_flag;
       tc_fence_after();
-      if (trace && tt == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 6] = clock64();
+      CB_STAMP(tt == 0 && seg_idx < 4, (8 + seg_idx) * 8 + 6);
       seg_geometry();
       const bool whole = seg.parts == 1;
       float* stg = reinterpret_cast<float*>(smem);
@@ -610,7 +606,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           }
         }
       }
-      if (trace && tt == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
+      CB_STAMP(tt == 0 && seg_idx < 4, (8 + seg_idx) * 8 + 7);
     };
 
     if (warp >= kSkFirstDecodeWarp) {
@@ -641,7 +637,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           for (int jj = skip; jj < len; jj += kSkDecodeGroups) {
             const int ig = i_global + jj;
             if (!mbar_wait_park(smem_u32(&ctl->c_full[rc.s]), rc.wraps & 1u, abort_flag)) { ok = false; break; }
-            if (trace && r == 0 && ig < 64) trace[ig * 8 + 2] = clock64();
+            CB_STAMP(r == 0 && ig < 64, ig * 8 + 2);
             const uint8_t* pk = c_ring + static_cast<size_t>(rc.s) * kSkCStageBytes;
             const uint4 w0 = *reinterpret_cast<const uint4*>(pk + code_off);
             const uint4 w1 = *reinterpret_cast<const uint4*>(pk + code_off + 128 * 16);
@@ -703,7 +699,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
               if (PAIR && rank != 0) mbar_arrive_cluster(cluster_map(smem_u32(&ctl->full[ra.s]), 0));
               else mbar_arrive(smem_u32(&ctl->full[ra.s]));
             }
-            if (trace && r == 0 && ig < 64) trace[ig * 8 + 3] = clock64();
+            CB_STAMP(r == 0 && ig < 64, ig * 8 + 3);
             const int step = len - jj < kSkDecodeGroups ? len - jj : kSkDecodeGroups;
             rc.advance_by(step, NC);
             ra.advance_by(step, S);
@@ -730,7 +726,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         bool ok = mbar_wait_park(smem_u32(&ctl->acc_full[buf]), use & 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok) && !*abort_flag;
         tc_fence_after();
-        if (trace && et == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 6] = clock64();
+        CB_STAMP(et == 0 && seg_idx < 4, (8 + seg_idx) * 8 + 6);
         seg_geometry();
         const bool whole = seg.parts == 1;
         if (ok) {
@@ -785,7 +781,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           if (PAIR && rank != 0) mbar_arrive_cluster(cluster_map(smem_u32(&ctl->acc_empty[buf]), 0));
           else mbar_arrive(smem_u32(&ctl->acc_empty[buf]));
         }
-        if (trace && et == 0 && seg_idx < 4) trace[(8 + seg_idx) * 8 + 7] = clock64();
+        CB_STAMP(et == 0 && seg_idx < 4, (8 + seg_idx) * 8 + 7);
 
         bool finalized = whole;
         if (!whole) {
@@ -830,12 +826,8 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   // a CTA of a pair leaves only when its peer is done too: until then the peer may arrive on this CTA's barriers
   // and rank 0's MMAs may read this CTA's shared memory; the tensor memory of the pair is freed after it
   if (PAIR) cluster_sync_all();
-  if (trace && threadIdx.x == 0) trace[7] = clock64();
-  if (p.trace && threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    p.trace[blockIdx.x * 8 + 1] = t;
-  }
+  CB_STAMP(threadIdx.x == 0, 7);
+  CB_WALL_STAMP(1);
   if (warp == 1) {
     tc_fence_after();
     if (PAIR) tmem_dealloc_pair(tmem_base, p.tmem_cols);
@@ -856,11 +848,13 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 template <int FMT>
 static int launch_sk_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemmParams& p, int grid, size_t smem,
                          cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};     // per device, like the attribute itself
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -18;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured[dev] = true;
   }
   wq_gemm_sk_kernel<FMT, false><<<grid, kSkThreads, smem, stream>>>(tx, tw, p);
   return static_cast<int>(cudaGetLastError());
@@ -870,11 +864,13 @@ static int launch_sk_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqG
 template <int FMT>
 static int launch_sk_pair_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqGemmParams& p, int grid, size_t smem,
                               cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};     // per device, like the attribute itself
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -18;
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(wq_gemm_sk_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);

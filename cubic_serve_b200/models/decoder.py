@@ -115,6 +115,11 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     down; vocab-sharded embedding and lm_head (reference ownership planners:
     ``models/parallel_weights.py:72-352``).  ``layer_range`` keeps only the layers ``[lo, hi)`` of one pipeline
     stage; every layer draws from its own generator, so a stage holds exactly the weights the whole model would.
+
+    The model does not depend on the partition: every rank draws the FULL matrix of a projection from a generator
+    seeded by (seed, layer) only and keeps its rows / columns, so the shards of any ``tp_size`` are slices of the
+    one-GPU model (quantization groups lie along K in multiples of the shard widths, so quantizing a slice equals
+    slicing the quantized matrix).  Outputs of different partitions can therefore be compared with each other.
     """
     assert cfg.num_q_heads % tp_size == 0 and cfg.num_kv_heads % tp_size == 0
     gen = torch.Generator(device=device)
@@ -125,6 +130,21 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     def rnd(n, k):
         return torch.randn(n, k, device=device, generator=gen, dtype=torch.float32) * std
 
+    r = tp_rank
+
+    def rows_of(full, width):
+        """This rank's ``width`` rows of a matrix whose rows are owned in rank order."""
+        return full[r * width:(r + 1) * width]
+
+    def sections(full, widths):
+        """``full`` is a stack of sections of ``tp_size * w`` rows each; this rank keeps rows ``[r w, (r + 1) w)`` of
+        every section (q | k | v heads, gate | up features, ...)."""
+        out, base = [], 0
+        for w in widths:
+            out.append(full[base + r * w:base + (r + 1) * w])
+            base += w * tp_size
+        return torch.cat(out)
+
     def norm_w():
         # zero-centred norms multiply by (1 + w)
         return torch.full((H,), 0.0 if cfg.zero_centered_norm else 1.0, device=device, dtype=torch.bfloat16)
@@ -132,37 +152,40 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     layers = []
     lo, hi = layer_range or (0, cfg.num_layers)
     for li in range(lo, hi):
-        gen.manual_seed((seed * 1000 + tp_rank) * 4096 + li)
+        gen.manual_seed(seed * 4096000 + li)
         if cfg.layer_is_gdn(li):
             gk, gv = cfg.gdn_k_heads // tp_size, cfg.gdn_v_heads // tp_size
             f32 = dict(device=device, dtype=torch.float32)
             lw = LayerWeights(ln1=norm_w(), ln2=norm_w(), gdn=GdnWeights(
-                in_proj=quantize_linear(rnd(2 * gk * 128 + 2 * gv * 128, H), cfg),
-                in_ba=wq_pack.pack_bf16(rnd(2 * gv, H)),
-                conv_w=torch.randn((2 * gk + gv) * 128, 4, generator=gen, **f32) * 0.3,
-                a_log=torch.randn(gv, generator=gen, **f32) * 0.5,
-                dt_bias=torch.randn(gv, generator=gen, **f32) * 0.5,
+                in_proj=quantize_linear(sections(rnd(2 * gk * 128 * tp_size + 2 * gv * 128 * tp_size, H),
+                                                 [gk * 128, gk * 128, gv * 128, gv * 128]), cfg),
+                in_ba=wq_pack.pack_bf16(sections(rnd(2 * gv * tp_size, H), [gv, gv])),
+                conv_w=sections(torch.randn((2 * gk + gv) * 128 * tp_size, 4, generator=gen, **f32) * 0.3,
+                                [gk * 128, gk * 128, gv * 128]),
+                a_log=rows_of(torch.randn(gv * tp_size, generator=gen, **f32) * 0.5, gv),
+                dt_bias=rows_of(torch.randn(gv * tp_size, generator=gen, **f32) * 0.5, gv),
                 norm_w=torch.ones(128, **f32),
-                out=quantize_linear(rnd(H, gv * 128), cfg), hk=gk, hv=gv))
+                out=quantize_linear(rnd(H, gv * 128 * tp_size)[:, r * gv * 128:(r + 1) * gv * 128].contiguous(), cfg),
+                hk=gk, hv=gv))
         else:
             lw = LayerWeights(
                 ln1=norm_w(), ln2=norm_w(),
-                qkv=quantize_linear(rnd((hq + 2 * hkv) * D, H), cfg),
-                o=quantize_linear(rnd(H, hq * D), cfg),
+                qkv=quantize_linear(sections(rnd((hq + 2 * hkv) * D * tp_size, H), [hq * D, hkv * D, hkv * D]), cfg),
+                o=quantize_linear(rnd(H, hq * D * tp_size)[:, r * hq * D:(r + 1) * hq * D].contiguous(), cfg),
             )
             if cfg.attn_output_gate:
-                lw.attn_gate = quantize_linear(rnd(hq * D, H), cfg)
+                lw.attn_gate = quantize_linear(rows_of(rnd(hq * D * tp_size, H), hq * D), cfg)
         if cfg.qk_norm and lw.gdn is None:
             lw.q_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
             lw.k_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
         if cfg.is_moe:
             from .moe import random_moe_weights
-            lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std)
+            lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std, layer_seed=seed * 4096000 + li)
         else:
-            lw.gate_up = quantize_linear(rnd(2 * inter, H), cfg)
-            lw.down = quantize_linear(rnd(H, inter), cfg)
+            lw.gate_up = quantize_linear(sections(rnd(2 * inter * tp_size, H), [inter, inter]), cfg)
+            lw.down = quantize_linear(rnd(H, inter * tp_size)[:, r * inter:(r + 1) * inter].contiguous(), cfg)
         layers.append(lw)
-    gen.manual_seed((seed * 1000 + tp_rank) * 4096 + 4095)
+    gen.manual_seed(seed * 4096000 + 4095)
     v_local = cfg.vocab_size // tp_size
     # the embedding table is generated identically on every rank (rank-independent stream), kept whole
     # for the fused path (each rank embeds only the rows it owns) and sliced for the vocab-sharded baseline
@@ -172,7 +195,7 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     if cfg.tie_embeddings:
         head = embed
     else:
-        head = (torch.randn(v_local, H, device=device, generator=gen) * std).to(torch.bfloat16)
+        head = rows_of((torch.randn(v_local * tp_size, H, device=device, generator=gen) * std).to(torch.bfloat16), v_local)
     lm_head = quantize_linear(head.float(), cfg) if cfg.quant.lm_head_quantized else wq_pack.pack_bf16(head)
     return DecoderWeights(embed=embed, layers=layers, final_norm=norm_w(), lm_head=lm_head,
                           vocab_start=tp_rank * v_local, extras={"embed_full": embed_full})

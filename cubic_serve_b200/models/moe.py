@@ -83,15 +83,18 @@ class MoeLayer:
         return K.moe_combine(sc.y, sc, t, self.out[:t] if out is None else out, residual)
 
 
-def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size: int = 1, std: float = 0.02) -> MoeLayer:
-    """Random experts for EP = tp_size (contiguous expert-id slices per rank), router replicated."""
+def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size: int = 1, std: float = 0.02,
+                       layer_seed: int = 0) -> MoeLayer:
+    """Random experts for EP = tp_size (contiguous expert-id slices per rank), router replicated.  Expert ``e`` of a
+    layer draws from a generator seeded by (layer, e) only, so every partition holds slices of the same model."""
     from .decoder import quantize_linear
     H, I, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
     local = E // tp_size
-    shared = torch.Generator(device=device).manual_seed(12345)
+    shared = torch.Generator(device=device).manual_seed(12345 + layer_seed)
     router = (torch.randn(E, H, device=device, generator=shared) * std).to(torch.bfloat16)
     gus, downs = [], []
-    for _ in range(local):
+    for e in range(tp_rank * local, (tp_rank + 1) * local):
+        gen.manual_seed(layer_seed * 1024 + e + 1)
         gus.append(quantize_linear(torch.randn(2 * I, H, device=device, generator=gen) * std, cfg))
         downs.append(quantize_linear(torch.randn(H, I, device=device, generator=gen) * std, cfg))
     gu, gcs, gms = stack_experts(gus)

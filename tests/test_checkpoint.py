@@ -221,3 +221,36 @@ def test_asymmetric_int_checkpoint_slices_zero_points_with_the_rows(tmp_path):
     save_file(t, str(path / "model.safetensors"))
     with pytest.raises(C.CheckpointError, match="act-order"):
         C.admit_checkpoint(path)
+
+
+def test_random_weights_of_any_partition_are_slices_of_one_model():
+    """``random_decoder_weights`` draws rank-independent full matrices: the shards of two ranks put together give the
+    one-GPU model's matrices bit for bit (dense and MoE), so outputs of different partitions are comparable."""
+    from cubic_serve_b200.models.decoder import random_decoder_weights
+    cfg = replace(BASE, quant=QuantSpec("cubic", 4, 128))
+    one = random_decoder_weights(cfg, "cpu", seed=3)
+    two = [random_decoder_weights(cfg, "cpu", seed=3, tp_rank=r, tp_size=2) for r in range(2)]
+    d = wq_pack.unpack_to_dense
+    D = cfg.head_dim
+    for li in range(cfg.num_layers):
+        full, parts = one.layers[li], [t.layers[li] for t in two]
+        qkv = d(full.qkv)
+        hq, hkv = cfg.num_q_heads * D, cfg.num_kv_heads * D
+        want = [torch.cat([qkv[r * hq // 2:(r + 1) * hq // 2], qkv[hq + r * hkv // 2:hq + (r + 1) * hkv // 2],
+                           qkv[hq + hkv + r * hkv // 2:hq + hkv + (r + 1) * hkv // 2]]) for r in range(2)]
+        for r in range(2):
+            assert torch.equal(d(parts[r].qkv)[:want[r].shape[0]], want[r])
+        assert torch.equal(torch.cat([d(p.o)[:cfg.hidden_size] for p in parts], 1), d(full.o)[:cfg.hidden_size])
+        assert torch.equal(torch.cat([d(p.down)[:cfg.hidden_size] for p in parts], 1), d(full.down)[:cfg.hidden_size])
+        gu, I = d(full.gate_up), cfg.intermediate_size
+        for r in range(2):
+            want_gu = torch.cat([gu[r * I // 2:(r + 1) * I // 2], gu[I + r * I // 2:I + (r + 1) * I // 2]])
+            assert torch.equal(d(parts[r].gate_up)[:I], want_gu)
+    assert torch.equal(torch.cat([d(t.lm_head)[:cfg.vocab_size // 2] for t in two]), d(one.lm_head)[:cfg.vocab_size])
+    moe = replace(BASE, family="gqa_moe", num_experts=4, experts_per_token=2, moe_intermediate_size=128,
+                  quant=QuantSpec("cubic", 4, 128))
+    m1 = random_decoder_weights(moe, "cpu", seed=1)
+    m2 = [random_decoder_weights(moe, "cpu", seed=1, tp_rank=r, tp_size=2) for r in range(2)]
+    assert torch.equal(torch.cat([t.layers[1].moe.gate_up.codes for t in m2]), m1.layers[1].moe.gate_up.codes)
+    assert torch.equal(m2[0].layers[0].moe.router.codes, m1.layers[0].moe.router.codes)
+    assert not torch.equal(m1.layers[0].moe.router.codes, m1.layers[1].moe.router.codes)
