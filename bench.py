@@ -42,6 +42,11 @@ def parse_args():
     ap.add_argument("--kv", default="", help="K,V cache bits, e.g. 8,8 or 4,8 (default: 8,8 dense, 4,8 MoE)")
     ap.add_argument("--prefill-tokens", type=int, default=8192, help="token budget of a prefill step")
     ap.add_argument("--spec-depth", type=int, default=0, help="MTP draft tokens per round (0 = no speculation)")
+    ap.add_argument("--context", default="mean", choices=["mean", "start"],
+                    help="where in the 512-token decode the timed steps sit: around its mean context (input + 256) or "
+                         "right after the prefill")
+    ap.add_argument("--output-len", type=int, default=512, help="output tokens per request of the benchmark config")
+    ap.add_argument("--no-check", action="store_true", help="skip the untimed multi-GPU logit check")
     ap.add_argument("--accept", type=float, default=0.7,
                     help="forced per-depth acceptance probability of speculative rounds (random weights never agree)")
     return ap.parse_args()
@@ -150,13 +155,23 @@ def main() -> None:
             tp = TensorParallel(tp_group, dev, mode=mode, hidden=cfg.hidden_size,
                                 max_tokens=args.prefill_tokens, rows_max=max(args.concurrency, 512))
     C, L = args.concurrency, args.input_len
-    total_steps = args.warmup + args.steps
+    # the config decodes `output_len` tokens per request: the timed steps sit around the MEAN context of that decode
+    # (input + output / 2); the steps before them run untimed
+    advance = 0
+    if args.context == "mean" and not args.spec_depth:
+        advance = max(0, args.output_len // 2 - args.steps // 2 - args.warmup)
+    total_steps = args.warmup + args.steps + advance
     max_len = L + total_steps * (1 + args.spec_depth) + 8 + args.spec_depth
     pages_per_req = -(-max_len // 16)
     num_pages = C * pages_per_req + 8
     prefill_tokens = args.prefill_tokens
 
     weights = random_decoder_weights(cfg, dev, seed=0, tp_rank=tp_rank, tp_size=tp_size, layer_range=layer_range)
+    # untimed prologue: the multi-GPU paths against each other and against one GPU, at the logit level
+    check = {"n_gpus": world, "note": "one GPU: no partition to compare"}
+    if tp is not None and pp is None and not args.no_check:
+        from cubic_serve_b200.parallel.tp_check import run_check
+        check = run_check(cfg, dev, tp_group, weights=weights, k_bits=k_bits, v_bits=v_bits, tp1_layers=4)
     runner = DecoderRunner(cfg, weights, num_pages=num_pages, max_tokens=prefill_tokens, k_bits=k_bits, v_bits=v_bits,
                            tp=tp, pp=pp, max_requests=max(C, 1))
     if args.spec_depth:
@@ -199,10 +214,18 @@ def main() -> None:
     prefill_s = time.perf_counter() - t0
     assert len(eng.scheduler.running) == C, len(eng.scheduler.running)
 
-    # ---- decode: W warm-up steps, K timed steps
+    # ---- decode: the steps up to the mean context (untimed), W warm-up steps, K timed steps
+    early_ms = None
+    if advance:
+        ex.device_ms = []
+        for _ in range(advance):
+            outs = eng.step()
+        sync()
+        early_ms = float(np.median(ex.device_ms[3:3 + args.steps])) if len(ex.device_ms) > 3 else None
     for _ in range(args.warmup):
         outs = eng.step()
         assert len(outs) >= C
+    context_at_timed = int(L + advance + args.warmup)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -233,13 +256,20 @@ def main() -> None:
             "metric": f"output tok/s @{C} concurrent (decode steps, device-timed, max over ranks)",
             "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 3), "dtype": f"bf16 activations, {cfg.quant.method} {cfg.quant.bits}-bit weights, INT{k_bits}/INT{v_bits} KV",
+            # the reference publishes no B200 number: this ratio is against its best published figure on OTHER hardware
+            # and another model (dense, 4 x SM120, C = 256), kept for context only
+            "vs_baseline": round(value / BASELINE_TOK_S, 3), "vs_baseline_note": "published 4xSM120 figure, other model",
+            "dtype": f"bf16 activations, {cfg.quant.method} {cfg.quant.bits}-bit weights, INT{k_bits}/INT{v_bits} KV",
             "data": "synthetic (random token ids; random-init N(0,0.02) weights quantized offline)",
             "impl": "ours",
             "config": {"model": cfg.name + ("" if not args.layers else f"-{args.layers}layers-INVALID"),
                        "global_batch": C, "seq_len": L, "parallelism": f"tp{tp_size}" + (f"pp{args.pp}" if args.pp > 1 else ""),
                        "comm": (tp.mode if tp is not None else "none"), "cuda_graphs": True, "kv_cache": f"int{k_bits}/int{v_bits}",
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
+                       "context_at_timed_steps": [context_at_timed, context_at_timed + args.steps],
+                       "output_len": args.output_len,
+                       **({"ms_per_step_at_start_of_decode": round(early_ms, 4),
+                           "tok_s_at_start_of_decode": round(C / (early_ms / 1e3), 1)} if early_ms else {}),
                        "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,
                        # all C requests are submitted at t = 0: TTFT includes queueing behind earlier prefill chunks
                        "ttft_p50_ms": round(1e3 * float(np.median(sorted(first_token_at.values()))), 1) if first_token_at else None,
@@ -252,6 +282,7 @@ def main() -> None:
             "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": int(ex.h2d_bytes_last),
                     "d2h_bytes_per_step": int(ex.d2h_bytes_last), "api": "LLMEngine.step()"},
             "gpu_launches": int(launches),
+            "check": check,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -6,6 +6,8 @@
 // embedding/immutable.cu:3.  All are bandwidth-bound: 128-bit accesses, one
 // pass over the row held in registers.
 #include "ptx.cuh"
+#include "launch.cuh"
+#include <atomic>
 
 namespace cb {
 
@@ -29,10 +31,14 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* residual, __nv_bfloat16* residual_out,
                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int H, float eps,
-               int zero_centered) {
+               int zero_centered, const long long* __restrict__ x_rows) {
   __shared__ float red[8];
   const size_t row = blockIdx.x;
   const int nvec = H >> 3;  // 8 bf16 per 16 bytes
+  pdl_wait();
+  pdl_launch_dependents();
+  // x_rows: output row i is the norm of input row x_rows[i] (the rows whose logits are wanted, gathered in passing)
+  if (x_rows) x += (static_cast<size_t>(x_rows[row]) - row) * H;
   float vals[kNormMaxVec][8];
   float ss = 0.f;
 #pragma unroll
@@ -93,6 +99,8 @@ __global__ void __launch_bounds__(256)
 swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I) {
   // grid = (vector blocks of a row, rows): no per-thread 64-bit division
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   if (v >= (I >> 3)) return;
   const size_t row = blockIdx.y;
   const uint4 g = reinterpret_cast<const uint4*>(gu + row * 2 * I)[v];
@@ -115,6 +123,8 @@ __global__ void __launch_bounds__(128)
 embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
                  int H, int vocab_start, int vocab_count) {
   const size_t t = blockIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   const int id = ids[t] - vocab_start;
   const bool owned = id >= 0 && id < vocab_count;
   const int nvec = H >> 3;
@@ -127,18 +137,35 @@ embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ 
 
 }  // namespace cb
 
+static std::atomic<int> g_pdl{1};
+
 extern "C" {
+
+// Programmatic dependent launch of the library's kernels (see launch.cuh): 1 (default) on, 0 off.
+void cb_set_pdl(int on) { g_pdl.store(on ? 1 : 0); }
+int cb_pdl_enabled() { return g_pdl.load(std::memory_order_relaxed); }
 
 int cb_rmsnorm(const void* x, const void* residual, void* residual_out, const void* w, void* out, int rows, int H,
                float eps, int zero_centered, void* stream) {
   using namespace cb;
   if (rows <= 0) return 0;
   if (H % 8 != 0 || H > kNormThreads * kNormMaxVec * 8) return -10;
-  rmsnorm_kernel<<<rows, kNormThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  return static_cast<int>(launch(rmsnorm_kernel, dim3(rows), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(w),
-      static_cast<__nv_bfloat16*>(out), H, eps, zero_centered);
-  return static_cast<int>(cudaGetLastError());
+      static_cast<__nv_bfloat16*>(out), H, eps, zero_centered, static_cast<const long long*>(nullptr)));
+}
+
+// out[i] = rmsnorm(x[x_rows[i]]): the final norm of a step over the rows that feed the output projection.
+int cb_rmsnorm_rows(const void* x, const void* x_rows, const void* w, void* out, int rows, int H, float eps,
+                    int zero_centered, void* stream) {
+  using namespace cb;
+  if (rows <= 0) return 0;
+  if (H % 8 != 0 || H > kNormThreads * kNormMaxVec * 8 || !x_rows) return -10;
+  return static_cast<int>(launch(rmsnorm_kernel, dim3(rows), dim3(kNormThreads), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(nullptr),
+      static_cast<__nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(out), H, eps, zero_centered, static_cast<const long long*>(x_rows)));
 }
 
 int cb_swiglu(const void* gate_up, void* out, int rows, int I, void* stream) {
@@ -156,9 +183,8 @@ int cb_swiglu(const void* gate_up, void* out, int rows, int I, void* stream) {
     return 0;
   }
   const dim3 grid(static_cast<unsigned>(((I >> 3) + 255) / 256), static_cast<unsigned>(rows));
-  swiglu_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), I);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(swiglu_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), I));
 }
 
 int cb_embedding(const void* ids, const void* table, void* out, int tokens, int H, int vocab_start, int vocab_count,
@@ -166,10 +192,9 @@ int cb_embedding(const void* ids, const void* table, void* out, int tokens, int 
   using namespace cb;
   if (tokens <= 0) return 0;
   if (H % 8 != 0) return -10;
-  embedding_kernel<<<tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  return static_cast<int>(launch(embedding_kernel, dim3(tokens), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const int*>(ids), static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), H,
-      vocab_start, vocab_count);
-  return static_cast<int>(cudaGetLastError());
+      vocab_start, vocab_count));
 }
 
 }  // extern "C"

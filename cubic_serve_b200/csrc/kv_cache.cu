@@ -7,6 +7,7 @@
 // (c, c+64) and a 32-channel quantization group (c/32) are both warp-local.
 #include "ptx.cuh"
 #include "kv_layout.cuh"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -99,6 +100,8 @@ static constexpr int kRopeWarps = 8;
 // part of this kernel, and one warp per (token, head) paid it 6x as often.
 __global__ void __launch_bounds__(kRopeWarps * 32)
 rope_kv_write_kernel(const KvWriteParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -172,6 +175,8 @@ rope_kv_write_kernel(const KvWriteParams p) {
 __global__ void __launch_bounds__(256)
 hadamard_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_bfloat16* __restrict__ y, int ldy, int vectors,
                 int rows) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const long long w = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (w >= static_cast<long long>(rows) * vectors) return;
@@ -223,17 +228,17 @@ int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* posi
   p.inv_freq = static_cast<const float*>(inv_freq);
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.rotary_dim = rotary_dim; p.eps = eps; p.rotate = rotate;
   p.lay = make_kv_layout(D, k_bits, v_bits);
-  rope_kv_write_kernel<<<static_cast<unsigned>(T), kRopeWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(rope_kv_write_kernel, dim3(static_cast<unsigned>(T)), dim3(kRopeWarps * 32), 0,
+                                 static_cast<cudaStream_t>(stream), p));
 }
 
 // y[r, 128 h .. 128 h + 127] = normalised Walsh-Hadamard transform of x[r, same], h < vectors (bf16, in place allowed).
 int cb_hadamard(const void* x, int ldx, void* y, int ldy, int vectors, int rows, void* stream) {
   if (rows <= 0 || vectors <= 0) return 0;
   const long long warps = static_cast<long long>(rows) * vectors;
-  cb::hadamard_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy, vectors, rows);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(cb::launch(cb::hadamard_kernel, dim3(static_cast<unsigned>((warps + 7) / 8)), dim3(256), 0,
+                                     static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), ldx,
+                                     static_cast<__nv_bfloat16*>(y), ldy, vectors, rows));
 }
 
 int cb_copy_pages(void* cache, const void* src_pages, const void* dst_pages, int n, long long page_bytes,

@@ -16,6 +16,7 @@
 //
 // Waits are bounded; on a timeout the CTA records Status and exits cleanly.
 #include "ptx.cuh"
+#include "launch.cuh"
 #include "kv_layout.cuh"
 
 namespace cb {
@@ -256,6 +257,8 @@ paged_attn_kernel(const AttnParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int kvh = blockIdx.x, rb = blockIdx.y, split = blockIdx.z;
+  pdl_wait();
+  pdl_launch_dependents();
   const int qcount = p.rb_qcount[rb];
   if (qcount <= 0) return;  // padding block (uniform across the CTA)
   const int req = p.rb_req[rb], qstart = p.rb_qstart[rb], ctx = p.rb_ctx[rb];
@@ -480,8 +483,7 @@ static int launch_attn(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  paged_attn_kernel<KB, VB><<<grid, kAttnWarps * 32, smem, st>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(paged_attn_kernel<KB, VB>, grid, dim3(kAttnWarps * 32), smem, st, p));
 }
 
 }  // namespace cb

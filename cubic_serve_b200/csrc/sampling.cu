@@ -6,6 +6,7 @@
 // argmax with min-id ties and grammar mask), sampling/topk_topp.py:23 (root
 // top-k/top-p/temperature + Philox), sampling/speculative.py (K=1 verify).
 #include "ptx.cuh"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -106,6 +107,8 @@ sample_kernel(const SampleParams p) {
   __shared__ Cand red[kSampleThreads / 32];
   __shared__ Cand top[kMaxTopK];
   const int row = blockIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   const __nv_bfloat16* lg = p.logits + static_cast<size_t>(row) * p.ld;
   const uint32_t* mk = p.mask ? p.mask + static_cast<size_t>(row) * p.mask_words : nullptr;
   const float temp = p.temperature ? p.temperature[row] : 0.f;
@@ -160,6 +163,8 @@ sample_merge_kernel(const float* cand_val, const int* cand_id, int sources, long
   __shared__ Cand tops[4][kMaxTopK];
   const int wrp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + wrp;
+  pdl_wait();
+  pdl_launch_dependents();
   if (row >= rows) return;
   const float temp = temperature ? temperature[row] : 0.f;
   int K = 1;
@@ -218,6 +223,8 @@ sample_merge_kernel(const float* cand_val, const int* cand_id, int sources, long
 __global__ void verify_greedy_kernel(const int* target_ids, const int* draft_ids, const int* depth, int max_depth,
                                      const int* forced_reject_at, int* accepted, int* bonus, int requests) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   if (r >= requests) return;
   const int d = depth[r];
   int a = 0;
@@ -240,6 +247,8 @@ __global__ void __launch_bounds__(128)
 reasoning_budget_kernel(int* __restrict__ ids, const int* __restrict__ row_slot, const int* __restrict__ init,
                         int* __restrict__ left, int* __restrict__ fpos, int rows, int end_id, int4 seq, int seq_len) {
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
   if (row >= rows) return;
   const int slot = row_slot[row];
   if (slot < 0) return;
@@ -286,8 +295,7 @@ int cb_sample(const void* logits, int ld, const void* mask, int mask_words, cons
   p.vocab = vocab; p.ld = ld; p.mask_words = mask_words;
   p.cand_val = nullptr;
   p.cand_id = nullptr;
-  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), p));
 }
 
 // Rank-local half of vocab-sharded sampling: the row's best candidates (20 slots per row, see SampleParams).
@@ -305,8 +313,7 @@ int cb_sample_candidates(const void* logits, int ld, const void* mask, int mask_
   p.vocab = vocab; p.ld = ld; p.mask_words = mask_words;
   p.cand_val = static_cast<float*>(cand_val);
   p.cand_id = static_cast<int*>(cand_id);
-  sample_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, static_cast<cudaStream_t>(stream), p));
 }
 
 // Merge `sources` candidate sets (source s at cand + s * source_stride elements, [rows, 20] each) and draw.
@@ -316,22 +323,20 @@ int cb_sample_merge(const void* cand_val, const void* cand_id, int sources, long
   using namespace cb;
   if (rows <= 0) return 0;
   if (sources < 1 || sources > 8) return -10;
-  sample_merge_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  return static_cast<int>(launch(sample_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const float*>(cand_val), static_cast<const int*>(cand_id), sources, source_stride, rows,
       static_cast<const float*>(temperature), static_cast<const float*>(top_p), static_cast<const int*>(top_k),
       static_cast<const unsigned long long*>(seeds), static_cast<const unsigned long long*>(counters),
-      static_cast<int*>(out_ids), static_cast<float*>(out_logprob));
-  return static_cast<int>(cudaGetLastError());
+      static_cast<int*>(out_ids), static_cast<float*>(out_logprob)));
 }
 
 int cb_verify_greedy(const void* target_ids, const void* draft_ids, const void* depth, int max_depth,
                      const void* forced_reject_at, void* accepted, void* bonus, int requests, void* stream) {
   if (requests <= 0) return 0;
-  cb::verify_greedy_kernel<<<(requests + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  return static_cast<int>(cb::launch(cb::verify_greedy_kernel, dim3((requests + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const int*>(target_ids), static_cast<const int*>(draft_ids), static_cast<const int*>(depth),
       max_depth, static_cast<const int*>(forced_reject_at), static_cast<int*>(accepted), static_cast<int*>(bonus),
-      requests);
-  return static_cast<int>(cudaGetLastError());
+      requests));
 }
 
 // ids[rows] (in place), row_slot / init [rows], left / fpos [slots]; `seq` = 1..4 tokens of the forced end sequence
@@ -341,10 +346,9 @@ int cb_reasoning_budget(void* ids, const void* row_slot, const void* init, void*
   if (rows <= 0) return 0;
   if (!seq || seq_len < 1 || seq_len > 4) return -20;
   int4 q = make_int4(seq[0], seq_len > 1 ? seq[1] : 0, seq_len > 2 ? seq[2] : 0, seq_len > 3 ? seq[3] : 0);
-  cb::reasoning_budget_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  return static_cast<int>(cb::launch(cb::reasoning_budget_kernel, dim3((rows + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<int*>(ids), static_cast<const int*>(row_slot), static_cast<const int*>(init), static_cast<int*>(left),
-      static_cast<int*>(fpos), rows, end_id, q, seq_len);
-  return static_cast<int>(cudaGetLastError());
+      static_cast<int*>(fpos), rows, end_id, q, seq_len));
 }
 
 }  // extern "C"

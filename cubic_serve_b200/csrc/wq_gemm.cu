@@ -31,6 +31,7 @@
 //                   of the k-block; w = (code - 8) * scale + that; one block per k-block
 //          NVFP4  : word h = bf16x2(block scale of columns 32h..32h+15, ..+16..31)
 #include "wq_gemm_common.cuh"
+#include "launch.cuh"
 #include <atomic>
 
 namespace cb {
@@ -53,7 +54,8 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: [stage: x tile | A tile | packed codes+meta] * S, then control block
   const uint32_t x_bytes = static_cast<uint32_t>(p.mb) * 128u;
-  const uint32_t stage_bytes = x_bytes + kATileBytes + (FMT == kFmtBf16 ? 0 : kCodeBytes + kMetaBytes);
+  constexpr uint32_t kMeta = static_cast<uint32_t>(meta_bytes(FMT));
+  const uint32_t stage_bytes = x_bytes + kATileBytes + (FMT == kFmtBf16 ? 0 : kCodeBytes + kMeta);
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
 
@@ -68,7 +70,9 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint8_t* codes_base = p.codes;
   const uint8_t* meta_base = p.meta;
   int w_row0 = 0;                        // bf16 weights: first row of this expert in the stacked [E * N, K] matrix
+  pdl_launch_dependents();
   if (grouped) {
+    pdl_wait();                             // the work list is written by the routing kernels
     const int item = blockIdx.y;
     if (item >= p.group_tiles[0]) return;   // uniform for the CTA, before any barrier or TMEM allocation
     const int e = p.group_tiles[1 + 3 * item];
@@ -115,7 +119,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
-      const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? kATileBytes : kCodeBytes + kMetaBytes);
+      const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? kATileBytes : kCodeBytes + kMeta);
       // stage index and phase are carried as counters: `i % S` and `i / S` with a run-time S cost two
       // integer divisions (~300 cycles on one thread), which was most of the per-k-block time of this loop
       auto load_weights = [&](int i, int s) {
@@ -127,9 +131,9 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row0 + n_tile * kTileN, bar);
         } else {
           const uint8_t* csrc = codes_base + (static_cast<size_t>(n_tile) * p.k_blocks + kb) * kCodeBytes;
-          const uint8_t* msrc = meta_base + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMetaBytes;
+          const uint8_t* msrc = meta_base + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMeta;
           bulk_g2s(smem_u32(st + x_bytes + kATileBytes), csrc, kCodeBytes, bar);
-          bulk_g2s(smem_u32(st + x_bytes + kATileBytes + kCodeBytes), msrc, kMetaBytes, bar);
+          bulk_g2s(smem_u32(st + x_bytes + kATileBytes + kCodeBytes), msrc, kMeta, bar);
         }
       };
       auto load_x = [&](int i, int s) {
@@ -140,6 +144,8 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // all-gather still in flight overlaps with weight streaming
       const int pre = iters < S ? iters : S;
       for (int i = 0; i < pre; ++i) load_weights(i, i);
+      // everything up to here (set-up, the first weight copies) may overlap the tail of the previous kernel
+      pdl_wait();
       bool ok = true;
       if (p.tp.mode & kTpGatherWait) {
         const uint32_t target = p.tp.ag_state[0] + p.tp.ag_expected;   // arrivals consumed so far + this launch's
@@ -222,42 +228,51 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint8_t* pk = st + x_bytes + kATileBytes;
         const uint4 w0 = *reinterpret_cast<const uint4*>(pk + code_off);
         const uint4 w1 = *reinterpret_cast<const uint4*>(pk + code_off + 128 * 16);
-        const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
-        // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py): Cubic {A, B} and {C, -} of the
-        // row's scale group; the other formats {scale, offset} (or two block scales) of each 32-column half
-        const uint32_t m0 = meta[r], m1 = meta[128 + r];
         uint8_t* arow = st + a_off;
+        if constexpr (FMT == kFmtCubic4) {
+          // the row's level table (16 bytes, see cubic_lut8): one scale group covers the whole k-block
+          const uint4 t = *reinterpret_cast<const uint4*>(pk + kCodeBytes + code_off);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint4 words = h ? w1 : w0;
-          uint32_t c0, c1, c2;
-          if (FMT == kFmtCubic4) {
-            c0 = bf2_dup(m0);        // A = s * a / 7
-            c1 = bf2_dup_hi(m0);     // B = s * b / 49
-            c2 = bf2_dup(m1);        // C = s * (1 - a - b) / 343
-          } else {
+          for (int h = 0; h < 2; ++h) {
+            const uint4 words = h ? w1 : w0;
+            uint32_t o[4][4];
+            cubic_lut8(words.x, t, o[0]);
+            cubic_lut8(words.y, t, o[1]);
+            cubic_lut8(words.z, t, o[2]);
+            cubic_lut8(words.w, t, o[3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(arow + ((static_cast<uint32_t>(h * 4 + j) ^ sw) << 4)) =
+                  make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+          }
+        } else {
+          // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py): {scale, offset} (or two block
+          // scales) of each 32-column half
+          const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
+          const uint32_t m0 = meta[r], m1 = meta[128 + r];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 words = h ? w1 : w0;
             const uint32_t so = h ? m1 : m0;
-            c0 = bf2_dup(so);
-            c1 = bf2_dup_hi(so);
-            c2 = 0;
-          }
-          uint32_t o[4][4];
-          if (FMT == kFmtNvfp4) {
-            // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
-            decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
-            decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
-            decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
-            decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
-          } else {
-            decode8<FMT>(words.x, c0, c1, c2, o[0]);
-            decode8<FMT>(words.y, c0, c1, c2, o[1]);
-            decode8<FMT>(words.z, c0, c1, c2, o[2]);
-            decode8<FMT>(words.w, c0, c1, c2, o[3]);
-          }
+            const uint32_t c0 = bf2_dup(so), c1 = bf2_dup_hi(so);
+            uint32_t o[4][4];
+            if constexpr (FMT == kFmtNvfp4) {
+              // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
+              decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
+              decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
+              decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
+              decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+            } else {
+              decode8<FMT>(words.x, c0, c1, 0u, o[0]);
+              decode8<FMT>(words.y, c0, c1, 0u, o[1]);
+              decode8<FMT>(words.z, c0, c1, 0u, o[2]);
+              decode8<FMT>(words.w, c0, c1, 0u, o[3]);
+            }
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(arow + ((static_cast<uint32_t>(h * 4 + j) ^ sw) << 4)) =
-                make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(arow + ((static_cast<uint32_t>(h * 4 + j) ^ sw) << 4)) =
+                  make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
+          }
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -268,6 +283,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
     }
     // epilogue: TMEM lane = output feature, column = batch row
+    pdl_wait();                             // before this thread's first global access (residual, output, partials)
     const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_full), 0, abort_flag));
     tc_fence_after();
     CB_STAMP(dq == 0, 8 + 6);
@@ -599,25 +615,12 @@ static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams
   if (p.cluster_splitk) {
     // the K splits of a tile (grid.y) as one cluster; only if every cluster of the launch can be resident at once
     // (a cluster's CTAs share a GPC), otherwise the launch would run in waves: fall back to the workspace path
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = grid.y;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
     if (resident_clusters<FMT>(static_cast<int>(grid.y)) >= static_cast<int>(grid.x * grid.z))
-      return static_cast<int>(cudaLaunchKernelEx(&cfg, wq_gemm_kernel<FMT>, tx, tw, p));
+      return static_cast<int>(launch(wq_gemm_kernel<FMT>, grid, dim3(kThreads), smem, stream, dim3(1, grid.y, 1), tx, tw, p));
     p.cluster_splitk = 0;
     if (!p.workspace || !p.counters) return -13;
   }
-  wq_gemm_kernel<FMT><<<grid, kThreads, smem, stream>>>(tx, tw, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(wq_gemm_kernel<FMT>, grid, dim3(kThreads), smem, stream, tx, tw, p));
 }
 
 }  // namespace cb
@@ -793,7 +796,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(p.mb)) cols <<= 1;
   p.tmem_cols = cols;
-  const size_t stage = static_cast<size_t>(p.mb) * 128 + kATileBytes + (fmt == kFmtBf16 ? 0 : kCodeBytes + kMetaBytes);
+  const size_t stage = static_cast<size_t>(p.mb) * 128 + kATileBytes + (fmt == kFmtBf16 ? 0 : kCodeBytes + meta_bytes(fmt));
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SmemCtl);
   int stages = static_cast<int>(budget / stage);
   if (stages > 8) stages = 8;

@@ -12,7 +12,9 @@ enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 =
 static constexpr int kTileN = 128;       // output features per CTA (UMMA M)
 static constexpr int kBlockK = 64;       // K columns per stage (one 128-byte swizzle row)
 static constexpr int kCodeBytes = 4096;  // 128 x 64 x 4 bit
-static constexpr int kMetaBytes = 1024;
+static constexpr int kMetaBytes = 1024;       // affine4 / nvfp4: two 32-bit words per row
+static constexpr int kMetaBytesCubic = 2048;  // cubic4: four 32-bit words per row (the row's level table)
+__host__ __device__ constexpr int meta_bytes(int fmt) { return fmt == 0 ? kMetaBytesCubic : kMetaBytes; }
 static constexpr int kATileBytes = kTileN * kBlockK * 2;  // 16 KiB bf16
 static constexpr int kNumDequantWarps = 16;  // 4 per scheduler: the decode chains are latency-bound with fewer
 static constexpr int kThreads = (2 + kNumDequantWarps) * 32;
@@ -148,7 +150,7 @@ __device__ __forceinline__ void store_act4(const WqGemmParams& p, int m, int n_t
 // offset of activation feature j (0..63) of a tile inside a 128-float tile row: gate value there, up value 16 on
 __device__ __forceinline__ int act_gate_col(int j) { return ((j >> 4) << 5) + (j & 15); }
 
-// ---- packed bf16x2 decode ---------------------------------------------------
+// ---- packed bf16x2 decode (affine4, nvfp4) ---------------------------------
 // A 32-bit word holds 8 codes; nibble i (i < 4) is column 2i and nibble i + 4 is
 // column 2i + 1 of the 8-column chunk, so ONE mask pulls an adjacent column pair
 // into the two halves of a register:  ((w >> 4i) & 0x000F000F) | 0x43004300 is
@@ -194,19 +196,34 @@ __device__ __forceinline__ void decode8(uint32_t w, uint32_t c0, uint32_t c1, ui
 template <>
 __device__ __forceinline__ void decode8<kFmtBf16>(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t (&)[4]) {}
 
-// CUBIC4: c = n - 8;  w = c * (A + |c| * (B + |c| * C)),  A/B/C broadcast bf16x2
-template <>
-__device__ __forceinline__ void decode8<kFmtCubic4>(uint32_t w, uint32_t A, uint32_t B, uint32_t C,
-                                                    uint32_t (&out)[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t x = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;  // 128 + n
-    const uint32_t c = bf2_sub(x, 0x43084308u);                        // n - 8 (exact)
-    const uint32_t m = bf2_abs(c);                                     // |c| (a source modifier of the next fma)
-    uint32_t p = bf2_fma(m, C, B);
-    p = bf2_fma(m, p, A);
-    out[i] = bf2_mul(c, p);
-  }
+// CUBIC4 goes through a level table instead of arithmetic.  A Cubic weight is sign(c) * level[|c|] with eight
+// levels per (row, K group); the host stores them as bf16, rounded once from the fp32 curve
+//   level[m] = s t (a + t (b + t (1 - a - b))),  t = m / 7,
+// split into low bytes (words tl0 = levels 0..3, tl1 = levels 4..7) and high bytes (th0, th1).  A code word holds
+// eight codes in sign-magnitude form: nibble i carries |c_i| of column i in its low three bits (so that the
+// masked word IS a byte-permute selector), the sign of column i (i < 4) sits in bit 8 i + 7 and that of column
+// 4 + i in bit 8 i + 3 -- the spare top bits of the nibbles, placed where one mask (after one shift for the second
+// four) puts them on the sign bits of the looked-up high bytes.  13 integer instructions per eight weights
+// (mask, shift, four look-ups, three for the signs, four interleaves) against 28 for the arithmetic form, and the
+// weights are bit-exact roundings of the fp32 curve.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ void cubic_lut8(uint32_t w, const uint4& t, uint32_t (&out)[4]) {
+  const uint32_t m = w & 0x77777777u;       // selectors of columns 0..3 (low 16 bits are used by prmt)
+  const uint32_t mb = m >> 16;              // ... of columns 4..7
+  const uint32_t lo_a = prmt(t.x, t.y, m);
+  uint32_t hi_a = prmt(t.z, t.w, m);
+  const uint32_t lo_b = prmt(t.x, t.y, mb);
+  uint32_t hi_b = prmt(t.z, t.w, mb);
+  hi_a ^= w & 0x80808080u;
+  hi_b ^= (w << 4) & 0x80808080u;
+  out[0] = prmt(lo_a, hi_a, 0x5140u);       // {column 0, column 1} as a bf16 pair
+  out[1] = prmt(lo_a, hi_a, 0x7362u);
+  out[2] = prmt(lo_b, hi_b, 0x5140u);
+  out[3] = prmt(lo_b, hi_b, 0x7362u);
 }
 
 // AFFINE4: w = (n - 8) * scale + offset8   (offset8 = offset + 8 * scale, small in magnitude)

@@ -30,6 +30,7 @@
 // Every wait is bounded (ptx.cuh); on a timeout the CTA-wide abort flag makes every role fall through to the
 // common exit, which frees tensor memory and records a status word.
 #include "wq_gemm_common.cuh"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -43,7 +44,7 @@ static constexpr int kSkFirstDecodeWarp = 7;
 static constexpr int kSkThreads = (kSkFirstDecodeWarp + kSkDecodeWarps) * 32;   // 736
 static constexpr int kSkMaxAx = 6;
 static constexpr int kSkMaxC = 8;
-static constexpr int kSkCStageBytes = kCodeBytes + kMetaBytes;
+__host__ __device__ constexpr int sk_cstage_bytes(int fmt) { return kCodeBytes + meta_bytes(fmt); }
 
 // One contiguous run of k-blocks of one tile, as dealt to a CTA.
 struct SkSegment {
@@ -316,7 +317,9 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t ax_bytes = x_bytes + kATileBytes;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* c_ring = smem + static_cast<size_t>(p.ax_stages) * ax_bytes;
-  float* epi_scratch = reinterpret_cast<float*>(c_ring + (FMT == kFmtBf16 ? 0 : static_cast<size_t>(p.c_stages) * kSkCStageBytes));
+  constexpr uint32_t kMeta = static_cast<uint32_t>(meta_bytes(FMT));
+  constexpr uint32_t kCStage = kCodeBytes + kMeta;
+  float* epi_scratch = reinterpret_cast<float*>(c_ring + (FMT == kFmtBf16 ? 0 : static_cast<size_t>(p.c_stages) * kCStage));
   SkCtl* ctl = reinterpret_cast<SkCtl*>(reinterpret_cast<uint8_t*>(epi_scratch) + kSkEpiScratchBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -370,6 +373,11 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const uint32_t tmem_base = ctl->tmem_base;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
+  // Programmatic dependent launch: the set-up above and the first copies of the packed weights (which no kernel
+  // writes) may run while the previous kernel of the stream is still finishing; every role that reads activations,
+  // residuals, counters or a device work list, or writes results, waits for it first.
+  pdl_launch_dependents();
+  if (p.group_tiles) pdl_wait();            // the deal itself reads the work list written by the routing kernels
   SkIter it;
   it.init(p, cta);
   SkSegment seg;
@@ -379,6 +387,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
       if (FMT == kFmtBf16) tma_prefetch_desc(&tmap_w);
+      pdl_wait();
       bool ok = true;
       if (p.tp.mode & kTpGatherWait) {
         // the packed weights stream meanwhile (warp 2 does not wait): all-gather overlapped with weight traffic
@@ -420,14 +429,14 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint8_t* cbase = p.codes + static_cast<size_t>(c.expert) * p.group_code_stride +
                                static_cast<size_t>(c.n_tile) * p.k_blocks * kCodeBytes;
         const uint8_t* mbase = p.meta + static_cast<size_t>(c.expert) * p.group_meta_stride +
-                               static_cast<size_t>(c.n_tile) * p.meta_blocks * kMetaBytes;
+                               static_cast<size_t>(c.n_tile) * p.meta_blocks * kMeta;
         for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
           if (r.wraps && !mbar_wait_park(smem_u32(&ctl->c_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
-          const uint32_t dst = smem_u32(c_ring + static_cast<size_t>(r.s) * kSkCStageBytes);
+          const uint32_t dst = smem_u32(c_ring + static_cast<size_t>(r.s) * kCStage);
           const uint32_t bar = smem_u32(&ctl->c_full[r.s]);
-          mbar_expect_tx(bar, kSkCStageBytes);
+          mbar_expect_tx(bar, kCStage);
           bulk_g2s(dst, cbase + static_cast<size_t>(kb) * kCodeBytes, kCodeBytes, bar);
-          bulk_g2s(dst + kCodeBytes, mbase + static_cast<size_t>(kb >> p.meta_shift) * kMetaBytes, kMetaBytes, bar);
+          bulk_g2s(dst + kCodeBytes, mbase + static_cast<size_t>(kb >> p.meta_shift) * kMeta, kMeta, bar);
           r.advance(NC);
         }
       }
@@ -513,6 +522,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // All 640 threads execute every tail_bar() whatever happened before: work is switched off by `ok`, never
     // the control flow.
     auto tail_epilogue = [&](int seg_idx, bool ok) {
+      pdl_wait();                                             // long since satisfied; orders this thread's global accesses
       const int tt = threadIdx.x - kSkFirstEpiWarp * 32;      // 0..639
       const int nthr = (kSkEpiWarps + kSkDecodeWarps) * 32;
       const int buf = seg_idx & 1;
@@ -638,18 +648,18 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             const int ig = i_global + jj;
             if (!mbar_wait_park(smem_u32(&ctl->c_full[rc.s]), rc.wraps & 1u, abort_flag)) { ok = false; break; }
             CB_STAMP(r == 0 && ig < 64, ig * 8 + 2);
-            const uint8_t* pk = c_ring + static_cast<size_t>(rc.s) * kSkCStageBytes;
+            const uint8_t* pk = c_ring + static_cast<size_t>(rc.s) * kCStage;
             const uint4 w0 = *reinterpret_cast<const uint4*>(pk + code_off);
             const uint4 w1 = *reinterpret_cast<const uint4*>(pk + code_off + 128 * 16);
-            const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
-            // metadata words are bf16 pairs prepared on the host (see ops/wq_pack.py)
-            uint32_t m0, m1;
-            if (FMT == kFmtCubic4) {
-              m0 = meta[r];            // {A = s a / 7, B = s b / 49}: one scale group covers the whole k-block
-              m1 = meta[128 + r];      // {C = s (1 - a - b) / 343, -}
+            // metadata: Cubic = the row's level table (16 bytes; one scale group covers the whole k-block); the other
+            // formats = bf16 pairs {scale, offset} (or the two 16-column block scales) of each 32-column half
+            uint4 t = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (FMT == kFmtCubic4) {
+              t = *reinterpret_cast<const uint4*>(pk + kCodeBytes + code_off);
             } else {
-              m0 = meta[r];            // {scale, offset} (or the two 16-column block scales) of half 0
-              m1 = meta[128 + r];      // ... of half 1
+              const uint32_t* meta = reinterpret_cast<const uint32_t*>(pk + kCodeBytes);
+              t.x = meta[r];
+              t.y = meta[128 + r];
             }
             // the codes and metadata are in registers: hand the slot back to the copy warp right away
             __syncwarp();
@@ -658,29 +668,27 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const uint4 words = h ? w1 : w0;
-              uint32_t c0, c1, c2;
-              if (FMT == kFmtCubic4) {
-                c0 = bf2_dup(m0);
-                c1 = bf2_dup_hi(m0);
-                c2 = bf2_dup(m1);
-              } else {
-                const uint32_t so = h ? m1 : m0;
-                c0 = bf2_dup(so);
-                c1 = bf2_dup_hi(so);
-                c2 = 0;
-              }
               uint32_t o[4][4];
-              if (FMT == kFmtNvfp4) {
-                // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
-                decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
-                decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
-                decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
-                decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+              if constexpr (FMT == kFmtCubic4) {
+                cubic_lut8(words.x, t, o[0]);
+                cubic_lut8(words.y, t, o[1]);
+                cubic_lut8(words.z, t, o[2]);
+                cubic_lut8(words.w, t, o[3]);
               } else {
-                decode8<FMT>(words.x, c0, c1, c2, o[0]);
-                decode8<FMT>(words.y, c0, c1, c2, o[1]);
-                decode8<FMT>(words.z, c0, c1, c2, o[2]);
-                decode8<FMT>(words.w, c0, c1, c2, o[3]);
+                const uint32_t so = h ? t.y : t.x;
+                const uint32_t c0 = bf2_dup(so), c1 = bf2_dup_hi(so);
+                if constexpr (FMT == kFmtNvfp4) {
+                  // columns 32h + 8j: the 16-column block scale is the low half for j < 2, the high half after
+                  decode8<FMT>(words.x, c0, 0u, 0u, o[0]);
+                  decode8<FMT>(words.y, c0, 0u, 0u, o[1]);
+                  decode8<FMT>(words.z, c1, 0u, 0u, o[2]);
+                  decode8<FMT>(words.w, c1, 0u, 0u, o[3]);
+                } else {
+                  decode8<FMT>(words.x, c0, c1, 0u, o[0]);
+                  decode8<FMT>(words.y, c0, c1, 0u, o[1]);
+                  decode8<FMT>(words.z, c0, c1, 0u, o[2]);
+                  decode8<FMT>(words.w, c0, c1, 0u, o[3]);
+                }
               }
               if (h == 0) {
                 // the arithmetic above ran while the slot may still be read by MMAs; only the stores wait for it
@@ -716,6 +724,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int quad = warp & 3;                                 // TMEM lane quadrant this warp may read
       const int et = threadIdx.x - kSkFirstEpiWarp * 32;         // 0..127
       int seg_idx = 0;
+      pdl_wait();
       while (it.next(p, cta, grid, seg)) {
         if (!it.has_more(p)) {
           tail_epilogue(seg_idx, true);
@@ -856,8 +865,8 @@ static int launch_sk_fmt(const CUtensorMap& tx, const CUtensorMap& tw, const WqG
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
-  wq_gemm_sk_kernel<FMT, false><<<grid, kSkThreads, smem, stream>>>(tx, tw, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(wq_gemm_sk_kernel<FMT, false>, dim3(static_cast<unsigned>(grid)), dim3(kSkThreads), smem,
+                                 stream, tx, tw, p));
 }
 
 // CTA pairs: `grid` CTAs (even) launched as clusters of two.
@@ -872,19 +881,8 @@ static int launch_sk_pair_fmt(const CUtensorMap& tx, const CUtensorMap& tw, cons
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kSkThreads, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, wq_gemm_sk_kernel<FMT, true>, tx, tw, p));
+  return static_cast<int>(launch(wq_gemm_sk_kernel<FMT, true>, dim3(static_cast<unsigned>(grid)), dim3(kSkThreads), smem,
+                                 stream, dim3(2, 1, 1), tx, tw, p));
 }
 
 // How many CTA pairs can be resident at once (both CTAs of a cluster sit in one GPC, so a GPC with an odd number of
@@ -996,6 +994,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
 
   const size_t ax = static_cast<size_t>(p.pair ? p.mb >> 1 : p.mb) * 128 + kATileBytes;
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SkCtl) - kSkEpiScratchBytes;
+  const size_t kSkCStageBytes = static_cast<size_t>(sk_cstage_bytes(fmt));
   int S, NC;
   if (fmt == kFmtBf16) {
     NC = 0;

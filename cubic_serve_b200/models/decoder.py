@@ -414,8 +414,9 @@ class DecoderRunner:
     def forward_logits(self, b: StepBatch, hidden: torch.Tensor, logits_out: torch.Tensor) -> torch.Tensor:
         """Final norm + lm_head for the selected rows -> bf16 logits ``[R, V(/tp)]``."""
         R = b.num_logit_rows
-        rows = torch.index_select(hidden, 0, b.logit_rows[:R])
-        xn = K.rmsnorm(rows, self.w.final_norm, self.cfg.rms_eps, zero_centered=self.cfg.zero_centered_norm)
+        # the normed-activation buffer is free once the last layer has run: it takes the gathered + normed rows
+        xn = K.rmsnorm_rows(hidden, b.logit_rows[:R], self.w.final_norm, self.cfg.rms_eps, out=self.x[:R],
+                            zero_centered=self.cfg.zero_centered_norm)
         K.wq_gemm(xn, self.w.lm_head, out=logits_out[:R], ws=self.ws)
         self.launches_per_step += 2
         return logits_out[:R]

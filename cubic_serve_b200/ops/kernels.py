@@ -256,6 +256,20 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
+def rmsnorm_rows(x: torch.Tensor, rows: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor | None = None,
+                 zero_centered: bool = False) -> torch.Tensor:
+    """``out[i] = rmsnorm(x[rows[i]])`` (``rows`` int64): the final norm over the rows whose logits are wanted, with the
+    row gather done by the kernel's own loads."""
+    assert rows.dtype == torch.int64 and x.stride(1) == 1 and x.stride(0) == x.shape[1]
+    n, h = rows.numel(), x.shape[1]
+    if out is None:
+        out = torch.empty((n, h), dtype=x.dtype, device=x.device)
+    code = native.lib().cb_rmsnorm_rows(x.data_ptr(), rows.data_ptr(), weight.data_ptr(), out.data_ptr(), n, h,
+                                        float(eps), int(zero_centered), _stream())
+    native.check(code, "cb_rmsnorm_rows")
+    return out
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     rows, two_i = gate_up.shape
     i = two_i // 2

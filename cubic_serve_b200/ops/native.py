@@ -160,6 +160,8 @@ def lib() -> ctypes.CDLL:
                         ) from exc
             _lib = ctypes.CDLL(str(LIB_PATH))
             _declare(_lib)
+            if os.environ.get("CUBIC_SERVE_PDL", "1") == "0":
+                _lib.cb_set_pdl(0)       # programmatic dependent launch of the kernels off (csrc/launch.cuh)
         return _lib
 
 
@@ -171,6 +173,12 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_workspace_bytes.restype = ll
     l.cb_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i, i, f, i, vp]
     l.cb_rmsnorm.restype = i
+    l.cb_rmsnorm_rows.argtypes = [vp, vp, vp, vp, i, i, f, i, vp]
+    l.cb_rmsnorm_rows.restype = i
+    l.cb_set_pdl.argtypes = [i]
+    l.cb_set_pdl.restype = None
+    l.cb_pdl_enabled.argtypes = []
+    l.cb_pdl_enabled.restype = i
     l.cb_swiglu.argtypes = [vp, vp, i, i, vp]
     l.cb_swiglu.restype = i
     l.cb_embedding.argtypes = [vp, vp, vp, i, i, i, i, vp]

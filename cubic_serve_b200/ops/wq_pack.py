@@ -6,10 +6,16 @@ the sm_100a kernel in ``csrc/wq_gemm.cu``:
 
 * ``codes``: ``uint8 [n_tiles, k_blocks, 2, 128, 16]`` -- per (128-row tile,
   64-column k-block) one contiguous 4 KiB block that a single bulk copy moves;
-  32-bit word ``j`` of row ``r``, half ``h`` covers columns ``64*kb + 32*h + 8*j .. +7``;
-  its nibble ``i`` (``i < 4``) is column ``2i`` of those, nibble ``i + 4`` is column
-  ``2i + 1`` (an adjacent column pair comes out with one mask), offset-binary;
-* ``meta``: ``uint8 [n_tiles, meta_blocks, 2, 128, 4]`` -- 1 KiB per block.
+  32-bit word ``j`` of row ``r``, half ``h`` covers columns ``64*kb + 32*h + 8*j .. +7``.
+  Affine / NVFP4: nibble ``i`` (``i < 4``) is column ``2i`` of those, nibble ``i + 4`` is column
+  ``2i + 1`` (an adjacent column pair comes out with one mask), offset-binary.
+  Cubic: sign-magnitude, nibble ``i`` holds ``|c|`` of column ``i`` in its low three bits, the sign of column
+  ``i < 4`` is bit ``8i + 7`` of the word and that of column ``4 + i`` bit ``8i + 3`` (``cubic_lut8`` in
+  ``csrc/wq_gemm_common.cuh`` turns such a word into eight bf16 weights with byte permutes);
+* ``meta``: affine / NVFP4 ``uint8 [n_tiles, meta_blocks, 2, 128, 4]`` -- 1 KiB per block; Cubic
+  ``uint8 [n_tiles, groups, 1, 128, 16]`` -- 2 KiB per K group: per row the eight levels
+  ``s t (a + t (b + t (1 - a - b)))``, ``t = m / 7``, evaluated in fp32 and rounded ONCE to bf16 (the reference's
+  decode contract), stored as low bytes of levels 0..3, 4..7, then high bytes of levels 0..3, 4..7.
 
 All functions are pure tensor code and run on CPU or GPU.
 """
@@ -80,6 +86,50 @@ def _pad_rows(t: torch.Tensor, rows: int, value) -> torch.Tensor:
     return torch.cat([t, pad], 0)
 
 
+def _tile_words(words: torch.Tensor) -> torch.Tensor:
+    """``int32 [N_pad, K / 8]`` code words (eight columns each) -> tiled bytes ``[nt, kb, 2, 128, 16]``."""
+    n, w = words.shape
+    nt, kb = n // TILE_N, w // 8
+    v = words.reshape(nt, TILE_N, kb, 2, 4).permute(0, 2, 3, 1, 4).contiguous()      # [nt, kb, h, r, j]
+    return v.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 16)
+
+
+def _untile_words(codes: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``_tile_words``: tiled bytes -> ``int32 [N_pad, K / 8]`` code words."""
+    nt, kb = codes.shape[0], codes.shape[1]
+    v = codes.contiguous().view(torch.int32).reshape(nt, kb, 2, TILE_N, 4).permute(0, 3, 1, 2, 4)
+    return v.reshape(nt * TILE_N, kb * 8)
+
+
+def cubic_code_words(codes: torch.Tensor) -> torch.Tensor:
+    """Signed 4-bit codes ``[N, K]`` (reserved most-negative code already 0) -> sign-magnitude words ``int32 [N, K/8]``."""
+    n, k = codes.shape
+    c = codes.to(torch.int64).reshape(n, k // 8, 8)
+    mag = c.abs().clamp(max=7)
+    neg = (c < 0).to(torch.int64)
+    i = torch.arange(8, device=codes.device)
+    sign_bit = torch.where(i < 4, 8 * i + 7, 8 * (i - 4) + 3)
+    words = ((mag << (4 * i)) | (neg << sign_bit)).sum(-1)
+    return torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+
+
+def cubic_codes_from_words(words: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``cubic_code_words``: ``int32 [N, K/8]`` -> signed codes ``int64 [N, K]``."""
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    i = torch.arange(8, device=words.device)
+    sign_bit = torch.where(i < 4, 8 * i + 7, 8 * (i - 4) + 3)
+    mag = (w.unsqueeze(-1) >> (4 * i)) & 7
+    neg = (w.unsqueeze(-1) >> sign_bit) & 1
+    return (mag * (1 - 2 * neg)).reshape(words.shape[0], -1)
+
+
+def cubic_levels(scale: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """The eight non-negative levels of every (row, group): fp32 curve rounded once to bf16, ``[..., 8]``."""
+    t = (torch.arange(8, device=scale.device, dtype=torch.float32) / 7.0)
+    s, a, b = scale.float().unsqueeze(-1), a.float().unsqueeze(-1), b.float().unsqueeze(-1)
+    return (s * t * (a + t * (b + t * (1.0 - a - b)))).to(torch.bfloat16)
+
+
 def pack_cubic4(codes: torch.Tensor, scale: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
                 group_k: int) -> PackedWeight:
     """Signed 4-bit Cubic codes ``int8 [N, K]`` (reserved code already 0) + variant-A metadata."""
@@ -87,18 +137,16 @@ def pack_cubic4(codes: torch.Tensor, scale: torch.Tensor, a: torch.Tensor, b: to
     if k % BLOCK_K or group_k % BLOCK_K:
         raise ValueError("K and the Cubic group must be multiples of 64")
     n_pad = -(-n // TILE_N) * TILE_N
-    nib = _pad_rows((codes.to(torch.int16) + 8).to(torch.uint8), n_pad, 8)
+    words = cubic_code_words(_pad_rows(codes.to(torch.int16), n_pad, 0))
     groups = -(-k // group_k)
     sc = _pad_rows(scale.float().reshape(n, groups), n_pad, 0.0)
     af = _pad_rows(a.float().reshape(n, groups), n_pad, 0.0)
     bf = _pad_rows(b.float().reshape(n, groups), n_pad, 0.0)
-    # polynomial in the integer code c: w = c * (A + |c| * (B + |c| * C))
-    w0 = _bf16_pair_words(sc * af / 7.0, sc * bf / 49.0)
-    w1 = _bf16_pair_words(sc * (1.0 - af - bf) / 343.0, torch.zeros_like(sc))
-    words = torch.stack([w0, w1], 0)                                # [2, N, G]
+    lv = cubic_levels(sc, af, bf).contiguous().view(torch.uint8).reshape(n_pad, groups, 8, 2)   # [.., level, lo / hi byte]
+    table = torch.cat([lv[..., 0], lv[..., 1]], -1)                                 # [N, G, 16]: 8 low bytes, 8 high bytes
     nt = n_pad // TILE_N
-    meta = words.reshape(2, nt, TILE_N, groups).permute(1, 3, 0, 2).contiguous()  # [nt, G, 2, 128]
-    return PackedWeight(FMT_CUBIC4, n, k, group_k, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, groups, 2, TILE_N, 4))
+    meta = table.reshape(nt, TILE_N, groups, 16).permute(0, 2, 1, 3).contiguous().reshape(nt, groups, 1, TILE_N, 16)
+    return PackedWeight(FMT_CUBIC4, n, k, group_k, _tile_words(words), meta)
 
 
 def pack_affine4(q: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, group_k: int) -> PackedWeight:
@@ -206,12 +254,21 @@ def swiglu_interleave(pw: PackedWeight, stacked: bool = False) -> PackedWeight:
 def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
     """Oracle: rebuild the fp32 ``[N, K]`` matrix a PackedWeight represents, from its packed bytes (CPU or GPU).
 
-    Uses the bf16-rounded metadata exactly as stored but evaluates in fp32, i.e. it is
-    the value the kernel approximates with packed bf16 arithmetic.
+    Cubic weights are exactly the bf16 levels the kernel looks up; for the other formats the bf16-rounded metadata
+    is used as stored but evaluated in fp32, i.e. the value the kernel approximates with packed bf16 arithmetic.
     """
     if pw.fmt == FMT_BF16:
         return pw.codes.float()
     nt = pw.codes.shape[0]
+    if pw.fmt == FMT_CUBIC4:
+        c = cubic_codes_from_words(_untile_words(pw.codes))                        # [N_pad, K]
+        n_pad, k = c.shape
+        g = pw.meta.shape[1]
+        table = pw.meta.reshape(nt, g, TILE_N, 16).permute(0, 2, 1, 3).reshape(n_pad, g, 16)
+        lv = torch.stack([table[..., :8], table[..., 8:]], -1).contiguous().view(torch.bfloat16).reshape(n_pad, g, 8).float()
+        col = (torch.arange(k, device=c.device) // pw.group_k).expand(n_pad, k)
+        mag = lv[torch.arange(n_pad, device=c.device).unsqueeze(1), col, c.abs()]
+        return (mag * torch.sign(c).float())[: pw.n]
     nib = _untile_nibbles(pw.codes)
     n_pad, k = nib.shape
     words = pw.meta.reshape(nt, -1, 2, TILE_N, 4).view(torch.int32).reshape(nt, -1, 2, TILE_N)
@@ -220,14 +277,6 @@ def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
         pair = w.contiguous().view(torch.bfloat16).reshape(*w.shape, 2).float()
         return pair[..., 0], pair[..., 1]
 
-    if pw.fmt == FMT_CUBIC4:
-        g = words.shape[1]
-        A, B = halves(words[:, :, 0].permute(0, 2, 1).reshape(n_pad, g))
-        C, _ = halves(words[:, :, 1].permute(0, 2, 1).reshape(n_pad, g))
-        col = torch.arange(k, device=nib.device) // pw.group_k
-        c = nib - 8.0
-        m = c.abs()
-        return (c * (A[:, col] + m * (B[:, col] + m * C[:, col])))[: pw.n]
     lo, hi = halves(words.permute(0, 3, 1, 2).reshape(n_pad, -1))   # [N, K/32] each
     if pw.fmt == FMT_AFFINE4:
         col = torch.arange(k, device=nib.device) // 32

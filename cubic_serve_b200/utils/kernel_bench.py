@@ -75,14 +75,11 @@ def timeit_graph(fn, flush: torch.Tensor, launches: int = 10, repeats: int = 3) 
 
 
 def random_cubic_weight(n: int, k: int, group: int = 128) -> wq_pack.PackedWeight:
-    """Random codes with unit-ish curve metadata directly in packed form (no quantizer pass)."""
-    nt, kb, g = (n + 127) // 128, k // 64, k // group
-    codes = torch.randint(0, 256, (nt, kb, 2, 128, 16), dtype=torch.uint8, device=DEV)
-    meta = torch.zeros(nt, g, 2, 128, dtype=torch.int32, device=DEV)
-    s, a, b = 0.02, 0.75, 0.25   # scale and curve -> bf16 polynomial coefficients A, B, C
-    meta[:, :, 0] = torch.tensor([s * a / 7, s * b / 49], dtype=torch.bfloat16, device=DEV).view(torch.int32)
-    meta[:, :, 1] = torch.tensor([s * (1 - a - b) / 343, 0.0], dtype=torch.bfloat16, device=DEV).view(torch.int32)
-    return wq_pack.PackedWeight(wq_pack.FMT_CUBIC4, n, k, group, codes, meta.view(torch.uint8).reshape(nt, g, 2, 128, 4))
+    """Random codes with unit-ish curve metadata, packed without a quantizer pass."""
+    codes = torch.randint(-7, 8, (n, k), dtype=torch.int8, device=DEV)
+    g = k // group
+    full = lambda v: torch.full((n, g), v, device=DEV)
+    return wq_pack.pack_cubic4(codes, full(0.02), full(0.75), full(0.25), group)
 
 
 def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str = "cubic4",

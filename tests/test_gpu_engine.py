@@ -51,6 +51,28 @@ def test_overlapped_decode_matches_stepwise_on_device():
     assert _engine(True)[0].generate(prompts[:4], sp2) == _engine(False)[0].generate(prompts[:4], sp2)
 
 
+def test_programmatic_dependent_launch_changes_no_token():
+    """Kernels may start while their predecessor is still running (csrc/launch.cuh); each waits for it before it
+    touches dependent memory.  Eager steps and graph replays with the overlap on give the tokens of a run with it off."""
+    from cubic_serve_b200.ops import native
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    lib = native.lib()
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (17, 40, 33, 64, 5, 9, 21, 50, 31, 12)]
+    sp = SamplingParams(max_tokens=32, ignore_eos=True)
+    try:
+        lib.cb_set_pdl(0)
+        want = _engine(True)[0].generate(prompts, sp)
+        lib.cb_set_pdl(1)
+        assert lib.cb_pdl_enabled() == 1
+        for _ in range(3):
+            eng, _, runner = _engine(True)
+            assert eng.generate(prompts, sp) == want
+            runner.ws.check_status()
+    finally:
+        lib.cb_set_pdl(1)
+
+
 def test_preempted_requests_read_their_own_pages_after_readmission():
     """A pool too small for all requests: some are preempted, re-admitted (often into their old slot, with other
     pages) and must produce the tokens of an unpreempted run.  A stale page-table row would make attention read
@@ -124,7 +146,7 @@ def test_thinking_budget_state_machine_and_engine():
         runner.enable_reasoning_budget(2047, [2046, 2047])
         ex = GpuExecutor(runner, max_rows=16, max_prefill_tokens=512, max_model_len=256)
         ex.capture_decode_graphs()
-        eng = LLMEngine(ex, pool_pages, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
+        eng = LLMEngine(ex, 256, SchedulerConfig(max_running_requests=16, max_model_len=256, max_batched_tokens=512,
                                                  enable_prefix_cache=False))
         prompts = [np.random.default_rng(i).integers(0, 2000, 20 + i).tolist() for i in range(3)]
         ids = [eng.add_request(p, SamplingParams(max_tokens=14, ignore_eos=True,

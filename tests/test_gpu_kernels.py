@@ -37,7 +37,8 @@ def _cubic_weight(n, k, seed=0, group=128):
 def test_wq_gemm_cubic4(m, n, k, splits):
     K = _k()
     pw, dense = _cubic_weight(n, k, seed=m + n)
-    assert _rel(wq_pack.unpack_to_dense(pw), dense) < 4e-3      # bf16 curve coefficients
+    # the packed levels are the fp32 decode rounded once to bf16 (the reference's contract), bit for bit
+    assert torch.equal(wq_pack.unpack_to_dense(pw), dense.to(torch.bfloat16).float())
     x = (torch.randn(m, k, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16)
     ref = x.float() @ dense.t()
     y = K.wq_gemm(x.to(DEV), pw.to(DEV), splits=splits)
@@ -45,6 +46,8 @@ def test_wq_gemm_cubic4(m, n, k, splits):
     K.workspace(y.device).check_status()
     assert y.shape == (m, n)
     assert _rel(y.cpu(), ref) < 1e-2
+    # against the same bf16 weights the kernel decodes, only the fp32 accumulation order and the output rounding differ
+    assert _rel(y.cpu(), x.float() @ wq_pack.unpack_to_dense(pw).t()) < 3e-3
     # repeat: split-K counters must have been restored
     y2 = K.wq_gemm(x.to(DEV), pw.to(DEV), splits=splits)
     assert torch.equal(y, y2)
