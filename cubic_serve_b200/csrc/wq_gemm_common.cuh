@@ -88,12 +88,12 @@ struct WqGemmParams {
 };
 
 // Pipeline timeline of the first CTA(s) of a launch, for development builds only (-DCB_KERNEL_TRACE): clock64
-// stamps into `p.trace` ([row][8] 64-bit words).  The product build compiles the stamps and the hook out.
+// stamps into `p.trace` ([row][8] 64-bit words; rows 256 + CTA hold every CTA's wall-clock entry / exit).  The product build compiles the stamps and the hook out.
 #ifdef CB_KERNEL_TRACE
 #define CB_TRACE_ONLY(...) __VA_ARGS__
 #define CB_STAMP(cond, idx) do { if (trace && (cond)) trace[idx] = clock64(); } while (0)
 #define CB_WALL_STAMP(slot) do { if (p.trace && threadIdx.x == 0) { unsigned long long t_; \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[blockIdx.x * 8 + (slot)] = t_; } } while (0)
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.trace[(256 + blockIdx.x) * 8 + (slot)] = t_; } } while (0)
 #else
 #define CB_TRACE_ONLY(...)
 #define CB_STAMP(cond, idx) do { } while (0)
@@ -119,6 +119,19 @@ __device__ __forceinline__ bool wait_counter(const uint32_t* p, uint32_t target,
     }
   }
   return true;
+}
+
+// The same for a counter that CTAs of THIS kernel raise (device scope), reaching at least `target`.
+__device__ __forceinline__ bool wait_counter_gpu(const uint32_t* p, uint32_t target, volatile uint32_t* abort_flag) {
+  const long long t0 = clock64();
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (v >= target) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) return false;
+    __nanosleep(200);
+  }
 }
 
 // SwiGLU on a pair of accumulators, with the rounding points of the unfused path (the projection's output is

@@ -69,6 +69,7 @@ struct __align__(8) SkCtl {
   // waits for the end of the CTA, where all 20 epilogue + decode warps do it (at most two: the CTA's first run
   // and the run before its whole tiles)
   uint32_t deferred_count;
+  uint32_t deferred_next;        // fix-ups [0, deferred_next) are done (sliced form: by the epilogue warps, in the background)
   SkSegment deferred[2];
 };
 
@@ -224,39 +225,66 @@ __device__ __forceinline__ void sk_store4(const WqGemmParams& p, int m, int n0, 
 // and the up float4 of every part.  Out of line: it runs once per streamed tile and its registers stay out of the
 // kernel's allocation.
 __device__ __noinline__ void sk_reduce_write_act(const WqGemmParams& p, const float* slots, int parts, int own_part,
-                                                 const float* own, int tid, int nthreads, int m0, int rows_here, int n_tile) {
+                                                 const float* own, int tid, int nthreads, int m0, int row_lo, int row_hi,
+                                                 int n_tile) {
   const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
   const size_t stride = static_cast<size_t>(2) << p.pair;      // slots between consecutive parts of a tile
-  for (int idx = tid; idx < rows_here * 16; idx += nthreads) {
-    const int mm = idx >> 4, j0 = (idx & 15) * 4;
-    const int e = mm * kTileN + act_gate_col(j0);
-    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+  constexpr int kB = 1;                                        // items per thread and round: 2 loads of 16 bytes per part,
+                                                               // four parts in flight (the sum stays in part order)
+  const int items = (row_hi - row_lo) * 16;
+  for (int base = tid; base < items; base += nthreads * kB) {
+    float4 g[kB], u[kB];
+    int e[kB];
+#pragma unroll
+    for (int b = 0; b < kB; ++b) {
+      const int idx = base + b * nthreads;
+      const int safe = idx < items ? idx : tid;            // out-of-range slots re-read a valid item, never stored
+      e[b] = (row_lo + (safe >> 4)) * kTileN + act_gate_col((safe & 15) * 4);
+      g[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+      u[b] = g[b];
+    }
+#pragma unroll 4
     for (int sp = 0; sp < parts; ++sp) {
-      float4 a, b;
+      float4 a[kB], c[kB];
       if (sp == own_part) {
-        a = *reinterpret_cast<const float4*>(own + e);
-        b = *reinterpret_cast<const float4*>(own + e + 16);
+#pragma unroll
+        for (int b = 0; b < kB; ++b) {
+          a[b] = *reinterpret_cast<const float4*>(own + e[b]);
+          c[b] = *reinterpret_cast<const float4*>(own + e[b] + 16);
+        }
       } else {
         const float* src = slots + (static_cast<size_t>(sp) * stride + (sp == 0 ? 1 : 0)) * part_elems;
-        a = __ldcg(reinterpret_cast<const float4*>(src + e));
-        b = __ldcg(reinterpret_cast<const float4*>(src + e + 16));
+#pragma unroll
+        for (int b = 0; b < kB; ++b) {
+          a[b] = __ldcg(reinterpret_cast<const float4*>(src + e[b]));
+          c[b] = __ldcg(reinterpret_cast<const float4*>(src + e[b] + 16));
+        }
       }
-      g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-      u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+#pragma unroll
+      for (int b = 0; b < kB; ++b) {
+        g[b].x += a[b].x; g[b].y += a[b].y; g[b].z += a[b].z; g[b].w += a[b].w;
+        u[b].x += c[b].x; u[b].y += c[b].y; u[b].z += c[b].z; u[b].w += c[b].w;
+      }
     }
-    g.x *= p.alpha; g.y *= p.alpha; g.z *= p.alpha; g.w *= p.alpha;
-    u.x *= p.alpha; u.y *= p.alpha; u.z *= p.alpha; u.w *= p.alpha;
-    store_act4(p, m0 + mm, n_tile, j0, g, u);
+#pragma unroll
+    for (int b = 0; b < kB; ++b) {
+      const int idx = base + b * nthreads;
+      if (idx < items) {
+        g[b].x *= p.alpha; g[b].y *= p.alpha; g[b].z *= p.alpha; g[b].w *= p.alpha;
+        u[b].x *= p.alpha; u[b].y *= p.alpha; u[b].z *= p.alpha; u[b].w *= p.alpha;
+        store_act4(p, m0 + row_lo + (idx >> 4), n_tile, (idx & 15) * 4, g[b], u[b]);
+      }
+    }
   }
 }
 
-// Fix-up of a streamed tile by the last CTA to arrive: sum the fp32 partials of all parts IN PART ORDER
-// (bit-identical whichever CTA happens to be last) and write the tile.  `own` (optional) is this CTA's own part
+// Fix-up of rows [row_lo, row_hi) of a streamed tile: sum the fp32 partials of all parts IN PART ORDER (bit-identical
+// whoever does it) and write those rows.  `own` (optional) is this CTA's own part
 // still in shared memory, read instead of its copy in L2.  kBatch items per thread are in flight at once: the
 // partials come from L2 at ~1 k cycles per round trip, so the loop is latency bound without batching.
-template <int kBatch>
+template <int kBatch, int kPartUnroll>
 __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkSegment& seg, int unit, int tid,
-                                                int nthreads, int m0, int rows_here, int n_base, const float* own) {
+                                                int nthreads, int m0, int row_lo, int row_hi, int n_base, const float* own) {
   const size_t part_elems = static_cast<size_t>(p.mb) * kTileN;
   const size_t stride = static_cast<size_t>(2) << p.pair;      // slots between consecutive parts (CTAs, or pairs of CTAs)
   const int g_first = unit - (seg.part << p.pair);             // the CTA (of this rank) that holds part 0
@@ -264,10 +292,10 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
   const int own_part = own ? seg.part : -1;
   const float* slots = p.workspace + static_cast<size_t>(g_first) * 2 * part_elems;   // part q > 0 at + q * stride * part_elems
   if (p.swiglu) {
-    sk_reduce_write_act(p, slots, parts, own_part, own, tid, nthreads, m0, rows_here, n_base / kTileN);
+    sk_reduce_write_act(p, slots, parts, own_part, own, tid, nthreads, m0, row_lo, row_hi, n_base / kTileN);
     return;
   }
-  const int items = rows_here * (kTileN / 4);
+  const int items = (row_hi - row_lo) * (kTileN / 4);
   for (int base = tid; base < items; base += nthreads * kBatch) {
     float4 acc[kBatch];
     int e[kBatch];
@@ -275,12 +303,13 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
     for (int b = 0; b < kBatch; ++b) {
       const int idx = base + b * nthreads;
       const int safe = idx < items ? idx : tid;            // out-of-range slots re-read a valid item, never stored
-      e[b] = (safe >> 5) * kTileN + (safe & 31) * 4;
+      e[b] = (row_lo + (safe >> 5)) * kTileN + (safe & 31) * 4;
       acc[b] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     // the test on the part is uniform over the CTA and sits OUTSIDE the batch loop, so the kBatch loads of a
-    // part are issued back to back; unrolling by two lets the next part's loads start under this part's adds
-#pragma unroll 2
+    // part are issued back to back; unrolling over the parts lets the loads of several parts be in flight at once
+    // (the sum stays in part order)
+#pragma unroll kPartUnroll
     for (int sp = 0; sp < parts; ++sp) {
       float4 v[kBatch];
       if (sp == own_part) {
@@ -297,7 +326,7 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
 #pragma unroll
     for (int b = 0; b < kBatch; ++b) {
       const int idx = base + b * nthreads;
-      if (idx < items) sk_store4(p, m0 + (idx >> 5), n_base + (idx & 31) * 4, acc[b]);
+      if (idx < items) sk_store4(p, m0 + row_lo + (idx >> 5), n_base + (idx & 31) * 4, acc[b]);
     }
   }
 }
@@ -355,6 +384,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     ctl->abort_flag = 0;
     ctl->is_last = 0;
     ctl->deferred_count = 0;
+    ctl->deferred_next = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -396,11 +426,14 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
       const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? static_cast<uint32_t>(kATileBytes) : 0u);
       SkRing r;
+      CB_TRACE_ONLY(int ti = 0;)
       while (ok && it.next(p, cta, grid, seg)) {
         const SkCoords c = sk_coords(p, seg.tile, rank);
         const int w_row = c.expert * p.N + c.n_tile * kTileN;   // bf16 weights: experts stacked as [E * N, K]
         for (int kb = seg.kb_lo; kb < seg.kb_hi; ++kb) {
           if (r.wraps && !mbar_wait_park(smem_u32(&ctl->ax_empty[r.s]), (r.wraps - 1u) & 1u, abort_flag)) { ok = false; break; }
+          CB_STAMP(ti < 64, ti * 8 + 0);
+          CB_TRACE_ONLY(++ti;)
           uint8_t* st = smem + static_cast<size_t>(r.s) * ax_bytes;
           const uint32_t bar = smem_u32(&ctl->full[r.s]);
           if (PAIR) {
@@ -521,6 +554,10 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // of the partial), and a last arriver reduces with 640 threads, reading its own part from shared memory.
     // All 640 threads execute every tail_bar() whatever happened before: work is switched off by `ok`, never
     // the control flow.
+    // Streamed tiles are finished by ALL their contributors, each summing its share of the rows at the end of its CTA,
+    // instead of by the last contributor alone (15 us of serial tail on a third of the CTAs at 256 batch rows).
+    // Rows pushed to other ranks keep the single finisher: their arrival counters are raised once per tile.
+    const bool sliced = !(p.tp.mode & kTpScatterPush);
     auto tail_epilogue = [&](int seg_idx, bool ok) {
       pdl_wait();                                             // long since satisfied; orders this thread's global accesses
       const int tt = threadIdx.x - kSkFirstEpiWarp * 32;      // 0..639
@@ -573,8 +610,14 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           uint32_t last = 0;
           if (ok) {
             const uint32_t prev = atomicAdd(&p.counters[tile_id], 1u);
-            last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
-            if (last) p.counters[tile_id] = 0;
+            if (sliced) {
+              // every contributor sums its own share of the rows further down (SkCtl::deferred)
+              ctl->deferred[ctl->deferred_count] = seg;
+              ctl->deferred_count = ctl->deferred_count + 1;
+            } else {
+              last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
+              if (last) p.counters[tile_id] = 0;
+            }
           }
           ctl->is_last = last;
         }
@@ -582,7 +625,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (ctl->is_last && !*abort_flag) {
           __threadfence();
           finalized = true;
-          sk_reduce_write<4>(p, seg, unit, tt, nthr, m0, rows_here, n_base, stg);
+          sk_reduce_write<4, 2>(p, seg, unit, tt, nthr, m0, 0, rows_here, n_base, stg);
         }
       }
       if (p.tp.mode & kTpScatterPush) {
@@ -596,15 +639,35 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             red_relaxed_sys_add(p.tp.rs_flag[o] + p.tp.rank, 1u);
         }
       }
-      // fix-ups deferred by the earlier segments of this CTA (see SkCtl::deferred), now with 640 threads
+      // fix-ups deferred by the segments of this CTA (see SkCtl::deferred), now with 640 threads.  Sliced form:
+      // this CTA sums ITS share of the rows of every streamed tile it contributed to, once all parts of the tile
+      // have landed (they were written long ago as a rule: streamed runs come first in every CTA's deal); the
+      // arrival counter counts the parts, then the finished shares, and the last share puts it back to zero.
       tail_bar();
       const uint32_t n_def = ctl->deferred_count;
-      for (uint32_t di = 0; di < n_def; ++di) {
+      for (uint32_t di = ctl->deferred_next; di < n_def; ++di) {
         const SkSegment ds = ctl->deferred[di];
         const SkCoords c = sk_coords(p, ds.tile, rank);
+        int row_lo = 0, row_hi = c.rows;
+        if (sliced) {
+          row_lo = c.rows * ds.part / ds.parts;
+          row_hi = c.rows * (ds.part + 1) / ds.parts;
+          if (tt == 0 && !wait_counter_gpu(&p.counters[c.tile_id], static_cast<uint32_t>(ds.parts), abort_flag)) *abort_flag = 2;
+          tail_bar();
+        }
         if (!*abort_flag) {
-          __threadfence();
-          sk_reduce_write<4>(p, ds, unit, tt, nthr, c.m0, c.rows, c.n_tile * kTileN, nullptr);
+          // sliced: thread 0 has acquired the counter and the barrier orders the CTA behind it; the partials are
+          // read from L2 (ld.cg), where the writers' fences put them
+          if (!sliced) __threadfence();
+          if (sliced) sk_reduce_write<2, 4>(p, ds, unit, tt, nthr, c.m0, row_lo, row_hi, c.n_tile * kTileN, nullptr);
+          else sk_reduce_write<4, 2>(p, ds, unit, tt, nthr, c.m0, row_lo, row_hi, c.n_tile * kTileN, nullptr);
+        }
+        if (sliced) {
+          tail_bar();
+          if (tt == 0 && !*abort_flag) {
+            const uint32_t prev = atomicAdd(&p.counters[c.tile_id], 1u);
+            if (prev == 2u * static_cast<uint32_t>(ds.parts) - 1u) p.counters[c.tile_id] = 0;
+          }
         }
         if (p.tp.mode & kTpScatterPush) {
           tail_bar();
@@ -801,8 +864,12 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             uint32_t last = 0;
             if (ok) {
               const uint32_t prev = atomicAdd(&p.counters[tile_id], 1u);
-              last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
-              if (last) p.counters[tile_id] = 0;
+              if (sliced) {
+                last = 1u;                                  // every contributor finishes its share at the end of the CTA
+              } else {
+                last = (prev == static_cast<uint32_t>(seg.parts) - 1u) ? 1u : 0u;
+                if (last) p.counters[tile_id] = 0;
+              }
             }
             ctl->is_last = last;
           }
