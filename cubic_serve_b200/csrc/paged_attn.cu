@@ -22,7 +22,13 @@
 namespace cb {
 
 static constexpr int kAttnWarps = 4;
+#ifdef CB_ATTN_OCC4
+static constexpr int kAttnStages = 3;
+static constexpr int kAttnMinCtas = 4;
+#else
 static constexpr int kAttnStages = 4;
+static constexpr int kAttnMinCtas = 1;
+#endif
 static constexpr int kD = 128;
 
 struct AttnParams {
@@ -251,7 +257,7 @@ __device__ __forceinline__ void process_page(const uint8_t* blob, const KvLayout
 }
 
 template <int KBITS, int VBITS>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+__global__ void __launch_bounds__(kAttnWarps * 32, kAttnMinCtas)
 paged_attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -20,6 +20,7 @@
 // expected of this launch), so nothing is reset while a peer may still write and
 // the expected count may differ from launch to launch (prefill vs decode shapes).
 #include "ptx.cuh"
+#include "launch.cuh"
 
 namespace cb {
 
@@ -68,6 +69,8 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
   const int row = blockIdx.x;
   const int m = p.rank * p.rows_per_rank + row;
   if (threadIdx.x == 0) ok_flag = 1;
+  pdl_launch_dependents();
+  pdl_wait();                     // the residual rows and the counters' base are written by earlier kernels of this GPU
   __syncthreads();
   if (p.rs_expected) {
     if (threadIdx.x < p.size) {
@@ -90,15 +93,23 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         uint4 hv = reinterpret_cast<const uint4*>(p.h + static_cast<size_t>(row) * p.H)[v];
         if (p.rs_expected) {
-          for (int r = 0; r < p.size; ++r) {  // ascending rank order, fp32
-            const uint4 pv = __ldcg(reinterpret_cast<const uint4*>(
-                p.recv + (static_cast<size_t>(r) * p.rows_per_rank + row) * p.H) + v);
-            const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&pv);
+          // all ranks' partial vectors are requested before the first is used (the loads are independent; a loop
+          // with a run-time bound would issue them one round trip at a time), then summed in ascending rank order
+          uint4 pv[kMaxRanksTp];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(pp[j]);
-              acc[2 * j] += f.x;
-              acc[2 * j + 1] += f.y;
+          for (int r = 0; r < kMaxRanksTp; ++r)
+            if (r < p.size)
+              pv[r] = __ldcg(reinterpret_cast<const uint4*>(p.recv + (static_cast<size_t>(r) * p.rows_per_rank + row) * p.H) + v);
+#pragma unroll
+          for (int r = 0; r < kMaxRanksTp; ++r) {
+            if (r < p.size) {
+              const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&pv[r]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(pp[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+              }
             }
           }
           // bf16(residual + bf16(sum)), the reference's rounding points
@@ -177,6 +188,8 @@ __global__ void tp_wait_kernel(const uint32_t* ag_flag, uint32_t* ag_state, uint
                                uint32_t* status) {
   __shared__ uint32_t ok_flag;
   if (threadIdx.x == 0) ok_flag = 1;
+  pdl_launch_dependents();
+  pdl_wait();
   __syncthreads();
   if (threadIdx.x < size) {
     if (!wait_ge(ag_flag + threadIdx.x, ag_state[0] + expected)) ok_flag = 0;
@@ -209,6 +222,8 @@ __global__ void __launch_bounds__(256)
 tp_argmax_merge_kernel(const ArgmaxMergeParams p) {
   __shared__ uint32_t ok_flag;
   if (threadIdx.x == 0) ok_flag = 1;
+  pdl_launch_dependents();
+  pdl_wait();
   for (int i = threadIdx.x; i < p.rows; i += blockDim.x) {
     const float v = p.local_val[i];
     const int id = p.local_id[i];
@@ -260,6 +275,8 @@ __global__ void __launch_bounds__(256)
 tp_exchange_kernel(const ExchangeParams p) {
   __shared__ uint32_t ok_flag;
   if (threadIdx.x == 0) ok_flag = 1;
+  pdl_launch_dependents();
+  pdl_wait();
   for (int g = 0; g < p.segments; ++g) {
     for (int i = threadIdx.x; i < p.seg_words; i += blockDim.x) {
       const uint32_t v = p.local[g * p.seg_stride + i];
@@ -304,8 +321,7 @@ int cb_tp_exchange(const CbExchange* a, void* stream) {
   p.status = static_cast<uint32_t*>(a->status);
   p.rank = a->rank; p.size = a->size; p.segments = a->segments; p.seg_words = a->seg_words;
   p.seg_stride = a->seg_stride; p.area_words = a->area_words;
-  tp_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(tp_exchange_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
 }
 
 struct CbReduceNorm {
@@ -331,15 +347,14 @@ int cb_tp_reduce_norm(const CbReduceNorm* a, void* stream) {
   p.status = static_cast<uint32_t*>(a->status);
   p.rank = a->rank; p.size = a->size; p.rows_per_rank = a->rows_per_rank; p.H = a->H; p.M = a->M;
   p.eps = a->eps; p.zero_centered = a->zero_centered; p.local_only = a->local_only;
-  tp_reduce_norm_kernel<<<a->rows_per_rank, kRnThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(tp_reduce_norm_kernel, dim3(a->rows_per_rank), dim3(kRnThreads), 0,
+                                 static_cast<cudaStream_t>(stream), p));
 }
 
 int cb_tp_wait(const void* ag_flag, void* ag_state, unsigned expected, int size, void* status, void* stream) {
-  cb::tp_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  return static_cast<int>(cb::launch(cb::tp_wait_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream),
       static_cast<const uint32_t*>(ag_flag), static_cast<uint32_t*>(ag_state), expected, size,
-      static_cast<uint32_t*>(status));
-  return static_cast<int>(cudaGetLastError());
+      static_cast<uint32_t*>(status)));
 }
 
 struct CbArgmaxMerge {
@@ -366,8 +381,7 @@ int cb_tp_argmax_merge(const CbArgmaxMerge* a, void* stream) {
   p.out_id = static_cast<int*>(a->out_id);
   p.status = static_cast<uint32_t*>(a->status);
   p.rank = a->rank; p.size = a->size; p.rows = a->rows; p.rows_max = a->rows_max;
-  tp_argmax_merge_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch(tp_argmax_merge_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
 }
 
 }  // extern "C"

@@ -508,6 +508,24 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
           }
           const float o4[4] = {acc.x * p.alpha, acc.y * p.alpha, acc.z * p.alpha, acc.w * p.alpha};
+          if (p.tp.mode & kTpScatterPush) {
+            // partial rows go straight to the receive buffer of the rank that owns them (slot = this rank)
+            const int m = m0 + mm;
+            const int ow = m / p.tp.rows_per_rank;
+            const int lr = m - ow * p.tp.rows_per_rank;
+            __nv_bfloat16* dst = p.tp.recv[ow] + (static_cast<size_t>(p.tp.rank) * p.tp.rows_per_rank + lr) * p.N + n_base + c4;
+            if (n_base + c4 + 3 < p.N && (p.N & 3) == 0) {
+              uint2 ov;
+              ov.x = pack_bf16x2(o4[0], o4[1]);
+              ov.y = pack_bf16x2(o4[2], o4[3]);
+              *reinterpret_cast<uint2*>(dst) = ov;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (n_base + c4 + j < p.N) dst[j] = __float2bfloat16(o4[j]);
+            }
+            continue;
+          }
           const size_t o = static_cast<size_t>(m0 + mm) * p.ldy + n_base + c4;
           if (n_base + c4 + 3 < p.N && (p.ldy & 3) == 0) {
             float r4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -540,7 +558,9 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if ((p.tp.mode & kTpScatterPush) && warp >= 2) {
     // every partial row of this CTA is on its way: make the stores visible system-wide,
     // then raise the arrival counter of each owner whose rows this tile touched
-    const bool pusher = (p.splits == 1) || ctl->is_last;
+    // with the K splits in a cluster every CTA pushed its share of the rows before the cluster's second barrier, so
+    // CTA 0 of the cluster speaks for all of them: one system-scope fence per tile
+    const bool pusher = (p.splits == 1) || (p.cluster_splitk ? cluster_ctarank() == 0 : ctl->is_last != 0);
     // CTA barrier first (every thread's stores then happen before thread 64 continues), then ONE release fence
     // at system scope by that thread (cumulative: it orders all of the tile's stores) and relaxed counter updates
     asm volatile("bar.sync 1, %0;" ::"r"(kNumDequantWarps * 32));
@@ -785,10 +805,9 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.k_blocks = K / kBlockK;
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
-  // K splits of the per-tile kernel meet in a thread-block cluster (distributed shared memory) unless the tile's rows
-  // are pushed to other ranks (their arrival counters are raised once per tile by the last split)
-  p.cluster_splitk = (splits > 1 && splits <= 8 && cluster_default && !stream_k && !o.tiles &&
-                      !(p.tp.mode & kTpScatterPush)) ? 1 : 0;
+  // K splits of the per-tile kernel meet in a thread-block cluster (distributed shared memory), also when the tile's
+  // rows are pushed to other ranks (CTA 0 of the cluster raises the owners' arrival counters once per tile)
+  p.cluster_splitk = (splits > 1 && splits <= 8 && cluster_default && !stream_k && !o.tiles) ? 1 : 0;
   if (splits > 1 && !p.cluster_splitk && (!workspace || !counters)) return -13;
   p.splits = splits;
   p.meta_k_blocks = (fmt == kFmtCubic4) ? group_k / kBlockK : 1;

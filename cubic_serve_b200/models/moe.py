@@ -21,12 +21,25 @@ from .config import ModelConfig
 def stack_experts(packed: list[wq_pack.PackedWeight]) -> tuple[wq_pack.PackedWeight, int, int]:
     """Stack per-expert packed weights along a leading axis; returns (stacked, code stride, meta stride) in bytes."""
     first = packed[0]
+    alpha = first.alpha
+    if first.fmt == wq_pack.FMT_NVFP4 and any(p.alpha != alpha for p in packed):
+        # every expert carries its own global scale, the grouped GEMM applies ONE: the largest becomes the stack's and
+        # each expert's ratio to it is folded into its block scales (bf16 pairs in the metadata)
+        alpha = max(p.alpha for p in packed)
+        packed = [p if p.alpha == alpha else _rescaled_nvfp4(p, p.alpha / alpha) for p in packed]
     codes = torch.stack([p.codes for p in packed])
     meta = torch.stack([p.meta for p in packed]) if first.meta is not None else None
-    stacked = wq_pack.PackedWeight(first.fmt, first.n, first.k, first.group_k, codes, meta, first.alpha)
+    stacked = wq_pack.PackedWeight(first.fmt, first.n, first.k, first.group_k, codes, meta, alpha)
     cs = codes[0].numel() * codes.element_size()
     ms = meta[0].numel() if meta is not None else 0
     return stacked, cs, ms
+
+
+def _rescaled_nvfp4(p: wq_pack.PackedWeight, ratio: float) -> wq_pack.PackedWeight:
+    """The same NVFP4 matrix with its block scales multiplied by ``ratio`` (and its global scale divided by it)."""
+    scales = p.meta.contiguous().view(torch.bfloat16).float() * ratio
+    meta = scales.to(torch.bfloat16).view(torch.uint8).reshape(p.meta.shape)
+    return wq_pack.PackedWeight(p.fmt, p.n, p.k, p.group_k, p.codes, meta, p.alpha / ratio, p.act_interleaved)
 
 
 @dataclass

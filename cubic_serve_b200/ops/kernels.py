@@ -96,9 +96,9 @@ def choose_splits(m: int, n: int, k: int, sms: int = 148, fmt: int = FMT_CUBIC4,
 
     The splits of a tile form a thread-block cluster and sum their partial tiles through distributed shared
     memory; that only works when all clusters of the launch are resident at once, so the largest factor whose
-    clusters fit is taken (48 tiles: 2, because only ~40 clusters of 3 fit on 8 GPCs).  ``cluster`` False (rows
-    pushed to other ranks: partials go through the workspace, the last split sums them) keeps the plain rule.  A
-    split pays off while each CTA still has >= 8 k-blocks of work.
+    clusters fit is taken (48 tiles: 2, because only ~40 clusters of 3 fit on 8 GPCs).  ``cluster`` False (partials
+    through the workspace, the last split sums them) keeps the plain rule.  A split pays off while each CTA still
+    has >= 8 k-blocks of work.
     """
     from .strategies import active
     g = active().gemm
@@ -180,7 +180,7 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
         native.check(code, "cb_wq_gemm_sk")
         return out
     if splits is None:
-        splits = choose_splits(m, w.n, k, fmt=w.fmt, cluster=not push)
+        splits = choose_splits(m, w.n, k, fmt=w.fmt)
     if splits > 1:
         need = l.cb_wq_gemm_workspace_bytes(m, w.n, splits)
         if need > ws.gemm.numel():

@@ -61,11 +61,19 @@ def _step_logits(cfg, weights, dev, tp, prompts, k_bits, v_bits):
     return (l0, l1), (ids0, ids1)
 
 
-def _rel_rows(a, b) -> float:
-    """Largest per-row relative L2 error of ``a`` against ``b``."""
-    num = (a - b).norm(dim=1)
-    den = b.norm(dim=1).clamp_min(1e-20)
-    return float((num / den).max())
+def _rel_rows(a, b):
+    """Per-row relative L2 error of ``a`` against ``b``."""
+    return (a - b).norm(dim=1) / b.norm(dim=1).clamp_min(1e-20)
+
+
+def _summary(errs, bound: float) -> dict:
+    """Worst and median row, and the share of rows inside the bound.  A mixture-of-experts model routes by a discrete
+    top-k: rounding noise can hand a row a different expert, which moves that row's logits by far more than the
+    rounding itself, so for those models the median and the share of rows are what a correct execution bounds."""
+    import torch
+    e = torch.cat([x.flatten() for x in errs])
+    return {"max_rel_logit_err": round(float(e.max()), 6), "p50_rel_logit_err": round(float(e.median()), 6),
+            "rows_within_bound": round(float((e <= bound).float().mean()), 4)}
 
 
 def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int = 48, k_bits: int = 8, v_bits: int = 8,
@@ -109,7 +117,7 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
     if "fused" in res:
         (f0, f1), (fi0, fi1) = res["fused"]
         (n0, n1), (ni0, ni1) = res["nccl"]
-        report["max_rel_logit_err"] = round(max(_rel_rows(f0, n0), _rel_rows(f1, n1)), 6)
+        report.update(_summary([_rel_rows(f0, n0), _rel_rows(f1, n1)], report["bound"]))
         report["fused_eq_nccl_tokens"] = round(float(np.mean([a == b for a, b in zip(fi0 + fi1, ni0 + ni1)])), 4)
         # every rank must hold the same tokens (the vocabulary-sharded samplers draw the same candidate everywhere)
         t = torch.tensor(fi0 + fi1 + ni0 + ni1, device=dev)
@@ -121,21 +129,24 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
         ws = random_decoder_weights(small, dev, seed=seed, tp_rank=rank, tp_size=size)
         part = both_modes(small, ws)
         del ws
-        vals = torch.zeros(3, dtype=torch.float64, device=dev)
+        bound1 = per_op * (2 * small.num_layers) ** 0.5
+        vals = torch.zeros(4, dtype=torch.float64, device=dev)
         if rank == 0:
             w1 = random_decoder_weights(small, dev, seed=seed)
             (o0, o1), (oi0, oi1) = _step_logits(small, w1, dev, None, prompts, k_bits, v_bits)
             del w1
-            worst = 0.0
+            errs = []
             for mode, ((a0, a1), _) in part.items():
-                worst = max(worst, _rel_rows(a0, o0), _rel_rows(a1, o1))
+                errs += [_rel_rows(a0, o0), _rel_rows(a1, o1)]
+            sm = _summary(errs, bound1)
             mode = "fused" if "fused" in part else "nccl"
             agree = float(np.mean([a == b for a, b in zip(part[mode][1][0] + part[mode][1][1], oi0 + oi1)]))
-            vals = torch.tensor([worst, agree, 1.0], dtype=torch.float64, device=dev)
+            vals = torch.tensor([sm["max_rel_logit_err"], agree, sm["p50_rel_logit_err"], sm["rows_within_bound"]],
+                                dtype=torch.float64, device=dev)
         dist.broadcast(vals, src=dist.get_global_rank(group, 0), group=group)
         report["vs_one_gpu"] = {"layers": small.num_layers, "max_rel_logit_err": round(float(vals[0]), 6),
-                                "token_agreement": round(float(vals[1]), 4),
-                                "bound": round(per_op * (2 * small.num_layers) ** 0.5, 5)}
+                                "p50_rel_logit_err": round(float(vals[2]), 6), "rows_within_bound": round(float(vals[3]), 4),
+                                "token_agreement": round(float(vals[1]), 4), "bound": round(bound1, 5)}
     torch.cuda.synchronize(dev)
     dist.barrier(group)
     return report

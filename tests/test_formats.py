@@ -198,3 +198,23 @@ def test_out_of_tree_format_through_an_installed_entry_point(tmp_path, monkeypat
     finally:
         registry._extensions.pop("halfscale", None)
         sys.modules.pop("halfscale_fmt", None)
+
+
+def test_stacked_nvfp4_experts_keep_their_own_global_scales():
+    """Every NVFP4 expert has its own global scale, the grouped GEMM applies one per stack: stacking folds each
+    expert's ratio into its block scales, so every expert still decodes to its own values."""
+    import torch
+    from cubic_serve_b200.models.moe import stack_experts
+    from cubic_serve_b200.ops import wq_pack
+    from cubic_serve_b200.quantization import nvfp4
+    torch.manual_seed(0)
+    experts = []
+    for e in range(3):
+        q = nvfp4.quantize(torch.randn(128, 128) * 0.02 * (1 + e))
+        experts.append(wq_pack.pack_nvfp4(q["weight_packed"], q["weight_scale"].float(), 1.0 / float(q["weight_global_scale"])))
+    assert len({p.alpha for p in experts}) == 3
+    st, _, _ = stack_experts(experts)
+    for e, p in enumerate(experts):
+        got = wq_pack.unpack_to_dense(wq_pack.PackedWeight(st.fmt, st.n, st.k, st.group_k, st.codes[e], st.meta[e], st.alpha))
+        want = wq_pack.unpack_to_dense(p)
+        assert float((got - want).norm() / want.norm()) < 4e-3
