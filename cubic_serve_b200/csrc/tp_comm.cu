@@ -42,6 +42,23 @@ __device__ __forceinline__ bool wait_ge(const uint32_t* p, uint32_t target) {
   return true;
 }
 
+// NVLS: one instruction addressed to a multicast mapping of a symmetric buffer acts on every rank's copy, inside the
+// NVSwitch.  The sum of `multimem.ld_reduce` is accumulated in fp32 and rounded once to bf16, like the ordered sum it
+// replaces, but in an order the switch chooses: results may differ in the last bit from run to run.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
 struct ReduceNormParams {
   const __nv_bfloat16* recv;     // local [size][rows_per_rank][H] partial rows, slot = source rank
   const uint32_t* rs_flag;       // local arrival counters [size]
@@ -57,6 +74,11 @@ struct ReduceNormParams {
   int zero_centered;
   int local_only;                // 1: keep the normalised rows on this rank (no all-gather, no counters); the
                                  // consumer is a later kernel of the same stream (expert-parallel dispatch)
+  // NVLS forms (null = plain peer loads / stores):
+  const __nv_bfloat16* recv_mc;  // multicast mapping of the partial-sum buffers, every rank's laid out [M_pad][H] by
+                                 // GLOBAL row (the GEMMs wrote their partial rows locally): one ld_reduce per 16 bytes
+                                 // sums all ranks' partials in the switch
+  __nv_bfloat16* x_mc;           // multicast mapping of the gathered activation buffers: one store reaches every rank
 };
 
 static constexpr int kRnThreads = 256;
@@ -92,7 +114,21 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         uint4 hv = reinterpret_cast<const uint4*>(p.h + static_cast<size_t>(row) * p.H)[v];
-        if (p.rs_expected) {
+        if (p.rs_expected && p.recv_mc) {
+          const uint4 pv = multimem_ld_reduce_bf16x8(p.recv_mc + static_cast<size_t>(m) * p.H + static_cast<size_t>(v) * 8);
+          const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&pv);
+          const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&hv);
+          uint4 ov;
+          __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 sm = __bfloat1622float2(pp[j]);            // bf16(sum), rounded by the switch
+            const float2 hh = __bfloat1622float2(hp[j]);
+            op[j] = __floats2bfloat162_rn(hh.x + sm.x, hh.y + sm.y);
+          }
+          reinterpret_cast<uint4*>(p.h + static_cast<size_t>(row) * p.H)[v] = ov;
+          hv = ov;
+        } else if (p.rs_expected) {
           // all ranks' partial vectors are requested before the first is used (the loads are independent; a loop
           // with a run-time bound would issue them one round trip at a time), then summed in ascending rank order
           uint4 pv[kMaxRanksTp];
@@ -159,6 +195,8 @@ tp_reduce_norm_kernel(const ReduceNormParams p) {
         // all-gather by push: the same 16 bytes to every rank's buffer (self included)
         if (p.local_only) {
           reinterpret_cast<uint4*>(p.x_peer[p.rank] + static_cast<size_t>(m) * p.H)[v] = ov;
+        } else if (p.x_mc) {
+          multimem_st_16(p.x_mc + static_cast<size_t>(m) * p.H + static_cast<size_t>(v) * 8, ov);
         } else {
           for (int r = 0; r < p.size; ++r)
             reinterpret_cast<uint4*>(p.x_peer[r] + static_cast<size_t>(m) * p.H)[v] = ov;
@@ -328,6 +366,7 @@ struct CbReduceNorm {
   const void* recv; const void* rs_flag; void* rs_state; unsigned rs_expected;
   void* h; const void* norm_w; void* x_peer[8]; void* ag_flag_peer[8]; void* status;
   int rank, size, rows_per_rank, H, M; float eps; int zero_centered; int local_only;
+  const void* recv_mc; void* x_mc;
 };
 
 int cb_tp_reduce_norm(const CbReduceNorm* a, void* stream) {
@@ -347,6 +386,8 @@ int cb_tp_reduce_norm(const CbReduceNorm* a, void* stream) {
   p.status = static_cast<uint32_t*>(a->status);
   p.rank = a->rank; p.size = a->size; p.rows_per_rank = a->rows_per_rank; p.H = a->H; p.M = a->M;
   p.eps = a->eps; p.zero_centered = a->zero_centered; p.local_only = a->local_only;
+  p.recv_mc = static_cast<const __nv_bfloat16*>(a->recv_mc);
+  p.x_mc = static_cast<__nv_bfloat16*>(a->x_mc);
   return static_cast<int>(launch(tp_reduce_norm_kernel, dim3(a->rows_per_rank), dim3(kRnThreads), 0,
                                  static_cast<cudaStream_t>(stream), p));
 }

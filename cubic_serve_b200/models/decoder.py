@@ -76,8 +76,9 @@ class DecoderWeights:
         return total
 
 
-def quantize_linear(w: torch.Tensor, cfg: ModelConfig) -> wq_pack.PackedWeight:
-    """Quantize a dense ``[N, K]`` matrix with the config's weight format and re-tile it for the GEMM."""
+def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None) -> wq_pack.PackedWeight:
+    """Quantize a dense ``[N, K]`` matrix with the config's weight format and re-tile it for the GEMM.  ``amax``: the
+    largest magnitude of the matrix ``w`` is a shard of (formats with one scale per tensor, i.e. NVFP4)."""
     q = cfg.quant
     if q.method == "none":
         return wq_pack.pack_bf16(w)
@@ -101,7 +102,7 @@ def quantize_linear(w: torch.Tensor, cfg: ModelConfig) -> wq_pack.PackedWeight:
         return wq_pack.pack_affine4(qv, scale, lo, g)
     if q.method == "nvfp4":
         from ..quantization import nvfp4
-        payload = nvfp4.quantize(w)
+        payload = nvfp4.quantize(w, amax)
         return wq_pack.pack_nvfp4(payload["weight_packed"], payload["weight_scale"].float(),
                                   1.0 / float(payload["weight_global_scale"]))
     raise NotImplementedError(f"weight format {q.method}")
@@ -136,6 +137,13 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
         """This rank's ``width`` rows of a matrix whose rows are owned in rank order."""
         return full[r * width:(r + 1) * width]
 
+    def shard_q(full, pick):
+        """Quantized shard ``pick(full)`` of a matrix, with the per-tensor scale (if the format has one) of the whole."""
+        return quantize_linear(pick(full).contiguous(), cfg, float(full.abs().amax()) if cfg.quant.method == "nvfp4" else None)
+
+    def cols_of(width):
+        return lambda full: full[:, r * width:(r + 1) * width]
+
     def sections(full, widths):
         """``full`` is a stack of sections of ``tp_size * w`` rows each; this rank keeps rows ``[r w, (r + 1) w)`` of
         every section (q | k | v heads, gate | up features, ...)."""
@@ -157,24 +165,24 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             gk, gv = cfg.gdn_k_heads // tp_size, cfg.gdn_v_heads // tp_size
             f32 = dict(device=device, dtype=torch.float32)
             lw = LayerWeights(ln1=norm_w(), ln2=norm_w(), gdn=GdnWeights(
-                in_proj=quantize_linear(sections(rnd(2 * gk * 128 * tp_size + 2 * gv * 128 * tp_size, H),
-                                                 [gk * 128, gk * 128, gv * 128, gv * 128]), cfg),
+                in_proj=shard_q(rnd(2 * gk * 128 * tp_size + 2 * gv * 128 * tp_size, H),
+                                lambda f: sections(f, [gk * 128, gk * 128, gv * 128, gv * 128])),
                 in_ba=wq_pack.pack_bf16(sections(rnd(2 * gv * tp_size, H), [gv, gv])),
                 conv_w=sections(torch.randn((2 * gk + gv) * 128 * tp_size, 4, generator=gen, **f32) * 0.3,
                                 [gk * 128, gk * 128, gv * 128]),
                 a_log=rows_of(torch.randn(gv * tp_size, generator=gen, **f32) * 0.5, gv),
                 dt_bias=rows_of(torch.randn(gv * tp_size, generator=gen, **f32) * 0.5, gv),
                 norm_w=torch.ones(128, **f32),
-                out=quantize_linear(rnd(H, gv * 128 * tp_size)[:, r * gv * 128:(r + 1) * gv * 128].contiguous(), cfg),
+                out=shard_q(rnd(H, gv * 128 * tp_size), cols_of(gv * 128)),
                 hk=gk, hv=gv))
         else:
             lw = LayerWeights(
                 ln1=norm_w(), ln2=norm_w(),
-                qkv=quantize_linear(sections(rnd((hq + 2 * hkv) * D * tp_size, H), [hq * D, hkv * D, hkv * D]), cfg),
-                o=quantize_linear(rnd(H, hq * D * tp_size)[:, r * hq * D:(r + 1) * hq * D].contiguous(), cfg),
+                qkv=shard_q(rnd((hq + 2 * hkv) * D * tp_size, H), lambda f: sections(f, [hq * D, hkv * D, hkv * D])),
+                o=shard_q(rnd(H, hq * D * tp_size), cols_of(hq * D)),
             )
             if cfg.attn_output_gate:
-                lw.attn_gate = quantize_linear(rows_of(rnd(hq * D * tp_size, H), hq * D), cfg)
+                lw.attn_gate = shard_q(rnd(hq * D * tp_size, H), lambda f: rows_of(f, hq * D))
         if cfg.qk_norm and lw.gdn is None:
             lw.q_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
             lw.k_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
@@ -182,8 +190,8 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             from .moe import random_moe_weights
             lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std, layer_seed=seed * 4096000 + li)
         else:
-            lw.gate_up = quantize_linear(sections(rnd(2 * inter * tp_size, H), [inter, inter]), cfg)
-            lw.down = quantize_linear(rnd(H, inter * tp_size)[:, r * inter:(r + 1) * inter].contiguous(), cfg)
+            lw.gate_up = shard_q(rnd(2 * inter * tp_size, H), lambda f: sections(f, [inter, inter]))
+            lw.down = shard_q(rnd(H, inter * tp_size), cols_of(inter))
         layers.append(lw)
     gen.manual_seed(seed * 4096000 + 4095)
     v_local = cfg.vocab_size // tp_size

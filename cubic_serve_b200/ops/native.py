@@ -284,7 +284,7 @@ class ReduceNormStruct(ctypes.Structure):
                 ("x_peer", ctypes.c_void_p * 8), ("ag_flag_peer", ctypes.c_void_p * 8), ("status", ctypes.c_void_p),
                 ("rank", ctypes.c_int), ("size", ctypes.c_int), ("rows_per_rank", ctypes.c_int), ("H", ctypes.c_int),
                 ("M", ctypes.c_int), ("eps", ctypes.c_float), ("zero_centered", ctypes.c_int),
-                ("local_only", ctypes.c_int)]
+                ("local_only", ctypes.c_int), ("recv_mc", ctypes.c_void_p), ("x_mc", ctypes.c_void_p)]
 
 
 class ExchangeStruct(ctypes.Structure):

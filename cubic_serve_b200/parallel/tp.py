@@ -48,6 +48,8 @@ class TpBuffers:
     xchg_val: torch.Tensor        # fp32 [size, rows_max]
     xchg_id: torch.Tensor         # int32 [size, rows_max]
     cand: torch.Tensor            # int32 [size, 2 * rows_max * CAND]  per source: values (fp32 bits) then ids
+    recv_mc: int = 0              # NVLS multicast mappings of recv / xfull (0 = none: plain peer loads and stores)
+    xfull_mc: int = 0
     recv_ptrs: list[int] = field(default_factory=list)
     xfull_ptrs: list[int] = field(default_factory=list)
     flags_ptrs: list[int] = field(default_factory=list)
@@ -103,6 +105,9 @@ def symmetric_buffers(group, hidden: int, max_tokens: int, rows_max: int, device
     dist.barrier(group)
     ptrs = [[int(p) for p in h.buffer_ptrs] for _, h in handles]
     b.recv_ptrs, b.xfull_ptrs, b.flags_ptrs, b.xval_ptrs, b.xid_ptrs, b.cand_ptrs = ptrs
+    # NVLS: the multicast mappings of the two big buffers, when the fabric offers them (NVSwitch)
+    b.recv_mc = int(getattr(handles[0][1], "multicast_ptr", 0) or 0)
+    b.xfull_mc = int(getattr(handles[1][1], "multicast_ptr", 0) or 0)
     b._handles = handles  # keep the mappings alive
     return b
 
@@ -123,6 +128,13 @@ class FusedTp:
         self._links: dict = {}
         self.rows_max = bufs.xchg_val.shape[1]
         self.cand_local = torch.zeros(2, self.rows_max, CAND, dtype=torch.int32, device=device)
+        # NVLS forms of the two collectives of a site (CUBIC_SERVE_NVLS: "0" off, "gather" only the all-gather store,
+        # "1" / unset both where the fabric has multicast).  The reduction inside the switch sums in an order of its
+        # choosing: results are no longer bit-identical from run to run, the all-gather store changes no bit.
+        import os
+        mode = os.environ.get("CUBIC_SERVE_NVLS", "gather")
+        self.nvls_gather = mode != "0" and bufs.xfull_mc != 0
+        self.nvls_reduce = mode == "1" and bufs.recv_mc != 0 and bufs.xfull_mc != 0
 
     # ---------------------------------------------------------------- helpers
     def begin_step(self, m: int) -> None:
@@ -151,7 +163,12 @@ class FusedTp:
         link = native.TpLinkStruct()
         link.mode, link.rank, link.size, link.rows_per_rank = MODE_SCATTER_PUSH, self.rank, self.size, self.rpr
         for r in range(self.size):
-            link.recv[r] = self.b.recv_ptrs[r] + self._recv_off(s)
+            if self.nvls_reduce:
+                # partial rows stay in THIS rank's buffer, laid out by global row: owner r's "slot of this rank" is
+                # made to start at row r * rpr of the local buffer; the owner sums all ranks' copies in the switch
+                link.recv[r] = self.b.recv.data_ptr() + self._recv_off(s) + (r - self.rank) * self.rpr * w.n * 2
+            else:
+                link.recv[r] = self.b.recv_ptrs[r] + self._recv_off(s)
             link.rs_flag[r] = self.b.flags_ptrs[r] + self._flag_off(s, 0)
         K.wq_gemm(x, w, out=None, ws=self.ws, link=link)
 
@@ -182,6 +199,8 @@ class FusedTp:
         a.status = self.ws.status.data_ptr()
         a.rank, a.size, a.rows_per_rank, a.H, a.M = self.rank, self.size, self.rpr, self.b.hidden, self.m
         a.eps, a.zero_centered, a.local_only = float(eps), int(zero_centered), int(local_only)
+        a.recv_mc = (self.b.recv_mc + self._recv_off(s)) if (self.nvls_reduce and reduce) else None
+        a.x_mc = (self.b.xfull_mc + self._x_off(s)) if (self.nvls_gather and not local_only) else None
         native.check(native.lib().cb_tp_reduce_norm(ctypes.byref(a), K._stream()), "cb_tp_reduce_norm")
 
     def _gather_link(self, s: int):

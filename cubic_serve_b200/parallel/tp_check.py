@@ -108,7 +108,8 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
     if weights is None:
         weights = random_decoder_weights(cfg, dev, seed=seed, tp_rank=rank, tp_size=size)
     res = both_modes(cfg, weights)
-    report: dict = {"ranks": size, "model": cfg.name, "layers": cfg.num_layers, "rows": requests, "prompt_len": prompt_len}
+    report: dict = {"ranks": size, "model": cfg.name, "layers": cfg.num_layers, "rows": requests, "prompt_len": prompt_len,
+                    "nvls": os.environ.get("CUBIC_SERVE_NVLS", "gather")}
     # a row of logits is the end of a chain of length-H .. length-I dot products of bf16 operands rounded to bf16 at every
     # layer boundary; one layer's bound times sqrt(2 x layers) independent roundings is what two correct executions with
     # different summation orders may differ by

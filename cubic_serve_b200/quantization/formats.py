@@ -177,11 +177,14 @@ def nvfp4_global_multiplier(payload: dict) -> float:
     return float(payload["weight_scale_2"].float().reshape(()))
 
 
-def nvfp4_quantize(w: torch.Tensor) -> dict:
-    """Compressed-tensors convention: block scale = e4m3(amax * g / 6), codes ties-to-even on the level grid."""
+def nvfp4_quantize(w: torch.Tensor, amax: float | None = None) -> dict:
+    """Compressed-tensors convention: block scale = e4m3(amax * g / 6), codes ties-to-even on the level grid.
+
+    ``amax``: largest magnitude that sets the global scale (default: of ``w`` itself); a shard quantized with the
+    whole matrix's value gets exactly the codes and scales the whole matrix would have in its rows / columns."""
     wf = w.float()
     n, k = wf.shape
-    amax = wf.abs().amax().clamp_min(1e-12)
+    amax = (wf.abs().amax() if amax is None else torch.as_tensor(float(amax), device=wf.device)).clamp_min(1e-12)
     g = (448.0 * 6.0) / amax                                   # global scale (stored inverse: decode divides by it)
     blocks = wf.reshape(n, k // 16, 16)
     bs = (blocks.abs().amax(-1) * g / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)

@@ -247,6 +247,11 @@ def test_random_weights_of_any_partition_are_slices_of_one_model():
             want_gu = torch.cat([gu[r * I // 2:(r + 1) * I // 2], gu[I + r * I // 2:I + (r + 1) * I // 2]])
             assert torch.equal(d(parts[r].gate_up)[:I], want_gu)
     assert torch.equal(torch.cat([d(t.lm_head)[:cfg.vocab_size // 2] for t in two]), d(one.lm_head)[:cfg.vocab_size])
+    # NVFP4 has one scale per tensor: shards are quantized with the whole matrix's largest magnitude
+    nv = replace(BASE, quant=QuantSpec("nvfp4", 4, 16))
+    n1 = random_decoder_weights(nv, "cpu", seed=3)
+    n2 = [random_decoder_weights(nv, "cpu", seed=3, tp_rank=r, tp_size=2) for r in range(2)]
+    assert torch.equal(torch.cat([d(t.layers[0].down)[:nv.hidden_size] for t in n2], 1), d(n1.layers[0].down)[:nv.hidden_size])
     moe = replace(BASE, family="gqa_moe", num_experts=4, experts_per_token=2, moe_intermediate_size=128,
                   quant=QuantSpec("cubic", 4, 128))
     m1 = random_decoder_weights(moe, "cpu", seed=1)
