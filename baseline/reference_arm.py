@@ -39,6 +39,11 @@ def probe() -> str | None:
 
 
 def run(args) -> dict:
+    """The reference's engine cannot start on this image (``probe``).  Below the engine, its operator layer was tried
+    on a B200 of this pool through its own public API (``baseline/reference_ops.py``): the stock Marlin path raises
+    "Native CUDA compilation requires the CUDA 13.0 baseline", its Triton path fails to compile under Triton 3.6
+    ("PassManager::run failed") or to launch ("function takes exactly 38 arguments (24 given)"); the record is
+    ``profiles/reference_ops_same_box.md``.  So there is nothing of the reference that produces the metric here."""
     reason = probe()
     if reason is None:
         reason = ("reference serves only qwen3_5/qwen3_5_moe/qwen4_exp checkpoints; the dense 8B GQA benchmark config "
