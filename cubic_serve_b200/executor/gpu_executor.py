@@ -351,7 +351,25 @@ class GpuExecutor:
         self.graph_rt = rt
         for c, why in rt.poison_log:
             log.error("decode graph for %d rows is out of service: %s", c, why)
+        self.execution_plan = self._describe_execution(sorted(ready.sealed))
         return list(ready.sealed)
+
+    def _describe_execution(self, capacities):
+        """The sealed execution plan of this rank: topology, replayable capacities and the operator signatures of a
+        decode step at the largest one, sealed with the implementation identity and the device (what the ranks of a
+        deployment compare before they declare themselves ready)."""
+        from ..contracts.implementation import identity
+        from ..contracts.plan import ExecutionPlan, decoder_step_operators
+        if not capacities:
+            return None
+        tp = self.runner.tp_size
+        topo = f"tp{tp}" + (f"pp{self.runner.pp.stages}" if self.runner.pp is not None and hasattr(self.runner.pp, "stages") else "")
+        try:
+            impl = identity().digest
+        except Exception:  # noqa: BLE001 - identity is evidence, not a precondition of serving
+            impl = "unknown"
+        plan = ExecutionPlan(topo, tuple(capacities), decoder_step_operators(self.cfg, max(capacities), tp, topo))
+        return plan.seal(impl, torch.cuda.get_device_name(self.device))
 
     def _replay_equals_eager(self, slot, b: StepBatch, cap: int):
         """Qualification of a captured decode graph: the eager step on the capture inputs and one replay must sample
