@@ -95,6 +95,14 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--save", help="write the report (verdict, error and result digest of every check) to this JSON file")
     q.add_argument("--against", help="compare with a report saved earlier: which checks kept their bits, which changed")
 
+    rf = sub.add_parser("reference", help="greedy-decode a prompt of token ids with the eager fp32 reference decoder "
+                                          "(the oracle the native kernels are qualified against)")
+    rf.add_argument("model", help="checkpoint directory or random:<config>")
+    rf.add_argument("--prompt-ids", required=True, help="comma-separated token ids")
+    rf.add_argument("--max-tokens", type=int, default=16)
+    rf.add_argument("--kv", default="16,16", help="simulated K,V cache bits (16 = unquantized)")
+    rf.add_argument("--seed", type=int, default=0)
+
     ci = sub.add_parser("check-install", help="check python modules, the native library and the GPUs")
     ci.add_argument("--build", action="store_true", help="(re)build the native library first")
     ci.add_argument("--json", action="store_true")
@@ -132,7 +140,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--http-keep-alive-seconds", type=int, default=5)
     g.add_argument("--log-config")
     g = s.add_argument_group("Model and generation")
-    g.add_argument("--compute-mode", choices=("wna16", "wna8"), default="wna16")
+    g.add_argument("--compute-mode", choices=("wna16", "wna8"), default="wna16",
+                   help="wna16: packed weights, 16-bit activations (the only mode of this build; wna8 is refused)")
     g.add_argument("--dtype", choices=("bfloat16",), default="bfloat16")
     g.add_argument("--max-model-len", type=int)
     g.add_argument("--chat-template")
@@ -181,8 +190,34 @@ def _kv_bits(name: str) -> int:
     return bits
 
 
+def _reference(args) -> int:
+    """``cubic reference``: the reference's ``reference-qwen3-5`` subcommand for this build's oracle decoder."""
+    import torch
+
+    from .models.config import NAMED_CONFIGS
+    from .models.reference import EagerDecoder, dense_weights_from_checkpoint, random_dense_weights
+    if args.model.startswith("random:"):
+        cfg = NAMED_CONFIGS[args.model.split(":", 1)[1]]()
+        weights = random_dense_weights(cfg, args.seed)
+    else:
+        from .models.checkpoint import admit_checkpoint
+        ck = admit_checkpoint(args.model)
+        cfg, weights = ck.cfg, dense_weights_from_checkpoint(ck)
+    ids = [int(t) for t in args.prompt_ids.split(",") if t.strip()]
+    if not ids or any(t < 0 or t >= cfg.vocab_size for t in ids):
+        raise SystemExit(f"prompt ids must lie in [0, {cfg.vocab_size})")
+    kb, vb = (int(b) for b in args.kv.split(","))
+    dec = EagerDecoder(cfg, weights, kv_bits=None if kb >= 16 and vb >= 16 else (kb, vb))
+    tokens, _ = dec.generate(torch.tensor([ids]), args.max_tokens)
+    print(json.dumps({"model": cfg.name, "prompt_ids": ids, "output_ids": [int(t) for t in tokens[0]]}))
+    return 0
+
+
 def _serve(args) -> int:
     from .runtime.serving import build_backend, run_http_server
+    if args.compute_mode != "wna16":
+        raise SystemExit("--compute-mode wna8 (INT8 activations) is not available in this build: packed weights run "
+                         "with 16-bit activations (wna16)")
     spec = parse_speculative_config(args.speculative_config)
     devices = parse_devices(args.devices)
     tp = args.tp_size or max(1, len(devices) // args.pp_size)
@@ -310,6 +345,8 @@ def main(argv: list[str] | None = None) -> int:
         report = audit_checkpoint(args.checkpoint, args.reference, digests=not args.no_digests)
         print(json.dumps(report, indent=1) if args.json else format_audit(report, args.verbose))
         return 0 if report["ok"] else 1
+    if args.command == "reference":
+        return _reference(args)
     if args.command == "check-install":
         from .utils.check_install import format_report, run_checks
         report = run_checks(build=args.build)

@@ -62,6 +62,37 @@ def random_dense_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> 
     return DenseWeights(embed, layers, torch.ones(H), head)
 
 
+def dense_weights_from_checkpoint(ck) -> DenseWeights:
+    """fp32 weights of a dense full-attention decoder checkpoint, every linear decoded by its quantization extension
+    (the values the packed kernels approximate): what the eager reference engine and ``cubic reference`` run on."""
+    from .checkpoint import CheckpointError, _dense_of, _layer_modules, logical_inventory
+    cfg = ck.cfg
+    if cfg.is_moe or cfg.is_hybrid:
+        raise CheckpointError("the eager reference decoder covers dense full-attention decoders")
+    shapes, _ = logical_inventory(cfg)
+    method, q = cfg.quant.method, cfg.quant
+
+    def lin(module):
+        p = ck.payload(module)
+        if len(p) == 1 and "weight" in p:                 # an unquantized module of a quantized checkpoint
+            return p["weight"].float()
+        return _dense_of(method, p, shapes[module], q).float()
+
+    get = lambda name: ck.store.get(name).float()  # noqa: E731
+    layers = []
+    for i in range(cfg.num_layers):
+        m = _layer_modules(cfg, i)
+        pre = f"model.layers.{i}"
+        layers.append(DenseLayer(
+            get(f"{pre}.input_layernorm.weight"), get(f"{pre}.post_attention_layernorm.weight"),
+            lin(m["q"]), lin(m["k"]), lin(m["v"]), lin(m["o"]), lin(m["gate"]), lin(m["up"]), lin(m["down"]),
+            get(f"{pre}.self_attn.q_norm.weight") if cfg.qk_norm else None,
+            get(f"{pre}.self_attn.k_norm.weight") if cfg.qk_norm else None))
+    embed = get("model.embed_tokens.weight")
+    head = embed if cfg.tie_embeddings else get("lm_head.weight")
+    return DenseWeights(embed, layers, get("model.norm.weight"), head)
+
+
 def cubic_roundtrip(w: torch.Tensor, bits: int = 4, group: int = 128) -> torch.Tensor:
     scheme = cubic.CubicScheme(bits=bits, group_in=group)
     return cubic.decode(cubic.quantize(w, scheme), scheme, tuple(w.shape))

@@ -102,11 +102,12 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
                             enable_prefix_cache=args.prefix_cache)
     if eager:
         from ..executor.eager_executor import EagerPagedExecutor
-        from ..models.reference import random_dense_weights
-        if ck is not None or gguf_weights is not None:
-            raise SystemExit("eager execution mode serves random:<config> models only")
+        from ..models.reference import dense_weights_from_checkpoint, random_dense_weights
+        if gguf_weights is not None:
+            raise SystemExit("eager execution mode serves checkpoint directories and random:<config> models")
         pages = 4096
-        executor = EagerPagedExecutor(cfg, random_dense_weights(cfg, args.seed), pages, kv_bits=(k_bits, v_bits))
+        dense = dense_weights_from_checkpoint(ck) if ck is not None else random_dense_weights(cfg, args.seed)
+        executor = EagerPagedExecutor(cfg, dense, pages, kv_bits=(k_bits, v_bits))
     else:
         from ..executor.gpu_executor import GpuExecutor
         dev = torch.device("cuda", devices[0])

@@ -84,3 +84,32 @@ def test_trace_record_and_replay_between_two_schedules(tmp_path, capsys):
     assert cli.main(["trace", "replay", str(trace), "random:toy", "--serve-args", "--execution-mode eager"]) == 1
     diff = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["first_difference"]
     assert diff["position"] == 0 and "request_id" in diff
+
+
+def test_reference_subcommand_decodes_a_written_checkpoint(tmp_path, capsys):
+    """``cubic reference``: the eager fp32 decoder on a checkpoint's decoded weights; the eager serving mode loads the
+    same weights (``--execution-mode eager`` with a checkpoint directory)."""
+    import json
+
+    from cubic_serve_b200 import cli
+    from cubic_serve_b200.models import checkpoint as C
+    from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+    from cubic_serve_b200.models.reference import EagerDecoder, dense_weights_from_checkpoint
+    cfg = ModelConfig(name="tiny", num_layers=2, hidden_size=256, num_q_heads=4, num_kv_heads=2, head_dim=128,
+                      intermediate_size=512, vocab_size=320, qk_norm=True, quant=QuantSpec("int", 4, 128))
+    path = C.write_random_checkpoint(tmp_path / "ck", cfg, seed=1)
+    assert cli.main(["reference", str(path), "--prompt-ids", "1,2,3,4", "--max-tokens", "5"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["prompt_ids"] == [1, 2, 3, 4] and len(out["output_ids"]) == 5
+    import torch
+    dense = dense_weights_from_checkpoint(C.admit_checkpoint(path))
+    tokens, _ = EagerDecoder(cfg, dense).generate(torch.tensor([[1, 2, 3, 4]]), 5)
+    assert out["output_ids"] == [int(t) for t in tokens[0]]
+
+
+def test_wna8_compute_mode_is_refused_not_ignored():
+    import pytest
+
+    from cubic_serve_b200 import cli
+    with pytest.raises(SystemExit, match="wna8"):
+        cli.main(["serve", "random:toy", "--compute-mode", "wna8"])
