@@ -134,12 +134,14 @@ class ModelSpec:
                           "state": None if self.state is None else dataclasses.asdict(self.state),
                           "manifest": None if self.manifest is None else self.manifest.digest})
 
-    def kv_pages(self, free_bytes: int, reserve_bytes: int, max_model_len: int, max_running: int) -> int:
+    def kv_pages(self, free_bytes: int, reserve_bytes: int, max_model_len: int, max_running: int,
+                 state_snapshots: int = 0) -> int:
         """Pages that fit into what is left of the device after the reserve and the recurrent state of
-        ``max_running`` requests, capped by what ``max_running`` requests of ``max_model_len`` tokens can use."""
+        ``max_running`` requests (plus ``state_snapshots`` snapshot rows kept for cached prefixes), capped by what
+        ``max_running`` requests of ``max_model_len`` tokens can use."""
         budget = max(0, free_bytes - reserve_bytes)
         if self.state is not None:
-            budget = max(0, budget - max_running * self.state.bytes_per_request)
+            budget = max(0, budget - (max_running + state_snapshots) * self.state.bytes_per_request)
         cap = max_running * (-(-max_model_len // self.cache.page_tokens)) + 64
         if self.cache.page_bytes == 0:                 # a stage without full-attention layers still needs page ids
             return int(cap)

@@ -198,7 +198,8 @@ copy_pages_kernel(uint8_t* cache, const int* src_pages, const int* dst_pages, in
   if (s < 0 || d < 0 || s == d) return;
   const uint4* sp = reinterpret_cast<const uint4*>(cache + static_cast<size_t>(s) * page_bytes_vec * 16);
   uint4* dp = reinterpret_cast<uint4*>(cache + static_cast<size_t>(d) * page_bytes_vec * 16);
-  for (int i = threadIdx.x; i < page_bytes_vec; i += blockDim.x) dp[i] = sp[i];
+  // blockIdx.y strides over the page, so that rows of megabytes (recurrent-state rows) use more than one SM
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < page_bytes_vec; i += blockDim.x * gridDim.y) dp[i] = sp[i];
 }
 
 }  // namespace cb
@@ -245,7 +246,9 @@ int cb_copy_pages(void* cache, const void* src_pages, const void* dst_pages, int
                   void* stream) {
   if (n <= 0) return 0;
   if (page_bytes % 16 != 0) return -10;
-  cb::copy_pages_kernel<<<n, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const long long vecs = page_bytes / 16;
+  const unsigned chunks = static_cast<unsigned>(vecs > 256 * 16 ? (vecs / (256 * 16) > 64 ? 64 : vecs / (256 * 16)) : 1);
+  cb::copy_pages_kernel<<<dim3(static_cast<unsigned>(n), chunks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint8_t*>(cache), static_cast<const int*>(src_pages), static_cast<const int*>(dst_pages),
       static_cast<int>(page_bytes / 16));
   return static_cast<int>(cudaGetLastError());

@@ -403,6 +403,20 @@ class GpuExecutor:
         """Sealed decode graphs by capacity (read-only view)."""
         return {c: s.graph for c, s in self.graph_rt.slots.items() if s.state is GraphState.SEALED}
 
+    @property
+    def state_checkpoint_rows(self) -> tuple[int, ...]:
+        return tuple(getattr(self.runner, "state_checkpoint_rows", ()))
+
+    def copy_state(self, pairs) -> None:
+        """Recurrent-state row copies ``(src row, dst row)`` in stream order with the steps: a snapshot taken after the
+        step that ended on a page boundary, or a snapshot restored into the row of a request that resumes there."""
+        if not pairs:
+            return
+        src = torch.tensor([p[0] for p in pairs], dtype=torch.int32, device=self.device)
+        dst = torch.tensor([p[1] for p in pairs], dtype=torch.int32, device=self.device)
+        with torch.cuda.stream(self.stream):
+            self.runner.copy_state(src, dst)
+
     def copy_pages(self, pairs) -> None:
         """Copy-on-write page copies (all layers) ahead of a step."""
         if not pairs:

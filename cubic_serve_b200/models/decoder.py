@@ -231,6 +231,7 @@ class StepBatch:
 class DecoderRunner:
     def __init__(self, cfg: ModelConfig, weights: DecoderWeights, num_pages: int, max_tokens: int,
                  k_bits: int = 8, v_bits: int = 8, tp=None, device=None, pp=None, max_requests: int = 256,
+                 state_checkpoints: int = 0,
                  kv_rotation: bool = False) -> None:
         """``max_requests``: rows of the per-request recurrent state of Gated DeltaNet layers (= page-table rows).
         ``kv_rotation``: q / k / v head vectors are Walsh-Hadamard transformed before the cache write (smoother
@@ -261,6 +262,9 @@ class DecoderRunner:
         # Gated DeltaNet layers: per request the last three conv inputs of every channel and one 128 x 128 fp32 state
         # per value head; a request's row is its page-table row, reset implicitly when it starts at position 0
         self.max_requests = max_requests
+        # rows [max_requests, max_requests + state_checkpoints) of the recurrent-state arrays hold snapshots taken at
+        # page boundaries of prompts, so that cached prefixes of models with recurrent layers can be resumed
+        self.state_checkpoint_rows = tuple(range(max_requests, max_requests + state_checkpoints))
         self.gdn_conv_state, self.gdn_state = {}, {}
         gdn_first = next((lw.gdn for lw in weights.layers if lw.gdn is not None), None)
         if gdn_first is not None:
@@ -270,8 +274,9 @@ class DecoderRunner:
             C = (2 * gk + gv) * 128
             for li, lw in enumerate(weights.layers):
                 if lw.gdn is not None:
-                    self.gdn_conv_state[li] = torch.zeros(max_requests, 3, C, dtype=torch.bfloat16, device=dev)
-                    self.gdn_state[li] = torch.zeros(max_requests, gv, 128, 128, dtype=torch.float32, device=dev)
+                    rows = max_requests + state_checkpoints
+                    self.gdn_conv_state[li] = torch.zeros(rows, 3, C, dtype=torch.bfloat16, device=dev)
+                    self.gdn_state[li] = torch.zeros(rows, gv, 128, 128, dtype=torch.float32, device=dev)
             self.gdn_in = torch.empty(max_tokens, gdn_first.in_proj.n, dtype=torch.bfloat16, device=dev)
             self.gdn_ba = torch.empty(max_tokens, 2 * gv, dtype=torch.bfloat16, device=dev)
             self.gdn_mix = torch.empty(max_tokens, C, dtype=torch.bfloat16, device=dev)
@@ -306,6 +311,14 @@ class DecoderRunner:
             from ..parallel.ep import FusedEp, symmetric_ep_buffers
             bufs = symmetric_ep_buffers(tp.group, H, cfg.experts_per_token, tp.fused.b.max_tokens, dev)
             self.ep = FusedEp(bufs, dev, cfg.num_experts, 2 * cfg.moe_intermediate_size, ws=self.ws)
+
+    def copy_state(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        """Bit-preserving copies of whole recurrent-state rows ``src[i] -> dst[i]`` (int32 device tensors) in every
+        Gated DeltaNet layer: delta-rule state and convolution history (reference: the captured owner-row copies of
+        ``executor/state_transfer.py:140``).  Rows are request rows or snapshot rows."""
+        for li, st in self.gdn_state.items():
+            K.copy_rows(st, src, dst)
+            K.copy_rows(self.gdn_conv_state[li], src, dst)
 
     # ---------------------------------------------------------------- forward
     def forward_hidden(self, b: StepBatch) -> torch.Tensor:

@@ -328,6 +328,14 @@ def copy_pages(cache: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> Non
                                             page_bytes, _stream()), "cb_copy_pages")
 
 
+def copy_rows(t: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
+    """``t[dst[i]] = t[src[i]]`` for whole leading-axis rows of a contiguous tensor (bit-preserving; the page-copy
+    kernel with a row as the page).  A row must be a multiple of 16 bytes."""
+    if not t.is_contiguous() or (t.stride(0) * t.element_size()) % 16:
+        raise ValueError("copy_rows: rows must be contiguous multiples of 16 bytes")
+    copy_pages(t, src, dst)
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                     rb_req: torch.Tensor, rb_qstart: torch.Tensor, rb_qcount: torch.Tensor, rb_ctx: torch.Tensor,
                     hq: int, hkv: int, head_dim: int, k_bits: int, v_bits: int, scale: float | None = None,

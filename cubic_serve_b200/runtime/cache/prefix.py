@@ -33,10 +33,18 @@ def block_digests(tokens, extra: bytes = b"", limit_blocks: int | None = None) -
 
 
 class PrefixCache:
-    def __init__(self, pool: PagePool, enabled: bool = True) -> None:
+    def __init__(self, pool: PagePool, enabled: bool = True, checkpoint_slots: tuple[int, ...] | None = None) -> None:
+        """``checkpoint_slots``: rows of the executor's recurrent-state arrays set aside for snapshots.  Given (models
+        with recurrent layers), a prefix can only be resumed where such a snapshot exists: ``match`` returns the longest
+        cached prefix that ENDS at a checkpointed block, and ``publish_checkpoint`` records one (reference: the state
+        slot snapshots shared by refcount beside the pages, ``runtime/performance.py:11018-11152``)."""
         self.pool = pool
         self.enabled = enabled
         self._map: OrderedDict[bytes, int] = OrderedDict()
+        self.needs_checkpoint = checkpoint_slots is not None
+        self._free_ckpt: list[int] = list(checkpoint_slots or ())
+        self._ckpt: dict[bytes, int] = {}          # digest of a chain's last block -> checkpoint slot
+        self.last_checkpoint: int | None = None    # snapshot slot of the prefix returned by the latest ``match``
         self.hits = 0
         self.lookups = 0
         self.hit_tokens = 0
@@ -61,6 +69,14 @@ class PrefixCache:
                 break
             found.append(d)
             pages.append(page)
+        self.last_checkpoint = None
+        if self.needs_checkpoint:
+            # only a boundary with a snapshot of the recurrent state can be resumed from
+            while found and found[-1] not in self._ckpt:
+                found.pop()
+                pages.pop()
+            if found:
+                self.last_checkpoint = self._ckpt[found[-1]]
         self._touch(found)
         self.lookups += 1
         self.lookup_tokens += len(tokens)
@@ -85,6 +101,31 @@ class PrefixCache:
         self._touch(chain[:len(pages)])
         return added
 
+    def publish_checkpoint(self, tokens, extra: bytes = b"") -> int | None:
+        """Reserve a snapshot slot for the boundary at the end of ``tokens`` (whole blocks, already published as pages);
+        returns the slot to copy the request's recurrent state into, or None (nothing free and nothing evictable, or the
+        boundary is checkpointed already)."""
+        if not self.enabled or not self.needs_checkpoint:
+            return None
+        chain = block_digests(tokens, extra)
+        if not chain or chain[-1] not in self._map or chain[-1] in self._ckpt:
+            return None
+        if not self._free_ckpt:
+            self._evict_checkpoint(exclude=set(chain))
+        if not self._free_ckpt:
+            return None
+        slot = self._free_ckpt.pop()
+        self._ckpt[chain[-1]] = slot
+        return slot
+
+    def _evict_checkpoint(self, exclude: set) -> None:
+        """Free the least recently used snapshot whose block nobody else holds.  The block's page stays cached: it is
+        still part of longer chains that end at another snapshot."""
+        for d in list(self._map.keys()):
+            if d in self._ckpt and d not in exclude and self.pool.refcount(self._map[d]) == 1:
+                self._free_ckpt.append(self._ckpt.pop(d))
+                return
+
     def _touch(self, chain) -> None:
         """Mark a chain of blocks as used, leaf first and root last: a block is only reachable through the blocks
         before it, so within a chain the LEAF must be the first to go.  (Touching in chain order would make the
@@ -106,6 +147,8 @@ class PrefixCache:
             page = self._map[d]
             if self.pool.refcount(page) == 1:
                 del self._map[d]
+                if d in self._ckpt:
+                    self._free_ckpt.append(self._ckpt.pop(d))
                 self.pool.release([page])
                 freed += 1
         return freed
@@ -114,6 +157,8 @@ class PrefixCache:
         for page in self._map.values():
             self.pool.release([page])
         self._map.clear()
+        self._free_ckpt += list(self._ckpt.values())
+        self._ckpt.clear()
 
     @property
     def hit_rate(self) -> float:

@@ -40,12 +40,18 @@ class LLMEngine:
                  eos_token_id: int | None = None) -> None:
         self.executor = executor
         self.cfg = scheduler_config or SchedulerConfig()
-        if getattr(getattr(executor, "cfg", None), "is_hybrid", False) and self.cfg.enable_prefix_cache:
-            # recurrent (Gated DeltaNet) state is not part of the paged prefix cache: every request prefills from 0
+        rows = tuple(getattr(executor, "state_checkpoint_rows", ()) or ())
+        if (getattr(getattr(executor, "cfg", None), "is_hybrid", False) or rows) and self.cfg.enable_prefix_cache:
+            # recurrent (Gated DeltaNet) state: a cached prefix is resumable only with a snapshot of the state at its
+            # end; executors that set rows aside for snapshots (``state_checkpoint_rows``) keep the prefix cache on
             from dataclasses import replace
-            self.cfg = replace(self.cfg, enable_prefix_cache=False)
+            if rows and hasattr(executor, "copy_state"):
+                self.cfg = replace(self.cfg, state_checkpoint_slots=rows)
+            else:
+                self.cfg = replace(self.cfg, enable_prefix_cache=False)
         self.pool = PagePool(num_pages)
-        self.prefix = PrefixCache(self.pool, enabled=self.cfg.enable_prefix_cache)
+        self.prefix = PrefixCache(self.pool, enabled=self.cfg.enable_prefix_cache,
+                                  checkpoint_slots=self.cfg.state_checkpoint_slots or None)
         self.scheduler = ContinuousScheduler(self.cfg, self.pool, self.prefix)
         self.scheduler.decode_lookahead = getattr(executor, "speculative_depth", 0)
         self.eos_token_id = eos_token_id
@@ -155,7 +161,7 @@ class LLMEngine:
         if getattr(self, "_ahead_stale", False):
             self._ahead_stale = False
             return False
-        return bool(plan.segments) and not plan.copies and not plan.finished and all(
+        return bool(plan.segments) and not plan.copies and not plan.finished and not plan.state_restores and all(
             s.count == 1 and s.sample and s.request.sampling.matcher is None for s in plan.segments)
 
     def _segments(self, plan: BatchPlan, ahead: bool = False) -> list:
@@ -190,6 +196,8 @@ class LLMEngine:
         return max(0, b - len(r.output))
 
     def _run(self, plan: BatchPlan) -> list[StepOutput]:
+        if plan.state_restores:
+            self.executor.copy_state(plan.state_restores)
         if plan.copies:
             self.executor.copy_pages(plan.copies)
             if hasattr(self.executor, "invalidate_page_rows"):
@@ -224,6 +232,10 @@ class LLMEngine:
             else:
                 self.prefill_tokens += s.count
         finished = {r.request_id: r for r in self.scheduler.commit(plan, sampled, self.eos_token_id)}
+        if self.scheduler.state_saves:
+            # snapshots of the recurrent state at freshly published page boundaries (stream-ordered after the step)
+            saves, self.scheduler.state_saves = self.scheduler.state_saves, []
+            self.executor.copy_state(saves)
         outs = []
         for s in plan.segments:
             if not s.sample or s.request.request_id not in sampled:

@@ -117,6 +117,9 @@ class BatchPlan:
     # requests the scheduler itself ended while planning: the pool cannot hold their next position even when
     # they run alone (finish reason LENGTH); the engine reports them without a token
     finished: list[Request] = field(default_factory=list)
+    # recurrent-state row copies (src row, dst row) to run BEFORE the step (a resumed request gets the snapshot of its
+    # cached prefix) -- models with recurrent layers only
+    state_restores: list[tuple[int, int]] = field(default_factory=list)
 
     @property
     def num_tokens(self) -> int:
@@ -134,6 +137,9 @@ class SchedulerConfig:
     prefill_chunk_tokens: int = 4096
     max_model_len: int = 4096
     enable_prefix_cache: bool = True
+    # rows of the executor's recurrent-state arrays reserved for prefix snapshots (models with recurrent layers: a
+    # cached prefix is resumable only with the state at its end); () = the model has no recurrent state
+    state_checkpoint_slots: tuple[int, ...] = ()
 
 
 class AdmissionError(RuntimeError):
@@ -148,7 +154,10 @@ class ContinuousScheduler:
     def __init__(self, cfg: SchedulerConfig, pool: PagePool, prefix: PrefixCache | None = None) -> None:
         self.cfg = cfg
         self.pool = pool
-        self.prefix = prefix if prefix is not None else PrefixCache(pool, enabled=cfg.enable_prefix_cache)
+        self.prefix = prefix if prefix is not None else PrefixCache(
+            pool, enabled=cfg.enable_prefix_cache, checkpoint_slots=cfg.state_checkpoint_slots or None)
+        self._pending_restores: list[tuple[int, int]] = []
+        self.state_saves: list[tuple[int, int]] = []      # (request row, snapshot row) copies to run AFTER the last step
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self._clock = itertools.count()
@@ -232,6 +241,8 @@ class ContinuousScheduler:
         req.slot = self._free_slots.pop()
         req.status = RequestStatus.RUNNING
         self.running.append(req)
+        if pages and self.prefix.needs_checkpoint:
+            self._pending_restores.append((self.prefix.last_checkpoint, req.slot))
         return True
 
     def _preempt_newest(self, keep: Request | None) -> Request | None:
@@ -265,6 +276,7 @@ class ContinuousScheduler:
         if not self.running:
             return None
         plan = BatchPlan([])
+        plan.state_restores, self._pending_restores = self._pending_restores, []
         budget = cfg.max_batched_tokens
         order = self.running[self._rotate % len(self.running):] + self.running[:self._rotate % len(self.running)]
         self._rotate += 1
@@ -285,6 +297,12 @@ class ContinuousScheduler:
                 if r.status is not RequestStatus.RUNNING:
                     continue
                 n = min(r.remaining, share, cfg.prefill_chunk_tokens, budget)
+                if self.prefix.needs_checkpoint and self.prefix.enabled and not r.output:
+                    # a chunk ends exactly at the last page boundary of the prompt: the recurrent state after it is the
+                    # snapshot that makes the prompt's pages resumable
+                    ck = (len(r.prompt) - 1) // BLOCK * BLOCK
+                    if r.num_computed < ck < r.num_computed + n:
+                        n = ck - r.num_computed
                 if n < r.remaining:
                     n = max(BLOCK, n - (r.num_computed + n) % BLOCK) if n >= BLOCK else n  # end chunks on page boundaries
                     n = min(n, r.remaining, budget)
@@ -366,6 +384,11 @@ class ContinuousScheduler:
             if full > r.num_published and self.prefix.enabled:
                 self.prefix.publish(r.tokens[:full * BLOCK], r.pages[:full])
                 r.num_published = full
+                if self.prefix.needs_checkpoint and r.num_computed == full * BLOCK and not seg.sample:
+                    # the step ended on a page boundary inside the prompt: its recurrent state is a valid snapshot
+                    slot = self.prefix.publish_checkpoint(r.tokens[:full * BLOCK])
+                    if slot is not None:
+                        self.state_saves.append((r.slot, slot))
             if seg.sample:
                 toks = sampled[r.request_id]
                 # a speculative round hands back several tokens (accepted drafts + the bonus token); each extra

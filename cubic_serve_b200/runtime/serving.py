@@ -53,7 +53,7 @@ def reasoning_end_tokens(tok) -> tuple[int, list[int]] | None:
 
 
 def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int, v_bits: int, max_model_len: int,
-                  max_running: int, layers: int | None = None) -> int:
+                  max_running: int, layers: int | None = None, state_snapshots: int = 0) -> int:
     """Pages that fit in the remaining device memory (one page = 16 tokens of every local layer's rank-local KV
     heads; ``layers`` = decoder layers held by this pipeline stage, default all)."""
     from ..contracts.model import CacheSpec, ModelSpec, StateSpec
@@ -62,7 +62,8 @@ def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int
     cache = CacheSpec(n_layers - n_gdn, cfg.num_kv_heads // tp, cfg.head_dim, k_bits, v_bits)
     # Gated DeltaNet layers keep, per request, one 128 x 128 fp32 state per value head and three conv inputs
     state = StateSpec(n_gdn, cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp) if n_gdn else None
-    return ModelSpec(cfg.name, cfg.family, "", cache, state).kv_pages(free_bytes, reserve_bytes, max_model_len, max_running)
+    return ModelSpec(cfg.name, cfg.family, "", cache, state).kv_pages(free_bytes, reserve_bytes, max_model_len, max_running,
+                                                                      state_snapshots)
 
 
 def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: int):
@@ -131,10 +132,13 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         free, _total = torch.cuda.mem_get_info(dev)
         if args.gpu_memory_gib:
             free = min(free, int(args.gpu_memory_gib * 2 ** 30) - torch.cuda.memory_allocated(dev))
+        # models with recurrent layers resume a cached prefix from a snapshot of the state taken at its last page
+        # boundary: as many snapshot rows as request rows
+        snapshots = args.max_running_requests if cfg.is_hybrid and args.prefix_cache else 0
         pages = plan_kv_pages(free, int(args.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, 1, k_bits, v_bits, max_len,
-                              args.max_running_requests)
+                              args.max_running_requests, state_snapshots=snapshots)
         runner = defn.build_runner(cfg, weights, num_pages=pages, max_tokens=args.token_budget, k_bits=k_bits, v_bits=v_bits,
-                                   max_requests=args.max_running_requests,
+                                   max_requests=args.max_running_requests, state_checkpoints=snapshots,
                                    kv_rotation=bool(getattr(args, "enable_kv_cache_rotation", False)))
         depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None else 0
         if depth and getattr(spec, "method", "mtp") == "ngram":

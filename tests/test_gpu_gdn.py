@@ -95,20 +95,21 @@ def _hybrid_cfg(layers=4, interval=4):
                        quant=QuantSpec("cubic", 4, 128))
 
 
-def _engine(cfg, graphs, chunk, seed=0):
+def _engine(cfg, graphs, chunk, seed=0, snapshots=0):
     from cubic_serve_b200.executor.gpu_executor import GpuExecutor
     from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
     from cubic_serve_b200.runtime.engine import LLMEngine
     from cubic_serve_b200.runtime.scheduler import SchedulerConfig
     dev = torch.device("cuda")
     w = random_decoder_weights(cfg, dev, seed=seed, std=0.05)
-    runner = DecoderRunner(cfg, w, num_pages=128, max_tokens=512, max_requests=8)
+    runner = DecoderRunner(cfg, w, num_pages=128, max_tokens=512, max_requests=8, state_checkpoints=snapshots)
     ex = GpuExecutor(runner, max_rows=8, max_prefill_tokens=512, max_model_len=256, use_graphs=graphs)
     if graphs:
         ex.capture_decode_graphs()
     eng = LLMEngine(ex, 128, SchedulerConfig(max_running_requests=8, max_model_len=256, max_batched_tokens=512,
                                              prefill_chunk_tokens=chunk))
-    assert not eng.cfg.enable_prefix_cache          # recurrent state is not in the prefix cache
+    # without snapshot rows a cached prefix of a recurrent model cannot be resumed: the cache is off
+    assert eng.cfg.enable_prefix_cache == bool(snapshots)
     return eng, runner
 
 
@@ -175,6 +176,37 @@ def test_hybrid_engine_chunked_prefill_and_graph_decode_agree():
     # a second wave of requests reuses the state slots: same prompts, same tokens
     b2 = eng_b.generate(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
     assert b2 == b
+
+
+def test_hybrid_prefix_cache_resumes_from_a_state_snapshot():
+    """With snapshot rows the prefix cache serves a recurrent model: the second request with the same prompt restores
+    the Gated DeltaNet state saved at the prompt's last page boundary and computes only the tail; same tokens."""
+    import numpy as np
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    cfg = _hybrid_cfg()
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, cfg.vocab_size, 70).tolist()
+    sp = SamplingParams(max_tokens=10, ignore_eos=True)
+    eng, runner = _engine(cfg, graphs=True, chunk=512, snapshots=4)
+    first = eng.generate([prompt], sp)[0]
+    assert eng.prefix.hit_tokens == 0
+    before = eng.prefill_tokens
+    again = eng.generate([prompt], sp)[0]
+    runner.ws.check_status()
+    assert eng.prefix.hit_tokens == 64 and eng.prefill_tokens - before == 0      # the 6-token tail is a sampling segment
+    assert again == first
+    # another continuation of the cached 64 tokens against an engine that computes it cold
+    other = prompt[:64] + rng.integers(0, cfg.vocab_size, 9).tolist()
+    warm = eng.generate([other], sp)[0]
+    cold_eng, cold_runner = _engine(cfg, graphs=True, chunk=512)
+    cold = cold_eng.generate([other], sp)[0]
+    cold_runner.ws.check_status()
+    assert eng.prefix.hit_tokens == 128
+    assert np.mean([a == b for a, b in zip(warm, cold)]) >= 0.8, (warm, cold)
+    # two requests at once resuming from the same snapshot, beside a fresh one
+    mixed = eng.generate([prompt, prompt, other[:40]], sp)
+    assert mixed[0] == mixed[1]
+    assert np.mean([a == b for a, b in zip(mixed[0], first)]) >= 0.8, (mixed[0], first)
 
 
 def test_hybrid_moe_family_decodes_the_same_eagerly_and_in_graphs():
