@@ -49,13 +49,15 @@ struct __align__(8) SmemCtl {
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
-               const __grid_constant__ CUtensorMap tmap_w,  // only for kFmtBf16
+               const __grid_constant__ CUtensorMap tmap_w,  // only for the direct formats (bf16, fp8)
                const WqGemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: [stage: x tile | A tile | packed codes+meta] * S, then control block
   const uint32_t x_bytes = static_cast<uint32_t>(p.mb) * 128u;
   constexpr uint32_t kMeta = static_cast<uint32_t>(meta_bytes(FMT));
-  const uint32_t stage_bytes = x_bytes + kATileBytes + (FMT == kFmtBf16 ? 0 : kCodeBytes + kMeta);
+  constexpr bool kDirect = fmt_is_direct(FMT);
+  constexpr int kBK = fmt_block_k(FMT);
+  const uint32_t stage_bytes = x_bytes + kATileBytes + (kDirect ? 0 : kCodeBytes + kMeta);
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
 
@@ -119,7 +121,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
-      const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? kATileBytes : kCodeBytes + kMeta);
+      const uint32_t tx = x_bytes + (kDirect ? kATileBytes : kCodeBytes + kMeta);
       // stage index and phase are carried as counters: `i % S` and `i / S` with a run-time S cost two
       // integer divisions (~300 cycles on one thread), which was most of the per-k-block time of this loop
       auto load_weights = [&](int i, int s) {
@@ -127,8 +129,8 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
         const uint32_t bar = smem_u32(&ctl->full[s]);
         mbar_expect_tx(bar, tx);
-        if (FMT == kFmtBf16) {
-          tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row0 + n_tile * kTileN, bar);
+        if (kDirect) {
+          tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBK, w_row0 + n_tile * kTileN, bar);
         } else {
           const uint8_t* csrc = codes_base + (static_cast<size_t>(n_tile) * p.k_blocks + kb) * kCodeBytes;
           const uint8_t* msrc = meta_base + (static_cast<size_t>(n_tile) * p.meta_blocks + kb / p.meta_k_blocks) * kMeta;
@@ -138,7 +140,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       };
       auto load_x = [&](int i, int s) {
         uint8_t* st = smem + static_cast<size_t>(s) * stage_bytes;
-        tma_load_2d(smem_u32(st), &tmap_x, (kb_lo + i) * kBlockK, m0, smem_u32(&ctl->full[s]));
+        tma_load_2d(smem_u32(st), &tmap_x, (kb_lo + i) * kBK, m0, smem_u32(&ctl->full[s]));
       };
       // weights of the first S stages go out before anything else, so that an
       // all-gather still in flight overlaps with weight streaming
@@ -172,7 +174,9 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // there from a divergent lane's registers before every MMA.
     {
       const bool leader = elect_one();
-      const uint32_t idesc = umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+      // operand formats: bf16 x bf16 (kind::f16) or e4m3 x e4m3 (kind::f8f6f4), fp32 accumulators either way
+      const uint32_t idesc = FMT == kFmtFp8 ? umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 0u, 0u)
+                                            : umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
       const uint32_t tmem_d = __shfl_sync(0xffffffffu, tmem_base, 0);
       const uint32_t smem_base = smem_u32(smem);
       const uint64_t desc_hi = umma_desc_sw128(0);      // every field except the start address
@@ -182,7 +186,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       uint32_t accumulate = 0;
       for (int i = 0; i < iters && ok; ++i) {
         // decoded formats: `ready` implies `full` (the decode warps waited for the copies themselves)
-        ok = (FMT == kFmtBf16) ? mbar_wait_park(smem_u32(&ctl->full[s]), ph, abort_flag)
+        ok = kDirect ? mbar_wait_park(smem_u32(&ctl->full[s]), ph, abort_flag)
                                : mbar_wait_park(smem_u32(&ctl->ready[s]), ph, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -194,8 +198,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (leader) {
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
-            // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
-            umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field: 16 bf16 or 32 e4m3 columns,
+            // one instruction's K either way
+            if constexpr (FMT == kFmtFp8)
+              umma_f8f6f4(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            else
+              umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
           }
           tc_commit(smem_u32(&ctl->empty[s]));
         }
@@ -209,7 +217,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ------------------------------------------------- dequant + epilogue
     const int dq = threadIdx.x - 64;  // 0..511
-    if (FMT != kFmtBf16) {
+    if (!kDirect) {
       // Four groups of four warps, group g takes every fourth k-block; a thread decodes one whole 128-byte row of
       // the k-block (64 weights: two 16-byte code loads, eight 16-byte tile stores), so the per-k-block costs --
       // barrier wait, metadata, fence, arrive, ring arithmetic -- are paid once per 64 weights by 4 warps (the
@@ -303,6 +311,23 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         p.y[off] = __float2bfloat16(v);
       }
     };
+    // fp8: the feature's weight scale times the token's activation scale, applied as the sums leave tensor memory
+    // (partial sums of K splits are linear in both, so every later path sees finished values)
+    float w_scale = 1.f;
+    if constexpr (FMT == kFmtFp8) {
+      const int nn = n_tile * kTileN + quad * 32 + lane;
+      w_scale = nn < p.N ? p.row_scale[w_row0 + nn] : 0.f;
+    }
+    auto scale_acc = [&](uint32_t (&acc)[16], int ci) {
+      if constexpr (FMT == kFmtFp8) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + ci * 16 + j;
+          const float xs = m < m_end ? __ldg(p.col_scale + m) : 0.f;
+          acc[j] = __float_as_uint(__uint_as_float(acc[j]) * (w_scale * xs));
+        }
+      }
+    };
     if (acc_ok && iters > 0) {
       if (p.splits == 1) {
         // TMEM -> registers -> fp32 tile [row][128 features] in the (now idle) stage memory, then all 512 threads
@@ -312,6 +337,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           uint32_t acc[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
           tmem_ld_wait();
+          scale_acc(acc, ci);
 #pragma unroll
           for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]) * p.alpha;
         }
@@ -373,6 +399,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           uint32_t acc[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
           tmem_ld_wait();
+          scale_acc(acc, ci);
 #pragma unroll
           for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
         }
@@ -383,6 +410,7 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
           uint32_t acc[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
           tmem_ld_wait();
+          scale_acc(acc, ci);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             ws[static_cast<size_t>(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
@@ -648,6 +676,7 @@ static int launch_fmt(const CUtensorMap& tx, const CUtensorMap& tw, WqGemmParams
 // Per-launch options of the common launcher.  Everything that steers ONE launch travels in this struct (not in
 // process-wide variables), so launches made concurrently from several host threads cannot see each other's choices.
 struct WqLaunchOpts {
+  const float* x_scale = nullptr;      // fp8: one scale per row of x (the weight scales travel as `meta`)
   const int* tiles = nullptr;          // grouped (expert) launch: device work list, see WqGemmParams::group_tiles
   size_t code_stride = 0, meta_stride = 0;
   int max_items = 0, num_experts = 0;
@@ -773,8 +802,9 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   const long long workspace_bytes = o.workspace_bytes;
   const int pair_mode = g_pair_mode.load(std::memory_order_relaxed);
   const int cluster_default = o.cluster_splitk >= 0 ? o.cluster_splitk : g_cluster_splitk.load(std::memory_order_relaxed);
-  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % 8) != 0) return -10;
-  if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4) return -11;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % (fmt == kFmtFp8 ? 16 : 8)) != 0) return -10;
+  if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4 && fmt != kFmtFp8) return -11;
+  if (fmt == kFmtFp8 && (!o.x_scale || !meta || stream_k)) return -15;
   if (fmt == kFmtCubic4 && (group_k % kBlockK) != 0) return -12;
   WqGemmParams p{};
   p.codes = static_cast<const uint8_t*>(codes);
@@ -802,7 +832,10 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   }
   p.mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
   if (o.tiles && o.mb_hint > 0) p.mb = o.mb_hint;
-  p.k_blocks = K / kBlockK;
+  p.row_scale = fmt == kFmtFp8 ? static_cast<const float*>(meta) : nullptr;
+  p.col_scale = o.x_scale;
+  // fp8 stages cover 128 columns; a ragged last stage reads zeros from both tensor maps
+  p.k_blocks = (K + fmt_block_k(fmt) - 1) / fmt_block_k(fmt);
   if (splits < 1) splits = 1;
   if (splits > p.k_blocks) splits = p.k_blocks;
   // K splits of the per-tile kernel meet in a thread-block cluster (distributed shared memory), also when the tile's
@@ -815,7 +848,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(p.mb)) cols <<= 1;
   p.tmem_cols = cols;
-  const size_t stage = static_cast<size_t>(p.mb) * 128 + kATileBytes + (fmt == kFmtBf16 ? 0 : kCodeBytes + meta_bytes(fmt));
+  const size_t stage = static_cast<size_t>(p.mb) * 128 + kATileBytes + (fmt_is_direct(fmt) ? 0 : kCodeBytes + meta_bytes(fmt));
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SmemCtl);
   int stages = static_cast<int>(budget / stage);
   if (stages > 8) stages = 8;
@@ -831,8 +864,13 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.pair = (stream_k && (pair_mode == 2 || (pair_mode == 1 && M > 256)) && streamk_pair_eligible(p, N)) ? 1 : 0;
   CUtensorMap tx, tw;
   // with CTA pairs each CTA of a pair fetches half of the rows of an activation tile
-  if (make_tmap_bf16(&tx, x, M, K, ldx, p.pair ? p.mb / 2 : p.mb) != 0) return -20;
-  if (fmt == kFmtBf16) {
+  if (fmt == kFmtFp8) {
+    const uint64_t w_rows = static_cast<uint64_t>(N) * (o.tiles ? o.num_experts : 1);
+    if (make_tmap_u8(&tx, x, M, K, ldx, p.mb) != 0) return -20;
+    if (make_tmap_u8(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
+  } else if (make_tmap_bf16(&tx, x, M, K, ldx, p.pair ? p.mb / 2 : p.mb) != 0) {
+    return -20;
+  } else if (fmt == kFmtBf16) {
     const uint64_t w_rows = static_cast<uint64_t>(N) * (o.tiles ? o.num_experts : 1);
     if (make_tmap_bf16(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
   } else {
@@ -863,6 +901,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
     case kFmtCubic4: return launch_fmt<kFmtCubic4>(tx, tw, p, grid, smem, st);
     case kFmtAffine4: return launch_fmt<kFmtAffine4>(tx, tw, p, grid, smem, st);
     case kFmtNvfp4: return launch_fmt<kFmtNvfp4>(tx, tw, p, grid, smem, st);
+    case kFmtFp8: return launch_fmt<kFmtFp8>(tx, tw, p, grid, smem, st);
     default: return launch_fmt<kFmtBf16>(tx, tw, p, grid, smem, st);
   }
 }
@@ -902,6 +941,7 @@ int cb_wq_gemm_resident_clusters(int fmt, int size) {
     case cb::kFmtCubic4: return cb::resident_clusters<cb::kFmtCubic4>(size);
     case cb::kFmtAffine4: return cb::resident_clusters<cb::kFmtAffine4>(size);
     case cb::kFmtNvfp4: return cb::resident_clusters<cb::kFmtNvfp4>(size);
+    case cb::kFmtFp8: return cb::resident_clusters<cb::kFmtFp8>(size);
     default: return cb::resident_clusters<cb::kFmtBf16>(size);
   }
 }
@@ -944,6 +984,41 @@ int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const
                        void* stream) {
   return wq_gemm_grouped_launch(fmt, x, ldx, codes, meta, y, ldy, alpha, total_rows, N, K, group_k, tiles, max_items, mb,
                                 num_experts, code_stride, meta_stride, status, stream, 0);
+}
+
+// W8A8 on the fp8 tensor-core path (tcgen05.mma.kind::f8f6f4, e4m3 x e4m3, fp32 accumulate):
+//   y[m, n] = x_scale[m] * w_scale[n] * sum_k xq[m, k] * wq[n, k]   (+ residual)
+// xq: e4m3 [M, K] (ldx bytes per row, a multiple of 16), x_scale: fp32 [M] (see cb_fp8_quantize_rows);
+// wq: e4m3 [N, K] row-major exactly as in the checkpoint, w_scale: fp32 [N].  `swiglu`: wq's rows are in the
+// interleaved gate / up order and y has N / 2 columns.  K splits meet in a cluster or in `workspace`.
+// Counterpart of the reference's dynamic-token FP8 linear (quantization/extensions/fp8/kernels.py:81-130).
+int cb_wq_gemm_fp8(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, void* y, int ldy,
+                   const void* residual, int M, int N, int K, int splits, int swiglu, void* workspace, void* counters,
+                   void* status, void* stream, const CbTpLink* link) {
+  if (swiglu && ((N % 32) != 0 || ldy < N / 2)) return -50;
+  WqLaunchOpts o;
+  o.x_scale = static_cast<const float*>(x_scale);
+  o.swiglu = swiglu;
+  return wq_gemm_dispatch(cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, residual, 1.f, M, N, K, K, splits, workspace,
+                          counters, status, stream, link, o);
+}
+
+// The grouped (expert) form: wq is the stack [experts * N, K], w_scale [experts * N]; rows of xq / x_scale / y are the
+// routed rows in work-list order (see cb_wq_gemm_grouped).
+int cb_wq_gemm_fp8_grouped(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, void* y,
+                           int ldy, int total_rows, int N, int K, const void* tiles, int max_items, int mb,
+                           int num_experts, int swiglu, void* status, void* stream) {
+  if (!tiles || max_items <= 0 || mb <= 0 || mb > 256 || (mb % 16) != 0 || num_experts <= 0) return -40;
+  if (swiglu && ((N % 32) != 0 || ldy < N / 2)) return -50;
+  WqLaunchOpts o;
+  o.x_scale = static_cast<const float*>(x_scale);
+  o.num_experts = num_experts;
+  o.tiles = static_cast<const int*>(tiles);
+  o.max_items = max_items;
+  o.mb_hint = mb;
+  o.swiglu = swiglu;
+  return wq_gemm_dispatch(cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, nullptr, 1.f, total_rows, N, K, K, 1, nullptr,
+                          nullptr, status, stream, nullptr, o);
 }
 
 }  // extern "C"

@@ -7,7 +7,14 @@
 
 namespace cb {
 
-enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 = 3 };
+// kFmtFp8: e4m3 weights [N, K] with one fp32 scale per output feature, multiplied on the tensor cores with e4m3
+// ACTIVATIONS (one fp32 scale per token) by tcgen05.mma.kind::f8f6f4 -- no software decode at all: both operands go
+// from global memory to the swizzled shared-memory tiles by TMA, as for bf16 weights, with 128 K columns per stage.
+enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 = 3, kFmtFp8 = 4 };
+// formats whose weight tile is fetched by TMA straight into the MMA layout (no decode warps, no code ring)
+__host__ __device__ constexpr bool fmt_is_direct(int fmt) { return fmt == kFmtBf16 || fmt == kFmtFp8; }
+// K columns of one pipeline stage: one 128-byte swizzle row of the operand's element type
+__host__ __device__ constexpr int fmt_block_k(int fmt) { return fmt == kFmtFp8 ? 128 : 64; }
 
 static constexpr int kTileN = 128;       // output features per CTA (UMMA M)
 static constexpr int kBlockK = 64;       // K columns per stage (one 128-byte swizzle row)
@@ -61,6 +68,9 @@ struct WqGemmParams {
   int meta_blocks;          // metadata blocks per n-tile
   int stages;
   float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
+  // kFmtFp8: accumulators are scaled as they leave tensor memory, acc[n][m] *= row_scale[n] * col_scale[m]
+  const float* row_scale;   // [N] (grouped: [experts * N]) weight scale per output feature
+  const float* col_scale;   // [M] activation scale per token (row of x)
   uint32_t tmem_cols;       // power of two >= max(32, mb)
   TpLink tp;
   // grouped (mixture-of-experts) mode: blockIdx.y indexes a device-side work list
@@ -279,6 +289,21 @@ static inline EncodeTiledFn encode_tiled_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(sym);
   }
   return fn;
+}
+
+// 8-bit row-major [rows, cols] (row stride ld bytes), box = {128 cols, box_rows}, 128-byte swizzle
+static inline int make_tmap_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                               uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
 }
 
 // bf16 row-major [rows, cols] (row stride ld elements), box = {64 cols, box_rows}, 128-byte swizzle

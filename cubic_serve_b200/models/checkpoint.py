@@ -246,13 +246,21 @@ def pack_logical(method: str, parts: list[tuple[dict, tuple[int, int]]], q: Quan
                  ) -> wq_pack.PackedWeight:
     """Concatenate logical matrices along N (e.g. q, k, v) and pack them for the GEMM.
 
-    4-bit Cubic / INT / AWQ / NVFP4 payloads stay 4-bit; everything else is decoded to bf16 at load.
+    4-bit Cubic / INT / AWQ / NVFP4 payloads stay 4-bit and channel-scaled FP8 payloads stay e4m3 bytes (the fp8
+    tensor-core GEMM consumes them as stored); everything else is decoded to bf16 at load.
     ``k_slice`` selects a column range (row-parallel shards), aligned to the scale groups.
     """
     lo, hi = k_slice if k_slice else (0, parts[0][1][1])
     native4 = method == "cubic" and q.bits == 4 or method in ("awq",) or (method == "int" and q.bits == 4) or method == "nvfp4"
     plain = any(len(p) == 1 and "weight" in p and p["weight"].dtype in (torch.bfloat16, torch.float16, torch.float32)
                 for p, _ in parts)
+    fp8_rows = (method == "fp8" and not plain and (hi - lo) % 64 == 0 and all(
+        "weight" in p and "weight_scale" in p and p["weight"].dtype == torch.float8_e4m3fn
+        and p["weight_scale"].numel() == s[0] for p, s in parts))
+    if fp8_rows:
+        # e4m3 weights with one scale per output row: W8A8 on the fp8 tensor path, no expansion
+        w8 = torch.cat([p["weight"].view(torch.uint8)[:, lo:hi] for p, _ in parts], 0)
+        return wq_pack.pack_fp8(w8, torch.cat([p["weight_scale"].float().reshape(-1) for p, _ in parts]))
     if not native4 or plain:
         dense = torch.cat([_dense_of(method, p, s, q) for p, s in parts], 0)
         return wq_pack.pack_bf16(dense[:, lo:hi])

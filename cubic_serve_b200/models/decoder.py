@@ -100,6 +100,10 @@ def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None
         scale = ((hi - lo) / 15.0).clamp_min(1e-8)
         qv = torch.round((wg - lo[..., None]) / scale[..., None]).clamp(0, 15).to(torch.uint8).reshape(n, k)
         return wq_pack.pack_affine4(qv, scale, lo, g)
+    if q.method == "fp8":
+        from ..quantization import formats
+        payload = formats.fp8_quantize(w, block=False)
+        return wq_pack.pack_fp8(payload["weight"], payload["weight_scale"])
     if q.method == "nvfp4":
         from ..quantization import nvfp4
         payload = nvfp4.quantize(w, amax)

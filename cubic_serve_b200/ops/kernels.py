@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from . import native
-from .wq_pack import FMT_BF16, FMT_CUBIC4, PackedWeight
+from .wq_pack import FMT_BF16, FMT_CUBIC4, FMT_FP8, PackedWeight
 
 PAGE_TOKENS = 16
 
@@ -42,6 +42,17 @@ class Workspace:
         self.attn_counters = torch.zeros(counters, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._retired: list[torch.Tensor] = []
+        # e4m3 activation operand of the fp8 GEMMs (codes and per-token scales), grown on demand
+        self.fp8_q = torch.empty(0, dtype=torch.uint8, device=device)
+        self.fp8_scale = torch.empty(0, dtype=torch.float32, device=device)
+
+    def ensure_fp8(self, rows: int, k: int) -> None:
+        if rows * k > self.fp8_q.numel():
+            self._retired.append(self.fp8_q)          # captured graphs may hold the old address: retire, never free
+            self.fp8_q = torch.empty(max(rows * k, 256 * 16384), dtype=torch.uint8, device=self.device)
+        if rows > self.fp8_scale.numel():
+            self._retired.append(self.fp8_scale)
+            self.fp8_scale = torch.empty(max(rows, 8192), dtype=torch.float32, device=self.device)
 
     def ensure_attn(self, floats: int) -> None:
         if floats > self.attn.numel():
@@ -143,6 +154,82 @@ def use_stream_k(m: int, n: int, fmt: int, sms: int = 148, k: int = 4096) -> boo
     return m <= g.stream_k_max_rows or (fmt == FMT_BF16 and g.stream_k_bf16)
 
 
+@dataclass
+class Fp8Act:
+    """Activations quantized per token for the fp8 GEMMs: e4m3 bytes ``q [M, K]`` and fp32 scales ``scale [M]``."""
+    q: torch.Tensor
+    scale: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    @property
+    def device(self):
+        return self.q.device
+
+
+def fp8_quantize(x: torch.Tensor, ws: Workspace | None = None, out: Fp8Act | None = None) -> Fp8Act:
+    """Dynamic per-token e4m3 quantization of ``x [M, K]`` (bf16): ``scale = max(amax / 448, 1 / (448 * 512))``,
+    ``q = e4m3(x / scale)`` (the reference's rule, ``quantization/extensions/fp8/reference.py:47-59`` there).  Without
+    ``out`` the result lives in the workspace's fp8 buffers until the next quantization."""
+    m, k = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1
+    if out is None:
+        ws = ws or workspace(x.device)
+        ws.ensure_fp8(m, k)
+        out = Fp8Act(ws.fp8_q[:m * k].view(m, k), ws.fp8_scale[:m])
+    code = native.lib().cb_fp8_quantize_rows(x.data_ptr(), x.stride(0), out.q.data_ptr(), out.q.stride(0),
+                                             out.scale.data_ptr(), m, k, _stream())
+    native.check(code, "cb_fp8_quantize_rows")
+    return out
+
+
+def rmsnorm_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+                zero_centered: bool = False, ws: Workspace | None = None) -> Fp8Act:
+    """RMSNorm whose output leaves as e4m3 + per-token scales (the bf16-rounded norm output is what gets quantized,
+    so the result equals ``fp8_quantize(rmsnorm(...))``)."""
+    m, h = x.shape
+    ws = ws or workspace(x.device)
+    ws.ensure_fp8(m, h)
+    out = Fp8Act(ws.fp8_q[:m * h].view(m, h), ws.fp8_scale[:m])
+    code = native.lib().cb_rmsnorm_fp8(x.data_ptr(), _ptr(residual), _ptr(residual), weight.data_ptr(), out.q.data_ptr(), h,
+                                       out.scale.data_ptr(), m, h, float(eps), int(zero_centered), _stream())
+    native.check(code, "cb_rmsnorm_fp8")
+    return out
+
+
+def swiglu_fp8(gate_up: torch.Tensor, ws: Workspace | None = None) -> Fp8Act:
+    """SwiGLU of ``[gate | up]`` whose output leaves as e4m3 + per-token scales."""
+    m, two_i = gate_up.shape
+    i = two_i // 2
+    ws = ws or workspace(gate_up.device)
+    ws.ensure_fp8(m, i)
+    out = Fp8Act(ws.fp8_q[:m * i].view(m, i), ws.fp8_scale[:m])
+    code = native.lib().cb_swiglu_fp8(gate_up.data_ptr(), out.q.data_ptr(), i, out.scale.data_ptr(), m, i, _stream())
+    native.check(code, "cb_swiglu_fp8")
+    return out
+
+
+def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link, swiglu: bool) -> torch.Tensor:
+    """The fp8 branch of ``wq_gemm`` / ``wq_gemm_act``: quantize the activations per token unless the caller already
+    holds them as ``Fp8Act``, then e4m3 x e4m3 on the tensor cores with both scales applied in the epilogue."""
+    a = x if isinstance(x, Fp8Act) else fp8_quantize(x, ws)
+    m, k = a.q.shape
+    push = link is not None and (link.mode & 2)
+    if splits is None:
+        splits = choose_splits(m, w.n, k, fmt=w.fmt)
+    l = native.lib()
+    if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
+        splits = 1
+    code = l.cb_wq_gemm_fp8(a.q.data_ptr(), a.q.stride(0), a.scale.data_ptr(), w.codes.data_ptr(), w.meta.data_ptr(),
+                            None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual), m, w.n, k,
+                            int(splits), int(swiglu), ws.gemm.data_ptr(), ws.gemm_counters.data_ptr(),
+                            ws.status.data_ptr(), _stream(), None if link is None else ctypes.byref(link))
+    native.check(code, "cb_wq_gemm_fp8")
+    return out
+
+
 def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
             residual: torch.Tensor | None = None, splits: int | None = None,
             ws: Workspace | None = None, link=None, min_units: int | None = None) -> torch.Tensor:
@@ -153,7 +240,7 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
     used (``use_stream_k``).  ``splits`` forces the first with that split-K factor; ``min_units`` forces the
     second (0 = its own schedule, > 0 = the smallest run of k-blocks a CTA is dealt).
     """
-    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    assert isinstance(x, Fp8Act) or (x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1)
     m, k = x.shape
     assert k == w.k, (k, w.k)
     push = link is not None and (link.mode & 2)
@@ -163,6 +250,8 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
     if residual is not None:
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
+    if w.fmt == FMT_FP8:
+        return _wq_gemm_fp8(x, w, out, residual, splits, ws, link, False)
     l = native.lib()
     if splits is None and min_units is None and link is None and TUNED_PLANS:
         tuned = TUNED_PLANS.get(f"{w.fmt}:{m}:{w.n}:{k}:0")
@@ -203,13 +292,15 @@ def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = Non
     give the same values; the ``[M, N]`` intermediate is never written.  Kernel choice as in ``wq_gemm``.
     """
     assert w.act_interleaved, "weight rows are not in the SwiGLU order"
-    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    assert isinstance(x, Fp8Act) or (x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1)
     m, k = x.shape
     assert k == w.k, (k, w.k)
     if out is None:
         out = torch.empty((m, w.n // 2), dtype=torch.bfloat16, device=x.device)
     assert out.stride(1) == 1 and out.shape == (m, w.n // 2)
     ws = ws or workspace(x.device)
+    if w.fmt == FMT_FP8:
+        return _wq_gemm_fp8(x, w, out, None, splits, ws, link, True)
     l = native.lib()
     if splits is None and min_units is None and link is None and TUNED_PLANS:
         tuned = TUNED_PLANS.get(f"{w.fmt}:{m}:{w.n}:{k}:1")
@@ -450,6 +541,16 @@ def wq_gemm_grouped(x: torch.Tensor, w: PackedWeight, out: torch.Tensor, rows: i
     """
     ws = ws or workspace(x.device)
     assert swiglu == w.act_interleaved
+    if w.fmt == FMT_FP8:
+        # the routed rows (plus the slack rows a work item's tile may touch) are quantized per token, then one grouped
+        # launch over the stacked e4m3 experts
+        a = fp8_quantize(x[:min(x.shape[0], rows + sc.mb)], ws)
+        code = native.lib().cb_wq_gemm_fp8_grouped(a.q.data_ptr(), a.q.stride(0), a.scale.data_ptr(), w.codes.data_ptr(),
+                                                   w.meta.data_ptr(), out.data_ptr(), out.stride(0), rows, w.n, w.k,
+                                                   sc.tiles.data_ptr(), sc.max_items, sc.mb, w.codes.shape[0], int(swiglu),
+                                                   ws.status.data_ptr(), _stream())
+        native.check(code, "cb_wq_gemm_fp8_grouped")
+        return out
     entry = native.lib().cb_wq_gemm_grouped_act if swiglu else native.lib().cb_wq_gemm_grouped
     code = entry(w.fmt, x.data_ptr(), x.stride(0), w.codes.data_ptr(), _ptr(w.meta),
                                            out.data_ptr(), out.stride(0), float(w.alpha), rows, w.n, w.k, w.group_k,

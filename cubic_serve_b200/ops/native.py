@@ -253,6 +253,17 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_grouped.restype = i
     l.cb_wq_gemm_grouped_act.argtypes = l.cb_wq_gemm_grouped.argtypes
     l.cb_wq_gemm_grouped_act.restype = i
+    # fp8 (e4m3 x e4m3) tensor path: activation quantizers and the GEMM entries
+    l.cb_fp8_quantize_rows.argtypes = [vp, i, vp, i, vp, i, i, vp]
+    l.cb_fp8_quantize_rows.restype = i
+    l.cb_rmsnorm_fp8.argtypes = [vp, vp, vp, vp, vp, i, vp, i, i, f, i, vp]
+    l.cb_rmsnorm_fp8.restype = i
+    l.cb_swiglu_fp8.argtypes = [vp, vp, i, vp, i, i, vp]
+    l.cb_swiglu_fp8.restype = i
+    l.cb_wq_gemm_fp8.argtypes = [vp, i, vp, vp, vp, vp, i, vp, i, i, i, i, i, vp, vp, vp, vp, vp]
+    l.cb_wq_gemm_fp8.restype = i
+    l.cb_wq_gemm_fp8_grouped.argtypes = [vp, i, vp, vp, vp, vp, i, i, i, i, vp, i, i, i, i, vp, vp]
+    l.cb_wq_gemm_fp8_grouped.restype = i
 
 
 class TpLinkStruct(ctypes.Structure):

@@ -29,6 +29,7 @@ FMT_CUBIC4 = 0
 FMT_AFFINE4 = 1
 FMT_NVFP4 = 2
 FMT_BF16 = 3
+FMT_FP8 = 4          # e4m3 weights [N, K] as stored in the checkpoint + one fp32 scale per row; W8A8 on the fp8 tensor path
 
 TILE_N = 128
 BLOCK_K = 64
@@ -41,7 +42,7 @@ class PackedWeight:
     k: int
     group_k: int
     codes: torch.Tensor          # uint8 (or bf16 [N, K] for FMT_BF16)
-    meta: torch.Tensor | None    # uint8
+    meta: torch.Tensor | None    # uint8 (fp32 row scales for FMT_FP8)
     alpha: float = 1.0
     act_interleaved: bool = False   # gate / up rows interleaved for the fused SwiGLU epilogue (swiglu_interleave)
 
@@ -51,7 +52,7 @@ class PackedWeight:
 
     @property
     def nbytes(self) -> int:
-        return self.codes.numel() * self.codes.element_size() + (0 if self.meta is None else self.meta.numel())
+        return self.codes.numel() * self.codes.element_size() + (0 if self.meta is None else self.meta.numel() * self.meta.element_size())
 
 
 def _tile_nibbles(nib: torch.Tensor) -> torch.Tensor:
@@ -200,6 +201,20 @@ def pack_bf16(weight: torch.Tensor) -> PackedWeight:
     return PackedWeight(FMT_BF16, n, k, k, weight.to(torch.bfloat16).contiguous(), None)
 
 
+def pack_fp8(weight: torch.Tensor, scale: torch.Tensor) -> PackedWeight:
+    """Channel-scaled e4m3 weights for the fp8 tensor-core GEMM (``tcgen05.mma.kind::f8f6f4``): the checkpoint's bytes
+    are the operand (TMA fetches 128 x 128-byte tiles of the row-major matrix), ``meta`` holds the fp32 row scales.
+    ``weight``: ``torch.float8_e4m3fn`` or its bytes, ``[N, K]``; ``scale``: ``[N]`` or ``[N, 1]``."""
+    n, k = weight.shape
+    if k % BLOCK_K:
+        raise ValueError("K must be a multiple of 64")
+    codes = weight.contiguous().view(torch.uint8)
+    meta = scale.to(torch.float32).reshape(-1).contiguous()
+    if meta.numel() != n:
+        raise ValueError("fp8 weights need one scale per output row")
+    return PackedWeight(FMT_FP8, n, k, k, codes, meta)
+
+
 def swiglu_row_order(inter: int) -> torch.Tensor:
     """Row order of a ``[gate; up]`` matrix (``2 * inter`` rows) for the fused SwiGLU epilogue of the GEMM.
 
@@ -220,6 +235,9 @@ def permute_rows(pw: PackedWeight, order: torch.Tensor) -> PackedWeight:
         raise ValueError("row order must cover every row")
     if pw.fmt == FMT_BF16:
         return PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, pw.codes[order.to(pw.codes.device)].contiguous(), None, pw.alpha)
+    if pw.fmt == FMT_FP8:
+        o = order.to(pw.codes.device)
+        return PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, pw.codes[o].contiguous(), pw.meta[o].contiguous(), pw.alpha)
     nt = pw.codes.shape[0]
     full = torch.cat([order, torch.arange(pw.n, nt * TILE_N)]).to(pw.codes.device)
 
@@ -259,6 +277,8 @@ def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
     """
     if pw.fmt == FMT_BF16:
         return pw.codes.float()
+    if pw.fmt == FMT_FP8:
+        return pw.codes.view(torch.float8_e4m3fn).float() * pw.meta.reshape(-1, 1)
     nt = pw.codes.shape[0]
     if pw.fmt == FMT_CUBIC4:
         c = cubic_codes_from_words(_untile_words(pw.codes))                        # [N_pad, K]

@@ -154,9 +154,13 @@ def fp8_quantize(w: torch.Tensor, block: bool = False) -> dict:
 
 
 def fp8_activation_quantize(x: torch.Tensor):
-    """Dynamic per-token e4m3 activation quantisation (scale floored at 1 / (448 * 512), as the reference does)."""
-    s = (x.float().abs().amax(-1, keepdim=True) / 448.0).clamp_min(1.0 / (448.0 * 512.0))
-    return (x.float() / s).to(torch.float8_e4m3fn), s
+    """Dynamic per-token e4m3 activation quantisation (scale floored at 1 / (448 * 512), as the reference does).  The
+    divisions are carried out in double and rounded once to fp32, i.e. correctly rounded fp32 divisions (a CUDA
+    tensor divided by a Python scalar is multiplied by the scalar's reciprocal, which is one ulp off now and then)."""
+    xf = x.float()
+    s = (xf.abs().amax(-1, keepdim=True).double() / 448.0).float().clamp_min(1.0 / (448.0 * 512.0))
+    q = (xf.double() / s.double()).float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, s
 
 
 # --------------------------------------------------------------------- NVFP4
@@ -222,6 +226,9 @@ def to_packed_weight(method: str, payload: dict, shape: tuple[int, int], bits: i
     if method == "awq":
         q, s, z = awq_decode(payload, group)
         return wq_pack.pack_affine4(q.to(torch.uint8), s, -z * s, group)
+    if method == "fp8" and payload["weight"].dtype == torch.float8_e4m3fn and payload["weight_scale"].numel() == n \
+            and k % 64 == 0:
+        return wq_pack.pack_fp8(payload["weight"], payload["weight_scale"])
     if method in ("fp8", "fp8_block"):
         return wq_pack.pack_bf16(fp8_dense(payload))
     if method == "nvfp4":

@@ -89,14 +89,24 @@ def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str 
     if fmt == "bf16":
         w = wq_pack.pack_bf16(torch.randn(n, k, device=DEV) * 0.02)
         wbytes = n * k * 2
+    elif fmt == "fp8":
+        # e4m3 weights with row scales; the timed call is the GEMM on activations quantized beforehand (the fused
+        # norm / activation kernels produce them in a model step), ``fp8+quant`` adds the stand-alone quantizer
+        from ..quantization import formats
+        p = formats.fp8_quantize(torch.randn(n, k, device=DEV) * 0.02)
+        w = wq_pack.pack_fp8(p["weight"], p["weight_scale"])
+        wbytes = n * k + n * 4
     else:
         w = random_cubic_weight(n, k)
         wbytes = n * k // 2 + n * (k // 128) * 8
     x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
     y = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
-    stream_k = kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(m, n, w.fmt))
-    sp = None if stream_k else (splits or K.choose_splits(m, n, k))
+    stream_k = fmt != "fp8" and (kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(m, n, w.fmt)))
+    sp = None if stream_k else (splits or K.choose_splits(m, n, k, fmt=w.fmt))
+    if fmt == "fp8":
+        x = K.fp8_quantize(x, out=K.Fp8Act(torch.empty(m, k, dtype=torch.uint8, device=DEV),
+                                           torch.empty(m, dtype=torch.float32, device=DEV)))
     if act:
         w = wq_pack.swiglu_interleave(w)
         y = torch.empty(m, n // 2, device=DEV, dtype=torch.bfloat16)
@@ -241,6 +251,9 @@ def main() -> None:
             for n, k in ((6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)):
                 print(json.dumps(bench_gemm(m, n, k, None, a.iters)), flush=True)
         print(json.dumps(bench_gemm(256, 151936, 4096, None, a.iters, "bf16")), flush=True)
+        for m in (16, 256, 4096):
+            for n, k in ((6144, 4096), (24576, 4096), (4096, 12288)):
+                print(json.dumps(bench_gemm(m, n, k, None, a.iters, "fp8")), flush=True)
         for kb, vb in ((8, 8), (4, 8), (4, 4)):
             print(json.dumps(bench_attn(256, 1280, 32, 8, kb, vb, 1, a.iters)), flush=True)
         print(json.dumps(bench_attn(8, 4096, 32, 8, 8, 8, 8, a.iters)), flush=True)

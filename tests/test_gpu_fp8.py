@@ -1,0 +1,115 @@
+"""The fp8 tensor-core path (``tcgen05.mma.kind::f8f6f4``): e4m3 weights with one scale per output row times e4m3
+activations quantized per token, against plain PyTorch fp32 arithmetic on the same codes (the reference checks its FP8
+linear the same way, ``quantization/extensions/fp8/tests`` there)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-20))
+
+
+def _fp8_weight(n, k, dev, seed=0):
+    from cubic_serve_b200.ops import wq_pack
+    from cubic_serve_b200.quantization import formats
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = torch.randn(n, k, device=dev, generator=g) * 0.05
+    w[:: 7] *= 4.0                                            # rows of different magnitude: the row scales matter
+    p = formats.fp8_quantize(w, block=False)
+    return wq_pack.pack_fp8(p["weight"], p["weight_scale"]), p
+
+
+def _oracle(xq, xs, p):
+    return (xq.float() @ p["weight"].float().t()) * xs.reshape(-1, 1) * p["weight_scale"].float().reshape(1, -1)
+
+
+@pytest.mark.parametrize("m,k", [(5, 4096), (256, 1024), (300, 12288), (16, 192)])
+def test_activation_quantizer_matches_the_rule(m, k):
+    from cubic_serve_b200.ops import kernels as K
+    from cubic_serve_b200.quantization import formats
+    dev = torch.device("cuda")
+    x = (torch.randn(m, k, device=dev) * torch.rand(m, 1, device=dev) * 3).to(torch.bfloat16)
+    x[0] = 0                                                  # an all-zero row takes the floor scale
+    a = K.fp8_quantize(x)
+    q_ref, s_ref = formats.fp8_activation_quantize(x)
+    assert torch.equal(a.scale, s_ref.reshape(-1))
+    got = a.q.view(torch.float8_e4m3fn).float()
+    want = q_ref.float()
+    # the kernel divides with round-to-nearest like the oracle; codes are equal
+    assert torch.equal(got, want)
+
+
+def test_fused_norm_and_swiglu_quantizers_equal_the_unfused_chain():
+    from cubic_serve_b200.ops import kernels as K
+    dev = torch.device("cuda")
+    x = torch.randn(40, 4096, device=dev).to(torch.bfloat16)
+    res = torch.randn(40, 4096, device=dev).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(4096, device=dev)).to(torch.bfloat16)
+    r1, r2 = res.clone(), res.clone()
+    plain = K.rmsnorm(x, w, 1e-6, residual=r1)
+    a = K.fp8_quantize(plain)
+    q1, s1 = a.q.clone(), a.scale.clone()
+    b = K.rmsnorm_fp8(x, w, 1e-6, residual=r2)
+    assert torch.equal(r1, r2) and torch.equal(q1, b.q) and torch.equal(s1, b.scale)
+    gu = torch.randn(33, 2 * 1536, device=dev).to(torch.bfloat16)
+    a = K.fp8_quantize(K.swiglu(gu))
+    q1, s1 = a.q.clone(), a.scale.clone()
+    b = K.swiglu_fp8(gu)
+    assert torch.equal(q1, b.q) and torch.equal(s1, b.scale)
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(16, 256, 512, 1), (64, 4096, 4096, None), (256, 6144, 4096, None),
+                                          (256, 4096, 12288, 4), (200, 1000, 1088, 1), (48, 512, 2048, 16),
+                                          (700, 1024, 4096, 1)])
+def test_fp8_gemm_matches_fp32_on_the_same_codes(m, n, k, splits):
+    from cubic_serve_b200.ops import kernels as K
+    dev = torch.device("cuda")
+    pw, p = _fp8_weight(n, k, dev)
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    a = K.fp8_quantize(x)
+    want = _oracle(a.q.view(torch.float8_e4m3fn), a.scale, p)
+    res = torch.randn(m, n, device=dev).to(torch.bfloat16)
+    y = K.wq_gemm(x, pw, residual=res, splits=splits)
+    torch.cuda.synchronize()
+    K.workspace(dev).check_status()
+    assert _rel(y.float() - res.float(), want) < 6e-3          # bf16 rounding of the output (plus the residual's)
+    # against the unquantized product the error is the two quantizations'
+    assert _rel(y.float() - res.float(), x.float() @ (p["weight"].float() * p["weight_scale"].float()).t()) < 5e-2
+
+
+def test_fp8_gemm_with_swiglu_epilogue_and_grouped_experts():
+    from cubic_serve_b200.models import moe
+    from cubic_serve_b200.ops import kernels as K
+    from cubic_serve_b200.ops import wq_pack
+    dev = torch.device("cuda")
+    inter, h, m = 1536, 2048, 96
+    pw, p = _fp8_weight(2 * inter, h, dev, seed=3)
+    x = torch.randn(m, h, device=dev).to(torch.bfloat16)
+    a = K.fp8_quantize(x)
+    gu = _oracle(a.q.view(torch.float8_e4m3fn), a.scale, p).to(torch.bfloat16).float()
+    want = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+    act = K.wq_gemm_act(x, wq_pack.swiglu_interleave(pw))
+    torch.cuda.synchronize()
+    assert _rel(act, want) < 8e-3
+    # grouped: 4 experts, top-2 routing through the MoE layer against the dense oracle
+    E, top_k, I = 4, 2, 256
+    gus, downs, gu_d, dn_d = [], [], [], []
+    for e in range(E):
+        a_pw, a_p = _fp8_weight(2 * I, h, dev, seed=10 + e)
+        b_pw, b_p = _fp8_weight(h, I, dev, seed=20 + e)
+        gus.append(a_pw); downs.append(b_pw)
+        gu_d.append(wq_pack.unpack_to_dense(a_pw)); dn_d.append(wq_pack.unpack_to_dense(b_pw))
+    gu_s, gcs, gms = moe.stack_experts(gus)
+    dn_s, dcs, dms = moe.stack_experts(downs)
+    router = (torch.randn(E, h, device=dev) * 0.05).to(torch.bfloat16)
+    layer = moe.MoeLayer(wq_pack.pack_bf16(router), gu_s, dn_s, (gcs, gms, dcs, dms), E, top_k, 0, E)
+    layer.fuse_activation()
+    t = 50
+    xt = torch.randn(t, h, device=dev).to(torch.bfloat16)
+    y = layer.forward(xt)
+    torch.cuda.synchronize()
+    K.workspace(dev).check_status()
+    want = moe.moe_reference(xt, router, gu_d, dn_d, top_k)
+    assert _rel(y, want) < 6e-2                                # the oracle multiplies unquantized activations
