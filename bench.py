@@ -38,6 +38,9 @@ def parse_args():
     ap.add_argument("--input-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collective path")
+    ap.add_argument("--weights", default="", choices=["", "fp8"],
+                    help="weight format instead of the config's own (fp8: e4m3 weights with row scales, per-token e4m3 "
+                         "activations, fp8 tensor cores; a different benchmark than the 4-bit headline)")
     ap.add_argument("--pp", type=int, default=1, choices=[1, 2], help="pipeline stages (tp = gpus / pp)")
     ap.add_argument("--kv", default="", help="K,V cache bits, e.g. 8,8 or 4,8 (default: 8,8 dense, 4,8 MoE)")
     ap.add_argument("--prefill-tokens", type=int, default=8192, help="token budget of a prefill step")
@@ -133,6 +136,11 @@ def main() -> None:
     if args.layers:
         from dataclasses import replace
         cfg = replace(cfg, num_layers=args.layers)
+    if args.weights == "fp8":
+        from dataclasses import replace
+        cfg = replace(cfg, quant=replace(cfg.quant, method="fp8", bits=8, group_size=0))
+        if args.comm == "fused" and args.gpus > 1:
+            args.comm = "nccl"          # the fp8 activation quantizer is a kernel of its own (see DecoderRunner)
     k_bits, v_bits = (int(b) for b in (args.kv or ("4,8" if cfg.is_moe else "8,8")).split(","))
     tp = pp = None
     tp_size, tp_rank, layer_range = world // args.pp, rank % (world // args.pp), None

@@ -247,6 +247,11 @@ class DecoderRunner:
         self.pp = pp                # parallel.pp.PipelineStage or None
         if pp is not None and tp is not None and tp.fused is not None:
             raise ValueError("pipeline stages use the NCCL tensor-parallel collectives (tp mode 'nccl')")
+        if tp is not None and tp.fused is not None and any(
+                pw is not None and pw.fmt == wq_pack.FMT_FP8 for lw in weights.layers for pw in (lw.qkv, lw.o, lw.gate_up, lw.down)):
+            # the fp8 GEMM's activation operand is quantized per token by a kernel of its own, which would read rows
+            # that the fused all-gather has not delivered yet
+            raise ValueError("FP8 weights run with the NCCL tensor-parallel collectives (tp mode 'nccl')")
         self.tp_size = tp.size if tp is not None else 1
         self.k_bits, self.v_bits = k_bits, v_bits
         self.kv_rotation = kv_rotation
@@ -380,14 +385,24 @@ class DecoderRunner:
             if self.tp is not None:
                 self.tp.all_reduce(h)
         pending = None  # partial sum waiting to be folded into h by the next norm (TP > 1)
+        fp8 = wq_pack.FMT_FP8
+
+        def norm(src, weight, residual, consumers):
+            """RMSNorm into ``x``; when every consumer of the result is an fp8 GEMM the norm kernel quantizes its own
+            output per token and the e4m3 operand is returned instead (no bf16 round trip, no extra launch)."""
+            if consumers and all(c is not None and c.fmt == fp8 for c in consumers):
+                return K.rmsnorm_fp8(src, weight, cfg.rms_eps, residual=residual, zero_centered=cfg.zero_centered_norm,
+                                     ws=self.ws)
+            return K.rmsnorm(src, weight, cfg.rms_eps, out=x, residual=residual, zero_centered=cfg.zero_centered_norm)
+
         for li, lw in enumerate(w.layers):
-            K.rmsnorm(pending if pending is not None else h, lw.ln1, cfg.rms_eps, out=x,
-                      residual=h if pending is not None else None, zero_centered=cfg.zero_centered_norm)
+            xin = norm(pending if pending is not None else h, lw.ln1, h if pending is not None else None,
+                       [] if lw.gdn is not None else [lw.qkv] + ([lw.attn_gate] if lw.attn_gate is not None else []))
             if lw.gdn is not None:
                 mixed, o_w = self._gdn_mixer(li, lw.gdn, x, b, t0, t1), lw.gdn.out
                 n += 5
             else:
-                K.wq_gemm(x, lw.qkv, out=qkv, ws=self.ws)
+                K.wq_gemm(xin, lw.qkv, out=qkv, ws=self.ws)
                 K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
                                 self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
                                 rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation)
@@ -400,19 +415,21 @@ class DecoderRunner:
                     n += 1
                 if lw.attn_gate is not None:
                     gate = self.gate[t0:t1]
-                    K.wq_gemm(x, lw.attn_gate, out=gate, ws=self.ws)
+                    K.wq_gemm(xin, lw.attn_gate, out=gate, ws=self.ws)
                     K.sigmoid_gate(attn, gate)
                     n += 2
                 mixed, o_w = attn, lw.o
+            ffn_in = [] if lw.moe is not None else [lw.gate_up]
             if self.tp is None:
                 K.wq_gemm(mixed, o_w, out=h, residual=h, ws=self.ws)
-                K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x, zero_centered=cfg.zero_centered_norm)
+                xin = norm(h, lw.ln2, None, ffn_in)
             else:
                 part = self.part[t0:t1]
                 K.wq_gemm(mixed, o_w, out=part, ws=self.ws)
                 self.tp.all_reduce(part)
-                K.rmsnorm(part, lw.ln2, cfg.rms_eps, out=x, residual=h, zero_centered=cfg.zero_centered_norm)
-            n += 2
+                xin = norm(part, lw.ln2, h, ffn_in)
+            # fp8 projections whose input is not a norm's output (attention output, activation) quantize it first
+            n += 2 + (o_w.fmt == fp8) + (lw.moe is None and lw.down.fmt == fp8)
             if lw.moe is not None:
                 n += lw.moe.launches
                 if self.tp is None:
@@ -424,7 +441,7 @@ class DecoderRunner:
                     pending = out
             else:
                 gu, act = self.gu[t0:t1], self.act[t0:t1]
-                n += 1 + K.gate_up_act(x, lw.gate_up, gu, act, ws=self.ws)
+                n += 1 + K.gate_up_act(xin, lw.gate_up, gu, act, ws=self.ws)
                 if self.tp is None:
                     K.wq_gemm(act, lw.down, out=h, residual=h, ws=self.ws)
                 else:

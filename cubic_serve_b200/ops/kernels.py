@@ -214,6 +214,8 @@ def swiglu_fp8(gate_up: torch.Tensor, ws: Workspace | None = None) -> Fp8Act:
 def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link, swiglu: bool) -> torch.Tensor:
     """The fp8 branch of ``wq_gemm`` / ``wq_gemm_act``: quantize the activations per token unless the caller already
     holds them as ``Fp8Act``, then e4m3 x e4m3 on the tensor cores with both scales applied in the epilogue."""
+    if link is not None and (link.mode & 1) and not isinstance(x, Fp8Act):
+        raise ValueError("an fp8 GEMM cannot wait for gathered rows: its quantizer would read them before they arrive")
     a = x if isinstance(x, Fp8Act) else fp8_quantize(x, ws)
     m, k = a.q.shape
     push = link is not None and (link.mode & 2)

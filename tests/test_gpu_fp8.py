@@ -113,3 +113,33 @@ def test_fp8_gemm_with_swiglu_epilogue_and_grouped_experts():
     K.workspace(dev).check_status()
     want = moe.moe_reference(xt, router, gu_d, dn_d, top_k)
     assert _rel(y, want) < 6e-2                                # the oracle multiplies unquantized activations
+
+
+def test_fp8_model_step_tracks_the_same_model_with_dequantized_weights():
+    """A decoder whose projections are FP8 (W8A8 on the fp8 tensor path, quantizers fused behind the norms) against the
+    same weights dequantized to bf16 (W16A16): the logits differ by the activation quantization only."""
+    import dataclasses
+    import numpy as np
+    from cubic_serve_b200.models.config import toy_config
+    from cubic_serve_b200.models.decoder import random_decoder_weights
+    from cubic_serve_b200.ops import wq_pack
+    from cubic_serve_b200.parallel.tp_check import _rel_rows, _step_logits
+    dev = torch.device("cuda")
+    cfg = dataclasses.replace(toy_config(), num_layers=3, hidden_size=512, intermediate_size=1024, num_q_heads=4,
+                              num_kv_heads=2, head_dim=128, vocab_size=1024)
+    cfg = dataclasses.replace(cfg, quant=dataclasses.replace(cfg.quant, method="fp8", bits=8, group_size=0))
+    w8 = random_decoder_weights(cfg, dev, seed=1, std=0.05)
+    assert w8.layers[0].qkv.fmt == wq_pack.FMT_FP8 and w8.layers[0].down.fmt == wq_pack.FMT_FP8
+    w16 = random_decoder_weights(cfg, dev, seed=1, std=0.05)
+    for lw in w16.layers:
+        for name in ("qkv", "o", "gate_up", "down"):
+            setattr(lw, name, wq_pack.pack_bf16(wq_pack.unpack_to_dense(getattr(lw, name))))
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(6, 40)).tolist()
+    (a0, a1), ids8 = _step_logits(cfg, w8, dev, None, prompts, 8, 8)
+    (b0, b1), ids16 = _step_logits(cfg, w16, dev, None, prompts, 8, 8)
+    # a dozen GEMMs with e4m3 activations (3 mantissa bits, ~2.5 % rms each) lie between the embedding and the logits;
+    # the decode step is compared where both models sampled the same first token
+    same = torch.tensor([a == b for a, b in zip(ids8[0], ids16[0])], device=dev)
+    err = torch.cat([_rel_rows(a0, b0), _rel_rows(a1, b1)[same]])
+    assert float(err.max()) < 0.25, err
+    assert float(err.median()) < 0.16, err
