@@ -63,11 +63,13 @@ __device__ __forceinline__ uint2 pack_e4m3x8(const float (&v)[8], float scale) {
 // MODE 0: q = quant(x)                                   (x bf16 [rows, K], row stride ldx)
 // MODE 1: q = quant(bf16(rmsnorm(x [+ residual]) * w))   (the residual sum is written back like rmsnorm_kernel)
 // MODE 2: q = quant(bf16(silu(x[:, :K]) * x[:, K:]))     (x = [gate | up], 2 K columns)
+// `phase` (MODE 0 only) splits the work for operands whose K dimension is sharded over tensor-parallel ranks: 1 = write
+// the row's scale only (the ranks then take the maximum of their scales), 2 = quantize with the scale found in `scales`.
 template <int MODE>
 __global__ void __launch_bounds__(kQThreads)
 fp8_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* residual, __nv_bfloat16* residual_out,
                 const __nv_bfloat16* __restrict__ w, float eps, int zero_centered, uint8_t* __restrict__ q, int ldq,
-                float* __restrict__ scales, int K) {
+                float* __restrict__ scales, int K, int phase) {
   __shared__ float red[8];
   const size_t row = blockIdx.x;
   const int nvec = K >> 3;
@@ -143,9 +145,15 @@ fp8_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat1
       }
     }
   }
-  amax = block_max(amax, red);
-  const float scale = fmaxf(__fdiv_rn(amax, kFp8Max), kFp8MinScale);
-  if (threadIdx.x == 0) scales[row] = scale;
+  float scale;
+  if (phase == 2) {
+    scale = scales[row];
+  } else {
+    amax = block_max(amax, red);
+    scale = fmaxf(__fdiv_rn(amax, kFp8Max), kFp8MinScale);
+    if (threadIdx.x == 0) scales[row] = scale;
+    if (phase == 1) return;
+  }
   uint8_t* qr = q + row * ldq;
 #pragma unroll
   for (int it = 0; it < kQMaxVec; ++it) {
@@ -173,7 +181,23 @@ int cb_fp8_quantize_rows(const void* x, int ldx, void* q, int ldq, void* scales,
   return static_cast<int>(launch(fp8_rows_kernel<0>, dim3(rows), dim3(kQThreads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(nullptr),
       static_cast<__nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(nullptr), 0.f, 0,
-      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), K));
+      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), K, 0));
+}
+
+// The same in two launches for an operand whose K dimension is sharded over tensor-parallel ranks: phase 1 writes
+// every row's local scale, the caller reduces `scales` with MAX over the ranks, phase 2 quantizes with the result --
+// every rank then uses the scale the unsharded row would have had (reference: the `_ScaleCollective` all_reduce(MAX)
+// of its FP8 linears, quantization/extensions/fp8/linear.py there).
+int cb_fp8_quantize_rows_phase(const void* x, int ldx, void* q, int ldq, void* scales, int rows, int K, int phase,
+                               void* stream) {
+  using namespace cb;
+  const int c = fp8_check(rows, K, ldq);
+  if (c) return c < 0 ? c : 0;
+  if (ldx % 8 != 0 || (phase != 1 && phase != 2)) return -10;
+  return static_cast<int>(launch(fp8_rows_kernel<0>, dim3(rows), dim3(kQThreads), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(nullptr),
+      static_cast<__nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(nullptr), 0.f, 0,
+      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), K, phase));
 }
 
 // RMSNorm (optionally of x + residual, the sum written to residual_out) whose output leaves as e4m3 + scales.
@@ -185,7 +209,7 @@ int cb_rmsnorm_fp8(const void* x, const void* residual, void* residual_out, cons
   return static_cast<int>(launch(fp8_rows_kernel<1>, dim3(rows), dim3(kQThreads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(x), H, static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(residual_out), static_cast<const __nv_bfloat16*>(w), eps, zero_centered,
-      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), H));
+      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), H, 0));
 }
 
 // SwiGLU of gate_up [rows, 2 I] whose output leaves as e4m3 [rows, I] + scales.
@@ -196,7 +220,7 @@ int cb_swiglu_fp8(const void* gate_up, void* q, int ldq, void* scales, int rows,
   return static_cast<int>(launch(fp8_rows_kernel<2>, dim3(rows), dim3(kQThreads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(gate_up), 2 * I, static_cast<const __nv_bfloat16*>(nullptr),
       static_cast<__nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(nullptr), 0.f, 0,
-      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), I));
+      static_cast<uint8_t*>(q), ldq, static_cast<float*>(scales), I, 0));
 }
 
 }  // extern "C"

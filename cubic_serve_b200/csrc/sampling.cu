@@ -234,6 +234,121 @@ __global__ void verify_greedy_kernel(const int* target_ids, const int* draft_ids
   bonus[r] = target_ids[r * (max_depth + 1) + a];
 }
 
+// Speculative verification for SAMPLED requests: p / q rejection sampling over sparse candidate distributions
+// (reference: generation/tp_sampling.py:154-217 verify_speculative_chain, ops/cuda/sampling/speculative.py:54).
+// Row (r, i) of `q_*` holds the draft head's top candidates when it proposed draft token i, row (r, i) of `p_*` the
+// target's candidates after consuming the root and drafts 0 .. i - 1 ([.., kMaxTopK] (value desc, id asc), padded
+// with (-inf, INT_MAX)).  Both are shaped by the request's temperature / top-k / top-p exactly like a plain draw.
+//   accept draft i  iff  q(d_i) > 0 and u_i < min(1, p(d_i) / q(d_i));
+//   at the first rejection the next token is drawn from normalise(max(0, p - q)) (from p if that is empty);
+//   with every draft accepted the bonus token is drawn from the last target row.
+// A greedy request (temperature 0) has one-hot p and q: the rule reduces to the longest-matching-prefix check.
+// Uniforms come from the request's Philox stream at counter draws | (sub-draw + 1) << 40: sub-draw 2 i decides draft
+// i, sub-draw 2 i + 1 draws its replacement, sub-draw 2 depth draws the bonus token, so a replay of the round draws
+// the same numbers.  emitted[r] = accepted drafts followed by the next token ([.., max_depth + 1]).
+struct VerifySampledParams {
+  const float* q_val; const int* q_id;      // [requests, max_depth, kMaxTopK]
+  const float* p_val; const int* p_id;      // [requests, max_depth + 1, kMaxTopK]
+  const int* draft_ids;                     // [requests, max_depth]
+  const int* depth;                         // [requests]
+  const float* temperature; const float* top_p; const int* top_k;
+  const unsigned long long* seeds; const unsigned long long* counters;
+  int* accepted; int* bonus; int* emitted;
+  int max_depth, requests;
+};
+
+// Shaped probabilities of one candidate row; returns the number of real candidates kept (the rest get 0).
+__device__ __forceinline__ int shaped_probs(const float* val, const int* id, float temp, float tp, int top_k, float* probs) {
+  int K = 0;
+  const int cap = temp <= 0.f ? 1 : ((top_k <= 0 || top_k > kMaxTopK) ? kMaxTopK : top_k);
+  while (K < cap && id[K] != 0x7fffffff && val[K] > -INFINITY) ++K;
+  for (int k = 0; k < kMaxTopK; ++k) probs[k] = 0.f;
+  if (K == 0) return 0;
+  if (temp <= 0.f) { probs[0] = 1.f; return 1; }
+  const float inv_t = 1.f / temp;
+  float sum = 0.f;
+  for (int k = 0; k < K; ++k) { probs[k] = __expf((val[k] - val[0]) * inv_t); sum += probs[k]; }
+  int keep = K;
+  if (tp < 1.f) {
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) { acc += probs[k] / sum; if (acc >= tp) { keep = k + 1; break; } }
+  }
+  float ksum = 0.f;
+  for (int k = 0; k < keep; ++k) ksum += probs[k];
+  for (int k = 0; k < kMaxTopK; ++k) probs[k] = k < keep ? probs[k] / ksum : 0.f;
+  return keep;
+}
+
+__device__ __forceinline__ int draw_index(const float* probs, int n, float u) {
+  float total = 0.f;
+  for (int k = 0; k < n; ++k) total += probs[k];
+  float acc = 0.f;
+  int pick = -1;
+  for (int k = 0; k < n; ++k) {
+    if (probs[k] <= 0.f) continue;
+    pick = k;                                  // the last candidate with mass catches rounding at the top end
+    acc += probs[k];
+    if (u * total < acc) break;
+  }
+  return pick;
+}
+
+__global__ void __launch_bounds__(64)
+verify_sampled_kernel(const VerifySampledParams p) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  pdl_launch_dependents();
+  if (r >= p.requests) return;
+  const int D = p.max_depth, d = min(p.depth[r], D);
+  const float temp = p.temperature ? p.temperature[r] : 0.f;
+  const float tp = p.top_p ? p.top_p[r] : 1.f;
+  const int tk = p.top_k ? p.top_k[r] : 0;
+  const unsigned long long seed = p.seeds ? p.seeds[r] : 0ull;
+  const unsigned long long base = p.counters ? p.counters[r] : 0ull;
+  auto uniform = [&](int sub) { return philox_uniform(seed, base | (static_cast<unsigned long long>(sub + 1) << 40)); };
+  float pp[kMaxTopK], qq[kMaxTopK];
+  int* out = p.emitted + static_cast<size_t>(r) * (D + 1);
+  int a = 0, next = 0;
+  bool done = false;
+  for (; a < d; ++a) {
+    const float* pv = p.p_val + (static_cast<size_t>(r) * (D + 1) + a) * kMaxTopK;
+    const int* pi = p.p_id + (static_cast<size_t>(r) * (D + 1) + a) * kMaxTopK;
+    const float* qv = p.q_val + (static_cast<size_t>(r) * D + a) * kMaxTopK;
+    const int* qi = p.q_id + (static_cast<size_t>(r) * D + a) * kMaxTopK;
+    const int np_ = shaped_probs(pv, pi, temp, tp, tk, pp);
+    const int nq = shaped_probs(qv, qi, temp, tp, tk, qq);
+    const int tok = p.draft_ids[r * D + a];
+    float pd = 0.f, qd = 0.f;
+    for (int k = 0; k < np_; ++k) if (pi[k] == tok) pd = pp[k];
+    for (int k = 0; k < nq; ++k) if (qi[k] == tok) qd = qq[k];
+    if (qd > 0.f && uniform(2 * a) < fminf(1.f, pd / qd)) { out[a] = tok; continue; }
+    // rejected: residual max(0, p - q) over the target's candidates
+    float res[kMaxTopK];
+    float mass = 0.f;
+    for (int k = 0; k < kMaxTopK; ++k) {
+      float q_here = 0.f;
+      if (k < np_) for (int j = 0; j < nq; ++j) if (qi[j] == pi[k]) q_here = qq[j];
+      res[k] = k < np_ ? fmaxf(0.f, pp[k] - q_here) : 0.f;
+      mass += res[k];
+    }
+    const int pick = mass > 0.f ? draw_index(res, np_, uniform(2 * a + 1)) : draw_index(pp, np_, uniform(2 * a + 1));
+    next = pick >= 0 ? pi[pick] : (np_ > 0 ? pi[0] : 0);
+    done = true;
+    break;
+  }
+  if (!done) {
+    const float* pv = p.p_val + (static_cast<size_t>(r) * (D + 1) + d) * kMaxTopK;
+    const int* pi = p.p_id + (static_cast<size_t>(r) * (D + 1) + d) * kMaxTopK;
+    const int np_ = shaped_probs(pv, pi, temp, tp, tk, pp);
+    const int pick = draw_index(pp, np_, uniform(2 * d));
+    next = pick >= 0 ? pi[pick] : 0;
+    a = d;
+  }
+  out[a] = next;
+  p.accepted[r] = a;
+  p.bonus[r] = next;
+}
+
 // Thinking-token budgets, enforced on the device so that decode graphs (and steps launched ahead of the host) need no
 // host decision: an integer state machine per request slot, run on every sampled id right after the sampler.
 //   left[slot]  >= 0: the request is in its reasoning phase and may still emit that many thinking tokens; < 0: inactive
@@ -337,6 +452,27 @@ int cb_verify_greedy(const void* target_ids, const void* draft_ids, const void* 
       static_cast<const int*>(target_ids), static_cast<const int*>(draft_ids), static_cast<const int*>(depth),
       max_depth, static_cast<const int*>(forced_reject_at), static_cast<int*>(accepted), static_cast<int*>(bonus),
       requests));
+}
+
+// p / q rejection sampling of a speculative round (see verify_sampled_kernel); candidate arrays as written by
+// cb_sample_candidates, `emitted` [requests, max_depth + 1] receives the accepted drafts and the next token.
+int cb_verify_sampled(const void* q_val, const void* q_id, const void* p_val, const void* p_id, const void* draft_ids,
+                      const void* depth, int max_depth, const void* temperature, const void* top_p, const void* top_k,
+                      const void* seeds, const void* counters, void* accepted, void* bonus, void* emitted, int requests,
+                      void* stream) {
+  if (requests <= 0) return 0;
+  if (max_depth <= 0) return -10;
+  cb::VerifySampledParams p;
+  p.q_val = static_cast<const float*>(q_val); p.q_id = static_cast<const int*>(q_id);
+  p.p_val = static_cast<const float*>(p_val); p.p_id = static_cast<const int*>(p_id);
+  p.draft_ids = static_cast<const int*>(draft_ids); p.depth = static_cast<const int*>(depth);
+  p.temperature = static_cast<const float*>(temperature); p.top_p = static_cast<const float*>(top_p);
+  p.top_k = static_cast<const int*>(top_k);
+  p.seeds = static_cast<const unsigned long long*>(seeds); p.counters = static_cast<const unsigned long long*>(counters);
+  p.accepted = static_cast<int*>(accepted); p.bonus = static_cast<int*>(bonus); p.emitted = static_cast<int*>(emitted);
+  p.max_depth = max_depth; p.requests = requests;
+  return static_cast<int>(cb::launch(cb::verify_sampled_kernel, dim3((requests + 63) / 64), dim3(64), 0,
+                                     static_cast<cudaStream_t>(stream), p));
 }
 
 // ids[rows] (in place), row_slot / init [rows], left / fpos [slots]; `seq` = 1..4 tokens of the forced end sequence

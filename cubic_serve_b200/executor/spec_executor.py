@@ -1,9 +1,14 @@
-"""Speculative decoding round on the GPU: MTP proposals -> target review -> greedy verification.
+"""Speculative decoding round on the GPU: MTP proposals -> target review -> verification (greedy, or p / q rejection
+sampling when a request of the round samples).
 
 One round, in the order of the reference's ``execute_draft_batch`` (``runtime/performance.py:7189-7556`` there):
 (1) proposal passes of the MTP head, depth by depth, chaining draft tokens and hidden states on the device;
 (2) ONE target pass over ``[root, d1 .. dK]`` per request (segment length K + 1, every row sampled);
-(3) greedy verification on the device (longest matching prefix, bonus token = the target's choice after it);
+(3) verification on the device: greedy requests keep the longest matching prefix (bonus token = the target's choice
+    after it); with a sampling request in the round every draft is DRAWN from the head's shaped distribution q and
+    accepted with probability min(1, p / q) against the target's p, the first rejected position is redrawn from
+    normalise(max(0, p - q)) (``csrc/sampling.cu::verify_sampled_kernel``; reference
+    ``generation/tp_sampling.py:154-217``), so the emitted tokens are distributed as plain sampling from p;
 (4) the hidden state of the last accepted position becomes the head's input for the next round.
 Rejected positions need no repair: their KV slots are simply rewritten by the next round.
 
@@ -21,6 +26,8 @@ from .gpu_executor import GpuExecutor, Segment
 
 
 class SpeculativeGpuExecutor(GpuExecutor):
+    speculative_sampling = True      # rounds also serve requests with temperature > 0 (p / q rejection sampling)
+
     def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
                  **kw) -> None:
         if runner.cfg.is_hybrid:
@@ -43,6 +50,13 @@ class SpeculativeGpuExecutor(GpuExecutor):
         self.depth_t = torch.full((rows,), depth, dtype=torch.int32, device=dev)
         self.forced = torch.zeros(rows, dtype=torch.int32, device=dev)
         self.mtp_logits = torch.empty(rows, runner.w.lm_head.n, dtype=torch.bfloat16, device=dev)
+        # candidate distributions of a sampled round: the head's (q) per draft, the target's (p) per review row
+        C = K.SAMPLE_CANDIDATES
+        self.q_val = torch.zeros(rows * depth, C, dtype=torch.float32, device=dev)
+        self.q_id = torch.zeros(rows * depth, C, dtype=torch.int32, device=dev)
+        self.p_val = torch.zeros(rows * (depth + 1), C, dtype=torch.float32, device=dev)
+        self.p_id = torch.zeros(rows * (depth + 1), C, dtype=torch.int32, device=dev)
+        self.cand_tmp = (torch.zeros(rows, C, dtype=torch.float32, device=dev), torch.zeros(rows, C, dtype=torch.int32, device=dev))
         self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0}
 
     # ------------------------------------------------------------- plain steps
@@ -110,6 +124,17 @@ class SpeculativeGpuExecutor(GpuExecutor):
         draft_ids = self.draft_ids.view(-1)[:R * Kd].view(R, Kd)
         target_ids = self.target_ids.view(-1)[:R * (Kd + 1)].view(R, Kd + 1)
         self.depth_t[:R].copy_(torch.tensor(per_req, dtype=torch.int32), non_blocking=True)
+        # a round with a sampling request draws its drafts and verifies by rejection sampling; forced acceptance is a
+        # benchmark device of the greedy path
+        self._sampling = None
+        if any(s.temperature > 0 for s in segs) and self.force_acceptance is None:
+            self._sampling = {
+                "temperature": torch.tensor([s.temperature for s in segs], dtype=torch.float32, device=dev),
+                "top_p": torch.tensor([s.top_p for s in segs], dtype=torch.float32, device=dev),
+                "top_k": torch.tensor([s.top_k for s in segs], dtype=torch.int32, device=dev),
+                "seeds": torch.tensor([s.seed for s in segs], dtype=torch.int64, device=dev),
+                "draws": torch.tensor([s.draw for s in segs], dtype=torch.int64, device=dev)}
+        sm = self._sampling
         with torch.cuda.stream(self.stream):
             ev0, ev1 = self._ev[0]
             if not hasattr(self, "_ev_mid"):
@@ -128,7 +153,18 @@ class SpeculativeGpuExecutor(GpuExecutor):
                 hid = self.mtp.forward(b, prev)
                 lg = self.mtp.logits(hid, R, self.mtp_logits)
                 tmp = self.out_ids[:R]
-                K.sample(lg, tmp, vocab=lg.shape[1])
+                if sm is None:
+                    K.sample(lg, tmp, vocab=lg.shape[1])
+                else:
+                    # the draft is drawn from the head's shaped distribution; its candidates are kept as q.  Draft draws
+                    # live in their own part of the request's Philox stream (sub-stream 0x4000 + depth)
+                    cv, ci = self.cand_tmp[0][:R], self.cand_tmp[1][:R]
+                    K.sample_candidates(lg, cv, ci, temperature=sm["temperature"], top_k=sm["top_k"], vocab=lg.shape[1])
+                    self.q_val[:R * Kd].view(R, Kd, -1)[:, d].copy_(cv)
+                    self.q_id[:R * Kd].view(R, Kd, -1)[:, d].copy_(ci)
+                    K.sample(lg, tmp, temperature=sm["temperature"], top_p=sm["top_p"], top_k=sm["top_k"],
+                             seeds=sm["seeds"], counters=sm["draws"] | ((0x4000 + d) << 40), vocab=lg.shape[1])
+                    launches += 3
                 draft_ids[:, d].copy_(tmp)
                 prev = hid[:R].clone()
                 launches += self.mtp.launches + 4
@@ -179,6 +215,16 @@ class SpeculativeGpuExecutor(GpuExecutor):
         b.num_logit_rows = T
         hidden = r.forward_hidden(b)
         logits = r.forward_logits(b, hidden, self._review_logits(T))
+        sm = getattr(self, "_sampling", None)
+        if sm is not None:
+            # p / q rejection sampling over the candidate distributions; `target_ids` receives the emitted tokens
+            rep = lambda t: t.repeat_interleave(Kd + 1)                                # noqa: E731
+            K.sample_candidates(logits, self.p_val[:T], self.p_id[:T], temperature=rep(sm["temperature"]),
+                                top_k=rep(sm["top_k"]), vocab=logits.shape[1])
+            K.verify_sampled(self.q_val, self.q_id, self.p_val, self.p_id, draft_ids, self.depth_t[:R], Kd,
+                             sm["temperature"], sm["top_p"], sm["top_k"], sm["seeds"], sm["draws"], self.accepted,
+                             self.bonus, target_ids)
+            return hidden
         K.sample(logits, target_ids.view(-1), vocab=logits.shape[1])
         forced = None
         if self.force_acceptance is not None:
@@ -200,6 +246,8 @@ class SpeculativeGpuExecutor(GpuExecutor):
 
 
 class NgramSpeculativeGpuExecutor(SpeculativeGpuExecutor):
+    speculative_sampling = False     # prompt-lookup drafts are verified against the target's greedy choice only
+
     """Speculative rounds whose drafts come from the host (n-gram / prompt lookup, ``runtime/ngram.py``): no draft
     model, no proposal passes, no carried hidden state -- a round is the target review over ``[root, d1 .. dk]`` plus
     the device-side verification.  Requests without a draft take part with depth 0 (their row is a plain decode row);

@@ -395,6 +395,14 @@ class DecoderRunner:
                                      ws=self.ws)
             return K.rmsnorm(src, weight, cfg.rms_eps, out=x, residual=residual, zero_centered=cfg.zero_centered_norm)
 
+        def row_in(t, weight):
+            """Input of a row-parallel projection under tensor parallelism: an fp8 projection's operand is quantized
+            with the MAX over the ranks of the per-token scales, i.e. with the scale of the unsharded row, so that
+            the partition does not change the codes (the reference's scale collective)."""
+            if weight.fmt != fp8:
+                return t
+            return K.fp8_quantize(t, self.ws, scale_max=self.tp.all_reduce_max)
+
         for li, lw in enumerate(w.layers):
             xin = norm(pending if pending is not None else h, lw.ln1, h if pending is not None else None,
                        [] if lw.gdn is not None else [lw.qkv] + ([lw.attn_gate] if lw.attn_gate is not None else []))
@@ -425,11 +433,12 @@ class DecoderRunner:
                 xin = norm(h, lw.ln2, None, ffn_in)
             else:
                 part = self.part[t0:t1]
-                K.wq_gemm(mixed, o_w, out=part, ws=self.ws)
+                K.wq_gemm(row_in(mixed, o_w), o_w, out=part, ws=self.ws)
                 self.tp.all_reduce(part)
                 xin = norm(part, lw.ln2, h, ffn_in)
             # fp8 projections whose input is not a norm's output (attention output, activation) quantize it first
-            n += 2 + (o_w.fmt == fp8) + (lw.moe is None and lw.down.fmt == fp8)
+            per_quant = 1 if self.tp is None else 3          # sharded operands: scale, MAX over ranks, quantize
+            n += 2 + per_quant * ((o_w.fmt == fp8) + (lw.moe is None and lw.down.fmt == fp8))
             if lw.moe is not None:
                 n += lw.moe.launches
                 if self.tp is None:
@@ -446,7 +455,7 @@ class DecoderRunner:
                     K.wq_gemm(act, lw.down, out=h, residual=h, ws=self.ws)
                 else:
                     part = self.part[t0:t1]
-                    K.wq_gemm(act, lw.down, out=part, ws=self.ws)
+                    K.wq_gemm(row_in(act, lw.down), lw.down, out=part, ws=self.ws)
                     self.tp.all_reduce(part)
                     pending = part
         if pending is not None:

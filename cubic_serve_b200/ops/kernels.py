@@ -169,16 +169,27 @@ class Fp8Act:
         return self.q.device
 
 
-def fp8_quantize(x: torch.Tensor, ws: Workspace | None = None, out: Fp8Act | None = None) -> Fp8Act:
+def fp8_quantize(x: torch.Tensor, ws: Workspace | None = None, out: Fp8Act | None = None, scale_max=None) -> Fp8Act:
     """Dynamic per-token e4m3 quantization of ``x [M, K]`` (bf16): ``scale = max(amax / 448, 1 / (448 * 512))``,
     ``q = e4m3(x / scale)`` (the reference's rule, ``quantization/extensions/fp8/reference.py:47-59`` there).  Without
-    ``out`` the result lives in the workspace's fp8 buffers until the next quantization."""
+    ``out`` the result lives in the workspace's fp8 buffers until the next quantization.
+
+    ``scale_max``: a callable that reduces the fp32 scale vector in place with MAX over the tensor-parallel ranks; given
+    for operands whose K dimension is sharded, so that every rank quantizes with the scale of the whole row."""
     m, k = x.shape
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1
     if out is None:
         ws = ws or workspace(x.device)
         ws.ensure_fp8(m, k)
         out = Fp8Act(ws.fp8_q[:m * k].view(m, k), ws.fp8_scale[:m])
+    if scale_max is not None:
+        for phase in (1, 2):
+            code = native.lib().cb_fp8_quantize_rows_phase(x.data_ptr(), x.stride(0), out.q.data_ptr(), out.q.stride(0),
+                                                           out.scale.data_ptr(), m, k, phase, _stream())
+            native.check(code, "cb_fp8_quantize_rows_phase")
+            if phase == 1:
+                scale_max(out.scale)
+        return out
     code = native.lib().cb_fp8_quantize_rows(x.data_ptr(), x.stride(0), out.q.data_ptr(), out.q.stride(0),
                                              out.scale.data_ptr(), m, k, _stream())
     native.check(code, "cb_fp8_quantize_rows")
@@ -496,6 +507,21 @@ def verify_greedy(target_ids: torch.Tensor, draft_ids: torch.Tensor, depth: torc
                                          _ptr(forced_reject_at), accepted.data_ptr(), bonus.data_ptr(),
                                          depth.numel(), _stream())
     native.check(code, "cb_verify_greedy")
+
+
+def verify_sampled(q_val: torch.Tensor, q_id: torch.Tensor, p_val: torch.Tensor, p_id: torch.Tensor,
+                   draft_ids: torch.Tensor, depth: torch.Tensor, max_depth: int, temperature: torch.Tensor,
+                   top_p: torch.Tensor, top_k: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
+                   accepted: torch.Tensor, bonus: torch.Tensor, emitted: torch.Tensor) -> None:
+    """p / q rejection sampling of a speculative round over sparse candidate distributions (``[R, D, 20]`` draft
+    candidates, ``[R, D + 1, 20]`` target candidates as written by ``sample_candidates``); ``emitted [R, D + 1]``
+    receives every request's accepted drafts followed by its next token.  See ``csrc/sampling.cu``."""
+    code = native.lib().cb_verify_sampled(q_val.data_ptr(), q_id.data_ptr(), p_val.data_ptr(), p_id.data_ptr(),
+                                          draft_ids.data_ptr(), depth.data_ptr(), int(max_depth), temperature.data_ptr(),
+                                          top_p.data_ptr(), top_k.data_ptr(), seeds.data_ptr(), counters.data_ptr(),
+                                          accepted.data_ptr(), bonus.data_ptr(), emitted.data_ptr(), depth.numel(),
+                                          _stream())
+    native.check(code, "cb_verify_sampled")
 
 
 # ------------------------------------------------------------------ mixture of experts

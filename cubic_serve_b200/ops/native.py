@@ -253,9 +253,13 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_grouped.restype = i
     l.cb_wq_gemm_grouped_act.argtypes = l.cb_wq_gemm_grouped.argtypes
     l.cb_wq_gemm_grouped_act.restype = i
+    l.cb_verify_sampled.argtypes = [vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, i, vp]
+    l.cb_verify_sampled.restype = i
     # fp8 (e4m3 x e4m3) tensor path: activation quantizers and the GEMM entries
     l.cb_fp8_quantize_rows.argtypes = [vp, i, vp, i, vp, i, i, vp]
     l.cb_fp8_quantize_rows.restype = i
+    l.cb_fp8_quantize_rows_phase.argtypes = [vp, i, vp, i, vp, i, i, i, vp]
+    l.cb_fp8_quantize_rows_phase.restype = i
     l.cb_rmsnorm_fp8.argtypes = [vp, vp, vp, vp, vp, i, vp, i, i, f, i, vp]
     l.cb_rmsnorm_fp8.restype = i
     l.cb_swiglu_fp8.argtypes = [vp, vp, i, vp, i, i, vp]

@@ -290,6 +290,10 @@ class TensorParallel:
         import torch.distributed as dist
         dist.all_reduce(t, group=self.group)
 
+    def all_reduce_max(self, t: torch.Tensor) -> None:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+
     def sample_sharded_nccl(self, logits: torch.Tensor, rows: int, out_ids: torch.Tensor, d: dict, vocab_start: int,
                             mask: torch.Tensor | None = None) -> None:
         """Baseline of ``FusedTp.sample_sharded``: NCCL all-gather of the candidates, same merge kernel."""

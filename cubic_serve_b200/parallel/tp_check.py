@@ -96,8 +96,8 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
     def both_modes(c, w):
         out = {}
         for mode in ("nccl", "fused"):
-            if c.is_hybrid and mode == "fused":
-                continue
+            if (c.is_hybrid or c.quant.method == "fp8") and mode == "fused":
+                continue          # these run with the NCCL collectives (see DecoderRunner)
             tp = TensorParallel(group, dev, mode=mode, hidden=c.hidden_size, max_tokens=T, rows_max=max(requests, 16))
             out[mode] = _step_logits(c, w, dev, tp, prompts, k_bits, v_bits)
             del tp

@@ -205,9 +205,12 @@ class LLMEngine:
         segs = self._segments(plan)
         spec = getattr(self.executor, "speculative_depth", 0)
         constrained = any(s.mask is not None for s in segs)
-        # rounds verify drafts against the target's greedy choice, so they serve greedy requests; a step with a sampled
-        # (temperature > 0) or constrained request runs the plain way
-        if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample and s.temperature == 0 for s in segs):
+        # rounds serve greedy requests (drafts verified against the target's greedy choice) and, on executors that
+        # verify by p / q rejection sampling (``speculative_sampling``), sampling requests too; a step with a
+        # constrained request runs the plain way
+        samples = bool(getattr(self.executor, "speculative_sampling", False))
+        if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample and (samples or s.temperature == 0)
+                                                     for s in segs):
             # speculative round: every request gets its accepted drafts plus one bonus token
             ids = self._speculative_round(plan, segs, spec)
             self.spec_rounds = getattr(self, "spec_rounds", 0) + 1

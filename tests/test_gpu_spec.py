@@ -144,3 +144,93 @@ def test_mtp_head_loaded_from_a_checkpoint_drafts_losslessly(tmp_path):
     r2.ws.check_status()
     agree = np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)])
     assert agree >= 0.9 and ex.stats["rounds"] > 0, (agree, plain, spec)
+
+
+def _shaped(val, temp, top_p, top_k):
+    """fp64 oracle of the sampler's shaping over one candidate row (value desc)."""
+    k = len(val) if top_k <= 0 else min(top_k, len(val))
+    w = np.exp((val[:k] - val[0]) / temp)
+    pr = w / w.sum()
+    keep = k
+    if top_p < 1.0:
+        keep = int(np.searchsorted(np.cumsum(pr), top_p) + 1)
+    out = np.zeros(len(val))
+    out[:keep] = w[:keep] / w[:keep].sum()
+    return out
+
+
+def test_rejection_sampling_emits_the_targets_distribution():
+    """p / q verification (``verify_sampled_kernel``): with drafts drawn from q, the first emitted token is distributed
+    as the target's shaped distribution p whatever q is; greedy rows reduce to the prefix match; a replay is equal."""
+    from cubic_serve_b200.ops import kernels as K
+    dev = torch.device("cuda")
+    C, R, D = K.SAMPLE_CANDIDATES, 40000, 2
+    rng = np.random.default_rng(0)
+    ids = np.arange(100, 100 + C)
+    p_val = np.sort(rng.normal(0, 1.5, C))[::-1].copy()
+    q_order = rng.permutation(C)                       # the head ranks the same tokens differently
+    q_val = np.sort(rng.normal(0, 1.5, C))[::-1].copy()
+    q_ids = ids[q_order]
+    temp, top_p, top_k = 0.8, 0.9, 12
+    P, Q = _shaped(p_val, temp, top_p, top_k), _shaped(q_val, temp, top_p, top_k)
+    drafts = q_ids[rng.choice(C, size=(R, D), p=Q)]
+
+    def t(a, dt):
+        return torch.tensor(np.ascontiguousarray(a), dtype=dt, device=dev)
+
+    qv = t(np.broadcast_to(q_val, (R, D, C)), torch.float32)
+    qi = t(np.broadcast_to(q_ids, (R, D, C)), torch.int32)
+    pv = t(np.broadcast_to(p_val, (R, D + 1, C)), torch.float32)
+    pi = t(np.broadcast_to(ids, (R, D + 1, C)), torch.int32)
+    args = dict(draft_ids=t(drafts, torch.int32), depth=torch.full((R,), D, dtype=torch.int32, device=dev), max_depth=D,
+                temperature=torch.full((R,), temp, device=dev), top_p=torch.full((R,), top_p, device=dev),
+                top_k=torch.full((R,), top_k, dtype=torch.int32, device=dev),
+                seeds=torch.arange(R, dtype=torch.int64, device=dev) * 7919 + 13,
+                counters=torch.full((R,), 5, dtype=torch.int64, device=dev))
+    acc, bonus = torch.zeros(R, dtype=torch.int32, device=dev), torch.zeros(R, dtype=torch.int32, device=dev)
+    out = torch.zeros(R, D + 1, dtype=torch.int32, device=dev)
+    K.verify_sampled(qv, qi, pv, pi, accepted=acc, bonus=bonus, emitted=out, **args)
+    torch.cuda.synchronize()
+    first = out[:, 0].cpu().numpy()
+    emp = np.array([(first == i).mean() for i in ids])
+    assert np.abs(emp - P).max() < 0.012, (emp, P)                      # ~4 sigma at 40 k samples
+    assert set(np.unique(first)) <= set(ids[P > 0])                      # nothing outside the shaped support
+    a = acc.cpu().numpy()
+    # acceptance rate of one draft = sum_x min(p, q)
+    Qp = np.zeros(C); Qp[q_order] = Q                                    # q's probability of token ids[j]
+    assert abs((a >= 1).mean() - np.minimum(P, Qp).sum()) < 0.012
+    # the token after the accepted prefix is the bonus, the prefix itself is the drafts
+    o = out.cpu().numpy()
+    assert all((o[r, :a[r]] == drafts[r, :a[r]]).all() and o[r, a[r]] == bonus[r].item() for r in range(0, R, 997))
+    out2 = torch.zeros_like(out)
+    K.verify_sampled(qv, qi, pv, pi, accepted=acc, bonus=bonus, emitted=out2, **args)
+    assert torch.equal(out, out2)
+    # greedy requests: one-hot distributions, longest matching prefix
+    args["temperature"] = torch.zeros(R, device=dev)
+    g_drafts = np.full((R, D), ids[0]); g_drafts[::2, 1] = ids[3]
+    args["draft_ids"] = t(g_drafts, torch.int32)
+    # (a greedy draft is the head's own first candidate: q is one-hot there, so q ranks the tokens like p here)
+    qi_g = t(np.broadcast_to(ids, (R, D, C)), torch.int32)
+    K.verify_sampled(qv, qi_g, pv, pi, accepted=acc, bonus=bonus, emitted=out, **args)
+    a = acc.cpu().numpy()
+    assert (a[1::2] == 2).all() and (a[::2] == 1).all() and (bonus.cpu().numpy() == ids[0]).all()
+
+
+def test_sampled_requests_take_speculative_rounds():
+    """Requests with temperature > 0 run through the rounds (drafts drawn from the head, p / q verification): same
+    seeds give the same tokens, and every token lies in the target's top-k."""
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (20, 35, 48)]
+    sp = SamplingParams(max_tokens=16, ignore_eos=True, temperature=0.9, top_k=8, top_p=0.95, seed=1234)
+    eng, ex, runner = _build(3)
+    a = eng.generate(prompts, sp)
+    runner.ws.check_status()
+    assert ex.stats["rounds"] > 0 and all(len(o) == 16 for o in a)
+    eng2, ex2, runner2 = _build(3)
+    b = eng2.generate(prompts, sp)
+    assert a == b
+    # a different seed gives other tokens
+    eng3, ex3, _ = _build(3)
+    c = eng3.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True, temperature=0.9, top_k=8, top_p=0.95, seed=99))
+    assert a != c
