@@ -76,9 +76,12 @@ class DecoderWeights:
         return total
 
 
-def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None) -> wq_pack.PackedWeight:
+def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None,
+                    row_amax: torch.Tensor | None = None) -> wq_pack.PackedWeight:
     """Quantize a dense ``[N, K]`` matrix with the config's weight format and re-tile it for the GEMM.  ``amax``: the
-    largest magnitude of the matrix ``w`` is a shard of (formats with one scale per tensor, i.e. NVFP4)."""
+    largest magnitude of the matrix ``w`` is a shard of (formats with one scale per tensor, i.e. NVFP4); ``row_amax``:
+    the largest magnitude of every row of that matrix (formats with one scale per row, i.e. FP8), so that a column
+    shard carries the codes and scales of the whole rows."""
     q = cfg.quant
     if q.method == "none":
         return wq_pack.pack_bf16(w)
@@ -102,8 +105,11 @@ def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None
         return wq_pack.pack_affine4(qv, scale, lo, g)
     if q.method == "fp8":
         from ..quantization import formats
-        payload = formats.fp8_quantize(w, block=False)
-        return wq_pack.pack_fp8(payload["weight"], payload["weight_scale"])
+        if row_amax is None:
+            payload = formats.fp8_quantize(w, block=False)
+            return wq_pack.pack_fp8(payload["weight"], payload["weight_scale"])
+        scale = (row_amax.float().reshape(-1, 1) / 448.0).clamp_min(1e-12)
+        return wq_pack.pack_fp8((w.float() / scale).to(torch.float8_e4m3fn), scale)
     if q.method == "nvfp4":
         from ..quantization import nvfp4
         payload = nvfp4.quantize(w, amax)
@@ -143,6 +149,12 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
 
     def shard_q(full, pick):
         """Quantized shard ``pick(full)`` of a matrix, with the per-tensor scale (if the format has one) of the whole."""
+        if cfg.quant.method == "fp8":
+            # which rows the shard keeps: a row pick maps the probe's row numbers, a column pick keeps every row
+            probe = torch.arange(full.shape[0], device=full.device).view(-1, 1)
+            kept = pick(probe)
+            rows = probe[:, 0] if kept.shape[1] == 0 else kept[:, 0]
+            return quantize_linear(pick(full).contiguous(), cfg, row_amax=full.abs().amax(1)[rows])
         return quantize_linear(pick(full).contiguous(), cfg, float(full.abs().amax()) if cfg.quant.method == "nvfp4" else None)
 
     def cols_of(width):

@@ -252,6 +252,13 @@ def test_random_weights_of_any_partition_are_slices_of_one_model():
     n1 = random_decoder_weights(nv, "cpu", seed=3)
     n2 = [random_decoder_weights(nv, "cpu", seed=3, tp_rank=r, tp_size=2) for r in range(2)]
     assert torch.equal(torch.cat([d(t.layers[0].down)[:nv.hidden_size] for t in n2], 1), d(n1.layers[0].down)[:nv.hidden_size])
+    # FP8 has one scale per output row: column shards are quantized with the whole row's largest magnitude
+    f8 = replace(BASE, quant=QuantSpec("fp8", 8, 0))
+    f1 = random_decoder_weights(f8, "cpu", seed=3)
+    f2 = [random_decoder_weights(f8, "cpu", seed=3, tp_rank=r, tp_size=2) for r in range(2)]
+    assert f1.layers[0].down.fmt == wq_pack.FMT_FP8
+    assert torch.equal(torch.cat([d(t.layers[0].down) for t in f2], 1), d(f1.layers[0].down))
+    assert torch.equal(torch.cat([d(t.layers[1].o) for t in f2], 1), d(f1.layers[1].o))
     moe = replace(BASE, family="gqa_moe", num_experts=4, experts_per_token=2, moe_intermediate_size=128,
                   quant=QuantSpec("cubic", 4, 128))
     m1 = random_decoder_weights(moe, "cpu", seed=1)
