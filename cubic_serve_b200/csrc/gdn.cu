@@ -12,6 +12,12 @@
 //                      with the 128 x 128 fp32 state of the head held in registers for the whole segment, then the
 //                      gated RMSNorm of the head (o * rsqrt(mean o^2 + eps) * w * silu(z))
 //
+// Speculative review passes run both kernels with commit = 0: outputs are produced for every row, the persistent
+// state is left as it was.  Once the accepted prefix is known (on the device), the SAME kernels run again over the
+// recorded inputs of the review rows with segments whose count is the accepted length and commit = 1: that fold
+// brings conv and delta state to the accepted position without a host round trip (the reference's separate fold
+// kernel: ops/cuda/linear_attention/gated_delta_fold.cu:22).
+//
 // Reference counterparts: ops/cuda/linear_attention/causal_conv_native.cu:13, gated_delta_native.cu:36,
 // gated_delta_coefficients_native.cu:17 and the oracle ops/eager/hybrid.py:255-548 (fp32 recurrence branch).
 #include "ptx.cuh"
@@ -33,7 +39,7 @@ gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_bfloat16* __r
                 const float* __restrict__ w,            // [C, 4], tap 3 multiplies the current input
                 const float* __restrict__ bias,         // [C] or null
                 __nv_bfloat16* __restrict__ state,      // [slots, 3, C]
-                GdnSegments seg, int C) {
+                GdnSegments seg, int C, int commit) {
   const int c = blockIdx.x * 128 + threadIdx.x;
   const int s = blockIdx.y;
   const int n = seg.count[s];
@@ -69,6 +75,7 @@ gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_bfloat16* __r
     yp[static_cast<size_t>(t) * ldy] = __float2bfloat16(silu_fast(a));
     h0 = h1; h1 = h2; h2 = v;
   }
+  if (!commit) return;
   st[0] = __float2bfloat16(h0);
   st[static_cast<size_t>(C)] = __float2bfloat16(h1);
   st[static_cast<size_t>(2) * C] = __float2bfloat16(h2);
@@ -90,6 +97,7 @@ struct GdnDeltaParams {
   int Hk, Hv;
   float eps_norm;             // RMSNorm epsilon
   float eps_l2;               // L2-normalisation epsilon
+  int commit;                 // 0: the state is read but not written back (speculative review pass)
   GdnSegments seg;
 };
 
@@ -255,6 +263,7 @@ gdn_delta_kernel(const GdnDeltaParams p) {
     // (the next block's phase A writes q / k / v / z: z of this block is still being read here, hence the barrier)
     if (t0 + kGdnBlock < n) __syncthreads();
   }
+  if (!p.commit) return;
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -287,14 +296,14 @@ struct CbGdnSegments {
 };
 
 int cb_gdn_conv(const void* x, int ldx, void* y, int ldy, const void* w, const void* bias, void* state,
-                const CbGdnSegments* seg, int C, void* stream) {
+                const CbGdnSegments* seg, int C, int commit, void* stream) {
   if (!seg || seg->num <= 0 || C <= 0 || seg->num > 65535) return -60;
   cb::GdnSegments s{static_cast<const int*>(seg->row0), static_cast<const int*>(seg->count),
                     static_cast<const int*>(seg->slot), static_cast<const int*>(seg->pos0)};
   dim3 grid((C + 127) / 128, seg->num);
   cb::gdn_conv_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<__nv_bfloat16*>(y), ldy, static_cast<const float*>(w),
-      static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(state), s, C);
+      static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(state), s, C, commit);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -309,6 +318,7 @@ struct CbGdnDelta {
   void* out; int ldo;
   int Hk, Hv;
   float eps_norm, eps_l2;
+  int commit;
 };
 
 int cb_gdn_delta(const CbGdnDelta* a, const CbGdnSegments* seg, void* stream) {
@@ -324,6 +334,7 @@ int cb_gdn_delta(const CbGdnDelta* a, const CbGdnSegments* seg, void* stream) {
   p.out = static_cast<__nv_bfloat16*>(a->out); p.ldo = a->ldo;
   p.Hk = a->Hk; p.Hv = a->Hv;
   p.eps_norm = a->eps_norm; p.eps_l2 = a->eps_l2;
+  p.commit = a->commit;
   p.seg = cb::GdnSegments{static_cast<const int*>(seg->row0), static_cast<const int*>(seg->count),
                           static_cast<const int*>(seg->slot), static_cast<const int*>(seg->pos0)};
   dim3 grid(a->Hv, seg->num);

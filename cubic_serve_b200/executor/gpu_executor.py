@@ -234,7 +234,7 @@ class GpuExecutor:
         self.max_rows = max_rows
         self.max_tokens = max(max_prefill_tokens, max_rows)
         assert self.max_tokens <= runner.max_tokens
-        if runner.cfg.is_hybrid and max_rows * rows_per_request > runner.max_requests:
+        if runner.cfg.is_hybrid and max_rows > runner.max_requests:
             raise ValueError("the runner's recurrent state has fewer rows than the executor has request slots")
         self.builder = BatchBuilder(max_rows * rows_per_request, self.max_tokens, max_model_len,
                                     runner.hq // runner.hkv, runner.hkv, self.device)

@@ -30,10 +30,8 @@ class SpeculativeGpuExecutor(GpuExecutor):
 
     def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
                  **kw) -> None:
-        if runner.cfg.is_hybrid:
-            # a rejected draft would have to roll the recurrent state back to the accepted prefix (the reference's
-            # fold kernel, ops/cuda/linear_attention/gated_delta_fold.cu); not built
-            raise NotImplementedError("speculative decoding is not available for models with Gated DeltaNet layers")
+        # models with Gated DeltaNet layers: the review pass leaves the recurrent state untouched and the accepted
+        # prefix is folded into it afterwards (DecoderRunner.begin_gdn_review / fold_gdn)
         super().__init__(runner, rows_per_request=depth + 1, use_graphs=False, **kw)
         self.mtp = mtp
         self.speculative_depth = depth
@@ -213,8 +211,23 @@ class SpeculativeGpuExecutor(GpuExecutor):
                           draft_ids], 1).reshape(-1)
         self.stage.d["token_ids"][:T].copy_(toks)
         b.num_logit_rows = T
+        r.begin_gdn_review(T)
         hidden = r.forward_hidden(b)
         logits = r.forward_logits(b, hidden, self._review_logits(T))
+        hidden = self._verify(segs, Kd, draft_ids, target_ids, logits, hidden)
+        if r.gdn_review is not None:
+            # recurrent layers: replay the accepted rows (root + accepted drafts) into the state, all on the device
+            i32 = dict(dtype=torch.int32, device=dev)
+            fold = K.GdnSegments(torch.arange(R, **i32) * (Kd + 1), (self.accepted[:R] + 1).to(torch.int32),
+                                 torch.tensor([s.request_slot for s in segs], **i32),
+                                 torch.tensor([s.start for s in segs], **i32), R)
+            self._fold_launches = r.fold_gdn(fold, T)
+        return hidden
+
+    def _verify(self, segs, Kd: int, draft_ids: torch.Tensor, target_ids: torch.Tensor, logits: torch.Tensor,
+                hidden: torch.Tensor) -> torch.Tensor:
+        r, dev = self.runner, self.device
+        R, T = len(segs), len(segs) * (Kd + 1)
         sm = getattr(self, "_sampling", None)
         if sm is not None:
             # p / q rejection sampling over the candidate distributions; `target_ids` receives the emitted tokens

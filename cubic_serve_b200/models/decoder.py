@@ -287,6 +287,8 @@ class DecoderRunner:
         # page boundaries of prompts, so that cached prefixes of models with recurrent layers can be resumed
         self.state_checkpoint_rows = tuple(range(max_requests, max_requests + state_checkpoints))
         self.gdn_conv_state, self.gdn_state = {}, {}
+        self.gdn_review = None       # set by begin_gdn_review(): the record of a speculative review pass
+        self._gdn_record = None
         gdn_first = next((lw.gdn for lw in weights.layers if lw.gdn is not None), None)
         if gdn_first is not None:
             if tp is not None and tp.fused is not None:
@@ -371,16 +373,60 @@ class DecoderRunner:
             raise RuntimeError("Gated DeltaNet layers need the step's request segments (StepBatch.segments)")
         if t0 != 0 or t1 != b.num_tokens:
             raise NotImplementedError("pipeline lanes split a step's rows; Gated DeltaNet layers take whole steps")
-        proj, ba = self.gdn_in[t0:t1], self.gdn_ba[t0:t1]
+        rec = self.gdn_review
+        if rec is None:
+            proj, ba = self.gdn_in[t0:t1], self.gdn_ba[t0:t1]
+        else:
+            # speculative review pass: the layer's projections are kept (the fold replays the accepted prefix from
+            # them) and the recurrent state is read but not written
+            proj, ba = rec["proj"][li][t0:t1], rec["ba"][li][t0:t1]
         K.wq_gemm(x, g.in_proj, out=proj, ws=self.ws)
         K.wq_gemm(x, g.in_ba, out=ba, ws=self.ws)
         C = (2 * g.hk + g.hv) * 128
         mix, out = self.gdn_mix[t0:t1], self.gdn_out[t0:t1]
-        K.gdn_conv(proj, g.conv_w, self.gdn_conv_state[li], b.segments, mix)
+        K.gdn_conv(proj, g.conv_w, self.gdn_conv_state[li], b.segments, mix, commit=rec is None)
         z = proj[:, C:C + g.hv * 128]
         K.gdn_delta(mix, z, ba, g.a_log, g.dt_bias, g.norm_w, self.gdn_state[li], b.segments, out, g.hk, g.hv,
-                    eps_norm=self.cfg.rms_eps)
+                    eps_norm=self.cfg.rms_eps, commit=rec is None)
         return out
+
+    def begin_gdn_review(self, rows: int) -> None:
+        """The next ``forward_hidden`` is a speculative review pass over ``rows`` token rows: Gated DeltaNet layers
+        leave their state untouched and keep their projections for ``fold_gdn``."""
+        if not self.gdn_state:
+            return
+        if self._gdn_record is None or self._gdn_record["rows"] < rows:
+            first = next(lw.gdn for lw in self.w.layers if lw.gdn is not None)
+            dev = self.device
+            self._gdn_record = {"rows": rows,
+                                "proj": {li: torch.empty(rows, first.in_proj.n, dtype=torch.bfloat16, device=dev)
+                                         for li in self.gdn_state},
+                                "ba": {li: torch.empty(rows, 2 * first.hv, dtype=torch.bfloat16, device=dev)
+                                       for li in self.gdn_state}}
+        self.gdn_review = self._gdn_record
+
+    def fold_gdn(self, segments: "K.GdnSegments", rows: int) -> int:
+        """Bring the recurrent state of every Gated DeltaNet layer to the accepted position of a reviewed round:
+        ``segments`` describes, per request, the first row of its review rows and HOW MANY of them were accepted
+        (a device tensor, so no host round trip); the conv and delta kernels replay exactly those rows from the
+        projections kept by the review pass, this time writing the state.  Returns the launches made.
+        (Reference: ``ops/cuda/linear_attention/gated_delta_fold.cu:22``, a kernel of its own there.)"""
+        rec, self.gdn_review = self.gdn_review, None
+        if rec is None:
+            return 0
+        n = 0
+        for li, lw in enumerate(self.w.layers):
+            g = lw.gdn
+            if g is None:
+                continue
+            C = (2 * g.hk + g.hv) * 128
+            proj, ba = rec["proj"][li][:rows], rec["ba"][li][:rows]
+            mix, out = self.gdn_mix[:rows], self.gdn_out[:rows]
+            K.gdn_conv(proj, g.conv_w, self.gdn_conv_state[li], segments, mix)
+            K.gdn_delta(mix, proj[:, C:C + g.hv * 128], ba, g.a_log, g.dt_bias, g.norm_w, self.gdn_state[li], segments,
+                        out, g.hk, g.hv, eps_norm=self.cfg.rms_eps)
+            n += 2
+        return n
 
     def _run_layers(self, b: StepBatch, t0: int, t1: int, rb0: int, rb1: int, embed: bool) -> None:
         """Layers of this stage over rows ``[t0, t1)`` whose attention row blocks are ``[rb0, rb1)``."""

@@ -615,24 +615,26 @@ class GdnSegments:
 
 
 def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, seg: GdnSegments, out: torch.Tensor,
-             bias: torch.Tensor | None = None) -> torch.Tensor:
+             bias: torch.Tensor | None = None, commit: bool = True) -> torch.Tensor:
     """Depthwise causal conv1d (kernel 4) + SiLU over ``x[T, C]`` per request segment; ``state[slots, 3, C]`` holds
-    every request's last three inputs and is updated.  ``w``: fp32 ``[C, 4]`` (tap 3 multiplies the current input)."""
+    every request's last three inputs and is updated unless ``commit`` is False (speculative review pass).
+    ``w``: fp32 ``[C, 4]`` (tap 3 multiplies the current input)."""
     c = w.shape[0]
     assert w.dtype == torch.float32 and w.shape[1] == 4 and w.is_contiguous()
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] >= c
     assert state.dtype == torch.bfloat16 and state.shape[1:] == (3, c) and state.is_contiguous()
     st = seg.struct()
     code = native.lib().cb_gdn_conv(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), w.data_ptr(), _ptr(bias),
-                                    state.data_ptr(), ctypes.byref(st), c, _stream())
+                                    state.data_ptr(), ctypes.byref(st), c, int(commit), _stream())
     native.check(code, "cb_gdn_conv")
     return out
 
 
 def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
               norm_w: torch.Tensor, state: torch.Tensor, seg: GdnSegments, out: torch.Tensor, hk: int, hv: int,
-              eps_norm: float = 1e-6, eps_l2: float = 1e-6) -> torch.Tensor:
-    """Gated delta rule + gated RMSNorm per (segment, value head); ``state[slots, Hv, 128, 128]`` fp32 is updated.
+              eps_norm: float = 1e-6, eps_l2: float = 1e-6, commit: bool = True) -> torch.Tensor:
+    """Gated delta rule + gated RMSNorm per (segment, value head); ``state[slots, Hv, 128, 128]`` fp32 is updated
+    unless ``commit`` is False (speculative review pass: the state is read, the outputs are written, nothing else).
 
     ``qkv[T, 2 Hk 128 + Hv 128]`` (after ``gdn_conv``), ``z[T, Hv 128]``, ``ba[T, 2 Hv]`` = ``[b | a]``.
     """
@@ -643,6 +645,7 @@ def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch
     d.qkv, d.ldqkv, d.z, d.ldz, d.ba, d.ldba = qkv.data_ptr(), qkv.stride(0), z.data_ptr(), z.stride(0), ba.data_ptr(), ba.stride(0)
     d.a_log, d.dt_bias, d.norm_w, d.state = a_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr(), state.data_ptr()
     d.out, d.ldo, d.Hk, d.Hv, d.eps_norm, d.eps_l2 = out.data_ptr(), out.stride(0), hk, hv, eps_norm, eps_l2
+    d.commit = int(commit)
     st = seg.struct()
     native.check(native.lib().cb_gdn_delta(ctypes.byref(d), ctypes.byref(st), _stream()), "cb_gdn_delta")
     return out

@@ -225,7 +225,7 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_grouped_mode.restype = None
     l.cb_reasoning_budget.argtypes = [vp, vp, vp, vp, vp, i, i, ctypes.POINTER(ctypes.c_int), i, vp]
     l.cb_reasoning_budget.restype = i
-    l.cb_gdn_conv.argtypes = [vp, i, vp, i, vp, vp, vp, vp, i, vp]
+    l.cb_gdn_conv.argtypes = [vp, i, vp, i, vp, vp, vp, vp, i, i, vp]
     l.cb_gdn_conv.restype = i
     l.cb_gdn_delta.argtypes = [vp, vp, vp]
     l.cb_gdn_delta.restype = i
@@ -289,7 +289,7 @@ class GdnDeltaStruct(ctypes.Structure):
                 ("ba", ctypes.c_void_p), ("ldba", ctypes.c_int), ("a_log", ctypes.c_void_p),
                 ("dt_bias", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("state", ctypes.c_void_p),
                 ("out", ctypes.c_void_p), ("ldo", ctypes.c_int), ("Hk", ctypes.c_int), ("Hv", ctypes.c_int),
-                ("eps_norm", ctypes.c_float), ("eps_l2", ctypes.c_float)]
+                ("eps_norm", ctypes.c_float), ("eps_l2", ctypes.c_float), ("commit", ctypes.c_int)]
 
 
 class ReduceNormStruct(ctypes.Structure):

@@ -209,6 +209,95 @@ def test_hybrid_prefix_cache_resumes_from_a_state_snapshot():
     assert np.mean([a == b for a, b in zip(mixed[0], first)]) >= 0.8, (mixed[0], first)
 
 
+def test_hybrid_model_speculates_with_the_state_folded_to_the_accepted_prefix():
+    """MTP rounds on a model with Gated DeltaNet layers: the review pass leaves the recurrent state alone, the accepted
+    rows are folded into it on the device.  Greedy rounds then reproduce plain greedy decoding; with every draft
+    rejected or accepted at random (forced), the state must still be the one of the emitted tokens."""
+    import numpy as np
+    from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.models.mtp import MtpRunner, random_mtp_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = _hybrid_cfg()
+    dev = torch.device("cuda")
+    rng = np.random.default_rng(7)
+    prompts = [rng.integers(0, cfg.vocab_size, n).tolist() for n in (21, 40, 33)]
+    sp = SamplingParams(max_tokens=14, ignore_eos=True)
+    plain_eng, plain_runner = _engine(cfg, graphs=False, chunk=512)
+    plain = plain_eng.generate(prompts, sp)
+
+    def spec_engine(force):
+        w = random_decoder_weights(cfg, dev, seed=0, std=0.05)
+        runner = DecoderRunner(cfg, w, num_pages=128, max_tokens=512, max_requests=8)
+        ex = SpeculativeGpuExecutor(runner, MtpRunner(runner, random_mtp_weights(cfg, dev, std=0.05)), 3,
+                                    force_acceptance=force, max_rows=8, max_prefill_tokens=512, max_model_len=256)
+        eng = LLMEngine(ex, 128, SchedulerConfig(max_running_requests=8, max_model_len=256, max_batched_tokens=512,
+                                                 enable_prefix_cache=False))
+        return eng, ex, runner
+
+    eng, ex, runner = spec_engine(None)
+    spec = eng.generate(prompts, sp)
+    runner.ws.check_status()
+    assert ex.stats["rounds"] > 0 and all(len(o) == 14 for o in spec)
+    agree = np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)])
+    assert agree >= 0.9, (agree, plain[0], spec[0])
+
+
+def test_review_pass_leaves_the_state_and_the_fold_replays_the_accepted_rows():
+    """Runner level: after a prefill, four tokens are (a) consumed one decode step at a time, the recurrent state cloned
+    after each, and (b) reviewed as one four-row segment without committing, then folded for 1, 2, 3 and 4 accepted
+    rows: the folded state is the state (a) had after that many tokens, and the review changed nothing by itself."""
+    import numpy as np
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor, Segment
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    from cubic_serve_b200.ops import kernels as K
+    cfg = _hybrid_cfg()
+    dev = torch.device("cuda")
+    rng = np.random.default_rng(11)
+    prompt = rng.integers(0, cfg.vocab_size, 37).tolist()
+    toks = rng.integers(0, cfg.vocab_size, 4).tolist()
+    P, slot, pages = len(prompt), 2, [1, 2, 3]
+
+    def build():
+        w = random_decoder_weights(cfg, dev, seed=0, std=0.05)
+        runner = DecoderRunner(cfg, w, num_pages=16, max_tokens=256, max_requests=8)
+        ex = GpuExecutor(runner, max_rows=8, max_prefill_tokens=256, max_model_len=64, use_graphs=False)
+        ex.execute([Segment(slot, prompt, 0, pages, True, uid=1)])
+        return runner, ex
+
+    def states(runner):
+        return {li: (runner.gdn_state[li][slot].clone(), runner.gdn_conv_state[li][slot].clone()) for li in runner.gdn_state}
+
+    r1, ex1 = build()
+    after = []
+    for j, t in enumerate(toks):
+        ex1.execute([Segment(slot, [t], P + j, pages, True, uid=1)])
+        torch.cuda.synchronize()
+        after.append(states(r1))
+    for accepted_rows in (1, 2, 3, 4):
+        r2, ex2 = build()
+        before = states(r2)
+        b, _ = ex2._fill([Segment(slot, toks, P, pages, True, uid=1)])
+        with torch.cuda.stream(ex2.stream):
+            ex2.stage.upload()
+            r2.begin_gdn_review(4)
+            r2.forward_hidden(b)
+            ex2.stream.synchronize()
+            now = states(r2)
+            assert all(torch.equal(now[li][0], before[li][0]) and torch.equal(now[li][1], before[li][1]) for li in now)
+            i32 = dict(dtype=torch.int32, device=dev)
+            fold = K.GdnSegments(torch.tensor([0], **i32), torch.tensor([accepted_rows], **i32),
+                                 torch.tensor([slot], **i32), torch.tensor([P], **i32), 1)
+            assert r2.fold_gdn(fold, 4) == 2 * len(r2.gdn_state) and r2.gdn_review is None
+            ex2.stream.synchronize()
+        r2.ws.check_status()
+        got, want = states(r2), after[accepted_rows - 1]
+        for li in got:
+            assert _rel(got[li][0], want[li][0]) < 2e-2, (accepted_rows, li)
+            assert _rel(got[li][1].float(), want[li][1].float()) < 2e-2, (accepted_rows, li)
+
+
 def test_hybrid_moe_family_decodes_the_same_eagerly_and_in_graphs():
     """The hybrid family with routed experts (Gated DeltaNet / gated attention mixers, mixture-of-experts feed-forward):
     one-shot prefill with eager decode against chunked prefill with CUDA-graph decode."""
