@@ -41,6 +41,8 @@ struct __align__(8) SmemCtl {
   uint64_t ready[8];
   uint64_t empty[8];
   uint64_t acc_full;
+  uint64_t acc_ready[2];   // kFmtFp8Block: a stage's product is complete in tensor-memory buffer b
+  uint64_t acc_free[2];    //               buffer b has been promoted into registers by all epilogue warps
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t is_last;
@@ -102,6 +104,10 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     mbar_init(smem_u32(&ctl->acc_full), 1);
+    for (int b2 = 0; b2 < 2; ++b2) {
+      mbar_init(smem_u32(&ctl->acc_ready[b2]), 1);
+      mbar_init(smem_u32(&ctl->acc_free[b2]), kNumDequantWarps);
+    }
     ctl->abort_flag = 0;
     ctl->is_last = 0;
     mbar_fence_init();
@@ -175,8 +181,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
     {
       const bool leader = elect_one();
       // operand formats: bf16 x bf16 (kind::f16) or e4m3 x e4m3 (kind::f8f6f4), fp32 accumulators either way
-      const uint32_t idesc = FMT == kFmtFp8 ? umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 0u, 0u)
-                                            : umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+      const uint32_t idesc = fmt_is_fp8(FMT) ? umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 0u, 0u)
+                                             : umma_idesc(kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+      // block-scaled fp8: stage i accumulates from zero into buffer i & 1 (p.tmem_cols / 2 columns each)
+      const uint32_t buf_cols = p.tmem_cols >> 1;
+      int buf = 0;
+      uint32_t buf_ph = 1;                   // a fresh barrier passes a wait on the previous phase: both buffers start free
       const uint32_t tmem_d = __shfl_sync(0xffffffffu, tmem_base, 0);
       const uint32_t smem_base = smem_u32(smem);
       const uint64_t desc_hi = umma_desc_sw128(0);      // every field except the start address
@@ -195,7 +205,20 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint32_t st = smem_base + static_cast<uint32_t>(s) * stage_bytes;
         const uint64_t bdesc = desc_hi | static_cast<uint64_t>((st & 0x3FFFFu) >> 4);
         const uint64_t adesc = desc_hi | static_cast<uint64_t>(((st + x_bytes) & 0x3FFFFu) >> 4);
-        if (leader) {
+        if constexpr (FMT == kFmtFp8Block) {
+          ok = __all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_free[buf]), buf_ph, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          if (leader) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+              umma_f8f6f4(tmem_d + static_cast<uint32_t>(buf) * buf_cols, adesc + 2u * k4, bdesc + 2u * k4, idesc,
+                          k4 > 0 ? 1u : 0u);
+            tc_commit(smem_u32(&ctl->empty[s]));
+            tc_commit(smem_u32(&ctl->acc_ready[buf]));
+          }
+          if (++buf == 2) { buf = 0; buf_ph ^= 1u; }
+        } else if (leader) {
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field: 16 bf16 or 32 e4m3 columns,
@@ -290,6 +313,41 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         while (s >= S) { s -= S; ph ^= 1u; }
       }
     }
+    // block-scaled fp8: promote every stage's product into registers with the stage's block scale while the MMA
+    // warp fills the other tensor-memory buffer.  A warp owns the same (lane quadrant, 16-column chunks) as in the
+    // epilogue below: chunk ci = pair + 4 * it lives in racc[it].
+    float racc[FMT == kFmtFp8Block ? 4 : 1][16];
+    if constexpr (FMT == kFmtFp8Block) {
+      const int pquad = warp & 3, ppair = (warp - 2) >> 2, pchunks = p.mb >> 4;
+#pragma unroll
+      for (int it = 0; it < 4; ++it)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) racc[it][j] = 0.f;
+      const float* bs = p.row_scale + (static_cast<size_t>(w_row0 / kTileN) + n_tile) * p.k_blocks + kb_lo;
+      const uint32_t buf_cols = p.tmem_cols >> 1;
+      int buf = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < iters; ++i) {
+        if (!__all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_ready[buf]), ph, abort_flag))) break;
+        tc_fence_after();
+        const float sc = __ldg(bs + i);
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int ci = ppair + 4 * it;
+          if (ci < pchunks) {
+            uint32_t part[16];
+            tmem_ld_32x16(tmem_base + static_cast<uint32_t>(buf) * buf_cols + (static_cast<uint32_t>(pquad * 32) << 16) + ci * 16, part);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) racc[it][j] = fmaf(sc, __uint_as_float(part[j]), racc[it][j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->acc_free[buf]));
+        if (++buf == 2) { buf = 0; ph ^= 1u; }
+      }
+    }
     // epilogue: TMEM lane = output feature, column = batch row
     pdl_wait();                             // before this thread's first global access (residual, output, partials)
     const bool acc_ok = __all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_full), 0, abort_flag));
@@ -318,8 +376,18 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const int nn = n_tile * kTileN + quad * 32 + lane;
       w_scale = nn < p.N ? p.row_scale[w_row0 + nn] : 0.f;
     }
+    // the accumulators of chunk ci (= pair + 4 * it): from tensor memory, or (block-scaled fp8) the promoted registers
+    auto load_acc = [&](uint32_t (&acc)[16], int ci, int it) {
+      if constexpr (FMT == kFmtFp8Block) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(racc[it][j]);
+      } else {
+        tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
+        tmem_ld_wait();
+      }
+    };
     auto scale_acc = [&](uint32_t (&acc)[16], int ci) {
-      if constexpr (FMT == kFmtFp8) {
+      if constexpr (fmt_is_fp8(FMT)) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = m0 + ci * 16 + j;
@@ -333,10 +401,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // TMEM -> registers -> fp32 tile [row][128 features] in the (now idle) stage memory, then all 512 threads
         // write 16-byte row segments: coalesced for the local output and for the peers' receive buffers alike
         float* stg = reinterpret_cast<float*>(smem);
-        for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int ci = pair + 4 * it;
+          if (ci >= chunks) continue;
           uint32_t acc[16];
-          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
-          tmem_ld_wait();
+          load_acc(acc, ci, it);
           scale_acc(acc, ci);
 #pragma unroll
           for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]) * p.alpha;
@@ -395,10 +465,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // the tile's K splits are one cluster: the raw fp32 partial is staged in this CTA's (now idle) stage memory
         // and summed by the cluster below, after all threads of all its CTAs have met
         float* stg = reinterpret_cast<float*>(smem);
-        for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int ci = pair + 4 * it;
+          if (ci >= chunks) continue;
           uint32_t acc[16];
-          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
-          tmem_ld_wait();
+          load_acc(acc, ci, it);
           scale_acc(acc, ci);
 #pragma unroll
           for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
@@ -406,10 +478,12 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
       } else {
         float* ws = p.workspace +
                     ((static_cast<size_t>(m_tile) * gridDim.x + n_tile) * p.splits + split) * (static_cast<size_t>(p.mb) * kTileN);
-        for (int ci = pair; ci < chunks; ci += kNumDequantWarps / 4) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int ci = pair + 4 * it;
+          if (ci >= chunks) continue;
           uint32_t acc[16];
-          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ci * 16, acc);
-          tmem_ld_wait();
+          load_acc(acc, ci, it);
           scale_acc(acc, ci);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -802,9 +876,10 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   const long long workspace_bytes = o.workspace_bytes;
   const int pair_mode = g_pair_mode.load(std::memory_order_relaxed);
   const int cluster_default = o.cluster_splitk >= 0 ? o.cluster_splitk : g_cluster_splitk.load(std::memory_order_relaxed);
-  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % (fmt == kFmtFp8 ? 16 : 8)) != 0) return -10;
-  if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4 && fmt != kFmtFp8) return -11;
-  if (fmt == kFmtFp8 && (!o.x_scale || !meta || stream_k)) return -15;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % (fmt_is_fp8(fmt) ? 16 : 8)) != 0) return -10;
+  if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4 && !fmt_is_fp8(fmt)) return -11;
+  if (fmt_is_fp8(fmt) && (!o.x_scale || !meta || stream_k)) return -15;
+  if (fmt == kFmtFp8Block && o.tiles && (N % kTileN) != 0) return -16;   // stacked experts: whole block rows each
   if (fmt == kFmtCubic4 && (group_k % kBlockK) != 0) return -12;
   WqGemmParams p{};
   p.codes = static_cast<const uint8_t*>(codes);
@@ -832,7 +907,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   }
   p.mb = M >= 256 ? 256 : ((M + 15) / 16) * 16;
   if (o.tiles && o.mb_hint > 0) p.mb = o.mb_hint;
-  p.row_scale = fmt == kFmtFp8 ? static_cast<const float*>(meta) : nullptr;
+  p.row_scale = fmt_is_fp8(fmt) ? static_cast<const float*>(meta) : nullptr;
   p.col_scale = o.x_scale;
   // fp8 stages cover 128 columns; a ragged last stage reads zeros from both tensor maps
   p.k_blocks = (K + fmt_block_k(fmt) - 1) / fmt_block_k(fmt);
@@ -847,7 +922,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.meta_blocks = (p.k_blocks + p.meta_k_blocks - 1) / p.meta_k_blocks;
   uint32_t cols = 32;
   while (cols < static_cast<uint32_t>(p.mb)) cols <<= 1;
-  p.tmem_cols = cols;
+  p.tmem_cols = fmt == kFmtFp8Block ? 2 * cols : cols;     // two alternating stage buffers (at most 2 x 256 columns)
   const size_t stage = static_cast<size_t>(p.mb) * 128 + kATileBytes + (fmt_is_direct(fmt) ? 0 : kCodeBytes + meta_bytes(fmt));
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SmemCtl);
   int stages = static_cast<int>(budget / stage);
@@ -864,7 +939,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   p.pair = (stream_k && (pair_mode == 2 || (pair_mode == 1 && M > 256)) && streamk_pair_eligible(p, N)) ? 1 : 0;
   CUtensorMap tx, tw;
   // with CTA pairs each CTA of a pair fetches half of the rows of an activation tile
-  if (fmt == kFmtFp8) {
+  if (fmt_is_fp8(fmt)) {
     const uint64_t w_rows = static_cast<uint64_t>(N) * (o.tiles ? o.num_experts : 1);
     if (make_tmap_u8(&tx, x, M, K, ldx, p.mb) != 0) return -20;
     if (make_tmap_u8(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
@@ -902,6 +977,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
     case kFmtAffine4: return launch_fmt<kFmtAffine4>(tx, tw, p, grid, smem, st);
     case kFmtNvfp4: return launch_fmt<kFmtNvfp4>(tx, tw, p, grid, smem, st);
     case kFmtFp8: return launch_fmt<kFmtFp8>(tx, tw, p, grid, smem, st);
+    case kFmtFp8Block: return launch_fmt<kFmtFp8Block>(tx, tw, p, grid, smem, st);
     default: return launch_fmt<kFmtBf16>(tx, tw, p, grid, smem, st);
   }
 }
@@ -942,6 +1018,7 @@ int cb_wq_gemm_resident_clusters(int fmt, int size) {
     case cb::kFmtAffine4: return cb::resident_clusters<cb::kFmtAffine4>(size);
     case cb::kFmtNvfp4: return cb::resident_clusters<cb::kFmtNvfp4>(size);
     case cb::kFmtFp8: return cb::resident_clusters<cb::kFmtFp8>(size);
+    case cb::kFmtFp8Block: return cb::resident_clusters<cb::kFmtFp8Block>(size);
     default: return cb::resident_clusters<cb::kFmtBf16>(size);
   }
 }
@@ -992,21 +1069,22 @@ int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const
 // wq: e4m3 [N, K] row-major exactly as in the checkpoint, w_scale: fp32 [N].  `swiglu`: wq's rows are in the
 // interleaved gate / up order and y has N / 2 columns.  K splits meet in a cluster or in `workspace`.
 // Counterpart of the reference's dynamic-token FP8 linear (quantization/extensions/fp8/kernels.py:81-130).
-int cb_wq_gemm_fp8(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, void* y, int ldy,
-                   const void* residual, int M, int N, int K, int splits, int swiglu, void* workspace, void* counters,
-                   void* status, void* stream, const CbTpLink* link) {
+// `block`: w_scale holds one scale per 128 x 128 block, [ceil(N / 128), ceil(K / 128)], instead of one per row.
+int cb_wq_gemm_fp8(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, int block, void* y,
+                   int ldy, const void* residual, int M, int N, int K, int splits, int swiglu, void* workspace,
+                   void* counters, void* status, void* stream, const CbTpLink* link) {
   if (swiglu && ((N % 32) != 0 || ldy < N / 2)) return -50;
   WqLaunchOpts o;
   o.x_scale = static_cast<const float*>(x_scale);
   o.swiglu = swiglu;
-  return wq_gemm_dispatch(cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, residual, 1.f, M, N, K, K, splits, workspace,
+  return wq_gemm_dispatch(block ? cb::kFmtFp8Block : cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, residual, 1.f, M, N, K, K, splits, workspace,
                           counters, status, stream, link, o);
 }
 
 // The grouped (expert) form: wq is the stack [experts * N, K], w_scale [experts * N]; rows of xq / x_scale / y are the
 // routed rows in work-list order (see cb_wq_gemm_grouped).
-int cb_wq_gemm_fp8_grouped(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, void* y,
-                           int ldy, int total_rows, int N, int K, const void* tiles, int max_items, int mb,
+int cb_wq_gemm_fp8_grouped(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, int block,
+                           void* y, int ldy, int total_rows, int N, int K, const void* tiles, int max_items, int mb,
                            int num_experts, int swiglu, void* status, void* stream) {
   if (!tiles || max_items <= 0 || mb <= 0 || mb > 256 || (mb % 16) != 0 || num_experts <= 0) return -40;
   if (swiglu && ((N % 32) != 0 || ldy < N / 2)) return -50;
@@ -1017,7 +1095,7 @@ int cb_wq_gemm_fp8_grouped(const void* xq, int ldx, const void* x_scale, const v
   o.max_items = max_items;
   o.mb_hint = mb;
   o.swiglu = swiglu;
-  return wq_gemm_dispatch(cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, nullptr, 1.f, total_rows, N, K, K, 1, nullptr,
+  return wq_gemm_dispatch(block ? cb::kFmtFp8Block : cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, nullptr, 1.f, total_rows, N, K, K, 1, nullptr,
                           nullptr, status, stream, nullptr, o);
 }
 

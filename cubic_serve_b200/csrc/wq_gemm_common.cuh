@@ -10,11 +10,17 @@ namespace cb {
 // kFmtFp8: e4m3 weights [N, K] with one fp32 scale per output feature, multiplied on the tensor cores with e4m3
 // ACTIVATIONS (one fp32 scale per token) by tcgen05.mma.kind::f8f6f4 -- no software decode at all: both operands go
 // from global memory to the swizzled shared-memory tiles by TMA, as for bf16 weights, with 128 K columns per stage.
-enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 = 3, kFmtFp8 = 4 };
+// kFmtFp8Block: e4m3 weights with one fp32 scale per 128 x 128 block ([ceil(N / 128), ceil(K / 128)], the
+// `weight_scale_inv` of block-quantized checkpoints).  A weight tile is one block row and a stage one block column, so
+// every stage's product has ONE scale: the MMA warp accumulates each stage into a fresh tensor-memory buffer (two
+// buffers alternate) and the epilogue warps, idle in the main loop of a direct format, promote it into fp32
+// registers with that scale (acc += s * partial) while the next stage's MMAs run.
+enum WqFormat : int { kFmtCubic4 = 0, kFmtAffine4 = 1, kFmtNvfp4 = 2, kFmtBf16 = 3, kFmtFp8 = 4, kFmtFp8Block = 5 };
+__host__ __device__ constexpr bool fmt_is_fp8(int fmt) { return fmt == kFmtFp8 || fmt == kFmtFp8Block; }
 // formats whose weight tile is fetched by TMA straight into the MMA layout (no decode warps, no code ring)
-__host__ __device__ constexpr bool fmt_is_direct(int fmt) { return fmt == kFmtBf16 || fmt == kFmtFp8; }
+__host__ __device__ constexpr bool fmt_is_direct(int fmt) { return fmt == kFmtBf16 || fmt_is_fp8(fmt); }
 // K columns of one pipeline stage: one 128-byte swizzle row of the operand's element type
-__host__ __device__ constexpr int fmt_block_k(int fmt) { return fmt == kFmtFp8 ? 128 : 64; }
+__host__ __device__ constexpr int fmt_block_k(int fmt) { return fmt_is_fp8(fmt) ? 128 : 64; }
 
 static constexpr int kTileN = 128;       // output features per CTA (UMMA M)
 static constexpr int kBlockK = 64;       // K columns per stage (one 128-byte swizzle row)
@@ -69,7 +75,8 @@ struct WqGemmParams {
   int stages;
   float alpha;              // epilogue scale (per-tensor global scale), 1.0 when unused
   // kFmtFp8: accumulators are scaled as they leave tensor memory, acc[n][m] *= row_scale[n] * col_scale[m]
-  const float* row_scale;   // [N] (grouped: [experts * N]) weight scale per output feature
+  const float* row_scale;   // [N] (grouped: [experts * N]) weight scale per output feature; kFmtFp8Block: the block
+                            // scales [n tiles (grouped: experts * n tiles)][k_blocks]
   const float* col_scale;   // [M] activation scale per token (row of x)
   uint32_t tmem_cols;       // power of two >= max(32, mb)
   TpLink tp;

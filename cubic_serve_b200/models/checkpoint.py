@@ -246,8 +246,8 @@ def pack_logical(method: str, parts: list[tuple[dict, tuple[int, int]]], q: Quan
                  ) -> wq_pack.PackedWeight:
     """Concatenate logical matrices along N (e.g. q, k, v) and pack them for the GEMM.
 
-    4-bit Cubic / INT / AWQ / NVFP4 payloads stay 4-bit and channel-scaled FP8 payloads stay e4m3 bytes (the fp8
-    tensor-core GEMM consumes them as stored); everything else is decoded to bf16 at load.
+    4-bit Cubic / INT / AWQ / NVFP4 payloads stay 4-bit and FP8 payloads (one scale per row, or per 128 x 128 block)
+    stay e4m3 bytes (the fp8 tensor-core GEMM consumes them as stored); everything else is decoded to bf16 at load.
     ``k_slice`` selects a column range (row-parallel shards), aligned to the scale groups.
     """
     lo, hi = k_slice if k_slice else (0, parts[0][1][1])
@@ -261,6 +261,18 @@ def pack_logical(method: str, parts: list[tuple[dict, tuple[int, int]]], q: Quan
         # e4m3 weights with one scale per output row: W8A8 on the fp8 tensor path, no expansion
         w8 = torch.cat([p["weight"].view(torch.uint8)[:, lo:hi] for p, _ in parts], 0)
         return wq_pack.pack_fp8(w8, torch.cat([p["weight_scale"].float().reshape(-1) for p, _ in parts]))
+    def block_scales(p):
+        return p["weight_scale_inv"] if "weight_scale_inv" in p else p.get("weight_scale")
+
+    fp8_blocks = (method in ("fp8", "fp8_block") and not plain and lo % 128 == 0 and (hi - lo) % 64 == 0 and all(
+        "weight" in p and p["weight"].dtype == torch.float8_e4m3fn and block_scales(p) is not None
+        and block_scales(p).dim() == 2 and tuple(block_scales(p).shape) == (-(-s[0] // 128), -(-s[1] // 128))
+        and (s[0] % 128 == 0 or len(parts) == 1) for p, s in parts)) and not fp8_rows
+    if fp8_blocks:
+        # e4m3 weights with one scale per 128 x 128 block: the block-scaled form of the fp8 tensor-core GEMM
+        w8 = torch.cat([p["weight"].view(torch.uint8)[:, lo:hi] for p, _ in parts], 0)
+        bs = torch.cat([block_scales(p).float()[:, lo // 128:-(-hi // 128)] for p, _ in parts], 0)
+        return wq_pack.pack_fp8_block(w8, bs)
     if not native4 or plain:
         dense = torch.cat([_dense_of(method, p, s, q) for p, s in parts], 0)
         return wq_pack.pack_bf16(dense[:, lo:hi])

@@ -110,6 +110,10 @@ def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None
             return wq_pack.pack_fp8(payload["weight"], payload["weight_scale"])
         scale = (row_amax.float().reshape(-1, 1) / 448.0).clamp_min(1e-12)
         return wq_pack.pack_fp8((w.float() / scale).to(torch.float8_e4m3fn), scale)
+    if q.method == "fp8_block":
+        from ..quantization import formats
+        payload = formats.fp8_quantize(w, block=True)
+        return wq_pack.pack_fp8_block(payload["weight"], payload["weight_scale_inv"])
     if q.method == "nvfp4":
         from ..quantization import nvfp4
         payload = nvfp4.quantize(w, amax)
@@ -260,7 +264,7 @@ class DecoderRunner:
         if pp is not None and tp is not None and tp.fused is not None:
             raise ValueError("pipeline stages use the NCCL tensor-parallel collectives (tp mode 'nccl')")
         if tp is not None and tp.fused is not None and any(
-                pw is not None and pw.fmt == wq_pack.FMT_FP8 for lw in weights.layers for pw in (lw.qkv, lw.o, lw.gate_up, lw.down)):
+                pw is not None and pw.fmt in (wq_pack.FMT_FP8, wq_pack.FMT_FP8_BLOCK) for lw in weights.layers for pw in (lw.qkv, lw.o, lw.gate_up, lw.down)):
             # the fp8 GEMM's activation operand is quantized per token by a kernel of its own, which would read rows
             # that the fused all-gather has not delivered yet
             raise ValueError("FP8 weights run with the NCCL tensor-parallel collectives (tp mode 'nccl')")
@@ -443,12 +447,12 @@ class DecoderRunner:
             if self.tp is not None:
                 self.tp.all_reduce(h)
         pending = None  # partial sum waiting to be folded into h by the next norm (TP > 1)
-        fp8 = wq_pack.FMT_FP8
+        fp8s = (wq_pack.FMT_FP8, wq_pack.FMT_FP8_BLOCK)
 
         def norm(src, weight, residual, consumers):
             """RMSNorm into ``x``; when every consumer of the result is an fp8 GEMM the norm kernel quantizes its own
             output per token and the e4m3 operand is returned instead (no bf16 round trip, no extra launch)."""
-            if consumers and all(c is not None and c.fmt == fp8 for c in consumers):
+            if consumers and all(c is not None and c.fmt in fp8s for c in consumers):
                 return K.rmsnorm_fp8(src, weight, cfg.rms_eps, residual=residual, zero_centered=cfg.zero_centered_norm,
                                      ws=self.ws)
             return K.rmsnorm(src, weight, cfg.rms_eps, out=x, residual=residual, zero_centered=cfg.zero_centered_norm)
@@ -457,7 +461,7 @@ class DecoderRunner:
             """Input of a row-parallel projection under tensor parallelism: an fp8 projection's operand is quantized
             with the MAX over the ranks of the per-token scales, i.e. with the scale of the unsharded row, so that
             the partition does not change the codes (the reference's scale collective)."""
-            if weight.fmt != fp8:
+            if weight.fmt not in fp8s:
                 return t
             return K.fp8_quantize(t, self.ws, scale_max=self.tp.all_reduce_max)
 
@@ -496,7 +500,7 @@ class DecoderRunner:
                 xin = norm(part, lw.ln2, h, ffn_in)
             # fp8 projections whose input is not a norm's output (attention output, activation) quantize it first
             per_quant = 1 if self.tp is None else 3          # sharded operands: scale, MAX over ranks, quantize
-            n += 2 + per_quant * ((o_w.fmt == fp8) + (lw.moe is None and lw.down.fmt == fp8))
+            n += 2 + per_quant * ((o_w.fmt in fp8s) + (lw.moe is None and lw.down.fmt in fp8s))
             if lw.moe is not None:
                 n += lw.moe.launches
                 if self.tp is None:

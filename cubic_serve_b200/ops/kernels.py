@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from . import native
-from .wq_pack import FMT_BF16, FMT_CUBIC4, FMT_FP8, PackedWeight
+from .wq_pack import FMT_BF16, FMT_CUBIC4, FMT_FP8, FMT_FP8_BLOCK, PackedWeight
 
 PAGE_TOKENS = 16
 
@@ -236,7 +236,7 @@ def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link,
     if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
         splits = 1
     code = l.cb_wq_gemm_fp8(a.q.data_ptr(), a.q.stride(0), a.scale.data_ptr(), w.codes.data_ptr(), w.meta.data_ptr(),
-                            None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual), m, w.n, k,
+                            int(w.fmt == FMT_FP8_BLOCK), None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual), m, w.n, k,
                             int(splits), int(swiglu), ws.gemm.data_ptr(), ws.gemm_counters.data_ptr(),
                             ws.status.data_ptr(), _stream(), None if link is None else ctypes.byref(link))
     native.check(code, "cb_wq_gemm_fp8")
@@ -263,7 +263,7 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
     if residual is not None:
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
-    if w.fmt == FMT_FP8:
+    if w.fmt in (FMT_FP8, FMT_FP8_BLOCK):
         return _wq_gemm_fp8(x, w, out, residual, splits, ws, link, False)
     l = native.lib()
     if splits is None and min_units is None and link is None and TUNED_PLANS:
@@ -312,7 +312,7 @@ def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = Non
         out = torch.empty((m, w.n // 2), dtype=torch.bfloat16, device=x.device)
     assert out.stride(1) == 1 and out.shape == (m, w.n // 2)
     ws = ws or workspace(x.device)
-    if w.fmt == FMT_FP8:
+    if w.fmt in (FMT_FP8, FMT_FP8_BLOCK):
         return _wq_gemm_fp8(x, w, out, None, splits, ws, link, True)
     l = native.lib()
     if splits is None and min_units is None and link is None and TUNED_PLANS:
@@ -569,12 +569,13 @@ def wq_gemm_grouped(x: torch.Tensor, w: PackedWeight, out: torch.Tensor, rows: i
     """
     ws = ws or workspace(x.device)
     assert swiglu == w.act_interleaved
-    if w.fmt == FMT_FP8:
+    if w.fmt in (FMT_FP8, FMT_FP8_BLOCK):
         # the routed rows (plus the slack rows a work item's tile may touch) are quantized per token, then one grouped
         # launch over the stacked e4m3 experts
         a = fp8_quantize(x[:min(x.shape[0], rows + sc.mb)], ws)
         code = native.lib().cb_wq_gemm_fp8_grouped(a.q.data_ptr(), a.q.stride(0), a.scale.data_ptr(), w.codes.data_ptr(),
-                                                   w.meta.data_ptr(), out.data_ptr(), out.stride(0), rows, w.n, w.k,
+                                                   w.meta.data_ptr(), int(w.fmt == FMT_FP8_BLOCK), out.data_ptr(),
+                                                   out.stride(0), rows, w.n, w.k,
                                                    sc.tiles.data_ptr(), sc.max_items, sc.mb, w.codes.shape[0], int(swiglu),
                                                    ws.status.data_ptr(), _stream())
         native.check(code, "cb_wq_gemm_fp8_grouped")

@@ -30,6 +30,7 @@ FMT_AFFINE4 = 1
 FMT_NVFP4 = 2
 FMT_BF16 = 3
 FMT_FP8 = 4          # e4m3 weights [N, K] as stored in the checkpoint + one fp32 scale per row; W8A8 on the fp8 tensor path
+FMT_FP8_BLOCK = 5    # the same with one fp32 scale per 128 x 128 block ([ceil(N / 128), ceil(K / 128)])
 
 TILE_N = 128
 BLOCK_K = 64
@@ -215,6 +216,19 @@ def pack_fp8(weight: torch.Tensor, scale: torch.Tensor) -> PackedWeight:
     return PackedWeight(FMT_FP8, n, k, k, codes, meta)
 
 
+def pack_fp8_block(weight: torch.Tensor, block_scale: torch.Tensor) -> PackedWeight:
+    """Block-scaled e4m3 weights (``weight_scale_inv`` of block-quantized checkpoints: one fp32 scale per 128 x 128
+    block) for the fp8 tensor-core GEMM, whose weight tile is one block row and whose pipeline stage is one block
+    column.  ``weight``: ``[N, K]`` e4m3 (or its bytes); ``block_scale``: ``[ceil(N / 128), ceil(K / 128)]``."""
+    n, k = weight.shape
+    if k % BLOCK_K:
+        raise ValueError("K must be a multiple of 64")
+    meta = block_scale.to(torch.float32).contiguous()
+    if tuple(meta.shape) != (-(-n // 128), -(-k // 128)):
+        raise ValueError(f"block scales of a {n} x {k} matrix have shape {(-(-n // 128), -(-k // 128))}, not {tuple(meta.shape)}")
+    return PackedWeight(FMT_FP8_BLOCK, n, k, 128, weight.contiguous().view(torch.uint8), meta)
+
+
 def swiglu_row_order(inter: int) -> torch.Tensor:
     """Row order of a ``[gate; up]`` matrix (``2 * inter`` rows) for the fused SwiGLU epilogue of the GEMM.
 
@@ -235,6 +249,8 @@ def permute_rows(pw: PackedWeight, order: torch.Tensor) -> PackedWeight:
         raise ValueError("row order must cover every row")
     if pw.fmt == FMT_BF16:
         return PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, pw.codes[order.to(pw.codes.device)].contiguous(), None, pw.alpha)
+    if pw.fmt == FMT_FP8_BLOCK:
+        raise ValueError("rows of block-scaled weights cannot be reordered across scale blocks")
     if pw.fmt == FMT_FP8:
         o = order.to(pw.codes.device)
         return PackedWeight(pw.fmt, pw.n, pw.k, pw.group_k, pw.codes[o].contiguous(), pw.meta[o].contiguous(), pw.alpha)
@@ -255,6 +271,10 @@ def swiglu_interleave(pw: PackedWeight, stacked: bool = False) -> PackedWeight:
     ``stacked``: ``codes`` / ``meta`` carry a leading expert dimension and every expert is re-ordered.
     """
     if pw.act_interleaved:
+        return pw
+    if pw.fmt == FMT_FP8_BLOCK:
+        # a 128-row tile of the interleaved order would mix gate and up rows of different scale blocks: block-scaled
+        # weights keep their row order and the activation runs as a kernel of its own
         return pw
     order = swiglu_row_order(pw.n // 2)
     if not stacked:
@@ -279,6 +299,9 @@ def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
         return pw.codes.float()
     if pw.fmt == FMT_FP8:
         return pw.codes.view(torch.float8_e4m3fn).float() * pw.meta.reshape(-1, 1)
+    if pw.fmt == FMT_FP8_BLOCK:
+        s = pw.meta.repeat_interleave(128, 0)[:pw.n].repeat_interleave(128, 1)[:, :pw.k]
+        return pw.codes.view(torch.float8_e4m3fn).float() * s
     nt = pw.codes.shape[0]
     if pw.fmt == FMT_CUBIC4:
         c = cubic_codes_from_words(_untile_words(pw.codes))                        # [N_pad, K]

@@ -229,6 +229,10 @@ def to_packed_weight(method: str, payload: dict, shape: tuple[int, int], bits: i
     if method == "fp8" and payload["weight"].dtype == torch.float8_e4m3fn and payload["weight_scale"].numel() == n \
             and k % 64 == 0:
         return wq_pack.pack_fp8(payload["weight"], payload["weight_scale"])
+    if method in ("fp8", "fp8_block") and payload["weight"].dtype == torch.float8_e4m3fn and k % 64 == 0:
+        bs = payload.get("weight_scale_inv", payload.get("weight_scale"))
+        if bs is not None and bs.dim() == 2 and tuple(bs.shape) == (-(-n // 128), -(-k // 128)) and bs.shape[1] > 1:
+            return wq_pack.pack_fp8_block(payload["weight"], bs)
     if method in ("fp8", "fp8_block"):
         return wq_pack.pack_bf16(fp8_dense(payload))
     if method == "nvfp4":

@@ -143,3 +143,78 @@ def test_fp8_model_step_tracks_the_same_model_with_dequantized_weights():
     err = torch.cat([_rel_rows(a0, b0), _rel_rows(a1, b1)[same]])
     assert float(err.max()) < 0.25, err
     assert float(err.median()) < 0.16, err
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(16, 256, 512, 1), (64, 4096, 4096, None), (256, 1536, 4096, None),
+                                          (256, 4096, 1536, 2), (200, 1000, 1088, 1), (700, 1024, 4096, 1),
+                                          (48, 512, 2048, 16)])
+def test_block_scaled_fp8_gemm_matches_fp32_on_the_same_codes(m, n, k, splits):
+    """e4m3 weights with one scale per 128 x 128 block: every stage's product is promoted with its block's scale."""
+    from cubic_serve_b200.ops import kernels as K
+    from cubic_serve_b200.ops import wq_pack
+    from cubic_serve_b200.quantization import formats
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(4)
+    w = torch.randn(n, k, device=dev, generator=g) * 0.05
+    # blocks of very different magnitude, so that a wrong or missing block scale cannot hide
+    w *= (torch.rand(-(-n // 128), -(-k // 128), device=dev, generator=g) * 8 + 0.1).repeat_interleave(128, 0)[:n] \
+        .repeat_interleave(128, 1)[:, :k]
+    p = formats.fp8_quantize(w, block=True)
+    pw = wq_pack.pack_fp8_block(p["weight"], p["weight_scale_inv"])
+    dense = wq_pack.unpack_to_dense(pw)
+    assert _rel(dense, w) < 0.04
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    a = K.fp8_quantize(x)
+    want = (a.q.view(torch.float8_e4m3fn).float() @ dense.t()) * a.scale.reshape(-1, 1)
+    y = K.wq_gemm(x, pw, splits=splits)
+    torch.cuda.synchronize()
+    K.workspace(dev).check_status()
+    assert _rel(y, want) < 5e-3
+
+
+def test_block_scaled_fp8_experts_and_model_step():
+    import dataclasses
+    import numpy as np
+    from cubic_serve_b200.models import moe
+    from cubic_serve_b200.models.config import toy_config
+    from cubic_serve_b200.models.decoder import random_decoder_weights
+    from cubic_serve_b200.ops import kernels as K
+    from cubic_serve_b200.ops import wq_pack
+    from cubic_serve_b200.parallel.tp_check import _rel_rows, _step_logits
+    from cubic_serve_b200.quantization import formats
+    dev = torch.device("cuda")
+    h, E, top_k, I = 1024, 4, 2, 256
+
+    def blockw(n, k, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        p = formats.fp8_quantize(torch.randn(n, k, device=dev, generator=g) * 0.05, block=True)
+        return wq_pack.pack_fp8_block(p["weight"], p["weight_scale_inv"])
+
+    gus, downs = [blockw(2 * I, h, 10 + e) for e in range(E)], [blockw(h, I, 20 + e) for e in range(E)]
+    gu_s, gcs, gms = moe.stack_experts(gus)
+    dn_s, dcs, dms = moe.stack_experts(downs)
+    router = (torch.randn(E, h, device=dev) * 0.05).to(torch.bfloat16)
+    layer = moe.MoeLayer(wq_pack.pack_bf16(router), gu_s, dn_s, (gcs, gms, dcs, dms), E, top_k, 0, E)
+    layer.fuse_activation()                       # a no-op for block-scaled experts: the activation stays a kernel
+    assert not layer.gate_up.act_interleaved
+    xt = torch.randn(50, h, device=dev).to(torch.bfloat16)
+    y = layer.forward(xt)
+    torch.cuda.synchronize()
+    K.workspace(dev).check_status()
+    want = moe.moe_reference(xt, router, [wq_pack.unpack_to_dense(w) for w in gus],
+                             [wq_pack.unpack_to_dense(w) for w in downs], top_k)
+    assert _rel(y, want) < 6e-2
+    # a dense model whose projections are block-scaled, against the same weights dequantized
+    cfg = dataclasses.replace(toy_config(), num_layers=3, hidden_size=512, intermediate_size=1024, num_q_heads=4,
+                              num_kv_heads=2, head_dim=128, vocab_size=1024)
+    cfg = dataclasses.replace(cfg, quant=dataclasses.replace(cfg.quant, method="fp8_block", bits=8, group_size=128))
+    w8 = random_decoder_weights(cfg, dev, seed=1, std=0.05)
+    assert w8.layers[0].gate_up.fmt == wq_pack.FMT_FP8_BLOCK
+    w16 = random_decoder_weights(cfg, dev, seed=1, std=0.05)
+    for lw in w16.layers:
+        for name in ("qkv", "o", "gate_up", "down"):
+            setattr(lw, name, wq_pack.pack_bf16(wq_pack.unpack_to_dense(getattr(lw, name))))
+    prompts = np.random.default_rng(0).integers(0, cfg.vocab_size, size=(6, 40)).tolist()
+    (a0, a1), ids8 = _step_logits(cfg, w8, dev, None, prompts, 8, 8)
+    (b0, b1), ids16 = _step_logits(cfg, w16, dev, None, prompts, 8, 8)
+    assert float(_rel_rows(a0, b0).max()) < 0.25
