@@ -38,9 +38,14 @@ def parse_args():
     ap.add_argument("--input-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"], help="TP collective path")
-    ap.add_argument("--weights", default="", choices=["", "fp8"],
-                    help="weight format instead of the config's own (fp8: e4m3 weights with row scales, per-token e4m3 "
-                         "activations, fp8 tensor cores; a different benchmark than the 4-bit headline)")
+    ap.add_argument("--weights", default="", choices=["", "fp8", "fp8_block", "q4k"],
+                    help="weight format instead of the config's own (fp8 / fp8_block: e4m3 weights with row or 128 x 128 "
+                         "block scales, per-token e4m3 activations, fp8 tensor cores; q4k: 4-bit k-quant style affine "
+                         "sub-blocks of 32; each is a different benchmark than the 4-bit Cubic headline)")
+    ap.add_argument("--shared-prefix", type=int, default=0,
+                    help="the first N tokens of every prompt are the same and the prefix cache is on: one request is "
+                         "prefilled first, the others resume from its pages")
+    ap.add_argument("--dynamic-draft", action="store_true", help="speculative rounds: per-request draft length 1..depth")
     ap.add_argument("--pp", type=int, default=1, choices=[1, 2], help="pipeline stages (tp = gpus / pp)")
     ap.add_argument("--kv", default="", help="K,V cache bits, e.g. 8,8 or 4,8 (default: 8,8 dense, 4,8 MoE)")
     ap.add_argument("--prefill-tokens", type=int, default=8192, help="token budget of a prefill step")
@@ -136,11 +141,14 @@ def main() -> None:
     if args.layers:
         from dataclasses import replace
         cfg = replace(cfg, num_layers=args.layers)
-    if args.weights == "fp8":
+    if args.weights in ("fp8", "fp8_block"):
         from dataclasses import replace
-        cfg = replace(cfg, quant=replace(cfg.quant, method="fp8", bits=8, group_size=0))
+        cfg = replace(cfg, quant=replace(cfg.quant, method=args.weights, bits=8, group_size=128 if args.weights == "fp8_block" else 0))
         if args.comm == "fused" and args.gpus > 1:
             args.comm = "nccl"          # the fp8 activation quantizer is a kernel of its own (see DecoderRunner)
+    elif args.weights == "q4k":
+        from dataclasses import replace
+        cfg = replace(cfg, quant=replace(cfg.quant, method="gguf", bits=4, group_size=32))
     k_bits, v_bits = (int(b) for b in (args.kv or ("4,8" if cfg.is_moe else "8,8")).split(","))
     tp = pp = None
     tp_size, tp_rank, layer_range = world // args.pp, rank % (world // args.pp), None
@@ -169,7 +177,8 @@ def main() -> None:
     if args.context == "mean" and not args.spec_depth:
         advance = max(0, args.output_len // 2 - args.steps // 2 - args.warmup)
     total_steps = args.warmup + args.steps + advance
-    max_len = L + total_steps * (1 + args.spec_depth) + 8 + args.spec_depth
+    slack = 64 * (1 + args.spec_depth) if args.shared_prefix else 0   # the first request decodes while the others prefill
+    max_len = L + total_steps * (1 + args.spec_depth) + 8 + args.spec_depth + slack
     pages_per_req = -(-max_len // 16)
     num_pages = C * pages_per_req + 8
     prefill_tokens = args.prefill_tokens
@@ -196,11 +205,24 @@ def main() -> None:
     eng = LLMEngine(ex, num_pages=num_pages,
                     scheduler_config=SchedulerConfig(max_running_requests=C, max_batched_tokens=prefill_tokens,
                                                      prefill_chunk_tokens=prefill_tokens, max_model_len=max_len,
-                                                     enable_prefix_cache=False))
+                                                     enable_prefix_cache=args.shared_prefix > 0))
+    if args.spec_depth and args.dynamic_draft:
+        eng.enable_dynamic_draft()
     rng = np.random.default_rng(1)
     prompts = rng.integers(0, cfg.vocab_size, size=(C, L)).tolist()
-    sp = SamplingParams(temperature=0.0, max_tokens=total_steps * (1 + args.spec_depth) + 4, ignore_eos=True)
-    for p in prompts:
+    if args.shared_prefix:
+        shared = rng.integers(0, cfg.vocab_size, size=min(args.shared_prefix, L - 1)).tolist()
+        prompts = [shared + p[len(shared):] for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=total_steps * (1 + args.spec_depth) + 4 + slack, ignore_eos=True)
+    if args.shared_prefix and C > 1:
+        # the first request's prefill publishes the shared pages; the others are admitted after it and resume there
+        eng.add_request(prompts[0], SamplingParams(**vars(sp)))
+        while any(r.remaining > 1 for r in eng.scheduler.running + eng.scheduler.waiting):
+            eng.step()
+        prompts_rest = prompts[1:]
+    else:
+        prompts_rest = prompts
+    for p in prompts_rest:
         eng.add_request(p, SamplingParams(**vars(sp)))
 
     def sync():
@@ -286,6 +308,8 @@ def main() -> None:
                        "l2": "inputs larger than L2 (weights + KV read per step >> 126 MB)",
                        "context_at_timed_steps": [context_at_timed, context_at_timed + args.steps],
                        "output_len": args.output_len, "timed_step_ms": step_stats,
+                       **({"shared_prefix": args.shared_prefix, "prefix_hit_rate": round(eng.prefix.hit_rate, 4)}
+                          if args.shared_prefix else {}),
                        **({"ms_per_step_at_start_of_decode": round(early_ms, 4),
                            "tok_s_at_start_of_decode": round(C / (early_ms / 1e3), 1)} if early_ms else {}),
                        "prefill_tok_s": round(C * L / prefill_s, 1), "prefill_steps": n_prefill_steps,

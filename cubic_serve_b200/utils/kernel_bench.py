@@ -89,12 +89,13 @@ def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str 
     if fmt == "bf16":
         w = wq_pack.pack_bf16(torch.randn(n, k, device=DEV) * 0.02)
         wbytes = n * k * 2
-    elif fmt == "fp8":
-        # e4m3 weights with row scales; the timed call is the GEMM on activations quantized beforehand (the fused
-        # norm / activation kernels produce them in a model step), ``fp8+quant`` adds the stand-alone quantizer
+    elif fmt in ("fp8", "fp8_block"):
+        # e4m3 weights with row (or 128 x 128 block) scales; the timed call is the GEMM on activations quantized
+        # beforehand (the fused norm / activation kernels produce them in a model step)
         from ..quantization import formats
-        p = formats.fp8_quantize(torch.randn(n, k, device=DEV) * 0.02)
-        w = wq_pack.pack_fp8(p["weight"], p["weight_scale"])
+        p = formats.fp8_quantize(torch.randn(n, k, device=DEV) * 0.02, block=fmt == "fp8_block")
+        w = (wq_pack.pack_fp8_block(p["weight"], p["weight_scale_inv"]) if fmt == "fp8_block"
+             else wq_pack.pack_fp8(p["weight"], p["weight_scale"]))
         wbytes = n * k + n * 4
     else:
         w = random_cubic_weight(n, k)
@@ -102,9 +103,9 @@ def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str 
     x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
     y = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
-    stream_k = fmt != "fp8" and (kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(m, n, w.fmt)))
+    stream_k = not fmt.startswith("fp8") and (kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(m, n, w.fmt)))
     sp = None if stream_k else (splits or K.choose_splits(m, n, k, fmt=w.fmt))
-    if fmt == "fp8":
+    if fmt.startswith("fp8"):
         x = K.fp8_quantize(x, out=K.Fp8Act(torch.empty(m, k, dtype=torch.uint8, device=DEV),
                                            torch.empty(m, dtype=torch.float32, device=DEV)))
     if act:
