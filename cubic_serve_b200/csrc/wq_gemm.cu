@@ -888,7 +888,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   const int cluster_default = o.cluster_splitk >= 0 ? o.cluster_splitk : g_cluster_splitk.load(std::memory_order_relaxed);
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0 || (ldx % (fmt_is_fp8(fmt) ? 16 : 8)) != 0) return -10;
   if (fmt != kFmtBf16 && fmt != kFmtCubic4 && fmt != kFmtAffine4 && fmt != kFmtNvfp4 && !fmt_is_fp8(fmt)) return -11;
-  if (fmt_is_fp8(fmt) && (!o.x_scale || !meta || stream_k)) return -15;
+  if (fmt_is_fp8(fmt) && (!o.x_scale || !meta || (stream_k && fmt != kFmtFp8))) return -15;
   if (fmt == kFmtFp8Block && o.tiles && (N % kTileN) != 0) return -16;   // stacked experts: whole block rows each
   if (fmt == kFmtCubic4 && (group_k % kBlockK) != 0) return -12;
   WqGemmParams p{};
@@ -951,7 +951,7 @@ static int wq_gemm_dispatch(int fmt, const void* x, int ldx, const void* codes, 
   // with CTA pairs each CTA of a pair fetches half of the rows of an activation tile
   if (fmt_is_fp8(fmt)) {
     const uint64_t w_rows = static_cast<uint64_t>(N) * (o.tiles ? o.num_experts : 1);
-    if (make_tmap_u8(&tx, x, M, K, ldx, p.mb) != 0) return -20;
+    if (make_tmap_u8(&tx, x, M, K, ldx, p.pair ? p.mb / 2 : p.mb) != 0) return -20;
     if (make_tmap_u8(&tw, codes, w_rows, K, K, kTileN) != 0) return -21;
   } else if (make_tmap_bf16(&tx, x, M, K, ldx, p.pair ? p.mb / 2 : p.mb) != 0) {
     return -20;
@@ -1080,13 +1080,20 @@ int cb_wq_gemm_grouped(int fmt, const void* x, int ldx, const void* codes, const
 // interleaved gate / up order and y has N / 2 columns.  K splits meet in a cluster or in `workspace`.
 // Counterpart of the reference's dynamic-token FP8 linear (quantization/extensions/fp8/kernels.py:81-130).
 // `block`: w_scale holds one scale per 128 x 128 block, [ceil(N / 128), ceil(K / 128)], instead of one per row.
+// `stream_k`: the persistent kernel (row scales only; CTA pairs above 256 rows), `min_units` / `workspace_bytes` as in
+// cb_wq_gemm_sk.
 int cb_wq_gemm_fp8(const void* xq, int ldx, const void* x_scale, const void* wq, const void* w_scale, int block, void* y,
-                   int ldy, const void* residual, int M, int N, int K, int splits, int swiglu, void* workspace,
-                   void* counters, void* status, void* stream, const CbTpLink* link) {
+                   int ldy, const void* residual, int M, int N, int K, int splits, int swiglu, int stream_k,
+                   int min_units, void* workspace, long long workspace_bytes, void* counters, void* status, void* stream,
+                   const CbTpLink* link) {
   if (swiglu && ((N % 32) != 0 || ldy < N / 2)) return -50;
   WqLaunchOpts o;
   o.x_scale = static_cast<const float*>(x_scale);
   o.swiglu = swiglu;
+  o.stream_k = stream_k != 0 && !block;
+  o.min_units = min_units;
+  o.workspace_bytes = workspace_bytes;
+  if (o.stream_k) splits = 1;
   return wq_gemm_dispatch(block ? cb::kFmtFp8Block : cb::kFmtFp8, xq, ldx, wq, w_scale, y, ldy, residual, 1.f, M, N, K, K, splits, workspace,
                           counters, status, stream, link, o);
 }

@@ -339,7 +339,7 @@ __device__ __forceinline__ void sk_reduce_write(const WqGemmParams& p, const SkS
 template <int FMT, bool PAIR>
 __global__ void __launch_bounds__(kSkThreads, 1)
 wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                  const __grid_constant__ CUtensorMap tmap_w,  // only for kFmtBf16
+                  const __grid_constant__ CUtensorMap tmap_w,  // only for the direct formats (bf16, fp8)
                   const __grid_constant__ WqGemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t x_bytes = static_cast<uint32_t>(PAIR ? p.mb >> 1 : p.mb) * 128u;   // this CTA's rows of the activation tile
@@ -348,7 +348,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   uint8_t* c_ring = smem + static_cast<size_t>(p.ax_stages) * ax_bytes;
   constexpr uint32_t kMeta = static_cast<uint32_t>(meta_bytes(FMT));
   constexpr uint32_t kCStage = kCodeBytes + kMeta;
-  float* epi_scratch = reinterpret_cast<float*>(c_ring + (FMT == kFmtBf16 ? 0 : static_cast<size_t>(p.c_stages) * kCStage));
+  float* epi_scratch = reinterpret_cast<float*>(c_ring + (fmt_is_direct(FMT) ? 0 : static_cast<size_t>(p.c_stages) * kCStage));
   SkCtl* ctl = reinterpret_cast<SkCtl*>(reinterpret_cast<uint8_t*>(epi_scratch) + kSkEpiScratchBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -369,7 +369,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSkMaxAx; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), 1 + (FMT == kFmtBf16 ? 0 : kSkGroupWarps * kPeers));
+      mbar_init(smem_u32(&ctl->full[s]), 1 + (fmt_is_direct(FMT) ? 0 : kSkGroupWarps * kPeers));
       mbar_init(smem_u32(&ctl->ax_empty[s]), 1);
     }
     for (int s = 0; s < kSkMaxC; ++s) {
@@ -416,7 +416,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // ------------------------------------------------ activation (and bf16 weight) tiles
     if (lane == 0) {
       tma_prefetch_desc(&tmap_x);
-      if (FMT == kFmtBf16) tma_prefetch_desc(&tmap_w);
+      if (fmt_is_direct(FMT)) tma_prefetch_desc(&tmap_w);
       pdl_wait();
       bool ok = true;
       if (p.tp.mode & kTpGatherWait) {
@@ -424,7 +424,8 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
         const uint32_t target = p.tp.ag_state[0] + p.tp.ag_expected;
         for (int r = 0; r < p.tp.size && ok; ++r) ok = wait_counter(p.tp.ag_flag + r, target, abort_flag);
       }
-      const uint32_t tx = x_bytes + (FMT == kFmtBf16 ? static_cast<uint32_t>(kATileBytes) : 0u);
+      const uint32_t tx = x_bytes + (fmt_is_direct(FMT) ? static_cast<uint32_t>(kATileBytes) : 0u);
+      constexpr int kBK = fmt_block_k(FMT);        // K columns per stage: 64 bf16 or 128 e4m3 (128 bytes either way)
       SkRing r;
       CB_TRACE_ONLY(int ti = 0;)
       while (ok && it.next(p, cta, grid, seg)) {
@@ -441,12 +442,12 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             // lands before the expectation is posted only drives the count negative inside the same phase
             const uint32_t bar0 = cluster_map(bar, 0);
             if (rank == 0) mbar_expect_tx(bar, 2u * tx);
-            tma_load_2d_pair(smem_u32(st), &tmap_x, kb * kBlockK, c.m0 + rank * (p.mb >> 1), bar0);
-            if (FMT == kFmtBf16) tma_load_2d_pair(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row, bar0);
+            tma_load_2d_pair(smem_u32(st), &tmap_x, kb * kBK, c.m0 + rank * (p.mb >> 1), bar0);
+            if (fmt_is_direct(FMT)) tma_load_2d_pair(smem_u32(st + x_bytes), &tmap_w, kb * kBK, w_row, bar0);
           } else {
             mbar_expect_tx(bar, tx);
-            tma_load_2d(smem_u32(st), &tmap_x, kb * kBlockK, c.m0, bar);
-            if (FMT == kFmtBf16) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBlockK, w_row, bar);
+            tma_load_2d(smem_u32(st), &tmap_x, kb * kBK, c.m0, bar);
+            if (fmt_is_direct(FMT)) tma_load_2d(smem_u32(st + x_bytes), &tmap_w, kb * kBK, w_row, bar);
           }
           r.advance(S);
         }
@@ -454,7 +455,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     }
   } else if (warp == 2) {
     // ------------------------------------------------ packed codes + metadata
-    if (FMT != kFmtBf16 && lane == 0) {
+    if (!fmt_is_direct(FMT) && lane == 0) {
       bool ok = true;
       SkRing r;
       while (ok && it.next(p, cta, grid, seg)) {
@@ -481,7 +482,9 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // complete ONE barrier (`full`), tested once.  (A loop run by a single thread of the warp was measured slower:
     // 550-700 cycles from the barrier to the commit instead of 150-300.)
     const bool leader = elect_one();
-    const uint32_t idesc = umma_idesc(PAIR ? 2 * kTileN : kTileN, static_cast<uint32_t>(p.mb), 1u, 1u);
+    // operand formats: bf16 x bf16 (kind::f16) or e4m3 x e4m3 (kind::f8f6f4)
+    const uint32_t idesc = umma_idesc(PAIR ? 2 * kTileN : kTileN, static_cast<uint32_t>(p.mb), FMT == kFmtFp8 ? 0u : 1u,
+                                      FMT == kFmtFp8 ? 0u : 1u);
     const uint32_t smem_base = smem_u32(smem);
     const uint64_t desc_hi = umma_desc_sw128(0);
     SkRing r;
@@ -513,8 +516,13 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
-            if (PAIR) umma_f16_pair(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
-            else umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            if constexpr (FMT == kFmtFp8) {
+              if (PAIR) umma_f8f6f4_pair(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+              else umma_f8f6f4(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            } else {
+              if (PAIR) umma_f16_pair(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+              else umma_f16(tmem_d, adesc + 2u * k4, bdesc + 2u * k4, idesc, k4 > 0 ? 1u : accumulate);
+            }
           }
           if (PAIR) {
             tc_commit_pair(smem_u32(&ctl->ax_empty[r.s]), 3u);
@@ -540,13 +548,29 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
   } else {
     // ------------------------------------------------ decode (warps 7..22) and epilogue (warps 3..6)
     // Geometry of the current segment (set by seg_geometry) and the shared LAST-segment epilogue.
-    int m0 = 0, rows_here = 0, n_base = 0, tile_id = 0;
+    int m0 = 0, rows_here = 0, n_base = 0, tile_id = 0, w_base = 0;
     auto seg_geometry = [&]() {
       const SkCoords c = sk_coords(p, seg.tile, rank);
       tile_id = c.tile_id;
       m0 = c.m0;
       rows_here = c.rows;
       n_base = c.n_tile * kTileN;
+      w_base = c.expert * p.N;              // first weight row of the tile's expert in the stacked matrix
+    };
+    // fp8: the feature's weight scale times the token's activation scale, applied as the sums leave tensor memory
+    // (partial sums of a streamed tile are linear in both, so every later path sees finished values); `quad` is the
+    // warp's lane quadrant, c0 the first batch row of the 16-column chunk
+    auto scale_acc = [&](uint32_t (&acc)[16], int quad, int c0) {
+      if constexpr (FMT == kFmtFp8) {
+        const int nn = n_base + quad * 32 + lane;
+        const float ws = nn < p.N ? p.row_scale[w_base + nn] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int r = c0 + j;
+          const float xs = r < rows_here ? __ldg(p.col_scale + m0 + r) : 0.f;
+          acc[j] = __float_as_uint(__uint_as_float(acc[j]) * (ws * xs));
+        }
+      }
     };
     // Last segment of the CTA: nothing is left to overlap with, so all 20 of these warps (640 threads) do the
     // epilogue together.  The rings are idle once the accumulator is complete, so the whole fp32 tile is staged
@@ -578,6 +602,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
           uint32_t acc[16];
           tmem_ld_32x16(taddr + ci * 16, acc);
           tmem_ld_wait();
+          scale_acc(acc, quad, ci * 16);
 #pragma unroll
           for (int j = 0; j < 16; ++j) stg[(ci * 16 + j) * kTileN + quad * 32 + lane] = __uint_as_float(acc[j]);
         }
@@ -700,7 +725,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
       // never leaves the loop early: the last segment ends at barriers shared with the epilogue warps
       while (it.next(p, cta, grid, seg)) {
         const bool tail = !it.has_more(p);
-        if (FMT != kFmtBf16 && ok) {
+        if (!fmt_is_direct(FMT) && ok) {
           // this group's k-blocks are every fourth one; the rings are stepped over the other groups' k-blocks
           // arithmetically instead of by empty loop iterations
           const int len = seg.kb_hi - seg.kb_lo;
@@ -814,6 +839,7 @@ wq_gemm_sk_kernel(const __grid_constant__ CUtensorMap tmap_x,
             uint32_t acc[16];
             tmem_ld_32x16(taddr + c0, acc);
             tmem_ld_wait();
+            scale_acc(acc, quad, c0);
 #pragma unroll
             for (int j = 0; j < 16; ++j) scr[j * 32 + lane] = __uint_as_float(acc[j]);
             __syncwarp();
@@ -984,6 +1010,7 @@ static int max_resident_pairs_fmt(int fmt) {
     case kFmtCubic4: return max_resident_pairs<kFmtCubic4>();
     case kFmtAffine4: return max_resident_pairs<kFmtAffine4>();
     case kFmtNvfp4: return max_resident_pairs<kFmtNvfp4>();
+    case kFmtFp8: return max_resident_pairs<kFmtFp8>();
     default: return max_resident_pairs<kFmtBf16>();
   }
 }
@@ -1063,7 +1090,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
   const size_t budget = 232448 - 1024 - 1024 - sizeof(SkCtl) - kSkEpiScratchBytes;
   const size_t kSkCStageBytes = static_cast<size_t>(sk_cstage_bytes(fmt));
   int S, NC;
-  if (fmt == kFmtBf16) {
+  if (fmt_is_direct(fmt)) {
     NC = 0;
     S = static_cast<int>(budget / ax);
   } else {
@@ -1073,7 +1100,8 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
     if (NC > kSkMaxC) NC = kSkMaxC;
   }
   if (S > kSkMaxAx) S = kSkMaxAx;
-  if (S < 2 || (fmt != kFmtBf16 && NC < 2)) return -14;
+  if (S < 2 || (!fmt_is_direct(fmt) && NC < 2)) return -14;
+  if (fmt == kFmtFp8Block) return -14;            // block scales need the per-stage promotion of the per-tile kernel
   p.ax_stages = S;
   p.c_stages = NC;
   size_t smem = S * ax + static_cast<size_t>(NC) * kSkCStageBytes + kSkEpiScratchBytes + sizeof(SkCtl) + 1024;
@@ -1086,6 +1114,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
       case kFmtCubic4: return launch_sk_pair_fmt<kFmtCubic4>(tx, tw, p, 2 * grid, smem, stream);
       case kFmtAffine4: return launch_sk_pair_fmt<kFmtAffine4>(tx, tw, p, 2 * grid, smem, stream);
       case kFmtNvfp4: return launch_sk_pair_fmt<kFmtNvfp4>(tx, tw, p, 2 * grid, smem, stream);
+      case kFmtFp8: return launch_sk_pair_fmt<kFmtFp8>(tx, tw, p, 2 * grid, smem, stream);
       default: return launch_sk_pair_fmt<kFmtBf16>(tx, tw, p, 2 * grid, smem, stream);
     }
   }
@@ -1093,6 +1122,7 @@ int launch_streamk(int fmt, const CUtensorMap& tx, const CUtensorMap& tw, WqGemm
     case kFmtCubic4: return launch_sk_fmt<kFmtCubic4>(tx, tw, p, grid, smem, stream);
     case kFmtAffine4: return launch_sk_fmt<kFmtAffine4>(tx, tw, p, grid, smem, stream);
     case kFmtNvfp4: return launch_sk_fmt<kFmtNvfp4>(tx, tw, p, grid, smem, stream);
+    case kFmtFp8: return launch_sk_fmt<kFmtFp8>(tx, tw, p, grid, smem, stream);
     default: return launch_sk_fmt<kFmtBf16>(tx, tw, p, grid, smem, stream);
   }
 }

@@ -448,6 +448,8 @@ class GpuExecutor:
             self._uploaded.synchronize()
             self._upload_pending = False
         b, rows = self._fill(segs, pad_rows_to=cap)
+        if cap is not None and getattr(self, "audit_poison_padding", False):
+            self._poison_padding(total, cap)
         k = self._launches & 1
         # the result buffer of this launch must have been collected: a third outstanding launch is an error, not an overwrite
         self._leases[k] = self.graph_rt.leases.acquire(k, f"launch {self._launches}")
@@ -471,6 +473,20 @@ class GpuExecutor:
                 self.out_host[k, :rows].copy_(self.out_ids[:rows], non_blocking=True)
             self._done[k].record(self.stream)
         return {"k": k, "rows": rows, "h2d": h2d, "launches": launches}
+
+    def _poison_padding(self, rows: int, cap: int) -> None:
+        """Audit facility (``guardrail/graph_audit.py``): the padding rows ``[rows, cap)`` of a decode bucket get random
+        token ids and positions, and the activations that a step leaves unwritten for them (the attention output) are
+        filled with NaN, so that any path from a padding row into a real row shows up in the real rows' logits.  The
+        rows still write no cache slot and attend to nothing."""
+        rng = np.random.default_rng(rows * 7919 + cap)
+        h = self.stage.h
+        h["token_ids"][rows:cap] = rng.integers(0, self.cfg.vocab_size, cap - rows)
+        h["positions"][rows:cap] = rng.integers(0, 1 << 12, cap - rows)
+        attn = getattr(self.runner, "attn", None)
+        if isinstance(attn, torch.Tensor):
+            with torch.cuda.stream(self.stream):
+                attn[rows:cap].fill_(float("nan"))
 
     def collect(self, handle: dict) -> np.ndarray:
         """Wait for a launched step and return its sampled ids (host array)."""

@@ -230,15 +230,25 @@ def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link,
     a = x if isinstance(x, Fp8Act) else fp8_quantize(x, ws)
     m, k = a.q.shape
     push = link is not None and (link.mode & 2)
-    if splits is None:
-        splits = choose_splits(m, w.n, k, fmt=w.fmt)
     l = native.lib()
-    if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
-        splits = 1
+    # the persistent kernel (stream-K at decode sizes with more tiles than SMs, CTA pairs above 256 rows) serves row
+    # scales; block scales and explicit split factors stay on the per-tile kernel
+    stream_k = (splits is None and w.fmt == FMT_FP8 and link is None
+                and use_stream_k(m, w.n, FMT_CUBIC4, sm_count(a.q.device), k // 2))
+    min_units = 0
+    if stream_k:
+        from .strategies import active
+        min_units = active().gemm.stream_k_min_units
+    else:
+        if splits is None:
+            splits = choose_splits(m, w.n, k, fmt=w.fmt)
+        if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
+            splits = 1
     code = l.cb_wq_gemm_fp8(a.q.data_ptr(), a.q.stride(0), a.scale.data_ptr(), w.codes.data_ptr(), w.meta.data_ptr(),
-                            int(w.fmt == FMT_FP8_BLOCK), None if push else out.data_ptr(), w.n if push else out.stride(0), _ptr(residual), m, w.n, k,
-                            int(splits), int(swiglu), ws.gemm.data_ptr(), ws.gemm_counters.data_ptr(),
-                            ws.status.data_ptr(), _stream(), None if link is None else ctypes.byref(link))
+                            int(w.fmt == FMT_FP8_BLOCK), None if push else out.data_ptr(), w.n if push else out.stride(0),
+                            _ptr(residual), m, w.n, k, int(splits or 1), int(swiglu), int(stream_k), int(min_units),
+                            ws.gemm.data_ptr(), ws.gemm.numel(), ws.gemm_counters.data_ptr(), ws.status.data_ptr(),
+                            _stream(), None if link is None else ctypes.byref(link))
     native.check(code, "cb_wq_gemm_fp8")
     return out
 

@@ -264,7 +264,7 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_rmsnorm_fp8.restype = i
     l.cb_swiglu_fp8.argtypes = [vp, vp, i, vp, i, i, vp]
     l.cb_swiglu_fp8.restype = i
-    l.cb_wq_gemm_fp8.argtypes = [vp, i, vp, vp, vp, i, vp, i, vp, i, i, i, i, i, vp, vp, vp, vp, vp]
+    l.cb_wq_gemm_fp8.argtypes = [vp, i, vp, vp, vp, i, vp, i, vp, i, i, i, i, i, i, i, vp, ll, vp, vp, vp, vp]
     l.cb_wq_gemm_fp8.restype = i
     l.cb_wq_gemm_fp8_grouped.argtypes = [vp, i, vp, vp, vp, i, vp, i, i, i, i, vp, i, i, i, i, vp, vp]
     l.cb_wq_gemm_fp8_grouped.restype = i

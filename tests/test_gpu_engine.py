@@ -246,3 +246,27 @@ def test_prefix_resume_equals_cold_start_on_device():
     r0.ws.check_status()
     r1.ws.check_status()
     assert eng.pool.num_used == len(eng.prefix)                 # only cache entries keep pages
+
+
+def test_captured_decode_graphs_pass_the_graph_level_audits():
+    """Whole-graph audits (``guardrail/graph_audit.py``): two bucket sizes agree, poisoned padding rows change no bit
+    of the real rows, and a request's logits do not depend on the row it occupies."""
+    from cubic_serve_b200.executor.gpu_executor import GpuExecutor
+    from cubic_serve_b200.guardrail.graph_audit import audit_decode_graphs
+    from cubic_serve_b200.models.decoder import DecoderRunner, random_decoder_weights
+    dev = torch.device("cuda")
+    cfg = ModelConfig(name="audit", num_layers=3, hidden_size=512, num_q_heads=8, num_kv_heads=2, head_dim=128,
+                      intermediate_size=1024, vocab_size=2048, rope_theta=1e6, quant=QuantSpec("cubic", 4, 128))
+    w = random_decoder_weights(cfg, dev, seed=0, std=0.05)
+
+    def build():
+        runner = DecoderRunner(cfg, w, num_pages=64, max_tokens=256)
+        return GpuExecutor(runner, max_rows=32, max_prefill_tokens=256, max_model_len=128)
+
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, cfg.vocab_size, n).tolist() for n in (19, 33, 40, 27, 16)]
+    rep = audit_decode_graphs(build, prompts, capacities=(8, 32), steps=3)
+    assert rep.cross_m_ids_equal and rep.cross_m_max_rel < 2e-2, rep
+    assert rep.poisoned_padding_bit_identical and rep.poisoned_padding_finite, rep
+    assert rep.permutation_bit_identical, rep
+    assert rep.ok
