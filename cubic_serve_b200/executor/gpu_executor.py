@@ -41,6 +41,9 @@ class Segment:
     uid: int = -1                # identity of the request owning the slot (page-table row reuse detection)
     mask: np.ndarray | None = None   # allowed-token bitmask of the sampled row (uint32 words, bit set = allowed)
     budget_init: int = -2        # thinking budget of the sampled row's request: -2 keep, -1 none, >= 0 (re)start with it
+    # speculative rounds of a constrained request: callable(drafts) -> uint32 [len(drafts) + 1, words], row j = the
+    # allowed tokens after the request's grammar has accepted drafts[:j] (the matcher is left where it was)
+    mask_fn: object = None
 
 
 class _Staging:

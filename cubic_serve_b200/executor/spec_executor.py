@@ -27,6 +27,7 @@ from .gpu_executor import GpuExecutor, Segment
 
 class SpeculativeGpuExecutor(GpuExecutor):
     speculative_sampling = True      # rounds also serve requests with temperature > 0 (p / q rejection sampling)
+    speculative_grammar = True       # ... and constrained requests: every review row is sampled under the grammar's mask
 
     def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
                  **kw) -> None:
@@ -168,6 +169,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
                 launches += self.mtp.launches + 4
             if self.timing:
                 self._ev_mid.record(self.stream)
+            self._review_mask = self._grammar_masks(segs, Kd, draft_ids)
             hidden = self._review_and_verify(segs, Kd, draft_ids, target_ids)
             launches += r.launches_per_step + 1
             rows = torch.arange(R, device=dev) * (Kd + 1) + self.accepted[:R].long()
@@ -194,6 +196,29 @@ class SpeculativeGpuExecutor(GpuExecutor):
         self.kernel_launches_last = launches + 2
         self.d2h_bytes_last = R * (Kd + 2) * 4
         return out
+
+    def _grammar_masks(self, segs: list[Segment], Kd: int, draft_ids: torch.Tensor):
+        """Allowed-token masks of the review rows when a request of the round is constrained: row j of a request is
+        sampled under its grammar's state after drafts[:j] (reference: the per-round grammar transactions of
+        ``generation/constraints.py`` there).  The drafts are read back for this, so a constrained round pays one
+        synchronisation between proposals and review; rounds without constraints do not.  Returns a device tensor
+        ``[R (Kd + 1), words]`` or None."""
+        if not any(s.mask_fn is not None for s in segs):
+            return None
+        R, T = len(segs), len(segs) * (Kd + 1)
+        drafts = draft_ids.cpu().numpy()                   # synchronises with the proposal passes on this stream
+        words = -(-self.cfg.vocab_size // 32)
+        if getattr(self, "_rm_host", None) is None or self._rm_host.shape[0] < T:
+            self._rm_host = torch.empty(max(T, self.max_rows * (self.speculative_depth + 1)), words, dtype=torch.int32,
+                                        pin_memory=True)
+            self._rm_dev = torch.empty_like(self._rm_host, device=self.device)
+        hm = self._rm_host.numpy().view(np.uint32)
+        hm[:T] = 0xFFFFFFFF
+        for i, s in enumerate(segs):
+            if s.mask_fn is not None:
+                hm[i * (Kd + 1):(i + 1) * (Kd + 1)] = s.mask_fn([int(t) for t in drafts[i]])
+        self._rm_dev[:T].copy_(self._rm_host[:T], non_blocking=True)
+        return self._rm_dev[:T]
 
     def _review_and_verify(self, segs: list[Segment], Kd: int, draft_ids: torch.Tensor, target_ids: torch.Tensor) -> torch.Tensor:
         """ONE target pass over ``[root, d1 .. dK]`` of every request (greedy ids of all rows into ``target_ids``) and
@@ -229,16 +254,17 @@ class SpeculativeGpuExecutor(GpuExecutor):
         r, dev = self.runner, self.device
         R, T = len(segs), len(segs) * (Kd + 1)
         sm = getattr(self, "_sampling", None)
+        mask = getattr(self, "_review_mask", None)          # grammar masks of the review rows (constrained requests)
         if sm is not None:
             # p / q rejection sampling over the candidate distributions; `target_ids` receives the emitted tokens
             rep = lambda t: t.repeat_interleave(Kd + 1)                                # noqa: E731
             K.sample_candidates(logits, self.p_val[:T], self.p_id[:T], temperature=rep(sm["temperature"]),
-                                top_k=rep(sm["top_k"]), vocab=logits.shape[1])
+                                top_k=rep(sm["top_k"]), vocab=logits.shape[1], mask=mask)
             K.verify_sampled(self.q_val, self.q_id, self.p_val, self.p_id, draft_ids, self.depth_t[:R], Kd,
                              sm["temperature"], sm["top_p"], sm["top_k"], sm["seeds"], sm["draws"], self.accepted,
                              self.bonus, target_ids)
             return hidden
-        K.sample(logits, target_ids.view(-1), vocab=logits.shape[1])
+        K.sample(logits, target_ids.view(-1), vocab=logits.shape[1], mask=mask)
         forced = None
         if self.force_acceptance is not None:
             draws = self._rng.random((R, Kd)) < self.force_acceptance

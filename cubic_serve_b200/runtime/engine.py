@@ -173,15 +173,41 @@ class LLMEngine:
             r = s.request
             toks = [0] if ahead else r.tokens[s.start:s.start + s.count]
             sp = r.sampling
-            mask = None
+            mask = mask_fn = None
             if s.sample and sp.matcher is not None:
                 mask = np.zeros(self._mask_words, dtype=np.uint32)
                 sp.matcher.fill_bitmask(mask)
+                mask_fn = self._review_masks_of(sp.matcher)
             segs.append(Segment(r.slot, toks, s.start, r.pages, s.sample, sp.temperature, sp.top_p, sp.top_k,
                                 sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF,
                                 r.draws + (1 if ahead else 0), (r.arrival << 16) | (r.preemptions & 0xFFFF), mask,
-                                self._budget_init(r) if s.sample and end_id is not None else -2))
+                                self._budget_init(r) if s.sample and end_id is not None else -2, mask_fn))
         return segs
+
+    def _review_masks_of(self, matcher):
+        """The mask rows of a speculative round for one constrained request: row j allows what the grammar allows after
+        it has accepted the first j drafts.  The drafts are fed to the matcher tentatively and rolled back, so the
+        matcher is where it was afterwards; rows behind a draft the grammar refuses are never reached by the
+        verification (the refused draft cannot equal the masked choice) and are left open."""
+        words = self._mask_words
+
+        def masks(drafts: list[int]) -> np.ndarray:
+            out = np.full((len(drafts) + 1, words), 0xFFFFFFFF, dtype=np.uint32)
+            row = np.zeros(words, dtype=np.uint32)
+            matcher.fill_bitmask(row)
+            out[0] = row
+            fed = 0
+            for j, t in enumerate(drafts):
+                if getattr(matcher, "finished", False) or not matcher.accept(int(t)):
+                    break
+                fed += 1
+                row = np.zeros(words, dtype=np.uint32)
+                matcher.fill_bitmask(row)
+                out[j + 1] = row
+            if fed:
+                matcher.rollback(fed)
+            return out
+        return masks
 
     def _budget_init(self, r: Request) -> int:
         """Thinking-budget command of a sampled row: the device counter of the request's slot is (re)armed on the
@@ -209,6 +235,8 @@ class LLMEngine:
         # verify by p / q rejection sampling (``speculative_sampling``), sampling requests too; a step with a
         # constrained request runs the plain way
         samples = bool(getattr(self.executor, "speculative_sampling", False))
+        if constrained and getattr(self.executor, "speculative_grammar", False):
+            constrained = False          # the review rows are sampled under the grammars' masks (Segment.mask_fn)
         if spec and segs and not constrained and all(len(s.token_ids) == 1 and s.sample and (samples or s.temperature == 0)
                                                      for s in segs):
             # speculative round: every request gets its accepted drafts plus one bonus token
@@ -230,8 +258,14 @@ class LLMEngine:
                     continue
                 sampled[s.request.request_id] = [int(t) for t in v] if isinstance(v, (list, tuple)) else int(v)
                 m = s.request.sampling.matcher
-                if m is not None and not isinstance(v, (list, tuple)) and not m.accept(int(v)):
-                    raise RuntimeError(f"request {s.request.request_id}: sampled token {int(v)} violates its constraint")
+                if m is not None:
+                    # a speculative round hands back several tokens: accepted drafts and the next token, all sampled
+                    # under the grammar's masks; tokens after the one that completes the grammar are cut by the stop rule
+                    for t in (v if isinstance(v, (list, tuple)) else [v]):
+                        if getattr(m, "finished", False):
+                            break
+                        if not m.accept(int(t)):
+                            raise RuntimeError(f"request {s.request.request_id}: sampled token {int(t)} violates its constraint")
             else:
                 self.prefill_tokens += s.count
         finished = {r.request_id: r for r in self.scheduler.commit(plan, sampled, self.eos_token_id)}

@@ -234,3 +234,42 @@ def test_sampled_requests_take_speculative_rounds():
     eng3, ex3, _ = _build(3)
     c = eng3.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True, temperature=0.9, top_k=8, top_p=0.95, seed=99))
     assert a != c
+
+
+def test_constrained_requests_take_speculative_rounds_under_their_grammar():
+    """A ``choice`` constraint during MTP rounds: every review row is sampled under the grammar's mask for its position,
+    so the emitted tokens spell one of the options and equal what plain constrained decoding emits."""
+    from cubic_serve_b200.generation.constraints import ChoiceMatcher
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [100 + ord(c) for c in text]
+
+    eos = 3
+    options = ["alpha beta", "alphabet soup", "gamma"]
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (18, 31)]
+
+    def run(depth):
+        eng, ex, runner = _build(depth)
+        outs = []
+        for p in prompts:
+            sp = SamplingParams(max_tokens=24, stop_token_ids=(eos,), matcher=ChoiceMatcher(options, Tok(), eos))
+            rid = eng.add_request(p, sp)
+            req = eng.requests[rid]
+            free = eng.add_request(p[::-1], SamplingParams(max_tokens=9, ignore_eos=True))   # shares the rounds
+            free_req = eng.requests[free]
+            while eng.has_unfinished:
+                eng.step()
+            assert len(free_req.output) == 9
+            outs.append(list(req.output))
+        runner.ws.check_status()
+        return outs, ex
+
+    plain, _ = run(0)
+    spec, ex = run(3)
+    assert ex.stats["rounds"] > 0
+    for toks in spec:
+        assert toks[-1] == eos and "".join(chr(t - 100) for t in toks[:-1]) in options
+    assert spec == plain
