@@ -194,8 +194,9 @@ def main() -> None:
     if args.spec_depth:
         from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
         from cubic_serve_b200.models.mtp import MtpRunner, random_mtp_weights
-        assert world == 1, "speculative rounds run with tensor parallel size 1 in this benchmark"
-        ex = SpeculativeGpuExecutor(runner, MtpRunner(runner, random_mtp_weights(cfg, dev)), args.spec_depth,
+        assert pp is None and (tp is None or tp.mode == "nccl"), "speculative rounds: --comm nccl, no pipeline stages"
+        ex = SpeculativeGpuExecutor(runner, MtpRunner(runner, random_mtp_weights(cfg, dev, tp_rank=tp_rank, tp_size=tp_size)),
+                                    args.spec_depth,
                                     force_acceptance=args.accept, max_rows=C, max_prefill_tokens=prefill_tokens,
                                     max_model_len=max_len)
     else:

@@ -35,6 +35,10 @@ class SpeculativeGpuExecutor(GpuExecutor):
         # prefix is folded into it afterwards (DecoderRunner.begin_gdn_review / fold_gdn)
         super().__init__(runner, rows_per_request=depth + 1, use_graphs=False, **kw)
         self.mtp = mtp
+        if runner.tp is not None:
+            # vocabulary-sharded logits: drafts and review rows are sampled by the candidate exchange + merge of the
+            # tensor-parallel sampler (greedy requests; p / q verification needs merged candidate lists)
+            self.speculative_sampling = False
         self.speculative_depth = depth
         self.force_acceptance = force_acceptance
         self._rng = np.random.default_rng(seed)
@@ -74,8 +78,12 @@ class SpeculativeGpuExecutor(GpuExecutor):
             d = self.stage.d
             if rows:
                 logits = r.forward_logits(b, hidden, self.logits)
-                K.sample(logits, self.out_ids[:rows], temperature=d["temperature"][:rows], top_p=d["top_p"][:rows],
-                         top_k=d["top_k"][:rows], seeds=d["seeds"][:rows], counters=d["draws"][:rows], vocab=logits.shape[1])
+                if r.tp is None:
+                    K.sample(logits, self.out_ids[:rows], temperature=d["temperature"][:rows], top_p=d["top_p"][:rows],
+                             top_k=d["top_k"][:rows], seeds=d["seeds"][:rows], counters=d["draws"][:rows],
+                             vocab=logits.shape[1])
+                else:
+                    r.tp.sample_sharded_nccl(logits, rows, self.out_ids, d, r.w.vocab_start)
             # MTP pass over the same rows: row i is preceded by the target hidden of row i - 1 (the first row of a
             # segment by the request's carried hidden)
             prev = self.hidden_rows[:total]
@@ -153,7 +161,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
                 lg = self.mtp.logits(hid, R, self.mtp_logits)
                 tmp = self.out_ids[:R]
                 if sm is None:
-                    K.sample(lg, tmp, vocab=lg.shape[1])
+                    self._sample_greedy(lg, R, tmp)
                 else:
                     # the draft is drawn from the head's shaped distribution; its candidates are kept as q.  Draft draws
                     # live in their own part of the request's Philox stream (sub-stream 0x4000 + depth)
@@ -264,7 +272,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
                              sm["temperature"], sm["top_p"], sm["top_k"], sm["seeds"], sm["draws"], self.accepted,
                              self.bonus, target_ids)
             return hidden
-        K.sample(logits, target_ids.view(-1), vocab=logits.shape[1], mask=mask)
+        self._sample_greedy(logits, T, target_ids.view(-1), mask)
         forced = None
         if self.force_acceptance is not None:
             draws = self._rng.random((R, Kd)) < self.force_acceptance
@@ -277,6 +285,21 @@ class SpeculativeGpuExecutor(GpuExecutor):
             draft_ids.copy_(torch.where(keep, agree, draft_ids))
         K.verify_greedy(target_ids, draft_ids, self.depth_t[:R], Kd, self.accepted, self.bonus, forced)
         return hidden
+
+    def _sample_greedy(self, logits: torch.Tensor, rows: int, out_ids: torch.Tensor, mask=None) -> None:
+        """Greedy ids of ``rows`` rows: over the whole vocabulary, or (tensor parallel) merged over the ranks' shards."""
+        r = self.runner
+        if r.tp is None:
+            K.sample(logits, out_ids, vocab=logits.shape[1], mask=mask)
+            return
+        if getattr(self, "_greedy_d", None) is None or self._greedy_d["temperature"].shape[0] < rows:
+            n = max(rows, self.max_rows * (self.speculative_depth + 1))
+            z = lambda dt: torch.zeros(n, dtype=dt, device=self.device)          # noqa: E731
+            self._greedy_d = {"temperature": z(torch.float32), "top_p": torch.ones(n, device=self.device),
+                              "top_k": z(torch.int32), "seeds": z(torch.int64), "draws": z(torch.int64)}
+        if mask is not None:
+            mask = mask[:rows, r.w.vocab_start // 32:]
+        r.tp.sample_sharded_nccl(logits, rows, out_ids, self._greedy_d, r.w.vocab_start, mask)
 
     def _review_logits(self, rows: int) -> torch.Tensor:
         if not hasattr(self, "_rl") or self._rl.shape[0] < rows:

@@ -31,18 +31,38 @@ class MtpWeights:
     norm: torch.Tensor
 
 
-def random_mtp_weights(cfg: ModelConfig, device, seed: int = 1, std: float = 0.02) -> MtpWeights:
+def random_mtp_weights(cfg: ModelConfig, device, seed: int = 1, std: float = 0.02, tp_rank: int = 0,
+                       tp_size: int = 1) -> MtpWeights:
+    """Random head weights.  Under tensor parallelism every rank draws the FULL matrices from the same seed and keeps
+    its rows (QKV: whole heads, gate / up features) or columns (o, down), like ``random_decoder_weights``; the
+    2H -> H input projection and the norms are replicated."""
     gen = torch.Generator(device=device).manual_seed(seed * 7919)
     H, D = cfg.hidden_size, cfg.head_dim
+    hq, hkv, inter = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.intermediate_size // tp_size
+    r = tp_rank
 
     def rnd(n, k):
         return torch.randn(n, k, device=device, generator=gen) * std
 
+    def sections(full, widths):
+        out, base = [], 0
+        for w in widths:
+            out.append(full[base + r * w:base + (r + 1) * w])
+            base += w * tp_size
+        return torch.cat(out).contiguous()
+
+    def cols(full, width):
+        return full[:, r * width:(r + 1) * width].contiguous()
+
     ones = lambda n: torch.ones(n, device=device, dtype=torch.bfloat16)  # noqa: E731
-    layer = LayerWeights(ln1=ones(H), ln2=ones(H), qkv=quantize_linear(rnd((cfg.num_q_heads + 2 * cfg.num_kv_heads) * D, H), cfg),
-                         o=quantize_linear(rnd(H, cfg.q_size), cfg),
-                         gate_up=quantize_linear(rnd(2 * cfg.intermediate_size, H), cfg),
-                         down=quantize_linear(rnd(H, cfg.intermediate_size), cfg))
+    qkv = rnd((cfg.num_q_heads + 2 * cfg.num_kv_heads) * D, H)
+    o = rnd(H, cfg.q_size)
+    gate_up = rnd(2 * cfg.intermediate_size, H)
+    down = rnd(H, cfg.intermediate_size)
+    layer = LayerWeights(ln1=ones(H), ln2=ones(H), qkv=quantize_linear(sections(qkv, [hq * D, hkv * D, hkv * D]), cfg),
+                         o=quantize_linear(cols(o, hq * D), cfg),
+                         gate_up=quantize_linear(sections(gate_up, [inter, inter]), cfg),
+                         down=quantize_linear(cols(down, inter), cfg))
     return MtpWeights(ones(H), ones(H), quantize_linear(rnd(H, 2 * H), cfg), layer, ones(H))
 
 
@@ -53,6 +73,10 @@ class MtpRunner:
         self.t = target
         self.w = weights
         cfg, dev = target.cfg, target.device
+        if target.tp is not None and target.tp.fused is not None:
+            raise ValueError("the MTP head runs with the NCCL tensor-parallel collectives (tp mode 'nccl')")
+        self.part = (torch.empty(target.max_tokens, cfg.hidden_size, dtype=torch.bfloat16, device=dev)
+                     if target.tp is not None else None)
         blob = K.kv_blob_bytes(target.D, target.k_bits, target.v_bits)
         self.kv = torch.zeros(target.num_pages, target.hkv, blob, dtype=torch.uint8, device=dev)
         T, H = target.max_tokens, cfg.hidden_size
@@ -74,7 +98,10 @@ class MtpRunner:
         t, w, cfg = self.t, self.w, self.t.cfg
         T, H = b.num_tokens, cfg.hidden_size
         emb, cat, h = self.emb[:T], self.cat[:T], self.h[:T]
+        tp = t.tp
         K.embedding(b.token_ids[:T], t.w.embed, out=emb, vocab_start=t.w.vocab_start)
+        if tp is not None:
+            tp.all_reduce(emb)                      # vocabulary-sharded table: the owner contributes the row, the others zeros
         # the two normalised halves sit side by side in `cat` (row stride 2H); the norm kernel writes dense
         # rows, so it goes through dense temporaries and the halves are copied in
         e_n = K.rmsnorm(emb, w.enorm, cfg.rms_eps)
@@ -94,12 +121,24 @@ class MtpRunner:
                           t.v_bits, splits=b.attn_splits, ws=t.ws)
         if t.kv_rotation:
             K.hadamard(attn)
-        K.wq_gemm(attn, lw.o, out=h, residual=h, ws=t.ws)
-        K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x)
+        if tp is None:
+            K.wq_gemm(attn, lw.o, out=h, residual=h, ws=t.ws)
+            K.rmsnorm(h, lw.ln2, cfg.rms_eps, out=x)
+        else:
+            part = self.part[:T]
+            K.wq_gemm(attn, lw.o, out=part, ws=t.ws)
+            tp.all_reduce(part)
+            K.rmsnorm(part, lw.ln2, cfg.rms_eps, out=x, residual=h)      # h += sum of the ranks' partial rows
         gu, act = t.gu[:T], t.act[:T]
         fused = 2 - K.gate_up_act(x, lw.gate_up, gu, act, ws=t.ws)
-        K.wq_gemm(act, lw.down, out=h, residual=h, ws=t.ws)
-        self.launches = 16 - fused
+        if tp is None:
+            K.wq_gemm(act, lw.down, out=h, residual=h, ws=t.ws)
+        else:
+            part = self.part[:T]
+            K.wq_gemm(act, lw.down, out=part, ws=t.ws)
+            tp.all_reduce(part)
+            h.add_(part)
+        self.launches = 16 - fused + (4 if tp is not None else 0)
         return h
 
     def logits(self, hidden: torch.Tensor, rows: int, out: torch.Tensor) -> torch.Tensor:

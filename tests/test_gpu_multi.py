@@ -52,3 +52,10 @@ def test_two_pipeline_stages_give_the_one_gpu_tokens():
     one = pp_check.main(["--pp", "1"])
     two = _torchrun(2, "cubic_serve_b200.parallel.pp_check", "--pp", "2")
     assert two["tokens"] == one["tokens"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_mtp_rounds_under_tensor_parallelism_emit_the_one_gpu_greedy_tokens():
+    rep = _torchrun(2, "cubic_serve_b200.parallel.spec_check", "--depth", "3")
+    assert rep["rounds"] > 0 and rep["lengths_ok"]
+    assert rep["token_agreement_with_one_gpu_greedy"] >= 0.9, rep
