@@ -331,25 +331,17 @@ wq_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x,
         if (!__all_sync(0xffffffffu, mbar_wait_park(smem_u32(&ctl->acc_ready[buf]), ph, abort_flag))) break;
         tc_fence_after();
         const float sc = __ldg(bs + i);
-        // a tensor-memory load takes a few hundred cycles to return and a warp has up to four of them per stage: they
-        // go out two at a time (32 values in flight beside the 64 accumulators fit the register budget of 18 warps)
-        const uint32_t tbase = tmem_base + static_cast<uint32_t>(buf) * buf_cols + (static_cast<uint32_t>(pquad * 32) << 16);
+        // one chunk at a time: 16 values in flight beside the 64 accumulators is what the register budget of 18 warps
+        // holds without spilling (two or four loads in flight spilled and ran 1.7 x slower)
 #pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-          uint32_t part[2][16];
+        for (int it = 0; it < 4; ++it) {
+          const int ci = ppair + 4 * it;
+          if (ci < pchunks) {
+            uint32_t part[16];
+            tmem_ld_32x16(tmem_base + static_cast<uint32_t>(buf) * buf_cols + (static_cast<uint32_t>(pquad * 32) << 16) + ci * 16, part);
+            tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int ci = ppair + 4 * (2 * h2 + e);
-            if (ci < pchunks) tmem_ld_32x16(tbase + ci * 16, part[e]);
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int ci = ppair + 4 * (2 * h2 + e);
-            if (ci < pchunks) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) racc[2 * h2 + e][j] = fmaf(sc, __uint_as_float(part[e][j]), racc[2 * h2 + e][j]);
-            }
+            for (int j = 0; j < 16; ++j) racc[it][j] = fmaf(sc, __uint_as_float(part[j]), racc[it][j]);
           }
         }
         tc_fence_before();

@@ -70,6 +70,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
 
     def _execute_with_hidden(self, segs):
         total = sum(len(s.token_ids) for s in segs)
+        masked = self._stage_masks(segs)                # allowed-token masks of constrained requests' sampled rows
         b, rows = self._fill(segs)
         r = self.runner
         with torch.cuda.stream(self.stream):
@@ -78,12 +79,13 @@ class SpeculativeGpuExecutor(GpuExecutor):
             d = self.stage.d
             if rows:
                 logits = r.forward_logits(b, hidden, self.logits)
+                mask = d["mask"][:rows, r.w.vocab_start // 32:] if masked else None
                 if r.tp is None:
                     K.sample(logits, self.out_ids[:rows], temperature=d["temperature"][:rows], top_p=d["top_p"][:rows],
                              top_k=d["top_k"][:rows], seeds=d["seeds"][:rows], counters=d["draws"][:rows],
-                             vocab=logits.shape[1])
+                             vocab=logits.shape[1], mask=mask)
                 else:
-                    r.tp.sample_sharded_nccl(logits, rows, self.out_ids, d, r.w.vocab_start)
+                    r.tp.sample_sharded_nccl(logits, rows, self.out_ids, d, r.w.vocab_start, mask)
             # MTP pass over the same rows: row i is preceded by the target hidden of row i - 1 (the first row of a
             # segment by the request's carried hidden)
             prev = self.hidden_rows[:total]

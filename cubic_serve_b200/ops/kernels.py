@@ -222,7 +222,8 @@ def swiglu_fp8(gate_up: torch.Tensor, ws: Workspace | None = None) -> Fp8Act:
     return out
 
 
-def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link, swiglu: bool) -> torch.Tensor:
+def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link, swiglu: bool,
+                 min_units: int | None = None) -> torch.Tensor:
     """The fp8 branch of ``wq_gemm`` / ``wq_gemm_act``: quantize the activations per token unless the caller already
     holds them as ``Fp8Act``, then e4m3 x e4m3 on the tensor cores with both scales applied in the epilogue."""
     if link is not None and (link.mode & 1) and not isinstance(x, Fp8Act):
@@ -233,13 +234,15 @@ def _wq_gemm_fp8(x, w: PackedWeight, out, residual, splits, ws: Workspace, link,
     l = native.lib()
     # the persistent kernel (stream-K at decode sizes with more tiles than SMs, CTA pairs above 256 rows) serves row
     # scales; block scales and explicit split factors stay on the per-tile kernel
+    # (measured: the fp8 loop is bound by the L2 -> SM operand feed in both kernels; CTA pairs pay off for deep K at
+    # prefill sizes -- 4096 x 4096 x 12288: 153 us against 176 us -- and nowhere else, stream-K at decode sizes ties)
     stream_k = (splits is None and w.fmt == FMT_FP8 and link is None
-                and use_stream_k(m, w.n, FMT_CUBIC4, sm_count(a.q.device), k // 2))
-    min_units = 0
-    if stream_k:
+                and (min_units is not None or (m >= 2048 and k >= 8192 and (-(-w.n // 128)) % 2 == 0)))
+    if stream_k and min_units is None:
         from .strategies import active
         min_units = active().gemm.stream_k_min_units
-    else:
+    min_units = min_units or 0
+    if not stream_k:
         if splits is None:
             splits = choose_splits(m, w.n, k, fmt=w.fmt)
         if splits > 1 and l.cb_wq_gemm_workspace_bytes(m, w.n, splits) > ws.gemm.numel():
@@ -274,7 +277,7 @@ def wq_gemm(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = None,
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     ws = ws or workspace(x.device)
     if w.fmt in (FMT_FP8, FMT_FP8_BLOCK):
-        return _wq_gemm_fp8(x, w, out, residual, splits, ws, link, False)
+        return _wq_gemm_fp8(x, w, out, residual, splits, ws, link, False, min_units)
     l = native.lib()
     if splits is None and min_units is None and link is None and TUNED_PLANS:
         tuned = TUNED_PLANS.get(f"{w.fmt}:{m}:{w.n}:{k}:0")
@@ -323,7 +326,7 @@ def wq_gemm_act(x: torch.Tensor, w: PackedWeight, out: torch.Tensor | None = Non
     assert out.stride(1) == 1 and out.shape == (m, w.n // 2)
     ws = ws or workspace(x.device)
     if w.fmt in (FMT_FP8, FMT_FP8_BLOCK):
-        return _wq_gemm_fp8(x, w, out, None, splits, ws, link, True)
+        return _wq_gemm_fp8(x, w, out, None, splits, ws, link, True, min_units)
     l = native.lib()
     if splits is None and min_units is None and link is None and TUNED_PLANS:
         tuned = TUNED_PLANS.get(f"{w.fmt}:{m}:{w.n}:{k}:1")

@@ -103,7 +103,8 @@ def bench_gemm(m: int, n: int, k: int, splits: int | None, iters: int, fmt: str 
     x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
     y = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
-    stream_k = not fmt.startswith("fp8") and (kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(m, n, w.fmt)))
+    stream_k = fmt != "fp8_block" and (kernel == "streamk" or (kernel == "auto" and splits is None and K.use_stream_k(
+        m, n, wq_pack.FMT_CUBIC4 if fmt == "fp8" else w.fmt, k=k // 2 if fmt == "fp8" else k)))
     sp = None if stream_k else (splits or K.choose_splits(m, n, k, fmt=w.fmt))
     if fmt.startswith("fp8"):
         x = K.fp8_quantize(x, out=K.Fp8Act(torch.empty(m, k, dtype=torch.uint8, device=DEV),
