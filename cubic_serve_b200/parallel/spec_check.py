@@ -1,6 +1,7 @@
 """Speculative decoding under tensor parallelism, on real GPUs: MTP rounds of a tensor-parallel model (NCCL
-collectives, vocabulary-sharded sampling of drafts and review rows) must emit the tokens of plain greedy decoding on
-one GPU, because greedy rounds are lossless.
+collectives, vocabulary-sharded sampling of drafts and review rows) must emit the tokens of plain greedy decoding of
+the SAME partition, because greedy rounds are lossless (one GPU holding the whole model is decoded too, for the record:
+its sums are ordered differently, and a token that rounding flips sends the rest of that request elsewhere).
 
 Run under ``python -m torch.distributed.run --nproc-per-node N -m cubic_serve_b200.parallel.spec_check``; every rank
 drives the same engine in lockstep (as ``bench.py`` does), rank 0 also decodes the same prompts on its own and prints
@@ -58,12 +59,18 @@ def main(argv=None) -> dict | None:
 
     tp = TensorParallel(dist.group.WORLD, dev, mode="nccl", hidden=cfg.hidden_size, max_tokens=512) if world > 1 else None
     spec, stats = generate(tp, rank if tp else 0, world if tp else 1, args.depth)
+    same_partition, _ = generate(tp, rank if tp else 0, world if tp else 1, 0)
     report = None
     if rank == 0:
         plain, _ = generate(None, 0, 1, 0)
-        agree = float(np.mean([a == b for pa, pb in zip(plain, spec) for a, b in zip(pa, pb)]))
+
+        def agreement(a, b):
+            return round(float(np.mean([x == y for pa, pb in zip(a, b) for x, y in zip(pa, pb)])), 4)
+
         report = {"ranks": world, "depth": args.depth, "rounds": stats["rounds"], "proposed": stats["proposed"],
-                  "accepted": stats["accepted"], "token_agreement_with_one_gpu_greedy": round(agree, 4),
+                  "accepted": stats["accepted"], "token_agreement_with_plain_greedy": agreement(same_partition, spec),
+                  "token_agreement_with_one_gpu_greedy": agreement(plain, spec),
+                  "first_tokens_equal_one_gpu": agreement([p[:1] for p in plain], [p[:1] for p in spec]),
                   "lengths_ok": all(len(o) == args.tokens for o in spec)}
         print(json.dumps(report), flush=True)
     if world > 1:

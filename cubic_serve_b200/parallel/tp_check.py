@@ -118,7 +118,12 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
     if "fused" in res:
         (f0, f1), (fi0, fi1) = res["fused"]
         (n0, n1), (ni0, ni1) = res["nccl"]
-        report.update(_summary([_rel_rows(f0, n0), _rel_rows(f1, n1)], report["bound"]))
+        # the decode step consumes the token each execution sampled itself: its logits are compared for the rows where
+        # both sampled the same one (a near-tie of random weights that rounding resolves differently is a different
+        # input, not an error of the step)
+        same = torch.tensor([a == b for a, b in zip(fi0, ni0)], device=dev)
+        report.update(_summary([_rel_rows(f0, n0), _rel_rows(f1, n1)[same]], report["bound"]))
+        report["first_tokens_equal"] = round(float(same.float().mean()), 4)
         report["fused_eq_nccl_tokens"] = round(float(np.mean([a == b for a, b in zip(fi0 + fi1, ni0 + ni1)])), 4)
         # every rank must hold the same tokens (the vocabulary-sharded samplers draw the same candidate everywhere)
         t = torch.tensor(fi0 + fi1 + ni0 + ni1, device=dev)
@@ -137,8 +142,9 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
             (o0, o1), (oi0, oi1) = _step_logits(small, w1, dev, None, prompts, k_bits, v_bits)
             del w1
             errs = []
-            for mode, ((a0, a1), _) in part.items():
-                errs += [_rel_rows(a0, o0), _rel_rows(a1, o1)]
+            for mode, ((a0, a1), (ai0, _)) in part.items():
+                same1 = torch.tensor([a == b for a, b in zip(ai0, oi0)], device=dev)
+                errs += [_rel_rows(a0, o0), _rel_rows(a1, o1)[same1]]
             sm = _summary(errs, bound1)
             mode = "fused" if "fused" in part else "nccl"
             agree = float(np.mean([a == b for a, b in zip(part[mode][1][0] + part[mode][1][1], oi0 + oi1)]))

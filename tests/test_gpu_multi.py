@@ -58,4 +58,4 @@ def test_two_pipeline_stages_give_the_one_gpu_tokens():
 def test_mtp_rounds_under_tensor_parallelism_emit_the_one_gpu_greedy_tokens():
     rep = _torchrun(2, "cubic_serve_b200.parallel.spec_check", "--depth", "3")
     assert rep["rounds"] > 0 and rep["lengths_ok"]
-    assert rep["token_agreement_with_one_gpu_greedy"] >= 0.9, rep
+    assert rep["token_agreement_with_plain_greedy"] >= 0.9, rep
