@@ -121,9 +121,9 @@ class ModelSpec:
                     manifest: WeightManifest | None = None) -> "ModelSpec":
         lo, hi = layers or (0, cfg.num_layers)
         n_gdn = sum(cfg.layer_is_gdn(i) for i in range(lo, hi))
-        if cfg.num_kv_heads % tp:
-            raise ValueError(f"{cfg.num_kv_heads} key/value heads do not split over {tp} ranks")
-        cache = CacheSpec(hi - lo - n_gdn, cfg.num_kv_heads // tp, cfg.head_dim, k_bits, v_bits)
+        from ..models.config import kv_heads_of_rank
+        kv_local = kv_heads_of_rank(cfg.num_kv_heads, 0, tp)[1]       # a head shared by several ranks is cached on each
+        cache = CacheSpec(hi - lo - n_gdn, kv_local, cfg.head_dim, k_bits, v_bits)
         state = StateSpec(n_gdn, cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp) if n_gdn else None
         return ModelSpec(cfg.name, cfg.family, digest_of(dataclasses.asdict(cfg)), cache, state, manifest)
 

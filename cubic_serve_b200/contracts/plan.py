@@ -330,7 +330,8 @@ def decoder_step_operators(cfg, rows: int, tp_size: int = 1, topology_id: str = 
     """Operator signatures of one decode step of a decoder (the shapes the graphs of capacity ``rows`` were captured
     with): what ``cubic qualify`` and the readiness seal identify a captured step by."""
     H, D = cfg.hidden_size, cfg.head_dim
-    hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
+    from ..models.config import kv_heads_of_rank
+    hq, hkv = cfg.num_q_heads // tp_size, kv_heads_of_rank(cfg.num_kv_heads, 0, tp_size)[1]
     fmt = f"{cfg.quant.method}{cfg.quant.bits}"
     bf = "bf16"
 

@@ -326,7 +326,9 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
         except PartitionError as exc:
             raise CheckpointError(f"{cfg.name} does not split over {tp_size} ranks: {exc}") from exc
     D = cfg.head_dim
-    hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
+    from .config import kv_heads_of_rank
+    kv_first, hkv = kv_heads_of_rank(cfg.num_kv_heads, tp_rank, tp_size)     # a copy of a shared head when ranks outnumber them
+    hq = cfg.num_q_heads // tp_size
     inter = cfg.intermediate_size // tp_size
     bf = torch.bfloat16
 
@@ -388,8 +390,8 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
                 attn_gate = pack_logical(method, [rows(m["q"], h * 2 * D + D, (h + 1) * 2 * D, qn) for h in heads], q)
             else:
                 q_parts = [rows(m["q"], tp_rank * hq * D, (tp_rank + 1) * hq * D, cfg.q_size)]
-            qkv = pack_logical(method, q_parts + [rows(m["k"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size),
-                                                  rows(m["v"], tp_rank * hkv * D, (tp_rank + 1) * hkv * D, cfg.kv_size)], q)
+            qkv = pack_logical(method, q_parts + [rows(m["k"], kv_first * D, (kv_first + hkv) * D, cfg.kv_size),
+                                                  rows(m["v"], kv_first * D, (kv_first + hkv) * D, cfg.kv_size)], q)
             o = pack_logical(method, [(ck.payload(m["o"]), ck_shapes[m["o"]])], q,
                              (tp_rank * hq * D, (tp_rank + 1) * hq * D))
         moe = gu = down = None

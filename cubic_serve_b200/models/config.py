@@ -174,6 +174,21 @@ def moe_235b_config() -> ModelConfig:
                        quant=QuantSpec("fp8_block", 8, 128))
 
 
+def kv_heads_of_rank(num_kv_heads: int, tp_rank: int, tp_size: int) -> tuple[int, int]:
+    """Key/value heads ``[first, first + count)`` that tensor-parallel rank ``tp_rank`` holds.  With at least as many
+    heads as ranks every rank owns ``num_kv_heads / tp_size`` of them; with fewer, ``tp_size / num_kv_heads``
+    neighbouring ranks hold a copy of the same head (their query heads share it), as the reference replicates key/value
+    heads of grouped-query models across a wide tensor-parallel group."""
+    if num_kv_heads >= tp_size:
+        if num_kv_heads % tp_size:
+            raise ValueError(f"{num_kv_heads} key/value heads do not split over {tp_size} ranks")
+        n = num_kv_heads // tp_size
+        return tp_rank * n, n
+    if tp_size % num_kv_heads:
+        raise ValueError(f"{tp_size} ranks do not share {num_kv_heads} key/value heads evenly")
+    return tp_rank // (tp_size // num_kv_heads), 1
+
+
 NAMED_CONFIGS = {
     "toy": toy_config,
     "dense-8b": dense_8b_config,

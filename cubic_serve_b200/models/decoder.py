@@ -136,11 +136,22 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     one-GPU model (quantization groups lie along K in multiples of the shard widths, so quantizing a slice equals
     slicing the quantized matrix).  Outputs of different partitions can therefore be compared with each other.
     """
-    assert cfg.num_q_heads % tp_size == 0 and cfg.num_kv_heads % tp_size == 0
+    from .config import kv_heads_of_rank
+    assert cfg.num_q_heads % tp_size == 0
+    kv_first, kv_count = kv_heads_of_rank(cfg.num_kv_heads, tp_rank, tp_size)
     gen = torch.Generator(device=device)
     H, D = cfg.hidden_size, cfg.head_dim
-    hq, hkv = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size
+    hq, hkv = cfg.num_q_heads // tp_size, kv_count
     inter = cfg.intermediate_size // tp_size
+
+    def qkv_rows(full):
+        """This rank's query heads and its key/value heads (a copy of a shared head when ranks outnumber them) out of
+        the full [q | k | v] projection."""
+        kb = cfg.num_q_heads * D
+        vb = kb + cfg.num_kv_heads * D
+        return torch.cat([full[tp_rank * hq * D:(tp_rank + 1) * hq * D],
+                          full[kb + kv_first * D:kb + (kv_first + hkv) * D],
+                          full[vb + kv_first * D:vb + (kv_first + hkv) * D]])
 
     def rnd(n, k):
         return torch.randn(n, k, device=device, generator=gen, dtype=torch.float32) * std
@@ -198,7 +209,7 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
         else:
             lw = LayerWeights(
                 ln1=norm_w(), ln2=norm_w(),
-                qkv=shard_q(rnd((hq + 2 * hkv) * D * tp_size, H), lambda f: sections(f, [hq * D, hkv * D, hkv * D])),
+                qkv=shard_q(rnd((cfg.num_q_heads + 2 * cfg.num_kv_heads) * D, H), qkv_rows),
                 o=shard_q(rnd(H, hq * D * tp_size), cols_of(hq * D)),
             )
             if cfg.attn_output_gate:
@@ -273,7 +284,8 @@ class DecoderRunner:
         self.kv_rotation = kv_rotation
         self.reasoning = None        # K.ReasoningBudget once enable_reasoning_budget() was called
         self.hq = cfg.num_q_heads // self.tp_size
-        self.hkv = cfg.num_kv_heads // self.tp_size
+        from .config import kv_heads_of_rank
+        self.hkv = kv_heads_of_rank(cfg.num_kv_heads, 0, self.tp_size)[1]     # a shared head is held whole by its ranks
         self.D = cfg.head_dim
         self.max_tokens = max_tokens
         H = cfg.hidden_size

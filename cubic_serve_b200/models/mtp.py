@@ -38,7 +38,9 @@ def random_mtp_weights(cfg: ModelConfig, device, seed: int = 1, std: float = 0.0
     2H -> H input projection and the norms are replicated."""
     gen = torch.Generator(device=device).manual_seed(seed * 7919)
     H, D = cfg.hidden_size, cfg.head_dim
-    hq, hkv, inter = cfg.num_q_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.intermediate_size // tp_size
+    from .config import kv_heads_of_rank
+    kv_first, hkv = kv_heads_of_rank(cfg.num_kv_heads, tp_rank, tp_size)
+    hq, inter = cfg.num_q_heads // tp_size, cfg.intermediate_size // tp_size
     r = tp_rank
 
     def rnd(n, k):
@@ -59,7 +61,10 @@ def random_mtp_weights(cfg: ModelConfig, device, seed: int = 1, std: float = 0.0
     o = rnd(H, cfg.q_size)
     gate_up = rnd(2 * cfg.intermediate_size, H)
     down = rnd(H, cfg.intermediate_size)
-    layer = LayerWeights(ln1=ones(H), ln2=ones(H), qkv=quantize_linear(sections(qkv, [hq * D, hkv * D, hkv * D]), cfg),
+    kb, vb = cfg.num_q_heads * D, (cfg.num_q_heads + cfg.num_kv_heads) * D
+    qkv_local = torch.cat([qkv[r * hq * D:(r + 1) * hq * D], qkv[kb + kv_first * D:kb + (kv_first + hkv) * D],
+                           qkv[vb + kv_first * D:vb + (kv_first + hkv) * D]]).contiguous()
+    layer = LayerWeights(ln1=ones(H), ln2=ones(H), qkv=quantize_linear(qkv_local, cfg),
                          o=quantize_linear(cols(o, hq * D), cfg),
                          gate_up=quantize_linear(sections(gate_up, [inter, inter]), cfg),
                          down=quantize_linear(cols(down, inter), cfg))

@@ -137,7 +137,16 @@ def plan_partition(cfg: ModelConfig, tp: int = 1, pp: int = 1, ep: int = 1) -> P
             AxisSpan.whole(cfg.num_experts) if cfg.is_moe else None)
         part = RankPartition(rank, place.stage, t, (lo, hi), experts)
         qh = AxisSpan.shard(cfg.num_q_heads, t, tp, what="query heads")
-        kvh = AxisSpan.shard(cfg.num_kv_heads, t, tp, what="key/value heads")
+        if cfg.num_kv_heads >= tp:
+            kvh = AxisSpan.shard(cfg.num_kv_heads, t, tp, what="key/value heads")
+        else:
+            # fewer key/value heads than ranks: neighbouring ranks hold a copy of the same head
+            from .config import kv_heads_of_rank
+            try:
+                first, count = kv_heads_of_rank(cfg.num_kv_heads, t, tp)
+            except ValueError as exc:
+                raise PartitionError(str(exc)) from exc
+            kvh = AxisSpan(first, first + count, cfg.num_kv_heads)
         whole_h = AxisSpan.whole(H)
         for i in range(lo, hi):
             p = f"model.layers.{i}"

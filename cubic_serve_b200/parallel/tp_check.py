@@ -164,6 +164,8 @@ def main(argv=None) -> None:
     ap.add_argument("--model", default="dense-8b")
     ap.add_argument("--layers", type=int, default=4, help="layers of the checked model (0 = the named config's own)")
     ap.add_argument("--experts", type=int, default=0, help="MoE: number of experts (0 = the config's own)")
+    ap.add_argument("--kv-heads", type=int, default=0,
+                    help="override the key/value head count (fewer heads than ranks: ranks share copies of a head)")
     ap.add_argument("--requests", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=48)
     ap.add_argument("--kv", default="8,8")
@@ -181,6 +183,8 @@ def main(argv=None) -> None:
         cfg = replace(cfg, num_layers=args.layers)
     if args.experts and cfg.is_moe:
         cfg = replace(cfg, num_experts=args.experts)
+    if args.kv_heads:
+        cfg = replace(cfg, num_kv_heads=args.kv_heads)
     kb, vb = (int(b) for b in args.kv.split(","))
     report = run_check(cfg, dev, dist.group.WORLD, requests=args.requests, prompt_len=args.prompt_len, k_bits=kb, v_bits=vb,
                        tp1_layers=cfg.num_layers)

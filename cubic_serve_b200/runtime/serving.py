@@ -59,7 +59,8 @@ def plan_kv_pages(free_bytes: int, reserve_bytes: int, cfg, tp: int, k_bits: int
     from ..contracts.model import CacheSpec, ModelSpec, StateSpec
     n_layers = layers or cfg.num_layers
     n_gdn = sum(cfg.layer_is_gdn(i) for i in range(cfg.num_layers)) if layers is None else 0
-    cache = CacheSpec(n_layers - n_gdn, cfg.num_kv_heads // tp, cfg.head_dim, k_bits, v_bits)
+    from ..models.config import kv_heads_of_rank
+    cache = CacheSpec(n_layers - n_gdn, kv_heads_of_rank(cfg.num_kv_heads, 0, tp)[1], cfg.head_dim, k_bits, v_bits)
     # Gated DeltaNet layers keep, per request, one 128 x 128 fp32 state per value head and three conv inputs
     state = StateSpec(n_gdn, cfg.gdn_k_heads // tp, cfg.gdn_v_heads // tp) if n_gdn else None
     return ModelSpec(cfg.name, cfg.family, "", cache, state).kv_pages(free_bytes, reserve_bytes, max_model_len, max_running,

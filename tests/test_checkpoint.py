@@ -252,6 +252,16 @@ def test_random_weights_of_any_partition_are_slices_of_one_model():
     n1 = random_decoder_weights(nv, "cpu", seed=3)
     n2 = [random_decoder_weights(nv, "cpu", seed=3, tp_rank=r, tp_size=2) for r in range(2)]
     assert torch.equal(torch.cat([d(t.layers[0].down)[:nv.hidden_size] for t in n2], 1), d(n1.layers[0].down)[:nv.hidden_size])
+    # fewer key/value heads than ranks: neighbouring ranks hold a copy of the same head, every rank its own query heads
+    few = replace(BASE, num_kv_heads=2, quant=QuantSpec("cubic", 4, 128))
+    k1 = random_decoder_weights(few, "cpu", seed=3)
+    k4 = [random_decoder_weights(few, "cpu", seed=3, tp_rank=r, tp_size=4) for r in range(4)]
+    fq, hq4 = d(k1.layers[0].qkv), few.num_q_heads // 4 * D
+    kb, vb = few.num_q_heads * D, (few.num_q_heads + 2) * D
+    for r in range(4):
+        want = torch.cat([fq[r * hq4:(r + 1) * hq4], fq[kb + (r // 2) * D:kb + (r // 2 + 1) * D],
+                          fq[vb + (r // 2) * D:vb + (r // 2 + 1) * D]])
+        assert torch.equal(d(k4[r].layers[0].qkv)[:want.shape[0]], want)
     # FP8 has one scale per output row: column shards are quantized with the whole row's largest magnitude
     f8 = replace(BASE, quant=QuantSpec("fp8", 8, 0))
     f1 = random_decoder_weights(f8, "cpu", seed=3)

@@ -109,12 +109,16 @@ def test_axis_spans_and_partition_plans():
     assert (q.rows.start, q.rows.stop, q.cols.full) == (1024, 2048, True) and (o.cols.start, o.cols.stop) == (1024, 2048)
     total = sum(r.weight_bytes for r in plan.ranks)
     assert abs(total - one.weight_bytes) / one.weight_bytes < 0.25         # a split moves bytes, it does not create many
-    with pytest.raises(PartitionError, match="key/value heads"):
-        plan_partition(dense, tp=16)
+    # more ranks than key/value heads: neighbouring ranks hold a copy of the same head (8 heads over 16 ranks)
+    shared = plan_partition(dense, tp=16)
+    k = [next(x for x in r.shares if x.module == "model.layers.0.self_attn.k_proj").rows for r in shared.ranks[:4]]
+    assert [(s.start, s.stop) for s in k] == [(0, 128), (0, 128), (128, 256), (128, 256)]
     import dataclasses
-    moe = NAMED_CONFIGS["moe-30b-a3b"]()
     with pytest.raises(PartitionError, match="key/value heads"):
-        plan_partition(moe, tp=8)                              # 4 key/value heads
+        plan_partition(dataclasses.replace(dense, num_kv_heads=3, num_q_heads=24), tp=2)
+    moe = NAMED_CONFIGS["moe-30b-a3b"]()
+    kv8 = plan_partition(moe, tp=8, ep=8)                      # 4 key/value heads on 8 ranks: two ranks per head
+    assert next(x for x in kv8.ranks[5].shares if x.module.endswith("layers.0.self_attn.k_proj")).rows.start == 2 * 128
     wide = dataclasses.replace(moe, num_kv_heads=8)
     with pytest.raises(PartitionError, match="expert intermediate size"):
         plan_partition(wide, tp=8)                             # 768 / 8 = 96 columns: not a multiple of the K block
