@@ -31,8 +31,8 @@ def _ranks():
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("model,extra", [("dense-8b", []), ("moe-30b-a3b", ["--experts", "32", "--kv", "4,8"]),
-                                         # one key/value head for all ranks: every rank caches a copy of it
-                                         ("dense-8b", ["--kv-heads", "1"])])
+                                         # two key/value heads: on four or more ranks neighbours cache copies of a head
+                                         ("moe-30b-a3b", ["--experts", "32", "--kv", "4,8", "--kv-heads", "2"])])
 def test_fused_and_nccl_tensor_parallel_logits_match_one_gpu(model, extra):
     rep = _torchrun(_ranks(), "cubic_serve_b200.parallel.tp_check", "--model", model, "--layers", "4", *extra)
     assert rep["ranks_agree"]
