@@ -30,7 +30,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
     speculative_grammar = True       # ... and constrained requests: every review row is sampled under the grammar's mask
 
     def __init__(self, runner, mtp: MtpRunner, depth: int, force_acceptance: float | None = None, seed: int = 0,
-                 **kw) -> None:
+                 round_graphs: bool = True, **kw) -> None:
         # models with Gated DeltaNet layers: the review pass leaves the recurrent state untouched and the accepted
         # prefix is folded into it afterwards (DecoderRunner.begin_gdn_review / fold_gdn)
         super().__init__(runner, rows_per_request=depth + 1, use_graphs=False, **kw)
@@ -60,7 +60,15 @@ class SpeculativeGpuExecutor(GpuExecutor):
         self.p_val = torch.zeros(rows * (depth + 1), C, dtype=torch.float32, device=dev)
         self.p_id = torch.zeros(rows * (depth + 1), C, dtype=torch.int32, device=dev)
         self.cand_tmp = (torch.zeros(rows, C, dtype=torch.float32, device=dev), torch.zeros(rows, C, dtype=torch.int32, device=dev))
-        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0}
+        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0, "graphed_rounds": 0}
+        # captured rounds (greedy requests of models without recurrent layers on one GPU): one graph per row capacity
+        # for a proposal pass of the head, one per (capacity, depth) for review + verification; see _round_graphed
+        self.round_graphs = bool(round_graphs) and runner.tp is None and not runner.gdn_state and runner.pp is None
+        self._round_graph: dict = {}
+        self.g_prev = torch.zeros(rows, H, dtype=torch.bfloat16, device=dev)       # hidden that precedes a proposal row
+        self.g_tok = torch.zeros(rows, dtype=torch.int32, device=dev)              # proposal input token / sampled draft
+        self.g_hid_sel = torch.zeros(rows, H, dtype=torch.bfloat16, device=dev)    # target hidden of the last accepted row
+        self._rl = torch.empty(rows * (depth + 1), runner.w.lm_head.n, dtype=torch.bfloat16, device=dev)
 
     # ------------------------------------------------------------- plain steps
     def execute(self, segs):
@@ -127,6 +135,8 @@ class SpeculativeGpuExecutor(GpuExecutor):
             return [[int(t)] for t in ids]
         per_req = [Kd] * R if depths is None else [min(int(d), Kd) for d in depths]
         r, dev = self.runner, self.device
+        if (self.round_graphs and not any(s.temperature > 0 or s.mask_fn is not None for s in segs)):
+            return self._round_graphed(segs, Kd, per_req)
         sl = torch.tensor([s.request_slot for s in segs], device=dev)
         launches = 0
         # compact [R, Kd] / [R, Kd + 1] views: the verification kernel's row strides follow the round's depth
@@ -204,6 +214,164 @@ class SpeculativeGpuExecutor(GpuExecutor):
         self.last_round = {"depth": Kd, "accepted": [int(a) for a in acc], "proposed": per_req, "proposal_ms": prop_ms,
                            "target_ms": tgt_ms}
         self.kernel_launches_last = launches + 2
+        self.d2h_bytes_last = R * (Kd + 2) * 4
+        return out
+
+    # ---------------------------------------------------------- captured rounds
+    @staticmethod
+    def _capacity(n: int) -> int:
+        c = 1
+        while c < n:
+            c *= 2
+        return c
+
+    def _staged(self, segs, pad_rows_to=None):
+        """``_fill`` + upload, after the previous upload has left the pinned staging buffer (with captured passes the
+        host runs far ahead of the device)."""
+        if self._upload_pending:
+            self._uploaded.synchronize()
+        b, _ = self._fill(segs, pad_rows_to=pad_rows_to)
+        return b
+
+    def _upload(self) -> int:
+        n = self.stage.upload()
+        self._uploaded.record(self.stream)
+        self._upload_pending = True
+        return n
+
+    def _proposal_body(self, b, cap: int) -> None:
+        self.stage.d["token_ids"][:cap].copy_(self.g_tok[:cap])
+        hid = self.mtp.forward(b, self.g_prev)
+        lg = self.mtp.logits(hid, cap, self.mtp_logits)
+        K.sample(lg, self.g_tok[:cap], vocab=lg.shape[1])
+        self.g_prev[:cap].copy_(hid[:cap])
+
+    def _review_body(self, b, cap: int, Kd: int, draft_ids: torch.Tensor, target_ids: torch.Tensor) -> None:
+        r, T = self.runner, cap * (Kd + 1)
+        self.stage.d["token_ids"][:T].view(cap, Kd + 1)[:, 1:].copy_(draft_ids)
+        hidden = r.forward_hidden(b)
+        logits = r.forward_logits(b, hidden, self._rl)
+        K.sample(logits, target_ids.view(-1), vocab=logits.shape[1])
+        forced = None
+        if self.force_acceptance is not None:
+            # forced acceptance: the draft is *declared* equal to the target up to the depth drawn on the host
+            forced = self.forced
+            keep = torch.arange(Kd, device=self.device)[None, :] < self.forced[:cap, None]
+            draft_ids.copy_(torch.where(keep, target_ids[:, :Kd], draft_ids))
+        K.verify_greedy(target_ids, draft_ids, self.depth_t[:cap], Kd, self.accepted, self.bonus, forced)
+        rows = torch.arange(cap, device=self.device) * (Kd + 1) + self.accepted[:cap].long()
+        self.g_hid_sel[:cap].copy_(hidden.index_select(0, rows))
+
+    def _captured(self, key, body, restore) -> "torch.cuda.CUDAGraph":
+        """The graph for ``key``, captured on first use from the staged inputs of the current round: two eager runs, the
+        capture, and ``restore()`` before each so that every run (and the first replay) starts from the same inputs."""
+        g = self._round_graph.get(key)
+        if g is None:
+            for _ in range(2):
+                body()
+                restore()
+            self.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self.stream):
+                body()
+            restore()
+            self._round_graph[key] = g
+        return g
+
+    def _round_graphed(self, segs: list[Segment], Kd: int, per_req: list[int]):
+        """A round of greedy requests on captured graphs: per proposal pass one replay of the head's graph for the row
+        capacity, then one replay of the review + verification graph for (capacity, depth).  The host stages the
+        inputs of each pass (positions, cache slots, page tables; tokens and hidden states chain on the device) and
+        reads back accepted counts and tokens once.  Reference: one captured graph per (review capacity, depth),
+        ``executor/draft_graph.py:574`` there; here the proposal passes are graphs of their own so that one capture
+        serves every depth."""
+        R, dev, r = len(segs), self.device, self.runner
+        cap = self._capacity(R)
+        draft_ids = self.draft_ids.view(-1)[:cap * Kd].view(cap, Kd)
+        target_ids = self.target_ids.view(-1)[:cap * (Kd + 1)].view(cap, Kd + 1)
+        depth_host = torch.zeros(cap, dtype=torch.int32)
+        depth_host[:R] = torch.tensor(per_req, dtype=torch.int32)
+        sl = torch.tensor([s.request_slot for s in segs], device=dev)
+        if not hasattr(self, "_ev_mid"):
+            self._ev_mid = torch.cuda.Event(enable_timing=True)
+        launches = 0
+        with torch.cuda.stream(self.stream):
+            ev0, ev1 = self._ev[0]
+            if self.timing:
+                ev0.record(self.stream)
+            self.depth_t[:cap].copy_(depth_host, non_blocking=True)
+            self.g_prev[:R].copy_(self.last_hidden.index_select(0, sl))
+            for d in range(Kd):
+                step = [Segment(s.request_slot, [s.token_ids[0] if d == 0 else 0], s.start + d, s.pages, True, uid=s.uid)
+                        for s in segs]
+                b = self._staged(step, pad_rows_to=cap)
+                self.h2d_bytes_last = self._upload()
+                if d == 0:
+                    self.g_tok[:cap].copy_(self.stage.d["token_ids"][:cap])
+                restore = None
+                if ("proposal", cap) not in self._round_graph:
+                    keep_tok, keep_prev = self.g_tok[:cap].clone(), self.g_prev[:cap].clone()
+
+                    def restore():
+                        self.g_tok[:cap].copy_(keep_tok)
+                        self.g_prev[:cap].copy_(keep_prev)
+                self._captured(("proposal", cap), lambda: self._proposal_body(b, cap), restore).replay()
+                draft_ids[:, d].copy_(self.g_tok[:cap])
+                launches += 4
+            if self.timing:
+                self._ev_mid.record(self.stream)
+            # review rows: the requests' [root, d1 .. dK], then whole dummy requests up to the capacity; their rows
+            # write no cache slot and attend to nothing
+            pad_slot = self.max_rows                       # a page-table row no request uses
+            review = [Segment(s.request_slot, [s.token_ids[0]] + [0] * Kd, s.start, s.pages, True, uid=s.uid) for s in segs]
+            review += [Segment(pad_slot, [0] * (Kd + 1), 0, [0], True, uid=-1) for _ in range(cap - R)]
+            b = self._staged(review)
+            T, Tr = cap * (Kd + 1), R * (Kd + 1)
+            h = self.stage.h
+            nb = -(-(Kd + 1) // self.builder.qb)
+            h["slots"][Tr:T] = -1
+            h["rb_qcount"][R * nb:cap * nb] = 0
+            h["logit_rows"][:T] = np.arange(T)
+            h["temperature"][:T] = 0
+            b.num_logit_rows = T
+            self.h2d_bytes_last += self._upload()
+            if self.force_acceptance is not None:
+                draws = self._rng.random((R, Kd)) < self.force_acceptance
+                first_fail = np.zeros(cap, dtype=np.int32)
+                first_fail[:R] = np.where(draws.all(1), Kd, draws.argmin(1))
+                self.forced[:cap].copy_(torch.from_numpy(first_fail), non_blocking=False)
+            restore_review = None
+            if ("review", cap, Kd) not in self._round_graph:
+                keep_drafts = draft_ids.clone()
+
+                def restore_review():
+                    draft_ids.copy_(keep_drafts)
+            self._captured(("review", cap, Kd), lambda: self._review_body(b, cap, Kd, draft_ids, target_ids),
+                           restore_review).replay()
+            self.last_hidden.index_copy_(0, sl, self.g_hid_sel[:R])
+            launches += 6
+            if self.timing:
+                ev1.record(self.stream)
+            acc = self.accepted[:R].cpu()
+            tg = target_ids[:R].cpu()
+            self.stream.synchronize()
+        prop_ms = tgt_ms = 0.0
+        if self.timing:
+            self.device_ms.append(ev0.elapsed_time(ev1))
+            prop_ms, tgt_ms = ev0.elapsed_time(self._ev_mid), self._ev_mid.elapsed_time(ev1)
+        out = []
+        for i in range(R):
+            a = int(acc[i])
+            out.append([int(t) for t in tg[i, :a + 1]])
+            self.stats["accepted"] += a
+            self.stats["emitted"] += a + 1
+        self.stats["rounds"] += 1
+        self.stats["graphed_rounds"] += 1
+        self.stats["proposed"] += sum(per_req)
+        self.last_round = {"depth": Kd, "accepted": [int(a) for a in acc], "proposed": per_req, "proposal_ms": prop_ms,
+                           "target_ms": tgt_ms}
+        # kernels inside the replayed graphs count as launched kernels of this step
+        self.kernel_launches_last = launches + Kd * (self.mtp.launches + 3) + r.launches_per_step + 6
         self.d2h_bytes_last = R * (Kd + 2) * 4
         return out
 
@@ -304,7 +472,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
         r.tp.sample_sharded_nccl(logits, rows, out_ids, self._greedy_d, r.w.vocab_start, mask)
 
     def _review_logits(self, rows: int) -> torch.Tensor:
-        if not hasattr(self, "_rl") or self._rl.shape[0] < rows:
+        if getattr(self, "_rl", None) is None or self._rl.shape[0] < rows:
             self._rl = torch.empty(rows, self.runner.w.lm_head.n, dtype=torch.bfloat16, device=self.device)
         return self._rl
 
@@ -335,7 +503,9 @@ class NgramSpeculativeGpuExecutor(SpeculativeGpuExecutor):
         self.depth_t = torch.zeros(rows, dtype=torch.int32, device=dev)
         self.forced = torch.zeros(rows, dtype=torch.int32, device=dev)
         self._draft_host = torch.zeros(rows, depth, dtype=torch.int32, pin_memory=torch.cuda.is_available())
-        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0}
+        self.stats = {"rounds": 0, "accepted": 0, "proposed": 0, "emitted": 0, "graphed_rounds": 0}
+        self.round_graphs = False          # host-drafted rounds run eagerly
+        self._round_graph = {}
 
     def execute(self, segs):
         return GpuExecutor.execute(self, segs)

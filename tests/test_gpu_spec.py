@@ -273,3 +273,34 @@ def test_constrained_requests_take_speculative_rounds_under_their_grammar():
     for toks in spec:
         assert toks[-1] == eos and "".join(chr(t - 100) for t in toks[:-1]) in options
     assert spec == plain
+
+
+def test_captured_rounds_equal_eager_rounds():
+    """Greedy rounds replay captured graphs (a proposal graph per capacity, a review + verification graph per
+    capacity and depth); they must emit exactly what the eager rounds emit, also when the number of requests changes
+    between rounds (other capacity, padded rows) and with forced acceptance (accepted prefixes of every length)."""
+    from cubic_serve_b200.executor.spec_executor import SpeculativeGpuExecutor
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, 2048, n).tolist() for n in (17, 40, 33, 64, 21)]
+    lens = [12, 5, 9, 12, 7]                           # requests leave at different times: capacities 8 -> 4 -> 2 -> 1
+
+    def run(graphs, force):
+        eng, ex, runner = _build(3, force=force)
+        ex.round_graphs = graphs
+        ex._rng = np.random.default_rng(0)
+        rids = [eng.add_request(p, SamplingParams(max_tokens=n, ignore_eos=True)) for p, n in zip(prompts, lens)]
+        reqs = [eng.requests[r] for r in rids]
+        while eng.has_unfinished:
+            eng.step()
+        runner.ws.check_status()
+        return [list(r.output) for r in reqs], ex.stats
+
+    for force in (None, 0.6):
+        eager, st_e = run(False, force)
+        graphed, st_g = run(True, force)
+        assert st_e["graphed_rounds"] == 0 and st_g["graphed_rounds"] == st_g["rounds"] > 0
+        assert [len(o) for o in graphed] == lens
+        assert graphed == eager, (force, graphed[0], eager[0])
+        if force is not None:
+            assert st_g["accepted"] == st_e["accepted"] > 0
