@@ -152,13 +152,6 @@ def main() -> None:
     k_bits, v_bits = (int(b) for b in (args.kv or ("4,8" if cfg.is_moe else "8,8")).split(","))
     tp = pp = None
     tp_size, tp_rank, layer_range = world // args.pp, rank % (world // args.pp), None
-    if args.pp > 1 and world // args.pp > 1:
-        # two pipeline stages of tensor-parallel width > 1 stopped making progress in this benchmark on 4 and on 8 GPUs
-        # (ended by the run's time limit, the GPUs answered afterwards); stages of width 1 pass
-        # (`python -m cubic_serve_b200.parallel.pp_check --pp 2`).  Until the cause is found the combination is refused
-        # here instead of occupying GPUs.
-        raise SystemExit("bench.py: --pp 2 with more than one GPU per stage is not available (see parallel/pp_check.py "
-                         "for the pipeline check on two GPUs)")
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         from cubic_serve_b200.parallel.tp import TensorParallel

@@ -60,6 +60,12 @@ class PipelineStage:
     def from_topology(topology, rank: int, group=None, lanes: int = 2) -> "PipelineStage":
         p = topology.placement(rank)
         tp = topology.tp
+        if tp > 1:
+            # Stages of tensor-parallel width > 1 run ONE lane per step.  With two lanes such stages stopped making
+            # progress on 4 and on 8 GPUs at 256 rows per step (every rank's GPU work enqueued, none finishing: the
+            # lanes interleave point-to-point transfers on the world communicator with all-reduces on the stage's
+            # own communicator); one lane per step ran to completion.  Stages of width 1 keep the two-lane wavefront.
+            lanes = 1
         prev_rank = rank - tp if p.stage > 0 else None
         next_rank = rank + tp if p.stage + 1 < topology.pp else None
         return PipelineStage(p.stage, topology.pp, prev_rank, next_rank, topology.sampler_rank, group, lanes)
