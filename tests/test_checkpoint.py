@@ -276,3 +276,61 @@ def test_random_weights_of_any_partition_are_slices_of_one_model():
     assert torch.equal(torch.cat([t.layers[1].moe.gate_up.codes for t in m2]), m1.layers[1].moe.gate_up.codes)
     assert torch.equal(m2[0].layers[0].moe.router.codes, m1.layers[0].moe.router.codes)
     assert not torch.equal(m1.layers[0].moe.router.codes, m1.layers[1].moe.router.codes)
+
+
+@pytest.mark.parametrize("method,fmt", [("fp8", "FMT_FP8"), ("fp8_block", "FMT_FP8_BLOCK")])
+def test_fp8_checkpoints_stay_e4m3_at_load(tmp_path, method, fmt):
+    """FP8 checkpoints (one scale per row, or per 128 x 128 block) are not expanded: the loader hands the e4m3 bytes and
+    their scales to the fp8 GEMM, whole and as tensor-parallel shards, and they decode to the checkpoint's values."""
+    from safetensors.torch import load_file
+    from cubic_serve_b200.quantization import formats
+    cfg = replace(BASE, hidden_size=256, intermediate_size=512, num_q_heads=4, num_kv_heads=2, head_dim=128,
+                  quant=QuantSpec(method, 8, 128 if method == "fp8_block" else 0))
+    path = C.write_random_checkpoint(tmp_path / method, cfg, seed=5)
+    t = load_file(str(path / "model.safetensors"))
+    ck = C.admit_checkpoint(path)
+    assert ck.cfg.quant.method == method
+    want_fmt = getattr(wq_pack, fmt)
+
+    def dense(module):
+        keys = ("weight", "weight_scale", "weight_scale_inv")
+        return formats.fp8_dense({k: t[f"{module}.{k}"] for k in keys if f"{module}.{k}" in t})
+
+    w1 = C.load_decoder_weights(ck, "cpu")
+    lw = w1.layers[0]
+    assert lw.qkv.fmt == lw.o.fmt == lw.gate_up.fmt == lw.down.fmt == want_fmt
+    assert lw.qkv.codes.dtype == torch.uint8 and lw.qkv.meta.dtype == torch.float32
+    q, k, v = (dense(f"model.layers.0.self_attn.{p}_proj") for p in "qkv")
+    assert torch.equal(wq_pack.unpack_to_dense(lw.qkv), torch.cat([q, k, v]))
+    assert torch.equal(wq_pack.unpack_to_dense(lw.down), dense("model.layers.0.mlp.down_proj"))
+    # two tensor-parallel ranks: row shards of q / k / v / gate / up, column shards of o / down
+    two = [C.load_decoder_weights(ck, "cpu", tp_rank=r, tp_size=2) for r in range(2)]
+    assert all(x.layers[0].down.fmt == want_fmt and x.layers[0].qkv.fmt == want_fmt for x in two)
+    full_down = dense("model.layers.0.mlp.down_proj")
+    assert torch.equal(torch.cat([wq_pack.unpack_to_dense(x.layers[0].down) for x in two], 1), full_down)
+    full_o = dense("model.layers.0.self_attn.o_proj")
+    assert torch.equal(torch.cat([wq_pack.unpack_to_dense(x.layers[0].o) for x in two], 1), full_o)
+    hq, hkv = 2 * 128, 128
+    for r, x in enumerate(two):
+        want = torch.cat([q[r * hq:(r + 1) * hq], k[r * hkv:(r + 1) * hkv], v[r * hkv:(r + 1) * hkv]])
+        assert torch.equal(wq_pack.unpack_to_dense(x.layers[0].qkv), want)
+
+
+def test_fp8_block_experts_load_as_stacked_e4m3(tmp_path):
+    """A mixture-of-experts checkpoint with 128 x 128 block-scaled FP8 experts: every expert keeps its e4m3 bytes and
+    block scales in the stack the grouped GEMM reads."""
+    from safetensors.torch import load_file
+    from cubic_serve_b200.quantization import formats
+    cfg = replace(BASE, family="gqa_moe", hidden_size=256, num_q_heads=4, num_kv_heads=2, head_dim=128, num_experts=4,
+                  experts_per_token=2, moe_intermediate_size=128, intermediate_size=0, quant=QuantSpec("fp8_block", 8, 128))
+    path = C.write_random_checkpoint(tmp_path / "moe_fp8", cfg, seed=2)
+    t = load_file(str(path / "model.safetensors"))
+    w = C.load_decoder_weights(C.admit_checkpoint(path), "cpu")
+    layer = w.layers[0].moe
+    assert layer.gate_up.fmt == layer.down.fmt == wq_pack.FMT_FP8_BLOCK
+    assert tuple(layer.gate_up.codes.shape) == (4, 256, 256) and tuple(layer.gate_up.meta.shape) == (4, 2, 2)
+    for e in (0, 3):
+        one = wq_pack.PackedWeight(layer.down.fmt, layer.down.n, layer.down.k, 128, layer.down.codes[e], layer.down.meta[e])
+        mod = f"model.layers.0.mlp.experts.{e}.down_proj"
+        want = formats.fp8_dense({k: t[f"{mod}.{k}"] for k in ("weight", "weight_scale_inv") if f"{mod}.{k}" in t})
+        assert torch.equal(wq_pack.unpack_to_dense(one), want)
