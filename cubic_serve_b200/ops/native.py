@@ -255,6 +255,10 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_wq_gemm_grouped_act.restype = i
     l.cb_verify_sampled.argtypes = [vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, vp, vp, vp, vp, i, vp]
     l.cb_verify_sampled.restype = i
+    l.cb_canary_fill.argtypes = [vp, ll, ctypes.c_uint, vp]
+    l.cb_canary_fill.restype = i
+    l.cb_canary_check.argtypes = [vp, ll, ctypes.c_uint, i, vp, vp]
+    l.cb_canary_check.restype = i
     # fp8 (e4m3 x e4m3) tensor path: activation quantizers and the GEMM entries
     l.cb_fp8_quantize_rows.argtypes = [vp, i, vp, i, vp, i, i, vp]
     l.cb_fp8_quantize_rows.restype = i
