@@ -70,6 +70,21 @@ def shard_dense_weights(w: DenseWeights, cfg: ModelConfig, part: RankPartition) 
     return DenseWeights(w.embed, layers, w.final_norm, w.lm_head)
 
 
+def moe_expert_parallel_reference(x: torch.Tensor, router: torch.Tensor, gate_up: list[torch.Tensor],
+                                  down: list[torch.Tensor], top_k: int, group, normalize: bool = True) -> torch.Tensor:
+    """Eager expert-parallel mixture-of-experts block: every rank of ``group`` routes ALL tokens with the replicated
+    router, computes only the experts it owns (contiguous expert ids in rank order; ``gate_up`` / ``down`` hold this
+    rank's experts) and the partial outputs are summed in rank order.  Equals the single-process ``moe_reference`` over
+    all experts up to fp32 summation order.  Reference counterpart: ``models/qwen3_5_moe/distributed.py`` there."""
+    from .moe import moe_reference
+    rank, size = dist.get_rank(group), dist.get_world_size(group)
+    total = router.shape[0]
+    if total % size or len(gate_up) != total // size or len(down) != len(gate_up):
+        raise ValueError("every rank owns num_experts / group size experts")
+    partial = moe_reference(x, router, gate_up, down, top_k, normalize, expert_lo=rank * (total // size))
+    return tp_all_reduce(partial, group)
+
+
 class DistributedEagerDecoder:
     """One rank of the reference.  ``tp_group``: the ranks of this stage; ``prev`` / ``next``: global ranks of the
     same tensor rank in the neighbouring stages (None at the ends)."""

@@ -77,3 +77,46 @@ def test_shards_follow_the_ownership_plan():
     assert len(s.layers) == 2
     assert torch.equal(s.layers[0].wq, w.layers[2].wq[32:64]) and torch.equal(s.layers[0].wo, w.layers[2].wo[:, 32:64])
     assert torch.equal(s.layers[1].w_down, w.layers[3].w_down[:, 64:128]) and s.layers[1].wk.shape == (16, 64)
+
+
+def _moe_rank(rank, world, port, q):
+    import torch.distributed as dist
+    from cubic_serve_b200.models.distributed_reference import moe_expert_parallel_reference
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(11)
+    E, H, I, T = 8, 32, 48, 9
+    router = (torch.randn(E, H, generator=g) * 0.3).to(torch.bfloat16)
+    gate_up = [(torch.randn(2 * I, H, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    down = [(torch.randn(H, I, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    per = E // world
+    y = moe_expert_parallel_reference(x, router, gate_up[rank * per:(rank + 1) * per], down[rank * per:(rank + 1) * per],
+                                      2, dist.group.WORLD)
+    q.put((rank, y))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_reference_equals_the_single_process_block():
+    from cubic_serve_b200.models.moe import moe_reference
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_moe_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    g = torch.Generator().manual_seed(11)
+    E, H, I, T = 8, 32, 48, 9
+    router = (torch.randn(E, H, generator=g) * 0.3).to(torch.bfloat16)
+    gate_up = [(torch.randn(2 * I, H, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    down = [(torch.randn(H, I, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    want = moe_reference(x, router, gate_up, down, 2)
+    assert torch.equal(got[0], got[1])                      # rank-ordered sum: the same bits on every rank
+    assert float((got[0] - want).norm() / want.norm()) < 1e-5
