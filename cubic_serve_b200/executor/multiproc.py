@@ -120,10 +120,13 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
             tp = TensorParallel(tp_group, dev, mode="nccl" if spec.pp > 1 else spec.tp_comm, hidden=cfg.hidden_size,
                                 max_tokens=spec.token_budget, rows_max=max(512, spec.max_rows))
         pages = spec.num_pages
+        # models with recurrent layers keep as many state snapshot rows as request rows, for prefix caching
+        snapshots = spec.max_rows if cfg.is_hybrid else 0
         if pages is None:
             free, _ = torch.cuda.mem_get_info(dev)
             pages = plan_kv_pages(free, int(spec.gpu_reserve_gib * 2 ** 30) + (2 << 30), cfg, spec.tp, spec.k_bits,
-                                  spec.v_bits, spec.max_model_len, spec.max_rows, layers=layers[1] - layers[0])
+                                  spec.v_bits, spec.max_model_len, spec.max_rows, layers=layers[1] - layers[0],
+                                  state_snapshots=snapshots)
         if spec.world > 1:
             # every rank runs the same code on the same model; the KV pool is the smallest any rank can hold
             import dataclasses
@@ -136,7 +139,7 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
             pages = int(agreed["pages"])
         runner = DecoderRunner(cfg, weights, num_pages=pages, max_tokens=spec.token_budget, k_bits=spec.k_bits,
                                v_bits=spec.v_bits, tp=tp, pp=pp, max_requests=spec.max_rows,
-                               kv_rotation=spec.kv_rotation)
+                               state_checkpoints=snapshots, kv_rotation=spec.kv_rotation)
         from ..runtime.serving import _tokenizer_for, reasoning_end_tokens
         think = reasoning_end_tokens(_tokenizer_for(spec.model, cfg.vocab_size))
         if think is not None:
@@ -145,7 +148,8 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
                          max_model_len=spec.max_model_len)
         caps = ex.capture_decode_graphs()
         conn.send(("ready", rank, {"pages": pages, "capacities": caps, "vocab": cfg.vocab_size, "name": cfg.name,
-                                   "reasoning_end_id": ex.reasoning_end_id, "hybrid": cfg.is_hybrid}))
+                                   "reasoning_end_id": ex.reasoning_end_id, "hybrid": cfg.is_hybrid,
+                                   "state_rows": list(ex.state_checkpoint_rows)}))
         while True:
             cmd = conn.recv()
             if cmd[0] == "execute":
@@ -156,6 +160,8 @@ def _worker_main(rank: int, spec: WorkerSpec, port: int, conn) -> None:
             elif cmd[0] == "copy":
                 ex.copy_pages(cmd[1])
                 ex.invalidate_page_rows(cmd[2])
+            elif cmd[0] == "copy_state":
+                ex.copy_state(cmd[1])                   # recurrent-state rows: snapshot taken / snapshot restored
             elif cmd[0] == "close":
                 break
         if spec.world > 1:
@@ -239,13 +245,29 @@ class MultiprocExecutor:
 
     @property
     def cfg(self):
-        """Family properties of the served model that the engine reads (recurrent layers switch prefix caching off)."""
+        """Properties of the served model that the engine reads: recurrent layers (prefix caching then needs state
+        snapshots) and the vocabulary size (width of the allowed-token masks of constrained requests)."""
         from types import SimpleNamespace
-        return SimpleNamespace(is_hybrid=bool(self.info.get("hybrid", False)))
+        return SimpleNamespace(is_hybrid=bool(self.info.get("hybrid", False)), vocab_size=int(self.info.get("vocab", 0)))
+
+    @property
+    def state_checkpoint_rows(self) -> tuple[int, ...]:
+        """Snapshot rows of the workers' recurrent-state arrays (empty for models without recurrent layers)."""
+        return tuple(self.info.get("state_rows", ()))
+
+    def copy_state(self, pairs) -> None:
+        if pairs:
+            for c in self._conns:
+                c.send(("copy_state", list(pairs)))
 
     def execute(self, segs) -> np.ndarray:
         if self.poisoned:
             raise WorkerFailure("executor is poisoned")
+        if any(getattr(s, "mask_fn", None) is not None for s in segs):
+            # the review-mask callbacks of speculative rounds are closures over the controller's grammar matchers:
+            # they do not cross the pipe (the workers run plain steps, which use Segment.mask)
+            from dataclasses import replace
+            segs = [replace(s, mask_fn=None) if s.mask_fn is not None else s for s in segs]
         for c in self._conns:
             c.send(("execute", segs))
         c0 = self._conns[0]
