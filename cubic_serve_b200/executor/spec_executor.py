@@ -479,6 +479,7 @@ class SpeculativeGpuExecutor(GpuExecutor):
 
 class NgramSpeculativeGpuExecutor(SpeculativeGpuExecutor):
     speculative_sampling = False     # prompt-lookup drafts are verified against the target's greedy choice only
+    speculative_grammar = False      # and a constrained request makes its step a plain one
 
     """Speculative rounds whose drafts come from the host (n-gram / prompt lookup, ``runtime/ngram.py``): no draft
     model, no proposal passes, no carried hidden state -- a round is the target review over ``[root, d1 .. dk]`` plus
