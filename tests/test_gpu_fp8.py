@@ -65,7 +65,8 @@ def test_fused_norm_and_swiglu_quantizers_equal_the_unfused_chain():
                                           (700, 1024, 4096, 1),
                                           # the persistent kernel: stream-K (more tiles than SMs) and CTA pairs (> 256 rows)
                                           (256, 24576, 4096, None), (64, 24576, 2048, None), (1024, 6144, 4096, None),
-                                          (2048, 24576, 1024, None)])
+                                          (2048, 24576, 1024, None),
+                                          (2048, 512, 8192, None)])          # deep K at prefill size: CTA pairs by the dispatcher
 def test_fp8_gemm_matches_fp32_on_the_same_codes(m, n, k, splits):
     from cubic_serve_b200.ops import kernels as K
     dev = torch.device("cuda")
