@@ -267,18 +267,19 @@ __device__ __forceinline__ void decode8<kFmtAffine4>(uint32_t w, uint32_t scale,
   }
 }
 
-// NVFP4: nibble = sign(1) exp(2) man(1).  exp|man placed at bf16 bits 8..6 and
-// multiplied by 2^126 gives {0,.5,1,1.5,2,3,4,6} exactly (exp = 0 codes are bf16
-// subnormals that the multiply normalises); then one multiply by the block scale.
+// NVFP4: the codes arrive as sign-magnitude words like Cubic's (ops/wq_pack.py re-tiles them at load): the low three
+// bits of a nibble, exponent and mantissa of the e2m1 value, index ONE constant table whose entry m is the bf16
+// pattern m << 6 = magnitude x 2^-126 ({0, .5, 1, 1.5, 2, 3, 4, 6}; the two smallest are bf16 subnormals that the
+// multiply below normalises).  One packed multiply per pair by the block scale, stored as scale x 2^118, finishes the
+// weights (the remaining 2^8 rides in alpha): 13 integer instructions + 4 multiplies per eight weights against 28
+// for the shift-and-mask form.
 template <>
 __device__ __forceinline__ void decode8<kFmtNvfp4>(uint32_t w, uint32_t scale, uint32_t, uint32_t,
                                                    uint32_t (&out)[4]) {
+  const uint4 t = make_uint4(0xC0804000u, 0xC0804000u, 0x00000000u, 0x01010101u);   // low bytes 0..3, 4..7; high bytes
+  cubic_lut8(w, t, out);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t t = (w >> (4 * i)) & 0x000F000Fu;
-    const uint32_t bits = ((t & 0x00070007u) << 6) | ((t & 0x00080008u) << 12);
-    out[i] = bf2_mul(bf2_mul(bits, 0x7E807E80u), scale);
-  }
+  for (int i = 0; i < 4; ++i) out[i] = bf2_mul(out[i], scale);
 }
 
 // ------------------------------------------------------------------ host

@@ -173,11 +173,20 @@ def pack_affine4(q: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, gro
     return PackedWeight(FMT_AFFINE4, n, k, group_k, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4))
 
 
+NVFP4_META_SHIFT = 118      # block scales are stored times 2**118 (and alpha times 2**8): see pack_nvfp4
+
+
 def pack_nvfp4(packed: torch.Tensor, block_scale: torch.Tensor, global_scale: float) -> PackedWeight:
     """NVFP4 ``weight_packed uint8 [N, K/2]`` (low nibble first), e4m3 block scales ``[N, K/16]``.
 
     ``global_scale`` multiplies the result (pass ``1 / weight_global_scale`` for
     compressed-tensors checkpoints, ``weight_scale_2`` for ModelOpt).
+
+    Kernel form: the codes are re-tiled into the sign-magnitude words of the Cubic path (a nibble's low three bits,
+    exponent and mantissa of the e2m1 value, are a byte-permute selector), so eight codes become four bf16 pairs
+    ``magnitude x 2**-126`` through one constant table in 13 integer instructions, and ONE packed multiply per pair by
+    the block scale finishes them.  For that the metadata holds ``scale x 2**118`` (exact in bf16: e4m3 scales reach
+    448, so ``x 2**126`` would overflow) and ``alpha`` carries the remaining ``2**8``.
     """
     n, k2 = packed.shape
     k = k2 * 2
@@ -185,14 +194,15 @@ def pack_nvfp4(packed: torch.Tensor, block_scale: torch.Tensor, global_scale: fl
         raise ValueError("K must be a multiple of 64")
     n_pad = -(-n // TILE_N) * TILE_N
     p32 = packed.to(torch.int32)
-    nib = torch.stack([p32 & 15, p32 >> 4], -1).reshape(n, k).to(torch.uint8)
+    nib = torch.stack([p32 & 15, p32 >> 4], -1).reshape(n, k)
     nib = _pad_rows(nib, n_pad, 0)
-    bs = _pad_rows(block_scale.float().reshape(n, k // 16), n_pad, 0.0).reshape(n_pad, k // 32, 2)
+    signed = (nib & 7) * (1 - 2 * (nib >> 3))                 # -0 becomes 0: the same value
+    bs = _pad_rows(block_scale.float().reshape(n, k // 16), n_pad, 0.0).reshape(n_pad, k // 32, 2) * float(2 ** NVFP4_META_SHIFT)
     words = _bf16_pair_words(bs[..., 0], bs[..., 1])
     nt, kb = n_pad // TILE_N, k // BLOCK_K
     meta = words.reshape(nt, TILE_N, kb, 2).permute(0, 2, 3, 1).contiguous()
-    return PackedWeight(FMT_NVFP4, n, k, 16, _tile_nibbles(nib), meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4),
-                        alpha=float(global_scale))
+    return PackedWeight(FMT_NVFP4, n, k, 16, _tile_words(cubic_code_words(signed)),
+                        meta.view(torch.uint8).reshape(nt, kb, 2, TILE_N, 4), alpha=float(global_scale) * 256.0)
 
 
 def pack_bf16(weight: torch.Tensor) -> PackedWeight:
@@ -312,7 +322,11 @@ def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
         col = (torch.arange(k, device=c.device) // pw.group_k).expand(n_pad, k)
         mag = lv[torch.arange(n_pad, device=c.device).unsqueeze(1), col, c.abs()]
         return (mag * torch.sign(c).float())[: pw.n]
-    nib = _untile_nibbles(pw.codes)
+    if pw.fmt == FMT_NVFP4:
+        c = cubic_codes_from_words(_untile_words(pw.codes))                        # signed magnitude indices [N_pad, K]
+        nib = (c.abs() + 8 * (c < 0)).float()
+    else:
+        nib = _untile_nibbles(pw.codes)
     n_pad, k = nib.shape
     words = pw.meta.reshape(nt, -1, 2, TILE_N, 4).view(torch.int32).reshape(nt, -1, 2, TILE_N)
 
@@ -327,4 +341,5 @@ def unpack_to_dense(pw: PackedWeight) -> torch.Tensor:
     lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6], device=nib.device)
     bs = torch.stack([lo, hi], -1).reshape(n_pad, k // 16)
     col = torch.arange(k, device=nib.device) // 16
-    return (lut[nib.long()] * bs[:, col] * pw.alpha)[: pw.n]
+    # stored scales carry 2**118 and alpha 2**8 (see pack_nvfp4); the table values stand for magnitude x 2**-126
+    return (lut[nib.long()] * (bs[:, col] * float(2.0 ** -126)) * pw.alpha)[: pw.n]
