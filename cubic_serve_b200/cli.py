@@ -168,6 +168,14 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--token-budget", type=int, default=8192)
     g.add_argument("--cuda-graph-max-tokens", default="auto")
     g.add_argument("--prefill-chunk-tokens", type=int, default=4096)
+    g = s.add_argument_group("Multimodal input")
+    g.add_argument("--encoder-memory-gib", type=float, default=2.0,
+                   help="transient memory one call of the vision tower may use; larger items are cut at frame boundaries "
+                        "or refused")
+    g.add_argument("--feature-store-mib", type=int, default=1024, help="host memory for encoded media, reused by content")
+    g.add_argument("--media-file-root", action="append", default=[], help="directory file: media may be read from")
+    g.add_argument("--media-http-host", action="append", default=[], help="host name http(s): media may be fetched from")
+    g.add_argument("--max-media-items", type=int, default=16)
     g = s.add_argument_group("Advanced")
     g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
     g.add_argument("--startup-numerical-audit", action="store_true",

@@ -20,6 +20,8 @@ PAGE = 16
 
 
 class EagerPagedExecutor:
+    accepts_features = True          # segments may carry encoder feature rows and three-axis positions
+
     def __init__(self, cfg: ModelConfig, weights: DenseWeights, num_pages: int,
                  kv_bits: tuple[int, int] | None = None) -> None:
         self.cfg = cfg
@@ -66,6 +68,13 @@ class EagerPagedExecutor:
         pos = torch.arange(s.start, s.start + n)
         total = s.start + n
         h = w.embed[torch.as_tensor(np.asarray(s.token_ids), dtype=torch.long)].float()
+        for off, rows in (s.embeds or ()):                        # encoder features take the place of the embedding
+            h[off:off + rows.shape[0]] = rows.float()
+        pos3 = None
+        if s.positions3 is not None and cfg.mrope_section is not None:
+            pos3 = torch.as_tensor(np.asarray(s.positions3), dtype=torch.long)
+        rot = (lambda t: eager.rope(t, pos, dec.inv_freq)) if pos3 is None else \
+            (lambda t: eager.rope3(t, pos3, dec.inv_freq, cfg.mrope_section))
         Hq, Hkv, D = cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim
         for li, l in enumerate(w.layers):
             x = eager.rmsnorm(h, l.ln1, cfg.rms_eps, cfg.zero_centered_norm)
@@ -74,7 +83,7 @@ class EagerPagedExecutor:
             v = (x @ l.wv.t()).view(n, Hkv, D)
             if l.q_norm is not None:
                 q, k = eager.rmsnorm(q, l.q_norm, cfg.rms_eps), eager.rmsnorm(k, l.k_norm, cfg.rms_eps)
-            q, k = eager.rope(q, pos, dec.inv_freq), eager.rope(k, pos, dec.inv_freq)
+            q, k = rot(q), rot(k)
             if dec.kv_bits is not None:
                 k, v = dec._kvq(k, dec.kv_bits[0]), dec._kvq(v, dec.kv_bits[1])
             self.k[li][pages[pos // PAGE], pos % PAGE] = k

@@ -44,6 +44,10 @@ class Segment:
     # speculative rounds of a constrained request: callable(drafts) -> uint32 [len(drafts) + 1, words], row j = the
     # allowed tokens after the request's grammar has accepted drafts[:j] (the matcher is left where it was)
     mask_fn: object = None
+    # multimodal prefill: ``embeds`` = [(offset into this segment's tokens, rows [n, hidden])] replace the embedding of
+    # those tokens with encoder features; ``positions3`` = int [3, count] rotary positions (None: all axes = position)
+    embeds: object = None
+    positions3: object = None
 
 
 class _Staging:

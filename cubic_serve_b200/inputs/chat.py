@@ -93,6 +93,7 @@ class PreparedInput:
     token_ids: list[int]
     prompt_text: str
     starts_in_reasoning: bool = False
+    multimodal: object = None        # ``runtime.multimodal.MultimodalInput`` when the prompt carries media
 
 
 class ChatInputProcessor:

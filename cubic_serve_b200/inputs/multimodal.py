@@ -1,0 +1,134 @@
+"""Chat requests with image / video parts -> prompt tokens, placeholder runs, feature rows and positions.
+
+``MultimodalChatProcessor`` extends the text processor:
+
+1. every media part is resolved (``inputs/media.py``: data / file / http under the deployment's policy), decoded and
+   cut into patches (``inputs/vision_patches.py``); a video part may also carry already decoded frames in
+   ``ContentPart.data`` (container decoding needs a codec library that this build does not ship: mp4 / webm urls are
+   refused with a 400);
+2. the prompt is rendered with ``<|vision_start|><|image_pad|><|vision_end|>`` (``<|video_pad|>`` for clips) where
+   the part stood, tokenized, and each pad token is expanded into as many copies as the item has feature rows;
+3. the vision service encodes the items (or finds them in its store) and the three-axis rotary positions of the
+   expanded prompt are computed (``models/vision.py::mrope_positions``).
+
+The result is a ``PreparedInput`` whose ``multimodal`` field (``runtime/multimodal.py::MultimodalInput``) the engine
+takes with the token ids.
+
+Reference counterpart: ``models/qwen3_5/multimodal.py:1148-1358`` (processor: decode, resize, patchify),
+``:1360-1727`` (bridge: expand the prompt, positions, encode, cache keys).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+import numpy as np
+
+from ..contracts.request import CanonicalChatRequest, ContentPart, RequestError
+from ..models.vision import mrope_positions
+from ..runtime.multimodal import MultimodalInput
+from .chat import ChatInputProcessor, PreparedInput
+from .media import MediaError, MediaResolver
+from .vision_patches import (MediaPatches, PatchGeometry, VisionInputError, decode_image, patchify_image,
+                             patchify_video)
+
+
+@dataclass(frozen=True)
+class VisionTokens:
+    """Token ids of the checkpoint's ``config.json`` (``image_token_id`` ...) and the strings the template emits."""
+    image: int
+    video: int
+    start: int
+    end: int
+    image_text: str = "<|image_pad|>"
+    video_text: str = "<|video_pad|>"
+    start_text: str = "<|vision_start|>"
+    end_text: str = "<|vision_end|>"
+
+    @staticmethod
+    def from_hf(cfg: dict) -> "VisionTokens":
+        try:
+            return VisionTokens(int(cfg["image_token_id"]), int(cfg["video_token_id"]),
+                                int(cfg["vision_start_token_id"]), int(cfg["vision_end_token_id"]))
+        except KeyError as e:
+            raise ValueError(f"config.json lacks {e.args[0]!r}") from None
+
+
+class MultimodalChatProcessor(ChatInputProcessor):
+    def __init__(self, tokenizer, vision_service, tokens: VisionTokens, geometry: PatchGeometry | None = None,
+                 resolver: MediaResolver | None = None, default_thinking: bool | None = None,
+                 max_model_len: int | None = None, max_items: int = 16) -> None:
+        super().__init__(tokenizer, default_thinking, max_model_len)
+        self.vision, self.tokens = vision_service, tokens
+        cfg = vision_service.encoder.cfg
+        self.geometry = geometry or PatchGeometry(cfg.patch_size, cfg.spatial_merge_size, cfg.temporal_patch_size)
+        if (self.geometry.patch_size, self.geometry.merge_size, self.geometry.temporal_patch_size) != \
+                (cfg.patch_size, cfg.spatial_merge_size, cfg.temporal_patch_size):
+            raise ValueError("the patch geometry differs from the vision tower's")
+        self.resolver = resolver or MediaResolver()
+        self.max_items = max_items
+
+    # ------------------------------------------------------------------ media parts -> patches
+    def _patches(self, part: ContentPart) -> MediaPatches:
+        try:
+            if part.kind == "image":
+                if part.data is not None:
+                    return patchify_image(part.data, self.geometry)
+                media = self.resolver.resolve(part.media_url, "image")
+                return patchify_image(decode_image(media.data), self.geometry)
+            if part.data is not None:
+                return patchify_video(list(part.data), self.geometry)
+            self.resolver.resolve(part.media_url, "video")          # policy and type checks still apply
+            raise RequestError("video containers cannot be decoded by this deployment; send frames as images",
+                               param="messages")
+        except (MediaError, VisionInputError) as e:
+            raise RequestError(str(e), param="messages") from None
+
+    def build(self, req: CanonicalChatRequest) -> PreparedInput:
+        t = self.tokens
+        items: list[tuple[str, MediaPatches]] = []
+        msgs = []
+        for m in req.messages:
+            parts = []
+            for p in m.parts:
+                if p.kind in ("image", "video"):
+                    items.append((p.kind, self._patches(p)))
+                    pad = t.image_text if p.kind == "image" else t.video_text
+                    parts.append(ContentPart("text", t.start_text + pad + t.end_text))
+                else:
+                    parts.append(p)
+            msgs.append(replace(m, parts=tuple(parts)))
+        if not items:
+            return super().build(req)
+        if len(items) > self.max_items:
+            raise RequestError(f"a request may carry {self.max_items} media items", param="messages")
+        base = super().build(replace(req, messages=tuple(msgs)))
+        merge = self.geometry.merge_size
+        # expand every pad token into the item's rows
+        ids: list[int] = []
+        spans_at: list[int] = []
+        k = 0
+        for tok in base.token_ids:
+            if tok in (t.image, t.video):
+                if k >= len(items) or (tok == t.image) != (items[k][0] == "image"):
+                    raise RequestError("the rendered prompt's media placeholders do not match the media parts",
+                                       param="messages")
+                spans_at.append(len(ids))
+                ids.extend([tok] * items[k][1].rows(merge))
+                k += 1
+            else:
+                ids.append(tok)
+        if k != len(items):
+            raise RequestError("the chat template dropped a media part", param="messages")
+        if self.max_model_len is not None and len(ids) + 1 > self.max_model_len:
+            raise RequestError(f"the prompt has {len(ids)} tokens with its media; the context limit is "
+                               f"{self.max_model_len}", param="messages")
+        try:
+            encoded = self.vision.encode([(mp.pixels, mp.grid) for _, mp in items])
+        except ValueError as e:                                       # capacity limits of the encoder
+            raise RequestError(str(e), param="messages") from None
+        spans = [(at, rows, digest) for at, (rows, digest) in zip(spans_at, encoded)]
+        pos, delta = mrope_positions(ids, [(at, mp.rows(merge), mp.grid) for at, (_, mp) in zip(spans_at, items)], merge)
+        mm = MultimodalInput(spans, np.asarray(pos, dtype=np.int32), delta)
+        out = PreparedInput(ids, base.prompt_text, starts_in_reasoning=base.starts_in_reasoning)
+        out.multimodal = mm
+        return out

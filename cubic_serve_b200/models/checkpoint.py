@@ -59,6 +59,17 @@ class SafetensorsDirectory:
                         raise CheckpointError(f"tensor {name} appears in two shards")
                     sl = sf.get_slice(name)
                     self.tensors[name] = TensorRef(name, f, str(sl.get_dtype()), tuple(sl.get_shape()))
+        # multimodal checkpoints keep the decoder under ``model.language_model.``: it is read under the text-only names
+        # (``TensorRef.name`` stays the name in the file)
+        nested = "model.language_model."
+        if any(n.startswith(nested) for n in self.tensors):
+            renamed = {}
+            for n, ref in self.tensors.items():
+                alias = "model." + n[len(nested):] if n.startswith(nested) else n
+                if alias in renamed or (alias != n and alias in self.tensors):
+                    raise CheckpointError(f"tensor {alias} exists both nested and at the top level")
+                renamed[alias] = ref
+            self.tensors = renamed
         self._handles: dict[str, object] = {}
 
     def get(self, name: str) -> torch.Tensor:
@@ -66,7 +77,7 @@ class SafetensorsDirectory:
         h = self._handles.get(ref.file)
         if h is None:
             h = self._handles[ref.file] = self._open(str(self.path / ref.file), framework="pt")
-        return h.get_tensor(name)
+        return h.get_tensor(ref.name)
 
     def __contains__(self, name: str) -> bool:
         return name in self.tensors
@@ -149,6 +160,10 @@ class AdmittedCheckpoint:
     store: SafetensorsDirectory
     payloads: dict[str, dict[str, str]]      # module -> suffix -> tensor name
     plain: dict[str, str]
+    # multimodal checkpoints: the tower's configuration, the name prefix of its tensors and the raw config.json
+    vision: object | None = None
+    vision_prefix: str = ""
+    raw_config: dict | None = None
 
     def payload(self, module: str) -> dict[str, torch.Tensor]:
         return {suffix: self.store.get(name) for suffix, name in self.payloads[module].items()}
@@ -186,10 +201,38 @@ def admit_checkpoint(path: str | Path) -> AdmittedCheckpoint:
             raise CheckpointError(f"missing tensor {name}")
         plain_map[name] = name
         claimed.add(name)
+    raw = json.loads((path / "config.json").read_text())
+    vision, vprefix = None, ""
+    if isinstance(raw.get("vision_config"), dict):
+        from .vision import VisionConfig, VisionConfigError, vision_tensor_shapes
+        try:
+            vision = VisionConfig.from_hf(raw["vision_config"])
+        except VisionConfigError as exc:
+            raise CheckpointError(str(exc)) from exc
+        if vision.out_hidden_size != cfg.hidden_size:
+            raise CheckpointError("the vision tower's output width differs from the decoder's hidden size")
+        vprefix = next((p for p in ("model.visual.", "visual.") if f"{p}pos_embed.weight" in store), "model.visual.")
+        for name, shape in vision_tensor_shapes(vision).items():
+            full = vprefix + name
+            if full not in store:
+                raise CheckpointError(f"missing tensor {full}")
+            if tuple(store.tensors[full].shape) != shape:
+                raise CheckpointError(f"{full}: shape {tuple(store.tensors[full].shape)}, expected {shape}")
+            claimed.add(full)
     unowned = sorted(set(store.tensors) - claimed)
     if unowned:
         raise CheckpointError(f"checkpoint has {len(unowned)} tensors no logical weight owns, e.g. {unowned[:3]}")
-    return AdmittedCheckpoint(cfg, store, payloads, plain_map)
+    return AdmittedCheckpoint(cfg, store, payloads, plain_map, vision, vprefix, raw)
+
+
+def load_vision_weights(ck: AdmittedCheckpoint, device="cpu", dtype=torch.bfloat16, tp_rank: int = 0, tp_size: int = 1) -> dict:
+    """The tower's tensors of an admitted multimodal checkpoint (this rank's shard under tensor parallelism)."""
+    from .vision import shard_vision_weights, vision_tensor_shapes
+    if ck.vision is None:
+        raise CheckpointError("the checkpoint has no vision tower")
+    w = {n: ck.store.get(ck.vision_prefix + n).to(dtype) for n in vision_tensor_shapes(ck.vision)}
+    w = shard_vision_weights(ck.vision, w, tp_rank, tp_size)
+    return {n: t.to(device) for n, t in w.items()}
 
 
 def inspect_checkpoint(path: str | Path) -> dict:

@@ -21,6 +21,17 @@ class QuantSpec:
     lm_head_quantized: bool = False
 
 
+def _mrope_section(text: dict):
+    """``mrope_section`` of ``rope_parameters`` / ``rope_scaling`` when the checkpoint declares three-axis positions."""
+    for key in ("rope_parameters", "rope_scaling"):
+        sec = (text.get(key) or {}).get("mrope_section") if isinstance(text.get(key), dict) else None
+        if sec is not None:
+            if len(sec) != 3:
+                raise ValueError("mrope_section lists three counts")
+            return tuple(int(v) for v in sec)
+    return None
+
+
 @dataclass(frozen=True)
 class ModelConfig:
     name: str = "toy"
@@ -56,6 +67,9 @@ class ModelConfig:
     mtp_layers: int = 0
     quant: QuantSpec = field(default_factory=QuantSpec)
     eos_token_id: int | None = None
+    # three-axis rotary positions of the multimodal checkpoints: how many frequency slots follow the (temporal, row,
+    # column) axis; None = one axis
+    mrope_section: tuple[int, int, int] | None = None
 
     @property
     def q_size(self) -> int:
@@ -129,6 +143,7 @@ class ModelConfig:
             mtp_layers=int(text.get("mtp_num_hidden_layers") or text.get("num_nextn_predict_layers") or 0),
             quant=quant_spec_from_hf(qc),
             eos_token_id=(text.get("eos_token_id") if isinstance(text.get("eos_token_id"), int) else None),
+            mrope_section=_mrope_section(text),
         )
 
 

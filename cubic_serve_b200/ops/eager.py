@@ -40,6 +40,36 @@ def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> to
     return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], -1)
 
 
+def mrope_axes(section, half: int) -> list[int]:
+    """Axis (0 temporal, 1 row, 2 column) of every frequency slot under the interleaved three-axis layout: the row axis
+    takes slots 1, 4, 7, ... and the column axis 2, 5, 8, ... as far as their counts reach, the rest is temporal
+    (reference: ``ops/eager/hybrid.py:112-193``)."""
+    t, h, w = (int(v) for v in section)
+    if t + h + w != half or min(t, h, w) <= 0:
+        raise ValueError("the three section counts are positive and sum to half the rotary width")
+    if max(3 * h - 2, 3 * w - 1) >= half:
+        raise ValueError("the section counts do not fit the interleaved layout")
+    axes = [0] * half
+    for i in range(1, 3 * h, 3):
+        axes[i] = 1
+    for i in range(2, 3 * w, 3):
+        axes[i] = 2
+    return axes
+
+
+def rope3(x: torch.Tensor, positions3: torch.Tensor, inv_freq: torch.Tensor, section) -> torch.Tensor:
+    """Rotate-half RoPE on ``[T, H, D]`` with ``positions3 [3, T]``: frequency slot ``j`` turns by the position on axis
+    ``mrope_axes(section)[j]``.  Equal rows of ``positions3`` give ``rope``."""
+    half = inv_freq.numel()
+    axes = torch.tensor(mrope_axes(section, half), device=positions3.device)
+    pos = positions3.float()[axes, :].t()                      # [T, half]: the position each slot uses
+    ang = pos * inv_freq[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    xf = x.float()
+    a, b, rest = xf[..., :half], xf[..., half:2 * half], xf[..., 2 * half:]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin, rest], -1)
+
+
 def kv_quantize(x: torch.Tensor, bits: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Symmetric per-(token, head, 32-channel group) quantization.
 

@@ -78,10 +78,12 @@ class _Live:
 
 class TokenChatBackend:
     def __init__(self, engine: LLMEngine, tokenizer, default_thinking: bool | None = None,
-                 reasoning_parser: bool = True, default_max_tokens: int = 1024) -> None:
+                 reasoning_parser: bool = True, default_max_tokens: int = 1024, processor=None) -> None:
+        """``processor``: the input processor (default: text only); a ``MultimodalChatProcessor`` makes the backend
+        accept image and video parts."""
         self.engine = engine
         self.tokenizer = tokenizer
-        self.processor = ChatInputProcessor(tokenizer, default_thinking, engine.cfg.max_model_len)
+        self.processor = processor or ChatInputProcessor(tokenizer, default_thinking, engine.cfg.max_model_len)
         self.reasoning_parser = reasoning_parser
         self.default_max_tokens = default_max_tokens
         self.ready = True
@@ -131,7 +133,7 @@ class TokenChatBackend:
                             thinking_budget=req.reasoning.budget_tokens if prepared.starts_in_reasoning else None)
         with self._lock:
             self._live[req.request_id] = live
-            self._inbox.append((req.request_id, prepared.token_ids, sp))
+            self._inbox.append((req.request_id, prepared.token_ids, sp, prepared.multimodal))
         self._wake.set()
         return self._events(live)
 
@@ -191,12 +193,12 @@ class TokenChatBackend:
                 inbox = list(self._inbox)
                 self._inbox.clear()
                 cancelled = [l for l in self._live.values() if l.cancelled and not l.done]
-            for rid, ids, sp in inbox:
+            for rid, ids, sp, mm in inbox:
                 live = self._live.get(rid)
                 if live is None or live.cancelled:
                     continue
                 try:
-                    live.engine_id = self.engine.add_request(ids, sp, request_id=rid)
+                    live.engine_id = self.engine.add_request(ids, sp, request_id=rid, multimodal=mm)
                     by_engine_id[rid] = live
                     self.stats["requests"] += 1
                     self._publish(live, live.pipeline.start_events(), batch)

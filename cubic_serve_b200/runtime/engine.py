@@ -77,15 +77,22 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ API
     def add_request(self, prompt_token_ids: list[int], sampling: SamplingParams | None = None,
-                    request_id: str | None = None) -> str:
+                    request_id: str | None = None, multimodal=None) -> str:
+        """``multimodal``: a ``runtime.multimodal.MultimodalInput`` for prompts whose media were expanded into
+        placeholder tokens; only executors that take feature rows (``accepts_features``) admit such requests."""
         if self.poisoned:
             raise EnginePoisoned("engine is poisoned")
+        if multimodal is not None:
+            if not getattr(self.executor, "accepts_features", False):
+                raise AdmissionError("this executor serves text only; requests with media are not accepted", status=400)
+            if multimodal.prompt_length != len(prompt_token_ids):
+                raise AdmissionError("the media positions do not cover the prompt", status=400)
         rid = request_id or f"req-{next(self._ids)}"
         if rid in self.requests:
             raise AdmissionError(f"duplicate request id {rid}")
         if len(self.scheduler.waiting) + len(self.scheduler.running) >= 4 * self.cfg.max_running_requests:
             raise AdmissionError("too many queued requests", status=429)
-        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams())
+        req = Request(rid, list(prompt_token_ids), sampling or SamplingParams(), multimodal=multimodal)
         self.scheduler.add(req)
         self.requests[rid] = req
         return rid
@@ -182,6 +189,8 @@ class LLMEngine:
                                 sp.seed if sp.seed is not None else hash(r.request_id) & 0x7FFFFFFF,
                                 r.draws + (1 if ahead else 0), (r.arrival << 16) | (r.preemptions & 0xFFFF), mask,
                                 self._budget_init(r) if s.sample and end_id is not None else -2, mask_fn))
+            if r.multimodal is not None:
+                segs[-1].embeds, segs[-1].positions3 = r.multimodal.segment_inputs(s.start, s.count)
         return segs
 
     def _review_masks_of(self, matcher):

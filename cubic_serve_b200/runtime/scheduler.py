@@ -79,6 +79,9 @@ class Request:
     preemptions: int = 0
     last_committed: int = 0        # tokens kept by the most recent commit (a stop can cut a speculative burst)
     tokens: list[int] = field(default_factory=list)   # prompt + output, maintained incrementally
+    # multimodal prompt (``runtime/multimodal.py::MultimodalInput``): encoder feature rows that replace the embedding
+    # of placeholder tokens, three-axis positions, and per-row content keys for the prefix cache
+    multimodal: object | None = None
 
     def __post_init__(self) -> None:
         if not self.tokens:
@@ -99,6 +102,13 @@ class Request:
     @property
     def remaining(self) -> int:
         return self.num_tokens - self.num_computed
+
+
+def _keys(req: Request, tokens: list[int]) -> list[int]:
+    """What the prefix cache hashes for ``tokens`` (a prefix of the request's tokens): placeholder tokens of a media
+    item are replaced by numbers derived from the item's content and the row, so two prompts share cached pages over
+    a media span only when the media are the same."""
+    return tokens if req.multimodal is None else req.multimodal.key_tokens(tokens)
 
 
 @dataclass
@@ -222,7 +232,7 @@ class ContinuousScheduler:
         if not self._free_slots:
             return False
         # restore the longest cached prefix, always leaving >= 1 prompt token to compute
-        pages = self.prefix.match(req.prompt, max_tokens=len(req.prompt) - 1) if not req.pages else []
+        pages = self.prefix.match(_keys(req, req.prompt), max_tokens=len(req.prompt) - 1) if not req.pages else []
         if pages:
             req.pages = list(pages)
             req.num_computed = len(pages) * BLOCK
@@ -382,11 +392,11 @@ class ContinuousScheduler:
             r.num_computed += seg.count
             full = r.num_computed // BLOCK
             if full > r.num_published and self.prefix.enabled:
-                self.prefix.publish(r.tokens[:full * BLOCK], r.pages[:full])
+                self.prefix.publish(_keys(r, r.tokens[:full * BLOCK]), r.pages[:full])
                 r.num_published = full
                 if self.prefix.needs_checkpoint and r.num_computed == full * BLOCK and not seg.sample:
                     # the step ended on a page boundary inside the prompt: its recurrent state is a valid snapshot
-                    slot = self.prefix.publish_checkpoint(r.tokens[:full * BLOCK])
+                    slot = self.prefix.publish_checkpoint(_keys(r, r.tokens[:full * BLOCK]))
                     if slot is not None:
                         self.state_saves.append((r.slot, slot))
             if seg.sample:

@@ -188,8 +188,39 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
     if spec is not None and getattr(spec, "mode", "fixed") == "dynamic" and getattr(executor, "speculative_depth", 0):
         from .speculative import DraftPolicyConfig
         engine.enable_dynamic_draft(DraftPolicyConfig.from_dict(spec.policy) if spec.policy else None)
-    backend = TokenChatBackend(engine, tok, default_thinking=args.thinking)
+    processor = None
+    if ck is not None and ck.vision is not None:
+        processor = build_media_processor(args, ck, tok, executor, max_len)
+    backend = TokenChatBackend(engine, tok, default_thinking=args.thinking, processor=processor)
     return backend, (args.served_model_name or cfg.name)
+
+
+def build_media_processor(args, ck, tok, executor, max_len: int):
+    """The input processor of a multimodal checkpoint: vision tower (on the executor's device when it has one), encoded
+    feature store, media policy.  Executors that take no feature rows serve such a checkpoint as text only."""
+    import torch
+    if not getattr(executor, "accepts_features", False):
+        log.warning("the checkpoint has a vision tower, but this execution mode serves text only "
+                    "(--execution-mode eager serves image and video parts)")
+        return None
+    from ..executor.vision import EncodedFeatureStore, VisionService
+    from ..inputs.media import MediaPolicy, MediaResolver
+    from ..inputs.multimodal import MultimodalChatProcessor, VisionTokens
+    from ..models.checkpoint import load_vision_weights
+    from ..models.vision import VisionEncoder
+    device = getattr(executor, "device", "cpu")
+    dtype = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+    encoder = VisionEncoder(ck.vision, load_vision_weights(ck, device, dtype))
+    service = VisionService(encoder, EncodedFeatureStore(getattr(args, "feature_store_mib", 1024) << 20),
+                            memory_bytes=int(getattr(args, "encoder_memory_gib", 2.0) * 2 ** 30),
+                            max_prompt_tokens=max_len - 1, identity=ck.cfg.name.encode())
+    policy = MediaPolicy(file_roots=tuple(getattr(args, "media_file_root", ()) or ()),
+                         http_hosts=tuple(getattr(args, "media_http_host", ()) or ()))
+    log.info("vision tower: %d layers, %d patches per encoder call, feature store %d MiB", ck.vision.depth,
+             service.plan.max_patches_per_call, getattr(args, "feature_store_mib", 1024))
+    return MultimodalChatProcessor(tok, service, VisionTokens.from_hf(ck.raw_config), resolver=MediaResolver(policy),
+                                   default_thinking=args.thinking, max_model_len=max_len,
+                                   max_items=getattr(args, "max_media_items", 16))
 
 
 class StatusReporter(threading.Thread):

@@ -1,0 +1,415 @@
+"""Vision tower, patch preprocessing, feature store / encoder service and the multimodal path through the engine
+(CPU).  The tower and the patch cutter are checked against the HuggingFace implementations of the same public
+architecture when those are importable."""
+import base64
+import io
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from cubic_serve_b200.executor.vision import (EncodedFeatureStore, EncoderCapacityError, EncoderMemoryPlan, VisionService,
+                                              media_digest)
+from cubic_serve_b200.inputs.vision_patches import (PatchGeometry, VisionInputError, decode_image, patchify_frames,
+                                                    patchify_image, patchify_video, smart_resize)
+from cubic_serve_b200.models.vision import (VisionConfig, VisionConfigError, VisionEncoder, check_vision_weights,
+                                            mrope_positions, random_vision_weights, shard_vision_weights)
+from cubic_serve_b200.ops import eager
+
+RAW = dict(depth=2, hidden_size=64, hidden_act="gelu_pytorch_tanh", intermediate_size=128, num_heads=4, in_channels=3,
+           patch_size=4, spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, num_position_embeddings=64,
+           deepstack_visual_indexes=[])
+
+
+def _cfg(**kw) -> VisionConfig:
+    return VisionConfig.from_hf({**RAW, **kw})
+
+
+# ------------------------------------------------------------------ tower
+@pytest.mark.parametrize("deep", [[], [0]])
+def test_tower_matches_the_public_implementation(deep):
+    hf_cfg = pytest.importorskip("transformers.models.qwen3_vl.configuration_qwen3_vl")
+    hf_mod = pytest.importorskip("transformers.models.qwen3_vl.modeling_qwen3_vl")
+    c = hf_cfg.Qwen3VLVisionConfig(**{**RAW, "deepstack_visual_indexes": deep})
+    c._attn_implementation = "eager"
+    torch.manual_seed(0)
+    ref = hf_mod.Qwen3VLVisionModel(c).eval()
+    for p in ref.parameters():
+        p.data.normal_(0, 0.1)
+    cfg = _cfg(deepstack_visual_indexes=deep)
+    w = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    check_vision_weights(cfg, w)
+    grid = torch.tensor([[1, 4, 6], [2, 2, 2], [1, 10, 4]])
+    px = torch.randn(int(grid.prod(-1).sum()), cfg.patch_width)
+    with torch.no_grad():
+        out = ref(px, grid_thw=grid)
+    mine, deepstack = VisionEncoder(cfg, w).encode(px, grid)
+    assert mine.shape == out.pooler_output.shape == (18, 32)
+    assert (mine - out.pooler_output).abs().max() < 1e-5
+    if deep:
+        assert (deepstack[0] - out.deepstack_features[0]).abs().max() < 1e-5
+
+
+def test_frames_are_independent_and_rows_follow_the_grid():
+    cfg = _cfg()
+    enc = VisionEncoder(cfg, random_vision_weights(cfg, 1))
+    g = torch.Generator().manual_seed(2)
+    a, b = torch.randn(24, cfg.patch_width, generator=g), torch.randn(16, cfg.patch_width, generator=g)
+    both, _ = enc.encode(torch.cat([a, b]), torch.tensor([[1, 4, 6], [1, 4, 4]]))
+    ra, _ = enc.encode(a, torch.tensor([[1, 4, 6]]))
+    rb, _ = enc.encode(b, torch.tensor([[1, 4, 4]]))
+    assert both.shape == (10, 32)
+    assert torch.allclose(both, torch.cat([ra, rb]), atol=1e-6)
+    with pytest.raises(ValueError):
+        enc.encode(a, torch.tensor([[1, 4, 5]]))                # width not a whole number of merge blocks
+    with pytest.raises(ValueError):
+        enc.encode(a[:, :-1], torch.tensor([[1, 4, 6]]))
+
+
+def test_sharded_tower_sums_to_the_whole():
+    cfg = _cfg()
+    w = random_vision_weights(cfg, 3)
+    px = torch.randn(24, cfg.patch_width, generator=torch.Generator().manual_seed(4))
+    grid = torch.tensor([[1, 4, 6]])
+    want, _ = VisionEncoder(cfg, w).encode(px, grid)
+    size = 2
+    barrier = threading.Barrier(size)
+    slots: list = [None] * size
+    out: list = [None] * size
+
+    def rank(r: int) -> None:
+        def reduce(t: torch.Tensor) -> torch.Tensor:
+            slots[r] = t
+            barrier.wait()
+            total = sum(slots[i] for i in range(size))          # ascending rank order on every rank
+            barrier.wait()
+            return total
+        enc = VisionEncoder(cfg, shard_vision_weights(cfg, w, r, size), r, size, reduce)
+        out[r] = enc.encode(px, grid)[0]
+    ts = [threading.Thread(target=rank, args=(r,)) for r in range(size)]
+    [t.start() for t in ts]
+    [t.join(60) for t in ts]
+    assert torch.equal(out[0], out[1])
+    assert (out[0] - want).abs().max() < 1e-5
+    with pytest.raises(VisionConfigError):
+        shard_vision_weights(cfg, w, 0, 3)
+    with pytest.raises(ValueError):
+        VisionEncoder(cfg, w, 0, 2)
+
+
+def test_config_is_strict():
+    with pytest.raises(VisionConfigError):
+        _cfg(surprise=1)
+    with pytest.raises(VisionConfigError):
+        _cfg(num_position_embeddings=60)
+    with pytest.raises(VisionConfigError):
+        _cfg(deepstack_visual_indexes=[5])
+    with pytest.raises(VisionConfigError):
+        check_vision_weights(_cfg(), {})
+
+
+# ------------------------------------------------------------------ patches
+@pytest.mark.parametrize("hw", [(70, 123), (224, 224), (31, 500)])
+def test_patches_match_the_public_image_processor(hw):
+    mod = pytest.importorskip("transformers.models.qwen2_vl.image_processing_qwen2_vl")
+    from PIL import Image
+    arr = np.random.default_rng(0).integers(0, 256, (*hw, 3), dtype=np.uint8)
+    img = Image.fromarray(arr)
+    geo = PatchGeometry(16, 2, 2, min_pixels=64 * 64, max_pixels=256 * 256)
+    proc = mod.Qwen2VLImageProcessor(patch_size=16, merge_size=2, temporal_patch_size=2, min_pixels=64 * 64,
+                                     max_pixels=256 * 256, image_mean=[0.5] * 3, image_std=[0.5] * 3)
+    want = proc(images=[img], return_tensors="pt")
+    mine = patchify_image(img, geo)
+    assert list(mine.grid) == want["image_grid_thw"][0].tolist()
+    assert np.abs(want["pixel_values"].numpy() - mine.pixels).max() < 1e-6
+
+
+def test_resize_and_patch_order():
+    assert smart_resize(100, 100, 32, 32 * 32, 1 << 20) == (96, 96)
+    h, w = smart_resize(4000, 3000, 32, 32 * 32, 256 * 256)
+    assert h % 32 == 0 and w % 32 == 0 and h * w <= 256 * 256
+    h, w = smart_resize(10, 20, 32, 64 * 64, 1 << 20)
+    assert h * w >= 64 * 64
+    with pytest.raises(VisionInputError):
+        smart_resize(1, 500, 32, 1, 1 << 20)
+    # merge-block order: rows 0..3 of the output are the 2 x 2 block at the top left
+    geo = PatchGeometry(2, 2, 1, mean=(0.0,), std=(1.0,))
+    frame = np.zeros((1, 8, 8, 1), dtype=np.uint8)
+    for r in range(4):
+        for c in range(4):
+            frame[0, 2 * r:2 * r + 2, 2 * c:2 * c + 2, 0] = r * 4 + c
+    p = patchify_frames(frame, geo)
+    assert p.grid == (1, 4, 4) and p.pixels.shape == (16, 4)
+    ids = np.rint(p.pixels[:, 0] * 255).astype(int).tolist()
+    assert ids == [0, 1, 4, 5, 2, 3, 6, 7, 8, 9, 12, 13, 10, 11, 14, 15]
+    # an odd number of frames is padded with the last one
+    geo2 = PatchGeometry(2, 2, 2, mean=(0.0,), std=(1.0,))
+    three = np.stack([np.full((4, 4, 1), v, dtype=np.uint8) for v in (10, 20, 30)])
+    v = patchify_frames(three, geo2)
+    assert v.grid == (2, 2, 2) and v.rows(2) == 2
+    assert np.allclose(v.pixels[4:, :] * 255, 30)
+
+
+def _png(h: int, w: int, seed: int = 0, mode: str = "RGB") -> bytes:
+    from PIL import Image
+    ch = {"RGB": 3, "RGBA": 4}[mode]
+    arr = np.random.default_rng(seed).integers(0, 256, (h, w, ch), dtype=np.uint8)
+    buf = io.BytesIO()
+    Image.fromarray(arr, mode).save(buf, "PNG")
+    return buf.getvalue()
+
+
+def test_decode_image_bounds_and_alpha():
+    img = decode_image(_png(20, 30, mode="RGBA"))
+    assert img.mode == "RGB" and img.size == (30, 20)
+    with pytest.raises(VisionInputError):
+        decode_image(b"\x89PNG\r\n\x1a\nnot a png")
+    with pytest.raises(VisionInputError):
+        decode_image(_png(20, 30), max_side=16)
+    from PIL import Image
+    frames = [Image.fromarray(np.full((40, 40, 3), v, dtype=np.uint8)) for v in (0, 100, 200)]
+    clip = patchify_video(frames, PatchGeometry(4, 2, 2, min_pixels=16 * 16, max_pixels=64 * 64))
+    assert clip.grid[0] == 2
+    with pytest.raises(VisionInputError):
+        patchify_video([], PatchGeometry())
+
+
+# ------------------------------------------------------------------ positions
+def test_three_axis_positions():
+    # 3 text tokens, an image of 4 x 6 patches (2 x 3 rows after the merge), 2 text tokens
+    pos, delta = mrope_positions(list(range(11)), [(3, 6, (1, 4, 6))], 2)
+    assert pos[0] == [0, 1, 2, 3, 3, 3, 3, 3, 3, 6, 7]
+    assert pos[1] == [0, 1, 2, 3, 3, 3, 4, 4, 4, 6, 7]
+    assert pos[2] == [0, 1, 2, 3, 4, 5, 3, 4, 5, 6, 7]
+    assert delta == 8 - 11
+    # a clip advances the temporal axis per frame group
+    pos, delta = mrope_positions([0] * 9, [(1, 8, (2, 4, 4))], 2)
+    assert pos[0][1:9] == [1, 1, 1, 1, 2, 2, 2, 2]
+    with pytest.raises(ValueError):
+        mrope_positions([0] * 4, [(0, 6, (1, 4, 6))], 2)
+    # equal axes reduce to the one-axis rotation
+    x = torch.randn(5, 2, 16)
+    inv = eager.rope_inv_freq(8, 10000.0)
+    p = torch.arange(3, 8)
+    assert torch.allclose(eager.rope3(x, p[None].expand(3, -1), inv, (2, 1, 1)), eager.rope(x, p, inv))
+    assert eager.mrope_axes((11, 11, 10), 32).count(1) == 11
+    assert eager.mrope_axes((2, 1, 1), 4) == [0, 1, 2, 0]
+    with pytest.raises(ValueError):
+        eager.mrope_axes((1, 2, 1), 4)
+    y = eager.rope3(x, torch.stack([p, p + 1, p + 2]), inv, (2, 1, 1))
+    assert not torch.allclose(y, eager.rope(x, p, inv))
+
+
+# ------------------------------------------------------------------ store, plan, service
+def test_feature_store_is_bounded_lru():
+    st = EncodedFeatureStore(max_bytes=3 * 40)
+    rows = [torch.full((10,), float(i)) for i in range(4)]          # 40 bytes each
+    for i in range(3):
+        st.put(bytes([i]), rows[i])
+    assert st.get(bytes([0])) is not None                           # 0 is now the most recent
+    st.put(bytes([3]), rows[3])
+    assert st.get(bytes([1])) is None and st.get(bytes([0])) is not None and len(st) == 3
+    assert st.bytes == 120 and st.evictions == 1
+    st.put(b"big", torch.zeros(100))                                # larger than the store: not kept
+    assert st.get(b"big") is None
+    assert media_digest(np.zeros((4, 8), np.float32), (1, 2, 2)) != media_digest(np.zeros((4, 8), np.float32), (1, 2, 2), b"x")
+
+
+def test_service_cuts_clips_and_reuses_features():
+    cfg = _cfg()
+    enc = VisionEncoder(cfg, random_vision_weights(cfg, 5))
+    px = np.random.default_rng(6).standard_normal((6 * 16, cfg.patch_width)).astype(np.float32)
+    whole = VisionService(enc, memory_bytes=1 << 30)
+    rows, digest = whole.encode([(px, (6, 4, 4))])[0]
+    assert rows.shape == (6 * 4, 32) and whole.encode_calls == 1
+    # a budget that holds two frames per call
+    per = enc.activation_bytes(1)
+    small = VisionService(enc, memory_bytes=int(2.6 * 16 * per) + 4 * 32 * 32 * 4 * 2)
+    assert small.plan.max_patches_per_call < 6 * 16
+    rows2, digest2 = small.encode([(px, (6, 4, 4))])[0]
+    assert small.encode_calls > 1 and digest2 == digest
+    assert torch.allclose(rows2, rows, atol=1e-6)
+    small.encode([(px, (6, 4, 4))])
+    assert small.store.hits == 1
+    with pytest.raises(EncoderCapacityError):
+        small.encode([(np.zeros((400, cfg.patch_width), np.float32), (1, 20, 20))])
+    with pytest.raises(EncoderCapacityError):
+        EncoderMemoryPlan.build(enc, 16, 100)
+    tiny = VisionService(enc, max_prompt_tokens=8)
+    with pytest.raises(EncoderCapacityError):
+        tiny.encode([(px, (6, 4, 4))])
+    # the owned thread serves futures and survives a failing request
+    fut_bad = small.submit([(px[:5], (1, 4, 4))])
+    fut_ok = small.submit([(px, (6, 4, 4))])
+    with pytest.raises(ValueError):
+        fut_bad.result(60)
+    assert torch.allclose(fut_ok.result(60)[0][0], rows, atol=1e-6)
+    small.close()
+
+
+# ------------------------------------------------------------------ through the engine
+def _engine(max_tokens_per_step=None, pages=64):
+    from cubic_serve_b200.executor.eager_executor import EagerPagedExecutor
+    from cubic_serve_b200.models.config import ModelConfig
+    from cubic_serve_b200.models.reference import random_dense_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SchedulerConfig
+    from dataclasses import replace
+    cfg = replace(ModelConfig(), mrope_section=(16, 8, 8), vocab_size=1024)
+    ex = EagerPagedExecutor(cfg, random_dense_weights(cfg, 0, std=0.2), pages)
+    sc = SchedulerConfig() if max_tokens_per_step is None else SchedulerConfig(prefill_chunk_tokens=max_tokens_per_step)
+    return LLMEngine(ex, pages, sc), cfg
+
+
+def _mm(prompt_len, first, feats, digest, grid):
+    from cubic_serve_b200.runtime.multimodal import MultimodalInput
+    pos, delta = mrope_positions([0] * prompt_len, [(first, feats.shape[0], grid)], 2)
+    return MultimodalInput([(first, feats, digest)], np.asarray(pos), delta)
+
+
+def _run(eng, prompt, mm, n=6):
+    from cubic_serve_b200.runtime.scheduler import SamplingParams
+    rid = eng.add_request(prompt, SamplingParams(max_tokens=n), multimodal=mm)
+    toks = []
+    while eng.has_unfinished:
+        toks += [o.token_id for o in eng.step() if o.request_id == rid and o.token_id is not None]
+    return toks
+
+
+def test_engine_serves_feature_rows():
+    prompt = [5, 6, 7] + [900] * 24 + list(range(20, 43))          # 50 tokens, 24 placeholder rows at 3
+    g = torch.Generator().manual_seed(1)
+    fa, fb = torch.randn(24, 256, generator=g), torch.randn(24, 256, generator=g)
+    grid = (1, 8, 12)
+    eng, _ = _engine()
+    a1 = _run(eng, prompt, _mm(50, 3, fa, b"A", grid))
+    hits0 = eng.prefix.hit_tokens
+    a2 = _run(eng, prompt, _mm(50, 3, fa, b"A", grid))             # same media: resumed from cached pages
+    assert eng.prefix.hit_tokens > hits0 and a2 == a1
+    hits1 = eng.prefix.hit_tokens
+    b1 = _run(eng, prompt, _mm(50, 3, fb, b"B", grid))             # other media: nothing of the span is shared
+    assert eng.prefix.hit_tokens == hits1
+    cold, _ = _engine()
+    assert _run(cold, prompt, _mm(50, 3, fb, b"B", grid)) == b1
+    assert b1 != a1
+    # chunked prefill cuts the media span; the tokens do not change
+    chunked, _ = _engine(max_tokens_per_step=16)
+    assert _run(chunked, prompt, _mm(50, 3, fa, b"A", grid)) == a1
+    # the positions matter: the same rows under another grid give another continuation
+    other = _run(_engine()[0], prompt, _mm(50, 3, fa, b"A", (1, 4, 24)))
+    assert other != a1
+
+
+def test_text_only_executor_refuses_media():
+    from cubic_serve_b200.runtime.scheduler import AdmissionError
+    eng, _ = _engine()
+    eng.executor.accepts_features = False
+    with pytest.raises(AdmissionError):
+        eng.add_request([1, 2, 3], multimodal=_mm(3, 0, torch.zeros(1, 256), b"x", (1, 2, 2)))
+    eng2, _ = _engine()
+    with pytest.raises(AdmissionError):
+        eng2.add_request([1, 2], multimodal=_mm(3, 0, torch.zeros(1, 256), b"x", (1, 2, 2)))
+
+
+def test_chat_processor_expands_media_parts():
+    from cubic_serve_b200.contracts.request import CanonicalChatRequest, ContentPart, Message, RequestError, Role
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    from cubic_serve_b200.inputs.multimodal import MultimodalChatProcessor, VisionTokens
+
+    class Tok(ByteTokenizer):
+        SPECIALS = ByteTokenizer.SPECIALS + ("<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+    tok = Tok()
+    ids = tok.special_ids
+    vt = VisionTokens(ids["<|image_pad|>"], ids["<|video_pad|>"], ids["<|vision_start|>"], ids["<|vision_end|>"])
+    cfg = _cfg()
+    svc = VisionService(VisionEncoder(cfg, random_vision_weights(cfg, 7)))
+    proc = MultimodalChatProcessor(tok, svc, vt, PatchGeometry(4, 2, 2, min_pixels=8 * 8, max_pixels=32 * 32))
+    url = "data:image/png;base64," + base64.b64encode(_png(24, 40)).decode()
+    msg = Message(Role.USER, (ContentPart("text", "look: "), ContentPart("image", media_url=url), ContentPart("text", " what?")))
+    kw = {"protocol": "openai", "model": "m", "messages": (msg,), "request_id": "r1"}
+    req = CanonicalChatRequest(**kw)
+    out = proc.build(req)
+    mm = out.multimodal
+    assert mm is not None and len(mm.spans) == 1
+    first, rows, digest = mm.spans[0]
+    assert rows.shape[1] == 32 and out.token_ids[first - 1] == vt.start and out.token_ids[first + rows.shape[0]] == vt.end
+    assert all(t == vt.image for t in out.token_ids[first:first + rows.shape[0]])
+    assert mm.positions.shape == (3, len(out.token_ids))
+    assert mm.delta < 0 or rows.shape[0] == 1
+    keys = mm.key_tokens(out.token_ids)
+    assert all(k < 0 for k in keys[first:first + rows.shape[0]]) and keys[:first] == out.token_ids[:first]
+    again = proc.build(req)
+    assert svc.store.hits == 1 and again.multimodal.spans[0][2] == digest
+    # text-only requests go through unchanged
+    plain = proc.build(CanonicalChatRequest(**{**kw, "messages": (Message(Role.USER, (ContentPart("text", "hi"),)),)}))
+    assert plain.multimodal is None
+    bad = Message(Role.USER, (ContentPart("image", media_url="data:image/png;base64,AAAA"),))
+    with pytest.raises(RequestError):
+        proc.build(CanonicalChatRequest(**{**kw, "messages": (bad,)}))
+    vid = Message(Role.USER, (ContentPart("video", media_url="data:video/mp4;base64,AAAAGGZ0eXBtcDQy"),))
+    with pytest.raises(RequestError):
+        proc.build(CanonicalChatRequest(**{**kw, "messages": (vid,)}))
+
+
+def test_multimodal_checkpoint_is_admitted_and_served(tmp_path):
+    """A checkpoint with the decoder nested under ``model.language_model.`` and a vision tower: the closed inventory
+    owns the tower's tensors, and the serving builder yields a processor whose output the eager engine serves."""
+    import json
+    from argparse import Namespace
+    from dataclasses import replace
+
+    from safetensors.torch import load_file, save_file
+
+    from cubic_serve_b200.contracts.request import CanonicalChatRequest, ContentPart, Message, Role
+    from cubic_serve_b200.executor.eager_executor import EagerPagedExecutor
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    from cubic_serve_b200.models import checkpoint as C
+    from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+    from cubic_serve_b200.models.reference import dense_weights_from_checkpoint
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.serving import build_media_processor
+    base = replace(ModelConfig(), qk_norm=True, name="Qwen3ForCausalLM", quant=QuantSpec("none", 16, 0))
+    path = C.write_random_checkpoint(tmp_path / "mm", base, seed=2, std=0.1)
+    t = load_file(str(path / "model.safetensors"))
+    nested = {("model.language_model." + n[len("model."):] if n.startswith("model.") else n): v for n, v in t.items()}
+    vcfg = _cfg(out_hidden_size=base.hidden_size)
+    nested.update({"model.visual." + n: v.to(torch.bfloat16) for n, v in random_vision_weights(vcfg, 9).items()})
+    save_file(nested, str(path / "model.safetensors"))
+    raw = json.loads((path / "config.json").read_text())
+    text = {k: v for k, v in raw.items() if k not in ("architectures",)}
+    text["rope_parameters"] = {"mrope_section": [16, 8, 8], "rope_theta": raw.get("rope_theta", 10000.0)}
+    doc = {"architectures": raw["architectures"], "text_config": text, "image_token_id": 261, "video_token_id": 262,
+           "vision_start_token_id": 259, "vision_end_token_id": 260,
+           "vision_config": {**RAW, "out_hidden_size": base.hidden_size, "model_type": "x"}}
+    if "quantization_config" in raw:
+        doc["quantization_config"] = raw["quantization_config"]
+    (path / "config.json").write_text(json.dumps(doc))
+    ck = C.admit_checkpoint(path)
+    assert ck.vision is not None and ck.vision_prefix == "model.visual." and ck.cfg.mrope_section == (16, 8, 8)
+    vw = C.load_vision_weights(ck, dtype=torch.float32)
+    assert vw["pos_embed.weight"].shape == (64, 64)
+    # a missing tower tensor is refused like any other
+    broken = dict(nested)
+    del broken["model.visual.merger.norm.bias"]
+    save_file(broken, str(path / "model.safetensors"))
+    with pytest.raises(C.CheckpointError, match="missing tensor"):
+        C.admit_checkpoint(path)
+    save_file(nested, str(path / "model.safetensors"))
+
+    class Tok(ByteTokenizer):
+        SPECIALS = ByteTokenizer.SPECIALS + ("<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+    tok = Tok()
+    assert (tok.special_ids["<|image_pad|>"], tok.special_ids["<|vision_start|>"]) == (261, 259)
+    ex = EagerPagedExecutor(ck.cfg, dense_weights_from_checkpoint(ck), 64)
+    args = Namespace(thinking=None, encoder_memory_gib=0.25, feature_store_mib=4)
+    proc = build_media_processor(args, ck, tok, ex, 512)
+    proc.geometry = replace(proc.geometry, min_pixels=8 * 8, max_pixels=32 * 32)
+    url = "data:image/png;base64," + base64.b64encode(_png(24, 40)).decode()
+    msg = Message(Role.USER, (ContentPart("text", "see "), ContentPart("image", media_url=url)))
+    out = proc.build(CanonicalChatRequest("openai", "m", (msg,), request_id="r"))
+    eng = LLMEngine(ex, 64)
+    toks = _run(eng, out.token_ids, out.multimodal, n=4)
+    assert len(toks) == 4
+    ex.accepts_features = False
+    assert build_media_processor(args, ck, tok, ex, 512) is None
