@@ -19,6 +19,24 @@ from .gpu_executor import Segment
 PAGE = 16
 
 
+def sample_row(logits: torch.Tensor, s: Segment) -> int:
+    """The sampled token of one row of fp32 logits under the segment's mask and sampling parameters."""
+    if getattr(s, "mask", None) is not None:                  # structured output: disallowed tokens cannot win
+        bits = np.unpackbits(np.asarray(s.mask, dtype=np.uint32).view(np.uint8), bitorder="little")
+        allowed = torch.from_numpy(bits[:logits.numel()].astype(bool))
+        logits = logits.masked_fill(~allowed, float("-inf"))
+    if s.temperature <= 0:
+        return int(logits.argmax())
+    k = s.top_k if 0 < s.top_k <= 20 else 20
+    vals, idx = logits.topk(k)
+    p = torch.softmax(vals / s.temperature, -1)
+    if s.top_p < 1:
+        keep = int((p.cumsum(0) < s.top_p).sum()) + 1
+        p = p[:keep] / p[:keep].sum()
+    g = torch.Generator().manual_seed((s.seed * 1000003 + s.draw) & 0x7FFFFFFF)
+    return int(idx[torch.multinomial(p, 1, generator=g)])
+
+
 class EagerPagedExecutor:
     accepts_features = True          # segments may carry encoder feature rows and three-axis positions
 
@@ -42,23 +60,8 @@ class EagerPagedExecutor:
         out = []
         for s in segs:
             logits = self._run_segment(s)
-            if not s.sample:
-                continue
-            if getattr(s, "mask", None) is not None:              # structured output: disallowed tokens cannot win
-                bits = np.unpackbits(np.asarray(s.mask, dtype=np.uint32).view(np.uint8), bitorder="little")
-                allowed = torch.from_numpy(bits[:logits.numel()].astype(bool))
-                logits = logits.masked_fill(~allowed, float("-inf"))
-            if s.temperature <= 0:
-                out.append(int(logits.argmax()))
-            else:
-                k = s.top_k if 0 < s.top_k <= 20 else 20
-                vals, idx = logits.topk(k)
-                p = torch.softmax(vals / s.temperature, -1)
-                if s.top_p < 1:
-                    keep = int((p.cumsum(0) < s.top_p).sum()) + 1
-                    p = p[:keep] / p[:keep].sum()
-                g = torch.Generator().manual_seed((s.seed * 1000003 + s.draw) & 0x7FFFFFFF)
-                out.append(int(idx[torch.multinomial(p, 1, generator=g)]))
+            if s.sample:
+                out.append(sample_row(logits, s))
         return np.asarray(out, dtype=np.int32)
 
     def _run_segment(self, s: Segment) -> torch.Tensor:

@@ -211,3 +211,11 @@ NAMED_CONFIGS = {
     "hybrid-8b": hybrid_8b_config,
     "moe-235b-a22b": moe_235b_config,
 }
+
+
+def _qwen4_exp_tiny():
+    from .qwen4_exp import tiny_config
+    return tiny_config()
+
+
+NAMED_CONFIGS["qwen4-exp-tiny"] = _qwen4_exp_tiny          # served by the eager executor of ``models/qwen4_exp.py``

@@ -70,6 +70,28 @@ def _builtin() -> None:
     register(ModelDefinition("qwen3_5_moe", ("Qwen3_5MoeForCausalLM",),
                              description="hybrid decoder with routed experts", **common))
 
+    def parse_q4(path: Path):
+        from .qwen4_exp import parse_qwen4_exp_config_json
+        p = Path(path)
+        return parse_qwen4_exp_config_json((p / "config.json" if p.is_dir() else p).read_bytes())
+
+    def random_q4(cfg, device="cpu", seed=0, *a, **kw):
+        from .qwen4_exp import random_qwen4_exp_weights
+        return random_qwen4_exp_weights(cfg, seed)
+
+    def load_q4(ck, device="cpu", *a, **kw):
+        from .qwen4_exp import qwen4_exp_tensor_shapes
+        return {n: ck.store.get(n) for n in qwen4_exp_tensor_shapes(ck.cfg)}
+
+    def runner_q4(cfg, weights, **kw):
+        from .qwen4_exp import Qwen4ExpEagerExecutor
+        return Qwen4ExpEagerExecutor(cfg, weights)
+
+    register(ModelDefinition("qwen4_exp", ("Qwen4ExpForConditionalGeneration", "Qwen4ExpForCausalLM"),
+                             parse_config=parse_q4, random_weights=random_q4, load_weights=load_q4, build_runner=runner_q4,
+                             description="multi-stream residual decoder: Gated DeltaNet and block-selective attention "
+                                         "layers, n-gram lexical embeddings, routed experts (eager executor)"))
+
 
 def get(family: str) -> ModelDefinition:
     _builtin()

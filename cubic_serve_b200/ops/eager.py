@@ -195,11 +195,11 @@ def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, bias:
 
 def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
               norm_w: torch.Tensor, state: torch.Tensor | None, hk: int, hv: int, eps_norm: float = 1e-6,
-              eps_l2: float = 1e-6):
+              eps_l2: float = 1e-6, d: int = 128, gate: str = "silu"):
     """Gated delta rule + gated RMSNorm over ONE request's rows (fp32 recurrence; reference oracle:
-    ``ops/eager/hybrid.py:340-548``).  ``state[Hv, 128, 128]`` fp32 or None.  Returns ``(out[n, Hv 128] bf16, state)``."""
+    ``ops/eager/hybrid.py:340-548``).  ``state[Hv, d, d]`` fp32 or None; ``gate``: activation of the output gate
+    (``silu`` or ``sigmoid``).  Returns ``(out[n, Hv d] bf16, state)``."""
     n = qkv.shape[0]
-    d = 128
     bf = torch.bfloat16
     q = qkv[:, :hk * d].float().cpu().view(n, hk, d)
     k = qkv[:, hk * d:2 * hk * d].float().cpu().view(n, hk, d)
@@ -221,5 +221,6 @@ def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch
         S = S + delta[:, :, None] * kn[:, None, :]
         o = (S * qn[:, None, :]).sum(-1).to(bf).float()
         normed = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps_norm)).to(bf).float()
-        out[t] = normed * norm_w.float().cpu()[None, :] * (zz[t] / (1 + torch.exp(-zz[t])))
+        act = 1 / (1 + torch.exp(-zz[t]))
+        out[t] = normed * norm_w.float().cpu()[None, :] * (act if gate == "sigmoid" else zz[t] * act)
     return out.reshape(n, hv * d).to(bf), S

@@ -87,6 +87,10 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
     if model.startswith("random:"):
         cfg = NAMED_CONFIGS[model.split(":", 1)[1]]()
         ck = None
+        if getattr(cfg, "family", "") == "qwen4_exp":
+            return _build_qwen4_exp_backend(args, cfg, None)
+    elif _model_type_of(model) == "qwen4_exp":
+        return _build_qwen4_exp_backend(args, None, model)
     elif model.endswith(".gguf"):
         import gguf
 
@@ -193,6 +197,50 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         processor = build_media_processor(args, ck, tok, executor, max_len)
     backend = TokenChatBackend(engine, tok, default_thinking=args.thinking, processor=processor)
     return backend, (args.served_model_name or cfg.name)
+
+
+def _model_type_of(model: str) -> str | None:
+    import json
+    from pathlib import Path
+    p = Path(model) / "config.json"
+    try:
+        return json.loads(p.read_text()).get("model_type") if p.is_file() else None
+    except (OSError, ValueError):
+        return None
+
+
+def _build_qwen4_exp_backend(args, cfg, path):
+    """The qwen4_exp family is served by its eager executor (explicit per-request state, no prefix sharing)."""
+    from ..models.qwen4_exp import Qwen4ExpEagerExecutor, admit_qwen4_exp_checkpoint, random_qwen4_exp_weights
+    from ..runtime.async_engine import TokenChatBackend
+    from ..runtime.engine import LLMEngine
+    from ..runtime.scheduler import SchedulerConfig
+    if args.execution_mode == "cuda":
+        log.warning("the qwen4_exp family runs on the eager executor; --execution-mode cuda has no native runner for it")
+    store = None
+    if path is not None:
+        cfg, weights, store = admit_qwen4_exp_checkpoint(path)
+    else:
+        weights = random_qwen4_exp_weights(cfg, args.seed)
+    max_len = args.max_model_len or min(cfg.max_position, 8192)
+    sched = SchedulerConfig(max_running_requests=args.max_running_requests, max_batched_tokens=args.token_budget,
+                            prefill_chunk_tokens=min(args.prefill_chunk_tokens, args.token_budget), max_model_len=max_len,
+                            enable_prefix_cache=False)
+    executor = Qwen4ExpEagerExecutor(cfg, weights)
+    tok = _tokenizer_for(path or "random:qwen4-exp-tiny", cfg.vocab_size)
+    engine = LLMEngine(executor, num_pages=max(4096, args.max_running_requests * (max_len // 16 + 1)), scheduler_config=sched,
+                       eos_token_id=getattr(tok, "eos_token_id", None))
+    processor = None
+    if store is not None and cfg.vision is not None:
+        import json
+        from pathlib import Path
+        from types import SimpleNamespace
+        # the same builder as for the other multimodal checkpoints: tower, feature store, media policy
+        ck = SimpleNamespace(vision=cfg.vision, vision_prefix="model.visual.", store=store, cfg=cfg,
+                             raw_config=json.loads((Path(path) / "config.json").read_text()))
+        processor = build_media_processor(args, ck, tok, executor, max_len)
+    return (TokenChatBackend(engine, tok, default_thinking=args.thinking, processor=processor),
+            (args.served_model_name or cfg.name))
 
 
 def build_media_processor(args, ck, tok, executor, max_len: int):
