@@ -103,6 +103,15 @@ class ParallelTopology:
         e = self.placements[rank].expert_rank
         return e * per, (e + 1) * per
 
+    def expert_feature_slice(self, rank: int, intermediate: int) -> tuple[int, int]:
+        """Intermediate features ``[lo, hi)`` of every owned expert that the rank's lane holds (the lanes of one expert
+        owner divide each expert's gate / up rows and down columns)."""
+        if intermediate % self.etp:
+            raise ValueError("expert features must divide evenly over the expert-tensor lanes")
+        per = intermediate // self.etp
+        lane = self.placements[rank].expert_tensor_rank
+        return lane * per, (lane + 1) * per
+
     def layer_range(self, stage: int, num_layers: int) -> tuple[int, int]:
         per = -(-num_layers // self.pp)
         return stage * per, min(num_layers, (stage + 1) * per)

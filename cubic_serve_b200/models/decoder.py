@@ -123,8 +123,11 @@ def quantize_linear(w: torch.Tensor, cfg: ModelConfig, amax: float | None = None
 
 
 def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                           std: float = 0.02, layer_range: tuple[int, int] | None = None) -> DecoderWeights:
+                           std: float = 0.02, layer_range: tuple[int, int] | None = None,
+                           ep_size: int | None = None) -> DecoderWeights:
     """Random-init N(0, std) weights, quantized offline into the config's format, rank-local TP shards.
+    ``ep_size`` (mixture-of-experts models): expert owners among the ``tp_size`` ranks; the ``tp_size / ep_size`` lanes
+    of an owner divide every owned expert's intermediate features (None: every rank owns whole experts).
 
     Column-parallel: QKV (whole heads per rank), gate/up; row-parallel: o_proj,
     down; vocab-sharded embedding and lm_head (reference ownership planners:
@@ -219,7 +222,8 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             lw.k_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
         if cfg.is_moe:
             from .moe import random_moe_weights
-            lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std, layer_seed=seed * 4096000 + li)
+            lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std, layer_seed=seed * 4096000 + li,
+                                        ep_size=ep_size)
         else:
             lw.gate_up = shard_q(rnd(2 * inter * tp_size, H), lambda f: sections(f, [inter, inter]))
             lw.down = shard_q(rnd(H, inter * tp_size), cols_of(inter))
@@ -347,6 +351,9 @@ class DecoderRunner:
         self.ep = None
         if cfg.is_moe and tp is not None and tp.fused is not None:
             # expert parallelism over the tensor-parallel group: fused dispatch / combine on the row-sharded stream
+            if any(lw.moe is not None and lw.moe.expert_count * self.tp_size != cfg.num_experts for lw in weights.layers):
+                raise ValueError("experts divided into feature lanes use the NCCL tensor-parallel collectives "
+                                 "(tp mode 'nccl'): the fused dispatch moves rows to owners of WHOLE experts")
             from ..parallel.ep import FusedEp, symmetric_ep_buffers
             bufs = symmetric_ep_buffers(tp.group, H, cfg.experts_per_token, tp.fused.b.max_tokens, dev)
             self.ep = FusedEp(bufs, dev, cfg.num_experts, 2 * cfg.moe_intermediate_size, ws=self.ws)

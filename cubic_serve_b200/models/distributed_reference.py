@@ -71,17 +71,23 @@ def shard_dense_weights(w: DenseWeights, cfg: ModelConfig, part: RankPartition) 
 
 
 def moe_expert_parallel_reference(x: torch.Tensor, router: torch.Tensor, gate_up: list[torch.Tensor],
-                                  down: list[torch.Tensor], top_k: int, group, normalize: bool = True) -> torch.Tensor:
+                                  down: list[torch.Tensor], top_k: int, group, normalize: bool = True,
+                                  ep_size: int | None = None) -> torch.Tensor:
     """Eager expert-parallel mixture-of-experts block: every rank of ``group`` routes ALL tokens with the replicated
-    router, computes only the experts it owns (contiguous expert ids in rank order; ``gate_up`` / ``down`` hold this
-    rank's experts) and the partial outputs are summed in rank order.  Equals the single-process ``moe_reference`` over
-    all experts up to fp32 summation order.  Reference counterpart: ``models/qwen3_5_moe/distributed.py`` there."""
-    from .moe import moe_reference
+    router, computes only the experts it owns (contiguous expert ids in owner order; ``gate_up`` / ``down`` hold this
+    rank's experts) and the partial outputs are summed in rank order.  With ``ep_size`` smaller than the group, the
+    group is ``ep_size`` owners times lanes: the lanes of an owner hold the same experts, ``gate_up`` / ``down`` then
+    carry this lane's share of every expert's intermediate features (gate rows, up rows; down columns), and the same
+    sum over all ranks completes both the experts and their features.  Equals the single-process ``moe_reference``
+    over all experts up to summation order and the rounding of the per-expert output (each lane rounds its partial).
+    Reference counterpart: ``models/qwen3_5_moe/distributed.py`` and ``contracts/execution.py:238-248`` there."""
+    from .moe import expert_coordinates, moe_reference
     rank, size = dist.get_rank(group), dist.get_world_size(group)
-    total = router.shape[0]
-    if total % size or len(gate_up) != total // size or len(down) != len(gate_up):
-        raise ValueError("every rank owns num_experts / group size experts")
-    partial = moe_reference(x, router, gate_up, down, top_k, normalize, expert_lo=rank * (total // size))
+    owner, _lane, lanes = expert_coordinates(rank, size, ep_size)
+    total, owners = router.shape[0], size // lanes
+    if total % owners or len(gate_up) != total // owners or len(down) != len(gate_up):
+        raise ValueError("every owner holds num_experts / owners experts")
+    partial = moe_reference(x, router, gate_up, down, top_k, normalize, expert_lo=owner * (total // owners))
     return tp_all_reduce(partial, group)
 
 

@@ -96,24 +96,46 @@ class MoeLayer:
         return K.moe_combine(sc.y, sc, t, self.out[:t] if out is None else out, residual)
 
 
+def expert_coordinates(tp_rank: int, tp_size: int, ep_size: int | None) -> tuple[int, int, int]:
+    """``(expert owner, lane, lanes)`` of a tensor rank: the ``tp_size`` ranks of a stage are ``ep_size`` expert owners
+    times ``tp_size / ep_size`` lanes; the lanes of one owner hold the same experts and divide every expert's
+    intermediate features among them (reference: ``contracts/execution.py:238-248``).  ``ep_size`` None = ``tp_size``
+    (every rank owns whole experts)."""
+    ep = tp_size if ep_size is None else ep_size
+    if ep < 1 or tp_size % ep:
+        raise ValueError("the expert-parallel size divides the tensor-parallel size")
+    lanes = tp_size // ep
+    return tp_rank // lanes, tp_rank % lanes, lanes
+
+
 def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size: int = 1, std: float = 0.02,
-                       layer_seed: int = 0) -> MoeLayer:
-    """Random experts for EP = tp_size (contiguous expert-id slices per rank), router replicated.  Expert ``e`` of a
-    layer draws from a generator seeded by (layer, e) only, so every partition holds slices of the same model."""
+                       layer_seed: int = 0, ep_size: int | None = None) -> MoeLayer:
+    """Random experts, router replicated.  Rank ``(owner, lane)`` holds the contiguous expert ids of its owner and, of
+    each, the gate / up rows and down columns of its lane (``ep_size`` None: whole experts, one owner per rank).
+    Expert ``e`` of a layer draws from a generator seeded by (layer, e) only, so every partition holds slices of the
+    same model."""
     from .decoder import quantize_linear
     H, I, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
-    local = E // tp_size
+    owner, lane, lanes = expert_coordinates(tp_rank, tp_size, ep_size)
+    if E % (tp_size // lanes) or I % lanes or (I // lanes) % 128:
+        raise ValueError("experts divide over the owners and every lane keeps whole 128-feature groups of an expert")
+    local, il = E // (tp_size // lanes), I // lanes
     shared = torch.Generator(device=device).manual_seed(12345 + layer_seed)
     router = (torch.randn(E, H, device=device, generator=shared) * std).to(torch.bfloat16)
     gus, downs = [], []
-    for e in range(tp_rank * local, (tp_rank + 1) * local):
+    for e in range(owner * local, (owner + 1) * local):
         gen.manual_seed(layer_seed * 1024 + e + 1)
-        gus.append(quantize_linear(torch.randn(2 * I, H, device=device, generator=gen) * std, cfg))
-        downs.append(quantize_linear(torch.randn(H, I, device=device, generator=gen) * std, cfg))
+        gu_full = torch.randn(2 * I, H, device=device, generator=gen) * std
+        dn_full = torch.randn(H, I, device=device, generator=gen) * std
+        if lanes > 1:
+            gu_full = torch.cat([gu_full[lane * il:(lane + 1) * il], gu_full[I + lane * il:I + (lane + 1) * il]])
+            dn_full = dn_full[:, lane * il:(lane + 1) * il].contiguous()
+        gus.append(quantize_linear(gu_full, cfg))
+        downs.append(quantize_linear(dn_full, cfg))
     gu, gcs, gms = stack_experts(gus)
     dn, dcs, dms = stack_experts(downs)
     return MoeLayer(wq_pack.pack_bf16(router), gu, dn, (gcs, gms, dcs, dms), E, cfg.experts_per_token,
-                    tp_rank * local, local, cfg.norm_topk_prob)
+                    owner * local, local, cfg.norm_topk_prob)
 
 
 def load_moe_layer(ck, layer: int, device, tp_rank: int = 0, tp_size: int = 1) -> MoeLayer:

@@ -77,10 +77,10 @@ def _summary(errs, bound: float) -> dict:
 
 
 def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int = 48, k_bits: int = 8, v_bits: int = 8,
-              tp1_layers: int = 0, seed: int = 0) -> dict:
+              tp1_layers: int = 0, seed: int = 0, ep_size: int | None = None) -> dict:
     """Compare fused vs NCCL (on ``cfg`` with ``weights``, this rank's shard) and, when ``tp1_layers`` > 0, both against
     one GPU holding a ``tp1_layers``-layer version of the model.  Collective over ``group``; every rank returns the
-    same dictionary."""
+    same dictionary.  ``ep_size`` below the group's size divides every expert's features over lanes (NCCL mode only)."""
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -96,7 +96,7 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
     def both_modes(c, w):
         out = {}
         for mode in ("nccl", "fused"):
-            if (c.is_hybrid or c.quant.method == "fp8") and mode == "fused":
+            if (c.is_hybrid or c.quant.method == "fp8" or (ep_size or size) != size) and mode == "fused":
                 continue          # these run with the NCCL collectives (see DecoderRunner)
             tp = TensorParallel(group, dev, mode=mode, hidden=c.hidden_size, max_tokens=T, rows_max=max(requests, 16))
             out[mode] = _step_logits(c, w, dev, tp, prompts, k_bits, v_bits)
@@ -106,7 +106,7 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
         return out
 
     if weights is None:
-        weights = random_decoder_weights(cfg, dev, seed=seed, tp_rank=rank, tp_size=size)
+        weights = random_decoder_weights(cfg, dev, seed=seed, tp_rank=rank, tp_size=size, ep_size=ep_size)
     res = both_modes(cfg, weights)
     report: dict = {"ranks": size, "model": cfg.name, "layers": cfg.num_layers, "rows": requests, "prompt_len": prompt_len,
                     "nvls": os.environ.get("CUBIC_SERVE_NVLS", "gather")}
@@ -132,7 +132,7 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
         report["ranks_agree"] = bool(all(torch.equal(p, parts[0]) for p in parts))
     if tp1_layers > 0:
         small = replace(cfg, num_layers=min(tp1_layers, cfg.num_layers))
-        ws = random_decoder_weights(small, dev, seed=seed, tp_rank=rank, tp_size=size)
+        ws = random_decoder_weights(small, dev, seed=seed, tp_rank=rank, tp_size=size, ep_size=ep_size)
         part = both_modes(small, ws)
         del ws
         bound1 = per_op * (2 * small.num_layers) ** 0.5
@@ -166,6 +166,9 @@ def main(argv=None) -> None:
     ap.add_argument("--experts", type=int, default=0, help="MoE: number of experts (0 = the config's own)")
     ap.add_argument("--kv-heads", type=int, default=0,
                     help="override the key/value head count (fewer heads than ranks: ranks share copies of a head)")
+    ap.add_argument("--ep", type=int, default=0,
+                    help="MoE: expert owners among the ranks (0 = every rank owns whole experts); the ranks of an owner "
+                         "divide each expert's intermediate features")
     ap.add_argument("--requests", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=48)
     ap.add_argument("--kv", default="8,8")
@@ -187,7 +190,7 @@ def main(argv=None) -> None:
         cfg = replace(cfg, num_kv_heads=args.kv_heads)
     kb, vb = (int(b) for b in args.kv.split(","))
     report = run_check(cfg, dev, dist.group.WORLD, requests=args.requests, prompt_len=args.prompt_len, k_bits=kb, v_bits=vb,
-                       tp1_layers=cfg.num_layers)
+                       tp1_layers=cfg.num_layers, ep_size=args.ep or None)
     if rank == 0:
         print(json.dumps(report), flush=True)
     torch.cuda.synchronize(dev)

@@ -120,3 +120,91 @@ def test_expert_parallel_reference_equals_the_single_process_block():
     want = moe_reference(x, router, gate_up, down, 2)
     assert torch.equal(got[0], got[1])                      # rank-ordered sum: the same bits on every rank
     assert float((got[0] - want).norm() / want.norm()) < 1e-5
+
+
+def _moe_etp_rank(rank, world, port, q):
+    import torch.distributed as dist
+    from cubic_serve_b200.models.distributed_reference import moe_expert_parallel_reference
+    from cubic_serve_b200.models.moe import expert_coordinates
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(13)
+    E, H, I, T = 8, 32, 48, 9
+    router = (torch.randn(E, H, generator=g) * 0.3).to(torch.bfloat16)
+    gate_up = [(torch.randn(2 * I, H, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    down = [(torch.randn(H, I, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    owner, lane, lanes = expert_coordinates(rank, world, 2)          # 2 owners x 2 lanes
+    per, il = E // 2, I // lanes
+    mine = range(owner * per, (owner + 1) * per)
+    gu = [torch.cat([gate_up[e][lane * il:(lane + 1) * il], gate_up[e][I + lane * il:I + (lane + 1) * il]]) for e in mine]
+    dn = [down[e][:, lane * il:(lane + 1) * il] for e in mine]
+    y = moe_expert_parallel_reference(x, router, gu, dn, 2, dist.group.WORLD, ep_size=2)
+    q.put((rank, y))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_tensor_lanes_complete_the_experts():
+    """Two expert owners times two lanes: every lane holds half of each owned expert's features; the sum over the four
+    ranks is the whole block (each lane rounds its partial expert output to bf16, hence the tolerance)."""
+    from cubic_serve_b200.contracts.execution import ParallelTopology
+    from cubic_serve_b200.models.moe import expert_coordinates, moe_reference
+    world = 4
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_moe_etp_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    g = torch.Generator().manual_seed(13)
+    E, H, I, T = 8, 32, 48, 9
+    router = (torch.randn(E, H, generator=g) * 0.3).to(torch.bfloat16)
+    gate_up = [(torch.randn(2 * I, H, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    down = [(torch.randn(H, I, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    want = moe_reference(x, router, gate_up, down, 2)
+    assert all(torch.equal(got[0], got[r]) for r in range(1, world))
+    assert float((got[0] - want).norm() / want.norm()) < 5e-3
+    topo = ParallelTopology.single_node(range(4), tp=4, ep=2)
+    for r in range(4):
+        owner, lane, lanes = expert_coordinates(r, 4, 2)
+        assert (topo.placement(r).expert_rank, topo.placement(r).expert_tensor_rank, topo.etp) == (owner, lane, lanes)
+        assert topo.expert_slice(r, 8) == (owner * 4, owner * 4 + 4)
+        assert topo.expert_feature_slice(r, 48) == (lane * 24, lane * 24 + 24)
+    with pytest.raises(ValueError):
+        expert_coordinates(0, 4, 3)
+
+
+def test_random_expert_shards_with_lanes_are_slices_of_one_model():
+    from dataclasses import replace
+
+    from cubic_serve_b200.models.config import ModelConfig, QuantSpec
+    from cubic_serve_b200.models.moe import moe_reference, random_moe_weights
+    from cubic_serve_b200.ops import wq_pack
+    cfg = replace(ModelConfig(), family="gqa_moe", hidden_size=128, num_experts=4, experts_per_token=2,
+                  moe_intermediate_size=256, quant=QuantSpec("none", 16, 0))
+    gen = torch.Generator()
+    x = (torch.randn(6, 128, generator=torch.Generator().manual_seed(1))).to(torch.bfloat16)
+
+    def dense(layer):
+        gu = wq_pack.unpack_to_dense(layer.gate_up)
+        dn = wq_pack.unpack_to_dense(layer.down)
+        return (layer.router, list(gu.view(layer.expert_count, -1, gu.shape[-1])),
+                list(dn.view(layer.expert_count, -1, dn.shape[-1])))
+    whole = random_moe_weights(cfg, "cpu", gen, 0, 1, std=0.1, layer_seed=5)
+    r, gu, dn = dense(whole)
+    want = moe_reference(x, wq_pack.unpack_to_dense(r), gu, dn, 2)
+    total = torch.zeros_like(want)
+    for rank in range(4):                                               # 2 owners x 2 lanes
+        part = random_moe_weights(cfg, "cpu", gen, rank, 4, std=0.1, layer_seed=5, ep_size=2)
+        assert part.expert_count == 2 and part.expert_lo == (rank // 2) * 2 and part.gate_up.n == 256
+        r, gu, dn = dense(part)
+        total += moe_reference(x, wq_pack.unpack_to_dense(r), gu, dn, 2, expert_lo=part.expert_lo)
+    assert float((total - want).norm() / want.norm()) < 5e-3
+    with pytest.raises(ValueError):
+        random_moe_weights(cfg, "cpu", gen, 0, 4, ep_size=1)            # 64-feature lanes: not whole groups
