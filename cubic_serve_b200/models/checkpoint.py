@@ -119,8 +119,16 @@ def logical_inventory(cfg: ModelConfig) -> tuple[dict[str, tuple[int, int]], lis
             linears[m["k"]] = (cfg.kv_size, H)
             linears[m["v"]] = (cfg.kv_size, H)
             linears[m["o"]] = (H, cfg.q_size)
+            if cfg.qkv_bias:
+                plain += [f"{m[k]}.bias" for k in ("q", "k", "v")]
         if cfg.is_moe:
             plain.append(f"model.layers.{i}.mlp.gate.weight")
+            if cfg.shared_intermediate_size:
+                sp = f"model.layers.{i}.mlp.shared_expert"
+                linears[f"{sp}.gate_proj"] = (cfg.shared_intermediate_size, H)
+                linears[f"{sp}.up_proj"] = (cfg.shared_intermediate_size, H)
+                linears[f"{sp}.down_proj"] = (H, cfg.shared_intermediate_size)
+                plain.append(f"model.layers.{i}.mlp.shared_expert_gate.weight")
             for e in range(cfg.num_experts):
                 ep = f"model.layers.{i}.mlp.experts.{e}"
                 linears[f"{ep}.gate_proj"] = (cfg.moe_intermediate_size, H)
@@ -387,6 +395,9 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
         return _slice_rows(payload(module), method, lo, hi, n, q.bits), (hi - lo, ck_shapes[module][1])
 
     ck_shapes, _ = logical_inventory(cfg)
+    if cfg.shared_intermediate_size or cfg.qkv_bias:
+        raise CheckpointError("shared experts and projection biases are served by the eager execution mode "
+                              "(--execution-mode eager); the native runner has no kernels for them")
     layers = []
     for i in range(*(layer_range or (0, cfg.num_layers))):
         m = _layer_modules(cfg, i)
@@ -453,8 +464,10 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
                           gate_up=None if gu is None else gu.to(device), down=None if down is None else down.to(device),
                           moe=moe)
         if cfg.qk_norm and gdn is None:
-            lw.q_norm = ck.store.get(f"{p}.self_attn.q_norm.weight").to(device, bf)
-            lw.k_norm = ck.store.get(f"{p}.self_attn.k_norm.weight").to(device, bf)
+            # the kernels multiply by the vector they are given: checkpoints with zero-centred norms store w of (1 + w)
+            one = 1.0 if cfg.zero_centered_norm else 0.0
+            lw.q_norm = (ck.store.get(f"{p}.self_attn.q_norm.weight").float() + one).to(device, bf)
+            lw.k_norm = (ck.store.get(f"{p}.self_attn.k_norm.weight").float() + one).to(device, bf)
         layers.append(lw)
     embed_full = ck.store.get("model.embed_tokens.weight").to(device, bf)
     v_local = cfg.vocab_size // tp_size
@@ -535,6 +548,11 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
                                        dtype=torch.bfloat16)
         elif name.endswith("mlp.gate.weight"):
             tensors[name] = (torch.randn(cfg.num_experts, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
+        elif name.endswith("shared_expert_gate.weight"):
+            tensors[name] = (torch.randn(1, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
+        elif name.endswith("_proj.bias"):
+            rows = cfg.q_size if name.endswith("q_proj.bias") else cfg.kv_size
+            tensors[name] = (torch.randn(rows, generator=g) * std).to(torch.bfloat16)
         else:
             tensors[name] = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
     save_file(tensors, str(path / "model.safetensors"))
@@ -553,6 +571,11 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
     if cfg.is_moe:
         hf.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token,
                   moe_intermediate_size=cfg.moe_intermediate_size, norm_topk_prob=cfg.norm_topk_prob)
+        if cfg.shared_intermediate_size:
+            hf["shared_expert_intermediate_size"] = cfg.shared_intermediate_size
+    hf["qkv_bias"] = cfg.qkv_bias
+    if cfg.mrope_section is not None:
+        hf["rope_parameters"] = {"mrope_section": list(cfg.mrope_section), "rope_theta": cfg.rope_theta}
     qc = _quant_config_json(cfg.quant)
     if qc:
         hf["quantization_config"] = qc

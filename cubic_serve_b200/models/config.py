@@ -67,6 +67,10 @@ class ModelConfig:
     mtp_layers: int = 0
     quant: QuantSpec = field(default_factory=QuantSpec)
     eos_token_id: int | None = None
+    # sigmoid-gated shared expert beside the routed experts (width of its SwiGLU; 0 = none) and biases on the q / k / v
+    # projections (Qwen2 family): both are served by the eager execution mode only
+    shared_intermediate_size: int = 0
+    qkv_bias: bool = False
     # three-axis rotary positions of the multimodal checkpoints: how many frequency slots follow the (temporal, row,
     # column) axis; None = one axis
     mrope_section: tuple[int, int, int] | None = None
@@ -112,6 +116,9 @@ class ModelConfig:
         heads = text["num_attention_heads"]
         hd = text.get("head_dim") or text["hidden_size"] // heads
         n_exp = text.get("num_experts") or text.get("num_local_experts") or 0
+        rope = text.get("rope_parameters") if isinstance(text.get("rope_parameters"), dict) else {}
+        if text.get("attention_bias"):
+            raise ValueError("checkpoints with biases on all attention projections (attention_bias) are not served")
         hybrid = {}
         if text.get("linear_num_value_heads"):
             if int(text.get("linear_key_head_dim", 128)) != 128 or int(text.get("linear_value_head_dim", 128)) != 128:
@@ -119,7 +126,7 @@ class ModelConfig:
             hybrid = dict(gdn_interval=int(text.get("full_attention_interval", 4)),
                           gdn_k_heads=int(text["linear_num_key_heads"]), gdn_v_heads=int(text["linear_num_value_heads"]),
                           attn_output_gate=bool(text.get("attn_output_gate", True)), zero_centered_norm=True,
-                          rotary_dim=int(hd * float(text.get("partial_rotary_factor", 0.25))))
+                          rotary_dim=int(hd * float(rope.get("partial_rotary_factor", text.get("partial_rotary_factor", 0.25)))))
         return ModelConfig(
             **hybrid,
             name=cfg.get("_name_or_path") or arch,
@@ -131,9 +138,11 @@ class ModelConfig:
             head_dim=hd,
             intermediate_size=text.get("intermediate_size", 0),
             vocab_size=text["vocab_size"],
-            rope_theta=float(text.get("rope_theta", 10000.0)),
+            rope_theta=float(text.get("rope_theta", rope.get("rope_theta", 10000.0))),
             rms_eps=float(text.get("rms_norm_eps", 1e-6)),
             qk_norm="Qwen3" in arch,
+            shared_intermediate_size=int(text.get("shared_expert_intermediate_size") or 0) if n_exp else 0,
+            qkv_bias=bool(text.get("qkv_bias", arch.startswith("Qwen2"))),
             tie_embeddings=bool(text.get("tie_word_embeddings", False)),
             max_position=int(text.get("max_position_embeddings", 40960)),
             num_experts=n_exp,

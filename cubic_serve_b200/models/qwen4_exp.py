@@ -596,6 +596,7 @@ class Qwen4ExpEagerExecutor:
     (the state holds K / V), and there is no prefix sharing."""
 
     accepts_features = True
+    keeps_request_state = True
 
     def __init__(self, cfg: Qwen4ExpConfig, weights: Mapping[str, torch.Tensor]) -> None:
         self.cfg = cfg

@@ -41,7 +41,8 @@ class LLMEngine:
         self.executor = executor
         self.cfg = scheduler_config or SchedulerConfig()
         rows = tuple(getattr(executor, "state_checkpoint_rows", ()) or ())
-        if (getattr(getattr(executor, "cfg", None), "is_hybrid", False) or rows) and self.cfg.enable_prefix_cache:
+        if (getattr(getattr(executor, "cfg", None), "is_hybrid", False) or rows
+                or getattr(executor, "keeps_request_state", False)) and self.cfg.enable_prefix_cache:
             # recurrent (Gated DeltaNet) state: a cached prefix is resumable only with a snapshot of the state at its
             # end; executors that set rows aside for snapshots (``state_checkpoint_rows``) keep the prefix cache on
             from dataclasses import replace

@@ -112,8 +112,15 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         if gguf_weights is not None:
             raise SystemExit("eager execution mode serves checkpoint directories and random:<config> models")
         pages = 4096
-        dense = dense_weights_from_checkpoint(ck) if ck is not None else random_dense_weights(cfg, args.seed)
-        executor = EagerPagedExecutor(cfg, dense, pages, kv_bits=(k_bits, v_bits))
+        if cfg.is_moe or cfg.is_hybrid or cfg.qkv_bias:
+            # the families beyond the dense full-attention decoder (experts, shared experts, Gated DeltaNet layers,
+            # projection biases, any head width) run on the eager family model with per-request state
+            from ..models.eager_family import EagerFamilyExecutor, family_weights_from_checkpoint, random_family_weights
+            fw = family_weights_from_checkpoint(ck) if ck is not None else random_family_weights(cfg, args.seed)
+            executor = EagerFamilyExecutor(cfg, fw, kv_bits=(k_bits, v_bits))
+        else:
+            dense = dense_weights_from_checkpoint(ck) if ck is not None else random_dense_weights(cfg, args.seed)
+            executor = EagerPagedExecutor(cfg, dense, pages, kv_bits=(k_bits, v_bits))
     else:
         from ..executor.gpu_executor import GpuExecutor
         dev = torch.device("cuda", devices[0])
