@@ -249,6 +249,17 @@ def inspect_checkpoint(path: str | Path) -> dict:
         from .gguf import inspect_gguf
         return inspect_gguf(path)
     from ..contracts.model import WeightManifest
+    cfg_file = path / "config.json"
+    if cfg_file.is_file() and json.loads(cfg_file.read_text()).get("model_type") == "qwen4_exp":
+        from .qwen4_exp import admit_qwen4_exp_checkpoint
+        qcfg, _w, store = admit_qwen4_exp_checkpoint(path)
+        return {"model": qcfg.name, "family": qcfg.family, "layers": qcfg.num_layers, "hidden": qcfg.hidden_size,
+                "heads": f"{qcfg.num_q_heads}q/{qcfg.num_kv_heads}kv x {qcfg.head_dim}", "vocab": qcfg.vocab_size,
+                "residual_streams": qcfg.streams, "experts": f"{qcfg.num_experts} top-{qcfg.experts_per_token}",
+                "gated_deltanet_layers": sum(qcfg.layer_is_gdn(i) for i in range(qcfg.num_layers)),
+                "ngram_layers": list(qcfg.ple_layer_ids), "vision_tower": qcfg.vision is not None,
+                "tensors": len(store.tensors), "elements": sum(math.prod(t.shape) for t in store.tensors.values()),
+                "manifest_digest": WeightManifest.from_store(store).digest, "execution_mode": "eager"}
     ck = admit_checkpoint(path)
     total = sum(math.prod(t.shape) for t in ck.store.tensors.values())
     by_dtype: dict[str, int] = {}

@@ -302,3 +302,27 @@ def test_checkpoint_admission_and_serving_backend(tmp_path):
                      served_model_name=None)
     backend, name = build_backend(args, [0], 1, None, 8, 8)
     assert name == "qwen4-exp-tiny" and not backend.engine.prefix.enabled
+
+
+def test_inspect_reports_the_family(tmp_path):
+    from safetensors.torch import save_file
+
+    from cubic_serve_b200.models.checkpoint import inspect_checkpoint
+    cfg = Q.tiny_config()
+    d = tmp_path / "q"
+    d.mkdir()
+    raw = {"model_type": "qwen4_exp", "language_model_only": True, "text_config": {
+        "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+        "layer_types": list(cfg.layer_types), "num_attention_heads": cfg.num_q_heads, "num_key_value_heads": cfg.num_kv_heads,
+        "head_dim": cfg.head_dim, "rope_parameters": {"mrope_section": [2, 1, 1], "rope_theta": 1e4, "partial_rotary_factor": 0.5},
+        "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 8, "linear_value_head_dim": 8,
+        "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 16, "shared_expert_intermediate_size": 16,
+        "hc_count": 4, "hc_lowrank": 8, "indexer_n_heads": 2, "indexer_head_dim": 16, "indexer_budget": 16,
+        "indexer_compress_ratio": 4, "ple_layer_ids": [2], "ple_embed_dim": 32, "ngram_size": 3, "heads_per_ngram": 2,
+        "ngram_vocab_size_base": 500, "make_ngram_vocab_size_divisible_by": 4, "split_ngram_parts": 4,
+        "ngram_shard_rows": 512, "eos_token_id": 1, "max_position_embeddings": 4096}}
+    (d / "config.json").write_text(json.dumps(raw))
+    save_file({n: t.contiguous() for n, t in Q.random_qwen4_exp_weights(cfg, 1).items()}, str(d / "model.safetensors"))
+    info = inspect_checkpoint(d)
+    assert info["family"] == "qwen4_exp" and info["residual_streams"] == 4 and info["gated_deltanet_layers"] == 2
+    assert info["ngram_layers"] == [2] and info["execution_mode"] == "eager" and not info["vision_tower"]
