@@ -132,6 +132,52 @@ class CanonicalChatRequest:
     template_kwargs: tuple[tuple[str, Any], ...] = ()
 
 
+@dataclass(frozen=True)
+class MediaPlacement:
+    """Where a media item sits in the expanded prompt: ``rows`` placeholder tokens from ``first_token`` on are replaced
+    by the item's encoder features; ``grid`` = (t, h, w) in patches; ``digest`` identifies the content."""
+    kind: str                  # image | video
+    first_token: int
+    rows: int
+    grid: tuple[int, int, int]
+    digest: bytes = field(repr=False, default=b"")
+
+
+@dataclass(frozen=True)
+class EncoderJob:
+    """One item for the vision tower: ``patches`` is a float32 array [t h w, patch width] in merge-block order."""
+    digest: bytes = field(repr=False)
+    kind: str = "image"
+    grid: tuple[int, int, int] = (1, 0, 0)
+    patches: Any = field(repr=False, default=None)
+
+
+@dataclass(frozen=True)
+class InputPlan:
+    """A prepared prompt before its media are encoded: token ids with placeholder runs, rotary positions on the three
+    axes (None for text-only prompts: the sequence index), media placements in prompt order and the encoder jobs
+    that will produce their feature rows (one per placement, same order)."""
+    token_ids: tuple[int, ...]
+    prompt_text: str = ""
+    starts_in_reasoning: bool = False
+    positions: Any = None                       # int [3, len(token_ids)] or None
+    position_delta: int = 0                     # position of a generated token = its sequence index + delta
+    placements: tuple[MediaPlacement, ...] = ()
+    jobs: tuple[EncoderJob, ...] = field(default=(), repr=False)
+
+    def __post_init__(self) -> None:
+        if len(self.placements) != len(self.jobs):
+            raise ValueError("one encoder job per media placement")
+        at = 0
+        for p in self.placements:
+            t, h, w = p.grid
+            if p.first_token < at or p.rows <= 0 or p.first_token + p.rows > len(self.token_ids) or min(t, h, w) <= 0:
+                raise ValueError("media placements are ordered, disjoint and inside the prompt")
+            at = p.first_token + p.rows
+        if self.placements and self.positions is None:
+            raise ValueError("a prompt with media carries its positions")
+
+
 class EventKind(str, enum.Enum):
     START = "start"
     REASONING = "reasoning"

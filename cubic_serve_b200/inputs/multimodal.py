@@ -23,7 +23,8 @@ from dataclasses import dataclass, replace
 
 import numpy as np
 
-from ..contracts.request import CanonicalChatRequest, ContentPart, RequestError
+from ..contracts.request import (CanonicalChatRequest, ContentPart, EncoderJob, InputPlan, MediaPlacement,
+                                 RequestError)
 from ..models.vision import mrope_positions
 from ..runtime.multimodal import MultimodalInput
 from .chat import ChatInputProcessor, PreparedInput
@@ -83,7 +84,9 @@ class MultimodalChatProcessor(ChatInputProcessor):
         except (MediaError, VisionInputError) as e:
             raise RequestError(str(e), param="messages") from None
 
-    def build(self, req: CanonicalChatRequest) -> PreparedInput:
+    def plan(self, req: CanonicalChatRequest) -> InputPlan:
+        """Everything except the encoding: media resolved, decoded and cut into patches, the prompt rendered and its
+        placeholders expanded, positions computed, the encoder's capacity limits checked."""
         t = self.tokens
         items: list[tuple[str, MediaPatches]] = []
         msgs = []
@@ -98,16 +101,16 @@ class MultimodalChatProcessor(ChatInputProcessor):
                     parts.append(p)
             msgs.append(replace(m, parts=tuple(parts)))
         if not items:
-            return super().build(req)
+            base = super().build(req)
+            return InputPlan(tuple(base.token_ids), base.prompt_text, base.starts_in_reasoning)
         if len(items) > self.max_items:
             raise RequestError(f"a request may carry {self.max_items} media items", param="messages")
         base = super().build(replace(req, messages=tuple(msgs)))
         merge = self.geometry.merge_size
-        # expand every pad token into the item's rows
         ids: list[int] = []
         spans_at: list[int] = []
         k = 0
-        for tok in base.token_ids:
+        for tok in base.token_ids:                                    # expand every pad token into the item's rows
             if tok in (t.image, t.video):
                 if k >= len(items) or (tok == t.image) != (items[k][0] == "image"):
                     raise RequestError("the rendered prompt's media placeholders do not match the media parts",
@@ -123,12 +126,44 @@ class MultimodalChatProcessor(ChatInputProcessor):
             raise RequestError(f"the prompt has {len(ids)} tokens with its media; the context limit is "
                                f"{self.max_model_len}", param="messages")
         try:
-            encoded = self.vision.encode([(mp.pixels, mp.grid) for _, mp in items])
+            self.vision.plan.check_request([mp.grid for _, mp in items], merge)
         except ValueError as e:                                       # capacity limits of the encoder
             raise RequestError(str(e), param="messages") from None
-        spans = [(at, rows, digest) for at, (rows, digest) in zip(spans_at, encoded)]
-        pos, delta = mrope_positions(ids, [(at, mp.rows(merge), mp.grid) for at, (_, mp) in zip(spans_at, items)], merge)
-        mm = MultimodalInput(spans, np.asarray(pos, dtype=np.int32), delta)
-        out = PreparedInput(ids, base.prompt_text, starts_in_reasoning=base.starts_in_reasoning)
-        out.multimodal = mm
+        placements, jobs = [], []
+        for at, (kind, mp) in zip(spans_at, items):
+            d = self.vision.digest(mp.pixels, mp.grid)
+            placements.append(MediaPlacement(kind, at, mp.rows(merge), tuple(mp.grid), d))
+            jobs.append(EncoderJob(d, kind, tuple(mp.grid), mp.pixels))
+        pos, delta = mrope_positions(ids, [(p.first_token, p.rows, p.grid) for p in placements], merge)
+        return InputPlan(tuple(ids), base.prompt_text, base.starts_in_reasoning, np.asarray(pos, dtype=np.int32), delta,
+                         tuple(placements), tuple(jobs))
+
+    @staticmethod
+    def assemble(plan: InputPlan, encoded: list) -> MultimodalInput | None:
+        """The engine's view of a plan whose jobs were encoded (``encoded``: ``(rows, digest)`` per job, in order)."""
+        if not plan.placements:
+            return None
+        spans = []
+        for p, (rows, digest) in zip(plan.placements, encoded):
+            if rows.shape[0] != p.rows or digest != p.digest:
+                raise ValueError("the encoder's rows do not match the plan's placement")
+            spans.append((p.first_token, rows, digest))
+        return MultimodalInput(spans, plan.positions, plan.position_delta)
+
+    def encode(self, plan: InputPlan) -> list:
+        return self.vision.encode([(j.patches, j.grid) for j in plan.jobs])
+
+    def submit(self, plan: InputPlan):
+        """Future of ``encode(plan)`` on the vision service's own thread."""
+        return self.vision.submit([(j.patches, j.grid) for j in plan.jobs])
+
+    def build(self, req: CanonicalChatRequest) -> PreparedInput:
+        """``plan`` + encoding on the calling thread (library use; the serving backend encodes on the encoder thread)."""
+        plan = self.plan(req)
+        out = PreparedInput(list(plan.token_ids), plan.prompt_text, starts_in_reasoning=plan.starts_in_reasoning)
+        if plan.jobs:
+            try:
+                out.multimodal = self.assemble(plan, self.encode(plan))
+            except ValueError as e:
+                raise RequestError(str(e), param="messages") from None
         return out

@@ -105,7 +105,15 @@ class TokenChatBackend:
             if not constraint_supported(req.structured):
                 raise RequestError("this structured output constraint is not available in this deployment",
                                    param="response_format")
-        prepared = self.processor.build(req)
+        plan = None
+        if hasattr(self.processor, "plan"):
+            # prompts with media: everything but the encoding happens here; the vision tower runs on its own thread and
+            # the request reaches the engine when its feature rows exist
+            plan = self.processor.plan(req)
+            from ..inputs.chat import PreparedInput
+            prepared = PreparedInput(list(plan.token_ids), plan.prompt_text, starts_in_reasoning=plan.starts_in_reasoning)
+        else:
+            prepared = self.processor.build(req)
         loop = asyncio.get_running_loop()
         stream = TokenStream(loop)
         forced = req.tool_choice.name if req.tool_choice.mode == "named" else None
@@ -133,7 +141,18 @@ class TokenChatBackend:
                             thinking_budget=req.reasoning.budget_tokens if prepared.starts_in_reasoning else None)
         with self._lock:
             self._live[req.request_id] = live
-            self._inbox.append((req.request_id, prepared.token_ids, sp, prepared.multimodal))
+            if plan is None or not plan.jobs:
+                self._inbox.append((req.request_id, prepared.token_ids, sp, prepared.multimodal))
+        if plan is not None and plan.jobs:
+            def encoded(fut, rid=req.request_id, ids=prepared.token_ids) -> None:
+                try:
+                    item = self.processor.assemble(plan, fut.result())
+                except BaseException as exc:  # noqa: BLE001 - handed to the request's stream by the dispatcher
+                    item = exc
+                with self._lock:
+                    self._inbox.append((rid, ids, sp, item))
+                self._wake.set()
+            self.processor.submit(plan).add_done_callback(encoded)
         self._wake.set()
         return self._events(live)
 
@@ -198,6 +217,9 @@ class TokenChatBackend:
                 if live is None or live.cancelled:
                     continue
                 try:
+                    if isinstance(mm, BaseException):          # the encoder refused or failed this request's media
+                        raise ValueError(str(mm)) if isinstance(mm, ValueError) else AdmissionError(
+                            "the media of this request could not be encoded", status=500)
                     live.engine_id = self.engine.add_request(ids, sp, request_id=rid, multimodal=mm)
                     by_engine_id[rid] = live
                     self.stats["requests"] += 1

@@ -413,3 +413,63 @@ def test_multimodal_checkpoint_is_admitted_and_served(tmp_path):
     assert len(toks) == 4
     ex.accepts_features = False
     assert build_media_processor(args, ck, tok, ex, 512) is None
+
+
+def test_http_request_with_an_image_goes_through_the_encoder_thread():
+    """OpenAI ``image_url`` part -> plan on the request's thread, encoding on the vision service's thread, admission when
+    the rows exist; a broken image is a 400 before anything is queued; the same image again is served from the store."""
+    import asyncio
+    import json
+    from dataclasses import replace
+
+    from test_api import _call
+
+    from cubic_serve_b200.api.server import CubicASGIApp
+    from cubic_serve_b200.executor.eager_executor import EagerPagedExecutor
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    from cubic_serve_b200.inputs.multimodal import MultimodalChatProcessor, VisionTokens
+    from cubic_serve_b200.models.config import ModelConfig
+    from cubic_serve_b200.models.reference import random_dense_weights
+    from cubic_serve_b200.runtime.async_engine import TokenChatBackend
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SchedulerConfig
+
+    class Tok(ByteTokenizer):
+        SPECIALS = ByteTokenizer.SPECIALS + ("<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+    tok = Tok()
+    ids = tok.special_ids
+    cfg = replace(ModelConfig(num_layers=1, hidden_size=64, num_q_heads=2, num_kv_heads=1, head_dim=32, intermediate_size=128,
+                              vocab_size=tok.vocab_size), mrope_section=(8, 4, 4))
+    eng = LLMEngine(EagerPagedExecutor(cfg, random_dense_weights(cfg, 0), 64), 64,
+                    SchedulerConfig(max_running_requests=4, max_model_len=512, max_batched_tokens=256))
+    vcfg = _cfg(out_hidden_size=64)
+    svc = VisionService(VisionEncoder(vcfg, random_vision_weights(vcfg, 3)))
+    threads = []
+    encode = svc.encode
+    svc.encode = lambda items: (threads.append(threading.current_thread().name), encode(items))[1]
+    proc = MultimodalChatProcessor(tok, svc, VisionTokens(ids["<|image_pad|>"], ids["<|video_pad|>"], ids["<|vision_start|>"],
+                                                          ids["<|vision_end|>"]),
+                                   PatchGeometry(4, 2, 2, min_pixels=8 * 8, max_pixels=32 * 32), max_model_len=512)
+    url = "data:image/png;base64," + base64.b64encode(_png(24, 40)).decode()
+
+    async def go():
+        backend = TokenChatBackend(eng, tok, default_max_tokens=8, processor=proc)
+        app = CubicASGIApp(backend, "toy")
+        body = {"model": "toy", "max_tokens": 5, "temperature": 0, "messages": [{"role": "user", "content": [
+            {"type": "text", "text": "what is this? "}, {"type": "image_url", "image_url": {"url": url}}]}]}
+        first = await _call(app, "POST", "/v1/chat/completions", body)
+        second = await _call(app, "POST", "/v1/chat/completions", body)
+        text = await _call(app, "POST", "/v1/chat/completions", {**body, "messages": [{"role": "user", "content": "hi"}]})
+        bad = {**body, "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {
+            "url": "data:image/png;base64,iVBORw0KGgoAAAANSUhEUg=="}}]}]}
+        broken = await _call(app, "POST", "/v1/chat/completions", bad)
+        backend.close()
+        return first, second, text, broken
+    (s1, b1), (s2, b2), (s3, _), (s4, b4) = asyncio.run(go())
+    assert s1 == s2 == s3 == 200 and s4 == 400
+    j1, j2 = json.loads(b1), json.loads(b2)
+    assert j1["usage"]["completion_tokens"] == 5 and j1["usage"]["prompt_tokens"] > 15
+    assert j1["choices"][0]["message"]["content"] == j2["choices"][0]["message"]["content"]
+    assert threads and all(t == "vision-encoder" for t in threads)
+    assert svc.store.hits >= 1 and "messages" in json.dumps(json.loads(b4))
+    svc.close()
