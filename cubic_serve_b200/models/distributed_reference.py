@@ -91,6 +91,61 @@ def moe_expert_parallel_reference(x: torch.Tensor, router: torch.Tensor, gate_up
     return tp_all_reduce(partial, group)
 
 
+def moe_dispatch_combine_reference(x_local: torch.Tensor, router: torch.Tensor, gate_up: list[torch.Tensor],
+                                   down: list[torch.Tensor], top_k: int, group, normalize: bool = True):
+    """Eager expert parallelism on a ROW-SHARDED stream, the schedule of ``parallel/ep.py``: every rank holds its own
+    rows ``x_local`` and the experts ``[rank E / n, (rank + 1) E / n)``.
+
+    1. dispatch: a rank routes its rows and sends each row ONCE to every rank that owns at least one of the row's
+       experts, with the ids and weights of the experts that rank has to apply;
+    2. the owner runs its experts on the rows it received and pre-sums a row's expert outputs with their weights:
+       one row goes back per (row, owner);
+    3. combine: the home rank adds the returned rows in ascending owner order.
+
+    Returns ``(y_local, rows_sent)`` where ``rows_sent[d]`` counts the rows this rank sent to rank ``d`` (its own
+    included).  ``y_local`` equals ``moe_reference`` over all experts on the same rows up to the order of the final
+    sum.  Reference counterpart: ``models/qwen3_5_moe/distributed.py:191`` (``_DistributedMoe``) there."""
+    from .moe import moe_reference
+    rank, size = dist.get_rank(group), dist.get_world_size(group)
+    E = router.shape[0]
+    if E % size or len(gate_up) != E // size or len(down) != len(gate_up):
+        raise ValueError("every rank owns num_experts / group size experts")
+    per = E // size
+    xf = x_local.float()
+    logits = (xf @ router.float().t()).to(torch.bfloat16).float()
+    order = torch.argsort(-logits, dim=-1, stable=True)[:, :top_k]
+    sel = torch.gather(logits, 1, order)
+    w = torch.softmax(sel, -1) if normalize else torch.softmax(logits, -1).gather(1, order)
+    outbox: list[list] = [[] for _ in range(size)]                  # per destination: (row, [(expert, weight)...], vector)
+    for t in range(x_local.shape[0]):
+        by_dest: dict[int, list] = {}
+        for j in range(top_k):
+            e = int(order[t, j])
+            by_dest.setdefault(e // per, []).append((e, float(w[t, j])))
+        for d, routes in sorted(by_dest.items()):
+            outbox[d].append((t, routes, x_local[t]))
+    inbox: list = [None] * size
+    dist.all_gather_object(inbox, outbox, group=group)              # inbox[src][dst]
+    returned: list[list] = [[] for _ in range(size)]                # per source rank: (row, pre-summed vector)
+    for src in range(size):
+        for t, routes, vec in inbox[src][rank]:
+            acc = torch.zeros(x_local.shape[1])
+            for e, weight in routes:
+                le = e - rank * per
+                gu = (vec.float() @ gate_up[le].float().t()).to(torch.bfloat16).float()
+                half = gu.shape[0] // 2
+                act = (torch.nn.functional.silu(gu[:half]) * gu[half:]).to(torch.bfloat16).float()
+                acc += weight * (act @ down[le].float().t()).to(torch.bfloat16).float()
+            returned[src].append((t, acc))
+    back: list = [None] * size
+    dist.all_gather_object(back, returned, group=group)             # back[owner][home]
+    y = torch.zeros(x_local.shape[0], x_local.shape[1])
+    for owner in range(size):                                       # ascending owner order: the same bits on any run
+        for t, vec in back[owner][rank]:
+            y[t] += vec
+    return y, [len(o) for o in outbox]
+
+
 class DistributedEagerDecoder:
     """One rank of the reference.  ``tp_group``: the ranks of this stage; ``prev`` / ``next``: global ranks of the
     same tensor rank in the neighbouring stages (None at the ends)."""

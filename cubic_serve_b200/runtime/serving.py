@@ -195,6 +195,8 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
             caps = executor.capture_decode_graphs()
             log.info("captured decode graphs for capacities %s; %d KV pages", caps, pages)
     tok = _tokenizer_for(model, cfg.vocab_size)
+    from ..models.protocol import check_executor
+    log.info("executor %s: %s", type(executor).__name__, check_executor(executor))
     engine = LLMEngine(executor, num_pages=pages, scheduler_config=sched, eos_token_id=getattr(tok, "eos_token_id", None))
     if spec is not None and getattr(spec, "mode", "fixed") == "dynamic" and getattr(executor, "speculative_depth", 0):
         from .speculative import DraftPolicyConfig

@@ -208,3 +208,52 @@ def test_random_expert_shards_with_lanes_are_slices_of_one_model():
     assert float((total - want).norm() / want.norm()) < 5e-3
     with pytest.raises(ValueError):
         random_moe_weights(cfg, "cpu", gen, 0, 4, ep_size=1)            # 64-feature lanes: not whole groups
+
+
+def _moe_dispatch_rank(rank, world, port, q):
+    import torch.distributed as dist
+    from cubic_serve_b200.models.distributed_reference import moe_dispatch_combine_reference
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(17)
+    E, H, I, T = 8, 32, 48, 12
+    router = (torch.randn(E, H, generator=g) * 0.3).to(torch.bfloat16)
+    gate_up = [(torch.randn(2 * I, H, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    down = [(torch.randn(H, I, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    per, rows = E // world, T // world
+    y, sent = moe_dispatch_combine_reference(x[rank * rows:(rank + 1) * rows], router, gate_up[rank * per:(rank + 1) * per],
+                                             down[rank * per:(rank + 1) * per], 3, dist.group.WORLD)
+    q.put((rank, y, sent))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_sharded_dispatch_and_combine_equals_the_single_process_block():
+    """Rows live on their home rank, experts on their owners: every row travels once per owner it needs (never once per
+    expert), comes back pre-summed, and the home rank's sum equals the block computed in one process."""
+    from cubic_serve_b200.models.moe import moe_reference
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_moe_dispatch_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {r: (y, sent) for r, y, sent in (q.get(timeout=120) for _ in range(world))}
+    for p in procs:
+        p.join(timeout=60)
+    g = torch.Generator().manual_seed(17)
+    E, H, I, T = 8, 32, 48, 12
+    router = (torch.randn(E, H, generator=g) * 0.3).to(torch.bfloat16)
+    gate_up = [(torch.randn(2 * I, H, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    down = [(torch.randn(H, I, generator=g) * 0.2).to(torch.bfloat16) for _ in range(E)]
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    want = moe_reference(x, router, gate_up, down, 3)
+    y = torch.cat([got[0][0], got[1][0]])
+    assert float((y - want).norm() / want.norm()) < 1e-5
+    for r in range(world):
+        sent = got[r][1]
+        # top-3 of 8 experts on 2 owners: a row needs one or two owners, never three transfers
+        assert 6 <= sum(sent) <= 12 and max(sent) <= 6
