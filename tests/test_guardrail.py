@@ -55,6 +55,47 @@ def test_trace_record_and_replay(tmp_path):
     assert not bad.ok and bad.first_difference["position"] >= 0 and "request_id" in bad.first_difference
 
 
+def test_replay_compares_the_cache_lifecycle(tmp_path):
+    """Same tokens, different cache behaviour: the lifecycle records tell a run with prefix sharing from one without,
+    and a run on a smaller pool (evictions / preemptions) from the recorded one."""
+    import numpy as np
+    from cubic_serve_b200.executor.eager_executor import EagerPagedExecutor
+    from cubic_serve_b200.guardrail.replay import TraceRecorder, replay_trace
+    from cubic_serve_b200.models.config import toy_config
+    from cubic_serve_b200.models.reference import random_dense_weights
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = toy_config()
+
+    def engine(prefix=True, pages=64):
+        return LLMEngine(EagerPagedExecutor(cfg, random_dense_weights(cfg, 0), num_pages=pages), num_pages=pages,
+                         scheduler_config=SchedulerConfig(max_running_requests=4, max_batched_tokens=64,
+                                                          prefill_chunk_tokens=64, max_model_len=128,
+                                                          enable_prefix_cache=prefix))
+    rng = np.random.default_rng(1)
+    shared = rng.integers(0, cfg.vocab_size, 40).tolist()
+    rec = TraceRecorder(engine())
+    rec.add_request(shared + [5, 6, 7], SamplingParams(max_tokens=4))
+    rec.run()
+    rec.add_request(shared + [9, 9], SamplingParams(max_tokens=4))          # resumes from the first request's pages
+    rec.run()
+    trace = rec.records
+    steps = [r for r in trace if r["kind"] == "step"]
+    admitted = {}
+    for r in steps:
+        admitted.update(r["lifecycle"]["admitted"])
+    assert sorted(admitted.values()) == [0, 32] and steps[-1]["lifecycle"]["prefix_hit_tokens"] == 32
+    assert steps[-1]["lifecycle"]["prefix_blocks"] >= 2
+    assert replay_trace(trace, engine(), check_lifecycle=True).ok
+    cold = replay_trace(trace, engine(prefix=False))                         # the tokens agree ...
+    assert cold.ok
+    cold = replay_trace(trace, engine(prefix=False), check_lifecycle=True)   # ... the cache behaviour does not
+    assert not cold.ok and ("lifecycle" in cold.first_difference or "reason" in cold.first_difference)
+    old = [dict(r, lifecycle=None) if r["kind"] == "step" else r for r in trace]
+    rep = replay_trace(old, engine(), check_lifecycle=True)
+    assert not rep.ok and "no lifecycle" in rep.first_difference["reason"]
+
+
 def test_qualification_reports_compare_by_result_digest():
     import torch
     from cubic_serve_b200.guardrail.qualify import compare_reports, tensor_digest
