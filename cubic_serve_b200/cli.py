@@ -125,6 +125,9 @@ def build_parser() -> argparse.ArgumentParser:
                                       "report the first token that differs (another build, execution mode or topology)")
     tr.add_argument("action", choices=("record", "replay"))
     tr.add_argument("trace", help="trace file (JSON lines)")
+    tr.add_argument("--check-lifecycle", action="store_true",
+                    help="replay: also compare pages in use, prefix-cache contents and cached-prefix lengths step by step "
+                         "(same scheduler flags and cache size as the recording)")
     tr.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
     tr.add_argument("--requests", type=int, default=8, help="record: number of synthetic requests")
     tr.add_argument("--max-tokens", type=int, default=16)
@@ -276,7 +279,7 @@ def _trace(args) -> int:
             tokens = sum(len(t) for r in rec.records if r["kind"] == "step" for t in r["emitted"].values())
             print(json.dumps({"recorded": args.trace, "requests": args.requests, "tokens": tokens}))
             return 0
-        report = replay_trace(args.trace, engine)
+        report = replay_trace(args.trace, engine, check_lifecycle=getattr(args, "check_lifecycle", False))
         print(report.to_json())
         return 0 if report.ok else 1
     finally:
