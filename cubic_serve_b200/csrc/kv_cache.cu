@@ -15,7 +15,10 @@ struct KvWriteParams {
   const __nv_bfloat16* qkv;    // [T, (Hq + 2*Hkv) * D]
   __nv_bfloat16* q_out;        // [T, Hq * D]
   uint8_t* cache;              // [pages][Hkv][blob]
-  const int* positions;        // [T] rotary position
+  const int* positions;        // [T] rotary position (the temporal axis when pos_h / pos_w are given)
+  const int* pos_h;            // [T] or null: row-axis positions of the three-axis rotary form
+  const int* pos_w;            // [T] or null: column-axis positions
+  int mrope_h, mrope_w;        // frequency slots 1, 4, 7, .. (< 3 mrope_h) follow pos_h, slots 2, 5, 8, .. (< 3 mrope_w) pos_w
   const int* slots;            // [T] page * 16 + offset, < 0: do not write (padding row)
   const __nv_bfloat16* q_norm; // [D] or null
   const __nv_bfloat16* k_norm; // [D] or null
@@ -109,12 +112,21 @@ rope_kv_write_kernel(const KvWriteParams p) {
   const int D = p.lay.head_dim;  // == 128
   const int half = p.rotary_dim >> 1;
   const float pos = static_cast<float>(p.positions[t]);
+  // three-axis form: frequency slot j turns by the position on its axis (interleaved layout: temporal by default, the
+  // row axis on slots 1, 4, 7, .., the column axis on 2, 5, 8, .. as far as their counts reach)
+  auto slot_pos = [&](int j) -> float {
+    if (p.pos_h == nullptr) return pos;
+    const int r = j % 3;
+    if (r == 1 && j < 3 * p.mrope_h) return static_cast<float>(p.pos_h[t]);
+    if (r == 2 && j < 3 * p.mrope_w) return static_cast<float>(p.pos_w[t]);
+    return pos;
+  };
   float sn[2] = {0.f, 0.f}, cs[2] = {1.f, 1.f};
   if (half == 64) {
 #pragma unroll
-    for (int k = 0; k < 2; ++k) sincosf(pos * p.inv_freq[lane + 32 * k], &sn[k], &cs[k]);
+    for (int k = 0; k < 2; ++k) sincosf(slot_pos(lane + 32 * k) * p.inv_freq[lane + 32 * k], &sn[k], &cs[k]);
   } else if (half == 32) {
-    sincosf(pos * p.inv_freq[lane], &sn[0], &cs[0]);
+    sincosf(slot_pos(lane) * p.inv_freq[lane], &sn[0], &cs[0]);
   }
   const int slot = p.slots[t];
   for (int h = warp; h < heads; h += kRopeWarps) {
@@ -210,15 +222,39 @@ int cb_kv_blob_bytes(int head_dim, int k_bits, int v_bits) {
   return cb::make_kv_layout(head_dim, k_bits, v_bits).blob_bytes;
 }
 
+// Three-axis rotary positions: ``positions`` is the temporal axis, ``pos_h`` / ``pos_w`` the row and column axes (both
+// null: one axis); ``mrope_h`` / ``mrope_w`` are the frequency-slot counts of those two axes.
+int cb_rope_kv_write_axes(const void* qkv, void* q_out, void* cache, const void* positions, const void* pos_h,
+                          const void* pos_w, int mrope_h, int mrope_w, const void* slots, const void* q_norm,
+                          const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D, int rotary_dim,
+                          float eps, int k_bits, int v_bits, int rotate, void* stream);
+
 int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* positions, const void* slots,
                      const void* q_norm, const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D,
                      int rotary_dim, float eps, int k_bits, int v_bits, int rotate, void* stream) {
+  return cb_rope_kv_write_axes(qkv, q_out, cache, positions, nullptr, nullptr, 0, 0, slots, q_norm, k_norm, inv_freq, T,
+                               Hq, Hkv, D, rotary_dim, eps, k_bits, v_bits, rotate, stream);
+}
+
+int cb_rope_kv_write_axes(const void* qkv, void* q_out, void* cache, const void* positions, const void* pos_h,
+                          const void* pos_w, int mrope_h, int mrope_w, const void* slots, const void* q_norm,
+                          const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D, int rotary_dim,
+                          float eps, int k_bits, int v_bits, int rotate, void* stream) {
   using namespace cb;
   if (T <= 0) return 0;
   if (D != 128) return -10;
   if (!(k_bits == 8 || k_bits == 6 || k_bits == 4) || !(v_bits == 8 || v_bits == 6 || v_bits == 4)) return -11;
   if (!(rotary_dim == 128 || rotary_dim == 64 || rotary_dim == 0)) return -12;
+  if ((pos_h == nullptr) != (pos_w == nullptr)) return -13;
+  if (pos_h != nullptr) {
+    const int half = rotary_dim / 2;   // the last slot of either axis has to exist: 3 h - 2 and 3 w - 1 below half
+    if (mrope_h <= 0 || mrope_w <= 0 || 3 * mrope_h - 2 >= half || 3 * mrope_w - 1 >= half) return -14;
+  }
   KvWriteParams p;
+  p.pos_h = static_cast<const int*>(pos_h);
+  p.pos_w = static_cast<const int*>(pos_w);
+  p.mrope_h = mrope_h;
+  p.mrope_w = mrope_w;
   p.qkv = static_cast<const __nv_bfloat16*>(qkv);
   p.q_out = static_cast<__nv_bfloat16*>(q_out);
   p.cache = static_cast<uint8_t*>(cache);

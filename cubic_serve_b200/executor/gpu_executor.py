@@ -67,6 +67,8 @@ class _Staging:
             # per sampled row: the request's slot and its thinking-budget command (device-side budget state machine)
             ("row_slot", np.int32, max_rows), ("budget_init", np.int32, max_rows),
             ("page_table", np.int32, max_rows * max_pages),
+            # row- and column-axis rotary positions of multimodal prefill steps (``positions`` is the temporal axis)
+            ("positions_h", np.int32, max_tokens), ("positions_w", np.int32, max_tokens),
         ]
         off = 0
         self.offsets = {}
@@ -105,6 +107,7 @@ class BatchBuilder:
         self.max_pages = -(-max_model_len // K.PAGE_TOKENS)
         max_rb = max(max_rows, max_tokens // self.qb + max_rows)
         self.stage = _Staging(max_tokens, max_rows, max_rb, self.max_pages, device)
+        self.device = device
         self._page_rows: list[tuple[int, int]] = [(-2, 0)] * max_rows
 
     def _splits(self, row_blocks: int) -> int:
@@ -139,6 +142,7 @@ class BatchBuilder:
         st = self.stage
         h = st.h
         qb = self.qb
+        axes, embeds = False, []
         for s in segs:
             self._sync_page_row(s)
         if all(len(s.token_ids) == 1 for s in segs):
@@ -147,6 +151,9 @@ class BatchBuilder:
             h["token_ids"][:n] = [s.token_ids[0] for s in segs]
             starts = np.fromiter((s.start for s in segs), dtype=np.int32, count=n)
             h["positions"][:n] = starts
+            for i, s in enumerate(segs):
+                if s.positions3 is not None:               # a request with media decodes at sequence index + its offset
+                    h["positions"][i] = int(np.asarray(s.positions3)[0, 0])
             h["slots"][:n] = [s.pages[s.start >> 4] * 16 + (s.start & 15) for s in segs]
             h["rb_req"][:n] = [s.request_slot for s in segs]
             ar = np.arange(n, dtype=np.int32)
@@ -180,12 +187,24 @@ class BatchBuilder:
         else:
             t = rb = rows = 0
             nseg = len(segs)
+            # three-axis rotary positions are staged only for steps in which some row's axes differ
+            axes = any(s.positions3 is not None and not (np.asarray(s.positions3)[0] == np.asarray(s.positions3)[1:]).all()
+                       for s in segs)
             for i, s in enumerate(segs):
                 n = len(s.token_ids)
                 h["seg_row0"][i], h["seg_count"][i], h["seg_slot"][i], h["seg_pos0"][i] = t, n, s.request_slot, s.start
                 h["token_ids"][t:t + n] = s.token_ids
                 pos = np.arange(s.start, s.start + n, dtype=np.int32)
-                h["positions"][t:t + n] = pos
+                if s.positions3 is None:
+                    h["positions"][t:t + n] = pos
+                    if axes:
+                        h["positions_h"][t:t + n] = pos
+                        h["positions_w"][t:t + n] = pos
+                else:
+                    p3 = np.asarray(s.positions3, dtype=np.int32)
+                    h["positions"][t:t + n], h["positions_h"][t:t + n], h["positions_w"][t:t + n] = p3[0], p3[1], p3[2]
+                for off, feat in (s.embeds or ()):
+                    embeds.append((t + off, feat))
                 pages = np.asarray(s.pages, dtype=np.int32)
                 h["slots"][t:t + n] = pages[pos >> 4] * 16 + (pos & 15)
                 nb = -(-n // qb)
@@ -228,7 +247,10 @@ class BatchBuilder:
                          positions=d["positions"], slots=d["slots"], page_table=d["page_table"], rb_req=d["rb_req"],
                          rb_qstart=d["rb_qstart"], rb_qcount=d["rb_qcount"], rb_ctx=d["rb_ctx"],
                          logit_rows=d["logit_rows"], attn_splits=splits,
-                         segments=K.GdnSegments(d["seg_row0"], d["seg_count"], d["seg_slot"], d["seg_pos0"], nseg)), rows
+                         segments=K.GdnSegments(d["seg_row0"], d["seg_count"], d["seg_slot"], d["seg_pos0"], nseg),
+                         positions_hw=(d["positions_h"], d["positions_w"]) if axes else None,
+                         embeds=[(first, feat.to(self.device, torch.bfloat16, non_blocking=True))
+                                 for first, feat in embeds] or None), rows
 
 
 class GpuExecutor:
@@ -236,6 +258,10 @@ class GpuExecutor:
                  max_model_len: int = 4096, use_graphs: bool = True, rows_per_request: int = 1) -> None:
         """``rows_per_request`` > 1 sizes the sampled-row staging for speculative review (K + 1 rows per request)."""
         self.runner = runner
+        # encoder feature rows and three-axis positions are taken on one GPU by the plain executor (the speculative
+        # executors and the tensor-parallel embedding path do not carry them)
+        self.accepts_features = type(self) is GpuExecutor and runner.tp is None and getattr(runner, "pp", None) is None \
+            and runner.cfg.mrope_section is not None
         self.cfg = runner.cfg
         self.device = runner.device
         self.max_rows = max_rows

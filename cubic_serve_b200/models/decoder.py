@@ -261,6 +261,10 @@ class StepBatch:
     logit_rows: torch.Tensor     # int64 [R] rows of the hidden state that feed lm_head
     attn_splits: int = 1
     segments: object | None = None   # K.GdnSegments: the step's rows grouped by request (Gated DeltaNet layers)
+    # multimodal prefill steps (one GPU): row- and column-axis rotary positions int32 [T] each (``positions`` is then
+    # the temporal axis) and encoder feature rows ``[(first row, bf16 [n, H])]`` that replace token embeddings
+    positions_hw: tuple | None = None
+    embeds: list | None = None
 
 
 class DecoderRunner:
@@ -465,6 +469,10 @@ class DecoderRunner:
             n += 1
             if self.tp is not None:
                 self.tp.all_reduce(h)
+            for first, rows in (b.embeds or ()):               # encoder features take the place of the embeddings
+                lo, hi = max(first, t0), min(first + rows.shape[0], t1)
+                if lo < hi:
+                    h[lo - t0:hi - t0].copy_(rows[lo - first:hi - first])
         pending = None  # partial sum waiting to be folded into h by the next norm (TP > 1)
         fp8s = (wq_pack.FMT_FP8, wq_pack.FMT_FP8_BLOCK)
 
@@ -492,9 +500,11 @@ class DecoderRunner:
                 n += 5
             else:
                 K.wq_gemm(xin, lw.qkv, out=qkv, ws=self.ws)
+                hw = None if b.positions_hw is None else (b.positions_hw[0][t0:t1], b.positions_hw[1][t0:t1])
                 K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
                                 self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
-                                rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation)
+                                rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation, positions_hw=hw,
+                                mrope_section=cfg.mrope_section if hw is not None else None)
                 K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
                                   b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
                                   splits=b.attn_splits, ws=self.ws)

@@ -94,3 +94,31 @@ def test_same_slot_same_arrival_new_admission_rewrites_the_row():
     # the same request (arrival 3) re-admitted after a preemption: same slot, same page count, other pages
     bb.fill([Segment(1, [5], 48, [4, 5, 6, 7], True, uid=(3 << 16) | 1)])
     assert bb.stage.h["page_table"][1, :4].tolist() == [4, 5, 6, 7]
+
+
+def test_three_axis_positions_and_feature_rows_are_staged():
+    import numpy as np
+    import torch
+
+    from cubic_serve_b200.executor.gpu_executor import BatchBuilder, Segment
+    bb = BatchBuilder(max_rows=4, max_tokens=64, max_model_len=128, group=4, kv_heads=2, device="cpu")
+    p3 = np.stack([np.arange(6), np.arange(6) + 2, np.arange(6) * 3]).astype(np.int32)
+    feats = torch.ones(2, 8)
+    segs = [Segment(0, list(range(6)), 0, [3], embeds=[(1, feats)], positions3=p3),
+            Segment(1, [7, 8, 9], 16, [4, 5])]
+    b, rows = bb.fill(segs)
+    h = bb.stage.h
+    assert b.positions_hw is not None and rows == 2
+    assert h["positions"][:9].tolist() == [0, 1, 2, 3, 4, 5, 16, 17, 18]
+    assert h["positions_h"][:9].tolist() == [2, 3, 4, 5, 6, 7, 16, 17, 18]
+    assert h["positions_w"][:9].tolist() == [0, 3, 6, 9, 12, 15, 16, 17, 18]
+    assert [(f, tuple(r.shape), r.dtype) for f, r in b.embeds] == [(1, (2, 8), torch.bfloat16)]
+    assert h["slots"][6:9].tolist() == [5 * 16, 5 * 16 + 1, 5 * 16 + 2]       # cache slots follow the sequence index
+    # equal axes: the one-axis kernel path; a decode row of a request with media sits at index + offset
+    same = np.stack([np.arange(4) + 10] * 3).astype(np.int32)
+    b2, _ = bb.fill([Segment(0, [1, 2, 3, 4], 10, [3])])
+    assert b2.positions_hw is None and b2.embeds is None
+    b3, _ = bb.fill([Segment(0, [1, 2, 3, 4], 10, [3], positions3=same)])
+    assert b3.positions_hw is None
+    b4, _ = bb.fill([Segment(0, [5], 40, [3, 4, 5], positions3=np.full((3, 1), 33, np.int32)), Segment(1, [6], 20, [6, 7])])
+    assert h["positions"][:2].tolist() == [33, 20] and h["rb_ctx"][:2].tolist() == [41, 21]
