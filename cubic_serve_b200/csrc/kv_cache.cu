@@ -19,6 +19,7 @@ struct KvWriteParams {
   const int* pos_h;            // [T] or null: row-axis positions of the three-axis rotary form
   const int* pos_w;            // [T] or null: column-axis positions
   int mrope_h, mrope_w;        // frequency slots 1, 4, 7, .. (< 3 mrope_h) follow pos_h, slots 2, 5, 8, .. (< 3 mrope_w) pos_w
+  const __nv_bfloat16* qkv_bias;  // [(Hq + 2 Hkv) D] or null: bias of the q / k / v projections, added before the norm
   const int* slots;            // [T] page * 16 + offset, < 0: do not write (padding row)
   const __nv_bfloat16* q_norm; // [D] or null
   const __nv_bfloat16* k_norm; // [D] or null
@@ -134,6 +135,12 @@ rope_kv_write_kernel(const KvWriteParams p) {
     float v[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) v[k] = __bfloat162float(src[lane + 32 * k]);
+    if (p.qkv_bias != nullptr) {
+      // the projection's output was rounded to bf16 by the GEMM; the sum is rounded again, as an unfused add would
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        v[k] = __bfloat162float(__float2bfloat16(v[k] + __bfloat162float(p.qkv_bias[h * D + lane + 32 * k])));
+    }
 
     const bool is_q = h < p.Hq;
     const bool is_k = !is_q && h < p.Hq + p.Hkv;
@@ -223,23 +230,24 @@ int cb_kv_blob_bytes(int head_dim, int k_bits, int v_bits) {
 }
 
 // Three-axis rotary positions: ``positions`` is the temporal axis, ``pos_h`` / ``pos_w`` the row and column axes (both
-// null: one axis); ``mrope_h`` / ``mrope_w`` are the frequency-slot counts of those two axes.
+// null: one axis); ``mrope_h`` / ``mrope_w`` are the frequency-slot counts of those two axes.  ``qkv_bias`` (or null) is
+// added to every q / k / v row as it is read.
 int cb_rope_kv_write_axes(const void* qkv, void* q_out, void* cache, const void* positions, const void* pos_h,
-                          const void* pos_w, int mrope_h, int mrope_w, const void* slots, const void* q_norm,
-                          const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D, int rotary_dim,
-                          float eps, int k_bits, int v_bits, int rotate, void* stream);
+                          const void* pos_w, int mrope_h, int mrope_w, const void* qkv_bias, const void* slots,
+                          const void* q_norm, const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D,
+                          int rotary_dim, float eps, int k_bits, int v_bits, int rotate, void* stream);
 
 int cb_rope_kv_write(const void* qkv, void* q_out, void* cache, const void* positions, const void* slots,
                      const void* q_norm, const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D,
                      int rotary_dim, float eps, int k_bits, int v_bits, int rotate, void* stream) {
-  return cb_rope_kv_write_axes(qkv, q_out, cache, positions, nullptr, nullptr, 0, 0, slots, q_norm, k_norm, inv_freq, T,
-                               Hq, Hkv, D, rotary_dim, eps, k_bits, v_bits, rotate, stream);
+  return cb_rope_kv_write_axes(qkv, q_out, cache, positions, nullptr, nullptr, 0, 0, nullptr, slots, q_norm, k_norm,
+                               inv_freq, T, Hq, Hkv, D, rotary_dim, eps, k_bits, v_bits, rotate, stream);
 }
 
 int cb_rope_kv_write_axes(const void* qkv, void* q_out, void* cache, const void* positions, const void* pos_h,
-                          const void* pos_w, int mrope_h, int mrope_w, const void* slots, const void* q_norm,
-                          const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D, int rotary_dim,
-                          float eps, int k_bits, int v_bits, int rotate, void* stream) {
+                          const void* pos_w, int mrope_h, int mrope_w, const void* qkv_bias, const void* slots,
+                          const void* q_norm, const void* k_norm, const void* inv_freq, int T, int Hq, int Hkv, int D,
+                          int rotary_dim, float eps, int k_bits, int v_bits, int rotate, void* stream) {
   using namespace cb;
   if (T <= 0) return 0;
   if (D != 128) return -10;
@@ -255,6 +263,7 @@ int cb_rope_kv_write_axes(const void* qkv, void* q_out, void* cache, const void*
   p.pos_w = static_cast<const int*>(pos_w);
   p.mrope_h = mrope_h;
   p.mrope_w = mrope_w;
+  p.qkv_bias = static_cast<const __nv_bfloat16*>(qkv_bias);
   p.qkv = static_cast<const __nv_bfloat16*>(qkv);
   p.q_out = static_cast<__nv_bfloat16*>(q_out);
   p.cache = static_cast<uint8_t*>(cache);

@@ -406,9 +406,9 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
         return _slice_rows(payload(module), method, lo, hi, n, q.bits), (hi - lo, ck_shapes[module][1])
 
     ck_shapes, _ = logical_inventory(cfg)
-    if cfg.shared_intermediate_size or cfg.qkv_bias:
-        raise CheckpointError("shared experts and projection biases are served by the eager execution mode "
-                              "(--execution-mode eager); the native runner has no kernels for them")
+    if cfg.shared_intermediate_size:
+        raise CheckpointError("shared experts are served by the eager execution mode (--execution-mode eager); the "
+                              "native runner has no kernels for them")
     layers = []
     for i in range(*(layer_range or (0, cfg.num_layers))):
         m = _layer_modules(cfg, i)
@@ -474,6 +474,13 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
                           attn_gate=None if attn_gate is None else attn_gate.to(device),
                           gate_up=None if gu is None else gu.to(device), down=None if down is None else down.to(device),
                           moe=moe)
+        if cfg.qkv_bias and gdn is None:
+            if cfg.attn_output_gate:
+                raise CheckpointError("projection biases together with a gated query projection are not served")
+            # this rank's heads of the q / k / v biases, in the order of the fused projection's rows
+            bq, bk, bv = (ck.store.get(f"{m[k]}.bias").float() for k in ("q", "k", "v"))
+            lw.qkv_bias = torch.cat([bq[tp_rank * hq * D:(tp_rank + 1) * hq * D], bk[kv_first * D:(kv_first + hkv) * D],
+                                     bv[kv_first * D:(kv_first + hkv) * D]]).to(device, bf).contiguous()
         if cfg.qk_norm and gdn is None:
             # the kernels multiply by the vector they are given: checkpoints with zero-centred norms store w of (1 + w)
             one = 1.0 if cfg.zero_centered_norm else 0.0

@@ -51,6 +51,7 @@ class LayerWeights:
     q_norm: torch.Tensor | None = None
     k_norm: torch.Tensor | None = None
     moe: object | None = None
+    qkv_bias: torch.Tensor | None = None            # bf16 [(hq + 2 hkv) D]: q / k / v projection biases of this rank's heads
 
 
 @dataclass
@@ -220,6 +221,9 @@ def random_decoder_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
         if cfg.qk_norm and lw.gdn is None:
             lw.q_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
             lw.k_norm = torch.ones(D, device=device, dtype=torch.bfloat16)
+        if cfg.qkv_bias and lw.gdn is None:
+            full = torch.randn((cfg.num_q_heads + 2 * cfg.num_kv_heads) * D, 1, device=device, generator=gen) * std
+            lw.qkv_bias = qkv_rows(full).flatten().to(torch.bfloat16).contiguous()
         if cfg.is_moe:
             from .moe import random_moe_weights
             lw.moe = random_moe_weights(cfg, device, gen, tp_rank, tp_size, std, layer_seed=seed * 4096000 + li,
@@ -504,7 +508,7 @@ class DecoderRunner:
                 K.rope_kv_write(qkv, q, self.kv[li], b.positions[t0:t1], b.slots[t0:t1], self.inv_freq, self.hq, self.hkv,
                                 self.D, self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
                                 rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation, positions_hw=hw,
-                                mrope_section=cfg.mrope_section if hw is not None else None)
+                                mrope_section=cfg.mrope_section if hw is not None else None, qkv_bias=lw.qkv_bias)
                 K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
                                   b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
                                   splits=b.attn_splits, ws=self.ws)
@@ -588,7 +592,7 @@ class DecoderRunner:
             f.gemm_gather(lw.qkv, qkv, s)
             K.rope_kv_write(qkv, q, self.kv[li], b.positions, b.slots, self.inv_freq, self.hq, self.hkv, self.D,
                             self.k_bits, self.v_bits, q_norm=lw.q_norm, k_norm=lw.k_norm, eps=cfg.rms_eps,
-                            rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation)
+                            rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation, qkv_bias=lw.qkv_bias)
             K.paged_attention(q.view(T, self.hq, self.D), attn.view(T, self.hq, self.D), self.kv[li], b.page_table,
                               b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, self.hq, self.hkv,
                               self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)

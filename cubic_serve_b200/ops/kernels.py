@@ -418,27 +418,34 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor, p
                   k_bits: int, v_bits: int, q_norm: torch.Tensor | None = None,
                   k_norm: torch.Tensor | None = None, eps: float = 1e-6, rotary_dim: int | None = None,
                   rotate: bool = False, positions_hw: tuple[torch.Tensor, torch.Tensor] | None = None,
-                  mrope_section: tuple[int, int, int] | None = None) -> None:
+                  mrope_section: tuple[int, int, int] | None = None, qkv_bias: torch.Tensor | None = None) -> None:
     """``rotate``: every q / k / v head vector is Walsh-Hadamard transformed (after RoPE) before it is written, which
     spreads outlier channels over the 32-channel quantization groups; ``q . k`` is unchanged and the attention
     output is transformed back with ``hadamard`` (reference: ``ops/cuda/cache_rotation_native.cu:12``).
     ``positions_hw``: int32 row- and column-axis positions ``[T]`` each; with them ``positions`` is the temporal axis
     and ``mrope_section`` says how many frequency slots follow each axis (interleaved layout; reference:
-    ``ops/cuda/position/qwen_mrope.py:25``)."""
+    ``ops/cuda/position/qwen_mrope.py:25``).  ``qkv_bias``: bf16 ``[(hq + 2 hkv) head_dim]`` added to the rows as they
+    are read (projection biases of the Qwen2 family)."""
     t = qkv.shape[0]
     rot = head_dim if rotary_dim is None else rotary_dim
-    if positions_hw is None:
+    if qkv_bias is not None:
+        assert qkv_bias.dtype == torch.bfloat16 and qkv_bias.numel() == (hq + 2 * hkv) * head_dim and qkv_bias.is_contiguous()
+    if positions_hw is None and qkv_bias is None:
         code = native.lib().cb_rope_kv_write(qkv.data_ptr(), q_out.data_ptr(), cache.data_ptr(), positions.data_ptr(),
                                              slots.data_ptr(), _ptr(q_norm), _ptr(k_norm), inv_freq.data_ptr(), t, hq,
                                              hkv, head_dim, rot, float(eps), k_bits, v_bits, int(rotate), _stream())
         native.check(code, "cb_rope_kv_write")
         return
-    if mrope_section is None or sum(mrope_section) != rot // 2:
-        raise ValueError("three-axis positions need the section counts of the rotary width")
-    ph, pw = positions_hw
-    assert ph.dtype == pw.dtype == torch.int32 and ph.numel() >= t and pw.numel() >= t
+    ph = pw = None
+    sec = (0, 0, 0)
+    if positions_hw is not None:
+        if mrope_section is None or sum(mrope_section) != rot // 2:
+            raise ValueError("three-axis positions need the section counts of the rotary width")
+        ph, pw = positions_hw
+        sec = mrope_section
+        assert ph.dtype == pw.dtype == torch.int32 and ph.numel() >= t and pw.numel() >= t
     code = native.lib().cb_rope_kv_write_axes(qkv.data_ptr(), q_out.data_ptr(), cache.data_ptr(), positions.data_ptr(),
-                                              ph.data_ptr(), pw.data_ptr(), int(mrope_section[1]), int(mrope_section[2]),
+                                              _ptr(ph), _ptr(pw), int(sec[1]), int(sec[2]), _ptr(qkv_bias),
                                               slots.data_ptr(), _ptr(q_norm), _ptr(k_norm), inv_freq.data_ptr(), t, hq,
                                               hkv, head_dim, rot, float(eps), k_bits, v_bits, int(rotate), _stream())
     native.check(code, "cb_rope_kv_write_axes")

@@ -189,7 +189,7 @@ def _declare(l: ctypes.CDLL) -> None:
     l.cb_hadamard.argtypes = [vp, i, vp, i, i, i, vp]
     l.cb_hadamard.restype = i
     l.cb_rope_kv_write.restype = i
-    l.cb_rope_kv_write_axes.argtypes = [vp, vp, vp, vp, vp, vp, i, i, vp, vp, vp, vp, i, i, i, i, i, f, i, i, i, vp]
+    l.cb_rope_kv_write_axes.argtypes = [vp, vp, vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, i, i, i, vp]
     l.cb_rope_kv_write_axes.restype = i
     l.cb_copy_pages.argtypes = [vp, vp, vp, i, ll, vp]
     l.cb_copy_pages.restype = i

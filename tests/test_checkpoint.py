@@ -334,3 +334,23 @@ def test_fp8_block_experts_load_as_stacked_e4m3(tmp_path):
         mod = f"model.layers.0.mlp.experts.{e}.down_proj"
         want = formats.fp8_dense({k: t[f"{mod}.{k}"] for k in ("weight", "weight_scale_inv") if f"{mod}.{k}" in t})
         assert torch.equal(wq_pack.unpack_to_dense(one), want)
+
+
+def test_projection_biases_follow_the_rank_heads(tmp_path):
+    """Qwen2-style q / k / v biases: the loader hands every rank the biases of its own heads in the order of the fused
+    projection's rows; random weights of a partition are slices of the one-GPU model's."""
+    from cubic_serve_b200.models.decoder import random_decoder_weights
+    cfg = replace(BASE, qk_norm=False, qkv_bias=True, name="Qwen2ForCausalLM", quant=QuantSpec("int", 4, 128))
+    ck = C.admit_checkpoint(C.write_random_checkpoint(tmp_path / "b", cfg, seed=3))
+    assert ck.cfg.qkv_bias and not ck.cfg.qk_norm
+    bq, bk, bv = (ck.store.get(f"model.layers.1.self_attn.{n}_proj.bias").float() for n in "qkv")
+    whole = C.load_decoder_weights(ck, "cpu").layers[1].qkv_bias
+    assert torch.equal(whole.float(), torch.cat([bq, bk, bv]))
+    r1 = C.load_decoder_weights(ck, "cpu", tp_rank=1, tp_size=2).layers[1].qkv_bias
+    hq, hkv = cfg.q_size // 2, cfg.kv_size // 2
+    assert torch.equal(r1.float(), torch.cat([bq[hq:], bk[hkv:], bv[hkv:]]))
+    one = random_decoder_weights(cfg, "cpu", seed=5).layers[0].qkv_bias
+    half = random_decoder_weights(cfg, "cpu", seed=5, tp_rank=1, tp_size=2).layers[0].qkv_bias
+    assert torch.equal(half, torch.cat([one[hq:cfg.q_size], one[cfg.q_size + hkv:cfg.q_size + cfg.kv_size],
+                                        one[cfg.q_size + cfg.kv_size + hkv:]]))
+    assert random_decoder_weights(replace(cfg, qkv_bias=False), "cpu", seed=5).layers[0].qkv_bias is None
