@@ -406,9 +406,9 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
         return _slice_rows(payload(module), method, lo, hi, n, q.bits), (hi - lo, ck_shapes[module][1])
 
     ck_shapes, _ = logical_inventory(cfg)
-    if cfg.shared_intermediate_size:
-        raise CheckpointError("shared experts are served by the eager execution mode (--execution-mode eager); the "
-                              "native runner has no kernels for them")
+    if cfg.head_dim != 128:
+        raise CheckpointError(f"attention heads of width {cfg.head_dim} are served by the eager execution mode "
+                              "(--execution-mode eager); the native attention kernels are built for 128")
     layers = []
     for i in range(*(layer_range or (0, cfg.num_layers))):
         m = _layer_modules(cfg, i)
@@ -574,7 +574,8 @@ def write_random_checkpoint(path: str | Path, cfg: ModelConfig, seed: int = 0, s
         else:
             tensors[name] = (torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * std).to(torch.bfloat16)
     save_file(tensors, str(path / "model.safetensors"))
-    arch = "Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_norm else "LlamaForCausalLM")
+    arch = ("Qwen3MoeForCausalLM" if cfg.qk_norm else "Qwen2MoeForCausalLM") if cfg.is_moe else \
+        ("Qwen3ForCausalLM" if cfg.qk_norm else "LlamaForCausalLM")
     hf = {"architectures": ["Qwen3NextForCausalLM" if cfg.is_hybrid else arch],
           "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_q_heads,
           "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim, "intermediate_size": cfg.intermediate_size,

@@ -70,7 +70,7 @@ class DecoderWeights:
             if l.gdn is not None:
                 ws += [l.gdn.in_proj, l.gdn.in_ba, l.gdn.out]
             if l.moe is not None:
-                ws += [l.moe.router, l.moe.gate_up, l.moe.down]
+                ws += [l.moe.router, l.moe.gate_up, l.moe.down, l.moe.shared_gate_up, l.moe.shared_down]
             for w in ws:
                 if w is not None:
                     total += w.nbytes
@@ -359,6 +359,8 @@ class DecoderRunner:
         self.ep = None
         if cfg.is_moe and tp is not None and tp.fused is not None:
             # expert parallelism over the tensor-parallel group: fused dispatch / combine on the row-sharded stream
+            if any(lw.moe is not None and lw.moe.shared_gate_up is not None for lw in weights.layers):
+                raise ValueError("shared experts use the NCCL tensor-parallel collectives (tp mode 'nccl')")
             if any(lw.moe is not None and lw.moe.expert_count * self.tp_size != cfg.num_experts for lw in weights.layers):
                 raise ValueError("experts divided into feature lanes use the NCCL tensor-parallel collectives "
                                  "(tp mode 'nccl'): the fused dispatch moves rows to owners of WHOLE experts")

@@ -55,10 +55,33 @@ class MoeLayer:
     normalize: bool = True
     scratch: K.MoeScratch | None = None
     launches: int = 7
+    # shared expert (Qwen2-MoE / Qwen3.5-MoE): a dense SwiGLU feed-forward over every token whose output is scaled by
+    # sigmoid(x . gate) and added to the routed experts' sum.  Under tensor parallelism a rank holds its share of the
+    # intermediate features (a partial sum like the routed part); the gate vector is replicated.
+    shared_gate_up: wq_pack.PackedWeight | None = None    # [2 Is(/tp), H]
+    shared_down: wq_pack.PackedWeight | None = None       # [H, Is(/tp)]
+    shared_gate: wq_pack.PackedWeight | None = None       # bf16 [8, H]: row 0 is the gate vector, the others zero
 
     def fuse_activation(self) -> None:
         """Re-order every expert's ``[gate; up]`` rows so that the grouped GEMM applies SwiGLU in its epilogue."""
         self.gate_up = wq_pack.swiglu_interleave(self.gate_up, stacked=True)
+        if self.shared_gate_up is not None and (self.shared_gate_up.n // 2) % 16 == 0 \
+                and self.shared_gate_up.fmt != wq_pack.FMT_FP8_BLOCK:
+            self.shared_gate_up = wq_pack.swiglu_interleave(self.shared_gate_up)
+
+    def _shared(self, x: torch.Tensor, out: torch.Tensor, ws) -> None:
+        """``out += sigmoid(x . gate) * shared_expert(x)`` (fixed buffers: the step may be captured in a CUDA graph)."""
+        t = x.shape[0]
+        act = self.sh_act[:t]
+        if self.shared_gate_up.act_interleaved:
+            K.wq_gemm_act(x, self.shared_gate_up, out=act, ws=ws)
+        else:
+            K.wq_gemm(x, self.shared_gate_up, out=self.sh_gu[:t], ws=ws)
+            K.swiglu(self.sh_gu[:t], out=act)
+        K.wq_gemm(act, self.shared_down, out=self.sh_out[:t], ws=ws)
+        K.wq_gemm(x, self.shared_gate, out=self.sh_logit[:t], ws=ws)
+        torch.sigmoid(self.sh_logit[:t, :1], out=self.sh_sig[:t])
+        out.addcmul_(self.sh_out[:t], self.sh_sig[:t])
 
     def experts(self, sc: K.MoeScratch, rows: int, ws) -> None:
         """Grouped gate/up GEMM, SwiGLU, grouped down GEMM over the sorted rows ``sc.xs`` -> ``sc.y``."""
@@ -78,6 +101,13 @@ class MoeLayer:
             self.scratch = K.MoeScratch(max_tokens, self.top_k, hidden, self.gate_up.n, self.expert_count, mb, device)
             self.logits = torch.empty(max_tokens, self.num_experts, dtype=torch.bfloat16, device=device)
             self.out = torch.empty(max_tokens, hidden, dtype=torch.bfloat16, device=device)
+            if self.shared_gate_up is not None:
+                bf = dict(dtype=torch.bfloat16, device=device)
+                self.sh_gu = torch.empty(max_tokens, self.shared_gate_up.n, **bf)
+                self.sh_act = torch.empty(max_tokens, self.shared_gate_up.n // 2, **bf)
+                self.sh_out = torch.empty(max_tokens, hidden, **bf)
+                self.sh_logit = torch.empty(max_tokens, self.shared_gate.n, **bf)
+                self.sh_sig = torch.empty(max_tokens, 1, **bf)
         return self.scratch
 
     def forward(self, x: torch.Tensor, runner=None, residual: torch.Tensor | None = None,
@@ -93,7 +123,10 @@ class MoeLayer:
         K.moe_route(logits, x, self.top_k, sc, self.normalize, self.expert_lo, self.expert_count)
         rows = t * self.top_k
         self.experts(sc, rows, ws)
-        return K.moe_combine(sc.y, sc, t, self.out[:t] if out is None else out, residual)
+        res = K.moe_combine(sc.y, sc, t, self.out[:t] if out is None else out, residual)
+        if self.shared_gate_up is not None:
+            self._shared(x, res, ws)
+        return res
 
 
 def expert_coordinates(tp_rank: int, tp_size: int, ep_size: int | None) -> tuple[int, int, int]:
@@ -134,8 +167,29 @@ def random_moe_weights(cfg: ModelConfig, device, gen, tp_rank: int = 0, tp_size:
         downs.append(quantize_linear(dn_full, cfg))
     gu, gcs, gms = stack_experts(gus)
     dn, dcs, dms = stack_experts(downs)
-    return MoeLayer(wq_pack.pack_bf16(router), gu, dn, (gcs, gms, dcs, dms), E, cfg.experts_per_token,
-                    owner * local, local, cfg.norm_topk_prob)
+    layer = MoeLayer(wq_pack.pack_bf16(router), gu, dn, (gcs, gms, dcs, dms), E, cfg.experts_per_token,
+                     owner * local, local, cfg.norm_topk_prob)
+    if cfg.shared_intermediate_size:
+        Is = cfg.shared_intermediate_size
+        if Is % tp_size or (Is // tp_size) % 128:
+            raise ValueError("every rank keeps whole 128-feature groups of the shared expert")
+        sl = Is // tp_size
+        sgu = torch.randn(2 * Is, H, device=device, generator=shared) * std
+        sdn = torch.randn(H, Is, device=device, generator=shared) * std
+        gate = torch.randn(1, H, device=device, generator=shared) * std
+        lo = tp_rank * sl
+        layer.shared_gate_up = quantize_linear(torch.cat([sgu[lo:lo + sl], sgu[Is + lo:Is + lo + sl]]), cfg)
+        layer.shared_down = quantize_linear(sdn[:, lo:lo + sl].contiguous(), cfg)
+        layer.shared_gate = shared_gate_matrix(gate)
+        layer.launches += 5
+    return layer
+
+
+def shared_gate_matrix(gate: torch.Tensor) -> wq_pack.PackedWeight:
+    """The shared expert's gate vector ``[1, H]`` as a bf16 GEMM operand of 8 rows (row 0 = the vector)."""
+    m = torch.zeros(8, gate.shape[-1], dtype=torch.bfloat16, device=gate.device)
+    m[0] = gate.reshape(-1).to(torch.bfloat16)
+    return wq_pack.pack_bf16(m)
 
 
 def load_moe_layer(ck, layer: int, device, tp_rank: int = 0, tp_size: int = 1) -> MoeLayer:
@@ -158,8 +212,23 @@ def load_moe_layer(ck, layer: int, device, tp_rank: int = 0, tp_size: int = 1) -
     gu, gcs, gms = stack_experts(gus)
     dn, dcs, dms = stack_experts(downs)
     router = ck.store.get(f"model.layers.{layer}.mlp.gate.weight").to(torch.bfloat16)
-    return MoeLayer(wq_pack.pack_bf16(router).to(device), gu.to(device), dn.to(device), (gcs, gms, dcs, dms), E,
-                    cfg.experts_per_token, tp_rank * local, local, cfg.norm_topk_prob)
+    out = MoeLayer(wq_pack.pack_bf16(router).to(device), gu.to(device), dn.to(device), (gcs, gms, dcs, dms), E,
+                   cfg.experts_per_token, tp_rank * local, local, cfg.norm_topk_prob)
+    if cfg.shared_intermediate_size:
+        from .checkpoint import _slice_rows
+        Is = cfg.shared_intermediate_size
+        if Is % tp_size or (Is // tp_size) % 128:
+            raise CheckpointError("every rank keeps whole 128-feature groups of the shared expert")
+        lo, hi = tp_rank * (Is // tp_size), (tp_rank + 1) * (Is // tp_size)
+        sp = f"model.layers.{layer}.mlp.shared_expert"
+        parts = [(_slice_rows(ck.payload(f"{sp}.{m}"), q.method, lo, hi, Is, q.bits), (hi - lo, cfg.hidden_size))
+                 for m in ("gate_proj", "up_proj")]
+        out.shared_gate_up = pack_logical(q.method, parts, q).to(device)
+        out.shared_down = pack_logical(q.method, [(ck.payload(f"{sp}.down_proj"), shapes[f"{sp}.down_proj"])], q,
+                                       (lo, hi)).to(device)
+        out.shared_gate = shared_gate_matrix(ck.store.get(f"model.layers.{layer}.mlp.shared_expert_gate.weight")).to(device)
+        out.launches += 5
+    return out
 
 
 def moe_reference(x: torch.Tensor, router: torch.Tensor, gate_up: list[torch.Tensor], down: list[torch.Tensor],

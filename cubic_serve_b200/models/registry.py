@@ -63,7 +63,7 @@ def _builtin() -> None:
                   build_runner=runner)
     register(ModelDefinition("gqa_decoder", ("LlamaForCausalLM", "Qwen2ForCausalLM", "Qwen3ForCausalLM", "MistralForCausalLM"),
                              description="grouped-query attention decoder with a SwiGLU feed-forward", **common))
-    register(ModelDefinition("gqa_moe", ("Qwen3MoeForCausalLM", "MixtralForCausalLM"),
+    register(ModelDefinition("gqa_moe", ("Qwen3MoeForCausalLM", "Qwen2MoeForCausalLM", "MixtralForCausalLM"),
                              description="grouped-query attention decoder with routed experts", **common))
     register(ModelDefinition("qwen3_5", ("Qwen3NextForCausalLM", "Qwen3_5ForCausalLM"),
                              description="hybrid decoder: Gated DeltaNet layers with periodic gated full attention", **common))

@@ -96,7 +96,8 @@ def run_check(cfg, dev, group, weights=None, requests: int = 16, prompt_len: int
     def both_modes(c, w):
         out = {}
         for mode in ("nccl", "fused"):
-            if (c.is_hybrid or c.quant.method == "fp8" or (ep_size or size) != size) and mode == "fused":
+            if (c.is_hybrid or c.quant.method == "fp8" or (ep_size or size) != size or c.shared_intermediate_size) \
+                    and mode == "fused":
                 continue          # these run with the NCCL collectives (see DecoderRunner)
             tp = TensorParallel(group, dev, mode=mode, hidden=c.hidden_size, max_tokens=T, rows_max=max(requests, 16))
             out[mode] = _step_logits(c, w, dev, tp, prompts, k_bits, v_bits)
@@ -169,6 +170,8 @@ def main(argv=None) -> None:
     ap.add_argument("--ep", type=int, default=0,
                     help="MoE: expert owners among the ranks (0 = every rank owns whole experts); the ranks of an owner "
                          "divide each expert's intermediate features")
+    ap.add_argument("--shared-expert", type=int, default=0, help="MoE: width of a sigmoid-gated shared expert (0 = none)")
+    ap.add_argument("--qkv-bias", action="store_true", help="biases on the q / k / v projections")
     ap.add_argument("--requests", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=48)
     ap.add_argument("--kv", default="8,8")
@@ -188,6 +191,10 @@ def main(argv=None) -> None:
         cfg = replace(cfg, num_experts=args.experts)
     if args.kv_heads:
         cfg = replace(cfg, num_kv_heads=args.kv_heads)
+    if args.shared_expert and cfg.is_moe:
+        cfg = replace(cfg, shared_intermediate_size=args.shared_expert)
+    if args.qkv_bias:
+        cfg = replace(cfg, qkv_bias=True)
     kb, vb = (int(b) for b in args.kv.split(","))
     report = run_check(cfg, dev, dist.group.WORLD, requests=args.requests, prompt_len=args.prompt_len, k_bits=kb, v_bits=vb,
                        tp1_layers=cfg.num_layers, ep_size=args.ep or None)

@@ -354,3 +354,30 @@ def test_projection_biases_follow_the_rank_heads(tmp_path):
     assert torch.equal(half, torch.cat([one[hq:cfg.q_size], one[cfg.q_size + hkv:cfg.q_size + cfg.kv_size],
                                         one[cfg.q_size + cfg.kv_size + hkv:]]))
     assert random_decoder_weights(replace(cfg, qkv_bias=False), "cpu", seed=5).layers[0].qkv_bias is None
+
+
+def test_shared_expert_is_loaded_per_rank(tmp_path):
+    """A sigmoid-gated shared expert beside the routed ones: admitted by the closed inventory, loaded as this rank's share
+    of its intermediate features; wide heads stay with the eager execution mode."""
+    cfg = ModelConfig(name="shared", family="gqa_moe", num_layers=1, hidden_size=256, num_q_heads=2, num_kv_heads=1,
+                      head_dim=128, intermediate_size=0, vocab_size=512, qk_norm=True, num_experts=4, experts_per_token=2,
+                      moe_intermediate_size=128, shared_intermediate_size=256, quant=QuantSpec("cubic", 4, 128))
+    ck = C.admit_checkpoint(C.write_random_checkpoint(tmp_path / "s", cfg, seed=3, std=0.05))
+    sp = "model.layers.0.mlp.shared_expert"
+    gate = C._dense_of("cubic", ck.payload(f"{sp}.gate_proj"), (256, 256), cfg.quant)
+    up = C._dense_of("cubic", ck.payload(f"{sp}.up_proj"), (256, 256), cfg.quant)
+    down = C._dense_of("cubic", ck.payload(f"{sp}.down_proj"), (256, 256), cfg.quant)
+    for tp, rank in ((1, 0), (2, 1)):
+        moe = C.load_decoder_weights(ck, "cpu", tp_rank=rank, tp_size=tp).layers[0].moe
+        lo, hi = rank * 256 // tp, (rank + 1) * 256 // tp
+        gu = wq_pack.unpack_to_dense(moe.shared_gate_up)[:2 * (hi - lo)]
+        assert ((gu - torch.cat([gate[lo:hi], up[lo:hi]])).norm() / gu.norm()).item() < 6e-3
+        dn = wq_pack.unpack_to_dense(moe.shared_down)[:256]
+        assert ((dn - down[:, lo:hi]).norm() / dn.norm()).item() < 6e-3
+        g = wq_pack.unpack_to_dense(moe.shared_gate)
+        want = ck.store.get("model.layers.0.mlp.shared_expert_gate.weight").float()
+        assert torch.equal(g[:1].float(), want.to(torch.bfloat16).float()) and float(g[1:].abs().max()) == 0
+    wide = replace(cfg, head_dim=256, name="wide")
+    ck2 = C.admit_checkpoint(C.write_random_checkpoint(tmp_path / "w", wide, seed=3))
+    with pytest.raises(C.CheckpointError, match="eager execution mode"):
+        C.load_decoder_weights(ck2, "cpu")
