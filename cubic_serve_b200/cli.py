@@ -202,25 +202,52 @@ def _kv_bits(name: str) -> int:
 
 
 def _reference(args) -> int:
-    """``cubic reference``: the reference's ``reference-qwen3-5`` subcommand for this build's oracle decoder."""
+    """``cubic reference``: greedy decoding of a prompt of token ids on the eager models (the reference's
+    ``reference-qwen3-5`` subcommand for every family of this build: dense decoders on the reference decoder, experts /
+    hybrid layers / biases / wide heads on the family model, ``qwen4_exp`` on its own)."""
     import torch
 
     from .models.config import NAMED_CONFIGS
-    from .models.reference import EagerDecoder, dense_weights_from_checkpoint, random_dense_weights
+    from .runtime.serving import _model_type_of
+    kb, vb = (int(b) for b in args.kv.split(","))
+    kv_bits = None if kb >= 16 and vb >= 16 else (kb, vb)
+    ck = None
     if args.model.startswith("random:"):
         cfg = NAMED_CONFIGS[args.model.split(":", 1)[1]]()
-        weights = random_dense_weights(cfg, args.seed)
+    elif _model_type_of(args.model) == "qwen4_exp":
+        cfg = None
     else:
         from .models.checkpoint import admit_checkpoint
         ck = admit_checkpoint(args.model)
-        cfg, weights = ck.cfg, dense_weights_from_checkpoint(ck)
+        cfg = ck.cfg
+    stateful = None
+    if cfg is None or getattr(cfg, "family", "") == "qwen4_exp":
+        from .models.qwen4_exp import Qwen4ExpModel, admit_qwen4_exp_checkpoint, random_qwen4_exp_weights
+        if cfg is None:
+            cfg, weights, _ = admit_qwen4_exp_checkpoint(args.model)
+        else:
+            weights = random_qwen4_exp_weights(cfg, args.seed)
+        stateful = Qwen4ExpModel(cfg, weights)
+    elif cfg.is_moe or cfg.is_hybrid or cfg.qkv_bias:
+        from .models.eager_family import EagerFamilyModel, family_weights_from_checkpoint, random_family_weights
+        stateful = EagerFamilyModel(cfg, family_weights_from_checkpoint(ck) if ck is not None
+                                    else random_family_weights(cfg, args.seed), kv_bits)
     ids = [int(t) for t in args.prompt_ids.split(",") if t.strip()]
     if not ids or any(t < 0 or t >= cfg.vocab_size for t in ids):
         raise SystemExit(f"prompt ids must lie in [0, {cfg.vocab_size})")
-    kb, vb = (int(b) for b in args.kv.split(","))
-    dec = EagerDecoder(cfg, weights, kv_bits=None if kb >= 16 and vb >= 16 else (kb, vb))
-    tokens, _ = dec.generate(torch.tensor([ids]), args.max_tokens)
-    print(json.dumps({"model": cfg.name, "prompt_ids": ids, "output_ids": [int(t) for t in tokens[0]]}))
+    if stateful is not None:
+        logits, state = stateful.forward(ids, last_only=True)
+        out = []
+        for _ in range(args.max_tokens):
+            out.append(int(logits[0].argmax()))
+            if len(out) < args.max_tokens:
+                logits, state = stateful.forward([out[-1]], state, last_only=True)
+    else:
+        from .models.reference import EagerDecoder, dense_weights_from_checkpoint, random_dense_weights
+        weights = dense_weights_from_checkpoint(ck) if ck is not None else random_dense_weights(cfg, args.seed)
+        tokens, _ = EagerDecoder(cfg, weights, kv_bits=kv_bits).generate(torch.tensor([ids]), args.max_tokens)
+        out = [int(t) for t in tokens[0]]
+    print(json.dumps({"model": cfg.name, "family": getattr(cfg, "family", "?"), "prompt_ids": ids, "output_ids": out}))
     return 0
 
 
