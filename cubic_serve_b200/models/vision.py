@@ -178,6 +178,17 @@ def shard_vision_weights(cfg: VisionConfig, weights: Mapping[str, torch.Tensor],
     return out
 
 
+def group_reduce(group=None) -> Callable[[torch.Tensor], torch.Tensor]:
+    """The ``reduce`` of a sharded tower bound to a ``torch.distributed`` group: the partial rows of a row-parallel
+    projection summed over the ranks of the first pipeline stage (every rank gets the same bits)."""
+    import torch.distributed as dist
+
+    def reduce(t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=group)
+        return t
+    return reduce
+
+
 # ------------------------------------------------------------------ geometry of a request's grids
 def _grids(grid_thw) -> list[tuple[int, int, int]]:
     g = torch.as_tensor(grid_thw).reshape(-1, 3).tolist()

@@ -473,3 +473,43 @@ def test_http_request_with_an_image_goes_through_the_encoder_thread():
     assert threads and all(t == "vision-encoder" for t in threads)
     assert svc.store.hits >= 1 and "messages" in json.dumps(json.loads(b4))
     svc.close()
+
+
+def _tower_rank(rank, world, port, q):
+    import datetime
+    import os
+
+    import torch.distributed as dist
+
+    from cubic_serve_b200.models.vision import group_reduce
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    torch.set_num_threads(1)
+    cfg = _cfg()
+    w = random_vision_weights(cfg, 3)
+    px = torch.randn(40, cfg.patch_width, generator=torch.Generator().manual_seed(4))
+    enc = VisionEncoder(cfg, shard_vision_weights(cfg, w, rank, world), rank, world, group_reduce())
+    q.put((rank, enc.encode(px, torch.tensor([[1, 4, 6], [1, 4, 4]]))[0]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tower_sharded_over_a_process_group():
+    import socket
+
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_tower_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    cfg = _cfg()
+    px = torch.randn(40, cfg.patch_width, generator=torch.Generator().manual_seed(4))
+    want, _ = VisionEncoder(cfg, random_vision_weights(cfg, 3)).encode(px, torch.tensor([[1, 4, 6], [1, 4, 4]]))
+    assert torch.equal(got[0], got[1]) and (got[0] - want).abs().max() < 1e-5
