@@ -406,7 +406,7 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
         return _slice_rows(payload(module), method, lo, hi, n, q.bits), (hi - lo, ck_shapes[module][1])
 
     ck_shapes, _ = logical_inventory(cfg)
-    if cfg.head_dim != 128:
+    if cfg.head_dim > 128:
         raise CheckpointError(f"attention heads of width {cfg.head_dim} are served by the eager execution mode "
                               "(--execution-mode eager); the native attention kernels are built for 128")
     layers = []
