@@ -179,6 +179,9 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--media-file-root", action="append", default=[], help="directory file: media may be read from")
     g.add_argument("--media-http-host", action="append", default=[], help="host name http(s): media may be fetched from")
     g.add_argument("--max-media-items", type=int, default=16)
+    g.add_argument("--encoder-graph-buckets", default="",
+                   help="comma-separated patch capacities (e.g. 1024,4096): encode calls that fit replay a CUDA graph of the "
+                        "vision tower captured for the smallest bucket that holds them (off by default: eager calls)")
     g = s.add_argument_group("Advanced")
     g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
     g.add_argument("--startup-numerical-audit", action="store_true",

@@ -119,12 +119,72 @@ class EncoderMemoryPlan:
         return rows
 
 
+class VisionGraphBucket:
+    """One captured encode call of ``capacity`` patches: fixed-address inputs, the tower's fixed-shape form recorded in a
+    CUDA graph after two eager warm-up runs, replayed for every item that fits.  A small image is bound by the
+    launches of the tower's ~16 kernels per layer; a replay issues them as one graph.  On a host without CUDA the
+    bucket runs the fixed-shape form eagerly (the arithmetic is the same; tests use this)."""
+
+    def __init__(self, encoder: VisionEncoder, capacity: int) -> None:
+        cfg = encoder.cfg
+        m2 = cfg.spatial_merge_size ** 2
+        if capacity <= 0 or capacity % m2:
+            raise ValueError("a bucket holds whole merge blocks")
+        self.encoder, self.capacity = encoder, capacity
+        dev = encoder.device
+        self.px = torch.zeros(capacity, cfg.patch_width, dtype=encoder.dtype, device=dev)
+        self.fx = encoder.fixed_inputs(torch.tensor([[1, cfg.spatial_merge_size, cfg.spatial_merge_size]]), capacity)
+        self.out: torch.Tensor | None = None
+        self.graph = None
+        self.replays = 0
+
+    def _capture(self) -> None:
+        enc = self.encoder
+        if not str(enc.device).startswith("cuda"):
+            return
+        side = torch.cuda.Stream(enc.device)
+        side.wait_stream(torch.cuda.current_stream(enc.device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                enc.encode_fixed(self.px, self.fx)
+        torch.cuda.current_stream(enc.device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        # the capture runs on the encoder's own thread while the engine thread keeps launching: only this thread's
+        # calls belong to it
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.out = enc.encode_fixed(self.px, self.fx)
+
+    def encode(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+        enc = self.encoder
+        n = int(pixel_values.shape[0])
+        new = enc.fixed_inputs(grid_thw, self.capacity)
+        for k, t in new.items():
+            self.fx[k].copy_(t)
+        self.px.zero_()
+        self.px[:n].copy_(pixel_values.to(enc.device, enc.dtype))
+        if self.graph is None and self.out is None:
+            self._capture()
+        if self.graph is not None:
+            self.graph.replay()
+            out = self.out
+        else:
+            out = enc.encode_fixed(self.px, self.fx)
+        self.replays += 1
+        rows = n // enc.cfg.spatial_merge_size ** 2
+        return out[:rows].clone()
+
+
 class VisionService:
     """Encodes media items ``(pixels [patches, width] float32, grid)`` to feature rows, through the store."""
 
     def __init__(self, encoder: VisionEncoder, store: EncodedFeatureStore | None = None,
-                 memory_bytes: int = 2 << 30, max_prompt_tokens: int = 1 << 15, identity: bytes = b"") -> None:
+                 memory_bytes: int = 2 << 30, max_prompt_tokens: int = 1 << 15, identity: bytes = b"",
+                 graph_buckets: tuple[int, ...] = ()) -> None:
+        """``graph_buckets``: patch capacities of captured encode calls (ascending); a call of at most that many patches
+        replays the smallest bucket that holds it, larger calls run eagerly.  Not used by a sharded tower (its
+        collectives are not captured)."""
         self.encoder = encoder
+        self.buckets = [VisionGraphBucket(encoder, c) for c in sorted(set(graph_buckets))] if encoder.tp_size == 1 else []
         self.store = store if store is not None else EncodedFeatureStore()
         self.plan = EncoderMemoryPlan.build(encoder, memory_bytes, max_prompt_tokens)
         self.identity = identity
@@ -151,7 +211,12 @@ class VisionService:
                 parts = []
                 for f0, f1 in self.plan.calls(grid):
                     px = torch.from_numpy(np.ascontiguousarray(pixels[f0 * h * w:f1 * h * w]))
-                    feats, _ = self.encoder.encode(px, torch.tensor([[f1 - f0, h, w]]))
+                    call_grid = torch.tensor([[f1 - f0, h, w]])
+                    bucket = next((b for b in self.buckets if b.capacity >= px.shape[0]), None)
+                    if bucket is not None and not self.encoder.cfg.deepstack_visual_indexes:
+                        feats = bucket.encode(px, call_grid)
+                    else:
+                        feats, _ = self.encoder.encode(px, call_grid)
                     parts.append(feats)
                     self.encode_calls += 1
                 rows = torch.cat(parts, 0) if len(parts) > 1 else parts[0]

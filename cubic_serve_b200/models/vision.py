@@ -337,6 +337,57 @@ class VisionEncoder:
         self.encoded_patches += int(pixel_values.shape[0])
         return self._merge(x, "merger", False), deep
 
+    # ------------------------------------------------------------------ fixed-shape form (CUDA-graph buckets)
+    def fixed_inputs(self, grid_thw, capacity: int) -> dict[str, torch.Tensor]:
+        """Everything of ``encode`` that depends on the grids, padded to ``capacity`` patches: table reads and weights,
+        rotary cosines / sines, and the attention mask (a patch sees the patches of its own frame; a padding row sees
+        itself, so no row of the softmax is empty)."""
+        cfg, dev, m = self.cfg, self.device, self.cfg.spatial_merge_size
+        lengths = frame_lengths(grid_thw)
+        n = sum(lengths)
+        if n > capacity or capacity % (m * m):
+            raise ValueError("the bucket holds whole merge blocks and at least the patches given")
+        idx = torch.zeros(4, capacity, dtype=torch.long, device=dev)
+        wts = torch.zeros(4, capacity, dtype=torch.float32, device=dev)
+        idx[:, :n], wts[:, :n] = bilinear_table_reads(grid_thw, cfg.side, m, dev)
+        pos = torch.zeros(capacity, 2, dtype=torch.float32, device=dev)
+        pos[:n] = patch_positions(grid_thw, m, dev).float()
+        ang = (pos[:, :, None] * self.inv_freq[None, None, :]).flatten(1)
+        ang = torch.cat((ang, ang), -1)[:, None, :]
+        frame = torch.arange(capacity, device=dev) + len(lengths)                  # padding rows: one frame each
+        frame[:n] = torch.repeat_interleave(torch.arange(len(lengths), device=dev),
+                                            torch.tensor(lengths, device=dev))
+        return {"idx": idx, "wts": wts, "cos": ang.cos(), "sin": ang.sin(), "mask": frame[:, None] == frame[None, :]}
+
+    @torch.no_grad()
+    def encode_fixed(self, pixel_values: torch.Tensor, fx: dict[str, torch.Tensor]) -> torch.Tensor:
+        """``encode`` on a full bucket: the same arithmetic with the frames separated by the mask instead of by slicing,
+        so every shape is fixed and the call can be captured in a CUDA graph.  Rows of real patches equal ``encode``'s;
+        rows of padding are finite and ignored by the caller."""
+        cfg = self.cfg
+        d = cfg.head_dim
+        x = F.linear(pixel_values.to(self.dtype), self.patch_w, self.w["patch_embed.proj.bias"])
+        table = self.w["pos_embed.weight"]
+        x = x + (table[fx["idx"]] * fx["wts"][:, :, None].to(table.dtype)).sum(0).to(x.dtype)
+        cos, sin, mask = fx["cos"], fx["sin"], fx["mask"]
+        n = x.shape[0]
+        for l in range(cfg.depth):
+            p = f"blocks.{l}"
+            h = self._norm(x, p + ".norm1")
+            qkv = F.linear(h, self.w[p + ".attn.qkv.weight"], self.w[p + ".attn.qkv.bias"]).view(n, 3, self.heads, d)
+            q, k, v = qkv.unbind(1)
+
+            def rot(t: torch.Tensor) -> torch.Tensor:
+                tf = t.float()
+                return (tf * cos + torch.cat((-tf[..., d // 2:], tf[..., :d // 2]), -1) * sin).to(t.dtype)
+            o = F.scaled_dot_product_attention(rot(q).transpose(0, 1)[None], rot(k).transpose(0, 1)[None],
+                                               v.transpose(0, 1)[None], attn_mask=mask)
+            x = x + self._row(o[0].transpose(0, 1).reshape(n, self.heads * d), p + ".attn.proj")
+            hmid = self._act(F.linear(self._norm(x, p + ".norm2"), self.w[p + ".mlp.linear_fc1.weight"],
+                                      self.w[p + ".mlp.linear_fc1.bias"]))
+            x = x + self._row(hmid, p + ".mlp.linear_fc2")
+        return self._merge(x, "merger", False)
+
     def activation_bytes(self, patches: int) -> int:
         """Upper bound of the transient memory one ``encode`` of ``patches`` rows holds: the residual, the normalised
         copy, q / k / v and the attention output, the MLP's hidden features, in the tower's dtype; rotary tables in

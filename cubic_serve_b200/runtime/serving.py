@@ -270,7 +270,9 @@ def build_media_processor(args, ck, tok, executor, max_len: int):
     encoder = VisionEncoder(ck.vision, load_vision_weights(ck, device, dtype))
     service = VisionService(encoder, EncodedFeatureStore(getattr(args, "feature_store_mib", 1024) << 20),
                             memory_bytes=int(getattr(args, "encoder_memory_gib", 2.0) * 2 ** 30),
-                            max_prompt_tokens=max_len - 1, identity=ck.cfg.name.encode())
+                            max_prompt_tokens=max_len - 1, identity=ck.cfg.name.encode(),
+                            graph_buckets=tuple(int(c) for c in str(getattr(args, "encoder_graph_buckets", "") or "").split(",")
+                                                if c.strip()))
     policy = MediaPolicy(file_roots=tuple(getattr(args, "media_file_root", ()) or ()),
                          http_hosts=tuple(getattr(args, "media_http_host", ()) or ()))
     log.info("vision tower: %d layers, %d patches per encoder call, feature store %d MiB", ck.vision.depth,

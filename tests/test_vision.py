@@ -513,3 +513,35 @@ def test_tower_sharded_over_a_process_group():
     px = torch.randn(40, cfg.patch_width, generator=torch.Generator().manual_seed(4))
     want, _ = VisionEncoder(cfg, random_vision_weights(cfg, 3)).encode(px, torch.tensor([[1, 4, 6], [1, 4, 4]]))
     assert torch.equal(got[0], got[1]) and (got[0] - want).abs().max() < 1e-5
+
+
+def test_fixed_shape_buckets_equal_the_exact_encode():
+    """The bucket form (padded to a capacity, frames separated by a mask) gives the rows of the exact call; the service
+    sends calls that fit to the smallest bucket and the rest to the eager path."""
+    from cubic_serve_b200.executor.vision import VisionGraphBucket
+    cfg = _cfg()
+    enc = VisionEncoder(cfg, random_vision_weights(cfg, 11))
+    g = torch.Generator().manual_seed(12)
+    for grid in ([[1, 4, 6]], [[3, 4, 4]], [[1, 2, 2]]):
+        n = sum(t * h * w for t, h, w in grid)
+        px = torch.randn(n, cfg.patch_width, generator=g)
+        want, _ = enc.encode(px, torch.tensor(grid))
+        got = VisionGraphBucket(enc, 64).encode(px, torch.tensor(grid))
+        assert got.shape == want.shape and (got - want).abs().max() < 1e-5
+    bucket = VisionGraphBucket(enc, 32)
+    a = bucket.encode(torch.randn(24, cfg.patch_width, generator=g), torch.tensor([[1, 4, 6]]))
+    px = torch.randn(16, cfg.patch_width, generator=g)
+    b = bucket.encode(px, torch.tensor([[1, 4, 4]]))                       # a reused bucket forgets the previous item
+    assert (b - enc.encode(px, torch.tensor([[1, 4, 4]]))[0]).abs().max() < 1e-5 and bucket.replays == 2 and a.shape[0] == 6
+    with pytest.raises(ValueError):
+        bucket.encode(torch.randn(48, cfg.patch_width), torch.tensor([[1, 8, 6]]))
+    with pytest.raises(ValueError):
+        VisionGraphBucket(enc, 30)
+    svc = VisionService(enc, graph_buckets=(16, 64))
+    small = np.random.default_rng(0).standard_normal((16, cfg.patch_width)).astype(np.float32)
+    big = np.random.default_rng(1).standard_normal((96, cfg.patch_width)).astype(np.float32)
+    rows_small = svc.encode([(small, (1, 4, 4))])[0][0]
+    rows_big = svc.encode([(big, (1, 8, 12))])[0][0]
+    assert [b.replays for b in svc.buckets] == [1, 0]
+    assert (rows_small - enc.encode(torch.from_numpy(small), torch.tensor([[1, 4, 4]]))[0]).abs().max() < 1e-5
+    assert rows_big.shape == (24, 32)
