@@ -303,6 +303,21 @@ def qwen4_exp_tensor_shapes(cfg: Qwen4ExpConfig) -> dict[str, tuple[int, ...]]:
     return s
 
 
+def qwen4_exp_mtp_tensor_shapes(cfg: Qwen4ExpConfig) -> dict[str, tuple[int, ...]]:
+    """Tensors of the draft head (``mtp.*``): projections of the next token's embedding and of the target's multi-stream
+    residual, one block-selective attention layer with experts, and its own final mixer; embeddings and ``lm_head`` are
+    the target's."""
+    H, sw = cfg.hidden_size, cfg.stream_width
+    s: dict[str, tuple[int, ...]] = {"mtp.pre_fc_norm_embedding.weight": (H,), "mtp.fc_embedding.weight": (H, H),
+                                     "mtp.pre_fc_norm_hidden.weight": (sw,), "mtp.fc_hidden.weight": (H, H)}
+    s.update(_stream_mixer("mtp.hyper_connection_mixer", cfg, inject=False))
+    one = replace(cfg, num_layers=1, layer_types=("full_attention",), ple_layer_ids=())
+    for name, shape in qwen4_exp_tensor_shapes(one).items():
+        if name.startswith(f"{LM}.layers.0."):
+            s["mtp.layers.0." + name[len(f"{LM}.layers.0."):]] = shape
+    return s
+
+
 def ngram_head_vocab_sizes(cfg: Qwen4ExpConfig) -> list[int]:
     """Moduli of the hash heads: distinct multiples of ``ngram_vocab_multiple`` upward from the base size, so the heads
     of one order collide on different ids; their sum fits the table."""
@@ -317,11 +332,14 @@ def ngram_head_vocab_sizes(cfg: Qwen4ExpConfig) -> list[int]:
     return sizes
 
 
-def random_qwen4_exp_weights(cfg: Qwen4ExpConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+def random_qwen4_exp_weights(cfg: Qwen4ExpConfig, seed: int = 0, std: float = 0.05, draft_head: bool = False) -> dict[str, torch.Tensor]:
     g = torch.Generator().manual_seed(seed)
     w: dict[str, torch.Tensor] = {}
     sizes = ngram_head_vocab_sizes(cfg) if cfg.ple_layer_ids else []
-    for name, shape in qwen4_exp_tensor_shapes(cfg).items():
+    shapes = dict(qwen4_exp_tensor_shapes(cfg))
+    if draft_head:
+        shapes.update(qwen4_exp_mtp_tensor_shapes(cfg))
+    for name, shape in shapes.items():
         if name.endswith("layer_multipliers"):
             w[name] = torch.randint(1, 1 << 40, shape, generator=g, dtype=torch.int64) * 2 + 1
         elif name.endswith("ngram_heads_vocab_sizes"):
@@ -344,7 +362,9 @@ def random_qwen4_exp_weights(cfg: Qwen4ExpConfig, seed: int = 0, std: float = 0.
 
 
 def check_qwen4_exp_weights(cfg: Qwen4ExpConfig, weights: Mapping[str, torch.Tensor]) -> None:
-    want = qwen4_exp_tensor_shapes(cfg)
+    want = dict(qwen4_exp_tensor_shapes(cfg))
+    if any(n.startswith("mtp.") for n in weights):
+        want.update(qwen4_exp_mtp_tensor_shapes(cfg))                  # the draft head comes whole or not at all
     missing, extra = sorted(set(want) - set(weights)), sorted(set(weights) - set(want))
     if missing or extra:
         raise Qwen4ExpConfigError(f"tensors missing {missing[:3]} unexpected {extra[:3]}")
@@ -585,52 +605,172 @@ class Qwen4ExpModel:
             mixed, n = self._mix(h, p + ".mlp_hyper_connection")
             h = self._inject(h, self._mlp(mixed, p + ".mlp"), n, p + ".mlp_hyper_connection")
         state.length = start + T
+        self.last_feedback = h                                        # the multi-stream residual before the final mixer
         mixed, _ = self._mix(h[-1:] if last_only else h, f"{LM}.hyper_connection_mixer")
         return self._lin(mixed, "lm_head"), state
 
+    # ------------------------------------------------------------------ draft head
+    @property
+    def has_draft_head(self) -> bool:
+        return "mtp.fc_hidden.weight" in self.w
+
+    @torch.no_grad()
+    def draft_forward(self, tokens: list[int], feedback: torch.Tensor, state: RequestState | None = None):
+        """The draft head on ``tokens`` (token ``i + 1`` of the sequence) paired with ``feedback`` (the target's
+        multi-stream residual at position ``i``, ``[T, S H]``): logits for token ``i + 2``, the head's own residual
+        (the feedback of the next proposal) and its state (one attention layer).  The embedding is normalised and
+        projected, every stream of the feedback is normalised over the whole multi-stream width and projected by the
+        same matrix, and the sum enters one decoder layer; the head has no lexical embedding."""
+        c, w = self.cfg, self.w
+        if not self.has_draft_head:
+            raise ValueError("the checkpoint carries no draft head")
+        T = len(tokens)
+        if feedback.shape != (T, c.stream_width):
+            raise ValueError("one multi-stream residual row per token")
+        state = state or RequestState()
+        if not state.layers:
+            state.layers = [LayerState()]
+        start = state.length
+        emb = w[f"{LM}.embed_tokens.weight"][torch.tensor([int(t) for t in tokens])]
+        pe = self._lin(eager.rmsnorm(emb, w["mtp.pre_fc_norm_embedding.weight"], c.rms_eps, True), "mtp.fc_embedding")
+        nf = eager.rmsnorm(feedback.float(), w["mtp.pre_fc_norm_hidden.weight"], c.rms_eps, True)
+        ph = self._lin(nf.view(T, c.streams, c.hidden_size), "mtp.fc_hidden")
+        h = (ph + pe[:, None, :]).flatten(-2)
+        pos3 = torch.arange(start, start + T)[None].expand(3, -1)
+        p, st = "mtp.layers.0", state.layers[0]
+        mixed, n = self._mix(h, p + ".attn_hyper_connection")
+        h = self._inject(h, self._attention(mixed, st, p + ".self_attn", start, pos3), n, p + ".attn_hyper_connection")
+        mixed, n = self._mix(h, p + ".mlp_hyper_connection")
+        h = self._inject(h, self._mlp(mixed, p + ".mlp"), n, p + ".mlp_hyper_connection")
+        state.length = start + T
+        mixed, _ = self._mix(h, "mtp.hyper_connection_mixer")
+        return self._lin(mixed, "lm_head"), h, state
+
 
 # ------------------------------------------------------------------ serving
+def copy_state(state: RequestState) -> RequestState:
+    """A state that can be advanced without touching ``state``: tensors are never written in place by the model, so the
+    copy shares them; the n-gram history is a list and is copied."""
+    return RequestState(state.length, [replace(l, ngram_history=None if l.ngram_history is None else list(l.ngram_history))
+                                       for l in state.layers])
+
+
+@dataclass
+class _Slot:
+    uid: int
+    state: RequestState
+    draft: RequestState | None = None          # the draft head's state: caught up to the position before the last one
+    carried: torch.Tensor | None = None        # the target's multi-stream residual at the last position, [1, S H]
+
+
 class Qwen4ExpEagerExecutor:
     """``execute(segments)`` of the engine on the eager model: one explicit state per request slot.  A segment that
     starts at position 0 (a new request, or one recomputed after preemption) starts a fresh state; pages are not used
-    (the state holds K / V), and there is no prefix sharing."""
+    (the state holds K / V), and there is no prefix sharing.
+
+    With ``speculative_depth`` > 0 (the checkpoint carries the draft head) decode steps of greedy, unconstrained
+    requests run as draft / review rounds: the head proposes up to ``depth`` tokens from the root token and the
+    target's residual of the previous position, the target reviews root + drafts in one pass on a copy of the state,
+    the longest agreeing prefix and the target's own next token are emitted, and the committed state is advanced over
+    the accepted tokens only.  The head's state follows the committed tokens with the TARGET's residuals (its draft
+    steps run on a copy), so proposals never depend on rejected drafts.  Lossless: the emitted tokens are those of
+    plain greedy decoding."""
 
     accepts_features = True
     keeps_request_state = True
 
-    def __init__(self, cfg: Qwen4ExpConfig, weights: Mapping[str, torch.Tensor]) -> None:
+    def __init__(self, cfg: Qwen4ExpConfig, weights: Mapping[str, torch.Tensor], speculative_depth: int = 0) -> None:
         self.cfg = cfg
         self.model = Qwen4ExpModel(cfg, weights)
-        self._states: dict[int, tuple[int, RequestState]] = {}
+        if speculative_depth and not self.model.has_draft_head:
+            raise ValueError("speculative rounds need the checkpoint's draft head (mtp.* tensors)")
+        self.speculative_depth = int(speculative_depth)
+        self._slots: dict[int, _Slot] = {}
+        self.last_round: dict | None = None
         self.h2d_bytes_last = self.d2h_bytes_last = self.kernel_launches_last = 0
 
     def copy_pages(self, pairs) -> None:
         if pairs:
             raise RuntimeError("this executor keeps no pages: copy-on-write cannot occur with the prefix cache off")
 
+    def _slot(self, s) -> _Slot:
+        held = self._slots.get(s.request_slot)
+        if s.start == 0 or held is None or held.uid != s.uid:
+            if s.start != 0:
+                raise RuntimeError(f"slot {s.request_slot}: no state for a segment that starts at {s.start}")
+            held = _Slot(s.uid, RequestState())
+            self._slots[s.request_slot] = held
+        if held.state.length != s.start:
+            raise RuntimeError(f"slot {s.request_slot}: state holds {held.state.length} tokens, the segment starts at {s.start}")
+        return held
+
+    def _advance(self, slot: _Slot, tokens: list[int], positions3=None, embeds=None) -> torch.Tensor:
+        """Run the target over ``tokens`` on the slot's committed state and let the draft head follow: the head sees
+        (token i + 1, residual of position i) for every position whose successor is known."""
+        logits, _ = self.model.forward(tokens, slot.state, positions3, embeds, last_only=True)
+        if self.speculative_depth:
+            fb = self.model.last_feedback
+            head_tokens = ([tokens[0]] if slot.carried is not None else []) + tokens[1:]
+            head_fb = torch.cat(([slot.carried] if slot.carried is not None else []) + [fb[:-1]])
+            if head_tokens:
+                _, _, slot.draft = self.model.draft_forward(head_tokens, head_fb, slot.draft)
+            slot.carried = fb[-1:].clone()
+        return logits[0]
+
     def execute(self, segs: list) -> np.ndarray:
         from ..executor.eager_executor import sample_row
         out = []
         for s in segs:
-            held = self._states.get(s.request_slot)
-            if s.start == 0 or held is None or held[0] != s.uid:
-                if s.start != 0:
-                    raise RuntimeError(f"slot {s.request_slot}: no state for a segment that starts at {s.start}")
-                held = (s.uid, RequestState())
-                self._states[s.request_slot] = held
-            state = held[1]
-            if state.length != s.start:
-                raise RuntimeError(f"slot {s.request_slot}: state holds {state.length} tokens, the segment starts at {s.start}")
-            logits, _ = self.model.forward(list(s.token_ids), state, s.positions3, s.embeds, last_only=True)
+            logits = self._advance(self._slot(s), [int(t) for t in s.token_ids], s.positions3, s.embeds)
             if s.sample:
-                out.append(sample_row(logits[0], s))
+                out.append(sample_row(logits, s))
         return np.asarray(out, dtype=np.int32)
+
+    def execute_speculative(self, segs: list, depths: list[int] | None = None) -> list[list[int]]:
+        """One round per decode segment (its root token); returns the emitted tokens of every request."""
+        from ..executor.eager_executor import sample_row
+        outs, accepted, proposed = [], [], []
+        for i, s in enumerate(segs):
+            K = self.speculative_depth if depths is None else min(self.speculative_depth, int(depths[i]))
+            slot = self._slot(s)
+            plain = K <= 0 or len(s.token_ids) != 1 or s.temperature > 0 or s.mask is not None or slot.carried is None
+            if plain:
+                outs.append([sample_row(self._advance(slot, [int(t) for t in s.token_ids], s.positions3, s.embeds), s)])
+                accepted.append(0)
+                proposed.append(0)
+                continue
+            root = int(s.token_ids[0])
+            # proposals on a copy of the head's state: draft steps feed on the head's own residual
+            dstate = copy_state(slot.draft) if slot.draft is not None else None
+            drafts, tok, fb = [], root, slot.carried
+            for _ in range(K):
+                lg, fb, dstate = self.model.draft_forward([tok], fb, dstate)
+                tok = int(lg[0].argmax())
+                drafts.append(tok)
+            # review: root + drafts in one pass on a copy of the committed state
+            pos3 = None
+            if s.positions3 is not None:
+                p0 = np.asarray(s.positions3)[:, :1]
+                pos3 = p0 + np.arange(K + 1)[None, :]
+            logits, _ = self.model.forward([root] + drafts, copy_state(slot.state), pos3)
+            target = logits.argmax(-1).tolist()
+            a = 0
+            while a < K and drafts[a] == target[a]:
+                a += 1
+            # commit the accepted prefix (the head follows with the target's residuals)
+            self._advance(slot, [root] + drafts[:a], None if pos3 is None else pos3[:, :a + 1])
+            outs.append([int(t) for t in target[:a + 1]])
+            accepted.append(a)
+            proposed.append(K)
+        self.last_round = {"depth": max(proposed, default=0), "accepted": accepted, "proposed": proposed,
+                           "proposal_ms": 0.0, "target_ms": 0.0}
+        return outs
 
 
 def admit_qwen4_exp_checkpoint(path):
     """``(cfg, weights, store)`` of a checkpoint directory under the closed inventory: every text tensor of
-    ``qwen4_exp_tensor_shapes`` present with its shape, the vision tower's tensors when the configuration has one, and
-    nothing else except the draft head (``mtp.*``), which is listed but not served."""
+    ``qwen4_exp_tensor_shapes`` present with its shape, the vision tower's tensors when the configuration has one, the
+    draft head (``mtp.*``) whole when the checkpoint carries it, and nothing else."""
     from pathlib import Path
 
     from .checkpoint import CheckpointError, SafetensorsDirectory
@@ -653,13 +793,22 @@ def admit_qwen4_exp_checkpoint(path):
             if full not in store or tuple(store.tensors[full].shape) != shape:
                 raise CheckpointError(f"missing or misshaped tensor {full}")
             claimed.add(full)
-    unowned = sorted(n for n in set(store.tensors) - claimed if not n.startswith("mtp."))
+    head = {}
+    if any(n.startswith("mtp.") for n in store.tensors):                # the draft head comes whole, with its shapes
+        head = qwen4_exp_mtp_tensor_shapes(cfg)
+        for n, shape in head.items():
+            if n not in store or tuple(store.tensors[n].shape) != shape:
+                raise CheckpointError(f"missing or misshaped tensor {n}")
+            claimed.add(n)
+    unowned = sorted(set(store.tensors) - claimed)
     if unowned:
         raise CheckpointError(f"checkpoint has {len(unowned)} tensors no logical weight owns, e.g. {unowned[:3]}")
     weights = {}
     for n in qwen4_exp_tensor_shapes(cfg):
         alias = nested + n[len(LM) + 1:] if n.startswith(LM + ".") else n
         weights[n] = store.get(alias)
+    for n in head:
+        weights[n] = store.get(n)
     return cfg, weights, store
 
 

@@ -88,9 +88,9 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
         cfg = NAMED_CONFIGS[model.split(":", 1)[1]]()
         ck = None
         if getattr(cfg, "family", "") == "qwen4_exp":
-            return _build_qwen4_exp_backend(args, cfg, None)
+            return _build_qwen4_exp_backend(args, cfg, None, spec)
     elif _model_type_of(model) == "qwen4_exp":
-        return _build_qwen4_exp_backend(args, None, model)
+        return _build_qwen4_exp_backend(args, None, model, spec)
     elif model.endswith(".gguf"):
         import gguf
 
@@ -218,8 +218,10 @@ def _model_type_of(model: str) -> str | None:
         return None
 
 
-def _build_qwen4_exp_backend(args, cfg, path):
-    """The qwen4_exp family is served by its eager executor (explicit per-request state, no prefix sharing)."""
+def _build_qwen4_exp_backend(args, cfg, path, spec=None):
+    """The qwen4_exp family is served by its eager executor (explicit per-request state, no prefix sharing); with
+    ``--speculative-config '{"method":"mtp",...}'`` and a checkpoint that carries the draft head, decode steps of greedy
+    requests run as draft / review rounds."""
     from ..models.qwen4_exp import Qwen4ExpEagerExecutor, admit_qwen4_exp_checkpoint, random_qwen4_exp_weights
     from ..runtime.async_engine import TokenChatBackend
     from ..runtime.engine import LLMEngine
@@ -227,15 +229,20 @@ def _build_qwen4_exp_backend(args, cfg, path):
     if args.execution_mode == "cuda":
         log.warning("the qwen4_exp family runs on the eager executor; --execution-mode cuda has no native runner for it")
     store = None
+    depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None and getattr(spec, "method", "") == "mtp" else 0
+    if spec is not None and getattr(spec, "method", "none") == "ngram":
+        raise SystemExit("the qwen4_exp executor runs draft-head rounds (method mtp); n-gram drafts are not wired to it")
     if path is not None:
         cfg, weights, store = admit_qwen4_exp_checkpoint(path)
+        if depth and "mtp.fc_hidden.weight" not in weights:
+            raise SystemExit("this checkpoint carries no draft head (no mtp.* tensors)")
     else:
-        weights = random_qwen4_exp_weights(cfg, args.seed)
+        weights = random_qwen4_exp_weights(cfg, args.seed, draft_head=depth > 0)
     max_len = args.max_model_len or min(cfg.max_position, 8192)
     sched = SchedulerConfig(max_running_requests=args.max_running_requests, max_batched_tokens=args.token_budget,
                             prefill_chunk_tokens=min(args.prefill_chunk_tokens, args.token_budget), max_model_len=max_len,
                             enable_prefix_cache=False)
-    executor = Qwen4ExpEagerExecutor(cfg, weights)
+    executor = Qwen4ExpEagerExecutor(cfg, weights, speculative_depth=depth)
     tok = _tokenizer_for(path or "random:qwen4-exp-tiny", cfg.vocab_size)
     engine = LLMEngine(executor, num_pages=max(4096, args.max_running_requests * (max_len // 16 + 1)), scheduler_config=sched,
                        eos_token_id=getattr(tok, "eos_token_id", None))

@@ -326,3 +326,141 @@ def test_inspect_reports_the_family(tmp_path):
     info = inspect_checkpoint(d)
     assert info["family"] == "qwen4_exp" and info["residual_streams"] == 4 and info["gated_deltanet_layers"] == 2
     assert info["ngram_layers"] == [2] and info["execution_mode"] == "eager" and not info["vision_tower"]
+
+
+def test_draft_head_rounds_are_lossless_and_accept_agreeing_drafts():
+    """The draft head's rounds through the engine emit exactly the tokens of plain greedy decoding; with a head that
+    agrees with the target (its logits replaced by the target's own next-token choice) whole rounds are accepted and the
+    committed state stays that of the accepted tokens."""
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = Q.tiny_config()
+    w = Q.random_qwen4_exp_weights(cfg, 3, std=0.15, draft_head=True)
+    assert set(Q.qwen4_exp_mtp_tensor_shapes(cfg)) <= set(w) and "mtp.layers.0.self_attn.indexer.index_qk_proj.weight" in w
+    assert "mtp.layers.0.ple.conv1d.weight" not in w
+    prompts = [list(range(2, 25)), [9, 8, 7, 6, 5, 4, 3], [11]]
+
+    def run(depth, patch=None, n=12):
+        ex = Q.Qwen4ExpEagerExecutor(cfg, w, speculative_depth=depth)
+        if patch:
+            patch(ex)
+        eng = LLMEngine(ex, 64, SchedulerConfig(prefill_chunk_tokens=16, max_model_len=256))
+        ids = [eng.add_request(p, SamplingParams(max_tokens=n)) for p in prompts]
+        got = {i: [] for i in ids}
+        while eng.has_unfinished:
+            for o in eng.step():
+                if o.token_id is not None:
+                    got[o.request_id].append(o.token_id)
+        return [got[i] for i in ids], ex, eng
+    plain, _, _ = run(0)
+    spec, ex, eng = run(3)
+    assert spec == plain and all(len(o) == 12 for o in spec)
+    assert getattr(eng, "spec_rounds", 0) > 0 and ex.last_round["proposed"]
+
+    with pytest.raises(ValueError):
+        Q.Qwen4ExpEagerExecutor(cfg, Q.random_qwen4_exp_weights(cfg, 3), speculative_depth=2)
+    with pytest.raises(Q.Qwen4ExpConfigError):
+        Q.Qwen4ExpModel(cfg, {k: v for k, v in w.items() if k != "mtp.fc_hidden.weight"})
+
+
+def test_round_bookkeeping_with_a_scripted_model():
+    """Acceptance, emitted tokens and what the committed states hold, on a model whose answers are scripted: the target
+    continues every token t with t + 1; the head agrees for its first two proposals of a round and errs on the third."""
+    from cubic_serve_b200.executor.gpu_executor import Segment
+
+    class Scripted:
+        has_draft_head = True
+        cfg = Q.tiny_config()
+
+        def __init__(self):
+            self.target_calls, self.head_calls = [], []
+
+        def forward(self, tokens, state=None, positions3=None, embeds=None, last_only=False):
+            state = state or Q.RequestState()
+            self.target_calls.append((state.length, list(tokens)))
+            state.length += len(tokens)
+            logits = torch.zeros(len(tokens), 320)
+            for i, t in enumerate(tokens):
+                logits[i, (t + 1) % 320] = 1
+            self.last_feedback = torch.tensor([[float(t)] for t in tokens]).repeat(1, 128)
+            return (logits[-1:] if last_only else logits), state
+
+        def draft_forward(self, tokens, feedback, state=None):
+            state = state or Q.RequestState()
+            self.head_calls.append((state.length, list(tokens), feedback[:, 0].tolist()))
+            n_before = getattr(state, "steps_in_round", 0)
+            state.length += len(tokens)
+            logits = torch.zeros(len(tokens), 320)
+            for i, t in enumerate(tokens):
+                wrong = getattr(state, "drafting", False) and n_before + i >= 2
+                logits[i, (t + (5 if wrong else 1)) % 320] = 1
+            if getattr(state, "drafting", False):
+                state.steps_in_round = n_before + len(tokens)
+            return logits, feedback.clone(), state
+    ex = Q.Qwen4ExpEagerExecutor.__new__(Q.Qwen4ExpEagerExecutor)
+    ex.cfg, ex.model, ex.speculative_depth, ex._slots, ex.last_round = Scripted.cfg, Scripted(), 3, {}, None
+    real_copy = Q.copy_state
+
+    def marking_copy(st):                       # the copies made for drafting are marked, so the script can err there
+        c = real_copy(st)
+        c.drafting = True
+        return c
+    Q.copy_state = marking_copy
+    try:
+        first = ex.execute([Segment(0, [10, 11, 12], 0, [], uid=1)])          # prefill: the target answers 13
+        assert first.tolist() == [13]
+        out = ex.execute_speculative([Segment(0, [13], 3, [], uid=1)])
+    finally:
+        Q.copy_state = real_copy
+    # drafts 14, 15 agree, the third (20) does not: two accepted, the target's 14, 15, 16 are emitted
+    assert out == [[14, 15, 16]] and ex.last_round["accepted"] == [2] and ex.last_round["proposed"] == [3]
+    slot = ex._slots[0]
+    assert slot.state.length == 6                                             # 10 11 12 | 13 14 15 committed
+    calls = ex.model.target_calls
+    assert calls[0] == (0, [10, 11, 12]) and calls[1] == (3, [13, 14, 15, 20]) and calls[2] == (3, [13, 14, 15])
+    # the head followed the committed tokens with the TARGET's residuals: (11, f10) (12, f11) | (13, f12) (14, f13) (15, f14)
+    committed = [c for c in ex.model.head_calls if c[1] in ([11, 12], [13, 14, 15])]
+    assert committed[0][2] == [10.0, 11.0] and committed[1][2] == [12.0, 13.0, 14.0]
+    assert slot.draft.length == 5 and float(slot.carried[0, 0]) == 15.0
+    # the next root is 16 at position 6
+    out2 = ex.execute_speculative([Segment(0, [16], 6, [], uid=1)], depths=[0])
+    assert out2 == [[17]] and ex.last_round["proposed"] == [0] and slot.state.length == 7
+
+
+def test_serving_backend_with_the_draft_head(tmp_path):
+    from argparse import Namespace
+
+    from safetensors.torch import save_file
+
+    from cubic_serve_b200.cli import SpeculativeConfig
+    from cubic_serve_b200.models.checkpoint import CheckpointError
+    from cubic_serve_b200.runtime.serving import build_backend
+    args = Namespace(model="random:qwen4-exp-tiny", execution_mode="eager", pp_size=1, seed=0, max_model_len=256,
+                     max_running_requests=4, token_budget=64, prefill_chunk_tokens=32, prefix_cache=True, thinking=None,
+                     served_model_name=None)
+    backend, _ = build_backend(args, [0], 1, SpeculativeConfig("mtp", 2), 8, 8)
+    assert backend.engine.executor.speculative_depth == 2 and backend.engine.scheduler.decode_lookahead == 2
+    backend.close()
+    # a checkpoint with half a draft head is refused
+    cfg = Q.tiny_config()
+    w = Q.random_qwen4_exp_weights(cfg, 1, draft_head=True)
+    d = tmp_path / "q"
+    d.mkdir()
+    src = json.loads(json.dumps({"model_type": "qwen4_exp", "language_model_only": True}))
+    src["text_config"] = {
+        "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+        "layer_types": list(cfg.layer_types), "num_attention_heads": cfg.num_q_heads, "num_key_value_heads": cfg.num_kv_heads,
+        "head_dim": cfg.head_dim, "rope_parameters": {"mrope_section": [2, 1, 1], "rope_theta": 1e4, "partial_rotary_factor": 0.5},
+        "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 8, "linear_value_head_dim": 8,
+        "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 16, "shared_expert_intermediate_size": 16,
+        "hc_count": 4, "hc_lowrank": 8, "indexer_n_heads": 2, "indexer_head_dim": 16, "indexer_budget": 16,
+        "indexer_compress_ratio": 4, "ple_layer_ids": [2], "ple_embed_dim": 32, "ngram_size": 3, "heads_per_ngram": 2,
+        "ngram_vocab_size_base": 500, "make_ngram_vocab_size_divisible_by": 4, "split_ngram_parts": 4,
+        "ngram_shard_rows": 512, "eos_token_id": 1, "max_position_embeddings": 4096, "mtp_num_hidden_layers": 1}
+    (d / "config.json").write_text(json.dumps(src))
+    save_file({n: t.contiguous() for n, t in w.items()}, str(d / "model.safetensors"))
+    got_cfg, got_w, _ = Q.admit_qwen4_exp_checkpoint(d)
+    assert got_cfg.mtp_layers == 1 and "mtp.fc_embedding.weight" in got_w and len(got_w) == len(w)
+    save_file({n: t.contiguous() for n, t in w.items() if n != "mtp.fc_hidden.weight"}, str(d / "model.safetensors"))
+    with pytest.raises(CheckpointError, match="mtp.fc_hidden"):
+        Q.admit_qwen4_exp_checkpoint(d)
