@@ -84,6 +84,23 @@ def kv_quantize(x: torch.Tensor, bits: int) -> tuple[torch.Tensor, torch.Tensor]
     return codes.reshape(x.shape), scale
 
 
+def kv_quantize_token_groups(k: torch.Tensor, bits: int, tokens_per_group: int = 32) -> torch.Tensor:
+    """Quantize-dequantize of keys ``[S, H, D]`` with ONE scale per (head, channel, block of ``tokens_per_group``
+    tokens); the incomplete last block stays in its native precision until it fills (the "tail").  This is the
+    token-grouped K form of the reference's cache ABI (``runtime/cache/quantization.py:113-286`` there); the native cache of
+    this build groups 32 CHANNELS of one token instead (``kv_quantize``).  Oracle for accuracy comparisons only."""
+    S = k.shape[0]
+    full = S // tokens_per_group * tokens_per_group
+    qmax = float((1 << (bits - 1)) - 1)
+    out = k.float().clone()
+    if full:
+        blk = out[:full].view(full // tokens_per_group, tokens_per_group, *k.shape[1:])
+        amax = blk.abs().amax(1, keepdim=True)
+        scale = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
+        out[:full] = (torch.round(blk / scale).clamp(-qmax, qmax) * scale).view(full, *k.shape[1:])
+    return out
+
+
 def kv_dequantize(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     g = codes.reshape(*codes.shape[:-1], codes.shape[-1] // KV_GROUP, KV_GROUP)
     return (g * scale[..., None]).reshape(codes.shape)
