@@ -118,7 +118,10 @@ class CubicASGIApp:
         self.sampling_defaults = dict(sampling_defaults or {})      # the checkpoint's generation_config.json
         self.backend = backend
         self.model_id = model_id
-        self.served_model_name = served_model_name or model_id
+        # several public names may be given: requests may use any of them, responses carry the first
+        names = [served_model_name] if isinstance(served_model_name, str) else list(served_model_name or ())
+        self.served_model_name = names[0] if names else model_id
+        self.accepted_names = tuple(dict.fromkeys([*names, model_id]))
         self._key_digest = hashlib.sha256(api_key.encode()).digest() if api_key else None
         self.created = int(time.time())
 
@@ -221,9 +224,12 @@ class CubicASGIApp:
                 req = normalize_openai_chat_completions(body, self.served_model_name, self.sampling_defaults)
             else:
                 req = normalize_anthropic_messages(body, self.served_model_name, self.sampling_defaults)
-            if req.model not in (self.served_model_name, self.model_id):
+            if req.model not in self.accepted_names:
                 raise RequestError(f"model {req.model!r} is not served here", param="model", status=404,
                                    code="model_not_found")
+            if req.model != self.served_model_name:
+                import dataclasses
+                req = dataclasses.replace(req, model=self.served_model_name)      # responses carry the first public name
             if not getattr(self.backend, "ready", True):
                 raise ChatBackendError(503, "the server is not ready", "service_unavailable")
             events = self.backend.start(req)

@@ -78,6 +78,8 @@ def validate_topology(devices: list[int], tp: int, pp: int, ep: int, spec: Specu
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="cubic", description="Blackwell-native quantized LLM serving")
+    from . import __version__ as version
+    ap.add_argument("--version", action="version", version=f"%(prog)s {version}")
     sub = ap.add_subparsers(dest="command", required=True)
 
     ins = sub.add_parser("inspect-model", help="print the architecture, quantization and tensor inventory of a checkpoint")
@@ -98,8 +100,8 @@ def build_parser() -> argparse.ArgumentParser:
     rf = sub.add_parser("reference", help="greedy-decode a prompt of token ids with the eager fp32 reference decoder "
                                           "(the oracle the native kernels are qualified against)")
     rf.add_argument("model", help="checkpoint directory or random:<config>")
-    rf.add_argument("--prompt-ids", required=True, help="comma-separated token ids")
-    rf.add_argument("--max-tokens", type=int, default=16)
+    rf.add_argument("--prompt-ids", "--input-ids", dest="prompt_ids", required=True, help="comma-separated token ids")
+    rf.add_argument("--max-tokens", "--max-new-tokens", dest="max_tokens", type=int, default=16)
     rf.add_argument("--kv", default="16,16", help="simulated K,V cache bits (16 = unquantized)")
     rf.add_argument("--seed", type=int, default=0)
 
@@ -136,7 +138,8 @@ def build_parser() -> argparse.ArgumentParser:
     s = sub.add_parser("serve", help="serve a checkpoint over OpenAI / Anthropic compatible HTTP")
     s.add_argument("model", help="checkpoint directory, .gguf file, or random:<named-config>")
     g = s.add_argument_group("Server")
-    g.add_argument("--served-model-name")
+    g.add_argument("--served-model-name", nargs="+", metavar="NAME",
+                   help="public model name(s): requests may use any of them, responses carry the first")
     g.add_argument("--host", default="127.0.0.1")
     g.add_argument("--port", type=int, default=8000)
     g.add_argument("--api-key", default=os.environ.get("CUBIC_API_KEY"))
@@ -172,11 +175,21 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--cuda-graph-max-tokens", default="auto")
     g.add_argument("--prefill-chunk-tokens", type=int, default=4096)
     g = s.add_argument_group("Multimodal input")
-    g.add_argument("--encoder-memory-gib", type=float, default=2.0,
+    g.add_argument("--encoder-memory-gib", "--multimodal-memory-gib", dest="encoder_memory_gib", type=float, default=2.0,
                    help="transient memory one call of the vision tower may use; larger items are cut at frame boundaries "
                         "or refused")
     g.add_argument("--feature-store-mib", type=int, default=1024, help="host memory for encoded media, reused by content")
-    g.add_argument("--media-file-root", action="append", default=[], help="directory file: media may be read from")
+    g.add_argument("--mm-feature-cache-gib", type=float, default=None,
+                   help="the same budget in GiB (overrides --feature-store-mib; 0 keeps nothing)")
+    g.add_argument("--media-file-root", "--allowed-local-media-path", dest="media_file_root", action="append", default=[],
+                   help="directory file: media may be read from")
+    g.add_argument("--mm-preprocess-workers", type=int, default=2,
+                   help="accepted for compatibility: media are decoded and cut into patches on the request's thread")
+    g.add_argument("--mm-worker-layout", choices=("colocated", "separate"), default="colocated",
+                   help="colocated: the vision tower shares the first GPU (the only layout of this build)")
+    g.add_argument("--video-fps", type=float, default=2.0,
+                   help="accepted for compatibility: clips arrive as decoded frames (no container decoding)")
+    g.add_argument("--video-max-frames", type=int, default=768, help="frames a clip may carry")
     g.add_argument("--media-http-host", action="append", default=[], help="host name http(s): media may be fetched from")
     g.add_argument("--max-media-items", type=int, default=16)
     g.add_argument("--encoder-graph-buckets", default="",
@@ -184,6 +197,14 @@ def build_parser() -> argparse.ArgumentParser:
                         "vision tower captured for the smallest bucket that holds them (off by default: eager calls)")
     g = s.add_argument_group("Advanced")
     g.add_argument("--execution-mode", choices=("cuda", "eager", "debug"), default="cuda")
+    g.add_argument("--recurrent-state-dtype", "--mamba-ssm-cache-dtype", dest="recurrent_state_dtype",
+                   choices=("auto", "float32", "bfloat16"), default="float32",
+                   help="storage of the Gated DeltaNet state: float32 (this build keeps the recurrent matrices in fp32; "
+                        "bfloat16 is refused)")
+    for flag in ("--activation-dtype", "--attention-dtype", "--softmax-dtype"):
+        g.add_argument(flag, choices=("auto", "fp32"), default=None,
+                       help="auto: bf16 operands with fp32 accumulation and fp32 softmax (the native kernels); fp32 selects "
+                            "the eager execution mode, whose arithmetic is fp32 throughout")
     g.add_argument("--startup-numerical-audit", action="store_true",
                    help="qualify the kernels against their oracles before serving (a passing receipt of the same code on "
                         "the same GPU model is reused); a failure refuses to serve")
@@ -259,6 +280,18 @@ def _serve(args) -> int:
     if args.compute_mode != "wna16":
         raise SystemExit("--compute-mode wna8 (INT8 activations) is not available in this build: packed weights run "
                          "with 16-bit activations (wna16)")
+    if args.recurrent_state_dtype == "bfloat16":
+        raise SystemExit("--recurrent-state-dtype bfloat16 is not available: the Gated DeltaNet state is kept in float32")
+    if any(getattr(args, n) == "fp32" for n in ("activation_dtype", "attention_dtype", "softmax_dtype")) \
+            and args.execution_mode == "cuda":
+        print("fp32 arithmetic requested: using --execution-mode eager", file=sys.stderr)
+        args.execution_mode = "eager"
+    if args.mm_worker_layout != "colocated":
+        raise SystemExit("--mm-worker-layout separate is not available: the vision tower runs on the first GPU")
+    if args.mm_feature_cache_gib is not None:
+        args.feature_store_mib = int(args.mm_feature_cache_gib * 1024)
+    if args.video_max_frames < 4:
+        raise SystemExit("--video-max-frames must be at least 4")
     spec = parse_speculative_config(args.speculative_config)
     devices = parse_devices(args.devices)
     tp = args.tp_size or max(1, len(devices) // args.pp_size)

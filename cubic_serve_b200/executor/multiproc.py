@@ -339,4 +339,5 @@ def build_multiproc_backend(args, devices, tp, spec_cfg, k_bits, v_bits):
                             enable_prefix_cache=args.prefix_cache)
     tok = _tokenizer_for(args.model, ex.info["vocab"])
     engine = LLMEngine(ex, num_pages=ex.info["pages"], scheduler_config=sched, eos_token_id=getattr(tok, "eos_token_id", None))
-    return TokenChatBackend(engine, tok, default_thinking=args.thinking), (args.served_model_name or ex.info["name"])
+    return TokenChatBackend(engine, tok, default_thinking=args.thinking), ((args.served_model_name if isinstance(args.served_model_name, str) else (args.served_model_name or [None])[0])
+                                                                                 or ex.info["name"])

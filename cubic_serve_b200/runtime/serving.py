@@ -205,7 +205,14 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
     if ck is not None and ck.vision is not None:
         processor = build_media_processor(args, ck, tok, executor, max_len)
     backend = TokenChatBackend(engine, tok, default_thinking=args.thinking, processor=processor)
-    return backend, (args.served_model_name or cfg.name)
+    return backend, (_first_name(args.served_model_name) or cfg.name)
+
+
+def _first_name(names):
+    """``--served-model-name`` takes one or several names; the first is the one responses carry."""
+    if not names:
+        return None
+    return names if isinstance(names, str) else names[0]
 
 
 def _model_type_of(model: str) -> str | None:
@@ -256,7 +263,7 @@ def _build_qwen4_exp_backend(args, cfg, path, spec=None):
                              raw_config=json.loads((Path(path) / "config.json").read_text()))
         processor = build_media_processor(args, ck, tok, executor, max_len)
     return (TokenChatBackend(engine, tok, default_thinking=args.thinking, processor=processor),
-            (args.served_model_name or cfg.name))
+            (_first_name(args.served_model_name) or cfg.name))
 
 
 def build_media_processor(args, ck, tok, executor, max_len: int):

@@ -113,3 +113,36 @@ def test_wna8_compute_mode_is_refused_not_ignored():
     from cubic_serve_b200 import cli
     with pytest.raises(SystemExit, match="wna8"):
         cli.main(["serve", "random:toy", "--compute-mode", "wna8"])
+
+
+def test_reference_flag_spellings_are_accepted():
+    """Flags of the reference's CLI that name the same thing here parse under their own names too."""
+    from cubic_serve_b200.cli import build_parser
+    p = build_parser()
+    a = p.parse_args(["serve", "random:toy", "--served-model-name", "a", "b", "--allowed-local-media-path", "/srv/m",
+                      "--multimodal-memory-gib", "3", "--mm-feature-cache-gib", "0.5", "--mm-preprocess-workers", "4",
+                      "--video-max-frames", "64", "--video-fps", "1", "--mamba-ssm-cache-dtype", "float32",
+                      "--softmax-dtype", "fp32", "--device", "0"])
+    assert a.served_model_name == ["a", "b"] and a.media_file_root == ["/srv/m"] and a.encoder_memory_gib == 3.0
+    assert a.mm_feature_cache_gib == 0.5 and a.recurrent_state_dtype == "float32" and a.softmax_dtype == "fp32"
+    r = p.parse_args(["reference", "random:toy", "--input-ids", "1,2", "--max-new-tokens", "3"])
+    assert r.prompt_ids == "1,2" and r.max_tokens == 3
+    import pytest
+    with pytest.raises(SystemExit):
+        p.parse_args(["--version"])
+
+
+def test_several_served_names_are_accepted_by_the_server():
+    import asyncio
+    import json
+
+    from test_api import ScriptedBackend, _call
+
+    from cubic_serve_b200.api.server import CubicASGIApp
+    app = CubicASGIApp(ScriptedBackend(), "ckpt", ["public", "alias"])
+    body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2}
+    for name, want in (("public", 200), ("alias", 200), ("ckpt", 200), ("other", 404)):
+        st, payload = asyncio.run(_call(app, "POST", "/v1/chat/completions", {**body, "model": name}))
+        assert st == want, (name, st, payload[:120])
+        if want == 200:
+            assert json.loads(payload)["model"] == "public"
