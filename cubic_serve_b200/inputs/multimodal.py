@@ -57,7 +57,7 @@ class VisionTokens:
 class MultimodalChatProcessor(ChatInputProcessor):
     def __init__(self, tokenizer, vision_service, tokens: VisionTokens, geometry: PatchGeometry | None = None,
                  resolver: MediaResolver | None = None, default_thinking: bool | None = None,
-                 max_model_len: int | None = None, max_items: int = 16) -> None:
+                 max_model_len: int | None = None, max_items: int = 16, video_max_frames: int = 768) -> None:
         super().__init__(tokenizer, default_thinking, max_model_len)
         self.vision, self.tokens = vision_service, tokens
         cfg = vision_service.encoder.cfg
@@ -67,6 +67,7 @@ class MultimodalChatProcessor(ChatInputProcessor):
             raise ValueError("the patch geometry differs from the vision tower's")
         self.resolver = resolver or MediaResolver()
         self.max_items = max_items
+        self.video_max_frames = video_max_frames
 
     # ------------------------------------------------------------------ media parts -> patches
     def _patches(self, part: ContentPart) -> MediaPatches:
@@ -77,7 +78,7 @@ class MultimodalChatProcessor(ChatInputProcessor):
                 media = self.resolver.resolve(part.media_url, "image")
                 return patchify_image(decode_image(media.data), self.geometry)
             if part.data is not None:
-                return patchify_video(list(part.data), self.geometry)
+                return patchify_video(list(part.data), self.geometry, max_frames=self.video_max_frames)
             self.resolver.resolve(part.media_url, "video")          # policy and type checks still apply
             raise RequestError("video containers cannot be decoded by this deployment; send frames as images",
                                param="messages")

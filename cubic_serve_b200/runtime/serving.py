@@ -293,7 +293,8 @@ def build_media_processor(args, ck, tok, executor, max_len: int):
              service.plan.max_patches_per_call, getattr(args, "feature_store_mib", 1024))
     return MultimodalChatProcessor(tok, service, VisionTokens.from_hf(ck.raw_config), resolver=MediaResolver(policy),
                                    default_thinking=args.thinking, max_model_len=max_len,
-                                   max_items=getattr(args, "max_media_items", 16))
+                                   max_items=getattr(args, "max_media_items", 16),
+                                   video_max_frames=getattr(args, "video_max_frames", 768))
 
 
 class StatusReporter(threading.Thread):
