@@ -545,3 +545,33 @@ def test_fixed_shape_buckets_equal_the_exact_encode():
     assert [b.replays for b in svc.buckets] == [1, 0]
     assert (rows_small - enc.encode(torch.from_numpy(small), torch.tensor([[1, 4, 4]]))[0]).abs().max() < 1e-5
     assert rows_big.shape == (24, 32)
+
+
+def test_clip_of_decoded_frames_through_the_processor():
+    from PIL import Image
+
+    from cubic_serve_b200.contracts.request import CanonicalChatRequest, ContentPart, Message, RequestError, Role
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    from cubic_serve_b200.inputs.multimodal import MultimodalChatProcessor, VisionTokens
+
+    class Tok(ByteTokenizer):
+        SPECIALS = ByteTokenizer.SPECIALS + ("<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+    tok = Tok()
+    ids = tok.special_ids
+    vt = VisionTokens(ids["<|image_pad|>"], ids["<|video_pad|>"], ids["<|vision_start|>"], ids["<|vision_end|>"])
+    cfg = _cfg()
+    svc = VisionService(VisionEncoder(cfg, random_vision_weights(cfg, 7)))
+    proc = MultimodalChatProcessor(tok, svc, vt, PatchGeometry(4, 2, 2, min_pixels=8 * 8, max_pixels=16 * 16), video_max_frames=6)
+    frames = [Image.fromarray(np.full((16, 16, 3), v, dtype=np.uint8)) for v in (0, 60, 120, 180)]
+    msg = Message(Role.USER, (ContentPart("video", data=frames), ContentPart("text", "what happens?")))
+    plan = proc.plan(CanonicalChatRequest("openai", "m", (msg,), request_id="v"))
+    (p,) = plan.placements
+    assert p.kind == "video" and p.grid == (2, 4, 4) and p.rows == 8                  # 4 frames = 2 temporal patches
+    assert all(t == vt.video for t in plan.token_ids[p.first_token:p.first_token + 8])
+    t_axis = plan.positions[0, p.first_token:p.first_token + 8].tolist()
+    assert t_axis == [t_axis[0]] * 4 + [t_axis[0] + 1] * 4                            # the temporal axis advances per patch
+    out = proc.build(CanonicalChatRequest("openai", "m", (msg,), request_id="v"))
+    assert out.multimodal.spans[0][1].shape == (8, 32)
+    too_long = Message(Role.USER, (ContentPart("video", data=frames * 2),))
+    with pytest.raises(RequestError):
+        proc.plan(CanonicalChatRequest("openai", "m", (too_long,), request_id="w"))
