@@ -373,6 +373,16 @@ def _inspect(args) -> int:
                 info["partition"] = plan_partition(cfg, args.tp, args.pp, args.ep).summary()
             except PartitionError as exc:
                 info["partition_error"] = str(exc)
+            else:
+                # the communication calls every rank issues per step, and the proof that they cannot block each other
+                from .contracts.execution import ParallelTopology
+                from .guardrail.collective_schedule import check_schedules, decoder_step_schedule
+                topo = ParallelTopology.single_node(range(args.tp * args.pp), tp=args.tp, pp=args.pp, ep=args.ep)
+                sch = {r: decoder_step_schedule(cfg, topo, r, rows=1) for r in range(topo.world_size)}
+                problems = check_schedules(topo, sch)
+                info["collectives_per_step"] = {f"rank {r}": len(s) for r, s in sch.items()}
+                info["collective_schedule"] = "every group agrees, transfers match, the step runs to its end" \
+                    if not problems else problems
     if args.json:
         print(json.dumps(info, indent=1, default=str))
     else:
