@@ -91,6 +91,8 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
             return _build_qwen4_exp_backend(args, cfg, None, spec)
     elif _model_type_of(model) == "qwen4_exp":
         return _build_qwen4_exp_backend(args, None, model, spec)
+    elif model.endswith(".gguf") and _gguf_architecture(model) == "qwen4exp":
+        return _build_qwen4_exp_backend(args, None, model, spec)
     elif model.endswith(".gguf"):
         import gguf
 
@@ -215,6 +217,12 @@ def _first_name(names):
     return names if isinstance(names, str) else names[0]
 
 
+def _gguf_architecture(path: str) -> str | None:
+    import gguf
+    f = gguf.GGUFReader(str(path)).fields.get("general.architecture")
+    return None if f is None else bytes(f.parts[f.data[0]]).decode()
+
+
 def _model_type_of(model: str) -> str | None:
     import json
     from pathlib import Path
@@ -239,7 +247,13 @@ def _build_qwen4_exp_backend(args, cfg, path, spec=None):
     depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None and getattr(spec, "method", "") == "mtp" else 0
     if spec is not None and getattr(spec, "method", "none") == "ngram":
         raise SystemExit("the qwen4_exp executor runs draft-head rounds (method mtp); n-gram drafts are not wired to it")
-    if path is not None:
+    if path is not None and str(path).endswith(".gguf"):
+        from ..models.qwen4_exp_gguf import load_qwen4_exp_gguf
+        cfg, weights = load_qwen4_exp_gguf(path)
+        if depth:
+            raise SystemExit("the draft head of this format lives in a file of its own, which is not read: serve without "
+                             "--speculative-config")
+    elif path is not None:
         cfg, weights, store = admit_qwen4_exp_checkpoint(path)
         if depth and "mtp.fc_hidden.weight" not in weights:
             raise SystemExit("this checkpoint carries no draft head (no mtp.* tensors)")
