@@ -29,7 +29,6 @@ Reference counterpart: ``models/qwen4_exp/model.py:588-1060`` (configuration), `
 from __future__ import annotations
 
 import json
-import math
 from dataclasses import dataclass, field, replace
 from typing import Mapping
 
