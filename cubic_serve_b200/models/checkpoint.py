@@ -148,13 +148,27 @@ def logical_inventory(cfg: ModelConfig) -> tuple[dict[str, tuple[int, int]], lis
             raise CheckpointError(f"checkpoints with {cfg.mtp_layers} MTP layers are not served (one layer is)")
         mp = "mtp.layers.0"
         linears["mtp.fc"] = (H, 2 * H)
-        linears[f"{mp}.self_attn.q_proj"] = (cfg.q_size, H)
+        # the head's layer is a full-attention layer of the model's own kind: gated query projection where the model
+        # has one, routed (and shared) experts where the model has them
+        linears[f"{mp}.self_attn.q_proj"] = (cfg.q_size * (2 if cfg.attn_output_gate else 1), H)
         linears[f"{mp}.self_attn.k_proj"] = (cfg.kv_size, H)
         linears[f"{mp}.self_attn.v_proj"] = (cfg.kv_size, H)
         linears[f"{mp}.self_attn.o_proj"] = (H, cfg.q_size)
-        linears[f"{mp}.mlp.gate_proj"] = (cfg.intermediate_size, H)
-        linears[f"{mp}.mlp.up_proj"] = (cfg.intermediate_size, H)
-        linears[f"{mp}.mlp.down_proj"] = (H, cfg.intermediate_size)
+        if cfg.is_moe:
+            plain.append(f"{mp}.mlp.gate.weight")
+            for e in range(cfg.num_experts):
+                linears[f"{mp}.mlp.experts.{e}.gate_proj"] = (cfg.moe_intermediate_size, H)
+                linears[f"{mp}.mlp.experts.{e}.up_proj"] = (cfg.moe_intermediate_size, H)
+                linears[f"{mp}.mlp.experts.{e}.down_proj"] = (H, cfg.moe_intermediate_size)
+            if cfg.shared_intermediate_size:
+                linears[f"{mp}.mlp.shared_expert.gate_proj"] = (cfg.shared_intermediate_size, H)
+                linears[f"{mp}.mlp.shared_expert.up_proj"] = (cfg.shared_intermediate_size, H)
+                linears[f"{mp}.mlp.shared_expert.down_proj"] = (H, cfg.shared_intermediate_size)
+                plain.append(f"{mp}.mlp.shared_expert_gate.weight")
+        else:
+            linears[f"{mp}.mlp.gate_proj"] = (cfg.intermediate_size, H)
+            linears[f"{mp}.mlp.up_proj"] = (cfg.intermediate_size, H)
+            linears[f"{mp}.mlp.down_proj"] = (H, cfg.intermediate_size)
         plain += ["mtp.pre_fc_norm_embedding.weight", "mtp.pre_fc_norm_hidden.weight", "mtp.norm.weight",
                   f"{mp}.input_layernorm.weight", f"{mp}.post_attention_layernorm.weight"]
         if cfg.qk_norm:

@@ -30,6 +30,7 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
+from ..executor.stateful_executor import StatefulEagerExecutor
 from ..ops import eager
 from .config import ModelConfig
 
@@ -40,10 +41,8 @@ def family_tensor_shapes(cfg: ModelConfig) -> dict[str, tuple[int, ...]]:
     from .checkpoint import logical_inventory
     linears, plain = logical_inventory(cfg)
     H, D = cfg.hidden_size, cfg.head_dim
-    out = {f"{m}.weight": shape for m, shape in linears.items() if not m.startswith("mtp.")}
+    out = {f"{m}.weight": shape for m, shape in linears.items()}
     for name in plain:
-        if name.startswith("mtp."):
-            continue
         if name.endswith("conv1d.weight"):
             out[name] = ((2 * cfg.gdn_k_heads + cfg.gdn_v_heads) * 128, 1, 4)
         elif name.endswith(("A_log", "dt_bias")):
@@ -52,7 +51,7 @@ def family_tensor_shapes(cfg: ModelConfig) -> dict[str, tuple[int, ...]]:
             out[name] = (128,)
         elif name.endswith(("q_norm.weight", "k_norm.weight")):
             out[name] = (D,)
-        elif name.endswith("norm.weight"):
+        elif name.endswith("norm.weight") or "pre_fc_norm" in name:
             out[name] = (H,)
         elif name.endswith("mlp.gate.weight"):
             out[name] = (cfg.num_experts, H)
@@ -77,7 +76,7 @@ def random_family_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.05) ->
             w[name] = torch.randn(shape, generator=g) * 0.5
         elif name.endswith("linear_attn.norm.weight"):
             w[name] = 1 + 0.1 * torch.randn(shape, generator=g)
-        elif name.endswith("norm.weight"):
+        elif name.endswith("norm.weight") or "pre_fc_norm" in name:
             centre = 0.0 if cfg.zero_centered_norm else 1.0
             w[name] = centre + 0.1 * torch.randn(shape, generator=g)
         elif name.endswith("conv1d.weight"):
@@ -94,14 +93,11 @@ def family_weights_from_checkpoint(ck) -> dict[str, torch.Tensor]:
     linears, plain = logical_inventory(cfg)
     w = {}
     for module, shape in linears.items():
-        if module.startswith("mtp."):
-            continue
         p = ck.payload(module)
         w[f"{module}.weight"] = p["weight"].float() if len(p) == 1 and "weight" in p else \
             _dense_of(cfg.quant.method, p, shape, cfg.quant).float()
     for name in plain:
-        if not name.startswith("mtp."):
-            w[name] = ck.store.get(name).float()
+        w[name] = ck.store.get(name).float()
     return w
 
 
@@ -235,41 +231,60 @@ class EagerFamilyModel:
                      self._attention(x, st, p + ".self_attn", start, pos3))
             h = h + self._ffn(self._norm(h, p + ".post_attention_layernorm.weight"), p + ".mlp")
         state.length = start + T
+        self.last_feedback = h                                    # the hidden rows before the final norm feed a draft head
         last = self._norm(h[-1:] if last_only else h, "model.norm.weight")
         head = self.w["model.embed_tokens.weight"] if c.tie_embeddings else self.w["lm_head.weight"]
         return last @ head.t(), state
 
+    @property
+    def has_draft_head(self) -> bool:
+        return "mtp.fc.weight" in self.w
 
-class EagerFamilyExecutor:
+    @torch.no_grad()
+    def draft_forward(self, tokens, feedback: torch.Tensor, state: FamilyState | None = None):
+        """The multi-token-prediction head on ``tokens`` (token ``i + 1``) paired with ``feedback`` (the target's hidden
+        row of position ``i``): ``fc([norm(embedding) ; norm(hidden)])`` enters one full-attention layer of the model's
+        kind, whose output (before ``mtp.norm``) is the feedback of the next proposal; logits through the shared head."""
+        c = self.cfg
+        if not self.has_draft_head:
+            raise ValueError("the checkpoint carries no draft head")
+        tokens = [int(t) for t in tokens]
+        T = len(tokens)
+        if feedback.shape != (T, c.hidden_size):
+            raise ValueError("one hidden row per token")
+        state = state or FamilyState()
+        if not state.layers:
+            state.layers = [FamilyLayerState()]
+        start = state.length
+        e = self._norm(self.w["model.embed_tokens.weight"][torch.tensor(tokens)], "mtp.pre_fc_norm_embedding.weight")
+        hh = self._norm(feedback.float(), "mtp.pre_fc_norm_hidden.weight")
+        h = torch.cat([e, hh], -1) @ self.w["mtp.fc.weight"].t()
+        p, st = "mtp.layers.0", state.layers[0]
+        h = h + self._attention(self._norm(h, p + ".input_layernorm.weight"), st, p + ".self_attn", start, None)
+        h = h + self._ffn(self._norm(h, p + ".post_attention_layernorm.weight"), p + ".mlp")
+        state.length = start + T
+        head = self.w["model.embed_tokens.weight"] if c.tie_embeddings else self.w["lm_head.weight"]
+        return self._norm(h, "mtp.norm.weight") @ head.t(), h, state
+
+
+def copy_family_state(state: FamilyState) -> FamilyState:
+    """A state that can be advanced without touching ``state`` (the model never writes its tensors in place)."""
+    from dataclasses import replace
+    return FamilyState(state.length, [replace(l) for l in state.layers])
+
+
+class EagerFamilyExecutor(StatefulEagerExecutor):
     """``execute(segments)`` on ``EagerFamilyModel`` with one explicit state per request slot (no pages, no prefix
-    sharing: ``keeps_request_state`` tells the engine so)."""
+    sharing: ``keeps_request_state`` tells the engine so); with ``speculative_depth`` > 0 and a checkpoint that carries
+    the multi-token-prediction head, greedy requests decode in lossless draft / review rounds."""
 
-    accepts_features = True
-    keeps_request_state = True
-
-    def __init__(self, cfg: ModelConfig, weights: Mapping[str, torch.Tensor], kv_bits: tuple[int, int] | None = None) -> None:
+    def __init__(self, cfg: ModelConfig, weights: Mapping[str, torch.Tensor], kv_bits: tuple[int, int] | None = None,
+                 speculative_depth: int = 0) -> None:
         self.cfg = cfg
-        self.model = EagerFamilyModel(cfg, weights, kv_bits)
-        self._states: dict[int, tuple[int, FamilyState]] = {}
-        self.h2d_bytes_last = self.d2h_bytes_last = self.kernel_launches_last = 0
+        super().__init__(EagerFamilyModel(cfg, weights, kv_bits), speculative_depth)
 
-    def copy_pages(self, pairs) -> None:
-        if pairs:
-            raise RuntimeError("this executor keeps no pages: copy-on-write cannot occur with the prefix cache off")
+    def _new_state(self) -> FamilyState:
+        return FamilyState()
 
-    def execute(self, segs: list) -> np.ndarray:
-        from ..executor.eager_executor import sample_row
-        out = []
-        for s in segs:
-            held = self._states.get(s.request_slot)
-            if s.start == 0 or held is None or held[0] != s.uid:
-                if s.start != 0:
-                    raise RuntimeError(f"slot {s.request_slot}: no state for a segment that starts at {s.start}")
-                held = (s.uid, FamilyState())
-                self._states[s.request_slot] = held
-            if held[1].length != s.start:
-                raise RuntimeError(f"slot {s.request_slot}: state holds {held[1].length} tokens, the segment starts at {s.start}")
-            logits, _ = self.model.forward(list(s.token_ids), held[1], s.positions3, s.embeds, last_only=True)
-            if s.sample:
-                out.append(sample_row(logits[0], s))
-        return np.asarray(out, dtype=np.int32)
+    def _copy(self, state: FamilyState) -> FamilyState:
+        return copy_family_state(state)

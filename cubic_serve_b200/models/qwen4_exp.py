@@ -36,6 +36,7 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
+from ..executor.stateful_executor import StatefulEagerExecutor
 from ..ops import eager
 from ..ops import eager_sparse as sp
 
@@ -654,116 +655,21 @@ def copy_state(state: RequestState) -> RequestState:
                                        for l in state.layers])
 
 
-@dataclass
-class _Slot:
-    uid: int
-    state: RequestState
-    draft: RequestState | None = None          # the draft head's state: caught up to the position before the last one
-    carried: torch.Tensor | None = None        # the target's multi-stream residual at the last position, [1, S H]
-
-
-class Qwen4ExpEagerExecutor:
-    """``execute(segments)`` of the engine on the eager model: one explicit state per request slot.  A segment that
-    starts at position 0 (a new request, or one recomputed after preemption) starts a fresh state; pages are not used
-    (the state holds K / V), and there is no prefix sharing.
-
-    With ``speculative_depth`` > 0 (the checkpoint carries the draft head) decode steps of greedy, unconstrained
-    requests run as draft / review rounds: the head proposes up to ``depth`` tokens from the root token and the
-    target's residual of the previous position, the target reviews root + drafts in one pass on a copy of the state,
-    the longest agreeing prefix and the target's own next token are emitted, and the committed state is advanced over
-    the accepted tokens only.  The head's state follows the committed tokens with the TARGET's residuals (its draft
-    steps run on a copy), so proposals never depend on rejected drafts.  Lossless: the emitted tokens are those of
-    plain greedy decoding."""
-
-    accepts_features = True
-    keeps_request_state = True
+class Qwen4ExpEagerExecutor(StatefulEagerExecutor):
+    """``execute(segments)`` of the engine on the eager model: one explicit state per request slot (a segment that
+    starts at position 0 starts a fresh state; the state holds K / V, so pages are not used and there is no prefix
+    sharing).  With ``speculative_depth`` > 0 and a checkpoint that carries the draft head, decode steps of greedy,
+    unconstrained requests run as lossless draft / review rounds (``executor/stateful_executor.py``)."""
 
     def __init__(self, cfg: Qwen4ExpConfig, weights: Mapping[str, torch.Tensor], speculative_depth: int = 0) -> None:
         self.cfg = cfg
-        self.model = Qwen4ExpModel(cfg, weights)
-        if speculative_depth and not self.model.has_draft_head:
-            raise ValueError("speculative rounds need the checkpoint's draft head (mtp.* tensors)")
-        self.speculative_depth = int(speculative_depth)
-        self._slots: dict[int, _Slot] = {}
-        self.last_round: dict | None = None
-        self.h2d_bytes_last = self.d2h_bytes_last = self.kernel_launches_last = 0
+        super().__init__(Qwen4ExpModel(cfg, weights), speculative_depth)
 
-    def copy_pages(self, pairs) -> None:
-        if pairs:
-            raise RuntimeError("this executor keeps no pages: copy-on-write cannot occur with the prefix cache off")
+    def _new_state(self) -> RequestState:
+        return RequestState()
 
-    def _slot(self, s) -> _Slot:
-        held = self._slots.get(s.request_slot)
-        if s.start == 0 or held is None or held.uid != s.uid:
-            if s.start != 0:
-                raise RuntimeError(f"slot {s.request_slot}: no state for a segment that starts at {s.start}")
-            held = _Slot(s.uid, RequestState())
-            self._slots[s.request_slot] = held
-        if held.state.length != s.start:
-            raise RuntimeError(f"slot {s.request_slot}: state holds {held.state.length} tokens, the segment starts at {s.start}")
-        return held
-
-    def _advance(self, slot: _Slot, tokens: list[int], positions3=None, embeds=None) -> torch.Tensor:
-        """Run the target over ``tokens`` on the slot's committed state and let the draft head follow: the head sees
-        (token i + 1, residual of position i) for every position whose successor is known."""
-        logits, _ = self.model.forward(tokens, slot.state, positions3, embeds, last_only=True)
-        if self.speculative_depth:
-            fb = self.model.last_feedback
-            head_tokens = ([tokens[0]] if slot.carried is not None else []) + tokens[1:]
-            head_fb = torch.cat(([slot.carried] if slot.carried is not None else []) + [fb[:-1]])
-            if head_tokens:
-                _, _, slot.draft = self.model.draft_forward(head_tokens, head_fb, slot.draft)
-            slot.carried = fb[-1:].clone()
-        return logits[0]
-
-    def execute(self, segs: list) -> np.ndarray:
-        from ..executor.eager_executor import sample_row
-        out = []
-        for s in segs:
-            logits = self._advance(self._slot(s), [int(t) for t in s.token_ids], s.positions3, s.embeds)
-            if s.sample:
-                out.append(sample_row(logits, s))
-        return np.asarray(out, dtype=np.int32)
-
-    def execute_speculative(self, segs: list, depths: list[int] | None = None) -> list[list[int]]:
-        """One round per decode segment (its root token); returns the emitted tokens of every request."""
-        from ..executor.eager_executor import sample_row
-        outs, accepted, proposed = [], [], []
-        for i, s in enumerate(segs):
-            K = self.speculative_depth if depths is None else min(self.speculative_depth, int(depths[i]))
-            slot = self._slot(s)
-            plain = K <= 0 or len(s.token_ids) != 1 or s.temperature > 0 or s.mask is not None or slot.carried is None
-            if plain:
-                outs.append([sample_row(self._advance(slot, [int(t) for t in s.token_ids], s.positions3, s.embeds), s)])
-                accepted.append(0)
-                proposed.append(0)
-                continue
-            root = int(s.token_ids[0])
-            # proposals on a copy of the head's state: draft steps feed on the head's own residual
-            dstate = copy_state(slot.draft) if slot.draft is not None else None
-            drafts, tok, fb = [], root, slot.carried
-            for _ in range(K):
-                lg, fb, dstate = self.model.draft_forward([tok], fb, dstate)
-                tok = int(lg[0].argmax())
-                drafts.append(tok)
-            # review: root + drafts in one pass on a copy of the committed state
-            pos3 = None
-            if s.positions3 is not None:
-                p0 = np.asarray(s.positions3)[:, :1]
-                pos3 = p0 + np.arange(K + 1)[None, :]
-            logits, _ = self.model.forward([root] + drafts, copy_state(slot.state), pos3)
-            target = logits.argmax(-1).tolist()
-            a = 0
-            while a < K and drafts[a] == target[a]:
-                a += 1
-            # commit the accepted prefix (the head follows with the target's residuals)
-            self._advance(slot, [root] + drafts[:a], None if pos3 is None else pos3[:, :a + 1])
-            outs.append([int(t) for t in target[:a + 1]])
-            accepted.append(a)
-            proposed.append(K)
-        self.last_round = {"depth": max(proposed, default=0), "accepted": accepted, "proposed": proposed,
-                           "proposal_ms": 0.0, "target_ms": 0.0}
-        return outs
+    def _copy(self, state: RequestState) -> RequestState:
+        return copy_state(state)
 
 
 def admit_qwen4_exp_checkpoint(path):

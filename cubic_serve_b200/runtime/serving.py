@@ -119,7 +119,10 @@ def build_backend(args, devices: list[int], tp: int, spec, k_bits: int, v_bits: 
             # projection biases, any head width) run on the eager family model with per-request state
             from ..models.eager_family import EagerFamilyExecutor, family_weights_from_checkpoint, random_family_weights
             fw = family_weights_from_checkpoint(ck) if ck is not None else random_family_weights(cfg, args.seed)
-            executor = EagerFamilyExecutor(cfg, fw, kv_bits=(k_bits, v_bits))
+            depth = getattr(spec, "num_speculative_tokens", 0) if spec is not None and getattr(spec, "method", "") == "mtp" else 0
+            if depth and not cfg.mtp_layers:
+                raise SystemExit("this checkpoint carries no MTP head (no mtp.* tensors)")
+            executor = EagerFamilyExecutor(cfg, fw, kv_bits=(k_bits, v_bits), speculative_depth=depth)
         else:
             dense = dense_weights_from_checkpoint(ck) if ck is not None else random_dense_weights(cfg, args.seed)
             executor = EagerPagedExecutor(cfg, dense, pages, kv_bits=(k_bits, v_bits))

@@ -121,3 +121,47 @@ def test_engine_serves_what_the_native_runner_refuses(tmp_path):
     w2["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(512)
     assert not torch.allclose(EF.EagerFamilyModel(ck.cfg, w2).forward(prompt, last_only=True)[0],
                               model.forward(prompt, last_only=True)[0], atol=1e-4)
+
+
+def test_draft_head_of_a_hybrid_expert_checkpoint_runs_lossless_rounds(tmp_path):
+    """A hybrid + experts checkpoint with its multi-token-prediction head (gated attention layer with routed and shared
+    experts): admitted by the closed inventory, and its draft / review rounds through the engine emit the tokens of
+    plain greedy decoding."""
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SamplingParams, SchedulerConfig
+    cfg = ModelConfig(name="hm", family="qwen3_5_moe", num_layers=4, hidden_size=128, num_q_heads=2, num_kv_heads=1,
+                      head_dim=64, intermediate_size=0, vocab_size=384, rotary_dim=32, qk_norm=True, zero_centered_norm=True,
+                      gdn_interval=4, gdn_k_heads=1, gdn_v_heads=2, attn_output_gate=True, num_experts=4, experts_per_token=2,
+                      moe_intermediate_size=128, shared_intermediate_size=128, mtp_layers=1, quant=QuantSpec("none", 16, 0))
+    ck = C.admit_checkpoint(C.write_random_checkpoint(tmp_path / "hm", cfg, seed=8, std=0.08))
+    assert ck.cfg.mtp_layers == 1 and ck.cfg.is_hybrid and ck.cfg.is_moe
+    assert "mtp.layers.0.mlp.experts.3.down_proj" in ck.payloads and "mtp.layers.0.mlp.shared_expert_gate.weight" in ck.plain
+    w = EF.family_weights_from_checkpoint(ck)
+    assert w["mtp.layers.0.self_attn.q_proj.weight"].shape == (2 * 2 * 64, 128) and w["mtp.fc.weight"].shape == (128, 256)
+    model = EF.EagerFamilyModel(ck.cfg, w)
+    assert model.has_draft_head
+    toks = list(range(30, 52))
+    _, st = model.forward(toks)
+    fb = model.last_feedback
+    d_all, h_all, _ = model.draft_forward(toks[1:], fb[:-1])
+    d1, _, s1 = model.draft_forward(toks[1:9], fb[:8])
+    d2, _, s1 = model.draft_forward(toks[9:], fb[8:-1], s1)
+    assert (torch.cat([d1, d2]) - d_all).abs().max() < 1e-4 and h_all.shape == (21, 128)
+    prompts = [toks, [7, 8, 9, 10, 11]]
+
+    def run(depth):
+        ex = EF.EagerFamilyExecutor(ck.cfg, w, speculative_depth=depth)
+        eng = LLMEngine(ex, 64, SchedulerConfig(prefill_chunk_tokens=16, max_model_len=128))
+        ids = [eng.add_request(p, SamplingParams(max_tokens=8)) for p in prompts]
+        got = {i: [] for i in ids}
+        while eng.has_unfinished:
+            for o in eng.step():
+                if o.token_id is not None:
+                    got[o.request_id].append(o.token_id)
+        return [got[i] for i in ids], eng, ex
+    plain, _, _ = run(0)
+    spec, eng, ex = run(2)
+    assert spec == plain and getattr(eng, "spec_rounds", 0) > 0 and ex.last_round["proposed"]
+    no_head = {k: v for k, v in w.items() if not k.startswith("mtp.")}
+    with pytest.raises(ValueError):
+        EF.EagerFamilyExecutor(replace(ck.cfg, mtp_layers=0), no_head, speculative_depth=2)
