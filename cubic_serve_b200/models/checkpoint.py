@@ -190,6 +190,15 @@ class AdmittedCheckpoint:
     def payload(self, module: str) -> dict[str, torch.Tensor]:
         return {suffix: self.store.get(name) for suffix, name in self.payloads[module].items()}
 
+    def plain_tensor(self, name: str) -> torch.Tensor:
+        """A tensor of the plain inventory.  The embedding table and ``lm_head`` of some checkpoints are quantized like
+        the projections; they are decoded here, once, at load (the kernels read them as bf16 rows)."""
+        module = name[:-len(".weight")] if name.endswith(".weight") else None
+        if module not in self.payloads:
+            return self.store.get(name)
+        rows = self.cfg.vocab_size
+        return _dense_of(self.cfg.quant.method, self.payload(module), (rows, self.cfg.hidden_size), self.cfg.quant)
+
 
 def admit_checkpoint(path: str | Path) -> AdmittedCheckpoint:
     path = Path(path)
@@ -219,6 +228,14 @@ def admit_checkpoint(path: str | Path) -> AdmittedCheckpoint:
                 raise CheckpointError(f"{module}: act-order (non-trivial weight_g_idx) checkpoints are not supported")
     plain_map = {}
     for name in plain:
+        if name in ("model.embed_tokens.weight", "lm_head.weight"):
+            module = name[:-len(".weight")]
+            found = {s: f"{module}.{s}" for s in suffixes if f"{module}.{s}" in store}
+            if set(found) - {"weight"}:                    # a quantized table: decoded at load (``plain_tensor``)
+                payloads[module] = found
+                claimed.update(found.values())
+                plain_map[name] = module
+                continue
         if name not in store:
             raise CheckpointError(f"missing tensor {name}")
         plain_map[name] = name
@@ -501,9 +518,9 @@ def load_decoder_weights(ck: AdmittedCheckpoint, device, tp_rank: int = 0, tp_si
             lw.q_norm = (ck.store.get(f"{p}.self_attn.q_norm.weight").float() + one).to(device, bf)
             lw.k_norm = (ck.store.get(f"{p}.self_attn.k_norm.weight").float() + one).to(device, bf)
         layers.append(lw)
-    embed_full = ck.store.get("model.embed_tokens.weight").to(device, bf)
+    embed_full = ck.plain_tensor("model.embed_tokens.weight").to(device, bf)
     v_local = cfg.vocab_size // tp_size
-    head = embed_full if cfg.tie_embeddings else ck.store.get("lm_head.weight").to(device, bf)
+    head = embed_full if cfg.tie_embeddings else ck.plain_tensor("lm_head.weight").to(device, bf)
     head = head[tp_rank * v_local:(tp_rank + 1) * v_local].contiguous()
     return DecoderWeights(embed=embed_full[tp_rank * v_local:(tp_rank + 1) * v_local], layers=layers,
                           final_norm=ck.store.get("model.norm.weight").to(device, bf), lm_head=wq_pack.pack_bf16(head),

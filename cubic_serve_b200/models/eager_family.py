@@ -97,7 +97,7 @@ def family_weights_from_checkpoint(ck) -> dict[str, torch.Tensor]:
         w[f"{module}.weight"] = p["weight"].float() if len(p) == 1 and "weight" in p else \
             _dense_of(cfg.quant.method, p, shape, cfg.quant).float()
     for name in plain:
-        w[name] = ck.store.get(name).float()
+        w[name] = ck.plain_tensor(name).float()
     return w
 
 

@@ -88,8 +88,8 @@ def dense_weights_from_checkpoint(ck) -> DenseWeights:
             lin(m["q"]), lin(m["k"]), lin(m["v"]), lin(m["o"]), lin(m["gate"]), lin(m["up"]), lin(m["down"]),
             get(f"{pre}.self_attn.q_norm.weight") if cfg.qk_norm else None,
             get(f"{pre}.self_attn.k_norm.weight") if cfg.qk_norm else None))
-    embed = get("model.embed_tokens.weight")
-    head = embed if cfg.tie_embeddings else get("lm_head.weight")
+    embed = ck.plain_tensor("model.embed_tokens.weight").float()
+    head = embed if cfg.tie_embeddings else ck.plain_tensor("lm_head.weight").float()
     return DenseWeights(embed, layers, get("model.norm.weight"), head)
 
 

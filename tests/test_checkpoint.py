@@ -381,3 +381,43 @@ def test_shared_expert_is_loaded_per_rank(tmp_path):
     ck2 = C.admit_checkpoint(C.write_random_checkpoint(tmp_path / "w", wide, seed=3))
     with pytest.raises(C.CheckpointError, match="eager execution mode"):
         C.load_decoder_weights(ck2, "cpu")
+
+
+@pytest.mark.parametrize("method,bits,group", [("cubic", 4, 128), ("int", 8, 128), ("fp8", 8, 0)])
+def test_quantized_head_and_embedding_are_decoded_at_load(tmp_path, method, bits, group):
+    """Checkpoints that quantize ``lm_head`` / ``embed_tokens`` like their projections: the payload is owned by the
+    inventory and decoded once at load."""
+    from safetensors.torch import load_file, save_file
+
+    from cubic_serve_b200.models.reference import dense_weights_from_checkpoint
+    cfg = replace(BASE, quant=QuantSpec(method, bits, group))
+    path = C.write_random_checkpoint(tmp_path / method, cfg, seed=6, std=0.05)
+    t = {k: v.clone() for k, v in load_file(str(path / "model.safetensors")).items()}      # no view of the file: it is rewritten
+    originals = {}
+    for name in ("lm_head.weight", "model.embed_tokens.weight"):
+        dense = t.pop(name).float()
+        originals[name] = dense
+        for suffix, v in C.quantize_payload(dense, cfg.quant).items():
+            t[f"{name[:-len('.weight')]}.{suffix}"] = v.contiguous()
+    save_file(t, str(path / "model.safetensors"))
+    ck = C.admit_checkpoint(path)
+    assert "lm_head" in ck.payloads and "model.embed_tokens" in ck.payloads
+    for name, dense in originals.items():
+        got = ck.plain_tensor(name).float()
+        assert got.shape == dense.shape and ((got - dense).norm() / dense.norm()).item() < (0.12 if bits == 4 else 0.04)
+    w = C.load_decoder_weights(ck, "cpu", tp_rank=1, tp_size=2)
+    v = cfg.vocab_size // 2
+    assert w.lm_head.n == v and w.embed.shape[0] == v
+    head = wq_pack.unpack_to_dense(w.lm_head)[:v].float()
+    assert ((head - ck.plain_tensor("lm_head.weight").float()[v:].to(torch.bfloat16).float()).abs().max()).item() < 1e-6
+    dw = dense_weights_from_checkpoint(ck)
+    assert dw.lm_head.shape == (cfg.vocab_size, cfg.hidden_size)
+    # a checkpoint that has neither form is still refused
+    for k in [k for k in t if k.startswith("lm_head.")]:
+        del t[k]
+    other = tmp_path / (method + "-nohead")
+    other.mkdir()
+    (other / "config.json").write_text((path / "config.json").read_text())
+    save_file(t, str(other / "model.safetensors"))
+    with pytest.raises(C.CheckpointError, match="missing tensor lm_head.weight"):
+        C.admit_checkpoint(other)
