@@ -143,7 +143,7 @@ class ModelConfig:
             qk_norm="Qwen3" in arch,
             shared_intermediate_size=int(text.get("shared_expert_intermediate_size") or 0) if n_exp else 0,
             qkv_bias=bool(text.get("qkv_bias", arch.startswith("Qwen2"))),
-            tie_embeddings=bool(text.get("tie_word_embeddings", False)),
+            tie_embeddings=bool(text.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False))),
             max_position=int(text.get("max_position_embeddings", 40960)),
             num_experts=n_exp,
             experts_per_token=text.get("num_experts_per_tok", 0) if n_exp else 0,

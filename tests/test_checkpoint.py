@@ -421,3 +421,16 @@ def test_quantized_head_and_embedding_are_decoded_at_load(tmp_path, method, bits
     save_file(t, str(other / "model.safetensors"))
     with pytest.raises(C.CheckpointError, match="missing tensor lm_head.weight"):
         C.admit_checkpoint(other)
+
+
+def test_multimodal_config_keys_at_the_root(tmp_path):
+    """``tie_word_embeddings`` of a multimodal ``config.json`` sits beside ``text_config``, rotary parameters inside it."""
+    import json
+    doc = {"architectures": ["Qwen3VLForConditionalGeneration"], "tie_word_embeddings": True,
+           "text_config": {"hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2,
+                           "head_dim": 64, "intermediate_size": 512, "vocab_size": 320,
+                           "rope_parameters": {"rope_theta": 5e6, "mrope_section": [16, 8, 8]}}}
+    p = tmp_path / "config.json"
+    p.write_text(json.dumps(doc))
+    cfg = ModelConfig.from_hf_config(p)
+    assert cfg.tie_embeddings and cfg.rope_theta == 5e6 and cfg.mrope_section == (16, 8, 8) and cfg.qk_norm
