@@ -575,3 +575,35 @@ def test_clip_of_decoded_frames_through_the_processor():
     too_long = Message(Role.USER, (ContentPart("video", data=frames * 2),))
     with pytest.raises(RequestError):
         proc.plan(CanonicalChatRequest("openai", "m", (too_long,), request_id="w"))
+
+
+def test_segment_inputs_cover_every_cut_of_a_prompt():
+    """However a prompt with two media spans is cut into segments, the pieces put together are the whole: feature rows
+    land on their tokens exactly once, positions follow the prompt and then the sequence index plus the offset."""
+    from cubic_serve_b200.runtime.multimodal import MultimodalInput
+    n = 40
+    a, b = torch.arange(6 * 4).float().view(6, 4), 100 + torch.arange(4 * 4).float().view(4, 4)
+    pos, delta = mrope_positions([0] * n, [(3, 6, (1, 4, 6)), (20, 4, (1, 4, 4))], 2)
+    mm = MultimodalInput([(3, a, b"a"), (20, b, b"b")], np.asarray(pos), delta)
+    rng = np.random.default_rng(0)
+    for _ in range(50):
+        cuts = sorted(set(rng.integers(1, n + 8, size=rng.integers(0, 6)).tolist()) | {0, n + 8})
+        rows = torch.full((n + 8, 4), -1.0)
+        got_pos = np.full((3, n + 8), -1, dtype=np.int64)
+        for lo, hi in zip(cuts, cuts[1:]):
+            embeds, p3 = mm.segment_inputs(lo, hi - lo)
+            assert p3.shape == (3, hi - lo)
+            got_pos[:, lo:hi] = p3
+            for off, r in embeds:
+                assert (rows[lo + off:lo + off + r.shape[0]] == -1).all()          # written once
+                rows[lo + off:lo + off + r.shape[0]] = r
+        assert torch.equal(rows[3:9], a) and torch.equal(rows[20:24], b) and float(rows[9:20].max()) == -1
+        assert (got_pos[:, :n] == np.asarray(pos)).all()
+        assert (got_pos[:, n:] == np.arange(n, n + 8)[None, :] + delta).all()
+    keys = mm.key_tokens(list(range(n)))
+    assert keys[:3] == [0, 1, 2] and all(k < 0 for k in keys[3:9] + keys[20:24]) and keys[9:20] == list(range(9, 20))
+    assert len(set(keys[3:9])) == 6
+    other = MultimodalInput([(3, a, b"x"), (20, b, b"b")], np.asarray(pos), delta).key_tokens(list(range(n)))
+    assert other[3:9] != keys[3:9] and other[20:24] == keys[20:24]
+    with pytest.raises(ValueError):
+        MultimodalInput([(3, a, b"a"), (5, b, b"b")], np.asarray(pos), delta)
