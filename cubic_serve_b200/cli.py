@@ -184,7 +184,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--media-file-root", "--allowed-local-media-path", dest="media_file_root", action="append", default=[],
                    help="directory file: media may be read from")
     g.add_argument("--mm-preprocess-workers", type=int, default=2,
-                   help="accepted for compatibility: media are decoded and cut into patches on the request's thread")
+                   help="threads that fetch, decode and cut the media of one request into patches")
     g.add_argument("--mm-worker-layout", choices=("colocated", "separate"), default="colocated",
                    help="colocated: the vision tower shares the first GPU (the only layout of this build)")
     g.add_argument("--video-fps", type=float, default=2.0,

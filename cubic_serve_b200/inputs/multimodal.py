@@ -57,7 +57,8 @@ class VisionTokens:
 class MultimodalChatProcessor(ChatInputProcessor):
     def __init__(self, tokenizer, vision_service, tokens: VisionTokens, geometry: PatchGeometry | None = None,
                  resolver: MediaResolver | None = None, default_thinking: bool | None = None,
-                 max_model_len: int | None = None, max_items: int = 16, video_max_frames: int = 768) -> None:
+                 max_model_len: int | None = None, max_items: int = 16, video_max_frames: int = 768,
+                 preprocess_workers: int = 2) -> None:
         super().__init__(tokenizer, default_thinking, max_model_len)
         self.vision, self.tokens = vision_service, tokens
         cfg = vision_service.encoder.cfg
@@ -68,6 +69,12 @@ class MultimodalChatProcessor(ChatInputProcessor):
         self.resolver = resolver or MediaResolver()
         self.max_items = max_items
         self.video_max_frames = video_max_frames
+        # media of one request are fetched, decoded and cut into patches concurrently (I/O, Pillow and the resize release
+        # the interpreter lock)
+        self._pool = None
+        if preprocess_workers > 1:
+            from concurrent.futures import ThreadPoolExecutor
+            self._pool = ThreadPoolExecutor(max_workers=preprocess_workers, thread_name_prefix="media-prep")
 
     # ------------------------------------------------------------------ media parts -> patches
     def _patches(self, part: ContentPart) -> MediaPatches:
@@ -89,13 +96,18 @@ class MultimodalChatProcessor(ChatInputProcessor):
         """Everything except the encoding: media resolved, decoded and cut into patches, the prompt rendered and its
         placeholders expanded, positions computed, the encoder's capacity limits checked."""
         t = self.tokens
+        media = [p for m in req.messages for p in m.parts if p.kind in ("image", "video")]
+        if len(media) > self.max_items:
+            raise RequestError(f"a request may carry {self.max_items} media items", param="messages")
+        patches = iter(list(self._pool.map(self._patches, media)) if self._pool is not None and len(media) > 1
+                       else [self._patches(p) for p in media])
         items: list[tuple[str, MediaPatches]] = []
         msgs = []
         for m in req.messages:
             parts = []
             for p in m.parts:
                 if p.kind in ("image", "video"):
-                    items.append((p.kind, self._patches(p)))
+                    items.append((p.kind, next(patches)))
                     pad = t.image_text if p.kind == "image" else t.video_text
                     parts.append(ContentPart("text", t.start_text + pad + t.end_text))
                 else:
@@ -104,8 +116,6 @@ class MultimodalChatProcessor(ChatInputProcessor):
         if not items:
             base = super().build(req)
             return InputPlan(tuple(base.token_ids), base.prompt_text, base.starts_in_reasoning)
-        if len(items) > self.max_items:
-            raise RequestError(f"a request may carry {self.max_items} media items", param="messages")
         base = super().build(replace(req, messages=tuple(msgs)))
         merge = self.geometry.merge_size
         ids: list[int] = []

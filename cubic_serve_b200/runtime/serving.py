@@ -315,7 +315,8 @@ def build_media_processor(args, ck, tok, executor, max_len: int):
     return MultimodalChatProcessor(tok, service, VisionTokens.from_hf(ck.raw_config), resolver=MediaResolver(policy),
                                    default_thinking=args.thinking, max_model_len=max_len,
                                    max_items=getattr(args, "max_media_items", 16),
-                                   video_max_frames=getattr(args, "video_max_frames", 768))
+                                   video_max_frames=getattr(args, "video_max_frames", 768),
+                                   preprocess_workers=getattr(args, "mm_preprocess_workers", 2))
 
 
 class StatusReporter(threading.Thread):

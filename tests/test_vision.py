@@ -607,3 +607,35 @@ def test_segment_inputs_cover_every_cut_of_a_prompt():
     assert other[3:9] != keys[3:9] and other[20:24] == keys[20:24]
     with pytest.raises(ValueError):
         MultimodalInput([(3, a, b"a"), (5, b, b"b")], np.asarray(pos), delta)
+
+
+def test_several_images_are_prepared_concurrently_and_keep_their_order():
+    from cubic_serve_b200.contracts.request import CanonicalChatRequest, ContentPart, Message, RequestError, Role
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    from cubic_serve_b200.inputs.multimodal import MultimodalChatProcessor, VisionTokens
+
+    class Tok(ByteTokenizer):
+        SPECIALS = ByteTokenizer.SPECIALS + ("<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+    tok = Tok()
+    ids = tok.special_ids
+    vt = VisionTokens(ids["<|image_pad|>"], ids["<|video_pad|>"], ids["<|vision_start|>"], ids["<|vision_end|>"])
+    cfg = _cfg()
+    svc = VisionService(VisionEncoder(cfg, random_vision_weights(cfg, 7)))
+    geo = PatchGeometry(4, 2, 2, min_pixels=8 * 8, max_pixels=32 * 32)
+    sizes = [(8, 8), (16, 24), (24, 8), (8, 32)]
+    urls = ["data:image/png;base64," + base64.b64encode(_png(h, w, seed=i)).decode() for i, (h, w) in enumerate(sizes)]
+    parts = []
+    for u in urls:
+        parts += [ContentPart("text", "and "), ContentPart("image", media_url=u)]
+    req = CanonicalChatRequest("openai", "m", (Message(Role.USER, tuple(parts)),), request_id="many")
+    threads = []
+    many = MultimodalChatProcessor(tok, svc, vt, geo, preprocess_workers=3)
+    inner = many._patches
+    many._patches = lambda p: (threads.append(threading.current_thread().name), inner(p))[1]
+    plan = many.plan(req)
+    one = MultimodalChatProcessor(tok, svc, vt, geo, preprocess_workers=1).plan(req)
+    assert [p.grid for p in plan.placements] == [(1, h // 4, w // 4) for h, w in sizes]
+    assert [p.digest for p in plan.placements] == [p.digest for p in one.placements] and plan.token_ids == one.token_ids
+    assert any(t.startswith("media-prep") for t in threads)
+    with pytest.raises(RequestError):
+        MultimodalChatProcessor(tok, svc, vt, geo, max_items=3).plan(req)
