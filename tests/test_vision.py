@@ -639,3 +639,31 @@ def test_several_images_are_prepared_concurrently_and_keep_their_order():
     assert any(t.startswith("media-prep") for t in threads)
     with pytest.raises(RequestError):
         MultimodalChatProcessor(tok, svc, vt, geo, max_items=3).plan(req)
+
+
+def test_preempted_request_with_media_recomputes_to_the_same_tokens():
+    """A pool too small for two requests preempts one; when it is recomputed (prompt and the tokens it had generated in
+    one prefill) its feature rows and positions are applied again, and the outputs equal those of a roomy pool."""
+    g = torch.Generator().manual_seed(5)
+    prompt_a = [5, 6, 7] + [900] * 24 + list(range(20, 41))             # 48 tokens
+    prompt_b = [8, 9] + [900] * 24 + list(range(50, 72))
+    fa, fb = torch.randn(24, 256, generator=g), torch.randn(24, 256, generator=g)
+    grid = (1, 8, 12)
+
+    def run(pages):
+        from cubic_serve_b200.runtime.scheduler import SamplingParams
+        eng, _ = _engine(pages=pages)
+        ra = eng.add_request(prompt_a, SamplingParams(max_tokens=40), multimodal=_mm(48, 3, fa, b"A", grid))
+        rb = eng.add_request(prompt_b, SamplingParams(max_tokens=40), multimodal=_mm(48, 2, fb, b"B", grid))
+        out = {ra: [], rb: []}
+        preempted = 0
+        while eng.has_unfinished:
+            for o in eng.step():
+                if o.token_id is not None:
+                    out[o.request_id].append(o.token_id)
+            preempted = max(preempted, sum(r.preemptions for r in eng.requests.values()))
+        return out[ra], out[rb], preempted
+    a0, b0, p0 = run(64)
+    a1, b1, p1 = run(10)                                                # 9 usable pages: not enough for 2 x 88 tokens
+    assert p0 == 0 and p1 > 0
+    assert (a1, b1) == (a0, b0) and len(a0) == 40
