@@ -106,6 +106,14 @@ def render_metrics(backend, model: str) -> str:
                 rows.append((name, kind, text, float(s[key])))
         rows.append(("cubic_last_step_seconds", "gauge", "host time of the last engine step", float(getattr(engine, "last_step_seconds", 0.0))))
         rows.append(("cubic_engine_poisoned", "gauge", "1 after a step failed (the engine refuses work)", 1.0 if getattr(engine, "poisoned", False) else 0.0))
+    vision = getattr(getattr(backend, "processor", None), "vision", None)
+    if vision is not None:                                   # deployments with a vision tower
+        store = vision.store
+        rows += [("cubic_media_encode_calls_total", "counter", "calls of the vision tower", float(vision.encode_calls)),
+                 ("cubic_media_patches_total", "counter", "patches the tower has encoded", float(vision.encoder.encoded_patches)),
+                 ("cubic_media_feature_store_hits_total", "counter", "media items served from encoded features", float(store.hits)),
+                 ("cubic_media_feature_store_misses_total", "counter", "media items that had to be encoded", float(store.misses)),
+                 ("cubic_media_feature_store_bytes", "gauge", "host memory held by encoded features", float(store.bytes))]
     out = []
     for name, kind, text, value in rows:
         out += [f"# HELP {name} {text}", f"# TYPE {name} {kind}", f"{name}{label} {value:g}"]

@@ -463,9 +463,13 @@ def test_http_request_with_an_image_goes_through_the_encoder_thread():
         bad = {**body, "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {
             "url": "data:image/png;base64,iVBORw0KGgoAAAANSUhEUg=="}}]}]}
         broken = await _call(app, "POST", "/v1/chat/completions", bad)
+        metrics = await _call(app, "GET", "/metrics")
         backend.close()
-        return first, second, text, broken
-    (s1, b1), (s2, b2), (s3, _), (s4, b4) = asyncio.run(go())
+        return first, second, text, broken, metrics
+    (s1, b1), (s2, b2), (s3, _), (s4, b4), (sm, bm) = asyncio.run(go())
+    m = {l.split(" ")[0].split("{")[0]: float(l.split(" ")[1]) for l in bm.decode().splitlines() if l and not l.startswith("#")}
+    assert sm == 200 and m["cubic_media_encode_calls_total"] == 1 and m["cubic_media_feature_store_hits_total"] >= 1
+    assert m["cubic_media_feature_store_bytes"] > 0 and m["cubic_media_feature_store_misses_total"] == 1
     assert s1 == s2 == s3 == 200 and s4 == 400
     j1, j2 = json.loads(b1), json.loads(b2)
     assert j1["usage"]["completion_tokens"] == 5 and j1["usage"]["prompt_tokens"] > 15
