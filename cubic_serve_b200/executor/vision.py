@@ -170,6 +170,7 @@ class VisionGraphBucket:
         else:
             out = enc.encode_fixed(self.px, self.fx)
         self.replays += 1
+        enc.encoded_patches += n
         rows = n // enc.cfg.spatial_merge_size ** 2
         return out[:rows].clone()
 
