@@ -11,7 +11,7 @@ import shutil
 from pathlib import Path
 
 REQUIRED_MODULES = ("torch", "numpy", "safetensors")
-OPTIONAL_MODULES = ("transformers", "uvicorn", "xgrammar", "gguf", "prometheus_client")
+OPTIONAL_MODULES = ("transformers", "uvicorn", "xgrammar", "gguf", "prometheus_client", "PIL")   # PIL: image parts
 REQUIRED_SYMBOLS = ("cb_wq_gemm", "cb_wq_gemm_sk", "cb_wq_gemm_act", "cb_wq_gemm_grouped", "cb_paged_attn",
                     "cb_rope_kv_write", "cb_rmsnorm", "cb_sample", "cb_tp_reduce_norm", "cb_ep_dispatch", "cb_moe_route",
                     "cb_gdn_conv", "cb_gdn_delta", "cb_hadamard", "cb_reasoning_budget")
