@@ -225,7 +225,8 @@ class TokenChatBackend:
                     self.stats["requests"] += 1
                     self._publish(live, live.pipeline.start_events(), batch)
                 except AdmissionError as exc:
-                    err = ChatBackendError(exc.status, str(exc), "invalid_request_error" if exc.status == 400 else "rate_limit_exceeded")
+                    kind = {400: "invalid_request_error", 429: "rate_limit_exceeded"}.get(exc.status, "api_error")
+                    err = ChatBackendError(exc.status, str(exc), kind)
                     live.stream.put_threadsafe_nowake(err)
                     live.done = True
                     batch.defer(live.stream)

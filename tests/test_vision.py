@@ -671,3 +671,60 @@ def test_preempted_request_with_media_recomputes_to_the_same_tokens():
     a1, b1, p1 = run(10)                                                # 9 usable pages: not enough for 2 x 88 tokens
     assert p0 == 0 and p1 > 0
     assert (a1, b1) == (a0, b0) and len(a0) == 40
+
+
+def test_a_failing_encoder_ends_the_request_with_a_server_error():
+    """The tower failing for one request (not a capacity refusal) is that request's 500; the backend keeps serving."""
+    import asyncio
+    import json
+    from dataclasses import replace
+
+    from test_api import _call
+
+    from cubic_serve_b200.api.server import CubicASGIApp
+    from cubic_serve_b200.executor.eager_executor import EagerPagedExecutor
+    from cubic_serve_b200.inputs.chat import ByteTokenizer
+    from cubic_serve_b200.inputs.multimodal import MultimodalChatProcessor, VisionTokens
+    from cubic_serve_b200.models.config import ModelConfig
+    from cubic_serve_b200.models.reference import random_dense_weights
+    from cubic_serve_b200.runtime.async_engine import TokenChatBackend
+    from cubic_serve_b200.runtime.engine import LLMEngine
+    from cubic_serve_b200.runtime.scheduler import SchedulerConfig
+
+    class Tok(ByteTokenizer):
+        SPECIALS = ByteTokenizer.SPECIALS + ("<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>")
+    tok = Tok()
+    ids = tok.special_ids
+    cfg = replace(ModelConfig(num_layers=1, hidden_size=64, num_q_heads=2, num_kv_heads=1, head_dim=32, intermediate_size=128,
+                              vocab_size=tok.vocab_size), mrope_section=(8, 4, 4))
+    eng = LLMEngine(EagerPagedExecutor(cfg, random_dense_weights(cfg, 0), 64), 64,
+                    SchedulerConfig(max_running_requests=4, max_model_len=512, max_batched_tokens=256))
+    vcfg = _cfg(out_hidden_size=64)
+    svc = VisionService(VisionEncoder(vcfg, random_vision_weights(vcfg, 3)))
+    calls = {"n": 0}
+    real = svc.encoder.encode
+
+    def flaky(px, grid):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise RuntimeError("out of memory")
+        return real(px, grid)
+    svc.encoder.encode = flaky
+    proc = MultimodalChatProcessor(tok, svc, VisionTokens(ids["<|image_pad|>"], ids["<|video_pad|>"], ids["<|vision_start|>"],
+                                                          ids["<|vision_end|>"]),
+                                   PatchGeometry(4, 2, 2, min_pixels=8 * 8, max_pixels=32 * 32), max_model_len=512)
+    url = "data:image/png;base64," + base64.b64encode(_png(16, 16)).decode()
+    body = {"model": "toy", "max_tokens": 3, "temperature": 0, "messages": [{"role": "user", "content": [
+        {"type": "image_url", "image_url": {"url": url}}]}]}
+
+    async def go():
+        backend = TokenChatBackend(eng, tok, default_max_tokens=8, processor=proc)
+        app = CubicASGIApp(backend, "toy")
+        first = await _call(app, "POST", "/v1/chat/completions", body)
+        second = await _call(app, "POST", "/v1/chat/completions", body)
+        backend.close()
+        return first, second
+    (s1, b1), (s2, b2) = asyncio.run(go())
+    assert s1 == 500 and json.loads(b1)["error"]["type"] == "api_error" and "out of memory" not in b1.decode()
+    assert s2 == 200 and json.loads(b2)["usage"]["completion_tokens"] == 3
+    svc.close()
