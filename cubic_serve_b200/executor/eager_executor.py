@@ -39,6 +39,7 @@ def sample_row(logits: torch.Tensor, s: Segment) -> int:
 
 class EagerPagedExecutor:
     accepts_features = True          # segments may carry encoder feature rows and three-axis positions
+    accepts_deepstack = True         # ... and additions after the first decoder layers
 
     def __init__(self, cfg: ModelConfig, weights: DenseWeights, num_pages: int,
                  kv_bits: tuple[int, int] | None = None) -> None:
@@ -98,5 +99,8 @@ class EagerPagedExecutor:
             h = h + attn.reshape(n, Hq * D) @ l.wo.t()
             x = eager.rmsnorm(h, l.ln2, cfg.rms_eps, cfg.zero_centered_norm)
             h = h + (torch.nn.functional.silu(x @ l.w_gate.t()) * (x @ l.w_up.t())) @ l.w_down.t()
+            for off, rows in (getattr(s, "deep_embeds", None) or ()):
+                if li < rows.shape[1]:
+                    h[off:off + rows.shape[0]] += rows[:, li].float()
         last = eager.rmsnorm(h[-1:], w.final_norm, cfg.rms_eps, cfg.zero_centered_norm)
         return (last @ w.lm_head.t())[0]

@@ -48,6 +48,9 @@ class Segment:
     # those tokens with encoder features; ``positions3`` = int [3, count] rotary positions (None: all axes = position)
     embeds: object = None
     positions3: object = None
+    # [(offset, rows [n, layers, hidden])]: additions to the hidden state at media positions after the first decoder
+    # layers (towers with intermediate outputs; executors that state ``accepts_deepstack``)
+    deep_embeds: object = None
 
 
 class _Staging:

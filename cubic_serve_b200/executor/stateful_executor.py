@@ -67,10 +67,11 @@ class StatefulEagerExecutor:
             raise RuntimeError(f"slot {s.request_slot}: state holds {held.state.length} tokens, the segment starts at {s.start}")
         return held
 
-    def _advance(self, slot: RequestSlot, tokens: list[int], positions3=None, embeds=None) -> torch.Tensor:
+    def _advance(self, slot: RequestSlot, tokens: list[int], positions3=None, embeds=None, deep=None) -> torch.Tensor:
         """Run the target over ``tokens`` on the slot's committed state and let the draft head follow: the head sees
         (token i + 1, feedback of position i) for every position whose successor is known."""
-        logits, _ = self.model.forward(tokens, slot.state, positions3, embeds, last_only=True)
+        extra = {"deep": deep} if deep else {}
+        logits, _ = self.model.forward(tokens, slot.state, positions3, embeds, last_only=True, **extra)
         if self.speculative_depth:
             fb = self.model.last_feedback
             head_tokens = ([tokens[0]] if slot.carried is not None else []) + tokens[1:]
@@ -84,7 +85,8 @@ class StatefulEagerExecutor:
         from .eager_executor import sample_row
         out = []
         for s in segs:
-            logits = self._advance(self._slot(s), [int(t) for t in s.token_ids], s.positions3, s.embeds)
+            logits = self._advance(self._slot(s), [int(t) for t in s.token_ids], s.positions3, s.embeds,
+                                   getattr(s, "deep_embeds", None))
             if s.sample:
                 out.append(sample_row(logits, s))
         return np.asarray(out, dtype=np.int32)

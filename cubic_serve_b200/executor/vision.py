@@ -217,7 +217,9 @@ class VisionService:
                     if bucket is not None and not self.encoder.cfg.deepstack_visual_indexes:
                         feats = bucket.encode(px, call_grid)
                     else:
-                        feats, _ = self.encoder.encode(px, call_grid)
+                        feats, deep = self.encoder.encode(px, call_grid)
+                        if deep:                               # intermediate outputs ride in extra columns of the rows
+                            feats = torch.cat([feats] + deep, 1)
                     parts.append(feats)
                     self.encode_calls += 1
                 rows = torch.cat(parts, 0) if len(parts) > 1 else parts[0]

@@ -149,8 +149,7 @@ class MultimodalChatProcessor(ChatInputProcessor):
         return InputPlan(tuple(ids), base.prompt_text, base.starts_in_reasoning, np.asarray(pos, dtype=np.int32), delta,
                          tuple(placements), tuple(jobs))
 
-    @staticmethod
-    def assemble(plan: InputPlan, encoded: list) -> MultimodalInput | None:
+    def assemble(self, plan: InputPlan, encoded: list) -> MultimodalInput | None:
         """The engine's view of a plan whose jobs were encoded (``encoded``: ``(rows, digest)`` per job, in order)."""
         if not plan.placements:
             return None
@@ -159,7 +158,9 @@ class MultimodalChatProcessor(ChatInputProcessor):
             if rows.shape[0] != p.rows or digest != p.digest:
                 raise ValueError("the encoder's rows do not match the plan's placement")
             spans.append((p.first_token, rows, digest))
-        return MultimodalInput(spans, plan.positions, plan.position_delta)
+        cfg = self.vision.encoder.cfg
+        return MultimodalInput(spans, plan.positions, plan.position_delta,
+                               hidden=cfg.out_hidden_size if cfg.deepstack_visual_indexes else None)
 
     def encode(self, plan: InputPlan) -> list:
         return self.vision.encode([(j.patches, j.grid) for j in plan.jobs])

@@ -207,7 +207,8 @@ class EagerFamilyModel:
         return out
 
     @torch.no_grad()
-    def forward(self, tokens, state: FamilyState | None = None, positions3=None, embeds=None, last_only: bool = False):
+    def forward(self, tokens, state: FamilyState | None = None, positions3=None, embeds=None, last_only: bool = False,
+                deep=None):
         """Logits ``[T, vocab]`` (``[1, vocab]`` with ``last_only``) of ``tokens`` appended to ``state`` (updated in
         place and returned)."""
         c = self.cfg
@@ -230,6 +231,9 @@ class EagerFamilyModel:
             h = h + (self._gdn(x, st, p + ".linear_attn") if c.layer_is_gdn(i) else
                      self._attention(x, st, p + ".self_attn", start, pos3))
             h = h + self._ffn(self._norm(h, p + ".post_attention_layernorm.weight"), p + ".mlp")
+            for off, rows in (deep or ()):                    # the tower's intermediate outputs join after early layers
+                if i < rows.shape[1]:
+                    h[off:off + rows.shape[0]] += rows[:, i].float()
         state.length = start + T
         self.last_feedback = h                                    # the hidden rows before the final norm feed a draft head
         last = self._norm(h[-1:] if last_only else h, "model.norm.weight")
@@ -277,6 +281,8 @@ class EagerFamilyExecutor(StatefulEagerExecutor):
     """``execute(segments)`` on ``EagerFamilyModel`` with one explicit state per request slot (no pages, no prefix
     sharing: ``keeps_request_state`` tells the engine so); with ``speculative_depth`` > 0 and a checkpoint that carries
     the multi-token-prediction head, greedy requests decode in lossless draft / review rounds."""
+
+    accepts_deepstack = True
 
     def __init__(self, cfg: ModelConfig, weights: Mapping[str, torch.Tensor], kv_bits: tuple[int, int] | None = None,
                  speculative_depth: int = 0) -> None:

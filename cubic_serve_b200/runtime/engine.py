@@ -86,6 +86,8 @@ class LLMEngine:
         if multimodal is not None:
             if not getattr(self.executor, "accepts_features", False):
                 raise AdmissionError("this executor serves text only; requests with media are not accepted", status=400)
+            if getattr(multimodal, "deep_layers", 0) and not getattr(self.executor, "accepts_deepstack", False):
+                raise AdmissionError("this executor does not consume the vision tower's intermediate outputs", status=400)
             if multimodal.prompt_length != len(prompt_token_ids):
                 raise AdmissionError("the media positions do not cover the prompt", status=400)
         rid = request_id or f"req-{next(self._ids)}"
@@ -192,6 +194,8 @@ class LLMEngine:
                                 self._budget_init(r) if s.sample and end_id is not None else -2, mask_fn))
             if r.multimodal is not None:
                 segs[-1].embeds, segs[-1].positions3 = r.multimodal.segment_inputs(s.start, s.count)
+                if getattr(r.multimodal, "deep_layers", 0):
+                    segs[-1].deep_embeds = r.multimodal.segment_deep(s.start, s.count)
         return segs
 
     def _review_masks_of(self, matcher):

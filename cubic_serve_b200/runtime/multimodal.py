@@ -25,6 +25,9 @@ class MultimodalInput:
     spans: list                                  # [(first token, rows tensor [n, hidden], digest bytes)]
     positions: np.ndarray                        # int32 [3, prompt length]
     delta: int
+    # width of the decoder's hidden state when the rows carry more than that: the extra columns are the tower's
+    # intermediate ("deepstack") outputs, one block of ``hidden`` columns per early decoder layer they are added after
+    hidden: int | None = None
     _keys: dict | None = field(default=None, repr=False)   # sequence index -> content key
 
     def __post_init__(self) -> None:
@@ -40,6 +43,22 @@ class MultimodalInput:
     @property
     def prompt_length(self) -> int:
         return int(self.positions.shape[1])
+
+    @property
+    def deep_layers(self) -> int:
+        """How many early decoder layers receive an addition at the media positions."""
+        if self.hidden is None or not self.spans:
+            return 0
+        return self.spans[0][1].shape[1] // self.hidden - 1
+
+    def segment_deep(self, start: int, count: int) -> list:
+        """``(offset into the segment, rows [n, layers, hidden])`` of the additions that fall into the segment."""
+        out = []
+        for first, rows, _ in self.spans:
+            lo, hi = max(first, start), min(first + rows.shape[0], start + count)
+            if lo < hi and self.deep_layers:
+                out.append((lo - start, rows[lo - first:hi - first, self.hidden:].reshape(hi - lo, self.deep_layers, self.hidden)))
+        return out
 
     def key_tokens(self, tokens: list[int]) -> list[int]:
         if self._keys is None:
@@ -63,7 +82,8 @@ class MultimodalInput:
         for first, rows, _ in self.spans:
             lo, hi = max(first, start), min(first + rows.shape[0], end)
             if lo < hi:
-                embeds.append((lo - start, rows[lo - first:hi - first]))
+                part = rows[lo - first:hi - first]
+                embeds.append((lo - start, part if self.hidden is None else part[:, :self.hidden]))
         n = self.prompt_length
         pos = np.empty((3, count), dtype=np.int32)
         inside = max(0, min(end, n) - start)

@@ -287,9 +287,9 @@ def build_media_processor(args, ck, tok, executor, max_len: int):
     """The input processor of a multimodal checkpoint: vision tower (on the executor's device when it has one), encoded
     feature store, media policy.  Executors that take no feature rows serve such a checkpoint as text only."""
     import torch
-    if ck.vision.deepstack_visual_indexes:
+    if ck.vision.deepstack_visual_indexes and not getattr(executor, "accepts_deepstack", False):
         log.warning("the vision tower feeds intermediate layers into the decoder (deepstack), which the decoders of this "
-                    "build do not consume: the checkpoint is served as text only")
+                    "execution mode does not consume (--execution-mode eager does): the checkpoint is served as text only")
         return None
     if not getattr(executor, "accepts_features", False):
         log.warning("the checkpoint has a vision tower, but this execution mode serves text only "
