@@ -117,7 +117,11 @@ class FamilyState:
 
 
 class EagerFamilyModel:
-    def __init__(self, cfg: ModelConfig, weights: Mapping[str, torch.Tensor], kv_bits: tuple[int, int] | None = None) -> None:
+    def __init__(self, cfg: ModelConfig, weights: Mapping[str, torch.Tensor], kv_bits: tuple[int, int] | None = None,
+                 exact: bool = False) -> None:
+        """``exact``: the Gated DeltaNet layers run without the storage roundings of the native kernels (bf16 between
+        their steps); the default reproduces those roundings, which is what the kernels are compared with."""
+        self.exact = exact
         want = family_tensor_shapes(cfg)
         missing = sorted(set(want) - set(weights))
         if missing:
@@ -177,13 +181,15 @@ class EagerFamilyModel:
         qkvz = self._lin(x, p + ".in_proj_qkvz").view(T, gk, (2 + 2 * r) * 128)
         q, k = qkvz[..., :128], qkvz[..., 128:256]
         v, z = qkvz[..., 256:256 + r * 128], qkvz[..., 256 + r * 128:]
-        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1).to(torch.bfloat16)
+        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
+        mixed = mixed if self.exact else mixed.to(torch.bfloat16)
         ba = self._lin(x, p + ".in_proj_ba").view(T, gk, 2, r)
         ba = torch.cat([ba[:, :, 0].reshape(T, gv), ba[:, :, 1].reshape(T, gv)], -1)
         conv_w = self.w[p + ".conv1d.weight"].reshape(-1, 4)
-        mixed, st.conv = eager.gdn_conv(mixed, conv_w, st.conv)
+        mixed, st.conv = eager.gdn_conv(mixed, conv_w, st.conv, exact=self.exact)
         out, st.recurrent = eager.gdn_delta(mixed, z.reshape(T, gv * 128), ba, self.w[p + ".A_log"], self.w[p + ".dt_bias"],
-                                            self.w[p + ".norm.weight"], st.recurrent, gk, gv, eps_norm=c.rms_eps)
+                                            self.w[p + ".norm.weight"], st.recurrent, gk, gv, eps_norm=c.rms_eps,
+                                            exact=self.exact)
         return out.float() @ self.w[p + ".out_proj.weight"].t()
 
     def _ffn(self, x: torch.Tensor, p: str) -> torch.Tensor:

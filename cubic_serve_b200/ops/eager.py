@@ -192,7 +192,8 @@ def decode_cache_page(blob: torch.Tensor, d: int, k_bits: int, v_bits: int):
 
 
 # ------------------------------------------------------------------ gated delta net (hybrid family) oracles
-def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, bias: torch.Tensor | None = None):
+def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, bias: torch.Tensor | None = None,
+             exact: bool = False):
     """Depthwise causal conv1d (kernel 4) + SiLU over ONE request's rows ``x[n, C]`` (bf16); ``state[3, C]`` = its
     previous three inputs (None = zeros).  Returns ``(y[n, C] bf16, new state[3, C] bf16)``.  fp32 arithmetic, the
     order of ``csrc/gdn.cu`` (reference oracle: ``ops/eager/hybrid.py:255``)."""
@@ -207,17 +208,19 @@ def gdn_conv(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor | None, bias:
         if bias is not None:
             a = a + bias.float().cpu()
         y[t] = a / (1 + torch.exp(-a))
+    if exact:                                   # fp32 throughout: the arithmetic without the kernels' storage roundings
+        return y, seq[-3:]
     return y.to(torch.bfloat16), seq[-3:].to(torch.bfloat16)
 
 
 def gdn_delta(qkv: torch.Tensor, z: torch.Tensor, ba: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
               norm_w: torch.Tensor, state: torch.Tensor | None, hk: int, hv: int, eps_norm: float = 1e-6,
-              eps_l2: float = 1e-6, d: int = 128, gate: str = "silu"):
+              eps_l2: float = 1e-6, d: int = 128, gate: str = "silu", exact: bool = False):
     """Gated delta rule + gated RMSNorm over ONE request's rows (fp32 recurrence; reference oracle:
     ``ops/eager/hybrid.py:340-548``).  ``state[Hv, d, d]`` fp32 or None; ``gate``: activation of the output gate
     (``silu`` or ``sigmoid``).  Returns ``(out[n, Hv d] bf16, state)``."""
     n = qkv.shape[0]
-    bf = torch.bfloat16
+    bf = torch.float32 if exact else torch.bfloat16      # ``exact``: no storage roundings between the steps
     q = qkv[:, :hk * d].float().cpu().view(n, hk, d)
     k = qkv[:, hk * d:2 * hk * d].float().cpu().view(n, hk, d)
     v = qkv[:, 2 * hk * d:2 * hk * d + hv * d].float().cpu().view(n, hv, d)
