@@ -21,6 +21,26 @@ class QuantSpec:
     lm_head_quantized: bool = False
 
 
+def _rope_scaling(text: dict):
+    """``rope_scaling`` / ``rope_parameters`` of a checkpoint as ``ModelConfig.rope_scaling``.  Forms that change the
+    rotation with the sequence length or rescale the attention logits (dynamic, yarn, longrope) are refused: served with
+    the plain table they would silently lose quality at long context."""
+    for key in ("rope_scaling", "rope_parameters"):
+        rs = text.get(key)
+        if not isinstance(rs, dict):
+            continue
+        kind = rs.get("rope_type", rs.get("type", "default"))
+        if kind in ("default", None) or "mrope_section" in rs and kind == "default":
+            continue
+        if kind == "linear":
+            return ("linear", float(rs["factor"]))
+        if kind == "llama3":
+            return ("llama3", float(rs["factor"]), float(rs["low_freq_factor"]), float(rs["high_freq_factor"]),
+                    int(rs["original_max_position_embeddings"]))
+        raise ValueError(f"rotary scaling of type {kind!r} is not served")
+    return None
+
+
 def _mrope_section(text: dict):
     """``mrope_section`` of ``rope_parameters`` / ``rope_scaling`` when the checkpoint declares three-axis positions."""
     for key in ("rope_parameters", "rope_scaling"):
@@ -71,6 +91,9 @@ class ModelConfig:
     # projections (Qwen2 family): both are served by the eager execution mode only
     shared_intermediate_size: int = 0
     qkv_bias: bool = False
+    # static rescaling of the rotary frequencies: ("linear", factor) or ("llama3", factor, low_freq_factor,
+    # high_freq_factor, original_max_position_embeddings); None = the plain table
+    rope_scaling: tuple | None = None
     # three-axis rotary positions of the multimodal checkpoints: how many frequency slots follow the (temporal, row,
     # column) axis; None = one axis
     mrope_section: tuple[int, int, int] | None = None
@@ -153,6 +176,7 @@ class ModelConfig:
             quant=quant_spec_from_hf(qc),
             eos_token_id=(text.get("eos_token_id") if isinstance(text.get("eos_token_id"), int) else None),
             mrope_section=_mrope_section(text),
+            rope_scaling=_rope_scaling(text),
         )
 
 

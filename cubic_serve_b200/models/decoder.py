@@ -334,7 +334,7 @@ class DecoderRunner:
             self.gdn_out = torch.empty(max_tokens, gv * 128, dtype=torch.bfloat16, device=dev)
         if any(lw.attn_gate is not None for lw in weights.layers):
             self.gate = torch.empty(max_tokens, self.hq * self.D, dtype=torch.bfloat16, device=dev)
-        self.inv_freq = rope_inv_freq(cfg.rotary_dim or self.D, cfg.rope_theta, dev)
+        self.inv_freq = rope_inv_freq(cfg.rotary_dim or self.D, cfg.rope_theta, dev, scaling=cfg.rope_scaling)
         bf = torch.bfloat16
         T = max_tokens
         self.h = torch.empty(T, H, dtype=bf, device=dev)           # residual stream

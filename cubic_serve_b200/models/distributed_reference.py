@@ -156,7 +156,7 @@ class DistributedEagerDecoder:
         self.tp_group, self.tp = tp_group, plan.tp
         self.prev = rank - plan.tp if self.part.stage > 0 else None
         self.next = rank + plan.tp if self.part.stage < plan.pp - 1 else None
-        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta)
+        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta, scaling=cfg.rope_scaling)
         v = cfg.vocab_size // plan.tp
         self.vocab = slice(self.part.tensor_rank * v, (self.part.tensor_rank + 1) * v)
 

@@ -131,7 +131,7 @@ class EagerFamilyModel:
                 raise ValueError(f"{n}: shape {tuple(weights[n].shape)}, expected {shape}")
         self.cfg, self.kv_bits = cfg, kv_bits
         self.w = {n: weights[n].float() for n in want}
-        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta)
+        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta, scaling=cfg.rope_scaling)
 
     def _lin(self, x: torch.Tensor, module: str) -> torch.Tensor:
         y = x @ self.w[module + ".weight"].t()

@@ -111,7 +111,7 @@ class EagerDecoder:
 
     def __init__(self, cfg: ModelConfig, weights: DenseWeights, kv_bits: tuple[int, int] | None = None) -> None:
         self.cfg, self.w, self.kv_bits = cfg, weights, kv_bits
-        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta)
+        self.inv_freq = eager.rope_inv_freq(cfg.rotary_dim or cfg.head_dim, cfg.rope_theta, scaling=cfg.rope_scaling)
 
     def _kvq(self, x: torch.Tensor, bits: int | None) -> torch.Tensor:
         if bits is None or bits >= 16:

@@ -26,8 +26,23 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.silu(g) * u
 
 
-def rope_inv_freq(rotary_dim: int, theta: float, device=None) -> torch.Tensor:
-    return 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, device=device, dtype=torch.float32) / rotary_dim))
+def rope_inv_freq(rotary_dim: int, theta: float, device=None, scaling: tuple | None = None) -> torch.Tensor:
+    """Rotary frequencies.  ``scaling`` (``ModelConfig.rope_scaling``): ``("linear", factor)`` divides every frequency;
+    ``("llama3", factor, low_freq_factor, high_freq_factor, original_max_position)`` keeps wavelengths below
+    ``original / high`` as they are, divides those above ``original / low`` by ``factor`` and blends in between.  Both
+    are static, so the kernels see them only as another frequency table."""
+    inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, device=device, dtype=torch.float32) / rotary_dim))
+    if scaling is None:
+        return inv
+    if scaling[0] == "linear":
+        return inv / float(scaling[1])
+    if scaling[0] == "llama3":
+        _, factor, low, high, original = scaling
+        wavelen = 2 * torch.pi / inv
+        smooth = ((original / wavelen - low) / (high - low)).clamp(0, 1)
+        blended = (1 - smooth) * inv / factor + smooth * inv
+        return torch.where(wavelen < original / high, inv, torch.where(wavelen > original / low, inv / factor, blended))
+    raise ValueError(f"unknown rotary scaling {scaling[0]!r}")
 
 
 def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:

@@ -434,3 +434,26 @@ def test_multimodal_config_keys_at_the_root(tmp_path):
     p.write_text(json.dumps(doc))
     cfg = ModelConfig.from_hf_config(p)
     assert cfg.tie_embeddings and cfg.rope_theta == 5e6 and cfg.mrope_section == (16, 8, 8) and cfg.qk_norm
+
+
+def test_rotary_scaling_forms(tmp_path):
+    import json
+
+    from cubic_serve_b200.ops import eager
+    base = {"architectures": ["LlamaForCausalLM"], "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4,
+            "num_key_value_heads": 2, "intermediate_size": 512, "vocab_size": 320, "rope_theta": 500000.0}
+    p = tmp_path / "config.json"
+    p.write_text(json.dumps({**base, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}}))
+    cfg = ModelConfig.from_hf_config(p)
+    assert cfg.rope_scaling == ("llama3", 8.0, 1.0, 4.0, 8192)
+    plain = eager.rope_inv_freq(64, 500000.0)
+    scaled = eager.rope_inv_freq(64, 500000.0, scaling=cfg.rope_scaling)
+    assert torch.equal(scaled[:8], plain[:8]) and torch.allclose(scaled[-1], plain[-1] / 8)      # short waves kept, long ones / 8
+    assert bool((scaled <= plain).all()) and bool((scaled >= plain / 8 - 1e-12).all())
+    assert torch.allclose(eager.rope_inv_freq(64, 1e4, scaling=("linear", 4.0)), eager.rope_inv_freq(64, 1e4) / 4)
+    p.write_text(json.dumps({**base, "rope_scaling": {"rope_type": "yarn", "factor": 4.0}}))
+    with pytest.raises(ValueError, match="yarn"):
+        ModelConfig.from_hf_config(p)
+    p.write_text(json.dumps({**base, "rope_scaling": None}))
+    assert ModelConfig.from_hf_config(p).rope_scaling is None

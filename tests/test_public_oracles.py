@@ -12,6 +12,9 @@ BASE = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_la
 MOE = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=1, mlp_only_layers=[])
 CASES = {
     "llama": ({}, "gqa_decoder"),
+    "llama:llama3-scaling": (dict(rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                "high_freq_factor": 4.0, "original_max_position_embeddings": 16}), "gqa_decoder"),
+    "llama:linear-scaling": (dict(rope_scaling={"rope_type": "linear", "factor": 4.0}), "gqa_decoder"),
     "mistral": (dict(head_dim=16, sliding_window=None), "gqa_decoder"),
     "qwen2": ({}, "gqa_decoder"),
     "qwen3": (dict(head_dim=16), "gqa_decoder"),
@@ -29,7 +32,7 @@ def test_checkpoints_of_the_public_implementations(model_type, tmp_path):
     transformers = pytest.importorskip("transformers")
     extra, family = CASES[model_type]
     try:
-        cfg = transformers.AutoConfig.for_model(model_type, **{**BASE, **extra})
+        cfg = transformers.AutoConfig.for_model(model_type.split(":")[0], **{**BASE, **extra})
     except (ValueError, KeyError):
         pytest.skip(f"{model_type} is not known to this transformers")
     cfg._attn_implementation = "eager"
@@ -52,6 +55,7 @@ def test_checkpoints_of_the_public_implementations(model_type, tmp_path):
     ck = C.admit_checkpoint(tmp_path)
     assert ck.cfg.family == family and ck.cfg.num_layers == cfg.num_hidden_layers
     assert ck.cfg.qkv_bias == (model_type in ("qwen2", "qwen2_moe")) and ck.cfg.qk_norm == model_type.startswith("qwen3")
+    assert (ck.cfg.rope_scaling is not None) == (":" in model_type)
     model = EF.EagerFamilyModel(ck.cfg, EF.family_weights_from_checkpoint(ck), exact=True)
     ids = torch.randint(0, 320, (1, 20), generator=torch.Generator().manual_seed(2))
     with torch.no_grad():
