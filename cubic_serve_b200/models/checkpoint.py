@@ -70,6 +70,20 @@ class SafetensorsDirectory:
                     raise CheckpointError(f"tensor {alias} exists both nested and at the top level")
                 renamed[alias] = ref
             self.tensors = renamed
+        # Mixtral names its expert block ``block_sparse_moe`` with projections w1 / w3 / w2 (gate / up / down): read under
+        # the names every other expert family uses
+        if any(".block_sparse_moe." in n for n in self.tensors):
+            swap = {".w1.": ".gate_proj.", ".w3.": ".up_proj.", ".w2.": ".down_proj."}
+            renamed = {}
+            for n, ref in self.tensors.items():
+                alias = n.replace(".block_sparse_moe.", ".mlp.")
+                if ".experts." in alias:
+                    for a, b in swap.items():
+                        alias = alias.replace(a, b)
+                if alias in renamed:
+                    raise CheckpointError(f"tensor {alias} appears under two names")
+                renamed[alias] = ref
+            self.tensors = renamed
         self._handles: dict[str, object] = {}
 
     def get(self, name: str) -> torch.Tensor:

@@ -21,6 +21,17 @@ class QuantSpec:
     lm_head_quantized: bool = False
 
 
+def _served_positions(text: dict, arch: str) -> int:
+    """Context the checkpoint is served at.  A model trained with sliding-window attention equals full attention only
+    inside one window: the kernels attend to the whole context, so such a checkpoint is served up to its window."""
+    limit = int(text.get("max_position_embeddings", 40960))
+    window = text.get("sliding_window")
+    applies = text.get("use_sliding_window", arch.startswith(("Mistral", "Mixtral")))
+    if isinstance(window, int) and window > 0 and applies:
+        limit = min(limit, window)
+    return limit
+
+
 def _rope_scaling(text: dict):
     """``rope_scaling`` / ``rope_parameters`` of a checkpoint as ``ModelConfig.rope_scaling``.  Forms that change the
     rotation with the sequence length or rescale the attention logits (dynamic, yarn, longrope) are refused: served with
@@ -142,6 +153,10 @@ class ModelConfig:
         rope = text.get("rope_parameters") if isinstance(text.get("rope_parameters"), dict) else {}
         if text.get("attention_bias"):
             raise ValueError("checkpoints with biases on all attention projections (attention_bias) are not served")
+        if text.get("mlp_bias"):
+            raise ValueError("checkpoints with biases on the feed-forward projections (mlp_bias) are not served")
+        if n_exp and (text.get("mlp_only_layers") or int(text.get("decoder_sparse_step", 1) or 1) != 1):
+            raise ValueError("checkpoints that mix dense and expert feed-forward layers are not served")
         hybrid = {}
         if text.get("linear_num_value_heads"):
             if int(text.get("linear_key_head_dim", 128)) != 128 or int(text.get("linear_value_head_dim", 128)) != 128:
@@ -167,10 +182,11 @@ class ModelConfig:
             shared_intermediate_size=int(text.get("shared_expert_intermediate_size") or 0) if n_exp else 0,
             qkv_bias=bool(text.get("qkv_bias", arch.startswith("Qwen2"))),
             tie_embeddings=bool(text.get("tie_word_embeddings", cfg.get("tie_word_embeddings", False))),
-            max_position=int(text.get("max_position_embeddings", 40960)),
+            max_position=_served_positions(text, arch),
             num_experts=n_exp,
             experts_per_token=text.get("num_experts_per_tok", 0) if n_exp else 0,
-            moe_intermediate_size=text.get("moe_intermediate_size", 0) if n_exp else 0,
+            # Mixtral gives its experts the width named ``intermediate_size``
+            moe_intermediate_size=(text.get("moe_intermediate_size") or text.get("intermediate_size", 0)) if n_exp else 0,
             norm_topk_prob=bool(text.get("norm_topk_prob", True)),
             mtp_layers=int(text.get("mtp_num_hidden_layers") or text.get("num_nextn_predict_layers") or 0),
             quant=quant_spec_from_hf(qc),

@@ -457,3 +457,27 @@ def test_rotary_scaling_forms(tmp_path):
         ModelConfig.from_hf_config(p)
     p.write_text(json.dumps({**base, "rope_scaling": None}))
     assert ModelConfig.from_hf_config(p).rope_scaling is None
+
+
+def test_configurations_that_are_refused_by_name(tmp_path):
+    import json
+    base = {"architectures": ["Qwen3MoeForCausalLM"], "hidden_size": 256, "num_hidden_layers": 4, "num_attention_heads": 4,
+            "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 512, "vocab_size": 320, "num_experts": 8,
+            "num_experts_per_tok": 2, "moe_intermediate_size": 128}
+    p = tmp_path / "config.json"
+    for extra, match in (({"mlp_only_layers": [0]}, "mix dense and expert"), ({"decoder_sparse_step": 2}, "mix dense and expert"),
+                         ({"mlp_bias": True}, "mlp_bias"), ({"attention_bias": True}, "attention_bias")):
+        p.write_text(json.dumps({**base, **extra}))
+        with pytest.raises(ValueError, match=match):
+            ModelConfig.from_hf_config(p)
+    p.write_text(json.dumps({**base, "mlp_only_layers": [], "decoder_sparse_step": 1}))
+    assert ModelConfig.from_hf_config(p).is_moe
+    # sliding-window checkpoints are served inside one window; Qwen2's unused window does not limit them
+    p.write_text(json.dumps({"architectures": ["MistralForCausalLM"], "hidden_size": 256, "num_hidden_layers": 2,
+                             "num_attention_heads": 4, "vocab_size": 320, "intermediate_size": 512,
+                             "max_position_embeddings": 32768, "sliding_window": 4096}))
+    assert ModelConfig.from_hf_config(p).max_position == 4096
+    p.write_text(json.dumps({"architectures": ["Qwen2ForCausalLM"], "hidden_size": 256, "num_hidden_layers": 2,
+                             "num_attention_heads": 4, "vocab_size": 320, "intermediate_size": 512,
+                             "max_position_embeddings": 32768, "sliding_window": 4096, "use_sliding_window": False}))
+    assert ModelConfig.from_hf_config(p).max_position == 32768

@@ -16,6 +16,8 @@ CASES = {
                                                 "high_freq_factor": 4.0, "original_max_position_embeddings": 16}), "gqa_decoder"),
     "llama:linear-scaling": (dict(rope_scaling={"rope_type": "linear", "factor": 4.0}), "gqa_decoder"),
     "mistral": (dict(head_dim=16, sliding_window=None), "gqa_decoder"),
+    "mixtral": (dict(intermediate_size=64, num_local_experts=4, num_experts_per_tok=2, sliding_window=None), "gqa_moe"),
+    "mistral:window": (dict(head_dim=16, sliding_window=64), "gqa_decoder"),
     "qwen2": ({}, "gqa_decoder"),
     "qwen3": (dict(head_dim=16), "gqa_decoder"),
     "qwen3_moe": (dict(head_dim=16, norm_topk_prob=True, **MOE), "gqa_moe"),
@@ -55,7 +57,8 @@ def test_checkpoints_of_the_public_implementations(model_type, tmp_path):
     ck = C.admit_checkpoint(tmp_path)
     assert ck.cfg.family == family and ck.cfg.num_layers == cfg.num_hidden_layers
     assert ck.cfg.qkv_bias == (model_type in ("qwen2", "qwen2_moe")) and ck.cfg.qk_norm == model_type.startswith("qwen3")
-    assert (ck.cfg.rope_scaling is not None) == (":" in model_type)
+    assert (ck.cfg.rope_scaling is not None) == ("scaling" in model_type)
+    assert ck.cfg.max_position == (64 if model_type == "mistral:window" else 512)
     model = EF.EagerFamilyModel(ck.cfg, EF.family_weights_from_checkpoint(ck), exact=True)
     ids = torch.randint(0, 320, (1, 20), generator=torch.Generator().manual_seed(2))
     with torch.no_grad():
