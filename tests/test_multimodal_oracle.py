@@ -136,3 +136,31 @@ def test_engine_carries_the_intermediate_outputs():
     refusing.accepts_deepstack = False
     with pytest.raises(AdmissionError):
         LLMEngine(refusing, 64).add_request(ids, multimodal=mm())
+
+
+def test_checkpoint_of_the_public_multimodal_model_is_admitted(tmp_path):
+    """``save_pretrained`` of the public model: nested decoder names, tower tensors and the two-level ``config.json`` are
+    admitted by the closed inventory; tower and decoder loaded from it give the public model's logits."""
+    from cubic_serve_b200.inputs.multimodal import VisionTokens
+    from cubic_serve_b200.models import checkpoint as C
+    ref = _public_model()
+    ref.save_pretrained(tmp_path, safe_serialization=True)
+    ck = C.admit_checkpoint(tmp_path)
+    assert ck.vision is not None and ck.vision.deepstack_visual_indexes == (0, 1) and ck.cfg.mrope_section == (4, 2, 2)
+    assert ck.cfg.qk_norm and ck.cfg.num_layers == 3 and ck.vision_prefix == "model.visual."
+    tokens = VisionTokens.from_hf(ck.raw_config)
+    assert (tokens.image, tokens.start, tokens.end) == (290, 292, 293)
+    tower = VisionEncoder(ck.vision, C.load_vision_weights(ck, dtype=torch.float32))
+    model = EF.EagerFamilyModel(ck.cfg, EF.family_weights_from_checkpoint(ck))
+    ids = [5, 6, 292] + [290] * 6 + [293, 7, 8, 9]
+    px = torch.randn(24, 96, generator=torch.Generator().manual_seed(4))
+    grid = torch.tensor([[1, 4, 6]])
+    tid = torch.tensor([ids])
+    with torch.no_grad():
+        want = ref(input_ids=tid, pixel_values=px, image_grid_thw=grid, mm_token_type_ids=(tid == 290).long()).logits[0]
+    feats, deep = tower.encode(px, grid)
+    pos, delta = mrope_positions(ids, [(3, 6, (1, 4, 6))], 2)
+    mm = MultimodalInput([(3, torch.cat([feats] + deep, 1), b"i")], np.asarray(pos), delta, hidden=64)
+    embeds, p3 = mm.segment_inputs(0, len(ids))
+    got, _ = model.forward(ids, positions3=p3, embeds=embeds, deep=mm.segment_deep(0, len(ids)))
+    assert (got - want).abs().max() < 2e-4
