@@ -96,6 +96,9 @@ def build_parser() -> argparse.ArgumentParser:
     q.add_argument("--reuse", action="store_true", help="accept a passing receipt made by the same code on the same GPU model")
     q.add_argument("--save", help="write the report (verdict, error and result digest of every check) to this JSON file")
     q.add_argument("--against", help="compare with a report saved earlier: which checks kept their bits, which changed")
+    q.add_argument("--operators", action="store_true",
+                   help="audit the plain PyTorch operators of one decoder layer against the enclosures of their own inputs "
+                        "(needs no GPU: checks that this torch build honours the arithmetic contract the kernels are held to)")
 
     rf = sub.add_parser("reference", help="greedy-decode a prompt of token ids with the eager fp32 reference decoder "
                                           "(the oracle the native kernels are qualified against)")
@@ -392,6 +395,13 @@ def _inspect(args) -> int:
 
 
 def _qualify(args) -> int:
+    if args.operators:
+        from .guardrail.enclosure import audit_layer_operators
+        rows = [{"operator": n, "ok": r.ok, "outside": r.outside, "of": r.total, "worst_excess_ulps": r.worst_excess_ulps}
+                for seed in range(2 if args.quick else 8) for n, r in audit_layer_operators(seed=seed)]
+        ok = all(r["ok"] for r in rows)
+        print(json.dumps({"ok": ok, "checks": len(rows), "failed": [r for r in rows if not r["ok"]]}, indent=1))
+        return 0 if ok else 1
     from .guardrail.qualify import qualify_with_receipt
     report, reused = qualify_with_receipt(args.device, quick=args.quick, evidence_dir=args.evidence_dir, force=not args.reuse)
     report = dict(report, receipt="reused" if reused else "new")

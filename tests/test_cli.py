@@ -146,3 +146,10 @@ def test_several_served_names_are_accepted_by_the_server():
         assert st == want, (name, st, payload[:120])
         if want == 200:
             assert json.loads(payload)["model"] == "public"
+
+
+def test_qualify_operators_needs_no_gpu(capsys):
+    import json
+    assert cli.main(["qualify", "--operators", "--quick"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["ok"] and report["checks"] == 18 and report["failed"] == []
