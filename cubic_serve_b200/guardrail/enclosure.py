@@ -308,3 +308,63 @@ def audit_layer_operators(ops=None, hidden: int = 256, heads: int = 4, head_dim:
     act = judged("silu_mul", silu_mul_enclosure(gate, up), ops.silu_mul(gate, up))
     judged("down_proj+residual", linear_enclosure(act, w_down, residual=x2), ops.linear(act, w_down, residual=x2))
     return out
+
+
+# ------------------------------------------------------------------------------------------------- expert routing
+@dataclass(frozen=True)
+class RouteEnclosure:
+    """Which experts a row MUST select (their logit's lower end beats the upper end of every expert outside the best
+    ``k``) and which it MAY select (their upper end reaches the ``k``-th largest lower end).  Between the two lies a
+    near-tie: implementations that accumulate the router product in another order may legitimately pick either
+    expert there, and token streams that part at such a row are both right."""
+    lo: torch.Tensor             # [rows, experts] logit enclosure (float64)
+    hi: torch.Tensor
+    k: int
+    normalise: bool              # selected weights divided by their sum
+
+    @property
+    def must(self) -> torch.Tensor:
+        kth_hi_outside = self.hi.sort(-1, descending=True).values[:, self.k:self.k + 1]          # (k+1)-th largest upper end
+        return self.lo > kth_hi_outside if self.hi.shape[-1] > self.k else torch.ones_like(self.lo, dtype=torch.bool)
+
+    @property
+    def may(self) -> torch.Tensor:
+        kth_lo = self.lo.sort(-1, descending=True).values[:, self.k - 1:self.k]
+        return self.hi >= kth_lo
+
+    def ambiguous_rows(self) -> torch.Tensor:
+        return (self.may.sum(-1) > self.k).nonzero().flatten()
+
+    def check(self, ids: torch.Tensor, weights: torch.Tensor | None = None) -> dict:
+        """``ids [rows, k]`` (any order), ``weights [rows, k]`` aligned with them.  Returns the rows with a selection no
+        ordering of the sums can produce and, for valid rows, the weights outside their enclosure."""
+        ids = ids.detach().cpu().long()
+        rows = torch.arange(ids.shape[0])[:, None]
+        chosen = torch.zeros_like(self.lo, dtype=torch.bool)
+        chosen[rows, ids] = True
+        bad = ((chosen & ~self.may).any(-1) | (self.must & ~chosen).any(-1) | (chosen.sum(-1) != self.k))
+        out = {"invalid_rows": bad.nonzero().flatten().tolist(), "ambiguous_rows": self.ambiguous_rows().tolist()}
+        if weights is not None:
+            slo, shi = self.lo[rows, ids], self.hi[rows, ids]
+            if self.normalise:                     # softmax over the selected logits = full softmax renormalised
+                wlo, whi = _softmax_interval(slo, shi)
+            else:
+                m = self.hi.amax(-1, keepdim=True)
+                rel, g = 3 * U32, gamma(self.lo.shape[-1])
+                dlo = (torch.exp(self.lo - m) * (1 - rel)).sum(-1, keepdim=True) * (1 - g)
+                dhi = (torch.exp(self.hi - m) * (1 + rel)).sum(-1, keepdim=True) * (1 + g)
+                wlo = torch.exp(slo - m) * (1 - rel) / dhi * (1 - 2 * U32)
+                whi = torch.exp(shi - m) * (1 + rel) / dlo * (1 + 2 * U32)
+            rep = Enclosure.of(wlo[~bad], whi[~bad], weights.dtype).check(weights.detach().cpu()[~bad])
+            out["weights"] = rep
+        out["ok"] = not out["invalid_rows"] and (weights is None or out["weights"].ok)
+        return out
+
+
+def route_enclosure(x: torch.Tensor, w_router: torch.Tensor, k: int, normalise: bool = True) -> RouteEnclosure:
+    """Router logits ``x [rows, hidden] @ w_router[experts, hidden].T`` accumulated in fp32 in any order and kept in
+    fp32 (the selection reads them before any storage rounding)."""
+    xd, wd = _d(x), _d(w_router)
+    exact, mag = xd @ wd.T, xd.abs() @ wd.abs().T
+    err = gamma(xd.shape[-1]) * mag
+    return RouteEnclosure(exact - err, exact + err, int(k), bool(normalise))

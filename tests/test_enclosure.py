@@ -183,3 +183,37 @@ def test_layer_audit_names_the_one_wrong_operator():
     assert [n for n, r in bad.items() if not r.ok] == ["silu_mul"]        # what follows is judged on its own inputs
     bad = dict(E.audit_layer_operators(Bf16Norm(), seed=3))
     assert [n for n, r in bad.items() if not r.ok] == ["input_norm", "post_norm"]
+
+
+def test_routing_must_may_sets_and_near_ties():
+    g = _g(9)
+    x = torch.randn(64, 256, generator=g).to(BF)
+    w = (torch.randn(16, 256, generator=g) * 0.06).to(BF)
+    w[5] = w[4]                                                # two experts with the same row: a tie wherever they rank
+    x[7] = 0
+    x[7, 0] = 1                                                # a row whose logits are single products: no slack at all
+    enc = E.route_enclosure(x, w, k=4, normalise=True)
+    logits = x.float() @ w.float().T
+    top = logits.topk(4, -1)
+    weights = torch.softmax(top.values, -1)
+    rep = enc.check(top.indices, weights)
+    assert rep["ok"] and not rep["invalid_rows"]
+    # another order of the sums picks other experts only on rows the enclosure calls ambiguous
+    rev = (x.float().flip(-1) @ w.float().flip(-1).T).topk(4, -1)
+    differ = {r for r in range(64) if set(rev.indices[r].tolist()) != set(top.indices[r].tolist())}
+    assert differ <= set(rep["ambiguous_rows"])
+    assert enc.check(rev.indices, torch.softmax(rev.values, -1))["ok"]
+    tied = [r for r in range(64) if (4 in top.indices[r]) != (5 in top.indices[r])]
+    assert tied and set(tied) <= set(rep["ambiguous_rows"])     # the twin experts straddle the cut somewhere
+    swapped = top.indices.clone()
+    r = tied[0]
+    swapped[r] = torch.where(swapped[r] == 4, 5, torch.where(swapped[r] == 5, 4, swapped[r]))
+    assert enc.check(swapped)["ok"]                            # either twin is a right answer
+    wrong = top.indices.clone()
+    clear = next(r for r in range(64) if r not in rep["ambiguous_rows"])
+    wrong[clear, 0] = logits[clear].argmin()
+    assert enc.check(wrong)["invalid_rows"] == [clear]
+    assert not enc.check(top.indices, weights * 1.001)["ok"]
+    plain = E.route_enclosure(x, w, k=4, normalise=False)
+    assert plain.check(top.indices, torch.softmax(logits, -1).gather(1, top.indices))["ok"]
+    assert not plain.check(top.indices, weights)["ok"]         # renormalised weights where plain ones are declared
