@@ -95,7 +95,7 @@ class EagerPagedExecutor:
             np_ = -(-total // PAGE)
             kk = self.k[li][pages[:np_]].reshape(np_ * PAGE, Hkv, D)[:total]
             vv = self.v[li][pages[:np_]].reshape(np_ * PAGE, Hkv, D)[:total]
-            attn = eager.attention_rows(q, kk, vv, pos + 1)
+            attn = eager.attention_rows(q, kk, vv, pos + 1, cfg.attention_scale)
             h = h + attn.reshape(n, Hq * D) @ l.wo.t()
             x = eager.rmsnorm(h, l.ln2, cfg.rms_eps, cfg.zero_centered_norm)
             h = h + (torch.nn.functional.silu(x @ l.w_gate.t()) * (x @ l.w_up.t())) @ l.w_down.t()

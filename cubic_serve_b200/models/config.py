@@ -8,6 +8,7 @@ MoE) and hybrid linear-attention decoders.
 from __future__ import annotations
 
 import json
+import math
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
 
@@ -34,7 +35,7 @@ def _served_positions(text: dict, arch: str) -> int:
 
 def _rope_scaling(text: dict):
     """``rope_scaling`` / ``rope_parameters`` of a checkpoint as ``ModelConfig.rope_scaling``.  Forms that change the
-    rotation with the sequence length or rescale the attention logits (dynamic, yarn, longrope) are refused: served with
+    rotation with the sequence length or need per-dimension logit factors (dynamic, longrope) are refused: served with
     the plain table they would silently lose quality at long context."""
     for key in ("rope_scaling", "rope_parameters"):
         rs = text.get(key)
@@ -48,6 +49,16 @@ def _rope_scaling(text: dict):
         if kind == "llama3":
             return ("llama3", float(rs["factor"]), float(rs["low_freq_factor"]), float(rs["high_freq_factor"]),
                     int(rs["original_max_position_embeddings"]))
+        if kind == "yarn":
+            if rs.get("mscale") or rs.get("mscale_all_dim") or rs.get("truncate", True) is not True:
+                raise ValueError("yarn rotary scaling with mscale / mscale_all_dim / truncate=false is not served")
+            if float(text.get("partial_rotary_factor", rs.get("partial_rotary_factor", 1.0)) or 1.0) != 1.0:
+                raise ValueError("yarn rotary scaling of partly rotated heads is not served")
+            factor = float(rs["factor"])
+            original = int(rs.get("original_max_position_embeddings") or text.get("max_position_embeddings", 40960))
+            af = rs.get("attention_factor")
+            af = float(af) if af is not None else (1.0 if factor <= 1 else 0.1 * math.log(factor) + 1.0)
+            return ("yarn", factor, original, float(rs.get("beta_fast") or 32), float(rs.get("beta_slow") or 1), af)
         raise ValueError(f"rotary scaling of type {kind!r} is not served")
     return None
 
@@ -102,12 +113,22 @@ class ModelConfig:
     # projections (Qwen2 family): both are served by the eager execution mode only
     shared_intermediate_size: int = 0
     qkv_bias: bool = False
-    # static rescaling of the rotary frequencies: ("linear", factor) or ("llama3", factor, low_freq_factor,
-    # high_freq_factor, original_max_position_embeddings); None = the plain table
+    # static rescaling of the rotary frequencies: ("linear", factor), ("llama3", factor, low_freq_factor,
+    # high_freq_factor, original_max_position_embeddings) or ("yarn", factor, original_max_position_embeddings, beta_fast,
+    # beta_slow, attention_factor); None = the plain table
     rope_scaling: tuple | None = None
     # three-axis rotary positions of the multimodal checkpoints: how many frequency slots follow the (temporal, row,
     # column) axis; None = one axis
     mrope_section: tuple[int, int, int] | None = None
+
+    @property
+    def attention_scale(self) -> float | None:
+        """Softmax scale of the attention logits when it is not ``1 / sqrt(head_dim)``: yarn scaling multiplies the
+        rotated queries AND keys by its attention factor, i.e. the logits of fully rotated heads by its square."""
+        rs = self.rope_scaling
+        if rs is None or rs[0] != "yarn" or rs[5] == 1.0:
+            return None
+        return rs[5] * rs[5] / math.sqrt(self.head_dim)
 
     @property
     def q_size(self) -> int:

@@ -513,7 +513,7 @@ class DecoderRunner:
                                 mrope_section=cfg.mrope_section if hw is not None else None, qkv_bias=lw.qkv_bias)
                 K.paged_attention(q_all, attn_all, self.kv[li], b.page_table, b.rb_req[rb0:rb1], b.rb_qstart[rb0:],
                                   b.rb_qcount[rb0:], b.rb_ctx[rb0:], self.hq, self.hkv, self.D, self.k_bits, self.v_bits,
-                                  splits=b.attn_splits, ws=self.ws)
+                                  scale=cfg.attention_scale, splits=b.attn_splits, ws=self.ws)
                 n += 4
                 if self.kv_rotation:
                     K.hadamard(attn)
@@ -597,7 +597,7 @@ class DecoderRunner:
                             rotary_dim=cfg.rotary_dim, rotate=self.kv_rotation, qkv_bias=lw.qkv_bias)
             K.paged_attention(q.view(T, self.hq, self.D), attn.view(T, self.hq, self.D), self.kv[li], b.page_table,
                               b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, self.hq, self.hkv,
-                              self.D, self.k_bits, self.v_bits, splits=b.attn_splits, ws=self.ws)
+                              self.D, self.k_bits, self.v_bits, scale=cfg.attention_scale, splits=b.attn_splits, ws=self.ws)
             if self.kv_rotation:
                 K.hadamard(attn)
                 n += 1

@@ -192,7 +192,7 @@ class DistributedEagerDecoder:
                 v = torch.cat([cache[li][1], v], 1)
             new_cache.append((k, v))
             vis = torch.arange(start + 1, start + S + 1)
-            attn = torch.stack([eager.attention_rows(q[b], k[b], v[b], vis) for b in range(B)])
+            attn = torch.stack([eager.attention_rows(q[b], k[b], v[b], vis, cfg.attention_scale) for b in range(B)])
             h = h + self._sum(attn.reshape(B, S, Hq * D) @ l.wo.t())            # row-parallel: partial sums
             x = eager.rmsnorm(h, l.ln2, cfg.rms_eps, cfg.zero_centered_norm)
             h = h + self._sum((torch.nn.functional.silu(x @ l.w_gate.t()) * (x @ l.w_up.t())) @ l.w_down.t())

@@ -169,7 +169,7 @@ class EagerFamilyModel:
             k, v = self._kvq(k, self.kv_bits[0]), self._kvq(v, self.kv_bits[1])
         st.key = k if st.key is None else torch.cat([st.key, k], 0)
         st.value = v if st.value is None else torch.cat([st.value, v], 0)
-        out = eager.attention_rows(q, st.key, st.value, torch.arange(start + 1, start + T + 1))
+        out = eager.attention_rows(q, st.key, st.value, torch.arange(start + 1, start + T + 1), c.attention_scale)
         if gate is not None:
             out = out * torch.sigmoid(gate)
         return out.reshape(T, Hq * D) @ self.w[p + ".o_proj.weight"].t()

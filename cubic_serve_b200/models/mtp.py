@@ -123,7 +123,7 @@ class MtpRunner:
                         rotate=t.kv_rotation)
         K.paged_attention(q.view(T, t.hq, t.D), attn.view(T, t.hq, t.D), self.kv, b.page_table,
                           b.rb_req[:b.num_row_blocks], b.rb_qstart, b.rb_qcount, b.rb_ctx, t.hq, t.hkv, t.D, t.k_bits,
-                          t.v_bits, splits=b.attn_splits, ws=t.ws)
+                          t.v_bits, scale=t.cfg.attention_scale, splits=b.attn_splits, ws=t.ws)
         if t.kv_rotation:
             K.hadamard(attn)
         if tp is None:

@@ -29,8 +29,10 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 def rope_inv_freq(rotary_dim: int, theta: float, device=None, scaling: tuple | None = None) -> torch.Tensor:
     """Rotary frequencies.  ``scaling`` (``ModelConfig.rope_scaling``): ``("linear", factor)`` divides every frequency;
     ``("llama3", factor, low_freq_factor, high_freq_factor, original_max_position)`` keeps wavelengths below
-    ``original / high`` as they are, divides those above ``original / low`` by ``factor`` and blends in between.  Both
-    are static, so the kernels see them only as another frequency table."""
+    ``original / high`` as they are, divides those above ``original / low`` by ``factor`` and blends in between;
+    ``("yarn", factor, original_max_position, beta_fast, beta_slow, attention_factor)`` blends by slot index (its
+    attention factor is a softmax scale, ``ModelConfig.attention_scale``).  All are static, so the kernels see them only
+    as another frequency table."""
     inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, device=device, dtype=torch.float32) / rotary_dim))
     if scaling is None:
         return inv
@@ -42,6 +44,18 @@ def rope_inv_freq(rotary_dim: int, theta: float, device=None, scaling: tuple | N
         smooth = ((original / wavelen - low) / (high - low)).clamp(0, 1)
         blended = (1 - smooth) * inv / factor + smooth * inv
         return torch.where(wavelen < original / high, inv, torch.where(wavelen > original / low, inv / factor, blended))
+    if scaling[0] == "yarn":
+        # wavelengths that turn more than ``beta_fast`` times inside the trained context keep their frequency, those
+        # that turn less than ``beta_slow`` times are stretched by ``factor``, a linear ramp over the slot index between
+        _, factor, original, beta_fast, beta_slow, _ = scaling
+
+        def slot(turns: float) -> float:
+            return rotary_dim * math.log(original / (turns * 2 * math.pi)) / (2 * math.log(theta))
+        low, high = max(math.floor(slot(beta_fast)), 0), min(math.ceil(slot(beta_slow)), rotary_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(rotary_dim // 2, device=device, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+        return inv / factor * ramp + inv * (1 - ramp)
     raise ValueError(f"unknown rotary scaling {scaling[0]!r}")
 
 

@@ -2,6 +2,8 @@
 import json
 from dataclasses import replace
 
+import math
+
 import pytest
 import torch
 
@@ -452,9 +454,25 @@ def test_rotary_scaling_forms(tmp_path):
     assert torch.equal(scaled[:8], plain[:8]) and torch.allclose(scaled[-1], plain[-1] / 8)      # short waves kept, long ones / 8
     assert bool((scaled <= plain).all()) and bool((scaled >= plain / 8 - 1e-12).all())
     assert torch.allclose(eager.rope_inv_freq(64, 1e4, scaling=("linear", 4.0)), eager.rope_inv_freq(64, 1e4) / 4)
-    p.write_text(json.dumps({**base, "rope_scaling": {"rope_type": "yarn", "factor": 4.0}}))
-    with pytest.raises(ValueError, match="yarn"):
+    p.write_text(json.dumps({**base, "max_position_embeddings": 131072,
+                             "rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32768}}))
+    cfg = ModelConfig.from_hf_config(p)
+    assert cfg.rope_scaling[:5] == ("yarn", 4.0, 32768, 32.0, 1.0) and abs(cfg.rope_scaling[5] - (0.1 * math.log(4.0) + 1)) < 1e-12
+    assert abs(cfg.attention_scale - cfg.rope_scaling[5] ** 2 / 8.0) < 1e-12                     # head width 64
+    yarn = eager.rope_inv_freq(64, 500000.0, scaling=cfg.rope_scaling)
+    assert torch.equal(yarn[:4], plain[:4]) and torch.allclose(yarn[-1], plain[-1] / 4)          # fast slots kept, slow ones / 4
+    assert bool((yarn[1:] <= yarn[:-1]).all())
+    for bad in ({"mscale": 1.0, "mscale_all_dim": 0.7}, {"truncate": False}):
+        p.write_text(json.dumps({**base, "rope_scaling": {"rope_type": "yarn", "factor": 4.0, **bad}}))
+        with pytest.raises(ValueError, match="yarn"):
+            ModelConfig.from_hf_config(p)
+    p.write_text(json.dumps({**base, "partial_rotary_factor": 0.5, "rope_scaling": {"rope_type": "yarn", "factor": 4.0}}))
+    with pytest.raises(ValueError, match="partly rotated"):
         ModelConfig.from_hf_config(p)
+    p.write_text(json.dumps({**base, "rope_scaling": {"rope_type": "longrope", "factor": 4.0}}))
+    with pytest.raises(ValueError, match="longrope"):
+        ModelConfig.from_hf_config(p)
+    assert ModelConfig().attention_scale is None
     p.write_text(json.dumps({**base, "rope_scaling": None}))
     assert ModelConfig.from_hf_config(p).rope_scaling is None
 

@@ -12,9 +12,10 @@ from cubic_serve_b200.models.config import ModelConfig, QuantSpec
 from cubic_serve_b200.ops import eager, wq_pack
 
 
-def test_dense_model_equals_the_reference_decoder():
+@pytest.mark.parametrize("scaling", [None, ("yarn", 4.0, 16, 32.0, 1.0, 1.2)])
+def test_dense_model_equals_the_reference_decoder(scaling):
     from cubic_serve_b200.models.reference import DenseLayer, DenseWeights, EagerDecoder
-    cfg = replace(ModelConfig(), qk_norm=True, rotary_dim=32)
+    cfg = replace(ModelConfig(), qk_norm=True, rotary_dim=32 if scaling is None else 0, rope_scaling=scaling)
     w = EF.random_family_weights(cfg, 1, std=0.15)
     layers = []
     for i in range(cfg.num_layers):

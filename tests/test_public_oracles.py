@@ -15,6 +15,10 @@ CASES = {
     "llama:llama3-scaling": (dict(rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
                                                 "high_freq_factor": 4.0, "original_max_position_embeddings": 16}), "gqa_decoder"),
     "llama:linear-scaling": (dict(rope_scaling={"rope_type": "linear", "factor": 4.0}), "gqa_decoder"),
+    "llama:yarn-scaling": (dict(rope_scaling={"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16,
+                                              "beta_fast": 8.0, "beta_slow": 1.0}), "gqa_decoder"),
+    "qwen3:yarn-scaling": (dict(head_dim=16, rope_scaling={"rope_type": "yarn", "factor": 8.0, "attention_factor": 1.3,
+                                                           "original_max_position_embeddings": 64}), "gqa_decoder"),
     "mistral": (dict(head_dim=16, sliding_window=None), "gqa_decoder"),
     "mixtral": (dict(intermediate_size=64, num_local_experts=4, num_experts_per_tok=2, sliding_window=None), "gqa_moe"),
     "mistral:window": (dict(head_dim=16, sliding_window=64), "gqa_decoder"),
