@@ -1,6 +1,8 @@
 """GGUF file inventory and logical weight views (reference: ``models/gguf.py:172``, ``models/gguf_weights.py:433``)."""
 from __future__ import annotations
 
+import math
+
 from pathlib import Path
 
 import numpy as np
@@ -107,7 +109,25 @@ def config_from_gguf(reader):
     head_dim = int(_field(reader, f"{arch}.attention.key_length", hidden // hq))
     vocab = shapes["token_embd.weight"][0]
     types = {t.tensor_type.name for t in reader.tensors if t.name.endswith(("attn_q.weight", "ffn_down.weight"))}
-    return ModelConfig(
+    # rotary scaling: a per-slot divisor table (the exporter's form of the llama3 rule) or the linear / yarn metadata
+    scaling = None
+    kind = str(_field(reader, f"{arch}.rope.scaling.type", "none") or "none")
+    factor = float(_field(reader, f"{arch}.rope.scaling.factor", 1.0) or 1.0)
+    table = next((t for t in reader.tensors if t.name == "rope_freqs.weight"), None)
+    if table is not None:
+        if kind not in ("none", "linear") or (kind == "linear" and factor != 1.0):
+            raise gq.GGUFFormatError("a GGUF file with both a rotary divisor table and rotary scaling metadata is not served")
+        scaling = ("factors", tuple(float(v) for v in np.asarray(table.data, dtype=np.float32).reshape(-1)))
+        if len(scaling[1]) != head_dim // 2:
+            raise gq.GGUFFormatError("rope_freqs.weight does not hold one divisor per rotary slot")
+    elif kind == "linear" and factor != 1.0:
+        scaling = ("linear", factor)
+    elif kind == "yarn":
+        original = int(need("rope.scaling.original_context_length"))
+        scaling = ("yarn", factor, original, 32.0, 1.0, 1.0 if factor <= 1 else 0.1 * math.log(factor) + 1.0)
+    elif kind not in ("none", "linear"):
+        raise gq.GGUFFormatError(f"rotary scaling of type {kind!r} is not served")
+    return ModelConfig(rope_scaling=scaling, 
         name=str(_field(reader, "general.name", Path(str(getattr(reader, "path", "gguf"))).stem)), family="gqa_decoder",
         num_layers=layers, hidden_size=hidden, num_q_heads=hq, num_kv_heads=hkv, head_dim=head_dim,
         intermediate_size=int(need("feed_forward_length")), vocab_size=vocab,

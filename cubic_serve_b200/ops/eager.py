@@ -44,6 +44,11 @@ def rope_inv_freq(rotary_dim: int, theta: float, device=None, scaling: tuple | N
         smooth = ((original / wavelen - low) / (high - low)).clamp(0, 1)
         blended = (1 - smooth) * inv / factor + smooth * inv
         return torch.where(wavelen < original / high, inv, torch.where(wavelen > original / low, inv / factor, blended))
+    if scaling[0] == "factors":                # one divisor per slot, as stored by GGUF exporters (``rope_freqs.weight``)
+        div = torch.tensor(scaling[1], device=device, dtype=torch.float32)
+        if div.numel() != inv.numel():
+            raise ValueError("the rotary divisor table does not match the rotary width")
+        return inv / div
     if scaling[0] == "yarn":
         # wavelengths that turn more than ``beta_fast`` times inside the trained context keep their frequency, those
         # that turn less than ``beta_slow`` times are stretched by ``factor``, a linear ramp over the slot index between

@@ -211,3 +211,59 @@ def test_gguf_model_decodes_like_the_eager_reference(tmp_path):
     want, _ = ref.generate(torch.tensor(prompts), 8)
     agree = np.mean([a == b for ga, wa in zip(got, want.tolist()) for a, b in zip(ga, wa)])
     assert agree >= 0.75, (agree, got, want.tolist())
+
+
+def _metadata_only_file(path, arch="llama", scaling=None, table=None):
+    """A file with the metadata and the two tensors the configuration reader needs."""
+    import gguf
+    w = gguf.GGUFWriter(str(path), arch)
+    w.add_block_count(1)
+    w.add_embedding_length(64)
+    w.add_head_count(4)
+    w.add_head_count_kv(2)
+    w.add_feed_forward_length(128)
+    w.add_rope_freq_base(500000.0)
+    w.add_key_length(16)
+    w.add_context_length(4096)
+    if scaling:
+        kind, factor, original = scaling
+        w.add_rope_scaling_type(getattr(gguf.RopeScalingType, kind))
+        w.add_rope_scaling_factor(factor)
+        if original:
+            w.add_rope_scaling_orig_ctx_len(original)
+    w.add_tensor("token_embd.weight", np.zeros((32, 64), dtype=np.float16))
+    if table is not None:
+        w.add_tensor("rope_freqs.weight", np.asarray(table, dtype=np.float32))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    import gguf as g2
+    return g2.GGUFReader(str(path))
+
+
+def test_rotary_scaling_of_a_gguf_file_is_served_not_dropped(tmp_path):
+    """The exporter's divisor table (its form of the llama3 rule) and the linear / yarn metadata reach the frequency
+    table; a file that announces a form this build does not serve is refused."""
+    import math
+
+    from cubic_serve_b200.models.gguf import config_from_gguf
+    from cubic_serve_b200.ops import eager
+    plain = eager.rope_inv_freq(16, 500000.0)
+    want = eager.rope_inv_freq(16, 500000.0, scaling=("llama3", 8.0, 1.0, 4.0, 64))
+    table = (plain / want).tolist()                               # what the converter stores: base frequency / scaled one
+    cfg = config_from_gguf(_metadata_only_file(tmp_path / "a.gguf", table=table))
+    assert cfg.rope_scaling[0] == "factors"
+    assert torch.allclose(eager.rope_inv_freq(16, 500000.0, scaling=cfg.rope_scaling), want, rtol=1e-6)
+    assert config_from_gguf(_metadata_only_file(tmp_path / "b.gguf")).rope_scaling is None
+    assert config_from_gguf(_metadata_only_file(tmp_path / "c.gguf", scaling=("LINEAR", 4.0, None))).rope_scaling == ("linear", 4.0)
+    y = config_from_gguf(_metadata_only_file(tmp_path / "d.gguf", arch="qwen3", scaling=("YARN", 4.0, 1024)))
+    assert y.rope_scaling[:5] == ("yarn", 4.0, 1024, 32.0, 1.0) and abs(y.rope_scaling[5] - (0.1 * math.log(4) + 1)) < 1e-12
+    assert y.attention_scale is not None
+    with pytest.raises(gq.GGUFFormatError, match="one divisor per rotary slot"):
+        config_from_gguf(_metadata_only_file(tmp_path / "e.gguf", table=[1.0] * 5))
+    with pytest.raises(gq.GGUFFormatError, match="both"):
+        config_from_gguf(_metadata_only_file(tmp_path / "f.gguf", scaling=("YARN", 4.0, 1024), table=table))
+    if hasattr(__import__("gguf").RopeScalingType, "LONGROPE"):
+        with pytest.raises(gq.GGUFFormatError, match="longrope"):
+            config_from_gguf(_metadata_only_file(tmp_path / "g.gguf", scaling=("LONGROPE", 4.0, 1024)))
