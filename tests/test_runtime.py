@@ -1,4 +1,6 @@
 """Page pool, prefix cache, scheduler and engine on CPU (eager executor / fake executor)."""
+from dataclasses import replace
+
 import numpy as np
 import pytest
 import torch
@@ -125,8 +127,9 @@ def test_preemption_when_pool_runs_dry():
     assert eng.pool.num_used == 0
 
 
-def test_engine_eager_executor_matches_reference_decoder():
-    cfg = toy_config()
+@pytest.mark.parametrize("scaling", [None, ("yarn", 4.0, 16, 32.0, 1.0, 1.25), ("llama3", 8.0, 1.0, 4.0, 16)])
+def test_engine_eager_executor_matches_reference_decoder(scaling):
+    cfg = replace(toy_config(), rope_scaling=scaling)
     w = random_dense_weights(cfg, seed=0)
     prompts = torch.randint(0, cfg.vocab_size, (3, 21), generator=torch.Generator().manual_seed(1))
     ref, _ = EagerDecoder(cfg, w).generate(prompts, 6)
